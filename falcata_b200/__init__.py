@@ -1,0 +1,22 @@
+"""falcata_b200 — a Blackwell-native gradient-boosted decision tree framework.
+
+Public surface (parity: python-package/falcata/__init__.py:L11-15, L81-84): ``Dataset``, ``Booster``,
+``train``, ``cv``, callbacks, sklearn-style estimators (``LGBM*`` / ``Falcata*`` names), model
+importers and plotting helpers.
+"""
+from .basic import Booster, Dataset, FalcataError, LightGBMError, cuda_available, register_logger
+from .callback import EarlyStopException, early_stopping, log_evaluation, record_evaluation, reset_parameter
+from .engine import CVBooster, cv, train
+
+__version__ = "0.1.0"
+
+__all__ = ["Dataset", "Booster", "CVBooster", "train", "cv", "FalcataError", "LightGBMError", "register_logger", "cuda_available",
+           "early_stopping", "log_evaluation", "record_evaluation", "reset_parameter", "EarlyStopException"]
+
+try:  # sklearn-style estimators are optional (scikit-learn may be absent)
+    from .sklearn import (FalcataClassifier, FalcataModel, FalcataRanker, FalcataRegressor, LGBMClassifier, LGBMModel, LGBMRanker,
+                          LGBMRegressor)
+
+    __all__ += ["LGBMModel", "LGBMClassifier", "LGBMRegressor", "LGBMRanker", "FalcataModel", "FalcataClassifier", "FalcataRegressor", "FalcataRanker"]
+except ImportError:  # pragma: no cover
+    pass

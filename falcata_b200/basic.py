@@ -1,0 +1,828 @@
+"""ctypes layer over the native core: ``Dataset`` and ``Booster``.
+
+Parity: python-package/falcata/basic.py (Dataset L1782, numpy ingest L2362, device-array ingest
+L2390-2447, Booster L3713, update L4268, save_model L4638, model_to_string L4895, predict
+L5165-5265, refit L5267). torch is used only for device tensors (ingest, custom gradients,
+device predict output) and for rank bootstrap; all training state lives in the C++/CUDA core.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+from pathlib import Path
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+
+from .libpath import load_lib
+
+_LIB = None
+
+
+def _lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = load_lib()
+        _LIB.FB_GetLastError.restype = ctypes.c_char_p
+        _register_default_logger()
+    return _LIB
+
+
+class FalcataError(Exception):
+    """Error raised by the native core."""
+
+
+LightGBMError = FalcataError
+
+
+def _safe_call(ret: int) -> None:
+    if ret != 0:
+        raise FalcataError(_lib().FB_GetLastError().decode("utf-8"))
+
+
+# ------------------------------------------------------------------ logging ----
+_LOGGER_FN: Optional[Callable[[str], None]] = None
+_LOG_CB = ctypes.CFUNCTYPE(None, ctypes.c_char_p)
+
+
+def _log_trampoline(msg: bytes) -> None:
+    text = msg.decode("utf-8", "replace").rstrip("\n")
+    if _LOGGER_FN is not None:
+        _LOGGER_FN(text)
+    else:
+        print(text, flush=True)
+
+
+_log_cb_holder = _LOG_CB(_log_trampoline)
+
+
+def _register_default_logger() -> None:
+    _LIB.FB_RegisterLogCallback(_log_cb_holder)
+
+
+def register_logger(logger: Any, info_method_name: str = "info", warning_method_name: str = "warning") -> None:
+    """Route native log lines to ``logger`` (a ``logging.Logger``-like object)."""
+    global _LOGGER_FN
+    info = getattr(logger, info_method_name)
+    warn = getattr(logger, warning_method_name)
+
+    def fn(text: str) -> None:
+        (warn if "[Warning]" in text else info)(text)
+
+    _LOGGER_FN = fn
+    _lib()
+
+
+# ------------------------------------------------------------------ helpers ----
+_DTYPE_CODE = {np.dtype("float32"): 0, np.dtype("float64"): 1, np.dtype("int8"): 2, np.dtype("int16"): 3,
+               np.dtype("uint8"): 4, np.dtype("uint16"): 5, np.dtype("float16"): 6, np.dtype("int32"): 7}
+
+_PARAM_ALIASES_NUM_ROUNDS = ("num_iterations", "num_iteration", "n_iter", "num_tree", "num_trees", "num_round", "num_rounds",
+                             "nrounds", "num_boost_round", "n_estimators", "max_iter")
+_EARLY_STOP_ALIASES = ("early_stopping_round", "early_stopping_rounds", "early_stopping", "n_iter_no_change")
+
+
+def _param_str(params: Optional[Dict[str, Any]]) -> bytes:
+    if not params:
+        return b""
+    parts = []
+    for k, v in params.items():
+        if v is None:
+            continue
+        if isinstance(v, (list, tuple, set)):
+            v = ",".join(str(x) for x in v)
+        elif isinstance(v, bool):
+            v = "true" if v else "false"
+        parts.append(f"{k}={v}")
+    return " ".join(parts).encode("utf-8")
+
+
+def _is_torch_tensor(x: Any) -> bool:
+    return type(x).__module__.startswith("torch") and hasattr(x, "data_ptr")
+
+
+def _is_cuda_array(x: Any) -> bool:
+    if _is_torch_tensor(x):
+        return x.is_cuda
+    return hasattr(x, "__cuda_array_interface__")
+
+
+def _to_numpy_2d(data: Any) -> np.ndarray:
+    if _is_torch_tensor(data):
+        data = data.detach().cpu().numpy()
+    if hasattr(data, "values") and not isinstance(data, np.ndarray):   # pandas
+        data = data.values
+    if hasattr(data, "toarray"):                                       # scipy sparse -> dense (device path is dense)
+        data = data.toarray()
+    arr = np.asarray(data)
+    if arr.ndim == 1:
+        arr = arr.reshape(-1, 1) if arr.dtype != object else np.stack(arr)
+    if arr.ndim != 2:
+        raise ValueError("Input data must be 2-dimensional")
+    if arr.dtype not in _DTYPE_CODE:
+        arr = arr.astype(np.float64 if arr.dtype == np.float64 else np.float32)
+    if not (arr.flags.c_contiguous or arr.flags.f_contiguous):
+        arr = np.ascontiguousarray(arr)
+    return arr
+
+
+def _get_string(fn: Callable, *args: Any) -> str:
+    out_len = ctypes.c_int64(0)
+    buf_len = 1 << 16
+    buf = ctypes.create_string_buffer(buf_len)
+    _safe_call(fn(*args, ctypes.c_int64(buf_len), ctypes.byref(out_len), buf))
+    if out_len.value > buf_len:
+        buf_len = out_len.value
+        buf = ctypes.create_string_buffer(buf_len)
+        _safe_call(fn(*args, ctypes.c_int64(buf_len), ctypes.byref(out_len), buf))
+    return buf.value.decode("utf-8")
+
+
+def _get_bytes(fn: Callable, *args: Any) -> bytes:
+    out_len = ctypes.c_int64(0)
+    _safe_call(fn(*args, ctypes.c_int64(0), ctypes.byref(out_len), None))
+    buf = ctypes.create_string_buffer(out_len.value)
+    _safe_call(fn(*args, ctypes.c_int64(out_len.value), ctypes.byref(out_len), buf))
+    return buf.raw[: out_len.value]
+
+
+def cuda_available() -> bool:
+    out = ctypes.c_int(0)
+    _safe_call(_lib().FB_CudaAvailable(ctypes.byref(out)))
+    return bool(out.value)
+
+
+# ------------------------------------------------------------------ Dataset ----
+class Dataset:
+    """Binned training / validation data.
+
+    ``data`` may be a numpy array, pandas frame, scipy sparse matrix (densified), a path to a
+    CSV/TSV/LibSVM/binary file, or a **CUDA tensor / ``__cuda_array_interface__`` object**: in that
+    case the rows are binned on the GPU and never leave it.
+    """
+
+    def __init__(self, data: Any, label: Any = None, reference: Optional["Dataset"] = None, weight: Any = None,
+                 group: Any = None, init_score: Any = None, feature_name: Union[str, List[str]] = "auto",
+                 categorical_feature: Union[str, List[int], List[str]] = "auto", params: Optional[Dict[str, Any]] = None,
+                 free_raw_data: bool = True, position: Any = None) -> None:
+        self.data = data
+        self.label = label
+        self.reference = reference
+        self.weight = weight
+        self.group = group
+        self.init_score = init_score
+        self.feature_name = feature_name
+        self.categorical_feature = categorical_feature
+        self.params = dict(params) if params else {}
+        self.free_raw_data = free_raw_data
+        self._handle: Optional[ctypes.c_void_p] = None
+        self.used_indices: Optional[np.ndarray] = None
+        self._predictor = None
+        self._keep: List[Any] = []   # arrays whose memory the native side points into
+        self._global_rows: Optional[Tuple[int, int]] = None   # (offset, total) when rows are one shard of many
+
+    # -- construction ---------------------------------------------------------------
+    def _merged_params(self) -> Dict[str, Any]:
+        p = dict(self.params)
+        cf = self.categorical_feature
+        if cf != "auto" and cf is not None and len(cf) > 0 and all(isinstance(c, (int, np.integer)) for c in cf):
+            p["categorical_feature"] = ",".join(str(int(c)) for c in cf)
+        return p
+
+    def construct(self) -> "Dataset":
+        if self._handle is not None:
+            return self
+        lib = _lib()
+        ref_handle = None
+        if self.reference is not None:
+            ref_handle = self.reference.construct()._handle
+        params = self._merged_params()
+        handle = ctypes.c_void_p()
+        if self.used_indices is not None and self.reference is not None and self.data is None:
+            idx = np.ascontiguousarray(self.used_indices, dtype=np.int32)
+            _safe_call(lib.FB_DatasetGetSubset(ref_handle, idx.ctypes.data_as(ctypes.c_void_p), ctypes.c_int32(len(idx)), ctypes.byref(handle)))
+            self._handle = handle
+        elif isinstance(self.data, (str, os.PathLike)):
+            _safe_call(lib.FB_DatasetCreateFromFile(str(self.data).encode(), _param_str(params), ref_handle, ctypes.byref(handle)))
+            self._handle = handle
+        elif _is_cuda_array(self.data):
+            self._construct_from_device(self.data, params, ref_handle)
+        else:
+            arr = _to_numpy_2d(self.data)
+            row_major = 1 if arr.flags.c_contiguous else 0
+            _safe_call(lib.FB_DatasetCreateFromMat(arr.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[arr.dtype], ctypes.c_int32(arr.shape[0]),
+                                                   ctypes.c_int32(arr.shape[1]), row_major, _param_str(params), ref_handle, ctypes.byref(handle)))
+            self._handle = handle
+            if hasattr(self.data, "columns") and self.feature_name == "auto":
+                self.feature_name = [str(c) for c in self.data.columns]
+        if self.feature_name != "auto" and self.feature_name is not None:
+            self.set_feature_name(self.feature_name)
+        if self.label is not None:
+            self.set_label(self.label)
+        if self.weight is not None:
+            self.set_weight(self.weight)
+        if self.group is not None:
+            self.set_group(self.group)
+        if self.init_score is not None:
+            self.set_init_score(self.init_score)
+        elif self._predictor is not None and self.data is not None:
+            init = self._predictor.predict(self.data, raw_score=True)
+            self.set_init_score(np.asarray(init, dtype=np.float64).T.reshape(-1))
+        if self.free_raw_data:
+            self.data = None
+        return self
+
+    def _construct_from_device(self, data: Any, params: Dict[str, Any], ref_handle: Any) -> None:
+        """Device ingest: sample rows on the GPU, find bins on the host from the sample, bin on the GPU."""
+        import torch
+
+        lib = _lib()
+        t = data if _is_torch_tensor(data) else torch.as_tensor(data, device="cuda")
+        if t.dim() != 2:
+            raise ValueError("Input data must be 2-dimensional")
+        if t.dtype == torch.float64 or t.dtype == torch.float32 or t.dtype == torch.float16:
+            pass
+        elif t.dtype in (torch.int8, torch.int16, torch.uint8, torch.int32):
+            pass
+        else:
+            t = t.float()
+        if not t.is_contiguous():
+            t = t.contiguous()
+        nrow, ncol = t.shape
+        handle = ctypes.c_void_p()
+        if ref_handle is not None:
+            _safe_call(lib.FB_DatasetCreateByReference(ref_handle, ctypes.byref(handle)))
+        else:
+            from .parallel import bootstrap
+
+            sample, total = bootstrap.gather_bin_sample(t, int(params.get("bin_construct_sample_cnt", 200000)), int(params.get("data_random_seed", 1)))
+            sample = np.ascontiguousarray(sample, dtype=np.float64)
+            _safe_call(lib.FB_DatasetCreateFromSample(sample.ctypes.data_as(ctypes.c_void_p), ctypes.c_int32(sample.shape[0]), ctypes.c_int32(ncol),
+                                                      ctypes.c_int64(total), _param_str(params), None, 0, ctypes.byref(handle)))
+        self._handle = handle
+        off, total = self._global_rows if self._global_rows is not None else (0, nrow)
+        keep_host = 1 if str(params.get("device_type", "")).lower() == "cpu" or params.get("keep_host_bins") else 0
+        _safe_call(lib.FB_DatasetInitRows(handle, ctypes.c_int32(nrow), ctypes.c_int64(off), ctypes.c_int64(total), 0))
+        code = {torch.float32: 0, torch.float64: 1, torch.int8: 2, torch.int16: 3, torch.uint8: 4, torch.float16: 6, torch.int32: 7}[t.dtype]
+        _safe_call(lib.FB_DatasetBinDeviceMat(handle, ctypes.c_void_p(t.data_ptr()), code, ctypes.c_int32(nrow), ctypes.c_int32(ncol), 1, keep_host))
+        torch.cuda.synchronize()
+
+    def set_global_rows(self, offset: int, total: int) -> "Dataset":
+        """Declare that this dataset holds rows [offset, offset + n) of a ``total``-row data set sharded over ranks."""
+        self._global_rows = (int(offset), int(total))
+        return self
+
+    @property
+    def handle(self) -> ctypes.c_void_p:
+        return self.construct()._handle
+
+    def create_valid(self, data: Any, label: Any = None, weight: Any = None, group: Any = None, init_score: Any = None,
+                     params: Optional[Dict[str, Any]] = None, position: Any = None) -> "Dataset":
+        ret = Dataset(data, label=label, reference=self, weight=weight, group=group, init_score=init_score, params=params or self.params,
+                      free_raw_data=self.free_raw_data)
+        ret._predictor = self._predictor
+        return ret
+
+    def subset(self, used_indices: Sequence[int], params: Optional[Dict[str, Any]] = None) -> "Dataset":
+        ret = Dataset(None, reference=self, params=params or self.params, free_raw_data=self.free_raw_data)
+        ret.used_indices = np.sort(np.asarray(used_indices, dtype=np.int32))
+        ret._predictor = self._predictor
+        return ret
+
+    # -- fields -----------------------------------------------------------------------
+    def _set_field(self, name: str, data: Any, dtype: Any) -> None:
+        lib = _lib()
+        if data is None:
+            _safe_call(lib.FB_DatasetSetField(self._handle, name.encode(), None, ctypes.c_int64(0), 0))
+            return
+        if _is_torch_tensor(data):
+            data = data.detach().cpu().numpy()
+        if hasattr(data, "values") and not isinstance(data, np.ndarray):
+            data = data.values
+        arr = np.ascontiguousarray(np.asarray(data).reshape(-1), dtype=dtype)
+        _safe_call(lib.FB_DatasetSetField(self._handle, name.encode(), arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(arr.size), _DTYPE_CODE[arr.dtype]))
+
+    def get_field(self, name: str) -> Optional[np.ndarray]:
+        lib = _lib()
+        n = ctypes.c_int64(0); ptr = ctypes.c_void_p(); typ = ctypes.c_int(0)
+        _safe_call(lib.FB_DatasetGetField(self.handle, name.encode(), ctypes.byref(n), ctypes.byref(ptr), ctypes.byref(typ)))
+        if n.value == 0 or not ptr.value:
+            return None
+        ct = {0: ctypes.c_float, 1: ctypes.c_double, 7: ctypes.c_int32}[typ.value]
+        return np.ctypeslib.as_array(ctypes.cast(ptr, ctypes.POINTER(ct)), shape=(n.value,)).copy()
+
+    def set_label(self, label: Any) -> "Dataset":
+        self.label = label
+        if self._handle is not None and label is not None:
+            self._set_field("label", label, np.float32)
+        return self
+
+    def set_weight(self, weight: Any) -> "Dataset":
+        self.weight = weight
+        if self._handle is not None:
+            self._set_field("weight", weight, np.float32)
+        return self
+
+    def set_group(self, group: Any) -> "Dataset":
+        self.group = group
+        if self._handle is not None and group is not None:
+            self._set_field("group", group, np.int32)
+        return self
+
+    def set_init_score(self, init_score: Any) -> "Dataset":
+        self.init_score = init_score
+        if self._handle is not None and init_score is not None:
+            arr = np.asarray(init_score.detach().cpu().numpy() if _is_torch_tensor(init_score) else init_score, dtype=np.float64)
+            if arr.ndim == 2:
+                arr = arr.T   # class-major
+            self._set_field("init_score", arr.reshape(-1), np.float64)
+        return self
+
+    def set_feature_name(self, feature_name: List[str]) -> "Dataset":
+        self.feature_name = feature_name
+        if self._handle is not None and feature_name != "auto" and feature_name is not None:
+            arr = (ctypes.c_char_p * len(feature_name))(*[str(s).encode() for s in feature_name])
+            _safe_call(_lib().FB_DatasetSetFeatureNames(self._handle, arr, len(feature_name)))
+        return self
+
+    def set_reference(self, reference: "Dataset") -> "Dataset":
+        self.reference = reference
+        return self
+
+    def get_label(self) -> Optional[np.ndarray]:
+        return self.get_field("label")
+
+    def get_weight(self) -> Optional[np.ndarray]:
+        return self.get_field("weight")
+
+    def get_init_score(self) -> Optional[np.ndarray]:
+        return self.get_field("init_score")
+
+    def get_group(self) -> Optional[np.ndarray]:
+        b = self.get_field("group")
+        return None if b is None else np.diff(b)
+
+    def get_feature_name(self) -> List[str]:
+        return _get_string(_lib().FB_DatasetGetFeatureNames, self.handle).split("\n")
+
+    def num_data(self) -> int:
+        out = ctypes.c_int32(0)
+        _safe_call(_lib().FB_DatasetGetNumData(self.handle, ctypes.byref(out)))
+        return out.value
+
+    def num_feature(self) -> int:
+        out = ctypes.c_int32(0)
+        _safe_call(_lib().FB_DatasetGetNumFeature(self.handle, ctypes.byref(out)))
+        return out.value
+
+    def info(self) -> Dict[str, int]:
+        out = (ctypes.c_int32 * 6)()
+        _safe_call(_lib().FB_DatasetGetInfo(self.handle, out))
+        keys = ["num_used_features", "num_groups", "num_total_bin", "max_group_bin", "has_device", "has_host"]
+        return dict(zip(keys, list(out)))
+
+    def binned_row(self, row: int) -> np.ndarray:
+        n = self.info()["num_used_features"]
+        out = (ctypes.c_int32 * n)()
+        _safe_call(_lib().FB_DatasetGetBinnedRow(self.handle, ctypes.c_int32(row), out))
+        return np.array(out[:], dtype=np.int32)
+
+    def save_binary(self, filename: Union[str, Path]) -> "Dataset":
+        _safe_call(_lib().FB_DatasetSaveBinary(self.handle, str(filename).encode()))
+        return self
+
+    def free_device_data(self) -> "Dataset":
+        if self._handle is not None:
+            _safe_call(_lib().FB_DatasetFreeDeviceData(self._handle))
+        return self
+
+    def _set_predictor(self, predictor: Any) -> "Dataset":
+        self._predictor = predictor
+        return self
+
+    def __del__(self) -> None:
+        try:
+            if self._handle is not None and _LIB is not None:
+                _LIB.FB_DatasetFree(self._handle)
+                self._handle = None
+        except Exception:
+            pass
+
+
+# ------------------------------------------------------------------ Booster ----
+class Booster:
+    """Gradient boosting model: train with :meth:`update`, evaluate, predict, save / load."""
+
+    def __init__(self, params: Optional[Dict[str, Any]] = None, train_set: Optional[Dataset] = None, model_file: Optional[Union[str, Path]] = None,
+                 model_str: Optional[Union[str, bytes]] = None) -> None:
+        lib = _lib()
+        self._handle = ctypes.c_void_p()
+        self.params = dict(params) if params else {}
+        self.train_set = train_set
+        self.valid_sets: List[Dataset] = []
+        self.name_valid_sets: List[str] = []
+        self.best_iteration = -1
+        self.best_score: Dict[str, Dict[str, float]] = {}
+        self._train_data_name = "training"
+        self._network = False
+        self.pandas_categorical = None
+        n_iter = ctypes.c_int(0)
+        if train_set is not None:
+            if not isinstance(train_set, Dataset):
+                raise TypeError(f"Training data should be Dataset instance, met {type(train_set).__name__}")
+            merged = dict(train_set.params); merged.update(self.params)
+            train_set.params = {**train_set.params, **{k: v for k, v in self.params.items() if k in _DATASET_PARAMS}}
+            train_set.construct()
+            _safe_call(lib.FB_BoosterCreate(train_set._handle, _param_str(self.params), ctypes.byref(self._handle)))
+        elif model_file is not None:
+            _safe_call(lib.FB_BoosterCreateFromModelfile(str(model_file).encode(), ctypes.byref(n_iter), ctypes.byref(self._handle)))
+        elif model_str is not None:
+            raw = model_str if isinstance(model_str, bytes) else model_str.encode("utf-8")
+            _safe_call(lib.FB_BoosterLoadModelFromString(raw, ctypes.c_int64(len(raw)), ctypes.byref(n_iter), ctypes.byref(self._handle)))
+        else:
+            raise TypeError("Need at least one training dataset or model file or model string to create Booster instance")
+        self._eval_names: Optional[List[str]] = None
+        self._eval_higher: Optional[List[bool]] = None
+
+    def __del__(self) -> None:
+        try:
+            if self._handle and _LIB is not None:
+                _LIB.FB_BoosterFree(self._handle)
+                self._handle = None
+        except Exception:
+            pass
+
+    # pickling goes through the text model
+    def __getstate__(self) -> Dict[str, Any]:
+        st = {k: v for k, v in self.__dict__.items() if k not in ("_handle", "train_set", "valid_sets")}
+        st["_model_str"] = self.model_to_string(num_iteration=-1)
+        return st
+
+    def __setstate__(self, state: Dict[str, Any]) -> None:
+        model_str = state.pop("_model_str")
+        self.__dict__.update(state)
+        self.train_set = None; self.valid_sets = []
+        self._handle = ctypes.c_void_p(); n_iter = ctypes.c_int(0)
+        raw = model_str.encode("utf-8")
+        _safe_call(_lib().FB_BoosterLoadModelFromString(raw, ctypes.c_int64(len(raw)), ctypes.byref(n_iter), ctypes.byref(self._handle)))
+
+    def __copy__(self) -> "Booster":
+        return self.__deepcopy__(None)
+
+    def __deepcopy__(self, _: Any) -> "Booster":
+        return Booster(model_str=self.model_to_string(num_iteration=-1))
+
+    # -- training ---------------------------------------------------------------------
+    def add_valid(self, data: Dataset, name: str) -> "Booster":
+        if data.reference is None and data is not self.train_set:
+            data.reference = self.train_set
+        data.construct()
+        _safe_call(_lib().FB_BoosterAddValidData(self._handle, data._handle))
+        self.valid_sets.append(data); self.name_valid_sets.append(name)
+        return self
+
+    def set_train_data_name(self, name: str) -> "Booster":
+        self._train_data_name = name
+        return self
+
+    def reset_parameter(self, params: Dict[str, Any]) -> "Booster":
+        _safe_call(_lib().FB_BoosterResetParameter(self._handle, _param_str(params)))
+        self.params.update(params)
+        return self
+
+    def update(self, train_set: Optional[Dataset] = None, fobj: Optional[Callable] = None) -> bool:
+        """One boosting iteration. Returns True when no further split is possible."""
+        lib = _lib()
+        fin = ctypes.c_int(0)
+        if fobj is None:
+            _safe_call(lib.FB_BoosterUpdateOneIter(self._handle, ctypes.byref(fin)))
+            return fin.value == 1
+        grad, hess = fobj(self._inner_predict_raw(0), self.train_set)
+        return self.__boost(grad, hess)
+
+    def __boost(self, grad: Any, hess: Any) -> bool:
+        lib = _lib()
+        fin = ctypes.c_int(0)
+        if _is_torch_tensor(grad) and grad.is_cuda:
+            import torch
+
+            g = grad.detach().to(torch.float32).contiguous().reshape(-1)
+            h = hess.detach().to(torch.float32).contiguous().reshape(-1)
+            _safe_call(lib.FB_BoosterUpdateOneIterCustom(self._handle, ctypes.c_void_p(g.data_ptr()), ctypes.c_void_p(h.data_ptr()), 1, ctypes.byref(fin)))
+            torch.cuda.synchronize()
+        else:
+            if _is_torch_tensor(grad):
+                grad = grad.detach().cpu().numpy(); hess = hess.detach().cpu().numpy()
+            g = np.asarray(grad, dtype=np.float32); h = np.asarray(hess, dtype=np.float32)
+            if g.ndim == 2:
+                g = g.T; h = h.T   # class-major
+            g = np.ascontiguousarray(g.reshape(-1)); h = np.ascontiguousarray(h.reshape(-1))
+            n_pred = self.__num_predict(0)
+            if g.size != n_pred or h.size != n_pred:
+                raise ValueError(f"Lengths of gradient ({g.size}) and Hessian ({h.size}) don't match training data length ({n_pred})")
+            if self._on_device():
+                import torch
+
+                gt = torch.from_numpy(g).cuda(); ht = torch.from_numpy(h).cuda()
+                _safe_call(lib.FB_BoosterUpdateOneIterCustom(self._handle, ctypes.c_void_p(gt.data_ptr()), ctypes.c_void_p(ht.data_ptr()), 1, ctypes.byref(fin)))
+                torch.cuda.synchronize()
+            else:
+                _safe_call(lib.FB_BoosterUpdateOneIterCustom(self._handle, g.ctypes.data_as(ctypes.c_void_p), h.ctypes.data_as(ctypes.c_void_p), 0, ctypes.byref(fin)))
+        return fin.value == 1
+
+    def _on_device(self) -> bool:
+        p = ctypes.c_void_p()
+        _safe_call(_lib().FB_BoosterGetTrainScoreDevicePtr(self._handle, ctypes.byref(p)))
+        return bool(p.value)
+
+    def train_score_tensor(self) -> Any:
+        """Raw training scores as a torch CUDA tensor view (class-major ``[k, n]``); CUDA boosters only."""
+        import torch
+
+        p = ctypes.c_void_p()
+        _safe_call(_lib().FB_BoosterGetTrainScoreDevicePtr(self._handle, ctypes.byref(p)))
+        if not p.value:
+            raise FalcataError("Booster is not device-resident")
+        n = self.train_set.num_data(); k = self.num_model_per_iteration()
+        from .utils.interop import tensor_from_ptr
+
+        return tensor_from_ptr(p.value, (k, n), torch.float32)
+
+    def rollback_one_iter(self) -> "Booster":
+        _safe_call(_lib().FB_BoosterRollbackOneIter(self._handle))
+        return self
+
+    def current_iteration(self) -> int:
+        out = ctypes.c_int(0)
+        _safe_call(_lib().FB_BoosterGetCurrentIteration(self._handle, ctypes.byref(out)))
+        return out.value
+
+    def num_model_per_iteration(self) -> int:
+        out = ctypes.c_int(0)
+        _safe_call(_lib().FB_BoosterNumModelPerIteration(self._handle, ctypes.byref(out)))
+        return out.value
+
+    def num_trees(self) -> int:
+        out = ctypes.c_int(0)
+        _safe_call(_lib().FB_BoosterNumberOfTotalModel(self._handle, ctypes.byref(out)))
+        return out.value
+
+    def num_feature(self) -> int:
+        out = ctypes.c_int(0)
+        _safe_call(_lib().FB_BoosterGetNumFeature(self._handle, ctypes.byref(out)))
+        return out.value
+
+    def feature_name(self) -> List[str]:
+        s = _get_string(_lib().FB_BoosterGetFeatureNames, self._handle)
+        return s.split("\n") if s else []
+
+    def upper_bound(self) -> float:
+        out = ctypes.c_double(0)
+        _safe_call(_lib().FB_BoosterGetUpperBoundValue(self._handle, ctypes.byref(out)))
+        return out.value
+
+    def lower_bound(self) -> float:
+        out = ctypes.c_double(0)
+        _safe_call(_lib().FB_BoosterGetLowerBoundValue(self._handle, ctypes.byref(out)))
+        return out.value
+
+    # -- evaluation -------------------------------------------------------------------
+    def __get_eval_info(self) -> None:
+        if self._eval_names is None:
+            s = _get_string(_lib().FB_BoosterGetEvalNames, self._handle)
+            items = [x for x in s.split("\n") if x]
+            self._eval_names = [x[1:] for x in items]
+            self._eval_higher = [x[0] == "+" for x in items]
+
+    def __num_predict(self, data_idx: int) -> int:
+        out = ctypes.c_int64(0)
+        _safe_call(_lib().FB_BoosterGetNumPredict(self._handle, data_idx, ctypes.byref(out)))
+        return out.value
+
+    def _inner_predict_raw(self, data_idx: int) -> Any:
+        """Raw scores of the training (0) or a validation set for custom objectives / metrics."""
+        if data_idx == 0 and self._on_device():
+            t = self.train_score_tensor()
+            return t[0] if t.shape[0] == 1 else t.t()
+        return self._inner_predict(data_idx, raw=True)
+
+    def _inner_predict(self, data_idx: int, raw: bool = False) -> np.ndarray:
+        n = self.__num_predict(data_idx)
+        out = np.empty(n, dtype=np.float64)
+        ln = ctypes.c_int64(0)
+        _safe_call(_lib().FB_BoosterGetPredict(self._handle, data_idx, ctypes.byref(ln), out.ctypes.data_as(ctypes.c_void_p)))
+        k = self.num_model_per_iteration()
+        return out if k == 1 else out.reshape(k, -1).T
+
+    def __inner_eval(self, data_name: str, data_idx: int, feval: Optional[Union[Callable, List[Callable]]] = None) -> List[Tuple[str, str, float, bool]]:
+        self.__get_eval_info()
+        ret: List[Tuple[str, str, float, bool]] = []
+        if self._eval_names:
+            res = (ctypes.c_double * len(self._eval_names))()
+            ln = ctypes.c_int(0)
+            _safe_call(_lib().FB_BoosterGetEval(self._handle, data_idx, ctypes.byref(ln), res))
+            for i in range(ln.value):
+                ret.append((data_name, self._eval_names[i], res[i], self._eval_higher[i]))
+        if feval is not None:
+            fevals = feval if isinstance(feval, (list, tuple)) else [feval]
+            ds = self.train_set if data_idx == 0 else self.valid_sets[data_idx - 1]
+            for f in fevals:
+                if f is None:
+                    continue
+                out = f(self._inner_predict(data_idx), ds)
+                outs = out if isinstance(out, list) else [out]
+                for name, val, hib in outs:
+                    ret.append((data_name, name, val, hib))
+        return ret
+
+    def eval_train(self, feval: Any = None) -> List[Tuple[str, str, float, bool]]:
+        return self.__inner_eval(self._train_data_name, 0, feval)
+
+    def eval_valid(self, feval: Any = None) -> List[Tuple[str, str, float, bool]]:
+        out: List[Tuple[str, str, float, bool]] = []
+        for i, name in enumerate(self.name_valid_sets):
+            out.extend(self.__inner_eval(name, i + 1, feval))
+        return out
+
+    def eval(self, data: Dataset, name: str, feval: Any = None) -> List[Tuple[str, str, float, bool]]:
+        if data is self.train_set:
+            return self.__inner_eval(name, 0, feval)
+        for i, v in enumerate(self.valid_sets):
+            if data is v:
+                return self.__inner_eval(name, i + 1, feval)
+        self.add_valid(data, name)
+        return self.__inner_eval(name, len(self.valid_sets), feval)
+
+    # -- prediction -------------------------------------------------------------------
+    def predict(self, data: Any, start_iteration: int = 0, num_iteration: Optional[int] = None, raw_score: bool = False, pred_leaf: bool = False,
+                pred_contrib: bool = False, data_has_header: bool = False, validate_features: bool = False, **kwargs: Any) -> Any:
+        """Predict for a numpy / pandas / scipy matrix (host traversal) or a CUDA tensor (device traversal kernel).
+
+        A CUDA tensor input returns a CUDA tensor; everything else returns numpy.
+        """
+        lib = _lib()
+        if isinstance(data, Dataset):
+            raise TypeError("Cannot use Dataset instance for prediction, please use raw data instead")
+        if num_iteration is None:
+            num_iteration = self.best_iteration if start_iteration <= 0 and self.best_iteration > 0 else -1
+        ptype = 1 if raw_score else 0
+        if pred_leaf:
+            ptype = 2
+        if pred_contrib:
+            ptype = 3
+        k = self.num_model_per_iteration()
+        if _is_cuda_array(data) and ptype in (0, 1) and cuda_available():
+            import torch
+
+            t = data if _is_torch_tensor(data) else torch.as_tensor(data, device="cuda")
+            if t.dtype not in (torch.float32, torch.float64, torch.float16):
+                t = t.float()
+            t = t.contiguous()
+            nrow, ncol = t.shape
+            out = torch.empty((k, nrow), dtype=torch.float32, device=t.device)
+            code = {torch.float32: 0, torch.float64: 1, torch.float16: 6}[t.dtype]
+            _safe_call(lib.FB_BoosterPredictForDeviceMat(self._handle, ctypes.c_void_p(t.data_ptr()), code, ctypes.c_int32(nrow), ctypes.c_int32(ncol), 1,
+                                                         ptype, start_iteration, num_iteration, ctypes.c_void_p(out.data_ptr())))
+            return out[0] if k == 1 else out.t().contiguous()
+        if isinstance(data, (str, os.PathLike)):
+            arr = np.loadtxt(str(data), delimiter="," if str(data).endswith(".csv") else None, skiprows=1 if data_has_header else 0, ndmin=2)[:, 1:]
+        else:
+            arr = _to_numpy_2d(data)
+        nrow, ncol = arr.shape
+        n_out = ctypes.c_int64(0)
+        _safe_call(lib.FB_BoosterCalcNumPredict(self._handle, nrow, ptype, start_iteration, num_iteration, ctypes.byref(n_out)))
+        out = np.empty(n_out.value, dtype=np.float64)
+        ln = ctypes.c_int64(0)
+        _safe_call(lib.FB_BoosterPredictForMat(self._handle, arr.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[arr.dtype], ctypes.c_int32(nrow), ctypes.c_int32(ncol),
+                                               1 if arr.flags.c_contiguous else 0, ptype, start_iteration, num_iteration, _param_str(kwargs),
+                                               ctypes.byref(ln), out.ctypes.data_as(ctypes.c_void_p)))
+        if pred_leaf:
+            return out.astype(np.int32).reshape(nrow, -1)
+        if out.size != nrow:
+            return out.reshape(nrow, -1)
+        return out
+
+    def refit(self, data: Any, label: Any, decay_rate: float = 0.9, **kwargs: Any) -> "Booster":
+        leaf_preds = self.predict(data, pred_leaf=True).astype(np.int32)
+        params = dict(self.params); params["refit_decay_rate"] = decay_rate; params["device_type"] = "cpu"
+        params.setdefault("objective", self._objective_from_model())
+        train = Dataset(data, label=label, params=params, **kwargs)
+        new = Booster(params, train)
+        new_handle = new._handle
+        # move the trees of this model into the new booster, then refit leaf values on the new data
+        _safe_call(_lib().FB_BoosterMerge(new_handle, self._handle))
+        lp = np.ascontiguousarray(leaf_preds)
+        _safe_call(_lib().FB_BoosterRefit(new_handle, lp.ctypes.data_as(ctypes.c_void_p), ctypes.c_int32(lp.shape[0]), ctypes.c_int32(lp.shape[1])))
+        return new
+
+    def _objective_from_model(self) -> str:
+        for line in self.model_to_string(num_iteration=1).split("\n"):
+            if line.startswith("objective="):
+                return line[len("objective="):].split(" ")[0]
+        return "regression"
+
+    # -- model IO ---------------------------------------------------------------------
+    def save_model(self, filename: Union[str, Path], num_iteration: Optional[int] = None, start_iteration: int = 0, importance_type: str = "split") -> "Booster":
+        if num_iteration is None:
+            num_iteration = self.best_iteration
+        _safe_call(_lib().FB_BoosterSaveModel(self._handle, start_iteration, num_iteration, 0 if importance_type == "split" else 1, str(filename).encode()))
+        return self
+
+    def model_to_string(self, num_iteration: Optional[int] = None, start_iteration: int = 0, importance_type: str = "split") -> str:
+        if num_iteration is None:
+            num_iteration = self.best_iteration
+        return _get_string(_lib().FB_BoosterSaveModelToString, self._handle, start_iteration, num_iteration, 0 if importance_type == "split" else 1)
+
+    def model_to_binary(self, num_iteration: Optional[int] = None, start_iteration: int = 0, f32_leaves: bool = False) -> bytes:
+        """Compressed sectioned binary model (``FALB``)."""
+        if num_iteration is None:
+            num_iteration = self.best_iteration
+        return _get_bytes(_lib().FB_BoosterSaveModelToBinary, self._handle, start_iteration, num_iteration, 1 if f32_leaves else 0)
+
+    @classmethod
+    def from_binary(cls, data: bytes) -> "Booster":
+        self = cls.__new__(cls)
+        self.params = {}; self.train_set = None; self.valid_sets = []; self.name_valid_sets = []; self.best_iteration = -1; self.best_score = {}
+        self._train_data_name = "training"; self._network = False; self.pandas_categorical = None; self._eval_names = None; self._eval_higher = None
+        self._handle = ctypes.c_void_p(); n_iter = ctypes.c_int(0)
+        _safe_call(_lib().FB_BoosterCreateFromBinary(data, ctypes.c_int64(len(data)), ctypes.byref(n_iter), ctypes.byref(self._handle)))
+        return self
+
+    def model_from_string(self, model_str: str) -> "Booster":
+        _lib().FB_BoosterFree(self._handle)
+        self._handle = ctypes.c_void_p(); n_iter = ctypes.c_int(0)
+        raw = model_str.encode("utf-8")
+        _safe_call(_lib().FB_BoosterLoadModelFromString(raw, ctypes.c_int64(len(raw)), ctypes.byref(n_iter), ctypes.byref(self._handle)))
+        return self
+
+    def dump_model(self, num_iteration: Optional[int] = None, start_iteration: int = 0, importance_type: str = "split") -> Dict[str, Any]:
+        if num_iteration is None:
+            num_iteration = self.best_iteration
+        s = _get_string(_lib().FB_BoosterDumpModel, self._handle, start_iteration, num_iteration, 0 if importance_type == "split" else 1)
+        return json.loads(s)
+
+    def model_to_if_else(self, num_iteration: int = -1) -> str:
+        return _get_string(_lib().FB_BoosterModelToIfElse, self._handle, num_iteration)
+
+    def feature_importance(self, importance_type: str = "split", iteration: Optional[int] = None) -> np.ndarray:
+        if iteration is None:
+            iteration = self.best_iteration
+        out = np.zeros(self.num_feature(), dtype=np.float64)
+        _safe_call(_lib().FB_BoosterFeatureImportance(self._handle, iteration, 0 if importance_type == "split" else 1, out.ctypes.data_as(ctypes.c_void_p)))
+        return out.astype(np.int32) if importance_type == "split" else out
+
+    def get_leaf_output(self, tree_id: int, leaf_id: int) -> float:
+        out = ctypes.c_double(0)
+        _safe_call(_lib().FB_BoosterGetLeafValue(self._handle, tree_id, leaf_id, ctypes.byref(out)))
+        return out.value
+
+    def set_leaf_output(self, tree_id: int, leaf_id: int, value: float) -> "Booster":
+        _safe_call(_lib().FB_BoosterSetLeafValue(self._handle, tree_id, leaf_id, ctypes.c_double(value)))
+        return self
+
+    def shuffle_models(self, start_iteration: int = 0, end_iteration: int = -1) -> "Booster":
+        _safe_call(_lib().FB_BoosterShuffleModels(self._handle, start_iteration, end_iteration))
+        return self
+
+    def trees_to_dataframe(self) -> Any:
+        import pandas as pd
+
+        model = self.dump_model()
+        rows: List[Dict[str, Any]] = []
+
+        def walk(tree_idx: int, node: Dict[str, Any], depth: int, parent: Optional[str]) -> None:
+            if "split_index" in node:
+                idx = f"{tree_idx}-S{node['split_index']}"
+                rows.append({"tree_index": tree_idx, "node_depth": depth, "node_index": idx, "parent_index": parent,
+                             "split_feature": model["feature_names"][node["split_feature"]], "split_gain": node["split_gain"],
+                             "threshold": node["threshold"], "decision_type": node["decision_type"], "missing_type": node["missing_type"],
+                             "value": node["internal_value"], "weight": node["internal_weight"], "count": node["internal_count"]})
+                walk(tree_idx, node["left_child"], depth + 1, idx); walk(tree_idx, node["right_child"], depth + 1, idx)
+            else:
+                idx = f"{tree_idx}-L{node.get('leaf_index', 0)}"
+                rows.append({"tree_index": tree_idx, "node_depth": depth, "node_index": idx, "parent_index": parent, "split_feature": None,
+                             "split_gain": None, "threshold": None, "decision_type": None, "missing_type": None, "value": node["leaf_value"],
+                             "weight": node.get("leaf_weight"), "count": node.get("leaf_count")})
+
+        for t in model["tree_info"]:
+            walk(t["tree_index"], t["tree_structure"], 1, None)
+        return pd.DataFrame(rows)
+
+    def gpu_launches(self) -> int:
+        """Number of kernels this booster's device engine has launched so far."""
+        out = ctypes.c_int64(0)
+        _safe_call(_lib().FB_BoosterGpuLaunches(self._handle, ctypes.byref(out)))
+        return out.value
+
+    def stage_report(self) -> str:
+        """Per-stage device time (CUDA events) accumulated by the device engine."""
+        return _get_string(_lib().FB_BoosterStageReport, self._handle)
+
+    def free_dataset(self) -> "Booster":
+        self.train_set = None; self.valid_sets = []
+        return self
+
+
+_DATASET_PARAMS = {"max_bin", "min_data_in_bin", "bin_construct_sample_cnt", "data_random_seed", "enable_bundle", "use_missing", "zero_as_missing",
+                   "feature_pre_filter", "categorical_feature", "max_bin_by_feature", "min_data_in_leaf", "device_type", "keep_host_bins"}

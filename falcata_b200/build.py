@@ -1,0 +1,91 @@
+"""In-tree build of the native core (``falcata_b200/lib/libfalcata_core.so``).
+
+Host sources are compiled with g++, device sources with nvcc for sm_100a only
+(``-gencode arch=compute_100a,code=sm_100a -lineinfo``); objects are cached by mtime under
+``csrc/build`` and compiled in parallel. The library links the CUDA runtime statically so it
+also loads on a machine without a GPU (the CPU learner and the model code work there).
+
+Run ``python -m falcata_b200.build`` (add ``--force`` to rebuild everything, ``--ptxas`` to
+print register / shared-memory usage of every kernel).
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+BUILD = CSRC / "build"
+LIB = ROOT / "lib" / "libfalcata_core.so"
+
+NVCC = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+CXX = os.environ.get("CXX") or shutil.which("g++") or "g++"
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON = ["-std=c++17", "-O3", f"-I{CSRC / 'include'}"]
+HOST_FLAGS = ["-fPIC", "-fopenmp", "-ffp-contract=off", "-Wall", "-Wno-sign-compare", "-Wno-unused-function"]
+
+
+def _sources():
+    cpp = sorted(CSRC.glob("core/*.cpp")) + sorted(CSRC.glob("cuda/*.cpp"))
+    cu = sorted(CSRC.glob("cuda/*.cu"))
+    return cpp, cu
+
+
+def _newest_header() -> float:
+    return max((p.stat().st_mtime for p in list(CSRC.glob("include/fb/*.h")) + list(CSRC.glob("cuda/*.cuh")) + list(CSRC.glob("cuda/*.h"))), default=0.0)
+
+
+def _compile(src: Path, obj: Path, ptxas: bool) -> str:
+    if src.suffix == ".cu":
+        cmd = [NVCC, *ARCH, "-lineinfo", *COMMON, "--expt-relaxed-constexpr", "-Xcompiler", ",".join(HOST_FLAGS),
+               "-Xcudafe", "--diag_suppress=177", "-c", str(src), "-o", str(obj)]
+        if ptxas:
+            cmd[1:1] = ["-Xptxas", "-v"]
+    else:
+        cmd = [CXX, *COMMON, *HOST_FLAGS, "-I/usr/local/cuda/include", "-c", str(src), "-o", str(obj)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"compile failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    return r.stderr if ptxas else ""
+
+
+def build(force: bool = False, ptxas: bool = False, verbose: bool = False) -> Path:
+    BUILD.mkdir(parents=True, exist_ok=True)
+    LIB.parent.mkdir(parents=True, exist_ok=True)
+    cpp, cu = _sources()
+    hdr_time = _newest_header()
+    jobs = []
+    objs = []
+    for src in cpp + cu:
+        obj = BUILD / (src.parent.name + "_" + src.stem + ".o")
+        objs.append(obj)
+        stale = force or ptxas or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_time)
+        if stale:
+            jobs.append((src, obj))
+    logs = []
+    if jobs:
+        with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
+            futs = {ex.submit(_compile, s, o, ptxas and s.suffix == ".cu"): s for s, o in jobs}
+            for fut in cf.as_completed(futs):
+                out = fut.result()
+                if verbose:
+                    print(f"compiled {futs[fut].name}", file=sys.stderr)
+                if out:
+                    logs.append(f"==== {futs[fut].name}\n{out}")
+    if jobs or not LIB.exists():
+        cmd = [NVCC, *ARCH, "-shared", "-Xcompiler", "-fPIC,-fopenmp", "-o", str(LIB), *map(str, objs), "-lz", "-lgomp"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    if ptxas:
+        print("\n".join(logs))
+    return LIB
+
+
+if __name__ == "__main__":
+    p = build(force="--force" in sys.argv, ptxas="--ptxas" in sys.argv, verbose=True)
+    print(p)

@@ -1,0 +1,158 @@
+"""Training callbacks: early stopping, evaluation logging / recording, parameter schedules.
+Parity: python-package/falcata/callback.py (early_stopping, log_evaluation, record_evaluation,
+reset_parameter and the CallbackEnv / EarlyStopException protocol)."""
+from __future__ import annotations
+
+from collections import OrderedDict
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional, Tuple, Union
+
+__all__ = ["EarlyStopException", "early_stopping", "log_evaluation", "record_evaluation", "reset_parameter", "CallbackEnv"]
+
+
+class EarlyStopException(Exception):
+    def __init__(self, best_iteration: int, best_score: List[Tuple[str, str, float, bool]]) -> None:
+        super().__init__()
+        self.best_iteration = best_iteration
+        self.best_score = best_score
+
+
+@dataclass
+class CallbackEnv:
+    model: Any
+    params: Dict[str, Any]
+    iteration: int
+    begin_iteration: int
+    end_iteration: int
+    evaluation_result_list: Optional[List[Tuple]]
+
+
+def _format_eval_result(value: Tuple, show_stdv: bool = True) -> str:
+    if len(value) == 4:
+        return f"{value[0]}'s {value[1]}: {value[2]:g}"
+    if len(value) == 5:
+        return f"{value[0]}'s {value[1]}: {value[2]:g} + {value[4]:g}" if show_stdv else f"{value[0]}'s {value[1]}: {value[2]:g}"
+    raise ValueError("Wrong metric value")
+
+
+def log_evaluation(period: int = 1, show_stdv: bool = True) -> Callable:
+    def _callback(env: CallbackEnv) -> None:
+        if period > 0 and env.evaluation_result_list and (env.iteration + 1) % period == 0:
+            result = "\t".join(_format_eval_result(x, show_stdv) for x in env.evaluation_result_list)
+            print(f"[{env.iteration + 1}]\t{result}", flush=True)
+
+    _callback.order = 10  # type: ignore[attr-defined]
+    return _callback
+
+
+def record_evaluation(eval_result: Dict[str, Dict[str, List[Any]]]) -> Callable:
+    if not isinstance(eval_result, dict):
+        raise TypeError("eval_result should be a dictionary")
+
+    def _init(env: CallbackEnv) -> None:
+        eval_result.clear()
+        for item in env.evaluation_result_list or []:
+            data_name, eval_name = item[0], item[1]
+            eval_result.setdefault(data_name, OrderedDict())
+            if len(item) == 4:
+                eval_result[data_name].setdefault(eval_name, [])
+            else:
+                eval_result[data_name].setdefault(f"{eval_name}-mean", [])
+                eval_result[data_name].setdefault(f"{eval_name}-stdv", [])
+
+    def _callback(env: CallbackEnv) -> None:
+        if env.iteration == env.begin_iteration:
+            _init(env)
+        for item in env.evaluation_result_list or []:
+            if len(item) == 4:
+                eval_result[item[0]][item[1]].append(item[2])
+            else:
+                eval_result[item[0]][f"{item[1]}-mean"].append(item[2])
+                eval_result[item[0]][f"{item[1]}-stdv"].append(item[4])
+
+    _callback.order = 20  # type: ignore[attr-defined]
+    return _callback
+
+
+def reset_parameter(**kwargs: Union[list, Callable]) -> Callable:
+    def _callback(env: CallbackEnv) -> None:
+        new_parameters = {}
+        for key, value in kwargs.items():
+            if isinstance(value, list):
+                if len(value) != env.end_iteration - env.begin_iteration:
+                    raise ValueError(f"Length of list {key!r} has to equal to 'num_boost_round'.")
+                new_param = value[env.iteration - env.begin_iteration]
+            elif callable(value):
+                new_param = value(env.iteration - env.begin_iteration)
+            else:
+                raise ValueError("Only list and callable values are supported as a mapping from boosting round index to new parameter value.")
+            if new_param != env.params.get(key, None):
+                new_parameters[key] = new_param
+        if new_parameters:
+            if hasattr(env.model, "reset_parameter"):
+                env.model.reset_parameter(new_parameters)
+            env.params.update(new_parameters)
+
+    _callback.before_iteration = True  # type: ignore[attr-defined]
+    _callback.order = 10  # type: ignore[attr-defined]
+    return _callback
+
+
+def early_stopping(stopping_rounds: int, first_metric_only: bool = False, verbose: bool = True, min_delta: Union[float, List[float]] = 0.0) -> Callable:
+    if not isinstance(stopping_rounds, int) or stopping_rounds <= 0:
+        raise ValueError(f"stopping_rounds should be an integer and greater than 0. got: {stopping_rounds}")
+    state: Dict[str, Any] = {"enabled": True, "best_score": [], "best_iter": [], "best_list": [], "cmp": [], "first_metric": ""}
+
+    def _init(env: CallbackEnv) -> None:
+        state["enabled"] = bool(env.evaluation_result_list)
+        if not state["enabled"]:
+            raise ValueError("For early stopping, at least one dataset and eval metric is required for evaluation")
+        only_train = all(item[0] in ("training", getattr(env.model, "_train_data_name", "training")) for item in env.evaluation_result_list)
+        if only_train and not hasattr(env.model, "cvfolds"):
+            state["enabled"] = False
+            return
+        if verbose:
+            print(f"Training until validation scores don't improve for {stopping_rounds} rounds", flush=True)
+        n = len(env.evaluation_result_list)
+        deltas = min_delta if isinstance(min_delta, list) else [min_delta] * n
+        if len(deltas) < n:
+            deltas = (deltas * n)[:n]
+        state["best_score"] = []; state["best_iter"] = []; state["best_list"] = []; state["cmp"] = []
+        state["first_metric"] = env.evaluation_result_list[0][1].split(" ")[-1]
+        for item, d in zip(env.evaluation_result_list, deltas):
+            state["best_iter"].append(0); state["best_list"].append(None)
+            if item[3]:
+                state["best_score"].append(float("-inf")); state["cmp"].append(lambda a, b, d=d: a > b + d)
+            else:
+                state["best_score"].append(float("inf")); state["cmp"].append(lambda a, b, d=d: a < b - d)
+
+    def _final_check(env: CallbackEnv, i: int) -> None:
+        if env.iteration == env.end_iteration - 1:
+            if verbose:
+                best = "\t".join(_format_eval_result(x) for x in state["best_list"][i])
+                print(f"Did not meet early stopping. Best iteration is:\n[{state['best_iter'][i] + 1}]\t{best}", flush=True)
+            raise EarlyStopException(state["best_iter"][i], state["best_list"][i])
+
+    def _callback(env: CallbackEnv) -> None:
+        if env.iteration == env.begin_iteration:
+            _init(env)
+        if not state["enabled"]:
+            return
+        for i, item in enumerate(env.evaluation_result_list):
+            score = item[2]
+            if state["best_list"][i] is None or state["cmp"][i](score, state["best_score"][i]):
+                state["best_score"][i] = score; state["best_iter"][i] = env.iteration; state["best_list"][i] = env.evaluation_result_list
+            metric_name = item[1].split(" ")[-1]
+            if first_metric_only and state["first_metric"] != metric_name:
+                continue
+            if item[0] in ("training", getattr(env.model, "_train_data_name", "training")) and not hasattr(env.model, "cvfolds"):
+                continue
+            if env.iteration - state["best_iter"][i] >= stopping_rounds:
+                if verbose:
+                    best = "\t".join(_format_eval_result(x) for x in state["best_list"][i])
+                    print(f"Early stopping, best iteration is:\n[{state['best_iter'][i] + 1}]\t{best}", flush=True)
+                raise EarlyStopException(state["best_iter"][i], state["best_list"][i])
+            _final_check(env, i)
+
+    _callback.order = 30  # type: ignore[attr-defined]
+    return _callback

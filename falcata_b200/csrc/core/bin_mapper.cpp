@@ -1,0 +1,260 @@
+// Bin boundary search for one feature from a value sample.
+// Parity (semantics, not code): src/io/bin.cpp:L81-160 (greedy equal-frequency search with
+// big-count values), L247-303 (zero gets its own bin), L316-511 (FindBin: missing type,
+// distinct values, categorical by frequency, trivial-feature filter, default/most-freq bin).
+#include "fb/bin.h"
+
+#include <numeric>
+
+namespace fb {
+
+namespace {
+
+// Smallest double strictly above the midpoint is not needed: values <= bound go left, and the
+// bound is the midpoint of two distinct sampled values, nudged up when rounding collapsed it.
+inline double UpperBoundBetween(double lo, double hi) {
+  double mid = (lo + hi) / 2.0;
+  if (!(mid >= lo) || mid >= hi) mid = lo;   // adjacent doubles: keep lo as the inclusive bound
+  return mid;
+}
+
+// Boundaries over one sign side. `vals`/`cnts` are ascending distinct values with their counts.
+std::vector<double> GreedyBounds(const double* vals, const int* cnts, int n, int max_bin, size_t total, int min_data_in_bin) {
+  std::vector<double> bounds;
+  if (max_bin <= 0 || n == 0) return bounds;
+  if (n <= max_bin) {
+    int acc = 0;
+    for (int i = 0; i < n - 1; ++i) {
+      acc += cnts[i];
+      if (acc >= min_data_in_bin) { bounds.push_back(UpperBoundBetween(vals[i], vals[i + 1])); acc = 0; }
+    }
+    bounds.push_back(std::numeric_limits<double>::infinity());
+    return bounds;
+  }
+  if (min_data_in_bin > 0) max_bin = std::max(1, std::min(max_bin, static_cast<int>(total / min_data_in_bin)));
+  double mean_size = static_cast<double>(total) / max_bin;
+  std::vector<char> big(n, 0);
+  int rest_bins = max_bin; size_t rest_cnt = total;
+  for (int i = 0; i < n; ++i) if (cnts[i] >= mean_size) { big[i] = 1; --rest_bins; rest_cnt -= cnts[i]; }
+  mean_size = rest_bins > 0 ? static_cast<double>(rest_cnt) / rest_bins : std::numeric_limits<double>::infinity();
+  std::vector<double> hi_of_bin, lo_of_next;
+  int acc = 0, bins_made = 0;
+  for (int i = 0; i < n - 1; ++i) {
+    if (!big[i]) rest_cnt -= cnts[i];
+    acc += cnts[i];
+    bool close = big[i] || acc >= mean_size || (big[i + 1] && acc >= std::max(1.0, mean_size * 0.5));
+    if (close) {
+      hi_of_bin.push_back(vals[i]); lo_of_next.push_back(vals[i + 1]);
+      ++bins_made; acc = 0;
+      if (bins_made >= max_bin - 1) break;
+      if (!big[i]) { --rest_bins; mean_size = rest_bins > 0 ? static_cast<double>(rest_cnt) / rest_bins : std::numeric_limits<double>::infinity(); }
+    }
+  }
+  for (size_t i = 0; i < hi_of_bin.size(); ++i) {
+    double b = UpperBoundBetween(hi_of_bin[i], lo_of_next[i]);
+    if (bounds.empty() || b > bounds.back()) bounds.push_back(b);
+  }
+  bounds.push_back(std::numeric_limits<double>::infinity());
+  return bounds;
+}
+
+// Zero keeps a bin of its own, (-kZeroThreshold, kZeroThreshold]; negatives and positives get
+// bin budgets proportional to their sample counts.
+std::vector<double> BoundsZeroOwnBin(const std::vector<double>& vals, const std::vector<int>& cnts, int max_bin,
+                                     size_t total, int min_data_in_bin) {
+  const int n = static_cast<int>(vals.size());
+  int n_neg = 0; size_t cnt_neg = 0, cnt_pos = 0, cnt_zero = 0;
+  int first_pos = n;
+  for (int i = 0; i < n; ++i) {
+    if (vals[i] <= -kZeroThreshold) { ++n_neg; cnt_neg += cnts[i]; }
+    else if (vals[i] > kZeroThreshold) { if (first_pos == n) first_pos = i; cnt_pos += cnts[i]; }
+    else cnt_zero += cnts[i];
+  }
+  const int n_pos = n - first_pos;
+  std::vector<double> bounds;
+  int budget = max_bin - 1;  // one bin is the zero bin
+  int neg_bins = 0;
+  if (n_neg > 0) {
+    double share = static_cast<double>(cnt_neg) / std::max<size_t>(1, cnt_neg + cnt_pos);
+    neg_bins = std::max(1, static_cast<int>(share * budget));
+    if (n_pos > 0) neg_bins = std::min(neg_bins, budget - 1);
+    neg_bins = std::max(1, neg_bins);
+    auto nb = GreedyBounds(vals.data(), cnts.data(), n_neg, neg_bins, cnt_neg, min_data_in_bin);
+    if (!nb.empty()) nb.back() = -kZeroThreshold;   // the last negative bin ends just below zero
+    bounds = nb;
+  }
+  int pos_bins = budget - static_cast<int>(bounds.size());
+  if (n_pos > 0 && pos_bins > 0) {
+    bounds.push_back(kZeroThreshold);               // zero bin
+    auto pb = GreedyBounds(vals.data() + first_pos, cnts.data() + first_pos, n_pos, pos_bins, cnt_pos, min_data_in_bin);
+    bounds.insert(bounds.end(), pb.begin(), pb.end());
+  } else {
+    bounds.push_back(std::numeric_limits<double>::infinity());  // zero (and any positives) share the last bin
+  }
+  (void)cnt_zero;
+  return bounds;
+}
+
+inline bool NearlyEqualOrdered(double a, double b) {
+  // a <= b assumed; equal or adjacent representable doubles are merged.
+  return b <= std::nextafter(a, std::numeric_limits<double>::infinity());
+}
+
+}  // namespace
+
+void BinMapper::FindBin(double* values, int num_values, size_t total_sample_cnt, int max_bin, int min_data_in_bin,
+                        int min_split_data, bool pre_filter, BinType type, bool use_missing, bool zero_as_missing,
+                        const std::vector<double>& forced_upper_bounds) {
+  bin_type = type;
+  default_bin = 0;
+  // NaNs are moved out first.
+  int na_cnt = 0, m = 0;
+  for (int i = 0; i < num_values; ++i) { if (std::isnan(values[i])) ++na_cnt; else values[m++] = values[i]; }
+  num_values = m;
+  if (!use_missing) missing_type = MissingType::None;
+  else if (zero_as_missing) missing_type = MissingType::Zero;
+  else missing_type = na_cnt > 0 ? MissingType::NaN : MissingType::None;
+  const size_t zero_cnt = total_sample_cnt - static_cast<size_t>(num_values) - static_cast<size_t>(na_cnt);
+
+  std::stable_sort(values, values + num_values);
+  std::vector<double> dv; std::vector<int> dc;
+  bool zero_pushed = false;
+  auto push_zero = [&] {
+    if (!zero_pushed && zero_cnt > 0) {
+      if (!dv.empty() && dv.back() == 0.0) dc.back() += static_cast<int>(zero_cnt);
+      else { dv.push_back(0.0); dc.push_back(static_cast<int>(zero_cnt)); }
+    }
+    zero_pushed = true;
+  };
+  if (num_values == 0 || values[0] > 0.0) push_zero();
+  for (int i = 0; i < num_values; ++i) {
+    if (!zero_pushed && values[i] > 0.0) push_zero();
+    if (!dv.empty() && dv.back() != 0.0 && NearlyEqualOrdered(dv.back(), values[i])) { dv.back() = values[i]; ++dc.back(); }
+    else if (!dv.empty() && dv.back() == values[i]) { ++dc.back(); }
+    else { dv.push_back(values[i]); dc.push_back(1); }
+  }
+  if (!zero_pushed) push_zero();
+  if (dv.empty()) { dv.push_back(0.0); dc.push_back(static_cast<int>(total_sample_cnt)); }
+  min_val = dv.front(); max_val = dv.back();
+  const int nd = static_cast<int>(dv.size());
+  std::vector<int> cnt_in_bin;
+
+  if (type == BinType::Numerical) {
+    std::vector<double> ub;
+    if (!forced_upper_bounds.empty()) {
+      ub = forced_upper_bounds;
+      std::sort(ub.begin(), ub.end());
+      ub.push_back(std::numeric_limits<double>::infinity());
+      if (static_cast<int>(ub.size()) > max_bin - (missing_type == MissingType::NaN ? 1 : 0)) ub.resize(max_bin - (missing_type == MissingType::NaN ? 1 : 0)), ub.back() = std::numeric_limits<double>::infinity();
+    } else if (missing_type == MissingType::Zero) {
+      ub = BoundsZeroOwnBin(dv, dc, max_bin, total_sample_cnt - na_cnt, min_data_in_bin);
+      if (ub.size() == 2) missing_type = MissingType::None;
+    } else if (missing_type == MissingType::None) {
+      ub = BoundsZeroOwnBin(dv, dc, max_bin, total_sample_cnt - na_cnt, min_data_in_bin);
+    } else {
+      ub = BoundsZeroOwnBin(dv, dc, max_bin - 1, total_sample_cnt - na_cnt, min_data_in_bin);
+      ub.push_back(std::numeric_limits<double>::quiet_NaN());
+    }
+    bin_upper_bound = ub;
+    num_bin = static_cast<int>(ub.size());
+    cnt_in_bin.assign(num_bin, 0);
+    int b = 0;
+    for (int i = 0; i < nd; ++i) {
+      while (b < num_bin - 1 && !(dv[i] <= bin_upper_bound[b])) ++b;
+      cnt_in_bin[b] += dc[i];
+    }
+    if (missing_type == MissingType::NaN) cnt_in_bin[num_bin - 1] = na_cnt;
+    FB_CHECK(num_bin <= max_bin);
+  } else {
+    // categorical: by count, keep until 99% of the non-NaN mass or max_bin; bin 0 = NaN/other/negative
+    std::vector<int> ci; std::vector<int> cc;
+    int neg_or_na = na_cnt;
+    for (int i = 0; i < nd; ++i) {
+      int v = static_cast<int>(dv[i]);
+      if (v < 0) { neg_or_na += dc[i]; continue; }
+      if (!ci.empty() && ci.back() == v) cc.back() += dc[i]; else { ci.push_back(v); cc.push_back(dc[i]); }
+    }
+    std::vector<int> order(ci.size());
+    std::iota(order.begin(), order.end(), 0);
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return cc[a] > cc[b]; });
+    size_t mass = 0; for (int c : cc) mass += c;
+    const size_t cut = static_cast<size_t>(0.99 * static_cast<double>(mass));
+    bin_2_categorical.clear(); categorical_2_bin.clear();
+    bin_2_categorical.push_back(-1); cnt_in_bin.push_back(0);
+    size_t used = 0;
+    int cap = std::min(max_bin, static_cast<int>(ci.size()) + 1);
+    for (size_t k = 0; k < order.size(); ++k) {
+      if (static_cast<int>(bin_2_categorical.size()) >= cap) break;
+      if (used >= cut && k > 0) break;
+      int idx = order[k];
+      categorical_2_bin[ci[idx]] = static_cast<int>(bin_2_categorical.size());
+      bin_2_categorical.push_back(ci[idx]);
+      cnt_in_bin.push_back(cc[idx]);
+      used += cc[idx];
+    }
+    num_bin = static_cast<int>(bin_2_categorical.size());
+    cnt_in_bin[0] = static_cast<int>(total_sample_cnt - used);
+    missing_type = (cnt_in_bin[0] > 0 && use_missing) ? MissingType::NaN : MissingType::None;
+    (void)neg_or_na;
+  }
+
+  is_trivial = num_bin <= 1;
+  if (!is_trivial && pre_filter && min_split_data > 0) {
+    // No threshold can leave >= min_split_data on both sides -> unusable feature.
+    bool usable = false; int left = 0; int total = 0;
+    for (int c : cnt_in_bin) total += c;
+    if (type == BinType::Numerical) {
+      for (int i = 0; i < num_bin - 1; ++i) { left += cnt_in_bin[i]; if (left >= min_split_data && total - left >= min_split_data) { usable = true; break; } }
+    } else {
+      for (int i = 0; i < num_bin; ++i) { if (cnt_in_bin[i] >= min_split_data && total - cnt_in_bin[i] >= min_split_data) { usable = true; break; } }
+    }
+    if (!usable) is_trivial = true;
+  }
+  if (!is_trivial) {
+    default_bin = ValueToBin(0.0);
+    most_freq_bin = static_cast<int>(std::max_element(cnt_in_bin.begin(), cnt_in_bin.end()) - cnt_in_bin.begin());
+    double top_share = static_cast<double>(cnt_in_bin[most_freq_bin]) / std::max<size_t>(1, total_sample_cnt);
+    if (most_freq_bin != default_bin && top_share < kSparseThreshold) most_freq_bin = default_bin;
+    sparse_rate = static_cast<double>(cnt_in_bin[most_freq_bin]) / std::max<size_t>(1, total_sample_cnt);
+  } else {
+    sparse_rate = 1.0; most_freq_bin = 0;
+  }
+}
+
+std::string BinMapper::InfoString() const {
+  if (bin_type == BinType::Categorical) {
+    std::string s;
+    for (size_t i = 1; i < bin_2_categorical.size(); ++i) { if (i > 1) s += ":"; s += std::to_string(bin_2_categorical[i]); }
+    if (s.empty()) s = "none";
+    return s;
+  }
+  return "[" + DoubleToStr17(min_val) + ":" + DoubleToStr17(max_val) + "]";
+}
+
+void BinMapper::Serialize(std::vector<char>* out) const {
+  auto put = [&](const void* p, size_t n) { const char* c = static_cast<const char*>(p); out->insert(out->end(), c, c + n); };
+  int32_t hdr[6] = {num_bin, static_cast<int>(missing_type), static_cast<int>(bin_type), is_trivial ? 1 : 0, default_bin, most_freq_bin};
+  put(hdr, sizeof(hdr));
+  double d[3] = {sparse_rate, min_val, max_val};
+  put(d, sizeof(d));
+  int32_t nu = static_cast<int32_t>(bin_upper_bound.size()), nc = static_cast<int32_t>(bin_2_categorical.size());
+  put(&nu, 4); put(&nc, 4);
+  put(bin_upper_bound.data(), nu * sizeof(double));
+  put(bin_2_categorical.data(), nc * sizeof(int));
+}
+
+const char* BinMapper::Deserialize(const char* p) {
+  int32_t hdr[6]; memcpy(hdr, p, sizeof(hdr)); p += sizeof(hdr);
+  num_bin = hdr[0]; missing_type = static_cast<MissingType>(hdr[1]); bin_type = static_cast<BinType>(hdr[2]);
+  is_trivial = hdr[3] != 0; default_bin = hdr[4]; most_freq_bin = hdr[5];
+  double d[3]; memcpy(d, p, sizeof(d)); p += sizeof(d);
+  sparse_rate = d[0]; min_val = d[1]; max_val = d[2];
+  int32_t nu, nc; memcpy(&nu, p, 4); p += 4; memcpy(&nc, p, 4); p += 4;
+  bin_upper_bound.resize(nu); memcpy(bin_upper_bound.data(), p, nu * sizeof(double)); p += nu * sizeof(double);
+  bin_2_categorical.resize(nc); memcpy(bin_2_categorical.data(), p, nc * sizeof(int)); p += nc * sizeof(int);
+  categorical_2_bin.clear();
+  for (int i = 1; i < nc; ++i) categorical_2_bin[bin_2_categorical[i]] = i;
+  return p;
+}
+
+}  // namespace fb

@@ -1,0 +1,393 @@
+// C API implementation. Parity: src/c_api.cpp (Booster wrapper L179-480, API functions L1021-3238).
+#include "fb/c_api.h"
+
+#include <fstream>
+#include <memory>
+#include <mutex>
+
+#include "fb/gbdt.h"
+
+namespace fb {
+// device-side entry points implemented by the CUDA module
+void DeviceBinDataset(Dataset* ds, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, bool keep_host_copy);
+void DevicePredict(const GBDT* gbdt, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, int predict_type,
+                   int start_iter, int num_iter, float* out_device);
+}  // namespace fb
+
+using namespace fb;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+struct BoosterWrap {
+  Config config;
+  std::unique_ptr<ObjectiveFunction> objective;
+  std::unique_ptr<GBDT> gbdt;
+  const Dataset* train = nullptr;
+  std::mutex mu;
+};
+
+int CopyOut(const std::string& s, int64_t buffer_len, int64_t* out_len, char* out) {
+  *out_len = static_cast<int64_t>(s.size()) + 1;
+  if (buffer_len >= *out_len && out != nullptr) memcpy(out, s.c_str(), s.size() + 1);
+  return 0;
+}
+
+std::vector<int> ParseCategorical(const Config& cfg, int ncol) {
+  std::vector<int> out;
+  for (auto& t : SplitAny(cfg.categorical_feature, ",")) {
+    std::string s = Trim(t);
+    if (s.empty() || StartsWith(s, "name:")) continue;
+    int v = atoi(s.c_str()); if (v >= 0 && v < ncol) out.push_back(v);
+  }
+  return out;
+}
+
+}  // namespace
+
+#define API_BEGIN() try {
+#define API_END() } catch (std::exception& ex) { g_last_error = ex.what(); return -1; } catch (...) { g_last_error = "unknown exception"; return -1; } return 0;
+
+extern "C" {
+
+const char* FB_GetLastError() { return g_last_error.c_str(); }
+
+int FB_RegisterLogCallback(void (*callback)(const char*)) { API_BEGIN(); Log::callback() = callback; API_END(); }
+int FB_CudaAvailable(int* out) { API_BEGIN(); *out = CudaAvailable() ? 1 : 0; API_END(); }
+int FB_SetTimeTag(int enabled) { API_BEGIN(); StageTimer::Get().enabled = enabled != 0; if (!enabled) StageTimer::Get().Clear(); API_END(); }
+int FB_GetTimeTagReport(int64_t buffer_len, int64_t* out_len, char* out_str) { API_BEGIN(); CopyOut(StageTimer::Get().Report(), buffer_len, out_len, out_str); API_END(); }
+
+int FB_NetworkInitWithFunctions(int num_machines, int rank, void* allreduce_sum_fn, void* allgather_fn) {
+  API_BEGIN();
+  Network::world() = num_machines; Network::rank() = rank;
+  Network::allreduce() = reinterpret_cast<Network::AllreduceSumFn>(allreduce_sum_fn);
+  Network::allgather() = reinterpret_cast<Network::AllgatherFn>(allgather_fn);
+  API_END();
+}
+int FB_NetworkFree() { API_BEGIN(); Network::world() = 1; Network::rank() = 0; Network::allreduce() = nullptr; Network::allgather() = nullptr; API_END(); }
+
+// ------------------------------------------------------------- Dataset ----
+int FB_DatasetCreateFromMat(const void* data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, const char* parameters,
+                            const DatasetHandle reference, DatasetHandle* out) {
+  API_BEGIN();
+  Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());
+  std::unique_ptr<Dataset> ds(new Dataset());
+  if (reference != nullptr) {
+    ds->CopySchemaFrom(*static_cast<const Dataset*>(reference));
+  } else {
+    Random rnd(cfg.data_random_seed);
+    const int ns = std::min<int>(nrow, cfg.bin_construct_sample_cnt);
+    std::vector<int> idx = rnd.Sample(nrow, ns);
+    std::vector<double> sample(static_cast<size_t>(idx.size()) * ncol);
+    Dataset tmp;   // reuse the dtype reader through a one-row push? simpler: read directly
+    for (size_t r = 0; r < idx.size(); ++r) for (int j = 0; j < ncol; ++j) {
+      const size_t src = is_row_major ? static_cast<size_t>(idx[r]) * ncol + j : static_cast<size_t>(j) * nrow + idx[r];
+      double v;
+      switch (dtype) {
+        case kF32: v = static_cast<const float*>(data)[src]; break;
+        case kF64: v = static_cast<const double*>(data)[src]; break;
+        case kI8: v = static_cast<const int8_t*>(data)[src]; break;
+        case kI16: v = static_cast<const int16_t*>(data)[src]; break;
+        case kU8: v = static_cast<const uint8_t*>(data)[src]; break;
+        case kU16: v = static_cast<const uint16_t*>(data)[src]; break;
+        case kI32: v = static_cast<const int32_t*>(data)[src]; break;
+        default: Log::Fatal("Unsupported dtype code %d", dtype);
+      }
+      sample[r * ncol + j] = v;
+    }
+    ds->ConstructSchema(sample.data(), static_cast<int>(idx.size()), ncol, nrow, cfg, ParseCategorical(cfg, ncol));
+  }
+  ds->AllocateRows(nrow);
+  ds->PushDense(data, dtype, nrow, ncol, is_row_major != 0, 0);
+  *out = ds.release();
+  API_END();
+}
+
+int FB_DatasetCreateFromFile(const char* filename, const char* parameters, const DatasetHandle reference, DatasetHandle* out) {
+  API_BEGIN();
+  Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());
+  Dataset* bin = Dataset::LoadBinary(filename);
+  *out = bin != nullptr ? bin : LoadDatasetFromFile(filename, cfg, static_cast<const Dataset*>(reference));
+  API_END();
+}
+
+int FB_DatasetCreateFromSample(const double* sample, int32_t ns, int32_t ncol, int64_t total, const char* parameters,
+                               const int32_t* categorical, int32_t num_categorical, DatasetHandle* out) {
+  API_BEGIN();
+  Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());
+  std::unique_ptr<Dataset> ds(new Dataset());
+  std::vector<int> cats = ParseCategorical(cfg, ncol);
+  for (int i = 0; i < num_categorical; ++i) cats.push_back(categorical[i]);
+  ds->ConstructSchema(sample, ns, ncol, total, cfg, cats);
+  *out = ds.release();
+  API_END();
+}
+
+int FB_DatasetCreateByReference(const DatasetHandle reference, DatasetHandle* out) {
+  API_BEGIN();
+  std::unique_ptr<Dataset> ds(new Dataset()); ds->CopySchemaFrom(*static_cast<const Dataset*>(reference)); *out = ds.release();
+  API_END();
+}
+
+int FB_DatasetSerializeSchema(DatasetHandle handle, int64_t buffer_len, int64_t* out_len, char* out) {
+  API_BEGIN();
+  std::vector<char> buf; static_cast<Dataset*>(handle)->SerializeSchema(&buf);
+  *out_len = static_cast<int64_t>(buf.size());
+  if (buffer_len >= *out_len && out != nullptr) memcpy(out, buf.data(), buf.size());
+  API_END();
+}
+
+int FB_DatasetCreateFromSchema(const char* schema, int64_t len, const char* parameters, DatasetHandle* out) {
+  API_BEGIN();
+  Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());
+  std::unique_ptr<Dataset> ds(new Dataset()); ds->DeserializeSchema(schema, static_cast<size_t>(len), cfg); *out = ds.release();
+  API_END();
+}
+
+int FB_DatasetInitRows(DatasetHandle handle, int32_t nrow, int64_t global_row_offset, int64_t global_num_row, int host_bins) {
+  API_BEGIN();
+  Dataset* ds = static_cast<Dataset*>(handle);
+  ds->global_row_offset = global_row_offset; ds->global_num_data = global_num_row > 0 ? global_num_row : nrow;
+  if (host_bins) ds->AllocateRows(nrow); else { ds->num_data = nrow; ds->metadata.num_data = nrow; }
+  API_END();
+}
+
+int FB_DatasetPushRows(DatasetHandle handle, const void* data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, int32_t start_row) {
+  API_BEGIN();
+  static_cast<Dataset*>(handle)->PushDense(data, dtype, nrow, ncol, is_row_major != 0, start_row);
+  API_END();
+}
+
+int FB_DatasetBinDeviceMat(DatasetHandle handle, const void* device_data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, int keep_host_copy) {
+  API_BEGIN();
+  DeviceBinDataset(static_cast<Dataset*>(handle), device_data, dtype, nrow, ncol, is_row_major != 0, keep_host_copy != 0);
+  API_END();
+}
+
+int FB_DatasetSetField(DatasetHandle handle, const char* field_name, const void* data, int64_t n, int dtype) {
+  API_BEGIN();
+  Dataset* ds = static_cast<Dataset*>(handle); const std::string f = field_name;
+  auto as_float = [&](std::vector<float>* v) {
+    v->resize(n);
+    for (int64_t i = 0; i < n; ++i) (*v)[i] = dtype == kF32 ? static_cast<const float*>(data)[i] : (dtype == kF64 ? static_cast<float>(static_cast<const double*>(data)[i]) : static_cast<float>(static_cast<const int32_t*>(data)[i]));
+  };
+  if (f == "label" || f == "target") { if (n != ds->num_data) Log::Fatal("Length of labels (%lld) differs from the number of rows (%d)", static_cast<long long>(n), ds->num_data); std::vector<float> v; as_float(&v); ds->metadata.label.swap(v); }
+  else if (f == "weight" || f == "weights") { if (n == 0) ds->metadata.SetWeights(nullptr, 0); else { std::vector<float> v; as_float(&v); ds->metadata.SetWeights(v.data(), static_cast<data_size_t>(n)); } }
+  else if (f == "group" || f == "query") { if (dtype != kI32) Log::Fatal("group must be int32"); ds->metadata.num_data = ds->num_data; ds->metadata.SetGroup(static_cast<const int32_t*>(data), static_cast<data_size_t>(n)); }
+  else if (f == "init_score") {
+    std::vector<double> v(n);
+    for (int64_t i = 0; i < n; ++i) v[i] = dtype == kF64 ? static_cast<const double*>(data)[i] : static_cast<const float*>(data)[i];
+    ds->metadata.SetInitScore(v.data(), n);
+  } else Log::Fatal("Unknown field name %s", field_name);
+  API_END();
+}
+
+int FB_DatasetGetField(DatasetHandle handle, const char* field_name, int64_t* out_len, const void** out_ptr, int* out_type) {
+  API_BEGIN();
+  Dataset* ds = static_cast<Dataset*>(handle); const std::string f = field_name;
+  if (f == "label" || f == "target") { *out_len = ds->metadata.label.size(); *out_ptr = ds->metadata.label.data(); *out_type = kF32; }
+  else if (f == "weight" || f == "weights") { *out_len = ds->metadata.weights.size(); *out_ptr = ds->metadata.weights.data(); *out_type = kF32; }
+  else if (f == "group" || f == "query") { *out_len = ds->metadata.query_boundaries.size(); *out_ptr = ds->metadata.query_boundaries.data(); *out_type = kI32; }
+  else if (f == "init_score") { *out_len = ds->metadata.init_score.size(); *out_ptr = ds->metadata.init_score.data(); *out_type = kF64; }
+  else Log::Fatal("Unknown field name %s", field_name);
+  API_END();
+}
+
+int FB_DatasetGetNumData(DatasetHandle handle, int32_t* out) { API_BEGIN(); *out = static_cast<Dataset*>(handle)->num_data; API_END(); }
+int FB_DatasetGetNumFeature(DatasetHandle handle, int32_t* out) { API_BEGIN(); *out = static_cast<Dataset*>(handle)->num_total_features; API_END(); }
+int FB_DatasetGetInfo(DatasetHandle handle, int32_t* out) {
+  API_BEGIN();
+  Dataset* ds = static_cast<Dataset*>(handle);
+  out[0] = ds->num_features; out[1] = ds->num_groups; out[2] = ds->num_total_bin; out[3] = ds->max_group_bin; out[4] = ds->device != nullptr; out[5] = ds->has_host_bins();
+  API_END();
+}
+int FB_DatasetSetFeatureNames(DatasetHandle handle, const char** names, int num) {
+  API_BEGIN();
+  Dataset* ds = static_cast<Dataset*>(handle);
+  if (num != ds->num_total_features) Log::Fatal("Size of feature names (%d) differs from the number of features (%d)", num, ds->num_total_features);
+  ds->feature_names.clear();
+  for (int i = 0; i < num; ++i) { std::string s = names[i]; for (auto& c : s) if (c == ' ') c = '_'; ds->feature_names.push_back(s); }
+  API_END();
+}
+int FB_DatasetGetFeatureNames(DatasetHandle handle, int64_t buffer_len, int64_t* out_len, char* out) {
+  API_BEGIN();
+  std::string s; for (auto& n : static_cast<Dataset*>(handle)->feature_names) { if (!s.empty()) s += "\n"; s += n; }
+  CopyOut(s, buffer_len, out_len, out);
+  API_END();
+}
+int FB_DatasetGetBinnedRow(DatasetHandle handle, int32_t row, int32_t* out_bins) {
+  API_BEGIN();
+  Dataset* ds = static_cast<Dataset*>(handle);
+  if (!ds->has_host_bins()) Log::Fatal("Dataset has no host-resident bins");
+  for (int f = 0; f < ds->num_features; ++f) out_bins[f] = ds->FeatureBin(row, f);
+  API_END();
+}
+int FB_DatasetSaveBinary(DatasetHandle handle, const char* filename) { API_BEGIN(); static_cast<Dataset*>(handle)->SaveBinary(filename); API_END(); }
+int FB_DatasetGetSubset(const DatasetHandle handle, const int32_t* idx, int32_t n, DatasetHandle* out) { API_BEGIN(); *out = static_cast<const Dataset*>(handle)->Subset(idx, n); API_END(); }
+int FB_DatasetFreeDeviceData(DatasetHandle handle) { API_BEGIN(); Dataset* ds = static_cast<Dataset*>(handle); if (ds->device) { FreeDeviceDataset(ds->device); ds->device = nullptr; } API_END(); }
+int FB_DatasetFree(DatasetHandle handle) { API_BEGIN(); delete static_cast<Dataset*>(handle); API_END(); }
+
+// ------------------------------------------------------------- Booster ----
+int FB_BoosterCreate(const DatasetHandle train_data, const char* parameters, BoosterHandle* out) {
+  API_BEGIN();
+  std::unique_ptr<BoosterWrap> b(new BoosterWrap());
+  const Dataset* train = static_cast<const Dataset*>(train_data);
+  b->config.Set(Config::Str2Map(parameters), CudaAvailable());
+  if (b->config.is_cuda && !CudaAvailable()) Log::Fatal("device_type=cuda was requested but no CUDA device is available");
+  if (b->config.is_cuda && train->device == nullptr) {
+    // the device engine uploads host bins itself when the dataset was built on the host
+    if (!train->has_host_bins()) Log::Fatal("Dataset has neither device nor host bins");
+  }
+  if (!b->config.is_cuda && !train->has_host_bins()) Log::Fatal("device_type=cpu needs a dataset with host-resident bins");
+  b->train = train;
+  b->objective.reset(CreateObjective(b->config.objective, b->config));
+  if (b->objective) {
+    if (b->objective->NeedQueries() && train->metadata.query_boundaries.empty()) Log::Fatal("Ranking tasks require query information");
+    b->objective->Init(train->metadata, train->num_data);
+  }
+  b->gbdt.reset(new GBDT());
+  b->gbdt->Init(b->config, train, b->objective.get(), b->config.metric_list);
+  *out = b.release();
+  API_END();
+}
+
+static int LoadBooster(const std::string& text, int* out_iters, BoosterHandle* out) {
+  std::unique_ptr<BoosterWrap> b(new BoosterWrap());
+  b->gbdt.reset(new GBDT());
+  if (text.size() >= 4 && memcmp(text.data(), "FALB", 4) == 0) b->gbdt->LoadModelFromBinary(text.data(), text.size());
+  else b->gbdt->LoadModelFromString(text.data(), text.size());
+  *out_iters = b->gbdt->current_iteration();
+  *out = b.release();
+  return 0;
+}
+
+int FB_BoosterCreateFromModelfile(const char* filename, int* out_num_iterations, BoosterHandle* out) {
+  API_BEGIN();
+  std::ifstream f(filename, std::ios::binary);
+  if (!f) Log::Fatal("Model file %s is not available for reads", filename);
+  std::string text((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+  LoadBooster(text, out_num_iterations, out);
+  API_END();
+}
+int FB_BoosterLoadModelFromString(const char* model_str, int64_t len, int* out_num_iterations, BoosterHandle* out) {
+  API_BEGIN(); LoadBooster(std::string(model_str, len > 0 ? static_cast<size_t>(len) : strlen(model_str)), out_num_iterations, out); API_END();
+}
+int FB_BoosterCreateFromBinary(const char* data, int64_t len, int* out_num_iterations, BoosterHandle* out) {
+  API_BEGIN(); LoadBooster(std::string(data, static_cast<size_t>(len)), out_num_iterations, out); API_END();
+}
+int FB_BoosterFree(BoosterHandle handle) { API_BEGIN(); delete static_cast<BoosterWrap*>(handle); API_END(); }
+
+#define BW() BoosterWrap* b = static_cast<BoosterWrap*>(handle); std::lock_guard<std::mutex> lock(b->mu)
+
+int FB_BoosterAddValidData(BoosterHandle handle, const DatasetHandle valid_data) { API_BEGIN(); BW(); b->gbdt->AddValidData(static_cast<const Dataset*>(valid_data)); API_END(); }
+int FB_BoosterResetParameter(BoosterHandle handle, const char* parameters) {
+  API_BEGIN(); BW();
+  auto m = Config::Str2Map(parameters);
+  for (const char* frozen : {"max_bin", "min_data_in_bin", "bin_construct_sample_cnt", "enable_bundle", "use_missing", "zero_as_missing", "categorical_feature", "num_class", "objective", "boosting", "device_type"})
+    if (m.count(frozen)) Log::Fatal("Cannot change %s after the booster was constructed", frozen);
+  Config merged = b->config;
+  auto all = b->config.raw; for (auto& kv : m) all[kv.first] = kv.second;
+  merged = Config(); merged.Set(all, CudaAvailable());
+  b->config = merged; b->gbdt->ResetConfig(merged);
+  API_END();
+}
+int FB_BoosterUpdateOneIter(BoosterHandle handle, int* is_finished) { API_BEGIN(); BW(); *is_finished = b->gbdt->TrainOneIter(nullptr, nullptr) ? 1 : 0; API_END(); }
+int FB_BoosterUpdateOneIterCustom(BoosterHandle handle, const float* grad, const float* hess, int on_device, int* is_finished) {
+  API_BEGIN(); BW();
+  if (on_device && b->gbdt->engine() == nullptr) Log::Fatal("Device gradients need a CUDA booster");
+  if (!on_device && b->gbdt->engine() != nullptr) Log::Fatal("A CUDA booster takes custom gradients as device pointers");
+  *is_finished = b->gbdt->TrainOneIter(grad, hess) ? 1 : 0;
+  API_END();
+}
+int FB_BoosterRollbackOneIter(BoosterHandle handle) { API_BEGIN(); BW(); b->gbdt->RollbackOneIter(); API_END(); }
+int FB_BoosterGetCurrentIteration(BoosterHandle handle, int* out) { API_BEGIN(); BW(); *out = b->gbdt->current_iteration(); API_END(); }
+int FB_BoosterNumModelPerIteration(BoosterHandle handle, int* out) { API_BEGIN(); BW(); *out = b->gbdt->num_tree_per_iteration_; API_END(); }
+int FB_BoosterNumberOfTotalModel(BoosterHandle handle, int* out) { API_BEGIN(); BW(); *out = b->gbdt->NumModels(); API_END(); }
+int FB_BoosterGetNumClasses(BoosterHandle handle, int* out) { API_BEGIN(); BW(); *out = b->gbdt->num_class_; API_END(); }
+int FB_BoosterGetNumFeature(BoosterHandle handle, int* out) { API_BEGIN(); BW(); *out = b->gbdt->max_feature_idx_ + 1; API_END(); }
+int FB_BoosterGetEvalCounts(BoosterHandle handle, int* out) { API_BEGIN(); BW(); *out = static_cast<int>(b->gbdt->EvalNames().size()); API_END(); }
+int FB_BoosterGetEvalNames(BoosterHandle handle, int64_t buffer_len, int64_t* out_len, char* out) {
+  API_BEGIN(); BW();
+  auto names = b->gbdt->EvalNames(); auto hb = b->gbdt->EvalHigherBetter();
+  std::string s; for (size_t i = 0; i < names.size(); ++i) { if (i) s += "\n"; s += (hb[i] ? "+" : "-") + names[i]; }
+  CopyOut(s, buffer_len, out_len, out);
+  API_END();
+}
+int FB_BoosterGetEval(BoosterHandle handle, int data_idx, int* out_len, double* out_results) {
+  API_BEGIN(); BW();
+  auto v = b->gbdt->GetEval(data_idx); *out_len = static_cast<int>(v.size());
+  for (size_t i = 0; i < v.size(); ++i) out_results[i] = v[i];
+  API_END();
+}
+int FB_BoosterGetNumPredict(BoosterHandle handle, int data_idx, int64_t* out_len) { API_BEGIN(); BW(); *out_len = b->gbdt->GetNumPredict(data_idx); API_END(); }
+int FB_BoosterGetPredict(BoosterHandle handle, int data_idx, int64_t* out_len, double* out_result) { API_BEGIN(); BW(); *out_len = b->gbdt->GetNumPredict(data_idx); b->gbdt->GetPredictAt(data_idx, out_result); API_END(); }
+int FB_BoosterGetTrainScoreDevicePtr(BoosterHandle handle, void** out_ptr) { API_BEGIN(); BW(); *out_ptr = b->gbdt->TrainScoreDevicePtr(); API_END(); }
+int FB_BoosterCalcNumPredict(BoosterHandle handle, int num_row, int predict_type, int start_iteration, int num_iteration, int64_t* out_len) {
+  API_BEGIN(); BW(); *out_len = static_cast<int64_t>(num_row) * b->gbdt->NumPredictOneRow(predict_type, start_iteration, num_iteration); API_END();
+}
+int FB_BoosterPredictForMat(BoosterHandle handle, const void* data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, int predict_type,
+                            int start_iteration, int num_iteration, const char* parameter, int64_t* out_len, double* out_result) {
+  API_BEGIN(); BW();
+  auto m = Config::Str2Map(parameter);
+  if (m.count("pred_early_stop")) b->gbdt->config_.pred_early_stop = m["pred_early_stop"] == "true" || m["pred_early_stop"] == "1";
+  if (m.count("pred_early_stop_freq")) b->gbdt->config_.pred_early_stop_freq = atoi(m["pred_early_stop_freq"].c_str());
+  if (m.count("pred_early_stop_margin")) b->gbdt->config_.pred_early_stop_margin = ParseDouble(m["pred_early_stop_margin"]);
+  if (m.count("predict_disable_shape_check")) b->gbdt->config_.predict_disable_shape_check = m["predict_disable_shape_check"] == "true" || m["predict_disable_shape_check"] == "1";
+  *out_len = static_cast<int64_t>(nrow) * b->gbdt->NumPredictOneRow(predict_type, start_iteration, num_iteration);
+  b->gbdt->PredictMat(data, dtype, nrow, ncol, is_row_major != 0, predict_type, start_iteration, num_iteration, out_result);
+  API_END();
+}
+int FB_BoosterPredictForDeviceMat(BoosterHandle handle, const void* device_data, int dtype, int32_t nrow, int32_t ncol, int is_row_major,
+                                  int predict_type, int start_iteration, int num_iteration, float* out_device) {
+  API_BEGIN(); BW();
+  DevicePredict(b->gbdt.get(), device_data, dtype, nrow, ncol, is_row_major != 0, predict_type, start_iteration, num_iteration, out_device);
+  API_END();
+}
+int FB_BoosterSaveModel(BoosterHandle handle, int start_iteration, int num_iteration, int feature_importance_type, const char* filename) {
+  API_BEGIN(); BW();
+  std::ofstream f(filename, std::ios::binary);
+  if (!f) Log::Fatal("Model file %s is not available for writes", filename);
+  f << b->gbdt->SaveModelToString(start_iteration, num_iteration, feature_importance_type);
+  API_END();
+}
+int FB_BoosterSaveModelToString(BoosterHandle handle, int start_iteration, int num_iteration, int feature_importance_type, int64_t buffer_len,
+                                int64_t* out_len, char* out_str) {
+  API_BEGIN(); BW(); CopyOut(b->gbdt->SaveModelToString(start_iteration, num_iteration, feature_importance_type), buffer_len, out_len, out_str); API_END();
+}
+int FB_BoosterDumpModel(BoosterHandle handle, int start_iteration, int num_iteration, int feature_importance_type, int64_t buffer_len,
+                        int64_t* out_len, char* out_str) {
+  API_BEGIN(); BW(); CopyOut(b->gbdt->DumpModel(start_iteration, num_iteration, feature_importance_type), buffer_len, out_len, out_str); API_END();
+}
+int FB_BoosterModelToIfElse(BoosterHandle handle, int num_iteration, int64_t buffer_len, int64_t* out_len, char* out_str) {
+  API_BEGIN(); BW(); CopyOut(b->gbdt->ModelToIfElse(num_iteration), buffer_len, out_len, out_str); API_END();
+}
+int FB_BoosterSaveModelToBinary(BoosterHandle handle, int start_iteration, int num_iteration, int f32_leaves, int64_t buffer_len, int64_t* out_len, char* out) {
+  API_BEGIN(); BW();
+  auto buf = b->gbdt->SaveModelToBinary(start_iteration, num_iteration, f32_leaves != 0);
+  *out_len = static_cast<int64_t>(buf.size());
+  if (buffer_len >= *out_len && out != nullptr) memcpy(out, buf.data(), buf.size());
+  API_END();
+}
+int FB_BoosterGetLeafValue(BoosterHandle handle, int tree_idx, int leaf_idx, double* out_val) { API_BEGIN(); BW(); *out_val = b->gbdt->GetLeafValue(tree_idx, leaf_idx); API_END(); }
+int FB_BoosterSetLeafValue(BoosterHandle handle, int tree_idx, int leaf_idx, double val) { API_BEGIN(); BW(); b->gbdt->SetLeafValue(tree_idx, leaf_idx, val); API_END(); }
+int FB_BoosterFeatureImportance(BoosterHandle handle, int num_iteration, int importance_type, double* out_results) {
+  API_BEGIN(); BW(); auto v = b->gbdt->FeatureImportance(num_iteration, importance_type); for (size_t i = 0; i < v.size(); ++i) out_results[i] = v[i]; API_END();
+}
+int FB_BoosterGetFeatureNames(BoosterHandle handle, int64_t buffer_len, int64_t* out_len, char* out) {
+  API_BEGIN(); BW(); std::string s; for (auto& n : b->gbdt->feature_names_) { if (!s.empty()) s += "\n"; s += n; } CopyOut(s, buffer_len, out_len, out); API_END();
+}
+int FB_BoosterRefit(BoosterHandle handle, const int32_t* leaf_preds, int32_t nrow, int32_t ncol) { API_BEGIN(); BW(); b->gbdt->RefitTree(leaf_preds, nrow, ncol); API_END(); }
+int FB_BoosterMerge(BoosterHandle handle, BoosterHandle other_handle) { API_BEGIN(); BW(); b->gbdt->MergeFrom(static_cast<BoosterWrap*>(other_handle)->gbdt.get()); API_END(); }
+int FB_BoosterShuffleModels(BoosterHandle handle, int start_iter, int end_iter) { API_BEGIN(); BW(); b->gbdt->ShuffleModels(start_iter, end_iter); API_END(); }
+int FB_BoosterGetUpperBoundValue(BoosterHandle handle, double* out) { API_BEGIN(); BW(); *out = b->gbdt->UpperBound(); API_END(); }
+int FB_BoosterGetLowerBoundValue(BoosterHandle handle, double* out) { API_BEGIN(); BW(); *out = b->gbdt->LowerBound(); API_END(); }
+int FB_BoosterGetLoadedParam(BoosterHandle handle, int64_t buffer_len, int64_t* out_len, char* out_str) {
+  API_BEGIN(); BW(); CopyOut(b->gbdt->loaded_parameter_.empty() ? b->gbdt->config_.ToString() : b->gbdt->loaded_parameter_, buffer_len, out_len, out_str); API_END();
+}
+int FB_BoosterGpuLaunches(BoosterHandle handle, int64_t* out) { API_BEGIN(); BW(); *out = b->gbdt->engine() ? b->gbdt->engine()->GpuLaunches() : 0; API_END(); }
+int FB_BoosterStageReport(BoosterHandle handle, int64_t buffer_len, int64_t* out_len, char* out_str) {
+  API_BEGIN(); BW(); CopyOut(b->gbdt->engine() ? b->gbdt->engine()->StageReport() : std::string(), buffer_len, out_len, out_str); API_END();
+}
+
+}  // extern "C"

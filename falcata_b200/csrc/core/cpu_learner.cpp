@@ -1,0 +1,651 @@
+// Host histogram tree learner: serial, plus data-/feature-/voting-parallel over injected
+// collectives. See fb/learner.h for the parity notes.
+//
+// Growth policies:
+//   leaf  : best-first. The leaf with the largest gain is split until num_leaves is reached.
+//   level : all splittable leaves of a level are split together; when the leaf budget binds, the
+//           level's candidates with the largest gains win (ties: lower leaf index). Splits of a
+//           level are applied in ascending leaf order, which fixes the leaf numbering.
+// The device learner implements exactly the same two policies, so trees can be compared.
+#include "fb/learner.h"
+#include "fb/objective.h"
+
+#include <numeric>
+#include <queue>
+
+namespace fb {
+
+double Network::MaxDouble(double v) {
+  if (!active()) return v;
+  std::vector<char> all; Gather(&v, sizeof(double), &all);
+  double m = v; const double* p = reinterpret_cast<const double*>(all.data());
+  for (int i = 0; i < world(); ++i) m = std::max(m, p[i]);
+  return m;
+}
+
+// ------------------------------------------------------------ ColSampler ----
+void ColSampler::Init(const Config& cfg, const Dataset* ds) {
+  frac_bytree_ = cfg.feature_fraction; frac_bynode_ = cfg.feature_fraction_bynode; seed_ = cfg.feature_fraction_seed;
+  nfeat_ = ds->num_features; used_.assign(nfeat_, 1); num_used_ = nfeat_;
+  interaction_sets_.clear();
+  if (!cfg.interaction_constraints.empty()) {
+    // "[0,1,2],[2,3]" over real feature indices
+    std::string s = cfg.interaction_constraints; std::vector<int> cur; std::string num; bool in = false;
+    for (char c : s) {
+      if (c == '[') { in = true; cur.clear(); num.clear(); }
+      else if (c == ']') { if (!num.empty()) cur.push_back(atoi(num.c_str())); num.clear(); if (in) interaction_sets_.push_back(cur); in = false; }
+      else if (c == ',') { if (in && !num.empty()) { cur.push_back(atoi(num.c_str())); num.clear(); } }
+      else if (!isspace(static_cast<unsigned char>(c))) num.push_back(c);
+    }
+  }
+}
+
+// Deterministic subset: rank features by a Philox word keyed on (seed, tree, feature) and keep the
+// k smallest. Independent of any generator state, hence identical after a resume and on any rank.
+static std::vector<int8_t> SampleFeatures(int n, double frac, uint32_t seed, uint32_t a, uint32_t b, const std::vector<int8_t>* within) {
+  std::vector<int8_t> used(n, 0);
+  std::vector<int> pool;
+  for (int f = 0; f < n; ++f) if (within == nullptr || (*within)[f]) pool.push_back(f);
+  int k = std::max(1, static_cast<int>(std::floor(frac * static_cast<double>(pool.size()) + 0.5)));
+  k = std::min<int>(k, static_cast<int>(pool.size()));
+  std::vector<std::pair<uint32_t, int>> keyed;
+  for (int f : pool) keyed.emplace_back(Philox4x32_10(static_cast<uint32_t>(f), a, b, 0x51ED27u, seed, 0xC0FFEEu).v[0], f);
+  std::sort(keyed.begin(), keyed.end());
+  for (int i = 0; i < k; ++i) used[keyed[i].second] = 1;
+  return used;
+}
+
+void ColSampler::ResetByTree(int tree_index) {
+  if (frac_bytree_ >= 1.0) { used_.assign(nfeat_, 1); num_used_ = nfeat_; return; }
+  used_ = SampleFeatures(nfeat_, frac_bytree_, static_cast<uint32_t>(seed_), static_cast<uint32_t>(tree_index), 0u, nullptr);
+  num_used_ = 0; for (auto u : used_) num_used_ += u;
+}
+
+std::vector<int8_t> ColSampler::SampleByNode(int tree_index, int node_id) const {
+  if (frac_bynode_ >= 1.0) return used_;
+  return SampleFeatures(nfeat_, frac_bynode_, static_cast<uint32_t>(seed_), static_cast<uint32_t>(tree_index), static_cast<uint32_t>(node_id) + 1u, &used_);
+}
+
+// ----------------------------------------------------------- CPU learner ----
+namespace {
+
+struct LeafState {
+  int begin = 0, count = 0;          // window in indices_
+  double sum_g = 0, sum_h = 0;
+  int64_t sum_gi = 0, sum_hi = 0;
+  int64_t global_count = 0;          // rows of the leaf over all ranks
+  double output = 0;
+  int depth = 0;
+  SplitRecord best;
+  std::vector<double> hist;          // 2 * num_total_bin (g, h) real-valued, or
+  std::vector<int64_t> hist_i;       // 2 * num_total_bin integer sums when quantized
+  bool has_hist = false;
+  std::vector<int8_t> lo_bound_hi_bound;  // unused placeholder for monotone ranges
+  double min_constraint = -std::numeric_limits<double>::infinity(), max_constraint = std::numeric_limits<double>::infinity();
+};
+
+class CPUTreeLearner : public TreeLearner {
+ public:
+  explicit CPUTreeLearner(const Config& cfg) : cfg_(cfg) {}
+  void Init(const Dataset* train, const Config& cfg) override;
+  void ResetConfig(const Config& cfg) override { cfg_ = cfg; SetParams(); col_sampler_.Init(cfg_, ds_); }
+  Tree* Train(const score_t* grad, const score_t* hess, int tree_index) override;
+  void SetBaggingData(const data_size_t* used, data_size_t num) override {
+    if (used == nullptr) { bag_.clear(); use_bag_ = false; } else { bag_.assign(used, used + num); use_bag_ = true; }
+  }
+  void AddPredictionToScore(const Tree* tree, double* score) const override;
+  void RenewTreeOutput(Tree* tree, const ObjectiveFunction* obj, std::function<double(const label_t*, int)> residual,
+                       data_size_t total_num_data, const data_size_t* bag_indices, data_size_t bag_cnt, const double* score) const override;
+  Tree* FitByExistingTree(const Tree* old_tree, const score_t* grad, const score_t* hess) const override;
+  const data_size_t* LeafIndices(int leaf, data_size_t* count) const override { *count = leaves_[leaf].count; return indices_.data() + leaves_[leaf].begin; }
+
+ private:
+  void SetParams();
+  void Quantize(const score_t* grad, const score_t* hess, int tree_index);
+  void ConstructHistogram(LeafState* leaf);
+  void SubtractHistogram(const LeafState& parent_as_larger_src, const LeafState& smaller, LeafState* larger);
+  void FindBestSplit(LeafState* leaf, int leaf_id, int tree_index);
+  void ScanNumerical(const LeafState& leaf, int f, const LeafScanInfo& L, SplitRecord* best) const;
+  void ScanCategorical(const LeafState& leaf, int f, const LeafScanInfo& L, SplitRecord* best) const;
+  int ApplySplit(Tree* tree, int leaf_id);
+  void ReduceHistogramAcrossRanks(LeafState* leaf);
+  void SyncBestSplit(SplitRecord* rec) const;
+  bool FeatureOwned(int f) const { return !(parallel_data_ || parallel_feature_) || f % Network::world() == Network::rank(); }
+
+  Config cfg_;
+  SplitParams sp_;
+  const Dataset* ds_ = nullptr;
+  ColSampler col_sampler_;
+  std::vector<data_size_t> indices_, tmp_;
+  std::vector<LeafState> leaves_;
+  std::vector<data_size_t> bag_;
+  bool use_bag_ = false;
+  bool quant_ = false, parallel_data_ = false, parallel_feature_ = false, parallel_voting_ = false;
+  QuantState qs_;
+  std::vector<int32_t> gh_packed_;
+  const score_t* grad_ = nullptr; const score_t* hess_ = nullptr;
+  std::vector<int8_t> node_feature_mask_;
+  std::vector<int64_t> voted_hist_i_; std::vector<double> voted_hist_;
+  std::vector<int8_t> voted_;      // voting-parallel: features whose histograms are globally reduced for the current leaf
+  int cur_tree_index_ = 0;
+  Random extra_rand_{6};
+};
+
+void CPUTreeLearner::SetParams() {
+  sp_.lambda_l1 = cfg_.lambda_l1; sp_.lambda_l2 = cfg_.lambda_l2; sp_.max_delta_step = cfg_.max_delta_step; sp_.path_smooth = cfg_.path_smooth;
+  sp_.min_sum_hessian_in_leaf = cfg_.min_sum_hessian_in_leaf; sp_.min_gain_to_split = cfg_.min_gain_to_split;
+  sp_.min_data_in_leaf = cfg_.min_data_in_leaf; sp_.max_depth = cfg_.max_depth;
+  sp_.max_cat_threshold = cfg_.max_cat_threshold; sp_.max_cat_to_onehot = cfg_.max_cat_to_onehot; sp_.min_data_per_group = cfg_.min_data_per_group;
+  sp_.cat_l2 = cfg_.cat_l2; sp_.cat_smooth = cfg_.cat_smooth; sp_.extra_trees = cfg_.extra_trees ? 1 : 0;
+  quant_ = cfg_.quant != QuantMode::None;
+  qs_.bins = cfg_.quant_bins_resolved; qs_.stochastic = cfg_.quant == QuantMode::Stochastic;
+  const bool net = Network::active();
+  parallel_data_ = net && cfg_.tree_learner == "data";
+  parallel_feature_ = net && cfg_.tree_learner == "feature";
+  parallel_voting_ = net && cfg_.tree_learner == "voting";
+  extra_rand_ = Random(cfg_.extra_seed);
+}
+
+void CPUTreeLearner::Init(const Dataset* train, const Config& cfg) {
+  ds_ = train; cfg_ = cfg;
+  if (!ds_->has_host_bins()) Log::Fatal("The CPU learner needs host-resident bins (dataset was built device-only)");
+  SetParams();
+  col_sampler_.Init(cfg_, ds_);
+  indices_.resize(ds_->num_data); tmp_.resize(ds_->num_data);
+}
+
+void CPUTreeLearner::Quantize(const score_t* grad, const score_t* hess, int tree_index) {
+  const data_size_t n = ds_->num_data;
+  double mg = 0, mh = 0;
+  const data_size_t cnt = use_bag_ ? static_cast<data_size_t>(bag_.size()) : n;
+  for (data_size_t k = 0; k < cnt; ++k) {
+    data_size_t i = use_bag_ ? bag_[k] : k;
+    mg = std::max(mg, static_cast<double>(std::fabs(grad[i]))); mh = std::max(mh, static_cast<double>(std::fabs(hess[i])));
+  }
+  mg = Network::MaxDouble(mg); mh = Network::MaxDouble(mh);
+  // scales are computed in fp32 exactly as on the device
+  float gs = static_cast<float>(mg) / static_cast<float>(qs_.bins / 2), hs = static_cast<float>(mh) / static_cast<float>(qs_.bins);
+  if (!(gs > 0.f)) gs = 1.f;
+  if (!(hs > 0.f)) hs = 1.f;
+  qs_.g_scale = gs; qs_.h_scale = hs;
+  const float ig = 1.0f / gs, ih = 1.0f / hs;
+  gh_packed_.resize(n);
+  const uint32_t seed = static_cast<uint32_t>(cfg_.seed);
+#pragma omp parallel for schedule(static)
+  for (data_size_t i = 0; i < n; ++i)
+    gh_packed_[i] = QuantizeRow(grad[i], hess[i], ig, ih, qs_.stochastic, seed, static_cast<uint32_t>(tree_index), static_cast<uint64_t>(ds_->global_row_offset + i));
+}
+
+void CPUTreeLearner::ConstructHistogram(LeafState* leaf) {
+  const int nb = ds_->num_total_bin, ng = ds_->num_groups;
+  const data_size_t* idx = indices_.data() + leaf->begin;
+  if (quant_) {
+    leaf->hist_i.assign(2 * static_cast<size_t>(nb), 0);
+    int64_t* H = leaf->hist_i.data();
+    for (int k = 0; k < leaf->count; ++k) {
+      const data_size_t i = idx[k];
+      const int32_t w = gh_packed_[i];
+      const int64_t g = UnpackG(w), h = UnpackH(w);
+      for (int gidx = 0; gidx < ng; ++gidx) {
+        const int s = ds_->group_bin_start[gidx] + ds_->GroupBin(i, gidx);
+        H[2 * s] += g; H[2 * s + 1] += h;
+      }
+    }
+  } else {
+    leaf->hist.assign(2 * static_cast<size_t>(nb), 0.0);
+    double* H = leaf->hist.data();
+    for (int k = 0; k < leaf->count; ++k) {
+      const data_size_t i = idx[k];
+      const double g = grad_[i], h = hess_[i];
+      for (int gidx = 0; gidx < ng; ++gidx) {
+        const int s = ds_->group_bin_start[gidx] + ds_->GroupBin(i, gidx);
+        H[2 * s] += g; H[2 * s + 1] += h;
+      }
+    }
+  }
+  leaf->has_hist = true;
+  ReduceHistogramAcrossRanks(leaf);
+}
+
+void CPUTreeLearner::ReduceHistogramAcrossRanks(LeafState* leaf) {
+  if (!(parallel_data_ || parallel_voting_)) return;
+  // Data-parallel: sum every rank's local histogram. (The device path reduce-scatters into
+  // owners; on the host a full sum followed by owned-feature search is equivalent.)
+  if (parallel_voting_) return;   // voting reduces only voted features, inside FindBestSplit
+  if (quant_) Network::SumInt64(leaf->hist_i.data(), static_cast<int64_t>(leaf->hist_i.size()));
+  else Network::SumDouble(leaf->hist.data(), static_cast<int64_t>(leaf->hist.size()));
+}
+
+void CPUTreeLearner::SubtractHistogram(const LeafState& parent, const LeafState& smaller, LeafState* larger) {
+  if (quant_) {
+    larger->hist_i.resize(parent.hist_i.size());
+    for (size_t i = 0; i < parent.hist_i.size(); ++i) larger->hist_i[i] = parent.hist_i[i] - smaller.hist_i[i];
+  } else {
+    larger->hist.resize(parent.hist.size());
+    for (size_t i = 0; i < parent.hist.size(); ++i) larger->hist[i] = parent.hist[i] - smaller.hist[i];
+  }
+  larger->has_hist = true;
+}
+
+// Numerical threshold search of one feature: one forward prefix over the non-missing bins serves
+// both scan directions (see ScanRank in fb/split_math.h).
+void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanInfo& L, SplitRecord* best) const {
+  const FeatureMeta& m = ds_->feature_meta[f];
+  const int nb = m.num_bin;
+  auto slot = [&](int b) { return m.bundled ? m.hist_offset + (b < m.most_freq_bin ? b : b - 1) : m.hist_offset + b; };
+  // per-bin values (integers when quantized)
+  std::vector<int64_t> gi(nb, 0), hi(nb, 0);
+  std::vector<double> gd(nb, 0.0), hd(nb, 0.0);
+  if (quant_) {
+    int64_t og = 0, oh = 0;
+    for (int b = 0; b < nb; ++b) if (!(m.bundled && b == m.most_freq_bin)) { gi[b] = leaf.hist_i[2 * slot(b)]; hi[b] = leaf.hist_i[2 * slot(b) + 1]; og += gi[b]; oh += hi[b]; }
+    if (m.bundled) { gi[m.most_freq_bin] = L.sum_gi - og; hi[m.most_freq_bin] = L.sum_hi - oh; }
+  } else {
+    double og = 0, oh = 0;
+    for (int b = 0; b < nb; ++b) if (!(m.bundled && b == m.most_freq_bin)) { gd[b] = leaf.hist[2 * slot(b)]; hd[b] = leaf.hist[2 * slot(b) + 1]; og += gd[b]; oh += hd[b]; }
+    if (m.bundled) { gd[m.most_freq_bin] = L.sum_g - og; hd[m.most_freq_bin] = L.sum_h - oh; }
+  }
+  int skip = -1;
+  const bool two_pass = m.missing_type != static_cast<int>(MissingType::None) && nb > 2;
+  if (two_pass) skip = m.missing_type == static_cast<int>(MissingType::Zero) ? m.default_bin : nb - 1;
+  auto binh = [&](int b) { return quant_ ? FB_MUL(static_cast<double>(hi[b]), L.h_scale) : hd[b]; };
+  int64_t mgi = 0, mhi = 0; double mgd = 0, mhd = 0; int mcnt = 0;
+  if (skip >= 0) { mgi = gi[skip]; mhi = hi[skip]; mgd = gd[skip]; mhd = hd[skip]; mcnt = BinCountEstimate(binh(skip), L.cnt_factor); }
+  int rand_t = -1;
+  if (sp_.extra_trees && nb > 2) rand_t = const_cast<Random&>(extra_rand_).NextInt(0, nb - 1);
+  double best_gain = -std::numeric_limits<double>::infinity(); int best_rank = 1 << 30;
+  SplitRecord cand; InitSplitRecord(&cand);
+  int64_t pgi = 0, phi = 0; double pgd = 0, phd = 0; int pc = 0;
+  for (int t = 0; t <= nb - 2; ++t) {
+    if (t != skip) { pgi += gi[t]; phi += hi[t]; pgd += gd[t]; phd += hd[t]; pc += BinCountEstimate(binh(t), L.cnt_factor); }
+    if (rand_t >= 0 && t != rand_t) continue;
+    for (int pass = 0; pass < (two_pass ? 2 : 1); ++pass) {
+      if (t == skip && pass == 1 && m.missing_type == static_cast<int>(MissingType::Zero)) continue;
+      int64_t lgi = pgi, lhi = phi; double lg, lh; int lc = pc;
+      if (pass == 0 && skip >= 0) { lgi += mgi; lhi += mhi; lc += mcnt; }
+      if (quant_) { lg = FB_MUL(static_cast<double>(lgi), L.g_scale); lh = FB_MUL(static_cast<double>(lhi), L.h_scale); }
+      else { lg = pgd + ((pass == 0 && skip >= 0) ? mgd : 0.0); lh = phd + ((pass == 0 && skip >= 0) ? mhd : 0.0); }
+      double lo, ro;
+      const double gain = EvalCandidate(lg, lh, lc, L, sp_, m.monotone, &lo, &ro);
+      if (gain == -std::numeric_limits<double>::infinity()) continue;
+      const int rank = ScanRank(pass, t, nb);
+      if (gain > best_gain || (gain == best_gain && rank < best_rank)) {
+        best_gain = gain; best_rank = rank;
+        cand.gain = gain; cand.feature = f; cand.threshold = t; cand.default_left = pass == 0 ? 1 : 0;
+        cand.left_g = lg; cand.left_h = lh; cand.right_g = FB_SUB(L.sum_g, lg); cand.right_h = FB_SUB(L.sum_h, lh);
+        cand.left_out = lo; cand.right_out = ro; cand.left_gi = lgi; cand.left_hi = lhi;
+        cand.left_cnt = lc; cand.right_cnt = L.num_data - lc; cand.monotone = m.monotone;
+      }
+    }
+  }
+  if (cand.feature >= 0) {
+    cand.gain = FB_MUL(cand.gain, static_cast<double>(m.penalty));
+    if (SplitBetter(cand.gain, ds_->feature_meta[cand.feature].real_index, cand.threshold, best->gain,
+                    best->feature >= 0 ? ds_->feature_meta[best->feature].real_index : -1, best->threshold)) *best = cand;
+  }
+}
+
+// Categorical search: one-vs-rest for few categories, otherwise categories sorted by
+// sum_g / (sum_h + cat_smooth) and scanned from both ends (many-vs-many).
+void CPUTreeLearner::ScanCategorical(const LeafState& leaf, int f, const LeafScanInfo& L, SplitRecord* best) const {
+  const FeatureMeta& m = ds_->feature_meta[f];
+  const int nb = m.num_bin;
+  if (nb > 256) return;
+  auto slot = [&](int b) { return m.bundled ? m.hist_offset + (b < m.most_freq_bin ? b : b - 1) : m.hist_offset + b; };
+  std::vector<double> g(nb, 0), h(nb, 0);
+  double og = 0, oh = 0;
+  for (int b = 0; b < nb; ++b) if (!(m.bundled && b == m.most_freq_bin)) {
+    if (quant_) { g[b] = leaf.hist_i[2 * slot(b)] * L.g_scale; h[b] = leaf.hist_i[2 * slot(b) + 1] * L.h_scale; }
+    else { g[b] = leaf.hist[2 * slot(b)]; h[b] = leaf.hist[2 * slot(b) + 1]; }
+    og += g[b]; oh += h[b];
+  }
+  if (m.bundled) { g[m.most_freq_bin] = L.sum_g - og; h[m.most_freq_bin] = L.sum_h - oh; }
+  SplitParams p = sp_; p.lambda_l2 += sp_.cat_l2;
+  SplitRecord cand; InitSplitRecord(&cand);
+  double best_gain = -std::numeric_limits<double>::infinity();
+  auto consider = [&](double lg, double lh, int lc, const std::vector<int>& bins_left) {
+    double lo, ro;
+    double gain = EvalCandidate(lg, lh, lc, L, p, 0, &lo, &ro);
+    if (gain > best_gain) {
+      best_gain = gain; cand.gain = gain; cand.feature = f; cand.is_categorical = 1; cand.threshold = 0; cand.default_left = 0;
+      cand.left_g = lg; cand.left_h = lh; cand.right_g = L.sum_g - lg; cand.right_h = L.sum_h - lh; cand.left_out = lo; cand.right_out = ro;
+      cand.left_cnt = lc; cand.right_cnt = L.num_data - lc;
+      for (int i = 0; i < 8; ++i) cand.cat_bitset[i] = 0;
+      for (int b : bins_left) cand.cat_bitset[b >> 5] |= (1u << (b & 31));
+      cand.num_cat_bins = static_cast<int>(bins_left.size());
+    }
+  };
+  if (nb <= sp_.max_cat_to_onehot) {
+    for (int b = 1; b < nb; ++b) {   // bin 0 (NaN / other) always goes right
+      int c = BinCountEstimate(h[b], L.cnt_factor);
+      consider(g[b], h[b], c, {b});
+    }
+  } else {
+    std::vector<int> cats;
+    for (int b = 1; b < nb; ++b) if (BinCountEstimate(h[b], L.cnt_factor) >= sp_.cat_smooth) cats.push_back(b);
+    auto ratio = [&](int b) { return g[b] / (h[b] + sp_.cat_smooth); };
+    std::stable_sort(cats.begin(), cats.end(), [&](int a, int b) { return ratio(a) < ratio(b); });
+    const int used = static_cast<int>(cats.size());
+    const int max_num = std::min(sp_.max_cat_threshold, (used + 1) / 2);
+    for (int dir = 0; dir < 2; ++dir) {
+      double lg = 0, lh = 0; int lc = 0, grp = 0; std::vector<int> left;
+      for (int k = 0; k < used && k < max_num; ++k) {
+        int b = dir == 0 ? cats[k] : cats[used - 1 - k];
+        lg += g[b]; lh += h[b]; int c = BinCountEstimate(h[b], L.cnt_factor); lc += c; grp += c; left.push_back(b);
+        if (grp < sp_.min_data_per_group) continue;
+        grp = 0;
+        consider(lg, lh, lc, left);
+      }
+    }
+  }
+  if (cand.feature >= 0) {
+    cand.gain *= m.penalty;
+    if (SplitBetter(cand.gain, m.real_index, 0, best->gain, best->feature >= 0 ? ds_->feature_meta[best->feature].real_index : -1, best->threshold)) *best = cand;
+  }
+}
+
+void CPUTreeLearner::SyncBestSplit(SplitRecord* rec) const {
+  if (!(parallel_data_ || parallel_feature_ || parallel_voting_)) return;
+  std::vector<char> all; Network::Gather(rec, sizeof(SplitRecord), &all);
+  const SplitRecord* r = reinterpret_cast<const SplitRecord*>(all.data());
+  SplitRecord bestr; InitSplitRecord(&bestr);
+  for (int k = 0; k < Network::world(); ++k) {
+    const int fa = r[k].feature >= 0 ? ds_->feature_meta[r[k].feature].real_index : -1;
+    const int fb_ = bestr.feature >= 0 ? ds_->feature_meta[bestr.feature].real_index : -1;
+    if (SplitBetter(r[k].gain, fa, r[k].threshold, bestr.gain, fb_, bestr.threshold)) bestr = r[k];
+  }
+  *rec = bestr;
+}
+
+void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index) {
+  InitSplitRecord(&leaf->best);
+  if (sp_.max_depth > 0 && leaf->depth >= sp_.max_depth) return;
+  const int64_t n_global = leaf->global_count;
+  if (n_global < 2LL * sp_.min_data_in_leaf) return;
+  LeafScanInfo L;
+  L.sum_g = leaf->sum_g; L.sum_h = leaf->sum_h; L.sum_gi = leaf->sum_gi; L.sum_hi = leaf->sum_hi;
+  L.num_data = static_cast<int>(n_global); L.parent_output = leaf->output;
+  L.g_scale = quant_ ? qs_.g_scale : 1.0; L.h_scale = quant_ ? qs_.h_scale : 1.0;
+  L.cnt_factor = FB_DIV(static_cast<double>(L.num_data), L.sum_h);
+  L.min_gain_shift = FB_ADD(LeafGainGivenOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, leaf->output), sp_.min_gain_to_split);
+  if (sp_.max_delta_step <= 0.0 && sp_.path_smooth <= 0.0)
+    L.min_gain_shift = FB_ADD(LeafGain(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, L.num_data, leaf->output), sp_.min_gain_to_split);
+  const std::vector<int8_t> mask = col_sampler_.by_node() ? col_sampler_.SampleByNode(tree_index, leaf_id + 1000003 * leaf->depth) : col_sampler_.used_by_tree();
+
+  if (parallel_voting_) {
+    // PV-Tree: local top-k by local gain, global vote, reduce only the voted features.
+    LeafScanInfo Lloc = L;
+    double lg = 0, lh = 0; int64_t lgi = 0, lhi = 0;
+    // local totals from any one feature's bins
+    { const FeatureMeta& m0 = ds_->feature_meta[0]; const int g0 = m0.group;
+      for (int b = 0; b < ds_->group_num_bin[g0]; ++b) { int s = ds_->group_bin_start[g0] + b;
+        if (quant_) { lgi += leaf->hist_i[2 * s]; lhi += leaf->hist_i[2 * s + 1]; } else { lg += leaf->hist[2 * s]; lh += leaf->hist[2 * s + 1]; } } }
+    if (quant_) { lg = lgi * qs_.g_scale; lh = lhi * qs_.h_scale; }
+    Lloc.sum_g = lg; Lloc.sum_h = lh; Lloc.sum_gi = lgi; Lloc.sum_hi = lhi; Lloc.num_data = leaf->count;
+    Lloc.cnt_factor = lh > 0 ? leaf->count / lh : 0;
+    Lloc.min_gain_shift = LeafGain(lg, lh + 2 * kEpsilon, sp_, leaf->count, leaf->output) + sp_.min_gain_to_split;
+    SplitParams save = sp_;
+    sp_.min_data_in_leaf = std::max(1, sp_.min_data_in_leaf / Network::world());
+    sp_.min_sum_hessian_in_leaf = sp_.min_sum_hessian_in_leaf / Network::world();
+    std::vector<std::pair<double, int>> local;
+    for (int f = 0; f < ds_->num_features; ++f) {
+      if (!mask[f]) continue;
+      SplitRecord r; InitSplitRecord(&r);
+      if (ds_->feature_meta[f].bin_type == static_cast<int>(BinType::Numerical)) ScanNumerical(*leaf, f, Lloc, &r); else ScanCategorical(*leaf, f, Lloc, &r);
+      if (r.feature >= 0) local.emplace_back(r.gain, f);
+    }
+    sp_ = save;
+    std::stable_sort(local.begin(), local.end(), [](const std::pair<double, int>& a, const std::pair<double, int>& b) { return a.first > b.first; });
+    const int k = cfg_.top_k;
+    std::vector<int32_t> mine(k, -1);
+    for (int i = 0; i < k && i < static_cast<int>(local.size()); ++i) mine[i] = local[i].second;
+    std::vector<char> all; Network::Gather(mine.data(), k * sizeof(int32_t), &all);
+    const int32_t* v = reinterpret_cast<const int32_t*>(all.data());
+    std::vector<int> votes(ds_->num_features, 0);
+    for (int i = 0; i < k * Network::world(); ++i) if (v[i] >= 0) votes[v[i]]++;
+    std::vector<int> order(ds_->num_features); std::iota(order.begin(), order.end(), 0);
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return votes[a] > votes[b]; });
+    voted_.assign(ds_->num_features, 0);
+    for (int i = 0; i < 2 * k && i < ds_->num_features; ++i) if (votes[order[i]] > 0) voted_[order[i]] = 1;
+    // reduce voted features' slots only
+    std::vector<int> slots;
+    for (int f = 0; f < ds_->num_features; ++f) if (voted_[f]) {
+      const FeatureMeta& m = ds_->feature_meta[f]; const int n = m.bundled ? m.num_bin - 1 : m.num_bin;
+      for (int b = 0; b < n; ++b) slots.push_back(m.hist_offset + b);
+    }
+    if (quant_) { std::vector<int64_t> buf(2 * slots.size()); for (size_t i = 0; i < slots.size(); ++i) { buf[2 * i] = leaf->hist_i[2 * slots[i]]; buf[2 * i + 1] = leaf->hist_i[2 * slots[i] + 1]; }
+      Network::SumInt64(buf.data(), static_cast<int64_t>(buf.size()));
+      voted_hist_i_.assign(leaf->hist_i.size(), 0); for (size_t i = 0; i < slots.size(); ++i) { voted_hist_i_[2 * slots[i]] = buf[2 * i]; voted_hist_i_[2 * slots[i] + 1] = buf[2 * i + 1]; }
+    } else { std::vector<double> buf(2 * slots.size()); for (size_t i = 0; i < slots.size(); ++i) { buf[2 * i] = leaf->hist[2 * slots[i]]; buf[2 * i + 1] = leaf->hist[2 * slots[i] + 1]; }
+      Network::SumDouble(buf.data(), static_cast<int64_t>(buf.size()));
+      voted_hist_.assign(leaf->hist.size(), 0.0); for (size_t i = 0; i < slots.size(); ++i) { voted_hist_[2 * slots[i]] = buf[2 * i]; voted_hist_[2 * slots[i] + 1] = buf[2 * i + 1]; }
+    }
+    LeafState global = *leaf;   // copy with reduced bins of the voted features
+    if (quant_) global.hist_i = voted_hist_i_; else global.hist = voted_hist_;
+    SplitRecord best; InitSplitRecord(&best);
+    for (int f = 0; f < ds_->num_features; ++f) {
+      if (!voted_[f] || f % Network::world() != Network::rank()) continue;
+      if (ds_->feature_meta[f].bin_type == static_cast<int>(BinType::Numerical)) ScanNumerical(global, f, L, &best); else ScanCategorical(global, f, L, &best);
+    }
+    SyncBestSplit(&best);
+    leaf->best = best;
+    return;
+  }
+
+  SplitRecord best; InitSplitRecord(&best);
+  for (int f = 0; f < ds_->num_features; ++f) {
+    if (!mask[f] || !FeatureOwned(f)) continue;
+    if (ds_->feature_meta[f].bin_type == static_cast<int>(BinType::Numerical)) ScanNumerical(*leaf, f, L, &best);
+    else ScanCategorical(*leaf, f, L, &best);
+  }
+  SyncBestSplit(&best);
+  leaf->best = best;
+}
+
+int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
+  LeafState& P = leaves_[leaf_id];
+  const SplitRecord s = P.best;
+  const FeatureMeta& m = ds_->feature_meta[s.feature];
+  const BinMapper& bm = *ds_->mappers[m.real_index];
+  // stable partition of the leaf's window
+  data_size_t* idx = indices_.data() + P.begin;
+  int nl = 0, nr = 0;
+  const int nan_bin = m.num_bin - 1;
+  for (int k = 0; k < P.count; ++k) {
+    const data_size_t i = idx[k];
+    const int fbin = ds_->FeatureBin(i, s.feature);
+    bool left;
+    if (s.is_categorical) left = (s.cat_bitset[fbin >> 5] >> (fbin & 31)) & 1;
+    else if ((m.missing_type == 1 && fbin == m.default_bin) || (m.missing_type == 2 && fbin == nan_bin)) left = s.default_left != 0;
+    else left = fbin <= s.threshold;
+    if (left) idx[nl++] = i; else tmp_[nr++] = i;
+  }
+  std::copy(tmp_.begin(), tmp_.begin() + nr, idx + nl);
+  int64_t cnts[2] = {nl, nr};
+  if (parallel_data_ || parallel_voting_) Network::SumInt64(cnts, 2);
+  const int gl = static_cast<int>(cnts[0]), gr = static_cast<int>(cnts[1]);
+  int right_id;
+  if (s.is_categorical) {
+    std::vector<uint32_t> inner(s.cat_bitset, s.cat_bitset + 8);
+    while (inner.size() > 1 && inner.back() == 0) inner.pop_back();
+    std::vector<uint32_t> real;
+    for (int b = 0; b < m.num_bin; ++b) if ((s.cat_bitset[b >> 5] >> (b & 31)) & 1) {
+      int cat = bm.bin_2_categorical[b]; if (cat < 0) continue;
+      if (static_cast<int>(real.size()) <= (cat >> 5)) real.resize((cat >> 5) + 1, 0);
+      real[cat >> 5] |= (1u << (cat & 31));
+    }
+    if (real.empty()) real.push_back(0);
+    right_id = tree->SplitCategorical(leaf_id, s.feature, m.real_index, inner.data(), static_cast<int>(inner.size()), real.data(),
+                                      static_cast<int>(real.size()), s.left_out, s.right_out, gl, gr, s.left_h, s.right_h,
+                                      static_cast<float>(s.gain), m.missing_type);
+  } else {
+    right_id = tree->Split(leaf_id, s.feature, m.real_index, static_cast<uint32_t>(s.threshold), bm.BinToValue(s.threshold),
+                           s.left_out, s.right_out, gl, gr, s.left_h, s.right_h, static_cast<float>(s.gain), m.missing_type, s.default_left != 0);
+  }
+  if (static_cast<int>(leaves_.size()) <= right_id) leaves_.resize(right_id + 1);
+  LeafState& Lf = leaves_[leaf_id];     // reference may have moved after resize
+  LeafState parent_copy;                // keeps the parent's histogram for the subtraction
+  parent_copy.hist.swap(Lf.hist); parent_copy.hist_i.swap(Lf.hist_i);
+  LeafState& R = leaves_[right_id];
+  R = LeafState();
+  R.begin = Lf.begin + nl; R.count = nr; Lf.count = nl;
+  R.depth = Lf.depth + 1; Lf.depth += 1;
+  R.sum_g = s.right_g; R.sum_h = s.right_h; R.sum_gi = Lf.sum_gi - s.left_gi; R.sum_hi = Lf.sum_hi - s.left_hi;
+  Lf.sum_g = s.left_g; Lf.sum_h = s.left_h; Lf.sum_gi = s.left_gi; Lf.sum_hi = s.left_hi;
+  R.output = s.right_out; Lf.output = s.left_out;
+  R.global_count = gr; Lf.global_count = gl;
+  // monotone (basic): children inherit the parent's bounds, tightened at the mid point
+  R.min_constraint = Lf.min_constraint; R.max_constraint = Lf.max_constraint;
+  if (s.monotone != 0) {
+    const double mid = (s.left_out + s.right_out) / 2.0;
+    if (s.monotone > 0) { Lf.max_constraint = std::min(Lf.max_constraint, mid); R.min_constraint = std::max(R.min_constraint, mid); }
+    else { Lf.min_constraint = std::max(Lf.min_constraint, mid); R.max_constraint = std::min(R.max_constraint, mid); }
+  }
+  // histogram of the smaller child from data, the larger by subtraction. Smaller is decided on
+  // GLOBAL counts so that every rank constructs the same child.
+  LeafState* smaller = gl <= gr ? &Lf : &R;
+  LeafState* larger = gl <= gr ? &R : &Lf;
+  if (parallel_voting_) {
+    // local histograms stay local under voting; both children subtract locally
+    ConstructHistogram(smaller);
+    SubtractHistogram(parent_copy, *smaller, larger);
+  } else {
+    ConstructHistogram(smaller);
+    SubtractHistogram(parent_copy, *smaller, larger);
+  }
+  return right_id;
+}
+
+Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_index) {
+  ScopedTimer timer("CPUTreeLearner::Train");
+  grad_ = grad; hess_ = hess; cur_tree_index_ = tree_index;
+  col_sampler_.ResetByTree(tree_index);
+  if (quant_) Quantize(grad, hess, tree_index);
+  std::unique_ptr<Tree> tree(new Tree(cfg_.num_leaves, false, false));
+  leaves_.clear(); leaves_.resize(1);
+  LeafState& root = leaves_[0];
+  const data_size_t n = use_bag_ ? static_cast<data_size_t>(bag_.size()) : ds_->num_data;
+  if (use_bag_) std::copy(bag_.begin(), bag_.end(), indices_.begin()); else std::iota(indices_.begin(), indices_.end(), 0);
+  root.begin = 0; root.count = n;
+  if (quant_) {
+    int64_t sg = 0, sh = 0;
+    for (data_size_t k = 0; k < n; ++k) { int32_t w = gh_packed_[indices_[k]]; sg += UnpackG(w); sh += UnpackH(w); }
+    int64_t s[3] = {sg, sh, n};
+    if (parallel_data_ || parallel_voting_) Network::SumInt64(s, 3);
+    root.sum_gi = s[0]; root.sum_hi = s[1]; root.global_count = s[2];
+    root.sum_g = FB_MUL(static_cast<double>(s[0]), qs_.g_scale); root.sum_h = FB_MUL(static_cast<double>(s[1]), qs_.h_scale);
+  } else {
+    double sg = 0, sh = 0;
+    for (data_size_t k = 0; k < n; ++k) { sg += grad[indices_[k]]; sh += hess[indices_[k]]; }
+    double s[2] = {sg, sh}; int64_t c = n;
+    if (parallel_data_ || parallel_voting_) { Network::SumDouble(s, 2); Network::SumInt64(&c, 1); }
+    root.sum_g = s[0]; root.sum_h = s[1]; root.global_count = c;
+  }
+  root.output = LeafOutput(root.sum_g, FB_ADD(root.sum_h, 2 * kEpsilon), sp_, static_cast<int>(root.global_count), 0.0);
+  tree->leaf_value[0] = root.output; tree->leaf_count[0] = static_cast<int>(root.global_count); tree->leaf_weight[0] = root.sum_h;
+  ConstructHistogram(&root);
+  FindBestSplit(&root, 0, tree_index);
+
+  if (cfg_.grow_policy == "leaf") {
+    while (tree->num_leaves < cfg_.num_leaves) {
+      int best_leaf = -1;
+      for (int l = 0; l < tree->num_leaves; ++l) {
+        const SplitRecord& b = leaves_[l].best;
+        if (b.feature < 0 || !(b.gain > 0.0)) continue;
+        if (best_leaf < 0 || b.gain > leaves_[best_leaf].best.gain) best_leaf = l;
+      }
+      if (best_leaf < 0) break;
+      int right = ApplySplit(tree.get(), best_leaf);
+      FindBestSplit(&leaves_[best_leaf], best_leaf, tree_index);
+      FindBestSplit(&leaves_[right], right, tree_index);
+    }
+  } else {
+    std::vector<int> frontier = {0};
+    while (tree->num_leaves < cfg_.num_leaves && !frontier.empty()) {
+      std::vector<int> cand;
+      for (int l : frontier) if (leaves_[l].best.feature >= 0 && leaves_[l].best.gain > 0.0) cand.push_back(l);
+      if (cand.empty()) break;
+      const int budget = cfg_.num_leaves - tree->num_leaves;
+      if (static_cast<int>(cand.size()) > budget) {
+        std::stable_sort(cand.begin(), cand.end(), [&](int a, int b) {
+          if (leaves_[a].best.gain != leaves_[b].best.gain) return leaves_[a].best.gain > leaves_[b].best.gain;
+          return a < b; });
+        cand.resize(budget);
+        std::sort(cand.begin(), cand.end());
+      }
+      std::vector<int> next;
+      for (int l : cand) { int r = ApplySplit(tree.get(), l); next.push_back(l); next.push_back(r); }
+      for (int l : next) FindBestSplit(&leaves_[l], l, tree_index);
+      frontier.swap(next);
+    }
+  }
+  return tree.release();
+}
+
+void CPUTreeLearner::AddPredictionToScore(const Tree* tree, double* score) const {
+  for (int l = 0; l < tree->num_leaves; ++l) {
+    const double v = tree->leaf_value[l];
+    const data_size_t* idx = indices_.data() + leaves_[l].begin;
+    for (int k = 0; k < leaves_[l].count; ++k) score[idx[k]] += v;
+  }
+}
+
+void CPUTreeLearner::RenewTreeOutput(Tree* tree, const ObjectiveFunction* obj, std::function<double(const label_t*, int)> residual,
+                                     data_size_t, const data_size_t*, data_size_t, const double* score) const {
+  if (obj == nullptr || !obj->IsRenewTreeOutput()) return;
+  std::vector<double> outs(tree->num_leaves, 0.0); std::vector<double> have(tree->num_leaves, 0.0);
+  for (int l = 0; l < tree->num_leaves; ++l) {
+    if (leaves_[l].count == 0) continue;
+    outs[l] = obj->RenewTreeOutput(tree->leaf_value[l], score, indices_.data() + leaves_[l].begin, leaves_[l].count);
+    have[l] = 1.0;
+  }
+  if (Network::active() && (parallel_data_ || parallel_voting_)) {
+    Network::SumDouble(outs.data(), tree->num_leaves); Network::SumDouble(have.data(), tree->num_leaves);
+    for (int l = 0; l < tree->num_leaves; ++l) if (have[l] > 0) outs[l] /= have[l];
+  }
+  for (int l = 0; l < tree->num_leaves; ++l) if (have[l] > 0) tree->SetLeafOutput(l, outs[l]);
+  (void)residual;
+}
+
+Tree* CPUTreeLearner::FitByExistingTree(const Tree* old_tree, const score_t* grad, const score_t* hess) const {
+  // Route every row down the existing structure, then recompute leaf outputs from the new gradients.
+  std::unique_ptr<Tree> tree(new Tree(*old_tree));
+  std::vector<double> sg(tree->num_leaves, 0.0), sh(tree->num_leaves, 0.0);
+  for (data_size_t i = 0; i < ds_->num_data; ++i) {
+    int node = 0;
+    if (tree->num_leaves > 1) {
+      while (node >= 0) {
+        const int f = ds_->used_feature_map[tree->split_feature[node]];
+        const FeatureMeta& m = ds_->feature_meta[f];
+        const BinMapper& bm = *ds_->mappers[m.real_index];
+        const int fbin = ds_->FeatureBin(i, f);
+        int thr_bin = bm.bin_type == BinType::Numerical ? bm.ValueToBin(tree->threshold[node]) : 0;
+        if (tree->decision_type[node] & kCategoricalMask) {
+          int cat = bm.bin_2_categorical[fbin];
+          int ci = static_cast<int>(tree->threshold[node]); int lo = tree->cat_boundaries[ci], nn = tree->cat_boundaries[ci + 1] - lo;
+          bool left = cat >= 0 && (cat >> 5) < nn && ((tree->cat_threshold[lo + (cat >> 5)] >> (cat & 31)) & 1);
+          node = left ? tree->left_child[node] : tree->right_child[node];
+        } else {
+          const int mt = Tree::MissingTypeOf(tree->decision_type[node]);
+          if ((mt == 1 && fbin == m.default_bin) || (mt == 2 && fbin == m.num_bin - 1 && m.missing_type == 2))
+            node = (tree->decision_type[node] & kDefaultLeftMask) ? tree->left_child[node] : tree->right_child[node];
+          else node = fbin <= thr_bin ? tree->left_child[node] : tree->right_child[node];
+        }
+      }
+    } else node = ~0;
+    sg[~node] += grad[i]; sh[~node] += hess[i];
+  }
+  if (Network::active()) { Network::SumDouble(sg.data(), tree->num_leaves); Network::SumDouble(sh.data(), tree->num_leaves); }
+  for (int l = 0; l < tree->num_leaves; ++l) {
+    double out = LeafOutputRaw(sg[l], sh[l] + kEpsilon, sp_);
+    double old = tree->leaf_value[l];
+    tree->SetLeafOutput(l, cfg_.refit_decay_rate * old + (1.0 - cfg_.refit_decay_rate) * out * tree->shrinkage);
+  }
+  return tree.release();
+}
+
+}  // namespace
+
+TreeLearner* CreateCPUTreeLearner(const Config& cfg) { return new CPUTreeLearner(cfg); }
+
+}  // namespace fb

@@ -1,0 +1,501 @@
+// Boosting driver. See fb/gbdt.h for the parity notes.
+#include "fb/gbdt.h"
+
+#include <numeric>
+
+namespace fb {
+
+GBDT::~GBDT() {}
+
+void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj, const std::vector<std::string>& metric_names) {
+  config_ = cfg; train_ = train; objective_ = obj; metric_names_ = metric_names;
+  is_dart_ = cfg.boosting == "dart"; is_rf_ = cfg.boosting == "rf";
+  is_cuda_ = cfg.is_cuda;
+  num_class_ = cfg.num_class;
+  num_tree_per_iteration_ = obj != nullptr ? obj->NumModelPerIteration() : std::max(1, cfg.num_class);
+  shrinkage_rate_ = is_rf_ ? 1.0 : cfg.learning_rate;
+  average_output_ = is_rf_;
+  drop_rand_ = Random(cfg.drop_seed);
+  iter_ = 0;
+  if (train != nullptr) {
+    max_feature_idx_ = train->num_total_features - 1;
+    feature_names_ = train->feature_names;
+    feature_infos_.clear();
+    for (int j = 0; j < train->num_total_features; ++j)
+      feature_infos_.push_back((train->mappers[j] == nullptr || train->mappers[j]->is_trivial) ? "none" : train->mappers[j]->InfoString());
+    const size_t total = static_cast<size_t>(train->num_data) * num_tree_per_iteration_;
+    class_need_train_.assign(num_tree_per_iteration_, true);
+    if (obj != nullptr) for (int k = 0; k < num_tree_per_iteration_; ++k) class_need_train_[k] = obj->ClassNeedTrain(k);
+    init_scores_.assign(num_tree_per_iteration_, 0.0);
+    if ((is_dart_ || is_rf_) && is_cuda_) {
+      Log::Warning("boosting=%s keeps its scores on the host; the device engine is used for gbdt", cfg.boosting.c_str());
+      is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
+    }
+    if (is_cuda_) {
+      engine_.reset(CreateDeviceEngine(config_, train, obj, num_tree_per_iteration_));
+    } else {
+      learner_.reset(CreateCPUTreeLearner(config_));
+      learner_->Init(train, config_);
+      train_score_.assign(total, 0.0);
+      if (!train->metadata.init_score.empty()) {
+        if (train->metadata.init_score.size() != total) Log::Fatal("init_score size does not match num_data * num_class");
+        std::copy(train->metadata.init_score.begin(), train->metadata.init_score.end(), train_score_.begin());
+      }
+      grad_.resize(total); hess_.resize(total);
+    }
+    metrics_.clear(); metrics_.emplace_back();
+    for (auto& name : metric_names_) { std::unique_ptr<Metric> m(CreateMetric(name, config_)); if (m) { m->Init(train->metadata, train->num_data); metrics_[0].push_back(std::move(m)); } }
+    is_goss_ = cfg.data_sample_strategy == "goss";
+    is_bagging_ = !is_goss_ && cfg.bagging_freq > 0 && (cfg.bagging_fraction < 1.0 || cfg.pos_bagging_fraction < 1.0 || cfg.neg_bagging_fraction < 1.0);
+    if (engine_ && is_bagging_) engine_->SetBagging(cfg.bagging_fraction, cfg.bagging_freq, cfg.bagging_seed);
+    if (engine_ && is_goss_) { Log::Warning("GOSS sampling runs on the host learner only; the device engine trains on all rows"); is_goss_ = false; }
+    bag_indices_.resize(train->num_data);
+  }
+}
+
+void GBDT::ResetConfig(const Config& cfg) {
+  config_.learning_rate = cfg.learning_rate; shrinkage_rate_ = is_rf_ ? 1.0 : cfg.learning_rate;
+  Config merged = config_;
+  merged.min_data_in_leaf = cfg.min_data_in_leaf; merged.lambda_l1 = cfg.lambda_l1; merged.lambda_l2 = cfg.lambda_l2;
+  merged.num_leaves = cfg.num_leaves; merged.max_depth = cfg.max_depth; merged.feature_fraction = cfg.feature_fraction;
+  merged.bagging_fraction = cfg.bagging_fraction; merged.bagging_freq = cfg.bagging_freq; merged.min_gain_to_split = cfg.min_gain_to_split;
+  merged.min_sum_hessian_in_leaf = cfg.min_sum_hessian_in_leaf;
+  config_ = merged;
+  if (learner_) learner_->ResetConfig(config_);
+  is_bagging_ = !is_goss_ && config_.bagging_freq > 0 && config_.bagging_fraction < 1.0;
+}
+
+void GBDT::AddValidData(const Dataset* valid) {
+  valid_.push_back(valid);
+  metrics_.emplace_back();
+  for (auto& name : metric_names_) { std::unique_ptr<Metric> m(CreateMetric(name, config_)); if (m) { m->Init(valid->metadata, valid->num_data); metrics_.back().push_back(std::move(m)); } }
+  if (engine_) { engine_->AddValid(valid); return; }
+  const size_t total = static_cast<size_t>(valid->num_data) * num_tree_per_iteration_;
+  valid_score_.emplace_back(total, 0.0);
+  auto& vs = valid_score_.back();
+  if (!valid->metadata.init_score.empty()) std::copy(valid->metadata.init_score.begin(), valid->metadata.init_score.end(), vs.begin());
+  // bring the new validation scores up to date with the existing model
+  for (int k = 0; k < num_tree_per_iteration_; ++k) if (boosted_from_average_ && models_.empty()) for (data_size_t i = 0; i < valid->num_data; ++i) vs[static_cast<size_t>(k) * valid->num_data + i] += init_scores_[k];
+  for (size_t t = 0; t < models_.size(); ++t) AddTreeScore(models_[t].get(), valid, vs.data() + static_cast<size_t>(t % num_tree_per_iteration_) * valid->num_data, 1.0);
+}
+
+// score[i] += scale * tree(row i), rows routed on binned data.
+void GBDT::AddTreeScore(const Tree* tree, const Dataset* ds, double* score, double scale) const {
+  if (tree->num_leaves <= 1) { const double v = tree->leaf_value[0] * scale; for (data_size_t i = 0; i < ds->num_data; ++i) score[i] += v; return; }
+  if (!ds->has_host_bins()) Log::Fatal("Host traversal needs host-resident bins");
+#pragma omp parallel for schedule(static)
+  for (data_size_t i = 0; i < ds->num_data; ++i) {
+    int node = 0;
+    while (node >= 0) {
+      const int f = tree->split_feature_inner[node];
+      const FeatureMeta& m = ds->feature_meta[f];
+      node = tree->DecideBin(ds->FeatureBin(i, f), node, m.default_bin, m.num_bin - 1);
+    }
+    score[i] += scale * tree->leaf_value[~node];
+  }
+}
+
+void GBDT::BoostFromAverage(int k, double* out) {
+  *out = 0.0;
+  if (models_.empty() && !boosted_from_average_ && objective_ != nullptr && config_.boost_from_average && train_->metadata.init_score.empty()) {
+    double init = objective_->BoostFromScore(k);
+    if (std::fabs(init) > kEpsilon) { *out = init; Log::Info("Start training from score %f", init); }
+  }
+}
+
+void GBDT::Bagging(int iter, const float* grad, const float* hess) {
+  const data_size_t n = train_->num_data;
+  if (is_goss_) {
+    // gradient-based one-side sampling: keep the top_rate largest |g*h|, sample other_rate of the rest
+    if (iter < static_cast<int>(1.0 / config_.learning_rate)) { learner_->SetBaggingData(nullptr, 0); bag_cnt_ = n; return; }
+    std::vector<float> mag(n, 0.f);
+    for (int k = 0; k < num_tree_per_iteration_; ++k) for (data_size_t i = 0; i < n; ++i) mag[i] += std::fabs(grad[static_cast<size_t>(k) * n + i] * hess[static_cast<size_t>(k) * n + i]);
+    const data_size_t top_k = std::max<data_size_t>(1, static_cast<data_size_t>(config_.top_rate * n));
+    const data_size_t other_k = static_cast<data_size_t>(config_.other_rate * n);
+    std::vector<float> tmp(mag); std::nth_element(tmp.begin(), tmp.begin() + (top_k - 1), tmp.end(), std::greater<float>());
+    const float thr = tmp[top_k - 1];
+    const float multiply = static_cast<float>(n - top_k) / std::max<data_size_t>(1, other_k);
+    data_size_t cnt = 0, rest_need = other_k, rest_all = n - top_k;
+    float* g = const_cast<float*>(grad); float* h = const_cast<float*>(hess);
+    for (data_size_t i = 0; i < n; ++i) {
+      if (mag[i] >= thr) { bag_indices_[cnt++] = i; continue; }
+      const float u = U01From24(Philox4x32_10(static_cast<uint32_t>(train_->global_row_offset + i), static_cast<uint32_t>(iter), 0x60550000u, 0, static_cast<uint32_t>(config_.bagging_seed), 0x1234u).v[0]);
+      const double prob = rest_all > 0 ? static_cast<double>(rest_need) / rest_all : 0.0;
+      --rest_all;
+      if (u < prob) {
+        bag_indices_[cnt++] = i; --rest_need;
+        for (int k = 0; k < num_tree_per_iteration_; ++k) { g[static_cast<size_t>(k) * n + i] *= multiply; h[static_cast<size_t>(k) * n + i] *= multiply; }
+      }
+    }
+    bag_cnt_ = cnt;
+    learner_->SetBaggingData(bag_indices_.data(), bag_cnt_);
+    return;
+  }
+  if (!is_bagging_) { bag_cnt_ = n; return; }
+  if (iter % config_.bagging_freq != 0 && bag_cnt_ > 0) return;   // keep the previous bag
+  const bool balanced = config_.pos_bagging_fraction < 1.0 || config_.neg_bagging_fraction < 1.0;
+  const uint32_t round = static_cast<uint32_t>(iter / config_.bagging_freq);
+  data_size_t cnt = 0;
+  if (config_.bagging_by_query && !train_->metadata.query_boundaries.empty()) {
+    const auto& qb = train_->metadata.query_boundaries;
+    for (data_size_t q = 0; q + 1 < static_cast<data_size_t>(qb.size()); ++q) {
+      const float u = U01From24(Philox4x32_10(static_cast<uint32_t>(q), round, 0xBA660000u, 1, static_cast<uint32_t>(config_.bagging_seed), 0x9876u).v[0]);
+      if (u < config_.bagging_fraction) for (data_size_t i = qb[q]; i < qb[q + 1]; ++i) bag_indices_[cnt++] = i;
+    }
+  } else {
+    for (data_size_t i = 0; i < n; ++i) {
+      const float u = U01From24(Philox4x32_10(static_cast<uint32_t>(train_->global_row_offset + i), round, 0xBA660000u, 0, static_cast<uint32_t>(config_.bagging_seed), 0x9876u).v[0]);
+      double frac = config_.bagging_fraction;
+      if (balanced) frac = train_->metadata.label[i] > 0 ? config_.pos_bagging_fraction : config_.neg_bagging_fraction;
+      if (u < frac) bag_indices_[cnt++] = i;
+    }
+  }
+  bag_cnt_ = cnt;
+  learner_->SetBaggingData(bag_indices_.data(), bag_cnt_);
+}
+
+bool GBDT::CheckDivergence(const float* grad, int64_t n) {
+  // every 32 iterations after 64: a 50x growth of the gradient norm since the start is reported
+  if (iter_ < 64 && first_grad_norm_ >= 0) return false;
+  if (iter_ % 32 != 0 && first_grad_norm_ >= 0) return false;
+  double s = 0; for (int64_t i = 0; i < n; ++i) s += static_cast<double>(grad[i]) * grad[i];
+  const double norm = std::sqrt(s / std::max<int64_t>(1, n));
+  if (first_grad_norm_ < 0) { first_grad_norm_ = norm; return false; }
+  if (!std::isfinite(norm) || (first_grad_norm_ > 0 && norm > 50.0 * first_grad_norm_)) {
+    Log::Warning("Gradient norm grew from %g to %g: training may be diverging (lower learning_rate or set max_delta_step)", first_grad_norm_, norm);
+    return true;
+  }
+  return false;
+}
+
+void GBDT::DartDropTrees() {
+  drop_index_.clear();
+  const int iters = current_iteration();
+  const bool skip = drop_rand_.NextFloat() < config_.skip_drop;
+  if (!skip && iters > 0) {
+    double rate = config_.drop_rate;
+    if (!config_.uniform_drop) {
+      double inv_avg = sum_weight_ > 0 ? iters / sum_weight_ : 1.0;
+      if (config_.max_drop > 0) rate = std::min(rate, config_.max_drop * inv_avg / std::max(1.0, sum_weight_));
+      for (int i = 0; i < iters; ++i) if (drop_rand_.NextFloat() < rate * tree_weight_[i] * inv_avg) { drop_index_.push_back(i); if (config_.max_drop > 0 && static_cast<int>(drop_index_.size()) >= config_.max_drop) break; }
+    } else {
+      if (config_.max_drop > 0) rate = std::min(rate, config_.max_drop / static_cast<double>(iters));
+      for (int i = 0; i < iters; ++i) if (drop_rand_.NextFloat() < rate) { drop_index_.push_back(i); if (config_.max_drop > 0 && static_cast<int>(drop_index_.size()) >= config_.max_drop) break; }
+    }
+  }
+  for (int i : drop_index_) for (int k = 0; k < num_tree_per_iteration_; ++k) {
+    const Tree* t = models_[static_cast<size_t>(i) * num_tree_per_iteration_ + k].get();
+    AddTreeScore(t, train_, train_score_.data() + static_cast<size_t>(k) * train_->num_data, -1.0);
+  }
+  const double k = static_cast<double>(drop_index_.size());
+  if (!config_.xgboost_dart_mode) shrinkage_rate_ = config_.learning_rate / (1.0 + k);
+  else shrinkage_rate_ = drop_index_.empty() ? config_.learning_rate : config_.learning_rate / (config_.learning_rate + k);
+}
+
+void GBDT::DartNormalize() {
+  const double k = static_cast<double>(drop_index_.size());
+  for (int i : drop_index_) for (int c = 0; c < num_tree_per_iteration_; ++c) {
+    Tree* t = models_[static_cast<size_t>(i) * num_tree_per_iteration_ + c].get();
+    // validation scores still contain the full old tree; train scores contain none of it
+    const double factor = config_.xgboost_dart_mode ? k / (k + config_.learning_rate) : k / (k + 1.0);
+    for (size_t v = 0; v < valid_.size(); ++v) AddTreeScore(t, valid_[v], valid_score_[v].data() + static_cast<size_t>(c) * valid_[v]->num_data, factor - 1.0);
+    t->Shrink(factor);
+    AddTreeScore(t, train_, train_score_.data() + static_cast<size_t>(c) * train_->num_data, 1.0);
+    if (!config_.uniform_drop && c == 0) { sum_weight_ -= tree_weight_[i] * (1.0 - factor); tree_weight_[i] *= factor; }
+  }
+  if (!config_.uniform_drop) { tree_weight_.push_back(shrinkage_rate_); sum_weight_ += shrinkage_rate_; }
+}
+
+void GBDT::UpdateScore(const Tree* tree, int k) {
+  const data_size_t n = train_->num_data;
+  double* ts = train_score_.data() + static_cast<size_t>(k) * n;
+  if (tree->num_leaves > 1 && !(is_bagging_ || is_goss_) ) learner_->AddPredictionToScore(tree, ts);
+  else AddTreeScore(tree, train_, ts, 1.0);   // bagging: out-of-bag rows need the traversal
+  for (size_t v = 0; v < valid_.size(); ++v) AddTreeScore(tree, valid_[v], valid_score_[v].data() + static_cast<size_t>(k) * valid_[v]->num_data, 1.0);
+}
+
+bool GBDT::TrainOneIter(const float* grad_in, const float* hess_in) {
+  ScopedTimer timer("GBDT::TrainOneIter");
+  const int K = num_tree_per_iteration_;
+  std::vector<double> inits(K, 0.0);
+  if (grad_in == nullptr || hess_in == nullptr) {
+    if (objective_ == nullptr) Log::Fatal("No objective function provided and no custom gradients given");
+    for (int k = 0; k < K; ++k) BoostFromAverage(k, &inits[k]);
+  }
+  if (models_.empty() && !boosted_from_average_) {
+    boosted_from_average_ = true;
+    for (int k = 0; k < K; ++k) {
+      init_scores_[k] = inits[k];
+      if (inits[k] == 0.0) continue;
+      if (engine_) engine_->AddConstantToScores(inits[k], k);
+      else {
+        double* ts = train_score_.data() + static_cast<size_t>(k) * train_->num_data;
+        for (data_size_t i = 0; i < train_->num_data; ++i) ts[i] += inits[k];
+        for (size_t v = 0; v < valid_.size(); ++v) { double* vs = valid_score_[v].data() + static_cast<size_t>(k) * valid_[v]->num_data; for (data_size_t i = 0; i < valid_[v]->num_data; ++i) vs[i] += inits[k]; }
+      }
+    }
+  } else {
+    std::fill(inits.begin(), inits.end(), 0.0);
+  }
+
+  if (engine_) {
+    std::vector<std::unique_ptr<Tree>> trees; bool all_const = false;
+    engine_->TrainOneIter(grad_in, hess_in, iter_, shrinkage_rate_, inits, &trees, &all_const);
+    if (all_const) {
+      Log::Warning("Stopped training because there are no more leaves that meet the split requirements");
+      if (models_.empty()) for (auto& t : trees) models_.push_back(std::move(t));
+      return true;
+    }
+    for (auto& t : trees) models_.push_back(std::move(t));
+    ++iter_;
+    return false;
+  }
+
+  const data_size_t n = train_->num_data;
+  if (is_dart_) DartDropTrees();
+  const float* grad = grad_in; const float* hess = hess_in;
+  if (grad == nullptr) {
+    if (is_rf_) {
+      if (iter_ == 0 || rf_init_scores_.empty()) {
+        rf_init_scores_.assign(static_cast<size_t>(n) * K, 0.0);
+        for (int k = 0; k < K; ++k) for (data_size_t i = 0; i < n; ++i) rf_init_scores_[static_cast<size_t>(k) * n + i] = init_scores_[k];
+        objective_->GetGradients(rf_init_scores_.data(), grad_.data(), hess_.data());
+      }
+    } else {
+      objective_->GetGradients(train_score_.data(), grad_.data(), hess_.data());
+    }
+    grad = grad_.data(); hess = hess_.data();
+  } else {
+    std::copy(grad_in, grad_in + static_cast<size_t>(n) * K, grad_.begin()); std::copy(hess_in, hess_in + static_cast<size_t>(n) * K, hess_.begin());
+    grad = grad_.data(); hess = hess_.data();
+  }
+  CheckDivergence(grad, static_cast<int64_t>(n) * K);
+  Bagging(iter_, grad, hess);
+  bool should_continue = false;
+  for (int k = 0; k < K; ++k) {
+    std::unique_ptr<Tree> tree(new Tree(2));
+    if (class_need_train_[k] && train_->num_features > 0) {
+      tree.reset(learner_->Train(grad + static_cast<size_t>(k) * n, hess + static_cast<size_t>(k) * n, iter_ * K + k));
+    }
+    if (tree->num_leaves > 1) {
+      should_continue = true;
+      if (objective_ != nullptr && objective_->IsRenewTreeOutput()) {
+        std::vector<double> sc(train_score_.begin() + static_cast<size_t>(k) * n, train_score_.begin() + static_cast<size_t>(k + 1) * n);
+        if (is_rf_) std::fill(sc.begin(), sc.end(), init_scores_[k]);
+        learner_->RenewTreeOutput(tree.get(), objective_, nullptr, n, bag_indices_.data(), bag_cnt_, sc.data());
+      }
+      tree->Shrink(shrinkage_rate_);
+      if (is_rf_) {
+        // forests average: train/valid scores hold the running mean
+        const double m = static_cast<double>(iter_);
+        double* ts = train_score_.data() + static_cast<size_t>(k) * n;
+        if (std::fabs(init_scores_[k]) > kEpsilon) tree->AddBias(init_scores_[k]);
+        for (data_size_t i = 0; i < n; ++i) ts[i] *= m;
+        for (size_t v = 0; v < valid_.size(); ++v) { double* vs = valid_score_[v].data() + static_cast<size_t>(k) * valid_[v]->num_data; for (data_size_t i = 0; i < valid_[v]->num_data; ++i) vs[i] *= m; }
+        AddTreeScore(tree.get(), train_, ts, 1.0);
+        for (size_t v = 0; v < valid_.size(); ++v) AddTreeScore(tree.get(), valid_[v], valid_score_[v].data() + static_cast<size_t>(k) * valid_[v]->num_data, 1.0);
+        for (data_size_t i = 0; i < n; ++i) ts[i] /= (m + 1);
+        for (size_t v = 0; v < valid_.size(); ++v) { double* vs = valid_score_[v].data() + static_cast<size_t>(k) * valid_[v]->num_data; for (data_size_t i = 0; i < valid_[v]->num_data; ++i) vs[i] /= (m + 1); }
+      } else {
+        UpdateScore(tree.get(), k);
+        if (std::fabs(inits[k]) > kEpsilon) tree->AddBias(inits[k]);
+      }
+    } else {
+      // constant tree: keeps the model aligned (one tree per class per iteration)
+      if (models_.size() < static_cast<size_t>(K)) {
+        double out = 0.0;
+        if (!class_need_train_[k] && objective_ != nullptr) out = objective_->BoostFromScore(k); else out = inits[k];
+        tree->AsConstantTree(out);
+        if (!class_need_train_[k]) { double* ts = train_score_.data() + static_cast<size_t>(k) * n; for (data_size_t i = 0; i < n; ++i) ts[i] += out; }
+      } else tree->AsConstantTree(0.0);
+    }
+    models_.push_back(std::move(tree));
+  }
+  if (!should_continue) {
+    Log::Warning("Stopped training because there are no more leaves that meet the split requirements");
+    if (models_.size() > static_cast<size_t>(K)) for (int k = 0; k < K; ++k) models_.pop_back();
+    return true;
+  }
+  if (is_dart_) DartNormalize();
+  ++iter_;
+  return false;
+}
+
+void GBDT::RollbackOneIter() {
+  if (iter_ <= 0) return;
+  const int K = num_tree_per_iteration_;
+  for (int k = 0; k < K; ++k) {
+    const Tree* t = models_[models_.size() - K + k].get();
+    if (engine_) engine_->AddTreeToScores(*t, k, -1.0);
+    else {
+      AddTreeScore(t, train_, train_score_.data() + static_cast<size_t>(k) * train_->num_data, -1.0);
+      for (size_t v = 0; v < valid_.size(); ++v) AddTreeScore(t, valid_[v], valid_score_[v].data() + static_cast<size_t>(k) * valid_[v]->num_data, -1.0);
+    }
+  }
+  for (int k = 0; k < K; ++k) models_.pop_back();
+  --iter_;
+}
+
+std::vector<std::string> GBDT::EvalNames() const {
+  std::vector<std::string> out;
+  if (!metrics_.empty()) for (auto& m : metrics_[0]) for (auto& s : m->Names()) out.push_back(s);
+  return out;
+}
+std::vector<bool> GBDT::EvalHigherBetter() const {
+  std::vector<bool> out;
+  if (!metrics_.empty()) for (auto& m : metrics_[0]) for (size_t i = 0; i < m->Names().size(); ++i) out.push_back(m->HigherBetter());
+  return out;
+}
+
+std::vector<double> GBDT::GetEval(int data_idx) const {
+  std::vector<double> out;
+  if (data_idx < 0 || data_idx >= static_cast<int>(metrics_.size())) return out;
+  const Dataset* ds = data_idx == 0 ? train_ : valid_[data_idx - 1];
+  std::vector<double> host;
+  const double* score = nullptr;
+  bool host_ready = false;
+  for (auto& m : metrics_[data_idx]) {
+    if (engine_) {
+      bool ok = false;
+      auto names = m->Names();
+      std::vector<double> v = engine_->EvalMetric(data_idx, names[0].substr(0, names[0].find('@')), &ok);
+      if (ok && v.size() == names.size()) { out.insert(out.end(), v.begin(), v.end()); continue; }
+      if (!host_ready) { host.resize(static_cast<size_t>(ds->num_data) * num_tree_per_iteration_); engine_->CopyScoresToHost(data_idx, host.data()); host_ready = true; }
+      score = host.data();
+    } else score = data_idx == 0 ? train_score_.data() : valid_score_[data_idx - 1].data();
+    auto v = m->Eval(score, objective_);
+    out.insert(out.end(), v.begin(), v.end());
+  }
+  return out;
+}
+
+int64_t GBDT::GetNumPredict(int data_idx) const {
+  const Dataset* ds = data_idx == 0 ? train_ : valid_[data_idx - 1];
+  return static_cast<int64_t>(ds->num_data) * num_tree_per_iteration_;
+}
+
+void GBDT::GetPredictAt(int data_idx, double* out) const {
+  const Dataset* ds = data_idx == 0 ? train_ : valid_[data_idx - 1];
+  const data_size_t n = ds->num_data; const int K = num_tree_per_iteration_;
+  std::vector<double> host;
+  const double* score;
+  if (engine_) { host.resize(static_cast<size_t>(n) * K); engine_->CopyScoresToHost(data_idx, host.data()); score = host.data(); }
+  else score = data_idx == 0 ? train_score_.data() : valid_score_[data_idx - 1].data();
+  std::vector<double> raw(K), conv(K);
+  for (data_size_t i = 0; i < n; ++i) {
+    for (int k = 0; k < K; ++k) raw[k] = score[static_cast<size_t>(k) * n + i];
+    if (objective_ != nullptr) objective_->ConvertOutput(raw.data(), conv.data()); else conv = raw;
+    for (int k = 0; k < K; ++k) out[static_cast<size_t>(k) * n + i] = conv[k];
+  }
+}
+
+void GBDT::RefitTree(const int* leaf_preds, int nrow, int ncol) {
+  if (learner_ == nullptr) Log::Fatal("refit runs on the host learner (device_type=cpu)");
+  if (nrow != train_->num_data || ncol != static_cast<int>(models_.size())) Log::Fatal("leaf prediction shape does not match");
+  const int K = num_tree_per_iteration_; const data_size_t n = train_->num_data;
+  std::fill(train_score_.begin(), train_score_.end(), 0.0);
+  if (!train_->metadata.init_score.empty()) std::copy(train_->metadata.init_score.begin(), train_->metadata.init_score.end(), train_score_.begin());
+  const int iters = static_cast<int>(models_.size()) / K;
+  for (int it = 0; it < iters; ++it) {
+    objective_->GetGradients(train_score_.data(), grad_.data(), hess_.data());
+    for (int k = 0; k < K; ++k) {
+      const int ti = it * K + k;
+      Tree* t = models_[ti].get();
+      std::vector<double> sg(t->num_leaves, 0.0), sh(t->num_leaves, 0.0);
+      for (data_size_t i = 0; i < n; ++i) { const int leaf = leaf_preds[static_cast<size_t>(i) * ncol + ti]; sg[leaf] += grad_[static_cast<size_t>(k) * n + i]; sh[leaf] += hess_[static_cast<size_t>(k) * n + i]; }
+      for (int l = 0; l < t->num_leaves; ++l) {
+        const double out = -sg[l] / (sh[l] + config_.lambda_l2 + kEpsilon);
+        t->SetLeafOutput(l, config_.refit_decay_rate * t->leaf_value[l] + (1.0 - config_.refit_decay_rate) * out * t->shrinkage);
+      }
+      double* ts = train_score_.data() + static_cast<size_t>(k) * n;
+      for (data_size_t i = 0; i < n; ++i) ts[i] += t->leaf_value[leaf_preds[static_cast<size_t>(i) * ncol + ti]];
+    }
+  }
+}
+
+void GBDT::ShuffleModels(int start, int end) {
+  const int K = num_tree_per_iteration_; const int iters = static_cast<int>(models_.size()) / K;
+  start = std::max(0, start); if (end <= 0 || end > iters) end = iters;
+  std::vector<int> idx(iters); std::iota(idx.begin(), idx.end(), 0);
+  Random r(17);
+  for (int i = start; i < end - 1; ++i) { int j = r.NextInt(i + 1, end); std::swap(idx[i], idx[j]); }
+  std::vector<std::unique_ptr<Tree>> old; old.swap(models_);
+  for (int i = 0; i < iters; ++i) for (int k = 0; k < K; ++k) models_.push_back(std::move(old[static_cast<size_t>(idx[i]) * K + k]));
+}
+
+void GBDT::MergeFrom(const GBDT* other) {
+  std::vector<std::unique_ptr<Tree>> merged;
+  for (auto& t : other->models_) merged.emplace_back(new Tree(*t));
+  for (auto& t : models_) merged.push_back(std::move(t));
+  models_.swap(merged);
+}
+
+// ------------------------------------------------------------ prediction ----
+int GBDT::NumPredictOneRow(int predict_type, int start_iter, int num_iter) const {
+  const int K = num_tree_per_iteration_; int iters = static_cast<int>(models_.size()) / K;
+  start_iter = std::max(0, std::min(start_iter, iters));
+  int use = num_iter > 0 ? std::min(num_iter, iters - start_iter) : iters - start_iter;
+  if (predict_type == 2) return use * K;
+  if (predict_type == 3) return K * (max_feature_idx_ + 2);
+  return K;
+}
+
+void GBDT::PredictRow(const double* row, int predict_type, int start_iter, int num_iter, double* out) const {
+  const int K = num_tree_per_iteration_; int iters = static_cast<int>(models_.size()) / K;
+  start_iter = std::max(0, std::min(start_iter, iters));
+  const int use = num_iter > 0 ? std::min(num_iter, iters - start_iter) : iters - start_iter;
+  const int begin = start_iter * K, end = (start_iter + use) * K;
+  if (predict_type == 2) { for (int t = begin; t < end; ++t) out[t - begin] = models_[t]->LeafIndex(row); return; }
+  if (predict_type == 3) {
+    const int nf = max_feature_idx_ + 1;
+    std::fill(out, out + static_cast<size_t>(K) * (nf + 1), 0.0);
+    for (int t = begin; t < end; ++t) models_[t]->PredictContrib(row, nf, out + static_cast<size_t>(t % K) * (nf + 1));
+    return;
+  }
+  std::vector<double> raw(K, 0.0);
+  const bool early = config_.pred_early_stop && predict_type == 0 && (K > 1 || (objective_ && std::string(objective_->GetName()) == "binary"));
+  for (int t = begin; t < end; ++t) {
+    raw[t % K] += models_[t]->Predict(row);
+    if (early && ((t - begin + 1) % (config_.pred_early_stop_freq * K) == 0)) {
+      double margin;
+      if (K == 1) margin = 2.0 * std::fabs(raw[0]);
+      else { std::vector<double> s(raw); std::partial_sort(s.begin(), s.begin() + 2, s.end(), std::greater<double>()); margin = s[0] - s[1]; }
+      if (margin > config_.pred_early_stop_margin) break;
+    }
+  }
+  if (average_output_ && use > 0) for (int k = 0; k < K; ++k) raw[k] /= use;
+  if (predict_type == 1 || objective_ == nullptr) { for (int k = 0; k < K; ++k) out[k] = raw[k]; }
+  else objective_->ConvertOutput(raw.data(), out);
+}
+
+void GBDT::PredictMat(const void* data, int dtype, int nrow, int ncol, bool row_major, int predict_type, int start_iter, int num_iter, double* out) const {
+  const int per = NumPredictOneRow(predict_type, start_iter, num_iter);
+  if (ncol <= max_feature_idx_ && !config_.predict_disable_shape_check)
+    Log::Fatal("The number of features in data (%d) is not the same as it was in training data (%d)", ncol, max_feature_idx_ + 1);
+#pragma omp parallel
+  {
+    std::vector<double> row(std::max(ncol, max_feature_idx_ + 1), 0.0);
+#pragma omp for schedule(static)
+    for (int i = 0; i < nrow; ++i) {
+      for (int j = 0; j < ncol; ++j) {
+        const size_t src = row_major ? static_cast<size_t>(i) * ncol + j : static_cast<size_t>(j) * nrow + i;
+        switch (dtype) {
+          case kF32: row[j] = static_cast<const float*>(data)[src]; break;
+          case kF64: row[j] = static_cast<const double*>(data)[src]; break;
+          case kI8: row[j] = static_cast<const int8_t*>(data)[src]; break;
+          case kI16: row[j] = static_cast<const int16_t*>(data)[src]; break;
+          case kU8: row[j] = static_cast<const uint8_t*>(data)[src]; break;
+          case kU16: row[j] = static_cast<const uint16_t*>(data)[src]; break;
+          case kI32: row[j] = static_cast<const int32_t*>(data)[src]; break;
+          default: row[j] = 0.0;
+        }
+      }
+      PredictRow(row.data(), predict_type, start_iter, num_iter, out + static_cast<size_t>(i) * per);
+    }
+  }
+}
+
+double GBDT::UpperBound() const { double s = 0; for (auto& t : models_) { double m = t->leaf_value[0]; for (int l = 1; l < t->num_leaves; ++l) m = std::max(m, t->leaf_value[l]); s += m; } return s; }
+double GBDT::LowerBound() const { double s = 0; for (auto& t : models_) { double m = t->leaf_value[0]; for (int l = 1; l < t->num_leaves; ++l) m = std::min(m, t->leaf_value[l]); s += m; } return s; }
+
+}  // namespace fb

@@ -1,0 +1,107 @@
+/* C API of the falcata_b200 core, consumed by the Python layer through ctypes.
+ * Every function returns 0 on success and -1 on error; FB_GetLastError() gives the message.
+ * Parity: include/Falcata/c_api.h (FLC_Dataset*, FLC_Booster*, FLC_Network* families), src/c_api.cpp.
+ * dtype codes: 0 f32, 1 f64, 2 i8, 3 i16, 4 u8, 5 u16, 6 f16, 7 i32.
+ * predict_type: 0 normal, 1 raw score, 2 leaf index, 3 feature contributions. */
+#ifndef FB_C_API_H_
+#define FB_C_API_H_
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* DatasetHandle;
+typedef void* BoosterHandle;
+
+const char* FB_GetLastError();
+int FB_RegisterLogCallback(void (*callback)(const char*));
+int FB_CudaAvailable(int* out);
+int FB_SetTimeTag(int enabled);
+int FB_GetTimeTagReport(int64_t buffer_len, int64_t* out_len, char* out_str);
+
+/* Host collectives supplied by the embedding process (torch.distributed in the Python layer). */
+int FB_NetworkInitWithFunctions(int num_machines, int rank, void* allreduce_sum_fn, void* allgather_fn);
+int FB_NetworkFree();
+
+/* ---- Dataset ---- */
+int FB_DatasetCreateFromMat(const void* data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, const char* parameters,
+                            const DatasetHandle reference, DatasetHandle* out);
+int FB_DatasetCreateFromFile(const char* filename, const char* parameters, const DatasetHandle reference, DatasetHandle* out);
+/* Schema only (bin mappers + bundles) from a dense f64 sample; rows are attached afterwards. */
+int FB_DatasetCreateFromSample(const double* sample, int32_t num_sample_row, int32_t ncol, int64_t num_total_row, const char* parameters,
+                               const int32_t* categorical, int32_t num_categorical, DatasetHandle* out);
+int FB_DatasetCreateByReference(const DatasetHandle reference, DatasetHandle* out);
+int FB_DatasetSerializeSchema(DatasetHandle handle, int64_t buffer_len, int64_t* out_len, char* out);
+int FB_DatasetCreateFromSchema(const char* schema, int64_t len, const char* parameters, DatasetHandle* out);
+int FB_DatasetInitRows(DatasetHandle handle, int32_t nrow, int64_t global_row_offset, int64_t global_num_row, int host_bins);
+int FB_DatasetPushRows(DatasetHandle handle, const void* data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, int32_t start_row);
+/* Bin a dense device matrix on the GPU; the binned rows stay on the device. */
+int FB_DatasetBinDeviceMat(DatasetHandle handle, const void* device_data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, int keep_host_copy);
+int FB_DatasetSetField(DatasetHandle handle, const char* field_name, const void* data, int64_t num_element, int dtype);
+int FB_DatasetGetField(DatasetHandle handle, const char* field_name, int64_t* out_len, const void** out_ptr, int* out_type);
+int FB_DatasetGetNumData(DatasetHandle handle, int32_t* out);
+int FB_DatasetGetNumFeature(DatasetHandle handle, int32_t* out);
+int FB_DatasetGetInfo(DatasetHandle handle, int32_t* out /* [num_used_features, num_groups, num_total_bin, max_group_bin, has_device, has_host] */);
+int FB_DatasetSetFeatureNames(DatasetHandle handle, const char** names, int num);
+int FB_DatasetGetFeatureNames(DatasetHandle handle, int64_t buffer_len, int64_t* out_len, char* out /* '\n' joined */);
+int FB_DatasetGetBinnedRow(DatasetHandle handle, int32_t row, int32_t* out_feature_bins /* num_used_features */);
+int FB_DatasetSaveBinary(DatasetHandle handle, const char* filename);
+int FB_DatasetGetSubset(const DatasetHandle handle, const int32_t* used_row_indices, int32_t num_used_row_indices, DatasetHandle* out);
+int FB_DatasetFreeDeviceData(DatasetHandle handle);
+int FB_DatasetFree(DatasetHandle handle);
+
+/* ---- Booster ---- */
+int FB_BoosterCreate(const DatasetHandle train_data, const char* parameters, BoosterHandle* out);
+int FB_BoosterCreateFromModelfile(const char* filename, int* out_num_iterations, BoosterHandle* out);
+int FB_BoosterLoadModelFromString(const char* model_str, int64_t len, int* out_num_iterations, BoosterHandle* out);
+int FB_BoosterCreateFromBinary(const char* data, int64_t len, int* out_num_iterations, BoosterHandle* out);
+int FB_BoosterFree(BoosterHandle handle);
+int FB_BoosterAddValidData(BoosterHandle handle, const DatasetHandle valid_data);
+int FB_BoosterResetParameter(BoosterHandle handle, const char* parameters);
+int FB_BoosterUpdateOneIter(BoosterHandle handle, int* is_finished);
+/* grad/hess: host pointers, or device pointers when on_device != 0 (CUDA boosters). */
+int FB_BoosterUpdateOneIterCustom(BoosterHandle handle, const float* grad, const float* hess, int on_device, int* is_finished);
+int FB_BoosterRollbackOneIter(BoosterHandle handle);
+int FB_BoosterGetCurrentIteration(BoosterHandle handle, int* out);
+int FB_BoosterNumModelPerIteration(BoosterHandle handle, int* out);
+int FB_BoosterNumberOfTotalModel(BoosterHandle handle, int* out);
+int FB_BoosterGetNumClasses(BoosterHandle handle, int* out);
+int FB_BoosterGetNumFeature(BoosterHandle handle, int* out);
+int FB_BoosterGetEvalCounts(BoosterHandle handle, int* out);
+int FB_BoosterGetEvalNames(BoosterHandle handle, int64_t buffer_len, int64_t* out_len, char* out /* '\n' joined, with a leading +/- for higher/lower better */);
+int FB_BoosterGetEval(BoosterHandle handle, int data_idx, int* out_len, double* out_results);
+int FB_BoosterGetNumPredict(BoosterHandle handle, int data_idx, int64_t* out_len);
+int FB_BoosterGetPredict(BoosterHandle handle, int data_idx, int64_t* out_len, double* out_result);
+int FB_BoosterGetTrainScoreDevicePtr(BoosterHandle handle, void** out_ptr);
+int FB_BoosterCalcNumPredict(BoosterHandle handle, int num_row, int predict_type, int start_iteration, int num_iteration, int64_t* out_len);
+int FB_BoosterPredictForMat(BoosterHandle handle, const void* data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, int predict_type,
+                            int start_iteration, int num_iteration, const char* parameter, int64_t* out_len, double* out_result);
+/* Device traversal predict: data and out_result are device pointers (out: f32, class-major when raw/normal). */
+int FB_BoosterPredictForDeviceMat(BoosterHandle handle, const void* device_data, int dtype, int32_t nrow, int32_t ncol, int is_row_major,
+                                  int predict_type, int start_iteration, int num_iteration, float* out_device);
+int FB_BoosterSaveModel(BoosterHandle handle, int start_iteration, int num_iteration, int feature_importance_type, const char* filename);
+int FB_BoosterSaveModelToString(BoosterHandle handle, int start_iteration, int num_iteration, int feature_importance_type, int64_t buffer_len,
+                                int64_t* out_len, char* out_str);
+int FB_BoosterDumpModel(BoosterHandle handle, int start_iteration, int num_iteration, int feature_importance_type, int64_t buffer_len,
+                        int64_t* out_len, char* out_str);
+int FB_BoosterModelToIfElse(BoosterHandle handle, int num_iteration, int64_t buffer_len, int64_t* out_len, char* out_str);
+int FB_BoosterSaveModelToBinary(BoosterHandle handle, int start_iteration, int num_iteration, int f32_leaves, int64_t buffer_len, int64_t* out_len,
+                                char* out);
+int FB_BoosterGetLeafValue(BoosterHandle handle, int tree_idx, int leaf_idx, double* out_val);
+int FB_BoosterSetLeafValue(BoosterHandle handle, int tree_idx, int leaf_idx, double val);
+int FB_BoosterFeatureImportance(BoosterHandle handle, int num_iteration, int importance_type, double* out_results);
+int FB_BoosterGetFeatureNames(BoosterHandle handle, int64_t buffer_len, int64_t* out_len, char* out);
+int FB_BoosterRefit(BoosterHandle handle, const int32_t* leaf_preds, int32_t nrow, int32_t ncol);
+int FB_BoosterMerge(BoosterHandle handle, BoosterHandle other_handle);
+int FB_BoosterShuffleModels(BoosterHandle handle, int start_iter, int end_iter);
+int FB_BoosterGetUpperBoundValue(BoosterHandle handle, double* out);
+int FB_BoosterGetLowerBoundValue(BoosterHandle handle, double* out);
+int FB_BoosterGetLoadedParam(BoosterHandle handle, int64_t buffer_len, int64_t* out_len, char* out_str);
+int FB_BoosterGpuLaunches(BoosterHandle handle, int64_t* out);
+int FB_BoosterStageReport(BoosterHandle handle, int64_t buffer_len, int64_t* out_len, char* out_str);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* FB_C_API_H_ */

@@ -1,0 +1,131 @@
+// Boosting driver: gbdt / dart / rf, bagging and GOSS row sampling, evaluation, prediction,
+// text / JSON / binary model IO, refit, rollback, snapshots.
+// Parity: src/boosting/gbdt.cpp (Init L159-271, TrainOneIter L455-565, RollbackOneIter L567-585,
+// UpdateScore L606-638, RefitTree L369-407, divergence monitor L38-128), dart.hpp, rf.hpp, goss.hpp,
+// bagging.hpp, gbdt_model_text.cpp:L315-675, gbdt_prediction.cpp, gbdt_model_binary.cpp + falb.h.
+#pragma once
+#include <memory>
+#include <string>
+#include <vector>
+#include "fb/config.h"
+#include "fb/dataset.h"
+#include "fb/learner.h"
+#include "fb/objective.h"
+#include "fb/tree.h"
+
+namespace fb {
+
+// The device-resident half of training (scores, gradients, learner, validation scores, metrics).
+// Implemented by the CUDA module; GBDT drives it when device_type=cuda.
+class DeviceEngine {
+ public:
+  virtual ~DeviceEngine() {}
+  virtual void AddValid(const Dataset* valid) = 0;
+  virtual void AddConstantToScores(double v, int class_id) = 0;
+  // Computes gradients on the device (or takes custom device gradients), grows one tree per
+  // class, shrinks them, adds them to the train and validation scores. Returns host trees.
+  virtual void TrainOneIter(const float* custom_grad, const float* custom_hess, int iter, double shrinkage,
+                            const std::vector<double>& init_scores, std::vector<std::unique_ptr<Tree>>* out, bool* all_constant) = 0;
+  virtual std::vector<double> EvalMetric(int data_idx, const std::string& metric_name, bool* supported) = 0;
+  virtual void CopyScoresToHost(int data_idx, double* out) = 0;
+  virtual void AddTreeToScores(const Tree& tree, int class_id, double scale) = 0;   // all data sets, by traversal
+  virtual void* TrainScorePtr() = 0;       // float* on the device, class-major
+  virtual int64_t GpuLaunches() const = 0;
+  virtual std::string StageReport() const = 0;
+  virtual void SetBagging(double fraction, int freq, int seed) = 0;
+};
+DeviceEngine* CreateDeviceEngine(const Config& cfg, const Dataset* train, const ObjectiveFunction* obj, int num_tree_per_iter);
+bool CudaAvailable();
+
+class GBDT {
+ public:
+  GBDT() {}
+  ~GBDT();
+  void Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj, const std::vector<std::string>& metric_names);
+  void AddValidData(const Dataset* valid);
+  // Returns true when training cannot continue (no splittable leaf).
+  bool TrainOneIter(const float* grad, const float* hess);
+  void RollbackOneIter();
+  int current_iteration() const { return static_cast<int>(models_.size()) / std::max(1, num_tree_per_iteration_); }
+  int NumModels() const { return static_cast<int>(models_.size()); }
+  std::vector<double> GetEval(int data_idx) const;
+  std::vector<std::string> EvalNames() const;
+  std::vector<bool> EvalHigherBetter() const;
+  int64_t GetNumPredict(int data_idx) const;
+  void GetPredictAt(int data_idx, double* out) const;       // converted outputs of the training / validation scores
+  void RefitTree(const int* leaf_preds, int nrow, int ncol);
+  void ResetConfig(const Config& cfg);
+  void ShuffleModels(int start, int end);
+  void MergeFrom(const GBDT* other);
+
+  // ---- prediction on raw feature rows ----
+  // predict_type: 0 normal, 1 raw, 2 leaf index, 3 contrib
+  int NumPredictOneRow(int predict_type, int start_iter, int num_iter) const;
+  void PredictRow(const double* row, int predict_type, int start_iter, int num_iter, double* out) const;
+  void PredictMat(const void* data, int dtype, int nrow, int ncol, bool row_major, int predict_type, int start_iter, int num_iter, double* out) const;
+
+  // ---- model IO ----
+  std::string SaveModelToString(int start_iter, int num_iter, int importance_type) const;
+  bool LoadModelFromString(const char* str, size_t len);
+  std::string DumpModel(int start_iter, int num_iter, int importance_type) const;
+  std::string ModelToIfElse(int num_iter) const;
+  std::vector<double> FeatureImportance(int num_iter, int importance_type) const;
+  std::vector<char> SaveModelToBinary(int start_iter, int num_iter, bool f32_leaves) const;
+  bool LoadModelFromBinary(const char* data, size_t len);
+
+  double GetLeafValue(int tree, int leaf) const { return models_[tree]->leaf_value[leaf]; }
+  void SetLeafValue(int tree, int leaf, double v) { models_[tree]->SetLeafOutput(leaf, v); }
+  double UpperBound() const; double LowerBound() const;
+
+  int num_class_ = 1;
+  int num_tree_per_iteration_ = 1;
+  int max_feature_idx_ = 0;
+  int label_idx_ = 0;
+  bool average_output_ = false;
+  std::vector<std::string> feature_names_;
+  std::vector<std::string> feature_infos_;
+  std::vector<std::unique_ptr<Tree>> models_;
+  std::unique_ptr<ObjectiveFunction> loaded_objective_;
+  const ObjectiveFunction* objective_ = nullptr;
+  std::string loaded_parameter_;
+  Config config_;
+  DeviceEngine* engine() const { return engine_.get(); }
+  void* TrainScoreDevicePtr() const { return engine_ ? engine_->TrainScorePtr() : nullptr; }
+  const double* TrainScoreHost() const { return train_score_.data(); }
+  int iter_ = 0;
+
+ private:
+  void Bagging(int iter, const float* grad, const float* hess);
+  void BoostFromAverage(int class_id, double* out_init);
+  void UpdateScore(const Tree* tree, int class_id);
+  void DartDropTrees();
+  void DartNormalize();
+  bool CheckDivergence(const float* grad, int64_t n);
+  void AddTreeScore(const Tree* tree, const Dataset* ds, double* score, double scale) const;
+
+  const Dataset* train_ = nullptr;
+  std::vector<const Dataset*> valid_;
+  std::unique_ptr<TreeLearner> learner_;
+  std::unique_ptr<DeviceEngine> engine_;
+  std::vector<std::vector<std::unique_ptr<Metric>>> metrics_;   // [0] train, [1+] valid
+  std::vector<std::string> metric_names_;
+  std::vector<double> train_score_;                    // class-major
+  std::vector<std::vector<double>> valid_score_;
+  std::vector<float> grad_, hess_;
+  std::vector<data_size_t> bag_indices_;
+  data_size_t bag_cnt_ = 0;
+  bool is_bagging_ = false, is_goss_ = false;
+  bool is_dart_ = false, is_rf_ = false, is_cuda_ = false;
+  double shrinkage_rate_ = 0.1;
+  std::vector<int> drop_index_;
+  std::vector<double> tree_weight_;
+  double sum_weight_ = 0;
+  Random drop_rand_{4};
+  std::vector<double> init_scores_;
+  std::vector<bool> class_need_train_;
+  bool boosted_from_average_ = false;
+  double first_grad_norm_ = -1;
+  std::vector<double> rf_init_scores_;
+};
+
+}  // namespace fb

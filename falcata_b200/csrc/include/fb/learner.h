@@ -1,0 +1,118 @@
+// Tree learner interface, the host (CPU) histogram learner, the column sampler and the host
+// gradient quantizer. The CPU learner is both `device_type=cpu` and the oracle that every device
+// kernel and the multi-rank paths are checked against.
+//
+// Parity: include/Falcata/tree_learner.h (interface), src/treelearner/serial_tree_learner.cpp
+// (Train L189-262, ConstructHistograms L425, FindBestSplitsFromHistograms L494, SplitInner L783),
+// src/treelearner/data_partition.hpp, leaf_splits.hpp, col_sampler.hpp,
+// gradient_discretizer.cpp; parallel modes: data_parallel_tree_learner.cpp:L125-451,
+// feature_parallel_tree_learner.cpp:L38-79, voting_parallel_tree_learner.cpp:L152-481.
+#pragma once
+#include <functional>
+#include <memory>
+#include <vector>
+#include "fb/config.h"
+#include "fb/dataset.h"
+#include "fb/split_math.h"
+#include "fb/tree.h"
+
+namespace fb {
+
+// Host collectives injected by the embedding process (torch.distributed over gloo in the tests,
+// any other transport in production). Parity: FLC_NetworkInitWithFunctions, src/c_api.cpp:L3218.
+struct Network {
+  typedef void (*AllreduceSumFn)(void* buf, int64_t count, int dtype /*0 f64, 1 i64*/);
+  typedef void (*AllgatherFn)(const void* in, int64_t bytes, void* out /* world * bytes */);
+  static int& rank() { static int r = 0; return r; }
+  static int& world() { static int w = 1; return w; }
+  static AllreduceSumFn& allreduce() { static AllreduceSumFn f = nullptr; return f; }
+  static AllgatherFn& allgather() { static AllgatherFn f = nullptr; return f; }
+  static bool active() { return world() > 1 && allreduce() != nullptr && allgather() != nullptr; }
+  static void SumDouble(double* p, int64_t n) { if (active()) allreduce()(p, n, 0); }
+  static void SumInt64(int64_t* p, int64_t n) { if (active()) allreduce()(p, n, 1); }
+  static double MaxDouble(double v);
+  static void Gather(const void* in, int64_t bytes, std::vector<char>* out) {
+    out->resize(static_cast<size_t>(bytes) * world());
+    if (active()) allgather()(in, bytes, out->data()); else memcpy(out->data(), in, bytes);
+  }
+};
+
+// Counter-based per-tree / per-node feature sampling (resumable: depends only on seed and ids).
+class ColSampler {
+ public:
+  void Init(const Config& cfg, const Dataset* ds);
+  void ResetByTree(int tree_index);
+  const std::vector<int8_t>& used_by_tree() const { return used_; }
+  std::vector<int8_t> SampleByNode(int tree_index, int node_id) const;
+  bool by_node() const { return frac_bynode_ < 1.0; }
+  int num_used() const { return num_used_; }
+ private:
+  double frac_bytree_ = 1.0, frac_bynode_ = 1.0;
+  int seed_ = 0, nfeat_ = 0, num_used_ = 0;
+  std::vector<int8_t> used_;
+  std::vector<std::vector<int>> interaction_sets_;
+};
+
+// Quantization scales of one tree and the packed per-row words.
+struct QuantState {
+  double g_scale = 1.0, h_scale = 1.0;
+  int bins = 4;
+  bool stochastic = true;
+};
+// (int16 grad << 16) | uint16 hess
+inline int32_t PackGH(int gi, int hi) { return static_cast<int32_t>((static_cast<uint32_t>(gi) << 16) | (static_cast<uint32_t>(hi) & 0xFFFFu)); }
+FB_HD inline int UnpackG(int32_t w) { return w >> 16; }
+FB_HD inline int UnpackH(int32_t w) { return static_cast<int>(static_cast<uint32_t>(w) & 0xFFFFu); }
+
+// One row's quantized pair; the same code runs in the device kernel.
+FB_HD inline int32_t QuantizeRow(float g, float h, float inv_g_scale, float inv_h_scale, bool stochastic, uint32_t seed,
+                                 uint32_t iter_key, uint64_t global_row) {
+  int gi, hi;
+  if (stochastic) {
+    Philox4 r = Philox4x32_10(static_cast<uint32_t>(global_row), iter_key, 0x9E3779B9u ^ static_cast<uint32_t>(global_row >> 32), 0xBB67AE85u,
+                              seed, seed ^ 0x85EBCA6Bu);
+    const float ug = U01From24(r.v[0]), uh = U01From24(r.v[1]);
+#if defined(__CUDA_ARCH__)
+    gi = static_cast<int>(__fmaf_rn(g, inv_g_scale, g >= 0.f ? ug : -ug));
+    hi = static_cast<int>(__fmaf_rn(h, inv_h_scale, uh));
+#else
+    gi = static_cast<int>(std::fmaf(g, inv_g_scale, g >= 0.f ? ug : -ug));
+    hi = static_cast<int>(std::fmaf(h, inv_h_scale, uh));
+#endif
+  } else {
+#if defined(__CUDA_ARCH__)
+    gi = static_cast<int>(__fmaf_rn(g, inv_g_scale, g >= 0.f ? 0.5f : -0.5f));
+    hi = static_cast<int>(__fmaf_rn(h, inv_h_scale, 0.5f));
+#else
+    gi = static_cast<int>(std::fmaf(g, inv_g_scale, g >= 0.f ? 0.5f : -0.5f));
+    hi = static_cast<int>(std::fmaf(h, inv_h_scale, 0.5f));
+#endif
+  }
+  return static_cast<int32_t>((static_cast<uint32_t>(gi) << 16) | (static_cast<uint32_t>(hi) & 0xFFFFu));
+}
+
+class ObjectiveFunction;
+
+class TreeLearner {
+ public:
+  virtual ~TreeLearner() {}
+  virtual void Init(const Dataset* train, const Config& cfg) = 0;
+  virtual void ResetConfig(const Config& cfg) = 0;
+  // grad/hess: host pointers for the CPU learner, device pointers for the CUDA learner.
+  virtual Tree* Train(const score_t* grad, const score_t* hess, int tree_index) = 0;
+  virtual void SetBaggingData(const data_size_t* used_indices, data_size_t num) = 0;
+  // score += tree output for the training rows, through the final partition.
+  virtual void AddPredictionToScore(const Tree* tree, double* score) const = 0;
+  // Re-fit leaf outputs from a per-leaf functional (L1 / quantile / mape objectives).
+  virtual void RenewTreeOutput(Tree* tree, const ObjectiveFunction* obj, std::function<double(const label_t*, int)> residual,
+                               data_size_t total_num_data, const data_size_t* bag_indices, data_size_t bag_cnt, const double* score) const = 0;
+  virtual Tree* FitByExistingTree(const Tree* old_tree, const score_t* grad, const score_t* hess) const = 0;
+  virtual const data_size_t* LeafIndices(int leaf, data_size_t* count) const = 0;
+  virtual bool on_device() const { return false; }
+};
+
+TreeLearner* CreateTreeLearner(const Config& cfg);
+TreeLearner* CreateCPUTreeLearner(const Config& cfg);
+TreeLearner* CreateCUDATreeLearner(const Config& cfg);   // defined in the CUDA module
+
+}  // namespace fb

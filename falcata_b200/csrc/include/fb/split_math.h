@@ -1,0 +1,157 @@
+// Split gain / leaf output math and candidate evaluation, written once for the host learner
+// and the device kernels so that the two cannot drift apart.
+//
+// Parity (semantics): include/Falcata/tree_split_math.h:L33-89 (leaf output and gain),
+// src/treelearner/feature_histogram.hpp:L167-210, L393-440, L816-1041 (scan directions by
+// missing type, constraints, tie rules), src/treelearner/split_info.hpp:L138-166 (ordering).
+//
+// Every double operation goes through FB_MUL/FB_ADD/... so that neither compiler contracts
+// a*b+c into an FMA: with integer (quantized) histograms the host and the device then produce
+// bit-identical gains, which is what the cross-device equality tests rely on.
+#pragma once
+#include "fb/common.h"
+
+#if defined(__CUDA_ARCH__)
+#define FB_MUL(a, b) __dmul_rn((a), (b))
+#define FB_ADD(a, b) __dadd_rn((a), (b))
+#define FB_SUB(a, b) __dadd_rn((a), -(b))
+#define FB_DIV(a, b) __ddiv_rn((a), (b))
+#else
+#define FB_MUL(a, b) ((a) * (b))
+#define FB_ADD(a, b) ((a) + (b))
+#define FB_SUB(a, b) ((a) - (b))
+#define FB_DIV(a, b) ((a) / (b))
+#endif
+
+namespace fb {
+
+struct SplitParams {
+  double lambda_l1, lambda_l2, max_delta_step, path_smooth;
+  double min_sum_hessian_in_leaf, min_gain_to_split;
+  int min_data_in_leaf;
+  int max_depth;
+  // categorical
+  int max_cat_threshold, max_cat_to_onehot, min_data_per_group;
+  double cat_l2, cat_smooth;
+  int extra_trees;
+};
+
+// Fixed-size record of the best split of one leaf (or one (leaf, feature) task). POD: it is
+// written by device kernels, copied between ranks and read by the host.
+struct SplitRecord {
+  double gain;            // gain above the leaf's own (already minus min_gain_shift); <= 0 / -inf: none
+  int feature;            // inner feature index, -1 when no split
+  int threshold;          // bin index: feature bin <= threshold goes left (numerical)
+  int default_left;
+  int is_categorical;
+  double left_g, left_h, right_g, right_h;   // real-valued sums (scaled back when quantized)
+  double left_out, right_out;
+  int64_t left_gi, left_hi;                  // integer sums under quantized training
+  int left_cnt, right_cnt;                   // estimated at find time; exact after partition
+  int monotone;
+  int num_cat_bins;                          // categorical: number of bins in cat_bins (<= 8 words bitset)
+  uint32_t cat_bitset[8];                    // categorical: bins that go left
+};
+
+FB_HD inline void InitSplitRecord(SplitRecord* r) {
+  r->gain = -1.0 / 0.0; r->feature = -1; r->threshold = 0; r->default_left = 1; r->is_categorical = 0;
+  r->left_g = r->left_h = r->right_g = r->right_h = 0; r->left_out = r->right_out = 0;
+  r->left_gi = r->left_hi = 0; r->left_cnt = r->right_cnt = 0; r->monotone = 0; r->num_cat_bins = 0;
+  for (int i = 0; i < 8; ++i) r->cat_bitset[i] = 0;
+}
+
+// a is better than b: larger gain; on equal gain the lower feature index, then lower threshold.
+FB_HD inline bool SplitBetter(double gain_a, int feat_a, int thr_a, double gain_b, int feat_b, int thr_b) {
+  if (feat_a < 0) return false;
+  if (feat_b < 0) return true;
+  if (gain_a != gain_b) return gain_a > gain_b;
+  if (feat_a != feat_b) return feat_a < feat_b;
+  return thr_a < thr_b;
+}
+
+FB_HD inline double ThresholdL1(double s, double l1) {
+  double r = fabs(s) - l1;
+  if (r < 0.0) r = 0.0;
+  return s >= 0.0 ? r : -r;
+}
+
+FB_HD inline double LeafOutputRaw(double g, double h, const SplitParams& p) {
+  double num = p.lambda_l1 > 0.0 ? ThresholdL1(g, p.lambda_l1) : g;
+  double out = -FB_DIV(num, FB_ADD(h, p.lambda_l2));
+  if (p.max_delta_step > 0.0 && fabs(out) > p.max_delta_step) out = out >= 0.0 ? p.max_delta_step : -p.max_delta_step;
+  return out;
+}
+
+FB_HD inline double LeafOutput(double g, double h, const SplitParams& p, int num_data, double parent_output) {
+  double out = LeafOutputRaw(g, h, p);
+  if (p.path_smooth > 0.0) {
+    double w = FB_DIV(static_cast<double>(num_data), p.path_smooth);
+    out = FB_ADD(FB_DIV(FB_MUL(out, w), FB_ADD(w, 1.0)), FB_DIV(parent_output, FB_ADD(w, 1.0)));
+  }
+  return out;
+}
+
+FB_HD inline double LeafGainGivenOutput(double g, double h, const SplitParams& p, double out) {
+  double gg = p.lambda_l1 > 0.0 ? ThresholdL1(g, p.lambda_l1) : g;
+  return -FB_ADD(FB_MUL(FB_MUL(2.0, gg), out), FB_MUL(FB_MUL(FB_ADD(h, p.lambda_l2), out), out));
+}
+
+FB_HD inline double LeafGain(double g, double h, const SplitParams& p, int num_data, double parent_output) {
+  if (p.max_delta_step <= 0.0 && p.path_smooth <= 0.0) {
+    double gg = p.lambda_l1 > 0.0 ? ThresholdL1(g, p.lambda_l1) : g;
+    return FB_DIV(FB_MUL(gg, gg), FB_ADD(h, p.lambda_l2));
+  }
+  return LeafGainGivenOutput(g, h, p, LeafOutput(g, h, p, num_data, parent_output));
+}
+
+// Gain of a (left, right) pair; returns false when a monotone constraint is violated.
+FB_HD inline bool SplitGain(double lg, double lh, double rg, double rh, const SplitParams& p, int lcnt, int rcnt,
+                            double parent_output, int monotone, double* gain, double* lout, double* rout) {
+  *lout = LeafOutput(lg, lh, p, lcnt, parent_output);
+  *rout = LeafOutput(rg, rh, p, rcnt, parent_output);
+  if ((monotone > 0 && *lout > *rout) || (monotone < 0 && *lout < *rout)) { *gain = 0.0; return false; }
+  if (p.max_delta_step <= 0.0 && p.path_smooth <= 0.0) {
+    *gain = FB_ADD(LeafGain(lg, lh, p, lcnt, parent_output), LeafGain(rg, rh, p, rcnt, parent_output));
+  } else {
+    *gain = FB_ADD(LeafGainGivenOutput(lg, lh, p, *lout), LeafGainGivenOutput(rg, rh, p, *rout));
+  }
+  return true;
+}
+
+// Per-leaf constants of the threshold search.
+struct LeafScanInfo {
+  double sum_g, sum_h;        // real-valued totals (sum_h without epsilon)
+  int64_t sum_gi, sum_hi;     // integer totals (quantized)
+  int num_data;
+  double parent_output;
+  double min_gain_shift;      // LeafGain(parent) + min_gain_to_split
+  double cnt_factor;          // num_data / sum_h
+  double g_scale, h_scale;    // quantized: real = int * scale; else 1
+};
+
+// Rounded row-count estimate of one bin from its hessian mass.
+FB_HD inline int BinCountEstimate(double h, double cnt_factor) { return static_cast<int>(FB_ADD(FB_MUL(h, cnt_factor), 0.5)); }
+
+// Evaluate the candidate "bins on the LEFT side sum to (lg, lh, lcnt)". Returns the gain above
+// min_gain_shift, or -inf when a constraint fails.
+FB_HD inline double EvalCandidate(double lg, double lh, int lcnt, const LeafScanInfo& L, const SplitParams& p, int monotone,
+                                  double* lout, double* rout) {
+  const double ninf = -1.0 / 0.0;
+  const int rcnt = L.num_data - lcnt;
+  const double rg = FB_SUB(L.sum_g, lg), rh = FB_SUB(L.sum_h, lh);
+  if (lcnt < p.min_data_in_leaf || rcnt < p.min_data_in_leaf) return ninf;
+  if (lh < p.min_sum_hessian_in_leaf || rh < p.min_sum_hessian_in_leaf) return ninf;
+  double gain;
+  if (!SplitGain(lg, FB_ADD(lh, kEpsilon), rg, FB_ADD(rh, kEpsilon), p, lcnt, rcnt, L.parent_output, monotone, &gain, lout, rout)) return ninf;
+  if (!(gain > L.min_gain_shift)) return ninf;
+  return FB_SUB(gain, L.min_gain_shift);
+}
+
+// Scan order of the numerical threshold search. For a feature with `nb` bins:
+//   pass 0 (reverse): t = last .. 0, missing values (zero bin / NaN bin) counted on the LEFT, default_left = 1
+//   pass 1 (forward): t = 0 .. last, missing values counted on the RIGHT, default_left = 0 (only when the
+//                     feature has a missing type and more than 2 bins)
+// Within a feature the first scanned candidate wins ties; `ScanRank` orders candidates accordingly.
+FB_HD inline int ScanRank(int pass, int t, int nb) { return pass == 0 ? (nb - 1 - t) : (nb + t); }
+
+}  // namespace fb
