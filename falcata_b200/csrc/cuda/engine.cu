@@ -1,0 +1,226 @@
+// Device engine: construction, buffers, score bookkeeping, validation sets, metrics.
+#include "engine.h"
+
+#include <sstream>
+
+namespace fb {
+
+// ------------------------------------------------------------ StageClock ----
+StageClock::~StageClock() { for (auto& p : pool) { cudaEventDestroy(p.first); cudaEventDestroy(p.second); } }
+int StageClock::Stage(const char* name) { names.push_back(name); total_ms.push_back(0.0); calls.push_back(0); return static_cast<int>(names.size()) - 1; }
+void StageClock::Begin(int stage, cudaStream_t s) {
+  if (!enabled) return;
+  if (next >= pool.size()) { cudaEvent_t a, b; FB_CUDA(cudaEventCreate(&a)); FB_CUDA(cudaEventCreate(&b)); pool.emplace_back(a, b); }
+  FB_CUDA(cudaEventRecord(pool[next].first, s));
+  pending.emplace_back(stage, static_cast<int>(next));
+  open_ = static_cast<int>(next); ++next;
+}
+void StageClock::End(cudaStream_t s) { if (!enabled || open_ < 0) return; FB_CUDA(cudaEventRecord(pool[open_].second, s)); open_ = -1; }
+void StageClock::Resolve() {
+  if (!enabled) return;
+  for (auto& pr : pending) { float ms = 0.f; if (cudaEventElapsedTime(&ms, pool[pr.second].first, pool[pr.second].second) == cudaSuccess) { total_ms[pr.first] += ms; calls[pr.first] += 1; } }
+  pending.clear(); next = 0;
+}
+std::string StageClock::Report() const {
+  std::ostringstream os;
+  for (size_t i = 0; i < names.size(); ++i) os << names[i] << ": " << total_ms[i] << " ms in " << calls[i] << " spans\n";
+  return os.str();
+}
+
+// --------------------------------------------------------------- engine ----
+DeviceEngine* CreateDeviceEngine(const Config& cfg, const Dataset* train, const ObjectiveFunction* obj, int num_tree_per_iter) {
+  return new CudaEngine(cfg, train, obj, num_tree_per_iter);
+}
+
+CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveFunction* obj, int K)
+    : cfg_(cfg), plan_(Plan::FromString(cfg.cuda_plan)), train_(train), obj_(obj), K_(K) {
+  if (!CudaAvailable()) Log::Fatal("device_type=cuda needs a CUDA device");
+  cudaDeviceProp prop; int dev = 0; FB_CUDA(cudaGetDevice(&dev)); FB_CUDA(cudaGetDeviceProperties(&prop, dev));
+  if (prop.major < 10) Log::Warning("This build targets sm_100a; device %s is compute %d.%d", prop.name, prop.major, prop.minor);
+  num_sms_ = prop.multiProcessorCount;
+  EnsureDeviceDataset(const_cast<Dataset*>(train));
+  dd_ = train->device; n_ = train->num_data;
+  FB_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+  SyncDeviceMetadata(train, stream_);
+  quant_ = cfg.quant != QuantMode::None;
+  sp_.lambda_l1 = cfg.lambda_l1; sp_.lambda_l2 = cfg.lambda_l2; sp_.max_delta_step = cfg.max_delta_step; sp_.path_smooth = cfg.path_smooth;
+  sp_.min_sum_hessian_in_leaf = cfg.min_sum_hessian_in_leaf; sp_.min_gain_to_split = cfg.min_gain_to_split; sp_.min_data_in_leaf = cfg.min_data_in_leaf;
+  sp_.max_depth = cfg.max_depth; sp_.max_cat_threshold = cfg.max_cat_threshold; sp_.max_cat_to_onehot = cfg.max_cat_to_onehot;
+  sp_.min_data_per_group = cfg.min_data_per_group; sp_.cat_l2 = cfg.cat_l2; sp_.cat_smooth = cfg.cat_smooth; sp_.extra_trees = 0;
+  if (cfg.extra_trees) Log::Warning("extra_trees is evaluated by the host learner only; the device learner searches all thresholds");
+  if (cfg.grow_policy == "leaf") Log::Warning("grow_policy=leaf runs on the host learner; the device learner grows level-wise with a gain-ranked leaf budget");
+  for (int f = 0; f < train->num_features; ++f) if (train->feature_meta[f].bin_type != 0) { Log::Warning("Categorical features are searched by the host learner only; the device learner skips them"); break; }
+  col_sampler_.Init(cfg, train);
+  clock_.enabled = getenv("FALCATA_STAGE_TIMING") != nullptr;
+  st_grad_ = clock_.Stage("gradients"); st_quant_ = clock_.Stage("quantize+root"); st_hist_ = clock_.Stage("histogram");
+  st_find_ = clock_.Stage("find-split"); st_part_ = clock_.Stage("partition"); st_score_ = clock_.Stage("score-update"); st_sync_ = clock_.Stage("level-readback");
+
+  // objective descriptor
+  objd_.kind = obj ? obj->DeviceKind() : kObjCustom; objd_.num_class = cfg.num_class; objd_.p0 = objd_.p1 = objd_.p2 = 0; objd_.max_docs = 0;
+  if (obj != nullptr) {
+    if (objd_.kind < 0) Log::Fatal("Objective %s has no device kernel; use device_type=cpu", obj->GetName());
+    objd_.p0 = obj->DeviceParam(0); objd_.p1 = obj->DeviceParam(1); objd_.p2 = obj->DeviceParam(2);
+    if (objd_.kind == kObjLambdarank) {
+      const auto& qb = train->metadata.query_boundaries;
+      for (size_t q = 0; q + 1 < qb.size(); ++q) max_docs_ = std::max(max_docs_, qb[q + 1] - qb[q]);
+      objd_.max_docs = max_docs_;
+      label_gain_.Upload(cfg.label_gain_vec, stream_);
+    }
+  }
+  const size_t total = static_cast<size_t>(n_) * K_;
+  score_.Alloc(total); score_.Zero(stream_);
+  if (!train->metadata.init_score.empty()) {
+    std::vector<float> f(train->metadata.init_score.begin(), train->metadata.init_score.end());
+    if (f.size() != total) Log::Fatal("init_score size does not match num_data * num_class");
+    score_.Upload(f, stream_);
+  }
+  grad_.Alloc(total); hess_.Alloc(total); maxbuf_.Alloc(2 * K_); scales_.Alloc(2); root_sums_i_.Alloc(2); root_sums_d_.Alloc(2);
+  partial_.Alloc(2 * (static_cast<size_t>(n_) / 256 + 2));
+  if (quant_) {
+    if (static_cast<double>(train->global_num_data) * cfg.quant_bins_resolved >= 2147483647.0)
+      Log::Fatal("num_data x quant_bins must stay below 2^31 for 32-bit histogram lanes; lower quant_bins");
+    if (plan_.gh_in_row && K_ == 1) { gh_base_ = dd_->rows.get() + dd_->gh_offset; gh_stride_ = dd_->row_stride; }
+    else { gh_sep_.Alloc(n_); gh_base_ = reinterpret_cast<const uint8_t*>(gh_sep_.get()); gh_stride_ = 4; }
+    hist_elem_ = sizeof(hist_q_t);
+  } else {
+    gh2_.Alloc(n_); gh_base_ = reinterpret_cast<const uint8_t*>(gh2_.get()); gh_stride_ = 8; hist_elem_ = sizeof(double2);
+  }
+  idx_[0].Alloc(n_); idx_[1].Alloc(n_);
+  const int NL = cfg.num_leaves;
+  leaves_.Alloc(NL); best_.Alloc(NL); h_leaves_.Alloc(NL); h_best_.Alloc(NL); leaf_value_.Alloc(NL);
+  host_leaves_.resize(NL);
+  BuildPartitions();
+  SetupOwnership();
+  pool_.Alloc(static_cast<size_t>(NL) * slot_stride_ * hist_elem_);
+  cand_.Alloc(static_cast<size_t>(NL) * std::max<size_t>(1, owned_features_.size()));
+  hist_tasks_.Alloc(NL);
+  const size_t max_chunks = static_cast<size_t>(n_) / kPartChunk + NL + 1;
+  bits_.Alloc(max_chunks * (kPartChunk / 32)); chunk_left_.Alloc(max_chunks); split_left_total_.Alloc(NL);
+  const size_t blob = static_cast<size_t>(NL) * (sizeof(PartSplit) + sizeof(ChildInit) + 2 * sizeof(FindChild)) + 256;
+  level_blob_.Alloc(blob); h_level_blob_.Alloc(blob);
+  features_.Alloc(std::max(1, train->num_features)); sub_features_.Alloc(std::max(1, train->num_features));
+  FB_CUDA(cudaStreamSynchronize(stream_));
+  Log::Info("CUDA engine: %d rows x %d groups (%d bins, %d partitions), row stride %d B, %s histograms, plan: %s", n_, dd_->num_groups,
+            train->num_total_bin, static_cast<int>(h_parts_.size()), dd_->row_stride, quant_ ? "integer" : "fp64", plan_.ToString().c_str());
+}
+
+CudaEngine::~CudaEngine() { if (stream_) cudaStreamDestroy(stream_); }
+
+// Feature partitions of the construct kernel: runs of groups, starting on a 4-group boundary (the
+// kernel loads 4 group bytes per item), whose bins fit the shared-memory tile.
+void CudaEngine::BuildPartitions() {
+  const int kMaxBins = 6144;
+  h_parts_.clear();
+  const int G = train_->num_groups;
+  int g = 0;
+  while (g < G) {
+    HistPartition p; p.group_begin = g; p.bin_begin = train_->group_bin_start[g]; p.bin_count = 0;
+    int e = g;
+    while (e < G) {
+      int e4 = std::min(G, e + 4); int add = 0;
+      for (int k = e; k < e4; ++k) add += train_->group_num_bin[k];
+      if (p.bin_count + add > kMaxBins && e > g) break;
+      p.bin_count += add; e = e4;
+    }
+    p.group_end = e; h_parts_.push_back(p); g = e;
+  }
+  max_part_bins_ = 0; for (auto& p : h_parts_) max_part_bins_ = std::max(max_part_bins_, p.bin_count);
+  parts_.Upload(h_parts_, stream_);
+}
+
+// Which rank owns which histogram bins. One rank: identity. (The multi-rank map is installed by the fabric.)
+void CudaEngine::SetupOwnership() {
+  const int nb = train_->num_total_bin;
+  std::vector<unsigned char> owner(nb, 0); std::vector<int> local(nb);
+  for (int b = 0; b < nb; ++b) local[b] = b;
+  bin_owner_.Upload(owner, stream_); bin_local_.Upload(local, stream_);
+  slot_stride_ = nb;
+  owned_features_.clear();
+  for (int f = 0; f < train_->num_features; ++f) owned_features_.push_back(f);
+}
+
+int CudaEngine::ChooseRowsPerBlock(long long total_rows) const {
+  long long target = total_rows / (static_cast<long long>(num_sms_) * 6) + 1;
+  long long rpb = 512; while (rpb < target && rpb < 8192) rpb <<= 1;
+  return static_cast<int>(rpb);
+}
+
+void CudaEngine::AddConstantToScores(double v, int k) {
+  LaunchAddConstant(score_.get() + static_cast<size_t>(k) * n_, n_, static_cast<float>(v), stream_);
+  for (auto& vs : valid_) LaunchAddConstant(vs.score.get() + static_cast<size_t>(k) * vs.ds->num_data, vs.ds->num_data, static_cast<float>(v), stream_);
+}
+
+void CudaEngine::AddValid(const Dataset* valid) {
+  EnsureDeviceDataset(const_cast<Dataset*>(valid));
+  SyncDeviceMetadata(valid, stream_);
+  valid_.emplace_back();
+  ValidSet& vs = valid_.back();
+  vs.ds = valid; vs.dd = valid->device;
+  const size_t total = static_cast<size_t>(valid->num_data) * K_;
+  vs.score.Alloc(total); vs.score.Zero(stream_);
+  if (!valid->metadata.init_score.empty()) { std::vector<float> f(valid->metadata.init_score.begin(), valid->metadata.init_score.end()); vs.score.Upload(f, stream_); }
+  FB_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void CudaEngine::UploadTreeForTraversal(const Tree& tree, const Dataset* ds, DevTree* out) {
+  const int ni = std::max(1, tree.num_leaves - 1), nl = tree.num_leaves;
+  std::vector<int> ints(static_cast<size_t>(ni) * 11, 0); std::vector<float> fl(nl); std::vector<signed char> dec(ni, 0);
+  int* left = ints.data(); int* right = left + ni; int* sf = right + ni; int* sg = sf + ni; int* tb = sg + ni; int* db = tb + ni; int* nanb = db + ni;
+  int* bun = nanb + ni; int* goff = bun + ni; int* mfb = goff + ni; int* nbin = mfb + ni;
+  for (int s = 0; s < tree.num_leaves - 1; ++s) {
+    const int f = tree.split_feature_inner[s]; const FeatureMeta& m = ds->feature_meta[f];
+    left[s] = tree.left_child[s]; right[s] = tree.right_child[s]; sf[s] = f; sg[s] = m.group; tb[s] = static_cast<int>(tree.threshold_in_bin[s]);
+    db[s] = m.default_bin; nanb[s] = m.num_bin - 1; bun[s] = m.bundled; goff[s] = m.group_offset; mfb[s] = m.most_freq_bin; nbin[s] = m.num_bin; dec[s] = tree.decision_type[s];
+  }
+  for (int l = 0; l < nl; ++l) fl[l] = static_cast<float>(tree.leaf_value[l]);
+  FB_CUDA(cudaStreamSynchronize(stream_));   // staging buffers are reused: the previous traversal must be done
+  tree_ints_.Upload(ints, stream_); tree_floats_.Upload(fl, stream_); tree_dec_.Upload(dec, stream_);
+  FB_CUDA(cudaStreamSynchronize(stream_));   // host vectors go out of scope
+  const int* d = tree_ints_.get();
+  out->num_leaves = nl; out->left = d; out->right = d + ni; out->split_feature = d + 2 * ni; out->split_group = d + 3 * ni; out->threshold_bin = d + 4 * ni;
+  out->default_bin = d + 5 * ni; out->nan_bin = d + 6 * ni; out->bundled = d + 7 * ni; out->group_offset = d + 8 * ni; out->most_freq_bin = d + 9 * ni; out->num_bin = d + 10 * ni;
+  out->threshold = nullptr; out->decision = tree_dec_.get(); out->leaf_value = tree_floats_.get();
+}
+
+void CudaEngine::AddTreeToScores(const Tree& tree, int k, double scale) {
+  DevTree dt; UploadTreeForTraversal(tree, train_, &dt);
+  LaunchAddTreeBinned(dt, dd_->rows.get(), dd_->row_stride, n_, static_cast<float>(scale), score_.get() + static_cast<size_t>(k) * n_, stream_);
+  for (auto& vs : valid_) LaunchAddTreeBinned(dt, vs.dd->rows.get(), vs.dd->row_stride, vs.ds->num_data, static_cast<float>(scale), vs.score.get() + static_cast<size_t>(k) * vs.ds->num_data, stream_);
+  FB_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void CudaEngine::CopyScoresToHost(int data_idx, double* out) {
+  const float* src = data_idx == 0 ? score_.get() : valid_[data_idx - 1].score.get();
+  const size_t total = static_cast<size_t>(data_idx == 0 ? n_ : valid_[data_idx - 1].ds->num_data) * K_;
+  std::vector<float> tmp(total);
+  FB_CUDA(cudaMemcpyAsync(tmp.data(), src, total * sizeof(float), cudaMemcpyDeviceToHost, stream_));
+  FB_CUDA(cudaStreamSynchronize(stream_));
+  for (size_t i = 0; i < total; ++i) out[i] = tmp[i];
+}
+
+std::vector<double> CudaEngine::EvalMetric(int data_idx, const std::string& name, bool* supported) {
+  *supported = false;
+  int kind = -1;
+  if (name == "l2") kind = kMetL2; else if (name == "rmse") kind = kMetRMSE; else if (name == "l1") kind = kMetL1;
+  else if (name == "binary_logloss") kind = kMetBinaryLogloss; else if (name == "binary_error") kind = kMetBinaryError;
+  else if (name == "multi_logloss") kind = kMetMultiLogloss; else if (name == "multi_error" && cfg_.multi_error_top_k == 1) kind = kMetMultiError;
+  if (kind < 0 || Network::active()) return {};
+  if ((kind == kMetL2 || kind == kMetRMSE || kind == kMetL1) && cfg_.reg_sqrt) return {};
+  const Dataset* ds = data_idx == 0 ? train_ : valid_[data_idx - 1].ds;
+  DeviceDataset* dd = data_idx == 0 ? dd_ : valid_[data_idx - 1].dd;
+  const float* score = data_idx == 0 ? score_.get() : valid_[data_idx - 1].score.get();
+  if (dd->label.size() == 0) return {};
+  const int n = ds->num_data;
+  if (partial_.size() < 2 * (static_cast<size_t>(n) / 256 + 2)) partial_.Alloc(2 * (static_cast<size_t>(n) / 256 + 2));
+  LaunchPointwiseMetric(kind == kMetRMSE ? kMetL2 : kind, objd_.kind, objd_.kind == kObjBinary || objd_.kind == kObjMulticlassOVA ? objd_.p0 : 1.0, score, dd->label.get(),
+                        dd->weight.size() ? dd->weight.get() : nullptr, n, K_, partial_.get(), static_cast<int>(partial_.size() / 2), root_sums_d_.get(), stream_);
+  double h[2];
+  FB_CUDA(cudaMemcpyAsync(h, root_sums_d_.get(), sizeof(h), cudaMemcpyDeviceToHost, stream_));
+  FB_CUDA(cudaStreamSynchronize(stream_));
+  *supported = true;
+  double v = h[1] > 0 ? h[0] / h[1] : 0.0;
+  if (kind == kMetRMSE) v = std::sqrt(v);
+  return {v};
+}
+
+}  // namespace fb

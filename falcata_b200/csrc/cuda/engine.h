@@ -1,0 +1,107 @@
+// Device training engine: owns the scores, gradients, index buffers, histogram pool and level
+// descriptors of one rank, and drives the level loop.
+// Parity: src/treelearner/cuda/cuda_single_gpu_tree_learner.cpp (Train L3245-3506, level-batched
+// prefix L1804-1937, EnqueueLevelBestSplitSearch L1129-1285, ApplyLevelBatched L1480-1716),
+// src/boosting/cuda/cuda_score_updater.cpp, src/boosting/cuda/nccl_gbdt.cpp (per-rank component).
+#pragma once
+#include <memory>
+#include <vector>
+
+#include "fb/gbdt.h"
+#include "kernels.cuh"
+
+namespace fb {
+
+void EnsureDeviceDataset(Dataset* ds);
+void SyncDeviceMetadata(const Dataset* ds, cudaStream_t s);
+class Fabric;   // symmetric heap + peer pointers of the multi-rank path (fabric.h)
+
+struct StageClock {
+  // CUDA-event stage timing without host synchronisation inside a tree: events are recorded on the
+  // stream and resolved once per tree.
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pool;
+  std::vector<std::pair<int, int>> pending;   // (stage, pool index)
+  std::vector<double> total_ms; std::vector<int64_t> calls; std::vector<std::string> names;
+  size_t next = 0; bool enabled = false;
+  int Stage(const char* name);
+  void Begin(int stage, cudaStream_t s);
+  void End(cudaStream_t s);
+  void Resolve();
+  std::string Report() const;
+  ~StageClock();
+ private:
+  int open_ = -1;
+};
+
+class CudaEngine : public DeviceEngine {
+ public:
+  CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveFunction* obj, int num_tree_per_iter);
+  ~CudaEngine() override;
+  void AddValid(const Dataset* valid) override;
+  void AddConstantToScores(double v, int class_id) override;
+  void TrainOneIter(const float* custom_grad, const float* custom_hess, int iter, double shrinkage, const std::vector<double>& init_scores,
+                    std::vector<std::unique_ptr<Tree>>* out, bool* all_constant) override;
+  std::vector<double> EvalMetric(int data_idx, const std::string& metric_name, bool* supported) override;
+  void CopyScoresToHost(int data_idx, double* out) override;
+  void AddTreeToScores(const Tree& tree, int class_id, double scale) override;
+  void* TrainScorePtr() override { return score_.get(); }
+  int64_t GpuLaunches() const override { return LaunchCounter().load(); }
+  std::string StageReport() const override { return clock_.Report(); }
+  void SetBagging(double fraction, int freq, int seed) override { bag_fraction_ = fraction; bag_freq_ = freq; bag_seed_ = seed; }
+
+ private:
+  struct HostLeaf { int begin = 0, count = 0, buffer = 0, depth = 0, slot = 0; SplitRecord best; bool valid = false; };
+  struct ValidSet { const Dataset* ds; DeviceDataset* dd; DevBuf<float> score; };
+
+  Tree* TrainTree(int class_id, int tree_index);
+  void BuildPartitions();
+  void SetupOwnership();
+  void RunRootHistogram();
+  void ReadBackLevel(int num_leaves);
+  void UploadTreeForTraversal(const Tree& tree, const Dataset* ds, DevTree* out);
+  int ChooseRowsPerBlock(long long total_rows) const;
+
+  Config cfg_; Plan plan_;
+  const Dataset* train_; DeviceDataset* dd_; const ObjectiveFunction* obj_;
+  int K_ = 1, n_ = 0;
+  bool quant_ = false;
+  cudaStream_t stream_ = nullptr;
+  int num_sms_ = 148;
+  SplitParams sp_;
+  ObjDesc objd_;
+  ColSampler col_sampler_;
+  StageClock clock_;
+  int st_grad_, st_quant_, st_hist_, st_find_, st_part_, st_score_, st_sync_;
+
+  DevBuf<float> score_, grad_, hess_, maxbuf_, scales_;
+  DevBuf<long long> root_sums_i_;
+  DevBuf<double> root_sums_d_, partial_, label_gain_;
+  DevBuf<int32_t> gh_sep_;
+  DevBuf<float2> gh2_;
+  const uint8_t* gh_base_ = nullptr; int gh_stride_ = 0;
+  DevBuf<int> idx_[2];
+  DevBuf<LeafInfo> leaves_;
+  DevBuf<SplitRecord> best_;
+  DevBuf<CandLite> cand_;
+  DevBuf<char> pool_;
+  long long slot_stride_ = 0;      // bins per pool slot on this rank
+  size_t hist_elem_ = 8;
+  DevBuf<HistPartition> parts_; std::vector<HistPartition> h_parts_; int max_part_bins_ = 0;
+  DevBuf<unsigned char> bin_owner_; DevBuf<int> bin_local_;
+  std::vector<int> owned_features_;
+  DevBuf<char> level_blob_; PinnedBuf<char> h_level_blob_;
+  DevBuf<HistTask> hist_tasks_;
+  DevBuf<unsigned int> bits_; DevBuf<int> chunk_left_, split_left_total_;
+  DevBuf<int> features_, sub_features_;
+  DevBuf<double> leaf_value_;
+  PinnedBuf<LeafInfo> h_leaves_; PinnedBuf<SplitRecord> h_best_;
+  std::vector<HostLeaf> host_leaves_;
+  std::vector<ValidSet> valid_;
+  // traversal staging
+  DevBuf<int> tree_ints_; DevBuf<float> tree_floats_; DevBuf<signed char> tree_dec_;
+  const float* cur_grad_ = nullptr; const float* cur_hess_ = nullptr;
+  double bag_fraction_ = 1.0; int bag_freq_ = 0, bag_seed_ = 0;
+  int max_docs_ = 0;
+};
+
+}  // namespace fb

@@ -1,0 +1,233 @@
+// Device engine: one boosting iteration and the level loop of one tree.
+//
+// Per level (all splitting leaves at once): partition flags -> scan + child/leaf/task setup ->
+// scatter -> construct (smaller children, fused reduce-scatter epilogue) -> find (+ in-place
+// larger = parent - smaller) -> per-leaf argmax -> ONE read-back of the leaf records and best
+// splits, on which the host applies the gain-ranked leaf budget. Exact child counts come back with
+// that read-back, so there is no second synchronisation per level.
+#include "engine.h"
+
+namespace fb {
+
+namespace {
+
+// Root leaf record from the device-side sums (no host round trip between quantize and the root histogram).
+__global__ void InitRootKernel(LeafInfo* leaves, const long long* sums_i, const double* sums_d, const float* scales, int quant, int n_local,
+                               long long n_global, SplitParams sp) {
+  LeafInfo L;
+  L.begin = 0; L.count = n_local; L.buffer = 0; L.depth = 0; L.hist_slot = 0; L.num_data_global = static_cast<int>(n_global);
+  if (quant) {
+    L.sum_gi = sums_i[0]; L.sum_hi = sums_i[1];
+    L.sum_g = FB_MUL(static_cast<double>(L.sum_gi), static_cast<double>(scales[0])); L.sum_h = FB_MUL(static_cast<double>(L.sum_hi), static_cast<double>(scales[1]));
+  } else { L.sum_gi = L.sum_hi = 0; L.sum_g = sums_d[0]; L.sum_h = sums_d[1]; }
+  L.output = LeafOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp, L.num_data_global, 0.0);
+  leaves[0] = L;
+}
+
+}  // namespace
+
+void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess, int iter, double shrinkage, const std::vector<double>& init_scores,
+                              std::vector<std::unique_ptr<Tree>>* out, bool* all_constant) {
+  const float* grad = grad_.get(); const float* hess = hess_.get();
+  clock_.Begin(st_grad_, stream_);
+  if (custom_grad != nullptr) {
+    grad = custom_grad; hess = custom_hess;
+    FB_CUDA(cudaStreamSynchronize(0));   // custom gradients were produced on the caller's (default) stream
+    LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_);
+  } else {
+    if (obj_ == nullptr) Log::Fatal("No objective function provided and no custom gradients given");
+    LaunchObjectiveGradients(objd_, score_.get(), dd_->label.get(), dd_->weight.size() ? dd_->weight.get() : nullptr,
+                             dd_->query_boundaries.size() ? dd_->query_boundaries.get() : nullptr, dd_->num_queries, label_gain_.get(),
+                             static_cast<int>(label_gain_.size()), n_, grad_.get(), hess_.get(), maxbuf_.get(), stream_);
+  }
+  clock_.End(stream_);
+  bool any_split = false;
+  for (int k = 0; k < K_; ++k) {
+    std::unique_ptr<Tree> tree;
+    const bool need = obj_ == nullptr || obj_->ClassNeedTrain(k);
+    if (need && train_->num_features > 0) {
+      // TrainTree reads grad_/hess_ through these members
+      cur_grad_ = grad + static_cast<size_t>(k) * n_; cur_hess_ = hess + static_cast<size_t>(k) * n_;
+      tree.reset(TrainTree(k, iter * K_ + k));
+    } else tree.reset(new Tree(2));
+    if (tree->num_leaves > 1) {
+      any_split = true;
+      tree->Shrink(shrinkage);
+      // training rows through the final partition; validation rows by traversal
+      clock_.Begin(st_score_, stream_);
+      FB_CUDA(cudaStreamSynchronize(stream_));
+      leaf_value_.Upload(tree->leaf_value.data(), tree->num_leaves, stream_);
+      LaunchAddLeafOutputs(leaves_.get(), leaf_value_.get(), tree->num_leaves, idx_[0].get(), idx_[1].get(), score_.get() + static_cast<size_t>(k) * n_, stream_);
+      clock_.End(stream_);
+      if (!valid_.empty()) {
+        DevTree dt; UploadTreeForTraversal(*tree, train_, &dt);
+        for (auto& vs : valid_) LaunchAddTreeBinned(dt, vs.dd->rows.get(), vs.dd->row_stride, vs.ds->num_data, 1.f, vs.score.get() + static_cast<size_t>(k) * vs.ds->num_data, stream_);
+      }
+      if (std::fabs(init_scores[k]) > kEpsilon) tree->AddBias(init_scores[k]);
+      FB_CUDA(cudaStreamSynchronize(stream_));   // leaf_value upload source and traversal staging are host memory
+    } else {
+      double outv = 0.0;
+      if (iter == 0) { outv = (!need && obj_ != nullptr) ? obj_->BoostFromScore(k) : init_scores[k]; if (!need) AddConstantToScores(outv, k); }
+      tree->AsConstantTree(outv);
+    }
+    out->push_back(std::move(tree));
+  }
+  clock_.Resolve();
+  *all_constant = !any_split;
+}
+
+Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
+  col_sampler_.ResetByTree(tree_index);
+  // features searched on this rank this tree (owned, sampled, numerical) and the rest of the owned ones
+  std::vector<int> feats, subs;
+  for (int f : owned_features_) { if (col_sampler_.used_by_tree()[f] && train_->feature_meta[f].bin_type == 0) feats.push_back(f); else subs.push_back(f); }
+  features_.Upload(feats, stream_); sub_features_.Upload(subs, stream_);
+  const int NF = static_cast<int>(feats.size()), NS = static_cast<int>(subs.size());
+
+  clock_.Begin(st_quant_, stream_);
+  if (quant_) {
+    LaunchQuantize(cur_grad_, cur_hess_, n_, maxbuf_.get() + 2 * class_id, nullptr, cfg_.quant_bins_resolved, cfg_.quant == QuantMode::Stochastic,
+                   static_cast<uint32_t>(cfg_.seed), static_cast<uint32_t>(tree_index), static_cast<uint64_t>(train_->global_row_offset),
+                   const_cast<uint8_t*>(gh_base_), gh_stride_, scales_.get(), root_sums_i_.get(), stream_);
+  } else {
+    LaunchInterleave(cur_grad_, cur_hess_, n_, gh2_.get(), partial_.get(), static_cast<int>(partial_.size() / 2), root_sums_d_.get(), stream_);
+  }
+  InitRootKernel<<<1, 1, 0, stream_>>>(leaves_.get(), root_sums_i_.get(), root_sums_d_.get(), scales_.get(), quant_ ? 1 : 0, n_, train_->global_num_data, sp_);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+  pool_.Zero(stream_);
+  LaunchInitIndices(idx_[0].get(), n_, stream_);
+  clock_.End(stream_);
+
+  // ---- common launch descriptors ----
+  HistArgs ha;
+  ha.rows = dd_->rows.get(); ha.row_stride = dd_->row_stride; ha.num_groups = dd_->num_groups; ha.gh_base = gh_base_; ha.gh_stride = gh_stride_;
+  ha.idx[0] = idx_[0].get(); ha.idx[1] = idx_[1].get(); ha.tasks = hist_tasks_.get(); ha.parts = parts_.get(); ha.num_parts = static_cast<int>(h_parts_.size());
+  ha.max_part_bins = max_part_bins_; ha.group_bin_start = dd_->group_bin_start.get();
+  const int qb = std::max(2, cfg_.quant_bins_resolved);
+  ha.sub_rows = quant_ ? std::max(1, std::min(65535 / qb, 32767 / std::max(1, qb / 2))) : (1 << 30);
+  for (int r = 0; r < 8; ++r) { ha.dest.pool[r] = nullptr; ha.dest.slot_stride[r] = 0; }
+  ha.dest.pool[0] = pool_.get(); ha.dest.slot_stride[0] = slot_stride_; ha.dest.bin_owner = bin_owner_.get(); ha.dest.bin_local = bin_local_.get();
+  ha.dest.num_ranks = 1; ha.dest.rank = 0;
+  FindArgs fa;
+  fa.features = features_.get(); fa.num_features = NF; fa.sub_features = sub_features_.get(); fa.num_sub_features = NS; fa.meta = dd_->feature_meta.get();
+  fa.bin_local = bin_local_.get(); fa.pool = pool_.get(); fa.slot_stride = slot_stride_; fa.leaves = leaves_.get(); fa.scales = scales_.get(); fa.params = sp_;
+  fa.cand = cand_.get(); fa.best = best_.get(); fa.quant = quant_ ? 1 : 0;
+
+  char* hb = h_level_blob_.get(); char* db = level_blob_.get();
+  std::unique_ptr<Tree> tree(new Tree(cfg_.num_leaves));
+
+  // ---- root ----
+  {
+    HistTask t; t.slot = 0; t.begin = 0; t.count = n_; t.buffer = 0; t.block_begin = 0; t.pad0 = t.pad1 = 0;
+    ha.rows_per_block = ChooseRowsPerBlock(n_); t.num_blocks = (n_ + ha.rows_per_block - 1) / ha.rows_per_block;
+    FindChild fc; fc.leaf = 0; fc.slot = 0; fc.other_slot = 0; fc.is_larger = 0;
+    memcpy(hb, &t, sizeof(t)); memcpy(hb + sizeof(t), &fc, sizeof(fc));
+    FB_CUDA(cudaMemcpyAsync(db, hb, sizeof(t) + sizeof(fc), cudaMemcpyHostToDevice, stream_));
+    FB_CUDA(cudaMemcpyAsync(hist_tasks_.get(), db, sizeof(t), cudaMemcpyDeviceToDevice, stream_));
+    ha.num_tasks = 1; ha.total_blocks = t.num_blocks; ha.identity_root = 1;
+    clock_.Begin(st_hist_, stream_);
+    if (quant_) LaunchHistConstructQuant(ha, stream_); else LaunchHistConstructFloat(ha, stream_);
+    clock_.End(stream_);
+    fa.children = reinterpret_cast<const FindChild*>(db + sizeof(t)); fa.num_children = 1;
+    clock_.Begin(st_find_, stream_);
+    LaunchFindSplits(fa, stream_); LaunchReduceBest(fa, stream_);
+    clock_.End(stream_);
+  }
+  ReadBackLevel(1);
+  {
+    const LeafInfo& R = h_leaves_[0];
+    HostLeaf& hl = host_leaves_[0];
+    hl.begin = 0; hl.count = n_; hl.buffer = 0; hl.depth = 0; hl.slot = 0; hl.best = h_best_[0]; hl.valid = true;
+    tree->leaf_value[0] = R.output; tree->leaf_count[0] = R.num_data_global; tree->leaf_weight[0] = R.sum_h;
+  }
+  int next_slot = 1;
+  std::vector<int> frontier = {0};
+  ha.identity_root = 0;
+  while (tree->num_leaves < cfg_.num_leaves && !frontier.empty()) {
+    std::vector<int> cand;
+    for (int l : frontier) if (host_leaves_[l].best.feature >= 0 && host_leaves_[l].best.gain > 0.0) cand.push_back(l);
+    if (cand.empty()) break;
+    const int budget = cfg_.num_leaves - tree->num_leaves;
+    if (static_cast<int>(cand.size()) > budget) {
+      std::stable_sort(cand.begin(), cand.end(), [&](int a, int b) {
+        if (host_leaves_[a].best.gain != host_leaves_[b].best.gain) return host_leaves_[a].best.gain > host_leaves_[b].best.gain;
+        return a < b; });
+      cand.resize(budget);
+      std::sort(cand.begin(), cand.end());
+    }
+    const int S = static_cast<int>(cand.size());
+    PartSplit* ps = reinterpret_cast<PartSplit*>(hb);
+    ChildInit* ci = reinterpret_cast<ChildInit*>(hb + sizeof(PartSplit) * S);
+    FindChild* fc = reinterpret_cast<FindChild*>(hb + (sizeof(PartSplit) + sizeof(ChildInit)) * S);
+    long long total_rows = 0; for (int l : cand) total_rows += host_leaves_[l].count;
+    ha.rows_per_block = ChooseRowsPerBlock(total_rows);
+    int chunk_cursor = 0, block_cursor = 0;
+    std::vector<int> next;
+    for (int s = 0; s < S; ++s) {
+      const int l = cand[s];
+      HostLeaf& P = host_leaves_[l];
+      const SplitRecord& b = P.best;
+      const FeatureMeta& m = train_->feature_meta[b.feature];
+      const BinMapper& bm = *train_->mappers[m.real_index];
+      const int right = tree->Split(l, b.feature, m.real_index, static_cast<uint32_t>(b.threshold), bm.BinToValue(b.threshold), b.left_out, b.right_out,
+                                    b.left_cnt, b.right_cnt, b.left_h, b.right_h, static_cast<float>(b.gain), m.missing_type, b.default_left != 0);
+      tree->internal_count[tree->num_leaves - 2] = h_leaves_[l].num_data_global;
+      PartSplit& q = ps[s];
+      q.leaf = l; q.right_leaf = right; q.begin = P.begin; q.count = P.count; q.buffer = P.buffer; q.group = m.group; q.bundled = m.bundled; q.group_offset = m.group_offset;
+      q.num_bin = m.num_bin; q.most_freq_bin = m.most_freq_bin; q.threshold = b.threshold; q.default_left = b.default_left; q.missing_type = m.missing_type;
+      q.default_bin = m.default_bin; q.is_categorical = 0; for (int w = 0; w < 8; ++w) q.cat_bitset[w] = 0;
+      q.chunk_begin = chunk_cursor; q.num_chunks = (P.count + kPartChunk - 1) / kPartChunk; chunk_cursor += q.num_chunks;
+      ChildInit& c = ci[s];
+      c.smaller_is_left = b.left_cnt <= b.right_cnt ? 1 : 0;
+      const int fresh = next_slot++;
+      c.left_slot = c.smaller_is_left ? fresh : P.slot; c.right_slot = c.smaller_is_left ? P.slot : fresh;
+      c.left_g = b.left_g; c.left_h = b.left_h; c.right_g = b.right_g; c.right_h = b.right_h; c.left_out = b.left_out; c.right_out = b.right_out;
+      c.left_gi = b.left_gi; c.left_hi = b.left_hi;
+      const LeafInfo& PL = h_leaves_[l];
+      c.right_gi = PL.sum_gi - b.left_gi; c.right_hi = PL.sum_hi - b.left_hi;
+      c.hist_block_begin = block_cursor; c.hist_num_blocks = (P.count + ha.rows_per_block - 1) / ha.rows_per_block; block_cursor += c.hist_num_blocks;
+      fc[2 * s].leaf = l; fc[2 * s].slot = c.left_slot; fc[2 * s].other_slot = c.right_slot; fc[2 * s].is_larger = c.smaller_is_left ? 0 : 1;
+      fc[2 * s + 1].leaf = right; fc[2 * s + 1].slot = c.right_slot; fc[2 * s + 1].other_slot = c.left_slot; fc[2 * s + 1].is_larger = c.smaller_is_left ? 1 : 0;
+      HostLeaf& Rl = host_leaves_[right];
+      Rl.slot = c.right_slot; P.slot = c.left_slot;
+      next.push_back(l); next.push_back(right);
+    }
+    const size_t blob_bytes = (sizeof(PartSplit) + sizeof(ChildInit) + 2 * sizeof(FindChild)) * S;
+    FB_CUDA(cudaMemcpyAsync(db, hb, blob_bytes, cudaMemcpyHostToDevice, stream_));
+    PartArgs pa;
+    pa.rows = dd_->rows.get(); pa.row_stride = dd_->row_stride; pa.idx[0] = idx_[0].get(); pa.idx[1] = idx_[1].get();
+    pa.splits = reinterpret_cast<const PartSplit*>(db); pa.num_splits = S; pa.total_chunks = chunk_cursor; pa.bits = bits_.get(); pa.chunk_left = chunk_left_.get();
+    pa.split_left_total = split_left_total_.get(); pa.leaves = leaves_.get(); pa.child_init = reinterpret_cast<const ChildInit*>(db + sizeof(PartSplit) * S);
+    pa.hist_tasks = hist_tasks_.get(); pa.rows_per_block = ha.rows_per_block;
+    clock_.Begin(st_part_, stream_);
+    LaunchPartitionFlags(pa, stream_); LaunchPartitionScanSetup(pa, stream_); LaunchPartitionScatter(pa, stream_);
+    clock_.End(stream_);
+    ha.num_tasks = S; ha.total_blocks = block_cursor;
+    clock_.Begin(st_hist_, stream_);
+    if (quant_) LaunchHistConstructQuant(ha, stream_); else LaunchHistConstructFloat(ha, stream_);
+    clock_.End(stream_);
+    fa.children = reinterpret_cast<const FindChild*>(db + (sizeof(PartSplit) + sizeof(ChildInit)) * S); fa.num_children = 2 * S;
+    clock_.Begin(st_find_, stream_);
+    LaunchFindSplits(fa, stream_); LaunchReduceBest(fa, stream_);
+    clock_.End(stream_);
+    ReadBackLevel(tree->num_leaves);
+    for (int l : next) {
+      const LeafInfo& R = h_leaves_[l];
+      HostLeaf& hl = host_leaves_[l];
+      hl.begin = R.begin; hl.count = R.count; hl.buffer = R.buffer; hl.depth = R.depth; hl.best = h_best_[l]; hl.valid = true;
+      tree->leaf_count[l] = R.num_data_global;
+    }
+    frontier.swap(next);
+  }
+  return tree.release();
+}
+
+void CudaEngine::ReadBackLevel(int num_leaves) {
+  clock_.Begin(st_sync_, stream_);
+  leaves_.Download(h_leaves_.get(), num_leaves, stream_);
+  best_.Download(h_best_.get(), num_leaves, stream_);
+  clock_.End(stream_);
+  FB_CUDA(cudaStreamSynchronize(stream_));
+}
+
+}  // namespace fb

@@ -1,0 +1,167 @@
+// K1q / K1: level-batched histogram construction with shared-memory atomics, and its fusion with
+// the cross-rank reduce-scatter (K1q-RS): the epilogue adds every non-zero bin of the block's tile
+// straight into the slot of the rank that OWNS the bin's feature — a local `red.add.u64`, or the
+// same instruction on a peer pointer over NVLink. No staging buffer, no NCCL call.
+//
+// Parity: src/treelearner/cuda/cuda_histogram_constructor.cu:L1602-1910 (quantized dense construct:
+// packed int32 (g16|h16) shared-memory atomics, rows per block capped so the 16-bit lanes cannot
+// overflow, level-batched launch), L530-832 (full-precision construct), and the staging kernels
+// around ncclAllReduce that this fusion removes (cuda_single_gpu_tree_learner.cu:L584-708).
+//
+// Work mapping: a block owns (task = one leaf's row window chunk, partition = a run of feature
+// groups whose bins fit the shared tile). Items are (row, 4-group word) pairs laid out flat over the
+// block's threads, so a warp reads whole 32-byte sectors of consecutive rows and its lanes hit
+// different features' bins (no same-address serialisation inside a row).
+#include "kernels.cuh"
+
+namespace fb {
+
+namespace {
+
+constexpr int kHistThreads = 256;
+
+__device__ inline int FindTask(const HistTask* tasks, int num_tasks, int block) {
+  int lo = 0, hi = num_tasks - 1;
+  while (lo < hi) { const int m = (lo + hi + 1) >> 1; if (tasks[m].block_begin <= block) lo = m; else hi = m - 1; }
+  return lo;
+}
+
+__device__ inline void FlushBinQuant(const HistDest& d, int slot, int global_bin, long long g, long long h) {
+  const int owner = d.bin_owner[global_bin];
+  hist_q_t* p = static_cast<hist_q_t*>(d.pool[owner]) + static_cast<long long>(slot) * d.slot_stride[owner] + d.bin_local[global_bin];
+  const hist_q_t v = HistQPack(g, h);
+  if (owner == d.rank) atomicAdd(p, v);
+  else atomicAdd_system(p, v);     // red.add.u64 on the peer's memory: the reduce-scatter, bin by bin
+}
+
+template <bool TWO_PHASE>
+__global__ void __launch_bounds__(kHistThreads) HistQuantKernel(HistArgs a) {
+  extern __shared__ int smem_i[];
+  const HistPartition part = a.parts[blockIdx.y];
+  int* s_packed = smem_i;                                        // [bin_count] (g16|h16)
+  int* s_wide = s_packed + part.bin_count;                       // TWO_PHASE: [2 * bin_count] int32 g, int32 h
+  int* s_gstart = TWO_PHASE ? s_wide + 2 * part.bin_count : s_packed + part.bin_count;   // [groups in partition]
+  const int ti = FindTask(a.tasks, a.num_tasks, blockIdx.x);
+  const HistTask task = a.tasks[ti];
+  const int chunk = blockIdx.x - task.block_begin;
+  const long long row0 = static_cast<long long>(chunk) * a.rows_per_block;
+  if (chunk >= task.num_blocks || row0 >= task.count) return;
+  const int nrows = static_cast<int>(min(static_cast<long long>(a.rows_per_block), task.count - row0));
+  const int ngroups = part.group_end - part.group_begin;
+  const int G4 = (ngroups + 3) >> 2;
+  for (int b = threadIdx.x; b < part.bin_count * (TWO_PHASE ? 3 : 1); b += kHistThreads) s_packed[b] = 0;
+  for (int g = threadIdx.x; g < ngroups; g += kHistThreads) s_gstart[g] = a.group_bin_start[part.group_begin + g] - part.bin_begin;
+  __syncthreads();
+  const int* idx = a.idx[task.buffer] + task.begin + row0;
+  const int step_r = kHistThreads / G4, step_w = kHistThreads % G4;
+  for (int sub0 = 0; sub0 < nrows; sub0 += a.sub_rows) {
+    const int sub_n = min(a.sub_rows, nrows - sub0);
+    int r = threadIdx.x / G4, w = threadIdx.x % G4;
+    while (r < sub_n) {
+      const int row = a.identity_root ? static_cast<int>(task.begin + row0 + sub0 + r) : idx[sub0 + r];
+      const uint8_t* rp = a.rows + static_cast<size_t>(row) * a.row_stride;
+      const unsigned int word = *reinterpret_cast<const unsigned int*>(rp + part.group_begin + 4 * w);
+      const int gh = *reinterpret_cast<const int*>(a.gh_base + static_cast<size_t>(row) * a.gh_stride);
+      const int g0 = 4 * w;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (g0 + k < ngroups) atomicAdd(&s_packed[s_gstart[g0 + k] + ((word >> (8 * k)) & 0xFF)], gh);
+      }
+      r += step_r; w += step_w;
+      if (w >= G4) { w -= G4; ++r; }
+    }
+    if (TWO_PHASE) {
+      __syncthreads();
+      for (int b = threadIdx.x; b < part.bin_count; b += kHistThreads) {
+        const int v = s_packed[b];
+        if (v != 0) { const int h = v & 0xFFFF; s_wide[2 * b] += (v - h) >> 16; s_wide[2 * b + 1] += h; s_packed[b] = 0; }
+      }
+      __syncthreads();
+    }
+  }
+  if (!TWO_PHASE) __syncthreads();
+  for (int b = threadIdx.x; b < part.bin_count; b += kHistThreads) {
+    long long g, h;
+    if (TWO_PHASE) { g = s_wide[2 * b]; h = s_wide[2 * b + 1]; }
+    else { const int v = s_packed[b]; h = v & 0xFFFF; g = (v - static_cast<int>(h)) >> 16; }
+    if (g != 0 || h != 0) FlushBinQuant(a.dest, task.slot, part.bin_begin + b, g, h);
+  }
+}
+
+__global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
+  extern __shared__ float smem_f[];
+  const HistPartition part = a.parts[blockIdx.y];
+  float* s_hist = smem_f;                                               // [2 * bin_count]
+  int* s_gstart = reinterpret_cast<int*>(s_hist + 2 * part.bin_count);
+  const int ti = FindTask(a.tasks, a.num_tasks, blockIdx.x);
+  const HistTask task = a.tasks[ti];
+  const int chunk = blockIdx.x - task.block_begin;
+  const long long row0 = static_cast<long long>(chunk) * a.rows_per_block;
+  if (chunk >= task.num_blocks || row0 >= task.count) return;
+  const int nrows = static_cast<int>(min(static_cast<long long>(a.rows_per_block), task.count - row0));
+  const int ngroups = part.group_end - part.group_begin;
+  const int G4 = (ngroups + 3) >> 2;
+  for (int b = threadIdx.x; b < 2 * part.bin_count; b += kHistThreads) s_hist[b] = 0.f;
+  for (int g = threadIdx.x; g < ngroups; g += kHistThreads) s_gstart[g] = a.group_bin_start[part.group_begin + g] - part.bin_begin;
+  __syncthreads();
+  const int* idx = a.idx[task.buffer] + task.begin + row0;
+  const int step_r = kHistThreads / G4, step_w = kHistThreads % G4;
+  int r = threadIdx.x / G4, w = threadIdx.x % G4;
+  while (r < nrows) {
+    const int row = a.identity_root ? static_cast<int>(task.begin + row0 + r) : idx[r];
+    const uint8_t* rp = a.rows + static_cast<size_t>(row) * a.row_stride;
+    const unsigned int word = *reinterpret_cast<const unsigned int*>(rp + part.group_begin + 4 * w);
+    const float2 gh = *reinterpret_cast<const float2*>(a.gh_base + static_cast<size_t>(row) * a.gh_stride);
+    const int g0 = 4 * w;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (g0 + k < ngroups) {
+        const int b = s_gstart[g0 + k] + ((word >> (8 * k)) & 0xFF);
+        atomicAdd(&s_hist[2 * b], gh.x); atomicAdd(&s_hist[2 * b + 1], gh.y);
+      }
+    }
+    r += step_r; w += step_w;
+    if (w >= G4) { w -= G4; ++r; }
+  }
+  __syncthreads();
+  const HistDest& d = a.dest;
+  for (int b = threadIdx.x; b < part.bin_count; b += kHistThreads) {
+    const float g = s_hist[2 * b], h = s_hist[2 * b + 1];
+    if (g == 0.f && h == 0.f) continue;
+    const int gb = part.bin_begin + b, owner = d.bin_owner[gb];
+    double* p = static_cast<double*>(d.pool[owner]) + 2 * (static_cast<long long>(task.slot) * d.slot_stride[owner] + d.bin_local[gb]);
+    if (owner == d.rank) { atomicAdd(p, static_cast<double>(g)); atomicAdd(p + 1, static_cast<double>(h)); }
+    else { atomicAdd_system(p, static_cast<double>(g)); atomicAdd_system(p + 1, static_cast<double>(h)); }
+  }
+}
+
+}  // namespace
+
+void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
+  if (a.total_blocks <= 0 || a.num_tasks <= 0) return;
+  const bool two_phase = a.rows_per_block > a.sub_rows;
+  int max_groups = 0;
+  // shared bytes: packed (+ wide) + group starts; sized for the largest partition
+  const size_t sm = static_cast<size_t>(a.max_part_bins) * (two_phase ? 12 : 4) + static_cast<size_t>(a.num_groups) * 4;
+  (void)max_groups;
+  dim3 grid(a.total_blocks, a.num_parts);
+  if (two_phase) {
+    static bool attr = false; if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr = true; }
+    HistQuantKernel<true><<<grid, kHistThreads, sm, s>>>(a);
+  } else {
+    static bool attr = false; if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr = true; }
+    HistQuantKernel<false><<<grid, kHistThreads, sm, s>>>(a);
+  }
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+
+void LaunchHistConstructFloat(const HistArgs& a, cudaStream_t s) {
+  if (a.total_blocks <= 0 || a.num_tasks <= 0) return;
+  const size_t sm = static_cast<size_t>(a.max_part_bins) * 8 + static_cast<size_t>(a.num_groups) * 4;
+  static bool attr = false; if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistFloatKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr = true; }
+  dim3 grid(a.total_blocks, a.num_parts);
+  HistFloatKernel<<<grid, kHistThreads, sm, s>>>(a);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+
+}  // namespace fb

@@ -1,0 +1,127 @@
+// Launcher declarations of every device kernel of the training and prediction paths.
+// One launcher per kernel (or fused kernel); the engine and the kernel-level test API call these.
+#pragma once
+#include "device_common.cuh"
+#include "fb/learner.h"
+
+namespace fb {
+
+// ------------------------------------------------------------- objective ----
+struct ObjDesc {
+  int kind;          // ObjKind
+  int num_class;
+  double p0, p1, p2; // binary: sigmoid, neg weight, pos weight; lambdarank: sigmoid, norm, truncation; others: their one parameter
+  int max_docs;      // lambdarank: largest query
+};
+
+void LaunchObjectiveGradients(const ObjDesc& d, const float* score, const float* label, const float* weight, const int* qb, int num_queries,
+                              const double* label_gain, int num_gain, int n, float* grad, float* hess, float* maxbuf, cudaStream_t s);
+void LaunchAbsMax(const float* grad, const float* hess, int n, int num_class, float* maxbuf, cudaStream_t s);
+void LaunchQuantize(const float* grad, const float* hess, int n, const float* maxbuf, const float* global_max, int bins, bool stochastic, uint32_t seed,
+                    uint32_t iter_key, uint64_t global_row_offset, uint8_t* gh_base, int gh_stride, float* scales_out, long long* root_sums, cudaStream_t s);
+void LaunchInterleave(const float* grad, const float* hess, int n, float2* gh2, double* partial, int partial_capacity, double* root_sums_d, cudaStream_t s);
+
+// ------------------------------------------------------------- histogram ----
+// Where a histogram bin lives: owner rank and index inside that rank's slot. With one rank the
+// map is the identity. Peer pools are device pointers mapped into this process (CUDA IPC).
+struct HistDest {
+  void* pool[8];            // pool base per rank (this rank's own pointer at [rank])
+  long long slot_stride[8]; // bins per slot of each rank's pool
+  const unsigned char* bin_owner;  // [num_total_bin]
+  const int* bin_local;            // [num_total_bin]
+  int num_ranks, rank;
+};
+
+struct HistArgs {
+  const uint8_t* rows; int row_stride; int num_groups;
+  const uint8_t* gh_base; int gh_stride;
+  const int* idx[2];
+  const HistTask* tasks; int num_tasks; int total_blocks;
+  const HistPartition* parts; int num_parts; int max_part_bins;
+  const int* group_bin_start;
+  int rows_per_block; int sub_rows;
+  int identity_root;        // 1: task rows are 0..count-1 (no index load)
+  HistDest dest;
+};
+void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s);
+void LaunchHistConstructFloat(const HistArgs& a, cudaStream_t s);
+// tcgen05 one-hot instance (same arguments, same result); returns false when the shape is outside what it covers
+bool LaunchHistConstructQuantTC(const HistArgs& a, cudaStream_t s);
+
+// ------------------------------------------------------------ split find ----
+struct FindChild { int leaf; int slot; int other_slot; int is_larger; };   // larger: bins = pool[slot] - pool[other_slot], written back to pool[slot]
+
+struct CandLite {      // best threshold of one (child, feature)
+  double gain; int feature; int threshold; int default_left; int left_cnt;
+  long long left_gi, left_hi; double left_g, left_h;
+};
+
+struct FindArgs {
+  const FindChild* children; int num_children;
+  const int* features; int num_features;          // inner feature indices searched on this rank (owned and sampled)
+  const int* sub_features; int num_sub_features;  // owned features that are not sampled: larger-child subtraction only
+  const FeatureMeta* meta;
+  const int* bin_local;                           // histogram slot index -> index inside this rank's pool slot
+  void* pool; long long slot_stride;
+  const LeafInfo* leaves;
+  const float* scales;                            // quantized: (g_scale, h_scale) of this tree
+  SplitParams params;
+  CandLite* cand;                                 // [num_children x num_features]
+  SplitRecord* best;                              // [leaf]
+  int quant;
+};
+void LaunchFindSplits(const FindArgs& a, cudaStream_t s);      // per (child, feature) search + in-place larger-child subtraction
+void LaunchReduceBest(const FindArgs& a, cudaStream_t s);      // per child argmax over features -> SplitRecord
+
+// ------------------------------------------------------------- partition ----
+constexpr int kPartChunk = 2048;
+struct ChildInit {     // host-decided child bookkeeping of one split
+  int left_slot, right_slot;       // histogram slots of the children
+  int smaller_is_left;
+  double left_g, left_h, right_g, right_h, left_out, right_out;
+  long long left_gi, left_hi, right_gi, right_hi;
+  int hist_block_begin, hist_num_blocks;
+};
+struct PartArgs {
+  const uint8_t* rows; int row_stride;
+  int* idx[2];
+  const PartSplit* splits; int num_splits; int total_chunks;
+  unsigned int* bits;        // kPartChunk/32 words per chunk
+  int* chunk_left;           // lefts per chunk, then exclusive offsets
+  int* split_left_total;     // [num_splits]
+  LeafInfo* leaves;
+  const ChildInit* child_init;
+  HistTask* hist_tasks;      // one per split: the smaller child
+  int rows_per_block;
+};
+void LaunchPartitionFlags(const PartArgs& a, cudaStream_t s);
+void LaunchPartitionScanSetup(const PartArgs& a, cudaStream_t s);
+void LaunchPartitionScatter(const PartArgs& a, cudaStream_t s);
+void LaunchInitIndices(int* idx, int n, cudaStream_t s);
+
+// ----------------------------------------------------------------- score ----
+void LaunchAddLeafOutputs(const LeafInfo* leaves, const double* leaf_value, int num_leaves, const int* idx0, const int* idx1, float* score, cudaStream_t s);
+void LaunchAddConstant(float* score, int n, float v, cudaStream_t s);
+
+// Device form of one tree for traversal.
+struct DevTree {
+  int num_leaves;
+  const int* left; const int* right; const int* split_feature; const int* split_group;
+  const float* threshold; const int* threshold_bin; const signed char* decision; const float* leaf_value;
+  const int* default_bin; const int* nan_bin; const int* bundled; const int* group_offset; const int* most_freq_bin; const int* num_bin;
+};
+// score[i] += scale * tree(row i) on binned rows (validation sets, out-of-bag rows, rollback)
+void LaunchAddTreeBinned(const DevTree& t, const uint8_t* rows, int row_stride, int n, float scale, float* score, cudaStream_t s);
+
+// Packed forest for raw-feature prediction: nodes of all trees in one array.
+struct ForestNode { float threshold; int feature; int left; int right; int flags; };   // flags: bit0 default_left, bits1-2 missing type, bit3 leaf; leaf: threshold = value
+template <typename T>
+void LaunchPredictRaw(const ForestNode* nodes, const int* tree_root, int num_trees, int num_class, const T* data, int nrow, int ncol, bool row_major,
+                      float* out /* [num_class x nrow] */, bool average, cudaStream_t s);
+void LaunchConvertOutput(int obj_kind, double sigmoid, float* out, int nrow, int num_class, cudaStream_t s);
+
+// --------------------------------------------------------------- metrics ----
+void LaunchPointwiseMetric(int metric_kind, int obj_kind, double sigmoid, const float* score, const float* label, const float* weight, int n, int num_class,
+                           double* partial, int partial_capacity, double* out2, cudaStream_t s);
+
+}  // namespace fb

@@ -1,0 +1,103 @@
+// Kernel-level C entry points: each runs ONE device kernel of the training path on caller-owned
+// device buffers, so that the numerics tests can compare it with a plain PyTorch reference.
+#include "kernels.cuh"
+
+using namespace fb;
+
+namespace {
+thread_local std::string g_ops_error;
+std::vector<HistPartition> MakePartitions(const std::vector<int>& gstart, const std::vector<int>& gbins, int max_bins) {
+  std::vector<HistPartition> parts; const int G = static_cast<int>(gbins.size()); int g = 0;
+  while (g < G) {
+    HistPartition p; p.group_begin = g; p.bin_begin = gstart[g]; p.bin_count = 0; int e = g;
+    while (e < G) { int e4 = std::min(G, e + 4), add = 0; for (int k = e; k < e4; ++k) add += gbins[k]; if (p.bin_count + add > max_bins && e > g) break; p.bin_count += add; e = e4; }
+    p.group_end = e; parts.push_back(p); g = e;
+  }
+  return parts;
+}
+}  // namespace
+
+#define OPS_BEGIN() try {
+#define OPS_END() } catch (std::exception& ex) { g_ops_error = ex.what(); return -1; } return 0;
+
+extern "C" {
+
+const char* FB_OpsLastError() { return g_ops_error.c_str(); }
+
+// Histogram of rows idx[0..count) (or rows 0..count-1 when idx is null).
+// quant != 0: gh is int32 packed (g16|h16) per row, out is int64 [total_bins x 2] (grad, hess sums).
+// quant == 0: gh is float2 per row, out is float64 [total_bins x 2].
+int FB_OpHistogram(const uint8_t* rows, int row_stride, int num_groups, const void* gh, int gh_stride, const int* idx, int count,
+                   const int* group_num_bin_host, int quant, int quant_bins, int rows_per_block, int max_part_bins, void* out) {
+  OPS_BEGIN();
+  std::vector<int> gbins(group_num_bin_host, group_num_bin_host + num_groups), gstart(num_groups);
+  int total = 0; for (int g = 0; g < num_groups; ++g) { gstart[g] = total; total += gbins[g]; }
+  auto parts = MakePartitions(gstart, gbins, max_part_bins > 0 ? max_part_bins : 6144);
+  int mpb = 0; for (auto& p : parts) mpb = std::max(mpb, p.bin_count);
+  cudaStream_t s = 0;
+  DevBuf<HistPartition> d_parts; d_parts.Upload(parts, s);
+  DevBuf<int> d_gstart; d_gstart.Upload(gstart, s);
+  std::vector<unsigned char> owner(total, 0); std::vector<int> local(total); for (int b = 0; b < total; ++b) local[b] = b;
+  DevBuf<unsigned char> d_owner; d_owner.Upload(owner, s); DevBuf<int> d_local; d_local.Upload(local, s);
+  HistTask t; t.slot = 0; t.begin = 0; t.count = count; t.buffer = 0; t.block_begin = 0; t.pad0 = t.pad1 = 0;
+  if (rows_per_block <= 0) rows_per_block = 2048;
+  t.num_blocks = (count + rows_per_block - 1) / rows_per_block;
+  DevBuf<HistTask> d_task; d_task.Upload(&t, 1, s);
+  DevBuf<char> pool; pool.Alloc(static_cast<size_t>(total) * (quant ? 8 : 16)); pool.Zero(s);
+  HistArgs a;
+  a.rows = rows; a.row_stride = row_stride; a.num_groups = num_groups; a.gh_base = static_cast<const uint8_t*>(gh); a.gh_stride = gh_stride;
+  a.idx[0] = idx; a.idx[1] = idx; a.tasks = d_task.get(); a.num_tasks = 1; a.total_blocks = t.num_blocks; a.parts = d_parts.get(); a.num_parts = static_cast<int>(parts.size());
+  a.max_part_bins = mpb; a.group_bin_start = d_gstart.get(); a.rows_per_block = rows_per_block;
+  const int qb = std::max(2, quant_bins);
+  a.sub_rows = quant ? std::max(1, std::min(65535 / qb, 32767 / std::max(1, qb / 2))) : (1 << 30);
+  a.identity_root = idx == nullptr ? 1 : 0;
+  for (int r = 0; r < 8; ++r) { a.dest.pool[r] = nullptr; a.dest.slot_stride[r] = 0; }
+  a.dest.pool[0] = pool.get(); a.dest.slot_stride[0] = total; a.dest.bin_owner = d_owner.get(); a.dest.bin_local = d_local.get(); a.dest.num_ranks = 1; a.dest.rank = 0;
+  if (quant) LaunchHistConstructQuant(a, s); else LaunchHistConstructFloat(a, s);
+  FB_CUDA(cudaStreamSynchronize(s));
+  if (quant) {
+    std::vector<hist_q_t> h(total); FB_CUDA(cudaMemcpy(h.data(), pool.get(), total * 8, cudaMemcpyDeviceToHost));
+    std::vector<long long> o(2 * static_cast<size_t>(total)); for (int b = 0; b < total; ++b) { o[2 * b] = HistQGrad(h[b]); o[2 * b + 1] = HistQHess(h[b]); }
+    FB_CUDA(cudaMemcpy(out, o.data(), o.size() * 8, cudaMemcpyHostToDevice));
+  } else FB_CUDA(cudaMemcpy(out, pool.get(), static_cast<size_t>(total) * 16, cudaMemcpyDeviceToDevice));
+  OPS_END();
+}
+
+// Quantize float gradients into packed words; returns scales (2 floats) and integer sums (2 int64) on the device.
+int FB_OpQuantize(const float* grad, const float* hess, int n, int bins, int stochastic, unsigned int seed, unsigned int iter_key, unsigned long long row_offset,
+                  int* out_packed, float* out_scales, long long* out_sums) {
+  OPS_BEGIN();
+  cudaStream_t s = 0;
+  DevBuf<float> maxbuf; maxbuf.Alloc(2);
+  LaunchAbsMax(grad, hess, n, 1, maxbuf.get(), s);
+  LaunchQuantize(grad, hess, n, maxbuf.get(), nullptr, bins, stochastic != 0, seed, iter_key, row_offset, reinterpret_cast<uint8_t*>(out_packed), 4, out_scales, out_sums, s);
+  FB_CUDA(cudaStreamSynchronize(s));
+  OPS_END();
+}
+
+// Stable partition of idx[0..count) by "bin(row, group) <= threshold"; writes the result to out_idx and the left count to *left_count (host).
+int FB_OpPartition(const uint8_t* rows, int row_stride, const int* idx, int count, int group, int threshold, int default_left, int missing_type, int default_bin,
+                   int num_bin, int* out_idx, int* left_count) {
+  OPS_BEGIN();
+  cudaStream_t s = 0;
+  PartSplit sp; memset(&sp, 0, sizeof(sp));
+  sp.leaf = 0; sp.right_leaf = 1; sp.begin = 0; sp.count = count; sp.buffer = 0; sp.group = group; sp.num_bin = num_bin; sp.threshold = threshold; sp.default_left = default_left;
+  sp.missing_type = missing_type; sp.default_bin = default_bin; sp.chunk_begin = 0; sp.num_chunks = (count + kPartChunk - 1) / kPartChunk;
+  ChildInit ci; memset(&ci, 0, sizeof(ci)); ci.left_slot = 0; ci.right_slot = 1; ci.smaller_is_left = 1; ci.hist_num_blocks = 1;
+  LeafInfo leaf; memset(&leaf, 0, sizeof(leaf)); leaf.count = count;
+  DevBuf<PartSplit> d_sp; d_sp.Upload(&sp, 1, s); DevBuf<ChildInit> d_ci; d_ci.Upload(&ci, 1, s);
+  DevBuf<LeafInfo> d_leaves; d_leaves.Alloc(2); d_leaves.Upload(&leaf, 1, s); d_leaves.Alloc(2);
+  DevBuf<LeafInfo> d_leaves2; d_leaves2.Alloc(2); FB_CUDA(cudaMemcpyAsync(d_leaves2.get(), d_leaves.get(), sizeof(LeafInfo), cudaMemcpyDeviceToDevice, s));
+  DevBuf<unsigned int> bits; bits.Alloc(static_cast<size_t>(sp.num_chunks + 1) * (kPartChunk / 32));
+  DevBuf<int> chunk_left; chunk_left.Alloc(sp.num_chunks + 1); DevBuf<int> left_total; left_total.Alloc(1); DevBuf<HistTask> tasks; tasks.Alloc(1);
+  PartArgs a; a.rows = rows; a.row_stride = row_stride; a.idx[0] = const_cast<int*>(idx); a.idx[1] = out_idx; a.splits = d_sp.get(); a.num_splits = 1; a.total_chunks = sp.num_chunks;
+  a.bits = bits.get(); a.chunk_left = chunk_left.get(); a.split_left_total = left_total.get(); a.leaves = d_leaves2.get(); a.child_init = d_ci.get(); a.hist_tasks = tasks.get(); a.rows_per_block = 2048;
+  LaunchPartitionFlags(a, s); LaunchPartitionScanSetup(a, s); LaunchPartitionScatter(a, s);
+  FB_CUDA(cudaMemcpyAsync(left_count, left_total.get(), sizeof(int), cudaMemcpyDeviceToHost, s));
+  FB_CUDA(cudaStreamSynchronize(s));
+  OPS_END();
+}
+
+int FB_OpLaunchCount(long long* out) { *out = LaunchCounter().load(); return 0; }
+
+}  // extern "C"

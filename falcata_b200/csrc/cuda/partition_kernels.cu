@@ -1,0 +1,165 @@
+// K5: level-batched stable row partition. Three launches per level for ALL splitting leaves:
+//   flags   : per 2048-row chunk, go-left ballot words + left count
+//   scan    : per split, exclusive scan of its chunks' counts; child windows, leaf records and the
+//             construct task of the smaller child are written here (no host round trip)
+//   scatter : popc-ranked stable scatter into the other index buffer (ping-pong, no copy back)
+// Parity: src/treelearner/cuda/cuda_data_partition.cu:L1380-1433 (ballot bit vectors, flat grid),
+// L1479 (per-split scan), L1562-1617 (stable scatter), L1681-1840 (tree-structure bookkeeping),
+// L1921 (copy back — removed here by the ping-pong buffers).
+#include "kernels.cuh"
+
+namespace fb {
+
+namespace {
+
+constexpr int kPartThreads = 256;
+constexpr int kRowsPerThread = kPartChunk / kPartThreads;   // 8
+constexpr int kWordsPerChunk = kPartChunk / 32;             // 64
+
+__device__ inline int FindSplitOfChunk(const PartSplit* splits, int num_splits, int chunk) {
+  int lo = 0, hi = num_splits - 1;
+  while (lo < hi) { const int m = (lo + hi + 1) >> 1; if (splits[m].chunk_begin <= chunk) lo = m; else hi = m - 1; }
+  return lo;
+}
+
+__device__ inline bool GoLeft(const PartSplit& sp, int gb) {
+  int fb = gb;
+  if (sp.bundled) {
+    const int rel = gb - sp.group_offset;
+    fb = (rel < 0 || rel >= sp.num_bin - 1) ? sp.most_freq_bin : (rel >= sp.most_freq_bin ? rel + 1 : rel);
+  }
+  if (sp.is_categorical) return (sp.cat_bitset[(fb >> 5) & 7] >> (fb & 31)) & 1;
+  if ((sp.missing_type == 1 && fb == sp.default_bin) || (sp.missing_type == 2 && fb == sp.num_bin - 1)) return sp.default_left != 0;
+  return fb <= sp.threshold;
+}
+
+__global__ void __launch_bounds__(kPartThreads) PartitionFlagsKernel(PartArgs a) {
+  const int chunk = blockIdx.x;
+  const int si = FindSplitOfChunk(a.splits, a.num_splits, chunk);
+  const PartSplit sp = a.splits[si];
+  const int local_chunk = chunk - sp.chunk_begin;
+  if (local_chunk >= sp.num_chunks) return;
+  const int* idx = a.idx[sp.buffer] + sp.begin;
+  const int pos0 = local_chunk * kPartChunk;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int cnt = 0;
+#pragma unroll
+  for (int k = 0; k < kRowsPerThread; ++k) {
+    const int pos = pos0 + k * kPartThreads + threadIdx.x;
+    bool left = false;
+    if (pos < sp.count) {
+      const int row = idx[pos];
+      left = GoLeft(sp, a.rows[static_cast<size_t>(row) * a.row_stride + sp.group]);
+    }
+    const unsigned int word = __ballot_sync(0xffffffffu, left);
+    if (lane == 0) { a.bits[static_cast<size_t>(chunk) * kWordsPerChunk + k * (kPartThreads / 32) + warp] = word; cnt += __popc(word); }
+  }
+  __shared__ int s_cnt[kPartThreads / 32];
+  if (lane == 0) s_cnt[warp] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) { int t = 0; for (int w = 0; w < kPartThreads / 32; ++w) t += s_cnt[w]; a.chunk_left[chunk] = t; }
+}
+
+__global__ void __launch_bounds__(kPartThreads) PartitionScanSetupKernel(PartArgs a) {
+  const int si = blockIdx.x;
+  const PartSplit sp = a.splits[si];
+  __shared__ int s_scan[kPartThreads];
+  __shared__ int s_carry;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  for (int c0 = 0; c0 < sp.num_chunks; c0 += kPartThreads) {
+    const int c = c0 + threadIdx.x;
+    const int v = c < sp.num_chunks ? a.chunk_left[sp.chunk_begin + c] : 0;
+    s_scan[threadIdx.x] = v;
+    __syncthreads();
+    for (int o = 1; o < kPartThreads; o <<= 1) {
+      const int t = threadIdx.x >= o ? s_scan[threadIdx.x - o] : 0;
+      __syncthreads();
+      s_scan[threadIdx.x] += t;
+      __syncthreads();
+    }
+    if (c < sp.num_chunks) a.chunk_left[sp.chunk_begin + c] = s_carry + s_scan[threadIdx.x] - v;   // exclusive offset
+    __syncthreads();
+    if (threadIdx.x == kPartThreads - 1) s_carry += s_scan[threadIdx.x];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const int nl = s_carry, nr = sp.count - nl;
+    a.split_left_total[si] = nl;
+    const ChildInit ci = a.child_init[si];
+    const LeafInfo parent = a.leaves[sp.leaf];
+    LeafInfo L = parent, R = parent;
+    L.count = nl; R.begin = parent.begin + nl; R.count = nr;
+    L.buffer = R.buffer = sp.buffer ^ 1;
+    L.depth = R.depth = parent.depth + 1;
+    L.hist_slot = ci.left_slot; R.hist_slot = ci.right_slot;
+    L.sum_g = ci.left_g; L.sum_h = ci.left_h; L.sum_gi = ci.left_gi; L.sum_hi = ci.left_hi; L.output = ci.left_out;
+    R.sum_g = ci.right_g; R.sum_h = ci.right_h; R.sum_gi = ci.right_gi; R.sum_hi = ci.right_hi; R.output = ci.right_out;
+    L.num_data_global = nl; R.num_data_global = nr;   // single rank: exact; multi-rank: summed over ranks by the exchange that follows
+    a.leaves[sp.leaf] = L; a.leaves[sp.right_leaf] = R;
+    HistTask t;
+    const LeafInfo& S = ci.smaller_is_left ? L : R;
+    t.slot = S.hist_slot; t.begin = S.begin; t.count = S.count; t.buffer = S.buffer; t.block_begin = ci.hist_block_begin; t.num_blocks = ci.hist_num_blocks; t.pad0 = t.pad1 = 0;
+    a.hist_tasks[si] = t;
+  }
+}
+
+__global__ void __launch_bounds__(kPartThreads) PartitionScatterKernel(PartArgs a) {
+  const int chunk = blockIdx.x;
+  const int si = FindSplitOfChunk(a.splits, a.num_splits, chunk);
+  const PartSplit sp = a.splits[si];
+  const int local_chunk = chunk - sp.chunk_begin;
+  if (local_chunk >= sp.num_chunks) return;
+  const int* src = a.idx[sp.buffer] + sp.begin;
+  int* dst = a.idx[sp.buffer ^ 1] + sp.begin;
+  const int total_left = a.split_left_total[si];
+  const int left_before = a.chunk_left[chunk];
+  const int pos0 = local_chunk * kPartChunk;
+  const int right_before = pos0 - left_before;
+  __shared__ unsigned int s_bits[kWordsPerChunk];
+  __shared__ int s_pref[kWordsPerChunk];
+  if (threadIdx.x < kWordsPerChunk) s_bits[threadIdx.x] = a.bits[static_cast<size_t>(chunk) * kWordsPerChunk + threadIdx.x];
+  __syncthreads();
+  if (threadIdx.x == 0) { int acc = 0; for (int w = 0; w < kWordsPerChunk; ++w) { s_pref[w] = acc; acc += __popc(s_bits[w]); } }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int k = 0; k < kRowsPerThread; ++k) {
+    const int in_chunk = k * kPartThreads + threadIdx.x;
+    const int pos = pos0 + in_chunk;
+    if (pos >= sp.count) continue;
+    const int w = k * (kPartThreads / 32) + warp;
+    const unsigned int word = s_bits[w];
+    const int lefts_before_me = s_pref[w] + __popc(word & ((1u << lane) - 1u));
+    const int row = src[pos];
+    if ((word >> lane) & 1u) dst[left_before + lefts_before_me] = row;
+    else dst[total_left + right_before + (in_chunk - lefts_before_me)] = row;
+  }
+}
+
+__global__ void InitIndicesKernel(int* idx, int n) { const int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < n) idx[i] = i; }
+
+}  // namespace
+
+void LaunchPartitionFlags(const PartArgs& a, cudaStream_t s) {
+  if (a.total_chunks <= 0) return;
+  PartitionFlagsKernel<<<a.total_chunks, kPartThreads, 0, s>>>(a);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+void LaunchPartitionScanSetup(const PartArgs& a, cudaStream_t s) {
+  if (a.num_splits <= 0) return;
+  PartitionScanSetupKernel<<<a.num_splits, kPartThreads, 0, s>>>(a);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+void LaunchPartitionScatter(const PartArgs& a, cudaStream_t s) {
+  if (a.total_chunks <= 0) return;
+  PartitionScatterKernel<<<a.total_chunks, kPartThreads, 0, s>>>(a);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+void LaunchInitIndices(int* idx, int n, cudaStream_t s) {
+  if (n <= 0) return;
+  InitIndicesKernel<<<(n + 255) / 256, 256, 0, s>>>(idx, n);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+
+}  // namespace fb

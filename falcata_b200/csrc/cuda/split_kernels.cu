@@ -1,0 +1,219 @@
+// K3 + K4 (K4q): threshold search on the owned feature slice, with the larger child's histogram
+// formed on the fly as parent - smaller and written back in place (no separate subtraction pass).
+// Parity: src/treelearner/cuda/cuda_best_split_finder.cu:L417-970 (per task prefix scan, gain,
+// min_data / min_hessian, missing-value directions), L3185-3285 (per-leaf argmax with the CPU's
+// tie order), cuda_histogram_constructor.cu:L2641-3107 (subtract / fix kernels that are folded in).
+// The candidate math is fb/split_math.h, shared with the host learner: with integer histograms the
+// two produce bit-identical gains.
+#include "kernels.cuh"
+
+namespace fb {
+
+namespace {
+
+constexpr int kFindThreads = 256;
+constexpr int kWarpsPerBlock = kFindThreads / 32;
+
+struct Acc {   // prefix accumulator of one lane
+  long long gi, hi; double gd, hd; int c;
+};
+
+template <bool QUANT>
+__device__ inline void LoadBin(const void* child, const void* other, bool larger, int j, long long* gi, long long* hi, double* gd, double* hd,
+                               hist_q_t* raw_q, double2* raw_d) {
+  if (QUANT) {
+    hist_q_t v = static_cast<const hist_q_t*>(child)[j];
+    if (larger) v -= static_cast<const hist_q_t*>(other)[j];
+    *raw_q = v; *gi = HistQGrad(v); *hi = HistQHess(v);
+  } else {
+    double2 v = static_cast<const double2*>(child)[j];
+    if (larger) { const double2 o = static_cast<const double2*>(other)[j]; v.x -= o.x; v.y -= o.y; }
+    *raw_d = v; *gd = v.x; *hd = v.y;
+  }
+}
+
+template <bool QUANT>
+__global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int fi = blockIdx.y * kWarpsPerBlock + warp;
+  if (fi >= a.num_features + a.num_sub_features) return;
+  const bool search = fi < a.num_features;
+  const int f = search ? a.features[fi] : a.sub_features[fi - a.num_features];
+  const FindChild ch = a.children[blockIdx.x];
+  if (!search && !ch.is_larger) return;
+  const FeatureMeta m = a.meta[f];
+  const LeafInfo leaf = a.leaves[ch.leaf];
+  const int nb = m.num_bin;
+  const int nstored = m.bundled ? nb - 1 : nb;
+  const long long base = a.bin_local[m.hist_offset];
+  const size_t esz = QUANT ? sizeof(hist_q_t) : sizeof(double2);
+  char* child = static_cast<char*>(a.pool) + (static_cast<long long>(ch.slot) * a.slot_stride + base) * esz;
+  const char* other = static_cast<const char*>(a.pool) + (static_cast<long long>(ch.other_slot) * a.slot_stride + base) * esz;
+  const bool larger = ch.is_larger != 0;
+
+  if (!search || m.bin_type != 0) {
+    // subtraction only (feature not sampled for this tree, or categorical: searched on the host path)
+    if (larger) for (int j = lane; j < nstored; j += 32) {
+      long long gi, hi; double gd, hd; hist_q_t rq; double2 rd;
+      LoadBin<QUANT>(child, other, true, j, &gi, &hi, &gd, &hd, &rq, &rd);
+      if (QUANT) reinterpret_cast<hist_q_t*>(child)[j] = rq; else reinterpret_cast<double2*>(child)[j] = rd;
+    }
+    if (search && lane == 0) { CandLite c; c.gain = -1.0 / 0.0; c.feature = -1; c.threshold = 0; c.default_left = 1; c.left_cnt = 0; c.left_gi = c.left_hi = 0; c.left_g = c.left_h = 0; a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + fi] = c; }
+    return;
+  }
+
+  LeafScanInfo L;
+  L.sum_g = leaf.sum_g; L.sum_h = leaf.sum_h; L.sum_gi = leaf.sum_gi; L.sum_hi = leaf.sum_hi; L.num_data = leaf.num_data_global;
+  L.parent_output = leaf.output; L.g_scale = QUANT ? static_cast<double>(a.scales[0]) : 1.0; L.h_scale = QUANT ? static_cast<double>(a.scales[1]) : 1.0;
+  L.cnt_factor = FB_DIV(static_cast<double>(L.num_data), L.sum_h);
+  if (a.params.max_delta_step <= 0.0 && a.params.path_smooth <= 0.0)
+    L.min_gain_shift = FB_ADD(LeafGain(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), a.params, L.num_data, leaf.output), a.params.min_gain_to_split);
+  else
+    L.min_gain_shift = FB_ADD(LeafGainGivenOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), a.params, leaf.output), a.params.min_gain_to_split);
+
+  const bool two_pass = m.missing_type != 0 && nb > 2;
+  const int skip = two_pass ? (m.missing_type == 1 ? m.default_bin : nb - 1) : -1;
+  const int mfb = m.bundled ? m.most_freq_bin : -1;
+
+  // pre-pass: the un-stored most-frequent bin of a bundled feature = leaf total - sum of stored bins
+  long long mfb_gi = 0, mfb_hi = 0; double mfb_gd = 0, mfb_hd = 0;
+  if (m.bundled) {
+    long long sgi = 0, shi = 0; double sgd = 0, shd = 0;
+    for (int j = lane; j < nstored; j += 32) {
+      long long gi = 0, hi = 0; double gd = 0, hd = 0; hist_q_t rq; double2 rd;
+      LoadBin<QUANT>(child, other, larger, j, &gi, &hi, &gd, &hd, &rq, &rd);
+      sgi += gi; shi += hi; sgd += gd; shd += hd;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      sgi += __shfl_xor_sync(0xffffffffu, sgi, o); shi += __shfl_xor_sync(0xffffffffu, shi, o);
+      sgd += __shfl_xor_sync(0xffffffffu, sgd, o); shd += __shfl_xor_sync(0xffffffffu, shd, o);
+    }
+    mfb_gi = L.sum_gi - sgi; mfb_hi = L.sum_hi - shi; mfb_gd = L.sum_g - sgd; mfb_hd = L.sum_h - shd;
+  }
+  // mass of the missing-value bin (kept out of the prefix, added on the left in pass 0)
+  long long Mgi = 0, Mhi = 0; double Mgd = 0, Mhd = 0; int Mc = 0;
+  if (skip >= 0) {
+    if (skip == mfb) { Mgi = mfb_gi; Mhi = mfb_hi; Mgd = mfb_gd; Mhd = mfb_hd; }
+    else { hist_q_t rq; double2 rd; LoadBin<QUANT>(child, other, larger, (mfb >= 0 && skip > mfb) ? skip - 1 : skip, &Mgi, &Mhi, &Mgd, &Mhd, &rq, &rd); }
+    const double hreal = QUANT ? FB_MUL(static_cast<double>(Mhi), L.h_scale) : Mhd;
+    Mc = BinCountEstimate(hreal, L.cnt_factor);
+  }
+
+  double best_gain = -1.0 / 0.0; int best_rank = 1 << 30, best_t = 0, best_pass = 0, best_lc = 0;
+  long long best_lgi = 0, best_lhi = 0; double best_lg = 0, best_lh = 0;
+  Acc carry; carry.gi = carry.hi = 0; carry.gd = carry.hd = 0; carry.c = 0;
+  for (int b0 = 0; b0 < nb; b0 += 32) {
+    const int b = b0 + lane;
+    long long gi = 0, hi = 0; double gd = 0, hd = 0; int c = 0;
+    if (b < nb) {
+      if (b == mfb) { gi = mfb_gi; hi = mfb_hi; gd = mfb_gd; hd = mfb_hd; }
+      else {
+        const int j = (mfb >= 0 && b > mfb) ? b - 1 : b;
+        hist_q_t rq; double2 rd;
+        LoadBin<QUANT>(child, other, larger, j, &gi, &hi, &gd, &hd, &rq, &rd);
+        if (larger) { if (QUANT) reinterpret_cast<hist_q_t*>(child)[j] = rq; else reinterpret_cast<double2*>(child)[j] = rd; }
+      }
+      if (b == skip) { gi = hi = 0; gd = hd = 0; }
+      else { const double hreal = QUANT ? FB_MUL(static_cast<double>(hi), L.h_scale) : hd; c = BinCountEstimate(hreal, L.cnt_factor); }
+    }
+    // inclusive warp scan
+    for (int o = 1; o < 32; o <<= 1) {
+      const long long tg = __shfl_up_sync(0xffffffffu, gi, o), th = __shfl_up_sync(0xffffffffu, hi, o);
+      const double dg = __shfl_up_sync(0xffffffffu, gd, o), dh = __shfl_up_sync(0xffffffffu, hd, o);
+      const int tc = __shfl_up_sync(0xffffffffu, c, o);
+      if (lane >= o) { gi += tg; hi += th; gd += dg; hd += dh; c += tc; }
+    }
+    gi += carry.gi; hi += carry.hi; gd += carry.gd; hd += carry.hd; c += carry.c;
+    if (b <= nb - 2) {
+      for (int pass = 0; pass < (two_pass ? 2 : 1); ++pass) {
+        if (b == skip && pass == 1 && m.missing_type == 1) continue;
+        long long lgi = gi, lhi = hi; int lc = c; double lg, lh;
+        const bool addm = pass == 0 && skip >= 0;
+        if (addm) { lgi += Mgi; lhi += Mhi; lc += Mc; }
+        if (QUANT) { lg = FB_MUL(static_cast<double>(lgi), L.g_scale); lh = FB_MUL(static_cast<double>(lhi), L.h_scale); }
+        else { lg = gd + (addm ? Mgd : 0.0); lh = hd + (addm ? Mhd : 0.0); }
+        double lo, ro;
+        const double gain = EvalCandidate(lg, lh, lc, L, a.params, m.monotone, &lo, &ro);
+        if (gain == -1.0 / 0.0) continue;
+        const int rank = ScanRank(pass, b, nb);
+        if (gain > best_gain || (gain == best_gain && rank < best_rank)) {
+          best_gain = gain; best_rank = rank; best_t = b; best_pass = pass; best_lc = lc; best_lgi = lgi; best_lhi = lhi; best_lg = lg; best_lh = lh;
+        }
+      }
+    }
+    carry.gi = __shfl_sync(0xffffffffu, gi, 31); carry.hi = __shfl_sync(0xffffffffu, hi, 31);
+    carry.gd = __shfl_sync(0xffffffffu, gd, 31); carry.hd = __shfl_sync(0xffffffffu, hd, 31); carry.c = __shfl_sync(0xffffffffu, c, 31);
+  }
+  // warp argmax: larger gain, then lower scan rank
+  for (int o = 16; o > 0; o >>= 1) {
+    const double og = __shfl_xor_sync(0xffffffffu, best_gain, o); const int orank = __shfl_xor_sync(0xffffffffu, best_rank, o);
+    const int ot = __shfl_xor_sync(0xffffffffu, best_t, o), op = __shfl_xor_sync(0xffffffffu, best_pass, o), olc = __shfl_xor_sync(0xffffffffu, best_lc, o);
+    const long long ogi = __shfl_xor_sync(0xffffffffu, best_lgi, o), ohi = __shfl_xor_sync(0xffffffffu, best_lhi, o);
+    const double olg = __shfl_xor_sync(0xffffffffu, best_lg, o), olh = __shfl_xor_sync(0xffffffffu, best_lh, o);
+    if (og > best_gain || (og == best_gain && orank < best_rank)) {
+      best_gain = og; best_rank = orank; best_t = ot; best_pass = op; best_lc = olc; best_lgi = ogi; best_lhi = ohi; best_lg = olg; best_lh = olh;
+    }
+  }
+  if (lane == 0) {
+    CandLite c;
+    const bool ok = best_gain != -1.0 / 0.0;
+    c.gain = ok ? FB_MUL(best_gain, static_cast<double>(m.penalty)) : best_gain;
+    c.feature = ok ? f : -1; c.threshold = best_t; c.default_left = best_pass == 0 ? 1 : 0; c.left_cnt = best_lc;
+    c.left_gi = best_lgi; c.left_hi = best_lhi; c.left_g = best_lg; c.left_h = best_lh;
+    a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + fi] = c;
+  }
+}
+
+__global__ void ReduceBestKernel(FindArgs a) {
+  const FindChild ch = a.children[blockIdx.x];
+  const LeafInfo leaf = a.leaves[ch.leaf];
+  __shared__ double s_gain[128]; __shared__ int s_feat[128], s_thr[128], s_idx[128];
+  double bg = -1.0 / 0.0; int bf = -1, bt = 0, bi = -1;
+  for (int k = threadIdx.x; k < a.num_features; k += blockDim.x) {
+    const CandLite c = a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + k];
+    const int rf = c.feature >= 0 ? a.meta[c.feature].real_index : -1;
+    if (SplitBetter(c.gain, rf, c.threshold, bg, bf, bt)) { bg = c.gain; bf = rf; bt = c.threshold; bi = k; }
+  }
+  s_gain[threadIdx.x] = bg; s_feat[threadIdx.x] = bf; s_thr[threadIdx.x] = bt; s_idx[threadIdx.x] = bi;
+  __syncthreads();
+  for (int o = blockDim.x / 2; o > 0; o >>= 1) {
+    if (threadIdx.x < o && SplitBetter(s_gain[threadIdx.x + o], s_feat[threadIdx.x + o], s_thr[threadIdx.x + o], s_gain[threadIdx.x], s_feat[threadIdx.x], s_thr[threadIdx.x])) {
+      s_gain[threadIdx.x] = s_gain[threadIdx.x + o]; s_feat[threadIdx.x] = s_feat[threadIdx.x + o]; s_thr[threadIdx.x] = s_thr[threadIdx.x + o]; s_idx[threadIdx.x] = s_idx[threadIdx.x + o];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    SplitRecord r; InitSplitRecord(&r);
+    const bool depth_ok = a.params.max_depth <= 0 || leaf.depth < a.params.max_depth;
+    const bool size_ok = leaf.num_data_global >= 2 * a.params.min_data_in_leaf;
+    if (s_idx[0] >= 0 && depth_ok && size_ok) {
+      const CandLite c = a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + s_idx[0]];
+      r.gain = c.gain; r.feature = c.feature; r.threshold = c.threshold; r.default_left = c.default_left;
+      r.left_g = c.left_g; r.left_h = c.left_h; r.right_g = FB_SUB(leaf.sum_g, c.left_g); r.right_h = FB_SUB(leaf.sum_h, c.left_h);
+      r.left_gi = c.left_gi; r.left_hi = c.left_hi; r.left_cnt = c.left_cnt; r.right_cnt = leaf.num_data_global - c.left_cnt;
+      r.monotone = a.meta[c.feature].monotone;
+      r.left_out = LeafOutput(r.left_g, FB_ADD(r.left_h, kEpsilon), a.params, r.left_cnt, leaf.output);
+      r.right_out = LeafOutput(r.right_g, FB_ADD(r.right_h, kEpsilon), a.params, r.right_cnt, leaf.output);
+    }
+    a.best[ch.leaf] = r;
+  }
+}
+
+}  // namespace
+
+void LaunchFindSplits(const FindArgs& a, cudaStream_t s) {
+  if (a.num_children <= 0) return;
+  const int nf = a.num_features + a.num_sub_features;
+  if (nf <= 0) return;
+  dim3 grid(a.num_children, (nf + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  if (a.quant) FindSplitsKernel<true><<<grid, kFindThreads, 0, s>>>(a); else FindSplitsKernel<false><<<grid, kFindThreads, 0, s>>>(a);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+
+void LaunchReduceBest(const FindArgs& a, cudaStream_t s) {
+  if (a.num_children <= 0) return;
+  ReduceBestKernel<<<a.num_children, 128, 0, s>>>(a);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+
+}  // namespace fb

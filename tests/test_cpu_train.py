@@ -1,0 +1,103 @@
+"""CPU end-to-end: training quality, model text / binary round trips, callbacks, cv."""
+import numpy as np
+import pytest
+
+import falcata_b200 as fb
+from util import auc, make_binary, make_multiclass, make_ranking, make_regression
+
+
+def test_binary_config1_quality():
+    X, y = make_binary()
+    ds = fb.Dataset(X[:8000], y[:8000])
+    bst = fb.train({"objective": "binary", "num_leaves": 31, "max_bin": 255, "learning_rate": 0.1, "device_type": "cpu", "verbosity": -1, "grow_policy": "leaf"}, ds, 100)
+    p = bst.predict(X[8000:])
+    assert auc(y[8000:], p) > 0.96
+
+
+@pytest.mark.parametrize("policy", ["leaf", "level"])
+@pytest.mark.parametrize("quant", ["none", "stochastic", "fixedpoint"])
+def test_policies_and_quant(policy, quant):
+    X, y = make_binary(6000, 12)
+    ds = fb.Dataset(X[:5000], y[:5000])
+    bst = fb.train({"objective": "binary", "num_leaves": 15, "device_type": "cpu", "verbosity": -1, "grow_policy": policy, "quant_mode": quant}, ds, 30)
+    assert auc(y[5000:], bst.predict(X[5000:])) > 0.93
+    # quantized training is deterministic
+    bst2 = fb.train({"objective": "binary", "num_leaves": 15, "device_type": "cpu", "verbosity": -1, "grow_policy": policy, "quant_mode": quant}, fb.Dataset(X[:5000], y[:5000]), 30)
+    assert bst.model_to_string() == bst2.model_to_string()
+
+
+def test_model_roundtrips(tmp_path):
+    X, y = make_binary(4000, 10)
+    bst = fb.train({"objective": "binary", "device_type": "cpu", "verbosity": -1}, fb.Dataset(X, y), 20)
+    s = bst.model_to_string()
+    b2 = fb.Booster(model_str=s)
+    assert b2.model_to_string() == s
+    np.testing.assert_array_equal(bst.predict(X), b2.predict(X))
+    f = tmp_path / "m.txt"
+    bst.save_model(f)
+    b3 = fb.Booster(model_file=f)
+    np.testing.assert_array_equal(bst.predict(X), b3.predict(X))
+    blob = bst.model_to_binary()
+    assert blob[:4] == b"FALB" and len(blob) < len(s)
+    b4 = fb.Booster.from_binary(blob)
+    np.testing.assert_allclose(bst.predict(X), b4.predict(X), rtol=0, atol=1e-12)
+    b5 = fb.Booster.from_binary(bst.model_to_binary(f32_leaves=True))
+    np.testing.assert_allclose(bst.predict(X), b5.predict(X), atol=1e-5)
+    d = bst.dump_model()
+    assert len(d["tree_info"]) == 20 and d["max_feature_idx"] == 9
+    assert "PredictTree0" in bst.model_to_if_else()
+
+
+def test_model_text_format_fields():
+    X, y = make_binary(2000, 6)
+    s = fb.train({"objective": "binary", "device_type": "cpu", "verbosity": -1, "num_leaves": 7}, fb.Dataset(X, y), 3).model_to_string()
+    lines = s.split("\n")
+    assert lines[0] == "tree" and lines[1] == "version=v4"
+    for key in ["num_class=1", "num_tree_per_iteration=1", "label_index=0", "max_feature_idx=5", "objective=binary sigmoid:1", "feature_names=", "feature_infos=", "tree_sizes=",
+                "Tree=0", "num_leaves=", "num_cat=0", "split_feature=", "split_gain=", "threshold=", "decision_type=", "left_child=", "right_child=", "leaf_value=", "leaf_weight=",
+                "leaf_count=", "internal_value=", "internal_weight=", "internal_count=", "is_linear=0", "shrinkage=", "end of trees", "feature_importances:", "parameters:", "end of parameters"]:
+        assert any(l.startswith(key) for l in lines), key
+    sizes = [int(v) for v in [l for l in lines if l.startswith("tree_sizes=")][0].split("=")[1].split()]
+    body = s[s.index("Tree=0"):s.index("end of trees")]
+    assert sum(sizes) == len(body)
+
+
+def test_regression_multiclass_ranking():
+    X, y = make_regression()
+    bst = fb.train({"objective": "regression", "device_type": "cpu", "verbosity": -1}, fb.Dataset(X[:4000], y[:4000]), 80)
+    assert np.mean((bst.predict(X[4000:]) - y[4000:]) ** 2) < 0.35 * np.var(y)
+    X, y = make_multiclass()
+    bst = fb.train({"objective": "multiclass", "num_class": 4, "device_type": "cpu", "verbosity": -1}, fb.Dataset(X[:5000], y[:5000]), 40)
+    p = bst.predict(X[5000:])
+    assert p.shape == (1000, 4) and np.allclose(p.sum(1), 1) and (p.argmax(1) == y[5000:]).mean() > 0.6
+    X, y, g = make_ranking()
+    res = {}
+    fb.train({"objective": "lambdarank", "metric": "ndcg", "eval_at": "5", "device_type": "cpu", "verbosity": -1, "min_data_in_leaf": 5}, fb.Dataset(X, y, group=g), 30,
+             valid_sets=[fb.Dataset(X, y, group=g)], callbacks=[fb.record_evaluation(res)])
+    nd = res["valid_0"]["ndcg@5"]
+    assert nd[-1] > nd[0] and nd[-1] > 0.8
+
+
+def test_early_stopping_and_cv():
+    X, y = make_binary(5000, 10)
+    ds = fb.Dataset(X[:4000], y[:4000]); dv = ds.create_valid(X[4000:], y[4000:])
+    bst = fb.train({"objective": "binary", "metric": "binary_logloss", "device_type": "cpu", "verbosity": -1, "learning_rate": 0.5, "num_leaves": 63, "min_data_in_leaf": 2}, ds, 300,
+                   valid_sets=[dv], callbacks=[fb.early_stopping(5, verbose=False)])
+    assert 0 < bst.best_iteration < 300
+    r = fb.cv({"objective": "binary", "metric": "auc", "device_type": "cpu", "verbosity": -1}, fb.Dataset(X, y), 10, nfold=3)
+    assert len(r["valid auc-mean"]) == 10 and r["valid auc-mean"][-1] > 0.9
+
+
+def test_custom_objective_and_continue():
+    X, y = make_regression(3000, 6)
+
+    def l2(preds, data):
+        return preds - data.get_label(), np.ones_like(preds)
+
+    ds = fb.Dataset(X, y, free_raw_data=False)
+    b1 = fb.train({"objective": l2, "device_type": "cpu", "verbosity": -1}, ds, 20)
+    b2 = fb.train({"objective": "regression", "device_type": "cpu", "verbosity": -1, "boost_from_average": False}, fb.Dataset(X, y), 20)
+    np.testing.assert_allclose(b1.predict(X), b2.predict(X), atol=1e-6)
+    b3 = fb.train({"objective": "regression", "device_type": "cpu", "verbosity": -1}, fb.Dataset(X, y, free_raw_data=False), 10, init_model=b2)
+    assert b3.num_trees() == 30
+    assert np.mean((b3.predict(X) - y) ** 2) < np.mean((b2.predict(X) - y) ** 2)

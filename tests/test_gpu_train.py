@@ -1,0 +1,92 @@
+"""Device training end to end: parity with the host learner, quality, predict kernel, device ingest."""
+import numpy as np
+import pytest
+import torch
+
+import falcata_b200 as fb
+from util import auc, make_binary, make_multiclass, make_ranking, make_regression, model_body
+
+pytestmark = pytest.mark.gpu
+
+
+def _l2_exact(preds, data):
+    lab = data.get_label()
+    if hasattr(preds, "is_cuda"):
+        lab = torch.as_tensor(lab, device=preds.device)
+        return preds - lab, torch.ones_like(preds)
+    return preds - lab, np.ones_like(preds)
+
+
+@pytest.mark.parametrize("quant", ["stochastic", "fixedpoint"])
+def test_first_tree_bit_identical_to_host(quant):
+    # with custom L2 gradients and a zero start score both arms see exactly the same float gradients:
+    # integer histograms + shared split math must then give the same tree, digit for digit
+    X, y = make_regression(20000, 12)
+    y = np.round(y * 8) / 8
+    base = {"objective": "none", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": quant, "grow_policy": "level", "min_data_in_leaf": 20, "seed": 3}
+    bc = fb.train({**base, "device_type": "cpu"}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
+    bg = fb.train({**base, "device_type": "cuda"}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
+    assert model_body(bc.model_to_string()) == model_body(bg.model_to_string())
+
+
+@pytest.mark.parametrize("quant", ["none", "stochastic"])
+def test_binary_quality_matches_host(quant):
+    X, y = make_binary(30000, 28)
+    p = {"objective": "binary", "num_leaves": 63, "max_bin": 63, "verbosity": -1, "quant_mode": quant, "grow_policy": "level"}
+    bc = fb.train({**p, "device_type": "cpu"}, fb.Dataset(X[:25000], y[:25000]), 40)
+    bg = fb.train({**p, "device_type": "cuda"}, fb.Dataset(X[:25000], y[:25000]), 40)
+    ac, ag = auc(y[25000:], bc.predict(X[25000:])), auc(y[25000:], bg.predict(X[25000:]))
+    assert ag > 0.95 and abs(ac - ag) < 0.01
+
+
+def test_quant_run_twice_identical_and_device_ingest():
+    X, y = make_binary(20000, 20)
+    p = {"objective": "binary", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "device_type": "cuda"}
+    a = fb.train(p, fb.Dataset(X, y), 15).model_to_string()
+    b = fb.train(p, fb.Dataset(X, y), 15).model_to_string()
+    assert a == b
+    # device-array ingest bins on the GPU; same bins as host ingest -> same model
+    c = fb.train(p, fb.Dataset(torch.from_numpy(X).cuda(), y, params={"bin_construct_sample_cnt": 20000}), 15).model_to_string()
+    d = fb.train(p, fb.Dataset(X, y, params={"bin_construct_sample_cnt": 20000}), 15).model_to_string()
+    assert model_body(c) == model_body(d)
+
+
+def test_device_predict_matches_host():
+    X, y = make_binary(20000, 16)
+    bst = fb.train({"objective": "binary", "num_leaves": 31, "verbosity": -1, "device_type": "cuda", "quant_mode": "stochastic"}, fb.Dataset(X, y), 30)
+    ph = bst.predict(X)
+    pd = bst.predict(torch.from_numpy(X).cuda())
+    assert pd.is_cuda
+    np.testing.assert_allclose(pd.cpu().numpy(), ph, atol=2e-5)
+    raw = bst.predict(torch.from_numpy(X).cuda(), raw_score=True).cpu().numpy()
+    np.testing.assert_allclose(raw, bst.predict(X, raw_score=True), atol=1e-4)
+
+
+def test_validation_metrics_on_device():
+    X, y = make_binary(20000, 16)
+    ds = fb.Dataset(X[:16000], y[:16000]); dv = ds.create_valid(X[16000:], y[16000:])
+    res = {}
+    bst = fb.train({"objective": "binary", "metric": "binary_logloss,auc", "verbosity": -1, "device_type": "cuda", "quant_mode": "stochastic"}, ds, 25, valid_sets=[dv],
+                   callbacks=[fb.record_evaluation(res)])
+    ll = res["valid_0"]["binary_logloss"]
+    assert ll[-1] < ll[0]
+    p = bst.predict(X[16000:])
+    ref = -np.mean(np.where(y[16000:] > 0, np.log(p), np.log(1 - p)))
+    assert abs(ref - ll[-1]) < 1e-4
+    assert abs(res["valid_0"]["auc"][-1] - auc(y[16000:], p)) < 1e-6
+
+
+def test_regression_multiclass_ranking_on_device():
+    X, y = make_regression(20000, 10)
+    bst = fb.train({"objective": "regression", "verbosity": -1, "device_type": "cuda", "quant_mode": "fixedpoint"}, fb.Dataset(X[:16000], y[:16000]), 60)
+    assert np.mean((bst.predict(X[16000:]) - y[16000:]) ** 2) < 0.3 * np.var(y)
+    X, y = make_multiclass(20000, 12, 4)
+    bst = fb.train({"objective": "multiclass", "num_class": 4, "verbosity": -1, "device_type": "cuda"}, fb.Dataset(X[:16000], y[:16000]), 30)
+    p = bst.predict(X[16000:])
+    assert p.shape == (4000, 4) and (p.argmax(1) == y[16000:]).mean() > 0.6
+    X, y, g = make_ranking(500, 20, 10)
+    res = {}
+    fb.train({"objective": "lambdarank", "metric": "ndcg", "eval_at": "5", "verbosity": -1, "device_type": "cuda", "min_data_in_leaf": 5}, fb.Dataset(X, y, group=g), 30,
+             valid_sets=[fb.Dataset(X, y, group=g)], callbacks=[fb.record_evaluation(res)])
+    nd = res["valid_0"]["ndcg@5"]
+    assert nd[-1] > nd[0] and nd[-1] > 0.8
