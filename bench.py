@@ -87,7 +87,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--stage-timing", action="store_true")
+    ap.add_argument("--plan", default="auto", help="cuda_plan string, e.g. auto,hist_lane:off")
     args = ap.parse_args()
+    PARAMS["cuda_plan"] = args.plan
     if args.impl == "reference":
         reference_arm(args)
         return

@@ -82,12 +82,29 @@ __global__ void BinRowsKernel(const T* __restrict__ data, int nrow, int ncol, bo
 
 int RowStrideFor(int num_groups) { return ((num_groups + 4 + 15) / 16) * 16; }
 
+// cols[g][i] = rows[i][g]; row index is the fast thread index so the stores coalesce (the strided
+// loads of neighbouring groups hit the same sectors in L1/L2).
+__global__ void TransposeRowsKernel(const uint8_t* __restrict__ rows, int row_stride, int n, int num_groups, uint8_t* __restrict__ cols) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const uint8_t* rp = rows + static_cast<size_t>(i) * row_stride;
+  for (int g = 0; g < num_groups; ++g) cols[static_cast<size_t>(g) * n + i] = rp[g];
+}
+
 void UploadMeta(const Dataset* ds, DeviceDataset* dd, cudaStream_t s) {
   dd->feature_meta.Upload(ds->feature_meta, s);
   dd->group_bin_start.Upload(ds->group_bin_start, s);
 }
 
 }  // namespace
+
+// Column-major copy of the bins for the partition kernels (built once, on first use).
+void EnsureColumnMajor(DeviceDataset* dd, cudaStream_t s) {
+  if (dd->cols.size() > 0 || dd->num_data == 0) return;
+  dd->cols.Alloc(static_cast<size_t>(dd->num_groups) * dd->num_data);
+  TransposeRowsKernel<<<(dd->num_data + 255) / 256, 256, 0, s>>>(dd->rows.get(), dd->row_stride, dd->num_data, dd->num_groups, dd->cols.get());
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
 
 // Metadata that training needs on the device; called lazily by the engine (labels may be set after binning).
 void SyncDeviceMetadata(const Dataset* ds, cudaStream_t s) {

@@ -82,6 +82,7 @@ struct DeviceDataset {
   int row_stride = 0;
   int gh_offset = -1;
   DevBuf<uint8_t> rows;
+  DevBuf<uint8_t> cols;        // optional column-major copy [num_groups x num_data]: the row partition reads ONE column
   DevBuf<float> label, weight;
   DevBuf<int> query_boundaries;
   int num_queries = 0;
@@ -115,7 +116,9 @@ struct PartSplit {
   uint32_t cat_bitset[8];
   int chunk_begin;     // first partition chunk of this split in the flat chunk grid
   int num_chunks;
+  int pad_[3];         // keeps sizeof a multiple of 16: arrays of different record types share one upload blob
 };
+static_assert(sizeof(PartSplit) % 16 == 0, "level blob records must keep 16-byte alignment");
 
 // Per-leaf device record (windows + totals) that the level kernels read and update.
 struct LeafInfo {

@@ -85,6 +85,16 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   } else {
     gh2_.Alloc(n_); gh_base_ = reinterpret_cast<const uint8_t*>(gh2_.get()); gh_stride_ = 8; hist_elem_ = sizeof(double2);
   }
+  {
+    const int qb = std::max(2, cfg.quant_bins_resolved);
+    sub_rows_ = quant_ ? std::max(1, std::min(65535 / qb, 32767 / std::max(1, qb / 2))) : (1 << 30);
+    lane_mode_ = 0; lane_bins_ = 64;
+    if (quant_ && (plan_.hist_lane || plan_.hist_lane_atomic) && train->max_group_bin <= 64) {
+      lane_mode_ = plan_.hist_lane_atomic ? 2 : 1;
+      lane_bins_ = train->max_group_bin <= 16 ? 16 : 64;
+    }
+    if (plan_.col_major_part) EnsureColumnMajor(dd_, stream_);
+  }
   idx_[0].Alloc(n_); idx_[1].Alloc(n_);
   const int NL = cfg.num_leaves;
   leaves_.Alloc(NL); best_.Alloc(NL); h_leaves_.Alloc(NL); h_best_.Alloc(NL); leaf_value_.Alloc(NL);
@@ -142,7 +152,10 @@ void CudaEngine::SetupOwnership() {
 int CudaEngine::ChooseRowsPerBlock(long long total_rows) const {
   long long target = total_rows / (static_cast<long long>(num_sms_) * 6) + 1;
   long long rpb = 512; while (rpb < target && rpb < 8192) rpb <<= 1;
-  return static_cast<int>(rpb);
+  // the 16-bit lanes of the packed shared-memory cells bound the rows one tile may take
+  if (lane_mode_ == 1) rpb = std::min<long long>(rpb, 8LL * sub_rows_);
+  else if (lane_mode_ == 2) rpb = std::min<long long>(rpb, sub_rows_);
+  return static_cast<int>(std::max<long long>(rpb, 32));
 }
 
 void CudaEngine::AddConstantToScores(double v, int k) {

@@ -14,6 +14,7 @@ namespace fb {
 
 void EnsureDeviceDataset(Dataset* ds);
 void SyncDeviceMetadata(const Dataset* ds, cudaStream_t s);
+void EnsureColumnMajor(DeviceDataset* dd, cudaStream_t s);
 class Fabric;   // symmetric heap + peer pointers of the multi-rank path (fabric.h)
 
 struct StageClock {
@@ -100,6 +101,7 @@ class CudaEngine : public DeviceEngine {
   // traversal staging
   DevBuf<int> tree_ints_; DevBuf<float> tree_floats_; DevBuf<signed char> tree_dec_;
   const float* cur_grad_ = nullptr; const float* cur_hess_ = nullptr;
+  int lane_mode_ = 0, lane_bins_ = 64, sub_rows_ = 1 << 30;
   double bag_fraction_ = 1.0; int bag_freq_ = 0, bag_seed_ = 0;
   int max_docs_ = 0;
 };

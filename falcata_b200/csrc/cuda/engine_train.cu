@@ -108,6 +108,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   for (int r = 0; r < 8; ++r) { ha.dest.pool[r] = nullptr; ha.dest.slot_stride[r] = 0; }
   ha.dest.pool[0] = pool_.get(); ha.dest.slot_stride[0] = slot_stride_; ha.dest.bin_owner = bin_owner_.get(); ha.dest.bin_local = bin_local_.get();
   ha.dest.num_ranks = 1; ha.dest.rank = 0;
+  ha.num_total_bin = train_->num_total_bin; ha.lane_mode = lane_mode_; ha.lane_bins = lane_bins_;
   FindArgs fa;
   fa.features = features_.get(); fa.num_features = NF; fa.sub_features = sub_features_.get(); fa.num_sub_features = NS; fa.meta = dd_->feature_meta.get();
   fa.bin_local = bin_local_.get(); fa.pool = pool_.get(); fa.slot_stride = slot_stride_; fa.leaves = leaves_.get(); fa.scales = scales_.get(); fa.params = sp_;
@@ -196,6 +197,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     FB_CUDA(cudaMemcpyAsync(db, hb, blob_bytes, cudaMemcpyHostToDevice, stream_));
     PartArgs pa;
     pa.rows = dd_->rows.get(); pa.row_stride = dd_->row_stride; pa.idx[0] = idx_[0].get(); pa.idx[1] = idx_[1].get();
+    pa.cols = dd_->cols.size() ? dd_->cols.get() : nullptr; pa.col_stride = n_;
     pa.splits = reinterpret_cast<const PartSplit*>(db); pa.num_splits = S; pa.total_chunks = chunk_cursor; pa.bits = bits_.get(); pa.chunk_left = chunk_left_.get();
     pa.split_left_total = split_left_total_.get(); pa.leaves = leaves_.get(); pa.child_init = reinterpret_cast<const ChildInit*>(db + sizeof(PartSplit) * S);
     pa.hist_tasks = hist_tasks_.get(); pa.rows_per_block = ha.rows_per_block;

@@ -14,6 +14,8 @@
 // different features' bins (no same-address serialisation inside a row).
 #include "kernels.cuh"
 
+#include <cuda_pipeline.h>
+
 namespace fb {
 
 namespace {
@@ -88,6 +90,120 @@ __global__ void __launch_bounds__(kHistThreads) HistQuantKernel(HistArgs a) {
   }
 }
 
+// Lane-per-group instance, fed by an asynchronous gather pipeline.
+//
+// Two measurements on B200 shaped this kernel. (1) With plain loads a block keeps only a few KB of
+// row data in flight; the construct then waits on DRAM latency, far from HBM bandwidth. Here every
+// thread copies one row's 32 bytes (and its gradient word) global->shared with cp.async, several
+// stages ahead, so each SM has tens of KB in flight without holding registers. (2) Shared-memory
+// atomics into a [group][bin] tile suffer bank conflicts between the lanes' random bins. Here lane l
+// of a warp owns feature group (32*blockIdx.y + l) and the tile is laid out [bin][32 lanes]: the 32
+// lanes of an instruction always touch 32 different banks. With PRIVATE tiles (one per warp) the
+// update is a plain load-add-store, no atomics at all, because no other thread touches a lane's column.
+constexpr int kLaneWarps = kHistThreads / 32;
+constexpr int kPipeStages = 4;
+template <int NB, bool PRIVATE>
+__global__ void __launch_bounds__(kHistThreads) HistQuantLaneKernel(HistArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int kTile = NB * 32;
+  constexpr int kTiles = PRIVATE ? kLaneWarps : 1;
+  int* tiles = reinterpret_cast<int*>(smem_raw);
+  unsigned char* stage_rows = smem_raw + sizeof(int) * kTiles * kTile;                    // [stages][256 rows][32 B]
+  int* stage_gh = reinterpret_cast<int*>(stage_rows + kPipeStages * kHistThreads * 32);   // [stages][256]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ti = FindTask(a.tasks, a.num_tasks, blockIdx.x);
+  const HistTask task = a.tasks[ti];
+  const int chunk = blockIdx.x - task.block_begin;
+  const long long row0 = static_cast<long long>(chunk) * a.rows_per_block;
+  if (chunk >= task.num_blocks || row0 >= task.count) return;
+  const int nrows = static_cast<int>(min(static_cast<long long>(a.rows_per_block), task.count - row0));
+  const int g0 = blockIdx.y * 32;
+  const int ng = min(32, a.num_groups - g0);
+  const int copy16 = min(2, (a.row_stride - g0) / 16);          // 16-byte pieces of this part inside the row
+  for (int i = threadIdx.x; i < kTiles * kTile; i += kHistThreads) tiles[i] = 0;
+  int* tile = tiles + (PRIVATE ? warp * kTile : 0);
+  const int* idx = a.idx[task.buffer] + task.begin + row0;
+  const int nstage = (nrows + kHistThreads - 1) / kHistThreads;
+  auto row_of = [&](int r) -> int { return a.identity_root ? static_cast<int>(task.begin + row0 + r) : idx[r]; };
+  auto issue = [&](int s, int row) {
+    if (s < nstage && s * kHistThreads + static_cast<int>(threadIdx.x) < nrows) {
+      const int slot = s % kPipeStages;
+      const unsigned char* src = a.rows + static_cast<size_t>(row) * a.row_stride + g0;
+      unsigned char* dst = stage_rows + (static_cast<size_t>(slot) * kHistThreads + threadIdx.x) * 32;
+      __pipeline_memcpy_async(dst, src, 16);
+      if (copy16 > 1) __pipeline_memcpy_async(dst + 16, src + 16, 16);
+      __pipeline_memcpy_async(stage_gh + slot * kHistThreads + threadIdx.x, a.gh_base + static_cast<size_t>(row) * a.gh_stride, 4);
+    }
+    __pipeline_commit();
+  };
+  // prologue: stages 0 .. S-2 in flight, and the row index of the next stage already loaded
+  int next_row = 0;
+  for (int s = 0; s < kPipeStages - 1; ++s) {
+    const int r = s * kHistThreads + threadIdx.x;
+    issue(s, (s < nstage && r < nrows) ? row_of(r) : 0);
+  }
+  { const int r = (kPipeStages - 1) * kHistThreads + threadIdx.x; next_row = (kPipeStages - 1 < nstage && r < nrows) ? row_of(r) : 0; }
+  __syncthreads();
+  const bool active = lane < ng;
+  for (int s = 0; s < nstage; ++s) {
+    issue(s + kPipeStages - 1, next_row);
+    { const int r = (s + kPipeStages) * kHistThreads + threadIdx.x; next_row = (s + kPipeStages < nstage && r < nrows) ? row_of(r) : 0; }
+    __pipeline_wait_prior(kPipeStages - 1);
+    __syncthreads();
+    const int slot = s % kPipeStages;
+    const int base = s * kHistThreads + warp * 32;
+    const int cnt = min(32, nrows - base);
+    if (cnt > 0) {
+      const unsigned char* sr = stage_rows + (static_cast<size_t>(slot) * kHistThreads + warp * 32) * 32 + lane;
+      const int ghv = stage_gh[slot * kHistThreads + warp * 32 + lane];
+      if (cnt == 32 && PRIVATE) {
+        // four rows per step: the four tile loads are issued together and equal addresses are
+        // forwarded in registers, so the dependent shared-memory chain is paid once per four rows
+#pragma unroll 2
+        for (int j = 0; j < 32; j += 4) {
+          const int a0 = sr[j * 32] * 32 + lane, a1 = sr[(j + 1) * 32] * 32 + lane, a2 = sr[(j + 2) * 32] * 32 + lane, a3 = sr[(j + 3) * 32] * 32 + lane;
+          const int g0v = __shfl_sync(0xffffffffu, ghv, j), g1v = __shfl_sync(0xffffffffu, ghv, j + 1);
+          const int g2v = __shfl_sync(0xffffffffu, ghv, j + 2), g3v = __shfl_sync(0xffffffffu, ghv, j + 3);
+          if (active) {
+            int v0 = tile[a0], v1 = tile[a1], v2 = tile[a2], v3 = tile[a3];
+            v0 += g0v;
+            v1 = (a1 == a0) ? v0 : v1; v1 += g1v;
+            v2 = (a2 == a1) ? v1 : ((a2 == a0) ? v0 : v2); v2 += g2v;
+            v3 = (a3 == a2) ? v2 : ((a3 == a1) ? v1 : ((a3 == a0) ? v0 : v3)); v3 += g3v;
+            tile[a0] = v0; tile[a1] = v1; tile[a2] = v2; tile[a3] = v3;   // program order: the last store to an address holds its full sum
+          }
+        }
+      } else if (cnt == 32) {
+#pragma unroll 8
+        for (int j = 0; j < 32; ++j) {
+          const int b = sr[j * 32];
+          const int g = __shfl_sync(0xffffffffu, ghv, j);
+          if (active) atomicAdd(&tile[b * 32 + lane], g);
+        }
+      } else {
+        for (int j = 0; j < cnt; ++j) {
+          const int b = sr[j * 32];
+          const int g = __shfl_sync(0xffffffffu, ghv, j);
+          if (active) { if (PRIVATE) tile[b * 32 + lane] += g; else atomicAdd(&tile[b * 32 + lane], g); }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  for (int cell = threadIdx.x; cell < kTile; cell += kHistThreads) {
+    const int l = cell & 31, b = cell >> 5;
+    if (l >= ng) continue;
+    const int g = g0 + l;
+    const int gstart = a.group_bin_start[g];
+    const int gbins = (g + 1 < a.num_groups ? a.group_bin_start[g + 1] : a.num_total_bin) - gstart;
+    if (b >= gbins) continue;
+    long long sg = 0, sh = 0;
+    for (int w = 0; w < kTiles; ++w) { const int v = tiles[w * kTile + cell]; const int h = v & 0xFFFF; sg += (v - h) >> 16; sh += h; }
+    if (sg != 0 || sh != 0) FlushBinQuant(a.dest, task.slot, gstart + b, sg, sh);
+  }
+}
+
+
 __global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
   extern __shared__ float smem_f[];
   const HistPartition part = a.parts[blockIdx.y];
@@ -139,6 +255,25 @@ __global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
 
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
   if (a.total_blocks <= 0 || a.num_tasks <= 0) return;
+  if (a.lane_mode != 0) {
+    const bool priv = a.lane_mode == 1;
+    const int cap = priv ? kLaneWarps * a.sub_rows : a.sub_rows;
+    if (a.rows_per_block > cap) Log::Fatal("lane histogram: %d rows per block would overflow the 16-bit lanes (cap %d)", a.rows_per_block, cap);
+    dim3 grid(a.total_blocks, (a.num_groups + 31) / 32);
+    const size_t sm = static_cast<size_t>(a.lane_bins) * 32 * 4 * (priv ? kLaneWarps : 1) + static_cast<size_t>(kPipeStages) * kHistThreads * (32 + 4);
+#define FB_LANE(NB, P)                                                                                                             \
+    {                                                                                                                              \
+      static bool attr = false;                                                                                                    \
+      if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantLaneKernel<NB, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr = true; } \
+      HistQuantLaneKernel<NB, P><<<grid, kHistThreads, sm, s>>>(a);                                                                \
+    }
+    if (a.lane_bins == 16) { if (priv) FB_LANE(16, true) else FB_LANE(16, false) }
+    else if (a.lane_bins == 64) { if (priv) FB_LANE(64, true) else FB_LANE(64, false) }
+    else Log::Fatal("lane histogram: unsupported tile of %d bins", a.lane_bins);
+#undef FB_LANE
+    FB_LAUNCHED(); FB_KERNEL_CHECK();
+    return;
+  }
   const bool two_phase = a.rows_per_block > a.sub_rows;
   int max_groups = 0;
   // shared bytes: packed (+ wide) + group starts; sized for the largest partition

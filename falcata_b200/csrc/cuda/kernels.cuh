@@ -41,6 +41,9 @@ struct HistArgs {
   const int* group_bin_start;
   int rows_per_block; int sub_rows;
   int identity_root;        // 1: task rows are 0..count-1 (no index load)
+  int num_total_bin;
+  int lane_mode;            // 0: flat items + shared atomics; 1: lane-per-group warp-private tiles (no atomics); 2: lane-per-group, one shared tile + atomics
+  int lane_bins;            // lane modes: bins per group tile (16 or 64)
   HistDest dest;
 };
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s);
@@ -84,6 +87,7 @@ struct ChildInit {     // host-decided child bookkeeping of one split
 };
 struct PartArgs {
   const uint8_t* rows; int row_stride;
+  const uint8_t* cols; long long col_stride;   // column-major copy (null: read the byte from the row)
   int* idx[2];
   const PartSplit* splits; int num_splits; int total_chunks;
   unsigned int* bits;        // kPartChunk/32 words per chunk

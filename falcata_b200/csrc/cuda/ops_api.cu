@@ -28,7 +28,7 @@ const char* FB_OpsLastError() { return g_ops_error.c_str(); }
 // quant != 0: gh is int32 packed (g16|h16) per row, out is int64 [total_bins x 2] (grad, hess sums).
 // quant == 0: gh is float2 per row, out is float64 [total_bins x 2].
 int FB_OpHistogram(const uint8_t* rows, int row_stride, int num_groups, const void* gh, int gh_stride, const int* idx, int count,
-                   const int* group_num_bin_host, int quant, int quant_bins, int rows_per_block, int max_part_bins, void* out) {
+                   const int* group_num_bin_host, int quant, int quant_bins, int rows_per_block, int max_part_bins, int lane_mode, void* out) {
   OPS_BEGIN();
   std::vector<int> gbins(group_num_bin_host, group_num_bin_host + num_groups), gstart(num_groups);
   int total = 0; for (int g = 0; g < num_groups; ++g) { gstart[g] = total; total += gbins[g]; }
@@ -51,6 +51,16 @@ int FB_OpHistogram(const uint8_t* rows, int row_stride, int num_groups, const vo
   const int qb = std::max(2, quant_bins);
   a.sub_rows = quant ? std::max(1, std::min(65535 / qb, 32767 / std::max(1, qb / 2))) : (1 << 30);
   a.identity_root = idx == nullptr ? 1 : 0;
+  a.num_total_bin = total; a.lane_mode = quant ? lane_mode : 0;
+  int mgb = 0; for (int v : gbins) mgb = std::max(mgb, v);
+  a.lane_bins = mgb <= 16 ? 16 : 64;
+  if (a.lane_mode != 0 && mgb > 64) Log::Fatal("lane histogram covers groups of at most 64 bins");
+  if (a.lane_mode == 1 && rows_per_block > 8 * a.sub_rows) { a.rows_per_block = rows_per_block = 8 * a.sub_rows; }
+  if (a.lane_mode == 2 && rows_per_block > a.sub_rows) { a.rows_per_block = rows_per_block = a.sub_rows; }
+  if (a.lane_mode != 0) {
+    t.num_blocks = (count + rows_per_block - 1) / rows_per_block; a.total_blocks = t.num_blocks;
+    d_task.Upload(&t, 1, s);
+  }
   for (int r = 0; r < 8; ++r) { a.dest.pool[r] = nullptr; a.dest.slot_stride[r] = 0; }
   a.dest.pool[0] = pool.get(); a.dest.slot_stride[0] = total; a.dest.bin_owner = d_owner.get(); a.dest.bin_local = d_local.get(); a.dest.num_ranks = 1; a.dest.rank = 0;
   if (quant) LaunchHistConstructQuant(a, s); else LaunchHistConstructFloat(a, s);
@@ -90,7 +100,7 @@ int FB_OpPartition(const uint8_t* rows, int row_stride, const int* idx, int coun
   DevBuf<LeafInfo> d_leaves2; d_leaves2.Alloc(2); FB_CUDA(cudaMemcpyAsync(d_leaves2.get(), d_leaves.get(), sizeof(LeafInfo), cudaMemcpyDeviceToDevice, s));
   DevBuf<unsigned int> bits; bits.Alloc(static_cast<size_t>(sp.num_chunks + 1) * (kPartChunk / 32));
   DevBuf<int> chunk_left; chunk_left.Alloc(sp.num_chunks + 1); DevBuf<int> left_total; left_total.Alloc(1); DevBuf<HistTask> tasks; tasks.Alloc(1);
-  PartArgs a; a.rows = rows; a.row_stride = row_stride; a.idx[0] = const_cast<int*>(idx); a.idx[1] = out_idx; a.splits = d_sp.get(); a.num_splits = 1; a.total_chunks = sp.num_chunks;
+  PartArgs a; a.rows = rows; a.row_stride = row_stride; a.cols = nullptr; a.col_stride = 0; a.idx[0] = const_cast<int*>(idx); a.idx[1] = out_idx; a.splits = d_sp.get(); a.num_splits = 1; a.total_chunks = sp.num_chunks;
   a.bits = bits.get(); a.chunk_left = chunk_left.get(); a.split_left_total = left_total.get(); a.leaves = d_leaves2.get(); a.child_init = d_ci.get(); a.hist_tasks = tasks.get(); a.rows_per_block = 2048;
   LaunchPartitionFlags(a, s); LaunchPartitionScanSetup(a, s); LaunchPartitionScatter(a, s);
   FB_CUDA(cudaMemcpyAsync(left_count, left_total.get(), sizeof(int), cudaMemcpyDeviceToHost, s));

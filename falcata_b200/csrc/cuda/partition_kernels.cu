@@ -49,7 +49,8 @@ __global__ void __launch_bounds__(kPartThreads) PartitionFlagsKernel(PartArgs a)
     bool left = false;
     if (pos < sp.count) {
       const int row = idx[pos];
-      left = GoLeft(sp, a.rows[static_cast<size_t>(row) * a.row_stride + sp.group]);
+      const int gb = a.cols != nullptr ? a.cols[static_cast<size_t>(sp.group) * a.col_stride + row] : a.rows[static_cast<size_t>(row) * a.row_stride + sp.group];
+      left = GoLeft(sp, gb);
     }
     const unsigned int word = __ballot_sync(0xffffffffu, left);
     if (lane == 0) { a.bits[static_cast<size_t>(chunk) * kWordsPerChunk + k * (kPartThreads / 32) + warp] = word; cnt += __popc(word); }

@@ -201,6 +201,9 @@ struct Plan {
   bool gh_in_row = true;         // packed gradient word stored next to the row's bins
   bool small_leaf_kernel = true; // one CTA per tiny leaf in the construct
   bool hist_sub = true;          // larger = parent - smaller
+  bool hist_lane = true;         // lane-per-group construct with bank-interleaved warp-private tiles (groups with <= 64 bins)
+  bool hist_lane_atomic = false; // lane-per-group construct with one shared tile per block and shared atomics
+  bool col_major_part = true;    // partition reads the split column from a column-major copy of the bins
   static Plan FromString(const std::string& s);
   std::string ToString() const;
 };

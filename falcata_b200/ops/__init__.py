@@ -27,7 +27,7 @@ def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
 
 
 def histogram(rows: torch.Tensor, gh: torch.Tensor, group_num_bin: Sequence[int], idx: Optional[torch.Tensor] = None, quant: bool = True, quant_bins: int = 4,
-              rows_per_block: int = 2048, max_part_bins: int = 6144, gh_stride: Optional[int] = None, count: Optional[int] = None) -> torch.Tensor:
+              rows_per_block: int = 2048, max_part_bins: int = 6144, gh_stride: Optional[int] = None, count: Optional[int] = None, lane_mode: int = 0) -> torch.Tensor:
     """Per-bin (grad, hess) sums of the selected rows. ``rows``: uint8 [n, stride]; ``gh``: int32 packed (quant) or float32 [n, 2]."""
     assert rows.is_cuda and rows.dtype == torch.uint8 and rows.is_contiguous()
     g = np.ascontiguousarray(np.asarray(group_num_bin, dtype=np.int32))
@@ -36,7 +36,7 @@ def histogram(rows: torch.Tensor, gh: torch.Tensor, group_num_bin: Sequence[int]
     out = torch.zeros((total, 2), dtype=torch.int64 if quant else torch.float64, device=rows.device)
     stride = gh_stride if gh_stride is not None else (4 if quant else 8)
     _check(_lib().FB_OpHistogram(_p(rows), rows.shape[1], len(g), _p(gh), stride, _p(idx), n, g.ctypes.data_as(ctypes.c_void_p), 1 if quant else 0, quant_bins,
-                                  rows_per_block, max_part_bins, _p(out)))
+                                  rows_per_block, max_part_bins, lane_mode, _p(out)))
     return out
 
 

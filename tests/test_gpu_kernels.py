@@ -27,9 +27,12 @@ def _ref_hist(rows, nbins, g, h, idx=None):
     return out
 
 
-@pytest.mark.parametrize("n,groups,nb,qbins,rpb", [(1, 1, 2, 4, 512), (33, 3, 16, 4, 512), (1023, 28, 64, 4, 512), (50000, 28, 64, 4, 8192), (40000, 7, 255, 64, 4096), (20000, 130, 255, 16, 2048)])
-def test_hist_quant_exact(n, groups, nb, qbins, rpb):
+@pytest.mark.parametrize("n,groups,nb,qbins,rpb", [(1, 1, 2, 4, 512), (33, 3, 16, 4, 512), (1023, 28, 64, 4, 512), (50000, 28, 64, 4, 8192), (30000, 40, 16, 64, 8192), (40000, 7, 255, 64, 4096), (20000, 130, 255, 16, 2048)])
+@pytest.mark.parametrize("lane_mode", [0, 1, 2])
+def test_hist_quant_exact(n, groups, nb, qbins, rpb, lane_mode):
     from falcata_b200 import ops
+    if lane_mode != 0 and nb > 64:
+        pytest.skip("lane tiles cover groups of at most 64 bins")
     nbins = [nb] * groups
     rows = _rows(n, groups, nbins)
     g = torch.Generator(device="cuda"); g.manual_seed(1)
@@ -37,10 +40,10 @@ def test_hist_quant_exact(n, groups, nb, qbins, rpb):
     hi = torch.randint(0, qbins + 1, (n,), generator=g, device="cuda", dtype=torch.int32)
     packed = (gi << 16) | (hi & 0xFFFF)
     ref = _ref_hist(rows, nbins, gi, hi)
-    out = ops.histogram(rows, packed, nbins, quant=True, quant_bins=qbins, rows_per_block=rpb)
+    out = ops.histogram(rows, packed, nbins, quant=True, quant_bins=qbins, rows_per_block=rpb, lane_mode=lane_mode)
     assert torch.equal(out, ref.long())
     idx = torch.randperm(n, generator=g, device="cuda")[: max(1, n // 3)].int().sort().values
-    out = ops.histogram(rows, packed, nbins, idx=idx, quant=True, quant_bins=qbins, rows_per_block=rpb)
+    out = ops.histogram(rows, packed, nbins, idx=idx, quant=True, quant_bins=qbins, rows_per_block=rpb, lane_mode=lane_mode)
     assert torch.equal(out, _ref_hist(rows, nbins, gi, hi, idx).long())
 
 
