@@ -111,6 +111,9 @@ def main() -> None:
 
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        from falcata_b200 import parallel
+
+        parallel.init()
     else:
         torch.cuda.set_device(0)
     dev = torch.device("cuda", local_rank)
@@ -193,7 +196,9 @@ def main() -> None:
         print(json.dumps(out))
     if world > 1:
         import torch.distributed as dist
+        from falcata_b200 import parallel
 
+        parallel.shutdown()
         dist.destroy_process_group()
 
 

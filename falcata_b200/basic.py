@@ -256,7 +256,8 @@ class Dataset:
         else:
             from .parallel import bootstrap
 
-            sample, total = bootstrap.gather_bin_sample(t, int(params.get("bin_construct_sample_cnt", 200000)), int(params.get("data_random_seed", 1)))
+            goff, gtot = self._global_rows if self._global_rows is not None else (0, 0)
+            sample, total = bootstrap.gather_bin_sample(t, int(params.get("bin_construct_sample_cnt", 200000)), int(params.get("data_random_seed", 1)), goff, gtot)
             sample = np.ascontiguousarray(sample, dtype=np.float64)
             _safe_call(lib.FB_DatasetCreateFromSample(sample.ctypes.data_as(ctypes.c_void_p), ctypes.c_int32(sample.shape[0]), ctypes.c_int32(ncol),
                                                       ctypes.c_int64(total), _param_str(params), None, 0, ctypes.byref(handle)))

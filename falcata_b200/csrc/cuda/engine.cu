@@ -38,6 +38,13 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   cudaDeviceProp prop; int dev = 0; FB_CUDA(cudaGetDevice(&dev)); FB_CUDA(cudaGetDeviceProperties(&prop, dev));
   if (prop.major < 10) Log::Warning("This build targets sm_100a; device %s is compute %d.%d", prop.name, prop.major, prop.minor);
   num_sms_ = prop.multiProcessorCount;
+  if (Fabric::Get().active() && cfg.tree_learner != "serial") {
+    if (cfg.tree_learner != "data") Log::Fatal("On the device, multi-GPU training is tree_learner=data (voting / feature run on the host learner)");
+    fabric_ = &Fabric::Get(); world_ = fabric_->world(); rank_ = fabric_->rank();
+    if (!Network::active()) Log::Fatal("Multi-GPU training needs the host collectives as well (falcata_b200.parallel.init())");
+  } else if (Network::active() && cfg.tree_learner != "serial") {
+    Log::Fatal("Multi-GPU training needs the device fabric (call falcata_b200.parallel.init() before creating the Booster)");
+  }
   EnsureDeviceDataset(const_cast<Dataset*>(train));
   dd_ = train->device; n_ = train->num_data;
   FB_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
@@ -101,7 +108,22 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   host_leaves_.resize(NL);
   BuildPartitions();
   SetupOwnership();
-  pool_.Alloc(static_cast<size_t>(NL) * slot_stride_ * hist_elem_);
+  if (world_ > 1) {
+    // same carving order on every rank: offsets name the same object everywhere
+    long long max_stride = 0; for (int r = 0; r < world_; ++r) max_stride = std::max(max_stride, slot_strides_[r]);
+    fabric_->Reset();
+    pool_bytes_ = static_cast<size_t>(NL) * max_stride * hist_elem_;
+    off_pool_ = fabric_->Alloc(pool_bytes_);
+    off_counts_ = fabric_->Alloc(static_cast<size_t>(world_) * NL * sizeof(int));
+    off_best_ = fabric_->Alloc(static_cast<size_t>(world_) * NL * sizeof(SplitRecord));
+    flag_hist_ = fabric_->NewFlagSlot(); flag_best_ = fabric_->NewFlagSlot();
+    pool_base_ = fabric_->Local<char>(off_pool_);
+    global_max_.Alloc(2 * K_);
+  } else {
+    pool_bytes_ = static_cast<size_t>(NL) * slot_stride_ * hist_elem_;
+    pool_.Alloc(pool_bytes_);
+    pool_base_ = pool_.get();
+  }
   cand_.Alloc(static_cast<size_t>(NL) * std::max<size_t>(1, owned_features_.size()));
   hist_tasks_.Alloc(NL);
   const size_t max_chunks = static_cast<size_t>(n_) / kPartChunk + NL + 1;
@@ -142,11 +164,30 @@ void CudaEngine::BuildPartitions() {
 void CudaEngine::SetupOwnership() {
   const int nb = train_->num_total_bin;
   std::vector<unsigned char> owner(nb, 0); std::vector<int> local(nb);
-  for (int b = 0; b < nb; ++b) local[b] = b;
-  bin_owner_.Upload(owner, stream_); bin_local_.Upload(local, stream_);
-  slot_stride_ = nb;
   owned_features_.clear();
-  for (int f = 0; f < train_->num_features; ++f) owned_features_.push_back(f);
+  if (world_ <= 1) {
+    for (int b = 0; b < nb; ++b) local[b] = b;
+    slot_stride_ = nb; slot_strides_[0] = nb;
+    for (int f = 0; f < train_->num_features; ++f) owned_features_.push_back(f);
+  } else {
+    // feature groups go to ranks greedily by bin count (largest first, least-loaded rank, ties to the
+    // lower rank): the same deterministic map on every rank. A group is never split between ranks.
+    const int G = train_->num_groups;
+    std::vector<int> order(G); for (int g = 0; g < G; ++g) order[g] = g;
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return train_->group_num_bin[a] > train_->group_num_bin[b]; });
+    std::vector<long long> load(world_, 0); std::vector<int> gowner(G, 0);
+    for (int g : order) { int best = 0; for (int r = 1; r < world_; ++r) if (load[r] < load[best]) best = r; gowner[g] = best; load[best] += train_->group_num_bin[g]; }
+    std::vector<int> cursor(world_, 0);
+    for (int g = 0; g < G; ++g) {
+      const int r = gowner[g], s = train_->group_bin_start[g];
+      for (int b = 0; b < train_->group_num_bin[g]; ++b) { owner[s + b] = static_cast<unsigned char>(r); local[s + b] = cursor[r] + b; }
+      cursor[r] += train_->group_num_bin[g];
+    }
+    for (int r = 0; r < world_; ++r) slot_strides_[r] = std::max(1, cursor[r]);
+    slot_stride_ = slot_strides_[rank_];
+    for (int f = 0; f < train_->num_features; ++f) if (gowner[train_->feature_meta[f].group] == rank_) owned_features_.push_back(f);
+  }
+  bin_owner_.Upload(owner, stream_); bin_local_.Upload(local, stream_);
 }
 
 int CudaEngine::ChooseRowsPerBlock(long long total_rows) const {
@@ -217,7 +258,7 @@ std::vector<double> CudaEngine::EvalMetric(int data_idx, const std::string& name
   if (name == "l2") kind = kMetL2; else if (name == "rmse") kind = kMetRMSE; else if (name == "l1") kind = kMetL1;
   else if (name == "binary_logloss") kind = kMetBinaryLogloss; else if (name == "binary_error") kind = kMetBinaryError;
   else if (name == "multi_logloss") kind = kMetMultiLogloss; else if (name == "multi_error" && cfg_.multi_error_top_k == 1) kind = kMetMultiError;
-  if (kind < 0 || Network::active()) return {};
+  if (kind < 0) return {};
   if ((kind == kMetL2 || kind == kMetRMSE || kind == kMetL1) && cfg_.reg_sqrt) return {};
   const Dataset* ds = data_idx == 0 ? train_ : valid_[data_idx - 1].ds;
   DeviceDataset* dd = data_idx == 0 ? dd_ : valid_[data_idx - 1].dd;
@@ -230,6 +271,7 @@ std::vector<double> CudaEngine::EvalMetric(int data_idx, const std::string& name
   double h[2];
   FB_CUDA(cudaMemcpyAsync(h, root_sums_d_.get(), sizeof(h), cudaMemcpyDeviceToHost, stream_));
   FB_CUDA(cudaStreamSynchronize(stream_));
+  Network::SumDouble(h, 2);   // rows are sharded over ranks: (weighted loss, weight) sums add up
   *supported = true;
   double v = h[1] > 0 ? h[0] / h[1] : 0.0;
   if (kind == kMetRMSE) v = std::sqrt(v);

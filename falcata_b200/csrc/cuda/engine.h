@@ -84,7 +84,13 @@ class CudaEngine : public DeviceEngine {
   DevBuf<LeafInfo> leaves_;
   DevBuf<SplitRecord> best_;
   DevBuf<CandLite> cand_;
-  DevBuf<char> pool_;
+  DevBuf<char> pool_;              // single rank: owned here; multi-rank: the pool lives in the symmetric heap
+  char* pool_base_ = nullptr; size_t pool_bytes_ = 0;
+  // ---- multi-rank state (world_ > 1) ----
+  Fabric* fabric_ = nullptr; int rank_ = 0, world_ = 1;
+  long long slot_strides_[kMaxRanks] = {0};
+  size_t off_pool_ = 0, off_counts_ = 0, off_best_ = 0, flag_hist_ = 0, flag_best_ = 0;
+  DevBuf<float> global_max_;
   long long slot_stride_ = 0;      // bins per pool slot on this rank
   size_t hist_elem_ = 8;
   DevBuf<HistPartition> parts_; std::vector<HistPartition> h_parts_; int max_part_bins_ = 0;

@@ -1,10 +1,15 @@
 // Device engine: one boosting iteration and the level loop of one tree.
 //
 // Per level (all splitting leaves at once): partition flags -> scan + child/leaf/task setup ->
-// scatter -> construct (smaller children, fused reduce-scatter epilogue) -> find (+ in-place
-// larger = parent - smaller) -> per-leaf argmax -> ONE read-back of the leaf records and best
-// splits, on which the host applies the gain-ranked leaf budget. Exact child counts come back with
-// that read-back, so there is no second synchronisation per level.
+// scatter -> construct (smaller children; the epilogue adds each bin into the slot of the rank that
+// owns its feature) -> find on the owned slice (+ in-place larger = parent - smaller) -> per-leaf
+// argmax (multi-rank: stored into every peer, then an argmax over the ranks' records) -> ONE
+// read-back of the leaf records and best splits, on which the host applies the gain-ranked leaf
+// budget. Exact child counts come back with that read-back: no second synchronisation per level.
+//
+// Multi-rank ordering (all inside kernels, no NCCL): construct's last block raises "construct done"
+// on every peer; the split search waits for all ranks' flags; its last block raises "best published";
+// the gather waits for those. Every wait is bounded and reports through the status word.
 #include "engine.h"
 
 namespace fb {
@@ -40,13 +45,14 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
                              dd_->query_boundaries.size() ? dd_->query_boundaries.get() : nullptr, dd_->num_queries, label_gain_.get(),
                              static_cast<int>(label_gain_.size()), n_, grad_.get(), hess_.get(), maxbuf_.get(), stream_);
   }
+  // quantization scales must be the same on every rank: max over ranks of the per-class maxima
+  if (world_ > 1 && quant_) fabric_->AllReduce(kFabricMaxF32, maxbuf_.get(), global_max_.get(), 2 * K_, stream_);
   clock_.End(stream_);
   bool any_split = false;
   for (int k = 0; k < K_; ++k) {
     std::unique_ptr<Tree> tree;
     const bool need = obj_ == nullptr || obj_->ClassNeedTrain(k);
     if (need && train_->num_features > 0) {
-      // TrainTree reads grad_/hess_ through these members
       cur_grad_ = grad + static_cast<size_t>(k) * n_; cur_hess_ = hess + static_cast<size_t>(k) * n_;
       tree.reset(TrainTree(k, iter * K_ + k));
     } else tree.reset(new Tree(2));
@@ -55,7 +61,6 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
       tree->Shrink(shrinkage);
       // training rows through the final partition; validation rows by traversal
       clock_.Begin(st_score_, stream_);
-      FB_CUDA(cudaStreamSynchronize(stream_));
       leaf_value_.Upload(tree->leaf_value.data(), tree->num_leaves, stream_);
       LaunchAddLeafOutputs(leaves_.get(), leaf_value_.get(), tree->num_leaves, idx_[0].get(), idx_[1].get(), score_.get() + static_cast<size_t>(k) * n_, stream_);
       clock_.End(stream_);
@@ -63,8 +68,8 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
         DevTree dt; UploadTreeForTraversal(*tree, train_, &dt);
         for (auto& vs : valid_) LaunchAddTreeBinned(dt, vs.dd->rows.get(), vs.dd->row_stride, vs.ds->num_data, 1.f, vs.score.get() + static_cast<size_t>(k) * vs.ds->num_data, stream_);
       }
-      if (std::fabs(init_scores[k]) > kEpsilon) tree->AddBias(init_scores[k]);
       FB_CUDA(cudaStreamSynchronize(stream_));   // leaf_value upload source and traversal staging are host memory
+      if (std::fabs(init_scores[k]) > kEpsilon) tree->AddBias(init_scores[k]);
     } else {
       double outv = 0.0;
       if (iter == 0) { outv = (!need && obj_ != nullptr) ? obj_->BoostFromScore(k) : init_scores[k]; if (!need) AddConstantToScores(outv, k); }
@@ -77,6 +82,7 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
 }
 
 Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
+  const int NL = cfg_.num_leaves;
   col_sampler_.ResetByTree(tree_index);
   // features searched on this rank this tree (owned, sampled, numerical) and the rest of the owned ones
   std::vector<int> feats, subs;
@@ -85,54 +91,77 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   const int NF = static_cast<int>(feats.size()), NS = static_cast<int>(subs.size());
 
   clock_.Begin(st_quant_, stream_);
+  // The pool is cleared BEFORE this tree's first cross-rank exchange: a peer can only start adding
+  // into this rank's slots after it has seen this rank's contribution to that exchange.
+  FB_CUDA(cudaMemsetAsync(pool_base_, 0, pool_bytes_, stream_));
   if (quant_) {
-    LaunchQuantize(cur_grad_, cur_hess_, n_, maxbuf_.get() + 2 * class_id, nullptr, cfg_.quant_bins_resolved, cfg_.quant == QuantMode::Stochastic,
-                   static_cast<uint32_t>(cfg_.seed), static_cast<uint32_t>(tree_index), static_cast<uint64_t>(train_->global_row_offset),
-                   const_cast<uint8_t*>(gh_base_), gh_stride_, scales_.get(), root_sums_i_.get(), stream_);
+    LaunchQuantize(cur_grad_, cur_hess_, n_, maxbuf_.get() + 2 * class_id, world_ > 1 ? global_max_.get() + 2 * class_id : nullptr, cfg_.quant_bins_resolved,
+                   cfg_.quant == QuantMode::Stochastic, static_cast<uint32_t>(cfg_.seed), static_cast<uint32_t>(tree_index),
+                   static_cast<uint64_t>(train_->global_row_offset), const_cast<uint8_t*>(gh_base_), gh_stride_, scales_.get(), root_sums_i_.get(), stream_);
+    if (world_ > 1) fabric_->AllReduce(kFabricSumI64, root_sums_i_.get(), root_sums_i_.get(), 2, stream_);
   } else {
     LaunchInterleave(cur_grad_, cur_hess_, n_, gh2_.get(), partial_.get(), static_cast<int>(partial_.size() / 2), root_sums_d_.get(), stream_);
+    if (world_ > 1) fabric_->AllReduce(kFabricSumF64, root_sums_d_.get(), root_sums_d_.get(), 2, stream_);
   }
   InitRootKernel<<<1, 1, 0, stream_>>>(leaves_.get(), root_sums_i_.get(), root_sums_d_.get(), scales_.get(), quant_ ? 1 : 0, n_, train_->global_num_data, sp_);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
-  pool_.Zero(stream_);
   LaunchInitIndices(idx_[0].get(), n_, stream_);
   clock_.End(stream_);
 
   // ---- common launch descriptors ----
-  HistArgs ha;
+  HistArgs ha = HistArgs();
   ha.rows = dd_->rows.get(); ha.row_stride = dd_->row_stride; ha.num_groups = dd_->num_groups; ha.gh_base = gh_base_; ha.gh_stride = gh_stride_;
   ha.idx[0] = idx_[0].get(); ha.idx[1] = idx_[1].get(); ha.tasks = hist_tasks_.get(); ha.parts = parts_.get(); ha.num_parts = static_cast<int>(h_parts_.size());
-  ha.max_part_bins = max_part_bins_; ha.group_bin_start = dd_->group_bin_start.get();
-  const int qb = std::max(2, cfg_.quant_bins_resolved);
-  ha.sub_rows = quant_ ? std::max(1, std::min(65535 / qb, 32767 / std::max(1, qb / 2))) : (1 << 30);
-  for (int r = 0; r < 8; ++r) { ha.dest.pool[r] = nullptr; ha.dest.slot_stride[r] = 0; }
-  ha.dest.pool[0] = pool_.get(); ha.dest.slot_stride[0] = slot_stride_; ha.dest.bin_owner = bin_owner_.get(); ha.dest.bin_local = bin_local_.get();
-  ha.dest.num_ranks = 1; ha.dest.rank = 0;
+  ha.max_part_bins = max_part_bins_; ha.group_bin_start = dd_->group_bin_start.get(); ha.sub_rows = sub_rows_;
+  ha.dest.bin_owner = bin_owner_.get(); ha.dest.bin_local = bin_local_.get(); ha.dest.num_ranks = world_; ha.dest.rank = rank_;
+  for (int r = 0; r < kMaxRanks; ++r) { ha.dest.pool[r] = nullptr; ha.dest.slot_stride[r] = 0; }
+  if (world_ > 1) { for (int r = 0; r < world_; ++r) { ha.dest.pool[r] = fabric_->Ptr<char>(r, off_pool_); ha.dest.slot_stride[r] = slot_strides_[r]; } }
+  else { ha.dest.pool[0] = pool_base_; ha.dest.slot_stride[0] = slot_stride_; }
   ha.num_total_bin = train_->num_total_bin; ha.lane_mode = lane_mode_; ha.lane_bins = lane_bins_;
-  FindArgs fa;
+  ha.sig.world = world_;
+  FindArgs fa = FindArgs();
   fa.features = features_.get(); fa.num_features = NF; fa.sub_features = sub_features_.get(); fa.num_sub_features = NS; fa.meta = dd_->feature_meta.get();
-  fa.bin_local = bin_local_.get(); fa.pool = pool_.get(); fa.slot_stride = slot_stride_; fa.leaves = leaves_.get(); fa.scales = scales_.get(); fa.params = sp_;
+  fa.bin_local = bin_local_.get(); fa.pool = pool_base_; fa.slot_stride = slot_stride_; fa.leaves = leaves_.get(); fa.scales = scales_.get(); fa.params = sp_;
   fa.cand = cand_.get(); fa.best = best_.get(); fa.quant = quant_ ? 1 : 0;
+  fa.wait.world = world_; fa.wait_best.world = world_; fa.sig.world = world_; fa.leaves_rw = leaves_.get();
+  if (world_ > 1) {
+    const FabricView v = fabric_->View();
+    ha.sig.done_counter = fabric_->done_counter(0); fa.sig.done_counter = fabric_->done_counter(1);
+    for (int r = 0; r < world_; ++r) {
+      ha.sig.peer_flag[r] = fabric_->Ptr<unsigned int>(r, flag_hist_) + rank_;
+      fa.sig.peer_flag[r] = fabric_->Ptr<unsigned int>(r, flag_best_) + rank_;
+      fa.peer_best[r] = fabric_->Ptr<SplitRecord>(r, off_best_) + static_cast<size_t>(rank_) * NL;
+    }
+    fa.wait.flags = fabric_->Local<unsigned int>(flag_hist_); fa.wait.max_spins = v.max_spins; fa.wait.status = v.status;
+    fa.wait_best.flags = fabric_->Local<unsigned int>(flag_best_); fa.wait_best.max_spins = v.max_spins; fa.wait_best.status = v.status;
+    fa.counts = fabric_->Local<int>(off_counts_); fa.counts_stride = NL;
+    fa.gathered = fabric_->Local<SplitRecord>(off_best_); fa.gathered_stride = NL;
+  }
+  auto construct_and_find = [&]() {
+    if (world_ > 1) { ha.sig.epoch = fabric_->NextEpoch(); fa.wait.epoch = ha.sig.epoch; }
+    clock_.Begin(st_hist_, stream_);
+    if (quant_) LaunchHistConstructQuant(ha, stream_); else LaunchHistConstructFloat(ha, stream_);
+    clock_.End(stream_);
+    if (world_ > 1) { fa.sig.epoch = fabric_->NextEpoch(); fa.wait_best.epoch = fa.sig.epoch; }
+    clock_.Begin(st_find_, stream_);
+    LaunchFindSplits(fa, stream_); LaunchReduceBest(fa, stream_); LaunchGatherBest(fa, stream_);
+    clock_.End(stream_);
+  };
 
   char* hb = h_level_blob_.get(); char* db = level_blob_.get();
-  std::unique_ptr<Tree> tree(new Tree(cfg_.num_leaves));
+  std::unique_ptr<Tree> tree(new Tree(NL));
 
   // ---- root ----
   {
     HistTask t; t.slot = 0; t.begin = 0; t.count = n_; t.buffer = 0; t.block_begin = 0; t.pad0 = t.pad1 = 0;
     ha.rows_per_block = ChooseRowsPerBlock(n_); t.num_blocks = (n_ + ha.rows_per_block - 1) / ha.rows_per_block;
-    FindChild fc; fc.leaf = 0; fc.slot = 0; fc.other_slot = 0; fc.is_larger = 0;
+    FindChild fc; fc.leaf = 0; fc.slot = 0; fc.other_slot = 0; fc.is_larger = 0; fc.split = -1; fc.is_left = 1; fc.parent_global = 0; fc.pad = 0;
     memcpy(hb, &t, sizeof(t)); memcpy(hb + sizeof(t), &fc, sizeof(fc));
     FB_CUDA(cudaMemcpyAsync(db, hb, sizeof(t) + sizeof(fc), cudaMemcpyHostToDevice, stream_));
     FB_CUDA(cudaMemcpyAsync(hist_tasks_.get(), db, sizeof(t), cudaMemcpyDeviceToDevice, stream_));
-    ha.num_tasks = 1; ha.total_blocks = t.num_blocks; ha.identity_root = 1;
-    clock_.Begin(st_hist_, stream_);
-    if (quant_) LaunchHistConstructQuant(ha, stream_); else LaunchHistConstructFloat(ha, stream_);
-    clock_.End(stream_);
+    ha.num_tasks = 1; ha.total_blocks = std::max(1, t.num_blocks); ha.identity_root = 1;
     fa.children = reinterpret_cast<const FindChild*>(db + sizeof(t)); fa.num_children = 1;
-    clock_.Begin(st_find_, stream_);
-    LaunchFindSplits(fa, stream_); LaunchReduceBest(fa, stream_);
-    clock_.End(stream_);
+    construct_and_find();
   }
   ReadBackLevel(1);
   {
@@ -144,11 +173,11 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   int next_slot = 1;
   std::vector<int> frontier = {0};
   ha.identity_root = 0;
-  while (tree->num_leaves < cfg_.num_leaves && !frontier.empty()) {
+  while (tree->num_leaves < NL && !frontier.empty()) {
     std::vector<int> cand;
     for (int l : frontier) if (host_leaves_[l].best.feature >= 0 && host_leaves_[l].best.gain > 0.0) cand.push_back(l);
     if (cand.empty()) break;
-    const int budget = cfg_.num_leaves - tree->num_leaves;
+    const int budget = NL - tree->num_leaves;
     if (static_cast<int>(cand.size()) > budget) {
       std::stable_sort(cand.begin(), cand.end(), [&](int a, int b) {
         if (host_leaves_[a].best.gain != host_leaves_[b].best.gain) return host_leaves_[a].best.gain > host_leaves_[b].best.gain;
@@ -170,48 +199,47 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
       const SplitRecord& b = P.best;
       const FeatureMeta& m = train_->feature_meta[b.feature];
       const BinMapper& bm = *train_->mappers[m.real_index];
+      const LeafInfo& PL = h_leaves_[l];
       const int right = tree->Split(l, b.feature, m.real_index, static_cast<uint32_t>(b.threshold), bm.BinToValue(b.threshold), b.left_out, b.right_out,
                                     b.left_cnt, b.right_cnt, b.left_h, b.right_h, static_cast<float>(b.gain), m.missing_type, b.default_left != 0);
-      tree->internal_count[tree->num_leaves - 2] = h_leaves_[l].num_data_global;
+      tree->internal_count[tree->num_leaves - 2] = PL.num_data_global;
       PartSplit& q = ps[s];
+      memset(&q, 0, sizeof(q));
       q.leaf = l; q.right_leaf = right; q.begin = P.begin; q.count = P.count; q.buffer = P.buffer; q.group = m.group; q.bundled = m.bundled; q.group_offset = m.group_offset;
       q.num_bin = m.num_bin; q.most_freq_bin = m.most_freq_bin; q.threshold = b.threshold; q.default_left = b.default_left; q.missing_type = m.missing_type;
-      q.default_bin = m.default_bin; q.is_categorical = 0; for (int w = 0; w < 8; ++w) q.cat_bitset[w] = 0;
+      q.default_bin = m.default_bin; q.is_categorical = 0;
       q.chunk_begin = chunk_cursor; q.num_chunks = (P.count + kPartChunk - 1) / kPartChunk; chunk_cursor += q.num_chunks;
       ChildInit& c = ci[s];
+      memset(&c, 0, sizeof(c));
       c.smaller_is_left = b.left_cnt <= b.right_cnt ? 1 : 0;
       const int fresh = next_slot++;
       c.left_slot = c.smaller_is_left ? fresh : P.slot; c.right_slot = c.smaller_is_left ? P.slot : fresh;
       c.left_g = b.left_g; c.left_h = b.left_h; c.right_g = b.right_g; c.right_h = b.right_h; c.left_out = b.left_out; c.right_out = b.right_out;
       c.left_gi = b.left_gi; c.left_hi = b.left_hi;
-      const LeafInfo& PL = h_leaves_[l];
       c.right_gi = PL.sum_gi - b.left_gi; c.right_hi = PL.sum_hi - b.left_hi;
       c.hist_block_begin = block_cursor; c.hist_num_blocks = (P.count + ha.rows_per_block - 1) / ha.rows_per_block; block_cursor += c.hist_num_blocks;
-      fc[2 * s].leaf = l; fc[2 * s].slot = c.left_slot; fc[2 * s].other_slot = c.right_slot; fc[2 * s].is_larger = c.smaller_is_left ? 0 : 1;
-      fc[2 * s + 1].leaf = right; fc[2 * s + 1].slot = c.right_slot; fc[2 * s + 1].other_slot = c.left_slot; fc[2 * s + 1].is_larger = c.smaller_is_left ? 1 : 0;
-      HostLeaf& Rl = host_leaves_[right];
-      Rl.slot = c.right_slot; P.slot = c.left_slot;
+      FindChild& fl = fc[2 * s]; FindChild& fr = fc[2 * s + 1];
+      fl.leaf = l; fl.slot = c.left_slot; fl.other_slot = c.right_slot; fl.is_larger = c.smaller_is_left ? 0 : 1; fl.split = s; fl.is_left = 1; fl.parent_global = PL.num_data_global; fl.pad = 0;
+      fr.leaf = right; fr.slot = c.right_slot; fr.other_slot = c.left_slot; fr.is_larger = c.smaller_is_left ? 1 : 0; fr.split = s; fr.is_left = 0; fr.parent_global = PL.num_data_global; fr.pad = 0;
+      host_leaves_[right].slot = c.right_slot; P.slot = c.left_slot;
       next.push_back(l); next.push_back(right);
     }
     const size_t blob_bytes = (sizeof(PartSplit) + sizeof(ChildInit) + 2 * sizeof(FindChild)) * S;
     FB_CUDA(cudaMemcpyAsync(db, hb, blob_bytes, cudaMemcpyHostToDevice, stream_));
-    PartArgs pa;
+    PartArgs pa = PartArgs();
     pa.rows = dd_->rows.get(); pa.row_stride = dd_->row_stride; pa.idx[0] = idx_[0].get(); pa.idx[1] = idx_[1].get();
     pa.cols = dd_->cols.size() ? dd_->cols.get() : nullptr; pa.col_stride = n_;
     pa.splits = reinterpret_cast<const PartSplit*>(db); pa.num_splits = S; pa.total_chunks = chunk_cursor; pa.bits = bits_.get(); pa.chunk_left = chunk_left_.get();
     pa.split_left_total = split_left_total_.get(); pa.leaves = leaves_.get(); pa.child_init = reinterpret_cast<const ChildInit*>(db + sizeof(PartSplit) * S);
     pa.hist_tasks = hist_tasks_.get(); pa.rows_per_block = ha.rows_per_block;
+    pa.world = world_;
+    if (world_ > 1) for (int r = 0; r < world_; ++r) pa.peer_counts[r] = fabric_->Ptr<int>(r, off_counts_) + static_cast<size_t>(rank_) * NL;
     clock_.Begin(st_part_, stream_);
     LaunchPartitionFlags(pa, stream_); LaunchPartitionScanSetup(pa, stream_); LaunchPartitionScatter(pa, stream_);
     clock_.End(stream_);
-    ha.num_tasks = S; ha.total_blocks = block_cursor;
-    clock_.Begin(st_hist_, stream_);
-    if (quant_) LaunchHistConstructQuant(ha, stream_); else LaunchHistConstructFloat(ha, stream_);
-    clock_.End(stream_);
+    ha.num_tasks = S; ha.total_blocks = std::max(1, block_cursor);
     fa.children = reinterpret_cast<const FindChild*>(db + (sizeof(PartSplit) + sizeof(ChildInit)) * S); fa.num_children = 2 * S;
-    clock_.Begin(st_find_, stream_);
-    LaunchFindSplits(fa, stream_); LaunchReduceBest(fa, stream_);
-    clock_.End(stream_);
+    construct_and_find();
     ReadBackLevel(tree->num_leaves);
     for (int l : next) {
       const LeafInfo& R = h_leaves_[l];
@@ -229,7 +257,12 @@ void CudaEngine::ReadBackLevel(int num_leaves) {
   leaves_.Download(h_leaves_.get(), num_leaves, stream_);
   best_.Download(h_best_.get(), num_leaves, stream_);
   clock_.End(stream_);
-  FB_CUDA(cudaStreamSynchronize(stream_));
+  if (world_ > 1) {
+    const int st = fabric_->CheckStatus(stream_);   // synchronises the stream
+    if (st != 0) Log::Fatal("A cross-rank wait gave up (device status %d): a peer rank did not reach the same step", st);
+  } else {
+    FB_CUDA(cudaStreamSynchronize(stream_));
+  }
 }
 
 }  // namespace fb

@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(kHistThreads) HistQuantKernel(HistArgs a) {
   const HistTask task = a.tasks[ti];
   const int chunk = blockIdx.x - task.block_begin;
   const long long row0 = static_cast<long long>(chunk) * a.rows_per_block;
-  if (chunk >= task.num_blocks || row0 >= task.count) return;
+  if (chunk >= task.num_blocks || row0 >= task.count) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
   const int nrows = static_cast<int>(min(static_cast<long long>(a.rows_per_block), task.count - row0));
   const int ngroups = part.group_end - part.group_begin;
   const int G4 = (ngroups + 3) >> 2;
@@ -88,6 +88,7 @@ __global__ void __launch_bounds__(kHistThreads) HistQuantKernel(HistArgs a) {
     else { const int v = s_packed[b]; h = v & 0xFFFF; g = (v - static_cast<int>(h)) >> 16; }
     if (g != 0 || h != 0) FlushBinQuant(a.dest, task.slot, part.bin_begin + b, g, h);
   }
+  if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y);
 }
 
 // Lane-per-group instance, fed by an asynchronous gather pipeline.
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(kHistThreads) HistQuantLaneKernel(HistArgs a) 
   const HistTask task = a.tasks[ti];
   const int chunk = blockIdx.x - task.block_begin;
   const long long row0 = static_cast<long long>(chunk) * a.rows_per_block;
-  if (chunk >= task.num_blocks || row0 >= task.count) return;
+  if (chunk >= task.num_blocks || row0 >= task.count) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
   const int nrows = static_cast<int>(min(static_cast<long long>(a.rows_per_block), task.count - row0));
   const int g0 = blockIdx.y * 32;
   const int ng = min(32, a.num_groups - g0);
@@ -201,6 +202,7 @@ __global__ void __launch_bounds__(kHistThreads) HistQuantLaneKernel(HistArgs a) 
     for (int w = 0; w < kTiles; ++w) { const int v = tiles[w * kTile + cell]; const int h = v & 0xFFFF; sg += (v - h) >> 16; sh += h; }
     if (sg != 0 || sh != 0) FlushBinQuant(a.dest, task.slot, gstart + b, sg, sh);
   }
+  if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y);
 }
 
 
@@ -213,7 +215,7 @@ __global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
   const HistTask task = a.tasks[ti];
   const int chunk = blockIdx.x - task.block_begin;
   const long long row0 = static_cast<long long>(chunk) * a.rows_per_block;
-  if (chunk >= task.num_blocks || row0 >= task.count) return;
+  if (chunk >= task.num_blocks || row0 >= task.count) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
   const int nrows = static_cast<int>(min(static_cast<long long>(a.rows_per_block), task.count - row0));
   const int ngroups = part.group_end - part.group_begin;
   const int G4 = (ngroups + 3) >> 2;
@@ -249,6 +251,7 @@ __global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
     if (owner == d.rank) { atomicAdd(p, static_cast<double>(g)); atomicAdd(p + 1, static_cast<double>(h)); }
     else { atomicAdd_system(p, static_cast<double>(g)); atomicAdd_system(p + 1, static_cast<double>(h)); }
   }
+  if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y);
 }
 
 }  // namespace

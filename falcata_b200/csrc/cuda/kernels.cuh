@@ -2,6 +2,7 @@
 // One launcher per kernel (or fused kernel); the engine and the kernel-level test API call these.
 #pragma once
 #include "device_common.cuh"
+#include "fabric.h"
 #include "fb/learner.h"
 
 namespace fb {
@@ -45,6 +46,7 @@ struct HistArgs {
   int lane_mode;            // 0: flat items + shared atomics; 1: lane-per-group warp-private tiles (no atomics); 2: lane-per-group, one shared tile + atomics
   int lane_bins;            // lane modes: bins per group tile (16 or 64)
   HistDest dest;
+  FabricSignal sig;         // world > 1: the last block raises this rank's "construct done" flag on every peer
 };
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s);
 void LaunchHistConstructFloat(const HistArgs& a, cudaStream_t s);
@@ -52,7 +54,7 @@ void LaunchHistConstructFloat(const HistArgs& a, cudaStream_t s);
 bool LaunchHistConstructQuantTC(const HistArgs& a, cudaStream_t s);
 
 // ------------------------------------------------------------ split find ----
-struct FindChild { int leaf; int slot; int other_slot; int is_larger; };   // larger: bins = pool[slot] - pool[other_slot], written back to pool[slot]
+struct FindChild { int leaf; int slot; int other_slot; int is_larger; int split; int is_left; int parent_global; int pad; };   // larger: bins = pool[slot] - pool[other_slot], written back to pool[slot]
 
 struct CandLite {      // best threshold of one (child, feature)
   double gain; int feature; int threshold; int default_left; int left_cnt;
@@ -72,9 +74,18 @@ struct FindArgs {
   CandLite* cand;                                 // [num_children x num_features]
   SplitRecord* best;                              // [leaf]
   int quant;
+  // ---- multi-rank (world > 1) ----
+  FabricWait wait;                                // construct-done flags of all ranks (the reduce-scatter is complete when they are up)
+  const int* counts; int counts_stride;           // [rank][split] local left counts published by every rank's partition
+  LeafInfo* leaves_rw;                            // exact global row counts are written back here
+  SplitRecord* peer_best[kMaxRanks];              // address of best_slots[this rank][0] inside every rank's heap
+  const SplitRecord* gathered; int gathered_stride;   // local [rank][leaf] records written by the peers
+  FabricSignal sig;                               // "rank-local best splits published" signal
+  FabricWait wait_best;
 };
 void LaunchFindSplits(const FindArgs& a, cudaStream_t s);      // per (child, feature) search + in-place larger-child subtraction
-void LaunchReduceBest(const FindArgs& a, cudaStream_t s);      // per child argmax over features -> SplitRecord
+void LaunchReduceBest(const FindArgs& a, cudaStream_t s);      // per child argmax over features -> SplitRecord (world > 1: stored into every peer)
+void LaunchGatherBest(const FindArgs& a, cudaStream_t s);      // world > 1: argmax over the ranks' records
 
 // ------------------------------------------------------------- partition ----
 constexpr int kPartChunk = 2048;
@@ -97,6 +108,7 @@ struct PartArgs {
   const ChildInit* child_init;
   HistTask* hist_tasks;      // one per split: the smaller child
   int rows_per_block;
+  int world; int* peer_counts[kMaxRanks];   // world > 1: address of counts[this rank][0] inside every rank's heap
 };
 void LaunchPartitionFlags(const PartArgs& a, cudaStream_t s);
 void LaunchPartitionScanSetup(const PartArgs& a, cudaStream_t s);

@@ -44,7 +44,7 @@ int FB_OpHistogram(const uint8_t* rows, int row_stride, int num_groups, const vo
   t.num_blocks = (count + rows_per_block - 1) / rows_per_block;
   DevBuf<HistTask> d_task; d_task.Upload(&t, 1, s);
   DevBuf<char> pool; pool.Alloc(static_cast<size_t>(total) * (quant ? 8 : 16)); pool.Zero(s);
-  HistArgs a;
+  HistArgs a = HistArgs();
   a.rows = rows; a.row_stride = row_stride; a.num_groups = num_groups; a.gh_base = static_cast<const uint8_t*>(gh); a.gh_stride = gh_stride;
   a.idx[0] = idx; a.idx[1] = idx; a.tasks = d_task.get(); a.num_tasks = 1; a.total_blocks = t.num_blocks; a.parts = d_parts.get(); a.num_parts = static_cast<int>(parts.size());
   a.max_part_bins = mpb; a.group_bin_start = d_gstart.get(); a.rows_per_block = rows_per_block;
@@ -100,7 +100,7 @@ int FB_OpPartition(const uint8_t* rows, int row_stride, const int* idx, int coun
   DevBuf<LeafInfo> d_leaves2; d_leaves2.Alloc(2); FB_CUDA(cudaMemcpyAsync(d_leaves2.get(), d_leaves.get(), sizeof(LeafInfo), cudaMemcpyDeviceToDevice, s));
   DevBuf<unsigned int> bits; bits.Alloc(static_cast<size_t>(sp.num_chunks + 1) * (kPartChunk / 32));
   DevBuf<int> chunk_left; chunk_left.Alloc(sp.num_chunks + 1); DevBuf<int> left_total; left_total.Alloc(1); DevBuf<HistTask> tasks; tasks.Alloc(1);
-  PartArgs a; a.rows = rows; a.row_stride = row_stride; a.cols = nullptr; a.col_stride = 0; a.idx[0] = const_cast<int*>(idx); a.idx[1] = out_idx; a.splits = d_sp.get(); a.num_splits = 1; a.total_chunks = sp.num_chunks;
+  PartArgs a = PartArgs(); a.rows = rows; a.row_stride = row_stride; a.cols = nullptr; a.col_stride = 0; a.idx[0] = const_cast<int*>(idx); a.idx[1] = out_idx; a.splits = d_sp.get(); a.num_splits = 1; a.total_chunks = sp.num_chunks;
   a.bits = bits.get(); a.chunk_left = chunk_left.get(); a.split_left_total = left_total.get(); a.leaves = d_leaves2.get(); a.child_init = d_ci.get(); a.hist_tasks = tasks.get(); a.rows_per_block = 2048;
   LaunchPartitionFlags(a, s); LaunchPartitionScanSetup(a, s); LaunchPartitionScatter(a, s);
   FB_CUDA(cudaMemcpyAsync(left_count, left_total.get(), sizeof(int), cudaMemcpyDeviceToHost, s));

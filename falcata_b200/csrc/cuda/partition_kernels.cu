@@ -87,6 +87,9 @@ __global__ void __launch_bounds__(kPartThreads) PartitionScanSetupKernel(PartArg
   if (threadIdx.x == 0) {
     const int nl = s_carry, nr = sp.count - nl;
     a.split_left_total[si] = nl;
+    // multi-rank: every rank learns every rank's left count (summed by the split search, which runs
+    // after the construct-done flags; this store is ordered before them by the stream)
+    for (int r = 0; r < a.world; ++r) if (a.world > 1) a.peer_counts[r][si] = nl;
     const ChildInit ci = a.child_init[si];
     const LeafInfo parent = a.leaves[sp.leaf];
     LeafInfo L = parent, R = parent;

@@ -32,8 +32,18 @@ __device__ inline void LoadBin(const void* child, const void* other, bool larger
   }
 }
 
+// Exact row count of a child over all ranks: every rank's partition published its local left count.
+__device__ inline int ChildGlobalCount(const FindArgs& a, const FindChild& ch, int local_value) {
+  if (a.wait.world <= 1 || ch.split < 0) return local_value;
+  int lsum = 0;
+  for (int r = 0; r < a.wait.world; ++r) lsum += __ldcg(a.counts + static_cast<size_t>(r) * a.counts_stride + ch.split);
+  return ch.is_left ? lsum : ch.parent_global - lsum;
+}
+
 template <bool QUANT>
 __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
+  // multi-rank: the owned slices are complete once every rank's construct has raised its flag
+  if (a.wait.world > 1) FabricWaitAll(a.wait);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int fi = blockIdx.y * kWarpsPerBlock + warp;
   if (fi >= a.num_features + a.num_sub_features) return;
@@ -42,7 +52,8 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
   const FindChild ch = a.children[blockIdx.x];
   if (!search && !ch.is_larger) return;
   const FeatureMeta m = a.meta[f];
-  const LeafInfo leaf = a.leaves[ch.leaf];
+  LeafInfo leaf = a.leaves[ch.leaf];
+  leaf.num_data_global = ChildGlobalCount(a, ch, leaf.num_data_global);
   const int nb = m.num_bin;
   const int nstored = m.bundled ? nb - 1 : nb;
   const long long base = a.bin_local[m.hist_offset];
@@ -166,7 +177,9 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
 
 __global__ void ReduceBestKernel(FindArgs a) {
   const FindChild ch = a.children[blockIdx.x];
-  const LeafInfo leaf = a.leaves[ch.leaf];
+  LeafInfo leaf = a.leaves[ch.leaf];
+  leaf.num_data_global = ChildGlobalCount(a, ch, leaf.num_data_global);
+  __shared__ SplitRecord s_rec;
   __shared__ double s_gain[128]; __shared__ int s_feat[128], s_thr[128], s_idx[128];
   double bg = -1.0 / 0.0; int bf = -1, bt = 0, bi = -1;
   for (int k = threadIdx.x; k < a.num_features; k += blockDim.x) {
@@ -195,11 +208,50 @@ __global__ void ReduceBestKernel(FindArgs a) {
       r.left_out = LeafOutput(r.left_g, FB_ADD(r.left_h, kEpsilon), a.params, r.left_cnt, leaf.output);
       r.right_out = LeafOutput(r.right_g, FB_ADD(r.right_h, kEpsilon), a.params, r.right_cnt, leaf.output);
     }
-    a.best[ch.leaf] = r;
+    if (a.wait.world > 1) { s_rec = r; a.leaves_rw[ch.leaf].num_data_global = leaf.num_data_global; }
+    else a.best[ch.leaf] = r;
+  }
+  if (a.wait.world > 1) {
+    // all-gather of the rank-local best split: plain stores into every rank's slot array, then the
+    // last block of the grid raises this rank's flag on every peer
+    __syncthreads();
+    const unsigned int* src = reinterpret_cast<const unsigned int*>(&s_rec);
+    constexpr int kWords = sizeof(SplitRecord) / 4;
+    for (int p = 0; p < a.wait.world; ++p) {
+      unsigned int* dst = reinterpret_cast<unsigned int*>(a.peer_best[p] + ch.leaf);
+      for (int w = threadIdx.x; w < kWords; w += blockDim.x) dst[w] = src[w];
+    }
+    FabricSignalDone(a.sig, gridDim.x);
   }
 }
 
+// Multi-rank: the best split of a leaf is the best of the ranks' records (each rank searched only
+// the features it owns). Every rank runs this on the same records, so all ranks decide alike.
+__global__ void GatherBestKernel(FindArgs a) {
+  FabricWaitAll(a.wait_best);
+  if (threadIdx.x != 0) return;
+  const FindChild ch = a.children[blockIdx.x];
+  SplitRecord best; InitSplitRecord(&best);
+  int best_real = -1;
+  constexpr int kWords = sizeof(SplitRecord) / 4;
+  for (int r = 0; r < a.wait_best.world; ++r) {
+    SplitRecord rec;
+    const unsigned int* src = reinterpret_cast<const unsigned int*>(a.gathered + static_cast<size_t>(r) * a.gathered_stride + ch.leaf);
+    unsigned int* dst = reinterpret_cast<unsigned int*>(&rec);
+    for (int w = 0; w < kWords; ++w) dst[w] = __ldcg(src + w);
+    const int real = rec.feature >= 0 ? a.meta[rec.feature].real_index : -1;
+    if (SplitBetter(rec.gain, real, rec.threshold, best.gain, best_real, best.threshold)) { best = rec; best_real = real; }
+  }
+  a.best[ch.leaf] = best;
+}
+
 }  // namespace
+
+void LaunchGatherBest(const FindArgs& a, cudaStream_t s) {
+  if (a.num_children <= 0 || a.wait_best.world <= 1) return;
+  GatherBestKernel<<<a.num_children, 32, 0, s>>>(a);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
 
 void LaunchFindSplits(const FindArgs& a, cudaStream_t s) {
   if (a.num_children <= 0) return;

@@ -1,2 +1,36 @@
 """Multi-GPU plumbing: rank bootstrap over ``torch.distributed``, host collective injection for the
-CPU learners, and the symmetric-heap handle exchange for the in-kernel NVLink collectives."""
+CPU learners, and the symmetric-heap handle exchange for the in-kernel NVLink collectives.
+
+Typical use (one process per GPU, started with torchrun)::
+
+    torch.cuda.set_device(local_rank); dist.init_process_group("nccl")
+    falcata_b200.parallel.init()
+    ds = falcata_b200.Dataset(shard_tensor, label).set_global_rows(offset, total_rows)
+    bst = falcata_b200.train({"tree_learner": "data", "device_type": "cuda", ...}, ds)
+"""
+from . import bootstrap
+from .bootstrap import free_host_network, init_device_fabric, init_host_network, shutdown_device_fabric, world
+
+
+def init(heap_bytes: int = 256 << 20, device: bool = True) -> None:
+    """Connect this rank to its peers: host collectives always, the device fabric when CUDA is used."""
+    init_host_network()
+    if device:
+        import torch
+
+        if torch.cuda.is_available():
+            init_device_fabric(heap_bytes)
+
+
+def shutdown() -> None:
+    import torch
+
+    if torch.cuda.is_available():
+        try:
+            shutdown_device_fabric()
+        except Exception:
+            pass
+    free_host_network()
+
+
+__all__ = ["init", "shutdown", "world", "init_host_network", "free_host_network", "init_device_fabric", "shutdown_device_fabric", "bootstrap"]

@@ -27,27 +27,52 @@ def world() -> Tuple[int, int]:
     return (d.get_rank(), d.get_world_size()) if d else (0, 1)
 
 
-def gather_bin_sample(t: Any, sample_cnt: int, seed: int) -> Tuple[np.ndarray, int]:
-    """Rows used to find bin boundaries: a seeded sample of this rank's rows, concatenated over ranks
-    so that every rank derives identical bin mappers. Returns (sample [ns, ncol] float64, total rows)."""
+def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total: int = 0) -> Tuple[np.ndarray, int]:
+    """Rows used to find bin boundaries.
+
+    A global row is sampled iff a uniform number drawn for it (from a generator seeded by the 256K-row
+    chunk the row falls into) is below ``sample_cnt / total``. The choice depends only on the GLOBAL
+    row id, so the sample - and with it every bin boundary - is the same however the rows are sharded
+    over ranks. Each rank contributes the sampled rows of its shard; the shards are concatenated in
+    rank order. Returns (sample [ns, ncol] float64, total rows)."""
     import torch
 
     rank, ws = world()
     n = t.shape[0]
-    total = n
     d = _dist()
-    if d and ws > 1:
-        cnt = torch.tensor([n], dtype=torch.int64, device=t.device if t.is_cuda and d.get_backend() == "nccl" else "cpu")
-        d.all_reduce(cnt)
-        total = int(cnt.item())
-    take = min(n, max(1, int(round(sample_cnt * (n / max(1, total))))))
-    g = torch.Generator(device="cpu"); g.manual_seed(seed * 7919 + rank)
-    idx = torch.randperm(n, generator=g)[:take].sort().values if take < n else torch.arange(n)
-    local = t[idx.to(t.device)].to(torch.float64).cpu().numpy()
+    if total <= 0:
+        total = n
+        if d and ws > 1:
+            cnt = torch.tensor([n], dtype=torch.int64, device=t.device if t.is_cuda and d.get_backend() == "nccl" else "cpu")
+            d.all_reduce(cnt)
+            total = int(cnt.item())
+            offs = [None] * ws
+            d.all_gather_object(offs, n)
+            offset = int(sum(offs[:rank]))
+    p = min(1.0, sample_cnt / max(1, total))
+    chunk = 1 << 18
+    picks = []
+    c = offset // chunk
+    pos = offset
+    end = offset + n
+    while pos < end:
+        lo = pos - c * chunk
+        hi = min(chunk, end - c * chunk)
+        g = torch.Generator(device=t.device)
+        g.manual_seed((seed * 1000003 + c) & 0x7FFFFFFFFFFF)
+        u = torch.rand(chunk, generator=g, device=t.device)[lo:hi]
+        sel = torch.nonzero(u < p, as_tuple=False).flatten() + (pos - offset)
+        picks.append(sel)
+        pos = c * chunk + hi
+        c += 1
+    idx = torch.cat(picks) if picks else torch.zeros(0, dtype=torch.int64, device=t.device)
+    local = t[idx].to(torch.float64).cpu().numpy()
     if d and ws > 1:
         parts = [None] * ws
         d.all_gather_object(parts, local)
         local = np.concatenate(parts, axis=0)
+    if local.shape[0] == 0:
+        local = t[:1].to(torch.float64).cpu().numpy()
     return local, total
 
 
@@ -98,3 +123,43 @@ def free_host_network() -> None:
 
     _safe_call(_lib().FB_NetworkFree())
     _CALLBACKS.clear()
+
+
+def init_device_fabric(heap_bytes: int = 256 << 20) -> None:
+    """Allocate this rank's symmetric heap on the current CUDA device and map every peer's heap.
+
+    The heap holds the histogram pool slices, the split-candidate slots, the per-split row counts and
+    the flag words that the training kernels read and write on peer GPUs directly over NVLink."""
+    import torch
+
+    from ..basic import _lib
+
+    d = _dist()
+    if d is None or d.get_world_size() == 1:
+        return
+    rank, ws = world()
+    lib = _lib()
+    lib.FB_FabricLastError.restype = ctypes.c_char_p
+    buf = ctypes.create_string_buffer(64)
+    if lib.FB_FabricCreate(rank, ws, ctypes.c_int64(heap_bytes), buf) != 0:
+        raise RuntimeError(lib.FB_FabricLastError().decode())
+    mine = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8)
+    dev = torch.device("cuda", torch.cuda.current_device()) if d.get_backend() == "nccl" else torch.device("cpu")
+    outs = [torch.empty(64, dtype=torch.uint8, device=dev) for _ in range(ws)]
+    d.all_gather(outs, mine.to(dev))
+    handles = b"".join(bytes(o.cpu().numpy().tobytes()) for o in outs)
+    if lib.FB_FabricConnect(handles) != 0:
+        raise RuntimeError(lib.FB_FabricLastError().decode())
+    d.barrier()
+
+
+def shutdown_device_fabric() -> None:
+    from ..basic import _lib
+
+    d = _dist()
+    if d is not None:
+        import torch
+
+        torch.cuda.synchronize()
+        d.barrier()
+    _lib().FB_FabricDestroy()

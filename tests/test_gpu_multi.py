@@ -1,0 +1,34 @@
+"""Multi-GPU data-parallel training: the quantized model must be bit-identical at any GPU count."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(world, out, extra=()):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    if world == 1:
+        cmd = [sys.executable, os.path.join(HERE, "multi_gpu_worker.py"), "--out", out, *extra]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", "29517",
+               os.path.join(HERE, "multi_gpu_worker.py"), "--out", out, *extra]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return open(out).read()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("quant", ["stochastic", "fixedpoint"])
+def test_bit_identical_across_gpu_counts(tmp_path, quant):
+    extra = ("--quant", quant)
+    ref = _run(1, str(tmp_path / "m1.txt"), extra)
+    assert "Tree=4" in ref
+    worlds = [w for w in (2, 4, 8) if w <= torch.cuda.device_count()]
+    for w in worlds:
+        got = _run(w, str(tmp_path / f"m{w}.txt"), extra)
+        assert got == ref, f"model differs at {w} GPUs"
