@@ -114,6 +114,9 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     fabric_->Reset();
     pool_bytes_ = static_cast<size_t>(NL) * max_stride * hist_elem_;
     off_pool_ = fabric_->Alloc(pool_bytes_);
+    off_stage_ = fabric_->Alloc(static_cast<size_t>(world_) * NL * max_stride * hist_elem_);
+    stage_local_.Alloc(static_cast<size_t>(NL) * train->num_total_bin * hist_elem_); stage_local_.Zero(stream_);
+    task_done_.Alloc(NL); task_done_.Zero(stream_);
     off_counts_ = fabric_->Alloc(static_cast<size_t>(world_) * NL * sizeof(int));
     off_best_ = fabric_->Alloc(static_cast<size_t>(world_) * NL * sizeof(SplitRecord));
     flag_hist_ = fabric_->NewFlagSlot(); flag_best_ = fabric_->NewFlagSlot();

@@ -91,6 +91,7 @@ class CudaEngine : public DeviceEngine {
   long long slot_strides_[kMaxRanks] = {0};
   size_t off_pool_ = 0, off_counts_ = 0, off_best_ = 0, flag_hist_ = 0, flag_best_ = 0;
   DevBuf<float> global_max_;
+  size_t off_stage_ = 0; DevBuf<char> stage_local_; DevBuf<unsigned int> task_done_;
   long long slot_stride_ = 0;      // bins per pool slot on this rank
   size_t hist_elem_ = 8;
   DevBuf<HistPartition> parts_; std::vector<HistPartition> h_parts_; int max_part_bins_ = 0;

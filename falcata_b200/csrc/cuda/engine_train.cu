@@ -115,8 +115,11 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   ha.max_part_bins = max_part_bins_; ha.group_bin_start = dd_->group_bin_start.get(); ha.sub_rows = sub_rows_;
   ha.dest.bin_owner = bin_owner_.get(); ha.dest.bin_local = bin_local_.get(); ha.dest.num_ranks = world_; ha.dest.rank = rank_;
   for (int r = 0; r < kMaxRanks; ++r) { ha.dest.pool[r] = nullptr; ha.dest.slot_stride[r] = 0; }
-  if (world_ > 1) { for (int r = 0; r < world_; ++r) { ha.dest.pool[r] = fabric_->Ptr<char>(r, off_pool_); ha.dest.slot_stride[r] = slot_strides_[r]; } }
-  else { ha.dest.pool[0] = pool_base_; ha.dest.slot_stride[0] = slot_stride_; }
+  for (int r = 0; r < kMaxRanks; ++r) ha.dest.peer_stage[r] = nullptr;
+  if (world_ > 1) {
+    for (int r = 0; r < world_; ++r) { ha.dest.pool[r] = fabric_->Ptr<char>(r, off_pool_); ha.dest.slot_stride[r] = slot_strides_[r]; ha.dest.peer_stage[r] = fabric_->Ptr<char>(r, off_stage_); }
+    ha.dest.stage_local = stage_local_.get(); ha.dest.task_done = task_done_.get(); ha.dest.stage_cap = NL;
+  } else { ha.dest.pool[0] = pool_base_; ha.dest.slot_stride[0] = slot_stride_; }
   ha.num_total_bin = train_->num_total_bin; ha.lane_mode = lane_mode_; ha.lane_bins = lane_bins_;
   ha.sig.world = world_;
   FindArgs fa = FindArgs();
@@ -135,6 +138,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     fa.wait.flags = fabric_->Local<unsigned int>(flag_hist_); fa.wait.max_spins = v.max_spins; fa.wait.status = v.status;
     fa.wait_best.flags = fabric_->Local<unsigned int>(flag_best_); fa.wait_best.max_spins = v.max_spins; fa.wait_best.status = v.status;
     fa.counts = fabric_->Local<int>(off_counts_); fa.counts_stride = NL;
+    fa.stage = fabric_->Local<char>(off_stage_); fa.stage_cap = NL;
     fa.gathered = fabric_->Local<SplitRecord>(off_best_); fa.gathered_stride = NL;
   }
   auto construct_and_find = [&]() {
@@ -154,8 +158,8 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   // ---- root ----
   {
     HistTask t; t.slot = 0; t.begin = 0; t.count = n_; t.buffer = 0; t.block_begin = 0; t.pad0 = t.pad1 = 0;
-    ha.rows_per_block = ChooseRowsPerBlock(n_); t.num_blocks = (n_ + ha.rows_per_block - 1) / ha.rows_per_block;
-    FindChild fc; fc.leaf = 0; fc.slot = 0; fc.other_slot = 0; fc.is_larger = 0; fc.split = -1; fc.is_left = 1; fc.parent_global = 0; fc.pad = 0;
+    ha.rows_per_block = ChooseRowsPerBlock(n_); t.num_blocks = std::max(1, (n_ + ha.rows_per_block - 1) / ha.rows_per_block);
+    FindChild fc; fc.leaf = 0; fc.slot = 0; fc.other_slot = 0; fc.is_larger = 0; fc.split = -1; fc.is_left = 1; fc.parent_global = 0; fc.task = 0;
     memcpy(hb, &t, sizeof(t)); memcpy(hb + sizeof(t), &fc, sizeof(fc));
     FB_CUDA(cudaMemcpyAsync(db, hb, sizeof(t) + sizeof(fc), cudaMemcpyHostToDevice, stream_));
     FB_CUDA(cudaMemcpyAsync(hist_tasks_.get(), db, sizeof(t), cudaMemcpyDeviceToDevice, stream_));
@@ -217,10 +221,10 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
       c.left_g = b.left_g; c.left_h = b.left_h; c.right_g = b.right_g; c.right_h = b.right_h; c.left_out = b.left_out; c.right_out = b.right_out;
       c.left_gi = b.left_gi; c.left_hi = b.left_hi;
       c.right_gi = PL.sum_gi - b.left_gi; c.right_hi = PL.sum_hi - b.left_hi;
-      c.hist_block_begin = block_cursor; c.hist_num_blocks = (P.count + ha.rows_per_block - 1) / ha.rows_per_block; block_cursor += c.hist_num_blocks;
+      c.hist_block_begin = block_cursor; c.hist_num_blocks = std::max(1, (P.count + ha.rows_per_block - 1) / ha.rows_per_block); block_cursor += c.hist_num_blocks;
       FindChild& fl = fc[2 * s]; FindChild& fr = fc[2 * s + 1];
-      fl.leaf = l; fl.slot = c.left_slot; fl.other_slot = c.right_slot; fl.is_larger = c.smaller_is_left ? 0 : 1; fl.split = s; fl.is_left = 1; fl.parent_global = PL.num_data_global; fl.pad = 0;
-      fr.leaf = right; fr.slot = c.right_slot; fr.other_slot = c.left_slot; fr.is_larger = c.smaller_is_left ? 1 : 0; fr.split = s; fr.is_left = 0; fr.parent_global = PL.num_data_global; fr.pad = 0;
+      fl.leaf = l; fl.slot = c.left_slot; fl.other_slot = c.right_slot; fl.is_larger = c.smaller_is_left ? 0 : 1; fl.split = s; fl.is_left = 1; fl.parent_global = PL.num_data_global; fl.task = s;
+      fr.leaf = right; fr.slot = c.right_slot; fr.other_slot = c.left_slot; fr.is_larger = c.smaller_is_left ? 1 : 0; fr.split = s; fr.is_left = 0; fr.parent_global = PL.num_data_global; fr.task = s;
       host_leaves_[right].slot = c.right_slot; P.slot = c.left_slot;
       next.push_back(l); next.push_back(right);
     }

@@ -28,12 +28,55 @@ __device__ inline int FindTask(const HistTask* tasks, int num_tasks, int block) 
   return lo;
 }
 
-__device__ inline void FlushBinQuant(const HistDest& d, int slot, int global_bin, long long g, long long h) {
-  const int owner = d.bin_owner[global_bin];
-  hist_q_t* p = static_cast<hist_q_t*>(d.pool[owner]) + static_cast<long long>(slot) * d.slot_stride[owner] + d.bin_local[global_bin];
+// One rank: the bin goes straight into the pool slot. Several ranks: into the LOCAL staging
+// histogram of the task (L2 atomics); PushTaskIfLast ships the finished task to the owners.
+__device__ inline void FlushBinQuant(const HistDest& d, int slot, int task_index, int num_total_bin, int global_bin, long long g, long long h) {
   const hist_q_t v = HistQPack(g, h);
-  if (owner == d.rank) atomicAdd(p, v);
-  else atomicAdd_system(p, v);     // red.add.u64 on the peer's memory: the reduce-scatter, bin by bin
+  if (d.num_ranks > 1) {
+    atomicAdd(static_cast<hist_q_t*>(d.stage_local) + static_cast<long long>(task_index) * num_total_bin + global_bin, v);
+  } else {
+    atomicAdd(static_cast<hist_q_t*>(d.pool[0]) + static_cast<long long>(slot) * d.slot_stride[0] + d.bin_local[global_bin], v);
+  }
+}
+
+// Reduce-scatter step, fused into the construct kernel. Called by every block that worked on task
+// `ti` after its flush. The last of them finds the task's histogram complete in the local staging
+// area and stores each feature slice into the staging slot [this rank][ti] of the rank that owns the
+// feature: plain 8/16-byte stores to peer memory, contiguous per feature group, over NVLink, while
+// other blocks are still constructing other leaves. Zeros are stored too, so the destination never
+// needs clearing, and the local staging cells are reset for the next level.
+template <bool QUANT>
+__device__ inline void PushTaskIfLast(const HistArgs& a, int ti, const HistTask& task) {
+  const HistDest& d = a.dest;
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int row_blocks = max(1, (task.count + a.rows_per_block - 1) / a.rows_per_block);
+    const unsigned int need = static_cast<unsigned int>(min(row_blocks, task.num_blocks)) * gridDim.y;
+    const unsigned int prev = atomicAdd(d.task_done + ti, 1u);
+    s_last = (prev + 1 == need) ? 1 : 0;
+    if (s_last) d.task_done[ti] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int nb = a.num_total_bin;
+  for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+    const int owner = d.bin_owner[b];
+    const long long dst_index = (static_cast<long long>(d.rank) * d.stage_cap + ti) * d.slot_stride[owner] + d.bin_local[b];
+    if (QUANT) {
+      hist_q_t* src = static_cast<hist_q_t*>(d.stage_local) + static_cast<long long>(ti) * nb + b;
+      const hist_q_t v = __ldcg(src);
+      *src = 0;
+      static_cast<hist_q_t*>(d.peer_stage[owner])[dst_index] = v;
+    } else {
+      double2* src = static_cast<double2*>(d.stage_local) + static_cast<long long>(ti) * nb + b;
+      const double2 v = __ldcg(src);
+      *src = make_double2(0.0, 0.0);
+      static_cast<double2*>(d.peer_stage[owner])[dst_index] = v;
+    }
+  }
 }
 
 template <bool TWO_PHASE>
@@ -47,8 +90,10 @@ __global__ void __launch_bounds__(kHistThreads) HistQuantKernel(HistArgs a) {
   const HistTask task = a.tasks[ti];
   const int chunk = blockIdx.x - task.block_begin;
   const long long row0 = static_cast<long long>(chunk) * a.rows_per_block;
-  if (chunk >= task.num_blocks || row0 >= task.count) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
-  const int nrows = static_cast<int>(min(static_cast<long long>(a.rows_per_block), task.count - row0));
+  // a task always keeps its first block (even with no local rows): it closes the task's reduce-scatter
+  const int row_blocks = max(1, (task.count + a.rows_per_block - 1) / a.rows_per_block);
+  if (chunk >= task.num_blocks || chunk >= row_blocks) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
+  const int nrows = static_cast<int>(max(0LL, min(static_cast<long long>(a.rows_per_block), task.count - row0)));
   const int ngroups = part.group_end - part.group_begin;
   const int G4 = (ngroups + 3) >> 2;
   for (int b = threadIdx.x; b < part.bin_count * (TWO_PHASE ? 3 : 1); b += kHistThreads) s_packed[b] = 0;
@@ -86,112 +131,107 @@ __global__ void __launch_bounds__(kHistThreads) HistQuantKernel(HistArgs a) {
     long long g, h;
     if (TWO_PHASE) { g = s_wide[2 * b]; h = s_wide[2 * b + 1]; }
     else { const int v = s_packed[b]; h = v & 0xFFFF; g = (v - static_cast<int>(h)) >> 16; }
-    if (g != 0 || h != 0) FlushBinQuant(a.dest, task.slot, part.bin_begin + b, g, h);
+    if (g != 0 || h != 0) FlushBinQuant(a.dest, task.slot, ti, a.num_total_bin, part.bin_begin + b, g, h);
   }
+  if (a.dest.num_ranks > 1) PushTaskIfLast<true>(a, ti, task);
   if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y);
 }
 
-// Lane-per-group instance, fed by an asynchronous gather pipeline.
+// Lane-per-group instance with warp-autonomous asynchronous pipelines.
 //
-// Two measurements on B200 shaped this kernel. (1) With plain loads a block keeps only a few KB of
-// row data in flight; the construct then waits on DRAM latency, far from HBM bandwidth. Here every
-// thread copies one row's 32 bytes (and its gradient word) global->shared with cp.async, several
-// stages ahead, so each SM has tens of KB in flight without holding registers. (2) Shared-memory
-// atomics into a [group][bin] tile suffer bank conflicts between the lanes' random bins. Here lane l
-// of a warp owns feature group (32*blockIdx.y + l) and the tile is laid out [bin][32 lanes]: the 32
-// lanes of an instruction always touch 32 different banks. With PRIVATE tiles (one per warp) the
-// update is a plain load-add-store, no atomics at all, because no other thread touches a lane's column.
-constexpr int kLaneWarps = kHistThreads / 32;
-constexpr int kPipeStages = 4;
-template <int NB, bool PRIVATE>
-__global__ void __launch_bounds__(kHistThreads) HistQuantLaneKernel(HistArgs a) {
+// Measurements on B200 that shaped this kernel:
+//  (1) with plain loads a block keeps only a few KB of row data in flight and the construct waits on
+//      DRAM latency; with block-wide stages the warps wait for each other at barriers instead.
+//      Here every WARP runs its own pipeline: per stage, lane l copies row l of the warp's next 32
+//      rows (32 bytes of bins + the packed gradient word) global->shared with cp.async, kLaneStages
+//      stages ahead, and waits only for its own copies. No block barrier until the final merge.
+//  (2) shared-memory atomics into a [group][bin] tile lose most of their rate to bank conflicts
+//      between the lanes' random bins. Here lane l owns feature group (32*blockIdx.y + l) and each
+//      warp has a private tile laid out [bin][32 lanes]: an instruction's 32 lanes always hit 32
+//      different banks and the update is a plain load-add-store (nobody else touches a lane's column).
+//  (3) the load-add-store chain is taken four rows at a time: four tile loads issue together and equal
+//      addresses are forwarded in registers.
+constexpr int kLaneWarps = 12;
+constexpr int kLaneThreads = kLaneWarps * 32;
+constexpr int kLaneStages = 8;
+template <int NB>
+__global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int kTile = NB * 32;
-  constexpr int kTiles = PRIVATE ? kLaneWarps : 1;
-  int* tiles = reinterpret_cast<int*>(smem_raw);
-  unsigned char* stage_rows = smem_raw + sizeof(int) * kTiles * kTile;                    // [stages][256 rows][32 B]
-  int* stage_gh = reinterpret_cast<int*>(stage_rows + kPipeStages * kHistThreads * 32);   // [stages][256]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* tiles = reinterpret_cast<int*>(smem_raw);                                                 // [warps][NB][32]
+  unsigned char* rows_w = smem_raw + sizeof(int) * kLaneWarps * kTile + static_cast<size_t>(warp) * kLaneStages * 32 * 32;   // [stages][32 rows][32 B]
+  int* gh_w = reinterpret_cast<int*>(smem_raw + sizeof(int) * kLaneWarps * kTile + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * 32) + warp * kLaneStages * 32;
   const int ti = FindTask(a.tasks, a.num_tasks, blockIdx.x);
   const HistTask task = a.tasks[ti];
   const int chunk = blockIdx.x - task.block_begin;
   const long long row0 = static_cast<long long>(chunk) * a.rows_per_block;
-  if (chunk >= task.num_blocks || row0 >= task.count) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
-  const int nrows = static_cast<int>(min(static_cast<long long>(a.rows_per_block), task.count - row0));
+  // a task always keeps its first block (even with no local rows): it closes the task's reduce-scatter
+  const int row_blocks = max(1, (task.count + a.rows_per_block - 1) / a.rows_per_block);
+  if (chunk >= task.num_blocks || chunk >= row_blocks) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
+  const int nrows = static_cast<int>(max(0LL, min(static_cast<long long>(a.rows_per_block), task.count - row0)));
   const int g0 = blockIdx.y * 32;
   const int ng = min(32, a.num_groups - g0);
   const int copy16 = min(2, (a.row_stride - g0) / 16);          // 16-byte pieces of this part inside the row
-  for (int i = threadIdx.x; i < kTiles * kTile; i += kHistThreads) tiles[i] = 0;
-  int* tile = tiles + (PRIVATE ? warp * kTile : 0);
-  const int* idx = a.idx[task.buffer] + task.begin + row0;
-  const int nstage = (nrows + kHistThreads - 1) / kHistThreads;
-  auto row_of = [&](int r) -> int { return a.identity_root ? static_cast<int>(task.begin + row0 + r) : idx[r]; };
+  int* tile = tiles + warp * kTile;
+  for (int i = lane; i < kTile; i += 32) tile[i] = 0;
+  __syncwarp();
+  // this warp's slice of the block's rows, in stages of 32 rows
+  const int per_warp = ((nrows + kLaneWarps - 1) / kLaneWarps + 31) / 32 * 32;
+  const int wbeg = min(nrows, warp * per_warp), wend = min(nrows, wbeg + per_warp);
+  const int nstage = (wend - wbeg + 31) / 32;
+  const int* idx = a.idx[task.buffer] + task.begin + row0 + wbeg;
+  const long long ident0 = task.begin + row0 + wbeg;
+  auto load_row = [&](int s) -> int {   // row id that this lane copies in stage s (-1: none)
+    const int r = s * 32 + lane;
+    if (s >= nstage || wbeg + r >= wend) return -1;
+    return a.identity_root ? static_cast<int>(ident0 + r) : idx[r];
+  };
   auto issue = [&](int s, int row) {
-    if (s < nstage && s * kHistThreads + static_cast<int>(threadIdx.x) < nrows) {
-      const int slot = s % kPipeStages;
+    if (row >= 0) {
+      const int slot = s % kLaneStages;
       const unsigned char* src = a.rows + static_cast<size_t>(row) * a.row_stride + g0;
-      unsigned char* dst = stage_rows + (static_cast<size_t>(slot) * kHistThreads + threadIdx.x) * 32;
+      unsigned char* dst = rows_w + (slot * 32 + lane) * 32;
       __pipeline_memcpy_async(dst, src, 16);
       if (copy16 > 1) __pipeline_memcpy_async(dst + 16, src + 16, 16);
-      __pipeline_memcpy_async(stage_gh + slot * kHistThreads + threadIdx.x, a.gh_base + static_cast<size_t>(row) * a.gh_stride, 4);
+      __pipeline_memcpy_async(gh_w + slot * 32 + lane, a.gh_base + static_cast<size_t>(row) * a.gh_stride, 4);
     }
     __pipeline_commit();
   };
-  // prologue: stages 0 .. S-2 in flight, and the row index of the next stage already loaded
-  int next_row = 0;
-  for (int s = 0; s < kPipeStages - 1; ++s) {
-    const int r = s * kHistThreads + threadIdx.x;
-    issue(s, (s < nstage && r < nrows) ? row_of(r) : 0);
-  }
-  { const int r = (kPipeStages - 1) * kHistThreads + threadIdx.x; next_row = (kPipeStages - 1 < nstage && r < nrows) ? row_of(r) : 0; }
-  __syncthreads();
+  for (int s = 0; s < kLaneStages - 1; ++s) issue(s, load_row(s));
+  // row ids are fetched three stages before they are needed, so their latency is off the critical path
+  int q0 = load_row(kLaneStages - 1), q1 = load_row(kLaneStages), q2 = load_row(kLaneStages + 1);
   const bool active = lane < ng;
   for (int s = 0; s < nstage; ++s) {
-    issue(s + kPipeStages - 1, next_row);
-    { const int r = (s + kPipeStages) * kHistThreads + threadIdx.x; next_row = (s + kPipeStages < nstage && r < nrows) ? row_of(r) : 0; }
-    __pipeline_wait_prior(kPipeStages - 1);
-    __syncthreads();
-    const int slot = s % kPipeStages;
-    const int base = s * kHistThreads + warp * 32;
-    const int cnt = min(32, nrows - base);
-    if (cnt > 0) {
-      const unsigned char* sr = stage_rows + (static_cast<size_t>(slot) * kHistThreads + warp * 32) * 32 + lane;
-      const int ghv = stage_gh[slot * kHistThreads + warp * 32 + lane];
-      if (cnt == 32 && PRIVATE) {
-        // four rows per step: the four tile loads are issued together and equal addresses are
-        // forwarded in registers, so the dependent shared-memory chain is paid once per four rows
+    issue(s + kLaneStages - 1, q0);
+    q0 = q1; q1 = q2; q2 = load_row(s + kLaneStages + 2);
+    __pipeline_wait_prior(kLaneStages - 1);
+    __syncwarp();
+    const int slot = s % kLaneStages;
+    const int cnt = min(32, wend - wbeg - s * 32);
+    const unsigned char* sr = rows_w + slot * 32 * 32 + lane;
+    const int* sg = gh_w + slot * 32;
+    if (cnt == 32) {
 #pragma unroll 2
-        for (int j = 0; j < 32; j += 4) {
-          const int a0 = sr[j * 32] * 32 + lane, a1 = sr[(j + 1) * 32] * 32 + lane, a2 = sr[(j + 2) * 32] * 32 + lane, a3 = sr[(j + 3) * 32] * 32 + lane;
-          const int g0v = __shfl_sync(0xffffffffu, ghv, j), g1v = __shfl_sync(0xffffffffu, ghv, j + 1);
-          const int g2v = __shfl_sync(0xffffffffu, ghv, j + 2), g3v = __shfl_sync(0xffffffffu, ghv, j + 3);
-          if (active) {
-            int v0 = tile[a0], v1 = tile[a1], v2 = tile[a2], v3 = tile[a3];
-            v0 += g0v;
-            v1 = (a1 == a0) ? v0 : v1; v1 += g1v;
-            v2 = (a2 == a1) ? v1 : ((a2 == a0) ? v0 : v2); v2 += g2v;
-            v3 = (a3 == a2) ? v2 : ((a3 == a1) ? v1 : ((a3 == a0) ? v0 : v3)); v3 += g3v;
-            tile[a0] = v0; tile[a1] = v1; tile[a2] = v2; tile[a3] = v3;   // program order: the last store to an address holds its full sum
-          }
-        }
-      } else if (cnt == 32) {
-#pragma unroll 8
-        for (int j = 0; j < 32; ++j) {
-          const int b = sr[j * 32];
-          const int g = __shfl_sync(0xffffffffu, ghv, j);
-          if (active) atomicAdd(&tile[b * 32 + lane], g);
-        }
-      } else {
-        for (int j = 0; j < cnt; ++j) {
-          const int b = sr[j * 32];
-          const int g = __shfl_sync(0xffffffffu, ghv, j);
-          if (active) { if (PRIVATE) tile[b * 32 + lane] += g; else atomicAdd(&tile[b * 32 + lane], g); }
+      for (int j = 0; j < 32; j += 4) {
+        const int a0 = sr[j * 32] * 32 + lane, a1 = sr[(j + 1) * 32] * 32 + lane, a2 = sr[(j + 2) * 32] * 32 + lane, a3 = sr[(j + 3) * 32] * 32 + lane;
+        const int4 g4 = *reinterpret_cast<const int4*>(sg + j);     // same address in every lane: one broadcast load
+        if (active) {
+          int v0 = tile[a0], v1 = tile[a1], v2 = tile[a2], v3 = tile[a3];
+          v0 += g4.x;
+          v1 = (a1 == a0) ? v0 : v1; v1 += g4.y;
+          v2 = (a2 == a1) ? v1 : ((a2 == a0) ? v0 : v2); v2 += g4.z;
+          v3 = (a3 == a2) ? v2 : ((a3 == a1) ? v1 : ((a3 == a0) ? v0 : v3)); v3 += g4.w;
+          tile[a0] = v0; tile[a1] = v1; tile[a2] = v2; tile[a3] = v3;   // program order: the last store to an address holds its full sum
         }
       }
+    } else {
+      for (int j = 0; j < cnt; ++j) { const int b = sr[j * 32]; const int g = sg[j]; if (active) tile[b * 32 + lane] += g; }
     }
-    __syncthreads();
+    __syncwarp();   // every lane is done with this stage's buffer before it is refilled
   }
-  for (int cell = threadIdx.x; cell < kTile; cell += kHistThreads) {
+  __syncthreads();
+  for (int cell = threadIdx.x; cell < kTile; cell += kLaneThreads) {
     const int l = cell & 31, b = cell >> 5;
     if (l >= ng) continue;
     const int g = g0 + l;
@@ -199,12 +239,12 @@ __global__ void __launch_bounds__(kHistThreads) HistQuantLaneKernel(HistArgs a) 
     const int gbins = (g + 1 < a.num_groups ? a.group_bin_start[g + 1] : a.num_total_bin) - gstart;
     if (b >= gbins) continue;
     long long sg = 0, sh = 0;
-    for (int w = 0; w < kTiles; ++w) { const int v = tiles[w * kTile + cell]; const int h = v & 0xFFFF; sg += (v - h) >> 16; sh += h; }
-    if (sg != 0 || sh != 0) FlushBinQuant(a.dest, task.slot, gstart + b, sg, sh);
+    for (int w = 0; w < kLaneWarps; ++w) { const int v = tiles[w * kTile + cell]; const int h = v & 0xFFFF; sg += (v - h) >> 16; sh += h; }
+    if (sg != 0 || sh != 0) FlushBinQuant(a.dest, task.slot, ti, a.num_total_bin, gstart + b, sg, sh);
   }
+  if (a.dest.num_ranks > 1) PushTaskIfLast<true>(a, ti, task);
   if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y);
 }
-
 
 __global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
   extern __shared__ float smem_f[];
@@ -215,8 +255,10 @@ __global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
   const HistTask task = a.tasks[ti];
   const int chunk = blockIdx.x - task.block_begin;
   const long long row0 = static_cast<long long>(chunk) * a.rows_per_block;
-  if (chunk >= task.num_blocks || row0 >= task.count) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
-  const int nrows = static_cast<int>(min(static_cast<long long>(a.rows_per_block), task.count - row0));
+  // a task always keeps its first block (even with no local rows): it closes the task's reduce-scatter
+  const int row_blocks = max(1, (task.count + a.rows_per_block - 1) / a.rows_per_block);
+  if (chunk >= task.num_blocks || chunk >= row_blocks) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
+  const int nrows = static_cast<int>(max(0LL, min(static_cast<long long>(a.rows_per_block), task.count - row0)));
   const int ngroups = part.group_end - part.group_begin;
   const int G4 = (ngroups + 3) >> 2;
   for (int b = threadIdx.x; b < 2 * part.bin_count; b += kHistThreads) s_hist[b] = 0.f;
@@ -246,11 +288,12 @@ __global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
   for (int b = threadIdx.x; b < part.bin_count; b += kHistThreads) {
     const float g = s_hist[2 * b], h = s_hist[2 * b + 1];
     if (g == 0.f && h == 0.f) continue;
-    const int gb = part.bin_begin + b, owner = d.bin_owner[gb];
-    double* p = static_cast<double*>(d.pool[owner]) + 2 * (static_cast<long long>(task.slot) * d.slot_stride[owner] + d.bin_local[gb]);
-    if (owner == d.rank) { atomicAdd(p, static_cast<double>(g)); atomicAdd(p + 1, static_cast<double>(h)); }
-    else { atomicAdd_system(p, static_cast<double>(g)); atomicAdd_system(p + 1, static_cast<double>(h)); }
+    const int gb = part.bin_begin + b;
+    double* p = d.num_ranks > 1 ? static_cast<double*>(d.stage_local) + 2 * (static_cast<long long>(ti) * a.num_total_bin + gb)
+                                : static_cast<double*>(d.pool[0]) + 2 * (static_cast<long long>(task.slot) * d.slot_stride[0] + d.bin_local[gb]);
+    atomicAdd(p, static_cast<double>(g)); atomicAdd(p + 1, static_cast<double>(h));
   }
+  if (d.num_ranks > 1) PushTaskIfLast<false>(a, ti, task);
   if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y);
 }
 
@@ -259,19 +302,18 @@ __global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
   if (a.total_blocks <= 0 || a.num_tasks <= 0) return;
   if (a.lane_mode != 0) {
-    const bool priv = a.lane_mode == 1;
-    const int cap = priv ? kLaneWarps * a.sub_rows : a.sub_rows;
+    const int cap = kLaneWarps * a.sub_rows;
     if (a.rows_per_block > cap) Log::Fatal("lane histogram: %d rows per block would overflow the 16-bit lanes (cap %d)", a.rows_per_block, cap);
     dim3 grid(a.total_blocks, (a.num_groups + 31) / 32);
-    const size_t sm = static_cast<size_t>(a.lane_bins) * 32 * 4 * (priv ? kLaneWarps : 1) + static_cast<size_t>(kPipeStages) * kHistThreads * (32 + 4);
-#define FB_LANE(NB, P)                                                                                                             \
+    const size_t sm = static_cast<size_t>(a.lane_bins) * 32 * 4 * kLaneWarps + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * (32 + 4);
+#define FB_LANE(NB)                                                                                                                \
     {                                                                                                                              \
       static bool attr = false;                                                                                                    \
-      if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantLaneKernel<NB, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr = true; } \
-      HistQuantLaneKernel<NB, P><<<grid, kHistThreads, sm, s>>>(a);                                                                \
+      if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantLaneKernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr = true; } \
+      HistQuantLaneKernel<NB><<<grid, kLaneThreads, sm, s>>>(a);                                                                   \
     }
-    if (a.lane_bins == 16) { if (priv) FB_LANE(16, true) else FB_LANE(16, false) }
-    else if (a.lane_bins == 64) { if (priv) FB_LANE(64, true) else FB_LANE(64, false) }
+    if (a.lane_bins == 16) FB_LANE(16)
+    else if (a.lane_bins == 64) FB_LANE(64)
     else Log::Fatal("lane histogram: unsupported tile of %d bins", a.lane_bins);
 #undef FB_LANE
     FB_LAUNCHED(); FB_KERNEL_CHECK();

@@ -31,6 +31,13 @@ struct HistDest {
   const unsigned char* bin_owner;  // [num_total_bin]
   const int* bin_local;            // [num_total_bin]
   int num_ranks, rank;
+  // num_ranks > 1: blocks add into a LOCAL staging histogram of their task; the last block of a
+  // task to finish stores the finished slices into the owner ranks' per-source staging slots
+  // (plain coalesced stores over NVLink) while other tasks' tiles are still being constructed.
+  void* stage_local;               // [stage_cap][num_total_bin] bins, zero between uses
+  unsigned int* task_done;         // [stage_cap] blocks finished per task
+  void* peer_stage[8];             // base of every rank's staging area: [source rank][stage_cap][slot_stride(owner)]
+  int stage_cap;
 };
 
 struct HistArgs {
@@ -54,7 +61,7 @@ void LaunchHistConstructFloat(const HistArgs& a, cudaStream_t s);
 bool LaunchHistConstructQuantTC(const HistArgs& a, cudaStream_t s);
 
 // ------------------------------------------------------------ split find ----
-struct FindChild { int leaf; int slot; int other_slot; int is_larger; int split; int is_left; int parent_global; int pad; };   // larger: bins = pool[slot] - pool[other_slot], written back to pool[slot]
+struct FindChild { int leaf; int slot; int other_slot; int is_larger; int split; int is_left; int parent_global; int task; };   // task: construct task of this pair's smaller child   // larger: bins = pool[slot] - pool[other_slot], written back to pool[slot]
 
 struct CandLite {      // best threshold of one (child, feature)
   double gain; int feature; int threshold; int default_left; int left_cnt;
@@ -76,6 +83,7 @@ struct FindArgs {
   int quant;
   // ---- multi-rank (world > 1) ----
   FabricWait wait;                                // construct-done flags of all ranks (the reduce-scatter is complete when they are up)
+  const void* stage; int stage_cap;               // this rank's staging area [source rank][stage_cap][slot_stride] written by the ranks' constructs
   const int* counts; int counts_stride;           // [rank][split] local left counts published by every rank's partition
   LeafInfo* leaves_rw;                            // exact global row counts are written back here
   SplitRecord* peer_best[kMaxRanks];              // address of best_slots[this rank][0] inside every rank's heap

@@ -18,16 +18,40 @@ struct Acc {   // prefix accumulator of one lane
   long long gi, hi; double gd, hd; int c;
 };
 
+// Where the bins of one (child, feature) come from.
+//  one rank  : child slot (smaller child: constructed there; larger child: still the parent) and,
+//              for the larger child, the sibling's slot to subtract.
+//  many ranks: the smaller child's bins are the sum over source ranks of this rank's staging slots
+//              (fixed rank order, so the full-precision path is deterministic); the larger child is
+//              parent minus that sum. Either way the result is written back to the child's slot.
+struct BinSrc {
+  const void* child; const void* other; bool larger;
+  const void* stage; int world; long long rank_stride;   // stage: source rank 0's slot for this (task, feature)
+};
+
 template <bool QUANT>
-__device__ inline void LoadBin(const void* child, const void* other, bool larger, int j, long long* gi, long long* hi, double* gd, double* hd,
-                               hist_q_t* raw_q, double2* raw_d) {
+__device__ inline void LoadBin(const BinSrc& s, int j, long long* gi, long long* hi, double* gd, double* hd, hist_q_t* raw_q, double2* raw_d) {
   if (QUANT) {
-    hist_q_t v = static_cast<const hist_q_t*>(child)[j];
-    if (larger) v -= static_cast<const hist_q_t*>(other)[j];
+    hist_q_t v;
+    if (s.world > 1) {
+      hist_q_t sum = 0;
+      for (int r = 0; r < s.world; ++r) sum += __ldcg(static_cast<const hist_q_t*>(s.stage) + r * s.rank_stride + j);
+      v = s.larger ? static_cast<const hist_q_t*>(s.child)[j] - sum : sum;
+    } else {
+      v = static_cast<const hist_q_t*>(s.child)[j];
+      if (s.larger) v -= static_cast<const hist_q_t*>(s.other)[j];
+    }
     *raw_q = v; *gi = HistQGrad(v); *hi = HistQHess(v);
   } else {
-    double2 v = static_cast<const double2*>(child)[j];
-    if (larger) { const double2 o = static_cast<const double2*>(other)[j]; v.x -= o.x; v.y -= o.y; }
+    double2 v;
+    if (s.world > 1) {
+      double2 sum = make_double2(0.0, 0.0);
+      for (int r = 0; r < s.world; ++r) { const double2 t = __ldcg(static_cast<const double2*>(s.stage) + r * s.rank_stride + j); sum.x += t.x; sum.y += t.y; }
+      if (s.larger) { v = static_cast<const double2*>(s.child)[j]; v.x -= sum.x; v.y -= sum.y; } else v = sum;
+    } else {
+      v = static_cast<const double2*>(s.child)[j];
+      if (s.larger) { const double2 o = static_cast<const double2*>(s.other)[j]; v.x -= o.x; v.y -= o.y; }
+    }
     *raw_d = v; *gd = v.x; *hd = v.y;
   }
 }
@@ -50,7 +74,7 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
   const bool search = fi < a.num_features;
   const int f = search ? a.features[fi] : a.sub_features[fi - a.num_features];
   const FindChild ch = a.children[blockIdx.x];
-  if (!search && !ch.is_larger) return;
+  if (!search && !ch.is_larger && a.wait.world <= 1) return;
   const FeatureMeta m = a.meta[f];
   LeafInfo leaf = a.leaves[ch.leaf];
   leaf.num_data_global = ChildGlobalCount(a, ch, leaf.num_data_global);
@@ -61,12 +85,17 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
   char* child = static_cast<char*>(a.pool) + (static_cast<long long>(ch.slot) * a.slot_stride + base) * esz;
   const char* other = static_cast<const char*>(a.pool) + (static_cast<long long>(ch.other_slot) * a.slot_stride + base) * esz;
   const bool larger = ch.is_larger != 0;
+  const int world = a.wait.world;
+  const bool write_back = larger || world > 1;
+  BinSrc src; src.child = child; src.other = other; src.larger = larger; src.world = world;
+  src.rank_stride = static_cast<long long>(a.stage_cap) * a.slot_stride;
+  src.stage = world > 1 ? static_cast<const char*>(a.stage) + (static_cast<long long>(ch.task) * a.slot_stride + base) * esz : nullptr;
 
   if (!search || m.bin_type != 0) {
-    // subtraction only (feature not sampled for this tree, or categorical: searched on the host path)
-    if (larger) for (int j = lane; j < nstored; j += 32) {
+    // materialisation only (feature not sampled for this tree, or categorical: searched on the host path)
+    if (write_back) for (int j = lane; j < nstored; j += 32) {
       long long gi, hi; double gd, hd; hist_q_t rq; double2 rd;
-      LoadBin<QUANT>(child, other, true, j, &gi, &hi, &gd, &hd, &rq, &rd);
+      LoadBin<QUANT>(src, j, &gi, &hi, &gd, &hd, &rq, &rd);
       if (QUANT) reinterpret_cast<hist_q_t*>(child)[j] = rq; else reinterpret_cast<double2*>(child)[j] = rd;
     }
     if (search && lane == 0) { CandLite c; c.gain = -1.0 / 0.0; c.feature = -1; c.threshold = 0; c.default_left = 1; c.left_cnt = 0; c.left_gi = c.left_hi = 0; c.left_g = c.left_h = 0; a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + fi] = c; }
@@ -92,7 +121,7 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
     long long sgi = 0, shi = 0; double sgd = 0, shd = 0;
     for (int j = lane; j < nstored; j += 32) {
       long long gi = 0, hi = 0; double gd = 0, hd = 0; hist_q_t rq; double2 rd;
-      LoadBin<QUANT>(child, other, larger, j, &gi, &hi, &gd, &hd, &rq, &rd);
+      LoadBin<QUANT>(src, j, &gi, &hi, &gd, &hd, &rq, &rd);
       sgi += gi; shi += hi; sgd += gd; shd += hd;
     }
     for (int o = 16; o > 0; o >>= 1) {
@@ -105,7 +134,7 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
   long long Mgi = 0, Mhi = 0; double Mgd = 0, Mhd = 0; int Mc = 0;
   if (skip >= 0) {
     if (skip == mfb) { Mgi = mfb_gi; Mhi = mfb_hi; Mgd = mfb_gd; Mhd = mfb_hd; }
-    else { hist_q_t rq; double2 rd; LoadBin<QUANT>(child, other, larger, (mfb >= 0 && skip > mfb) ? skip - 1 : skip, &Mgi, &Mhi, &Mgd, &Mhd, &rq, &rd); }
+    else { hist_q_t rq; double2 rd; LoadBin<QUANT>(src, (mfb >= 0 && skip > mfb) ? skip - 1 : skip, &Mgi, &Mhi, &Mgd, &Mhd, &rq, &rd); }
     const double hreal = QUANT ? FB_MUL(static_cast<double>(Mhi), L.h_scale) : Mhd;
     Mc = BinCountEstimate(hreal, L.cnt_factor);
   }
@@ -121,8 +150,8 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
       else {
         const int j = (mfb >= 0 && b > mfb) ? b - 1 : b;
         hist_q_t rq; double2 rd;
-        LoadBin<QUANT>(child, other, larger, j, &gi, &hi, &gd, &hd, &rq, &rd);
-        if (larger) { if (QUANT) reinterpret_cast<hist_q_t*>(child)[j] = rq; else reinterpret_cast<double2*>(child)[j] = rd; }
+        LoadBin<QUANT>(src, j, &gi, &hi, &gd, &hd, &rq, &rd);
+        if (write_back) { if (QUANT) reinterpret_cast<hist_q_t*>(child)[j] = rq; else reinterpret_cast<double2*>(child)[j] = rd; }
       }
       if (b == skip) { gi = hi = 0; gd = hd = 0; }
       else { const double hreal = QUANT ? FB_MUL(static_cast<double>(hi), L.h_scale) : hd; c = BinCountEstimate(hreal, L.cnt_factor); }

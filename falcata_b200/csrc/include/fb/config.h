@@ -198,7 +198,7 @@ struct Plan {
   bool fused_ag = true;          // split find epilogue stores the rank's best split into every peer
   bool pack4 = true;             // 4-bit row storage when every group has <= 16 bins
   bool compact_view = true;      // per-tree gather of feature_fraction-sampled columns
-  bool gh_in_row = true;         // packed gradient word stored next to the row's bins
+  bool gh_in_row = false;        // packed gradient word stored next to the row's bins (measured slower on B200: the separate 4 B/row array stays L2-resident)
   bool small_leaf_kernel = true; // one CTA per tiny leaf in the construct
   bool hist_sub = true;          // larger = parent - smaller
   bool hist_lane = true;         // lane-per-group construct with bank-interleaved warp-private tiles (groups with <= 64 bins)
