@@ -125,8 +125,10 @@ void Dataset::ConstructSchema(const double* sample, int ns, int ncol, int64_t to
   mappers.clear(); mappers.resize(ncol);
   const int min_split_data = total_rows > 0
       ? static_cast<int>(static_cast<double>(cfg.min_data_in_leaf) * ns / static_cast<double>(total_rows)) : 0;
-  std::vector<double> col(ns);
+  // one bin search per feature, independent of each other: spread over the host cores
+#pragma omp parallel for schedule(dynamic, 1)
   for (int j = 0; j < ncol; ++j) {
+    std::vector<double> col(ns);
     int m = 0;
     for (int i = 0; i < ns; ++i) {
       double v = sample[static_cast<size_t>(i) * ncol + j];

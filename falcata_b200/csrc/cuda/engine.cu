@@ -18,7 +18,11 @@ void StageClock::Begin(int stage, cudaStream_t s) {
 void StageClock::End(cudaStream_t s) { if (!enabled || open_ < 0) return; FB_CUDA(cudaEventRecord(pool[open_].second, s)); open_ = -1; }
 void StageClock::Resolve() {
   if (!enabled) return;
-  for (auto& pr : pending) { float ms = 0.f; if (cudaEventElapsedTime(&ms, pool[pr.second].first, pool[pr.second].second) == cudaSuccess) { total_ms[pr.first] += ms; calls[pr.first] += 1; } }
+  static const bool dump = getenv("FALCATA_STAGE_DUMP") != nullptr;
+  for (auto& pr : pending) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, pool[pr.second].first, pool[pr.second].second) == cudaSuccess) { total_ms[pr.first] += ms; calls[pr.first] += 1; if (dump) fprintf(stderr, "[stage] %s %.1f us\n", names[pr.first].c_str(), ms * 1000.f); }
+  }
   pending.clear(); next = 0;
 }
 std::string StageClock::Report() const {
@@ -194,11 +198,17 @@ void CudaEngine::SetupOwnership() {
 }
 
 int CudaEngine::ChooseRowsPerBlock(long long total_rows) const {
+  if (lane_mode_ != 0) {
+    // the lane kernel runs one 12-warp block per SM with a fixed cost per block (tile clear, pipeline
+    // fill, 12-tile merge): aim at about one and a half waves, in units of 384 rows (32 per warp),
+    // within what the 16-bit lanes of the packed cells allow per warp tile
+    long long rpb = (total_rows / (4LL * num_sms_) + 383) / 384 * 384;
+    rpb = std::min<long long>(std::max<long long>(rpb, 1536), 8064);
+    rpb = std::min<long long>(rpb, 12LL * (sub_rows_ / 32 * 32));
+    return static_cast<int>(rpb);
+  }
   long long target = total_rows / (static_cast<long long>(num_sms_) * 6) + 1;
   long long rpb = 512; while (rpb < target && rpb < 8192) rpb <<= 1;
-  // the 16-bit lanes of the packed shared-memory cells bound the rows one tile may take
-  if (lane_mode_ == 1) rpb = std::min<long long>(rpb, 8LL * sub_rows_);
-  else if (lane_mode_ == 2) rpb = std::min<long long>(rpb, sub_rows_);
   return static_cast<int>(std::max<long long>(rpb, 32));
 }
 
