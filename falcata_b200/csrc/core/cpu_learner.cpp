@@ -571,8 +571,8 @@ Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_i
           if (leaves_[a].best.gain != leaves_[b].best.gain) return leaves_[a].best.gain > leaves_[b].best.gain;
           return a < b; });
         cand.resize(budget);
-        std::sort(cand.begin(), cand.end());
       }
+      std::sort(cand.begin(), cand.end());   // a level's splits are always applied in ascending leaf order
       std::vector<int> next;
       for (int l : cand) { int r = ApplySplit(tree.get(), l); next.push_back(l); next.push_back(r); }
       for (int l : next) FindBestSplit(&leaves_[l], l, tree_index);

@@ -110,6 +110,11 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   const int NL = cfg.num_leaves;
   leaves_.Alloc(NL); best_.Alloc(NL); h_leaves_.Alloc(NL); h_best_.Alloc(NL); leaf_value_.Alloc(NL);
   host_leaves_.resize(NL);
+  use_ctrl_ = plan_.device_controller && NL <= 1024;
+  if (use_ctrl_) {
+    ctrl_.Alloc(1); frontier_.Alloc(NL + 2); journal_.Alloc(NL); h_ctrl_.Alloc(1); h_journal_.Alloc(NL); h_root_.Alloc(1);
+    levels_hint_ = 1; while ((1 << levels_hint_) < NL) ++levels_hint_;
+  }
   BuildPartitions();
   SetupOwnership();
   if (world_ > 1) {

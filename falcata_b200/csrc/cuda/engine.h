@@ -109,6 +109,10 @@ class CudaEngine : public DeviceEngine {
   DevBuf<int> tree_ints_; DevBuf<float> tree_floats_; DevBuf<signed char> tree_dec_;
   const float* cur_grad_ = nullptr; const float* cur_hess_ = nullptr;
   int lane_mode_ = 0, lane_bins_ = 64, sub_rows_ = 1 << 30;
+  // device controller state
+  bool use_ctrl_ = false; int levels_hint_ = 8;
+  DevBuf<LevelCtrl> ctrl_; DevBuf<int> frontier_; DevBuf<SplitJournal> journal_;
+  PinnedBuf<LevelCtrl> h_ctrl_; PinnedBuf<SplitJournal> h_journal_; PinnedBuf<LeafInfo> h_root_;
   double bag_fraction_ = 1.0; int bag_freq_ = 0, bag_seed_ = 0;
   int max_docs_ = 0;
 };

@@ -167,6 +167,66 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     fa.children = reinterpret_cast<const FindChild*>(db + sizeof(t)); fa.num_children = 1;
     construct_and_find();
   }
+  if (use_ctrl_) {
+    // ---- device-controlled growth: levels are enqueued ahead; the host reads one small record per batch ----
+    LaunchInitLevelCtrl(ctrl_.get(), frontier_.get(), stream_);
+    FB_CUDA(cudaMemcpyAsync(h_root_.get(), leaves_.get(), sizeof(LeafInfo), cudaMemcpyDeviceToHost, stream_));   // the root record, before any split rewrites leaf 0
+    const int rpb = ChooseRowsPerBlock(std::max(1, n_ / 2));
+    const int max_splits = NL / 2 + 1;
+    CtrlArgs ca;
+    ca.ctrl = ctrl_.get(); ca.frontier = frontier_.get(); ca.journal = journal_.get(); ca.leaves = leaves_.get(); ca.best = best_.get(); ca.meta = dd_->feature_meta.get();
+    ca.splits = reinterpret_cast<PartSplit*>(db); ca.child_init = reinterpret_cast<ChildInit*>(db + sizeof(PartSplit) * NL);
+    ca.children = reinterpret_cast<FindChild*>(db + (sizeof(PartSplit) + sizeof(ChildInit)) * NL);
+    ca.max_leaves = NL; ca.rows_per_block = rpb;
+    PartArgs pa = PartArgs();
+    pa.rows = dd_->rows.get(); pa.row_stride = dd_->row_stride; pa.idx[0] = idx_[0].get(); pa.idx[1] = idx_[1].get();
+    pa.cols = dd_->cols.size() ? dd_->cols.get() : nullptr; pa.col_stride = n_;
+    pa.splits = ca.splits; pa.num_splits = max_splits; pa.total_chunks = n_ / kPartChunk + max_splits; pa.bits = bits_.get(); pa.chunk_left = chunk_left_.get();
+    pa.split_left_total = split_left_total_.get(); pa.leaves = leaves_.get(); pa.child_init = ca.child_init; pa.hist_tasks = hist_tasks_.get(); pa.rows_per_block = rpb;
+    pa.world = world_; pa.ctrl = ctrl_.get();
+    if (world_ > 1) for (int r = 0; r < world_; ++r) pa.peer_counts[r] = fabric_->Ptr<int>(r, off_counts_) + static_cast<size_t>(rank_) * NL;
+    ha.identity_root = 0; ha.rows_per_block = rpb; ha.ctrl = ctrl_.get(); ha.num_tasks = max_splits; ha.total_blocks = n_ / rpb + max_splits;
+    fa.ctrl = ctrl_.get(); fa.children = ca.children; fa.num_children = 2 * max_splits;
+    auto enqueue_level = [&]() {
+      LaunchLevelController(ca, stream_);
+      clock_.Begin(st_part_, stream_);
+      LaunchPartitionFlags(pa, stream_); LaunchPartitionScanSetup(pa, stream_); LaunchPartitionScatter(pa, stream_);
+      clock_.End(stream_);
+      construct_and_find();
+    };
+    int enqueued = 0;
+    LevelCtrl hc;
+    for (;;) {
+      const int batch = enqueued == 0 ? std::max(1, levels_hint_) : 1;
+      for (int k = 0; k < batch; ++k) enqueue_level();
+      enqueued += batch;
+      clock_.Begin(st_sync_, stream_);
+      FB_CUDA(cudaMemcpyAsync(h_ctrl_.get(), ctrl_.get(), sizeof(LevelCtrl), cudaMemcpyDeviceToHost, stream_));
+      clock_.End(stream_);
+      if (world_ > 1) { const int st = fabric_->CheckStatus(stream_); if (st != 0) Log::Fatal("A cross-rank wait gave up (device status %d): a peer rank did not reach the same step", st); }
+      else FB_CUDA(cudaStreamSynchronize(stream_));
+      hc = *h_ctrl_.get();
+      if (hc.done || hc.num_leaves >= NL || hc.frontier_count == 0 || enqueued > 4 * NL) break;
+    }
+    levels_hint_ = std::max(1, hc.pad0);
+    journal_.Download(h_journal_.get(), hc.journal_count, stream_);
+    leaves_.Download(h_leaves_.get(), hc.num_leaves, stream_);
+    FB_CUDA(cudaStreamSynchronize(stream_));
+    if (hc.journal_count == 0) { const LeafInfo& R = *h_root_.get(); tree->leaf_value[0] = R.output; tree->leaf_count[0] = R.num_data_global; tree->leaf_weight[0] = R.sum_h; return tree.release(); }
+    { const LeafInfo& R = *h_root_.get(); tree->leaf_value[0] = R.output; tree->leaf_count[0] = R.num_data_global; tree->leaf_weight[0] = R.sum_h; }
+    for (int j = 0; j < hc.journal_count; ++j) {
+      const SplitJournal& sj = h_journal_[j];
+      const SplitRecord& b = sj.rec;
+      const FeatureMeta& m = train_->feature_meta[b.feature];
+      const BinMapper& bm = *train_->mappers[m.real_index];
+      const int right = tree->Split(sj.leaf, b.feature, m.real_index, static_cast<uint32_t>(b.threshold), bm.BinToValue(b.threshold), b.left_out, b.right_out,
+                                    b.left_cnt, b.right_cnt, b.left_h, b.right_h, static_cast<float>(b.gain), m.missing_type, b.default_left != 0);
+      tree->internal_count[tree->num_leaves - 2] = sj.parent_global;
+      if (right != sj.right_leaf) Log::Fatal("Device journal out of order (split %d)", j);
+    }
+    for (int l = 0; l < tree->num_leaves; ++l) tree->leaf_count[l] = h_leaves_[l].num_data_global;
+    return tree.release();
+  }
   ReadBackLevel(1);
   {
     const LeafInfo& R = h_leaves_[0];
@@ -187,8 +247,8 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
         if (host_leaves_[a].best.gain != host_leaves_[b].best.gain) return host_leaves_[a].best.gain > host_leaves_[b].best.gain;
         return a < b; });
       cand.resize(budget);
-      std::sort(cand.begin(), cand.end());
     }
+    std::sort(cand.begin(), cand.end());   // a level's splits are always applied in ascending leaf order
     const int S = static_cast<int>(cand.size());
     PartSplit* ps = reinterpret_cast<PartSplit*>(hb);
     ChildInit* ci = reinterpret_cast<ChildInit*>(hb + sizeof(PartSplit) * S);

@@ -86,7 +86,9 @@ __global__ void __launch_bounds__(kHistThreads) HistQuantKernel(HistArgs a) {
   int* s_packed = smem_i;                                        // [bin_count] (g16|h16)
   int* s_wide = s_packed + part.bin_count;                       // TWO_PHASE: [2 * bin_count] int32 g, int32 h
   int* s_gstart = TWO_PHASE ? s_wide + 2 * part.bin_count : s_packed + part.bin_count;   // [groups in partition]
-  const int ti = FindTask(a.tasks, a.num_tasks, blockIdx.x);
+  const int num_tasks = a.ctrl != nullptr ? a.ctrl->num_splits : a.num_tasks;
+  if (num_tasks <= 0 || static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->total_blocks : a.total_blocks)) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
+  const int ti = FindTask(a.tasks, num_tasks, blockIdx.x);
   const HistTask task = a.tasks[ti];
   const int chunk = blockIdx.x - task.block_begin;
   const long long row0 = static_cast<long long>(chunk) * a.rows_per_block;
@@ -162,7 +164,9 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
   int* tiles = reinterpret_cast<int*>(smem_raw);                                                 // [warps][NB][32]
   unsigned char* rows_w = smem_raw + sizeof(int) * kLaneWarps * kTile + static_cast<size_t>(warp) * kLaneStages * 32 * 32;   // [stages][32 rows][32 B]
   int* gh_w = reinterpret_cast<int*>(smem_raw + sizeof(int) * kLaneWarps * kTile + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * 32) + warp * kLaneStages * 32;
-  const int ti = FindTask(a.tasks, a.num_tasks, blockIdx.x);
+  const int num_tasks = a.ctrl != nullptr ? a.ctrl->num_splits : a.num_tasks;
+  if (num_tasks <= 0 || static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->total_blocks : a.total_blocks)) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
+  const int ti = FindTask(a.tasks, num_tasks, blockIdx.x);
   const HistTask task = a.tasks[ti];
   const int chunk = blockIdx.x - task.block_begin;
   const long long row0 = static_cast<long long>(chunk) * a.rows_per_block;
@@ -251,7 +255,9 @@ __global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
   const HistPartition part = a.parts[blockIdx.y];
   float* s_hist = smem_f;                                               // [2 * bin_count]
   int* s_gstart = reinterpret_cast<int*>(s_hist + 2 * part.bin_count);
-  const int ti = FindTask(a.tasks, a.num_tasks, blockIdx.x);
+  const int num_tasks = a.ctrl != nullptr ? a.ctrl->num_splits : a.num_tasks;
+  if (num_tasks <= 0 || static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->total_blocks : a.total_blocks)) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
+  const int ti = FindTask(a.tasks, num_tasks, blockIdx.x);
   const HistTask task = a.tasks[ti];
   const int chunk = blockIdx.x - task.block_begin;
   const long long row0 = static_cast<long long>(chunk) * a.rows_per_block;

@@ -7,6 +7,19 @@
 
 namespace fb {
 
+// -------------------------------------------------------- level controller ----
+// Device-resident state of the level loop. With the device controller the host enqueues the kernels
+// of several levels ahead with upper-bound grids; every kernel reads how much work the level really
+// has from this record, which the controller kernel rewrites between levels.
+struct LevelCtrl {
+  int num_leaves, next_slot, done, level;
+  int num_splits, num_children, total_chunks, total_blocks;
+  int frontier_count, journal_count, pad0, pad1;
+};
+// One applied split, in application order: enough for the host to rebuild the tree after the last level.
+struct SplitJournal { int leaf, right_leaf, parent_global, pad; SplitRecord rec; };
+struct ChildInit;
+
 // ------------------------------------------------------------- objective ----
 struct ObjDesc {
   int kind;          // ObjKind
@@ -54,6 +67,7 @@ struct HistArgs {
   int lane_bins;            // lane modes: bins per group tile (16 or 64)
   HistDest dest;
   FabricSignal sig;         // world > 1: the last block raises this rank's "construct done" flag on every peer
+  const LevelCtrl* ctrl;    // non-null: num_tasks / total_blocks come from the device controller
 };
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s);
 void LaunchHistConstructFloat(const HistArgs& a, cudaStream_t s);
@@ -90,7 +104,19 @@ struct FindArgs {
   const SplitRecord* gathered; int gathered_stride;   // local [rank][leaf] records written by the peers
   FabricSignal sig;                               // "rank-local best splits published" signal
   FabricWait wait_best;
+  const LevelCtrl* ctrl;                          // non-null: num_children comes from the device controller
 };
+
+// Device-side level controller: applies the gain-ranked leaf budget to the frontier's best splits
+// and writes the next level's descriptors, the journal and the new frontier.
+struct CtrlArgs {
+  LevelCtrl* ctrl; int* frontier; SplitJournal* journal;
+  LeafInfo* leaves; const SplitRecord* best; const FeatureMeta* meta;
+  PartSplit* splits; ChildInit* child_init; FindChild* children;
+  int max_leaves; int rows_per_block;
+};
+void LaunchLevelController(const CtrlArgs& a, cudaStream_t s);
+void LaunchInitLevelCtrl(LevelCtrl* ctrl, int* frontier, cudaStream_t s);
 void LaunchFindSplits(const FindArgs& a, cudaStream_t s);      // per (child, feature) search + in-place larger-child subtraction
 void LaunchReduceBest(const FindArgs& a, cudaStream_t s);      // per child argmax over features -> SplitRecord (world > 1: stored into every peer)
 void LaunchGatherBest(const FindArgs& a, cudaStream_t s);      // world > 1: argmax over the ranks' records
@@ -117,6 +143,7 @@ struct PartArgs {
   HistTask* hist_tasks;      // one per split: the smaller child
   int rows_per_block;
   int world; int* peer_counts[kMaxRanks];   // world > 1: address of counts[this rank][0] inside every rank's heap
+  const LevelCtrl* ctrl;     // non-null: num_splits / total_chunks come from the device controller
 };
 void LaunchPartitionFlags(const PartArgs& a, cudaStream_t s);
 void LaunchPartitionScanSetup(const PartArgs& a, cudaStream_t s);

@@ -35,7 +35,9 @@ __device__ inline bool GoLeft(const PartSplit& sp, int gb) {
 
 __global__ void __launch_bounds__(kPartThreads) PartitionFlagsKernel(PartArgs a) {
   const int chunk = blockIdx.x;
-  const int si = FindSplitOfChunk(a.splits, a.num_splits, chunk);
+  const int nsplits = a.ctrl != nullptr ? a.ctrl->num_splits : a.num_splits;
+  if (chunk >= (a.ctrl != nullptr ? a.ctrl->total_chunks : a.total_chunks)) return;
+  const int si = FindSplitOfChunk(a.splits, nsplits, chunk);
   const PartSplit sp = a.splits[si];
   const int local_chunk = chunk - sp.chunk_begin;
   if (local_chunk >= sp.num_chunks) return;
@@ -63,6 +65,7 @@ __global__ void __launch_bounds__(kPartThreads) PartitionFlagsKernel(PartArgs a)
 
 __global__ void __launch_bounds__(kPartThreads) PartitionScanSetupKernel(PartArgs a) {
   const int si = blockIdx.x;
+  if (si >= (a.ctrl != nullptr ? a.ctrl->num_splits : a.num_splits)) return;
   const PartSplit sp = a.splits[si];
   __shared__ int s_scan[kPartThreads];
   __shared__ int s_carry;
@@ -110,7 +113,9 @@ __global__ void __launch_bounds__(kPartThreads) PartitionScanSetupKernel(PartArg
 
 __global__ void __launch_bounds__(kPartThreads) PartitionScatterKernel(PartArgs a) {
   const int chunk = blockIdx.x;
-  const int si = FindSplitOfChunk(a.splits, a.num_splits, chunk);
+  const int nsplits = a.ctrl != nullptr ? a.ctrl->num_splits : a.num_splits;
+  if (chunk >= (a.ctrl != nullptr ? a.ctrl->total_chunks : a.total_chunks)) return;
+  const int si = FindSplitOfChunk(a.splits, nsplits, chunk);
   const PartSplit sp = a.splits[si];
   const int local_chunk = chunk - sp.chunk_begin;
   if (local_chunk >= sp.num_chunks) return;

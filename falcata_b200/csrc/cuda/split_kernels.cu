@@ -66,6 +66,7 @@ __device__ inline int ChildGlobalCount(const FindArgs& a, const FindChild& ch, i
 
 template <bool QUANT>
 __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
+  if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) return;
   // multi-rank: the owned slices are complete once every rank's construct has raised its flag
   if (a.wait.world > 1) FabricWaitAll(a.wait);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -205,6 +206,7 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
 }
 
 __global__ void ReduceBestKernel(FindArgs a) {
+  if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) { if (a.wait.world > 1) FabricSignalDone(a.sig, gridDim.x); return; }
   const FindChild ch = a.children[blockIdx.x];
   LeafInfo leaf = a.leaves[ch.leaf];
   leaf.num_data_global = ChildGlobalCount(a, ch, leaf.num_data_global);
@@ -257,6 +259,7 @@ __global__ void ReduceBestKernel(FindArgs a) {
 // Multi-rank: the best split of a leaf is the best of the ranks' records (each rank searched only
 // the features it owns). Every rank runs this on the same records, so all ranks decide alike.
 __global__ void GatherBestKernel(FindArgs a) {
+  if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) return;
   FabricWaitAll(a.wait_best);
   if (threadIdx.x != 0) return;
   const FindChild ch = a.children[blockIdx.x];

@@ -51,6 +51,16 @@ def test_quant_run_twice_identical_and_device_ingest():
     assert model_body(c) == model_body(d)
 
 
+@pytest.mark.parametrize("flip", ["device_controller:off", "hist_lane:off", "col_major_part:off", "gh_in_row:on"])
+def test_plan_flips_keep_quantized_model_identical(flip):
+    # performance-only plan keys must not change a single digit of a quantized model
+    X, y = make_binary(30000, 20)
+    p = {"objective": "binary", "num_leaves": 63, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "device_type": "cuda", "min_data_in_leaf": 5}
+    a = fb.train(dict(p, cuda_plan="auto"), fb.Dataset(X, y), 8).model_to_string()
+    b = fb.train(dict(p, cuda_plan="auto," + flip), fb.Dataset(X, y), 8).model_to_string()
+    assert model_body(a) == model_body(b)
+
+
 def test_device_predict_matches_host():
     X, y = make_binary(20000, 16)
     bst = fb.train({"objective": "binary", "num_leaves": 31, "verbosity": -1, "device_type": "cuda", "quant_mode": "stochastic"}, fb.Dataset(X, y), 30)
