@@ -167,6 +167,8 @@ def main() -> None:
         del X
         torch.cuda.empty_cache()
         barrier()
+        if os.environ.get("FALCATA_TIME_TAG"):
+            fb.set_time_tag(True)
         t0 = time.perf_counter()
         Xd = Xh.to(dev, non_blocking=True)
         ds2 = fb.Dataset(Xd, yh, params={"max_bin": PARAMS["max_bin"]}).set_global_rows(off, args.rows)
@@ -179,6 +181,8 @@ def main() -> None:
             import torch.distributed as dist
 
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        if os.environ.get("FALCATA_TIME_TAG") and rank == 0:
+            print(fb.time_tag_report(), file=sys.stderr)
         e2e = {"value": float(tt.item()) / K * 1000.0, "unit": "s/1000 rounds (ingest from pinned host memory + K rounds + per-round metric read, wall clock / K)",
                "h2d_bytes_per_step": int((Xh.numel() * Xh.element_size() + yh.nbytes) / K), "d2h_bytes_per_step": 16}
 

@@ -153,6 +153,16 @@ def cuda_available() -> bool:
     return bool(out.value)
 
 
+def set_time_tag(enabled: bool) -> None:
+    """Switch the host-side stage timers of the native library on or off (off clears them)."""
+    _safe_call(_lib().FB_SetTimeTag(ctypes.c_int(1 if enabled else 0)))
+
+
+def time_tag_report() -> str:
+    """Accumulated host-side stage times, one line per stage."""
+    return _get_string(_lib().FB_GetTimeTagReport)
+
+
 # ------------------------------------------------------------------ Dataset ----
 class Dataset:
     """Binned training / validation data.

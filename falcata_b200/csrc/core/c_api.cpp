@@ -115,6 +115,7 @@ int FB_DatasetCreateFromFile(const char* filename, const char* parameters, const
 int FB_DatasetCreateFromSample(const double* sample, int32_t ns, int32_t ncol, int64_t total, const char* parameters,
                                const int32_t* categorical, int32_t num_categorical, DatasetHandle* out) {
   API_BEGIN();
+  ScopedTimer api_timer("FB_DatasetCreateFromSample");
   Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());
   std::unique_ptr<Dataset> ds(new Dataset());
   std::vector<int> cats = ParseCategorical(cfg, ncol);
@@ -147,6 +148,7 @@ int FB_DatasetCreateFromSchema(const char* schema, int64_t len, const char* para
 
 int FB_DatasetInitRows(DatasetHandle handle, int32_t nrow, int64_t global_row_offset, int64_t global_num_row, int host_bins) {
   API_BEGIN();
+  ScopedTimer api_timer("FB_DatasetInitRows");
   Dataset* ds = static_cast<Dataset*>(handle);
   ds->global_row_offset = global_row_offset; ds->global_num_data = global_num_row > 0 ? global_num_row : nrow;
   if (host_bins) ds->AllocateRows(nrow); else { ds->num_data = nrow; ds->metadata.num_data = nrow; }
@@ -161,16 +163,20 @@ int FB_DatasetPushRows(DatasetHandle handle, const void* data, int dtype, int32_
 
 int FB_DatasetBinDeviceMat(DatasetHandle handle, const void* device_data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, int keep_host_copy) {
   API_BEGIN();
+  ScopedTimer api_timer("FB_DatasetBinDeviceMat");
   DeviceBinDataset(static_cast<Dataset*>(handle), device_data, dtype, nrow, ncol, is_row_major != 0, keep_host_copy != 0);
   API_END();
 }
 
 int FB_DatasetSetField(DatasetHandle handle, const char* field_name, const void* data, int64_t n, int dtype) {
   API_BEGIN();
+  ScopedTimer api_timer("FB_DatasetSetField");
   Dataset* ds = static_cast<Dataset*>(handle); const std::string f = field_name;
   auto as_float = [&](std::vector<float>* v) {
+    if (dtype == kF32) { v->assign(static_cast<const float*>(data), static_cast<const float*>(data) + n); return; }
     v->resize(n);
-    for (int64_t i = 0; i < n; ++i) (*v)[i] = dtype == kF32 ? static_cast<const float*>(data)[i] : (dtype == kF64 ? static_cast<float>(static_cast<const double*>(data)[i]) : static_cast<float>(static_cast<const int32_t*>(data)[i]));
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) (*v)[i] = dtype == kF64 ? static_cast<float>(static_cast<const double*>(data)[i]) : static_cast<float>(static_cast<const int32_t*>(data)[i]);
   };
   if (f == "label" || f == "target") { if (n != ds->num_data) Log::Fatal("Length of labels (%lld) differs from the number of rows (%d)", static_cast<long long>(n), ds->num_data); std::vector<float> v; as_float(&v); ds->metadata.label.swap(v); }
   else if (f == "weight" || f == "weights") { if (n == 0) ds->metadata.SetWeights(nullptr, 0); else { std::vector<float> v; as_float(&v); ds->metadata.SetWeights(v.data(), static_cast<data_size_t>(n)); } }
@@ -243,10 +249,12 @@ int FB_BoosterCreate(const DatasetHandle train_data, const char* parameters, Boo
   b->train = train;
   b->objective.reset(CreateObjective(b->config.objective, b->config));
   if (b->objective) {
+    ScopedTimer t("Booster::ObjectiveInit");
     if (b->objective->NeedQueries() && train->metadata.query_boundaries.empty()) Log::Fatal("Ranking tasks require query information");
     b->objective->Init(train->metadata, train->num_data);
   }
   b->gbdt.reset(new GBDT());
+  ScopedTimer t("Booster::GBDTInit");
   b->gbdt->Init(b->config, train, b->objective.get(), b->config.metric_list);
   *out = b.release();
   API_END();

@@ -32,6 +32,7 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
     if (is_cuda_) {
+      ScopedTimer t("GBDT::CreateDeviceEngine");
       engine_.reset(CreateDeviceEngine(config_, train, obj, num_tree_per_iteration_));
     } else {
       learner_.reset(CreateCPUTreeLearner(config_));
@@ -44,12 +45,13 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
       grad_.resize(total); hess_.resize(total);
     }
     metrics_.clear(); metrics_.emplace_back();
+    ScopedTimer tm("GBDT::MetricInit");
     for (auto& name : metric_names_) { std::unique_ptr<Metric> m(CreateMetric(name, config_)); if (m) { m->Init(train->metadata, train->num_data); metrics_[0].push_back(std::move(m)); } }
     is_goss_ = cfg.data_sample_strategy == "goss";
     is_bagging_ = !is_goss_ && cfg.bagging_freq > 0 && (cfg.bagging_fraction < 1.0 || cfg.pos_bagging_fraction < 1.0 || cfg.neg_bagging_fraction < 1.0);
     if (engine_ && is_bagging_) engine_->SetBagging(cfg.bagging_fraction, cfg.bagging_freq, cfg.bagging_seed);
     if (engine_ && is_goss_) { Log::Warning("GOSS sampling runs on the host learner only; the device engine trains on all rows"); is_goss_ = false; }
-    bag_indices_.resize(train->num_data);
+    if (!engine_) bag_indices_.resize(train->num_data);   // the device engine draws its own bags
   }
 }
 
@@ -220,6 +222,7 @@ bool GBDT::TrainOneIter(const float* grad_in, const float* hess_in) {
   std::vector<double> inits(K, 0.0);
   if (grad_in == nullptr || hess_in == nullptr) {
     if (objective_ == nullptr) Log::Fatal("No objective function provided and no custom gradients given");
+    ScopedTimer t("GBDT::BoostFromAverage");
     for (int k = 0; k < K; ++k) BoostFromAverage(k, &inits[k]);
   }
   if (models_.empty() && !boosted_from_average_) {
@@ -240,6 +243,7 @@ bool GBDT::TrainOneIter(const float* grad_in, const float* hess_in) {
 
   if (engine_) {
     std::vector<std::unique_ptr<Tree>> trees; bool all_const = false;
+    ScopedTimer te("GBDT::EngineIter");
     engine_->TrainOneIter(grad_in, hess_in, iter_, shrinkage_rate_, inits, &trees, &all_const);
     if (all_const) {
       Log::Warning("Stopped training because there are no more leaves that meet the split requirements");

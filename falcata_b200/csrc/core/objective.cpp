@@ -239,7 +239,10 @@ class BinaryLogloss : public ObjectiveFunction {
   void Init(const Metadata& md, data_size_t n) override {
     n_ = n; label_ = md.label.data(); weights_ = md.weights.empty() ? nullptr : md.weights.data();
     int64_t cnt[2] = {0, 0};
-    for (data_size_t i = 0; i < n; ++i) { if (is_pos_(label_[i])) ++cnt[0]; else ++cnt[1]; }
+    { int64_t c0 = 0, c1 = 0;
+#pragma omp parallel for schedule(static) reduction(+ : c0, c1)
+      for (data_size_t i = 0; i < n; ++i) { if (is_pos_(label_[i])) ++c0; else ++c1; }
+      cnt[0] = c0; cnt[1] = c1; }
     Network::SumInt64(cnt, 2);
     need_train_ = true;
     if (cnt[0] == 0 || cnt[1] == 0) { Log::Warning("Contains only one class"); need_train_ = false; }
@@ -265,7 +268,10 @@ class BinaryLogloss : public ObjectiveFunction {
     // weighted positive rate through exact integer sums (rank-count independent)
     const double kScale = 1048576.0;
     int64_t acc[2] = {0, 0};
-    for (data_size_t i = 0; i < n_; ++i) { const double w = weights_ ? weights_[i] : 1.0; if (is_pos_(label_[i])) acc[0] += llround(w * kScale); acc[1] += llround(w * kScale); }
+    { int64_t a0 = 0, a1 = 0;   // integer sums: the thread split cannot change the result
+#pragma omp parallel for schedule(static) reduction(+ : a0, a1)
+      for (data_size_t i = 0; i < n_; ++i) { const int64_t w = weights_ ? llround(weights_[i] * kScale) : 1048576; if (is_pos_(label_[i])) a0 += w; a1 += w; }
+      acc[0] = a0; acc[1] = a1; }
     Network::SumInt64(acc, 2);
     double p = acc[1] ? static_cast<double>(acc[0]) / static_cast<double>(acc[1]) : 0.5;
     p = std::min(std::max(p, 1e-15), 1.0 - 1e-15);

@@ -1,17 +1,21 @@
-// K1q / K1: level-batched histogram construction with shared-memory atomics, and its fusion with
-// the cross-rank reduce-scatter (K1q-RS): the epilogue adds every non-zero bin of the block's tile
-// straight into the slot of the rank that OWNS the bin's feature — a local `red.add.u64`, or the
-// same instruction on a peer pointer over NVLink. No staging buffer, no NCCL call.
+// K1q / K1: level-batched histogram construction, and its fusion with the cross-rank reduce-scatter
+// (K1q-RS). One rank: a block's non-zero bins are added into the leaf's pool slot with `red.add.u64`.
+// Several ranks: blocks add into a local staging histogram of the task; the LAST block of a task
+// (a per-task arrival counter) cuts the staged histogram by feature owner and writes each slice with
+// plain stores into the owner's [source rank][task] staging slot over NVLink, then signals the owner's
+// flag. The owner sums the R source slices in rank order when the split search loads a bin, so the
+// reduction order, and with integer bins the result, does not depend on timing. No NCCL call.
 //
 // Parity: src/treelearner/cuda/cuda_histogram_constructor.cu:L1602-1910 (quantized dense construct:
 // packed int32 (g16|h16) shared-memory atomics, rows per block capped so the 16-bit lanes cannot
 // overflow, level-batched launch), L530-832 (full-precision construct), and the staging kernels
 // around ncclAllReduce that this fusion removes (cuda_single_gpu_tree_learner.cu:L584-708).
 //
-// Work mapping: a block owns (task = one leaf's row window chunk, partition = a run of feature
-// groups whose bins fit the shared tile). Items are (row, 4-group word) pairs laid out flat over the
-// block's threads, so a warp reads whole 32-byte sectors of consecutive rows and its lanes hit
-// different features' bins (no same-address serialisation inside a row).
+// Work mapping of the atomic instances: a block owns (task = one leaf's row window chunk, partition =
+// a run of feature groups whose bins fit the shared tile). Items are (row, 4-group word) pairs laid out
+// flat over the block's threads, so a warp reads whole 32-byte sectors of consecutive rows and its
+// lanes hit different features' bins (no same-address serialisation inside a row). The lane-per-group
+// instance further down is the default for groups of at most 64 bins.
 #include "kernels.cuh"
 
 #include <cuda_pipeline.h>
