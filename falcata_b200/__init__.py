@@ -4,14 +4,14 @@ Public surface (parity: python-package/falcata/__init__.py:L11-15, L81-84): ``Da
 ``train``, ``cv``, callbacks, sklearn-style estimators (``LGBM*`` / ``Falcata*`` names), model
 importers and plotting helpers.
 """
-from .basic import (Booster, Dataset, FalcataError, LightGBMError, cuda_available, register_logger, set_time_tag,
+from .basic import (Booster, Dataset, FalcataError, LightGBMError, cuda_available, register_logger, get_num_threads, set_num_threads, set_time_tag,
                     time_tag_report)
 from .callback import EarlyStopException, early_stopping, log_evaluation, record_evaluation, reset_parameter
 from .engine import CVBooster, cv, train
 
 __version__ = "0.1.0"
 
-__all__ = ["Dataset", "Booster", "CVBooster", "train", "cv", "FalcataError", "LightGBMError", "register_logger", "cuda_available", "set_time_tag", "time_tag_report",
+__all__ = ["Dataset", "Booster", "CVBooster", "train", "cv", "FalcataError", "LightGBMError", "register_logger", "cuda_available", "set_time_tag", "set_num_threads", "get_num_threads", "time_tag_report",
            "early_stopping", "log_evaluation", "record_evaluation", "reset_parameter", "EarlyStopException"]
 
 try:  # sklearn-style estimators are optional (scikit-learn may be absent)

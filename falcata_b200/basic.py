@@ -153,6 +153,17 @@ def cuda_available() -> bool:
     return bool(out.value)
 
 
+def set_num_threads(n: int) -> None:
+    """Host worker threads of the native library's parallel loops (bin finding, label scans, host learners)."""
+    _safe_call(_lib().FB_SetNumThreads(ctypes.c_int(int(n))))
+
+
+def get_num_threads() -> int:
+    out = ctypes.c_int(0)
+    _safe_call(_lib().FB_GetNumThreads(ctypes.byref(out)))
+    return out.value
+
+
 def set_time_tag(enabled: bool) -> None:
     """Switch the host-side stage timers of the native library on or off (off clears them)."""
     _safe_call(_lib().FB_SetTimeTag(ctypes.c_int(1 if enabled else 0)))
@@ -218,6 +229,8 @@ class Dataset:
             self._handle = handle
         elif _is_cuda_array(self.data):
             self._construct_from_device(self.data, params, ref_handle)
+        elif self._global_rows is not None and ref_handle is None:
+            self._construct_sharded_host(_to_numpy_2d(self.data), params)
         else:
             arr = _to_numpy_2d(self.data)
             row_major = 1 if arr.flags.c_contiguous else 0
@@ -242,6 +255,29 @@ class Dataset:
         if self.free_raw_data:
             self.data = None
         return self
+
+    def _construct_sharded_host(self, arr: np.ndarray, params: Dict[str, Any]) -> None:
+        """Host ingest of one row shard: the bin sample is drawn by GLOBAL row id and gathered over all
+        ranks, so every rank derives the same bin boundaries; the local rows are then binned on the host.
+        Parity: src/io/dataset_loader.cpp:L672-759 (distributed bin finding)."""
+        import torch
+
+        from .parallel import bootstrap
+
+        lib = _lib()
+        if not arr.flags.c_contiguous:
+            arr = np.ascontiguousarray(arr)
+        nrow, ncol = arr.shape
+        goff, gtot = self._global_rows
+        sample, total = bootstrap.gather_bin_sample(torch.from_numpy(arr), int(params.get("bin_construct_sample_cnt", 200000)),
+                                                    int(params.get("data_random_seed", 1)), goff, gtot)
+        sample = np.ascontiguousarray(sample, dtype=np.float64)
+        handle = ctypes.c_void_p()
+        _safe_call(lib.FB_DatasetCreateFromSample(sample.ctypes.data_as(ctypes.c_void_p), ctypes.c_int32(sample.shape[0]), ctypes.c_int32(ncol),
+                                                  ctypes.c_int64(total), _param_str(params), None, 0, ctypes.byref(handle)))
+        self._handle = handle
+        _safe_call(lib.FB_DatasetInitRows(handle, ctypes.c_int32(nrow), ctypes.c_int64(goff), ctypes.c_int64(total), 1))
+        _safe_call(lib.FB_DatasetPushRows(handle, arr.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[arr.dtype], ctypes.c_int32(nrow), ctypes.c_int32(ncol), 1, 0))
 
     def _construct_from_device(self, data: Any, params: Dict[str, Any], ref_handle: Any) -> None:
         """Device ingest: sample rows on the GPU, find bins on the host from the sample, bin on the GPU."""

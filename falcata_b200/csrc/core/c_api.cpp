@@ -1,6 +1,8 @@
 // C API implementation. Parity: src/c_api.cpp (Booster wrapper L179-480, API functions L1021-3238).
 #include "fb/c_api.h"
 
+#include <omp.h>
+
 #include <fstream>
 #include <memory>
 #include <mutex>
@@ -55,6 +57,8 @@ const char* FB_GetLastError() { return g_last_error.c_str(); }
 
 int FB_RegisterLogCallback(void (*callback)(const char*)) { API_BEGIN(); Log::callback() = callback; API_END(); }
 int FB_CudaAvailable(int* out) { API_BEGIN(); *out = CudaAvailable() ? 1 : 0; API_END(); }
+int FB_SetNumThreads(int num_threads) { API_BEGIN(); if (num_threads > 0) omp_set_num_threads(num_threads); API_END(); }
+int FB_GetNumThreads(int* out) { API_BEGIN(); *out = omp_get_max_threads(); API_END(); }
 int FB_SetTimeTag(int enabled) { API_BEGIN(); StageTimer::Get().enabled = enabled != 0; if (!enabled) StageTimer::Get().Clear(); API_END(); }
 int FB_GetTimeTagReport(int64_t buffer_len, int64_t* out_len, char* out_str) { API_BEGIN(); CopyOut(StageTimer::Get().Report(), buffer_len, out_len, out_str); API_END(); }
 
@@ -240,6 +244,7 @@ int FB_BoosterCreate(const DatasetHandle train_data, const char* parameters, Boo
   std::unique_ptr<BoosterWrap> b(new BoosterWrap());
   const Dataset* train = static_cast<const Dataset*>(train_data);
   b->config.Set(Config::Str2Map(parameters), CudaAvailable());
+  if (b->config.num_threads > 0) omp_set_num_threads(b->config.num_threads);
   if (b->config.is_cuda && !CudaAvailable()) Log::Fatal("device_type=cuda was requested but no CUDA device is available");
   if (b->config.is_cuda && train->device == nullptr) {
     // the device engine uploads host bins itself when the dataset was built on the host

@@ -18,6 +18,9 @@ const char* FB_GetLastError();
 int FB_RegisterLogCallback(void (*callback)(const char*));
 int FB_CudaAvailable(int* out);
 int FB_SetTimeTag(int enabled);
+// Host worker threads of the OpenMP loops (bin finding, label scans, host learners). <= 0: leave as is.
+int FB_SetNumThreads(int num_threads);
+int FB_GetNumThreads(int* out);
 int FB_GetTimeTagReport(int64_t buffer_len, int64_t* out_len, char* out_str);
 
 /* Host collectives supplied by the embedding process (torch.distributed in the Python layer). */

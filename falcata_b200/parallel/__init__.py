@@ -13,7 +13,17 @@ from .bootstrap import free_host_network, init_device_fabric, init_host_network,
 
 
 def init(heap_bytes: int = 256 << 20, device: bool = True) -> None:
-    """Connect this rank to its peers: host collectives always, the device fabric when CUDA is used."""
+    """Connect this rank to its peers: host collectives always, the device fabric when CUDA is used.
+
+    torchrun exports OMP_NUM_THREADS=1 to every worker unless the user set it; bin finding at ingest is a
+    host loop over features, so in that case each rank takes an equal share of the cores instead."""
+    import os
+
+    if os.environ.get("TORCHELASTIC_RUN_ID") and os.environ.get("OMP_NUM_THREADS") == "1" and not os.environ.get("FALCATA_KEEP_OMP_THREADS"):
+        from ..basic import set_num_threads
+
+        local_world = max(1, int(os.environ.get("LOCAL_WORLD_SIZE", "1")))
+        set_num_threads(max(1, min(32, (os.cpu_count() or 1) // local_world)))
     init_host_network()
     if device:
         import torch

@@ -66,11 +66,24 @@ def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total
         pos = c * chunk + hi
         c += 1
     idx = torch.cat(picks) if picks else torch.zeros(0, dtype=torch.int64, device=t.device)
-    local = t[idx].to(torch.float64).cpu().numpy()
+    picked = t[idx].to(torch.float64)
     if d and ws > 1:
-        parts = [None] * ws
-        d.all_gather_object(parts, local)
-        local = np.concatenate(parts, axis=0)
+        # tensor collectives (no pickling): sizes first, then the rows padded to the largest shard
+        on_dev = picked.is_cuda and d.get_backend() == "nccl"
+        cdev = picked.device if on_dev else torch.device("cpu")
+        sizes = torch.zeros(ws, dtype=torch.int64, device=cdev)
+        sizes[rank] = picked.shape[0]
+        d.all_reduce(sizes)
+        sizes = sizes.cpu().tolist()
+        cap = max(1, max(sizes))
+        padded = torch.zeros((cap, t.shape[1]), dtype=torch.float64, device=cdev)
+        padded[: picked.shape[0]] = picked.to(cdev)
+        outs = torch.empty((ws, cap, t.shape[1]), dtype=torch.float64, device=cdev)
+        d.all_gather_into_tensor(outs, padded) if on_dev else d.all_gather(list(outs.unbind(0)), padded)
+        outs = outs.cpu().numpy()
+        local = np.concatenate([outs[r, : sizes[r]] for r in range(ws)], axis=0)
+    else:
+        local = picked.cpu().numpy()
     if local.shape[0] == 0:
         local = t[:1].to(torch.float64).cpu().numpy()
     return local, total

@@ -1,0 +1,72 @@
+"""Multi-process CPU training over gloo: the host parallel learners against the single-process learner,
+and failure detection when a rank dies on the host.
+Parity: tests/distributed/_test_distributed.py:L53-190 (N processes on localhost compared with one)."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+import falcata_b200 as fb
+from util import make_binary, model_body
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _launch(world, extra, timeout=180):
+    port = _free_port()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="2")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "dist_cpu_worker.py")] + extra, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+            o += "\nKILLED_BY_TEST_TIMEOUT"
+        outs.append((p.returncode, o))
+    return outs
+
+
+def _single(learner_rows, quant, rounds):
+    X, y = make_binary(learner_rows, 12)
+    params = {"objective": "binary", "num_leaves": 15, "max_bin": 63, "verbosity": -1, "device_type": "cpu", "grow_policy": "level", "quant_mode": quant,
+              "min_data_in_leaf": 5, "seed": 5}
+    return fb.train(params, fb.Dataset(X, y).set_global_rows(0, learner_rows), rounds).model_to_string()
+
+
+@pytest.mark.parametrize("learner,quant", [("data", "stochastic"), ("feature", "stochastic"), ("voting", "stochastic"), ("data", "none")])
+def test_two_ranks_match_single_process(tmp_path, learner, quant):
+    out = str(tmp_path / "model.txt")
+    res = _launch(2, ["--learner", learner, "--quant", quant, "--out", out])
+    for rc, o in res:
+        assert rc == 0, o[-2000:]
+    dist_model = open(out).read()
+    single = _single(6000, quant, 10)
+    if quant == "stochastic":
+        # integer histograms: the sharded sum is exact, so the model is the same digit for digit
+        assert model_body(dist_model) == model_body(single)
+    else:
+        a = fb.Booster(model_str=dist_model); b = fb.Booster(model_str=single)
+        X, _ = make_binary(6000, 12)
+        import numpy as np
+
+        assert np.abs(a.predict(X) - b.predict(X)).max() < 1e-3
+
+
+def test_rank_that_dies_is_detected_on_the_host():
+    res = _launch(2, ["--mode", "fail"], timeout=90)
+    assert res[1][0] == 7
+    rc0, o0 = res[0]
+    assert "KILLED_BY_TEST_TIMEOUT" not in o0, o0[-2000:]
+    assert rc0 != 0 and ("TRAIN_ERROR" in o0 or "Error" in o0), o0[-2000:]
