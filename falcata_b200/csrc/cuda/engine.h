@@ -59,6 +59,8 @@ class CudaEngine : public DeviceEngine {
   void SetupOwnership();
   void RunRootHistogram();
   void ReadBackLevel(int num_leaves);
+  void DrawBag(int round);
+  const uint8_t* bag_mask_ptr() const { return bag_active_ ? bag_mask_.get() : nullptr; }
   void UploadTreeForTraversal(const Tree& tree, const Dataset* ds, DevTree* out);
   int ChooseRowsPerBlock(long long total_rows) const;
 
@@ -113,7 +115,10 @@ class CudaEngine : public DeviceEngine {
   bool use_ctrl_ = false; int levels_hint_ = 8;
   DevBuf<LevelCtrl> ctrl_; DevBuf<int> frontier_; DevBuf<SplitJournal> journal_;
   PinnedBuf<LevelCtrl> h_ctrl_; PinnedBuf<SplitJournal> h_journal_; PinnedBuf<LeafInfo> h_root_;
+  // bagging (device-drawn; -1 = no bag drawn)
   double bag_fraction_ = 1.0; int bag_freq_ = 0, bag_seed_ = 0;
+  bool bag_active_ = false; int bag_count_ = -1, root_count_ = 0; long long bag_global_ = 0, root_global_ = 0;
+  DevBuf<uint8_t> bag_mask_; DevBuf<int> bag_idx_, bag_chunk_, bag_count_dev_; PinnedBuf<int> h_bag_count_;
   int max_docs_ = 0;
 };
 

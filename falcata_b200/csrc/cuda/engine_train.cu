@@ -34,16 +34,22 @@ __global__ void InitRootKernel(LeafInfo* leaves, const long long* sums_i, const 
 void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess, int iter, double shrinkage, const std::vector<double>& init_scores,
                               std::vector<std::unique_ptr<Tree>>* out, bool* all_constant) {
   const float* grad = grad_.get(); const float* hess = hess_.get();
+  const bool bagging = bag_freq_ > 0 && (cfg_.bagging_fraction < 1.0 || cfg_.pos_bagging_fraction < 1.0 || cfg_.neg_bagging_fraction < 1.0);
+  if (bagging && (iter % bag_freq_ == 0 || bag_count_ < 0)) DrawBag(iter / bag_freq_);
+  bag_active_ = bagging;
+  const uint8_t* mask = bag_mask_ptr();
+  root_count_ = bagging ? bag_count_ : n_; root_global_ = bagging ? bag_global_ : train_->global_num_data;
   clock_.Begin(st_grad_, stream_);
   if (custom_grad != nullptr) {
     grad = custom_grad; hess = custom_hess;
     FB_CUDA(cudaStreamSynchronize(0));   // custom gradients were produced on the caller's (default) stream
-    LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_);
+    LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_, mask);
   } else {
     if (obj_ == nullptr) Log::Fatal("No objective function provided and no custom gradients given");
     LaunchObjectiveGradients(objd_, score_.get(), dd_->label.get(), dd_->weight.size() ? dd_->weight.get() : nullptr,
                              dd_->query_boundaries.size() ? dd_->query_boundaries.get() : nullptr, dd_->num_queries, label_gain_.get(),
                              static_cast<int>(label_gain_.size()), n_, grad_.get(), hess_.get(), maxbuf_.get(), stream_);
+    if (bagging && quant_) LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_, mask);   // the scale comes from the bag's rows only
   }
   // quantization scales must be the same on every rank: max over ranks of the per-class maxima
   if (world_ > 1 && quant_) fabric_->AllReduce(kFabricMaxF32, maxbuf_.get(), global_max_.get(), 2 * K_, stream_);
@@ -61,11 +67,15 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
       tree->Shrink(shrinkage);
       // training rows through the final partition; validation rows by traversal
       clock_.Begin(st_score_, stream_);
-      leaf_value_.Upload(tree->leaf_value.data(), tree->num_leaves, stream_);
-      LaunchAddLeafOutputs(leaves_.get(), leaf_value_.get(), tree->num_leaves, idx_[0].get(), idx_[1].get(), score_.get() + static_cast<size_t>(k) * n_, stream_);
+      if (!bagging) {
+        leaf_value_.Upload(tree->leaf_value.data(), tree->num_leaves, stream_);
+        LaunchAddLeafOutputs(leaves_.get(), leaf_value_.get(), tree->num_leaves, idx_[0].get(), idx_[1].get(), score_.get() + static_cast<size_t>(k) * n_, stream_);
+      }
       clock_.End(stream_);
-      if (!valid_.empty()) {
+      if (!valid_.empty() || bagging) {
         DevTree dt; UploadTreeForTraversal(*tree, train_, &dt);
+        // out-of-bag rows are in no leaf window: with bagging the training scores take the traversal too
+        if (bagging) LaunchAddTreeBinned(dt, dd_->rows.get(), dd_->row_stride, n_, 1.f, score_.get() + static_cast<size_t>(k) * n_, stream_);
         for (auto& vs : valid_) LaunchAddTreeBinned(dt, vs.dd->rows.get(), vs.dd->row_stride, vs.ds->num_data, 1.f, vs.score.get() + static_cast<size_t>(k) * vs.ds->num_data, stream_);
       }
       FB_CUDA(cudaStreamSynchronize(stream_));   // leaf_value upload source and traversal staging are host memory
@@ -97,15 +107,17 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   if (quant_) {
     LaunchQuantize(cur_grad_, cur_hess_, n_, maxbuf_.get() + 2 * class_id, world_ > 1 ? global_max_.get() + 2 * class_id : nullptr, cfg_.quant_bins_resolved,
                    cfg_.quant == QuantMode::Stochastic, static_cast<uint32_t>(cfg_.seed), static_cast<uint32_t>(tree_index),
-                   static_cast<uint64_t>(train_->global_row_offset), const_cast<uint8_t*>(gh_base_), gh_stride_, scales_.get(), root_sums_i_.get(), stream_);
+                   static_cast<uint64_t>(train_->global_row_offset), const_cast<uint8_t*>(gh_base_), gh_stride_, scales_.get(), root_sums_i_.get(), stream_, bag_mask_ptr());
     if (world_ > 1) fabric_->AllReduce(kFabricSumI64, root_sums_i_.get(), root_sums_i_.get(), 2, stream_);
   } else {
-    LaunchInterleave(cur_grad_, cur_hess_, n_, gh2_.get(), partial_.get(), static_cast<int>(partial_.size() / 2), root_sums_d_.get(), stream_);
+    LaunchInterleave(cur_grad_, cur_hess_, n_, gh2_.get(), partial_.get(), static_cast<int>(partial_.size() / 2), root_sums_d_.get(), stream_, bag_mask_ptr());
     if (world_ > 1) fabric_->AllReduce(kFabricSumF64, root_sums_d_.get(), root_sums_d_.get(), 2, stream_);
   }
-  InitRootKernel<<<1, 1, 0, stream_>>>(leaves_.get(), root_sums_i_.get(), root_sums_d_.get(), scales_.get(), quant_ ? 1 : 0, n_, train_->global_num_data, sp_);
+  InitRootKernel<<<1, 1, 0, stream_>>>(leaves_.get(), root_sums_i_.get(), root_sums_d_.get(), scales_.get(), quant_ ? 1 : 0, root_count_, root_global_, sp_);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
-  LaunchInitIndices(idx_[0].get(), n_, stream_);
+  const bool bagged = bag_active_;
+  if (bagged) FB_CUDA(cudaMemcpyAsync(idx_[0].get(), bag_idx_.get(), sizeof(int) * static_cast<size_t>(root_count_), cudaMemcpyDeviceToDevice, stream_));
+  else LaunchInitIndices(idx_[0].get(), n_, stream_);
   clock_.End(stream_);
 
   // ---- common launch descriptors ----
@@ -157,13 +169,13 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
 
   // ---- root ----
   {
-    HistTask t; t.slot = 0; t.begin = 0; t.count = n_; t.buffer = 0; t.block_begin = 0; t.pad0 = t.pad1 = 0;
-    ha.rows_per_block = ChooseRowsPerBlock(n_); t.num_blocks = std::max(1, (n_ + ha.rows_per_block - 1) / ha.rows_per_block);
+    HistTask t; t.slot = 0; t.begin = 0; t.count = root_count_; t.buffer = 0; t.block_begin = 0; t.pad0 = t.pad1 = 0;
+    ha.rows_per_block = ChooseRowsPerBlock(root_count_); t.num_blocks = std::max(1, (root_count_ + ha.rows_per_block - 1) / ha.rows_per_block);
     FindChild fc; fc.leaf = 0; fc.slot = 0; fc.other_slot = 0; fc.is_larger = 0; fc.split = -1; fc.is_left = 1; fc.parent_global = 0; fc.task = 0;
     memcpy(hb, &t, sizeof(t)); memcpy(hb + sizeof(t), &fc, sizeof(fc));
     FB_CUDA(cudaMemcpyAsync(db, hb, sizeof(t) + sizeof(fc), cudaMemcpyHostToDevice, stream_));
     FB_CUDA(cudaMemcpyAsync(hist_tasks_.get(), db, sizeof(t), cudaMemcpyDeviceToDevice, stream_));
-    ha.num_tasks = 1; ha.total_blocks = std::max(1, t.num_blocks); ha.identity_root = 1;
+    ha.num_tasks = 1; ha.total_blocks = std::max(1, t.num_blocks); ha.identity_root = bagged ? 0 : 1;
     fa.children = reinterpret_cast<const FindChild*>(db + sizeof(t)); fa.num_children = 1;
     construct_and_find();
   }
@@ -231,7 +243,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   {
     const LeafInfo& R = h_leaves_[0];
     HostLeaf& hl = host_leaves_[0];
-    hl.begin = 0; hl.count = n_; hl.buffer = 0; hl.depth = 0; hl.slot = 0; hl.best = h_best_[0]; hl.valid = true;
+    hl.begin = 0; hl.count = root_count_; hl.buffer = 0; hl.depth = 0; hl.slot = 0; hl.best = h_best_[0]; hl.valid = true;
     tree->leaf_value[0] = R.output; tree->leaf_count[0] = R.num_data_global; tree->leaf_weight[0] = R.sum_h;
   }
   int next_slot = 1;
@@ -314,6 +326,29 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     frontier.swap(next);
   }
   return tree.release();
+}
+
+// A new bag: flags by global row id, compaction of the in-bag rows, and the (global) bag size.
+void CudaEngine::DrawBag(int round) {
+  if (bag_mask_.size() == 0) {
+    bag_mask_.Alloc(std::max(1, n_)); bag_idx_.Alloc(std::max(1, n_)); bag_chunk_.Alloc(n_ / 1024 + 2); bag_count_dev_.Alloc(1); h_bag_count_.Alloc(1);
+  }
+  BagArgs a;
+  a.n = n_; a.global_row_offset = static_cast<unsigned long long>(train_->global_row_offset); a.round = static_cast<uint32_t>(round);
+  a.seed = static_cast<uint32_t>(bag_seed_);
+  a.fraction = cfg_.bagging_fraction; a.pos_fraction = cfg_.pos_bagging_fraction; a.neg_fraction = cfg_.neg_bagging_fraction;
+  a.balanced = (cfg_.pos_bagging_fraction < 1.0 || cfg_.neg_bagging_fraction < 1.0) ? 1 : 0;
+  a.label = dd_->label.get();
+  a.by_query = (cfg_.bagging_by_query && dd_->num_queries > 0) ? 1 : 0;
+  a.query_boundaries = dd_->query_boundaries.size() ? dd_->query_boundaries.get() : nullptr; a.num_queries = dd_->num_queries; a.global_query_offset = 0;
+  a.mask = bag_mask_.get(); a.bag_idx = bag_idx_.get(); a.chunk_count = bag_chunk_.get(); a.bag_count = bag_count_dev_.get();
+  LaunchBagging(a, stream_);
+  bag_count_dev_.Download(h_bag_count_.get(), 1, stream_);
+  FB_CUDA(cudaStreamSynchronize(stream_));
+  bag_count_ = *h_bag_count_.get();
+  int64_t g = bag_count_;
+  if (world_ > 1) Network::SumInt64(&g, 1);
+  bag_global_ = g;
 }
 
 void CudaEngine::ReadBackLevel(int num_leaves) {

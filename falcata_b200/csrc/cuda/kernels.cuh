@@ -30,10 +30,12 @@ struct ObjDesc {
 
 void LaunchObjectiveGradients(const ObjDesc& d, const float* score, const float* label, const float* weight, const int* qb, int num_queries,
                               const double* label_gain, int num_gain, int n, float* grad, float* hess, float* maxbuf, cudaStream_t s);
-void LaunchAbsMax(const float* grad, const float* hess, int n, int num_class, float* maxbuf, cudaStream_t s);
+// `mask` (one byte per row, 0 = out of bag; nullptr = all rows) limits the maxima and root sums to the bag.
+void LaunchAbsMax(const float* grad, const float* hess, int n, int num_class, float* maxbuf, cudaStream_t s, const uint8_t* mask = nullptr);
 void LaunchQuantize(const float* grad, const float* hess, int n, const float* maxbuf, const float* global_max, int bins, bool stochastic, uint32_t seed,
-                    uint32_t iter_key, uint64_t global_row_offset, uint8_t* gh_base, int gh_stride, float* scales_out, long long* root_sums, cudaStream_t s);
-void LaunchInterleave(const float* grad, const float* hess, int n, float2* gh2, double* partial, int partial_capacity, double* root_sums_d, cudaStream_t s);
+                    uint32_t iter_key, uint64_t global_row_offset, uint8_t* gh_base, int gh_stride, float* scales_out, long long* root_sums, cudaStream_t s, const uint8_t* mask = nullptr);
+void LaunchInterleave(const float* grad, const float* hess, int n, float2* gh2, double* partial, int partial_capacity, double* root_sums_d, cudaStream_t s,
+                      const uint8_t* mask = nullptr);
 
 // ------------------------------------------------------------- histogram ----
 // Where a histogram bin lives: owner rank and index inside that rank's slot. With one rank the
@@ -149,6 +151,20 @@ void LaunchPartitionFlags(const PartArgs& a, cudaStream_t s);
 void LaunchPartitionScanSetup(const PartArgs& a, cudaStream_t s);
 void LaunchPartitionScatter(const PartArgs& a, cudaStream_t s);
 void LaunchInitIndices(int* idx, int n, cudaStream_t s);
+
+// ---------------------------------------------------------------- bagging ----
+// Row sampling on the device: a row is in the bag iff a Philox number keyed on (bagging seed, bagging
+// round, GLOBAL row id) is below its fraction, so the bag does not depend on how rows are sharded and is
+// the one the host learner draws. Outputs: a byte mask, the ascending list of in-bag rows, their count.
+struct BagArgs {
+  int n; unsigned long long global_row_offset; uint32_t round, seed;
+  double fraction, pos_fraction, neg_fraction; int balanced;    // balanced: fraction by label sign
+  const float* label;
+  const int* query_boundaries; int num_queries; int by_query;   // by_query: one draw per query, keyed on the global query id
+  unsigned long long global_query_offset;
+  uint8_t* mask; int* bag_idx; int* chunk_count; int* bag_count;
+};
+void LaunchBagging(const BagArgs& a, cudaStream_t s);
 
 // ----------------------------------------------------------------- score ----
 void LaunchAddLeafOutputs(const LeafInfo* leaves, const double* leaf_value, int num_leaves, const int* idx0, const int* idx1, float* score, cudaStream_t s);

@@ -105,10 +105,12 @@ __global__ void OvaGradKernel(ObjDesc d, const float* __restrict__ score, const 
 }
 
 // Custom gradients: only the maxima are needed.
-__global__ void AbsMaxKernel(const float* __restrict__ grad, const float* __restrict__ hess, int n, float* __restrict__ maxbuf) {
+__global__ void AbsMaxKernel(const float* __restrict__ grad, const float* __restrict__ hess, int n, float* __restrict__ maxbuf,
+                             const uint8_t* __restrict__ mask) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   const int c = blockIdx.y;
-  float g = i < n ? fabsf(grad[static_cast<size_t>(c) * n + i]) : 0.f, h = i < n ? fabsf(hess[static_cast<size_t>(c) * n + i]) : 0.f;
+  const bool in = i < n && (mask == nullptr || mask[i] != 0);   // out-of-bag rows do not set the scale
+  float g = in ? fabsf(grad[static_cast<size_t>(c) * n + i]) : 0.f, h = in ? fabsf(hess[static_cast<size_t>(c) * n + i]) : 0.f;
   BlockMax2(g, h, maxbuf + 2 * c);
 }
 
@@ -199,7 +201,7 @@ __global__ void LambdarankKernel(const float* __restrict__ score, const float* _
 __global__ void QuantizeKernel(const float* __restrict__ grad, const float* __restrict__ hess, int n, const float* __restrict__ maxbuf,
                                const float* __restrict__ global_max, int bins, int stochastic, uint32_t seed, uint32_t iter_key,
                                unsigned long long global_row_offset, uint8_t* __restrict__ gh_base, int gh_stride, float* __restrict__ scales_out,
-                               long long* __restrict__ root_sums) {
+                               long long* __restrict__ root_sums, const uint8_t* __restrict__ mask) {
   const float* mx = global_max != nullptr ? global_max : maxbuf;
   float gs = mx[0] / static_cast<float>(bins / 2), hs = mx[1] / static_cast<float>(bins);
   if (!(gs > 0.f)) gs = 1.f;
@@ -210,7 +212,7 @@ __global__ void QuantizeKernel(const float* __restrict__ grad, const float* __re
   if (i < n) {
     const int32_t w = QuantizeRow(grad[i], hess[i], ig, ih, stochastic != 0, seed, iter_key, global_row_offset + static_cast<unsigned long long>(i));
     *reinterpret_cast<int32_t*>(gh_base + static_cast<size_t>(i) * gh_stride) = w;
-    sg = UnpackG(w); sh = UnpackH(w);
+    if (mask == nullptr || mask[i] != 0) { sg = UnpackG(w); sh = UnpackH(w); }   // root sums cover the bag only
   }
   for (int o = 16; o > 0; o >>= 1) { sg += __shfl_xor_sync(0xffffffffu, sg, o); sh += __shfl_xor_sync(0xffffffffu, sh, o); }
   __shared__ long long s1[32], s2[32];
@@ -228,10 +230,10 @@ __global__ void QuantizeKernel(const float* __restrict__ grad, const float* __re
 
 // Full precision: interleave (g, h) and produce per-block partial sums (summed later in a fixed order).
 __global__ void InterleaveKernel(const float* __restrict__ grad, const float* __restrict__ hess, int n, float2* __restrict__ gh2,
-                                 double* __restrict__ partial /* 2 per block */) {
+                                 double* __restrict__ partial /* 2 per block */, const uint8_t* __restrict__ mask) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   double sg = 0, sh = 0;
-  if (i < n) { const float g = grad[i], h = hess[i]; gh2[i] = make_float2(g, h); sg = g; sh = h; }
+  if (i < n) { const float g = grad[i], h = hess[i]; gh2[i] = make_float2(g, h); if (mask == nullptr || mask[i] != 0) { sg = g; sh = h; } }
   for (int o = 16; o > 0; o >>= 1) { sg += __shfl_xor_sync(0xffffffffu, sg, o); sh += __shfl_xor_sync(0xffffffffu, sh, o); }
   __shared__ double s1[32], s2[32];
   const int wq = threadIdx.x >> 5, l = threadIdx.x & 31;
@@ -275,26 +277,26 @@ void LaunchObjectiveGradients(const ObjDesc& d, const float* score, const float*
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 
-void LaunchAbsMax(const float* grad, const float* hess, int n, int num_class, float* maxbuf, cudaStream_t s) {
+void LaunchAbsMax(const float* grad, const float* hess, int n, int num_class, float* maxbuf, cudaStream_t s, const uint8_t* mask) {
   FB_CUDA(cudaMemsetAsync(maxbuf, 0, sizeof(float) * 2 * num_class, s));
   if (n <= 0) return;
   const int threads = 256, blocks = (n + threads - 1) / threads;
-  AbsMaxKernel<<<dim3(blocks, num_class), threads, 0, s>>>(grad, hess, n, maxbuf);
+  AbsMaxKernel<<<dim3(blocks, num_class), threads, 0, s>>>(grad, hess, n, maxbuf, mask);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 
 void LaunchQuantize(const float* grad, const float* hess, int n, const float* maxbuf, const float* global_max, int bins, bool stochastic, uint32_t seed,
-                    uint32_t iter_key, uint64_t global_row_offset, uint8_t* gh_base, int gh_stride, float* scales_out, long long* root_sums, cudaStream_t s) {
+                    uint32_t iter_key, uint64_t global_row_offset, uint8_t* gh_base, int gh_stride, float* scales_out, long long* root_sums, cudaStream_t s, const uint8_t* mask) {
   FB_CUDA(cudaMemsetAsync(root_sums, 0, sizeof(long long) * 2, s));
   const int threads = 256, blocks = std::max(1, (n + threads - 1) / threads);
-  QuantizeKernel<<<blocks, threads, 0, s>>>(grad, hess, n, maxbuf, global_max, bins, stochastic ? 1 : 0, seed, iter_key, global_row_offset, gh_base, gh_stride, scales_out, root_sums);
+  QuantizeKernel<<<blocks, threads, 0, s>>>(grad, hess, n, maxbuf, global_max, bins, stochastic ? 1 : 0, seed, iter_key, global_row_offset, gh_base, gh_stride, scales_out, root_sums, mask);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 
-void LaunchInterleave(const float* grad, const float* hess, int n, float2* gh2, double* partial, int partial_capacity, double* root_sums_d, cudaStream_t s) {
+void LaunchInterleave(const float* grad, const float* hess, int n, float2* gh2, double* partial, int partial_capacity, double* root_sums_d, cudaStream_t s, const uint8_t* mask) {
   const int threads = 256, blocks = std::max(1, (n + threads - 1) / threads);
   if (blocks > partial_capacity) Log::Fatal("partial-sum buffer too small");
-  InterleaveKernel<<<blocks, threads, 0, s>>>(grad, hess, n, gh2, partial);
+  InterleaveKernel<<<blocks, threads, 0, s>>>(grad, hess, n, gh2, partial, mask);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
   SumPartialsKernel<<<1, 32, 0, s>>>(partial, blocks, root_sums_d);
   FB_LAUNCHED(); FB_KERNEL_CHECK();

@@ -100,3 +100,29 @@ def test_regression_multiclass_ranking_on_device():
              valid_sets=[fb.Dataset(X, y, group=g)], callbacks=[fb.record_evaluation(res)])
     nd = res["valid_0"]["ndcg@5"]
     assert nd[-1] > nd[0] and nd[-1] > 0.8
+
+
+@pytest.mark.parametrize("extra", [{"bagging_fraction": 0.6}, {"pos_bagging_fraction": 0.5, "neg_bagging_fraction": 0.9}])
+def test_device_bagging_draws_the_host_bag(extra):
+    # same Philox draw on both sides: with exact L2 gradients the first bagged tree is the same digit for digit
+    X, y = make_regression(20000, 12)
+    y = np.round(y * 8) / 8
+    base = {"objective": "none", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "grow_policy": "level", "min_data_in_leaf": 20,
+            "seed": 3, "bagging_freq": 1, **extra}
+    bc = fb.train({**base, "device_type": "cpu"}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
+    bg = fb.train({**base, "device_type": "cuda"}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
+    assert model_body(bc.model_to_string()) == model_body(bg.model_to_string())
+
+
+def test_device_bagging_trains_and_scores_out_of_bag_rows():
+    X, y = make_binary(30000, 20)
+    p = {"objective": "binary", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "device_type": "cuda", "bagging_fraction": 0.5,
+         "bagging_freq": 2, "metric": "binary_logloss"}
+    res = {}
+    ds = fb.Dataset(X[:25000], y[:25000])
+    bst = fb.train(p, ds, 30, valid_sets=[ds], valid_names=["train"], callbacks=[fb.record_evaluation(res)])
+    # the training metric is computed from the device scores of ALL rows: it must agree with a fresh prediction
+    pr = bst.predict(X[:25000])
+    ref = -np.mean(np.where(y[:25000] > 0, np.log(pr), np.log(1 - pr)))
+    assert abs(ref - res["train"]["binary_logloss"][-1]) < 1e-4
+    assert auc(y[25000:], bst.predict(X[25000:])) > 0.9
