@@ -293,22 +293,30 @@ void CPUTreeLearner::ScanCategorical(const LeafState& leaf, int f, const LeafSca
   if (nb > 256) return;
   auto slot = [&](int b) { return m.bundled ? m.hist_offset + (b < m.most_freq_bin ? b : b - 1) : m.hist_offset + b; };
   std::vector<double> g(nb, 0), h(nb, 0);
-  double og = 0, oh = 0;
+  std::vector<int64_t> gi(nb, 0), hi(nb, 0);   // quantized: integer sums ride along so that the children keep exact totals
+  double og = 0, oh = 0; int64_t ogi = 0, ohi = 0;
   for (int b = 0; b < nb; ++b) if (!(m.bundled && b == m.most_freq_bin)) {
-    if (quant_) { g[b] = leaf.hist_i[2 * slot(b)] * L.g_scale; h[b] = leaf.hist_i[2 * slot(b) + 1] * L.h_scale; }
-    else { g[b] = leaf.hist[2 * slot(b)]; h[b] = leaf.hist[2 * slot(b) + 1]; }
-    og += g[b]; oh += h[b];
+    if (quant_) {
+      gi[b] = leaf.hist_i[2 * slot(b)]; hi[b] = leaf.hist_i[2 * slot(b) + 1]; ogi += gi[b]; ohi += hi[b];
+      g[b] = FB_MUL(static_cast<double>(gi[b]), L.g_scale); h[b] = FB_MUL(static_cast<double>(hi[b]), L.h_scale);
+    } else { g[b] = leaf.hist[2 * slot(b)]; h[b] = leaf.hist[2 * slot(b) + 1]; }
+    og = FB_ADD(og, g[b]); oh = FB_ADD(oh, h[b]);
   }
-  if (m.bundled) { g[m.most_freq_bin] = L.sum_g - og; h[m.most_freq_bin] = L.sum_h - oh; }
-  SplitParams p = sp_; p.lambda_l2 += sp_.cat_l2;
+  if (m.bundled) {
+    const int q = m.most_freq_bin;
+    if (quant_) { gi[q] = L.sum_gi - ogi; hi[q] = L.sum_hi - ohi; g[q] = FB_MUL(static_cast<double>(gi[q]), L.g_scale); h[q] = FB_MUL(static_cast<double>(hi[q]), L.h_scale); }
+    else { g[q] = FB_SUB(L.sum_g, og); h[q] = FB_SUB(L.sum_h, oh); }
+  }
+  SplitParams p = sp_; p.lambda_l2 = FB_ADD(p.lambda_l2, sp_.cat_l2);
   SplitRecord cand; InitSplitRecord(&cand);
   double best_gain = -std::numeric_limits<double>::infinity();
-  auto consider = [&](double lg, double lh, int lc, const std::vector<int>& bins_left) {
+  auto consider = [&](double lg, double lh, int64_t lgi, int64_t lhi, int lc, const std::vector<int>& bins_left) {
     double lo, ro;
     double gain = EvalCandidate(lg, lh, lc, L, p, 0, &lo, &ro);
     if (gain > best_gain) {
       best_gain = gain; cand.gain = gain; cand.feature = f; cand.is_categorical = 1; cand.threshold = 0; cand.default_left = 0;
-      cand.left_g = lg; cand.left_h = lh; cand.right_g = L.sum_g - lg; cand.right_h = L.sum_h - lh; cand.left_out = lo; cand.right_out = ro;
+      cand.left_g = lg; cand.left_h = lh; cand.right_g = FB_SUB(L.sum_g, lg); cand.right_h = FB_SUB(L.sum_h, lh); cand.left_out = lo; cand.right_out = ro;
+      cand.left_gi = lgi; cand.left_hi = lhi;
       cand.left_cnt = lc; cand.right_cnt = L.num_data - lc;
       for (int i = 0; i < 8; ++i) cand.cat_bitset[i] = 0;
       for (int b : bins_left) cand.cat_bitset[b >> 5] |= (1u << (b & 31));
@@ -318,28 +326,29 @@ void CPUTreeLearner::ScanCategorical(const LeafState& leaf, int f, const LeafSca
   if (nb <= sp_.max_cat_to_onehot) {
     for (int b = 1; b < nb; ++b) {   // bin 0 (NaN / other) always goes right
       int c = BinCountEstimate(h[b], L.cnt_factor);
-      consider(g[b], h[b], c, {b});
+      consider(g[b], h[b], gi[b], hi[b], c, {b});
     }
   } else {
     std::vector<int> cats;
     for (int b = 1; b < nb; ++b) if (BinCountEstimate(h[b], L.cnt_factor) >= sp_.cat_smooth) cats.push_back(b);
-    auto ratio = [&](int b) { return g[b] / (h[b] + sp_.cat_smooth); };
+    auto ratio = [&](int b) { return FB_DIV(g[b], FB_ADD(h[b], sp_.cat_smooth)); };
     std::stable_sort(cats.begin(), cats.end(), [&](int a, int b) { return ratio(a) < ratio(b); });
     const int used = static_cast<int>(cats.size());
     const int max_num = std::min(sp_.max_cat_threshold, (used + 1) / 2);
     for (int dir = 0; dir < 2; ++dir) {
-      double lg = 0, lh = 0; int lc = 0, grp = 0; std::vector<int> left;
+      double lg = 0, lh = 0; int64_t lgi = 0, lhi = 0; int lc = 0, grp = 0; std::vector<int> left;
       for (int k = 0; k < used && k < max_num; ++k) {
         int b = dir == 0 ? cats[k] : cats[used - 1 - k];
-        lg += g[b]; lh += h[b]; int c = BinCountEstimate(h[b], L.cnt_factor); lc += c; grp += c; left.push_back(b);
+        lg = FB_ADD(lg, g[b]); lh = FB_ADD(lh, h[b]); lgi += gi[b]; lhi += hi[b];
+        int c = BinCountEstimate(h[b], L.cnt_factor); lc += c; grp += c; left.push_back(b);
         if (grp < sp_.min_data_per_group) continue;
         grp = 0;
-        consider(lg, lh, lc, left);
+        consider(lg, lh, lgi, lhi, lc, left);
       }
     }
   }
   if (cand.feature >= 0) {
-    cand.gain *= m.penalty;
+    cand.gain = FB_MUL(cand.gain, static_cast<double>(m.penalty));
     if (SplitBetter(cand.gain, m.real_index, 0, best->gain, best->feature >= 0 ? ds_->feature_meta[best->feature].real_index : -1, best->threshold)) *best = cand;
   }
 }

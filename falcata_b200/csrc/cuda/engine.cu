@@ -61,7 +61,6 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   sp_.min_data_per_group = cfg.min_data_per_group; sp_.cat_l2 = cfg.cat_l2; sp_.cat_smooth = cfg.cat_smooth; sp_.extra_trees = 0;
   if (cfg.extra_trees) Log::Warning("extra_trees is evaluated by the host learner only; the device learner searches all thresholds");
   if (cfg.grow_policy == "leaf") Log::Warning("grow_policy=leaf runs on the host learner; the device learner grows level-wise with a gain-ranked leaf budget");
-  for (int f = 0; f < train->num_features; ++f) if (train->feature_meta[f].bin_type != 0) { Log::Warning("Categorical features are searched by the host learner only; the device learner skips them"); break; }
   col_sampler_.Init(cfg, train);
   clock_.enabled = getenv("FALCATA_STAGE_TIMING") != nullptr;
   st_grad_ = clock_.Stage("gradients"); st_quant_ = clock_.Stage("quantize+root"); st_hist_ = clock_.Stage("histogram");
@@ -237,13 +236,18 @@ void CudaEngine::AddValid(const Dataset* valid) {
 
 void CudaEngine::UploadTreeForTraversal(const Tree& tree, const Dataset* ds, DevTree* out) {
   const int ni = std::max(1, tree.num_leaves - 1), nl = tree.num_leaves;
-  std::vector<int> ints(static_cast<size_t>(ni) * 11, 0); std::vector<float> fl(nl); std::vector<signed char> dec(ni, 0);
+  std::vector<int> ints(static_cast<size_t>(ni) * 19 /* 11 per-node arrays + 8 words of categorical bins per node */, 0); std::vector<float> fl(nl); std::vector<signed char> dec(ni, 0);
   int* left = ints.data(); int* right = left + ni; int* sf = right + ni; int* sg = sf + ni; int* tb = sg + ni; int* db = tb + ni; int* nanb = db + ni;
   int* bun = nanb + ni; int* goff = bun + ni; int* mfb = goff + ni; int* nbin = mfb + ni;
   for (int s = 0; s < tree.num_leaves - 1; ++s) {
     const int f = tree.split_feature_inner[s]; const FeatureMeta& m = ds->feature_meta[f];
     left[s] = tree.left_child[s]; right[s] = tree.right_child[s]; sf[s] = f; sg[s] = m.group; tb[s] = static_cast<int>(tree.threshold_in_bin[s]);
     db[s] = m.default_bin; nanb[s] = m.num_bin - 1; bun[s] = m.bundled; goff[s] = m.group_offset; mfb[s] = m.most_freq_bin; nbin[s] = m.num_bin; dec[s] = tree.decision_type[s];
+    if (tree.decision_type[s] & kCategoricalMask) {
+      const int ci = static_cast<int>(tree.threshold_in_bin[s]);
+      const int lo = tree.cat_boundaries_inner[ci], nw = std::min(8, tree.cat_boundaries_inner[ci + 1] - lo);
+      for (int w = 0; w < nw; ++w) ints[static_cast<size_t>(ni) * 11 + static_cast<size_t>(s) * 8 + w] = static_cast<int>(tree.cat_threshold_inner[lo + w]);
+    }
   }
   for (int l = 0; l < nl; ++l) fl[l] = static_cast<float>(tree.leaf_value[l]);
   FB_CUDA(cudaStreamSynchronize(stream_));   // staging buffers are reused: the previous traversal must be done
@@ -252,6 +256,7 @@ void CudaEngine::UploadTreeForTraversal(const Tree& tree, const Dataset* ds, Dev
   const int* d = tree_ints_.get();
   out->num_leaves = nl; out->left = d; out->right = d + ni; out->split_feature = d + 2 * ni; out->split_group = d + 3 * ni; out->threshold_bin = d + 4 * ni;
   out->default_bin = d + 5 * ni; out->nan_bin = d + 6 * ni; out->bundled = d + 7 * ni; out->group_offset = d + 8 * ni; out->most_freq_bin = d + 9 * ni; out->num_bin = d + 10 * ni;
+  out->cat_bits = reinterpret_cast<const unsigned int*>(d + 11 * ni);
   out->threshold = nullptr; out->decision = tree_dec_.get(); out->leaf_value = tree_floats_.get();
 }
 

@@ -29,6 +29,26 @@ __global__ void InitRootKernel(LeafInfo* leaves, const long long* sums_i, const 
   leaves[0] = L;
 }
 
+// One split of the device's record applied to the host tree (numerical threshold or categorical set).
+int ApplySplit(Tree* tree, const Dataset* ds, int leaf, const SplitRecord& b) {
+  const FeatureMeta& m = ds->feature_meta[b.feature];
+  const BinMapper& bm = *ds->mappers[m.real_index];
+  if (!b.is_categorical)
+    return tree->Split(leaf, b.feature, m.real_index, static_cast<uint32_t>(b.threshold), bm.BinToValue(b.threshold), b.left_out, b.right_out,
+                       b.left_cnt, b.right_cnt, b.left_h, b.right_h, static_cast<float>(b.gain), m.missing_type, b.default_left != 0);
+  std::vector<uint32_t> inner(b.cat_bitset, b.cat_bitset + 8);
+  while (inner.size() > 1 && inner.back() == 0) inner.pop_back();
+  std::vector<uint32_t> real;
+  for (int bin = 0; bin < m.num_bin; ++bin) if ((b.cat_bitset[bin >> 5] >> (bin & 31)) & 1) {
+    const int cat = bm.bin_2_categorical[bin]; if (cat < 0) continue;
+    if (static_cast<int>(real.size()) <= (cat >> 5)) real.resize((cat >> 5) + 1, 0);
+    real[cat >> 5] |= (1u << (cat & 31));
+  }
+  if (real.empty()) real.push_back(0);
+  return tree->SplitCategorical(leaf, b.feature, m.real_index, inner.data(), static_cast<int>(inner.size()), real.data(), static_cast<int>(real.size()),
+                                b.left_out, b.right_out, b.left_cnt, b.right_cnt, b.left_h, b.right_h, static_cast<float>(b.gain), m.missing_type);
+}
+
 }  // namespace
 
 void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess, int iter, double shrinkage, const std::vector<double>& init_scores,
@@ -96,7 +116,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   col_sampler_.ResetByTree(tree_index);
   // features searched on this rank this tree (owned, sampled, numerical) and the rest of the owned ones
   std::vector<int> feats, subs;
-  for (int f : owned_features_) { if (col_sampler_.used_by_tree()[f] && train_->feature_meta[f].bin_type == 0) feats.push_back(f); else subs.push_back(f); }
+  for (int f : owned_features_) { if (col_sampler_.used_by_tree()[f]) feats.push_back(f); else subs.push_back(f); }
   features_.Upload(feats, stream_); sub_features_.Upload(subs, stream_);
   const int NF = static_cast<int>(feats.size()), NS = static_cast<int>(subs.size());
 
@@ -138,6 +158,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   fa.features = features_.get(); fa.num_features = NF; fa.sub_features = sub_features_.get(); fa.num_sub_features = NS; fa.meta = dd_->feature_meta.get();
   fa.bin_local = bin_local_.get(); fa.pool = pool_base_; fa.slot_stride = slot_stride_; fa.leaves = leaves_.get(); fa.scales = scales_.get(); fa.params = sp_;
   fa.cand = cand_.get(); fa.best = best_.get(); fa.quant = quant_ ? 1 : 0;
+  fa.has_categorical = 0; for (int f : feats) if (train_->feature_meta[f].bin_type != 0) fa.has_categorical = 1;
   fa.wait.world = world_; fa.wait_best.world = world_; fa.sig.world = world_; fa.leaves_rw = leaves_.get();
   if (world_ > 1) {
     const FabricView v = fabric_->View();
@@ -229,10 +250,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     for (int j = 0; j < hc.journal_count; ++j) {
       const SplitJournal& sj = h_journal_[j];
       const SplitRecord& b = sj.rec;
-      const FeatureMeta& m = train_->feature_meta[b.feature];
-      const BinMapper& bm = *train_->mappers[m.real_index];
-      const int right = tree->Split(sj.leaf, b.feature, m.real_index, static_cast<uint32_t>(b.threshold), bm.BinToValue(b.threshold), b.left_out, b.right_out,
-                                    b.left_cnt, b.right_cnt, b.left_h, b.right_h, static_cast<float>(b.gain), m.missing_type, b.default_left != 0);
+      const int right = ApplySplit(tree.get(), train_, sj.leaf, b);
       tree->internal_count[tree->num_leaves - 2] = sj.parent_global;
       if (right != sj.right_leaf) Log::Fatal("Device journal out of order (split %d)", j);
     }
@@ -274,16 +292,14 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
       HostLeaf& P = host_leaves_[l];
       const SplitRecord& b = P.best;
       const FeatureMeta& m = train_->feature_meta[b.feature];
-      const BinMapper& bm = *train_->mappers[m.real_index];
       const LeafInfo& PL = h_leaves_[l];
-      const int right = tree->Split(l, b.feature, m.real_index, static_cast<uint32_t>(b.threshold), bm.BinToValue(b.threshold), b.left_out, b.right_out,
-                                    b.left_cnt, b.right_cnt, b.left_h, b.right_h, static_cast<float>(b.gain), m.missing_type, b.default_left != 0);
+      const int right = ApplySplit(tree.get(), train_, l, b);
       tree->internal_count[tree->num_leaves - 2] = PL.num_data_global;
       PartSplit& q = ps[s];
       memset(&q, 0, sizeof(q));
       q.leaf = l; q.right_leaf = right; q.begin = P.begin; q.count = P.count; q.buffer = P.buffer; q.group = m.group; q.bundled = m.bundled; q.group_offset = m.group_offset;
       q.num_bin = m.num_bin; q.most_freq_bin = m.most_freq_bin; q.threshold = b.threshold; q.default_left = b.default_left; q.missing_type = m.missing_type;
-      q.default_bin = m.default_bin; q.is_categorical = 0;
+      q.default_bin = m.default_bin; q.is_categorical = b.is_categorical; for (int w = 0; w < 8; ++w) q.cat_bitset[w] = b.cat_bitset[w];
       q.chunk_begin = chunk_cursor; q.num_chunks = (P.count + kPartChunk - 1) / kPartChunk; chunk_cursor += q.num_chunks;
       ChildInit& c = ci[s];
       memset(&c, 0, sizeof(c));

@@ -82,6 +82,7 @@ struct FindChild { int leaf; int slot; int other_slot; int is_larger; int split;
 struct CandLite {      // best threshold of one (child, feature)
   double gain; int feature; int threshold; int default_left; int left_cnt;
   long long left_gi, left_hi; double left_g, left_h;
+  int is_categorical, num_cat_bins; uint32_t cat_bitset[8];   // categorical: the bins that go left
 };
 
 struct FindArgs {
@@ -97,6 +98,7 @@ struct FindArgs {
   CandLite* cand;                                 // [num_children x num_features]
   SplitRecord* best;                              // [leaf]
   int quant;
+  int has_categorical;                            // some searched feature is categorical: the kernel gets its shared scratch
   // ---- multi-rank (world > 1) ----
   FabricWait wait;                                // construct-done flags of all ranks (the reduce-scatter is complete when they are up)
   const void* stage; int stage_cap;               // this rank's staging area [source rank][stage_cap][slot_stride] written by the ranks' constructs
@@ -176,14 +178,17 @@ struct DevTree {
   const int* left; const int* right; const int* split_feature; const int* split_group;
   const float* threshold; const int* threshold_bin; const signed char* decision; const float* leaf_value;
   const int* default_bin; const int* nan_bin; const int* bundled; const int* group_offset; const int* most_freq_bin; const int* num_bin;
+  const unsigned int* cat_bits;   // [internal nodes][8]: bins that go left at a categorical node (decision bit 0)
 };
 // score[i] += scale * tree(row i) on binned rows (validation sets, out-of-bag rows, rollback)
 void LaunchAddTreeBinned(const DevTree& t, const uint8_t* rows, int row_stride, int n, float scale, float* score, cudaStream_t s);
 
 // Packed forest for raw-feature prediction: nodes of all trees in one array.
-struct ForestNode { float threshold; int feature; int left; int right; int flags; };   // flags: bit0 default_left, bits1-2 missing type, bit3 leaf; leaf: threshold = value
+// flags: bit0 default_left, bits1-2 missing type, bit3 leaf (threshold = value), bit4 categorical (threshold holds,
+// as an int, the offset of the node's category bitset in the forest's word array; bits 8.. = number of words)
+struct ForestNode { float threshold; int feature; int left; int right; int flags; };
 template <typename T>
-void LaunchPredictRaw(const ForestNode* nodes, const int* tree_root, int num_trees, int num_class, const T* data, int nrow, int ncol, bool row_major,
+void LaunchPredictRaw(const ForestNode* nodes, const unsigned int* cat_words, const int* tree_root, int num_trees, int num_class, const T* data, int nrow, int ncol, bool row_major,
                       float* out /* [num_class x nrow] */, bool average, cudaStream_t s);
 void LaunchConvertOutput(int obj_kind, double sigmoid, float* out, int nrow, int num_class, cudaStream_t s);
 

@@ -1,6 +1,6 @@
 // K7 driver: pack the host trees into one node array and run the raw-feature traversal kernel.
 // Parity: python-package/falcata/basic.py:L5067-5163 (device predict route), include/Falcata/tree.h:L361-439
-// (decision semantics). Categorical splits are not packed: models that contain them predict on the host.
+// (decision semantics). Categorical nodes carry an offset into one word array with all nodes' category sets.
 #include "engine.h"
 
 #include <cuda_fp16.h>
@@ -16,10 +16,10 @@ void DevicePredict(const GBDT* gbdt, const void* device_data, int dtype, int32_t
   start_iter = std::max(0, std::min(start_iter, iters));
   const int use = num_iter > 0 ? std::min(num_iter, iters - start_iter) : iters - start_iter;
   if (ncol <= gbdt->max_feature_idx_) Log::Fatal("The number of features in data (%d) is not the same as it was in training data (%d)", ncol, gbdt->max_feature_idx_ + 1);
-  std::vector<ForestNode> nodes; std::vector<int> roots;
+  std::vector<ForestNode> nodes; std::vector<int> roots; std::vector<unsigned int> cat_words(1, 0u);
   for (int t = start_iter * K; t < (start_iter + use) * K; ++t) {
     const Tree& T = *gbdt->models_[t];
-    if (T.num_cat > 0 || T.is_linear) Log::Fatal("Device prediction does not cover categorical splits or linear leaves; predict on the host");
+    if (T.is_linear) Log::Fatal("Device prediction does not cover linear leaves; predict on the host");
     const int base = static_cast<int>(nodes.size());
     roots.push_back(base);
     const int ni = T.num_leaves - 1;
@@ -32,20 +32,28 @@ void DevicePredict(const GBDT* gbdt, const void* device_data, int dtype, int32_t
       nd.left = T.left_child[s] >= 0 ? base + T.left_child[s] : base + ni + (~T.left_child[s]);
       nd.right = T.right_child[s] >= 0 ? base + T.right_child[s] : base + ni + (~T.right_child[s]);
       nd.flags = ((T.decision_type[s] & kDefaultLeftMask) ? 1 : 0) | (Tree::MissingTypeOf(T.decision_type[s]) << 1);
+      if (T.decision_type[s] & kCategoricalMask) {
+        const int ci = static_cast<int>(T.threshold[s]);
+        const int lo = T.cat_boundaries[ci], nw = T.cat_boundaries[ci + 1] - lo;
+        const int off = static_cast<int>(cat_words.size());
+        for (int w = 0; w < nw; ++w) cat_words.push_back(T.cat_threshold[lo + w]);
+        memcpy(&nd.threshold, &off, sizeof(int));
+        nd.flags |= 16 | (nw << 8);
+      }
       nodes.push_back(nd);
     }
     for (int l = 0; l < T.num_leaves; ++l) { ForestNode nd; nd.threshold = static_cast<float>(T.leaf_value[l]); nd.feature = 0; nd.left = nd.right = 0; nd.flags = 8; nodes.push_back(nd); }
     if (ni == 0) roots.back() = base;   // single leaf: the root is the leaf itself
   }
   cudaStream_t s = 0;
-  DevBuf<ForestNode> d_nodes; DevBuf<int> d_roots;
-  d_nodes.Upload(nodes, s); d_roots.Upload(roots, s);
+  DevBuf<ForestNode> d_nodes; DevBuf<int> d_roots; DevBuf<unsigned int> d_cat;
+  d_nodes.Upload(nodes, s); d_roots.Upload(roots, s); d_cat.Upload(cat_words, s);
   const int nt = static_cast<int>(roots.size());
   if (nt == 0) { FB_CUDA(cudaMemsetAsync(out_device, 0, sizeof(float) * static_cast<size_t>(nrow) * K, s)); FB_CUDA(cudaStreamSynchronize(s)); return; }
   switch (dtype) {
-    case kF32: LaunchPredictRaw<float>(d_nodes.get(), d_roots.get(), nt, K, static_cast<const float*>(device_data), nrow, ncol, row_major, out_device, gbdt->average_output_, s); break;
-    case kF64: LaunchPredictRaw<double>(d_nodes.get(), d_roots.get(), nt, K, static_cast<const double*>(device_data), nrow, ncol, row_major, out_device, gbdt->average_output_, s); break;
-    case kF16: LaunchPredictRaw<__half>(d_nodes.get(), d_roots.get(), nt, K, static_cast<const __half*>(device_data), nrow, ncol, row_major, out_device, gbdt->average_output_, s); break;
+    case kF32: LaunchPredictRaw<float>(d_nodes.get(), d_cat.get(), d_roots.get(), nt, K, static_cast<const float*>(device_data), nrow, ncol, row_major, out_device, gbdt->average_output_, s); break;
+    case kF64: LaunchPredictRaw<double>(d_nodes.get(), d_cat.get(), d_roots.get(), nt, K, static_cast<const double*>(device_data), nrow, ncol, row_major, out_device, gbdt->average_output_, s); break;
+    case kF16: LaunchPredictRaw<__half>(d_nodes.get(), d_cat.get(), d_roots.get(), nt, K, static_cast<const __half*>(device_data), nrow, ncol, row_major, out_device, gbdt->average_output_, s); break;
     default: Log::Fatal("Device prediction takes f32, f64 or f16 input");
   }
   if (predict_type == 0 && gbdt->objective_ != nullptr) {

@@ -38,7 +38,8 @@ __global__ void AddTreeBinnedKernel(DevTree t, const uint8_t* __restrict__ rows,
     }
     const int dt = t.decision[node], mt = (dt >> 2) & 3;
     bool left;
-    if ((mt == 1 && fb == t.default_bin[node]) || (mt == 2 && fb == t.nan_bin[node])) left = (dt & 2) != 0;
+    if (dt & 1) left = (t.cat_bits[node * 8 + ((fb >> 5) & 7)] >> (fb & 31)) & 1;   // categorical: set of bins
+    else if ((mt == 1 && fb == t.default_bin[node]) || (mt == 2 && fb == t.nan_bin[node])) left = (dt & 2) != 0;
     else left = fb <= t.threshold_bin[node];
     node = left ? t.left[node] : t.right[node];
   }
@@ -51,7 +52,7 @@ template <> __device__ inline float LoadF<__half>(const __half* p, size_t i) { r
 // One thread per row; the packed forest is read through L1/L2 (all rows walk the same trees, so the
 // nodes stay cache-resident) and the row's features are re-read from its own cache lines.
 template <typename T>
-__global__ void PredictRawKernel(const ForestNode* __restrict__ nodes, const int* __restrict__ tree_root, int num_trees, int num_class,
+__global__ void PredictRawKernel(const ForestNode* __restrict__ nodes, const unsigned int* __restrict__ cat_words, const int* __restrict__ tree_root, int num_trees, int num_class,
                                  const T* __restrict__ data, int nrow, int ncol, bool row_major, float* __restrict__ out, float inv_avg) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= nrow) return;
@@ -64,6 +65,18 @@ __global__ void PredictRawKernel(const ForestNode* __restrict__ nodes, const int
         float v = LoadF<T>(data, row_major ? static_cast<size_t>(i) * ncol + nd.feature : static_cast<size_t>(nd.feature) * nrow + i);
         const int mt = (nd.flags >> 1) & 3;
         bool left;
+        if (nd.flags & 16) {
+          // categorical: left iff the (integer) category is in the node's set; NaN and negatives go right
+          left = false;
+          if (!isnan(v)) {
+            const int iv = static_cast<int>(v);
+            const int off = __float_as_int(nd.threshold), nw = nd.flags >> 8;
+            if (iv >= 0 && (iv >> 5) < nw) left = (cat_words[off + (iv >> 5)] >> (iv & 31)) & 1;
+          }
+          n = left ? nd.left : nd.right;
+          nd = nodes[n];
+          continue;
+        }
         if (isnan(v) && mt != 2) v = 0.f;
         if ((mt == 1 && fabsf(v) <= 1e-35f) || (mt == 2 && isnan(v))) left = nd.flags & 1;
         else left = v <= nd.threshold;
@@ -159,17 +172,17 @@ void LaunchAddTreeBinned(const DevTree& t, const uint8_t* rows, int row_stride, 
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 template <typename T>
-void LaunchPredictRaw(const ForestNode* nodes, const int* tree_root, int num_trees, int num_class, const T* data, int nrow, int ncol, bool row_major,
+void LaunchPredictRaw(const ForestNode* nodes, const unsigned int* cat_words, const int* tree_root, int num_trees, int num_class, const T* data, int nrow, int ncol, bool row_major,
                       float* out, bool average, cudaStream_t s) {
   if (nrow <= 0) return;
   const int iters = num_trees / std::max(1, num_class);
   const float inv = (average && iters > 0) ? 1.f / iters : 1.f;
-  PredictRawKernel<T><<<(nrow + 127) / 128, 128, 0, s>>>(nodes, tree_root, num_trees, num_class, data, nrow, ncol, row_major, out, inv);
+  PredictRawKernel<T><<<(nrow + 127) / 128, 128, 0, s>>>(nodes, cat_words, tree_root, num_trees, num_class, data, nrow, ncol, row_major, out, inv);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
-template void LaunchPredictRaw<float>(const ForestNode*, const int*, int, int, const float*, int, int, bool, float*, bool, cudaStream_t);
-template void LaunchPredictRaw<double>(const ForestNode*, const int*, int, int, const double*, int, int, bool, float*, bool, cudaStream_t);
-template void LaunchPredictRaw<__half>(const ForestNode*, const int*, int, int, const __half*, int, int, bool, float*, bool, cudaStream_t);
+template void LaunchPredictRaw<float>(const ForestNode*, const unsigned int*, const int*, int, int, const float*, int, int, bool, float*, bool, cudaStream_t);
+template void LaunchPredictRaw<double>(const ForestNode*, const unsigned int*, const int*, int, int, const double*, int, int, bool, float*, bool, cudaStream_t);
+template void LaunchPredictRaw<__half>(const ForestNode*, const unsigned int*, const int*, int, int, const __half*, int, int, bool, float*, bool, cudaStream_t);
 
 void LaunchConvertOutput(int obj_kind, double sigmoid, float* out, int nrow, int num_class, cudaStream_t s) {
   if (nrow <= 0) return;

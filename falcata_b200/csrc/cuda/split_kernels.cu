@@ -64,6 +64,111 @@ __device__ inline int ChildGlobalCount(const FindArgs& a, const FindChild& ch, i
   return ch.is_left ? lsum : ch.parent_global - lsum;
 }
 
+// Categorical search of one (child, feature) by one warp. The bins are staged in shared memory (and
+// written back where the child's histogram is formed on the fly); the sort by g / (h + cat_smooth) is a
+// rank count over all lanes (stable: ties keep bin order); the two directional scans run on lane 0 in
+// the host learner's order, operation for operation, so both produce the same record.
+// Parity: src/treelearner/cuda/cuda_best_split_finder.cu (categorical kernels), feature_histogram.hpp:L278-520.
+constexpr int kCatMaxBins = 256;
+struct CatScratch { double g[kCatMaxBins], h[kCatMaxBins]; long long gi[kCatMaxBins], hi[kCatMaxBins]; unsigned char order[kCatMaxBins]; };
+
+template <bool QUANT>
+__device__ void ScanCategoricalWarp(const FindArgs& a, const BinSrc& src, char* child, bool write_back, const FeatureMeta& m, const LeafInfo& leaf, int f, int fi,
+                                    int lane, int warp) {
+  extern __shared__ __align__(16) unsigned char find_smem[];
+  CatScratch& S = reinterpret_cast<CatScratch*>(find_smem)[warp];
+  const int nb = m.num_bin;
+  const int nstored = m.bundled ? nb - 1 : nb;
+  const int mfb = m.bundled ? m.most_freq_bin : -1;
+  const double g_scale = QUANT ? static_cast<double>(a.scales[0]) : 1.0, h_scale = QUANT ? static_cast<double>(a.scales[1]) : 1.0;
+  for (int b = lane; b < nb; b += 32) {
+    if (b == mfb) continue;
+    const int j = (mfb >= 0 && b > mfb) ? b - 1 : b;
+    long long gi = 0, hi = 0; double gd = 0, hd = 0; hist_q_t rq; double2 rd;
+    LoadBin<QUANT>(src, j, &gi, &hi, &gd, &hd, &rq, &rd);
+    if (write_back) { if (QUANT) reinterpret_cast<hist_q_t*>(child)[j] = rq; else reinterpret_cast<double2*>(child)[j] = rd; }
+    S.gi[b] = gi; S.hi[b] = hi;
+    S.g[b] = QUANT ? FB_MUL(static_cast<double>(gi), g_scale) : gd; S.h[b] = QUANT ? FB_MUL(static_cast<double>(hi), h_scale) : hd;
+  }
+  (void)nstored;
+  __syncwarp();
+  LeafScanInfo L;
+  L.sum_g = leaf.sum_g; L.sum_h = leaf.sum_h; L.sum_gi = leaf.sum_gi; L.sum_hi = leaf.sum_hi; L.num_data = leaf.num_data_global;
+  L.parent_output = leaf.output; L.g_scale = g_scale; L.h_scale = h_scale;
+  L.cnt_factor = FB_DIV(static_cast<double>(L.num_data), L.sum_h);
+  if (a.params.max_delta_step <= 0.0 && a.params.path_smooth <= 0.0)
+    L.min_gain_shift = FB_ADD(LeafGain(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), a.params, L.num_data, leaf.output), a.params.min_gain_to_split);
+  else
+    L.min_gain_shift = FB_ADD(LeafGainGivenOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), a.params, leaf.output), a.params.min_gain_to_split);
+  if (mfb >= 0 && lane == 0) {
+    // the un-stored most-frequent bin: leaf total minus the stored bins, summed in bin order like the host
+    double og = 0, oh = 0; long long ogi = 0, ohi = 0;
+    for (int b = 0; b < nb; ++b) if (b != mfb) { og = FB_ADD(og, S.g[b]); oh = FB_ADD(oh, S.h[b]); ogi += S.gi[b]; ohi += S.hi[b]; }
+    if (QUANT) { S.gi[mfb] = L.sum_gi - ogi; S.hi[mfb] = L.sum_hi - ohi; S.g[mfb] = FB_MUL(static_cast<double>(S.gi[mfb]), g_scale); S.h[mfb] = FB_MUL(static_cast<double>(S.hi[mfb]), h_scale); }
+    else { S.gi[mfb] = S.hi[mfb] = 0; S.g[mfb] = FB_SUB(L.sum_g, og); S.h[mfb] = FB_SUB(L.sum_h, oh); }
+  }
+  __syncwarp();
+  SplitParams p = a.params; p.lambda_l2 = FB_ADD(p.lambda_l2, a.params.cat_l2);
+  const bool onehot = nb <= a.params.max_cat_to_onehot;
+  int used = 0;
+  if (!onehot) {
+    // eligible categories in bin order, then their stable rank by ratio
+    // (eligibility and the count of earlier eligible bins are cheap enough to recompute per lane)
+    for (int b = 1 + lane; b < nb; b += 32) {
+      const bool ok = static_cast<double>(BinCountEstimate(S.h[b], L.cnt_factor)) >= a.params.cat_smooth;
+      if (!ok) continue;
+      const double rb = FB_DIV(S.g[b], FB_ADD(S.h[b], a.params.cat_smooth));
+      int rank = 0;
+      for (int o = 1; o < nb; ++o) {
+        if (o == b) continue;
+        if (!(static_cast<double>(BinCountEstimate(S.h[o], L.cnt_factor)) >= a.params.cat_smooth)) continue;
+        const double ro = FB_DIV(S.g[o], FB_ADD(S.h[o], a.params.cat_smooth));
+        if (ro < rb || (!(rb < ro) && o < b)) ++rank;   // stable: equal (or unordered) ratios keep bin order
+      }
+      S.order[rank] = static_cast<unsigned char>(b);
+    }
+    int cnt = 0;
+    for (int b = 1 + lane; b < nb; b += 32) cnt += static_cast<double>(BinCountEstimate(S.h[b], L.cnt_factor)) >= a.params.cat_smooth ? 1 : 0;
+    for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+    used = cnt;
+  }
+  __syncwarp();
+  if (lane != 0) return;
+  CandLite c; c.gain = -1.0 / 0.0; c.feature = -1; c.threshold = 0; c.default_left = 0; c.left_cnt = 0; c.left_gi = c.left_hi = 0; c.left_g = c.left_h = 0;
+  c.is_categorical = 1; c.num_cat_bins = 0; for (int w = 0; w < 8; ++w) c.cat_bitset[w] = 0;
+  double best_gain = -1.0 / 0.0; int best_dir = -1, best_k = -1;
+  if (onehot) {
+    for (int b = 1; b < nb; ++b) {
+      double lo, ro;
+      const int lc = BinCountEstimate(S.h[b], L.cnt_factor);
+      const double gain = EvalCandidate(S.g[b], S.h[b], lc, L, p, 0, &lo, &ro);
+      if (gain > best_gain) { best_gain = gain; best_k = b; c.left_g = S.g[b]; c.left_h = S.h[b]; c.left_gi = S.gi[b]; c.left_hi = S.hi[b]; c.left_cnt = lc; }
+    }
+    if (best_k >= 0) { c.cat_bitset[best_k >> 5] |= 1u << (best_k & 31); c.num_cat_bins = 1; }
+  } else {
+    const int max_num = min(a.params.max_cat_threshold, (used + 1) / 2);
+    for (int dir = 0; dir < 2; ++dir) {
+      double lg = 0, lh = 0; long long lgi = 0, lhi = 0; int lc = 0, grp = 0;
+      for (int k = 0; k < used && k < max_num; ++k) {
+        const int b = dir == 0 ? S.order[k] : S.order[used - 1 - k];
+        lg = FB_ADD(lg, S.g[b]); lh = FB_ADD(lh, S.h[b]); lgi += S.gi[b]; lhi += S.hi[b];
+        const int cb = BinCountEstimate(S.h[b], L.cnt_factor); lc += cb; grp += cb;
+        if (grp < a.params.min_data_per_group) continue;
+        grp = 0;
+        double lo, ro;
+        const double gain = EvalCandidate(lg, lh, lc, L, p, 0, &lo, &ro);
+        if (gain > best_gain) { best_gain = gain; best_dir = dir; best_k = k; c.left_g = lg; c.left_h = lh; c.left_gi = lgi; c.left_hi = lhi; c.left_cnt = lc; }
+      }
+    }
+    if (best_k >= 0) {
+      for (int k = 0; k <= best_k; ++k) { const int b = best_dir == 0 ? S.order[k] : S.order[used - 1 - k]; c.cat_bitset[b >> 5] |= 1u << (b & 31); }
+      c.num_cat_bins = best_k + 1;
+    }
+  }
+  if (best_k >= 0 && best_gain != -1.0 / 0.0) { c.gain = FB_MUL(best_gain, static_cast<double>(m.penalty)); c.feature = f; }
+  a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + fi] = c;
+}
+
 template <bool QUANT>
 __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
   if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) return;
@@ -92,14 +197,17 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
   src.rank_stride = static_cast<long long>(a.stage_cap) * a.slot_stride;
   src.stage = world > 1 ? static_cast<const char*>(a.stage) + (static_cast<long long>(ch.task) * a.slot_stride + base) * esz : nullptr;
 
-  if (!search || m.bin_type != 0) {
-    // materialisation only (feature not sampled for this tree, or categorical: searched on the host path)
+  if (search && m.bin_type != 0) {
+    ScanCategoricalWarp<QUANT>(a, src, child, write_back, m, leaf, f, fi, lane, warp);
+    return;
+  }
+  if (!search) {
+    // materialisation only (feature not sampled for this tree)
     if (write_back) for (int j = lane; j < nstored; j += 32) {
       long long gi, hi; double gd, hd; hist_q_t rq; double2 rd;
       LoadBin<QUANT>(src, j, &gi, &hi, &gd, &hd, &rq, &rd);
       if (QUANT) reinterpret_cast<hist_q_t*>(child)[j] = rq; else reinterpret_cast<double2*>(child)[j] = rd;
     }
-    if (search && lane == 0) { CandLite c; c.gain = -1.0 / 0.0; c.feature = -1; c.threshold = 0; c.default_left = 1; c.left_cnt = 0; c.left_gi = c.left_hi = 0; c.left_g = c.left_h = 0; a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + fi] = c; }
     return;
   }
 
@@ -201,6 +309,7 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
     c.gain = ok ? FB_MUL(best_gain, static_cast<double>(m.penalty)) : best_gain;
     c.feature = ok ? f : -1; c.threshold = best_t; c.default_left = best_pass == 0 ? 1 : 0; c.left_cnt = best_lc;
     c.left_gi = best_lgi; c.left_hi = best_lhi; c.left_g = best_lg; c.left_h = best_lh;
+    c.is_categorical = 0; c.num_cat_bins = 0; for (int w = 0; w < 8; ++w) c.cat_bitset[w] = 0;
     a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + fi] = c;
   }
 }
@@ -235,9 +344,11 @@ __global__ void ReduceBestKernel(FindArgs a) {
       r.gain = c.gain; r.feature = c.feature; r.threshold = c.threshold; r.default_left = c.default_left;
       r.left_g = c.left_g; r.left_h = c.left_h; r.right_g = FB_SUB(leaf.sum_g, c.left_g); r.right_h = FB_SUB(leaf.sum_h, c.left_h);
       r.left_gi = c.left_gi; r.left_hi = c.left_hi; r.left_cnt = c.left_cnt; r.right_cnt = leaf.num_data_global - c.left_cnt;
-      r.monotone = a.meta[c.feature].monotone;
-      r.left_out = LeafOutput(r.left_g, FB_ADD(r.left_h, kEpsilon), a.params, r.left_cnt, leaf.output);
-      r.right_out = LeafOutput(r.right_g, FB_ADD(r.right_h, kEpsilon), a.params, r.right_cnt, leaf.output);
+      r.monotone = c.is_categorical ? 0 : a.meta[c.feature].monotone;
+      r.is_categorical = c.is_categorical; r.num_cat_bins = c.num_cat_bins; for (int w = 0; w < 8; ++w) r.cat_bitset[w] = c.cat_bitset[w];
+      SplitParams p = a.params; if (c.is_categorical) p.lambda_l2 = FB_ADD(p.lambda_l2, a.params.cat_l2);
+      r.left_out = LeafOutput(r.left_g, FB_ADD(r.left_h, kEpsilon), p, r.left_cnt, leaf.output);
+      r.right_out = LeafOutput(r.right_g, FB_ADD(r.right_h, kEpsilon), p, r.right_cnt, leaf.output);
     }
     if (a.wait.world > 1) { s_rec = r; a.leaves_rw[ch.leaf].num_data_global = leaf.num_data_global; }
     else a.best[ch.leaf] = r;
@@ -290,7 +401,15 @@ void LaunchFindSplits(const FindArgs& a, cudaStream_t s) {
   const int nf = a.num_features + a.num_sub_features;
   if (nf <= 0) return;
   dim3 grid(a.num_children, (nf + kWarpsPerBlock - 1) / kWarpsPerBlock);
-  if (a.quant) FindSplitsKernel<true><<<grid, kFindThreads, 0, s>>>(a); else FindSplitsKernel<false><<<grid, kFindThreads, 0, s>>>(a);
+  // categorical features stage their bins in shared memory, one scratch per warp
+  const size_t sm = a.has_categorical ? sizeof(CatScratch) * kWarpsPerBlock : 0;
+  static bool attr = false;
+  if (sm > 48 * 1024 && !attr) {
+    FB_CUDA(cudaFuncSetAttribute(FindSplitsKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
+    FB_CUDA(cudaFuncSetAttribute(FindSplitsKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
+    attr = true;
+  }
+  if (a.quant) FindSplitsKernel<true><<<grid, kFindThreads, sm, s>>>(a); else FindSplitsKernel<false><<<grid, kFindThreads, sm, s>>>(a);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 

@@ -126,3 +126,46 @@ def test_device_bagging_trains_and_scores_out_of_bag_rows():
     ref = -np.mean(np.where(y[:25000] > 0, np.log(pr), np.log(1 - pr)))
     assert abs(ref - res["train"]["binary_logloss"][-1]) < 1e-4
     assert auc(y[25000:], bst.predict(X[25000:])) > 0.9
+
+
+def _make_categorical(n, seed=11):
+    rng = np.random.RandomState(seed)
+    Xn = rng.randn(n, 6).astype(np.float32)
+    c_small = rng.randint(0, 3, size=n)          # 3 categories -> one-vs-rest
+    c_big = rng.randint(0, 40, size=n)           # 40 categories -> sorted many-vs-many
+    eff = rng.randn(40)
+    y = (Xn[:, 0] + 0.5 * Xn[:, 1] * Xn[:, 2] + eff[c_big] + (c_small == 1) * 0.8 + 0.3 * rng.randn(n)).astype(np.float32)
+    X = np.column_stack([Xn, c_small.astype(np.float32), c_big.astype(np.float32)])
+    return X, y
+
+
+@pytest.mark.parametrize("quant", ["stochastic", "none"])
+def test_categorical_search_on_device_matches_host(quant):
+    X, y = _make_categorical(20000)
+    y = np.round(y * 8) / 8
+    base = {"objective": "none", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": quant, "grow_policy": "level", "min_data_in_leaf": 20, "seed": 3,
+            "min_data_per_group": 50, "cat_smooth": 10.0}
+    mk = lambda: fb.Dataset(X, y, categorical_feature=[6, 7], free_raw_data=False)
+    bc = fb.train({**base, "device_type": "cpu"}, mk(), 1, fobj=_l2_exact)
+    bg = fb.train({**base, "device_type": "cuda"}, mk(), 1, fobj=_l2_exact)
+    sc, sg = bc.model_to_string(), bg.model_to_string()
+    assert "cat_threshold" in sg       # the device tree really uses categorical splits
+    if quant == "stochastic":
+        assert model_body(sc) == model_body(sg)
+    else:
+        np.testing.assert_allclose(bg.predict(X), bc.predict(X), atol=1e-4)
+
+
+def test_categorical_training_and_device_predict():
+    X, y = _make_categorical(30000)
+    p = {"objective": "regression", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "device_type": "cuda", "metric": "l2"}
+    ds = fb.Dataset(X[:25000], y[:25000], categorical_feature=[6, 7])
+    dv = ds.create_valid(X[25000:], y[25000:])
+    res = {}
+    bst = fb.train(p, ds, 40, valid_sets=[dv], callbacks=[fb.record_evaluation(res)])
+    ph = bst.predict(X[25000:])
+    # validation scores are kept by binned traversal on the device: they must agree with the host walk on raw values
+    assert abs(np.mean((ph - y[25000:]) ** 2) - res["valid_0"]["l2"][-1]) < 1e-3
+    assert np.mean((ph - y[25000:]) ** 2) < 0.4 * np.var(y)
+    pd = bst.predict(torch.from_numpy(X[25000:]).cuda()).cpu().numpy()
+    np.testing.assert_allclose(pd, ph, atol=2e-4)
