@@ -202,6 +202,7 @@ class Dataset:
         self._predictor = None
         self._keep: List[Any] = []   # arrays whose memory the native side points into
         self._global_rows: Optional[Tuple[int, int]] = None   # (offset, total) when rows are one shard of many
+        self._replicated = False                               # every rank holds all rows (feature-parallel training)
 
     # -- construction ---------------------------------------------------------------
     def _merged_params(self) -> Dict[str, Any]:
@@ -303,7 +304,8 @@ class Dataset:
             from .parallel import bootstrap
 
             goff, gtot = self._global_rows if self._global_rows is not None else (0, 0)
-            sample, total = bootstrap.gather_bin_sample(t, int(params.get("bin_construct_sample_cnt", 200000)), int(params.get("data_random_seed", 1)), goff, gtot)
+            sample, total = bootstrap.gather_bin_sample(t, int(params.get("bin_construct_sample_cnt", 200000)), int(params.get("data_random_seed", 1)), goff, gtot,
+                                                        replicated=self._replicated)
             sample = np.ascontiguousarray(sample, dtype=np.float64)
             _safe_call(lib.FB_DatasetCreateFromSample(sample.ctypes.data_as(ctypes.c_void_p), ctypes.c_int32(sample.shape[0]), ctypes.c_int32(ncol),
                                                       ctypes.c_int64(total), _param_str(params), None, 0, ctypes.byref(handle)))
@@ -314,6 +316,11 @@ class Dataset:
         code = {torch.float32: 0, torch.float64: 1, torch.int8: 2, torch.int16: 3, torch.uint8: 4, torch.float16: 6, torch.int32: 7}[t.dtype]
         _safe_call(lib.FB_DatasetBinDeviceMat(handle, ctypes.c_void_p(t.data_ptr()), code, ctypes.c_int32(nrow), ctypes.c_int32(ncol), 1, keep_host))
         torch.cuda.synchronize()
+
+    def set_replicated(self) -> "Dataset":
+        """Declare that every rank holds ALL rows (``tree_learner=feature``): bins are found locally, nothing is gathered."""
+        self._replicated = True
+        return self
 
     def set_global_rows(self, offset: int, total: int) -> "Dataset":
         """Declare that this dataset holds rows [offset, offset + n) of a ``total``-row data set sharded over ranks."""
@@ -542,6 +549,10 @@ class Booster:
         """One boosting iteration. Returns True when no further split is possible."""
         lib = _lib()
         fin = ctypes.c_int(0)
+        from .parallel import bootstrap as _bs
+
+        if _bs.peer_check_enabled():
+            _bs.assert_peers_alive()   # multi-rank: never enqueue a round that would wait for a rank that has left
         if fobj is None:
             _safe_call(lib.FB_BoosterUpdateOneIter(self._handle, ctypes.byref(fin)))
             return fin.value == 1

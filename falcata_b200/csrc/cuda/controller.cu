@@ -91,7 +91,8 @@ __global__ void __launch_bounds__(kCtrlThreads) LevelControllerKernel(CtrlArgs a
     q.leaf = l; q.right_leaf = right; q.begin = P.begin; q.count = P.count; q.buffer = P.buffer; q.group = m.group; q.bundled = m.bundled; q.group_offset = m.group_offset;
     q.num_bin = m.num_bin; q.most_freq_bin = m.most_freq_bin; q.threshold = b.threshold; q.default_left = b.default_left; q.missing_type = m.missing_type;
     q.default_bin = m.default_bin; q.is_categorical = b.is_categorical; for (int w = 0; w < 8; ++w) q.cat_bitset[w] = b.cat_bitset[w];
-    q.chunk_begin = s_chunks[s]; q.num_chunks = s_chunks[s + 1] - s_chunks[s]; q.pad_[0] = q.pad_[1] = q.pad_[2] = 0;
+    q.chunk_begin = s_chunks[s]; q.num_chunks = s_chunks[s + 1] - s_chunks[s]; q.pad_[0] = q.pad_[1] = 0;
+    q.owner = a.bin_owner != nullptr ? a.bin_owner[m.hist_offset] : 0;
     a.splits[s] = q;
     ChildInit ci;
     ci.smaller_is_left = b.left_cnt <= b.right_cnt ? 1 : 0;

@@ -116,7 +116,8 @@ struct PartSplit {
   uint32_t cat_bitset[8];
   int chunk_begin;     // first partition chunk of this split in the flat chunk grid
   int num_chunks;
-  int pad_[3];         // keeps sizeof a multiple of 16: arrays of different record types share one upload blob
+  int owner;           // feature-parallel: rank that owns the split feature and broadcasts the bitmap
+  int pad_[2];         // keeps sizeof a multiple of 16: arrays of different record types share one upload blob
 };
 static_assert(sizeof(PartSplit) % 16 == 0, "level blob records must keep 16-byte alignment");
 

@@ -43,8 +43,9 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   if (prop.major < 10) Log::Warning("This build targets sm_100a; device %s is compute %d.%d", prop.name, prop.major, prop.minor);
   num_sms_ = prop.multiProcessorCount;
   if (Fabric::Get().active() && cfg.tree_learner != "serial") {
-    if (cfg.tree_learner != "data") Log::Fatal("On the device, multi-GPU training is tree_learner=data (voting / feature run on the host learner)");
+    if (cfg.tree_learner != "data" && cfg.tree_learner != "feature") Log::Fatal("On the device, multi-GPU training is tree_learner=data or feature (voting runs on the host learner)");
     fabric_ = &Fabric::Get(); world_ = fabric_->world(); rank_ = fabric_->rank();
+    feature_parallel_ = cfg.tree_learner == "feature";   // every rank holds all rows; features are split between the ranks
     if (!Network::active()) Log::Fatal("Multi-GPU training needs the host collectives as well (falcata_b200.parallel.init())");
   } else if (Network::active() && cfg.tree_learner != "serial") {
     Log::Fatal("Multi-GPU training needs the device fabric (call falcata_b200.parallel.init() before creating the Booster)");
@@ -117,7 +118,18 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   }
   BuildPartitions();
   SetupOwnership();
-  if (world_ > 1) {
+  if (feature_parallel_) {
+    // histograms stay local (own features only); the heap carries the best-split slots and the partition bitmap
+    fabric_->Reset();
+    off_best_ = fabric_->Alloc(static_cast<size_t>(world_) * NL * sizeof(SplitRecord));
+    const size_t max_chunks_fp = static_cast<size_t>(n_) / kPartChunk + NL + 1;
+    off_bits_ = fabric_->Alloc(max_chunks_fp * (kPartChunk / 32) * sizeof(unsigned int));
+    off_chunk_left_ = fabric_->Alloc(max_chunks_fp * sizeof(int));
+    flag_best_ = fabric_->NewFlagSlot(); flag_part_ = fabric_->NewFlagSlot();
+    pool_bytes_ = static_cast<size_t>(NL) * slot_stride_ * hist_elem_;
+    pool_.Alloc(pool_bytes_);
+    pool_base_ = pool_.get();
+  } else if (world_ > 1) {
     // same carving order on every rank: offsets name the same object everywhere
     long long max_stride = 0; for (int r = 0; r < world_; ++r) max_stride = std::max(max_stride, slot_strides_[r]);
     fabric_->Reset();
@@ -200,6 +212,7 @@ void CudaEngine::SetupOwnership() {
     for (int f = 0; f < train_->num_features; ++f) if (gowner[train_->feature_meta[f].group] == rank_) owned_features_.push_back(f);
   }
   bin_owner_.Upload(owner, stream_); bin_local_.Upload(local, stream_);
+  h_bin_owner_ = owner;
 }
 
 int CudaEngine::ChooseRowsPerBlock(long long total_rows) const {
@@ -295,7 +308,7 @@ std::vector<double> CudaEngine::EvalMetric(int data_idx, const std::string& name
   double h[2];
   FB_CUDA(cudaMemcpyAsync(h, root_sums_d_.get(), sizeof(h), cudaMemcpyDeviceToHost, stream_));
   FB_CUDA(cudaStreamSynchronize(stream_));
-  Network::SumDouble(h, 2);   // rows are sharded over ranks: (weighted loss, weight) sums add up
+  if (!feature_parallel_) Network::SumDouble(h, 2);   // rows sharded over ranks: (weighted loss, weight) sums add up; replicated rows: already complete
   *supported = true;
   double v = h[1] > 0 ? h[0] / h[1] : 0.0;
   if (kind == kMetRMSE) v = std::sqrt(v);

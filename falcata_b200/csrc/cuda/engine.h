@@ -60,6 +60,7 @@ class CudaEngine : public DeviceEngine {
   void RunRootHistogram();
   void ReadBackLevel(int num_leaves);
   void DrawBag(int round);
+  void SetupBitmapBroadcast(PartArgs* pa);
   const uint8_t* bag_mask_ptr() const { return bag_active_ ? bag_mask_.get() : nullptr; }
   void UploadTreeForTraversal(const Tree& tree, const Dataset* ds, DevTree* out);
   int ChooseRowsPerBlock(long long total_rows) const;
@@ -90,6 +91,9 @@ class CudaEngine : public DeviceEngine {
   char* pool_base_ = nullptr; size_t pool_bytes_ = 0;
   // ---- multi-rank state (world_ > 1) ----
   Fabric* fabric_ = nullptr; int rank_ = 0, world_ = 1;
+  bool feature_parallel_ = false;                      // tree_learner=feature: rows replicated, features split
+  bool data_parallel() const { return world_ > 1 && !feature_parallel_; }
+  size_t off_bits_ = 0, off_chunk_left_ = 0, flag_part_ = 0; std::vector<unsigned char> h_bin_owner_;
   long long slot_strides_[kMaxRanks] = {0};
   size_t off_pool_ = 0, off_counts_ = 0, off_best_ = 0, flag_hist_ = 0, flag_best_ = 0;
   DevBuf<float> global_max_;

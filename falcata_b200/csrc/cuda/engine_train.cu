@@ -72,7 +72,7 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
     if (bagging && quant_) LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_, mask);   // the scale comes from the bag's rows only
   }
   // quantization scales must be the same on every rank: max over ranks of the per-class maxima
-  if (world_ > 1 && quant_) fabric_->AllReduce(kFabricMaxF32, maxbuf_.get(), global_max_.get(), 2 * K_, stream_);
+  if (data_parallel() && quant_) fabric_->AllReduce(kFabricMaxF32, maxbuf_.get(), global_max_.get(), 2 * K_, stream_);
   clock_.End(stream_);
   bool any_split = false;
   for (int k = 0; k < K_; ++k) {
@@ -125,13 +125,13 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   // into this rank's slots after it has seen this rank's contribution to that exchange.
   FB_CUDA(cudaMemsetAsync(pool_base_, 0, pool_bytes_, stream_));
   if (quant_) {
-    LaunchQuantize(cur_grad_, cur_hess_, n_, maxbuf_.get() + 2 * class_id, world_ > 1 ? global_max_.get() + 2 * class_id : nullptr, cfg_.quant_bins_resolved,
+    LaunchQuantize(cur_grad_, cur_hess_, n_, maxbuf_.get() + 2 * class_id, data_parallel() ? global_max_.get() + 2 * class_id : nullptr, cfg_.quant_bins_resolved,
                    cfg_.quant == QuantMode::Stochastic, static_cast<uint32_t>(cfg_.seed), static_cast<uint32_t>(tree_index),
                    static_cast<uint64_t>(train_->global_row_offset), const_cast<uint8_t*>(gh_base_), gh_stride_, scales_.get(), root_sums_i_.get(), stream_, bag_mask_ptr());
-    if (world_ > 1) fabric_->AllReduce(kFabricSumI64, root_sums_i_.get(), root_sums_i_.get(), 2, stream_);
+    if (data_parallel()) fabric_->AllReduce(kFabricSumI64, root_sums_i_.get(), root_sums_i_.get(), 2, stream_);
   } else {
     LaunchInterleave(cur_grad_, cur_hess_, n_, gh2_.get(), partial_.get(), static_cast<int>(partial_.size() / 2), root_sums_d_.get(), stream_, bag_mask_ptr());
-    if (world_ > 1) fabric_->AllReduce(kFabricSumF64, root_sums_d_.get(), root_sums_d_.get(), 2, stream_);
+    if (data_parallel()) fabric_->AllReduce(kFabricSumF64, root_sums_d_.get(), root_sums_d_.get(), 2, stream_);
   }
   InitRootKernel<<<1, 1, 0, stream_>>>(leaves_.get(), root_sums_i_.get(), root_sums_d_.get(), scales_.get(), quant_ ? 1 : 0, root_count_, root_global_, sp_);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
@@ -145,37 +145,43 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   ha.rows = dd_->rows.get(); ha.row_stride = dd_->row_stride; ha.num_groups = dd_->num_groups; ha.gh_base = gh_base_; ha.gh_stride = gh_stride_;
   ha.idx[0] = idx_[0].get(); ha.idx[1] = idx_[1].get(); ha.tasks = hist_tasks_.get(); ha.parts = parts_.get(); ha.num_parts = static_cast<int>(h_parts_.size());
   ha.max_part_bins = max_part_bins_; ha.group_bin_start = dd_->group_bin_start.get(); ha.sub_rows = sub_rows_;
-  ha.dest.bin_owner = bin_owner_.get(); ha.dest.bin_local = bin_local_.get(); ha.dest.num_ranks = world_; ha.dest.rank = rank_;
+  const bool dp = data_parallel();
+  ha.dest.bin_owner = bin_owner_.get(); ha.dest.bin_local = bin_local_.get(); ha.dest.num_ranks = dp ? world_ : 1; ha.dest.rank = rank_;
+  ha.dest.owner_only = feature_parallel_ ? 1 : 0;
   for (int r = 0; r < kMaxRanks; ++r) { ha.dest.pool[r] = nullptr; ha.dest.slot_stride[r] = 0; }
   for (int r = 0; r < kMaxRanks; ++r) ha.dest.peer_stage[r] = nullptr;
-  if (world_ > 1) {
+  if (dp) {
     for (int r = 0; r < world_; ++r) { ha.dest.pool[r] = fabric_->Ptr<char>(r, off_pool_); ha.dest.slot_stride[r] = slot_strides_[r]; ha.dest.peer_stage[r] = fabric_->Ptr<char>(r, off_stage_); }
     ha.dest.stage_local = stage_local_.get(); ha.dest.task_done = task_done_.get(); ha.dest.stage_cap = NL;
   } else { ha.dest.pool[0] = pool_base_; ha.dest.slot_stride[0] = slot_stride_; }
   ha.num_total_bin = train_->num_total_bin; ha.lane_mode = lane_mode_; ha.lane_bins = lane_bins_;
-  ha.sig.world = world_;
+  ha.sig.world = dp ? world_ : 1;
   FindArgs fa = FindArgs();
   fa.features = features_.get(); fa.num_features = NF; fa.sub_features = sub_features_.get(); fa.num_sub_features = NS; fa.meta = dd_->feature_meta.get();
   fa.bin_local = bin_local_.get(); fa.pool = pool_base_; fa.slot_stride = slot_stride_; fa.leaves = leaves_.get(); fa.scales = scales_.get(); fa.params = sp_;
   fa.cand = cand_.get(); fa.best = best_.get(); fa.quant = quant_ ? 1 : 0;
   fa.has_categorical = 0; for (int f : feats) if (train_->feature_meta[f].bin_type != 0) fa.has_categorical = 1;
-  fa.wait.world = world_; fa.wait_best.world = world_; fa.sig.world = world_; fa.leaves_rw = leaves_.get();
+  // data-parallel: construct-done flags + staged slices + counts; both multi-rank modes all-gather the best records
+  fa.wait.world = dp ? world_ : 1; fa.wait_best.world = world_; fa.sig.world = world_; fa.leaves_rw = leaves_.get();
   if (world_ > 1) {
     const FabricView v = fabric_->View();
-    ha.sig.done_counter = fabric_->done_counter(0); fa.sig.done_counter = fabric_->done_counter(1);
+    fa.sig.done_counter = fabric_->done_counter(1);
     for (int r = 0; r < world_; ++r) {
-      ha.sig.peer_flag[r] = fabric_->Ptr<unsigned int>(r, flag_hist_) + rank_;
       fa.sig.peer_flag[r] = fabric_->Ptr<unsigned int>(r, flag_best_) + rank_;
       fa.peer_best[r] = fabric_->Ptr<SplitRecord>(r, off_best_) + static_cast<size_t>(rank_) * NL;
     }
-    fa.wait.flags = fabric_->Local<unsigned int>(flag_hist_); fa.wait.max_spins = v.max_spins; fa.wait.status = v.status;
     fa.wait_best.flags = fabric_->Local<unsigned int>(flag_best_); fa.wait_best.max_spins = v.max_spins; fa.wait_best.status = v.status;
-    fa.counts = fabric_->Local<int>(off_counts_); fa.counts_stride = NL;
-    fa.stage = fabric_->Local<char>(off_stage_); fa.stage_cap = NL;
     fa.gathered = fabric_->Local<SplitRecord>(off_best_); fa.gathered_stride = NL;
+    if (dp) {
+      ha.sig.done_counter = fabric_->done_counter(0);
+      for (int r = 0; r < world_; ++r) ha.sig.peer_flag[r] = fabric_->Ptr<unsigned int>(r, flag_hist_) + rank_;
+      fa.wait.flags = fabric_->Local<unsigned int>(flag_hist_); fa.wait.max_spins = v.max_spins; fa.wait.status = v.status;
+      fa.counts = fabric_->Local<int>(off_counts_); fa.counts_stride = NL;
+      fa.stage = fabric_->Local<char>(off_stage_); fa.stage_cap = NL;
+    }
   }
   auto construct_and_find = [&]() {
-    if (world_ > 1) { ha.sig.epoch = fabric_->NextEpoch(); fa.wait.epoch = ha.sig.epoch; }
+    if (dp) { ha.sig.epoch = fabric_->NextEpoch(); fa.wait.epoch = ha.sig.epoch; }
     clock_.Begin(st_hist_, stream_);
     if (quant_) LaunchHistConstructQuant(ha, stream_); else LaunchHistConstructFloat(ha, stream_);
     clock_.End(stream_);
@@ -210,18 +216,20 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     ca.ctrl = ctrl_.get(); ca.frontier = frontier_.get(); ca.journal = journal_.get(); ca.leaves = leaves_.get(); ca.best = best_.get(); ca.meta = dd_->feature_meta.get();
     ca.splits = reinterpret_cast<PartSplit*>(db); ca.child_init = reinterpret_cast<ChildInit*>(db + sizeof(PartSplit) * NL);
     ca.children = reinterpret_cast<FindChild*>(db + (sizeof(PartSplit) + sizeof(ChildInit)) * NL);
-    ca.max_leaves = NL; ca.rows_per_block = rpb;
+    ca.max_leaves = NL; ca.rows_per_block = rpb; ca.bin_owner = feature_parallel_ ? bin_owner_.get() : nullptr;
     PartArgs pa = PartArgs();
     pa.rows = dd_->rows.get(); pa.row_stride = dd_->row_stride; pa.idx[0] = idx_[0].get(); pa.idx[1] = idx_[1].get();
     pa.cols = dd_->cols.size() ? dd_->cols.get() : nullptr; pa.col_stride = n_;
     pa.splits = ca.splits; pa.num_splits = max_splits; pa.total_chunks = n_ / kPartChunk + max_splits; pa.bits = bits_.get(); pa.chunk_left = chunk_left_.get();
     pa.split_left_total = split_left_total_.get(); pa.leaves = leaves_.get(); pa.child_init = ca.child_init; pa.hist_tasks = hist_tasks_.get(); pa.rows_per_block = rpb;
-    pa.world = world_; pa.ctrl = ctrl_.get();
-    if (world_ > 1) for (int r = 0; r < world_; ++r) pa.peer_counts[r] = fabric_->Ptr<int>(r, off_counts_) + static_cast<size_t>(rank_) * NL;
+    pa.world = dp ? world_ : 1; pa.ctrl = ctrl_.get();
+    if (dp) for (int r = 0; r < world_; ++r) pa.peer_counts[r] = fabric_->Ptr<int>(r, off_counts_) + static_cast<size_t>(rank_) * NL;
+    if (feature_parallel_) SetupBitmapBroadcast(&pa);
     ha.identity_root = 0; ha.rows_per_block = rpb; ha.ctrl = ctrl_.get(); ha.num_tasks = max_splits; ha.total_blocks = n_ / rpb + max_splits;
     fa.ctrl = ctrl_.get(); fa.children = ca.children; fa.num_children = 2 * max_splits;
     auto enqueue_level = [&]() {
       LaunchLevelController(ca, stream_);
+      if (feature_parallel_) { pa.bc_sig.epoch = fabric_->NextEpoch(); pa.bc_wait.epoch = pa.bc_sig.epoch; }
       clock_.Begin(st_part_, stream_);
       LaunchPartitionFlags(pa, stream_); LaunchPartitionScanSetup(pa, stream_); LaunchPartitionScatter(pa, stream_);
       clock_.End(stream_);
@@ -301,6 +309,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
       q.num_bin = m.num_bin; q.most_freq_bin = m.most_freq_bin; q.threshold = b.threshold; q.default_left = b.default_left; q.missing_type = m.missing_type;
       q.default_bin = m.default_bin; q.is_categorical = b.is_categorical; for (int w = 0; w < 8; ++w) q.cat_bitset[w] = b.cat_bitset[w];
       q.chunk_begin = chunk_cursor; q.num_chunks = (P.count + kPartChunk - 1) / kPartChunk; chunk_cursor += q.num_chunks;
+      q.owner = feature_parallel_ ? h_bin_owner_[m.hist_offset] : 0;
       ChildInit& c = ci[s];
       memset(&c, 0, sizeof(c));
       c.smaller_is_left = b.left_cnt <= b.right_cnt ? 1 : 0;
@@ -324,8 +333,9 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     pa.splits = reinterpret_cast<const PartSplit*>(db); pa.num_splits = S; pa.total_chunks = chunk_cursor; pa.bits = bits_.get(); pa.chunk_left = chunk_left_.get();
     pa.split_left_total = split_left_total_.get(); pa.leaves = leaves_.get(); pa.child_init = reinterpret_cast<const ChildInit*>(db + sizeof(PartSplit) * S);
     pa.hist_tasks = hist_tasks_.get(); pa.rows_per_block = ha.rows_per_block;
-    pa.world = world_;
-    if (world_ > 1) for (int r = 0; r < world_; ++r) pa.peer_counts[r] = fabric_->Ptr<int>(r, off_counts_) + static_cast<size_t>(rank_) * NL;
+    pa.world = dp ? world_ : 1;
+    if (dp) for (int r = 0; r < world_; ++r) pa.peer_counts[r] = fabric_->Ptr<int>(r, off_counts_) + static_cast<size_t>(rank_) * NL;
+    if (feature_parallel_) { SetupBitmapBroadcast(&pa); pa.bc_sig.epoch = fabric_->NextEpoch(); pa.bc_wait.epoch = pa.bc_sig.epoch; }
     clock_.Begin(st_part_, stream_);
     LaunchPartitionFlags(pa, stream_); LaunchPartitionScanSetup(pa, stream_); LaunchPartitionScatter(pa, stream_);
     clock_.End(stream_);
@@ -342,6 +352,20 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     frontier.swap(next);
   }
   return tree.release();
+}
+
+// Feature-parallel: the partition's bit words and chunk counts live in the symmetric heap; the owner of a
+// split's feature writes them into every rank.
+void CudaEngine::SetupBitmapBroadcast(PartArgs* pa) {
+  const FabricView v = fabric_->View();
+  pa->bc_world = world_; pa->bc_rank = rank_;
+  pa->bits = fabric_->Local<unsigned int>(off_bits_); pa->chunk_left = fabric_->Local<int>(off_chunk_left_);
+  for (int r = 0; r < world_; ++r) {
+    pa->peer_bits[r] = fabric_->Ptr<unsigned int>(r, off_bits_); pa->peer_chunk_left[r] = fabric_->Ptr<int>(r, off_chunk_left_);
+    pa->bc_sig.peer_flag[r] = fabric_->Ptr<unsigned int>(r, flag_part_) + rank_;
+  }
+  pa->bc_sig.world = world_; pa->bc_sig.done_counter = fabric_->done_counter(2);
+  pa->bc_wait.world = world_; pa->bc_wait.flags = fabric_->Local<unsigned int>(flag_part_); pa->bc_wait.max_spins = v.max_spins; pa->bc_wait.status = v.status;
 }
 
 // A new bag: flags by global row id, compaction of the in-bag rows, and the (global) bag size.
@@ -363,7 +387,7 @@ void CudaEngine::DrawBag(int round) {
   FB_CUDA(cudaStreamSynchronize(stream_));
   bag_count_ = *h_bag_count_.get();
   int64_t g = bag_count_;
-  if (world_ > 1) Network::SumInt64(&g, 1);
+  if (data_parallel()) Network::SumInt64(&g, 1);
   bag_global_ = g;
 }
 

@@ -36,6 +36,7 @@ __device__ inline int FindTask(const HistTask* tasks, int num_tasks, int block) 
 // histogram of the task (L2 atomics); PushTaskIfLast ships the finished task to the owners.
 __device__ inline void FlushBinQuant(const HistDest& d, int slot, int task_index, int num_total_bin, int global_bin, long long g, long long h) {
   const hist_q_t v = HistQPack(g, h);
+  if (d.owner_only && d.bin_owner[global_bin] != d.rank) return;
   if (d.num_ranks > 1) {
     atomicAdd(static_cast<hist_q_t*>(d.stage_local) + static_cast<long long>(task_index) * num_total_bin + global_bin, v);
   } else {

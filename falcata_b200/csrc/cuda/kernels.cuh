@@ -46,6 +46,7 @@ struct HistDest {
   const unsigned char* bin_owner;  // [num_total_bin]
   const int* bin_local;            // [num_total_bin]
   int num_ranks, rank;
+  int owner_only;                  // feature-parallel: every rank sees all rows; only bins of owned features are kept (no exchange)
   // num_ranks > 1: blocks add into a LOCAL staging histogram of their task; the last block of a
   // task to finish stores the finished slices into the owner ranks' per-source staging slots
   // (plain coalesced stores over NVLink) while other tasks' tiles are still being constructed.
@@ -118,6 +119,7 @@ struct CtrlArgs {
   LeafInfo* leaves; const SplitRecord* best; const FeatureMeta* meta;
   PartSplit* splits; ChildInit* child_init; FindChild* children;
   int max_leaves; int rows_per_block;
+  const unsigned char* bin_owner;   // feature-parallel: owner rank of every histogram bin (null otherwise)
 };
 void LaunchLevelController(const CtrlArgs& a, cudaStream_t s);
 void LaunchInitLevelCtrl(LevelCtrl* ctrl, int* frontier, cudaStream_t s);
@@ -148,6 +150,14 @@ struct PartArgs {
   int rows_per_block;
   int world; int* peer_counts[kMaxRanks];   // world > 1: address of counts[this rank][0] inside every rank's heap
   const LevelCtrl* ctrl;     // non-null: num_splits / total_chunks come from the device controller
+  // ---- feature-parallel bitmap broadcast (bc_world > 1) ----
+  // Every rank holds all rows but only the histograms of the features it owns. The rank that owns a
+  // split's feature computes the go-left bit words of the leaf's rows and stores them, with the chunk
+  // counts, into EVERY rank's buffers over NVLink (N/8 bytes per level); the other ranks skip the
+  // column read and scatter from the received bitmap.
+  int bc_world, bc_rank;
+  unsigned int* peer_bits[kMaxRanks]; int* peer_chunk_left[kMaxRanks];
+  FabricSignal bc_sig; FabricWait bc_wait;
 };
 void LaunchPartitionFlags(const PartArgs& a, cudaStream_t s);
 void LaunchPartitionScanSetup(const PartArgs& a, cudaStream_t s);

@@ -20,6 +20,14 @@ std::vector<HistPartition> MakePartitions(const std::vector<int>& gstart, const 
 #define OPS_BEGIN() try {
 #define OPS_END() } catch (std::exception& ex) { g_ops_error = ex.what(); return -1; } return 0;
 
+namespace fb {
+__global__ void BoundedWaitProbeKernel(const unsigned int* flag, unsigned int* status, unsigned int* seen, unsigned long long max_spins) {
+  FabricWait w; w.world = 1; w.flags = flag; w.epoch = 1u; w.max_spins = max_spins; w.status = status;
+  FabricWaitAll(w);                       // the production wait: bounded, reports through the status word
+  if (threadIdx.x == 0) *seen = (*reinterpret_cast<const volatile unsigned int*>(flag) >= 1u) ? 1u : 0u;
+}
+}  // namespace fb
+
 extern "C" {
 
 const char* FB_OpsLastError() { return g_ops_error.c_str(); }
@@ -105,6 +113,22 @@ int FB_OpPartition(const uint8_t* rows, int row_stride, const int* idx, int coun
   LaunchPartitionFlags(a, s); LaunchPartitionScanSetup(a, s); LaunchPartitionScatter(a, s);
   FB_CUDA(cudaMemcpyAsync(left_count, left_total.get(), sizeof(int), cudaMemcpyDeviceToHost, s));
   FB_CUDA(cudaStreamSynchronize(s));
+  OPS_END();
+}
+
+// Failure-detection probe: one block waits, with the given spin budget, for a flag that nothing sets.
+// The wait must run out, record kStatusWaitTimeout in the status word and return: *out_status is that
+// word, *out_flag_seen tells whether the wait (wrongly) reported the flag as set.
+int FB_OpBoundedWaitProbe(long long max_spins, int* out_status, int* out_flag_seen) {
+  OPS_BEGIN();
+  cudaStream_t s = 0;
+  DevBuf<unsigned int> words; words.Alloc(3); words.Zero(s);   // [0] flag (stays 0), [1] status, [2] seen
+  BoundedWaitProbeKernel<<<1, 32, 0, s>>>(words.get(), words.get() + 1, words.get() + 2, static_cast<unsigned long long>(std::max(1LL, max_spins)));
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+  unsigned int h[3] = {0, 0, 0};
+  FB_CUDA(cudaMemcpyAsync(h, words.get(), sizeof(h), cudaMemcpyDeviceToHost, s));
+  FB_CUDA(cudaStreamSynchronize(s));
+  *out_status = static_cast<int>(h[1]); *out_flag_seen = static_cast<int>(h[2]);
   OPS_END();
 }
 

@@ -36,11 +36,13 @@ __device__ inline bool GoLeft(const PartSplit& sp, int gb) {
 __global__ void __launch_bounds__(kPartThreads) PartitionFlagsKernel(PartArgs a) {
   const int chunk = blockIdx.x;
   const int nsplits = a.ctrl != nullptr ? a.ctrl->num_splits : a.num_splits;
-  if (chunk >= (a.ctrl != nullptr ? a.ctrl->total_chunks : a.total_chunks)) return;
+  const bool bc = a.bc_world > 1;
+  if (chunk >= (a.ctrl != nullptr ? a.ctrl->total_chunks : a.total_chunks)) { if (bc) FabricSignalDone(a.bc_sig, gridDim.x); return; }
   const int si = FindSplitOfChunk(a.splits, nsplits, chunk);
   const PartSplit sp = a.splits[si];
   const int local_chunk = chunk - sp.chunk_begin;
-  if (local_chunk >= sp.num_chunks) return;
+  // feature-parallel: only the owner of the split feature reads the column; it writes every rank's bitmap
+  if (local_chunk >= sp.num_chunks || (bc && sp.owner != a.bc_rank)) { if (bc) FabricSignalDone(a.bc_sig, gridDim.x); return; }
   const int* idx = a.idx[sp.buffer] + sp.begin;
   const int pos0 = local_chunk * kPartChunk;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -55,17 +57,27 @@ __global__ void __launch_bounds__(kPartThreads) PartitionFlagsKernel(PartArgs a)
       left = GoLeft(sp, gb);
     }
     const unsigned int word = __ballot_sync(0xffffffffu, left);
-    if (lane == 0) { a.bits[static_cast<size_t>(chunk) * kWordsPerChunk + k * (kPartThreads / 32) + warp] = word; cnt += __popc(word); }
+    if (lane == 0) {
+      const size_t wi = static_cast<size_t>(chunk) * kWordsPerChunk + k * (kPartThreads / 32) + warp;
+      if (bc) { for (int r = 0; r < a.bc_world; ++r) a.peer_bits[r][wi] = word; } else a.bits[wi] = word;
+      cnt += __popc(word);
+    }
   }
   __shared__ int s_cnt[kPartThreads / 32];
   if (lane == 0) s_cnt[warp] = cnt;
   __syncthreads();
-  if (threadIdx.x == 0) { int t = 0; for (int w = 0; w < kPartThreads / 32; ++w) t += s_cnt[w]; a.chunk_left[chunk] = t; }
+  if (threadIdx.x == 0) {
+    int t = 0; for (int w = 0; w < kPartThreads / 32; ++w) t += s_cnt[w];
+    if (bc) { for (int r = 0; r < a.bc_world; ++r) a.peer_chunk_left[r][chunk] = t; } else a.chunk_left[chunk] = t;
+  }
+  if (bc) FabricSignalDone(a.bc_sig, gridDim.x);
 }
 
 __global__ void __launch_bounds__(kPartThreads) PartitionScanSetupKernel(PartArgs a) {
   const int si = blockIdx.x;
   if (si >= (a.ctrl != nullptr ? a.ctrl->num_splits : a.num_splits)) return;
+  // feature-parallel: the bitmaps of this level come from the owners of the split features
+  if (a.bc_world > 1) FabricWaitAll(a.bc_wait);
   const PartSplit sp = a.splits[si];
   __shared__ int s_scan[kPartThreads];
   __shared__ int s_carry;

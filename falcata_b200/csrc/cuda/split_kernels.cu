@@ -315,7 +315,8 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
 }
 
 __global__ void ReduceBestKernel(FindArgs a) {
-  if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) { if (a.wait.world > 1) FabricSignalDone(a.sig, gridDim.x); return; }
+  const bool gather = a.wait_best.world > 1;   // data-parallel and feature-parallel both all-gather the rank-local best
+  if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) { if (gather) FabricSignalDone(a.sig, gridDim.x); return; }
   const FindChild ch = a.children[blockIdx.x];
   LeafInfo leaf = a.leaves[ch.leaf];
   leaf.num_data_global = ChildGlobalCount(a, ch, leaf.num_data_global);
@@ -350,16 +351,16 @@ __global__ void ReduceBestKernel(FindArgs a) {
       r.left_out = LeafOutput(r.left_g, FB_ADD(r.left_h, kEpsilon), p, r.left_cnt, leaf.output);
       r.right_out = LeafOutput(r.right_g, FB_ADD(r.right_h, kEpsilon), p, r.right_cnt, leaf.output);
     }
-    if (a.wait.world > 1) { s_rec = r; a.leaves_rw[ch.leaf].num_data_global = leaf.num_data_global; }
+    if (gather) { s_rec = r; a.leaves_rw[ch.leaf].num_data_global = leaf.num_data_global; }
     else a.best[ch.leaf] = r;
   }
-  if (a.wait.world > 1) {
+  if (gather) {
     // all-gather of the rank-local best split: plain stores into every rank's slot array, then the
     // last block of the grid raises this rank's flag on every peer
     __syncthreads();
     const unsigned int* src = reinterpret_cast<const unsigned int*>(&s_rec);
     constexpr int kWords = sizeof(SplitRecord) / 4;
-    for (int p = 0; p < a.wait.world; ++p) {
+    for (int p = 0; p < a.wait_best.world; ++p) {
       unsigned int* dst = reinterpret_cast<unsigned int*>(a.peer_best[p] + ch.leaf);
       for (int w = threadIdx.x; w < kWords; w += blockDim.x) dst[w] = src[w];
     }

@@ -62,3 +62,13 @@ def launch_count() -> int:
     out = ctypes.c_longlong(0)
     _lib().FB_OpLaunchCount(ctypes.byref(out))
     return out.value
+
+
+def bounded_wait_probe(max_spins: int = 1000):
+    """Run the kernels' cross-rank wait on a flag that nothing sets. Returns (status word, flag seen): the
+    wait must give up after ``max_spins`` polls and report status 1 (wait timeout) without hanging."""
+    st, seen = ctypes.c_int(-1), ctypes.c_int(-1)
+    if _lib().FB_OpBoundedWaitProbe(ctypes.c_longlong(int(max_spins)), ctypes.byref(st), ctypes.byref(seen)) != 0:
+        _lib().FB_OpsLastError.restype = ctypes.c_char_p
+        raise RuntimeError(_lib().FB_OpsLastError().decode())
+    return st.value, seen.value

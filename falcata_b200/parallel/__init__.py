@@ -9,10 +9,10 @@ Typical use (one process per GPU, started with torchrun)::
     bst = falcata_b200.train({"tree_learner": "data", "device_type": "cuda", ...}, ds)
 """
 from . import bootstrap
-from .bootstrap import free_host_network, init_device_fabric, init_host_network, shutdown_device_fabric, world
+from .bootstrap import announce_departure, assert_peers_alive, enable_peer_check, free_host_network, init_device_fabric, init_host_network, shutdown_device_fabric, world
 
 
-def init(heap_bytes: int = 256 << 20, device: bool = True) -> None:
+def init(heap_bytes: int = 256 << 20, device: bool = True, peer_check: bool = False) -> None:
     """Connect this rank to its peers: host collectives always, the device fabric when CUDA is used.
 
     torchrun exports OMP_NUM_THREADS=1 to every worker unless the user set it; bin finding at ingest is a
@@ -24,6 +24,7 @@ def init(heap_bytes: int = 256 << 20, device: bool = True) -> None:
 
         local_world = max(1, int(os.environ.get("LOCAL_WORLD_SIZE", "1")))
         set_num_threads(max(1, min(32, (os.cpu_count() or 1) // local_world)))
+    enable_peer_check(peer_check or bool(os.environ.get("FALCATA_PEER_CHECK")))
     init_host_network()
     if device:
         import torch
@@ -43,4 +44,4 @@ def shutdown() -> None:
     free_host_network()
 
 
-__all__ = ["init", "shutdown", "world", "init_host_network", "free_host_network", "init_device_fabric", "shutdown_device_fabric", "bootstrap"]
+__all__ = ["init", "shutdown", "world", "announce_departure", "assert_peers_alive", "enable_peer_check", "init_host_network", "free_host_network", "init_device_fabric", "shutdown_device_fabric", "bootstrap"]

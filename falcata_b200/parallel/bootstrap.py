@@ -27,19 +27,22 @@ def world() -> Tuple[int, int]:
     return (d.get_rank(), d.get_world_size()) if d else (0, 1)
 
 
-def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total: int = 0) -> Tuple[np.ndarray, int]:
+def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total: int = 0, replicated: bool = False) -> Tuple[np.ndarray, int]:
     """Rows used to find bin boundaries.
 
     A global row is sampled iff a uniform number drawn for it (from a generator seeded by the 256K-row
     chunk the row falls into) is below ``sample_cnt / total``. The choice depends only on the GLOBAL
     row id, so the sample - and with it every bin boundary - is the same however the rows are sharded
     over ranks. Each rank contributes the sampled rows of its shard; the shards are concatenated in
-    rank order. Returns (sample [ns, ncol] float64, total rows)."""
+    rank order. ``replicated``: every rank holds ALL rows (feature-parallel training), so the local sample
+    is already the global one and nothing is exchanged. Returns (sample [ns, ncol] float64, total rows)."""
     import torch
 
     rank, ws = world()
     n = t.shape[0]
-    d = _dist()
+    d = None if replicated else _dist()
+    if replicated:
+        rank, ws, offset, total = 0, 1, 0, n
     if total <= 0:
         total = n
         if d and ws > 1:
@@ -87,6 +90,48 @@ def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total
     if local.shape[0] == 0:
         local = t[:1].to(torch.float64).cpu().numpy()
     return local, total
+
+
+# ---- liveness on the host ---------------------------------------------------------------------
+# A rank that stops (an exception in user code, a planned departure) announces it in the process
+# group's key-value store; with the check enabled every rank looks for such notices before it enqueues
+# the next boosting round, so nobody launches kernels that would wait for a peer that is gone. Ranks
+# that vanish without notice are caught by the bounded flag waits of the kernels (status word).
+_PEER_CHECK = False
+
+
+def _store():
+    from torch.distributed import distributed_c10d as c10d
+
+    return c10d._get_default_store()
+
+
+def enable_peer_check(on: bool = True) -> None:
+    global _PEER_CHECK
+    _PEER_CHECK = bool(on)
+
+
+def peer_check_enabled() -> bool:
+    return _PEER_CHECK and _dist() is not None
+
+
+def announce_departure(reason: str = "left") -> None:
+    """Tell the other ranks that this rank will not take part in further rounds."""
+    d = _dist()
+    if d is None:
+        return
+    _store().set(f"falcata/left/{d.get_rank()}", reason)
+    _store().add("falcata/left_count", 1)
+
+
+def assert_peers_alive() -> None:
+    """Raise if some rank has announced its departure (one small store read)."""
+    d = _dist()
+    if d is None:
+        return
+    if _store().add("falcata/left_count", 0) > 0:
+        gone = [r for r in range(d.get_world_size()) if _store().check([f"falcata/left/{r}"])]
+        raise RuntimeError(f"rank(s) {gone} left the job: stopping before the next launch")
 
 
 def init_host_network() -> None:

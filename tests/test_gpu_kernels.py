@@ -105,3 +105,14 @@ def test_partition_stable(n):
     b = rows[idx.long(), 1]
     goes_left = (b <= 10) & (b != 3)
     assert torch.equal(out, torch.cat([idx[goes_left], idx[~goes_left]]))
+
+
+def test_cross_rank_wait_is_bounded_and_reports_status():
+    # failure detection on the device: a wait on a flag that nothing sets must run out of its spin budget,
+    # record the timeout status for the host and return (the context stays usable afterwards)
+    from falcata_b200 import ops
+
+    status, seen = ops.bounded_wait_probe(2000)
+    assert status == 1 and seen == 0
+    x = torch.ones(8, device="cuda")
+    assert float(x.sum().item()) == 8.0

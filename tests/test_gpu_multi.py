@@ -10,6 +10,13 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+def _run_raw(world, out, extra=()):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", "29519",
+           os.path.join(HERE, "multi_gpu_worker.py"), "--out", out, *extra]
+    return subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=300)
+
+
 def _run(world, out, extra=()):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     if world == 1:
@@ -32,3 +39,21 @@ def test_bit_identical_across_gpu_counts(tmp_path, quant):
     for w in worlds:
         got = _run(w, str(tmp_path / f"m{w}.txt"), extra)
         assert got == ref, f"model differs at {w} GPUs"
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("extra", [(), ("--categorical",)])
+def test_feature_parallel_matches_single_gpu(tmp_path, extra):
+    # rows replicated, features split between the ranks, split bitmaps broadcast by the owner of the split
+    # feature: the model must be the single-GPU model, digit for digit
+    ref = _run(1, str(tmp_path / "m1.txt"), extra)
+    got = _run(2, str(tmp_path / "m2.txt"), ("--learner", "feature", *extra))
+    assert got == ref
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_departed_rank_is_noticed_before_the_next_launch(tmp_path):
+    r = _run_raw(2, str(tmp_path / "m.txt"), ("--skip-rank", "1", "--rounds", "50"))
+    out = r.stdout + r.stderr
+    assert "rank 1 leaves after round 2" in out
+    assert "TRAIN_ERROR" in out and "left the job" in out, out[-3000:]
