@@ -43,7 +43,8 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   if (prop.major < 10) Log::Warning("This build targets sm_100a; device %s is compute %d.%d", prop.name, prop.major, prop.minor);
   num_sms_ = prop.multiProcessorCount;
   if (Fabric::Get().active() && cfg.tree_learner != "serial") {
-    if (cfg.tree_learner != "data" && cfg.tree_learner != "feature") Log::Fatal("On the device, multi-GPU training is tree_learner=data or feature (voting runs on the host learner)");
+    if (cfg.tree_learner != "data" && cfg.tree_learner != "feature" && cfg.tree_learner != "voting") Log::Fatal("Unknown tree_learner %s", cfg.tree_learner.c_str());
+    voting_ = cfg.tree_learner == "voting";
     fabric_ = &Fabric::Get(); world_ = fabric_->world(); rank_ = fabric_->rank();
     feature_parallel_ = cfg.tree_learner == "feature";   // every rank holds all rows; features are split between the ranks
     if (!Network::active()) Log::Fatal("Multi-GPU training needs the host collectives as well (falcata_b200.parallel.init())");
@@ -129,6 +130,24 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     pool_bytes_ = static_cast<size_t>(NL) * slot_stride_ * hist_elem_;
     pool_.Alloc(pool_bytes_);
     pool_base_ = pool_.get();
+  } else if (voting_) {
+    // local pool with all features (identity bin map); the heap carries vote slots, the staging slots of the
+    // voted features, the row counts and the best-split slots
+    long long max_stride = 0; for (int r = 0; r < world_; ++r) max_stride = std::max(max_stride, slot_strides_[r]);
+    fabric_->Reset();
+    off_stage_ = fabric_->Alloc(static_cast<size_t>(world_) * NL * max_stride * hist_elem_);
+    off_counts_ = fabric_->Alloc(static_cast<size_t>(world_) * NL * sizeof(int));
+    off_best_ = fabric_->Alloc(static_cast<size_t>(world_) * NL * sizeof(SplitRecord));
+    off_votes_ = fabric_->Alloc(static_cast<size_t>(world_) * NL * std::max(1, cfg.top_k) * sizeof(int));
+    flag_hist_ = fabric_->NewFlagSlot(); flag_best_ = fabric_->NewFlagSlot(); flag_vote_ = fabric_->NewFlagSlot();
+    pool_bytes_ = static_cast<size_t>(NL) * train->num_total_bin * hist_elem_;
+    pool_.Alloc(pool_bytes_); pool_base_ = pool_.get();
+    std::vector<int> ident(train->num_total_bin); for (int b = 0; b < train->num_total_bin; ++b) ident[b] = b;
+    bin_identity_.Upload(ident, stream_);
+    const size_t F = std::max(1, train->num_features);
+    cand_local_.Alloc(static_cast<size_t>(NL) * F); vote_sums_.Alloc(NL); voted_.Alloc(static_cast<size_t>(NL) * F);
+    features_all_.Alloc(F); sub_features_all_.Alloc(F);
+    global_max_.Alloc(2 * K_);
   } else if (world_ > 1) {
     // same carving order on every rank: offsets name the same object everywhere
     long long max_stride = 0; for (int r = 0; r < world_; ++r) max_stride = std::max(max_stride, slot_strides_[r]);

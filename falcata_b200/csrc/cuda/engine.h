@@ -93,6 +93,10 @@ class CudaEngine : public DeviceEngine {
   Fabric* fabric_ = nullptr; int rank_ = 0, world_ = 1;
   bool feature_parallel_ = false;                      // tree_learner=feature: rows replicated, features split
   bool data_parallel() const { return world_ > 1 && !feature_parallel_; }
+  // tree_learner=voting: rows sharded, histograms local, only the voted features' bins are exchanged
+  bool voting_ = false;
+  size_t off_votes_ = 0, flag_vote_ = 0;
+  DevBuf<int> bin_identity_, features_all_, sub_features_all_; DevBuf<CandLite> cand_local_; DevBuf<VoteLocalSum> vote_sums_; DevBuf<unsigned char> voted_;
   size_t off_bits_ = 0, off_chunk_left_ = 0, flag_part_ = 0; std::vector<unsigned char> h_bin_owner_;
   long long slot_strides_[kMaxRanks] = {0};
   size_t off_pool_ = 0, off_counts_ = 0, off_best_ = 0, flag_hist_ = 0, flag_best_ = 0;

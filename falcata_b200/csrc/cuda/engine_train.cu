@@ -119,6 +119,11 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   for (int f : owned_features_) { if (col_sampler_.used_by_tree()[f]) feats.push_back(f); else subs.push_back(f); }
   features_.Upload(feats, stream_); sub_features_.Upload(subs, stream_);
   const int NF = static_cast<int>(feats.size()), NS = static_cast<int>(subs.size());
+  std::vector<int> feats_all, subs_all;   // voting: the local pass searches every sampled feature, owned or not
+  if (voting_) {
+    for (int f = 0; f < train_->num_features; ++f) { if (col_sampler_.used_by_tree()[f]) feats_all.push_back(f); else subs_all.push_back(f); }
+    features_all_.Upload(feats_all, stream_); sub_features_all_.Upload(subs_all, stream_);
+  }
 
   clock_.Begin(st_quant_, stream_);
   // The pool is cleared BEFORE this tree's first cross-rank exchange: a peer can only start adding
@@ -146,16 +151,17 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   ha.idx[0] = idx_[0].get(); ha.idx[1] = idx_[1].get(); ha.tasks = hist_tasks_.get(); ha.parts = parts_.get(); ha.num_parts = static_cast<int>(h_parts_.size());
   ha.max_part_bins = max_part_bins_; ha.group_bin_start = dd_->group_bin_start.get(); ha.sub_rows = sub_rows_;
   const bool dp = data_parallel();
-  ha.dest.bin_owner = bin_owner_.get(); ha.dest.bin_local = bin_local_.get(); ha.dest.num_ranks = dp ? world_ : 1; ha.dest.rank = rank_;
+  const bool rs = dp && !voting_;   // construct fused with the reduce-scatter (plain data-parallel)
+  ha.dest.bin_owner = bin_owner_.get(); ha.dest.bin_local = voting_ ? bin_identity_.get() : bin_local_.get(); ha.dest.num_ranks = rs ? world_ : 1; ha.dest.rank = rank_;
   ha.dest.owner_only = feature_parallel_ ? 1 : 0;
   for (int r = 0; r < kMaxRanks; ++r) { ha.dest.pool[r] = nullptr; ha.dest.slot_stride[r] = 0; }
   for (int r = 0; r < kMaxRanks; ++r) ha.dest.peer_stage[r] = nullptr;
-  if (dp) {
+  if (rs) {
     for (int r = 0; r < world_; ++r) { ha.dest.pool[r] = fabric_->Ptr<char>(r, off_pool_); ha.dest.slot_stride[r] = slot_strides_[r]; ha.dest.peer_stage[r] = fabric_->Ptr<char>(r, off_stage_); }
     ha.dest.stage_local = stage_local_.get(); ha.dest.task_done = task_done_.get(); ha.dest.stage_cap = NL;
-  } else { ha.dest.pool[0] = pool_base_; ha.dest.slot_stride[0] = slot_stride_; }
+  } else { ha.dest.pool[0] = pool_base_; ha.dest.slot_stride[0] = voting_ ? train_->num_total_bin : slot_stride_; }
   ha.num_total_bin = train_->num_total_bin; ha.lane_mode = lane_mode_; ha.lane_bins = lane_bins_;
-  ha.sig.world = dp ? world_ : 1;
+  ha.sig.world = rs ? world_ : 1;
   FindArgs fa = FindArgs();
   fa.features = features_.get(); fa.num_features = NF; fa.sub_features = sub_features_.get(); fa.num_sub_features = NS; fa.meta = dd_->feature_meta.get();
   fa.bin_local = bin_local_.get(); fa.pool = pool_base_; fa.slot_stride = slot_stride_; fa.leaves = leaves_.get(); fa.scales = scales_.get(); fa.params = sp_;
@@ -175,15 +181,51 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     if (dp) {
       ha.sig.done_counter = fabric_->done_counter(0);
       for (int r = 0; r < world_; ++r) ha.sig.peer_flag[r] = fabric_->Ptr<unsigned int>(r, flag_hist_) + rank_;
+      if (voting_) { fa.voted = voted_.get(); fa.voted_stride = train_->num_features; }
       fa.wait.flags = fabric_->Local<unsigned int>(flag_hist_); fa.wait.max_spins = v.max_spins; fa.wait.status = v.status;
       fa.counts = fabric_->Local<int>(off_counts_); fa.counts_stride = NL;
       fa.stage = fabric_->Local<char>(off_stage_); fa.stage_cap = NL;
     }
   }
+  VoteArgs va = VoteArgs(); FindArgs fl = fa;
+  if (voting_) {
+    const FabricView v = fabric_->View();
+    va.world = world_; va.rank = rank_; va.top_k = std::max(1, cfg_.top_k); va.quant = quant_ ? 1 : 0; va.meta = dd_->feature_meta.get();
+    va.num_inner_features = train_->num_features; va.local_pool = pool_base_; va.local_stride = train_->num_total_bin; va.g0_bins = train_->group_num_bin[0];
+    va.sums = vote_sums_.get(); va.scales = scales_.get(); va.cand_local = cand_local_.get(); va.num_searched = static_cast<int>(feats_all.size());
+    va.votes_all = fabric_->Local<int>(off_votes_); va.child_cap = NL; va.voted = voted_.get();
+    va.bin_owner = bin_owner_.get(); va.bin_local = bin_local_.get(); va.stage_cap = NL;
+    va.vote_sig.world = world_; va.vote_sig.done_counter = fabric_->done_counter(3);
+    va.hist_sig.world = world_; va.hist_sig.done_counter = fabric_->done_counter(0);
+    for (int r = 0; r < world_; ++r) {
+      va.peer_votes[r] = fabric_->Ptr<int>(r, off_votes_) + static_cast<size_t>(rank_) * NL * va.top_k;
+      va.peer_stage[r] = fabric_->Ptr<char>(r, off_stage_); va.slot_stride[r] = slot_strides_[r];
+      va.vote_sig.peer_flag[r] = fabric_->Ptr<unsigned int>(r, flag_vote_) + rank_;
+      va.hist_sig.peer_flag[r] = fabric_->Ptr<unsigned int>(r, flag_hist_) + rank_;
+    }
+    va.vote_wait.world = world_; va.vote_wait.flags = fabric_->Local<unsigned int>(flag_vote_); va.vote_wait.max_spins = v.max_spins; va.vote_wait.status = v.status;
+    // the local pass: every sampled feature on this rank's own histograms, thresholds scaled down to a rank's share
+    fl.features = features_all_.get(); fl.num_features = static_cast<int>(feats_all.size()); fl.sub_features = sub_features_all_.get(); fl.num_sub_features = static_cast<int>(subs_all.size());
+    fl.bin_local = bin_identity_.get(); fl.pool = pool_base_; fl.slot_stride = train_->num_total_bin; fl.cand = cand_local_.get();
+    fl.params.min_data_in_leaf = std::max(1, sp_.min_data_in_leaf / world_); fl.params.min_sum_hessian_in_leaf = sp_.min_sum_hessian_in_leaf / world_;
+    fl.wait.world = 1; fl.wait_best.world = 1; fl.sig.world = 1; fl.voted = nullptr; fl.local_vote = 1; fl.vote_sums = vote_sums_.get();
+    fl.has_categorical = 0; for (int f : feats_all) if (train_->feature_meta[f].bin_type != 0) fl.has_categorical = 1;
+  }
   auto construct_and_find = [&]() {
-    if (dp) { ha.sig.epoch = fabric_->NextEpoch(); fa.wait.epoch = ha.sig.epoch; }
+    if (rs) { ha.sig.epoch = fabric_->NextEpoch(); fa.wait.epoch = ha.sig.epoch; }
     clock_.Begin(st_hist_, stream_);
     if (quant_) LaunchHistConstructQuant(ha, stream_); else LaunchHistConstructFloat(ha, stream_);
+    if (voting_) {
+      // local search, vote (all-gather), restricted reduce-scatter of the voted features
+      va.children = fa.children; va.num_children = fa.num_children; va.ctrl = fa.ctrl;
+      fl.children = fa.children; fl.num_children = fa.num_children; fl.ctrl = fa.ctrl;
+      LaunchVoteLocalSums(va, stream_);
+      LaunchFindSplits(fl, stream_);
+      va.vote_sig.epoch = fabric_->NextEpoch(); va.vote_wait.epoch = va.vote_sig.epoch;
+      LaunchVoteTopK(va, stream_);
+      va.hist_sig.epoch = fabric_->NextEpoch(); fa.wait.epoch = va.hist_sig.epoch;
+      LaunchVoteTallyPush(va, stream_);
+    }
     clock_.End(stream_);
     if (world_ > 1) { fa.sig.epoch = fabric_->NextEpoch(); fa.wait_best.epoch = fa.sig.epoch; }
     clock_.Begin(st_find_, stream_);

@@ -100,6 +100,11 @@ struct FindArgs {
   SplitRecord* best;                              // [leaf]
   int quant;
   int has_categorical;                            // some searched feature is categorical: the kernel gets its shared scratch
+  // ---- voting-parallel (see VoteArgs) ----
+  int local_vote;                                 // 1: local pass - leaf totals and count are this rank's (vote_sums, LeafInfo.count)
+  const struct VoteLocalSum* vote_sums;           // [child] local totals of the child's histogram
+  const unsigned char* voted; int voted_stride;   // non-null: global pass - search only voted (child, feature) pairs; bins are the
+                                                  // sums of the ranks' staged slices of child blockIdx.x; nothing is written back
   // ---- multi-rank (world > 1) ----
   FabricWait wait;                                // construct-done flags of all ranks (the reduce-scatter is complete when they are up)
   const void* stage; int stage_cap;               // this rank's staging area [source rank][stage_cap][slot_stride] written by the ranks' constructs
@@ -122,6 +127,35 @@ struct CtrlArgs {
   const unsigned char* bin_owner;   // feature-parallel: owner rank of every histogram bin (null otherwise)
 };
 void LaunchLevelController(const CtrlArgs& a, cudaStream_t s);
+
+// ----------------------------------------------------------------- voting ----
+// Voting-parallel (PV-Tree) on the device, rows sharded over ranks. Histograms stay LOCAL (all features,
+// one pool slot per leaf); per level and child:
+//   1. VoteLocalSums   local totals of the child (bins of feature group 0)
+//   2. FindSplits      local pass: best local gain of every sampled feature
+//   3. VoteTopK        the rank's top_k features by local gain, stored into EVERY rank's vote slots (all-gather
+//                      by peer stores) + flag
+//   4. VoteTallyPush   waits for all ranks' votes, counts them, keeps the 2*top_k most voted features, and stores
+//                      ONLY their local bins into the owner rank's staging slot (restricted reduce-scatter) + flag
+//   5. FindSplits      global pass on the owned, voted features (bins = sum of the ranks' slices), then the usual
+//                      per-leaf argmax and all-gather of the best record.
+struct VoteLocalSum { long long gi, hi; double g, h; };
+struct VoteArgs {
+  const FindChild* children; int num_children; const LevelCtrl* ctrl;
+  int world, rank, top_k, quant;
+  const FeatureMeta* meta; int num_inner_features;
+  const void* local_pool; long long local_stride; int g0_bins;   // local histogram pool; number of bins of feature group 0
+  VoteLocalSum* sums; const float* scales;                       // [child]; quantized: (g_scale, h_scale) of this tree
+  const CandLite* cand_local; int num_searched;                  // [child][num_searched] local candidates
+  int* peer_votes[kMaxRanks]; const int* votes_all; int child_cap;   // votes: [source rank][child_cap][top_k] inner feature ids (-1: none)
+  FabricSignal vote_sig; FabricWait vote_wait;
+  unsigned char* voted;                                          // [child_cap][num_inner_features]
+  const unsigned char* bin_owner; const int* bin_local; void* peer_stage[kMaxRanks]; long long slot_stride[kMaxRanks]; int stage_cap;
+  FabricSignal hist_sig;
+};
+void LaunchVoteLocalSums(const VoteArgs& a, cudaStream_t s);
+void LaunchVoteTopK(const VoteArgs& a, cudaStream_t s);
+void LaunchVoteTallyPush(const VoteArgs& a, cudaStream_t s);
 void LaunchInitLevelCtrl(LevelCtrl* ctrl, int* frontier, cudaStream_t s);
 void LaunchFindSplits(const FindArgs& a, cudaStream_t s);      // per (child, feature) search + in-place larger-child subtraction
 void LaunchReduceBest(const FindArgs& a, cudaStream_t s);      // per child argmax over features -> SplitRecord (world > 1: stored into every peer)

@@ -184,18 +184,33 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
   const FeatureMeta m = a.meta[f];
   LeafInfo leaf = a.leaves[ch.leaf];
   leaf.num_data_global = ChildGlobalCount(a, ch, leaf.num_data_global);
+  if (a.local_vote) {
+    // voting, local pass: this rank's rows only
+    const VoteLocalSum ls = a.vote_sums[blockIdx.x];
+    leaf.sum_gi = ls.gi; leaf.sum_hi = ls.hi; leaf.sum_g = ls.g; leaf.sum_h = ls.h; leaf.num_data_global = leaf.count;
+  }
+  const bool vote_global = a.voted != nullptr;
   const int nb = m.num_bin;
   const int nstored = m.bundled ? nb - 1 : nb;
   const long long base = a.bin_local[m.hist_offset];
   const size_t esz = QUANT ? sizeof(hist_q_t) : sizeof(double2);
   char* child = static_cast<char*>(a.pool) + (static_cast<long long>(ch.slot) * a.slot_stride + base) * esz;
   const char* other = static_cast<const char*>(a.pool) + (static_cast<long long>(ch.other_slot) * a.slot_stride + base) * esz;
-  const bool larger = ch.is_larger != 0;
+  const bool larger = ch.is_larger != 0 && !vote_global;   // voting: every child's slices are staged afresh
   const int world = a.wait.world;
-  const bool write_back = larger || world > 1;
+  const bool write_back = (larger || world > 1) && !vote_global;
   BinSrc src; src.child = child; src.other = other; src.larger = larger; src.world = world;
   src.rank_stride = static_cast<long long>(a.stage_cap) * a.slot_stride;
-  src.stage = world > 1 ? static_cast<const char*>(a.stage) + (static_cast<long long>(ch.task) * a.slot_stride + base) * esz : nullptr;
+  const int stage_task = vote_global ? static_cast<int>(blockIdx.x) : ch.task;
+  src.stage = world > 1 ? static_cast<const char*>(a.stage) + (static_cast<long long>(stage_task) * a.slot_stride + base) * esz : nullptr;
+  if (vote_global && (!search || a.voted[static_cast<size_t>(blockIdx.x) * a.voted_stride + f] == 0)) {
+    if (search && lane == 0) {
+      CandLite c; c.gain = -1.0 / 0.0; c.feature = -1; c.threshold = 0; c.default_left = 1; c.left_cnt = 0; c.left_gi = c.left_hi = 0; c.left_g = c.left_h = 0;
+      c.is_categorical = 0; c.num_cat_bins = 0; for (int w = 0; w < 8; ++w) c.cat_bitset[w] = 0;
+      a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + fi] = c;
+    }
+    return;
+  }
 
   if (search && m.bin_type != 0) {
     ScanCategoricalWarp<QUANT>(a, src, child, write_back, m, leaf, f, fi, lane, warp);

@@ -25,6 +25,9 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=6000)
     ap.add_argument("--rounds", type=int, default=10)
     ap.add_argument("--out", default="")
+    ap.add_argument("--device", default="cpu", help="cpu: host learners; cuda: the device engine, one GPU per rank (gloo is still the plumbing)")
+    ap.add_argument("--top-k", type=int, default=12)
+    ap.add_argument("--leaves", type=int, default=15)
     args = ap.parse_args()
 
     import torch.distributed as dist
@@ -38,12 +41,16 @@ def main() -> None:
     if args.mode == "fail" and rank == 1:
         # a rank that dies on the host before joining any collective
         raise SystemExit(7)
-    parallel.init(device=False)
+    if args.device == "cuda":
+        import torch
+
+        torch.cuda.set_device(rank)
+    parallel.init(device=args.device == "cuda")
     X, y = make_binary(args.rows, 12)
-    params = {"objective": "binary", "num_leaves": 15, "max_bin": 63, "verbosity": -1, "device_type": "cpu", "tree_learner": args.learner,
+    params = {"objective": "binary", "num_leaves": args.leaves, "max_bin": 63, "verbosity": -1, "device_type": args.device, "tree_learner": args.learner,
               "grow_policy": "level", "quant_mode": args.quant, "min_data_in_leaf": 5, "seed": 5}
     if args.learner == "voting":
-        params["top_k"] = 12   # all features voted in: must equal the data-parallel result
+        params["top_k"] = args.top_k   # 12 = all features voted in: must equal the data-parallel result
     try:
         if args.learner == "feature":
             ds = fb.Dataset(X, y).set_global_rows(0, args.rows)       # every rank holds all rows

@@ -57,3 +57,35 @@ def test_departed_rank_is_noticed_before_the_next_launch(tmp_path):
     out = r.stdout + r.stderr
     assert "rank 1 leaves after round 2" in out
     assert "TRAIN_ERROR" in out and "left the job" in out, out[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_voting_with_every_feature_voted_matches_single_gpu(tmp_path):
+    # top_k >= number of features: the vote keeps everything, so the restricted reduce-scatter carries all
+    # features and the model must be the single-GPU model
+    ref = _run(1, str(tmp_path / "m1.txt"))
+    got = _run(2, str(tmp_path / "m2.txt"), ("--learner", "voting", "--top-k", "28"))
+    assert got == ref
+
+
+def _run_gloo(world, extra):
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT="29523", OMP_NUM_THREADS="4")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "dist_cpu_worker.py"), *extra], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    for p in procs:
+        o, _ = p.communicate(timeout=300)
+        assert p.returncode == 0, o[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_voting_with_small_top_k_matches_the_host_voting_learner(tmp_path):
+    # a real vote (3 of 12 features per rank): the device path must pick the features, reduce the bins and split
+    # exactly like the host voting learner run on the same two shards. One tree: from the second tree on the
+    # two arms see gradients that differ in the last float bit (host double vs device float sigmoid).
+    from util import model_body
+
+    common = ["--learner", "voting", "--quant", "stochastic", "--top-k", "3", "--rows", "40000", "--rounds", "1", "--leaves", "63"]
+    _run_gloo(2, [*common, "--device", "cpu", "--out", str(tmp_path / "host.txt")])
+    _run_gloo(2, [*common, "--device", "cuda", "--out", str(tmp_path / "dev.txt")])
+    assert model_body(open(tmp_path / "dev.txt").read()) == model_body(open(tmp_path / "host.txt").read())
