@@ -161,6 +161,28 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     ha.dest.stage_local = stage_local_.get(); ha.dest.task_done = task_done_.get(); ha.dest.stage_cap = NL;
   } else { ha.dest.pool[0] = pool_base_; ha.dest.slot_stride[0] = voting_ ? train_->num_total_bin : slot_stride_; }
   ha.num_total_bin = train_->num_total_bin; ha.lane_mode = lane_mode_; ha.lane_bins = lane_bins_;
+  // K9: when this tree samples few columns, construct from a dense per-tree copy of just those groups
+  // (feature-parallel: just the sampled groups this rank owns)
+  int first_group = 0;
+  if (plan_.compact_view && lane_mode_ != 0 && dd_->cols.size() > 0) {
+    std::vector<char> want(train_->num_groups, 0);
+    for (int f = 0; f < train_->num_features; ++f) if (col_sampler_.used_by_tree()[f]) {
+      const int g = train_->feature_meta[f].group;
+      if (!feature_parallel_ || h_bin_owner_[train_->group_bin_start[g]] == rank_) want[g] = 1;
+    }
+    std::vector<int> glist, gstart, gcount;
+    for (int g = 0; g < train_->num_groups; ++g) if (want[g]) { glist.push_back(g); gstart.push_back(train_->group_bin_start[g]); gcount.push_back(train_->group_num_bin[g]); }
+    if (!glist.empty() && 2 * glist.size() <= static_cast<size_t>(train_->num_groups)) {
+      const int cstride = (static_cast<int>(glist.size()) + 15) / 16 * 16;
+      compact_groups_.Upload(glist, stream_); compact_start_.Upload(gstart, stream_); compact_count_.Upload(gcount, stream_);
+      if (compact_rows_.size() < static_cast<size_t>(n_) * cstride) compact_rows_.Alloc(static_cast<size_t>(n_) * cstride);
+      LaunchCompactGather(dd_->cols.get(), n_, n_, compact_groups_.get(), static_cast<int>(glist.size()), compact_rows_.get(), cstride, stream_);
+      FB_CUDA(cudaStreamSynchronize(stream_));   // the host lists above go out of scope
+      ha.rows = compact_rows_.get(); ha.row_stride = cstride; ha.num_groups = static_cast<int>(glist.size());
+      ha.group_bin_start = compact_start_.get(); ha.group_bin_count = compact_count_.get();
+      first_group = glist[0];
+    }
+  }
   ha.sig.world = rs ? world_ : 1;
   FindArgs fa = FindArgs();
   fa.features = features_.get(); fa.num_features = NF; fa.sub_features = sub_features_.get(); fa.num_sub_features = NS; fa.meta = dd_->feature_meta.get();
@@ -191,7 +213,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   if (voting_) {
     const FabricView v = fabric_->View();
     va.world = world_; va.rank = rank_; va.top_k = std::max(1, cfg_.top_k); va.quant = quant_ ? 1 : 0; va.meta = dd_->feature_meta.get();
-    va.num_inner_features = train_->num_features; va.local_pool = pool_base_; va.local_stride = train_->num_total_bin; va.g0_bins = train_->group_num_bin[0];
+    va.num_inner_features = train_->num_features; va.local_pool = pool_base_; va.local_stride = train_->num_total_bin; va.g0_begin = train_->group_bin_start[first_group]; va.g0_bins = train_->group_num_bin[first_group];
     va.sums = vote_sums_.get(); va.scales = scales_.get(); va.cand_local = cand_local_.get(); va.num_searched = static_cast<int>(feats_all.size());
     va.votes_all = fabric_->Local<int>(off_votes_); va.child_cap = NL; va.voted = voted_.get();
     va.bin_owner = bin_owner_.get(); va.bin_local = bin_local_.get(); va.stage_cap = NL;

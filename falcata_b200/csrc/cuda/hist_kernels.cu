@@ -245,7 +245,7 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
     if (l >= ng) continue;
     const int g = g0 + l;
     const int gstart = a.group_bin_start[g];
-    const int gbins = (g + 1 < a.num_groups ? a.group_bin_start[g + 1] : a.num_total_bin) - gstart;
+    const int gbins = a.group_bin_count != nullptr ? a.group_bin_count[g] : (g + 1 < a.num_groups ? a.group_bin_start[g + 1] : a.num_total_bin) - gstart;
     if (b >= gbins) continue;
     long long sg = 0, sh = 0;
     for (int w = 0; w < kLaneWarps; ++w) { const int v = tiles[w * kTile + cell]; const int h = v & 0xFFFF; sg += (v - h) >> 16; sh += h; }
@@ -308,7 +308,31 @@ __global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
   if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y);
 }
 
+// Transpose tile of the compact view: 32 rows x 32 listed groups per block.
+__global__ void __launch_bounds__(256) CompactGatherKernel(const uint8_t* __restrict__ cols, long long col_stride, int n, const int* __restrict__ groups,
+                                                           int num_groups, uint8_t* __restrict__ out, int out_stride) {
+  __shared__ uint8_t tile[32][33];
+  const int row0 = blockIdx.x * 32, j0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+  for (int jj = ty; jj < 32; jj += 8) {
+    const int j = j0 + jj, row = row0 + tx;
+    tile[jj][tx] = (j < num_groups && row < n) ? cols[static_cast<size_t>(groups[j]) * col_stride + row] : 0;
+  }
+  __syncthreads();
+  for (int rr = ty; rr < 32; rr += 8) {
+    const int row = row0 + rr, j = j0 + tx;
+    if (row < n && j < out_stride) out[static_cast<size_t>(row) * out_stride + j] = tile[tx][rr];
+  }
+}
+
 }  // namespace
+
+void LaunchCompactGather(const uint8_t* cols, long long col_stride, int n, const int* groups, int num_groups, uint8_t* out, int out_stride, cudaStream_t s) {
+  if (n <= 0 || num_groups <= 0) return;
+  dim3 grid((n + 31) / 32, (out_stride + 31) / 32);
+  CompactGatherKernel<<<grid, 256, 0, s>>>(cols, col_stride, n, groups, num_groups, out, out_stride);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
 
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
   if (a.total_blocks <= 0 || a.num_tasks <= 0) return;

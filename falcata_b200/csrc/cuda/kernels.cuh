@@ -63,6 +63,7 @@ struct HistArgs {
   const HistTask* tasks; int num_tasks; int total_blocks;
   const HistPartition* parts; int num_parts; int max_part_bins;
   const int* group_bin_start;
+  const int* group_bin_count;   // non-null (compact view): bins per listed group; null: groups are consecutive in the bin space
   int rows_per_block; int sub_rows;
   int identity_root;        // 1: task rows are 0..count-1 (no index load)
   int num_total_bin;
@@ -73,6 +74,10 @@ struct HistArgs {
   const LevelCtrl* ctrl;    // non-null: num_tasks / total_blocks come from the device controller
 };
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s);
+// K9: per-tree compact view. out[row][j] = cols[groups[j]][row] for the listed (sampled) feature groups: a dense
+// row-major matrix with only the columns this tree can split on, read from the column-major copy (coalesced
+// along rows) and written in 32-byte row pieces through a shared-memory transpose tile.
+void LaunchCompactGather(const uint8_t* cols, long long col_stride, int n, const int* groups, int num_groups, uint8_t* out, int out_stride, cudaStream_t s);
 void LaunchHistConstructFloat(const HistArgs& a, cudaStream_t s);
 // tcgen05 one-hot instance (same arguments, same result); returns false when the shape is outside what it covers
 bool LaunchHistConstructQuantTC(const HistArgs& a, cudaStream_t s);
@@ -144,7 +149,7 @@ struct VoteArgs {
   const FindChild* children; int num_children; const LevelCtrl* ctrl;
   int world, rank, top_k, quant;
   const FeatureMeta* meta; int num_inner_features;
-  const void* local_pool; long long local_stride; int g0_bins;   // local histogram pool; number of bins of feature group 0
+  const void* local_pool; long long local_stride; int g0_begin, g0_bins;   // local histogram pool; bin range of one constructed feature group
   VoteLocalSum* sums; const float* scales;                       // [child]; quantized: (g_scale, h_scale) of this tree
   const CandLite* cand_local; int num_searched;                  // [child][num_searched] local candidates
   int* peer_votes[kMaxRanks]; const int* votes_all; int child_cap;   // votes: [source rank][child_cap][top_k] inner feature ids (-1: none)

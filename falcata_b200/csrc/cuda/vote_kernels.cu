@@ -14,8 +14,8 @@ constexpr int kVoteMaxFeatures = 8192;
 
 __device__ inline int NumChildren(const VoteArgs& a) { return a.ctrl != nullptr ? a.ctrl->num_children : a.num_children; }
 
-// Local totals of a child: every row falls into exactly one bin of feature group 0, so the sum of that
-// group's bins is the leaf total. The larger child's bins are still parent - smaller at this point.
+// Local totals of a child: every row falls into exactly one bin of a feature group, so the sum of one
+// constructed group's bins is the leaf total. The larger child's bins are still parent - smaller at this point.
 __global__ void VoteLocalSumsKernel(VoteArgs a) {
   if (static_cast<int>(blockIdx.x) >= NumChildren(a)) return;
   const FindChild ch = a.children[blockIdx.x];
@@ -23,12 +23,12 @@ __global__ void VoteLocalSumsKernel(VoteArgs a) {
   long long gi = 0, hi = 0; double gd = 0, hd = 0;
   for (int j = lane; j < a.g0_bins; j += 32) {
     if (a.quant) {
-      hist_q_t v = static_cast<const hist_q_t*>(a.local_pool)[static_cast<long long>(ch.slot) * a.local_stride + j];
-      if (ch.is_larger) v -= static_cast<const hist_q_t*>(a.local_pool)[static_cast<long long>(ch.other_slot) * a.local_stride + j];
+      hist_q_t v = static_cast<const hist_q_t*>(a.local_pool)[static_cast<long long>(ch.slot) * a.local_stride + a.g0_begin + j];
+      if (ch.is_larger) v -= static_cast<const hist_q_t*>(a.local_pool)[static_cast<long long>(ch.other_slot) * a.local_stride + a.g0_begin + j];
       gi += HistQGrad(v); hi += HistQHess(v);
     } else {
-      double2 v = static_cast<const double2*>(a.local_pool)[static_cast<long long>(ch.slot) * a.local_stride + j];
-      if (ch.is_larger) { const double2 o = static_cast<const double2*>(a.local_pool)[static_cast<long long>(ch.other_slot) * a.local_stride + j]; v.x -= o.x; v.y -= o.y; }
+      double2 v = static_cast<const double2*>(a.local_pool)[static_cast<long long>(ch.slot) * a.local_stride + a.g0_begin + j];
+      if (ch.is_larger) { const double2 o = static_cast<const double2*>(a.local_pool)[static_cast<long long>(ch.other_slot) * a.local_stride + a.g0_begin + j]; v.x -= o.x; v.y -= o.y; }
       gd += v.x; hd += v.y;
     }
   }

@@ -169,3 +169,15 @@ def test_categorical_training_and_device_predict():
     assert np.mean((ph - y[25000:]) ** 2) < 0.4 * np.var(y)
     pd = bst.predict(torch.from_numpy(X[25000:]).cuda()).cpu().numpy()
     np.testing.assert_allclose(pd, ph, atol=2e-4)
+
+
+def test_compact_column_view_keeps_the_model():
+    # feature_fraction 0.3: each tree constructs from a dense copy of its sampled columns only; same model as
+    # constructing from the full rows
+    X, y = make_binary(30000, 40)
+    p = {"objective": "binary", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "device_type": "cuda", "feature_fraction": 0.3,
+         "min_data_in_leaf": 5}
+    a = fb.train(dict(p, cuda_plan="auto"), fb.Dataset(X, y), 8).model_to_string()
+    b = fb.train(dict(p, cuda_plan="auto,compact_view:off"), fb.Dataset(X, y), 8).model_to_string()
+    assert model_body(a) == model_body(b)
+    assert len({int(t) for line in a.splitlines() if line.startswith("split_feature=") for t in line.split("=")[1].split()}) > 12
