@@ -588,6 +588,18 @@ Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_i
       frontier.swap(next);
     }
   }
+  if (quant_ && cfg_.quant_train_renew_leaf && tree->num_leaves > 1) {
+    // leaf values from the unquantized gradients of the rows in each leaf
+    std::vector<double> sums(2 * static_cast<size_t>(tree->num_leaves), 0.0);
+    for (int l = 0; l < tree->num_leaves; ++l) {
+      const data_size_t* idx = indices_.data() + leaves_[l].begin;
+      double g = 0, h = 0;
+      for (int k = 0; k < leaves_[l].count; ++k) { g += grad[idx[k]]; h += hess[idx[k]]; }
+      sums[2 * l] = g; sums[2 * l + 1] = h;
+    }
+    if (parallel_data_ || parallel_voting_) Network::SumDouble(sums.data(), static_cast<int64_t>(sums.size()));
+    for (int l = 0; l < tree->num_leaves; ++l) tree->SetLeafOutput(l, LeafOutputRaw(sums[2 * l], sums[2 * l + 1] + kEpsilon, sp_));
+  }
   return tree.release();
 }
 

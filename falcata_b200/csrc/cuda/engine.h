@@ -60,6 +60,8 @@ class CudaEngine : public DeviceEngine {
   void RunRootHistogram();
   void ReadBackLevel(int num_leaves);
   void DrawBag(int round);
+  void RenewLeavesFromTrueGradients(Tree* tree);
+  void RenewLeavesByObjective(Tree* tree, int class_id);
   void SetupBitmapBroadcast(PartArgs* pa);
   const uint8_t* bag_mask_ptr() const { return bag_active_ ? bag_mask_.get() : nullptr; }
   void UploadTreeForTraversal(const Tree& tree, const Dataset* ds, DevTree* out);
@@ -111,7 +113,7 @@ class CudaEngine : public DeviceEngine {
   DevBuf<HistTask> hist_tasks_;
   DevBuf<unsigned int> bits_; DevBuf<int> chunk_left_, split_left_total_;
   DevBuf<int> features_, sub_features_;
-  DevBuf<double> leaf_value_;
+  DevBuf<double> leaf_value_, renew_partial_; PinnedBuf<double> h_renew_partial_;
   PinnedBuf<LeafInfo> h_leaves_; PinnedBuf<SplitRecord> h_best_;
   std::vector<HostLeaf> host_leaves_;
   std::vector<ValidSet> valid_;

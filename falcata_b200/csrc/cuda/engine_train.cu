@@ -84,6 +84,8 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
     } else tree.reset(new Tree(2));
     if (tree->num_leaves > 1) {
       any_split = true;
+      if (quant_ && cfg_.quant_train_renew_leaf) RenewLeavesFromTrueGradients(tree.get());
+      else if (obj_ != nullptr && obj_->IsRenewTreeOutput()) RenewLeavesByObjective(tree.get(), k);
       tree->Shrink(shrinkage);
       // training rows through the final partition; validation rows by traversal
       clock_.Begin(st_score_, stream_);
@@ -430,6 +432,42 @@ void CudaEngine::SetupBitmapBroadcast(PartArgs* pa) {
   }
   pa->bc_sig.world = world_; pa->bc_sig.done_counter = fabric_->done_counter(2);
   pa->bc_wait.world = world_; pa->bc_wait.flags = fabric_->Local<unsigned int>(flag_part_); pa->bc_wait.max_spins = v.max_spins; pa->bc_wait.status = v.status;
+}
+
+// K6r: leaf values recomputed from the unquantized gradients of the rows that ended up in each leaf.
+// Parity: src/treelearner/cuda/cuda_single_gpu_tree_learner.cu:L20-79 (renew from true gradients), gradient_discretizer.cpp (RenewIntGradTreeOutput).
+void CudaEngine::RenewLeavesFromTrueGradients(Tree* tree) {
+  const int nl = tree->num_leaves, slices = LeafGradSumSlices();
+  if (renew_partial_.size() < static_cast<size_t>(2) * nl * slices) { renew_partial_.Alloc(static_cast<size_t>(2) * cfg_.num_leaves * slices); h_renew_partial_.Alloc(static_cast<size_t>(2) * cfg_.num_leaves * slices); }
+  LaunchLeafGradSums(leaves_.get(), nl, idx_[0].get(), idx_[1].get(), cur_grad_, cur_hess_, renew_partial_.get(), stream_);
+  renew_partial_.Download(h_renew_partial_.get(), static_cast<size_t>(2) * nl * slices, stream_);
+  FB_CUDA(cudaStreamSynchronize(stream_));
+  std::vector<double> sums(2 * static_cast<size_t>(nl), 0.0);
+  for (int l = 0; l < nl; ++l) for (int s = 0; s < slices; ++s) { sums[2 * l] += h_renew_partial_[2 * (l * slices + s)]; sums[2 * l + 1] += h_renew_partial_[2 * (l * slices + s) + 1]; }
+  if (data_parallel()) Network::SumDouble(sums.data(), static_cast<int64_t>(sums.size()));
+  for (int l = 0; l < nl; ++l) tree->SetLeafOutput(l, LeafOutputRaw(sums[2 * l], sums[2 * l + 1] + kEpsilon, sp_));
+}
+
+// Objectives whose leaf value is a statistic of the residuals (L1: median, quantile: the alpha-quantile): the
+// leaf windows and the scores come back to the host and the objective's own renewal runs there.
+void CudaEngine::RenewLeavesByObjective(Tree* tree, int class_id) {
+  const int nl = tree->num_leaves;
+  leaves_.Download(h_leaves_.get(), nl, stream_);
+  std::vector<int> h_idx0(n_), h_idx1(n_); std::vector<float> h_score(n_);
+  FB_CUDA(cudaMemcpyAsync(h_idx0.data(), idx_[0].get(), sizeof(int) * n_, cudaMemcpyDeviceToHost, stream_));
+  FB_CUDA(cudaMemcpyAsync(h_idx1.data(), idx_[1].get(), sizeof(int) * n_, cudaMemcpyDeviceToHost, stream_));
+  FB_CUDA(cudaMemcpyAsync(h_score.data(), score_.get() + static_cast<size_t>(class_id) * n_, sizeof(float) * n_, cudaMemcpyDeviceToHost, stream_));
+  FB_CUDA(cudaStreamSynchronize(stream_));
+  std::vector<double> sc(h_score.begin(), h_score.end());
+  std::vector<double> outs(nl, 0.0), have(nl, 0.0);
+  for (int l = 0; l < nl; ++l) {
+    const LeafInfo& L = h_leaves_[l];
+    if (L.count <= 0) continue;
+    const int* w = (L.buffer ? h_idx1.data() : h_idx0.data()) + L.begin;
+    outs[l] = obj_->RenewTreeOutput(tree->leaf_value[l], sc.data(), w, L.count); have[l] = 1.0;
+  }
+  if (data_parallel()) { Network::SumDouble(outs.data(), nl); Network::SumDouble(have.data(), nl); }   // ranks' statistics are averaged
+  for (int l = 0; l < nl; ++l) if (have[l] > 0) tree->SetLeafOutput(l, outs[l] / have[l]);
 }
 
 // A new bag: flags by global row id, compaction of the in-bag rows, and the (global) bag size.

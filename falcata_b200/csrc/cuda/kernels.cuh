@@ -220,6 +220,9 @@ void LaunchBagging(const BagArgs& a, cudaStream_t s);
 // ----------------------------------------------------------------- score ----
 void LaunchAddLeafOutputs(const LeafInfo* leaves, const double* leaf_value, int num_leaves, const int* idx0, const int* idx1, float* score, cudaStream_t s);
 void LaunchAddConstant(float* score, int n, float v, cudaStream_t s);
+// per-leaf (sum g, sum h) of float gradients over the leaf windows: partial[2 * (leaf * slices + slice) + {0,1}]
+int LeafGradSumSlices();
+void LaunchLeafGradSums(const LeafInfo* leaves, int num_leaves, const int* idx0, const int* idx1, const float* grad, const float* hess, double* partial, cudaStream_t s);
 
 // Device form of one tree for traversal.
 struct DevTree {

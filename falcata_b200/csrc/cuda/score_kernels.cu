@@ -22,6 +22,23 @@ __global__ void AddLeafOutputsKernel(const LeafInfo* __restrict__ leaves, const 
   for (int p = blockIdx.y * blockDim.x + threadIdx.x; p < L.count; p += gridDim.y * blockDim.x) score[idx[p]] += v;
 }
 
+// K6r: per-leaf sums of the TRUE (unquantized) gradients over the final partition, for leaf renewal.
+// grid (leaf, kRenewSlices): every slice walks a strided part of the leaf's window and reduces in a fixed
+// order; the host adds the slices (and the ranks) in a fixed order too.
+constexpr int kRenewSlices = 32;
+__global__ void __launch_bounds__(256) LeafGradSumsKernel(const LeafInfo* __restrict__ leaves, const int* __restrict__ idx0, const int* __restrict__ idx1,
+                                                          const float* __restrict__ grad, const float* __restrict__ hess, double* __restrict__ partial) {
+  const LeafInfo L = leaves[blockIdx.x];
+  const int* idx = (L.buffer ? idx1 : idx0) + L.begin;
+  double g = 0, h = 0;
+  for (int p = blockIdx.y * blockDim.x + threadIdx.x; p < L.count; p += gridDim.y * blockDim.x) { const int r = idx[p]; g += grad[r]; h += hess[r]; }
+  __shared__ double sg[256], sh[256];
+  sg[threadIdx.x] = g; sh[threadIdx.x] = h;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) { if (threadIdx.x < o) { sg[threadIdx.x] += sg[threadIdx.x + o]; sh[threadIdx.x] += sh[threadIdx.x + o]; } __syncthreads(); }
+  if (threadIdx.x == 0) { partial[2 * (blockIdx.x * gridDim.y + blockIdx.y)] = sg[0]; partial[2 * (blockIdx.x * gridDim.y + blockIdx.y) + 1] = sh[0]; }
+}
+
 __global__ void AddConstantKernel(float* score, int n, float v) { const int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < n) score[i] += v; }
 
 __global__ void AddTreeBinnedKernel(DevTree t, const uint8_t* __restrict__ rows, int row_stride, int n, float scale, float* __restrict__ score) {
@@ -159,6 +176,12 @@ __global__ void SumPartials2Kernel(const double* __restrict__ partial, int nbloc
 void LaunchAddLeafOutputs(const LeafInfo* leaves, const double* leaf_value, int num_leaves, const int* idx0, const int* idx1, float* score, cudaStream_t s) {
   if (num_leaves <= 0) return;
   AddLeafOutputsKernel<<<dim3(num_leaves, 64), 256, 0, s>>>(leaves, leaf_value, idx0, idx1, score);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+int LeafGradSumSlices() { return kRenewSlices; }
+void LaunchLeafGradSums(const LeafInfo* leaves, int num_leaves, const int* idx0, const int* idx1, const float* grad, const float* hess, double* partial, cudaStream_t s) {
+  if (num_leaves <= 0) return;
+  LeafGradSumsKernel<<<dim3(num_leaves, kRenewSlices), 256, 0, s>>>(leaves, idx0, idx1, grad, hess, partial);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 void LaunchAddConstant(float* score, int n, float v, cudaStream_t s) {

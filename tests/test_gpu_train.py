@@ -181,3 +181,23 @@ def test_compact_column_view_keeps_the_model():
     b = fb.train(dict(p, cuda_plan="auto,compact_view:off"), fb.Dataset(X, y), 8).model_to_string()
     assert model_body(a) == model_body(b)
     assert len({int(t) for line in a.splitlines() if line.startswith("split_feature=") for t in line.split("=")[1].split()}) > 12
+
+
+def test_leaf_renewal_on_device():
+    # (a) quantized training with leaf values renewed from the true gradients: close to the host arm and to the
+    #     un-renewed quantized model (stochastic rounding is unbiased, so neither is systematically better)
+    X, y = make_regression(20000, 10)
+    p = {"objective": "regression", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "quant_bins": 4, "grow_policy": "level"}
+    mse = lambda b: float(np.mean((b.predict(X) - y) ** 2))
+    plain = fb.train({**p, "device_type": "cuda"}, fb.Dataset(X, y), 20)
+    renew = fb.train({**p, "device_type": "cuda", "quant_train_renew_leaf": True}, fb.Dataset(X, y), 20)
+    host = fb.train({**p, "device_type": "cpu", "quant_train_renew_leaf": True}, fb.Dataset(X, y), 20)
+    assert renew.model_to_string() != plain.model_to_string() and mse(renew) < 1.1 * mse(plain)
+    assert abs(mse(renew) - mse(host)) < 0.05 * mse(host)
+    # (b) L1 regression: leaf values are medians of the residuals (objective-side renewal)
+    yl = y + (np.random.RandomState(3).rand(len(y)) < 0.05) * 50.0   # heavy outliers
+    pl = {"objective": "regression_l1", "num_leaves": 31, "verbosity": -1, "grow_policy": "level"}
+    dev = fb.train({**pl, "device_type": "cuda"}, fb.Dataset(X, yl), 30)
+    cpu = fb.train({**pl, "device_type": "cpu"}, fb.Dataset(X, yl), 30)
+    mae = lambda b: float(np.mean(np.abs(b.predict(X) - yl)))
+    assert abs(mae(dev) - mae(cpu)) < 0.05 * mae(cpu)
