@@ -8,10 +8,13 @@ from .basic import (Booster, Dataset, FalcataError, LightGBMError, cuda_availabl
                     time_tag_report)
 from .callback import EarlyStopException, early_stopping, log_evaluation, record_evaluation, reset_parameter
 from .engine import CVBooster, cv, train
+from .importers import from_catboost, from_xgboost
+from .oblique import ObliquePool
+from .plotting import create_tree_digraph, plot_importance, plot_metric, plot_split_value_histogram, plot_tree
 
 __version__ = "0.1.0"
 
-__all__ = ["Dataset", "Booster", "CVBooster", "train", "cv", "FalcataError", "LightGBMError", "register_logger", "cuda_available", "set_time_tag", "set_num_threads", "get_num_threads", "time_tag_report",
+__all__ = ["from_xgboost", "from_catboost", "ObliquePool", "plot_importance", "plot_metric", "plot_split_value_histogram", "plot_tree", "create_tree_digraph","Dataset", "Booster", "CVBooster", "train", "cv", "FalcataError", "LightGBMError", "register_logger", "cuda_available", "set_time_tag", "set_num_threads", "get_num_threads", "time_tag_report",
            "early_stopping", "log_evaluation", "record_evaluation", "reset_parameter", "EarlyStopException"]
 
 try:  # sklearn-style estimators are optional (scikit-learn may be absent)

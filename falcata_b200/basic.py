@@ -781,9 +781,16 @@ class Booster:
         return "regression"
 
     # -- model IO ---------------------------------------------------------------------
-    def save_model(self, filename: Union[str, Path], num_iteration: Optional[int] = None, start_iteration: int = 0, importance_type: str = "split") -> "Booster":
+    def save_model(self, filename: Union[str, Path], num_iteration: Optional[int] = None, start_iteration: int = 0, importance_type: str = "split",
+                   format: str = "txt", f32_leaves: bool = False, **_ignored: Any) -> "Booster":
+        """Write the model as LightGBM-compatible text (``format="txt"``) or as compressed binary FALB (``format="falb"``)."""
         if num_iteration is None:
             num_iteration = self.best_iteration
+        if format == "falb":
+            Path(filename).write_bytes(self.model_to_binary(num_iteration, start_iteration, f32_leaves))
+            return self
+        if format not in ("txt", "text"):
+            raise ValueError("format must be 'txt' or 'falb'")
         _safe_call(_lib().FB_BoosterSaveModel(self._handle, start_iteration, num_iteration, 0 if importance_type == "split" else 1, str(filename).encode()))
         return self
 

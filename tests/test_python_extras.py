@@ -1,0 +1,66 @@
+"""Model conversion CLI, plotting data helpers and the oblique projection pool (all host side)."""
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import falcata_b200 as fb
+from falcata_b200 import plotting
+from util import make_binary
+
+
+@pytest.fixture(scope="module")
+def small_model():
+    X, y = make_binary(3000, 8)
+    res = {}
+    ds = fb.Dataset(X[:2400], y[:2400]); dv = ds.create_valid(X[2400:], y[2400:])
+    bst = fb.train({"objective": "binary", "num_leaves": 15, "verbosity": -1, "device_type": "cpu", "metric": "binary_logloss,auc"}, ds, 20, valid_sets=[dv],
+                   callbacks=[fb.record_evaluation(res)])
+    return bst, res, X
+
+
+def test_convert_cli_round_trip(tmp_path, small_model):
+    bst, _, X = small_model
+    txt, falb, back = tmp_path / "m.txt", tmp_path / "m.falb", tmp_path / "back.txt"
+    bst.save_model(txt)
+    for a, b in ((txt, falb), (falb, back)):
+        r = subprocess.run([sys.executable, "-m", "falcata_b200", "convert", str(a), str(b)], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+    assert falb.stat().st_size < txt.stat().st_size
+    assert falb.read_bytes()[:4] == b"FALB"
+    np.testing.assert_allclose(fb.Booster(model_file=str(back)).predict(X), bst.predict(X))
+    np.testing.assert_allclose(fb.Booster(model_file=str(falb)).predict(X), bst.predict(X))
+
+
+def test_plot_data_helpers(small_model):
+    bst, res, X = small_model
+    table = plotting.importance_table(bst)
+    assert table == sorted(table, key=lambda p: p[1]) and sum(v for _, v in table) == bst.feature_importance().sum()
+    used = table[-1][0]
+    counts, edges = plotting.split_value_histogram(bst, used)
+    assert counts.sum() == dict(table)[used] and len(edges) == len(counts) + 1
+    name, curves = plotting.metric_curves(res, "auc")
+    assert name == "auc" and len(curves["valid_0"]) == 20
+    dot = plotting.tree_to_dot(bst, 0, show_info=["split_gain", "leaf_count"], example_case=X[0])
+    assert dot.startswith("digraph") and dot.count("->") == 2 * (dot.count("<=")) and "lightblue" in dot and "leaf_count" in dot
+    with pytest.raises(ImportError):
+        plotting.plot_importance(bst)   # matplotlib is not part of this environment
+
+
+def test_oblique_pool(tmp_path):
+    rng = np.random.RandomState(0)
+    X = rng.randn(4000, 6)
+    X[rng.rand(*X.shape) < 0.02] = np.nan
+    y = ((np.nan_to_num(X[:, 0]) + np.nan_to_num(X[:, 1]) - np.nan_to_num(X[:, 2])) > 0).astype(np.float64)   # oblique boundary
+    pool = fb.ObliquePool(num_projections=64, density=3, seed=17)
+    Xa = pool.fit_transform(X)
+    assert Xa.shape == (4000, 6 + 64) and not np.isnan(Xa[:, 6:]).any() and len(pool.feature_names()) == 70
+    pool.save(tmp_path / "pool.json")
+    again = fb.ObliquePool.load(tmp_path / "pool.json")
+    np.testing.assert_allclose(again.transform(X), Xa)
+    p = {"objective": "binary", "num_leaves": 7, "verbosity": -1, "device_type": "cpu"}
+    acc = lambda b, M: float(((b.predict(M[3000:]) > 0.5) == y[3000:]).mean())
+    plain = fb.train(p, fb.Dataset(X[:3000], y[:3000]), 15)
+    aug = fb.train(p, fb.Dataset(Xa[:3000], y[:3000]), 15)
+    assert acc(aug, Xa) >= acc(plain, X) - 0.01
