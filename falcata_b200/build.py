@@ -83,7 +83,22 @@ def build(force: bool = False, ptxas: bool = False, verbose: bool = False) -> Pa
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
     if ptxas:
         print("\n".join(logs))
+    _build_cli()
     return LIB
+
+
+def _build_cli() -> Path:
+    """The command-line application (train / predict / convert_model / refit / save_binary), linked against the core library."""
+    src = CSRC / "cli" / "main.cpp"
+    exe = LIB.parent.parent / "bin" / "falcata"
+    exe.parent.mkdir(parents=True, exist_ok=True)
+    if exe.exists() and exe.stat().st_mtime >= max(src.stat().st_mtime, LIB.stat().st_mtime):
+        return exe
+    cmd = [CXX, *COMMON, "-ffp-contract=off", str(src), "-o", str(exe), f"-L{LIB.parent}", "-lfalcata_core", "-Wl,-rpath,$ORIGIN/../lib"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"CLI build failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    return exe
 
 
 if __name__ == "__main__":

@@ -351,6 +351,26 @@ int FB_BoosterPredictForMat(BoosterHandle handle, const void* data, int dtype, i
   b->gbdt->PredictMat(data, dtype, nrow, ncol, is_row_major != 0, predict_type, start_iteration, num_iteration, out_result);
   API_END();
 }
+// Predict every row of a text data file (CSV / TSV / LibSVM) and write one line per row (tab-separated
+// values for multi-output predictions). Parity: src/c_api.cpp LGBM_BoosterPredictForFile, src/application/predictor.hpp.
+int FB_BoosterPredictForFile(BoosterHandle handle, const char* data_filename, int data_has_header, int predict_type, int start_iteration, int num_iteration,
+                             const char* parameter, const char* result_filename) {
+  API_BEGIN(); BW();
+  Config cfg; auto m = Config::Str2Map(parameter); m["header"] = data_has_header ? "true" : "false";
+  cfg.Set(m, CudaAvailable());
+  ParsedFile pf;
+  ParseDataFile(data_filename, cfg, b->gbdt->max_feature_idx_ + 1, &pf);
+  const int per_row = b->gbdt->NumPredictOneRow(predict_type, start_iteration, num_iteration);
+  std::vector<double> out(static_cast<size_t>(pf.num_rows) * per_row);
+  b->gbdt->PredictMat(pf.dense.data(), kF64, pf.num_rows, pf.num_features, true, predict_type, start_iteration, num_iteration, out.data());
+  std::ofstream f(result_filename);
+  if (!f) Log::Fatal("Prediction results file %s cannot be written", result_filename);
+  for (data_size_t i = 0; i < pf.num_rows; ++i) {
+    for (int k = 0; k < per_row; ++k) { if (k) f << '\t'; f << DoubleToStr17(out[static_cast<size_t>(i) * per_row + k]); }
+    f << '\n';
+  }
+  API_END();
+}
 int FB_BoosterPredictForDeviceMat(BoosterHandle handle, const void* device_data, int dtype, int32_t nrow, int32_t ncol, int is_row_major,
                                   int predict_type, int start_iteration, int num_iteration, float* out_device) {
   API_BEGIN(); BW();

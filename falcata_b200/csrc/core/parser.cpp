@@ -37,7 +37,7 @@ std::vector<double> ReadSideFile(const std::string& path) {
 
 }  // namespace
 
-Dataset* LoadDatasetFromFile(const std::string& path, const Config& cfg, const Dataset* reference) {
+void ParseDataFile(const std::string& path, const Config& cfg, int force_num_features, ParsedFile* out) {
   std::ifstream f(path);
   if (!f) Log::Fatal("Data file %s doesn't exist", path.c_str());
   std::vector<std::string> lines; std::string line;
@@ -88,10 +88,19 @@ Dataset* LoadDatasetFromFile(const std::string& path, const Config& cfg, const D
     col2feat[c] = nfeat++;
     names.push_back(c < static_cast<int>(header.size()) ? header[c] : "Column_" + std::to_string(nfeat - 1));
   }
-  if (reference != nullptr) nfeat = reference->num_total_features;
+  if (force_num_features > 0) nfeat = force_num_features;
   std::vector<double> dense(static_cast<size_t>(n) * nfeat, 0.0);
   for (data_size_t i = 0; i < n; ++i) for (auto& kv : rows[i]) { if (kv.first < ncol_raw && col2feat[kv.first] >= 0 && col2feat[kv.first] < nfeat) dense[static_cast<size_t>(i) * nfeat + col2feat[kv.first]] = kv.second; }
+  out->num_rows = n; out->num_features = nfeat; out->dense.swap(dense); out->label.swap(label); out->weight.swap(weight); out->group_ids.swap(groupv);
+  out->names.swap(names); out->has_header = !header.empty();
+}
 
+Dataset* LoadDatasetFromFile(const std::string& path, const Config& cfg, const Dataset* reference) {
+  ParsedFile pf;
+  ParseDataFile(path, cfg, reference != nullptr ? reference->num_total_features : 0, &pf);
+  const data_size_t n = pf.num_rows; const int nfeat = pf.num_features;
+  std::vector<double>& dense = pf.dense; std::vector<float>& label = pf.label; std::vector<float>& weight = pf.weight; std::vector<double>& groupv = pf.group_ids;
+  std::vector<std::string>& names = pf.names;
   std::unique_ptr<Dataset> ds(new Dataset());
   if (reference != nullptr) ds->CopySchemaFrom(*reference);
   else {
@@ -101,7 +110,7 @@ Dataset* LoadDatasetFromFile(const std::string& path, const Config& cfg, const D
     for (size_t r = 0; r < idx.size(); ++r) memcpy(&sample[r * nfeat], &dense[static_cast<size_t>(idx[r]) * nfeat], nfeat * sizeof(double));
     std::vector<int> cats;
     for (auto& t : SplitAny(cfg.categorical_feature, ",")) { std::string s = Trim(t); if (StartsWith(s, "name:")) { for (size_t k = 0; k < names.size(); ++k) if (names[k] == s.substr(5)) cats.push_back(static_cast<int>(k)); } else if (!s.empty()) cats.push_back(atoi(s.c_str())); }
-    if (!header.empty()) ds->feature_names = names;
+    if (pf.has_header) ds->feature_names = names;
     ds->ConstructSchema(sample.data(), static_cast<int>(idx.size()), nfeat, n, cfg, cats);
   }
   ds->AllocateRows(n);

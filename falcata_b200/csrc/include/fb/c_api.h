@@ -81,6 +81,8 @@ int FB_BoosterCalcNumPredict(BoosterHandle handle, int num_row, int predict_type
 int FB_BoosterPredictForMat(BoosterHandle handle, const void* data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, int predict_type,
                             int start_iteration, int num_iteration, const char* parameter, int64_t* out_len, double* out_result);
 /* Device traversal predict: data and out_result are device pointers (out: f32, class-major when raw/normal). */
+int FB_BoosterPredictForFile(BoosterHandle handle, const char* data_filename, int data_has_header, int predict_type, int start_iteration,
+                             int num_iteration, const char* parameter, const char* result_filename);
 int FB_BoosterPredictForDeviceMat(BoosterHandle handle, const void* device_data, int dtype, int32_t nrow, int32_t ncol, int is_row_major,
                                   int predict_type, int start_iteration, int num_iteration, float* out_device);
 int FB_BoosterSaveModel(BoosterHandle handle, int start_iteration, int num_iteration, int feature_importance_type, const char* filename);

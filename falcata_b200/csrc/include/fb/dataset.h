@@ -124,5 +124,11 @@ enum DType : int { kF32 = 0, kF64 = 1, kI8 = 2, kI16 = 3, kU8 = 4, kU16 = 5, kF1
 
 // Text file loader (CSV / TSV / LibSVM with optional header, label/weight/group columns).
 Dataset* LoadDatasetFromFile(const std::string& path, const Config& cfg, const Dataset* reference);
+// A text data file (CSV / TSV / LibSVM) as a dense row-major matrix plus its label / weight / group columns.
+struct ParsedFile {
+  data_size_t num_rows = 0; int num_features = 0; bool has_header = false;
+  std::vector<double> dense; std::vector<float> label, weight; std::vector<double> group_ids; std::vector<std::string> names;
+};
+void ParseDataFile(const std::string& path, const Config& cfg, int force_num_features, ParsedFile* out);
 
 }  // namespace fb
