@@ -50,7 +50,6 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
     is_goss_ = cfg.data_sample_strategy == "goss";
     is_bagging_ = !is_goss_ && cfg.bagging_freq > 0 && (cfg.bagging_fraction < 1.0 || cfg.pos_bagging_fraction < 1.0 || cfg.neg_bagging_fraction < 1.0);
     if (engine_ && is_bagging_) engine_->SetBagging(cfg.bagging_fraction, cfg.bagging_freq, cfg.bagging_seed);
-    if (engine_ && is_goss_) { Log::Warning("GOSS sampling runs on the host learner only; the device engine trains on all rows"); is_goss_ = false; }
     if (!engine_) bag_indices_.resize(train->num_data);   // the device engine draws its own bags
   }
 }
@@ -117,15 +116,16 @@ void GBDT::Bagging(int iter, const float* grad, const float* hess) {
     std::vector<float> tmp(mag); std::nth_element(tmp.begin(), tmp.begin() + (top_k - 1), tmp.end(), std::greater<float>());
     const float thr = tmp[top_k - 1];
     const float multiply = static_cast<float>(n - top_k) / std::max<data_size_t>(1, other_k);
-    data_size_t cnt = 0, rest_need = other_k, rest_all = n - top_k;
+    // the small-gradient rows are kept independently with probability other_k / (n - top_k): a draw keyed on the
+    // global row id, so the device engine and any rank count make the same choice
+    data_size_t cnt = 0;
+    const double prob = n > top_k ? static_cast<double>(other_k) / static_cast<double>(n - top_k) : 0.0;
     float* g = const_cast<float*>(grad); float* h = const_cast<float*>(hess);
     for (data_size_t i = 0; i < n; ++i) {
       if (mag[i] >= thr) { bag_indices_[cnt++] = i; continue; }
       const float u = U01From24(Philox4x32_10(static_cast<uint32_t>(train_->global_row_offset + i), static_cast<uint32_t>(iter), 0x60550000u, 0, static_cast<uint32_t>(config_.bagging_seed), 0x1234u).v[0]);
-      const double prob = rest_all > 0 ? static_cast<double>(rest_need) / rest_all : 0.0;
-      --rest_all;
-      if (u < prob) {
-        bag_indices_[cnt++] = i; --rest_need;
+      if (static_cast<double>(u) < prob) {
+        bag_indices_[cnt++] = i;
         for (int k = 0; k < num_tree_per_iteration_; ++k) { g[static_cast<size_t>(k) * n + i] *= multiply; h[static_cast<size_t>(k) * n + i] *= multiply; }
       }
     }

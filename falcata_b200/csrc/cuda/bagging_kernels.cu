@@ -4,6 +4,8 @@
 // Parity: src/boosting/cuda/cuda_bagging.cu:L43-114 (flags + scan + scatter), src/boosting/bagging.hpp.
 #include "kernels.cuh"
 
+#include <cub/device/device_radix_sort.cuh>
+
 namespace fb {
 
 namespace {
@@ -81,7 +83,52 @@ __global__ void __launch_bounds__(kBagChunk) BagScatterKernel(BagArgs a) {
   if (in) a.bag_idx[a.chunk_count[blockIdx.x] + warp_cnt[w] + __popc(b & ((1u << lane) - 1u))] = i;
 }
 
+__global__ void GossMagnitudeKernel(GossArgs a) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= a.n) return;
+  float m = 0.f;
+  for (int k = 0; k < a.num_class; ++k) m += fabsf(a.grad[static_cast<size_t>(k) * a.n + i] * a.hess[static_cast<size_t>(k) * a.n + i]);
+  a.mag[i] = m;
+}
+
+__global__ void __launch_bounds__(kBagChunk) GossFlagsKernel(GossArgs a) {
+  const int i = blockIdx.x * kBagChunk + threadIdx.x;
+  int in = 0;
+  if (i < a.n) {
+    const float thr = a.sorted[a.top_k - 1];   // the top_k-th largest magnitude
+    if (a.mag[i] >= thr) in = 1;
+    else {
+      const float u = U01From24(Philox4x32_10(static_cast<uint32_t>(a.global_row_offset + static_cast<unsigned long long>(i)), a.iter, 0x60550000u, 0u, a.seed, 0x1234u).v[0]);
+      if (static_cast<double>(u) < a.prob) {
+        in = 1;
+        for (int k = 0; k < a.num_class; ++k) { a.grad[static_cast<size_t>(k) * a.n + i] *= a.multiply; a.hess[static_cast<size_t>(k) * a.n + i] *= a.multiply; }
+      }
+    }
+    a.mask[i] = static_cast<uint8_t>(in);
+  }
+  const int cnt = __syncthreads_count(in);
+  if (threadIdx.x == 0) a.chunk_count[blockIdx.x] = cnt;
+}
+
 }  // namespace
+
+size_t GossSortTempBytes(int n) {
+  size_t bytes = 0;
+  cub::DeviceRadixSort::SortKeysDescending(nullptr, bytes, static_cast<const float*>(nullptr), static_cast<float*>(nullptr), n);
+  return bytes;
+}
+
+void LaunchGoss(const GossArgs& a, cudaStream_t s) {
+  if (a.n <= 0) { FB_CUDA(cudaMemsetAsync(a.bag_count, 0, sizeof(int), s)); return; }
+  GossMagnitudeKernel<<<(a.n + 255) / 256, 256, 0, s>>>(a); FB_LAUNCHED(); FB_KERNEL_CHECK();
+  size_t bytes = a.sort_temp_bytes;
+  FB_CUDA(cub::DeviceRadixSort::SortKeysDescending(a.sort_temp, bytes, a.mag, a.sorted, a.n, 0, 32, s)); FB_LAUNCHED();
+  const int chunks = (a.n + kBagChunk - 1) / kBagChunk;
+  GossFlagsKernel<<<chunks, kBagChunk, 0, s>>>(a); FB_LAUNCHED(); FB_KERNEL_CHECK();
+  BagScanKernel<<<1, 1024, 0, s>>>(a.chunk_count, chunks, a.bag_count); FB_LAUNCHED(); FB_KERNEL_CHECK();
+  BagArgs b = BagArgs(); b.n = a.n; b.mask = a.mask; b.bag_idx = a.bag_idx; b.chunk_count = a.chunk_count; b.bag_count = a.bag_count;
+  BagScatterKernel<<<chunks, kBagChunk, 0, s>>>(b); FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
 
 void LaunchBagging(const BagArgs& a, cudaStream_t s) {
   if (a.n <= 0) { FB_CUDA(cudaMemsetAsync(a.bag_count, 0, sizeof(int), s)); return; }

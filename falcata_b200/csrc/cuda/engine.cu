@@ -314,6 +314,33 @@ std::vector<double> CudaEngine::EvalMetric(int data_idx, const std::string& name
   if (name == "l2") kind = kMetL2; else if (name == "rmse") kind = kMetRMSE; else if (name == "l1") kind = kMetL1;
   else if (name == "binary_logloss") kind = kMetBinaryLogloss; else if (name == "binary_error") kind = kMetBinaryError;
   else if (name == "multi_logloss") kind = kMetMultiLogloss; else if (name == "multi_error" && cfg_.multi_error_top_k == 1) kind = kMetMultiError;
+  if (name == "auc" || name == "ndcg") {
+    const Dataset* ds = data_idx == 0 ? train_ : valid_[data_idx - 1].ds;
+    DeviceDataset* dd = data_idx == 0 ? dd_ : valid_[data_idx - 1].dd;
+    const float* score = data_idx == 0 ? score_.get() : valid_[data_idx - 1].score.get();
+    if (dd->label.size() == 0 || ds->num_data == 0) return {};
+    if (name == "auc") {
+      // rows sharded over ranks: the exact AUC needs every (positive, negative) pair, so the host metric gathers the scores
+      if (data_parallel() || K_ != 1) return {};
+      double r[3];
+      DeviceAuc(score, dd->label.get(), dd->weight.size() ? dd->weight.get() : nullptr, ds->num_data, r, stream_);
+      *supported = true;
+      return {r[0]};
+    }
+    if (dd->num_queries <= 0 || !ds->metadata.query_weights.empty() || cfg_.eval_at_vec.empty()) return {};
+    int max_docs = 0; const auto& qb = ds->metadata.query_boundaries;
+    for (size_t q = 0; q + 1 < qb.size(); ++q) max_docs = std::max(max_docs, qb[q + 1] - qb[q]);
+    if (metric_gain_.size() == 0) metric_gain_.Upload(cfg_.label_gain_vec, stream_);
+    std::vector<double> sums(cfg_.eval_at_vec.size() + 1, 0.0);
+    if (!DeviceNdcgSums(score, dd->label.get(), dd->query_boundaries.get(), dd->num_queries, max_docs, metric_gain_.get(), static_cast<int>(metric_gain_.size()),
+                        cfg_.eval_at_vec, sums.data(), stream_)) return {};
+    sums[cfg_.eval_at_vec.size()] = dd->num_queries;
+    if (data_parallel()) Network::SumDouble(sums.data(), static_cast<int64_t>(sums.size()));   // queries are sharded whole: per-query values add up
+    std::vector<double> out(cfg_.eval_at_vec.size());
+    for (size_t j = 0; j < out.size(); ++j) out[j] = sums[j] / sums[cfg_.eval_at_vec.size()];
+    *supported = true;
+    return out;
+  }
   if (kind < 0) return {};
   if ((kind == kMetL2 || kind == kMetRMSE || kind == kMetL1) && cfg_.reg_sqrt) return {};
   const Dataset* ds = data_idx == 0 ? train_ : valid_[data_idx - 1].ds;

@@ -60,6 +60,7 @@ class CudaEngine : public DeviceEngine {
   void RunRootHistogram();
   void ReadBackLevel(int num_leaves);
   void DrawBag(int round);
+  void DrawGoss(int iter);
   void RenewLeavesFromTrueGradients(Tree* tree);
   void RenewLeavesByObjective(Tree* tree, int class_id);
   void SetupBitmapBroadcast(PartArgs* pa);
@@ -81,7 +82,7 @@ class CudaEngine : public DeviceEngine {
 
   DevBuf<float> score_, grad_, hess_, maxbuf_, scales_;
   DevBuf<long long> root_sums_i_;
-  DevBuf<double> root_sums_d_, partial_, label_gain_;
+  DevBuf<double> root_sums_d_, partial_, label_gain_, metric_gain_;
   DevBuf<int32_t> gh_sep_;
   DevBuf<float2> gh2_;
   const uint8_t* gh_base_ = nullptr; int gh_stride_ = 0;
@@ -130,6 +131,7 @@ class CudaEngine : public DeviceEngine {
   // bagging (device-drawn; -1 = no bag drawn)
   double bag_fraction_ = 1.0; int bag_freq_ = 0, bag_seed_ = 0;
   bool bag_active_ = false; int bag_count_ = -1, root_count_ = 0; long long bag_global_ = 0, root_global_ = 0;
+  DevBuf<float> goss_mag_, goss_sorted_; DevBuf<char> goss_temp_;
   DevBuf<uint8_t> bag_mask_; DevBuf<int> bag_idx_, bag_chunk_, bag_count_dev_; PinnedBuf<int> h_bag_count_;
   int max_docs_ = 0;
 };

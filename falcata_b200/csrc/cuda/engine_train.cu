@@ -54,7 +54,9 @@ int ApplySplit(Tree* tree, const Dataset* ds, int leaf, const SplitRecord& b) {
 void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess, int iter, double shrinkage, const std::vector<double>& init_scores,
                               std::vector<std::unique_ptr<Tree>>* out, bool* all_constant) {
   const float* grad = grad_.get(); const float* hess = hess_.get();
-  const bool bagging = bag_freq_ > 0 && (cfg_.bagging_fraction < 1.0 || cfg_.pos_bagging_fraction < 1.0 || cfg_.neg_bagging_fraction < 1.0);
+  const bool goss = cfg_.data_sample_strategy == "goss" && iter >= static_cast<int>(1.0 / cfg_.learning_rate);
+  bool bagging = !goss && cfg_.data_sample_strategy != "goss" && bag_freq_ > 0 &&
+                 (cfg_.bagging_fraction < 1.0 || cfg_.pos_bagging_fraction < 1.0 || cfg_.neg_bagging_fraction < 1.0);
   if (bagging && (iter % bag_freq_ == 0 || bag_count_ < 0)) DrawBag(iter / bag_freq_);
   bag_active_ = bagging;
   const uint8_t* mask = bag_mask_ptr();
@@ -63,13 +65,24 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
   if (custom_grad != nullptr) {
     grad = custom_grad; hess = custom_hess;
     FB_CUDA(cudaStreamSynchronize(0));   // custom gradients were produced on the caller's (default) stream
-    LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_, mask);
+    if (goss) {
+      // one-side sampling rescales gradients in place: work on the engine's own copy
+      FB_CUDA(cudaMemcpyAsync(grad_.get(), custom_grad, sizeof(float) * static_cast<size_t>(n_) * K_, cudaMemcpyDeviceToDevice, stream_));
+      FB_CUDA(cudaMemcpyAsync(hess_.get(), custom_hess, sizeof(float) * static_cast<size_t>(n_) * K_, cudaMemcpyDeviceToDevice, stream_));
+      grad = grad_.get(); hess = hess_.get();
+    } else LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_, mask);
   } else {
     if (obj_ == nullptr) Log::Fatal("No objective function provided and no custom gradients given");
     LaunchObjectiveGradients(objd_, score_.get(), dd_->label.get(), dd_->weight.size() ? dd_->weight.get() : nullptr,
                              dd_->query_boundaries.size() ? dd_->query_boundaries.get() : nullptr, dd_->num_queries, label_gain_.get(),
                              static_cast<int>(label_gain_.size()), n_, grad_.get(), hess_.get(), maxbuf_.get(), stream_);
     if (bagging && quant_) LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_, mask);   // the scale comes from the bag's rows only
+  }
+  if (goss) {
+    DrawGoss(iter);
+    bagging = true; bag_active_ = true; mask = bag_mask_ptr();
+    root_count_ = bag_count_; root_global_ = bag_global_;
+    LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_, mask);
   }
   // quantization scales must be the same on every rank: max over ranks of the per-class maxima
   if (data_parallel() && quant_) fabric_->AllReduce(kFabricMaxF32, maxbuf_.get(), global_max_.get(), 2 * K_, stream_);
@@ -468,6 +481,30 @@ void CudaEngine::RenewLeavesByObjective(Tree* tree, int class_id) {
   }
   if (data_parallel()) { Network::SumDouble(outs.data(), nl); Network::SumDouble(have.data(), nl); }   // ranks' statistics are averaged
   for (int l = 0; l < nl; ++l) if (have[l] > 0) tree->SetLeafOutput(l, outs[l] / have[l]);
+}
+
+// Gradient-based one-side sampling for this iteration (works on grad_/hess_, which hold this iteration's gradients).
+void CudaEngine::DrawGoss(int iter) {
+  if (bag_mask_.size() == 0) {
+    bag_mask_.Alloc(std::max(1, n_)); bag_idx_.Alloc(std::max(1, n_)); bag_chunk_.Alloc(n_ / 1024 + 2); bag_count_dev_.Alloc(1); h_bag_count_.Alloc(1);
+  }
+  if (goss_mag_.size() == 0) { goss_mag_.Alloc(std::max(1, n_)); goss_sorted_.Alloc(std::max(1, n_)); goss_temp_.Alloc(GossSortTempBytes(n_) + 16); }
+  GossArgs a;
+  a.n = n_; a.num_class = K_; a.grad = grad_.get(); a.hess = hess_.get();
+  a.top_k = std::max(1, std::min(n_, static_cast<int>(cfg_.top_rate * n_)));
+  const int other_k = static_cast<int>(cfg_.other_rate * n_);
+  a.prob = n_ > a.top_k ? static_cast<double>(other_k) / static_cast<double>(n_ - a.top_k) : 0.0;
+  a.multiply = static_cast<float>(n_ - a.top_k) / static_cast<float>(std::max(1, other_k));
+  a.iter = static_cast<uint32_t>(iter); a.seed = static_cast<uint32_t>(cfg_.bagging_seed); a.global_row_offset = static_cast<unsigned long long>(train_->global_row_offset);
+  a.mag = goss_mag_.get(); a.sorted = goss_sorted_.get(); a.sort_temp = goss_temp_.get(); a.sort_temp_bytes = goss_temp_.size();
+  a.mask = bag_mask_.get(); a.bag_idx = bag_idx_.get(); a.chunk_count = bag_chunk_.get(); a.bag_count = bag_count_dev_.get();
+  LaunchGoss(a, stream_);
+  bag_count_dev_.Download(h_bag_count_.get(), 1, stream_);
+  FB_CUDA(cudaStreamSynchronize(stream_));
+  bag_count_ = *h_bag_count_.get();
+  int64_t g = bag_count_;
+  if (data_parallel()) Network::SumInt64(&g, 1);
+  bag_global_ = g;
 }
 
 // A new bag: flags by global row id, compaction of the in-bag rows, and the (global) bag size.

@@ -2,6 +2,8 @@
 // One launcher per kernel (or fused kernel); the engine and the kernel-level test API call these.
 #pragma once
 #include "device_common.cuh"
+#include <vector>
+
 #include "fabric.h"
 #include "fb/learner.h"
 
@@ -203,6 +205,13 @@ void LaunchPartitionScanSetup(const PartArgs& a, cudaStream_t s);
 void LaunchPartitionScatter(const PartArgs& a, cudaStream_t s);
 void LaunchInitIndices(int* idx, int n, cudaStream_t s);
 
+// ---------------------------------------------------------- rank metrics ----
+// AUC: out = [auc, sum of positive weights, sum of negative weights] (radix sort + tie-group reduction on the device).
+void DeviceAuc(const float* score, const float* label, const float* weight, int n, double out[3], cudaStream_t s);
+// NDCG: out[j] = sum over queries of ndcg@ks[j]; false when a query is longer than the kernel's shared tile.
+bool DeviceNdcgSums(const float* score, const float* label, const int* query_boundaries, int num_queries, int max_docs, const double* gains, int num_gains,
+                    const std::vector<int>& ks, double* out, cudaStream_t s);
+
 // ---------------------------------------------------------------- bagging ----
 // Row sampling on the device: a row is in the bag iff a Philox number keyed on (bagging seed, bagging
 // round, GLOBAL row id) is below its fraction, so the bag does not depend on how rows are sharded and is
@@ -216,6 +225,17 @@ struct BagArgs {
   uint8_t* mask; int* bag_idx; int* chunk_count; int* bag_count;
 };
 void LaunchBagging(const BagArgs& a, cudaStream_t s);
+// Gradient-based one-side sampling on the device: |g*h| per row (summed over classes), the top_k-th largest value by
+// a radix sort, rows at or above it kept, the others kept with probability `prob` (Philox on the global row id) and
+// their gradients scaled by `multiply`; then the same scan + scatter as bagging.
+struct GossArgs {
+  int n, num_class; float* grad; float* hess;   // [num_class][n], scaled in place for the sampled small-gradient rows
+  int top_k; double prob; float multiply; uint32_t iter, seed; unsigned long long global_row_offset;
+  float* mag; float* sorted; void* sort_temp; size_t sort_temp_bytes;
+  uint8_t* mask; int* bag_idx; int* chunk_count; int* bag_count;
+};
+size_t GossSortTempBytes(int n);
+void LaunchGoss(const GossArgs& a, cudaStream_t s);
 
 // ----------------------------------------------------------------- score ----
 void LaunchAddLeafOutputs(const LeafInfo* leaves, const double* leaf_value, int num_leaves, const int* idx0, const int* idx1, float* score, cudaStream_t s);

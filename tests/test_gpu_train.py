@@ -201,3 +201,43 @@ def test_leaf_renewal_on_device():
     cpu = fb.train({**pl, "device_type": "cpu"}, fb.Dataset(X, yl), 30)
     mae = lambda b: float(np.mean(np.abs(b.predict(X) - yl)))
     assert abs(mae(dev) - mae(cpu)) < 0.05 * mae(cpu)
+
+
+def test_goss_on_device():
+    X, y = make_binary(30000, 20)
+    p = {"objective": "binary", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "data_sample_strategy": "goss", "top_rate": 0.2,
+         "other_rate": 0.1, "learning_rate": 0.2, "metric": "binary_logloss"}
+    res = {}
+    ds = fb.Dataset(X[:25000], y[:25000])
+    dev = fb.train({**p, "device_type": "cuda"}, ds, 40, valid_sets=[ds], valid_names=["train"], callbacks=[fb.record_evaluation(res)])
+    cpu = fb.train({**p, "device_type": "cpu"}, fb.Dataset(X[:25000], y[:25000]), 40)
+    ad, ac = auc(y[25000:], dev.predict(X[25000:])), auc(y[25000:], cpu.predict(X[25000:]))
+    assert ad > 0.93 and abs(ad - ac) < 0.01, (ad, ac)
+    # the sampled trees really are smaller samples: leaf counts of a late tree add up to about (top + other) of the rows
+    late = dev.dump_model()["tree_info"][-1]["tree_structure"]
+    total = late["internal_count"]
+    assert 0.25 * 25000 < total < 0.36 * 25000, total
+    # scores of out-of-sample rows are kept up to date (training metric equals a fresh prediction)
+    pr = dev.predict(X[:25000])
+    ref = -np.mean(np.where(y[:25000] > 0, np.log(pr), np.log(1 - pr)))
+    assert abs(ref - res["train"]["binary_logloss"][-1]) < 1e-4
+
+
+def test_device_ndcg_matches_a_plain_computation():
+    X, y, g = make_ranking(300, 25, 10)
+    res = {}
+    ds = fb.Dataset(X, y, group=g)
+    bst = fb.train({"objective": "lambdarank", "metric": "ndcg", "eval_at": "3,10", "verbosity": -1, "device_type": "cuda", "min_data_in_leaf": 5}, ds, 10,
+                   valid_sets=[ds], valid_names=["train"], callbacks=[fb.record_evaluation(res)])
+    s = bst.predict(X, raw_score=True)
+    out = {3: [], 10: []}
+    pos = 0
+    for cnt in g:
+        sc, lab = s[pos:pos + cnt], y[pos:pos + cnt]; pos += cnt
+        order = np.argsort(-sc, kind="stable"); ideal = np.argsort(-lab, kind="stable")
+        for k in (3, 10):
+            disc = 1.0 / np.log2(2.0 + np.arange(min(k, cnt)))
+            dcg = np.sum((2.0 ** lab[order[:k]] - 1) * disc); idcg = np.sum((2.0 ** lab[ideal[:k]] - 1) * disc)
+            out[k].append(dcg / idcg if idcg > 0 else 1.0)
+    assert abs(np.mean(out[3]) - res["train"]["ndcg@3"][-1]) < 1e-5
+    assert abs(np.mean(out[10]) - res["train"]["ndcg@10"][-1]) < 1e-5
