@@ -8,6 +8,8 @@
 //           level are applied in ascending leaf order, which fixes the leaf numbering.
 // The device learner implements exactly the same two policies, so trees can be compared.
 #include "fb/learner.h"
+
+#include <omp.h>
 #include "fb/objective.h"
 
 #include <numeric>
@@ -177,31 +179,51 @@ void CPUTreeLearner::Quantize(const score_t* grad, const score_t* hess, int tree
 }
 
 void CPUTreeLearner::ConstructHistogram(LeafState* leaf) {
+  ScopedTimer timer("CPUTreeLearner::ConstructHistogram");
   const int nb = ds_->num_total_bin, ng = ds_->num_groups;
   const data_size_t* idx = indices_.data() + leaf->begin;
+  // large leaves: row blocks on worker threads with private histograms, merged in thread order (integer bins:
+  // exact for any thread count; real-valued bins: the summation order follows the thread count)
+  const int nthreads = leaf->count >= 8192 ? std::max(1, std::min(omp_get_max_threads(), leaf->count / 4096)) : 1;
   if (quant_) {
     leaf->hist_i.assign(2 * static_cast<size_t>(nb), 0);
-    int64_t* H = leaf->hist_i.data();
-    for (int k = 0; k < leaf->count; ++k) {
-      const data_size_t i = idx[k];
-      const int32_t w = gh_packed_[i];
-      const int64_t g = UnpackG(w), h = UnpackH(w);
-      for (int gidx = 0; gidx < ng; ++gidx) {
-        const int s = ds_->group_bin_start[gidx] + ds_->GroupBin(i, gidx);
-        H[2 * s] += g; H[2 * s + 1] += h;
+    std::vector<std::vector<int64_t>> priv(nthreads > 1 ? nthreads : 0);
+#pragma omp parallel num_threads(nthreads)
+    {
+      const int t = omp_get_thread_num();
+      int64_t* H = leaf->hist_i.data();
+      if (nthreads > 1) { priv[t].assign(2 * static_cast<size_t>(nb), 0); H = priv[t].data(); }
+      const int lo = static_cast<int>(static_cast<int64_t>(leaf->count) * t / nthreads), hi = static_cast<int>(static_cast<int64_t>(leaf->count) * (t + 1) / nthreads);
+      for (int k = lo; k < hi; ++k) {
+        const data_size_t i = idx[k];
+        const int32_t w = gh_packed_[i];
+        const int64_t g = UnpackG(w), h = UnpackH(w);
+        for (int gidx = 0; gidx < ng; ++gidx) {
+          const int s = ds_->group_bin_start[gidx] + ds_->GroupBin(i, gidx);
+          H[2 * s] += g; H[2 * s + 1] += h;
+        }
       }
     }
+    for (int t = 0; t < static_cast<int>(priv.size()); ++t) for (size_t b = 0; b < priv[t].size(); ++b) leaf->hist_i[b] += priv[t][b];
   } else {
     leaf->hist.assign(2 * static_cast<size_t>(nb), 0.0);
-    double* H = leaf->hist.data();
-    for (int k = 0; k < leaf->count; ++k) {
-      const data_size_t i = idx[k];
-      const double g = grad_[i], h = hess_[i];
-      for (int gidx = 0; gidx < ng; ++gidx) {
-        const int s = ds_->group_bin_start[gidx] + ds_->GroupBin(i, gidx);
-        H[2 * s] += g; H[2 * s + 1] += h;
+    std::vector<std::vector<double>> priv(nthreads > 1 ? nthreads : 0);
+#pragma omp parallel num_threads(nthreads)
+    {
+      const int t = omp_get_thread_num();
+      double* H = leaf->hist.data();
+      if (nthreads > 1) { priv[t].assign(2 * static_cast<size_t>(nb), 0.0); H = priv[t].data(); }
+      const int lo = static_cast<int>(static_cast<int64_t>(leaf->count) * t / nthreads), hi = static_cast<int>(static_cast<int64_t>(leaf->count) * (t + 1) / nthreads);
+      for (int k = lo; k < hi; ++k) {
+        const data_size_t i = idx[k];
+        const double g = grad_[i], h = hess_[i];
+        for (int gidx = 0; gidx < ng; ++gidx) {
+          const int s = ds_->group_bin_start[gidx] + ds_->GroupBin(i, gidx);
+          H[2 * s] += g; H[2 * s + 1] += h;
+        }
       }
     }
+    for (int t = 0; t < static_cast<int>(priv.size()); ++t) for (size_t b = 0; b < priv[t].size(); ++b) leaf->hist[b] += priv[t][b];
   }
   leaf->has_hist = true;
   ReduceHistogramAcrossRanks(leaf);
@@ -279,6 +301,8 @@ void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanI
     }
   }
   if (cand.feature >= 0) {
+    cand.left_out = LeafOutput(cand.left_g, FB_ADD(cand.left_h, kEpsilon), sp_, cand.left_cnt, L.parent_output);
+    cand.right_out = LeafOutput(cand.right_g, FB_ADD(cand.right_h, kEpsilon), sp_, cand.right_cnt, L.parent_output);
     cand.gain = FB_MUL(cand.gain, static_cast<double>(m.penalty));
     if (SplitBetter(cand.gain, ds_->feature_meta[cand.feature].real_index, cand.threshold, best->gain,
                     best->feature >= 0 ? ds_->feature_meta[best->feature].real_index : -1, best->threshold)) *best = cand;
@@ -348,6 +372,8 @@ void CPUTreeLearner::ScanCategorical(const LeafState& leaf, int f, const LeafSca
     }
   }
   if (cand.feature >= 0) {
+    cand.left_out = LeafOutput(cand.left_g, FB_ADD(cand.left_h, kEpsilon), p, cand.left_cnt, L.parent_output);
+    cand.right_out = LeafOutput(cand.right_g, FB_ADD(cand.right_h, kEpsilon), p, cand.right_cnt, L.parent_output);
     cand.gain = FB_MUL(cand.gain, static_cast<double>(m.penalty));
     if (SplitBetter(cand.gain, m.real_index, 0, best->gain, best->feature >= 0 ? ds_->feature_meta[best->feature].real_index : -1, best->threshold)) *best = cand;
   }
@@ -367,6 +393,7 @@ void CPUTreeLearner::SyncBestSplit(SplitRecord* rec) const {
 }
 
 void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index) {
+  ScopedTimer timer("CPUTreeLearner::FindBestSplit");
   InitSplitRecord(&leaf->best);
   if (sp_.max_depth > 0 && leaf->depth >= sp_.max_depth) return;
   const int64_t n_global = leaf->global_count;
@@ -442,16 +469,30 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
   }
 
   SplitRecord best; InitSplitRecord(&best);
-  for (int f = 0; f < ds_->num_features; ++f) {
-    if (!mask[f] || !FeatureOwned(f)) continue;
-    if (ds_->feature_meta[f].bin_type == static_cast<int>(BinType::Numerical)) ScanNumerical(*leaf, f, L, &best);
-    else ScanCategorical(*leaf, f, L, &best);
+  {
+    // one record per feature on the worker threads, merged in feature order (SplitBetter is a total order, so the
+    // result does not depend on the thread count); extra_trees draws from a shared generator and stays serial
+    std::vector<SplitRecord> per(ds_->num_features);
+    const int nt = sp_.extra_trees ? 1 : std::max(1, std::min(omp_get_max_threads(), ds_->num_features / 2));
+#pragma omp parallel for schedule(dynamic, 1) num_threads(nt)
+    for (int f = 0; f < ds_->num_features; ++f) {
+      InitSplitRecord(&per[f]);
+      if (!mask[f] || !FeatureOwned(f)) continue;
+      if (ds_->feature_meta[f].bin_type == static_cast<int>(BinType::Numerical)) ScanNumerical(*leaf, f, L, &per[f]);
+      else ScanCategorical(*leaf, f, L, &per[f]);
+    }
+    for (int f = 0; f < ds_->num_features; ++f) {
+      const SplitRecord& r = per[f];
+      if (r.feature < 0) continue;
+      if (SplitBetter(r.gain, ds_->feature_meta[r.feature].real_index, r.threshold, best.gain, best.feature >= 0 ? ds_->feature_meta[best.feature].real_index : -1, best.threshold)) best = r;
+    }
   }
   SyncBestSplit(&best);
   leaf->best = best;
 }
 
 int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
+  ScopedTimer timer("CPUTreeLearner::ApplySplit");
   LeafState& P = leaves_[leaf_id];
   const SplitRecord s = P.best;
   const FeatureMeta& m = ds_->feature_meta[s.feature];

@@ -107,10 +107,16 @@ FB_HD inline double LeafGain(double g, double h, const SplitParams& p, int num_d
 // Gain of a (left, right) pair; returns false when a monotone constraint is violated.
 FB_HD inline bool SplitGain(double lg, double lh, double rg, double rh, const SplitParams& p, int lcnt, int rcnt,
                             double parent_output, int monotone, double* gain, double* lout, double* rout) {
-  *lout = LeafOutput(lg, lh, p, lcnt, parent_output);
-  *rout = LeafOutput(rg, rh, p, rcnt, parent_output);
-  if ((monotone > 0 && *lout > *rout) || (monotone < 0 && *lout < *rout)) { *gain = 0.0; return false; }
-  if (p.max_delta_step <= 0.0 && p.path_smooth <= 0.0) {
+  // the leaf outputs enter the gain only with max_delta_step / path_smooth and the monotone check; otherwise they are
+  // left unset here (0) and the caller computes them once, for the winning candidate, with the same LeafOutput call
+  const bool plain = p.max_delta_step <= 0.0 && p.path_smooth <= 0.0;
+  if (plain && monotone == 0) { *lout = 0.0; *rout = 0.0; }
+  else {
+    *lout = LeafOutput(lg, lh, p, lcnt, parent_output);
+    *rout = LeafOutput(rg, rh, p, rcnt, parent_output);
+    if ((monotone > 0 && *lout > *rout) || (monotone < 0 && *lout < *rout)) { *gain = 0.0; return false; }
+  }
+  if (plain) {
     *gain = FB_ADD(LeafGain(lg, lh, p, lcnt, parent_output), LeafGain(rg, rh, p, rcnt, parent_output));
   } else {
     *gain = FB_ADD(LeafGainGivenOutput(lg, lh, p, *lout), LeafGainGivenOutput(rg, rh, p, *rout));
