@@ -272,10 +272,12 @@ class Dataset:
         goff, gtot = self._global_rows
         sample, total = bootstrap.gather_bin_sample(torch.from_numpy(arr), int(params.get("bin_construct_sample_cnt", 200000)),
                                                     int(params.get("data_random_seed", 1)), goff, gtot)
-        sample = np.ascontiguousarray(sample, dtype=np.float64)
+        sample = np.ascontiguousarray(sample)
+        if sample.dtype not in _DTYPE_CODE:
+            sample = sample.astype(np.float64)
         handle = ctypes.c_void_p()
-        _safe_call(lib.FB_DatasetCreateFromSample(sample.ctypes.data_as(ctypes.c_void_p), ctypes.c_int32(sample.shape[0]), ctypes.c_int32(ncol),
-                                                  ctypes.c_int64(total), _param_str(params), None, 0, ctypes.byref(handle)))
+        _safe_call(lib.FB_DatasetCreateFromSampleTyped(sample.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[sample.dtype], ctypes.c_int32(sample.shape[0]),
+                                                       ctypes.c_int32(ncol), ctypes.c_int64(total), _param_str(params), None, 0, ctypes.byref(handle)))
         self._handle = handle
         _safe_call(lib.FB_DatasetInitRows(handle, ctypes.c_int32(nrow), ctypes.c_int64(goff), ctypes.c_int64(total), 1))
         _safe_call(lib.FB_DatasetPushRows(handle, arr.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[arr.dtype], ctypes.c_int32(nrow), ctypes.c_int32(ncol), 1, 0))
@@ -306,9 +308,11 @@ class Dataset:
             goff, gtot = self._global_rows if self._global_rows is not None else (0, 0)
             sample, total = bootstrap.gather_bin_sample(t, int(params.get("bin_construct_sample_cnt", 200000)), int(params.get("data_random_seed", 1)), goff, gtot,
                                                         replicated=self._replicated)
-            sample = np.ascontiguousarray(sample, dtype=np.float64)
-            _safe_call(lib.FB_DatasetCreateFromSample(sample.ctypes.data_as(ctypes.c_void_p), ctypes.c_int32(sample.shape[0]), ctypes.c_int32(ncol),
-                                                      ctypes.c_int64(total), _param_str(params), None, 0, ctypes.byref(handle)))
+            sample = np.ascontiguousarray(sample)
+            if sample.dtype not in _DTYPE_CODE:
+                sample = sample.astype(np.float64)
+            _safe_call(lib.FB_DatasetCreateFromSampleTyped(sample.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[sample.dtype], ctypes.c_int32(sample.shape[0]),
+                                                           ctypes.c_int32(ncol), ctypes.c_int64(total), _param_str(params), None, 0, ctypes.byref(handle)))
         self._handle = handle
         off, total = self._global_rows if self._global_rows is not None else (0, nrow)
         keep_host = 1 if str(params.get("device_type", "")).lower() == "cpu" or params.get("keep_host_bins") else 0

@@ -129,6 +129,20 @@ int FB_DatasetCreateFromSample(const double* sample, int32_t ns, int32_t ncol, i
   API_END();
 }
 
+int FB_DatasetCreateFromSampleTyped(const void* sample, int dtype, int32_t ns, int32_t ncol, int64_t total, const char* parameters,
+                                    const int32_t* categorical, int32_t num_categorical, DatasetHandle* out) {
+  API_BEGIN();
+  ScopedTimer api_timer("FB_DatasetCreateFromSample");
+  Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());
+  if (cfg.num_threads > 0) omp_set_num_threads(cfg.num_threads);
+  std::unique_ptr<Dataset> ds(new Dataset());
+  std::vector<int> cats = ParseCategorical(cfg, ncol);
+  for (int i = 0; i < num_categorical; ++i) cats.push_back(categorical[i]);
+  ds->ConstructSchemaTyped(sample, dtype, ns, ncol, total, cfg, cats);
+  *out = ds.release();
+  API_END();
+}
+
 int FB_DatasetCreateByReference(const DatasetHandle reference, DatasetHandle* out) {
   API_BEGIN();
   std::unique_ptr<Dataset> ds(new Dataset()); ds->CopySchemaFrom(*static_cast<const Dataset*>(reference)); *out = ds.release();

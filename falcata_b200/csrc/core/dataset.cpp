@@ -117,6 +117,12 @@ inline double ReadValue(const void* data, int dtype, size_t i) {
 
 void Dataset::ConstructSchema(const double* sample, int ns, int ncol, int64_t total_rows, const Config& cfg,
                               const std::vector<int>& categorical) {
+  ConstructSchemaTyped(sample, kF64, ns, ncol, total_rows, cfg, categorical);
+}
+
+void Dataset::ConstructSchemaTyped(const void* sample, int dtype, int ns, int ncol, int64_t total_rows, const Config& cfg,
+                                   const std::vector<int>& categorical) {
+  ScopedTimer timer("Dataset::ConstructSchema");
   num_total_features = ncol;
   max_bin_param = cfg.max_bin;
   categorical_features = categorical;
@@ -125,20 +131,40 @@ void Dataset::ConstructSchema(const double* sample, int ns, int ncol, int64_t to
   mappers.clear(); mappers.resize(ncol);
   const int min_split_data = total_rows > 0
       ? static_cast<int>(static_cast<double>(cfg.min_data_in_leaf) * ns / static_cast<double>(total_rows)) : 0;
-  // one bin search per feature, independent of each other: spread over the host cores
+  // One bin search per feature, independent of each other: tiles of adjacent columns go to the host cores, and a
+  // tile's rows are read in order (the sample is row-major, so a single column on its own would stride by a row).
+  // The rows where a feature leaves its most frequent bin are collected in the same pass, for the bundling below.
+  const int kTile = 16;
+  const int ntiles = (ncol + kTile - 1) / kTile;
+  std::vector<std::vector<int>> nz_by_col(cfg.enable_bundle ? ncol : 0);
 #pragma omp parallel for schedule(dynamic, 1)
-  for (int j = 0; j < ncol; ++j) {
-    std::vector<double> col(ns);
-    int m = 0;
+  for (int t = 0; t < ntiles; ++t) {
+    const int j0 = t * kTile, j1 = std::min(ncol, j0 + kTile), w = j1 - j0;
+    std::vector<std::vector<double>> cols(w, std::vector<double>(ns));
+    std::vector<int> m(w, 0);
     for (int i = 0; i < ns; ++i) {
-      double v = sample[static_cast<size_t>(i) * ncol + j];
-      if (std::isnan(v) || std::fabs(v) > kZeroThreshold) col[m++] = v;
+      for (int c = 0; c < w; ++c) {
+        const double v = ReadValue(sample, dtype, static_cast<size_t>(i) * ncol + j0 + c);
+        if (std::isnan(v) || std::fabs(v) > kZeroThreshold) cols[c][m[c]++] = v;
+      }
     }
-    int mb = cfg.max_bin;
-    if (j < static_cast<int>(cfg.max_bin_by_feature_vec.size())) mb = cfg.max_bin_by_feature_vec[j];
-    mappers[j].reset(new BinMapper());
-    mappers[j]->FindBin(col.data(), m, ns, mb, cfg.min_data_in_bin, min_split_data, cfg.feature_pre_filter,
-                        is_cat[j] ? BinType::Categorical : BinType::Numerical, cfg.use_missing, cfg.zero_as_missing, {});
+    for (int c = 0; c < w; ++c) {
+      const int j = j0 + c;
+      int mb = cfg.max_bin;
+      if (j < static_cast<int>(cfg.max_bin_by_feature_vec.size())) mb = cfg.max_bin_by_feature_vec[j];
+      mappers[j].reset(new BinMapper());
+      mappers[j]->FindBin(cols[c].data(), m[c], ns, mb, cfg.min_data_in_bin, min_split_data, cfg.feature_pre_filter,
+                          is_cat[j] ? BinType::Categorical : BinType::Numerical, cfg.use_missing, cfg.zero_as_missing, {});
+    }
+    if (cfg.enable_bundle) {
+      for (int i = 0; i < ns; ++i) {
+        for (int c = 0; c < w; ++c) {
+          const BinMapper& bm = *mappers[j0 + c];
+          if (bm.is_trivial || bm.sparse_rate < 0.5) continue;   // dense features never share a bundle
+          if (bm.ValueToBin(ReadValue(sample, dtype, static_cast<size_t>(i) * ncol + j0 + c)) != bm.most_freq_bin) nz_by_col[j0 + c].push_back(i);
+        }
+      }
+    }
   }
   used_feature_map.assign(ncol, -1);
   real_feature_idx.clear();
@@ -160,18 +186,16 @@ void Dataset::ConstructSchema(const double* sample, int ns, int ncol, int64_t to
       if (bm.sparse_rate >= 0.5) any_sparse = true;
     }
     if (any_sparse) {
-      for (int f = 0; f < num_features; ++f) {
-        const BinMapper& bm = *mappers[real_feature_idx[f]];
-        const int j = real_feature_idx[f];
-        for (int i = 0; i < ns; ++i) if (bm.ValueToBin(sample[static_cast<size_t>(i) * ncol + j]) != bm.most_freq_bin) nz[f].push_back(i);
-      }
+      for (int f = 0; f < num_features; ++f) nz[f].swap(nz_by_col[real_feature_idx[f]]);
       const int max_conflict = ns / 10000;
-      std::vector<int> order1(num_features); std::iota(order1.begin(), order1.end(), 0);
+      std::vector<int> order1;   // only sparse features are offered to the bundler; dense ones stay alone
+      for (int f = 0; f < num_features; ++f) if (mappers[real_feature_idx[f]]->sparse_rate >= 0.5) order1.push_back(f);
       std::vector<int> order2 = order1;
       std::stable_sort(order2.begin(), order2.end(), [&](int a, int b) { return nz[a].size() > nz[b].size(); });
       auto g1 = BundleGreedy(order1, nz, nbins, ns, max_conflict, 256, static_cast<int>(total_rows & 0x7fffffff));
       auto g2 = BundleGreedy(order2, nz, nbins, ns, max_conflict, 256, static_cast<int>(total_rows & 0x7fffffff));
       groups = g2.size() < g1.size() ? g2 : g1;
+      for (int f = 0; f < num_features; ++f) if (mappers[real_feature_idx[f]]->sparse_rate < 0.5) groups.push_back({f});
       // dense features (sparse_rate small) gain nothing from a bundle slot: keep them alone
       std::vector<std::vector<int>> cleaned;
       for (auto& g : groups) {

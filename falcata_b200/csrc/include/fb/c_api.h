@@ -34,6 +34,9 @@ int FB_DatasetCreateFromFile(const char* filename, const char* parameters, const
 /* Schema only (bin mappers + bundles) from a dense f64 sample; rows are attached afterwards. */
 int FB_DatasetCreateFromSample(const double* sample, int32_t num_sample_row, int32_t ncol, int64_t num_total_row, const char* parameters,
                                const int32_t* categorical, int32_t num_categorical, DatasetHandle* out);
+// The sample in its own element type (DType code): no widening to double on the way in.
+int FB_DatasetCreateFromSampleTyped(const void* sample, int dtype, int32_t num_sample_row, int32_t ncol, int64_t num_total_row, const char* parameters,
+                                    const int32_t* categorical, int32_t num_categorical, DatasetHandle* out);
 int FB_DatasetCreateByReference(const DatasetHandle reference, DatasetHandle* out);
 int FB_DatasetSerializeSchema(DatasetHandle handle, int64_t buffer_len, int64_t* out_len, char* out);
 int FB_DatasetCreateFromSchema(const char* schema, int64_t len, const char* parameters, DatasetHandle* out);

@@ -88,6 +88,9 @@ class Dataset {
   // Build mappers + groups from a dense sample [ns x ncol] (row-major doubles).
   void ConstructSchema(const double* sample, int ns, int ncol, int64_t total_rows, const Config& cfg,
                        const std::vector<int>& categorical);
+  // same, with the sample in any supported element type (DType code)
+  void ConstructSchemaTyped(const void* sample, int dtype, int ns, int ncol, int64_t total_rows, const Config& cfg,
+                       const std::vector<int>& categorical);
   // Copy mappers/groups from another dataset (validation data aligned with training data).
   void CopySchemaFrom(const Dataset& ref);
   void AllocateRows(data_size_t n);

@@ -35,7 +35,8 @@ def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total
     row id, so the sample - and with it every bin boundary - is the same however the rows are sharded
     over ranks. Each rank contributes the sampled rows of its shard; the shards are concatenated in
     rank order. ``replicated``: every rank holds ALL rows (feature-parallel training), so the local sample
-    is already the global one and nothing is exchanged. Returns (sample [ns, ncol] float64, total rows)."""
+    is already the global one and nothing is exchanged. Returns (sample [ns, ncol] in the matrix's own element
+    type - float16/32/64, int8/16/32, uint8 - so nothing is widened on the way to the host; total rows)."""
     import torch
 
     rank, ws = world()
@@ -69,7 +70,9 @@ def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total
         pos = c * chunk + hi
         c += 1
     idx = torch.cat(picks) if picks else torch.zeros(0, dtype=torch.int64, device=t.device)
-    picked = t[idx].to(torch.float64)
+    keep = t.dtype in (torch.float16, torch.float32, torch.float64, torch.int8, torch.int16, torch.int32, torch.uint8)
+    sdt = t.dtype if keep else torch.float64
+    picked = t[idx].to(sdt)
     if d and ws > 1:
         # tensor collectives (no pickling): sizes first, then the rows padded to the largest shard
         on_dev = picked.is_cuda and d.get_backend() == "nccl"
@@ -79,16 +82,16 @@ def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total
         d.all_reduce(sizes)
         sizes = sizes.cpu().tolist()
         cap = max(1, max(sizes))
-        padded = torch.zeros((cap, t.shape[1]), dtype=torch.float64, device=cdev)
+        padded = torch.zeros((cap, t.shape[1]), dtype=sdt, device=cdev)
         padded[: picked.shape[0]] = picked.to(cdev)
-        outs = torch.empty((ws, cap, t.shape[1]), dtype=torch.float64, device=cdev)
+        outs = torch.empty((ws, cap, t.shape[1]), dtype=sdt, device=cdev)
         d.all_gather_into_tensor(outs, padded) if on_dev else d.all_gather(list(outs.unbind(0)), padded)
         outs = outs.cpu().numpy()
         local = np.concatenate([outs[r, : sizes[r]] for r in range(ws)], axis=0)
     else:
         local = picked.cpu().numpy()
     if local.shape[0] == 0:
-        local = t[:1].to(torch.float64).cpu().numpy()
+        local = t[:1].to(sdt).cpu().numpy()
     return local, total
 
 

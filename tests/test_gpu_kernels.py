@@ -74,7 +74,8 @@ def test_hist_float_close():
 @pytest.mark.parametrize("stochastic", [True, False])
 def test_quantize_matches_reference(stochastic):
     from falcata_b200 import ops
-    n, bins = 10000, 4
+    n, bins = 200000, 4
+    torch.manual_seed(0)
     g = torch.randn(n, device="cuda"); h = torch.rand(n, device="cuda")
     packed, scales, sums = ops.quantize(g, h, bins, stochastic, seed=7, iter_key=3)
     gs = g.abs().max() / (bins // 2); hs = h.abs().max() / bins
@@ -86,7 +87,7 @@ def test_quantize_matches_reference(stochastic):
         ref_g = torch.trunc(torch.addcmul(torch.where(g >= 0, 0.5, -0.5), g, (1.0 / gs).expand_as(g))).int()
         assert (ref_g != gi).float().mean() < 1e-3     # fused vs unfused rounding may differ on exact ties only
     else:
-        # unbiased: E[q * scale] = g
+        # unbiased: E[q * scale] = g (the mean error over 200k rows has a standard deviation of about 0.002)
         assert abs(float((gi.float() * gs - g).mean())) < 0.02
     p2, _, _ = ops.quantize(g, h, bins, stochastic, seed=7, iter_key=3)
     assert torch.equal(packed, p2)
