@@ -4,6 +4,8 @@
 // distinct values, categorical by frequency, trivial-feature filter, default/most-freq bin).
 #include "fb/bin.h"
 
+#include <cstring>
+
 #include <numeric>
 
 namespace fb {
@@ -96,10 +98,36 @@ std::vector<double> BoundsZeroOwnBin(const std::vector<double>& vals, const std:
 }
 
 inline bool NearlyEqualOrdered(double a, double b) {
-  // a <= b assumed; equal or adjacent representable doubles are merged.
+  // a <= b assumed; equal or adjacent representable doubles are merged. Neighbouring doubles differ by at most
+  // 2.3e-16 of their magnitude, so a wider gap settles the question without the library call.
+  if (b - a > std::fabs(a) * 2.3e-16 + 1e-300) return false;
   return b <= std::nextafter(a, std::numeric_limits<double>::infinity());
 }
 
+}  // namespace
+
+namespace {
+// Ascending sort of finite doubles. Large inputs take an LSD radix sort on the order-preserving integer image
+// of the IEEE bits (eight 8-bit digits; digits that are the same in every key, like the low mantissa bytes of
+// values that came from float32, are skipped): several times faster than a comparison sort on the 200k-value
+// columns of a bin sample, which is where ingest spends its host time.
+void SortValues(double* v, int n) {
+  if (n < 4096) { std::sort(v, v + n); return; }
+  if (std::is_sorted(v, v + n)) return;
+  std::vector<uint64_t> a(n), b(n);
+  for (int i = 0; i < n; ++i) { uint64_t u; memcpy(&u, &v[i], 8); a[i] = (u >> 63) ? ~u : (u | 0x8000000000000000ull); }
+  uint64_t* src = a.data(); uint64_t* dst = b.data();
+  for (int pass = 0; pass < 8; ++pass) {
+    const int shift = pass * 8;
+    uint32_t count[257] = {0};
+    for (int i = 0; i < n; ++i) ++count[((src[i] >> shift) & 255u) + 1];
+    if (count[((src[0] >> shift) & 255u) + 1] == static_cast<uint32_t>(n)) continue;   // all keys share this digit
+    for (int d = 0; d < 256; ++d) count[d + 1] += count[d];
+    for (int i = 0; i < n; ++i) dst[count[(src[i] >> shift) & 255u]++] = src[i];
+    std::swap(src, dst);
+  }
+  for (int i = 0; i < n; ++i) { uint64_t u = src[i]; u = (u >> 63) ? (u & 0x7FFFFFFFFFFFFFFFull) : ~u; memcpy(&v[i], &u, 8); }
+}
 }  // namespace
 
 void BinMapper::FindBin(double* values, int num_values, size_t total_sample_cnt, int max_bin, int min_data_in_bin,
@@ -116,8 +144,9 @@ void BinMapper::FindBin(double* values, int num_values, size_t total_sample_cnt,
   else missing_type = na_cnt > 0 ? MissingType::NaN : MissingType::None;
   const size_t zero_cnt = total_sample_cnt - static_cast<size_t>(num_values) - static_cast<size_t>(na_cnt);
 
-  std::stable_sort(values, values + num_values);
+  SortValues(values, num_values);
   std::vector<double> dv; std::vector<int> dc;
+  dv.reserve(static_cast<size_t>(num_values) + 1); dc.reserve(static_cast<size_t>(num_values) + 1);
   bool zero_pushed = false;
   auto push_zero = [&] {
     if (!zero_pushed && zero_cnt > 0) {

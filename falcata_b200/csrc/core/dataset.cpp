@@ -5,6 +5,8 @@
 // L1298-1356 (CopySubrow); src/io/metadata.cpp.
 #include "fb/dataset.h"
 
+#include <omp.h>
+
 #include <cstdio>
 #include <fstream>
 #include <numeric>
@@ -134,7 +136,8 @@ void Dataset::ConstructSchemaTyped(const void* sample, int dtype, int ns, int nc
   // One bin search per feature, independent of each other: tiles of adjacent columns go to the host cores, and a
   // tile's rows are read in order (the sample is row-major, so a single column on its own would stride by a row).
   // The rows where a feature leaves its most frequent bin are collected in the same pass, for the bundling below.
-  const int kTile = 16;
+  // narrow data: one column per task keeps every core busy; wide data: up to 16 columns per task
+  const int kTile = std::max(1, std::min(16, ncol / (4 * std::max(1, omp_get_max_threads()))));
   const int ntiles = (ncol + kTile - 1) / kTile;
   std::vector<std::vector<int>> nz_by_col(cfg.enable_bundle ? ncol : 0);
 #pragma omp parallel for schedule(dynamic, 1)

@@ -132,6 +132,32 @@ int FB_OpBoundedWaitProbe(long long max_spins, int* out_status, int* out_flag_se
   OPS_END();
 }
 
+// Rows of [global_offset, global_offset + n) whose Philox draw (keyed on seed and the GLOBAL row id) falls below
+// `fraction`, ascending, as local indices. The draw depends on nothing else, so any sharding of the rows and both
+// variants (device kernel, host loop) select the same global rows. Used for the bin-construction sample.
+int FB_OpBernoulliRowsDevice(int n, long long global_offset, unsigned int seed, double fraction, int* out_idx_device, int* out_count) {
+  OPS_BEGIN();
+  cudaStream_t s = 0;
+  DevBuf<uint8_t> mask; mask.Alloc(std::max(1, n)); DevBuf<int> chunk; chunk.Alloc(n / 1024 + 2); DevBuf<int> cnt; cnt.Alloc(1);
+  BagArgs a = BagArgs();
+  a.n = n; a.global_row_offset = static_cast<unsigned long long>(global_offset); a.round = 0x5A3Du; a.seed = seed; a.fraction = fraction; a.pos_fraction = a.neg_fraction = 1.0;
+  a.mask = mask.get(); a.bag_idx = out_idx_device; a.chunk_count = chunk.get(); a.bag_count = cnt.get();
+  LaunchBagging(a, s);
+  FB_CUDA(cudaMemcpyAsync(out_count, cnt.get(), sizeof(int), cudaMemcpyDeviceToHost, s));
+  FB_CUDA(cudaStreamSynchronize(s));
+  OPS_END();
+}
+int FB_OpBernoulliRowsHost(int n, long long global_offset, unsigned int seed, double fraction, int* out_idx, int* out_count) {
+  OPS_BEGIN();
+  int c = 0;
+  for (int i = 0; i < n; ++i) {
+    const float u = U01From24(Philox4x32_10(static_cast<uint32_t>(static_cast<unsigned long long>(global_offset) + static_cast<unsigned long long>(i)), 0x5A3Du, 0xBA660000u, 0u, seed, 0x9876u).v[0]);
+    if (static_cast<double>(u) < fraction) out_idx[c++] = i;
+  }
+  *out_count = c;
+  OPS_END();
+}
+
 int FB_OpLaunchCount(long long* out) { *out = LaunchCounter().load(); return 0; }
 
 }  // extern "C"

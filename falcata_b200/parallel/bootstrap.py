@@ -27,11 +27,35 @@ def world() -> Tuple[int, int]:
     return (d.get_rank(), d.get_world_size()) if d else (0, 1)
 
 
+def _bernoulli_rows(t: Any, n: int, offset: int, seed: int, p: float) -> Any:
+    """Local indices of the rows picked for the bin sample: a draw keyed on (seed, GLOBAL row id), made by the
+    library on the device for CUDA tensors and on the host otherwise - the same rows either way."""
+    import torch
+
+    from ..basic import _lib
+
+    lib = _lib()
+    cnt = ctypes.c_int(0)
+    if t.is_cuda:
+        out = torch.empty(max(1, n), dtype=torch.int32, device=t.device)
+        with torch.cuda.device(t.device):
+            torch.cuda.current_stream().synchronize()
+            rc = lib.FB_OpBernoulliRowsDevice(ctypes.c_int(n), ctypes.c_longlong(offset), ctypes.c_uint(seed & 0xFFFFFFFF), ctypes.c_double(p),
+                                              ctypes.c_void_p(out.data_ptr()), ctypes.byref(cnt))
+    else:
+        out = torch.empty(max(1, n), dtype=torch.int32)
+        rc = lib.FB_OpBernoulliRowsHost(ctypes.c_int(n), ctypes.c_longlong(offset), ctypes.c_uint(seed & 0xFFFFFFFF), ctypes.c_double(p),
+                                        ctypes.c_void_p(out.data_ptr()), ctypes.byref(cnt))
+    if rc != 0:
+        lib.FB_OpsLastError.restype = ctypes.c_char_p
+        raise RuntimeError(lib.FB_OpsLastError().decode())
+    return out[: cnt.value].long()
+
+
 def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total: int = 0, replicated: bool = False) -> Tuple[np.ndarray, int]:
     """Rows used to find bin boundaries.
 
-    A global row is sampled iff a uniform number drawn for it (from a generator seeded by the 256K-row
-    chunk the row falls into) is below ``sample_cnt / total``. The choice depends only on the GLOBAL
+    A global row is sampled iff a Philox number keyed on (seed, global row id) is below ``sample_cnt / total``. The choice depends only on the GLOBAL
     row id, so the sample - and with it every bin boundary - is the same however the rows are sharded
     over ranks. Each rank contributes the sampled rows of its shard; the shards are concatenated in
     rank order. ``replicated``: every rank holds ALL rows (feature-parallel training), so the local sample
@@ -54,22 +78,7 @@ def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total
             d.all_gather_object(offs, n)
             offset = int(sum(offs[:rank]))
     p = min(1.0, sample_cnt / max(1, total))
-    chunk = 1 << 18
-    picks = []
-    c = offset // chunk
-    pos = offset
-    end = offset + n
-    while pos < end:
-        lo = pos - c * chunk
-        hi = min(chunk, end - c * chunk)
-        g = torch.Generator(device=t.device)
-        g.manual_seed((seed * 1000003 + c) & 0x7FFFFFFFFFFF)
-        u = torch.rand(chunk, generator=g, device=t.device)[lo:hi]
-        sel = torch.nonzero(u < p, as_tuple=False).flatten() + (pos - offset)
-        picks.append(sel)
-        pos = c * chunk + hi
-        c += 1
-    idx = torch.cat(picks) if picks else torch.zeros(0, dtype=torch.int64, device=t.device)
+    idx = _bernoulli_rows(t, n, offset, seed, p)
     keep = t.dtype in (torch.float16, torch.float32, torch.float64, torch.int8, torch.int16, torch.int32, torch.uint8)
     sdt = t.dtype if keep else torch.float64
     picked = t[idx].to(sdt)
