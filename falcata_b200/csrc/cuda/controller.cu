@@ -19,7 +19,7 @@ constexpr int kCtrlMaxLeaves = 1024;
 
 __global__ void InitLevelCtrlKernel(LevelCtrl* c, int* frontier) {
   c->num_leaves = 1; c->next_slot = 1; c->done = 0; c->level = 0; c->num_splits = 0; c->num_children = 1; c->total_chunks = 0; c->total_blocks = 0;
-  c->frontier_count = 1; c->journal_count = 0; c->pad0 = c->pad1 = 0;
+  c->frontier_count = 1; c->journal_count = 0; c->pad0 = 0; c->skip_search = 0;
   frontier[0] = 0;
 }
 
@@ -114,8 +114,12 @@ __global__ void __launch_bounds__(kCtrlThreads) LevelControllerKernel(CtrlArgs a
   for (int s = threadIdx.x; s < S; s += kCtrlThreads) { a.frontier[2 * s] = chosen[s]; a.frontier[2 * s + 1] = base_leaf + s; }
   if (threadIdx.x == 0) {
     c->num_leaves = base_leaf + S; c->next_slot = base_slot + S; c->journal_count = base_journal + S; c->level += 1;
-    c->num_splits = S; c->num_children = 2 * S; c->total_chunks = s_chunks[S]; c->total_blocks = s_blocks[S];
-    c->frontier_count = 2 * S;
+    // A level that uses up the leaf budget ends the tree: its children are partitioned (the score update and the
+    // leaf counts need their windows) but neither constructed nor searched.
+    const bool last = base_leaf + S >= a.max_leaves;
+    c->num_splits = S; c->num_children = 2 * S; c->total_chunks = s_chunks[S]; c->total_blocks = last ? 0 : s_blocks[S];
+    c->skip_search = last ? 1 : 0;
+    c->frontier_count = last ? 0 : 2 * S;
     if (S == 0) c->done = 1; else c->pad0 = c->level;   // pad0: last level that applied a split
   }
 }

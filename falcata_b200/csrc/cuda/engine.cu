@@ -145,7 +145,7 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     std::vector<int> ident(train->num_total_bin); for (int b = 0; b < train->num_total_bin; ++b) ident[b] = b;
     bin_identity_.Upload(ident, stream_);
     const size_t F = std::max(1, train->num_features);
-    cand_local_.Alloc(static_cast<size_t>(NL) * F); vote_sums_.Alloc(NL); voted_.Alloc(static_cast<size_t>(NL) * F);
+    cand_local_.Alloc(static_cast<size_t>(NL) * F); cand_local_.Zero(stream_); vote_sums_.Alloc(NL); voted_.Alloc(static_cast<size_t>(NL) * F);
     features_all_.Alloc(F); sub_features_all_.Alloc(F);
     global_max_.Alloc(2 * K_);
   } else if (world_ > 1) {
@@ -167,7 +167,7 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     pool_.Alloc(pool_bytes_);
     pool_base_ = pool_.get();
   }
-  cand_.Alloc(static_cast<size_t>(NL) * std::max<size_t>(1, owned_features_.size()));
+  cand_.Alloc(static_cast<size_t>(NL) * std::max<size_t>(1, owned_features_.size())); cand_.Zero(stream_);
   hist_tasks_.Alloc(NL);
   const size_t max_chunks = static_cast<size_t>(n_) / kPartChunk + NL + 1;
   bits_.Alloc(max_chunks * (kPartChunk / 32)); chunk_left_.Alloc(max_chunks); split_left_total_.Alloc(NL);

@@ -16,7 +16,8 @@ namespace fb {
 struct LevelCtrl {
   int num_leaves, next_slot, done, level;
   int num_splits, num_children, total_chunks, total_blocks;
-  int frontier_count, journal_count, pad0, pad1;
+  int frontier_count, journal_count, pad0;
+  int skip_search;   // 1: this level used up the leaf budget - its children can never split, so their construct and search are skipped
 };
 // One applied split, in application order: enough for the host to rebuild the tree after the last level.
 struct SplitJournal { int leaf, right_leaf, parent_global, pad; SplitRecord rec; };

@@ -172,6 +172,7 @@ __device__ void ScanCategoricalWarp(const FindArgs& a, const BinSrc& src, char* 
 template <bool QUANT>
 __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
   if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) return;
+  if (a.ctrl != nullptr && a.ctrl->skip_search) return;   // the tree is complete: nothing was constructed for these children
   // multi-rank: the owned slices are complete once every rank's construct has raised its flag
   if (a.wait.world > 1) FabricWaitAll(a.wait);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -338,7 +339,10 @@ __global__ void ReduceBestKernel(FindArgs a) {
   __shared__ SplitRecord s_rec;
   __shared__ double s_gain[128]; __shared__ int s_feat[128], s_thr[128], s_idx[128];
   double bg = -1.0 / 0.0; int bf = -1, bt = 0, bi = -1;
-  for (int k = threadIdx.x; k < a.num_features; k += blockDim.x) {
+  // a level that ended the tree was not searched: its candidate slots hold nothing meaningful, the record stays
+  // empty and only the children's global row counts are settled here
+  const bool searched = !(a.ctrl != nullptr && a.ctrl->skip_search);
+  for (int k = threadIdx.x; searched && k < a.num_features; k += blockDim.x) {
     const CandLite c = a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + k];
     const int rf = c.feature >= 0 ? a.meta[c.feature].real_index : -1;
     if (SplitBetter(c.gain, rf, c.threshold, bg, bf, bt)) { bg = c.gain; bf = rf; bt = c.threshold; bi = k; }
