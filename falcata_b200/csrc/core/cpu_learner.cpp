@@ -129,7 +129,7 @@ class CPUTreeLearner : public TreeLearner {
   std::vector<int8_t> node_feature_mask_;
   std::vector<int64_t> voted_hist_i_; std::vector<double> voted_hist_;
   std::vector<int8_t> voted_;      // voting-parallel: features whose histograms are globally reduced for the current leaf
-  int cur_tree_index_ = 0;
+  int cur_tree_index_ = 0, cur_leaf_id_ = 0;
   Random extra_rand_{6};
 };
 
@@ -274,7 +274,7 @@ void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanI
   int64_t mgi = 0, mhi = 0; double mgd = 0, mhd = 0; int mcnt = 0;
   if (skip >= 0) { mgi = gi[skip]; mhi = hi[skip]; mgd = gd[skip]; mhd = hd[skip]; mcnt = BinCountEstimate(binh(skip), L.cnt_factor); }
   int rand_t = -1;
-  if (sp_.extra_trees && nb > 2) rand_t = const_cast<Random&>(extra_rand_).NextInt(0, nb - 1);
+  if (sp_.extra_trees && nb > 2) rand_t = ExtraTreesThreshold(static_cast<uint32_t>(cfg_.extra_seed), cur_tree_index_, cur_leaf_id_, m.real_index, nb);
   double best_gain = -std::numeric_limits<double>::infinity(); int best_rank = 1 << 30;
   SplitRecord cand; InitSplitRecord(&cand);
   int64_t pgi = 0, phi = 0; double pgd = 0, phd = 0; int pc = 0;
@@ -394,6 +394,7 @@ void CPUTreeLearner::SyncBestSplit(SplitRecord* rec) const {
 
 void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index) {
   ScopedTimer timer("CPUTreeLearner::FindBestSplit");
+  cur_leaf_id_ = leaf_id;
   InitSplitRecord(&leaf->best);
   if (sp_.max_depth > 0 && leaf->depth >= sp_.max_depth) return;
   const int64_t n_global = leaf->global_count;
@@ -471,9 +472,9 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
   SplitRecord best; InitSplitRecord(&best);
   {
     // one record per feature on the worker threads, merged in feature order (SplitBetter is a total order, so the
-    // result does not depend on the thread count); extra_trees draws from a shared generator and stays serial
+    // result does not depend on the thread count)
     std::vector<SplitRecord> per(ds_->num_features);
-    const int nt = sp_.extra_trees ? 1 : std::max(1, std::min(omp_get_max_threads(), ds_->num_features / 2));
+    const int nt = std::max(1, std::min(omp_get_max_threads(), ds_->num_features / 2));
 #pragma omp parallel for schedule(dynamic, 1) num_threads(nt)
     for (int f = 0; f < ds_->num_features; ++f) {
       InitSplitRecord(&per[f]);

@@ -203,6 +203,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   fa.features = features_.get(); fa.num_features = NF; fa.sub_features = sub_features_.get(); fa.num_sub_features = NS; fa.meta = dd_->feature_meta.get();
   fa.bin_local = bin_local_.get(); fa.pool = pool_base_; fa.slot_stride = slot_stride_; fa.leaves = leaves_.get(); fa.scales = scales_.get(); fa.params = sp_;
   fa.cand = cand_.get(); fa.best = best_.get(); fa.quant = quant_ ? 1 : 0;
+  fa.tree_index = tree_index; fa.extra_seed = static_cast<unsigned int>(cfg_.extra_seed);
   fa.has_categorical = 0; for (int f : feats) if (train_->feature_meta[f].bin_type != 0) fa.has_categorical = 1;
   // data-parallel: construct-done flags + staged slices + counts; both multi-rank modes all-gather the best records
   fa.wait.world = dp ? world_ : 1; fa.wait_best.world = world_; fa.sig.world = world_; fa.leaves_rw = leaves_.get();

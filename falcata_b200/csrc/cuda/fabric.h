@@ -87,10 +87,13 @@ class Fabric {
 };
 
 __device__ inline void FabricSignalDone(const FabricSignal& sig, unsigned int total_blocks) {
-  // call with all threads of the block; the block's global writes are ordered before the flag
+  // Call with all threads of the block; the block's global writes are ordered before the flag. Every block
+  // publishes its writes at device scope before it counts itself in (a device-scope fence is cheap; a
+  // system-scope one per block, with peer stores in flight, is not); the last block, which has observed all the
+  // others through the counter, issues the one system-scope fence and raises the flags with release stores.
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
+    __threadfence();
     const unsigned int prev = atomicAdd(sig.done_counter, 1u);
     if (prev + 1 == total_blocks) {
       *sig.done_counter = 0;

@@ -196,13 +196,23 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
     if (s >= nstage || wbeg + r >= wend) return -1;
     return a.identity_root ? static_cast<int>(ident0 + r) : idx[r];
   };
+  // Root level with 32-byte rows: a stage's 32 rows are one contiguous kilobyte, so the lanes copy it as 64
+  // consecutive 16-byte pieces (two fully coalesced requests per warp) instead of two half-used sectors per lane.
+  const bool block_copy = a.identity_root != 0 && a.row_stride == 32 && g0 == 0 && copy16 == 2;
   auto issue = [&](int s, int row) {
     if (row >= 0) {
       const int slot = s % kLaneStages;
-      const unsigned char* src = a.rows + static_cast<size_t>(row) * a.row_stride + g0;
-      unsigned char* dst = rows_w + (slot * 32 + lane) * 32;
-      __pipeline_memcpy_async(dst, src, 16);
-      if (copy16 > 1) __pipeline_memcpy_async(dst + 16, src + 16, 16);
+      if (block_copy && wbeg + s * 32 + 32 <= wend) {
+        const unsigned char* src = a.rows + static_cast<size_t>(ident0 + static_cast<long long>(s) * 32) * 32 + lane * 16;
+        unsigned char* dst = rows_w + slot * 32 * 32 + lane * 16;
+        __pipeline_memcpy_async(dst, src, 16);
+        __pipeline_memcpy_async(dst + 512, src + 512, 16);
+      } else {
+        const unsigned char* src = a.rows + static_cast<size_t>(row) * a.row_stride + g0;
+        unsigned char* dst = rows_w + (slot * 32 + lane) * 32;
+        __pipeline_memcpy_async(dst, src, 16);
+        if (copy16 > 1) __pipeline_memcpy_async(dst + 16, src + 16, 16);
+      }
       __pipeline_memcpy_async(gh_w + slot * 32 + lane, a.gh_base + static_cast<size_t>(row) * a.gh_stride, 4);
     }
     __pipeline_commit();

@@ -107,6 +107,7 @@ struct FindArgs {
   CandLite* cand;                                 // [num_children x num_features]
   SplitRecord* best;                              // [leaf]
   int quant;
+  int tree_index; unsigned int extra_seed;        // extra_trees: key of the per-(tree, leaf, feature) threshold draw
   int has_categorical;                            // some searched feature is categorical: the kernel gets its shared scratch
   // ---- voting-parallel (see VoteArgs) ----
   int local_vote;                                 // 1: local pass - leaf totals and count are this rank's (vote_sums, LeafInfo.count)

@@ -266,6 +266,7 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
 
   double best_gain = -1.0 / 0.0; int best_rank = 1 << 30, best_t = 0, best_pass = 0, best_lc = 0;
   long long best_lgi = 0, best_lhi = 0; double best_lg = 0, best_lh = 0;
+  const int rand_t = a.params.extra_trees ? ExtraTreesThreshold(a.extra_seed, a.tree_index, ch.leaf, m.real_index, nb) : -1;
   Acc carry; carry.gi = carry.hi = 0; carry.gd = carry.hd = 0; carry.c = 0;
   for (int b0 = 0; b0 < nb; b0 += 32) {
     const int b = b0 + lane;
@@ -289,7 +290,7 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
       if (lane >= o) { gi += tg; hi += th; gd += dg; hd += dh; c += tc; }
     }
     gi += carry.gi; hi += carry.hi; gd += carry.gd; hd += carry.hd; c += carry.c;
-    if (b <= nb - 2) {
+    if (b <= nb - 2 && (rand_t < 0 || b == rand_t)) {
       for (int pass = 0; pass < (two_pass ? 2 : 1); ++pass) {
         if (b == skip && pass == 1 && m.missing_type == 1) continue;
         long long lgi = gi, lhi = hi; int lc = c; double lg, lh;

@@ -153,6 +153,14 @@ FB_HD inline double EvalCandidate(double lg, double lh, int lcnt, const LeafScan
   return FB_SUB(gain, L.min_gain_shift);
 }
 
+// extra_trees: the one threshold (0 .. nb-2) that a (tree, leaf, feature) evaluates. A counter-based draw, so
+// the host learner, the device kernel and any rank count pick the same threshold.
+FB_HD inline int ExtraTreesThreshold(uint32_t seed, int tree_index, int leaf, int real_feature, int nb) {
+  if (nb <= 2) return -1;
+  const uint32_t r = Philox4x32_10(static_cast<uint32_t>(tree_index), static_cast<uint32_t>(leaf), static_cast<uint32_t>(real_feature), 0xE7E7u, seed, 0x7EE5u).v[0];
+  return static_cast<int>(r % static_cast<uint32_t>(nb - 1));
+}
+
 // Scan order of the numerical threshold search. For a feature with `nb` bins:
 //   pass 0 (reverse): t = last .. 0, missing values (zero bin / NaN bin) counted on the LEFT, default_left = 1
 //   pass 1 (forward): t = 0 .. last, missing values counted on the RIGHT, default_left = 0 (only when the

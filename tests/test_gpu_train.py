@@ -241,3 +241,17 @@ def test_device_ndcg_matches_a_plain_computation():
             out[k].append(dcg / idcg if idcg > 0 else 1.0)
     assert abs(np.mean(out[3]) - res["train"]["ndcg@3"][-1]) < 1e-5
     assert abs(np.mean(out[10]) - res["train"]["ndcg@10"][-1]) < 1e-5
+
+
+def test_extra_trees_on_device_matches_host():
+    # one random threshold per (tree, leaf, feature), drawn from a counter-based generator: both arms evaluate the
+    # same thresholds, so the first tree is the same digit for digit
+    X, y = make_regression(20000, 12)
+    y = np.round(y * 8) / 8
+    base = {"objective": "none", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "grow_policy": "level", "min_data_in_leaf": 20,
+            "seed": 3, "extra_trees": True}
+    bc = fb.train({**base, "device_type": "cpu"}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
+    bg = fb.train({**base, "device_type": "cuda"}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
+    plain = fb.train({**base, "device_type": "cuda", "extra_trees": False}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
+    assert model_body(bc.model_to_string()) == model_body(bg.model_to_string())
+    assert model_body(bg.model_to_string()) != model_body(plain.model_to_string())
