@@ -124,6 +124,7 @@ class CudaEngine : public DeviceEngine {
   int lane_mode_ = 0, lane_bins_ = 64, sub_rows_ = 1 << 30;
   // compact per-tree view of the sampled feature groups
   DevBuf<uint8_t> compact_rows_; DevBuf<int> compact_groups_, compact_start_, compact_count_;
+  std::vector<int> compact_list_; bool compact_p4_ = false;
   // device controller state
   bool use_ctrl_ = false; int levels_hint_ = 8;
   DevBuf<LevelCtrl> ctrl_; DevBuf<int> frontier_; DevBuf<SplitJournal> journal_;

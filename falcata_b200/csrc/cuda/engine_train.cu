@@ -187,13 +187,19 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     }
     std::vector<int> glist, gstart, gcount;
     for (int g = 0; g < train_->num_groups; ++g) if (want[g]) { glist.push_back(g); gstart.push_back(train_->group_bin_start[g]); gcount.push_back(train_->group_num_bin[g]); }
-    if (!glist.empty() && 2 * glist.size() <= static_cast<size_t>(train_->num_groups)) {
-      const int cstride = (static_cast<int>(glist.size()) + 15) / 16 * 16;
-      compact_groups_.Upload(glist, stream_); compact_start_.Upload(gstart, stream_); compact_count_.Upload(gcount, stream_);
-      if (compact_rows_.size() < static_cast<size_t>(n_) * cstride) compact_rows_.Alloc(static_cast<size_t>(n_) * cstride);
-      LaunchCompactGather(dd_->cols.get(), n_, n_, compact_groups_.get(), static_cast<int>(glist.size()), compact_rows_.get(), cstride, stream_);
-      FB_CUDA(cudaStreamSynchronize(stream_));   // the host lists above go out of scope
-      ha.rows = compact_rows_.get(); ha.row_stride = cstride; ha.num_groups = static_cast<int>(glist.size());
+    // groups of at most 16 bins are also packed two per byte (B4): the view then pays off even with every group listed
+    const bool p4 = plan_.pack4 && train_->max_group_bin <= 16;
+    if (!glist.empty() && (p4 || 2 * glist.size() <= static_cast<size_t>(train_->num_groups))) {
+      const int nlist = static_cast<int>(glist.size());
+      const int cstride = p4 ? ((nlist + 1) / 2 + 15) / 16 * 16 : (nlist + 15) / 16 * 16;
+      if (glist != compact_list_ || p4 != compact_p4_) {   // the view depends on the list only: trees that sample the same groups reuse it
+        compact_groups_.Upload(glist, stream_); compact_start_.Upload(gstart, stream_); compact_count_.Upload(gcount, stream_);
+        if (compact_rows_.size() < static_cast<size_t>(n_) * cstride) compact_rows_.Alloc(static_cast<size_t>(n_) * cstride);
+        LaunchCompactGather(dd_->cols.get(), n_, n_, compact_groups_.get(), nlist, compact_rows_.get(), cstride, stream_, p4);
+        FB_CUDA(cudaStreamSynchronize(stream_));   // the host lists above go out of scope
+        compact_list_ = glist; compact_p4_ = p4;
+      }
+      ha.rows = compact_rows_.get(); ha.row_stride = cstride; ha.num_groups = nlist; ha.pack4 = p4 ? 1 : 0;
       ha.group_bin_start = compact_start_.get(); ha.group_bin_count = compact_count_.get();
       first_group = glist[0];
     }

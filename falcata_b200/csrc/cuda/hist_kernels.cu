@@ -181,7 +181,8 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
   const int nrows = static_cast<int>(max(0LL, min(static_cast<long long>(a.rows_per_block), task.count - row0)));
   const int g0 = blockIdx.y * 32;
   const int ng = min(32, a.num_groups - g0);
-  const int copy16 = min(2, (a.row_stride - g0) / 16);          // 16-byte pieces of this part inside the row
+  const int byte0 = a.pack4 ? g0 / 2 : g0;                       // first byte of this 32-group part inside the row
+  const int copy16 = a.pack4 ? 1 : min(2, (a.row_stride - g0) / 16);   // 16-byte pieces of this part inside the row
   int* tile = tiles + warp * kTile;
   for (int i = lane; i < kTile; i += 32) tile[i] = 0;
   __syncwarp();
@@ -198,7 +199,7 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
   };
   // Root level with 32-byte rows: a stage's 32 rows are one contiguous kilobyte, so the lanes copy it as 64
   // consecutive 16-byte pieces (two fully coalesced requests per warp) instead of two half-used sectors per lane.
-  const bool block_copy = a.identity_root != 0 && a.row_stride == 32 && g0 == 0 && copy16 == 2;
+  const bool block_copy = a.identity_root != 0 && a.row_stride == 32 && g0 == 0 && copy16 == 2 && !a.pack4;
   auto issue = [&](int s, int row) {
     if (row >= 0) {
       const int slot = s % kLaneStages;
@@ -208,7 +209,7 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
         __pipeline_memcpy_async(dst, src, 16);
         __pipeline_memcpy_async(dst + 512, src + 512, 16);
       } else {
-        const unsigned char* src = a.rows + static_cast<size_t>(row) * a.row_stride + g0;
+        const unsigned char* src = a.rows + static_cast<size_t>(row) * a.row_stride + byte0;
         unsigned char* dst = rows_w + (slot * 32 + lane) * 32;
         __pipeline_memcpy_async(dst, src, 16);
         if (copy16 > 1) __pipeline_memcpy_async(dst + 16, src + 16, 16);
@@ -228,12 +229,14 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
     __syncwarp();
     const int slot = s % kLaneStages;
     const int cnt = min(32, wend - wbeg - s * 32);
-    const unsigned char* sr = rows_w + slot * 32 * 32 + lane;
+    const unsigned char* sr = rows_w + slot * 32 * 32 + (a.pack4 ? (lane >> 1) : lane);
     const int* sg = gh_w + slot * 32;
+    const int nshift = a.pack4 ? (lane & 1) * 4 : 0, nmask = a.pack4 ? 15 : 255;   // nibble of this lane's group inside its byte
     if (cnt == 32) {
 #pragma unroll 2
       for (int j = 0; j < 32; j += 4) {
-        const int a0 = sr[j * 32] * 32 + lane, a1 = sr[(j + 1) * 32] * 32 + lane, a2 = sr[(j + 2) * 32] * 32 + lane, a3 = sr[(j + 3) * 32] * 32 + lane;
+        const int a0 = ((sr[j * 32] >> nshift) & nmask) * 32 + lane, a1 = ((sr[(j + 1) * 32] >> nshift) & nmask) * 32 + lane,
+                  a2 = ((sr[(j + 2) * 32] >> nshift) & nmask) * 32 + lane, a3 = ((sr[(j + 3) * 32] >> nshift) & nmask) * 32 + lane;
         const int4 g4 = *reinterpret_cast<const int4*>(sg + j);     // same address in every lane: one broadcast load
         if (active) {
           int v0 = tile[a0], v1 = tile[a1], v2 = tile[a2], v3 = tile[a3];
@@ -245,7 +248,7 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
         }
       }
     } else {
-      for (int j = 0; j < cnt; ++j) { const int b = sr[j * 32]; const int g = sg[j]; if (active) tile[b * 32 + lane] += g; }
+      for (int j = 0; j < cnt; ++j) { const int b = (sr[j * 32] >> nshift) & nmask; const int g = sg[j]; if (active) tile[b * 32 + lane] += g; }
     }
     __syncwarp();   // every lane is done with this stage's buffer before it is refilled
   }
@@ -335,10 +338,33 @@ __global__ void __launch_bounds__(256) CompactGatherKernel(const uint8_t* __rest
   }
 }
 
+// 4-bit variant: 32 rows x 64 listed groups per block, two groups per output byte.
+__global__ void __launch_bounds__(256) CompactGatherPack4Kernel(const uint8_t* __restrict__ cols, long long col_stride, int n, const int* __restrict__ groups,
+                                                                int num_groups, uint8_t* __restrict__ out, int out_stride) {
+  __shared__ uint8_t tile[64][33];
+  const int row0 = blockIdx.x * 32, j0 = blockIdx.y * 64;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int jj = ty; jj < 64; jj += 8) {
+    const int j = j0 + jj, row = row0 + tx;
+    tile[jj][tx] = (j < num_groups && row < n) ? cols[static_cast<size_t>(groups[j]) * col_stride + row] : 0;
+  }
+  __syncthreads();
+  for (int rr = ty; rr < 32; rr += 8) {
+    const int row = row0 + rr, byte = j0 / 2 + tx;
+    if (row < n && byte < out_stride) out[static_cast<size_t>(row) * out_stride + byte] = static_cast<uint8_t>((tile[2 * tx][rr] & 15) | (tile[2 * tx + 1][rr] << 4));
+  }
+}
+
 }  // namespace
 
-void LaunchCompactGather(const uint8_t* cols, long long col_stride, int n, const int* groups, int num_groups, uint8_t* out, int out_stride, cudaStream_t s) {
+void LaunchCompactGather(const uint8_t* cols, long long col_stride, int n, const int* groups, int num_groups, uint8_t* out, int out_stride, cudaStream_t s, bool pack4) {
   if (n <= 0 || num_groups <= 0) return;
+  if (pack4) {
+    dim3 grid((n + 31) / 32, (2 * out_stride + 63) / 64);
+    CompactGatherPack4Kernel<<<grid, 256, 0, s>>>(cols, col_stride, n, groups, num_groups, out, out_stride);
+    FB_LAUNCHED(); FB_KERNEL_CHECK();
+    return;
+  }
   dim3 grid((n + 31) / 32, (out_stride + 31) / 32);
   CompactGatherKernel<<<grid, 256, 0, s>>>(cols, col_stride, n, groups, num_groups, out, out_stride);
   FB_LAUNCHED(); FB_KERNEL_CHECK();

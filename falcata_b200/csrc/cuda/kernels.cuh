@@ -66,6 +66,7 @@ struct HistArgs {
   const HistTask* tasks; int num_tasks; int total_blocks;
   const HistPartition* parts; int num_parts; int max_part_bins;
   const int* group_bin_start;
+  int pack4;                    // 1 (compact view of groups with at most 16 bins): two groups per byte, low nibble first
   const int* group_bin_count;   // non-null (compact view): bins per listed group; null: groups are consecutive in the bin space
   int rows_per_block; int sub_rows;
   int identity_root;        // 1: task rows are 0..count-1 (no index load)
@@ -80,7 +81,8 @@ void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s);
 // K9: per-tree compact view. out[row][j] = cols[groups[j]][row] for the listed (sampled) feature groups: a dense
 // row-major matrix with only the columns this tree can split on, read from the column-major copy (coalesced
 // along rows) and written in 32-byte row pieces through a shared-memory transpose tile.
-void LaunchCompactGather(const uint8_t* cols, long long col_stride, int n, const int* groups, int num_groups, uint8_t* out, int out_stride, cudaStream_t s);
+void LaunchCompactGather(const uint8_t* cols, long long col_stride, int n, const int* groups, int num_groups, uint8_t* out, int out_stride, cudaStream_t s,
+                         bool pack4 = false);   // pack4: out[row][j / 2] holds listed groups j (low nibble) and j + 1 (high nibble)
 void LaunchHistConstructFloat(const HistArgs& a, cudaStream_t s);
 // tcgen05 one-hot instance (same arguments, same result); returns false when the shape is outside what it covers
 bool LaunchHistConstructQuantTC(const HistArgs& a, cudaStream_t s);

@@ -255,3 +255,15 @@ def test_extra_trees_on_device_matches_host():
     plain = fb.train({**base, "device_type": "cuda", "extra_trees": False}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
     assert model_body(bc.model_to_string()) == model_body(bg.model_to_string())
     assert model_body(bg.model_to_string()) != model_body(plain.model_to_string())
+
+
+@pytest.mark.parametrize("ff", [1.0, 0.4])
+def test_four_bit_packed_view_keeps_the_model(ff):
+    # max_bin 15: every group fits a nibble, the construct kernel reads a two-groups-per-byte copy of the sampled columns
+    X, y = make_binary(30000, 37)
+    p = {"objective": "binary", "num_leaves": 31, "max_bin": 15, "verbosity": -1, "quant_mode": "stochastic", "device_type": "cuda", "feature_fraction": ff,
+         "min_data_in_leaf": 5}
+    mk = lambda: fb.Dataset(X, y, params={"max_bin": 15})
+    a = fb.train(dict(p, cuda_plan="auto"), mk(), 8).model_to_string()
+    b = fb.train(dict(p, cuda_plan="auto,pack4:off,compact_view:off"), mk(), 8).model_to_string()
+    assert model_body(a) == model_body(b)
