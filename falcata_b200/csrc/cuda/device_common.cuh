@@ -143,6 +143,13 @@ __device__ inline bool WaitFlagGE(const volatile unsigned int* flag, unsigned in
   return false;
 }
 
+// Flag store that follows an explicit system-scope fence: the fence orders the data, so the stores to the
+// individual peers need no ordering among themselves and go out back to back (a release store per peer would
+// wait for the previous one's round trip).
+__device__ inline void StoreFlagAfterFence(unsigned int* flag, unsigned int value) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
+}
+
 __device__ inline void StoreFlagRelease(unsigned int* flag, unsigned int value) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
 }

@@ -21,7 +21,7 @@ __global__ void FabricAllReduceKernel(FabricView v, int op, const void* src, voi
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
-    for (int r = 0; r < v.world; ++r) StoreFlagRelease(reinterpret_cast<unsigned int*>(v.base[r] + flag_off) + v.rank, epoch);
+    for (int r = 0; r < v.world; ++r) StoreFlagAfterFence(reinterpret_cast<unsigned int*>(v.base[r] + flag_off) + v.rank, epoch);
   }
   FabricWait w; w.world = v.world; w.flags = reinterpret_cast<const unsigned int*>(v.base[v.rank] + flag_off); w.epoch = epoch; w.max_spins = v.max_spins; w.status = v.status;
   FabricWaitAll(w);

@@ -98,7 +98,7 @@ __device__ inline void FabricSignalDone(const FabricSignal& sig, unsigned int to
     if (prev + 1 == total_blocks) {
       *sig.done_counter = 0;
       __threadfence_system();
-      for (int r = 0; r < sig.world; ++r) StoreFlagRelease(sig.peer_flag[r], sig.epoch);
+      for (int r = 0; r < sig.world; ++r) StoreFlagAfterFence(sig.peer_flag[r], sig.epoch);
     }
   }
 }
