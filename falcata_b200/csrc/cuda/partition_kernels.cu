@@ -47,15 +47,22 @@ __global__ void __launch_bounds__(kPartThreads) PartitionFlagsKernel(PartArgs a)
   const int pos0 = local_chunk * kPartChunk;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int cnt = 0;
+  // three separate unrolled passes keep eight independent row-id loads, then eight independent bin loads, in
+  // flight per thread (the kernel is bound by the latency of this dependent pair, not by bandwidth)
+  int rowv[kRowsPerThread]; int binv[kRowsPerThread];
 #pragma unroll
   for (int k = 0; k < kRowsPerThread; ++k) {
     const int pos = pos0 + k * kPartThreads + threadIdx.x;
-    bool left = false;
-    if (pos < sp.count) {
-      const int row = idx[pos];
-      const int gb = a.cols != nullptr ? a.cols[static_cast<size_t>(sp.group) * a.col_stride + row] : a.rows[static_cast<size_t>(row) * a.row_stride + sp.group];
-      left = GoLeft(sp, gb);
-    }
+    rowv[k] = pos < sp.count ? idx[pos] : -1;
+  }
+#pragma unroll
+  for (int k = 0; k < kRowsPerThread; ++k) {
+    const int row = rowv[k];
+    binv[k] = row < 0 ? 0 : (a.cols != nullptr ? a.cols[static_cast<size_t>(sp.group) * a.col_stride + row] : a.rows[static_cast<size_t>(row) * a.row_stride + sp.group]);
+  }
+#pragma unroll
+  for (int k = 0; k < kRowsPerThread; ++k) {
+    const bool left = rowv[k] >= 0 && GoLeft(sp, binv[k]);
     const unsigned int word = __ballot_sync(0xffffffffu, left);
     if (lane == 0) {
       const size_t wi = static_cast<size_t>(chunk) * kWordsPerChunk + k * (kPartThreads / 32) + warp;
@@ -141,7 +148,15 @@ __global__ void __launch_bounds__(kPartThreads) PartitionScatterKernel(PartArgs 
   __shared__ int s_pref[kWordsPerChunk];
   if (threadIdx.x < kWordsPerChunk) s_bits[threadIdx.x] = a.bits[static_cast<size_t>(chunk) * kWordsPerChunk + threadIdx.x];
   __syncthreads();
-  if (threadIdx.x == 0) { int acc = 0; for (int w = 0; w < kWordsPerChunk; ++w) { s_pref[w] = acc; acc += __popc(s_bits[w]); } }
+  if (threadIdx.x < 32) {
+    // exclusive prefix of the 64 word counts by one warp: two words per lane, then a shuffle scan of the lane sums
+    const int l = threadIdx.x;
+    const int c0 = __popc(s_bits[2 * l]), c1 = __popc(s_bits[2 * l + 1]);
+    int incl = c0 + c1;
+    for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, incl, o); if (l >= o) incl += y; }
+    const int excl = incl - (c0 + c1);
+    s_pref[2 * l] = excl; s_pref[2 * l + 1] = excl + c0;
+  }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
