@@ -70,7 +70,12 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   // objective descriptor
   objd_.kind = obj ? obj->DeviceKind() : kObjCustom; objd_.num_class = cfg.num_class; objd_.p0 = objd_.p1 = objd_.p2 = 0; objd_.max_docs = 0;
   if (obj != nullptr) {
-    if (objd_.kind < 0) Log::Fatal("Objective %s has no device kernel; use device_type=cpu", obj->GetName());
+    if (objd_.kind < 0) {
+      // no gradient kernel for this objective: the scores go to the host every round, the objective's own code
+      // computes the gradients there and they come back for the device learner
+      Log::Warning("Objective %s has no device gradient kernel: gradients are computed on the host every round", obj->GetName());
+      host_gradients_ = true;
+    }
     objd_.p0 = obj->DeviceParam(0); objd_.p1 = obj->DeviceParam(1); objd_.p2 = obj->DeviceParam(2);
     if (objd_.kind == kObjLambdarank) {
       const auto& qb = train->metadata.query_boundaries;

@@ -72,6 +72,7 @@ class CudaEngine : public DeviceEngine {
   const Dataset* train_; DeviceDataset* dd_; const ObjectiveFunction* obj_;
   int K_ = 1, n_ = 0;
   bool quant_ = false;
+  bool host_gradients_ = false;   // the objective has no device kernel: gradients come from its host code each round
   cudaStream_t stream_ = nullptr;
   int num_sms_ = 148;
   SplitParams sp_;

@@ -73,6 +73,18 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
     } else LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_, mask);
   } else {
     if (obj_ == nullptr) Log::Fatal("No objective function provided and no custom gradients given");
+    if (host_gradients_) {
+      const size_t total = static_cast<size_t>(n_) * K_;
+      std::vector<float> hs(total); std::vector<double> sc(total); std::vector<float> hg(total), hh(total);
+      FB_CUDA(cudaMemcpyAsync(hs.data(), score_.get(), sizeof(float) * total, cudaMemcpyDeviceToHost, stream_));
+      FB_CUDA(cudaStreamSynchronize(stream_));
+      for (size_t i = 0; i < total; ++i) sc[i] = hs[i];
+      obj_->GetGradients(sc.data(), hg.data(), hh.data());
+      FB_CUDA(cudaMemcpyAsync(grad_.get(), hg.data(), sizeof(float) * total, cudaMemcpyHostToDevice, stream_));
+      FB_CUDA(cudaMemcpyAsync(hess_.get(), hh.data(), sizeof(float) * total, cudaMemcpyHostToDevice, stream_));
+      FB_CUDA(cudaStreamSynchronize(stream_));
+      LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_, mask);
+    } else
     LaunchObjectiveGradients(objd_, score_.get(), dd_->label.get(), dd_->weight.size() ? dd_->weight.get() : nullptr,
                              dd_->query_boundaries.size() ? dd_->query_boundaries.get() : nullptr, dd_->num_queries, label_gain_.get(),
                              static_cast<int>(label_gain_.size()), n_, grad_.get(), hess_.get(), maxbuf_.get(), stream_);

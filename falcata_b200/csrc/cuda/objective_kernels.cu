@@ -246,12 +246,15 @@ __global__ void InterleaveKernel(const float* __restrict__ grad, const float* __
   }
 }
 
-__global__ void SumPartialsKernel(const double* __restrict__ partial, int nblocks, double* __restrict__ out2) {
-  // one warp, fixed order: lane l takes blocks l, l+32, ...; then a fixed shuffle tree
+__global__ void __launch_bounds__(1024) SumPartialsKernel(const double* __restrict__ partial, int nblocks, double* __restrict__ out2) {
+  // one block, fixed order: thread t takes blocks t, t+1024, ...; then a fixed shared-memory tree (the same sum on every run)
+  __shared__ double sa[1024], sb[1024];
   double a = 0, b = 0;
-  for (int k = threadIdx.x; k < nblocks; k += 32) { a += partial[2 * k]; b += partial[2 * k + 1]; }
-  for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
-  if (threadIdx.x == 0) { out2[0] = a; out2[1] = b; }
+  for (int k = threadIdx.x; k < nblocks; k += 1024) { a += partial[2 * k]; b += partial[2 * k + 1]; }
+  sa[threadIdx.x] = a; sb[threadIdx.x] = b;
+  __syncthreads();
+  for (int o = 512; o > 0; o >>= 1) { if (threadIdx.x < o) { sa[threadIdx.x] += sa[threadIdx.x + o]; sb[threadIdx.x] += sb[threadIdx.x + o]; } __syncthreads(); }
+  if (threadIdx.x == 0) { out2[0] = sa[0]; out2[1] = sb[0]; }
 }
 
 }  // namespace
@@ -298,7 +301,7 @@ void LaunchInterleave(const float* grad, const float* hess, int n, float2* gh2, 
   if (blocks > partial_capacity) Log::Fatal("partial-sum buffer too small");
   InterleaveKernel<<<blocks, threads, 0, s>>>(grad, hess, n, gh2, partial, mask);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
-  SumPartialsKernel<<<1, 32, 0, s>>>(partial, blocks, root_sums_d);
+  SumPartialsKernel<<<1, 1024, 0, s>>>(partial, blocks, root_sums_d);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 

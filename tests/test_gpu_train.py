@@ -267,3 +267,13 @@ def test_four_bit_packed_view_keeps_the_model(ff):
     a = fb.train(dict(p, cuda_plan="auto"), mk(), 8).model_to_string()
     b = fb.train(dict(p, cuda_plan="auto,pack4:off,compact_view:off"), mk(), 8).model_to_string()
     assert model_body(a) == model_body(b)
+
+
+def test_objective_without_device_kernel_trains_through_host_gradients():
+    X, y = make_regression(15000, 8)
+    y = np.abs(y) + 1.0
+    p = {"objective": "mape", "num_leaves": 15, "verbosity": -1, "grow_policy": "level", "metric": "mape"}
+    dev = fb.train({**p, "device_type": "cuda"}, fb.Dataset(X, y), 30)
+    cpu = fb.train({**p, "device_type": "cpu"}, fb.Dataset(X, y), 30)
+    mape = lambda b: float(np.mean(np.abs(b.predict(X) - y) / np.maximum(1.0, np.abs(y))))
+    assert abs(mape(dev) - mape(cpu)) < 0.05 * mape(cpu) + 1e-3
