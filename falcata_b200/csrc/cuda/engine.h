@@ -128,6 +128,8 @@ class CudaEngine : public DeviceEngine {
   std::vector<int> compact_list_; bool compact_p4_ = false;
   // device controller state
   bool use_ctrl_ = false; int levels_hint_ = 8;
+  // score update enqueued from the device's leaf records, before the per-tree read-back
+  bool fast_score_ok_ = false, score_done_ = false; double cur_shrinkage_ = 1.0; float* cur_score_ = nullptr;
   DevBuf<LevelCtrl> ctrl_; DevBuf<int> frontier_; DevBuf<SplitJournal> journal_;
   PinnedBuf<LevelCtrl> h_ctrl_; PinnedBuf<SplitJournal> h_journal_; PinnedBuf<LeafInfo> h_root_;
   // bagging (device-drawn; -1 = no bag drawn)

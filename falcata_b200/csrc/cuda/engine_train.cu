@@ -105,6 +105,8 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
     const bool need = obj_ == nullptr || obj_->ClassNeedTrain(k);
     if (need && train_->num_features > 0) {
       cur_grad_ = grad + static_cast<size_t>(k) * n_; cur_hess_ = hess + static_cast<size_t>(k) * n_;
+      cur_shrinkage_ = shrinkage; cur_score_ = score_.get() + static_cast<size_t>(k) * n_; score_done_ = false;
+      fast_score_ok_ = !bagging && !(quant_ && cfg_.quant_train_renew_leaf) && !(obj_ != nullptr && obj_->IsRenewTreeOutput());
       tree.reset(TrainTree(k, iter * K_ + k));
     } else tree.reset(new Tree(2));
     if (tree->num_leaves > 1) {
@@ -114,7 +116,7 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
       tree->Shrink(shrinkage);
       // training rows through the final partition; validation rows by traversal
       clock_.Begin(st_score_, stream_);
-      if (!bagging) {
+      if (!bagging && !score_done_) {
         leaf_value_.Upload(tree->leaf_value.data(), tree->num_leaves, stream_);
         LaunchAddLeafOutputs(leaves_.get(), leaf_value_.get(), tree->num_leaves, idx_[0].get(), idx_[1].get(), score_.get() + static_cast<size_t>(k) * n_, stream_);
       }
@@ -333,24 +335,39 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
       clock_.End(stream_);
       construct_and_find();
     };
-    int enqueued = 0;
+    int enqueued = 0; bool records_ready = false;
     LevelCtrl hc;
     for (;;) {
       const int batch = enqueued == 0 ? std::max(1, levels_hint_) : 1;
       for (int k = 0; k < batch; ++k) enqueue_level();
+      const bool first = enqueued == 0;
       enqueued += batch;
+      if (first && fast_score_ok_) {
+        // the usual case: this batch completes the tree. The score update and the tree's records ride behind it, so
+        // the host waits once per tree and the GPU already has the update while the host rebuilds the tree.
+        clock_.Begin(st_score_, stream_);
+        LaunchAddLeafOutputsFromRecords(leaves_.get(), ctrl_.get(), cur_shrinkage_, NL, idx_[0].get(), idx_[1].get(), cur_score_, stream_);
+        clock_.End(stream_);
+      }
       clock_.Begin(st_sync_, stream_);
       FB_CUDA(cudaMemcpyAsync(h_ctrl_.get(), ctrl_.get(), sizeof(LevelCtrl), cudaMemcpyDeviceToHost, stream_));
+      if (first) { journal_.Download(h_journal_.get(), NL, stream_); leaves_.Download(h_leaves_.get(), NL, stream_); }
       clock_.End(stream_);
       if (world_ > 1) { const int st = fabric_->CheckStatus(stream_); if (st != 0) Log::Fatal("A cross-rank wait gave up (device status %d): a peer rank did not reach the same step", st); }
       else FB_CUDA(cudaStreamSynchronize(stream_));
       hc = *h_ctrl_.get();
-      if (hc.done || hc.num_leaves >= NL || hc.frontier_count == 0 || enqueued > 4 * NL) break;
+      const bool complete = hc.done || hc.num_leaves >= NL || hc.frontier_count == 0;
+      if (first && complete) records_ready = true;   // the journal and leaf records fetched with this batch are final
+      if (first && complete && fast_score_ok_ && hc.num_leaves > 1) score_done_ = true;   // the device-side update applied itself
+      if (complete || enqueued > 4 * NL) break;
     }
     levels_hint_ = std::max(1, hc.pad0);
-    journal_.Download(h_journal_.get(), hc.journal_count, stream_);
-    leaves_.Download(h_leaves_.get(), hc.num_leaves, stream_);
-    FB_CUDA(cudaStreamSynchronize(stream_));
+    if (!records_ready) {
+      // the tree needed more levels than the first batch: fetch its records now
+      journal_.Download(h_journal_.get(), hc.journal_count, stream_);
+      leaves_.Download(h_leaves_.get(), hc.num_leaves, stream_);
+      FB_CUDA(cudaStreamSynchronize(stream_));
+    }
     if (hc.journal_count == 0) { const LeafInfo& R = *h_root_.get(); tree->leaf_value[0] = R.output; tree->leaf_count[0] = R.num_data_global; tree->leaf_weight[0] = R.sum_h; return tree.release(); }
     { const LeafInfo& R = *h_root_.get(); tree->leaf_value[0] = R.output; tree->leaf_count[0] = R.num_data_global; tree->leaf_weight[0] = R.sum_h; }
     for (int j = 0; j < hc.journal_count; ++j) {

@@ -243,6 +243,8 @@ void LaunchGoss(const GossArgs& a, cudaStream_t s);
 
 // ----------------------------------------------------------------- score ----
 void LaunchAddLeafOutputs(const LeafInfo* leaves, const double* leaf_value, int num_leaves, const int* idx0, const int* idx1, float* score, cudaStream_t s);
+void LaunchAddLeafOutputsFromRecords(const LeafInfo* leaves, const LevelCtrl* ctrl, double shrinkage, int max_leaves, const int* idx0, const int* idx1, float* score,
+                                     cudaStream_t s);
 void LaunchAddConstant(float* score, int n, float v, cudaStream_t s);
 // per-leaf (sum g, sum h) of float gradients over the leaf windows: partial[2 * (leaf * slices + slice) + {0,1}]
 int LeafGradSumSlices();

@@ -22,6 +22,21 @@ __global__ void AddLeafOutputsKernel(const LeafInfo* __restrict__ leaves, const 
   for (int p = blockIdx.y * blockDim.x + threadIdx.x; p < L.count; p += gridDim.y * blockDim.x) score[idx[p]] += v;
 }
 
+// The same update straight from the device's leaf records, enqueued behind the last level without waiting for the
+// host: leaf value = record output x shrinkage (what the host tree holds after Shrink). It applies itself only when
+// the controller reports the tree complete and split at least once; otherwise it does nothing and the host-side
+// update runs after the read-back.
+__global__ void AddLeafOutputsFromRecordsKernel(const LeafInfo* __restrict__ leaves, const LevelCtrl* __restrict__ ctrl, double shrinkage, int max_leaves,
+                                                const int* __restrict__ idx0, const int* __restrict__ idx1, float* __restrict__ score) {
+  const LevelCtrl c = *ctrl;
+  const bool complete = c.done || c.num_leaves >= max_leaves || c.frontier_count == 0;
+  if (!complete || c.num_leaves <= 1 || static_cast<int>(blockIdx.x) >= c.num_leaves) return;
+  const LeafInfo L = leaves[blockIdx.x];
+  const float v = static_cast<float>(L.output * shrinkage);
+  const int* idx = (L.buffer ? idx1 : idx0) + L.begin;
+  for (int p = blockIdx.y * blockDim.x + threadIdx.x; p < L.count; p += gridDim.y * blockDim.x) score[idx[p]] += v;
+}
+
 // K6r: per-leaf sums of the TRUE (unquantized) gradients over the final partition, for leaf renewal.
 // grid (leaf, kRenewSlices): every slice walks a strided part of the leaf's window and reduces in a fixed
 // order; the host adds the slices (and the ranks) in a fixed order too.
@@ -180,6 +195,12 @@ __global__ void __launch_bounds__(1024) SumPartials2Kernel(const double* __restr
 void LaunchAddLeafOutputs(const LeafInfo* leaves, const double* leaf_value, int num_leaves, const int* idx0, const int* idx1, float* score, cudaStream_t s) {
   if (num_leaves <= 0) return;
   AddLeafOutputsKernel<<<dim3(num_leaves, 64), 256, 0, s>>>(leaves, leaf_value, idx0, idx1, score);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+void LaunchAddLeafOutputsFromRecords(const LeafInfo* leaves, const LevelCtrl* ctrl, double shrinkage, int max_leaves, const int* idx0, const int* idx1, float* score,
+                                     cudaStream_t s) {
+  if (max_leaves <= 0) return;
+  AddLeafOutputsFromRecordsKernel<<<dim3(max_leaves, 64), 256, 0, s>>>(leaves, ctrl, shrinkage, max_leaves, idx0, idx1, score);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 int LeafGradSumSlices() { return kRenewSlices; }
