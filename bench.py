@@ -170,8 +170,9 @@ def main() -> None:
         if os.environ.get("FALCATA_TIME_TAG"):
             fb.set_time_tag(True)
         t0 = time.perf_counter()
-        Xd = Xh.to(dev, non_blocking=True)
-        ds2 = fb.Dataset(Xd, yh, params={"max_bin": PARAMS["max_bin"]}).set_global_rows(off, args.rows)
+        # the pinned host matrix goes straight into the public API: the library copies it to the device on a side stream
+        # while the host finds the bin boundaries, then bins on the device
+        ds2 = fb.Dataset(Xh, yh, params={"max_bin": PARAMS["max_bin"], "device_type": "cuda"}).set_global_rows(off, args.rows)
         b2 = fb.train(dict(PARAMS, is_provide_training_metric=True), ds2, K, valid_sets=[ds2], valid_names=["train"], keep_training_booster=True,
                       callbacks=[fb.record_evaluation({})])
         barrier()

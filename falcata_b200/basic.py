@@ -147,6 +147,13 @@ def _get_bytes(fn: Callable, *args: Any) -> bytes:
     return buf.raw[: out_len.value]
 
 
+def _resolved_int(params: Dict[str, Any], name: str) -> int:
+    """An integer parameter as the native config resolves it (aliases, defaults, values derived from ``seed``)."""
+    out = ctypes.c_int(0)
+    _safe_call(_lib().FB_ResolveParamInt(_param_str(params), name.encode(), ctypes.byref(out)))
+    return out.value
+
+
 def cuda_available() -> bool:
     out = ctypes.c_int(0)
     _safe_call(_lib().FB_CudaAvailable(ctypes.byref(out)))
@@ -230,6 +237,8 @@ class Dataset:
             self._handle = handle
         elif _is_cuda_array(self.data):
             self._construct_from_device(self.data, params, ref_handle)
+        elif self._host_matrix_for_device(params, ref_handle):
+            self._construct_host_via_device(params)
         elif self._global_rows is not None and ref_handle is None:
             self._construct_sharded_host(_to_numpy_2d(self.data), params)
         else:
@@ -257,6 +266,65 @@ class Dataset:
             self.data = None
         return self
 
+    def _host_matrix_for_device(self, params: Dict[str, Any], ref_handle: Any) -> bool:
+        """A dense host matrix that will train on the device is binned there too (unless host bins are asked for)."""
+        if ref_handle is not None or str(params.get("device_type", "")).lower() not in ("cuda", "gpu") or params.get("keep_host_bins"):
+            return False
+        if not cuda_available():
+            return False
+        d = self.data
+        if _is_torch_tensor(d):
+            return (not d.is_cuda) and d.dim() == 2 and d.is_contiguous()
+        return isinstance(d, np.ndarray) and d.ndim == 2 and d.flags.c_contiguous and d.dtype in _DTYPE_CODE and d.dtype != np.dtype("uint16")
+
+    def _construct_host_via_device(self, params: Dict[str, Any]) -> None:
+        """Host matrix -> device bins without binning on the host: the raw matrix goes to the device on a side stream
+        (in one piece when it fits a quarter of the free memory, else chunk by chunk through a reused buffer) while
+        the host draws the bin sample from its own copy and finds the bin boundaries; the device then bins the rows.
+        Parity: src/io/cuda/cuda_dense_binner.cu:L85-170 (chunked H2D -> kernel ring for host matrices)."""
+        import torch
+
+        from .parallel import bootstrap
+
+        lib = _lib()
+        t = self.data if _is_torch_tensor(self.data) else torch.from_numpy(self.data)
+        nrow, ncol = t.shape
+        dev = torch.device("cuda", torch.cuda.current_device())
+        free_bytes, _ = torch.cuda.mem_get_info(dev)
+        nbytes = t.numel() * t.element_size()
+        whole = nbytes <= free_bytes // 4
+        side = torch.cuda.Stream(device=dev)
+        Xd = None
+        if whole:
+            with torch.cuda.stream(side):
+                Xd = t.to(dev, non_blocking=True)   # overlaps with the host work below when the matrix is pinned
+        goff, gtot = self._global_rows if self._global_rows is not None else (0, 0)
+        sample, total = bootstrap.gather_bin_sample(t, _resolved_int(params, "bin_construct_sample_cnt"), _resolved_int(params, "data_random_seed"), goff, gtot,
+                                                    replicated=self._replicated)
+        sample = np.ascontiguousarray(sample)
+        if sample.dtype not in _DTYPE_CODE:
+            sample = sample.astype(np.float64)
+        handle = ctypes.c_void_p()
+        _safe_call(lib.FB_DatasetCreateFromSampleTyped(sample.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[sample.dtype], ctypes.c_int32(sample.shape[0]),
+                                                       ctypes.c_int32(ncol), ctypes.c_int64(total), _param_str(params), None, 0, ctypes.byref(handle)))
+        self._handle = handle
+        off, tot = self._global_rows if self._global_rows is not None else (0, nrow)
+        _safe_call(lib.FB_DatasetInitRows(handle, ctypes.c_int32(nrow), ctypes.c_int64(off), ctypes.c_int64(tot), 0))
+        code = {torch.float32: 0, torch.float64: 1, torch.int8: 2, torch.int16: 3, torch.uint8: 4, torch.float16: 6, torch.int32: 7}[t.dtype]
+        if whole:
+            side.synchronize()
+            _safe_call(lib.FB_DatasetBinDeviceChunk(handle, ctypes.c_void_p(Xd.data_ptr()), code, ctypes.c_int32(nrow), ctypes.c_int32(ncol), 0, ctypes.c_int32(nrow)))
+        else:
+            rows_per_chunk = max(1, int((free_bytes // 16) // max(1, ncol * t.element_size())))
+            for a in range(0, nrow, rows_per_chunk):
+                b = min(nrow, a + rows_per_chunk)
+                chunk = t[a:b].to(dev)
+                _safe_call(lib.FB_DatasetBinDeviceChunk(handle, ctypes.c_void_p(chunk.data_ptr()), code, ctypes.c_int32(b - a), ctypes.c_int32(ncol), ctypes.c_int32(a),
+                                                        ctypes.c_int32(nrow)))
+                del chunk
+        del Xd
+        torch.cuda.synchronize()
+
     def _construct_sharded_host(self, arr: np.ndarray, params: Dict[str, Any]) -> None:
         """Host ingest of one row shard: the bin sample is drawn by GLOBAL row id and gathered over all
         ranks, so every rank derives the same bin boundaries; the local rows are then binned on the host.
@@ -270,8 +338,8 @@ class Dataset:
             arr = np.ascontiguousarray(arr)
         nrow, ncol = arr.shape
         goff, gtot = self._global_rows
-        sample, total = bootstrap.gather_bin_sample(torch.from_numpy(arr), int(params.get("bin_construct_sample_cnt", 200000)),
-                                                    int(params.get("data_random_seed", 1)), goff, gtot)
+        sample, total = bootstrap.gather_bin_sample(torch.from_numpy(arr), _resolved_int(params, "bin_construct_sample_cnt"),
+                                                    _resolved_int(params, "data_random_seed"), goff, gtot, replicated=self._replicated)
         sample = np.ascontiguousarray(sample)
         if sample.dtype not in _DTYPE_CODE:
             sample = sample.astype(np.float64)
@@ -306,7 +374,7 @@ class Dataset:
             from .parallel import bootstrap
 
             goff, gtot = self._global_rows if self._global_rows is not None else (0, 0)
-            sample, total = bootstrap.gather_bin_sample(t, int(params.get("bin_construct_sample_cnt", 200000)), int(params.get("data_random_seed", 1)), goff, gtot,
+            sample, total = bootstrap.gather_bin_sample(t, _resolved_int(params, "bin_construct_sample_cnt"), _resolved_int(params, "data_random_seed"), goff, gtot,
                                                         replicated=self._replicated)
             sample = np.ascontiguousarray(sample)
             if sample.dtype not in _DTYPE_CODE:

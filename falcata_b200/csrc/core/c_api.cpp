@@ -12,6 +12,8 @@
 namespace fb {
 // device-side entry points implemented by the CUDA module
 void DeviceBinDataset(Dataset* ds, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, bool keep_host_copy);
+void DeviceBinDatasetChunk(Dataset* ds, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, bool keep_host_copy, int32_t start_row,
+                           int32_t total_rows);
 void DevicePredict(const GBDT* gbdt, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, int predict_type,
                    int start_iter, int num_iter, float* out_device);
 }  // namespace fb
@@ -59,6 +61,16 @@ int FB_RegisterLogCallback(void (*callback)(const char*)) { API_BEGIN(); Log::ca
 int FB_CudaAvailable(int* out) { API_BEGIN(); *out = CudaAvailable() ? 1 : 0; API_END(); }
 int FB_SetNumThreads(int num_threads) { API_BEGIN(); if (num_threads > 0) omp_set_num_threads(num_threads); API_END(); }
 int FB_GetNumThreads(int* out) { API_BEGIN(); *out = omp_get_max_threads(); API_END(); }
+// Resolved value of an integer parameter (aliases, defaults and seed derivation applied) for the Python layer.
+int FB_ResolveParamInt(const char* parameters, const char* name, int* out) {
+  API_BEGIN();
+  Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());
+  const std::string n = name;
+  if (n == "data_random_seed") *out = cfg.data_random_seed;
+  else if (n == "bin_construct_sample_cnt") *out = cfg.bin_construct_sample_cnt;
+  else Log::Fatal("FB_ResolveParamInt does not know %s", name);
+  API_END();
+}
 int FB_SetTimeTag(int enabled) { API_BEGIN(); StageTimer::Get().enabled = enabled != 0; if (!enabled) StageTimer::Get().Clear(); API_END(); }
 int FB_GetTimeTagReport(int64_t buffer_len, int64_t* out_len, char* out_str) { API_BEGIN(); CopyOut(StageTimer::Get().Report(), buffer_len, out_len, out_str); API_END(); }
 
@@ -80,9 +92,15 @@ int FB_DatasetCreateFromMat(const void* data, int dtype, int32_t nrow, int32_t n
   if (reference != nullptr) {
     ds->CopySchemaFrom(*static_cast<const Dataset*>(reference));
   } else {
-    Random rnd(cfg.data_random_seed);
-    const int ns = std::min<int>(nrow, cfg.bin_construct_sample_cnt);
-    std::vector<int> idx = rnd.Sample(nrow, ns);
+    // the bin sample: a row is in iff its Philox draw (data_random_seed, row id) is below sample_cnt / nrow - the
+    // draw the device ingest makes, so a matrix gets the same bin boundaries whichever way it comes in
+    const double frac = std::min(1.0, static_cast<double>(cfg.bin_construct_sample_cnt) / std::max(1, nrow));
+    std::vector<int> idx;
+    for (int i = 0; i < nrow; ++i) {
+      const float u = U01From24(Philox4x32_10(static_cast<uint32_t>(i), 0x5A3Du, 0xBA660000u, 0u, static_cast<uint32_t>(cfg.data_random_seed), 0x9876u).v[0]);
+      if (static_cast<double>(u) < frac) idx.push_back(i);
+    }
+    if (idx.empty() && nrow > 0) idx.push_back(0);
     std::vector<double> sample(static_cast<size_t>(idx.size()) * ncol);
     Dataset tmp;   // reuse the dtype reader through a one-row push? simpler: read directly
     for (size_t r = 0; r < idx.size(); ++r) for (int j = 0; j < ncol; ++j) {
@@ -183,6 +201,12 @@ int FB_DatasetBinDeviceMat(DatasetHandle handle, const void* device_data, int dt
   API_BEGIN();
   ScopedTimer api_timer("FB_DatasetBinDeviceMat");
   DeviceBinDataset(static_cast<Dataset*>(handle), device_data, dtype, nrow, ncol, is_row_major != 0, keep_host_copy != 0);
+  API_END();
+}
+
+int FB_DatasetBinDeviceChunk(DatasetHandle handle, const void* device_data, int dtype, int32_t nrow, int32_t ncol, int32_t start_row, int32_t total_rows) {
+  API_BEGIN();
+  DeviceBinDatasetChunk(static_cast<Dataset*>(handle), device_data, dtype, nrow, ncol, true, false, start_row, total_rows);
   API_END();
 }
 

@@ -132,15 +132,33 @@ void EnsureDeviceDataset(Dataset* ds) {
   ds->device = dd.release();
 }
 
+void DeviceBinDatasetChunk(Dataset* ds, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, bool keep_host_copy, int32_t start_row,
+                           int32_t total_rows);
+
 void DeviceBinDataset(Dataset* ds, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, bool keep_host_copy) {
+  DeviceBinDatasetChunk(ds, device_data, dtype, nrow, ncol, row_major, keep_host_copy, 0, nrow);
+}
+
+// Bins rows [start_row, start_row + nrow) of a data set of total_rows rows from a device-resident chunk of the raw
+// matrix. The first chunk (start_row 0) allocates the binned rows for the whole data set; a host matrix larger than
+// the device can spare is ingested as a sequence of such chunks (copy a chunk, bin it, reuse the buffer).
+void DeviceBinDatasetChunk(Dataset* ds, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, bool keep_host_copy, int32_t start_row,
+                           int32_t total_rows) {
   if (!CudaAvailable()) Log::Fatal("No CUDA device is available for device binning");
   if (ncol != ds->num_total_features) Log::Fatal("The number of columns (%d) differs from the dataset's (%d)", ncol, ds->num_total_features);
   if (ds->max_group_bin > 256) Log::Fatal("The CUDA learner stores one byte per feature group (max_bin <= 255)");
-  std::unique_ptr<DeviceDataset> dd(new DeviceDataset());
-  FB_CUDA(cudaGetDevice(&dd->device));
-  dd->num_data = nrow; dd->num_groups = ds->num_groups; dd->row_stride = RowStrideFor(ds->num_groups); dd->gh_offset = dd->row_stride - 4;
-  ds->num_data = nrow; ds->metadata.num_data = nrow;
-  if (ds->global_num_data == 0) ds->global_num_data = nrow;
+  if (start_row < 0 || start_row + nrow > total_rows) Log::Fatal("Chunk [%d, %d) is outside the data set of %d rows", start_row, start_row + nrow, total_rows);
+  if (start_row > 0 && (ds->device == nullptr || ds->device->num_data != total_rows)) Log::Fatal("Chunks must start with the chunk at row 0");
+  if (keep_host_copy && nrow != total_rows) Log::Fatal("A host copy of the bins needs the whole matrix in one chunk");
+  std::unique_ptr<DeviceDataset> fresh;
+  if (start_row == 0) {
+    fresh.reset(new DeviceDataset());
+    FB_CUDA(cudaGetDevice(&fresh->device));
+    fresh->num_data = total_rows; fresh->num_groups = ds->num_groups; fresh->row_stride = RowStrideFor(ds->num_groups); fresh->gh_offset = fresh->row_stride - 4;
+    ds->num_data = total_rows; ds->metadata.num_data = total_rows;
+    if (ds->global_num_data == 0) ds->global_num_data = total_rows;
+  }
+  DeviceDataset* dd = start_row == 0 ? fresh.get() : ds->device;
   std::vector<BinFeat> feats; std::vector<int> gbegin(ds->num_groups + 1, 0); std::vector<double> bounds; std::vector<int> cat_vals, cat_bins;
   for (int g = 0; g < ds->num_groups; ++g) {
     gbegin[g] = static_cast<int>(feats.size());
@@ -163,12 +181,12 @@ void DeviceBinDataset(Dataset* ds, const void* device_data, int dtype, int32_t n
   gbegin[ds->num_groups] = static_cast<int>(feats.size());
   DevBuf<BinFeat> d_feats; DevBuf<int> d_gbegin, d_cv, d_cb; DevBuf<double> d_bounds;
   d_feats.Upload(feats, 0); d_gbegin.Upload(gbegin, 0); d_bounds.Upload(bounds, 0); d_cv.Upload(cat_vals, 0); d_cb.Upload(cat_bins, 0);
-  dd->rows.Alloc(static_cast<size_t>(nrow) * dd->row_stride);
-  dd->rows.Zero(0);
+  if (start_row == 0) { dd->rows.Alloc(static_cast<size_t>(total_rows) * dd->row_stride); dd->rows.Zero(0); }
+  uint8_t* out_rows = dd->rows.get() + static_cast<size_t>(start_row) * dd->row_stride;
   const size_t total = static_cast<size_t>(nrow) * ds->num_groups;
   const int threads = 256; const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
   if (total > 0) {
-#define FB_BIN_LAUNCH(T) BinRowsKernel<T><<<blocks, threads>>>(static_cast<const T*>(device_data), nrow, ncol, row_major, d_feats.get(), d_gbegin.get(), ds->num_groups, d_bounds.get(), d_cv.get(), d_cb.get(), dd->rows.get(), dd->row_stride)
+#define FB_BIN_LAUNCH(T) BinRowsKernel<T><<<blocks, threads>>>(static_cast<const T*>(device_data), nrow, ncol, row_major, d_feats.get(), d_gbegin.get(), ds->num_groups, d_bounds.get(), d_cv.get(), d_cb.get(), out_rows, dd->row_stride)
     switch (dtype) {
       case kF32: FB_BIN_LAUNCH(float); break;
       case kF64: FB_BIN_LAUNCH(double); break;
@@ -183,7 +201,7 @@ void DeviceBinDataset(Dataset* ds, const void* device_data, int dtype, int32_t n
 #undef FB_BIN_LAUNCH
     FB_LAUNCHED(); FB_KERNEL_CHECK();
   }
-  UploadMeta(ds, dd.get(), 0);
+  if (start_row == 0) UploadMeta(ds, dd, 0);
   FB_CUDA(cudaStreamSynchronize(0));
   if (keep_host_copy) {
     std::vector<uint8_t> staged(static_cast<size_t>(nrow) * dd->row_stride);
@@ -192,8 +210,10 @@ void DeviceBinDataset(Dataset* ds, const void* device_data, int dtype, int32_t n
     ds->bins8.assign(static_cast<size_t>(nrow) * ds->num_groups, 0);
     for (int32_t i = 0; i < nrow; ++i) memcpy(&ds->bins8[static_cast<size_t>(i) * ds->num_groups], &staged[static_cast<size_t>(i) * dd->row_stride], ds->num_groups);
   }
-  if (ds->device != nullptr) FreeDeviceDataset(ds->device);
-  ds->device = dd.release();
+  if (start_row == 0) {
+    if (ds->device != nullptr) FreeDeviceDataset(ds->device);
+    ds->device = fresh.release();
+  }
 }
 
 }  // namespace fb

@@ -17,6 +17,7 @@ typedef void* BoosterHandle;
 const char* FB_GetLastError();
 int FB_RegisterLogCallback(void (*callback)(const char*));
 int FB_CudaAvailable(int* out);
+int FB_ResolveParamInt(const char* parameters, const char* name, int* out);
 int FB_SetTimeTag(int enabled);
 // Host worker threads of the OpenMP loops (bin finding, label scans, host learners). <= 0: leave as is.
 int FB_SetNumThreads(int num_threads);
@@ -44,6 +45,8 @@ int FB_DatasetInitRows(DatasetHandle handle, int32_t nrow, int64_t global_row_of
 int FB_DatasetPushRows(DatasetHandle handle, const void* data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, int32_t start_row);
 /* Bin a dense device matrix on the GPU; the binned rows stay on the device. */
 int FB_DatasetBinDeviceMat(DatasetHandle handle, const void* device_data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, int keep_host_copy);
+// Rows [start_row, start_row + nrow) of a total_rows data set from a device-resident row-major chunk (first chunk: start_row 0).
+int FB_DatasetBinDeviceChunk(DatasetHandle handle, const void* device_data, int dtype, int32_t nrow, int32_t ncol, int32_t start_row, int32_t total_rows);
 int FB_DatasetSetField(DatasetHandle handle, const char* field_name, const void* data, int64_t num_element, int dtype);
 int FB_DatasetGetField(DatasetHandle handle, const char* field_name, int64_t* out_len, const void** out_ptr, int* out_type);
 int FB_DatasetGetNumData(DatasetHandle handle, int32_t* out);

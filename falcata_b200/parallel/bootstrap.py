@@ -71,7 +71,7 @@ def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total
     if total <= 0:
         total = n
         if d and ws > 1:
-            cnt = torch.tensor([n], dtype=torch.int64, device=t.device if t.is_cuda and d.get_backend() == "nccl" else "cpu")
+            cnt = torch.tensor([n], dtype=torch.int64, device=(t.device if t.is_cuda else torch.device("cuda", torch.cuda.current_device())) if d.get_backend() == "nccl" else "cpu")
             d.all_reduce(cnt)
             total = int(cnt.item())
             offs = [None] * ws
@@ -84,8 +84,8 @@ def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total
     picked = t[idx].to(sdt)
     if d and ws > 1:
         # tensor collectives (no pickling): sizes first, then the rows padded to the largest shard
-        on_dev = picked.is_cuda and d.get_backend() == "nccl"
-        cdev = picked.device if on_dev else torch.device("cpu")
+        on_dev = d.get_backend() == "nccl"   # NCCL moves device tensors only: a host sample rides through the current device
+        cdev = (picked.device if picked.is_cuda else torch.device("cuda", torch.cuda.current_device())) if on_dev else torch.device("cpu")
         sizes = torch.zeros(ws, dtype=torch.int64, device=cdev)
         sizes[rank] = picked.shape[0]
         d.all_reduce(sizes)

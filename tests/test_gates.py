@@ -1,0 +1,49 @@
+"""The measurement gates on fake inputs (no GPU needed): quiet-GPU guard and the rolling-median perf gate."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "gates"))
+import gpu_guard  # noqa: E402
+import perf_gate  # noqa: E402
+
+
+def _fake_time():
+    t = {"now": 0.0}
+    return (lambda: t["now"]), (lambda dt: t.__setitem__("now", t["now"] + dt))
+
+
+def test_gpu_guard_waits_for_a_sustained_quiet_window():
+    clock, sleep = _fake_time()
+    samples = iter([(4.0, 90.0)] * 5 + [(60.0, 5.0)] * 3 + [(60.0, 70.0)] + [(60.0, 3.0)] * 40)
+    assert gpu_guard.wait_quiet(8, 20, 15, 600, sampler=lambda: next(samples), sleep=sleep, clock=clock) == 0
+    assert clock() >= 9 + 15           # the short quiet spell before the burst did not count
+    clock, sleep = _fake_time()
+    assert gpu_guard.wait_quiet(8, 20, 15, 30, sampler=lambda: (2.0, 99.0), sleep=sleep, clock=clock) == 3
+    assert gpu_guard.wait_quiet(8, 20, 15, 30, sampler=lambda: None) == 4
+    assert gpu_guard.query(run=lambda cmd: "81234, 7\n") == (81234 / 1024.0, 7.0)
+    assert gpu_guard.foreign_processes([11], run=lambda cmd: "11\n4242\n") == [4242]
+
+
+def test_perf_gate_uses_the_rolling_median_and_needs_two_bad_runs(tmp_path):
+    hist = tmp_path / "h.jsonl"
+    line = lambda v, **kw: {"value": v, "higher_is_better": False, "clocks": {"reasons": []}, **kw}
+    assert perf_gate.gate("k", line(3.0), hist)["status"] == "first"
+    for v in (3.05, 2.95, 3.0):
+        assert perf_gate.gate("k", line(v), hist)["status"] == "ok"
+    assert perf_gate.gate("k", line(3.5), hist)["status"] == "warn"            # +17 %
+    # +40 %: flagged, re-measured best of three, still slow -> flag; the next slow run fails
+    reruns = iter([line(4.3), line(4.25)])
+    assert perf_gate.gate("k", line(4.2), hist, rerun=lambda: next(reruns))["status"] == "flag"
+    assert perf_gate.gate("k", line(4.2), hist)["status"] == "fail"
+    # a noisy first try that re-measures fine is accepted
+    reruns = iter([line(3.02), line(3.4)])
+    assert perf_gate.gate("k2", line(3.0), hist)["status"] == "first"
+    assert perf_gate.gate("k2", line(4.5), hist, rerun=lambda: next(reruns))["status"] == "ok"
+    # contention is not judged and not recorded
+    n = len(hist.read_text().splitlines())
+    assert perf_gate.gate("k", line(9.9), hist, foreign=[4242])["status"] == "contended"
+    assert perf_gate.gate("k", line(9.9, clocks={"reasons": ["hw_thermal_slowdown"]}), hist)["status"] == "contended"
+    assert len(hist.read_text().splitlines()) == n
+    rows = [json.loads(l) for l in hist.read_text().splitlines()]
+    assert [r["accepted"] for r in rows if r["key"] == "k"][-2:] == [False, False]

@@ -277,3 +277,19 @@ def test_objective_without_device_kernel_trains_through_host_gradients():
     cpu = fb.train({**p, "device_type": "cpu"}, fb.Dataset(X, y), 30)
     mape = lambda b: float(np.mean(np.abs(b.predict(X) - y) / np.maximum(1.0, np.abs(y))))
     assert abs(mape(dev) - mape(cpu)) < 0.05 * mape(cpu) + 1e-3
+
+
+def test_host_matrix_is_binned_on_the_device_with_the_host_bins():
+    # a numpy matrix that trains on the device goes through chunk copies and the binning kernel; the bin sample is
+    # the same Philox draw as on the host path, so both ingests give the same bins and the same model
+    X, y = make_binary(260000, 10)       # more rows than the bin sample (200k): the draw matters
+    p = {"objective": "binary", "num_leaves": 15, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "device_type": "cuda"}
+    dev_ingest = fb.Dataset(X, y)
+    a = fb.train(p, dev_ingest, 5)
+    assert dev_ingest.info()["has_host"] == 0 and dev_ingest.info()["has_device"] == 1
+    host_ingest = fb.Dataset(X, y, params={"keep_host_bins": True})
+    b = fb.train(p, host_ingest, 5)
+    assert host_ingest.info()["has_host"] == 1
+    assert model_body(a.model_to_string()) == model_body(b.model_to_string())
+    t = fb.train(p, fb.Dataset(torch.from_numpy(X).pin_memory(), y), 5)
+    assert model_body(t.model_to_string()) == model_body(a.model_to_string())
