@@ -20,6 +20,8 @@ void DevicePredict(const GBDT* gbdt, const void* device_data, int dtype, int32_t
 
 using namespace fb;
 
+extern "C" int FB_OpBernoulliRowsHost(int n, long long global_offset, unsigned int seed, double fraction, int* out_idx, int* out_count);
+
 namespace {
 
 thread_local std::string g_last_error;
@@ -95,11 +97,10 @@ int FB_DatasetCreateFromMat(const void* data, int dtype, int32_t nrow, int32_t n
     // the bin sample: a row is in iff its Philox draw (data_random_seed, row id) is below sample_cnt / nrow - the
     // draw the device ingest makes, so a matrix gets the same bin boundaries whichever way it comes in
     const double frac = std::min(1.0, static_cast<double>(cfg.bin_construct_sample_cnt) / std::max(1, nrow));
-    std::vector<int> idx;
-    for (int i = 0; i < nrow; ++i) {
-      const float u = U01From24(Philox4x32_10(static_cast<uint32_t>(i), 0x5A3Du, 0xBA660000u, 0u, static_cast<uint32_t>(cfg.data_random_seed), 0x9876u).v[0]);
-      if (static_cast<double>(u) < frac) idx.push_back(i);
-    }
+    std::vector<int> idx(static_cast<size_t>(std::max(1, nrow)));
+    int picked = 0;
+    if (FB_OpBernoulliRowsHost(nrow, 0, static_cast<unsigned int>(cfg.data_random_seed), frac, idx.data(), &picked) != 0) Log::Fatal("Row sampling failed");
+    idx.resize(picked);
     if (idx.empty() && nrow > 0) idx.push_back(0);
     std::vector<double> sample(static_cast<size_t>(idx.size()) * ncol);
     Dataset tmp;   // reuse the dtype reader through a one-row push? simpler: read directly

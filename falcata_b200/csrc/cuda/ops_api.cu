@@ -2,6 +2,8 @@
 // device buffers, so that the numerics tests can compare it with a plain PyTorch reference.
 #include "kernels.cuh"
 
+#include <vector>
+
 using namespace fb;
 
 namespace {
@@ -149,12 +151,28 @@ int FB_OpBernoulliRowsDevice(int n, long long global_offset, unsigned int seed, 
 }
 int FB_OpBernoulliRowsHost(int n, long long global_offset, unsigned int seed, double fraction, int* out_idx, int* out_count) {
   OPS_BEGIN();
-  int c = 0;
-  for (int i = 0; i < n; ++i) {
-    const float u = U01From24(Philox4x32_10(static_cast<uint32_t>(static_cast<unsigned long long>(global_offset) + static_cast<unsigned long long>(i)), 0x5A3Du, 0xBA660000u, 0u, seed, 0x9876u).v[0]);
-    if (static_cast<double>(u) < fraction) out_idx[c++] = i;
+  // row blocks on the host cores: flags per block, block offsets in order, then the ascending fill
+  const int kBlock = 1 << 16;
+  const int nblocks = (n + kBlock - 1) / kBlock;
+  std::vector<int> count(nblocks + 1, 0);
+  std::vector<uint8_t> flag(static_cast<size_t>(std::max(1, n)));
+#pragma omp parallel for schedule(static)
+  for (int b = 0; b < nblocks; ++b) {
+    int c = 0;
+    for (int i = b * kBlock; i < std::min(n, (b + 1) * kBlock); ++i) {
+      const float u = U01From24(Philox4x32_10(static_cast<uint32_t>(static_cast<unsigned long long>(global_offset) + static_cast<unsigned long long>(i)), 0x5A3Du, 0xBA660000u, 0u, seed, 0x9876u).v[0]);
+      const bool in = static_cast<double>(u) < fraction;
+      flag[i] = in ? 1 : 0; c += in ? 1 : 0;
+    }
+    count[b + 1] = c;
   }
-  *out_count = c;
+  for (int b = 0; b < nblocks; ++b) count[b + 1] += count[b];
+#pragma omp parallel for schedule(static)
+  for (int b = 0; b < nblocks; ++b) {
+    int w = count[b];
+    for (int i = b * kBlock; i < std::min(n, (b + 1) * kBlock); ++i) if (flag[i]) out_idx[w++] = i;
+  }
+  *out_count = count[nblocks];
   OPS_END();
 }
 

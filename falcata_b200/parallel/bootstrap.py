@@ -36,9 +36,12 @@ def _bernoulli_rows(t: Any, n: int, offset: int, seed: int, p: float) -> Any:
 
     lib = _lib()
     cnt = ctypes.c_int(0)
-    if t.is_cuda:
-        out = torch.empty(max(1, n), dtype=torch.int32, device=t.device)
-        with torch.cuda.device(t.device):
+    # the draw needs the row ids only, not the data: with a GPU at hand it runs there even for a host matrix
+    on_gpu = t.is_cuda or (torch.cuda.is_available() and n >= (1 << 20))
+    if on_gpu:
+        gdev = t.device if t.is_cuda else torch.device("cuda", torch.cuda.current_device())
+        out = torch.empty(max(1, n), dtype=torch.int32, device=gdev)
+        with torch.cuda.device(gdev):
             torch.cuda.current_stream().synchronize()
             rc = lib.FB_OpBernoulliRowsDevice(ctypes.c_int(n), ctypes.c_longlong(offset), ctypes.c_uint(seed & 0xFFFFFFFF), ctypes.c_double(p),
                                               ctypes.c_void_p(out.data_ptr()), ctypes.byref(cnt))
@@ -49,7 +52,7 @@ def _bernoulli_rows(t: Any, n: int, offset: int, seed: int, p: float) -> Any:
     if rc != 0:
         lib.FB_OpsLastError.restype = ctypes.c_char_p
         raise RuntimeError(lib.FB_OpsLastError().decode())
-    return out[: cnt.value].long()
+    return out[: cnt.value].to(t.device).long()
 
 
 def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total: int = 0, replicated: bool = False) -> Tuple[np.ndarray, int]:
