@@ -293,3 +293,25 @@ def test_host_matrix_is_binned_on_the_device_with_the_host_bins():
     assert model_body(a.model_to_string()) == model_body(b.model_to_string())
     t = fb.train(p, fb.Dataset(torch.from_numpy(X).pin_memory(), y), 5)
     assert model_body(t.model_to_string()) == model_body(a.model_to_string())
+
+
+def test_bundled_sparse_features_match_host():
+    # mutually exclusive sparse columns are bundled into shared byte columns (EFB); the device binner, construct,
+    # search (most-frequent-bin reconstruction) and partition must treat the bundles exactly like the host learner
+    rng = np.random.RandomState(5)
+    n = 20000
+    dense = rng.randn(n, 4).astype(np.float32)
+    which = rng.randint(0, 12, size=n)
+    sparse = np.zeros((n, 12), dtype=np.float32)
+    sparse[np.arange(n), which] = rng.randint(1, 6, size=n)          # one non-zero per row: 12 exclusive features
+    X = np.column_stack([dense, sparse])
+    y = np.round((dense[:, 0] + 0.7 * (which % 3) + 0.2 * sparse.sum(1) + 0.1 * rng.randn(n)) * 8) / 8
+    base = {"objective": "none", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "grow_policy": "level", "min_data_in_leaf": 20, "seed": 3}
+    dc = fb.Dataset(X, y, free_raw_data=False); dg = fb.Dataset(X, y, free_raw_data=False)
+    bc = fb.train({**base, "device_type": "cpu"}, dc, 2, fobj=_l2_exact)
+    bg = fb.train({**base, "device_type": "cuda"}, dg, 2, fobj=_l2_exact)
+    assert dg.info()["num_groups"] < 16 and dg.info()["num_groups"] == dc.info()["num_groups"]     # bundling happened, the same on both paths
+    sc, sg = bc.model_to_string(), bg.model_to_string()
+    assert model_body(sc).split("Tree=1")[0] == model_body(sg).split("Tree=1")[0]
+    used = {int(t) for line in sg.splitlines() if line.startswith("split_feature=") for t in line.split("=")[1].split()}
+    assert any(f >= 4 for f in used)      # bundled features are split on
