@@ -172,7 +172,7 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     pool_base_ = pool_.get();
   }
   cand_.Alloc(static_cast<size_t>(NL) * std::max<size_t>(1, owned_features_.size())); cand_.Zero(stream_);
-  hist_tasks_.Alloc(NL);
+  hist_tasks_.Alloc(NL); hist_status_.Alloc(1); hist_status_.Zero(stream_); h_hist_status_.Alloc(1); *h_hist_status_.get() = 0;
   const size_t max_chunks = static_cast<size_t>(n_) / kPartChunk + NL + 1;
   bits_.Alloc(max_chunks * (kPartChunk / 32)); chunk_left_.Alloc(max_chunks); split_left_total_.Alloc(NL);
   const size_t blob = static_cast<size_t>(NL) * (sizeof(PartSplit) + sizeof(ChildInit) + 2 * sizeof(FindChild)) + 256;

@@ -112,7 +112,7 @@ class CudaEngine : public DeviceEngine {
   DevBuf<unsigned char> bin_owner_; DevBuf<int> bin_local_;
   std::vector<int> owned_features_;
   DevBuf<char> level_blob_; PinnedBuf<char> h_level_blob_;
-  DevBuf<HistTask> hist_tasks_;
+  DevBuf<HistTask> hist_tasks_; DevBuf<unsigned int> hist_status_; PinnedBuf<unsigned int> h_hist_status_;
   DevBuf<unsigned int> bits_; DevBuf<int> chunk_left_, split_left_total_;
   DevBuf<int> features_, sub_features_;
   DevBuf<double> leaf_value_, renew_partial_; PinnedBuf<double> h_renew_partial_;

@@ -190,6 +190,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     ha.dest.stage_local = stage_local_.get(); ha.dest.task_done = task_done_.get(); ha.dest.stage_cap = NL;
   } else { ha.dest.pool[0] = pool_base_; ha.dest.slot_stride[0] = voting_ ? train_->num_total_bin : slot_stride_; }
   ha.num_total_bin = train_->num_total_bin; ha.lane_mode = lane_mode_; ha.lane_bins = lane_bins_;
+  ha.bulk_root = plan_.bulk_root ? 1 : 0; ha.status = hist_status_.get();
   // K9: when this tree samples few columns, construct from a dense per-tree copy of just those groups
   // (feature-parallel: just the sampled groups this rank owns)
   int first_group = 0;
@@ -351,11 +352,12 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
       }
       clock_.Begin(st_sync_, stream_);
       FB_CUDA(cudaMemcpyAsync(h_ctrl_.get(), ctrl_.get(), sizeof(LevelCtrl), cudaMemcpyDeviceToHost, stream_));
-      if (first) { journal_.Download(h_journal_.get(), NL, stream_); leaves_.Download(h_leaves_.get(), NL, stream_); }
+      if (first) { journal_.Download(h_journal_.get(), NL, stream_); leaves_.Download(h_leaves_.get(), NL, stream_); hist_status_.Download(h_hist_status_.get(), 1, stream_); }
       clock_.End(stream_);
       if (world_ > 1) { const int st = fabric_->CheckStatus(stream_); if (st != 0) Log::Fatal("A cross-rank wait gave up (device status %d): a peer rank did not reach the same step", st); }
       else FB_CUDA(cudaStreamSynchronize(stream_));
       hc = *h_ctrl_.get();
+      if (first && *h_hist_status_.get() != 0) Log::Fatal("A bounded wait inside the construct kernel gave up (device status %u)", *h_hist_status_.get());
       const bool complete = hc.done || hc.num_leaves >= NL || hc.frontier_count == 0;
       if (first && complete) records_ready = true;   // the journal and leaf records fetched with this batch are final
       if (first && complete && fast_score_ok_ && hc.num_leaves > 1) score_done_ = true;   // the device-side update applied itself

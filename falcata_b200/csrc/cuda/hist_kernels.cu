@@ -158,6 +158,53 @@ __global__ void __launch_bounds__(kHistThreads) HistQuantKernel(HistArgs a) {
 //      different banks and the update is a plain load-add-store (nobody else touches a lane's column).
 //  (3) the load-add-store chain is taken four rows at a time: four tile loads issue together and equal
 //      addresses are forwarded in registers.
+// ---- bulk asynchronous copies (TMA engine, non-tensor form) with mbarrier completion ----
+__device__ inline uint32_t SmemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ inline void MbarInit(uint64_t* bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SmemAddr(bar)), "r"(count) : "memory"); }
+__device__ inline void MbarExpectTx(uint64_t* bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)), "r"(bytes) : "memory"); }
+__device__ inline bool MbarTryWait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(SmemAddr(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// global -> this block's shared memory, `bytes` a multiple of 16, both addresses 16-byte aligned; completion is counted on `bar`
+__device__ inline void BulkCopyG2S(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(SmemAddr(dst)), "l"(src), "r"(bytes), "r"(SmemAddr(bar)) : "memory");
+}
+// Bounded wait: false when the budget ran out (the caller records the status and winds down).
+__device__ inline bool MbarWaitBounded(uint64_t* bar, uint32_t parity) {
+  for (int i = 0; i < (1 << 16); ++i) if (MbarTryWait(bar, parity)) return true;
+  return false;
+}
+
+// One staged block of up to 32 rows (32 bytes apart in shared memory) added into a warp's private tile
+// [bin][32 lanes]: lane l owns the column of feature group l. Four rows per step: the four tile loads issue
+// together, and cells that repeat inside the four are forwarded in registers so that every store holds its full sum.
+// P4: two groups per byte (low nibble = even group).
+template <bool P4>
+__device__ __forceinline__ void ConsumeStage(int* __restrict__ tile, const unsigned char* __restrict__ stage_rows, const int* __restrict__ sg, int cnt, int lane, bool active) {
+  const unsigned char* sr = stage_rows + (P4 ? (lane >> 1) : lane);
+  const int nshift = (lane & 1) * 4;
+  auto bin_of = [&](int j) -> int { const int b = sr[j * 32]; return P4 ? ((b >> nshift) & 15) : b; };
+  if (cnt == 32) {
+#pragma unroll 2
+    for (int j = 0; j < 32; j += 4) {
+      const int a0 = bin_of(j) * 32 + lane, a1 = bin_of(j + 1) * 32 + lane, a2 = bin_of(j + 2) * 32 + lane, a3 = bin_of(j + 3) * 32 + lane;
+      const int4 g4 = *reinterpret_cast<const int4*>(sg + j);     // same address in every lane: one broadcast load
+      if (active) {
+        int v0 = tile[a0], v1 = tile[a1], v2 = tile[a2], v3 = tile[a3];
+        v0 += g4.x;
+        v1 = (a1 == a0) ? v0 : v1; v1 += g4.y;
+        v2 = (a2 == a1) ? v1 : ((a2 == a0) ? v0 : v2); v2 += g4.z;
+        v3 = (a3 == a2) ? v2 : ((a3 == a1) ? v1 : ((a3 == a0) ? v0 : v3)); v3 += g4.w;
+        tile[a0] = v0; tile[a1] = v1; tile[a2] = v2; tile[a3] = v3;   // program order: the last store to an address holds its full sum
+      }
+    }
+  } else {
+    for (int j = 0; j < cnt; ++j) { const int b = bin_of(j); const int g = sg[j]; if (active) tile[b * 32 + lane] += g; }
+  }
+}
+
 constexpr int kLaneWarps = 12;
 constexpr int kLaneThreads = kLaneWarps * 32;
 constexpr int kLaneStages = 8;
@@ -169,6 +216,7 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
   int* tiles = reinterpret_cast<int*>(smem_raw);                                                 // [warps][NB][32]
   unsigned char* rows_w = smem_raw + sizeof(int) * kLaneWarps * kTile + static_cast<size_t>(warp) * kLaneStages * 32 * 32;   // [stages][32 rows][32 B]
   int* gh_w = reinterpret_cast<int*>(smem_raw + sizeof(int) * kLaneWarps * kTile + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * 32) + warp * kLaneStages * 32;
+  uint64_t* bars_w = reinterpret_cast<uint64_t*>(smem_raw + sizeof(int) * kLaneWarps * kTile + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * (32 + 4)) + warp * kLaneStages;   // one "stage full" barrier per (warp, stage)
   const int num_tasks = a.ctrl != nullptr ? a.ctrl->num_splits : a.num_tasks;
   if (num_tasks <= 0 || static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->total_blocks : a.total_blocks)) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
   const int ti = FindTask(a.tasks, num_tasks, blockIdx.x);
@@ -218,39 +266,66 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
     }
     __pipeline_commit();
   };
+  const bool active = lane < ng;
+  auto consume = [&](int slot, int cnt) {   // add the stage's rows into this warp's tile
+    if (a.pack4) ConsumeStage<true>(tile, rows_w + slot * 32 * 32, gh_w + slot * 32, cnt, lane, active);
+    else ConsumeStage<false>(tile, rows_w + slot * 32 * 32, gh_w + slot * 32, cnt, lane, active);
+  };
+  // Root level of a 32-byte-row data set: a stage's rows are one contiguous kilobyte and its gradient words 128
+  // contiguous bytes, so ONE lane hands both to the TMA engine as bulk copies and everybody waits on the stage's
+  // mbarrier - no per-lane copy instructions, no address arithmetic in the other 31 lanes.
+  const bool bulk = a.bulk_root != 0 && block_copy && a.gh_stride == 4 && (ident0 & 31) == 0;
+  if (bulk) {
+    const int nfull = (wend - wbeg) / 32, tail = (wend - wbeg) - nfull * 32;
+    if (lane == 0) { for (int st = 0; st < kLaneStages; ++st) MbarInit(bars_w + st, 1); asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+    __syncwarp();
+    auto produce = [&](int s) {
+      if (s < nfull && lane == 0) {
+        const int slot = s % kLaneStages;
+        MbarExpectTx(bars_w + slot, 32 * 32 + 32 * 4);
+        BulkCopyG2S(rows_w + slot * 32 * 32, a.rows + static_cast<size_t>(ident0 + static_cast<long long>(s) * 32) * 32, 32 * 32, bars_w + slot);
+        BulkCopyG2S(gh_w + slot * 32, a.gh_base + static_cast<size_t>(ident0 + static_cast<long long>(s) * 32) * 4, 32 * 4, bars_w + slot);
+      }
+    };
+    for (int s = 0; s < kLaneStages - 1; ++s) produce(s);
+    bool ok = true;
+    int s = 0;
+    for (; s < nfull; ++s) {
+      produce(s + kLaneStages - 1);   // refills the slot consumed one iteration ago (all lanes passed that iteration's __syncwarp)
+      ok = __all_sync(0xffffffffu, MbarWaitBounded(bars_w + s % kLaneStages, (s / kLaneStages) & 1) ? 1 : 0) != 0;   // one decision per warp
+      if (!ok) break;
+      consume(s % kLaneStages, 32);
+      __syncwarp();
+    }
+    if (!ok) {
+      // the wait gave up: report it, then give every copy still in flight a (bounded) chance to land before leaving
+      if (lane == 0 && a.status != nullptr) atomicExch(a.status, static_cast<unsigned int>(kStatusWaitTimeout));
+      for (int t = s; t < min(nfull, s + kLaneStages); ++t) MbarWaitBounded(bars_w + t % kLaneStages, (t / kLaneStages) & 1);
+    } else if (tail > 0) {
+      // the last, partial stage comes in with plain loads (a bulk copy could run past the end of the arrays)
+      if (lane < tail) {
+        const size_t row = static_cast<size_t>(ident0) + static_cast<size_t>(nfull) * 32 + lane;
+        const uint4* src = reinterpret_cast<const uint4*>(a.rows + row * 32);
+        uint4* dst = reinterpret_cast<uint4*>(rows_w + lane * 32);
+        dst[0] = src[0]; dst[1] = src[1];
+        gh_w[lane] = *reinterpret_cast<const int*>(a.gh_base + row * 4);
+      }
+      __syncwarp();
+      consume(0, tail);
+      __syncwarp();
+    }
+  } else {
   for (int s = 0; s < kLaneStages - 1; ++s) issue(s, load_row(s));
   // row ids are fetched three stages before they are needed, so their latency is off the critical path
   int q0 = load_row(kLaneStages - 1), q1 = load_row(kLaneStages), q2 = load_row(kLaneStages + 1);
-  const bool active = lane < ng;
   for (int s = 0; s < nstage; ++s) {
     issue(s + kLaneStages - 1, q0);
     q0 = q1; q1 = q2; q2 = load_row(s + kLaneStages + 2);
     __pipeline_wait_prior(kLaneStages - 1);
     __syncwarp();
-    const int slot = s % kLaneStages;
-    const int cnt = min(32, wend - wbeg - s * 32);
-    const unsigned char* sr = rows_w + slot * 32 * 32 + (a.pack4 ? (lane >> 1) : lane);
-    const int* sg = gh_w + slot * 32;
-    const int nshift = a.pack4 ? (lane & 1) * 4 : 0, nmask = a.pack4 ? 15 : 255;   // nibble of this lane's group inside its byte
-    if (cnt == 32) {
-#pragma unroll 2
-      for (int j = 0; j < 32; j += 4) {
-        const int a0 = ((sr[j * 32] >> nshift) & nmask) * 32 + lane, a1 = ((sr[(j + 1) * 32] >> nshift) & nmask) * 32 + lane,
-                  a2 = ((sr[(j + 2) * 32] >> nshift) & nmask) * 32 + lane, a3 = ((sr[(j + 3) * 32] >> nshift) & nmask) * 32 + lane;
-        const int4 g4 = *reinterpret_cast<const int4*>(sg + j);     // same address in every lane: one broadcast load
-        if (active) {
-          int v0 = tile[a0], v1 = tile[a1], v2 = tile[a2], v3 = tile[a3];
-          v0 += g4.x;
-          v1 = (a1 == a0) ? v0 : v1; v1 += g4.y;
-          v2 = (a2 == a1) ? v1 : ((a2 == a0) ? v0 : v2); v2 += g4.z;
-          v3 = (a3 == a2) ? v2 : ((a3 == a1) ? v1 : ((a3 == a0) ? v0 : v3)); v3 += g4.w;
-          tile[a0] = v0; tile[a1] = v1; tile[a2] = v2; tile[a3] = v3;   // program order: the last store to an address holds its full sum
-        }
-      }
-    } else {
-      for (int j = 0; j < cnt; ++j) { const int b = (sr[j * 32] >> nshift) & nmask; const int g = sg[j]; if (active) tile[b * 32 + lane] += g; }
-    }
+    consume(s % kLaneStages, min(32, wend - wbeg - s * 32));
     __syncwarp();   // every lane is done with this stage's buffer before it is refilled
+  }
   }
   __syncthreads();
   for (int cell = threadIdx.x; cell < kTile; cell += kLaneThreads) {
@@ -376,7 +451,7 @@ void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
     const int cap = kLaneWarps * a.sub_rows;
     if (a.rows_per_block > cap) Log::Fatal("lane histogram: %d rows per block would overflow the 16-bit lanes (cap %d)", a.rows_per_block, cap);
     dim3 grid(a.total_blocks, (a.num_groups + 31) / 32);
-    const size_t sm = static_cast<size_t>(a.lane_bins) * 32 * 4 * kLaneWarps + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * (32 + 4);
+    const size_t sm = static_cast<size_t>(a.lane_bins) * 32 * 4 * kLaneWarps + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * (32 + 4) + static_cast<size_t>(kLaneWarps) * kLaneStages * 8;
 #define FB_LANE(NB)                                                                                                                \
     {                                                                                                                              \
       static bool attr = false;                                                                                                    \

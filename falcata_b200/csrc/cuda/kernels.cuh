@@ -66,6 +66,8 @@ struct HistArgs {
   const HistTask* tasks; int num_tasks; int total_blocks;
   const HistPartition* parts; int num_parts; int max_part_bins;
   const int* group_bin_start;
+  int bulk_root;                // 1: root level (rows in order, 32-byte rows) staged by bulk asynchronous copies with mbarrier completion
+  unsigned int* status;         // device status word (nullable): a bounded wait that gives up records kStatusWaitTimeout here
   int pack4;                    // 1 (compact view of groups with at most 16 bins): two groups per byte, low nibble first
   const int* group_bin_count;   // non-null (compact view): bins per listed group; null: groups are consecutive in the bin space
   int rows_per_block; int sub_rows;

@@ -62,6 +62,7 @@ int FB_OpHistogram(const uint8_t* rows, int row_stride, int num_groups, const vo
   a.sub_rows = quant ? std::max(1, std::min(65535 / qb, 32767 / std::max(1, qb / 2))) : (1 << 30);
   a.identity_root = idx == nullptr ? 1 : 0;
   a.num_total_bin = total; a.lane_mode = quant ? lane_mode : 0;
+  a.bulk_root = getenv("FALCATA_NO_BULK_ROOT") == nullptr ? 1 : 0;   // the kernel itself decides where the bulk-copy pipeline applies
   int mgb = 0; for (int v : gbins) mgb = std::max(mgb, v);
   a.lane_bins = mgb <= 16 ? 16 : 64;
   if (a.lane_mode != 0 && mgb > 64) Log::Fatal("lane histogram covers groups of at most 64 bins");

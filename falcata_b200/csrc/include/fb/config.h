@@ -204,6 +204,7 @@ struct Plan {
   bool hist_lane = true;         // lane-per-group construct with bank-interleaved warp-private tiles (groups with <= 64 bins)
   bool hist_lane_atomic = false; // lane-per-group construct with one shared tile per block and shared atomics
   bool col_major_part = true;    // partition reads the split column from a column-major copy of the bins
+  bool bulk_root = true;         // root level of the lane construct staged by bulk asynchronous copies (TMA engine, mbarrier completion)
   static Plan FromString(const std::string& s);
   std::string ToString() const;
 };
