@@ -80,6 +80,7 @@ struct HistArgs {
   const LevelCtrl* ctrl;    // non-null: num_tasks / total_blocks come from the device controller
 };
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s);
+int LaneRowsUnit();   // rows per stage of a lane-construct block (warps x 32): rows_per_block is chosen in these units
 // K9: per-tree compact view. out[row][j] = cols[groups[j]][row] for the listed (sampled) feature groups: a dense
 // row-major matrix with only the columns this tree can split on, read from the column-major copy (coalesced
 // along rows) and written in 32-byte row pieces through a shared-memory transpose tile.
