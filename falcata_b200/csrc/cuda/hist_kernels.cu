@@ -459,7 +459,7 @@ void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
 #define FB_LANE(NB)                                                                                                                \
     {                                                                                                                              \
       static bool attr = false;                                                                                                    \
-      if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantLaneKernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); attr = true; } \
+      if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantLaneKernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr = true; } \
       HistQuantLaneKernel<NB><<<grid, kLaneThreads, sm, s>>>(a);                                                                   \
     }
     if (a.lane_bins == 16) FB_LANE(16)
