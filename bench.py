@@ -1,6 +1,6 @@
 """Headline benchmark: seconds per 1000 boosting rounds on the 11M x 28 binary configuration.
 
-Config (BASELINE.json #2): 11,000,000 rows x 28 fp32 features (21 N(0,1) + 7 |x_i x_j|), label ~
+Config (the second of the project's five benchmark configurations): 11,000,000 rows x 28 fp32 features (21 N(0,1) + 7 |x_i x_j|), label ~
 Bernoulli(sigmoid(x.w + 0.5 x0 x1)); objective=binary, num_leaves=255, max_bin=63, learning_rate=0.1,
 quant_mode=stochastic with 4 bins, tree_learner=data, rows sharded over the GPUs of one box.
 
@@ -73,7 +73,7 @@ def reference_arm(args) -> None:
     # ships them as empty directories and the image has no copy, so it cannot be built offline here.
     ok = os.path.isdir(os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", "falcata"))
     if not ok:
-        print(json.dumps({"impl": "reference", "unavailable": "reference cannot be built offline: /root/reference is not pip-installable (no pyproject at its root) and its external_libs submodules (eigen, fast_double_parser, fmt) are empty and absent from the image"}))
+        print(json.dumps({"impl": "reference", "unavailable": "reference cannot be built offline: its source tree is not pip-installable (no pyproject at its root) and its external_libs submodules (eigen, fast_double_parser, fmt) are empty and absent from the image"}))
         return
     print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref exists but the native library was never built (missing Eigen / fast_double_parser sources)"}))
 

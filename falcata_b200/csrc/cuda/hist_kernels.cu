@@ -189,7 +189,7 @@ __device__ __forceinline__ void ConsumeStage(int* __restrict__ tile, const unsig
   const int nshift = (lane & 1) * 4;
   auto bin_of = [&](int j) -> int { const int b = sr[j * 32]; return P4 ? ((b >> nshift) & 15) : b; };
   if (cnt == 32) {
-#pragma unroll 2
+#pragma unroll
     for (int j = 0; j < 32; j += 4) {
       const int a0 = bin_of(j) * 32 + lane, a1 = bin_of(j + 1) * 32 + lane, a2 = bin_of(j + 2) * 32 + lane, a3 = bin_of(j + 3) * 32 + lane;
       const int4 g4 = *reinterpret_cast<const int4*>(sg + j);     // same address in every lane: one broadcast load
