@@ -53,6 +53,28 @@ def _compile(src: Path, obj: Path, ptxas: bool) -> str:
     return r.stderr if ptxas else ""
 
 
+def build_sanitized() -> Path:
+    """Host-only build of the core library with AddressSanitizer and UndefinedBehaviorSanitizer, for running the CPU
+    tests under sanitizers (``FALCATA_LIB=<path> python -m pytest tests -m "not gpu"`` with libasan preloaded).
+    The CUDA translation units are left out: device_type=cpu only."""
+    out_dir = BUILD / "asan"; out_dir.mkdir(parents=True, exist_ok=True)
+    cxx = "/usr/bin/g++" if Path("/usr/bin/g++").exists() else CXX   # the system compiler ships libasan / libubsan / libgomp
+    cpp = sorted(CSRC.glob("core/*.cpp"))
+    objs = []
+    for src in cpp:
+        obj = out_dir / (src.stem + ".o"); objs.append(obj)
+        cmd = [cxx, "-std=c++17", "-O1", "-g", f"-I{CSRC / 'include'}", "-I/usr/local/cuda/include", "-fPIC", "-fopenmp", "-ffp-contract=off",
+               "-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-DFB_NO_CUDA=1", "-c", str(src), "-o", str(obj)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"compile failed: {' '.join(cmd)}\n{r.stderr}")
+    lib = LIB.parent / "libfalcata_core_asan.so"
+    r = subprocess.run([cxx, "-shared", "-fsanitize=address,undefined", "-fopenmp", "-o", str(lib), *map(str, objs), "-lz"], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed\n{r.stderr}")
+    return lib
+
+
 def build(force: bool = False, ptxas: bool = False, verbose: bool = False) -> Path:
     BUILD.mkdir(parents=True, exist_ok=True)
     LIB.parent.mkdir(parents=True, exist_ok=True)
@@ -102,5 +124,7 @@ def _build_cli() -> Path:
 
 
 if __name__ == "__main__":
+    if "--sanitize" in sys.argv:
+        print(build_sanitized()); sys.exit(0)
     p = build(force="--force" in sys.argv, ptxas="--ptxas" in sys.argv, verbose=True)
     print(p)

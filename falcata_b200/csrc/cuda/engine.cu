@@ -1,6 +1,8 @@
 // Device engine: construction, buffers, score bookkeeping, validation sets, metrics.
 #include "engine.h"
 
+#include <nvtx3/nvToolsExt.h>
+
 #include <sstream>
 
 namespace fb {
@@ -9,13 +11,14 @@ namespace fb {
 StageClock::~StageClock() { for (auto& p : pool) { cudaEventDestroy(p.first); cudaEventDestroy(p.second); } }
 int StageClock::Stage(const char* name) { names.push_back(name); total_ms.push_back(0.0); calls.push_back(0); return static_cast<int>(names.size()) - 1; }
 void StageClock::Begin(int stage, cudaStream_t s) {
+  if (nvtx) { nvtxRangePushA(names[stage].c_str()); nvtx_open = true; }   // host-side range around the stage's launches (FALCATA_NVTX=1)
   if (!enabled) return;
   if (next >= pool.size()) { cudaEvent_t a, b; FB_CUDA(cudaEventCreate(&a)); FB_CUDA(cudaEventCreate(&b)); pool.emplace_back(a, b); }
   FB_CUDA(cudaEventRecord(pool[next].first, s));
   pending.emplace_back(stage, static_cast<int>(next));
   open_ = static_cast<int>(next); ++next;
 }
-void StageClock::End(cudaStream_t s) { if (!enabled || open_ < 0) return; FB_CUDA(cudaEventRecord(pool[open_].second, s)); open_ = -1; }
+void StageClock::End(cudaStream_t s) { if (nvtx_open) { nvtxRangePop(); nvtx_open = false; } if (!enabled || open_ < 0) return; FB_CUDA(cudaEventRecord(pool[open_].second, s)); open_ = -1; }
 void StageClock::Resolve() {
   if (!enabled) return;
   static const bool dump = getenv("FALCATA_STAGE_DUMP") != nullptr;
@@ -64,6 +67,7 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   if (cfg.grow_policy == "leaf") Log::Warning("grow_policy=leaf runs on the host learner; the device learner grows level-wise with a gain-ranked leaf budget");
   col_sampler_.Init(cfg, train);
   clock_.enabled = getenv("FALCATA_STAGE_TIMING") != nullptr;
+  clock_.nvtx = getenv("FALCATA_NVTX") != nullptr;
   st_grad_ = clock_.Stage("gradients"); st_quant_ = clock_.Stage("quantize+root"); st_hist_ = clock_.Stage("histogram");
   st_find_ = clock_.Stage("find-split"); st_part_ = clock_.Stage("partition"); st_score_ = clock_.Stage("score-update"); st_sync_ = clock_.Stage("level-readback");
 

@@ -23,7 +23,7 @@ struct StageClock {
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pool;
   std::vector<std::pair<int, int>> pending;   // (stage, pool index)
   std::vector<double> total_ms; std::vector<int64_t> calls; std::vector<std::string> names;
-  size_t next = 0; bool enabled = false;
+  size_t next = 0; bool enabled = false; bool nvtx = false, nvtx_open = false;   // nvtx: NVTX ranges named after the stages, for timeline tools
   int Stage(const char* name);
   void Begin(int stage, cudaStream_t s);
   void End(cudaStream_t s);

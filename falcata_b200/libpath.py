@@ -9,6 +9,11 @@ _LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfalcata_core.so"
 
 
 def find_lib_path() -> Path:
+    import os
+
+    override = os.environ.get("FALCATA_LIB")   # e.g. the sanitizer build made by ``python -m falcata_b200.build --sanitize``
+    if override:
+        return Path(override)
     if not _LIB_PATH.exists():
         from .build import build
 
