@@ -182,6 +182,15 @@ def time_tag_report() -> str:
 
 
 # ------------------------------------------------------------------ Dataset ----
+def _wants_linear(params: Dict[str, Any], reference: Any = None) -> bool:
+    """linear_tree keeps the raw feature values beside the bins, which only the host construction does."""
+    for k in ("linear_tree", "linear_trees"):
+        v = params.get(k)
+        if v is not None and str(v).lower() in ("1", "true", "+"):
+            return True
+    return reference is not None and _wants_linear(getattr(reference, "params", {}) or {})
+
+
 class Dataset:
     """Binned training / validation data.
 
@@ -235,7 +244,7 @@ class Dataset:
         elif isinstance(self.data, (str, os.PathLike)):
             _safe_call(lib.FB_DatasetCreateFromFile(str(self.data).encode(), _param_str(params), ref_handle, ctypes.byref(handle)))
             self._handle = handle
-        elif _is_cuda_array(self.data):
+        elif _is_cuda_array(self.data) and not _wants_linear(params, self.reference):
             self._construct_from_device(self.data, params, ref_handle)
         elif self._host_matrix_for_device(params, ref_handle):
             self._construct_host_via_device(params)
@@ -270,6 +279,8 @@ class Dataset:
         """A dense host matrix that will train on the device is binned there too (unless host bins are asked for)."""
         if ref_handle is not None or str(params.get("device_type", "")).lower() not in ("cuda", "gpu") or params.get("keep_host_bins"):
             return False
+        if _wants_linear(params, self.reference):
+            return False   # linear leaves are fitted on the host from the raw values
         if not cuda_available():
             return False
         d = self.data

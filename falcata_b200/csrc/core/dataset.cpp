@@ -127,6 +127,7 @@ void Dataset::ConstructSchemaTyped(const void* sample, int dtype, int ns, int nc
   ScopedTimer timer("Dataset::ConstructSchema");
   num_total_features = ncol;
   max_bin_param = cfg.max_bin;
+  keep_raw = cfg.linear_tree;
   categorical_features = categorical;
   std::vector<char> is_cat(ncol, 0);
   for (int c : categorical) if (c >= 0 && c < ncol) is_cat[c] = 1;
@@ -254,17 +255,24 @@ void Dataset::CopySchemaFrom(const Dataset& ref) {
   used_feature_map = ref.used_feature_map; real_feature_idx = ref.real_feature_idx;
   group_features = ref.group_features; group_bin_start = ref.group_bin_start; group_num_bin = ref.group_num_bin;
   feature_meta = ref.feature_meta; feature_names = ref.feature_names; categorical_features = ref.categorical_features;
-  bin_bytes = ref.bin_bytes; row_stride = ref.num_groups;
+  bin_bytes = ref.bin_bytes; row_stride = ref.num_groups; keep_raw = ref.keep_raw;
 }
 
 void Dataset::AllocateRows(data_size_t n) {
   num_data = n; metadata.num_data = n;
   if (global_num_data == 0) global_num_data = n;
   if (bin_bytes == 1) bins8.assign(static_cast<size_t>(n) * row_stride, 0); else bins16.assign(static_cast<size_t>(n) * row_stride, 0);
+  if (keep_raw) raw.assign(static_cast<size_t>(n) * num_total_features, 0.f);
 }
 
 void Dataset::PushDense(const void* data, int dtype, data_size_t n, int ncol, bool row_major, data_size_t row_begin) {
   if (ncol != num_total_features) Log::Fatal("The number of columns (%d) differs from the dataset's (%d)", ncol, num_total_features);
+  if (keep_raw && !raw.empty()) {
+#pragma omp parallel for schedule(static)
+    for (data_size_t i = 0; i < n; ++i)
+      for (int j = 0; j < ncol; ++j)
+        raw[static_cast<size_t>(row_begin + i) * ncol + j] = static_cast<float>(ReadValue(data, dtype, row_major ? static_cast<size_t>(i) * ncol + j : static_cast<size_t>(j) * n + i));
+  }
 #pragma omp parallel for schedule(static)
   for (data_size_t i = 0; i < n; ++i) {
     const size_t out = static_cast<size_t>(row_begin + i) * row_stride;
@@ -378,6 +386,7 @@ Dataset* Dataset::Subset(const data_size_t* idx, data_size_t n) const {
   for (data_size_t i = 0; i < n; ++i) {
     const size_t s = static_cast<size_t>(idx[i]) * row_stride, d = static_cast<size_t>(i) * row_stride;
     if (bin_bytes == 1) memcpy(&ds->bins8[d], &bins8[s], row_stride); else memcpy(&ds->bins16[d], &bins16[s], row_stride * 2);
+    if (has_raw()) memcpy(&ds->raw[static_cast<size_t>(i) * num_total_features], &raw[static_cast<size_t>(idx[i]) * num_total_features], sizeof(float) * num_total_features);
   }
   if (!metadata.label.empty()) { ds->metadata.label.resize(n); for (data_size_t i = 0; i < n; ++i) ds->metadata.label[i] = metadata.label[idx[i]]; }
   if (!metadata.weights.empty()) { ds->metadata.weights.resize(n); for (data_size_t i = 0; i < n; ++i) ds->metadata.weights[i] = metadata.weights[idx[i]]; }

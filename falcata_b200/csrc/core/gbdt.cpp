@@ -27,6 +27,11 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
     class_need_train_.assign(num_tree_per_iteration_, true);
     if (obj != nullptr) for (int k = 0; k < num_tree_per_iteration_; ++k) class_need_train_[k] = obj->ClassNeedTrain(k);
     init_scores_.assign(num_tree_per_iteration_, 0.0);
+    if (cfg.linear_tree && is_cuda_) {
+      Log::Warning("linear_tree trains on the host (the leaf regressions need the raw feature values)");
+      is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
+    }
+    if (cfg.linear_tree && !train->has_raw()) Log::Fatal("linear_tree needs the raw feature values: build the Dataset from host data with linear_tree=true in its params");
     if ((is_dart_ || is_rf_) && is_cuda_) {
       Log::Warning("boosting=%s keeps its scores on the host; the device engine is used for gbdt", cfg.boosting.c_str());
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
@@ -84,6 +89,7 @@ void GBDT::AddValidData(const Dataset* valid) {
 void GBDT::AddTreeScore(const Tree* tree, const Dataset* ds, double* score, double scale) const {
   if (tree->num_leaves <= 1) { const double v = tree->leaf_value[0] * scale; for (data_size_t i = 0; i < ds->num_data; ++i) score[i] += v; return; }
   if (!ds->has_host_bins()) Log::Fatal("Host traversal needs host-resident bins");
+  if (tree->is_linear && !ds->has_raw()) Log::Fatal("A linear tree needs the raw feature values of the dataset it scores (linear_tree=true in the Dataset params)");
 #pragma omp parallel for schedule(static)
   for (data_size_t i = 0; i < ds->num_data; ++i) {
     int node = 0;
@@ -92,7 +98,121 @@ void GBDT::AddTreeScore(const Tree* tree, const Dataset* ds, double* score, doub
       const FeatureMeta& m = ds->feature_meta[f];
       node = tree->DecideBin(ds->FeatureBin(i, f), node, m.default_bin, m.num_bin - 1);
     }
-    score[i] += scale * tree->leaf_value[~node];
+    const int leaf = ~node;
+    if (!tree->is_linear) { score[i] += scale * tree->leaf_value[leaf]; continue; }
+    double out = tree->leaf_const[leaf];
+    const float* row = ds->raw.data() + static_cast<size_t>(i) * ds->num_total_features;
+    const auto& fs = tree->leaf_features[leaf];
+    for (size_t k = 0; k < fs.size(); ++k) {
+      const float v = row[fs[k]];
+      if (std::isnan(v)) { out = tree->leaf_value[leaf]; break; }
+      out += tree->leaf_coeff[leaf][k] * static_cast<double>(v);
+    }
+    score[i] += scale * out;
+  }
+}
+
+namespace {
+// Solves A x = b for a small dense symmetric system by elimination with partial pivoting; false when singular.
+bool SolveDense(std::vector<double>* a_io, std::vector<double>* b_io, int n) {
+  std::vector<double>& a = *a_io; std::vector<double>& b = *b_io;
+  for (int c = 0; c < n; ++c) {
+    int piv = c; double best = std::fabs(a[static_cast<size_t>(c) * n + c]);
+    for (int r = c + 1; r < n; ++r) { const double v = std::fabs(a[static_cast<size_t>(r) * n + c]); if (v > best) { best = v; piv = r; } }
+    if (!(best > 1e-12)) return false;
+    if (piv != c) { for (int k = 0; k < n; ++k) std::swap(a[static_cast<size_t>(c) * n + k], a[static_cast<size_t>(piv) * n + k]); std::swap(b[c], b[piv]); }
+    const double inv = 1.0 / a[static_cast<size_t>(c) * n + c];
+    for (int r = c + 1; r < n; ++r) {
+      const double f = a[static_cast<size_t>(r) * n + c] * inv;
+      if (f == 0.0) continue;
+      for (int k = c; k < n; ++k) a[static_cast<size_t>(r) * n + k] -= f * a[static_cast<size_t>(c) * n + k];
+      b[r] -= f * b[c];
+    }
+  }
+  for (int c = n - 1; c >= 0; --c) {
+    double v = b[c];
+    for (int k = c + 1; k < n; ++k) v -= a[static_cast<size_t>(c) * n + k] * b[k];
+    b[c] = v / a[static_cast<size_t>(c) * n + c];
+    if (!std::isfinite(b[c])) return false;
+  }
+  return true;
+}
+}  // namespace
+
+// Piecewise-linear leaves: for every leaf, a second-order fit of the leaf's rows on the numerical features of its
+// root path, coefficients = -(X^T H X + lambda I)^-1 X^T g with an unpenalised intercept. Rows with a missing value
+// in a path feature stay on the constant output (kept in leaf_value). The first tree stays constant.
+// Parity: src/treelearner/linear_tree_learner.cpp (CalculateLinear: path features, per-leaf normal equations,
+// linear_lambda on the diagonal, fall back to the constant when a leaf has too few rows).
+void GBDT::FitLinearLeaves(Tree* tree, const float* grad, const float* hess, bool constant_only) const {
+  const int nl = tree->num_leaves;
+  tree->is_linear = true;
+  tree->leaf_const.assign(tree->leaf_value.begin(), tree->leaf_value.end());
+  tree->leaf_coeff.assign(tree->leaf_value.size(), {}); tree->leaf_features.assign(tree->leaf_value.size(), {}); tree->leaf_features_inner.assign(tree->leaf_value.size(), {});
+  if (constant_only || nl <= 1) return;
+  const Dataset* ds = train_;
+  if (!ds->has_raw()) Log::Fatal("linear_tree needs the raw feature values: build the Dataset from host data with linear_tree=true in its params");
+  // numerical features on the path of every leaf
+  std::vector<std::vector<int>> path(nl);
+  {
+    std::vector<std::pair<int, std::vector<int>>> stack; stack.push_back({0, {}});
+    while (!stack.empty()) {
+      auto cur = std::move(stack.back()); stack.pop_back();
+      const int node = cur.first;
+      if (node < 0) { std::sort(cur.second.begin(), cur.second.end()); cur.second.erase(std::unique(cur.second.begin(), cur.second.end()), cur.second.end()); path[~node] = std::move(cur.second); continue; }
+      std::vector<int> f = cur.second;
+      if (!(tree->decision_type[node] & kCategoricalMask)) f.push_back(tree->split_feature_inner[node]);
+      stack.push_back({tree->left_child[node], f}); stack.push_back({tree->right_child[node], std::move(f)});
+    }
+  }
+  // leaf of every fitting row (the bag when one is drawn)
+  const bool bagged = (is_bagging_ || is_goss_) && bag_cnt_ > 0 && bag_cnt_ < ds->num_data;
+  const data_size_t m = bagged ? bag_cnt_ : ds->num_data;
+  std::vector<int> leaf_of(m);
+#pragma omp parallel for schedule(static)
+  for (data_size_t t = 0; t < m; ++t) {
+    const data_size_t i = bagged ? bag_indices_[t] : t;
+    int node = 0;
+    while (node >= 0) {
+      const int f = tree->split_feature_inner[node];
+      const FeatureMeta& fm = ds->feature_meta[f];
+      node = tree->DecideBin(ds->FeatureBin(i, f), node, fm.default_bin, fm.num_bin - 1);
+    }
+    leaf_of[t] = ~node;
+  }
+  std::vector<std::vector<data_size_t>> rows(nl);
+  for (data_size_t t = 0; t < m; ++t) rows[leaf_of[t]].push_back(bagged ? bag_indices_[t] : t);
+  const int ncol = ds->num_total_features;
+  const double lambda = config_.linear_lambda;
+#pragma omp parallel for schedule(dynamic)
+  for (int leaf = 0; leaf < nl; ++leaf) {
+    const int d = static_cast<int>(path[leaf].size());
+    if (d == 0) continue;
+    std::vector<int> real(d);
+    for (int k = 0; k < d; ++k) real[k] = ds->real_feature_idx[path[leaf][k]];
+    const int dim = d + 1;
+    std::vector<double> A(static_cast<size_t>(dim) * dim, 0.0), b(dim, 0.0), x(dim);
+    data_size_t used = 0;
+    for (data_size_t i : rows[leaf]) {
+      const float* r = ds->raw.data() + static_cast<size_t>(i) * ncol;
+      bool nan = false;
+      for (int k = 0; k < d; ++k) { x[k] = r[real[k]]; if (std::isnan(x[k])) { nan = true; break; } }
+      if (nan) continue;
+      x[d] = 1.0;
+      const double g = grad[i], h = hess[i];
+      for (int p = 0; p < dim; ++p) { b[p] -= g * x[p]; const double hx = h * x[p]; for (int q = p; q < dim; ++q) A[static_cast<size_t>(p) * dim + q] += hx * x[q]; }
+      ++used;
+    }
+    if (used < static_cast<data_size_t>(dim)) continue;   // too few rows: the constant stays
+    for (int p = 0; p < dim; ++p) for (int q = 0; q < p; ++q) A[static_cast<size_t>(p) * dim + q] = A[static_cast<size_t>(q) * dim + p];
+    for (int p = 0; p < d; ++p) A[static_cast<size_t>(p) * dim + p] += lambda;
+    if (!SolveDense(&A, &b, dim)) continue;
+    std::vector<double> coeff; std::vector<int> feats, inner;
+    for (int k = 0; k < d; ++k) {
+      if (std::fabs(b[k]) <= kZeroThreshold) continue;
+      coeff.push_back(b[k]); feats.push_back(real[k]); inner.push_back(path[leaf][k]);
+    }
+    tree->leaf_const[leaf] = b[d]; tree->leaf_coeff[leaf] = std::move(coeff); tree->leaf_features[leaf] = std::move(feats); tree->leaf_features_inner[leaf] = std::move(inner);
   }
 }
 
@@ -211,7 +331,7 @@ void GBDT::DartNormalize() {
 void GBDT::UpdateScore(const Tree* tree, int k) {
   const data_size_t n = train_->num_data;
   double* ts = train_score_.data() + static_cast<size_t>(k) * n;
-  if (tree->num_leaves > 1 && !(is_bagging_ || is_goss_) ) learner_->AddPredictionToScore(tree, ts);
+  if (tree->num_leaves > 1 && !(is_bagging_ || is_goss_) && !tree->is_linear) learner_->AddPredictionToScore(tree, ts);
   else AddTreeScore(tree, train_, ts, 1.0);   // bagging: out-of-bag rows need the traversal
   for (size_t v = 0; v < valid_.size(); ++v) AddTreeScore(tree, valid_[v], valid_score_[v].data() + static_cast<size_t>(k) * valid_[v]->num_data, 1.0);
 }
@@ -288,6 +408,7 @@ bool GBDT::TrainOneIter(const float* grad_in, const float* hess_in) {
         if (is_rf_) std::fill(sc.begin(), sc.end(), init_scores_[k]);
         learner_->RenewTreeOutput(tree.get(), objective_, nullptr, n, bag_indices_.data(), bag_cnt_, sc.data());
       }
+      if (config_.linear_tree) FitLinearLeaves(tree.get(), grad + static_cast<size_t>(k) * n, hess + static_cast<size_t>(k) * n, models_.size() < static_cast<size_t>(K));
       tree->Shrink(shrinkage_rate_);
       if (is_rf_) {
         // forests average: train/valid scores hold the running mean

@@ -84,6 +84,10 @@ class Dataset {
   int64_t global_row_offset = 0;
   int64_t global_num_data = 0;
   int max_bin_param = 255;
+  // raw feature values [num_data x num_total_features], kept only for linear_tree (the leaf regressions need them)
+  bool keep_raw = false;
+  std::vector<float> raw;
+  bool has_raw() const { return !raw.empty(); }
 
   // Build mappers + groups from a dense sample [ns x ncol] (row-major doubles).
   void ConstructSchema(const double* sample, int ns, int ncol, int64_t total_rows, const Config& cfg,

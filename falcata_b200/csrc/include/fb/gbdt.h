@@ -102,6 +102,8 @@ class GBDT {
   void DartNormalize();
   bool CheckDivergence(const float* grad, int64_t n);
   void AddTreeScore(const Tree* tree, const Dataset* ds, double* score, double scale) const;
+  // linear_tree: replace the constant leaf outputs by a ridge regression on the leaf's path features
+  void FitLinearLeaves(Tree* tree, const float* grad, const float* hess, bool constant_only) const;
 
   const Dataset* train_ = nullptr;
   std::vector<const Dataset*> valid_;

@@ -101,3 +101,37 @@ def test_custom_objective_and_continue():
     b3 = fb.train({"objective": "regression", "device_type": "cpu", "verbosity": -1}, fb.Dataset(X, y, free_raw_data=False), 10, init_model=b2)
     assert b3.num_trees() == 30
     assert np.mean((b3.predict(X) - y) ** 2) < np.mean((b2.predict(X) - y) ** 2)
+
+
+def test_linear_tree_fits_piecewise_linear_target(tmp_path):
+    """linear_tree=true: ridge regression on each leaf's path features; beats constant leaves on a
+    piecewise-linear target, survives the text model round trip, validation scores equal predict()."""
+    rng = np.random.default_rng(0)
+    n = 8000
+
+    def target(A):
+        return np.where(A[:, 0] > 0, 2 * A[:, 1] + 1, -3 * A[:, 2]).astype(np.float32)
+
+    X = rng.normal(size=(n, 5)).astype(np.float32)
+    y = target(X) + 0.05 * rng.normal(size=n).astype(np.float32)
+    Xv = rng.normal(size=(2000, 5)).astype(np.float32)
+    Xv[::50, 1] = np.nan   # rows with a missing path feature fall back to the constant output
+    yv = target(np.nan_to_num(Xv))
+    mse = {}
+    for lin in (False, True):
+        p = {"objective": "regression", "num_leaves": 8, "learning_rate": 0.2, "linear_tree": lin, "linear_lambda": 0.01,
+             "verbose": -1, "min_data_in_leaf": 20}
+        ds = fb.Dataset(X, y, params=p)
+        dv = fb.Dataset(Xv, yv, reference=ds)
+        ev = {}
+        b = fb.train(p, ds, 25, valid_sets=[dv], valid_names=["v"], callbacks=[fb.record_evaluation(ev)])
+        pr = b.predict(Xv)
+        mse[lin] = float(np.mean((pr - yv) ** 2))
+        assert abs(ev["v"]["l2"][-1] - mse[lin]) < 1e-9
+        if lin:
+            s = b.model_to_string()
+            assert "is_linear=1" in s and "leaf_coeff=" in s
+            path = tmp_path / "lin.txt"
+            b.save_model(str(path))
+            assert np.array_equal(fb.Booster(model_file=str(path)).predict(Xv), pr)
+    assert mse[True] < 0.3 * mse[False]
