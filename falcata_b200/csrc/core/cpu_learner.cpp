@@ -139,6 +139,7 @@ void CPUTreeLearner::SetParams() {
   sp_.min_data_in_leaf = cfg_.min_data_in_leaf; sp_.max_depth = cfg_.max_depth;
   sp_.max_cat_threshold = cfg_.max_cat_threshold; sp_.max_cat_to_onehot = cfg_.max_cat_to_onehot; sp_.min_data_per_group = cfg_.min_data_per_group;
   sp_.cat_l2 = cfg_.cat_l2; sp_.cat_smooth = cfg_.cat_smooth; sp_.extra_trees = cfg_.extra_trees ? 1 : 0;
+  sp_.use_mc = 0; for (const auto& m : ds_->feature_meta) if (m.monotone != 0) sp_.use_mc = 1;
   quant_ = cfg_.quant != QuantMode::None;
   qs_.bins = cfg_.quant_bins_resolved; qs_.stochastic = cfg_.quant == QuantMode::Stochastic;
   const bool net = Network::active();
@@ -301,8 +302,8 @@ void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanI
     }
   }
   if (cand.feature >= 0) {
-    cand.left_out = LeafOutput(cand.left_g, FB_ADD(cand.left_h, kEpsilon), sp_, cand.left_cnt, L.parent_output);
-    cand.right_out = LeafOutput(cand.right_g, FB_ADD(cand.right_h, kEpsilon), sp_, cand.right_cnt, L.parent_output);
+    cand.left_out = ChildOutput(cand.left_g, FB_ADD(cand.left_h, kEpsilon), sp_, cand.left_cnt, L);
+    cand.right_out = ChildOutput(cand.right_g, FB_ADD(cand.right_h, kEpsilon), sp_, cand.right_cnt, L);
     cand.gain = FB_MUL(cand.gain, static_cast<double>(m.penalty));
     if (SplitBetter(cand.gain, ds_->feature_meta[cand.feature].real_index, cand.threshold, best->gain,
                     best->feature >= 0 ? ds_->feature_meta[best->feature].real_index : -1, best->threshold)) *best = cand;
@@ -372,8 +373,8 @@ void CPUTreeLearner::ScanCategorical(const LeafState& leaf, int f, const LeafSca
     }
   }
   if (cand.feature >= 0) {
-    cand.left_out = LeafOutput(cand.left_g, FB_ADD(cand.left_h, kEpsilon), p, cand.left_cnt, L.parent_output);
-    cand.right_out = LeafOutput(cand.right_g, FB_ADD(cand.right_h, kEpsilon), p, cand.right_cnt, L.parent_output);
+    cand.left_out = ChildOutput(cand.left_g, FB_ADD(cand.left_h, kEpsilon), p, cand.left_cnt, L);
+    cand.right_out = ChildOutput(cand.right_g, FB_ADD(cand.right_h, kEpsilon), p, cand.right_cnt, L);
     cand.gain = FB_MUL(cand.gain, static_cast<double>(m.penalty));
     if (SplitBetter(cand.gain, m.real_index, 0, best->gain, best->feature >= 0 ? ds_->feature_meta[best->feature].real_index : -1, best->threshold)) *best = cand;
   }
@@ -401,7 +402,7 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
   if (n_global < 2LL * sp_.min_data_in_leaf) return;
   LeafScanInfo L;
   L.sum_g = leaf->sum_g; L.sum_h = leaf->sum_h; L.sum_gi = leaf->sum_gi; L.sum_hi = leaf->sum_hi;
-  L.num_data = static_cast<int>(n_global); L.parent_output = leaf->output;
+  L.num_data = static_cast<int>(n_global); L.parent_output = leaf->output; L.min_c = leaf->min_constraint; L.max_c = leaf->max_constraint;
   L.g_scale = quant_ ? qs_.g_scale : 1.0; L.h_scale = quant_ ? qs_.h_scale : 1.0;
   L.cnt_factor = FB_DIV(static_cast<double>(L.num_data), L.sum_h);
   L.min_gain_shift = FB_ADD(LeafGainGivenOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, leaf->output), sp_.min_gain_to_split);

@@ -101,6 +101,7 @@ __global__ void __launch_bounds__(kCtrlThreads) LevelControllerKernel(CtrlArgs a
     ci.left_g = b.left_g; ci.left_h = b.left_h; ci.right_g = b.right_g; ci.right_h = b.right_h; ci.left_out = b.left_out; ci.right_out = b.right_out;
     ci.left_gi = b.left_gi; ci.left_hi = b.left_hi; ci.right_gi = P.sum_gi - b.left_gi; ci.right_hi = P.sum_hi - b.left_hi;
     ci.hist_block_begin = s_blocks[s]; ci.hist_num_blocks = s_blocks[s + 1] - s_blocks[s];
+    ci.monotone = b.monotone; ci.pad_ = 0;
     a.child_init[s] = ci;
     FindChild fl, fr;
     fl.leaf = l; fl.slot = ci.left_slot; fl.other_slot = ci.right_slot; fl.is_larger = ci.smaller_is_left ? 0 : 1; fl.split = s; fl.is_left = 1; fl.parent_global = P.num_data_global; fl.task = s;

@@ -129,6 +129,7 @@ struct LeafInfo {
   double sum_g, sum_h;         // real-valued totals
   long long sum_gi, sum_hi;    // integer totals (quantized)
   double output;
+  double min_c, max_c;         // monotone range of the output (-inf, +inf when unconstrained)
 };
 
 // Bounded spin on a flag written by a peer rank. Returns false when the budget ran out; callers

@@ -26,6 +26,7 @@ __global__ void InitRootKernel(LeafInfo* leaves, const long long* sums_i, const 
     L.sum_g = FB_MUL(static_cast<double>(L.sum_gi), static_cast<double>(scales[0])); L.sum_h = FB_MUL(static_cast<double>(L.sum_hi), static_cast<double>(scales[1]));
   } else { L.sum_gi = L.sum_hi = 0; L.sum_g = sums_d[0]; L.sum_h = sums_d[1]; }
   L.output = LeafOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp, L.num_data_global, 0.0);
+  L.min_c = -1.0 / 0.0; L.max_c = 1.0 / 0.0;
   leaves[0] = L;
 }
 
@@ -433,7 +434,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
       const int fresh = next_slot++;
       c.left_slot = c.smaller_is_left ? fresh : P.slot; c.right_slot = c.smaller_is_left ? P.slot : fresh;
       c.left_g = b.left_g; c.left_h = b.left_h; c.right_g = b.right_g; c.right_h = b.right_h; c.left_out = b.left_out; c.right_out = b.right_out;
-      c.left_gi = b.left_gi; c.left_hi = b.left_hi;
+      c.left_gi = b.left_gi; c.left_hi = b.left_hi; c.monotone = b.monotone;
       c.right_gi = PL.sum_gi - b.left_gi; c.right_hi = PL.sum_hi - b.left_hi;
       c.hist_block_begin = block_cursor; c.hist_num_blocks = std::max(1, (P.count + ha.rows_per_block - 1) / ha.rows_per_block); block_cursor += c.hist_num_blocks;
       FindChild& fl = fc[2 * s]; FindChild& fr = fc[2 * s + 1];

@@ -183,6 +183,7 @@ struct ChildInit {     // host-decided child bookkeeping of one split
   double left_g, left_h, right_g, right_h, left_out, right_out;
   long long left_gi, left_hi, right_gi, right_hi;
   int hist_block_begin, hist_num_blocks;
+  int monotone, pad_;              // constraint of the split feature: tightens the children's output ranges
 };
 struct PartArgs {
   const uint8_t* rows; int row_stride;

@@ -121,6 +121,11 @@ __global__ void __launch_bounds__(kPartThreads) PartitionScanSetupKernel(PartArg
     L.hist_slot = ci.left_slot; R.hist_slot = ci.right_slot;
     L.sum_g = ci.left_g; L.sum_h = ci.left_h; L.sum_gi = ci.left_gi; L.sum_hi = ci.left_hi; L.output = ci.left_out;
     R.sum_g = ci.right_g; R.sum_h = ci.right_h; R.sum_gi = ci.right_gi; R.sum_hi = ci.right_hi; R.output = ci.right_out;
+    if (ci.monotone != 0) {   // "basic" monotone method: the children's ranges meet at the mid point of their outputs
+      const double mid = (ci.left_out + ci.right_out) / 2.0;
+      if (ci.monotone > 0) { L.max_c = fmin(L.max_c, mid); R.min_c = fmax(R.min_c, mid); }
+      else { L.min_c = fmax(L.min_c, mid); R.max_c = fmin(R.max_c, mid); }
+    }
     L.num_data_global = nl; R.num_data_global = nr;   // single rank: exact; multi-rank: summed over ranks by the exchange that follows
     a.leaves[sp.leaf] = L; a.leaves[sp.right_leaf] = R;
     HistTask t;

@@ -94,7 +94,7 @@ __device__ void ScanCategoricalWarp(const FindArgs& a, const BinSrc& src, char* 
   __syncwarp();
   LeafScanInfo L;
   L.sum_g = leaf.sum_g; L.sum_h = leaf.sum_h; L.sum_gi = leaf.sum_gi; L.sum_hi = leaf.sum_hi; L.num_data = leaf.num_data_global;
-  L.parent_output = leaf.output; L.g_scale = g_scale; L.h_scale = h_scale;
+  L.parent_output = leaf.output; L.g_scale = g_scale; L.h_scale = h_scale; L.min_c = leaf.min_c; L.max_c = leaf.max_c;
   L.cnt_factor = FB_DIV(static_cast<double>(L.num_data), L.sum_h);
   if (a.params.max_delta_step <= 0.0 && a.params.path_smooth <= 0.0)
     L.min_gain_shift = FB_ADD(LeafGain(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), a.params, L.num_data, leaf.output), a.params.min_gain_to_split);
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
 
   LeafScanInfo L;
   L.sum_g = leaf.sum_g; L.sum_h = leaf.sum_h; L.sum_gi = leaf.sum_gi; L.sum_hi = leaf.sum_hi; L.num_data = leaf.num_data_global;
-  L.parent_output = leaf.output; L.g_scale = QUANT ? static_cast<double>(a.scales[0]) : 1.0; L.h_scale = QUANT ? static_cast<double>(a.scales[1]) : 1.0;
+  L.parent_output = leaf.output; L.g_scale = QUANT ? static_cast<double>(a.scales[0]) : 1.0; L.h_scale = QUANT ? static_cast<double>(a.scales[1]) : 1.0; L.min_c = leaf.min_c; L.max_c = leaf.max_c;
   L.cnt_factor = FB_DIV(static_cast<double>(L.num_data), L.sum_h);
   if (a.params.max_delta_step <= 0.0 && a.params.path_smooth <= 0.0)
     L.min_gain_shift = FB_ADD(LeafGain(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), a.params, L.num_data, leaf.output), a.params.min_gain_to_split);
@@ -370,6 +370,7 @@ __global__ void ReduceBestKernel(FindArgs a) {
       SplitParams p = a.params; if (c.is_categorical) p.lambda_l2 = FB_ADD(p.lambda_l2, a.params.cat_l2);
       r.left_out = LeafOutput(r.left_g, FB_ADD(r.left_h, kEpsilon), p, r.left_cnt, leaf.output);
       r.right_out = LeafOutput(r.right_g, FB_ADD(r.right_h, kEpsilon), p, r.right_cnt, leaf.output);
+      if (p.use_mc != 0) { r.left_out = ClampOutput(r.left_out, leaf.min_c, leaf.max_c); r.right_out = ClampOutput(r.right_out, leaf.min_c, leaf.max_c); }
     }
     if (gather) { s_rec = r; a.leaves_rw[ch.leaf].num_data_global = leaf.num_data_global; }
     else a.best[ch.leaf] = r;

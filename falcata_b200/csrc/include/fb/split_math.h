@@ -34,6 +34,7 @@ struct SplitParams {
   int max_cat_threshold, max_cat_to_onehot, min_data_per_group;
   double cat_l2, cat_smooth;
   int extra_trees;
+  int use_mc;   // some feature carries a monotone constraint: leaf outputs are clamped to the leaf's [min, max] range
 };
 
 // Fixed-size record of the best split of one leaf (or one (leaf, feature) task). POD: it is
@@ -104,16 +105,21 @@ FB_HD inline double LeafGain(double g, double h, const SplitParams& p, int num_d
   return LeafGainGivenOutput(g, h, p, LeafOutput(g, h, p, num_data, parent_output));
 }
 
+FB_HD inline double ClampOutput(double out, double lo, double hi) { return out < lo ? lo : (out > hi ? hi : out); }
+
 // Gain of a (left, right) pair; returns false when a monotone constraint is violated.
+// With use_mc the outputs are clamped to the leaf's range [min_c, max_c] (inherited from monotone splits above,
+// "basic" method) and the gain is evaluated at the clamped outputs.
 FB_HD inline bool SplitGain(double lg, double lh, double rg, double rh, const SplitParams& p, int lcnt, int rcnt,
-                            double parent_output, int monotone, double* gain, double* lout, double* rout) {
-  // the leaf outputs enter the gain only with max_delta_step / path_smooth and the monotone check; otherwise they are
-  // left unset here (0) and the caller computes them once, for the winning candidate, with the same LeafOutput call
-  const bool plain = p.max_delta_step <= 0.0 && p.path_smooth <= 0.0;
+                            double parent_output, int monotone, double min_c, double max_c, double* gain, double* lout, double* rout) {
+  // the leaf outputs enter the gain only with max_delta_step / path_smooth and the monotone constraints; otherwise they
+  // are left unset here (0) and the caller computes them once, for the winning candidate, with the same LeafOutput call
+  const bool plain = p.max_delta_step <= 0.0 && p.path_smooth <= 0.0 && p.use_mc == 0;
   if (plain && monotone == 0) { *lout = 0.0; *rout = 0.0; }
   else {
     *lout = LeafOutput(lg, lh, p, lcnt, parent_output);
     *rout = LeafOutput(rg, rh, p, rcnt, parent_output);
+    if (p.use_mc != 0) { *lout = ClampOutput(*lout, min_c, max_c); *rout = ClampOutput(*rout, min_c, max_c); }
     if ((monotone > 0 && *lout > *rout) || (monotone < 0 && *lout < *rout)) { *gain = 0.0; return false; }
   }
   if (plain) {
@@ -133,7 +139,14 @@ struct LeafScanInfo {
   double min_gain_shift;      // LeafGain(parent) + min_gain_to_split
   double cnt_factor;          // num_data / sum_h
   double g_scale, h_scale;    // quantized: real = int * scale; else 1
+  double min_c, max_c;        // monotone range of the leaf's output (-inf, +inf when unconstrained)
 };
+
+// Output of a child of leaf L: the regularised output, clamped to the leaf's monotone range when constraints are on.
+FB_HD inline double ChildOutput(double g, double h, const SplitParams& p, int num_data, const LeafScanInfo& L) {
+  const double out = LeafOutput(g, h, p, num_data, L.parent_output);
+  return p.use_mc != 0 ? ClampOutput(out, L.min_c, L.max_c) : out;
+}
 
 // Rounded row-count estimate of one bin from its hessian mass.
 FB_HD inline int BinCountEstimate(double h, double cnt_factor) { return static_cast<int>(FB_ADD(FB_MUL(h, cnt_factor), 0.5)); }
@@ -148,7 +161,7 @@ FB_HD inline double EvalCandidate(double lg, double lh, int lcnt, const LeafScan
   if (lcnt < p.min_data_in_leaf || rcnt < p.min_data_in_leaf) return ninf;
   if (lh < p.min_sum_hessian_in_leaf || rh < p.min_sum_hessian_in_leaf) return ninf;
   double gain;
-  if (!SplitGain(lg, FB_ADD(lh, kEpsilon), rg, FB_ADD(rh, kEpsilon), p, lcnt, rcnt, L.parent_output, monotone, &gain, lout, rout)) return ninf;
+  if (!SplitGain(lg, FB_ADD(lh, kEpsilon), rg, FB_ADD(rh, kEpsilon), p, lcnt, rcnt, L.parent_output, monotone, L.min_c, L.max_c, &gain, lout, rout)) return ninf;
   if (!(gain > L.min_gain_shift)) return ninf;
   return FB_SUB(gain, L.min_gain_shift);
 }

@@ -135,3 +135,36 @@ def test_linear_tree_fits_piecewise_linear_target(tmp_path):
             b.save_model(str(path))
             assert np.array_equal(fb.Booster(model_file=str(path)).predict(Xv), pr)
     assert mse[True] < 0.3 * mse[False]
+
+
+def _monotone_violations(bst, ncol, col, sign, rng, predict=None):
+    """Largest decrease (increase for sign < 0) of the prediction along `col` with the other columns fixed."""
+    base = rng.normal(size=(200, ncol)).astype(np.float32)
+    grid = np.linspace(-3, 3, 41, dtype=np.float32)
+    worst = 0.0
+    prev = None
+    for g in grid:
+        A = base.copy()
+        A[:, col] = g
+        p = np.asarray((predict or bst.predict)(A), dtype=np.float64)
+        if prev is not None:
+            worst = max(worst, float(np.max(sign * (prev - p))))
+        prev = p
+    return worst
+
+
+def test_monotone_constraints_hold_over_the_whole_tree():
+    """A constrained feature's effect is monotone in every tree: each split orders its children and the
+    children's output ranges are inherited by the whole subtree."""
+    rng = np.random.default_rng(3)
+    n = 6000
+    X = rng.normal(size=(n, 4)).astype(np.float32)
+    y = (np.sin(2 * X[:, 0]) + 0.5 * X[:, 0] - np.cos(2 * X[:, 1]) - 0.3 * X[:, 1] + X[:, 2] * X[:, 0] * 0.5
+         + 0.1 * rng.normal(size=n)).astype(np.float32)
+    p = {"objective": "regression", "num_leaves": 31, "learning_rate": 0.2, "verbose": -1, "min_data_in_leaf": 10,
+         "monotone_constraints": [1, -1, 0, 0]}
+    b = fb.train(p, fb.Dataset(X, y), 30)
+    assert _monotone_violations(b, 4, 0, +1, rng) <= 1e-10
+    assert _monotone_violations(b, 4, 1, -1, rng) <= 1e-10
+    free = fb.train({**p, "monotone_constraints": [0, 0, 0, 0]}, fb.Dataset(X, y), 30)
+    assert _monotone_violations(free, 4, 0, +1, rng) > 1e-3   # the target itself is not monotone

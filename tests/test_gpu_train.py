@@ -315,3 +315,34 @@ def test_bundled_sparse_features_match_host():
     assert model_body(sc).split("Tree=1")[0] == model_body(sg).split("Tree=1")[0]
     used = {int(t) for line in sg.splitlines() if line.startswith("split_feature=") for t in line.split("=")[1].split()}
     assert any(f >= 4 for f in used)      # bundled features are split on
+
+
+def test_monotone_constraints_on_device():
+    # every split orders its children and the device controller hands the output ranges down the subtree,
+    # so the prediction is monotone in a constrained feature whatever the other features are
+    rng = np.random.default_rng(3)
+    n = 20000
+    X = rng.normal(size=(n, 4)).astype(np.float32)
+    y = (np.sin(2 * X[:, 0]) + 0.5 * X[:, 0] - np.cos(2 * X[:, 1]) - 0.3 * X[:, 1] + X[:, 2] * X[:, 0] * 0.5
+         + 0.1 * rng.normal(size=n)).astype(np.float32)
+    p = {"objective": "regression", "num_leaves": 31, "learning_rate": 0.2, "verbosity": -1, "min_data_in_leaf": 10,
+         "monotone_constraints": [1, -1, 0, 0], "device_type": "cuda"}
+    b = fb.train(p, fb.Dataset(torch.as_tensor(X, device="cuda"), y), 30)
+
+    def worst(bst, col, sign):
+        base = rng.normal(size=(200, 4)).astype(np.float32)
+        prev, w = None, 0.0
+        for g in np.linspace(-3, 3, 41, dtype=np.float32):
+            A = base.copy()
+            A[:, col] = g
+            pr = bst.predict(A).astype(np.float64)
+            if prev is not None:
+                w = max(w, float(np.max(sign * (prev - pr))))
+            prev = pr
+        return w
+
+    assert worst(b, 0, +1) <= 1e-10 and worst(b, 1, -1) <= 1e-10
+    free = fb.train({**p, "monotone_constraints": [0, 0, 0, 0]}, fb.Dataset(torch.as_tensor(X, device="cuda"), y), 30)
+    assert worst(free, 0, +1) > 1e-3
+    mse_c = float(np.mean((b.predict(X) - y) ** 2))
+    assert mse_c < 0.6 * float(np.var(y))   # the constrained model still learns
