@@ -30,6 +30,7 @@ void ColSampler::Init(const Config& cfg, const Dataset* ds) {
   frac_bytree_ = cfg.feature_fraction; frac_bynode_ = cfg.feature_fraction_bynode; seed_ = cfg.feature_fraction_seed;
   nfeat_ = ds->num_features; used_.assign(nfeat_, 1); num_used_ = nfeat_;
   interaction_sets_.clear();
+  real_index_.assign(nfeat_, 0); for (int f = 0; f < nfeat_; ++f) real_index_[f] = ds->feature_meta[f].real_index;
   if (!cfg.interaction_constraints.empty()) {
     // "[0,1,2],[2,3]" over real feature indices
     std::string s = cfg.interaction_constraints; std::vector<int> cur; std::string num; bool in = false;
@@ -63,9 +64,24 @@ void ColSampler::ResetByTree(int tree_index) {
   num_used_ = 0; for (auto u : used_) num_used_ += u;
 }
 
-std::vector<int8_t> ColSampler::SampleByNode(int tree_index, int node_id) const {
-  if (frac_bynode_ >= 1.0) return used_;
-  return SampleFeatures(nfeat_, frac_bynode_, static_cast<uint32_t>(seed_), static_cast<uint32_t>(tree_index), static_cast<uint32_t>(node_id) + 1u, &used_);
+// Parity: src/treelearner/col_sampler.hpp (GetByNode: a constraint set applies when it holds every feature of the
+// branch; the allowed features are the union of the applying sets; the per-node sample is drawn inside them).
+std::vector<int8_t> ColSampler::SampleByNode(int tree_index, int node_id, const std::vector<int>* path_real) const {
+  std::vector<int8_t> within = used_;
+  if (!interaction_sets_.empty()) {
+    std::vector<int8_t> allowed_real;
+    for (const auto& set : interaction_sets_) {
+      bool applies = true;
+      if (path_real != nullptr) for (int pf : *path_real) if (std::find(set.begin(), set.end(), pf) == set.end()) { applies = false; break; }
+      if (!applies) continue;
+      for (int rf : set) { if (rf < 0) continue; if (static_cast<int>(allowed_real.size()) <= rf) allowed_real.resize(rf + 1, 0); allowed_real[rf] = 1; }
+    }
+    for (int f = 0; f < nfeat_; ++f) { const int rf = real_index_[f]; if (rf >= static_cast<int>(allowed_real.size()) || !allowed_real[rf]) within[f] = 0; }
+  }
+  if (frac_bynode_ >= 1.0) return within;
+  bool any = false; for (auto u : within) any = any || u;
+  if (!any) return within;
+  return SampleFeatures(nfeat_, frac_bynode_, static_cast<uint32_t>(seed_), static_cast<uint32_t>(tree_index), static_cast<uint32_t>(node_id) + 1u, &within);
 }
 
 // ----------------------------------------------------------- CPU learner ----
@@ -78,6 +94,7 @@ struct LeafState {
   int64_t global_count = 0;          // rows of the leaf over all ranks
   double output = 0;
   int depth = 0;
+  std::vector<int> path;             // real features split on above this leaf (interaction constraints)
   SplitRecord best;
   std::vector<double> hist;          // 2 * num_total_bin (g, h) real-valued, or
   std::vector<int64_t> hist_i;       // 2 * num_total_bin integer sums when quantized
@@ -408,7 +425,7 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
   L.min_gain_shift = FB_ADD(LeafGainGivenOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, leaf->output), sp_.min_gain_to_split);
   if (sp_.max_delta_step <= 0.0 && sp_.path_smooth <= 0.0)
     L.min_gain_shift = FB_ADD(LeafGain(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, L.num_data, leaf->output), sp_.min_gain_to_split);
-  const std::vector<int8_t> mask = col_sampler_.by_node() ? col_sampler_.SampleByNode(tree_index, leaf_id + 1000003 * leaf->depth) : col_sampler_.used_by_tree();
+  const std::vector<int8_t> mask = col_sampler_.by_node() ? col_sampler_.SampleByNode(tree_index, leaf_id + 1000003 * leaf->depth, &leaf->path) : col_sampler_.used_by_tree();
 
   if (parallel_voting_) {
     // PV-Tree: local top-k by local gain, global vote, reduce only the voted features.
@@ -542,6 +559,7 @@ int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
   R = LeafState();
   R.begin = Lf.begin + nl; R.count = nr; Lf.count = nl;
   R.depth = Lf.depth + 1; Lf.depth += 1;
+  { const int rf = ds_->feature_meta[s.feature].real_index; if (std::find(Lf.path.begin(), Lf.path.end(), rf) == Lf.path.end()) Lf.path.push_back(rf); R.path = Lf.path; }
   R.sum_g = s.right_g; R.sum_h = s.right_h; R.sum_gi = Lf.sum_gi - s.left_gi; R.sum_hi = Lf.sum_hi - s.left_hi;
   Lf.sum_g = s.left_g; Lf.sum_h = s.left_h; Lf.sum_gi = s.left_gi; Lf.sum_hi = s.left_hi;
   R.output = s.right_out; Lf.output = s.left_out;

@@ -126,6 +126,21 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     ctrl_.Alloc(1); frontier_.Alloc(NL + 2); journal_.Alloc(NL); h_ctrl_.Alloc(1); h_journal_.Alloc(NL); h_root_.Alloc(1);
     levels_hint_ = 1; while ((1 << levels_hint_) < NL) ++levels_hint_;
   }
+  node_mask_on_ = col_sampler_.by_node();
+  if (node_mask_on_) {
+    if (!use_ctrl_) Log::Fatal("feature_fraction_bynode / interaction_constraints on the device need the device level controller (num_leaves <= 1024)");
+    if (cfg.tree_learner == "voting" && world_ > 1) Log::Fatal("feature_fraction_bynode / interaction_constraints are not built for the device voting learner");
+    node_mask_.Alloc(static_cast<size_t>(2 * (NL / 2 + 1)) * std::max(1, train->num_features));
+    const auto& sets = col_sampler_.interaction_sets();
+    num_sets_ = static_cast<int>(sets.size());
+    if (num_sets_ > 0) {
+      path_words_ = (train->num_total_features + 31) / 32;
+      std::vector<unsigned int> bits(static_cast<size_t>(num_sets_) * path_words_, 0u);
+      for (int s = 0; s < num_sets_; ++s) for (int rf : sets[s]) if (rf >= 0 && rf < train->num_total_features) bits[static_cast<size_t>(s) * path_words_ + (rf >> 5)] |= 1u << (rf & 31);
+      set_bits_.Upload(bits, stream_);
+      path_bits_.Alloc(static_cast<size_t>(NL) * path_words_);
+    }
+  }
   BuildPartitions();
   SetupOwnership();
   if (feature_parallel_) {

@@ -115,6 +115,9 @@ class CudaEngine : public DeviceEngine {
   DevBuf<HistTask> hist_tasks_; DevBuf<unsigned int> hist_status_; PinnedBuf<unsigned int> h_hist_status_;
   DevBuf<unsigned int> bits_; DevBuf<int> chunk_left_, split_left_total_;
   DevBuf<int> features_, sub_features_;
+  // per-node feature masks (feature_fraction_bynode, interaction constraints)
+  bool node_mask_on_ = false; int path_words_ = 0, num_sets_ = 0;
+  DevBuf<unsigned char> node_mask_; DevBuf<unsigned int> path_bits_, set_bits_; DevBuf<int> mask_pool_;
   DevBuf<double> leaf_value_, renew_partial_; PinnedBuf<double> h_renew_partial_;
   PinnedBuf<LeafInfo> h_leaves_; PinnedBuf<SplitRecord> h_best_;
   std::vector<HostLeaf> host_leaves_;

@@ -247,6 +247,19 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
       fa.stage = fabric_->Local<char>(off_stage_); fa.stage_cap = NL;
     }
   }
+  NodeMaskArgs nm = NodeMaskArgs();
+  if (node_mask_on_) {
+    std::vector<int> pool;
+    for (int f = 0; f < train_->num_features; ++f) if (col_sampler_.used_by_tree()[f]) pool.push_back(f);
+    mask_pool_.Upload(pool, stream_);
+    if (num_sets_ > 0) path_bits_.Zero(stream_);
+    nm.leaves = leaves_.get(); nm.meta = dd_->feature_meta.get(); nm.num_inner = train_->num_features;
+    nm.pool = mask_pool_.get(); nm.pool_size = static_cast<int>(pool.size());
+    nm.fraction = col_sampler_.bynode_fraction(); nm.seed = static_cast<unsigned int>(col_sampler_.seed()); nm.tree_index = tree_index;
+    nm.path_bits = num_sets_ > 0 ? path_bits_.get() : nullptr; nm.set_bits = num_sets_ > 0 ? set_bits_.get() : nullptr; nm.num_sets = num_sets_; nm.words = path_words_;
+    nm.mask = node_mask_.get();
+    fa.node_mask = node_mask_.get(); fa.node_mask_stride = train_->num_features;
+  }
   VoteArgs va = VoteArgs(); FindArgs fl = fa;
   if (voting_) {
     const FabricView v = fabric_->View();
@@ -289,6 +302,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     clock_.End(stream_);
     if (world_ > 1) { fa.sig.epoch = fabric_->NextEpoch(); fa.wait_best.epoch = fa.sig.epoch; }
     clock_.Begin(st_find_, stream_);
+    if (node_mask_on_) { nm.children = fa.children; nm.num_children = fa.num_children; nm.ctrl = fa.ctrl; LaunchNodeMask(nm, stream_); }
     LaunchFindSplits(fa, stream_); LaunchReduceBest(fa, stream_); LaunchGatherBest(fa, stream_);
     clock_.End(stream_);
   };
@@ -331,6 +345,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     fa.ctrl = ctrl_.get(); fa.children = ca.children; fa.num_children = 2 * max_splits;
     auto enqueue_level = [&]() {
       LaunchLevelController(ca, stream_);
+      if (num_sets_ > 0) LaunchPathBits(ctrl_.get(), journal_.get(), dd_->feature_meta.get(), path_bits_.get(), path_words_, max_splits, stream_);
       if (feature_parallel_) { pa.bc_sig.epoch = fabric_->NextEpoch(); pa.bc_wait.epoch = pa.bc_sig.epoch; }
       clock_.Begin(st_part_, stream_);
       LaunchPartitionFlags(pa, stream_); LaunchPartitionScanSetup(pa, stream_); LaunchPartitionScatter(pa, stream_);

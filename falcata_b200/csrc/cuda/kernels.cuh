@@ -114,6 +114,7 @@ struct FindArgs {
   int quant;
   int tree_index; unsigned int extra_seed;        // extra_trees: key of the per-(tree, leaf, feature) threshold draw
   int has_categorical;                            // some searched feature is categorical: the kernel gets its shared scratch
+  const unsigned char* node_mask; int node_mask_stride;   // non-null: [child][inner feature], 0 = not searched at this node
   // ---- voting-parallel (see VoteArgs) ----
   int local_vote;                                 // 1: local pass - leaf totals and count are this rank's (vote_sums, LeafInfo.count)
   const struct VoteLocalSum* vote_sums;           // [child] local totals of the child's histogram
@@ -141,6 +142,21 @@ struct CtrlArgs {
   const unsigned char* bin_owner;   // feature-parallel: owner rank of every histogram bin (null otherwise)
 };
 void LaunchLevelController(const CtrlArgs& a, cudaStream_t s);
+
+// Per-node feature masks (feature_fraction_bynode, interaction constraints): mask[child][inner feature] = 1 when
+// the child's split search may use the feature.
+struct NodeMaskArgs {
+  const FindChild* children; int num_children; const LevelCtrl* ctrl;
+  const LeafInfo* leaves; const FeatureMeta* meta;
+  int num_inner;                               // row length of the mask
+  const int* pool; int pool_size;              // inner features sampled for this tree, ascending
+  double fraction; unsigned int seed; int tree_index;   // per-node sample: round(fraction * allowed) features, >= 1
+  const unsigned int* path_bits;               // [leaf][words] real features split on above the leaf
+  const unsigned int* set_bits; int num_sets; int words;   // interaction sets as bitsets over real features
+  unsigned char* mask;
+};
+void LaunchNodeMask(const NodeMaskArgs& a, cudaStream_t s);
+void LaunchPathBits(const LevelCtrl* ctrl, const SplitJournal* journal, const FeatureMeta* meta, unsigned int* path_bits, int words, int max_splits, cudaStream_t s);
 
 // ----------------------------------------------------------------- voting ----
 // Voting-parallel (PV-Tree) on the device, rows sharded over ranks. Histograms stay LOCAL (all features,

@@ -213,11 +213,17 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
     return;
   }
 
-  if (search && m.bin_type != 0) {
+  const bool node_masked = search && a.node_mask != nullptr && a.node_mask[static_cast<size_t>(blockIdx.x) * a.node_mask_stride + f] == 0;
+  if (node_masked && lane == 0) {
+    CandLite c; c.gain = -1.0 / 0.0; c.feature = -1; c.threshold = 0; c.default_left = 1; c.left_cnt = 0; c.left_gi = c.left_hi = 0; c.left_g = c.left_h = 0;
+    c.is_categorical = 0; c.num_cat_bins = 0; for (int w = 0; w < 8; ++w) c.cat_bitset[w] = 0;
+    a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + fi] = c;
+  }
+  if (search && !node_masked && m.bin_type != 0) {
     ScanCategoricalWarp<QUANT>(a, src, child, write_back, m, leaf, f, fi, lane, warp);
     return;
   }
-  if (!search) {
+  if (!search || node_masked) {
     // materialisation only (feature not sampled for this tree)
     if (write_back) for (int j = lane; j < nstored; j += 32) {
       long long gi, hi; double gd, hd; hist_q_t rq; double2 rd;

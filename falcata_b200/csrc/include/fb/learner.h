@@ -43,14 +43,20 @@ class ColSampler {
   void Init(const Config& cfg, const Dataset* ds);
   void ResetByTree(int tree_index);
   const std::vector<int8_t>& used_by_tree() const { return used_; }
-  std::vector<int8_t> SampleByNode(int tree_index, int node_id) const;
-  bool by_node() const { return frac_bynode_ < 1.0; }
+  // Features a node may search: the tree's sample, restricted to the interaction sets that contain every feature
+  // already used on the node's path (real feature indices), then sampled per node when feature_fraction_bynode < 1.
+  std::vector<int8_t> SampleByNode(int tree_index, int node_id, const std::vector<int>* path_real = nullptr) const;
+  bool by_node() const { return frac_bynode_ < 1.0 || !interaction_sets_.empty(); }
+  double bynode_fraction() const { return frac_bynode_; }
+  int seed() const { return seed_; }
+  const std::vector<std::vector<int>>& interaction_sets() const { return interaction_sets_; }
   int num_used() const { return num_used_; }
  private:
   double frac_bytree_ = 1.0, frac_bynode_ = 1.0;
   int seed_ = 0, nfeat_ = 0, num_used_ = 0;
   std::vector<int8_t> used_;
   std::vector<std::vector<int>> interaction_sets_;
+  std::vector<int> real_index_;   // inner feature -> real feature
 };
 
 // Quantization scales of one tree and the packed per-row words.

@@ -168,3 +168,40 @@ def test_monotone_constraints_hold_over_the_whole_tree():
     assert _monotone_violations(b, 4, 1, -1, rng) <= 1e-10
     free = fb.train({**p, "monotone_constraints": [0, 0, 0, 0]}, fb.Dataset(X, y), 30)
     assert _monotone_violations(free, 4, 0, +1, rng) > 1e-3   # the target itself is not monotone
+
+
+def _branch_feature_sets(bst):
+    """Feature set of every root-to-leaf path of every tree."""
+    out = []
+
+    def walk(node, feats):
+        if "split_feature" not in node:
+            out.append(frozenset(feats))
+            return
+        f = feats | {int(node["split_feature"])}
+        walk(node["left_child"], f)
+        walk(node["right_child"], f)
+
+    for t in bst.dump_model()["tree_info"]:
+        walk(t["tree_structure"], frozenset())
+    return out
+
+
+def test_interaction_constraints_and_bynode_sampling():
+    rng = np.random.default_rng(5)
+    n = 5000
+    X = rng.normal(size=(n, 6)).astype(np.float32)
+    y = (X[:, 0] * X[:, 1] + X[:, 2] * X[:, 3] + X[:, 4] + 0.1 * rng.normal(size=n)).astype(np.float32)
+    p = {"objective": "regression", "num_leaves": 15, "verbose": -1, "min_data_in_leaf": 10,
+         "interaction_constraints": "[0,1],[2,3,4]"}
+    b = fb.train(p, fb.Dataset(X, y), 10)
+    sets = _branch_feature_sets(b)
+    assert len(sets) > 20
+    for s in sets:
+        assert s <= {0, 1} or s <= {2, 3, 4}, s      # feature 5 is in no set: never used
+    # per-node sampling: still learns, and differs from the unsampled model
+    q = {"objective": "regression", "num_leaves": 15, "verbose": -1, "min_data_in_leaf": 10, "feature_fraction_bynode": 0.5}
+    b2 = fb.train(q, fb.Dataset(X, y), 10)
+    b3 = fb.train({**q, "feature_fraction_bynode": 1.0}, fb.Dataset(X, y), 10)
+    assert b2.model_to_string() != b3.model_to_string()
+    assert float(np.mean((b2.predict(X) - y) ** 2)) < 0.7 * float(np.var(y))

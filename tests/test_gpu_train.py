@@ -346,3 +346,28 @@ def test_monotone_constraints_on_device():
     assert worst(free, 0, +1) > 1e-3
     mse_c = float(np.mean((b.predict(X) - y) ** 2))
     assert mse_c < 0.6 * float(np.var(y))   # the constrained model still learns
+
+
+@pytest.mark.parametrize("case", ["bynode", "interaction", "both"])
+def test_per_node_feature_masks_on_device_match_host(case):
+    # the device draws the host learner's per-node sample (same Philox keys, same k) and applies the same
+    # interaction sets, so with identical gradients the first tree is the host's tree
+    X, y = make_regression(20000, 12)
+    y = np.round(y * 8) / 8
+    base = {"objective": "none", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "grow_policy": "level", "min_data_in_leaf": 20, "seed": 3}
+    if case in ("bynode", "both"):
+        base["feature_fraction_bynode"] = 0.5
+    if case in ("interaction", "both"):
+        base["interaction_constraints"] = "[0,1,2,3],[3,4,5,6,7],[8,9,10]"
+    else:
+        base["quant_mode"] = "stochastic"
+    bc = fb.train({**base, "device_type": "cpu"}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
+    bg = fb.train({**base, "device_type": "cuda"}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
+    assert bc.num_trees() == 1 and "num_leaves=31" in bc.model_to_string()
+    if "quant_mode" in base:
+        assert model_body(bc.model_to_string()) == model_body(bg.model_to_string())
+    else:
+        # float histograms: sums differ in the last digits between host and device, the structure must not
+        def structure(m):
+            return [ln for ln in m.model_to_string().splitlines() if ln.startswith(("split_feature=", "threshold=", "left_child=", "right_child="))]
+        assert structure(bc) == structure(bg)
