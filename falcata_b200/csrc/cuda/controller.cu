@@ -19,7 +19,7 @@ constexpr int kCtrlMaxLeaves = 1024;
 
 __global__ void InitLevelCtrlKernel(LevelCtrl* c, int* frontier) {
   c->num_leaves = 1; c->next_slot = 1; c->done = 0; c->level = 0; c->num_splits = 0; c->num_children = 1; c->total_chunks = 0; c->total_blocks = 0;
-  c->frontier_count = 1; c->journal_count = 0; c->pad0 = 0; c->skip_search = 0;
+  c->frontier_count = 1; c->journal_count = 0; c->pad0 = 0; c->skip_search = 0; c->num_eval = 0; c->pad1 = 0;
   frontier[0] = 0;
 }
 
@@ -42,6 +42,34 @@ __global__ void __launch_bounds__(kCtrlThreads) LevelControllerKernel(CtrlArgs a
   __syncthreads();
   const int ncand = s_ncand;
   const int budget = a.max_leaves - c->num_leaves;
+  if (a.leafwise_budget > 0) {
+    // 2'. leaf-wise: record the order keys of the newly evaluated nodes, then keep the candidates with fewer than
+    //     leafwise_budget evaluated nodes strictly before them; if the growth cap binds, the best of those by rank
+    const int base_eval = c->num_eval;
+    for (int i = threadIdx.x; i < ncand; i += kCtrlThreads) {
+      const int li = s_leaf[i];
+      LeafwiseChildKey(a.leaves[li].pkey, a.best[li].gain, a.eval_key + static_cast<size_t>(base_eval + i) * 4);
+    }
+    __syncthreads();
+    const int total = base_eval + ncand;
+    for (int i = threadIdx.x; i < ncand; i += kCtrlThreads) {
+      double ki[4]; for (int k = 0; k < 4; ++k) ki[k] = a.eval_key[static_cast<size_t>(base_eval + i) * 4 + k];
+      int rank = 0;
+      for (int j = 0; j < total; ++j) rank += LeafwiseKeyBefore(a.eval_key + static_cast<size_t>(j) * 4, ki) ? 1 : 0;
+      s_order[i] = rank < a.leafwise_budget ? rank : 0x7fffffff;
+    }
+    __syncthreads();
+    unsigned int keep_bits = 0;   // this thread's decisions, one bit per stride step (written back after all ranks were read)
+    for (int i = threadIdx.x, step = 0; i < ncand; i += kCtrlThreads, ++step) {
+      const int ri = s_order[i];
+      bool keep = ri != 0x7fffffff;
+      if (keep) { int better = 0; for (int j = 0; j < ncand; ++j) better += (s_order[j] < ri) || (s_order[j] == ri && s_leaf[j] < s_leaf[i]); keep = better < budget; }
+      if (keep) keep_bits |= 1u << step;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x, step = 0; i < ncand; i += kCtrlThreads, ++step) s_order[i] = (keep_bits >> step) & 1u;
+    if (threadIdx.x == 0) c->num_eval = total;
+  } else {
   // 2. rank by (gain desc, leaf asc) when the budget binds; 3. order the kept ones by leaf id
   for (int i = threadIdx.x; i < ncand; i += kCtrlThreads) {
     const int li = s_leaf[i]; const double gi = a.best[li].gain;
@@ -52,6 +80,7 @@ __global__ void __launch_bounds__(kCtrlThreads) LevelControllerKernel(CtrlArgs a
       keep = better < budget;
     }
     s_order[i] = keep ? 1 : 0;
+  }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < ncand; i += kCtrlThreads) {
@@ -101,13 +130,14 @@ __global__ void __launch_bounds__(kCtrlThreads) LevelControllerKernel(CtrlArgs a
     ci.left_g = b.left_g; ci.left_h = b.left_h; ci.right_g = b.right_g; ci.right_h = b.right_h; ci.left_out = b.left_out; ci.right_out = b.right_out;
     ci.left_gi = b.left_gi; ci.left_hi = b.left_hi; ci.right_gi = P.sum_gi - b.left_gi; ci.right_hi = P.sum_hi - b.left_hi;
     ci.hist_block_begin = s_blocks[s]; ci.hist_num_blocks = s_blocks[s + 1] - s_blocks[s];
-    ci.monotone = b.monotone; ci.pad_ = 0;
+    ci.monotone = b.monotone; ci.pad_ = 0; LeafwiseChildKey(P.pkey, b.gain, ci.pkey);
     a.child_init[s] = ci;
     FindChild fl, fr;
     fl.leaf = l; fl.slot = ci.left_slot; fl.other_slot = ci.right_slot; fl.is_larger = ci.smaller_is_left ? 0 : 1; fl.split = s; fl.is_left = 1; fl.parent_global = P.num_data_global; fl.task = s;
     fr.leaf = right; fr.slot = ci.right_slot; fr.other_slot = ci.left_slot; fr.is_larger = ci.smaller_is_left ? 1 : 0; fr.split = s; fr.is_left = 0; fr.parent_global = P.num_data_global; fr.task = s;
     a.children[2 * s] = fl; a.children[2 * s + 1] = fr;
     SplitJournal j; j.leaf = l; j.right_leaf = right; j.parent_global = P.num_data_global; j.pad = 0; j.rec = b;
+    j.begin = P.begin; j.count = P.count; j.buffer = P.buffer; j.depth = P.depth;
     a.journal[base_journal + s] = j;
   }
   __syncthreads();

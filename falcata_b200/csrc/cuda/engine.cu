@@ -65,7 +65,6 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   sp_.max_depth = cfg.max_depth; sp_.max_cat_threshold = cfg.max_cat_threshold; sp_.max_cat_to_onehot = cfg.max_cat_to_onehot;
   sp_.min_data_per_group = cfg.min_data_per_group; sp_.cat_l2 = cfg.cat_l2; sp_.cat_smooth = cfg.cat_smooth; sp_.extra_trees = cfg.extra_trees ? 1 : 0;
   sp_.use_mc = 0; for (const auto& m : train->feature_meta) if (m.monotone != 0) sp_.use_mc = 1;
-  if (cfg.grow_policy == "leaf") Log::Warning("grow_policy=leaf runs on the host learner; the device learner grows level-wise with a gain-ranked leaf budget");
   col_sampler_.Init(cfg, train);
   clock_.enabled = getenv("FALCATA_STAGE_TIMING") != nullptr;
   clock_.nvtx = getenv("FALCATA_NVTX") != nullptr;
@@ -118,7 +117,13 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     if (plan_.col_major_part) EnsureColumnMajor(dd_, stream_);
   }
   idx_[0].Alloc(n_); idx_[1].Alloc(n_);
-  const int NL = cfg.num_leaves;
+  leafwise_ = cfg.grow_policy == "leaf" && plan_.device_controller && cfg.num_leaves <= 512 && !voting_ && !feature_parallel_;
+  if (cfg.grow_policy == "leaf" && !leafwise_)
+    Log::Warning("grow_policy=leaf on the device needs the level controller, num_leaves <= 512 and tree_learner serial or data; growing level-wise with a gain-ranked leaf budget");
+  // leaf-wise: the device may grow past the budget (nodes that looked good enough when they were split); the cap bounds every buffer
+  grow_leaves_ = leafwise_ ? std::min(1024, 4 * cfg.num_leaves) : cfg.num_leaves;
+  const int NL = grow_leaves_;
+  if (leafwise_) eval_key_.Alloc(4 * (2 * static_cast<size_t>(NL) + 2));
   leaves_.Alloc(NL); best_.Alloc(NL); h_leaves_.Alloc(NL); h_best_.Alloc(NL); leaf_value_.Alloc(NL);
   host_leaves_.resize(NL);
   use_ctrl_ = plan_.device_controller && NL <= 1024;

@@ -115,6 +115,10 @@ class CudaEngine : public DeviceEngine {
   DevBuf<HistTask> hist_tasks_; DevBuf<unsigned int> hist_status_; PinnedBuf<unsigned int> h_hist_status_;
   DevBuf<unsigned int> bits_; DevBuf<int> chunk_left_, split_left_total_;
   DevBuf<int> features_, sub_features_;
+  // exact leaf-wise growth (grow_policy=leaf): the device grows up to grow_leaves_ leaves, the host keeps the best num_leaves
+  bool leafwise_ = false; int grow_leaves_ = 0;
+  DevBuf<double> eval_key_;
+  void FinalizeLeafwise(const LevelCtrl& hc, Tree* tree);
   // per-node feature masks (feature_fraction_bynode, interaction constraints)
   bool node_mask_on_ = false; int path_words_ = 0, num_sets_ = 0;
   DevBuf<unsigned char> node_mask_; DevBuf<unsigned int> path_bits_, set_bits_; DevBuf<int> mask_pool_;

@@ -26,7 +26,7 @@ __global__ void InitRootKernel(LeafInfo* leaves, const long long* sums_i, const 
     L.sum_g = FB_MUL(static_cast<double>(L.sum_gi), static_cast<double>(scales[0])); L.sum_h = FB_MUL(static_cast<double>(L.sum_hi), static_cast<double>(scales[1]));
   } else { L.sum_gi = L.sum_hi = 0; L.sum_g = sums_d[0]; L.sum_h = sums_d[1]; }
   L.output = LeafOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp, L.num_data_global, 0.0);
-  L.min_c = -1.0 / 0.0; L.max_c = 1.0 / 0.0;
+  L.min_c = -1.0 / 0.0; L.max_c = 1.0 / 0.0; for (int k = 0; k < 4; ++k) L.pkey[k] = 1.0 / 0.0;
   leaves[0] = L;
 }
 
@@ -107,7 +107,7 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
     if (need && train_->num_features > 0) {
       cur_grad_ = grad + static_cast<size_t>(k) * n_; cur_hess_ = hess + static_cast<size_t>(k) * n_;
       cur_shrinkage_ = shrinkage; cur_score_ = score_.get() + static_cast<size_t>(k) * n_; score_done_ = false;
-      fast_score_ok_ = !bagging && !(quant_ && cfg_.quant_train_renew_leaf) && !(obj_ != nullptr && obj_->IsRenewTreeOutput());
+      fast_score_ok_ = !leafwise_ && !bagging && !(quant_ && cfg_.quant_train_renew_leaf) && !(obj_ != nullptr && obj_->IsRenewTreeOutput());
       tree.reset(TrainTree(k, iter * K_ + k));
     } else tree.reset(new Tree(2));
     if (tree->num_leaves > 1) {
@@ -142,7 +142,7 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
 }
 
 Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
-  const int NL = cfg_.num_leaves;
+  const int NL = grow_leaves_;   // leaf capacity of the device tree (= num_leaves unless leaf-wise growth over-grows)
   col_sampler_.ResetByTree(tree_index);
   // features searched on this rank this tree (owned, sampled, numerical) and the rest of the owned ones
   std::vector<int> feats, subs;
@@ -332,6 +332,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     ca.ctrl = ctrl_.get(); ca.frontier = frontier_.get(); ca.journal = journal_.get(); ca.leaves = leaves_.get(); ca.best = best_.get(); ca.meta = dd_->feature_meta.get();
     ca.splits = reinterpret_cast<PartSplit*>(db); ca.child_init = reinterpret_cast<ChildInit*>(db + sizeof(PartSplit) * NL);
     ca.children = reinterpret_cast<FindChild*>(db + (sizeof(PartSplit) + sizeof(ChildInit)) * NL);
+    ca.leafwise_budget = leafwise_ ? cfg_.num_leaves - 1 : 0; ca.eval_key = leafwise_ ? eval_key_.get() : nullptr;
     ca.max_leaves = NL; ca.rows_per_block = rpb; ca.bin_owner = feature_parallel_ ? bin_owner_.get() : nullptr;
     PartArgs pa = PartArgs();
     pa.rows = dd_->rows.get(); pa.row_stride = dd_->row_stride; pa.idx[0] = idx_[0].get(); pa.idx[1] = idx_[1].get();
@@ -386,6 +387,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
       leaves_.Download(h_leaves_.get(), hc.num_leaves, stream_);
       FB_CUDA(cudaStreamSynchronize(stream_));
     }
+    if (leafwise_ && hc.journal_count > 0) { FinalizeLeafwise(hc, tree.get()); return tree.release(); }
     if (hc.journal_count == 0) { const LeafInfo& R = *h_root_.get(); tree->leaf_value[0] = R.output; tree->leaf_count[0] = R.num_data_global; tree->leaf_weight[0] = R.sum_h; return tree.release(); }
     { const LeafInfo& R = *h_root_.get(); tree->leaf_value[0] = R.output; tree->leaf_count[0] = R.num_data_global; tree->leaf_weight[0] = R.sum_h; }
     for (int j = 0; j < hc.journal_count; ++j) {
@@ -595,6 +597,72 @@ void CudaEngine::ReadBackLevel(int num_leaves) {
   } else {
     FB_CUDA(cudaStreamSynchronize(stream_));
   }
+}
+
+// Exact leaf-wise tree from an over-grown device tree. The journal lists every split the device applied (in level
+// order), h_leaves_ holds the final device leaves. The controller splits every node that best-first growth with the
+// leaf budget would split (and some more), so replaying best-first growth on the host over the device's splits
+// (largest gain among the current leaves, the order of the host leaf-wise learner) gives the exact tree; nodes the
+// device did not split count as unsplittable, which only matters when the growth cap was reached. The windows of
+// the tree's leaves (a pruned subtree keeps its root's window: later partitions only permute rows inside it)
+// replace the device leaf records, so the score update and the leaf renewal see the final tree.
+// Parity: src/treelearner/cuda/learner.cpp:L2526-3067 (selective grow-then-prune with a host heap simulation).
+void CudaEngine::FinalizeLeafwise(const LevelCtrl& hc, Tree* tree) {
+  struct Node { int parent = -1, left = -1, right = -1, journal = -1, dev_leaf = 0; bool is_left = true; };
+  const int J = hc.journal_count, LD = hc.num_leaves;
+  const SplitJournal* jr = h_journal_.get();
+  const LeafInfo* dl = h_leaves_.get();
+  std::vector<Node> nodes; nodes.reserve(2 * static_cast<size_t>(J) + 1);
+  std::vector<int> cur(LD, -1);
+  nodes.emplace_back(); cur[0] = 0;
+  for (int j = 0; j < J; ++j) {
+    const SplitJournal& s = jr[j];
+    if (s.leaf >= LD || s.right_leaf >= LD || cur[s.leaf] < 0) Log::Fatal("Device journal is inconsistent (split %d)", j);
+    const int v = cur[s.leaf];
+    nodes[v].journal = j;
+    Node l, r; l.parent = r.parent = v; l.dev_leaf = s.leaf; r.dev_leaf = s.right_leaf; l.is_left = true; r.is_left = false;
+    nodes[v].left = static_cast<int>(nodes.size()); nodes.push_back(l); cur[s.leaf] = nodes[v].left;
+    nodes[v].right = static_cast<int>(nodes.size()); nodes.push_back(r); cur[s.right_leaf] = nodes[v].right;
+  }
+  const LeafInfo& R = *h_root_.get();
+  tree->leaf_value[0] = R.output; tree->leaf_count[0] = R.num_data_global; tree->leaf_weight[0] = R.sum_h;
+  std::vector<int> node_of_leaf(cfg_.num_leaves, -1); node_of_leaf[0] = 0;
+  while (tree->num_leaves < cfg_.num_leaves) {
+    int best = -1; double best_gain = 0.0;
+    for (int t = 0; t < tree->num_leaves; ++t) {
+      const Node& n = nodes[node_of_leaf[t]];
+      if (n.journal < 0) continue;
+      const double g = jr[n.journal].rec.gain;
+      if (best < 0 || g > best_gain) { best = t; best_gain = g; }
+    }
+    if (best < 0) break;
+    const Node n = nodes[node_of_leaf[best]];
+    const SplitJournal& s = jr[n.journal];
+    const int right = ApplySplit(tree, train_, best, s.rec);
+    tree->internal_count[tree->num_leaves - 2] = s.parent_global;
+    node_of_leaf[best] = n.left; node_of_leaf[right] = n.right;
+  }
+  // leaf records of the final tree
+  std::vector<LeafInfo> fin(tree->num_leaves);
+  for (int t = 0; t < tree->num_leaves; ++t) {
+    const Node& n = nodes[node_of_leaf[t]];
+    LeafInfo L;
+    if (n.journal < 0) L = dl[n.dev_leaf];
+    else {
+      // split on the device, pruned here: the window and totals the node had when it was split
+      const SplitJournal& s = jr[n.journal];
+      L = dl[n.dev_leaf];
+      L.begin = s.begin; L.count = s.count; L.buffer = s.buffer; L.depth = s.depth; L.num_data_global = s.parent_global;
+      L.sum_g = FB_ADD(s.rec.left_g, s.rec.right_g); L.sum_h = FB_ADD(s.rec.left_h, s.rec.right_h);
+      const SplitJournal& ps = jr[nodes[n.parent].journal];
+      L.output = n.is_left ? ps.rec.left_out : ps.rec.right_out;
+      if (n.is_left) { L.sum_gi = ps.rec.left_gi; L.sum_hi = ps.rec.left_hi; }
+    }
+    fin[t] = L;
+    tree->leaf_count[t] = L.num_data_global;
+  }
+  for (int t = 0; t < tree->num_leaves; ++t) h_leaves_.get()[t] = fin[t];
+  FB_CUDA(cudaMemcpyAsync(leaves_.get(), h_leaves_.get(), sizeof(LeafInfo) * tree->num_leaves, cudaMemcpyHostToDevice, stream_));
 }
 
 }  // namespace fb

@@ -17,10 +17,11 @@ struct LevelCtrl {
   int num_leaves, next_slot, done, level;
   int num_splits, num_children, total_chunks, total_blocks;
   int frontier_count, journal_count, pad0;
+  int num_eval, pad1;   // leaf-wise growth: evaluated nodes recorded so far (eval_key)
   int skip_search;   // 1: this level used up the leaf budget - its children can never split, so their construct and search are skipped
 };
 // One applied split, in application order: enough for the host to rebuild the tree after the last level.
-struct SplitJournal { int leaf, right_leaf, parent_global, pad; SplitRecord rec; };
+struct SplitJournal { int leaf, right_leaf, parent_global, pad; int begin, count, buffer, depth; /* the parent's window and depth */ SplitRecord rec; };
 struct ChildInit;
 
 // ------------------------------------------------------------- objective ----
@@ -140,6 +141,13 @@ struct CtrlArgs {
   PartSplit* splits; ChildInit* child_init; FindChild* children;
   int max_leaves; int rows_per_block;
   const unsigned char* bin_owner;   // feature-parallel: owner rank of every histogram bin (null otherwise)
+  // Exact leaf-wise growth (grow_policy=leaf). A frontier leaf is split while fewer than B evaluated nodes sort
+  // strictly before it in best-first order (LeafwiseChildKey): that never misses a node that best-first growth
+  // with a budget of B splits would split, because a node's rank only gets worse as more nodes are evaluated.
+  // The tree is grown past the budget where needed (max_leaves is the growth cap) and the host keeps the
+  // best-first tree.
+  int leafwise_budget;              // B = num_leaves - 1; 0: level growth with a gain-ranked budget
+  double* eval_key;                 // [evaluated nodes][4] order keys
 };
 void LaunchLevelController(const CtrlArgs& a, cudaStream_t s);
 
@@ -200,6 +208,7 @@ struct ChildInit {     // host-decided child bookkeeping of one split
   long long left_gi, left_hi, right_gi, right_hi;
   int hist_block_begin, hist_num_blocks;
   int monotone, pad_;              // constraint of the split feature: tightens the children's output ranges
+  double pkey[4];                  // leaf-wise growth: order key of the split node (the children's parent key)
 };
 struct PartArgs {
   const uint8_t* rows; int row_stride;

@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(kPartThreads) PartitionScanSetupKernel(PartArg
     L.hist_slot = ci.left_slot; R.hist_slot = ci.right_slot;
     L.sum_g = ci.left_g; L.sum_h = ci.left_h; L.sum_gi = ci.left_gi; L.sum_hi = ci.left_hi; L.output = ci.left_out;
     R.sum_g = ci.right_g; R.sum_h = ci.right_h; R.sum_gi = ci.right_gi; R.sum_hi = ci.right_hi; R.output = ci.right_out;
+    for (int k = 0; k < 4; ++k) L.pkey[k] = R.pkey[k] = ci.pkey[k];
     if (ci.monotone != 0) {   // "basic" monotone method: the children's ranges meet at the mid point of their outputs
       const double mid = (ci.left_out + ci.right_out) / 2.0;
       if (ci.monotone > 0) { L.max_c = fmin(L.max_c, mid); R.min_c = fmax(R.min_c, mid); }

@@ -371,3 +371,35 @@ def test_per_node_feature_masks_on_device_match_host(case):
         def structure(m):
             return [ln for ln in m.model_to_string().splitlines() if ln.startswith(("split_feature=", "threshold=", "left_child=", "right_child="))]
         assert structure(bc) == structure(bg)
+
+
+@pytest.mark.parametrize("leaves", [15, 63])
+def test_leafwise_growth_on_device_is_the_host_best_first_tree(leaves):
+    # grow_policy=leaf: the device over-grows level by level (a leaf is split while it ranks among the best
+    # num_leaves-1 nodes by the smallest gain on its path) and the host keeps the best-first tree; with identical
+    # gradients and integer histograms that is the host leaf-wise learner's tree, digit for digit
+    X, y = make_regression(30000, 12)
+    y = np.round(y * 8) / 8
+    base = {"objective": "none", "num_leaves": leaves, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "grow_policy": "leaf",
+            "min_data_in_leaf": 20, "seed": 3}
+    bc = fb.train({**base, "device_type": "cpu"}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
+    bg = fb.train({**base, "device_type": "cuda"}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
+    assert f"num_leaves={leaves}" in bc.model_to_string()
+    assert model_body(bc.model_to_string()) == model_body(bg.model_to_string())
+    lvl = fb.train({**base, "device_type": "cuda", "grow_policy": "level"}, fb.Dataset(X, y, free_raw_data=False), 1, fobj=_l2_exact)
+    assert model_body(lvl.model_to_string()) != model_body(bg.model_to_string())
+
+
+def test_leafwise_growth_trains_and_scores_consistently():
+    # several rounds: the score update runs through the final tree's leaf windows, so the training metric the
+    # device reports must equal the metric of predict() on the same rows
+    X, y = make_binary(40000, 16)
+    p = {"objective": "binary", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "grow_policy": "leaf",
+         "device_type": "cuda", "metric": "binary_logloss", "min_data_in_leaf": 20}
+    ds = fb.Dataset(X, y, free_raw_data=False)
+    ev = {}
+    b = fb.train(p, ds, 20, valid_sets=[ds], valid_names=["train"], callbacks=[fb.record_evaluation(ev)])
+    pr = np.clip(b.predict(X), 1e-15, 1 - 1e-15)
+    ll = float(-np.mean(y * np.log(pr) + (1 - y) * np.log(1 - pr)))
+    assert abs(ll - ev["train"]["binary_logloss"][-1]) < 1e-5
+    assert auc(y, pr) > 0.9
