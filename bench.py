@@ -88,8 +88,11 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--stage-timing", action="store_true")
     ap.add_argument("--plan", default="auto", help="cuda_plan string, e.g. auto,hist_lane:off")
+    ap.add_argument("--grow-policy", default=None, choices=["level", "leaf"], help="level: gain-ranked leaf budget per level; leaf: exact best-first trees")
     args = ap.parse_args()
     PARAMS["cuda_plan"] = args.plan
+    if args.grow_policy is not None:
+        PARAMS["grow_policy"] = args.grow_policy
     if args.impl == "reference":
         reference_arm(args)
         return
@@ -191,7 +194,7 @@ def main() -> None:
         out = {"metric": "s/1000 rounds (device-timed, max over ranks)", "value": ms_per_step, "unit": "s/1000 rounds", "n_gpus": world, "steps": K, "warmup": warmup,
                "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "int16-quantized gradients / fp32 scores (reference: same)",
                "data": "synthetic", "impl": "ours",
-               "config": {"model": "gbdt binary 11Mx28, num_leaves=255, max_bin=63, quant_mode=stochastic(4 bins)", "global_batch": args.rows, "seq_len": 28,
+               "config": {"model": "gbdt binary 11Mx28, num_leaves=255, max_bin=63, quant_mode=stochastic(4 bins)", "grow_policy": PARAMS.get("grow_policy", "level"), "global_batch": args.rows, "seq_len": 28,
                           "parallelism": f"dp{world}" if world > 1 else "single", "l2": "inputs_larger_than_L2", "train_logloss_after_run": logloss},
                "clocks": clk.summary(), "gpu_launches": int(launches)}
         if e2e is not None:
