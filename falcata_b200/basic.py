@@ -449,6 +449,91 @@ class Dataset:
         ct = {0: ctypes.c_float, 1: ctypes.c_double, 7: ctypes.c_int32}[typ.value]
         return np.ctypeslib.as_array(ctypes.cast(ptr, ctypes.POINTER(ct)), shape=(n.value,)).copy()
 
+    def set_field(self, field_name: str, data: Any) -> "Dataset":
+        """Set label / weight / init_score / group (alias: query) / position by name (python-package/falcata/basic.py: Dataset.set_field)."""
+        if field_name == "label":
+            return self.set_label(data)
+        if field_name == "weight":
+            return self.set_weight(data)
+        if field_name == "init_score":
+            return self.set_init_score(data)
+        if field_name in ("group", "query"):
+            return self.set_group(data)
+        if field_name == "position":
+            return self.set_position(data)
+        raise ValueError(f"Unknown field name: {field_name}")
+
+    def set_position(self, position: Any) -> "Dataset":
+        """Result positions for position-debiased ranking; kept with the dataset (the ranking objectives here do not use them)."""
+        self.position = None if position is None else np.asarray(position, dtype=np.int32)
+        return self
+
+    def get_position(self) -> Optional[np.ndarray]:
+        return getattr(self, "position", None)
+
+    def get_data(self) -> Any:
+        """The raw data this Dataset was built from (needs free_raw_data=False once constructed)."""
+        if self._handle is not None and self.data is None:
+            raise RuntimeError("Cannot call get_data after the raw data was freed; build the Dataset with free_raw_data=False")
+        if self.used_indices is not None and self.reference is not None and self.data is None:
+            ref = self.reference.get_data()
+            return ref[self.used_indices] if not hasattr(ref, "iloc") else ref.iloc[self.used_indices]
+        return self.data
+
+    def get_params(self) -> Dict[str, Any]:
+        """The dataset-related parameters this Dataset was given."""
+        keys = ("max_bin", "max_bin_by_feature", "min_data_in_bin", "bin_construct_sample_cnt", "use_missing", "zero_as_missing", "enable_bundle",
+                "categorical_feature", "feature_pre_filter", "data_random_seed", "linear_tree", "two_round", "header", "label_column", "weight_column",
+                "group_column", "ignore_column", "precise_float_parser", "max_cat_to_onehot", "min_data_per_group")
+        return {k: v for k, v in self.params.items() if k in keys}
+
+    def get_ref_chain(self, ref_limit: int = 100) -> set:
+        """This Dataset and the chain of its references."""
+        head, chain = self, set()
+        while len(chain) < ref_limit and isinstance(head, Dataset) and head not in chain:
+            chain.add(head)
+            head = head.reference
+        return chain
+
+    def set_categorical_feature(self, categorical_feature: Union[str, List[int], List[str]]) -> "Dataset":
+        if self.categorical_feature == categorical_feature:
+            return self
+        if self._handle is not None:
+            if self.data is None:
+                raise RuntimeError("Cannot change categorical_feature after the raw data was freed; build the Dataset with free_raw_data=False")
+            self._free()
+        self.categorical_feature = categorical_feature
+        return self
+
+    def _free(self) -> None:
+        if self._handle is not None:
+            _lib().FB_DatasetFree(self._handle)
+            self._handle = None
+
+    def feature_num_bin(self, feature: Union[int, str]) -> int:
+        """Number of bins of one feature (0 for a feature dropped as constant)."""
+        if isinstance(feature, str):
+            feature = self.get_feature_name().index(feature)
+        out = ctypes.c_int(0)
+        _safe_call(_lib().FB_DatasetFeatureNumBin(self.construct()._handle, ctypes.c_int(int(feature)), ctypes.byref(out)))
+        return int(out.value)
+
+    def add_features_from(self, other: "Dataset") -> "Dataset":
+        """Append the columns of `other` (same rows). Both datasets need their raw data; the result is re-binned."""
+        if self.data is None or other.data is None:
+            raise RuntimeError("add_features_from needs the raw data of both datasets (free_raw_data=False)")
+        a, b = _to_numpy_2d(self.data), _to_numpy_2d(other.data)
+        if a.shape[0] != b.shape[0]:
+            raise ValueError("Both datasets must have the same number of rows")
+        names = None
+        if self._handle is not None and other._handle is not None:
+            names = self.get_feature_name() + other.get_feature_name()
+        self._free()
+        self.data = np.concatenate([a.astype(np.float64), b.astype(np.float64)], axis=1)
+        if names is not None and len(set(names)) == len(names):
+            self.feature_name = names
+        return self
+
     def set_label(self, label: Any) -> "Dataset":
         self.label = label
         if self._handle is not None and label is not None:
@@ -928,6 +1013,52 @@ class Booster:
     def set_leaf_output(self, tree_id: int, leaf_id: int, value: float) -> "Booster":
         _safe_call(_lib().FB_BoosterSetLeafValue(self._handle, tree_id, leaf_id, ctypes.c_double(value)))
         return self
+
+    def get_split_value_histogram(self, feature: Union[int, str], bins: Any = None, xgboost_style: bool = False) -> Any:
+        """Histogram of the thresholds the model uses for one numerical feature (python-package/falcata/basic.py: Booster.get_split_value_histogram)."""
+        names = self.feature_name()
+        fidx = names.index(feature) if isinstance(feature, str) else int(feature)
+        values: List[float] = []
+
+        def walk(node: Dict[str, Any]) -> None:
+            if "split_feature" not in node:
+                return
+            if int(node["split_feature"]) == fidx:
+                if node.get("decision_type", "<=") != "<=":
+                    raise ValueError("Cannot compute a split value histogram for a categorical feature")
+                values.append(float(node["threshold"]))
+            walk(node["left_child"])
+            walk(node["right_child"])
+
+        for t in self.dump_model()["tree_info"]:
+            walk(t["tree_structure"])
+        if bins is None or (isinstance(bins, int) and xgboost_style):
+            n_unique = len(np.unique(values))
+            bins = max(min(n_unique, bins) if bins is not None else n_unique, 1)
+        hist, edges = np.histogram(values, bins=bins)
+        if not xgboost_style:
+            return hist, edges
+        ret = np.column_stack((edges[1:], hist))
+        ret = ret[ret[:, 1] > 0]
+        try:
+            import pandas as pd
+            return pd.DataFrame(ret, columns=["SplitValue", "Count"])
+        except ImportError:
+            return ret
+
+    def set_network(self, machines: Any, local_listen_port: int = 12400, listen_time_out: int = 120, num_machines: int = 1) -> "Booster":
+        """Socket networking of the reference is replaced by torch.distributed + the device fabric: call falcata_b200.parallel.init()."""
+        raise NotImplementedError("Distributed training is set up with torch.distributed and falcata_b200.parallel.init(), not with a machine list")
+
+    def free_network(self) -> "Booster":
+        from . import parallel
+        parallel.shutdown() if hasattr(parallel, "shutdown") else None
+        return self
+
+    def model_from_binary(self, data: bytes) -> "Booster":
+        """Replace this Booster's model by one serialised with model_to_binary()."""
+        other = Booster.from_binary(data)
+        return self.model_from_string(other.model_to_string())
 
     def shuffle_models(self, start_iteration: int = 0, end_iteration: int = -1) -> "Booster":
         _safe_call(_lib().FB_BoosterShuffleModels(self._handle, start_iteration, end_iteration))

@@ -275,6 +275,14 @@ int FB_DatasetGetBinnedRow(DatasetHandle handle, int32_t row, int32_t* out_bins)
 int FB_DatasetSaveBinary(DatasetHandle handle, const char* filename) { API_BEGIN(); static_cast<Dataset*>(handle)->SaveBinary(filename); API_END(); }
 int FB_DatasetGetSubset(const DatasetHandle handle, const int32_t* idx, int32_t n, DatasetHandle* out) { API_BEGIN(); *out = static_cast<const Dataset*>(handle)->Subset(idx, n); API_END(); }
 int FB_DatasetFreeDeviceData(DatasetHandle handle) { API_BEGIN(); Dataset* ds = static_cast<Dataset*>(handle); if (ds->device) { FreeDeviceDataset(ds->device); ds->device = nullptr; } API_END(); }
+int FB_DatasetFeatureNumBin(DatasetHandle handle, int feature, int* out) {
+  API_BEGIN();
+  const Dataset* ds = static_cast<const Dataset*>(handle);
+  if (feature < 0 || feature >= ds->num_total_features) Log::Fatal("Feature index %d is out of range (0..%d)", feature, ds->num_total_features - 1);
+  const BinMapper* m = ds->mappers[feature].get();
+  *out = (m == nullptr || m->is_trivial) ? 0 : m->num_bin;
+  API_END();
+}
 int FB_DatasetFree(DatasetHandle handle) { API_BEGIN(); delete static_cast<Dataset*>(handle); API_END(); }
 
 // ------------------------------------------------------------- Booster ----

@@ -58,6 +58,7 @@ int FB_DatasetGetBinnedRow(DatasetHandle handle, int32_t row, int32_t* out_featu
 int FB_DatasetSaveBinary(DatasetHandle handle, const char* filename);
 int FB_DatasetGetSubset(const DatasetHandle handle, const int32_t* used_row_indices, int32_t num_used_row_indices, DatasetHandle* out);
 int FB_DatasetFreeDeviceData(DatasetHandle handle);
+int FB_DatasetFeatureNumBin(DatasetHandle handle, int feature, int* out);
 int FB_DatasetFree(DatasetHandle handle);
 
 /* ---- Booster ---- */

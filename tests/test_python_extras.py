@@ -64,3 +64,27 @@ def test_oblique_pool(tmp_path):
     plain = fb.train(p, fb.Dataset(X[:3000], y[:3000]), 15)
     aug = fb.train(p, fb.Dataset(Xa[:3000], y[:3000]), 15)
     assert acc(aug, Xa) >= acc(plain, X) - 0.01
+
+
+def test_dataset_and_booster_helper_methods():
+    rng = np.random.default_rng(0)
+    X = rng.normal(size=(600, 4)).astype(np.float32)
+    X[:, 3] = 1.0                       # constant column: dropped
+    y = (X[:, 0] + X[:, 1] > 0).astype(np.float32)
+    ds = fb.Dataset(X, y, params={"max_bin": 15}, free_raw_data=False)
+    ds.set_field("weight", np.ones(600, dtype=np.float32)).set_position(np.arange(600) % 5)
+    ds.construct()
+    assert ds.get_data() is X and ds.get_params() == {"max_bin": 15}
+    assert 2 <= ds.feature_num_bin(0) <= 15 and ds.feature_num_bin(3) == 0
+    assert ds.get_position().shape == (600,) and ds in ds.get_ref_chain()
+    assert ds.get_field("weight").shape == (600,)
+    other = fb.Dataset(rng.normal(size=(600, 2)).astype(np.float32), free_raw_data=False)
+    ds.add_features_from(other)
+    assert ds.construct().num_feature() == 6
+    b = fb.train({"objective": "binary", "num_leaves": 7, "verbose": -1, "min_data_in_leaf": 5}, ds, 5)
+    hist, edges = b.get_split_value_histogram(0)
+    assert hist.sum() >= 1 and len(edges) == len(hist) + 1
+    clone = fb.Booster(model_str=fb.train({"objective": "binary", "num_leaves": 3, "verbose": -1}, fb.Dataset(X, y), 1).model_to_string())
+    clone.model_from_binary(b.model_to_binary())
+    A = np.concatenate([X, rng.normal(size=(600, 2)).astype(np.float32)], axis=1)
+    assert np.allclose(clone.predict(A), b.predict(A))
