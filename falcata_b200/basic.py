@@ -109,6 +109,8 @@ def _is_cuda_array(x: Any) -> bool:
 
 
 def _to_numpy_2d(data: Any) -> np.ndarray:
+    if isinstance(data, DataSequence) or (isinstance(data, list) and len(data) > 0 and all(isinstance(d, DataSequence) for d in data)):
+        data = _materialize_sequences(data)
     if _is_torch_tensor(data):
         data = data.detach().cpu().numpy()
     if hasattr(data, "values") and not isinstance(data, np.ndarray):   # pandas
@@ -182,6 +184,51 @@ def time_tag_report() -> str:
 
 
 # ------------------------------------------------------------------ Dataset ----
+_PICKLE_FORMAT = os.environ.get("FALCATA_PICKLE_FORMAT", "falb").strip().lower()
+if _PICKLE_FORMAT not in ("falb", "text"):
+    _PICKLE_FORMAT = "falb"
+
+
+def set_pickle_format(fmt: str) -> None:
+    """Payload that pickle writes for a Booster: "falb" (compact binary model, the default) or "text" (the LightGBM
+    model text, for readers that only know that format). Unpickling accepts both.
+    Parity: python-package/falcata/basic.py (set_pickle_format / get_pickle_format)."""
+    global _PICKLE_FORMAT
+    fmt = fmt.strip().lower()
+    if fmt not in ("falb", "text"):
+        raise ValueError(f'pickle format must be "falb" or "text", got "{fmt}"')
+    _PICKLE_FORMAT = fmt
+
+
+def get_pickle_format() -> str:
+    return _PICKLE_FORMAT
+
+
+class DataSequence:
+    """Generic row access for building a Dataset without one big array: len(seq), seq[i] (one row), seq[a:b]
+    (a batch of rows) and an optional batch_size. Exported as ``Sequence``.
+    Parity: python-package/falcata/basic.py (class Sequence)."""
+
+    batch_size = 4096
+
+    def __getitem__(self, idx: Any) -> np.ndarray:
+        raise NotImplementedError("Sub-classes of Sequence must implement __getitem__()")
+
+    def __len__(self) -> int:
+        raise NotImplementedError("Sub-classes of Sequence must implement __len__()")
+
+
+def _materialize_sequences(data: Any) -> np.ndarray:
+    seqs = [data] if isinstance(data, DataSequence) else list(data)
+    parts = []
+    for seq in seqs:
+        bs = int(getattr(seq, "batch_size", None) or DataSequence.batch_size)
+        n = len(seq)
+        for start in range(0, n, bs):
+            parts.append(np.asarray(seq[start:min(start + bs, n)]))
+    return np.concatenate(parts, axis=0) if parts else np.zeros((0, 0), dtype=np.float32)
+
+
 def _wants_linear(params: Dict[str, Any], reference: Any = None) -> bool:
     """linear_tree keeps the raw feature values beside the bins, which only the host construction does."""
     for k in ("linear_tree", "linear_trees"):
@@ -678,16 +725,24 @@ class Booster:
     # pickling goes through the text model
     def __getstate__(self) -> Dict[str, Any]:
         st = {k: v for k, v in self.__dict__.items() if k not in ("_handle", "train_set", "valid_sets")}
-        st["_model_str"] = self.model_to_string(num_iteration=-1)
+        if _PICKLE_FORMAT == "falb":
+            st["_model_bin"] = self.model_to_binary(num_iteration=-1)
+        else:
+            st["_model_str"] = self.model_to_string(num_iteration=-1)
         return st
 
     def __setstate__(self, state: Dict[str, Any]) -> None:
-        model_str = state.pop("_model_str")
+        # both payloads load, whatever the current setting is
+        model_str = state.pop("_model_str", None)
+        model_bin = state.pop("_model_bin", None)
         self.__dict__.update(state)
         self.train_set = None; self.valid_sets = []
         self._handle = ctypes.c_void_p(); n_iter = ctypes.c_int(0)
-        raw = model_str.encode("utf-8")
-        _safe_call(_lib().FB_BoosterLoadModelFromString(raw, ctypes.c_int64(len(raw)), ctypes.byref(n_iter), ctypes.byref(self._handle)))
+        if model_bin is not None:
+            _safe_call(_lib().FB_BoosterCreateFromBinary(model_bin, ctypes.c_int64(len(model_bin)), ctypes.byref(n_iter), ctypes.byref(self._handle)))
+        else:
+            raw = model_str.encode("utf-8")
+            _safe_call(_lib().FB_BoosterLoadModelFromString(raw, ctypes.c_int64(len(raw)), ctypes.byref(n_iter), ctypes.byref(self._handle)))
 
     def __copy__(self) -> "Booster":
         return self.__deepcopy__(None)

@@ -177,6 +177,19 @@ class LGBMModel(BaseEstimator):
         return self.booster_.feature_name()
 
     @property
+    def n_estimators_(self) -> int:
+        """Boosting rounds actually trained (python-package/falcata/sklearn.py: n_estimators_)."""
+        return self.booster_.current_iteration()
+
+    @property
+    def n_iter_(self) -> int:
+        return self.booster_.current_iteration()
+
+    @property
+    def feature_names_in_(self) -> np.ndarray:
+        return np.array(self.feature_name_)
+
+    @property
     def objective_(self) -> Any:
         return self._objective or self._default_objective()
 
@@ -226,6 +239,10 @@ class LGBMClassifier(ClassifierMixin, LGBMModel):
         if self._n_classes > 2:
             return res
         return np.vstack((1.0 - res, res)).T
+
+    def decision_function(self, X: Any, *, start_iteration: int = 0, num_iteration: Optional[int] = None, **kwargs: Any) -> Any:
+        """Raw margin of every sample (python-package/falcata/sklearn.py: FalcataClassifier.decision_function)."""
+        return self.predict_proba(X, raw_score=True, start_iteration=start_iteration, num_iteration=num_iteration, **kwargs)
 
     def predict(self, X: Any, raw_score: bool = False, start_iteration: int = 0, num_iteration: Optional[int] = None, pred_leaf: bool = False,
                 pred_contrib: bool = False, **kwargs: Any) -> Any:

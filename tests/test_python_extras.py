@@ -88,3 +88,41 @@ def test_dataset_and_booster_helper_methods():
     clone.model_from_binary(b.model_to_binary())
     A = np.concatenate([X, rng.normal(size=(600, 2)).astype(np.float32)], axis=1)
     assert np.allclose(clone.predict(A), b.predict(A))
+
+
+def test_pickle_formats_sequence_input_and_sklearn_extras():
+    import pickle
+    rng = np.random.default_rng(1)
+    X = rng.normal(size=(900, 5)).astype(np.float32)
+    y = (X[:, 0] - X[:, 2] > 0).astype(np.float32)
+
+    class Rows(fb.Sequence):
+        batch_size = 256
+
+        def __init__(self, a):
+            self.a = a
+
+        def __getitem__(self, idx):
+            return self.a[idx]
+
+        def __len__(self):
+            return len(self.a)
+
+    p = {"objective": "binary", "num_leaves": 7, "verbose": -1, "min_data_in_leaf": 5}
+    b_seq = fb.train(p, fb.Dataset([Rows(X[:500]), Rows(X[500:])], y), 5)
+    b_arr = fb.train(p, fb.Dataset(X, y), 5)
+    assert b_seq.model_to_string() == b_arr.model_to_string()
+    assert fb.get_pickle_format() == "falb"
+    blob_bin = pickle.dumps(b_arr)
+    fb.set_pickle_format("text")
+    try:
+        blob_txt = pickle.dumps(b_arr)
+    finally:
+        fb.set_pickle_format("falb")
+    assert len(blob_bin) < len(blob_txt)
+    for blob in (blob_bin, blob_txt):
+        assert np.array_equal(pickle.loads(blob).predict(X), b_arr.predict(X))
+    clf = fb.LGBMClassifier(n_estimators=8, num_leaves=7, verbose=-1).fit(X, y)
+    assert clf.n_estimators_ == 8 and clf.n_iter_ == 8 and len(clf.feature_names_in_) == 5
+    margin = clf.decision_function(X)
+    assert np.array_equal(margin > 0, clf.predict(X) == 1)
