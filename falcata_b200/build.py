@@ -99,10 +99,13 @@ def build(force: bool = False, ptxas: bool = False, verbose: bool = False) -> Pa
                 if out:
                     logs.append(f"==== {futs[fut].name}\n{out}")
     if jobs or not LIB.exists():
-        cmd = [NVCC, *ARCH, "-shared", "-Xcompiler", "-fPIC,-fopenmp", "-o", str(LIB), *map(str, objs), "-lz", "-lgomp"]
+        # link beside the target and rename: a reader (an import, a copy of the tree) never sees a half-written library
+        tmp = LIB.with_name(LIB.name + ".tmp")
+        cmd = [NVCC, *ARCH, "-shared", "-Xcompiler", "-fPIC,-fopenmp", "-o", str(tmp), *map(str, objs), "-lz", "-lgomp"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB)
     if ptxas:
         print("\n".join(logs))
     _build_cli()

@@ -12,7 +12,10 @@
 #include <omp.h>
 #include "fb/objective.h"
 
+#include <fstream>
+#include <functional>
 #include <numeric>
+#include <sstream>
 #include <queue>
 
 namespace fb {
@@ -148,6 +151,12 @@ class CPUTreeLearner : public TreeLearner {
   std::vector<int8_t> voted_;      // voting-parallel: features whose histograms are globally reduced for the current leaf
   int cur_tree_index_ = 0, cur_leaf_id_ = 0;
   Random extra_rand_{6};
+  // forced splits (forcedsplits_filename): a tree of (feature, threshold) applied from the root before normal growth
+  struct ForcedNode { int feature = -1; double threshold = 0.0; int left = -1, right = -1; };
+  std::vector<ForcedNode> forced_;
+  int forced_feature_ = -1, forced_bin_ = -1;   // non-negative while FindBestSplit evaluates one forced (feature, bin)
+  void LoadForcedSplits();
+  void ForceSplits(Tree* tree, int tree_index);
 };
 
 void CPUTreeLearner::SetParams() {
@@ -172,6 +181,79 @@ void CPUTreeLearner::Init(const Dataset* train, const Config& cfg) {
   SetParams();
   col_sampler_.Init(cfg_, ds_);
   indices_.resize(ds_->num_data); tmp_.resize(ds_->num_data);
+  LoadForcedSplits();
+}
+
+// forcedsplits_filename: nested JSON objects {"feature": i, "threshold": v, "left": {...}, "right": {...}} over real
+// feature indices. Parity: src/treelearner/serial_tree_learner.cpp:L641-781 (ForceSplits: breadth-first from the
+// root, a forced split that does not improve the leaf is ignored together with its subtree).
+void CPUTreeLearner::LoadForcedSplits() {
+  forced_.clear();
+  if (cfg_.forcedsplits_filename.empty()) return;
+  std::ifstream f(cfg_.forcedsplits_filename);
+  if (!f) Log::Fatal("Cannot open forced splits file %s", cfg_.forcedsplits_filename.c_str());
+  std::stringstream ss; ss << f.rdbuf();
+  const std::string t = ss.str();
+  size_t pos = 0;
+  auto skip_ws = [&]() { while (pos < t.size() && isspace(static_cast<unsigned char>(t[pos]))) ++pos; };
+  std::function<int()> parse_object = [&]() -> int {
+    skip_ws();
+    if (pos >= t.size() || t[pos] != '{') Log::Fatal("Forced splits file: expected '{' at offset %d", static_cast<int>(pos));
+    ++pos;
+    const int id = static_cast<int>(forced_.size()); forced_.emplace_back();
+    for (;;) {
+      skip_ws();
+      if (pos < t.size() && t[pos] == '}') { ++pos; break; }
+      if (pos < t.size() && t[pos] == ',') { ++pos; continue; }
+      if (pos >= t.size() || t[pos] != '"') Log::Fatal("Forced splits file: expected a key at offset %d", static_cast<int>(pos));
+      const size_t e = t.find('"', pos + 1);
+      if (e == std::string::npos) Log::Fatal("Forced splits file: unterminated key");
+      const std::string key = t.substr(pos + 1, e - pos - 1);
+      pos = e + 1; skip_ws();
+      if (pos >= t.size() || t[pos] != ':') Log::Fatal("Forced splits file: expected ':' after \"%s\"", key.c_str());
+      ++pos; skip_ws();
+      if (key == "left" || key == "right") { const int c = parse_object(); if (key == "left") forced_[id].left = c; else forced_[id].right = c; }
+      else {
+        size_t e2 = pos; while (e2 < t.size() && t[e2] != ',' && t[e2] != '}') ++e2;
+        const double v = atof(t.substr(pos, e2 - pos).c_str());
+        if (key == "feature") forced_[id].feature = static_cast<int>(v); else if (key == "threshold") forced_[id].threshold = v;
+        pos = e2;
+      }
+    }
+    return id;
+  };
+  skip_ws();
+  if (pos < t.size()) parse_object();
+  if (!forced_.empty() && forced_[0].feature < 0) forced_.clear();   // "{}"
+}
+
+void CPUTreeLearner::ForceSplits(Tree* tree, int tree_index) {
+  std::queue<std::pair<int, int>> q;   // (leaf id, forced node)
+  q.push({0, 0});
+  while (!q.empty() && tree->num_leaves < cfg_.num_leaves) {
+    const int leaf = q.front().first; const ForcedNode fn = forced_[q.front().second]; q.pop();
+    if (fn.feature < 0 || fn.feature >= ds_->num_total_features) continue;
+    const int inner = ds_->used_feature_map[fn.feature];
+    if (inner < 0 || ds_->feature_meta[inner].bin_type != static_cast<int>(BinType::Numerical)) {
+      Log::Warning("Forced split on feature %d is ignored (constant or categorical feature)", fn.feature);
+      continue;
+    }
+    const int nb = ds_->feature_meta[inner].num_bin;
+    forced_feature_ = inner; forced_bin_ = std::min(static_cast<int>(ds_->mappers[fn.feature]->ValueToBin(fn.threshold)), nb - 2);
+    const SplitRecord kept = leaves_[leaf].best;
+    FindBestSplit(&leaves_[leaf], leaf, tree_index);
+    forced_feature_ = forced_bin_ = -1;
+    if (leaves_[leaf].best.feature < 0 || !(leaves_[leaf].best.gain > 0.0)) {
+      Log::Warning("Forced split on feature %d is ignored: it does not improve the leaf", fn.feature);
+      leaves_[leaf].best = kept;
+      continue;
+    }
+    const int right = ApplySplit(tree, leaf);
+    FindBestSplit(&leaves_[leaf], leaf, tree_index);
+    FindBestSplit(&leaves_[right], right, tree_index);
+    if (fn.left >= 0) q.push({leaf, fn.left});
+    if (fn.right >= 0) q.push({right, fn.right});
+  }
 }
 
 void CPUTreeLearner::Quantize(const score_t* grad, const score_t* hess, int tree_index) {
@@ -293,6 +375,7 @@ void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanI
   if (skip >= 0) { mgi = gi[skip]; mhi = hi[skip]; mgd = gd[skip]; mhd = hd[skip]; mcnt = BinCountEstimate(binh(skip), L.cnt_factor); }
   int rand_t = -1;
   if (sp_.extra_trees && nb > 2) rand_t = ExtraTreesThreshold(static_cast<uint32_t>(cfg_.extra_seed), cur_tree_index_, cur_leaf_id_, m.real_index, nb);
+  if (forced_bin_ >= 0 && f == forced_feature_) rand_t = forced_bin_;
   double best_gain = -std::numeric_limits<double>::infinity(); int best_rank = 1 << 30;
   SplitRecord cand; InitSplitRecord(&cand);
   int64_t pgi = 0, phi = 0; double pgd = 0, phd = 0; int pc = 0;
@@ -425,7 +508,8 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
   L.min_gain_shift = FB_ADD(LeafGainGivenOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, leaf->output), sp_.min_gain_to_split);
   if (sp_.max_delta_step <= 0.0 && sp_.path_smooth <= 0.0)
     L.min_gain_shift = FB_ADD(LeafGain(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, L.num_data, leaf->output), sp_.min_gain_to_split);
-  const std::vector<int8_t> mask = col_sampler_.by_node() ? col_sampler_.SampleByNode(tree_index, leaf_id + 1000003 * leaf->depth, &leaf->path) : col_sampler_.used_by_tree();
+  std::vector<int8_t> mask = col_sampler_.by_node() ? col_sampler_.SampleByNode(tree_index, leaf_id + 1000003 * leaf->depth, &leaf->path) : col_sampler_.used_by_tree();
+  if (forced_feature_ >= 0) { mask.assign(mask.size(), 0); mask[forced_feature_] = 1; }
 
   if (parallel_voting_) {
     // PV-Tree: local top-k by local gain, global vote, reduce only the voted features.
@@ -615,6 +699,7 @@ Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_i
   tree->leaf_value[0] = root.output; tree->leaf_count[0] = static_cast<int>(root.global_count); tree->leaf_weight[0] = root.sum_h;
   ConstructHistogram(&root);
   FindBestSplit(&root, 0, tree_index);
+  if (!forced_.empty()) ForceSplits(tree.get(), tree_index);
 
   if (cfg_.grow_policy == "leaf") {
     while (tree->num_leaves < cfg_.num_leaves) {
@@ -630,7 +715,7 @@ Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_i
       FindBestSplit(&leaves_[right], right, tree_index);
     }
   } else {
-    std::vector<int> frontier = {0};
+    std::vector<int> frontier(tree->num_leaves); std::iota(frontier.begin(), frontier.end(), 0);   // more than the root after forced splits
     while (tree->num_leaves < cfg_.num_leaves && !frontier.empty()) {
       std::vector<int> cand;
       for (int l : frontier) if (leaves_[l].best.feature >= 0 && leaves_[l].best.gain > 0.0) cand.push_back(l);

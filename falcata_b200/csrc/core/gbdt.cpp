@@ -31,6 +31,10 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
       Log::Warning("linear_tree trains on the host (the leaf regressions need the raw feature values)");
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
+    if (!cfg.forcedsplits_filename.empty() && is_cuda_) {
+      Log::Warning("forcedsplits_filename trains on the host learner");
+      is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
+    }
     if (cfg.linear_tree && !train->has_raw()) Log::Fatal("linear_tree needs the raw feature values: build the Dataset from host data with linear_tree=true in its params");
     if ((is_dart_ || is_rf_) && is_cuda_) {
       Log::Warning("boosting=%s keeps its scores on the host; the device engine is used for gbdt", cfg.boosting.c_str());

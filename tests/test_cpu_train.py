@@ -205,3 +205,23 @@ def test_interaction_constraints_and_bynode_sampling():
     b3 = fb.train({**q, "feature_fraction_bynode": 1.0}, fb.Dataset(X, y), 10)
     assert b2.model_to_string() != b3.model_to_string()
     assert float(np.mean((b2.predict(X) - y) ** 2)) < 0.7 * float(np.var(y))
+
+
+def test_forced_splits_shape_the_top_of_every_tree(tmp_path):
+    import json
+    rng = np.random.default_rng(7)
+    X = rng.normal(size=(4000, 5)).astype(np.float32)
+    y = (X[:, 0] + 0.5 * X[:, 1] * X[:, 2] + 0.1 * rng.normal(size=4000)).astype(np.float32)
+    forced = {"feature": 3, "threshold": 0.25, "left": {"feature": 4, "threshold": -0.5}, "right": {"feature": 1, "threshold": 0.0}}
+    path = tmp_path / "forced.json"
+    path.write_text(json.dumps(forced))
+    for policy in ("level", "leaf"):
+        p = {"objective": "regression", "num_leaves": 15, "verbose": -1, "min_data_in_leaf": 10, "grow_policy": policy,
+             "forcedsplits_filename": str(path)}
+        b = fb.train(p, fb.Dataset(X, y), 3)
+        for t in b.dump_model()["tree_info"]:
+            root = t["tree_structure"]
+            assert root["split_feature"] == 3 and abs(root["threshold"] - 0.25) < 0.2
+            assert root["left_child"]["split_feature"] == 4 and root["right_child"]["split_feature"] == 1
+            assert t["num_leaves"] == 15
+        assert float(np.mean((b.predict(X) - y) ** 2)) < float(np.var(y))
