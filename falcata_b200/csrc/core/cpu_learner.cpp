@@ -165,6 +165,7 @@ void CPUTreeLearner::SetParams() {
   sp_.min_data_in_leaf = cfg_.min_data_in_leaf; sp_.max_depth = cfg_.max_depth;
   sp_.max_cat_threshold = cfg_.max_cat_threshold; sp_.max_cat_to_onehot = cfg_.max_cat_to_onehot; sp_.min_data_per_group = cfg_.min_data_per_group;
   sp_.cat_l2 = cfg_.cat_l2; sp_.cat_smooth = cfg_.cat_smooth; sp_.extra_trees = cfg_.extra_trees ? 1 : 0;
+  sp_.cegb_split = cfg_.cegb_tradeoff * cfg_.cegb_penalty_split;
   sp_.use_mc = 0; for (const auto& m : ds_->feature_meta) if (m.monotone != 0) sp_.use_mc = 1;
   quant_ = cfg_.quant != QuantMode::None;
   qs_.bins = cfg_.quant_bins_resolved; qs_.stochastic = cfg_.quant == QuantMode::Stochastic;
@@ -566,6 +567,7 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
       if (!voted_[f] || f % Network::world() != Network::rank()) continue;
       if (ds_->feature_meta[f].bin_type == static_cast<int>(BinType::Numerical)) ScanNumerical(global, f, L, &best); else ScanCategorical(global, f, L, &best);
     }
+    if (best.feature >= 0 && sp_.cegb_split > 0.0) best.gain -= sp_.cegb_split * static_cast<double>(L.num_data);
     SyncBestSplit(&best);
     leaf->best = best;
     return;
@@ -590,6 +592,8 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
       if (SplitBetter(r.gain, ds_->feature_meta[r.feature].real_index, r.threshold, best.gain, best.feature >= 0 ? ds_->feature_meta[best.feature].real_index : -1, best.threshold)) best = r;
     }
   }
+  // Parity: src/treelearner/cost_effective_gradient_boosting.hpp (DeltaGain: tradeoff * penalty_split * rows of the leaf)
+  if (best.feature >= 0 && sp_.cegb_split > 0.0) best.gain -= sp_.cegb_split * static_cast<double>(L.num_data);
   SyncBestSplit(&best);
   leaf->best = best;
 }

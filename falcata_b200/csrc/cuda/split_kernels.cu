@@ -369,6 +369,7 @@ __global__ void ReduceBestKernel(FindArgs a) {
     if (s_idx[0] >= 0 && depth_ok && size_ok) {
       const CandLite c = a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + s_idx[0]];
       r.gain = c.gain; r.feature = c.feature; r.threshold = c.threshold; r.default_left = c.default_left;
+      if (a.params.cegb_split > 0.0) r.gain -= a.params.cegb_split * static_cast<double>(leaf.num_data_global);
       r.left_g = c.left_g; r.left_h = c.left_h; r.right_g = FB_SUB(leaf.sum_g, c.left_g); r.right_h = FB_SUB(leaf.sum_h, c.left_h);
       r.left_gi = c.left_gi; r.left_hi = c.left_hi; r.left_cnt = c.left_cnt; r.right_cnt = leaf.num_data_global - c.left_cnt;
       r.monotone = c.is_categorical ? 0 : a.meta[c.feature].monotone;

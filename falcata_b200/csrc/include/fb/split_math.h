@@ -34,6 +34,7 @@ struct SplitParams {
   int max_cat_threshold, max_cat_to_onehot, min_data_per_group;
   double cat_l2, cat_smooth;
   int extra_trees;
+  double cegb_split;   // cost-effective boosting: cegb_tradeoff * cegb_penalty_split, charged per row of the leaf against every split gain
   int use_mc;   // some feature carries a monotone constraint: leaf outputs are clamped to the leaf's [min, max] range
 };
 

@@ -225,3 +225,14 @@ def test_forced_splits_shape_the_top_of_every_tree(tmp_path):
             assert root["left_child"]["split_feature"] == 4 and root["right_child"]["split_feature"] == 1
             assert t["num_leaves"] == 15
         assert float(np.mean((b.predict(X) - y) ** 2)) < float(np.var(y))
+
+
+def test_cegb_split_penalty_makes_smaller_trees():
+    rng = np.random.default_rng(2)
+    X = rng.normal(size=(3000, 5)).astype(np.float32)
+    y = (X[:, 0] + 0.3 * X[:, 1] + 0.3 * rng.normal(size=3000)).astype(np.float32)
+    p = {"objective": "regression", "num_leaves": 31, "verbose": -1, "min_data_in_leaf": 5}
+    free = fb.train(p, fb.Dataset(X, y), 3)
+    taxed = fb.train({**p, "cegb_penalty_split": 0.05, "cegb_tradeoff": 1.0}, fb.Dataset(X, y), 3)
+    leaves = lambda b: sum(t["num_leaves"] for t in b.dump_model()["tree_info"])
+    assert leaves(free) == 93 and 3 < leaves(taxed) < leaves(free)
