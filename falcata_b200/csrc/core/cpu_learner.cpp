@@ -357,8 +357,11 @@ void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanI
   const int nb = m.num_bin;
   auto slot = [&](int b) { return m.bundled ? m.hist_offset + (b < m.most_freq_bin ? b : b - 1) : m.hist_offset + b; };
   // per-bin values (integers when quantized)
-  std::vector<int64_t> gi(nb, 0), hi(nb, 0);
-  std::vector<double> gd(nb, 0.0), hd(nb, 0.0);
+  // scratch per worker thread: four arrays of nb values, zeroed (no allocation per call)
+  static thread_local std::vector<int64_t> scratch_i; static thread_local std::vector<double> scratch_d;
+  if (scratch_i.size() < 2 * static_cast<size_t>(nb)) { scratch_i.resize(2 * static_cast<size_t>(nb)); scratch_d.resize(2 * static_cast<size_t>(nb)); }
+  std::fill(scratch_i.begin(), scratch_i.begin() + 2 * nb, 0); std::fill(scratch_d.begin(), scratch_d.begin() + 2 * nb, 0.0);
+  int64_t* gi = scratch_i.data(); int64_t* hi = gi + nb; double* gd = scratch_d.data(); double* hd = gd + nb;
   if (quant_) {
     int64_t og = 0, oh = 0;
     for (int b = 0; b < nb; ++b) if (!(m.bundled && b == m.most_freq_bin)) { gi[b] = leaf.hist_i[2 * slot(b)]; hi[b] = leaf.hist_i[2 * slot(b) + 1]; og += gi[b]; oh += hi[b]; }
