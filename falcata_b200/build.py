@@ -109,6 +109,7 @@ def build(force: bool = False, ptxas: bool = False, verbose: bool = False) -> Pa
     if ptxas:
         print("\n".join(logs))
     _build_cli()
+    _build_native_tests()
     return LIB
 
 
@@ -123,6 +124,20 @@ def _build_cli() -> Path:
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"CLI build failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    return exe
+
+
+def _build_native_tests() -> Path:
+    """Native unit tests of the core (plain asserts), linked against the core library: bin/falcata_core_tests."""
+    src = CSRC / "tests" / "core_tests.cpp"
+    exe = LIB.parent.parent / "bin" / "falcata_core_tests"
+    exe.parent.mkdir(parents=True, exist_ok=True)
+    if exe.exists() and exe.stat().st_mtime >= max(src.stat().st_mtime, LIB.stat().st_mtime, _newest_header()):
+        return exe
+    cmd = [CXX, *COMMON, "-ffp-contract=off", str(src), "-o", str(exe), f"-L{LIB.parent}", "-lfalcata_core", "-Wl,-rpath,$ORIGIN/../lib"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"native test build failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
     return exe
 
 

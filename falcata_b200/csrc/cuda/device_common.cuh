@@ -133,24 +133,6 @@ struct LeafInfo {
   double pkey[4];              // leaf-wise growth: the parent's order key (see LeafwiseChildKey), +inf padded
 };
 
-// Leaf-wise (best-first) order key. Along the path from the root, keep the gains that are smaller than every later
-// gain (a staircase of suffix minima, increasing): best-first growth pops node u before node v when u's staircase is
-// lexicographically larger (a missing element counts as +inf, so a bottleneck node precedes its subtree). Only the
-// first four steps are kept; equal truncated keys are treated as ties. The key of a node follows from its parent's
-// key and its own best gain g: drop the trailing steps larger than g, then append g.
-__host__ __device__ inline void LeafwiseChildKey(const double* parent_key, double g, double* key) {
-  const double inf = 1.0 / 0.0;
-  int n = 0;
-  for (int i = 0; i < 4; ++i) { key[i] = parent_key[i]; if (parent_key[i] != inf) n = i + 1; }
-  while (n > 0 && key[n - 1] > g) { key[n - 1] = inf; --n; }
-  if (n < 4) key[n] = g;
-}
-// a sorts strictly before b
-__host__ __device__ inline bool LeafwiseKeyBefore(const double* a, const double* b) {
-  for (int i = 0; i < 4; ++i) { if (a[i] != b[i]) return a[i] > b[i]; }
-  return false;
-}
-
 // Bounded spin on a flag written by a peer rank. Returns false when the budget ran out; callers
 // then record kStatusWaitTimeout and skip their work — the kernel always terminates.
 __device__ inline bool WaitFlagGE(const volatile unsigned int* flag, unsigned int expected, unsigned long long max_spins) {

@@ -167,6 +167,24 @@ FB_HD inline double EvalCandidate(double lg, double lh, int lcnt, const LeafScan
   return FB_SUB(gain, L.min_gain_shift);
 }
 
+// Leaf-wise (best-first) order key. Along the path from the root, keep the gains that are smaller than every later
+// gain (a staircase of suffix minima, increasing): best-first growth pops node u before node v when u's staircase is
+// lexicographically larger (a missing element counts as +inf, so a bottleneck node precedes its subtree). Only the
+// first four steps are kept; equal truncated keys are treated as ties. The key of a node follows from its parent's
+// key and its own best gain g: drop the trailing steps larger than g, then append g.
+FB_HD inline void LeafwiseChildKey(const double* parent_key, double g, double* key) {
+  const double inf = 1.0 / 0.0;
+  int n = 0;
+  for (int i = 0; i < 4; ++i) { key[i] = parent_key[i]; if (parent_key[i] != inf) n = i + 1; }
+  while (n > 0 && key[n - 1] > g) { key[n - 1] = inf; --n; }
+  if (n < 4) key[n] = g;
+}
+// a sorts strictly before b
+FB_HD inline bool LeafwiseKeyBefore(const double* a, const double* b) {
+  for (int i = 0; i < 4; ++i) { if (a[i] != b[i]) return a[i] > b[i]; }
+  return false;
+}
+
 // extra_trees: the one threshold (0 .. nb-2) that a (tree, leaf, feature) evaluates. A counter-based draw, so
 // the host learner, the device kernel and any rank count pick the same threshold.
 FB_HD inline int ExtraTreesThreshold(uint32_t seed, int tree_index, int leaf, int real_feature, int nb) {

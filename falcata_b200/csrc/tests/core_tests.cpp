@@ -1,0 +1,172 @@
+// Native unit tests of the core library (plain asserts, no framework): value formatting, binning, tree text round
+// trip, single-row prediction, counter-based random numbers, quantization, and the best-first order keys of the
+// device level controller checked against a brute-force best-first growth.
+// Parity: tests/cpp_tests/ (test_common.cpp, test_serialize.cpp, test_single_row.cpp) of the reference.
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <functional>
+#include <map>
+#include <queue>
+#include <string>
+#include <vector>
+
+#include "fb/bin.h"
+#include "fb/common.h"
+#include "fb/config.h"
+#include "fb/learner.h"
+#include "fb/split_math.h"
+#include "fb/tree.h"
+
+using namespace fb;
+
+static int g_failed = 0, g_checks = 0;
+#define CHECK(cond) do { ++g_checks; if (!(cond)) { ++g_failed; fprintf(stderr, "FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond); } } while (0)
+
+static void TestFormatting() {
+  const double vals[] = {0.1, -3.25, 1e-300, 12345678.9012345678, 1.0 / 3.0, 5e22};
+  for (double v : vals) CHECK(atof(DoubleToStr17(v).c_str()) == v);   // 17 significant digits round-trip a double
+  const auto parts = Split("a,b,,c", ',');
+  CHECK(parts.size() == 4 && parts[0] == "a" && parts[2].empty() && parts[3] == "c");
+}
+
+static void TestPhilox() {
+  const Philox4 a = Philox4x32_10(1, 2, 3, 4, 5, 6), b = Philox4x32_10(1, 2, 3, 4, 5, 6), c = Philox4x32_10(2, 2, 3, 4, 5, 6);
+  CHECK(memcmp(&a, &b, sizeof(a)) == 0);
+  CHECK(memcmp(&a, &c, sizeof(a)) != 0);
+  double mean = 0; const int n = 20000;
+  for (int i = 0; i < n; ++i) { const float u = U01From24(Philox4x32_10(i, 0, 0, 0, 7, 9).v[0]); CHECK(u >= 0.f && u < 1.f); mean += u; }
+  CHECK(std::fabs(mean / n - 0.5) < 0.01);
+}
+
+static void TestQuantizeRow() {
+  // stochastic rounding is unbiased and stays inside the signed 16-bit / unsigned 16-bit lanes
+  const float g = 0.37f, h = 0.21f, inv_g = 1.f / 0.25f, inv_h = 1.f / 0.25f;
+  double sg = 0, sh = 0; const int n = 40000;
+  for (int i = 0; i < n; ++i) {
+    const int32_t w = QuantizeRow(g, h, inv_g, inv_h, true, 11u, 3u, static_cast<uint64_t>(i));
+    sg += UnpackG(w); sh += UnpackH(w);
+    CHECK(UnpackG(w) == 1 || UnpackG(w) == 2);
+  }
+  CHECK(std::fabs(sg / n - g * inv_g) < 0.02 && std::fabs(sh / n - h * inv_h) < 0.02);
+  CHECK(UnpackG(PackGH(-5, 9)) == -5 && UnpackH(PackGH(-5, 9)) == 9);
+}
+
+static void TestBinMapper() {
+  std::vector<double> v;
+  for (int i = 0; i < 1000; ++i) v.push_back((i * 37 % 1000) / 10.0);
+  Config cfg;
+  BinMapper bm;
+  bm.FindBin(v.data(), static_cast<int>(v.size()), 1000, 16, 3, 20, true, BinType::Numerical, true, false, {});
+  CHECK(bm.num_bin >= 2 && bm.num_bin <= 16 && !bm.is_trivial);
+  int prev = -1;
+  for (double x = 0.0; x < 100.0; x += 0.5) { const int b = static_cast<int>(bm.ValueToBin(x)); CHECK(b >= prev && b < bm.num_bin); prev = b; }
+  CHECK(static_cast<int>(bm.ValueToBin(std::nan(""))) < bm.num_bin);
+}
+
+static void TestTreeRoundTripAndPredict() {
+  Tree t(4);
+  const int r1 = t.Split(0, 0, 0, 3, 0.5, -1.0, 2.0, 60, 40, 6.0, 4.0, 10.f, 0, true);
+  const int r2 = t.Split(r1, 1, 2, 5, -1.25, 0.25, 4.0, 30, 10, 3.0, 1.0, 5.f, 2, false);
+  CHECK(r1 == 1 && r2 == 2 && t.num_leaves == 3);
+  double row_a[3] = {0.4, 0.0, 9.0}, row_b[3] = {0.6, 0.0, -2.0}, row_c[3] = {0.6, 0.0, 7.0}, row_d[3] = {0.6, 0.0, std::nan("")};
+  CHECK(t.Predict(row_a) == -1.0 && t.Predict(row_b) == 0.25 && t.Predict(row_c) == 4.0);
+  CHECK(t.Predict(row_d) == 4.0);   // missing_type NaN with default right
+  const std::string text = t.ToString();
+  size_t used = 0;
+  Tree u(text.c_str(), &used);
+  CHECK(u.num_leaves == 3 && u.ToString() == text);
+  CHECK(u.Predict(row_a) == -1.0 && u.Predict(row_b) == 0.25 && u.Predict(row_c) == 4.0 && u.Predict(row_d) == 4.0);
+  t.Shrink(0.5);
+  CHECK(t.Predict(row_c) == 2.0 && t.shrinkage == 0.5);
+}
+
+static void TestSplitMath() {
+  SplitParams p; memset(&p, 0, sizeof(p));
+  p.lambda_l2 = 1.0; p.min_data_in_leaf = 1;
+  CHECK(LeafOutput(-6.0, 2.0, p, 10, 0.0) == 2.0);
+  CHECK(LeafGain(-6.0, 2.0, p, 10, 0.0) == 12.0);
+  p.lambda_l1 = 1.0;
+  CHECK(ThresholdL1(-6.0, 1.0) == -5.0 && LeafOutput(-6.0, 2.0, p, 10, 0.0) == 5.0 / 3.0);
+  // monotone ranges clamp the children and a violated order rejects the candidate
+  p.lambda_l1 = 0.0; p.use_mc = 1;
+  double gain, lo, ro;
+  CHECK(SplitGain(-4.0, 1.0, 4.0, 1.0, p, 5, 5, 0.0, +1, -1.0, 1.0, &gain, &lo, &ro) == false);   // left 2 > right -2 under +1
+  CHECK(SplitGain(4.0, 1.0, -4.0, 1.0, p, 5, 5, 0.0, +1, -1.0, 1.0, &gain, &lo, &ro) == true);
+  CHECK(lo == -1.0 && ro == 1.0);   // clamped from -2 / +2
+}
+
+// Best-first growth over a random gain tree, against the rule of the level controller: a node is split while fewer
+// than B evaluated nodes sort strictly before it by the order key; replaying best-first over the split nodes must
+// then give exactly the best-first tree.
+static void TestLeafwiseKeys() {
+  typedef std::vector<int> Path;
+  for (int seed = 0; seed < 60; ++seed) {
+    std::map<Path, double> gains;
+    auto gain = [&](const Path& v) {
+      auto it = gains.find(v);
+      if (it != gains.end()) return it->second;
+      uint32_t h = 2166136261u ^ static_cast<uint32_t>(seed * 7919);
+      for (int b : v) h = (h ^ static_cast<uint32_t>(b + 1)) * 16777619u;
+      const Philox4 r = Philox4x32_10(h, static_cast<uint32_t>(v.size()), 0, 0, 17, 23);
+      double g = U01From24(r.v[0]) * std::pow(seed % 2 ? 0.9 : 0.6, static_cast<double>(v.size()));
+      if (U01From24(r.v[1]) < 0.1) g = -1.0;
+      gains[v] = g; return g;
+    };
+    const int B = 3 + seed % 40;
+    auto best_first = [&](const std::map<Path, int>* allowed) {
+      std::vector<Path> picked;
+      std::priority_queue<std::pair<double, Path>> pq; pq.push({gain(Path()), Path()});
+      while (!pq.empty() && static_cast<int>(picked.size()) < B) {
+        const auto top = pq.top(); pq.pop();
+        if (!(top.first > 0.0)) break;
+        if (allowed != nullptr && !allowed->count(top.second)) continue;   // not split on the "device": unsplittable
+        picked.push_back(top.second);
+        for (int c = 0; c < 2; ++c) { Path ch = top.second; ch.push_back(c); pq.push({gain(ch), ch}); }
+      }
+      std::sort(picked.begin(), picked.end());
+      return picked;
+    };
+    const std::vector<Path> ref = best_first(nullptr);
+    // level-wise over-growth with the key rule
+    std::map<Path, std::vector<double>> key_of, pkey_of;
+    pkey_of[Path()] = std::vector<double>(4, 1.0 / 0.0);
+    std::vector<std::vector<double>> all_keys;
+    std::map<Path, int> split;
+    std::vector<Path> frontier = {Path()};
+    while (!frontier.empty() && split.size() < 4000) {
+      std::vector<Path> cand;
+      for (const Path& v : frontier) {
+        const double g = gain(v);
+        if (!(g > 0.0)) continue;
+        std::vector<double> k(4);
+        LeafwiseChildKey(pkey_of[v].data(), g, k.data());
+        key_of[v] = k; all_keys.push_back(k); cand.push_back(v);
+      }
+      std::vector<Path> next;
+      for (const Path& v : cand) {
+        int before = 0;
+        for (const auto& k : all_keys) before += LeafwiseKeyBefore(k.data(), key_of[v].data()) ? 1 : 0;
+        if (before >= B) continue;
+        split[v] = 1;
+        for (int c = 0; c < 2; ++c) { Path ch = v; ch.push_back(c); pkey_of[ch] = key_of[v]; next.push_back(ch); }
+      }
+      frontier.swap(next);
+    }
+    CHECK(best_first(&split) == ref);
+    CHECK(split.size() <= 4 * ref.size() + 4);   // the growth cap of the device learner is 4 x the leaf budget
+  }
+}
+
+int main() {
+  TestFormatting();
+  TestPhilox();
+  TestQuantizeRow();
+  TestBinMapper();
+  TestTreeRoundTripAndPredict();
+  TestSplitMath();
+  TestLeafwiseKeys();
+  printf("%d checks, %d failed\n", g_checks, g_failed);
+  return g_failed == 0 ? 0 : 1;
+}

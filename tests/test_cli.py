@@ -44,3 +44,16 @@ def test_cli_train_predict_convert_refit(tmp_path):
     assert fb.Booster(model_file=str(tmp_path / "refit.txt")).num_trees() == 20
     _run(tmp_path, "task=save_binary", "data=train.csv")
     assert (tmp_path / "train.csv.bin").exists()
+
+
+def test_native_core_unit_tests_pass():
+    """The C++ unit tests of the core library (formatting, binning, tree round trip, split math, best-first order keys)."""
+    import subprocess
+    from pathlib import Path
+    import falcata_b200
+    from falcata_b200 import build as fbuild
+    fbuild.build()
+    exe = Path(falcata_b200.__file__).parent / "bin" / "falcata_core_tests"
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert " 0 failed" in r.stdout
