@@ -113,6 +113,10 @@ def _to_numpy_2d(data: Any) -> np.ndarray:
         data = _materialize_sequences(data)
     if _is_torch_tensor(data):
         data = data.detach().cpu().numpy()
+    if type(data).__module__.startswith("pyarrow") and hasattr(data, "column_names"):   # pyarrow Table / RecordBatch
+        data = np.column_stack([np.asarray(data.column(i).to_numpy(zero_copy_only=False) if hasattr(data.column(i), "to_numpy") else data.column(i)) for i in range(data.num_columns)])
+    if isinstance(data, list) and len(data) > 0 and all(isinstance(d, np.ndarray) and d.ndim == 2 for d in data):   # row chunks
+        data = np.concatenate(data, axis=0)
     if hasattr(data, "values") and not isinstance(data, np.ndarray):   # pandas
         data = data.values
     if hasattr(data, "toarray"):                                       # scipy sparse -> dense (device path is dense)
@@ -303,7 +307,9 @@ class Dataset:
             _safe_call(lib.FB_DatasetCreateFromMat(arr.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[arr.dtype], ctypes.c_int32(arr.shape[0]),
                                                    ctypes.c_int32(arr.shape[1]), row_major, _param_str(params), ref_handle, ctypes.byref(handle)))
             self._handle = handle
-            if hasattr(self.data, "columns") and self.feature_name == "auto":
+            if hasattr(self.data, "column_names") and self.feature_name == "auto":     # pyarrow
+                self.feature_name = [str(c) for c in self.data.column_names]
+            elif hasattr(self.data, "columns") and self.feature_name == "auto":        # pandas
                 self.feature_name = [str(c) for c in self.data.columns]
         if self.feature_name != "auto" and self.feature_name is not None:
             self.set_feature_name(self.feature_name)

@@ -126,3 +126,17 @@ def test_pickle_formats_sequence_input_and_sklearn_extras():
     assert clf.n_estimators_ == 8 and clf.n_iter_ == 8 and len(clf.feature_names_in_) == 5
     margin = clf.decision_function(X)
     assert np.array_equal(margin > 0, clf.predict(X) == 1)
+
+
+def test_arrow_table_and_array_chunks_as_input():
+    import pyarrow as pa
+    rng = np.random.default_rng(4)
+    X = rng.normal(size=(700, 4)).astype(np.float64)
+    y = (X[:, 0] > 0).astype(np.float32)
+    p = {"objective": "binary", "num_leaves": 7, "verbose": -1, "min_data_in_leaf": 5}
+    ref = fb.train(p, fb.Dataset(X, y), 4).model_to_string()
+    table = pa.table({f"f{i}": X[:, i] for i in range(4)})
+    from_arrow = fb.train(p, fb.Dataset(table, y), 4)
+    assert from_arrow.feature_name() == ["f0", "f1", "f2", "f3"]
+    assert np.array_equal(from_arrow.predict(X), fb.Booster(model_str=ref).predict(X))
+    assert fb.train(p, fb.Dataset([X[:300], X[300:]], y), 4).model_to_string() == ref
