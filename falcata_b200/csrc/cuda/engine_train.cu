@@ -356,7 +356,9 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     int enqueued = 0; bool records_ready = false;
     LevelCtrl hc;
     for (;;) {
-      const int batch = enqueued == 0 ? std::max(1, levels_hint_) : 1;
+      // leaf-wise trees vary in depth from tree to tree: enqueue a few levels past the last tree's depth (a level after
+      // the tree is complete is a handful of empty launches) rather than pay a host round trip per extra level
+      const int batch = enqueued == 0 ? std::max(1, levels_hint_ + (leafwise_ ? 3 : 0)) : (leafwise_ ? 4 : 1);
       for (int k = 0; k < batch; ++k) enqueue_level();
       const bool first = enqueued == 0;
       enqueued += batch;
@@ -603,9 +605,10 @@ void CudaEngine::ReadBackLevel(int num_leaves) {
 // order), h_leaves_ holds the final device leaves. The controller splits every node that best-first growth with the
 // leaf budget would split (and some more), so replaying best-first growth on the host over the device's splits
 // (largest gain among the current leaves, the order of the host leaf-wise learner) gives the exact tree; nodes the
-// device did not split count as unsplittable, which only matters when the growth cap was reached. The windows of
-// the tree's leaves (a pruned subtree keeps its root's window: later partitions only permute rows inside it)
-// replace the device leaf records, so the score update and the leaf renewal see the final tree.
+// device did not split count as unsplittable, which only matters when the growth cap was reached. The device
+// leaves tile the rows by position; after their rows are gathered into index buffer 0 a pruned subtree is the
+// contiguous range it covered when it was split, and these ranges replace the device leaf records, so the score
+// update and the leaf renewal see the final tree.
 // Parity: src/treelearner/cuda/learner.cpp:L2526-3067 (selective grow-then-prune with a host heap simulation).
 void CudaEngine::FinalizeLeafwise(const LevelCtrl& hc, Tree* tree) {
   struct Node { int parent = -1, left = -1, right = -1, journal = -1, dev_leaf = 0; bool is_left = true; };
@@ -642,6 +645,9 @@ void CudaEngine::FinalizeLeafwise(const LevelCtrl& hc, Tree* tree) {
     tree->internal_count[tree->num_leaves - 2] = s.parent_global;
     node_of_leaf[best] = n.left; node_of_leaf[right] = n.right;
   }
+  // every device leaf's rows into index buffer 0 (the device still holds the device-leaf records here), so that a
+  // pruned subtree's rows are the contiguous range its leaves cover
+  LaunchCollapseLeafWindows(leaves_.get(), LD, idx_[0].get(), idx_[1].get(), stream_);
   // leaf records of the final tree
   std::vector<LeafInfo> fin(tree->num_leaves);
   for (int t = 0; t < tree->num_leaves; ++t) {
@@ -658,6 +664,7 @@ void CudaEngine::FinalizeLeafwise(const LevelCtrl& hc, Tree* tree) {
       L.output = n.is_left ? ps.rec.left_out : ps.rec.right_out;
       if (n.is_left) { L.sum_gi = ps.rec.left_gi; L.sum_hi = ps.rec.left_hi; }
     }
+    L.buffer = 0;
     fin[t] = L;
     tree->leaf_count[t] = L.num_data_global;
   }

@@ -271,6 +271,7 @@ size_t GossSortTempBytes(int n);
 void LaunchGoss(const GossArgs& a, cudaStream_t s);
 
 // ----------------------------------------------------------------- score ----
+void LaunchCollapseLeafWindows(const LeafInfo* leaves, int num_leaves, int* idx0, const int* idx1, cudaStream_t s);
 void LaunchAddLeafOutputs(const LeafInfo* leaves, const double* leaf_value, int num_leaves, const int* idx0, const int* idx1, float* score, cudaStream_t s);
 void LaunchAddLeafOutputsFromRecords(const LeafInfo* leaves, const LevelCtrl* ctrl, double shrinkage, int max_leaves, const int* idx0, const int* idx1, float* score,
                                      cudaStream_t s);

@@ -22,6 +22,16 @@ __global__ void AddLeafOutputsKernel(const LeafInfo* __restrict__ leaves, const 
   for (int p = blockIdx.y * blockDim.x + threadIdx.x; p < L.count; p += gridDim.y * blockDim.x) score[idx[p]] += v;
 }
 
+// Leaf-wise growth: bring every leaf's rows into index buffer 0 at the leaf's own positions. The leaves tile the row
+// range by position, so afterwards the rows of ANY node of the tree are the contiguous range of buffer 0 that its
+// leaves cover - which is what a pruned subtree needs to become one leaf again.
+// Parity: src/treelearner/cuda/part.cu:L1846 (CollapseLeafWindowsKernel).
+__global__ void CollapseLeafWindowsKernel(const LeafInfo* __restrict__ leaves, int* __restrict__ idx0, const int* __restrict__ idx1) {
+  const LeafInfo L = leaves[blockIdx.x];
+  if (L.buffer == 0) return;
+  for (int p = blockIdx.y * blockDim.x + threadIdx.x; p < L.count; p += gridDim.y * blockDim.x) idx0[L.begin + p] = idx1[L.begin + p];
+}
+
 // The same update straight from the device's leaf records, enqueued behind the last level without waiting for the
 // host: leaf value = record output x shrinkage (what the host tree holds after Shrink). It applies itself only when
 // the controller reports the tree complete and split at least once; otherwise it does nothing and the host-side
@@ -201,6 +211,11 @@ void LaunchAddLeafOutputsFromRecords(const LeafInfo* leaves, const LevelCtrl* ct
                                      cudaStream_t s) {
   if (max_leaves <= 0) return;
   AddLeafOutputsFromRecordsKernel<<<dim3(max_leaves, 64), 256, 0, s>>>(leaves, ctrl, shrinkage, max_leaves, idx0, idx1, score);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+void LaunchCollapseLeafWindows(const LeafInfo* leaves, int num_leaves, int* idx0, const int* idx1, cudaStream_t s) {
+  if (num_leaves <= 0) return;
+  CollapseLeafWindowsKernel<<<dim3(num_leaves, 64), 256, 0, s>>>(leaves, idx0, idx1);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 int LeafGradSumSlices() { return kRenewSlices; }
