@@ -28,6 +28,7 @@ __global__ void __launch_bounds__(kCtrlThreads) LevelControllerKernel(CtrlArgs a
   __shared__ double s_gain[kCtrlMaxLeaves / 2];   // gains as doubles for exact comparison (frontier <= max_leaves, candidates <= max_leaves / 2 + ...)
   __shared__ int s_order[kCtrlMaxLeaves];
   __shared__ int s_chunks[kCtrlMaxLeaves / 2 + 1], s_blocks[kCtrlMaxLeaves / 2 + 1];
+  __shared__ double s_first[2 * kCtrlMaxLeaves + 2];   // leaf-wise growth: first order-key step of every evaluated node
   __shared__ int s_ncand, s_nkeep;
   LevelCtrl* c = a.ctrl;
   const int nfront = c->done ? 0 : c->frontier_count;
@@ -52,11 +53,24 @@ __global__ void __launch_bounds__(kCtrlThreads) LevelControllerKernel(CtrlArgs a
     }
     __syncthreads();
     const int total = base_eval + ncand;
-    for (int i = threadIdx.x; i < ncand; i += kCtrlThreads) {
-      double ki[4]; for (int k = 0; k < 4; ++k) ki[k] = a.eval_key[static_cast<size_t>(base_eval + i) * 4 + k];
-      int rank = 0;
-      for (int j = 0; j < total; ++j) rank += LeafwiseKeyBefore(a.eval_key + static_cast<size_t>(j) * 4, ki) ? 1 : 0;
-      s_order[i] = rank < a.leafwise_budget ? rank : 0x7fffffff;
+    // first key step of every evaluated node in shared memory: it decides nearly every comparison
+    for (int j = threadIdx.x; j < total; j += kCtrlThreads) s_first[j] = a.eval_key[static_cast<size_t>(j) * 4];
+    __syncthreads();
+    {
+      // one warp per candidate, the lanes stride over the evaluated nodes
+      const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+      for (int i = warp; i < ncand; i += kCtrlThreads / 32) {
+        double ki[4]; for (int k = 0; k < 4; ++k) ki[k] = a.eval_key[static_cast<size_t>(base_eval + i) * 4 + k];
+        int cnt = 0;
+        for (int j = lane; j < total; j += 32) {
+          const double pj = s_first[j];
+          bool before = pj > ki[0];
+          if (pj == ki[0]) before = LeafwiseKeyBefore(a.eval_key + static_cast<size_t>(j) * 4, ki);
+          cnt += before ? 1 : 0;
+        }
+        for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+        if (lane == 0) s_order[i] = cnt < a.leafwise_budget ? cnt : 0x7fffffff;
+      }
     }
     __syncthreads();
     unsigned int keep_bits = 0;   // this thread's decisions, one bit per stride step (written back after all ranks were read)
