@@ -42,6 +42,17 @@ def test_bit_identical_across_gpu_counts(tmp_path, quant):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_leafwise_growth_bit_identical_across_gpu_counts(tmp_path):
+    # exact leaf-wise growth: every rank's controller sees the same gathered best splits, over-grows the same
+    # nodes and the host replay keeps the same tree, so the model is the single-GPU model at any GPU count
+    extra = ("--grow-policy", "leaf", "--leaves", "63")
+    ref = _run(1, str(tmp_path / "m1.txt"), extra)
+    assert "Tree=4" in ref
+    for w in [w for w in (2, 4, 8) if w <= torch.cuda.device_count()]:
+        assert _run(w, str(tmp_path / f"m{w}.txt"), extra) == ref, f"model differs at {w} GPUs"
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("extra", [(), ("--categorical",)])
 def test_feature_parallel_matches_single_gpu(tmp_path, extra):
     # rows replicated, features split between the ranks, split bitmaps broadcast by the owner of the split
