@@ -26,6 +26,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--rows-scale", type=float, default=1.0)
     ap.add_argument("--plan", default="auto")
+    ap.add_argument("--grow-policy", default="level", choices=["level", "leaf"], help="level: gain-ranked budget per level; leaf: exact best-first trees")
     args = ap.parse_args()
 
     import numpy as np
@@ -77,7 +78,7 @@ def main() -> None:
         X, y, group = synthetic.ranking(nq, query_offset=qoff, device=dev)
         total = totalq * 100; off, n = qoff * 100, nq * 100
         p = {"objective": "lambdarank", "metric": "ndcg", "eval_at": "10", "num_leaves": 255}
-    p.update({"device_type": "cuda", "verbosity": -1, "cuda_plan": args.plan, "tree_learner": extra.get("tree_learner", "data" if world > 1 else "serial")})
+    p.update({"device_type": "cuda", "verbosity": -1, "cuda_plan": args.plan, "grow_policy": args.grow_policy, "tree_learner": extra.get("tree_learner", "data" if world > 1 else "serial")})
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     ds = fb.Dataset(X, y.cpu().numpy(), group=None if group is None else group.numpy(), params={"max_bin": p["max_bin"] if "max_bin" in p else 255, "enable_bundle": p.get("enable_bundle", True)})
