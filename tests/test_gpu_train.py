@@ -390,12 +390,22 @@ def test_leafwise_growth_on_device_is_the_host_best_first_tree(leaves):
     assert model_body(lvl.model_to_string()) != model_body(bg.model_to_string())
 
 
-def test_leafwise_growth_trains_and_scores_consistently():
+@pytest.mark.parametrize("extra", [{}, {"bagging_fraction": 0.6, "bagging_freq": 1}, {"quant_train_renew_leaf": True}, {"objective": "regression_l1"}])
+def test_leafwise_growth_trains_and_scores_consistently(extra):
     # several rounds: the score update runs through the final tree's leaf windows, so the training metric the
     # device reports must equal the metric of predict() on the same rows
     X, y = make_binary(40000, 16)
     p = {"objective": "binary", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": "stochastic", "grow_policy": "leaf",
-         "device_type": "cuda", "metric": "binary_logloss", "min_data_in_leaf": 20}
+         "device_type": "cuda", "metric": "binary_logloss", "min_data_in_leaf": 20, **extra}
+    if p["objective"] == "regression_l1":
+        # leaf outputs renewed by the objective (medians through the final tree's leaf windows)
+        p["metric"] = "l1"
+        ds = fb.Dataset(X, y, free_raw_data=False)
+        ev = {}
+        b = fb.train(p, ds, 20, valid_sets=[ds], valid_names=["train"], callbacks=[fb.record_evaluation(ev)])
+        assert abs(float(np.mean(np.abs(b.predict(X) - y))) - ev["train"]["l1"][-1]) < 1e-5
+        assert ev["train"]["l1"][-1] < 0.8 * ev["train"]["l1"][0]
+        return
     ds = fb.Dataset(X, y, free_raw_data=False)
     ev = {}
     b = fb.train(p, ds, 20, valid_sets=[ds], valid_names=["train"], callbacks=[fb.record_evaluation(ev)])
