@@ -313,12 +313,13 @@ class Dataset:
                 self.feature_name = [str(c) for c in self.data.columns]
         if self.feature_name != "auto" and self.feature_name is not None:
             self.set_feature_name(self.feature_name)
-        if self.label is not None:
-            self.set_label(self.label)
-        if self.weight is not None:
-            self.set_weight(self.weight)
-        if self.group is not None:
-            self.set_group(self.group)
+        if not getattr(self, "_early_fields", False):
+            if self.label is not None:
+                self.set_label(self.label)
+            if self.weight is not None:
+                self.set_weight(self.weight)
+            if self.group is not None:
+                self.set_group(self.group)
         if self.init_score is not None:
             self.set_init_score(self.init_score)
         elif self._predictor is not None and self.data is not None:
@@ -376,6 +377,9 @@ class Dataset:
         _safe_call(lib.FB_DatasetInitRows(handle, ctypes.c_int32(nrow), ctypes.c_int64(off), ctypes.c_int64(tot), 0))
         code = {torch.float32: 0, torch.float64: 1, torch.int8: 2, torch.int16: 3, torch.uint8: 4, torch.float16: 6, torch.int32: 7}[t.dtype]
         if whole:
+            # label / weight / group go into the dataset now: tens of milliseconds of host copies for millions of rows,
+            # hidden behind the matrix copy that is still in flight
+            self._set_early_fields()
             side.synchronize()
             _safe_call(lib.FB_DatasetBinDeviceChunk(handle, ctypes.c_void_p(Xd.data_ptr()), code, ctypes.c_int32(nrow), ctypes.c_int32(ncol), 0, ctypes.c_int32(nrow)))
         else:
@@ -388,6 +392,16 @@ class Dataset:
                 del chunk
         del Xd
         torch.cuda.synchronize()
+
+    def _set_early_fields(self) -> None:
+        """Set label, weight and group on the native dataset ahead of the end of construct(), which then skips them."""
+        if self.label is not None:
+            self.set_label(self.label)
+        if self.weight is not None:
+            self.set_weight(self.weight)
+        if self.group is not None:
+            self.set_group(self.group)
+        self._early_fields = True
 
     def _construct_sharded_host(self, arr: np.ndarray, params: Dict[str, Any]) -> None:
         """Host ingest of one row shard: the bin sample is drawn by GLOBAL row id and gathered over all
