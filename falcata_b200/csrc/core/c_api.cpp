@@ -216,7 +216,18 @@ int FB_DatasetSetField(DatasetHandle handle, const char* field_name, const void*
   ScopedTimer api_timer("FB_DatasetSetField");
   Dataset* ds = static_cast<Dataset*>(handle); const std::string f = field_name;
   auto as_float = [&](std::vector<float>* v) {
-    if (dtype == kF32) { v->assign(static_cast<const float*>(data), static_cast<const float*>(data) + n); return; }
+    if (dtype == kF32) {
+      // a fresh block of this size is page-faulted in on first touch, ~2 us a page on one thread: touch every page
+      // of the reserved block from all threads first, then copy
+      v->reserve(static_cast<size_t>(n));
+      float* raw = v->data();
+      if (raw != nullptr && n > (1 << 20)) {
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; i += 1024) raw[i] = 0.f;
+      }
+      v->assign(static_cast<const float*>(data), static_cast<const float*>(data) + n);
+      return;
+    }
     v->resize(n);
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; ++i) (*v)[i] = dtype == kF64 ? static_cast<float>(static_cast<const double*>(data)[i]) : static_cast<float>(static_cast<const int32_t*>(data)[i]);

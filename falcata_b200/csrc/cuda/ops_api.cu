@@ -141,7 +141,10 @@ int FB_OpBoundedWaitProbe(long long max_spins, int* out_status, int* out_flag_se
 int FB_OpBernoulliRowsDevice(int n, long long global_offset, unsigned int seed, double fraction, int* out_idx_device, int* out_count) {
   OPS_BEGIN();
   cudaStream_t s = 0;
-  DevBuf<uint8_t> mask; mask.Alloc(std::max(1, n)); DevBuf<int> chunk; chunk.Alloc(n / 1024 + 2); DevBuf<int> cnt; cnt.Alloc(1);
+  // scratch kept between calls: freeing device memory waits for every copy in flight on the device, and this draw
+  // runs while the caller's matrix is still on its way to the GPU
+  static thread_local DevBuf<uint8_t> mask; static thread_local DevBuf<int> chunk, cnt;
+  mask.Alloc(std::max(1, n)); chunk.Alloc(n / 1024 + 2); cnt.Alloc(1);
   BagArgs a = BagArgs();
   a.n = n; a.global_row_offset = static_cast<unsigned long long>(global_offset); a.round = 0x5A3Du; a.seed = seed; a.fraction = fraction; a.pos_fraction = a.neg_fraction = 1.0;
   a.mask = mask.get(); a.bag_idx = out_idx_device; a.chunk_count = chunk.get(); a.bag_count = cnt.get();
