@@ -118,9 +118,9 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     if (plan_.col_major_part) EnsureColumnMajor(dd_, stream_);
   }
   idx_[0].Alloc(n_); idx_[1].Alloc(n_);
-  leafwise_ = cfg.grow_policy == "leaf" && plan_.device_controller && cfg.num_leaves <= 512 && !voting_ && !feature_parallel_;
+  leafwise_ = cfg.grow_policy == "leaf" && plan_.device_controller && cfg.num_leaves <= 512 && !voting_;
   if (cfg.grow_policy == "leaf" && !leafwise_)
-    Log::Warning("grow_policy=leaf on the device needs the level controller, num_leaves <= 512 and tree_learner serial or data; growing level-wise with a gain-ranked leaf budget");
+    Log::Warning("grow_policy=leaf on the device needs the level controller, num_leaves <= 512 and tree_learner serial, data or feature; growing level-wise with a gain-ranked leaf budget");
   // leaf-wise: the device may grow past the budget (nodes that looked good enough when they were split); the cap bounds every buffer
   grow_leaves_ = leafwise_ ? std::min(1024, 4 * cfg.num_leaves) : cfg.num_leaves;
   const int NL = grow_leaves_;

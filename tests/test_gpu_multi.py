@@ -53,6 +53,14 @@ def test_leafwise_growth_bit_identical_across_gpu_counts(tmp_path):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_leafwise_growth_feature_parallel_matches_single_gpu(tmp_path):
+    extra = ("--grow-policy", "leaf", "--leaves", "63")
+    ref = _run(1, str(tmp_path / "m1.txt"), extra)
+    got = _run(2, str(tmp_path / "m2.txt"), ("--learner", "feature", *extra))
+    assert got == ref
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("extra", [(), ("--categorical",)])
 def test_feature_parallel_matches_single_gpu(tmp_path, extra):
     # rows replicated, features split between the ranks, split bitmaps broadcast by the owner of the split
