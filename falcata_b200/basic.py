@@ -973,6 +973,13 @@ class Booster:
         if pred_contrib:
             ptype = 3
         k = self.num_model_per_iteration()
+        if _is_cuda_array(data) and ptype in (0, 1) and cuda_available() and self._has_linear_trees():
+            # the traversal kernel has constant leaves only: linear leaves are evaluated on the host, the result goes back
+            import torch
+
+            t = data if _is_torch_tensor(data) else torch.as_tensor(data, device="cuda")
+            host = self.predict(t.detach().cpu().numpy(), start_iteration=start_iteration, num_iteration=num_iteration, raw_score=raw_score)
+            return torch.as_tensor(np.asarray(host, dtype=np.float32), device=t.device)
         if _is_cuda_array(data) and ptype in (0, 1) and cuda_available():
             import torch
 
@@ -1003,6 +1010,16 @@ class Booster:
         if out.size != nrow:
             return out.reshape(nrow, -1)
         return out
+
+    def _has_linear_trees(self) -> bool:
+        if self.train_set is not None:   # a training booster knows from its parameters
+            return _wants_linear(self.params or {})
+        cached = getattr(self, "_linear_cache", None)
+        n = self.num_trees()
+        if cached is None or cached[0] != n:
+            cached = (n, "is_linear=1" in self.model_to_string(num_iteration=-1))
+            self._linear_cache = cached
+        return cached[1]
 
     def refit(self, data: Any, label: Any, decay_rate: float = 0.9, **kwargs: Any) -> "Booster":
         leaf_preds = self.predict(data, pred_leaf=True).astype(np.int32)

@@ -413,3 +413,20 @@ def test_leafwise_growth_trains_and_scores_consistently(extra):
     ll = float(-np.mean(y * np.log(pr) + (1 - y) * np.log(1 - pr)))
     assert abs(ll - ev["train"]["binary_logloss"][-1]) < 1e-5
     assert auc(y, pr) > 0.9
+
+
+def test_linear_tree_with_cuda_inputs_falls_back_to_the_host():
+    # linear leaves are fitted and evaluated on the host; CUDA tensors and device_type=cuda are accepted all the same
+    rng = np.random.default_rng(0)
+    X = rng.normal(size=(6000, 5)).astype(np.float32)
+    y = np.where(X[:, 0] > 0, 2 * X[:, 1] + 1, -3 * X[:, 2]).astype(np.float32)
+    p = {"objective": "regression", "num_leaves": 8, "learning_rate": 0.2, "linear_tree": True, "verbosity": -1, "device_type": "cuda"}
+    Xd = torch.as_tensor(X, device="cuda")
+    b = fb.train(p, fb.Dataset(Xd, y, params=p), 20)
+    pd = b.predict(Xd)
+    assert pd.is_cuda and "is_linear=1" in b.model_to_string()
+    ph = b.predict(X)
+    assert np.allclose(pd.cpu().numpy(), ph, atol=1e-5)
+    assert float(np.mean((ph - y) ** 2)) < 0.05
+    reloaded = fb.Booster(model_str=b.model_to_string())
+    assert np.allclose(reloaded.predict(Xd).cpu().numpy(), ph, atol=1e-5)
