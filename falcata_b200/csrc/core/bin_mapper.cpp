@@ -108,22 +108,35 @@ inline bool NearlyEqualOrdered(double a, double b) {
 
 namespace {
 // Ascending sort of finite doubles. Large inputs take an LSD radix sort on the order-preserving integer image
-// of the IEEE bits (eight 8-bit digits; digits that are the same in every key, like the low mantissa bytes of
-// values that came from float32, are skipped): several times faster than a comparison sort on the 200k-value
-// columns of a bin sample, which is where ingest spends its host time.
+// of the IEEE bits, over the bit range that actually differs between the keys (values that came from float32 share
+// their low 29 mantissa bits) in 12-bit digits, with all digit histograms counted in one read and the two key
+// buffers kept per thread: about twice as fast as eight 8-bit passes on the 200k-value columns of a bin sample,
+// which is where ingest spends its host time.
 void SortValues(double* v, int n) {
   if (n < 4096) { std::sort(v, v + n); return; }
   if (std::is_sorted(v, v + n)) return;
-  std::vector<uint64_t> a(n), b(n);
-  for (int i = 0; i < n; ++i) { uint64_t u; memcpy(&u, &v[i], 8); a[i] = (u >> 63) ? ~u : (u | 0x8000000000000000ull); }
+  static thread_local std::vector<uint64_t> tl_a, tl_b;
+  std::vector<uint64_t>& a = tl_a; std::vector<uint64_t>& b = tl_b;
+  if (a.size() < static_cast<size_t>(n)) { a.resize(n); b.resize(n); }
+  uint64_t all_or = 0, all_and = ~0ull;
+  for (int i = 0; i < n; ++i) { uint64_t u; memcpy(&u, &v[i], 8); u = (u >> 63) ? ~u : (u | 0x8000000000000000ull); a[i] = u; all_or |= u; all_and &= u; }
+  const uint64_t diff = all_or ^ all_and;
+  if (diff == 0) return;
+  const int lo = __builtin_ctzll(diff), hi = 63 - __builtin_clzll(diff);
+  constexpr int kDigit = 12, kRadix = 1 << kDigit;
+  const int passes = (hi - lo + 1 + kDigit - 1) / kDigit;
+  std::vector<uint32_t> count(static_cast<size_t>(passes) * (kRadix + 1), 0);
+  for (int i = 0; i < n; ++i) {
+    const uint64_t u = a[i] >> lo;
+    for (int p = 0; p < passes; ++p) ++count[static_cast<size_t>(p) * (kRadix + 1) + ((u >> (p * kDigit)) & (kRadix - 1)) + 1];
+  }
   uint64_t* src = a.data(); uint64_t* dst = b.data();
-  for (int pass = 0; pass < 8; ++pass) {
-    const int shift = pass * 8;
-    uint32_t count[257] = {0};
-    for (int i = 0; i < n; ++i) ++count[((src[i] >> shift) & 255u) + 1];
-    if (count[((src[0] >> shift) & 255u) + 1] == static_cast<uint32_t>(n)) continue;   // all keys share this digit
-    for (int d = 0; d < 256; ++d) count[d + 1] += count[d];
-    for (int i = 0; i < n; ++i) dst[count[(src[i] >> shift) & 255u]++] = src[i];
+  for (int p = 0; p < passes; ++p) {
+    uint32_t* c = count.data() + static_cast<size_t>(p) * (kRadix + 1);
+    const int shift = lo + p * kDigit;
+    if (c[((src[0] >> shift) & (kRadix - 1)) + 1] == static_cast<uint32_t>(n)) continue;   // all keys share this digit
+    for (int d = 0; d < kRadix; ++d) c[d + 1] += c[d];
+    for (int i = 0; i < n; ++i) dst[c[(src[i] >> shift) & (kRadix - 1)]++] = src[i];
     std::swap(src, dst);
   }
   for (int i = 0; i < n; ++i) { uint64_t u = src[i]; u = (u >> 63) ? (u & 0x7FFFFFFFFFFFFFFFull) : ~u; memcpy(&v[i], &u, 8); }
