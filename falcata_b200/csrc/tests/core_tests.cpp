@@ -97,6 +97,24 @@ static void TestSplitMath() {
   CHECK(lo == -1.0 && ro == 1.0);   // clamped from -2 / +2
 }
 
+static void TestConfig() {
+  Config cfg;
+  cfg.Set(Config::Str2Map("n_estimators=37 num_leaf=15 eta=0.25 quant_mode=none monotone_constraints=1,-1,0 min_data=7 objective=binary"), false);
+  CHECK(cfg.num_iterations == 37 && cfg.num_leaves == 15 && cfg.learning_rate == 0.25 && cfg.min_data_in_leaf == 7);
+  CHECK(cfg.quant == QuantMode::None && cfg.objective == "binary");
+  Config q; q.Set(Config::Str2Map("quant_mode=fixedpoint quant_bins=64"), false);
+  CHECK(q.quant == QuantMode::FixedPoint && q.quant_bins == 64);
+  CHECK(cfg.monotone_vec.size() == 3 && cfg.monotone_vec[0] == 1 && cfg.monotone_vec[1] == -1 && cfg.monotone_vec[2] == 0);
+  Config depth; depth.Set(Config::Str2Map("num_leaves=255 max_depth=4"), false);
+  CHECK(depth.num_leaves == 16);   // a depth cap bounds the leaf count
+  bool threw = false;
+  try { Config bad; bad.Set(Config::Str2Map("grow_policy=sideways"), false); } catch (const std::exception&) { threw = true; }
+  CHECK(threw);
+  threw = false;   // quantized training and monotone constraints do not combine
+  try { Config bad; bad.Set(Config::Str2Map("quant_mode=stochastic monotone_constraints=1,0"), false); } catch (const std::exception&) { threw = true; }
+  CHECK(threw);
+}
+
 // Best-first growth over a random gain tree, against the rule of the level controller: a node is split while fewer
 // than B evaluated nodes sort strictly before it by the order key; replaying best-first over the split nodes must
 // then give exactly the best-first tree.
@@ -166,6 +184,7 @@ int main() {
   TestBinMapper();
   TestTreeRoundTripAndPredict();
   TestSplitMath();
+  TestConfig();
   TestLeafwiseKeys();
   printf("%d checks, %d failed\n", g_checks, g_failed);
   return g_failed == 0 ? 0 : 1;
