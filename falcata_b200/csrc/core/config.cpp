@@ -3,7 +3,16 @@
 // L409-649 (conflict checks); include/Falcata/falcata_plan.h:L164-258 (plan grammar).
 #include "fb/config.h"
 
+#include <omp.h>
+
 namespace fb {
+
+int RowThreads(long long rows) {
+  const long long want = rows / 4096 + 1;
+  const long long cap = omp_get_max_threads();
+  return static_cast<int>(want < cap ? want : cap);
+}
+
 
 namespace {
 template <typename T> void ParseInto(const std::string& v, T* out);

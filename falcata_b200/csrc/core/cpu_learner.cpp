@@ -274,7 +274,7 @@ void CPUTreeLearner::Quantize(const score_t* grad, const score_t* hess, int tree
   const float ig = 1.0f / gs, ih = 1.0f / hs;
   gh_packed_.resize(n);
   const uint32_t seed = static_cast<uint32_t>(cfg_.seed);
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) num_threads(RowThreads(n))
   for (data_size_t i = 0; i < n; ++i)
     gh_packed_[i] = QuantizeRow(grad[i], hess[i], ig, ih, qs_.stochastic, seed, static_cast<uint32_t>(tree_index), static_cast<uint64_t>(ds_->global_row_offset + i));
 }
@@ -581,7 +581,8 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
     // one record per feature on the worker threads, merged in feature order (SplitBetter is a total order, so the
     // result does not depend on the thread count)
     std::vector<SplitRecord> per(ds_->num_features);
-    const int nt = std::max(1, std::min(omp_get_max_threads(), ds_->num_features / 2));
+    // a thread per ~2048 histogram bins to scan: waking more workers than that costs more than the scan itself
+    const int nt = std::max(1, std::min(std::min(omp_get_max_threads(), ds_->num_features / 2), ds_->num_total_bin / 2048 + 1));
 #pragma omp parallel for schedule(dynamic, 1) num_threads(nt)
     for (int f = 0; f < ds_->num_features; ++f) {
       InitSplitRecord(&per[f]);

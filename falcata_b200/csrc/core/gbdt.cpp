@@ -94,7 +94,7 @@ void GBDT::AddTreeScore(const Tree* tree, const Dataset* ds, double* score, doub
   if (tree->num_leaves <= 1) { const double v = tree->leaf_value[0] * scale; for (data_size_t i = 0; i < ds->num_data; ++i) score[i] += v; return; }
   if (!ds->has_host_bins()) Log::Fatal("Host traversal needs host-resident bins");
   if (tree->is_linear && !ds->has_raw()) Log::Fatal("A linear tree needs the raw feature values of the dataset it scores (linear_tree=true in the Dataset params)");
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) num_threads(RowThreads(ds->num_data))
   for (data_size_t i = 0; i < ds->num_data; ++i) {
     int node = 0;
     while (node >= 0) {

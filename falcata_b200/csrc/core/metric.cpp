@@ -58,7 +58,7 @@ struct Pointwise : public MetricBase {
   bool HigherBetter() const override { return Loss::kHigherBetter; }
   std::vector<double> Eval(const double* score, const ObjectiveFunction* obj) const override {
     double s = 0;
-#pragma omp parallel for schedule(static) reduction(+ : s)
+#pragma omp parallel for schedule(static) reduction(+ : s) num_threads(RowThreads(n_))
     for (data_size_t i = 0; i < n_; ++i) {
       double v = score[i];
       if (convert_ && obj != nullptr) obj->ConvertOutput(&score[i], &v);
@@ -153,7 +153,7 @@ struct MultiLogloss : public MetricBase {
   bool HigherBetter() const override { return false; }
   std::vector<double> Eval(const double* score, const ObjectiveFunction* obj) const override {
     double s = 0;
-#pragma omp parallel for schedule(static) reduction(+ : s)
+#pragma omp parallel for schedule(static) reduction(+ : s) num_threads(RowThreads(n_))
     for (data_size_t i = 0; i < n_; ++i) {
       std::vector<double> raw(k_), p(k_);
       for (int c = 0; c < k_; ++c) raw[c] = score[static_cast<size_t>(c) * n_ + i];

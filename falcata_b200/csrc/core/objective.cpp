@@ -71,7 +71,7 @@ class RegressionL2 : public RegressionBase {
   using RegressionBase::RegressionBase;
   const char* GetName() const override { return "regression"; }
   void GetGradients(const double* s, score_t* g, score_t* h) const override {
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) num_threads(RowThreads(n_))
     for (data_size_t i = 0; i < n_; ++i) { const double w = weights_ ? weights_[i] : 1.0; g[i] = static_cast<score_t>((s[i] - label_[i]) * w); h[i] = static_cast<score_t>(w); }
   }
   bool IsConstantHessian() const override { return weights_ == nullptr; }
@@ -257,7 +257,7 @@ class BinaryLogloss : public ObjectiveFunction {
   }
   void GetGradients(const double* s, score_t* g, score_t* h) const override {
     if (!need_train_) { for (data_size_t i = 0; i < n_; ++i) { g[i] = 0; h[i] = 0; } return; }
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) num_threads(RowThreads(n_))
     for (data_size_t i = 0; i < n_; ++i) {
       const bool pos = is_pos_(label_[i]); const double y = pos ? 1.0 : -1.0, lw = lw_[pos ? 1 : 0] * (weights_ ? weights_[i] : 1.0);
       const double r = -y * sigmoid_ / (1.0 + std::exp(y * sigmoid_ * s[i])), ar = std::fabs(r);
@@ -269,7 +269,7 @@ class BinaryLogloss : public ObjectiveFunction {
     const double kScale = 1048576.0;
     int64_t acc[2] = {0, 0};
     { int64_t a0 = 0, a1 = 0;   // integer sums: the thread split cannot change the result
-#pragma omp parallel for schedule(static) reduction(+ : a0, a1)
+#pragma omp parallel for schedule(static) reduction(+ : a0, a1) num_threads(RowThreads(n_))
       for (data_size_t i = 0; i < n_; ++i) { const int64_t w = weights_ ? llround(weights_[i] * kScale) : 1048576; if (is_pos_(label_[i])) a0 += w; a1 += w; }
       acc[0] = a0; acc[1] = a1; }
     Network::SumInt64(acc, 2);
@@ -308,7 +308,7 @@ class MulticlassSoftmax : public ObjectiveFunction {
     for (int c = 0; c < k_; ++c) class_init_[c] = prob[c] / std::max(sw, kEpsilon);
   }
   void GetGradients(const double* s, score_t* g, score_t* h) const override {
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) num_threads(RowThreads(n_))
     for (data_size_t i = 0; i < n_; ++i) {
       std::vector<double> p(k_);
       double mx = s[i]; for (int c = 1; c < k_; ++c) mx = std::max(mx, s[static_cast<size_t>(c) * n_ + i]);

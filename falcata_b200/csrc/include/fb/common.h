@@ -69,6 +69,10 @@ class Log {
   }
 };
 
+// Worker threads for a loop over `rows` cheap items: one per ~4096 rows, at most the OpenMP maximum. On a host with a
+// hundred cores, waking every one of them for ten thousand rows costs far more than the loop.
+int RowThreads(long long rows);
+
 #define FB_CHECK(cond) do { if (!(cond)) ::fb::Log::Fatal("Check failed: " #cond " at %s:%d", __FILE__, __LINE__); } while (0)
 
 // ---------------------------------------------------------------- timers ----
