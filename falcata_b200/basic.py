@@ -297,6 +297,8 @@ class Dataset:
             self._handle = handle
         elif _is_cuda_array(self.data) and not _wants_linear(params, self.reference):
             self._construct_from_device(self.data, params, ref_handle)
+        elif hasattr(self.data, "tocsr") and not _wants_linear(params, self.reference) and self._global_rows is None:
+            self._construct_sparse_host(self.data, params, ref_handle)
         elif self._host_matrix_for_device(params, ref_handle):
             self._construct_host_via_device(params)
         elif self._global_rows is not None and ref_handle is None:
@@ -392,6 +394,39 @@ class Dataset:
                 del chunk
         del Xd
         torch.cuda.synchronize()
+
+    def _construct_sparse_host(self, sp: Any, params: Dict[str, Any], ref_handle: Any) -> None:
+        """scipy sparse matrix -> host bins without a dense copy of the whole matrix: the bin sample (the same draw by
+        row id as for a dense matrix) is densified on its own, then the rows are binned block by block.
+        Parity: src/c_api.cpp (dataset creation from CSR / CSC: sampled rows first, then pushed row blocks)."""
+        import torch
+
+        from .parallel import bootstrap
+
+        lib = _lib()
+        sp = sp.tocsr()
+        nrow, ncol = sp.shape
+        dt = np.float32 if sp.dtype == np.float32 else np.float64
+        handle = ctypes.c_void_p()
+        if ref_handle is not None:
+            _safe_call(lib.FB_DatasetCreateByReference(ref_handle, ctypes.byref(handle)))
+        else:
+            cnt = _resolved_int(params, "bin_construct_sample_cnt")
+            p = min(1.0, cnt / max(1, nrow))
+            idx = bootstrap._bernoulli_rows(torch.empty(0), nrow, 0, _resolved_int(params, "data_random_seed"), p).numpy()
+            if idx.size == 0:
+                idx = np.arange(min(nrow, 1))
+            sample = np.ascontiguousarray(sp[idx].toarray().astype(dt, copy=False))
+            _safe_call(lib.FB_DatasetCreateFromSampleTyped(sample.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[sample.dtype], ctypes.c_int32(sample.shape[0]),
+                                                           ctypes.c_int32(ncol), ctypes.c_int64(nrow), _param_str(params), None, 0, ctypes.byref(handle)))
+        self._handle = handle
+        _safe_call(lib.FB_DatasetInitRows(handle, ctypes.c_int32(nrow), ctypes.c_int64(0), ctypes.c_int64(nrow), 1))
+        block = max(1, min(nrow, (64 << 20) // max(1, ncol * np.dtype(dt).itemsize)))   # about 64 MB of dense rows at a time
+        for a in range(0, nrow, block):
+            b = min(nrow, a + block)
+            dense = np.ascontiguousarray(sp[a:b].toarray().astype(dt, copy=False))
+            _safe_call(lib.FB_DatasetPushRows(handle, dense.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[dense.dtype], ctypes.c_int32(b - a), ctypes.c_int32(ncol), 1,
+                                              ctypes.c_int32(a)))
 
     def _set_early_fields(self) -> None:
         """Set label, weight and group on the native dataset ahead of the end of construct(), which then skips them."""

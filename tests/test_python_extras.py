@@ -140,3 +140,20 @@ def test_arrow_table_and_array_chunks_as_input():
     assert from_arrow.feature_name() == ["f0", "f1", "f2", "f3"]
     assert np.array_equal(from_arrow.predict(X), fb.Booster(model_str=ref).predict(X))
     assert fb.train(p, fb.Dataset([X[:300], X[300:]], y), 4).model_to_string() == ref
+
+
+def test_sparse_input_is_binned_in_blocks_like_the_dense_matrix():
+    import scipy.sparse as sps
+    rng = np.random.default_rng(6)
+    X = rng.normal(size=(5000, 12)).astype(np.float64)
+    X[rng.random(X.shape) < 0.8] = 0.0
+    y = (X[:, 0] + X[:, 3] - X[:, 7] > 0).astype(np.float32)
+    p = {"objective": "binary", "num_leaves": 15, "verbose": -1, "min_data_in_leaf": 5}
+    dense = fb.train(p, fb.Dataset(X, y), 6)
+    for fmt in (sps.csr_matrix, sps.csc_matrix):
+        sp_ds = fb.Dataset(fmt(X), y)
+        valid = fb.Dataset(fmt(X[:500]), y[:500], reference=sp_ds)
+        ev = {}
+        b = fb.train(p, sp_ds, 6, valid_sets=[valid], valid_names=["v"], callbacks=[fb.record_evaluation(ev)])
+        assert b.model_to_string() == dense.model_to_string()
+        assert len(ev["v"]["binary_logloss"]) == 6
