@@ -5,6 +5,7 @@
 
 #include <fstream>
 #include <memory>
+#include <map>
 #include <mutex>
 
 #include "fb/gbdt.h"
@@ -409,6 +410,154 @@ int FB_BoosterPredictForMat(BoosterHandle handle, const void* data, int dtype, i
   b->gbdt->PredictMat(data, dtype, nrow, ncol, is_row_major != 0, predict_type, start_iteration, num_iteration, out_result);
   API_END();
 }
+// ---- single-row and sparse entry points --------------------------------------------------------------------
+// Parity: src/c_api.cpp (LGBM_BoosterPredictForMatSingleRow[Fast[Init]], LGBM_BoosterPredictForCSR, LGBM_DatasetCreateFromCSR,
+// LGBM_GetSampleCount, LGBM_SampleIndices, LGBM_DumpParamAliases, LGBM_BoosterValidateFeatureNames, LGBM_DatasetDumpText).
+int FB_BoosterPredictForMatSingleRow(BoosterHandle handle, const void* data, int dtype, int32_t ncol, int is_row_major, int predict_type, int start_iteration,
+                                     int num_iteration, const char* parameter, int64_t* out_len, double* out_result) {
+  return FB_BoosterPredictForMat(handle, data, dtype, 1, ncol, is_row_major, predict_type, start_iteration, num_iteration, parameter, out_len, out_result);
+}
+
+namespace {
+struct FastConfig { BoosterHandle booster; int predict_type, start_iteration, num_iteration, dtype; int32_t ncol; std::string parameter; };
+// rows [r0, r1) of a CSR matrix as a dense row-major double block
+void DensifyCSR(const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t r0, int64_t r1, int64_t num_col, std::vector<double>* out) {
+  out->assign(static_cast<size_t>(r1 - r0) * num_col, 0.0);
+  auto ptr = [&](int64_t i) -> int64_t { return indptr_type == kI32 ? static_cast<const int32_t*>(indptr)[i] : static_cast<const int64_t*>(indptr)[i]; };
+  for (int64_t r = r0; r < r1; ++r)
+    for (int64_t k = ptr(r); k < ptr(r + 1); ++k) {
+      const int32_t c = indices[k];
+      if (c < 0 || c >= num_col) continue;
+      (*out)[static_cast<size_t>(r - r0) * num_col + c] = data_type == kF32 ? static_cast<double>(static_cast<const float*>(data)[k]) : static_cast<const double*>(data)[k];
+    }
+}
+}  // namespace
+
+int FB_BoosterPredictForMatSingleRowFastInit(BoosterHandle handle, int predict_type, int start_iteration, int num_iteration, int dtype, int32_t ncol,
+                                             const char* parameter, void** out_fast_config) {
+  API_BEGIN();
+  FastConfig* fc = new FastConfig{handle, predict_type, start_iteration, num_iteration, dtype, ncol, parameter ? parameter : ""};
+  *out_fast_config = fc;
+  API_END();
+}
+int FB_BoosterPredictForMatSingleRowFast(void* fast_config, const void* data, int64_t* out_len, double* out_result) {
+  const FastConfig* fc = static_cast<const FastConfig*>(fast_config);
+  return FB_BoosterPredictForMat(fc->booster, data, fc->dtype, 1, fc->ncol, 1, fc->predict_type, fc->start_iteration, fc->num_iteration, fc->parameter.c_str(), out_len, out_result);
+}
+int FB_FastConfigFree(void* fast_config) { API_BEGIN(); delete static_cast<FastConfig*>(fast_config); API_END(); }
+
+int FB_BoosterPredictForCSR(BoosterHandle handle, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr,
+                            int64_t nelem, int64_t num_col, int predict_type, int start_iteration, int num_iteration, const char* parameter, int64_t* out_len,
+                            double* out_result) {
+  (void)nelem;
+  const int64_t nrow = nindptr - 1;
+  int64_t total = 0;
+  std::vector<double> block;
+  const int64_t step = std::max<int64_t>(1, (8 << 20) / std::max<int64_t>(1, num_col));
+  for (int64_t r0 = 0; r0 < nrow; r0 += step) {
+    const int64_t r1 = std::min(nrow, r0 + step);
+    try { DensifyCSR(indptr, indptr_type, indices, data, data_type, r0, r1, num_col, &block); } catch (std::exception& ex) { g_last_error = ex.what(); return -1; }
+    int64_t len = 0;
+    if (FB_BoosterPredictForMat(handle, block.data(), kF64, static_cast<int32_t>(r1 - r0), static_cast<int32_t>(num_col), 1, predict_type, start_iteration, num_iteration,
+                                parameter, &len, out_result + total) != 0) return -1;
+    total += len;
+  }
+  *out_len = total;
+  return 0;
+}
+
+int FB_DatasetCreateFromCSR(const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr, int64_t nelem,
+                            int64_t num_col, const char* parameters, const DatasetHandle reference, DatasetHandle* out) {
+  API_BEGIN();
+  (void)nelem;
+  const int32_t nrow = static_cast<int32_t>(nindptr - 1), ncol = static_cast<int32_t>(num_col);
+  Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());
+  std::unique_ptr<Dataset> ds(new Dataset());
+  std::vector<double> block;
+  if (reference != nullptr) ds->CopySchemaFrom(*static_cast<const Dataset*>(reference));
+  else {
+    // the same draw by row id as for a dense matrix, so a matrix gets the same bins in either form
+    const double frac = std::min(1.0, static_cast<double>(cfg.bin_construct_sample_cnt) / std::max(1, nrow));
+    std::vector<int> idx(static_cast<size_t>(std::max(1, nrow)));
+    int picked = 0;
+    if (FB_OpBernoulliRowsHost(nrow, 0, static_cast<unsigned int>(cfg.data_random_seed), frac, idx.data(), &picked) != 0) Log::Fatal("Row sampling failed");
+    idx.resize(picked);
+    if (idx.empty() && nrow > 0) idx.push_back(0);
+    std::vector<double> sample(static_cast<size_t>(idx.size()) * ncol), one;
+    for (size_t r = 0; r < idx.size(); ++r) { DensifyCSR(indptr, indptr_type, indices, data, data_type, idx[r], idx[r] + 1, ncol, &one); std::copy(one.begin(), one.end(), sample.begin() + r * ncol); }
+    ds->ConstructSchema(sample.data(), static_cast<int>(idx.size()), ncol, nrow, cfg, ParseCategorical(cfg, ncol));
+  }
+  ds->AllocateRows(nrow);
+  const int64_t step = std::max<int64_t>(1, (8 << 20) / std::max<int64_t>(1, num_col));
+  for (int64_t r0 = 0; r0 < nrow; r0 += step) {
+    const int64_t r1 = std::min<int64_t>(nrow, r0 + step);
+    DensifyCSR(indptr, indptr_type, indices, data, data_type, r0, r1, ncol, &block);
+    ds->PushDense(block.data(), kF64, static_cast<data_size_t>(r1 - r0), ncol, true, static_cast<data_size_t>(r0));
+  }
+  *out = ds.release();
+  API_END();
+}
+
+int FB_GetSampleCount(int32_t num_total_row, const char* parameters, int* out) {
+  API_BEGIN();
+  Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());
+  *out = std::min<int>(num_total_row, cfg.bin_construct_sample_cnt);
+  API_END();
+}
+// The rows of the bin sample (ascending): the counter-based draw by row id that every ingest path makes.
+int FB_SampleIndices(int32_t num_total_row, const char* parameters, void* out, int32_t* out_len) {
+  API_BEGIN();
+  Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());
+  const double frac = std::min(1.0, static_cast<double>(cfg.bin_construct_sample_cnt) / std::max(1, num_total_row));
+  int picked = 0;
+  if (FB_OpBernoulliRowsHost(num_total_row, 0, static_cast<unsigned int>(cfg.data_random_seed), frac, static_cast<int*>(out), &picked) != 0) Log::Fatal("Row sampling failed");
+  *out_len = picked;
+  API_END();
+}
+int FB_DumpParamAliases(int64_t buffer_len, int64_t* out_len, char* out_str) {
+  API_BEGIN();
+  std::map<std::string, std::vector<std::string>> by_name;
+  for (const auto& kv : Config::AliasTable()) by_name[kv.second].push_back(kv.first);
+  std::string s = "{";
+  bool first = true;
+  for (auto& kv : by_name) {
+    std::sort(kv.second.begin(), kv.second.end());
+    if (!first) s += ", ";
+    first = false;
+    s += "\"" + kv.first + "\": [";
+    for (size_t i = 0; i < kv.second.size(); ++i) { if (i) s += ", "; s += "\"" + kv.second[i] + "\""; }
+    s += "]";
+  }
+  s += "}";
+  *out_len = static_cast<int64_t>(s.size()) + 1;
+  if (buffer_len >= *out_len && out_str != nullptr) memcpy(out_str, s.c_str(), s.size() + 1);
+  API_END();
+}
+int FB_BoosterValidateFeatureNames(BoosterHandle handle, const char** data_names, int data_num_features) {
+  API_BEGIN(); BW();
+  const auto& names = b->gbdt->feature_names_;
+  if (static_cast<int>(names.size()) != data_num_features) Log::Fatal("Model was trained on %d features, but got %d input features to predict", static_cast<int>(names.size()), data_num_features);
+  for (int i = 0; i < data_num_features; ++i)
+    if (names[i] != data_names[i]) Log::Fatal("Expected '%s' at position %d but found '%s'", names[i].c_str(), i, data_names[i]);
+  API_END();
+}
+int FB_BoosterGetLinear(BoosterHandle handle, int* out) { API_BEGIN(); BW(); *out = b->config.linear_tree ? 1 : 0; API_END(); }
+int FB_DatasetGetFeatureNumBin(DatasetHandle handle, int feature, int* out) { return FB_DatasetFeatureNumBin(handle, feature, out); }
+int FB_DatasetDumpText(DatasetHandle handle, const char* filename) {
+  API_BEGIN();
+  const Dataset* ds = static_cast<const Dataset*>(handle);
+  if (!ds->has_host_bins()) Log::Fatal("Dataset has no host-resident bins to dump");
+  std::ofstream f(filename);
+  if (!f) Log::Fatal("Cannot write %s", filename);
+  f << "num_features: " << ds->num_features << "\nnum_total_features: " << ds->num_total_features << "\nnum_groups: " << ds->num_groups << "\nnum_data: " << ds->num_data << "\n";
+  f << "feature_names: "; for (auto& n : ds->feature_names) f << n << ", "; f << "\n";
+  for (data_size_t i = 0; i < ds->num_data; ++i) { for (int fi = 0; fi < ds->num_features; ++fi) f << ds->FeatureBin(i, fi) << ", "; f << "\n"; }
+  API_END();
+}
+int FB_SetLastError(const char* msg) { g_last_error = msg ? msg : ""; return 0; }
+int FB_GetMaxThreads(int* out) { return FB_GetNumThreads(out); }
+int FB_SetMaxThreads(int num_threads) { return FB_SetNumThreads(num_threads); }
+
 // Predict every row of a text data file (CSV / TSV / LibSVM) and write one line per row (tab-separated
 // values for multi-output predictions). Parity: src/c_api.cpp LGBM_BoosterPredictForFile, src/application/predictor.hpp.
 int FB_BoosterPredictForFile(BoosterHandle handle, const char* data_filename, int data_has_header, int predict_type, int start_iteration, int num_iteration,

@@ -113,6 +113,29 @@ int FB_BoosterGetLoadedParam(BoosterHandle handle, int64_t buffer_len, int64_t* 
 int FB_BoosterGpuLaunches(BoosterHandle handle, int64_t* out);
 int FB_BoosterStageReport(BoosterHandle handle, int64_t buffer_len, int64_t* out_len, char* out_str);
 
+/* single-row, sparse and introspection entry points */
+int FB_BoosterPredictForMatSingleRow(BoosterHandle handle, const void* data, int dtype, int32_t ncol, int is_row_major, int predict_type, int start_iteration,
+                                     int num_iteration, const char* parameter, int64_t* out_len, double* out_result);
+int FB_BoosterPredictForMatSingleRowFastInit(BoosterHandle handle, int predict_type, int start_iteration, int num_iteration, int dtype, int32_t ncol,
+                                             const char* parameter, void** out_fast_config);
+int FB_BoosterPredictForMatSingleRowFast(void* fast_config, const void* data, int64_t* out_len, double* out_result);
+int FB_FastConfigFree(void* fast_config);
+int FB_BoosterPredictForCSR(BoosterHandle handle, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr,
+                            int64_t nelem, int64_t num_col, int predict_type, int start_iteration, int num_iteration, const char* parameter, int64_t* out_len,
+                            double* out_result);
+int FB_DatasetCreateFromCSR(const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr, int64_t nelem,
+                            int64_t num_col, const char* parameters, const DatasetHandle reference, DatasetHandle* out);
+int FB_GetSampleCount(int32_t num_total_row, const char* parameters, int* out);
+int FB_SampleIndices(int32_t num_total_row, const char* parameters, void* out, int32_t* out_len);
+int FB_DumpParamAliases(int64_t buffer_len, int64_t* out_len, char* out_str);
+int FB_BoosterValidateFeatureNames(BoosterHandle handle, const char** data_names, int data_num_features);
+int FB_BoosterGetLinear(BoosterHandle handle, int* out);
+int FB_DatasetGetFeatureNumBin(DatasetHandle handle, int feature, int* out);
+int FB_DatasetDumpText(DatasetHandle handle, const char* filename);
+int FB_SetLastError(const char* msg);
+int FB_GetMaxThreads(int* out);
+int FB_SetMaxThreads(int num_threads);
+
 #ifdef __cplusplus
 }
 #endif

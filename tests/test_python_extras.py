@@ -157,3 +157,65 @@ def test_sparse_input_is_binned_in_blocks_like_the_dense_matrix():
         b = fb.train(p, sp_ds, 6, valid_sets=[valid], valid_names=["v"], callbacks=[fb.record_evaluation(ev)])
         assert b.model_to_string() == dense.model_to_string()
         assert len(ev["v"]["binary_logloss"]) == 6
+
+
+def test_c_api_single_row_csr_and_introspection(tmp_path):
+    import ctypes
+    import json
+    import scipy.sparse as sps
+    from falcata_b200.basic import _lib, _param_str
+
+    lib = _lib()
+    rng = np.random.default_rng(8)
+    X = rng.normal(size=(2000, 6)).astype(np.float64)
+    X[rng.random(X.shape) < 0.6] = 0.0
+    y = (X[:, 0] - X[:, 2] > 0).astype(np.float32)
+    p = {"objective": "binary", "num_leaves": 7, "verbose": -1, "min_data_in_leaf": 5}
+    b = fb.train(p, fb.Dataset(X, y), 5)
+    ref = b.predict(X)
+    # single row, plain and with a prepared configuration
+    out = (ctypes.c_double * 1)(); n = ctypes.c_int64(0)
+    row = np.ascontiguousarray(X[3])
+    assert lib.FB_BoosterPredictForMatSingleRow(b._handle, row.ctypes.data_as(ctypes.c_void_p), 1, 6, 1, 0, 0, -1, b"", ctypes.byref(n), out) == 0
+    assert n.value == 1 and abs(out[0] - ref[3]) < 1e-12
+    fc = ctypes.c_void_p()
+    assert lib.FB_BoosterPredictForMatSingleRowFastInit(b._handle, 0, 0, -1, 1, 6, b"", ctypes.byref(fc)) == 0
+    for i in (0, 17, 1999):
+        row = np.ascontiguousarray(X[i])
+        assert lib.FB_BoosterPredictForMatSingleRowFast(fc, row.ctypes.data_as(ctypes.c_void_p), ctypes.byref(n), out) == 0
+        assert abs(out[0] - ref[i]) < 1e-12
+    assert lib.FB_FastConfigFree(fc) == 0
+    # CSR predict and CSR dataset
+    sp = sps.csr_matrix(X)
+    indptr = sp.indptr.astype(np.int32); indices = sp.indices.astype(np.int32); data = sp.data.astype(np.float64)
+    res = np.zeros(2000, dtype=np.float64)
+    assert lib.FB_BoosterPredictForCSR(b._handle, indptr.ctypes.data_as(ctypes.c_void_p), 7, indices.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)),
+                                       data.ctypes.data_as(ctypes.c_void_p), 1, ctypes.c_int64(len(indptr)), ctypes.c_int64(len(data)), ctypes.c_int64(6), 0, 0, -1, b"",
+                                       ctypes.byref(n), res.ctypes.data_as(ctypes.POINTER(ctypes.c_double))) == 0
+    assert n.value == 2000 and np.allclose(res, ref, atol=1e-12)
+    h = ctypes.c_void_p()
+    assert lib.FB_DatasetCreateFromCSR(indptr.ctypes.data_as(ctypes.c_void_p), 7, indices.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), data.ctypes.data_as(ctypes.c_void_p), 1,
+                                       ctypes.c_int64(len(indptr)), ctypes.c_int64(len(data)), ctypes.c_int64(6), _param_str({}), None, ctypes.byref(h)) == 0
+    nb = ctypes.c_int(0)
+    assert lib.FB_DatasetGetFeatureNumBin(h, 0, ctypes.byref(nb)) == 0 and nb.value == fb.Dataset(X, y).feature_num_bin(0)
+    dump = tmp_path / "ds.txt"
+    assert lib.FB_DatasetDumpText(h, str(dump).encode()) == 0 and "num_data: 2000" in dump.read_text()
+    lib.FB_DatasetFree(h)
+    # sample, aliases, feature-name check
+    cnt = ctypes.c_int(0)
+    assert lib.FB_GetSampleCount(5000, _param_str({"bin_construct_sample_cnt": 1000}), ctypes.byref(cnt)) == 0 and cnt.value == 1000
+    idx = np.zeros(5000, dtype=np.int32); k = ctypes.c_int32(0)
+    assert lib.FB_SampleIndices(5000, _param_str({"bin_construct_sample_cnt": 1000}), idx.ctypes.data_as(ctypes.c_void_p), ctypes.byref(k)) == 0
+    assert 800 < k.value < 1200 and np.all(np.diff(idx[: k.value]) > 0)
+    need = ctypes.c_int64(0)
+    lib.FB_DumpParamAliases(ctypes.c_int64(0), ctypes.byref(need), None)
+    buf = ctypes.create_string_buffer(need.value)
+    assert lib.FB_DumpParamAliases(ctypes.c_int64(need.value), ctypes.byref(need), buf) == 0
+    aliases = json.loads(buf.value.decode())
+    assert "n_estimators" in aliases["num_iterations"] and "eta" in aliases["learning_rate"]
+    names = (ctypes.c_char_p * 6)(*[f"Column_{i}".encode() for i in range(6)])
+    assert lib.FB_BoosterValidateFeatureNames(b._handle, names, 6) == 0
+    names[2] = b"other"
+    assert lib.FB_BoosterValidateFeatureNames(b._handle, names, 6) != 0
+    lin = ctypes.c_int(-1)
+    assert lib.FB_BoosterGetLinear(b._handle, ctypes.byref(lin)) == 0 and lin.value == 0
