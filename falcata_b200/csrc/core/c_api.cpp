@@ -498,6 +498,79 @@ int FB_DatasetCreateFromCSR(const void* indptr, int indptr_type, const int32_t* 
   API_END();
 }
 
+namespace {
+// column-compressed -> row-compressed (32-bit row pointers are enough below 2^31 elements; 64-bit ones are kept otherwise)
+void CscToCsr(const void* col_ptr, int col_ptr_type, const int32_t* indices, const void* data, int data_type, int64_t ncol_ptr, int64_t nelem, int64_t num_row,
+              std::vector<int64_t>* indptr, std::vector<int32_t>* out_idx, std::vector<double>* out_val) {
+  auto ptr = [&](int64_t i) -> int64_t { return col_ptr_type == kI32 ? static_cast<const int32_t*>(col_ptr)[i] : static_cast<const int64_t*>(col_ptr)[i]; };
+  indptr->assign(static_cast<size_t>(num_row) + 1, 0);
+  for (int64_t k = 0; k < nelem; ++k) { const int32_t r = indices[k]; if (r >= 0 && r < num_row) ++(*indptr)[r + 1]; }
+  for (int64_t r = 0; r < num_row; ++r) (*indptr)[r + 1] += (*indptr)[r];
+  out_idx->resize(static_cast<size_t>(nelem)); out_val->resize(static_cast<size_t>(nelem));
+  std::vector<int64_t> cursor(indptr->begin(), indptr->end() - 1);
+  for (int64_t c = 0; c + 1 < ncol_ptr; ++c)
+    for (int64_t k = ptr(c); k < ptr(c + 1); ++k) {
+      const int32_t r = indices[k];
+      if (r < 0 || r >= num_row) continue;
+      const int64_t at = cursor[r]++;
+      (*out_idx)[at] = static_cast<int32_t>(c);
+      (*out_val)[at] = data_type == kF32 ? static_cast<double>(static_cast<const float*>(data)[k]) : static_cast<const double*>(data)[k];
+    }
+}
+constexpr int kI64 = 8;   // row-pointer type code of the CSR entry points for 64-bit pointers (anything but kI32)
+}  // namespace
+
+int FB_DatasetCreateFromCSC(const void* col_ptr, int col_ptr_type, const int32_t* indices, const void* data, int data_type, int64_t ncol_ptr, int64_t nelem,
+                            int64_t num_row, const char* parameters, const DatasetHandle reference, DatasetHandle* out) {
+  std::vector<int64_t> indptr; std::vector<int32_t> idx; std::vector<double> val;
+  try { CscToCsr(col_ptr, col_ptr_type, indices, data, data_type, ncol_ptr, nelem, num_row, &indptr, &idx, &val); } catch (std::exception& ex) { g_last_error = ex.what(); return -1; }
+  return FB_DatasetCreateFromCSR(indptr.data(), kI64, idx.data(), val.data(), kF64, num_row + 1, nelem, ncol_ptr - 1, parameters, reference, out);
+}
+int FB_BoosterPredictForCSC(BoosterHandle handle, const void* col_ptr, int col_ptr_type, const int32_t* indices, const void* data, int data_type, int64_t ncol_ptr,
+                            int64_t nelem, int64_t num_row, int predict_type, int start_iteration, int num_iteration, const char* parameter, int64_t* out_len,
+                            double* out_result) {
+  std::vector<int64_t> indptr; std::vector<int32_t> idx; std::vector<double> val;
+  try { CscToCsr(col_ptr, col_ptr_type, indices, data, data_type, ncol_ptr, nelem, num_row, &indptr, &idx, &val); } catch (std::exception& ex) { g_last_error = ex.what(); return -1; }
+  return FB_BoosterPredictForCSR(handle, indptr.data(), kI64, idx.data(), val.data(), kF64, num_row + 1, nelem, ncol_ptr - 1, predict_type, start_iteration, num_iteration,
+                                 parameter, out_len, out_result);
+}
+// Several row blocks that together form one matrix (all row-major or all column-major, same element type).
+int FB_BoosterPredictForMats(BoosterHandle handle, const void** data, int dtype, int32_t nmat, const int32_t* nrow, int32_t ncol, int is_row_major, int predict_type,
+                             int start_iteration, int num_iteration, const char* parameter, int64_t* out_len, double* out_result) {
+  int64_t total = 0;
+  for (int32_t m = 0; m < nmat; ++m) {
+    int64_t len = 0;
+    if (FB_BoosterPredictForMat(handle, data[m], dtype, nrow[m], ncol, is_row_major, predict_type, start_iteration, num_iteration, parameter, &len, out_result + total) != 0) return -1;
+    total += len;
+  }
+  *out_len = total;
+  return 0;
+}
+int FB_DatasetCreateFromMats(int32_t nmat, const void** data, int dtype, const int32_t* nrow, int32_t ncol, int is_row_major, const char* parameters,
+                             const DatasetHandle reference, DatasetHandle* out) {
+  API_BEGIN();
+  // the blocks are read as one row-major double matrix (a copy; the single-matrix entry point then does the rest)
+  int64_t total = 0; for (int32_t m = 0; m < nmat; ++m) total += nrow[m];
+  std::vector<double> all(static_cast<size_t>(total) * ncol);
+  int64_t at = 0;
+  for (int32_t m = 0; m < nmat; ++m) {
+    for (int32_t i = 0; i < nrow[m]; ++i) for (int32_t j = 0; j < ncol; ++j) {
+      const size_t src = is_row_major ? static_cast<size_t>(i) * ncol + j : static_cast<size_t>(j) * nrow[m] + i;
+      double v;
+      switch (dtype) {
+        case kF32: v = static_cast<const float*>(data[m])[src]; break;
+        case kF64: v = static_cast<const double*>(data[m])[src]; break;
+        case kI32: v = static_cast<const int32_t*>(data[m])[src]; break;
+        default: Log::Fatal("FB_DatasetCreateFromMats takes float32, float64 or int32 blocks"); v = 0;
+      }
+      all[static_cast<size_t>(at + i) * ncol + j] = v;
+    }
+    at += nrow[m];
+  }
+  if (FB_DatasetCreateFromMat(all.data(), kF64, static_cast<int32_t>(total), ncol, 1, parameters, reference, out) != 0) throw std::runtime_error(g_last_error);
+  API_END();
+}
+
 int FB_GetSampleCount(int32_t num_total_row, const char* parameters, int* out) {
   API_BEGIN();
   Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());

@@ -125,6 +125,15 @@ int FB_BoosterPredictForCSR(BoosterHandle handle, const void* indptr, int indptr
                             double* out_result);
 int FB_DatasetCreateFromCSR(const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr, int64_t nelem,
                             int64_t num_col, const char* parameters, const DatasetHandle reference, DatasetHandle* out);
+int FB_DatasetCreateFromCSC(const void* col_ptr, int col_ptr_type, const int32_t* indices, const void* data, int data_type, int64_t ncol_ptr, int64_t nelem,
+                            int64_t num_row, const char* parameters, const DatasetHandle reference, DatasetHandle* out);
+int FB_BoosterPredictForCSC(BoosterHandle handle, const void* col_ptr, int col_ptr_type, const int32_t* indices, const void* data, int data_type, int64_t ncol_ptr,
+                            int64_t nelem, int64_t num_row, int predict_type, int start_iteration, int num_iteration, const char* parameter, int64_t* out_len,
+                            double* out_result);
+int FB_BoosterPredictForMats(BoosterHandle handle, const void** data, int dtype, int32_t nmat, const int32_t* nrow, int32_t ncol, int is_row_major, int predict_type,
+                             int start_iteration, int num_iteration, const char* parameter, int64_t* out_len, double* out_result);
+int FB_DatasetCreateFromMats(int32_t nmat, const void** data, int dtype, const int32_t* nrow, int32_t ncol, int is_row_major, const char* parameters,
+                             const DatasetHandle reference, DatasetHandle* out);
 int FB_GetSampleCount(int32_t num_total_row, const char* parameters, int* out);
 int FB_SampleIndices(int32_t num_total_row, const char* parameters, void* out, int32_t* out_len);
 int FB_DumpParamAliases(int64_t buffer_len, int64_t* out_len, char* out_str);

@@ -201,6 +201,30 @@ def test_c_api_single_row_csr_and_introspection(tmp_path):
     dump = tmp_path / "ds.txt"
     assert lib.FB_DatasetDumpText(h, str(dump).encode()) == 0 and "num_data: 2000" in dump.read_text()
     lib.FB_DatasetFree(h)
+    # CSC forms and row blocks
+    sc = sps.csc_matrix(X)
+    cptr = sc.indptr.astype(np.int32); cidx = sc.indices.astype(np.int32); cval = sc.data.astype(np.float64)
+    res2 = np.zeros(2000, dtype=np.float64)
+    assert lib.FB_BoosterPredictForCSC(b._handle, cptr.ctypes.data_as(ctypes.c_void_p), 7, cidx.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)),
+                                       cval.ctypes.data_as(ctypes.c_void_p), 1, ctypes.c_int64(len(cptr)), ctypes.c_int64(len(cval)), ctypes.c_int64(2000), 0, 0, -1, b"",
+                                       ctypes.byref(n), res2.ctypes.data_as(ctypes.POINTER(ctypes.c_double))) == 0
+    assert n.value == 2000 and np.allclose(res2, ref, atol=1e-12)
+    h2 = ctypes.c_void_p()
+    assert lib.FB_DatasetCreateFromCSC(cptr.ctypes.data_as(ctypes.c_void_p), 7, cidx.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), cval.ctypes.data_as(ctypes.c_void_p), 1,
+                                       ctypes.c_int64(len(cptr)), ctypes.c_int64(len(cval)), ctypes.c_int64(2000), _param_str({}), None, ctypes.byref(h2)) == 0
+    nd = ctypes.c_int32(0)
+    assert lib.FB_DatasetGetNumData(h2, ctypes.byref(nd)) == 0 and nd.value == 2000
+    lib.FB_DatasetFree(h2)
+    parts = [np.ascontiguousarray(X[:700]), np.ascontiguousarray(X[700:])]
+    ptrs = (ctypes.c_void_p * 2)(parts[0].ctypes.data, parts[1].ctypes.data)
+    rows = (ctypes.c_int32 * 2)(700, 1300)
+    res3 = np.zeros(2000, dtype=np.float64)
+    assert lib.FB_BoosterPredictForMats(b._handle, ptrs, 1, 2, rows, 6, 1, 0, 0, -1, b"", ctypes.byref(n), res3.ctypes.data_as(ctypes.POINTER(ctypes.c_double))) == 0
+    assert np.allclose(res3, ref, atol=1e-12)
+    h3 = ctypes.c_void_p()
+    assert lib.FB_DatasetCreateFromMats(2, ptrs, 1, rows, 6, 1, _param_str({}), None, ctypes.byref(h3)) == 0
+    assert lib.FB_DatasetGetNumData(h3, ctypes.byref(nd)) == 0 and nd.value == 2000
+    lib.FB_DatasetFree(h3)
     # sample, aliases, feature-name check
     cnt = ctypes.c_int(0)
     assert lib.FB_GetSampleCount(5000, _param_str({"bin_construct_sample_cnt": 1000}), ctypes.byref(cnt)) == 0 and cnt.value == 1000
