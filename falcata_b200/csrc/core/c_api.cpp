@@ -571,6 +571,64 @@ int FB_DatasetCreateFromMats(int32_t nmat, const void** data, int dtype, const i
   API_END();
 }
 
+// ---- streaming: rows and their metadata arrive in blocks, in any order of blocks --------------------------------
+// Parity: src/c_api.cpp (LGBM_DatasetInitStreaming, LGBM_DatasetPushRowsWithMetadata, LGBM_DatasetMarkFinished). The
+// dataset comes from FB_DatasetCreateByReference / FB_DatasetCreateFromSampleTyped and FB_DatasetInitRows(host_bins=1).
+namespace {
+struct StreamState { std::vector<int32_t> query_of_row; int nclasses = 1; };
+std::mutex g_stream_mu;
+std::map<const Dataset*, StreamState> g_stream;
+}  // namespace
+
+int FB_DatasetInitStreaming(DatasetHandle handle, int32_t has_weights, int32_t has_init_scores, int32_t has_queries, int32_t nclasses) {
+  API_BEGIN();
+  Dataset* ds = static_cast<Dataset*>(handle);
+  if (!ds->has_host_bins()) Log::Fatal("Streaming needs host bins: call FB_DatasetInitRows(handle, nrow, 0, 0, 1) first");
+  const size_t n = static_cast<size_t>(ds->num_data);
+  ds->metadata.label.assign(n, 0.f);
+  if (has_weights) ds->metadata.weights.assign(n, 1.f);
+  if (has_init_scores) ds->metadata.init_score.assign(n * std::max(1, nclasses), 0.0);
+  std::lock_guard<std::mutex> g(g_stream_mu);
+  StreamState& st = g_stream[ds];
+  st.nclasses = std::max(1, nclasses);
+  if (has_queries) st.query_of_row.assign(n, 0); else st.query_of_row.clear();
+  API_END();
+}
+int FB_DatasetPushRowsWithMetadata(DatasetHandle handle, const void* data, int dtype, int32_t nrow, int32_t ncol, int32_t start_row, const float* label,
+                                   const float* weight, const double* init_score, const int32_t* query) {
+  API_BEGIN();
+  Dataset* ds = static_cast<Dataset*>(handle);
+  if (start_row < 0 || static_cast<int64_t>(start_row) + nrow > ds->num_data) Log::Fatal("Pushed rows [%d, %d) are outside the dataset (%d rows)", start_row, start_row + nrow, ds->num_data);
+  ds->PushDense(data, dtype, nrow, ncol, true, start_row);
+  if (label != nullptr) std::copy(label, label + nrow, ds->metadata.label.begin() + start_row);
+  if (weight != nullptr && !ds->metadata.weights.empty()) std::copy(weight, weight + nrow, ds->metadata.weights.begin() + start_row);
+  std::lock_guard<std::mutex> g(g_stream_mu);
+  StreamState& st = g_stream[ds];
+  if (init_score != nullptr && !ds->metadata.init_score.empty())   // block layout: class-major within the pushed block
+    for (int k = 0; k < st.nclasses; ++k) std::copy(init_score + static_cast<size_t>(k) * nrow, init_score + static_cast<size_t>(k + 1) * nrow,
+                                                     ds->metadata.init_score.begin() + static_cast<size_t>(k) * ds->num_data + start_row);
+  if (query != nullptr && !st.query_of_row.empty()) std::copy(query, query + nrow, st.query_of_row.begin() + start_row);
+  API_END();
+}
+int FB_DatasetMarkFinished(DatasetHandle handle) {
+  API_BEGIN();
+  Dataset* ds = static_cast<Dataset*>(handle);
+  std::lock_guard<std::mutex> g(g_stream_mu);
+  auto it = g_stream.find(ds);
+  if (it != g_stream.end()) {
+    const auto& q = it->second.query_of_row;
+    if (!q.empty()) {   // consecutive rows with the same query id form one query
+      std::vector<int32_t> sizes;
+      for (size_t i = 0; i < q.size(); ++i) { if (i == 0 || q[i] != q[i - 1]) sizes.push_back(0); ++sizes.back(); }
+      ds->metadata.num_data = ds->num_data;
+      ds->metadata.SetGroup(sizes.data(), static_cast<data_size_t>(sizes.size()));
+    }
+    g_stream.erase(it);
+  }
+  ds->metadata.UpdateQueryWeights();
+  API_END();
+}
+
 int FB_GetSampleCount(int32_t num_total_row, const char* parameters, int* out) {
   API_BEGIN();
   Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());

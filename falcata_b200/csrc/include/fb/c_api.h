@@ -134,6 +134,11 @@ int FB_BoosterPredictForMats(BoosterHandle handle, const void** data, int dtype,
                              int start_iteration, int num_iteration, const char* parameter, int64_t* out_len, double* out_result);
 int FB_DatasetCreateFromMats(int32_t nmat, const void** data, int dtype, const int32_t* nrow, int32_t ncol, int is_row_major, const char* parameters,
                              const DatasetHandle reference, DatasetHandle* out);
+/* streaming ingest: FB_DatasetCreateByReference / ...FromSampleTyped, FB_DatasetInitRows(host_bins=1), then these */
+int FB_DatasetInitStreaming(DatasetHandle handle, int32_t has_weights, int32_t has_init_scores, int32_t has_queries, int32_t nclasses);
+int FB_DatasetPushRowsWithMetadata(DatasetHandle handle, const void* data, int dtype, int32_t nrow, int32_t ncol, int32_t start_row, const float* label,
+                                   const float* weight, const double* init_score, const int32_t* query);
+int FB_DatasetMarkFinished(DatasetHandle handle);
 int FB_GetSampleCount(int32_t num_total_row, const char* parameters, int* out);
 int FB_SampleIndices(int32_t num_total_row, const char* parameters, void* out, int32_t* out_len);
 int FB_DumpParamAliases(int64_t buffer_len, int64_t* out_len, char* out_str);

@@ -243,3 +243,30 @@ def test_c_api_single_row_csr_and_introspection(tmp_path):
     assert lib.FB_BoosterValidateFeatureNames(b._handle, names, 6) != 0
     lin = ctypes.c_int(-1)
     assert lib.FB_BoosterGetLinear(b._handle, ctypes.byref(lin)) == 0 and lin.value == 0
+
+
+def test_c_api_streaming_push_matches_one_shot_dataset():
+    import ctypes
+    from falcata_b200.basic import _lib
+
+    lib = _lib()
+    rng = np.random.default_rng(9)
+    X = rng.normal(size=(3000, 5)).astype(np.float64)
+    y = (X[:, 0] + X[:, 1] > 0).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, size=3000).astype(np.float32)
+    p = {"objective": "binary", "num_leaves": 7, "verbose": -1, "min_data_in_leaf": 5}
+    base = fb.Dataset(X, y, weight=w).construct()
+    ref_model = fb.train(p, base, 4).model_to_string()
+    h = ctypes.c_void_p()
+    assert lib.FB_DatasetCreateByReference(base._handle, ctypes.byref(h)) == 0
+    assert lib.FB_DatasetInitRows(h, 3000, ctypes.c_int64(0), ctypes.c_int64(3000), 1) == 0
+    assert lib.FB_DatasetInitStreaming(h, 1, 0, 0, 1) == 0
+    for a, b_ in ((2000, 3000), (0, 900), (900, 2000)):      # blocks in any order
+        blk = np.ascontiguousarray(X[a:b_]); yb = np.ascontiguousarray(y[a:b_]); wb = np.ascontiguousarray(w[a:b_])
+        assert lib.FB_DatasetPushRowsWithMetadata(h, blk.ctypes.data_as(ctypes.c_void_p), 1, b_ - a, 5, a, yb.ctypes.data_as(ctypes.POINTER(ctypes.c_float)),
+                                                  wb.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), None, None) == 0
+    assert lib.FB_DatasetMarkFinished(h) == 0
+    streamed = fb.Dataset.__new__(fb.Dataset)
+    fb.Dataset.__init__(streamed, None)
+    streamed._handle = h
+    assert fb.train(p, streamed, 4).model_to_string() == ref_model
