@@ -831,6 +831,14 @@ class Booster:
 
         if _bs.peer_check_enabled():
             _bs.assert_peers_alive()   # multi-rank: never enqueue a round that would wait for a rank that has left
+        if train_set is not None and train_set is not self.train_set:
+            if not isinstance(train_set, Dataset):
+                raise TypeError(f"Training data should be Dataset instance, met {type(train_set).__name__}")
+            if train_set.reference is None and self.train_set is not None:
+                train_set.reference = self.train_set   # same bin mappers as the data the trees were grown on
+            _safe_call(lib.FB_BoosterResetTrainingData(self._handle, train_set.construct()._handle))
+            self.train_set = train_set
+            self.valid_sets = []; self.name_valid_sets = []
         if fobj is None:
             _safe_call(lib.FB_BoosterUpdateOneIter(self._handle, ctypes.byref(fin)))
             return fin.value == 1

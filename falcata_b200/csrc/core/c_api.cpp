@@ -672,6 +672,19 @@ int FB_BoosterValidateFeatureNames(BoosterHandle handle, const char** data_names
     if (names[i] != data_names[i]) Log::Fatal("Expected '%s' at position %d but found '%s'", names[i].c_str(), i, data_names[i]);
   API_END();
 }
+int FB_BoosterResetTrainingData(BoosterHandle handle, const DatasetHandle train_data) {
+  API_BEGIN(); BW();
+  const Dataset* train = static_cast<const Dataset*>(train_data);
+  if (b->train != nullptr && train->num_total_features != b->train->num_total_features) Log::Fatal("Cannot reset training data: the new dataset has %d features, the model %d", train->num_total_features, b->train->num_total_features);
+  b->objective.reset(CreateObjective(b->config.objective, b->config));
+  if (b->objective) {
+    if (b->objective->NeedQueries() && train->metadata.query_boundaries.empty()) Log::Fatal("Ranking tasks require query information");
+    b->objective->Init(train->metadata, train->num_data);
+  }
+  b->train = train;
+  b->gbdt->ResetTrainingData(b->config, train, b->objective.get(), b->config.metric_list);
+  API_END();
+}
 int FB_BoosterGetLinear(BoosterHandle handle, int* out) { API_BEGIN(); BW(); *out = b->config.linear_tree ? 1 : 0; API_END(); }
 int FB_DatasetGetFeatureNumBin(DatasetHandle handle, int feature, int* out) { return FB_DatasetFeatureNumBin(handle, feature, out); }
 int FB_DatasetDumpText(DatasetHandle handle, const char* filename) {

@@ -63,6 +63,23 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
   }
 }
 
+// Parity: src/boosting/gbdt.cpp (GBDT::ResetTrainingData: new learner state and score updater, scores replayed tree by tree).
+void GBDT::ResetTrainingData(const Config& cfg, const Dataset* train, ObjectiveFunction* obj, const std::vector<std::string>& metric_names) {
+  std::vector<std::unique_ptr<Tree>> models = std::move(models_);
+  const int iter = iter_;
+  valid_.clear(); valid_score_.clear();
+  models_.clear();
+  Init(cfg, train, obj, metric_names);
+  models_ = std::move(models); iter_ = iter;
+  if (!models_.empty()) boosted_from_average_ = true;   // the first tree carries the start score
+  const int K = num_tree_per_iteration_;
+  for (size_t t = 0; t < models_.size(); ++t) {
+    const int k = static_cast<int>(t % K);
+    if (engine_) engine_->AddTreeToScores(*models_[t], k, 1.0);
+    else AddTreeScore(models_[t].get(), train_, train_score_.data() + static_cast<size_t>(k) * train_->num_data, 1.0);
+  }
+}
+
 void GBDT::ResetConfig(const Config& cfg) {
   config_.learning_rate = cfg.learning_rate; shrinkage_rate_ = is_rf_ ? 1.0 : cfg.learning_rate;
   Config merged = config_;

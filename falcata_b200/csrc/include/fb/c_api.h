@@ -143,6 +143,7 @@ int FB_GetSampleCount(int32_t num_total_row, const char* parameters, int* out);
 int FB_SampleIndices(int32_t num_total_row, const char* parameters, void* out, int32_t* out_len);
 int FB_DumpParamAliases(int64_t buffer_len, int64_t* out_len, char* out_str);
 int FB_BoosterValidateFeatureNames(BoosterHandle handle, const char** data_names, int data_num_features);
+int FB_BoosterResetTrainingData(BoosterHandle handle, const DatasetHandle train_data);
 int FB_BoosterGetLinear(BoosterHandle handle, int* out);
 int FB_DatasetGetFeatureNumBin(DatasetHandle handle, int feature, int* out);
 int FB_DatasetDumpText(DatasetHandle handle, const char* filename);

@@ -42,6 +42,9 @@ class GBDT {
   GBDT() {}
   ~GBDT();
   void Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj, const std::vector<std::string>& metric_names);
+  // Continue boosting the trees trained so far on another dataset with the same bin mappers: scores are rebuilt by
+  // replaying the model on the new rows; validation sets have to be added again.
+  void ResetTrainingData(const Config& cfg, const Dataset* train, ObjectiveFunction* obj, const std::vector<std::string>& metric_names);
   void AddValidData(const Dataset* valid);
   // Returns true when training cannot continue (no splittable leaf).
   bool TrainOneIter(const float* grad, const float* hess);

@@ -270,3 +270,23 @@ def test_c_api_streaming_push_matches_one_shot_dataset():
     fb.Dataset.__init__(streamed, None)
     streamed._handle = h
     assert fb.train(p, streamed, 4).model_to_string() == ref_model
+
+
+def test_update_on_new_training_data_continues_the_model():
+    rng = np.random.default_rng(10)
+    Xa = rng.normal(size=(3000, 5)).astype(np.float32); ya = (Xa[:, 0] + 0.5 * Xa[:, 1]).astype(np.float32)
+    Xb = rng.normal(size=(2500, 5)).astype(np.float32); yb = (Xb[:, 0] + 0.5 * Xb[:, 1]).astype(np.float32)
+    p = {"objective": "regression", "num_leaves": 15, "verbose": -1, "metric": "l2", "learning_rate": 0.2}
+    da = fb.Dataset(Xa, ya)
+    b = fb.Booster(p, da)
+    for _ in range(5):
+        b.update()
+    db = fb.Dataset(Xb, yb, reference=da)
+    b.update(train_set=db)                 # scores of the 5 trees are replayed on the new rows, then round 6 is trained on them
+    for _ in range(4):
+        b.update()
+    assert b.current_iteration() == 10
+    l2_reported = b.eval_train()[0][2]
+    l2_predict = float(np.mean((b.predict(Xb) - yb) ** 2))
+    assert abs(l2_reported - l2_predict) < 1e-9
+    assert l2_predict < 0.3 * float(np.var(yb))
