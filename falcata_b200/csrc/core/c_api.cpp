@@ -629,6 +629,74 @@ int FB_DatasetMarkFinished(DatasetHandle handle) {
   API_END();
 }
 
+// ---- Arrow C data interface ---------------------------------------------------------------------------------
+// Record batches (struct arrays) whose columns are primitive numbers or booleans; nulls read as NaN. The batches are
+// copied into one dense matrix and released, as the producer expects of a consumer.
+// Parity: src/c_api.cpp (LGBM_DatasetCreateFromArrow, LGBM_BoosterPredictForArrow), include/Falcata/arrow.h.
+namespace {
+struct FBArrowSchema { const char* format; const char* name; const char* metadata; int64_t flags; int64_t n_children; FBArrowSchema** children; FBArrowSchema* dictionary;
+                       void (*release)(FBArrowSchema*); void* private_data; };
+struct FBArrowArray { int64_t length; int64_t null_count; int64_t offset; int64_t n_buffers; int64_t n_children; const void** buffers; FBArrowArray** children;
+                      FBArrowArray* dictionary; void (*release)(FBArrowArray*); void* private_data; };
+
+double ArrowValue(const FBArrowArray* col, const char* fmt, int64_t i) {
+  const int64_t k = col->offset + i;
+  const uint8_t* valid = col->n_buffers > 0 ? static_cast<const uint8_t*>(col->buffers[0]) : nullptr;
+  if (valid != nullptr && col->null_count != 0 && !((valid[k >> 3] >> (k & 7)) & 1)) return std::numeric_limits<double>::quiet_NaN();
+  const void* d = col->buffers[1];
+  switch (fmt[0]) {
+    case 'g': return static_cast<const double*>(d)[k];
+    case 'f': return static_cast<const float*>(d)[k];
+    case 'l': return static_cast<double>(static_cast<const int64_t*>(d)[k]);
+    case 'L': return static_cast<double>(static_cast<const uint64_t*>(d)[k]);
+    case 'i': return static_cast<const int32_t*>(d)[k];
+    case 'I': return static_cast<const uint32_t*>(d)[k];
+    case 's': return static_cast<const int16_t*>(d)[k];
+    case 'S': return static_cast<const uint16_t*>(d)[k];
+    case 'c': return static_cast<const int8_t*>(d)[k];
+    case 'C': return static_cast<const uint8_t*>(d)[k];
+    case 'b': return (static_cast<const uint8_t*>(d)[k >> 3] >> (k & 7)) & 1;
+    default: Log::Fatal("Arrow column type '%s' is not a primitive number", fmt); return 0.0;
+  }
+}
+
+// all batches as one row-major double matrix; releases the batches and the schema
+void ArrowToDense(int64_t n_chunks, FBArrowArray* chunks, FBArrowSchema* schema, std::vector<double>* out, int64_t* nrow, int32_t* ncol) {
+  if (schema->format == nullptr || schema->format[0] != '+' || schema->format[1] != 's') Log::Fatal("The Arrow data must be record batches (struct arrays)");
+  *ncol = static_cast<int32_t>(schema->n_children);
+  *nrow = 0;
+  for (int64_t c = 0; c < n_chunks; ++c) *nrow += chunks[c].length;
+  out->assign(static_cast<size_t>(*nrow) * (*ncol), 0.0);
+  int64_t at = 0;
+  for (int64_t c = 0; c < n_chunks; ++c) {
+    const FBArrowArray& batch = chunks[c];
+    if (batch.n_children != schema->n_children) Log::Fatal("An Arrow batch has %lld columns, the schema %lld", static_cast<long long>(batch.n_children), static_cast<long long>(schema->n_children));
+    for (int32_t j = 0; j < *ncol; ++j) {
+      const FBArrowArray* col = batch.children[j];
+      const char* fmt = schema->children[j]->format;
+      for (int64_t i = 0; i < batch.length; ++i) (*out)[static_cast<size_t>(at + i) * (*ncol) + j] = ArrowValue(col, fmt, batch.offset + i);
+    }
+    at += batch.length;
+  }
+  for (int64_t c = 0; c < n_chunks; ++c) if (chunks[c].release != nullptr) chunks[c].release(&chunks[c]);
+  if (schema->release != nullptr) schema->release(schema);
+}
+}  // namespace
+
+int FB_DatasetCreateFromArrow(int64_t n_chunks, void* chunks, void* schema, const char* parameters, const DatasetHandle reference, DatasetHandle* out) {
+  std::vector<double> dense; int64_t nrow = 0; int32_t ncol = 0;
+  try { ArrowToDense(n_chunks, static_cast<FBArrowArray*>(chunks), static_cast<FBArrowSchema*>(schema), &dense, &nrow, &ncol); }
+  catch (std::exception& ex) { g_last_error = ex.what(); return -1; }
+  return FB_DatasetCreateFromMat(dense.data(), kF64, static_cast<int32_t>(nrow), ncol, 1, parameters, reference, out);
+}
+int FB_BoosterPredictForArrow(BoosterHandle handle, int64_t n_chunks, void* chunks, void* schema, int predict_type, int start_iteration, int num_iteration,
+                              const char* parameter, int64_t* out_len, double* out_result) {
+  std::vector<double> dense; int64_t nrow = 0; int32_t ncol = 0;
+  try { ArrowToDense(n_chunks, static_cast<FBArrowArray*>(chunks), static_cast<FBArrowSchema*>(schema), &dense, &nrow, &ncol); }
+  catch (std::exception& ex) { g_last_error = ex.what(); return -1; }
+  return FB_BoosterPredictForMat(handle, dense.data(), kF64, static_cast<int32_t>(nrow), ncol, 1, predict_type, start_iteration, num_iteration, parameter, out_len, out_result);
+}
+
 int FB_GetSampleCount(int32_t num_total_row, const char* parameters, int* out) {
   API_BEGIN();
   Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());

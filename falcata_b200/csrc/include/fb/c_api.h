@@ -139,6 +139,10 @@ int FB_DatasetInitStreaming(DatasetHandle handle, int32_t has_weights, int32_t h
 int FB_DatasetPushRowsWithMetadata(DatasetHandle handle, const void* data, int dtype, int32_t nrow, int32_t ncol, int32_t start_row, const float* label,
                                    const float* weight, const double* init_score, const int32_t* query);
 int FB_DatasetMarkFinished(DatasetHandle handle);
+/* Arrow C data interface: `chunks` is an array of n_chunks ArrowArray structs (record batches), `schema` one ArrowSchema; both are released */
+int FB_DatasetCreateFromArrow(int64_t n_chunks, void* chunks, void* schema, const char* parameters, const DatasetHandle reference, DatasetHandle* out);
+int FB_BoosterPredictForArrow(BoosterHandle handle, int64_t n_chunks, void* chunks, void* schema, int predict_type, int start_iteration, int num_iteration,
+                              const char* parameter, int64_t* out_len, double* out_result);
 int FB_GetSampleCount(int32_t num_total_row, const char* parameters, int* out);
 int FB_SampleIndices(int32_t num_total_row, const char* parameters, void* out, int32_t* out_len);
 int FB_DumpParamAliases(int64_t buffer_len, int64_t* out_len, char* out_str);

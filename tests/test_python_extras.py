@@ -290,3 +290,48 @@ def test_update_on_new_training_data_continues_the_model():
     l2_predict = float(np.mean((b.predict(Xb) - yb) ** 2))
     assert abs(l2_reported - l2_predict) < 1e-9
     assert l2_predict < 0.3 * float(np.var(yb))
+
+
+def test_c_api_arrow_record_batches():
+    import ctypes
+    import pyarrow as pa
+    from falcata_b200.basic import _lib, _param_str
+
+    class ArrowArray(ctypes.Structure):
+        _fields_ = [("length", ctypes.c_int64), ("null_count", ctypes.c_int64), ("offset", ctypes.c_int64), ("n_buffers", ctypes.c_int64), ("n_children", ctypes.c_int64),
+                    ("buffers", ctypes.c_void_p), ("children", ctypes.c_void_p), ("dictionary", ctypes.c_void_p), ("release", ctypes.c_void_p), ("private_data", ctypes.c_void_p)]
+
+    class ArrowSchema(ctypes.Structure):
+        _fields_ = [("format", ctypes.c_char_p), ("name", ctypes.c_char_p), ("metadata", ctypes.c_char_p), ("flags", ctypes.c_int64), ("n_children", ctypes.c_int64),
+                    ("children", ctypes.c_void_p), ("dictionary", ctypes.c_void_p), ("release", ctypes.c_void_p), ("private_data", ctypes.c_void_p)]
+
+    def export(table):
+        batches = table.to_batches(max_chunksize=400)
+        arrays = (ArrowArray * len(batches))()
+        schema = ArrowSchema()
+        for i, bt in enumerate(batches):
+            bt._export_to_c(ctypes.addressof(arrays[i]))
+        table.schema._export_to_c(ctypes.addressof(schema))
+        return len(batches), arrays, schema
+
+    lib = _lib()
+    rng = np.random.default_rng(11)
+    X = rng.normal(size=(1000, 4))
+    y = (X[:, 0] > 0).astype(np.float32)
+    b = fb.train({"objective": "binary", "num_leaves": 7, "verbose": -1, "min_data_in_leaf": 5}, fb.Dataset(X, y), 4)
+    table = pa.table({"a": X[:, 0], "b": X[:, 1].astype(np.float32), "c": X[:, 2], "d": X[:, 3]})
+    Xt = np.column_stack([X[:, 0], X[:, 1].astype(np.float32).astype(np.float64), X[:, 2], X[:, 3]])
+    n_chunks, arrays, schema = export(table)
+    assert n_chunks == 3
+    out = np.zeros(1000, dtype=np.float64); n = ctypes.c_int64(0)
+    assert lib.FB_BoosterPredictForArrow(b._handle, ctypes.c_int64(n_chunks), ctypes.byref(arrays), ctypes.byref(schema), 0, 0, -1, b"", ctypes.byref(n),
+                                         out.ctypes.data_as(ctypes.POINTER(ctypes.c_double))) == 0
+    assert n.value == 1000 and np.allclose(out, b.predict(Xt), atol=1e-12)
+    assert not schema.release       # the consumer released what it was given
+    n_chunks, arrays, schema = export(table)
+    h = ctypes.c_void_p()
+    assert lib.FB_DatasetCreateFromArrow(ctypes.c_int64(n_chunks), ctypes.byref(arrays), ctypes.byref(schema), _param_str({}), None, ctypes.byref(h)) == 0
+    nd = ctypes.c_int32(0); nf = ctypes.c_int32(0)
+    assert lib.FB_DatasetGetNumData(h, ctypes.byref(nd)) == 0 and nd.value == 1000
+    assert lib.FB_DatasetGetNumFeature(h, ctypes.byref(nf)) == 0 and nf.value == 4
+    lib.FB_DatasetFree(h)
