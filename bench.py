@@ -9,12 +9,31 @@ histogram construction with its reduce-scatter, split search) and the score upda
 on the device with CUDA events, max over ranks. The per-step working set (binned rows, 32 B/row)
 is larger than L2, so no explicit L2 flush is needed between steps.
 
+Two arms:
+  --impl ours       this repository's engine (one process per GPU; launched with torchrun for N > 1)
+  --impl reference  the unmodified reference framework installed under baseline/_ref by
+                    baseline/build_reference.py, through its own public API (falcata.Dataset / falcata.train /
+                    Booster.update) with device_type=cuda, tree_learner=serial, num_gpu=N, which is its row
+                    data-parallel mode. The reference drives all N GPUs from ONE process (a host thread per GPU),
+                    so under torchrun only rank 0 works and the other ranks leave at once. Nothing of this
+                    repository's package is imported in that arm.
+
+Tree shape. The headline `value` is measured on depth-capped trees (8 levels, 255 leaves): that is what
+the reference's quantized multi-GPU mode requires (2^max_depth <= num_leaves + 1), so it is the one shape both
+arms can grow at every GPU count; ours: grow_policy=level, reference: max_depth=8. The exact best-first
+(leaf-wise, no depth cap) trees of the same 255 leaves are reported in the `leafwise` sub-record
+(ours: grow_policy=leaf at every N; reference: only at N = 1).
+
 Usage: python bench.py [--gpus N] [--steps K] [--warmup W] [--rows R] [--impl ours|reference]
 For N > 1 launch with torchrun (one rank per GPU); RANK / LOCAL_RANK / WORLD_SIZE come from the env.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
+import glob
+import hashlib
+import importlib.util
 import json
 import os
 import statistics
@@ -23,11 +42,13 @@ import sys
 import threading
 import time
 
-sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
 
 ROWS = 11_000_000
 PARAMS = {"objective": "binary", "num_leaves": 255, "max_bin": 63, "learning_rate": 0.1, "quant_mode": "stochastic", "quant_bins": 4,
           "cuda_precision": "fp32", "tree_learner": "data", "device_type": "cuda", "verbosity": -1, "min_data_in_leaf": 20, "metric": "binary_logloss"}
+MODEL_NAME = "gbdt binary 11Mx28, num_leaves=255, max_bin=63, quant_mode=stochastic(4 bins)"
 
 
 class ClockSampler:
@@ -55,7 +76,7 @@ class ClockSampler:
                             self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(0.05)
 
     def __enter__(self):
         self._t.start()
@@ -68,16 +89,147 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def model_md5(model_text: str) -> str:
+    """md5 of the model text up to the parameter dump (trees and header only), the rule of the reference's lattice gate."""
+    cut = model_text.find("\nparameters:")
+    return hashlib.md5((model_text if cut < 0 else model_text[:cut]).encode()).hexdigest()
+
+
+def load_synthetic():
+    """The data generator, loaded by file path so that the reference arm does not import this repository's package."""
+    spec = importlib.util.spec_from_file_location("_bench_synthetic", os.path.join(HERE, "falcata_b200", "utils", "synthetic.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+# ------------------------------------------------------------------------------------------ reference arm ----
+def _preload(names) -> None:
+    """dlopen by soname needs the library on the loader path or already loaded: load the toolkit's / torch's copy first."""
+    roots = ["/usr/local/cuda/lib64"] + [os.path.join(p, "nvidia") for p in sys.path if p.endswith("site-packages")]
+    for name in names:
+        for root in roots:
+            hits = sorted(glob.glob(os.path.join(root, "**", name), recursive=True))
+            if hits:
+                try:
+                    ctypes.CDLL(hits[0], mode=ctypes.RTLD_GLOBAL)
+                    break
+                except OSError:
+                    continue
+
+
 def reference_arm(args) -> None:
-    # The reference needs its external_libs submodules (Eigen, fast_double_parser, fmt); the mounted tree
-    # ships them as empty directories and the image has no copy, so it cannot be built offline here.
-    ok = os.path.isdir(os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", "falcata"))
-    if not ok:
-        print(json.dumps({"impl": "reference", "unavailable": "reference cannot be built offline: its source tree is not pip-installable (no pyproject at its root) and its external_libs submodules (eigen, fast_double_parser, fmt) are empty and absent from the image"}))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return   # one process drives every GPU in the reference
+    ref_dir = os.path.join(HERE, "baseline", "_ref")
+    if not os.path.isfile(os.path.join(ref_dir, "falcata", "lib", "lib_falcata.so")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref holds no built reference (run python baseline/build_reference.py; it needs nvcc and about ten minutes)"}))
         return
-    print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref exists but the native library was never built (missing Eigen / fast_double_parser sources)"}))
+    import numpy as np
+    import torch
+
+    n_gpus = int(args.gpus)
+    if torch.cuda.device_count() < n_gpus:
+        print(json.dumps({"impl": "reference", "unavailable": f"{n_gpus} GPUs asked for, {torch.cuda.device_count()} visible"}))
+        return
+    # On an NVSwitch box peer-to-peer transport is the natural NCCL setting; the reference only sets
+    # NCCL_P2P_DISABLE=1 when the variable is unset (a workaround for PCIe boxes).
+    os.environ.setdefault("NCCL_P2P_DISABLE", "0")
+    _preload(["libnvrtc.so.12", "libnccl.so.2"])
+    sys.path.insert(0, ref_dir)
+    try:
+        import falcata
+    except Exception as e:   # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"the built reference does not load here: {type(e).__name__}: {str(e)[:160]}"}))
+        return
+
+    class _Quiet:
+        def info(self, msg): pass
+        def warning(self, msg): print(msg, file=sys.stderr)
+    falcata.register_logger(_Quiet())
+
+    synthetic = load_synthetic()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    warmup = max(3, args.warmup)
+    K = args.steps
+    X, y = synthetic.binary_higgs_like(args.rows, offset=0, seed=0, device=str(dev))
+    torch.cuda.synchronize()
+    yh = y.cpu().numpy()
+    label_md5 = hashlib.md5((yh > 0.5).astype(np.uint8).tobytes()).hexdigest()
+
+    def sync_all():
+        for d in range(n_gpus):
+            torch.cuda.synchronize(d)
+
+    def params_for(depth_capped: bool):
+        p = {"objective": "binary", "num_leaves": 255, "max_bin": 63, "learning_rate": 0.1, "quant_mode": "stochastic", "quant_bins": 4,
+             "cuda_precision": "fp32", "tree_learner": "serial", "device_type": "cuda", "num_gpu": n_gpus, "verbosity": -1, "min_data_in_leaf": 20,
+             "metric": "binary_logloss"}
+        if depth_capped:
+            p["max_depth"] = 8
+        return p
+
+    def timed_rounds(depth_capped: bool):
+        p = params_for(depth_capped)
+        ds = falcata.Dataset(X, yh, params={"max_bin": 63, "device_type": "cuda", "verbosity": -1}, free_raw_data=False)
+        bst = falcata.Booster(p, ds)
+        for _ in range(warmup):
+            bst.update()
+        sync_all()
+        with ClockSampler(0) as clk:
+            t0 = time.perf_counter()
+            for _ in range(K):
+                bst.update()
+            sync_all()
+            dt = time.perf_counter() - t0
+        ev = bst.eval_train()
+        logloss = ev[0][2] if ev else None
+        md5 = model_md5(bst.model_to_string())
+        del bst, ds
+        return dt * 1000.0 / K, clk.summary(), logloss, md5
+
+    out = {"metric": "s/1000 rounds (device-timed, max over ranks)", "unit": "s/1000 rounds", "n_gpus": n_gpus, "steps": K, "warmup": warmup,
+           "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "int16-quantized gradients / fp32 scores", "data": "synthetic", "impl": "reference"}
+    try:
+        ms, clocks, logloss, md5 = timed_rounds(True)
+    except Exception as e:   # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference raised on this configuration: {type(e).__name__}: {str(e)[:200]}"}))
+        return
+    out.update({"value": ms, "ms_per_step": ms, "clocks": clocks,
+                "config": {"model": MODEL_NAME, "tree_shape": "max_depth=8 (required by the reference's quantized multi-GPU mode; ours: grow_policy=level)", "same_config": True,
+                           "global_batch": args.rows, "seq_len": 28, "parallelism": f"num_gpu={n_gpus} (one process, NCCL all-reduce per level)" if n_gpus > 1 else "single",
+                           "l2": "inputs_larger_than_L2", "train_logloss_after_run": logloss, "model_md5": md5, "label_md5": label_md5,
+                           "NCCL_P2P_DISABLE": os.environ.get("NCCL_P2P_DISABLE"),
+                           "timing": "wall clock around K Booster.update() calls, device synchronize on both sides (the reference waits for the device every round)",
+                           "third_party": "built offline with stand-ins for the empty external_libs trees (fmt from the torch wheel; fast_double_parser, Eigen, nanoarrow: baseline/standins)"}})
+    if n_gpus == 1:
+        try:
+            ms2, _, ll2, md52 = timed_rounds(False)
+            out["leafwise"] = {"value": ms2, "unit": "s/1000 rounds", "tree_shape": "no depth cap (best-first, 255 leaves)", "train_logloss_after_run": ll2, "model_md5": md52}
+        except Exception as e:   # noqa: BLE001
+            out["leafwise"] = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
+    # ---- end to end: host matrix -> reference Dataset -> K rounds with the training metric read back every round ----
+    if not args.no_e2e:
+        try:
+            Xh = X.cpu().numpy()
+            del X
+            torch.cuda.empty_cache()
+            t0 = time.perf_counter()
+            ds2 = falcata.Dataset(Xh, yh, params={"max_bin": 63, "device_type": "cuda", "verbosity": -1})
+            rec = {}
+            falcata.train(dict(params_for(True), is_provide_training_metric=True), ds2, K, valid_sets=[ds2], valid_names=["train"], callbacks=[falcata.record_evaluation(rec)])
+            sync_all()
+            dt = time.perf_counter() - t0
+            out["e2e"] = {"value": dt / K * 1000.0, "unit": "s/1000 rounds (ingest from host memory + K rounds + per-round metric read, wall clock / K)",
+                          "h2d_bytes_per_step": int((Xh.nbytes + yh.nbytes) / K), "d2h_bytes_per_step": 16}
+        except Exception as e:   # noqa: BLE001
+            out["e2e"] = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
+    print(json.dumps(out))
 
 
+# ------------------------------------------------------------------------------------------------ our arm ----
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -86,6 +238,7 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=ROWS)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-leafwise", action="store_true", help="skip the leaf-wise sub-record")
     ap.add_argument("--stage-timing", action="store_true")
     ap.add_argument("--plan", default="auto", help="cuda_plan string, e.g. auto,hist_lane:off")
     ap.add_argument("--grow-policy", default=None, choices=["level", "leaf"], help="level: gain-ranked leaf budget per level; leaf: exact best-first trees")
@@ -103,7 +256,6 @@ def main() -> None:
     import torch
 
     import falcata_b200 as fb
-    from falcata_b200.parallel import bootstrap
     from falcata_b200.utils import synthetic
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -134,32 +286,59 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-timed steps (data already on the device) ----
-    ds = fb.Dataset(X, y.cpu().numpy(), params={"max_bin": PARAMS["max_bin"]}).set_global_rows(off, args.rows)
-    bst = fb.Booster(PARAMS, ds)
-    for _ in range(warmup):
-        bst.update()
-    barrier()
-    l0 = bst.gpu_launches()
-    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clk:
-        barrier()
-        e0.record()
-        for _ in range(K):
-            bst.update()
-        e1.record()
-        barrier()
-    ms = e0.elapsed_time(e1)
-    launches = bst.gpu_launches() - l0
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    def max_over_ranks(v: float) -> float:
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # md5 of the GLOBAL label vector (rank order): shows that every GPU count trains on the same data
+    lab8 = (y > 0.5).to(torch.uint8)
     if world > 1:
         import torch.distributed as dist
 
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_per_step = float(t.item()) / K
-    stage = bst.stage_report() if args.stage_timing else ""
-    logloss = bst.eval_train()[0][2] if bst.eval_train() else None
-    del bst, ds
+        sizes = [synthetic.shard(args.rows, r, world)[1] for r in range(world)]
+        parts = [torch.empty(s, dtype=torch.uint8, device=dev) for s in sizes]
+        dist.all_gather(parts, lab8)
+        lab8 = torch.cat(parts)
+    label_md5 = hashlib.md5(lab8.cpu().numpy().tobytes()).hexdigest()
+    del lab8
+
+    # ---- device-timed steps (data already on the device) ----
+    ds = fb.Dataset(X, y.cpu().numpy(), params={"max_bin": PARAMS["max_bin"]}).set_global_rows(off, args.rows)
+
+    def timed_rounds(params):
+        bst = fb.Booster(params, ds)
+        for _ in range(warmup):
+            bst.update()
+        barrier()
+        l0 = bst.gpu_launches()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clk:
+            barrier()
+            e0.record()
+            for _ in range(K):
+                bst.update()
+            e1.record()
+            barrier()
+        ms = max_over_ranks(e0.elapsed_time(e1)) / K
+        launches = bst.gpu_launches() - l0
+        stage = bst.stage_report() if args.stage_timing else ""
+        ev = bst.eval_train()
+        logloss = ev[0][2] if ev else None
+        md5 = model_md5(bst.model_to_string())
+        del bst
+        return ms, launches, clk.summary(), logloss, md5, stage
+
+    ms_per_step, launches, clocks, logloss, md5, stage = timed_rounds(PARAMS)
+    leafwise = None
+    if not args.no_leafwise and PARAMS.get("grow_policy", "level") == "level":
+        lms, llaunch, _, lll, lmd5, _ = timed_rounds(dict(PARAMS, grow_policy="leaf"))
+        leafwise = {"value": lms, "unit": "s/1000 rounds", "tree_shape": "no depth cap (exact best-first, 255 leaves)", "gpu_launches": int(llaunch),
+                    "train_logloss_after_run": lll, "model_md5": lmd5}
+    del ds
 
     # ---- end to end through the public API: pinned host matrix -> H2D -> on-device binning -> K rounds,
     # reading the training metric back to the host every round ----
@@ -176,27 +355,27 @@ def main() -> None:
         # the pinned host matrix goes straight into the public API: the library copies it to the device on a side stream
         # while the host finds the bin boundaries, then bins on the device
         ds2 = fb.Dataset(Xh, yh, params={"max_bin": PARAMS["max_bin"], "device_type": "cuda"}).set_global_rows(off, args.rows)
-        b2 = fb.train(dict(PARAMS, is_provide_training_metric=True), ds2, K, valid_sets=[ds2], valid_names=["train"], keep_training_booster=True,
-                      callbacks=[fb.record_evaluation({})])
+        fb.train(dict(PARAMS, is_provide_training_metric=True), ds2, K, valid_sets=[ds2], valid_names=["train"], keep_training_booster=True,
+                 callbacks=[fb.record_evaluation({})])
         barrier()
-        dt = time.perf_counter() - t0
-        tt = torch.tensor([dt], dtype=torch.float64, device=dev)
-        if world > 1:
-            import torch.distributed as dist
-
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = max_over_ranks(time.perf_counter() - t0)
         if os.environ.get("FALCATA_TIME_TAG") and rank == 0:
             print(fb.time_tag_report(), file=sys.stderr)
-        e2e = {"value": float(tt.item()) / K * 1000.0, "unit": "s/1000 rounds (ingest from pinned host memory + K rounds + per-round metric read, wall clock / K)",
+        e2e = {"value": dt / K * 1000.0, "unit": "s/1000 rounds (ingest from pinned host memory + K rounds + per-round metric read, wall clock / K)",
                "h2d_bytes_per_step": int((Xh.numel() * Xh.element_size() + yh.nbytes) / K), "d2h_bytes_per_step": 16}
 
     if rank == 0:
         out = {"metric": "s/1000 rounds (device-timed, max over ranks)", "value": ms_per_step, "unit": "s/1000 rounds", "n_gpus": world, "steps": K, "warmup": warmup,
                "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "int16-quantized gradients / fp32 scores (reference: same)",
                "data": "synthetic", "impl": "ours",
-               "config": {"model": "gbdt binary 11Mx28, num_leaves=255, max_bin=63, quant_mode=stochastic(4 bins)", "grow_policy": PARAMS.get("grow_policy", "level"), "global_batch": args.rows, "seq_len": 28,
-                          "parallelism": f"dp{world}" if world > 1 else "single", "l2": "inputs_larger_than_L2", "train_logloss_after_run": logloss},
-               "clocks": clk.summary(), "gpu_launches": int(launches)}
+               "config": {"model": MODEL_NAME, "grow_policy": PARAMS.get("grow_policy", "level"),
+                          "tree_shape": "8 levels, 255 leaves (grow_policy=level; the reference's max_depth=8)" if PARAMS.get("grow_policy", "level") == "level" else "no depth cap (exact best-first)",
+                          "global_batch": args.rows, "seq_len": 28,
+                          "parallelism": f"dp{world}" if world > 1 else "single", "l2": "inputs_larger_than_L2", "train_logloss_after_run": logloss,
+                          "model_md5": md5, "label_md5": label_md5},
+               "clocks": clocks, "gpu_launches": int(launches)}
+        if leafwise is not None:
+            out["leafwise"] = leafwise
         if e2e is not None:
             out["e2e"] = e2e
         if stage:

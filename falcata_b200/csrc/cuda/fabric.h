@@ -86,14 +86,15 @@ class Fabric {
   size_t ar_data_off_ = 0, ar_flag_off_ = 0;
 };
 
-__device__ inline void FabricSignalDone(const FabricSignal& sig, unsigned int total_blocks) {
-  // Call with all threads of the block; the block's global writes are ordered before the flag. Every block
-  // publishes its writes at device scope before it counts itself in (a device-scope fence is cheap; a
-  // system-scope one per block, with peer stores in flight, is not); the last block, which has observed all the
-  // others through the counter, issues the one system-scope fence and raises the flags with release stores.
+// Call with all threads of the block; the block's global writes are ordered before the flag.
+// `wrote_peers`: this block stored into other ranks' memory. Such a block publishes its own stores at SYSTEM
+// scope before it counts itself in, so the flag can never overtake data that is still on its way through
+// NVLink; blocks that only wrote local memory take the cheaper device-scope fence. The last block, which has
+// observed all the others through the counter, issues one more system-scope fence and raises the flags.
+__device__ inline void FabricSignalDone(const FabricSignal& sig, unsigned int total_blocks, bool wrote_peers = false) {
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
+    if (wrote_peers) __threadfence_system(); else __threadfence();
     const unsigned int prev = atomicAdd(sig.done_counter, 1u);
     if (prev + 1 == total_blocks) {
       *sig.done_counter = 0;

@@ -51,7 +51,7 @@ __device__ inline void FlushBinQuant(const HistDest& d, int slot, int task_index
 // other blocks are still constructing other leaves. Zeros are stored too, so the destination never
 // needs clearing, and the local staging cells are reset for the next level.
 template <bool QUANT>
-__device__ inline void PushTaskIfLast(const HistArgs& a, int ti, const HistTask& task) {
+__device__ inline bool PushTaskIfLast(const HistArgs& a, int ti, const HistTask& task) {
   const HistDest& d = a.dest;
   __shared__ int s_last;
   __syncthreads();
@@ -64,7 +64,7 @@ __device__ inline void PushTaskIfLast(const HistArgs& a, int ti, const HistTask&
     if (s_last) d.task_done[ti] = 0;
   }
   __syncthreads();
-  if (!s_last) return;
+  if (!s_last) return false;
   __threadfence();
   const int nb = a.num_total_bin;
   for (int b = threadIdx.x; b < nb; b += blockDim.x) {
@@ -82,6 +82,8 @@ __device__ inline void PushTaskIfLast(const HistArgs& a, int ti, const HistTask&
       static_cast<double2*>(d.peer_stage[owner])[dst_index] = v;
     }
   }
+  __threadfence_system();   // every storing thread publishes its own peer stores before the block counts itself done
+  return true;
 }
 
 template <bool TWO_PHASE>
@@ -140,8 +142,8 @@ __global__ void __launch_bounds__(kHistThreads) HistQuantKernel(HistArgs a) {
     else { const int v = s_packed[b]; h = v & 0xFFFF; g = (v - static_cast<int>(h)) >> 16; }
     if (g != 0 || h != 0) FlushBinQuant(a.dest, task.slot, ti, a.num_total_bin, part.bin_begin + b, g, h);
   }
-  if (a.dest.num_ranks > 1) PushTaskIfLast<true>(a, ti, task);
-  if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y);
+  const bool pushed = a.dest.num_ranks > 1 && PushTaskIfLast<true>(a, ti, task);
+  if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y, pushed);
 }
 
 // Lane-per-group instance with warp-autonomous asynchronous pipelines.
@@ -341,8 +343,8 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
     for (int w = 0; w < kLaneWarps; ++w) { const int v = tiles[w * kTile + cell]; const int h = v & 0xFFFF; sg += (v - h) >> 16; sh += h; }
     if (sg != 0 || sh != 0) FlushBinQuant(a.dest, task.slot, ti, a.num_total_bin, gstart + b, sg, sh);
   }
-  if (a.dest.num_ranks > 1) PushTaskIfLast<true>(a, ti, task);
-  if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y);
+  const bool pushed = a.dest.num_ranks > 1 && PushTaskIfLast<true>(a, ti, task);
+  if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y, pushed);
 }
 
 __global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
@@ -394,8 +396,8 @@ __global__ void __launch_bounds__(kHistThreads) HistFloatKernel(HistArgs a) {
                                 : static_cast<double*>(d.pool[0]) + 2 * (static_cast<long long>(task.slot) * d.slot_stride[0] + d.bin_local[gb]);
     atomicAdd(p, static_cast<double>(g)); atomicAdd(p + 1, static_cast<double>(h));
   }
-  if (d.num_ranks > 1) PushTaskIfLast<false>(a, ti, task);
-  if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y);
+  const bool pushed = d.num_ranks > 1 && PushTaskIfLast<false>(a, ti, task);
+  if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y, pushed);
 }
 
 // Transpose tile of the compact view: 32 rows x 32 listed groups per block.

@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(kPartThreads) PartitionFlagsKernel(PartArgs a)
     int t = 0; for (int w = 0; w < kPartThreads / 32; ++w) t += s_cnt[w];
     if (bc) { for (int r = 0; r < a.bc_world; ++r) a.peer_chunk_left[r][chunk] = t; } else a.chunk_left[chunk] = t;
   }
-  if (bc) FabricSignalDone(a.bc_sig, gridDim.x);
+  if (bc) FabricSignalDone(a.bc_sig, gridDim.x, true);
 }
 
 __global__ void __launch_bounds__(kPartThreads) PartitionScanSetupKernel(PartArgs a) {
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(kPartThreads) PartitionScanSetupKernel(PartArg
     a.split_left_total[si] = nl;
     // multi-rank: every rank learns every rank's left count (summed by the split search, which runs
     // after the construct-done flags; this store is ordered before them by the stream)
-    for (int r = 0; r < a.world; ++r) if (a.world > 1) a.peer_counts[r][si] = nl;
+    if (a.world > 1) { for (int r = 0; r < a.world; ++r) a.peer_counts[r][si] = nl; __threadfence_system(); }
     const ChildInit ci = a.child_init[si];
     const LeafInfo parent = a.leaves[sp.leaf];
     LeafInfo L = parent, R = parent;

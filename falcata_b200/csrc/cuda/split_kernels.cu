@@ -172,9 +172,11 @@ __device__ void ScanCategoricalWarp(const FindArgs& a, const BinSrc& src, char* 
 template <bool QUANT>
 __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
   if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) return;
-  if (a.ctrl != nullptr && a.ctrl->skip_search) return;   // the tree is complete: nothing was constructed for these children
-  // multi-rank: the owned slices are complete once every rank's construct has raised its flag
+  // multi-rank: the owned slices are complete once every rank's construct has raised its flag. The wait also
+  // orders the peers' child counts (stored by their partition, before their construct) ahead of the per-leaf
+  // argmax that follows, so it is taken even when the search itself is skipped.
   if (a.wait.world > 1) FabricWaitAll(a.wait);
+  if (a.ctrl != nullptr && a.ctrl->skip_search) return;   // the tree is complete: nothing was constructed for these children
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int fi = blockIdx.y * kWarpsPerBlock + warp;
   if (fi >= a.num_features + a.num_sub_features) return;
@@ -392,7 +394,7 @@ __global__ void ReduceBestKernel(FindArgs a) {
       unsigned int* dst = reinterpret_cast<unsigned int*>(a.peer_best[p] + ch.leaf);
       for (int w = threadIdx.x; w < kWords; w += blockDim.x) dst[w] = src[w];
     }
-    FabricSignalDone(a.sig, gridDim.x);
+    FabricSignalDone(a.sig, gridDim.x, true);
   }
 }
 

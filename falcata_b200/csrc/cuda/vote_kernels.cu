@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(kVoteThreads) VoteTopKKernel(VoteArgs a) {
   }
   for (int p = 0; p < a.world; ++p)
     for (int r = threadIdx.x; r < a.top_k; r += kVoteThreads) a.peer_votes[p][static_cast<size_t>(blockIdx.x) * a.top_k + r] = s_votes[r];
-  FabricSignalDone(a.vote_sig, gridDim.x);
+  FabricSignalDone(a.vote_sig, gridDim.x, true);
 }
 
 // Vote count, choice of the 2*top_k most voted features (ties: the lower feature), and the restricted
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(kVoteThreads) VoteTallyPushKernel(VoteArgs a) 
       else static_cast<double2*>(a.peer_stage[owner])[dst0 + b] = static_cast<const double2*>(a.local_pool)[src0 + b];
     }
   }
-  FabricSignalDone(a.hist_sig, gridDim.x);
+  FabricSignalDone(a.hist_sig, gridDim.x, true);
 }
 
 }  // namespace

@@ -3,6 +3,9 @@
 Rows are generated in fixed chunks of ``CHUNK`` rows, each from its own generator seeded by the
 chunk index, so rows ``[offset, offset + n)`` are the same numbers whichever rank (and however many
 ranks) asks for them: a model trained on 1, 2, 4 or 8 shards sees the same global data set.
+Everything derived from the random draws (interaction features, logits, labels) is computed on the
+WHOLE chunk and sliced afterwards: a reduction or matrix product over a slice whose shape depends on
+the shard may pick another kernel and round differently, which would flip a label near its threshold.
 """
 from __future__ import annotations
 
@@ -52,12 +55,13 @@ def binary_higgs_like(n: int, offset: int = 0, seed: int = 0, device: str = "cud
         g = _gen(seed, c, dev)
         base = torch.randn(CHUNK, 21, generator=g, device=dev)
         u = torch.rand(CHUNK, generator=g, device=dev)
-        base = base[lo:hi]
         inter = torch.stack([(base[:, int(i)] * base[:, int(j)]).abs() for i, j in pairs.tolist()], dim=1)
         x = torch.cat([base, inter], dim=1)
         logit = x @ w + 0.5 * x[:, 0] * x[:, 1]
-        xs.append(x)
-        ys.append((u[lo:hi] < torch.sigmoid(logit)).float())
+        label = (u < torch.sigmoid(logit)).float()
+        xs.append(x[lo:hi].clone())
+        ys.append(label[lo:hi].clone())
+        del base, inter, x, logit, label, u
     return torch.cat(xs), torch.cat(ys)
 
 
@@ -70,14 +74,14 @@ def regression_wide(n: int, f: int = 2000, offset: int = 0, seed: int = 0, devic
     xs, ys = [], []
     for c, lo, hi in _chunks(offset, n):
         g = _gen(seed, c, dev)
-        m = hi - lo
-        nz = torch.rand(CHUNK, f, generator=g, device=dev)[lo:hi] >= 0.8
-        val = torch.randint(1, 16, (CHUNK, f), generator=g, device=dev, dtype=torch.int8)[lo:hi]
+        nz = torch.rand(CHUNK, f, generator=g, device=dev) >= 0.8
+        val = torch.randint(1, 16, (CHUNK, f), generator=g, device=dev, dtype=torch.int8)
         x = torch.where(nz, val, torch.zeros_like(val))
-        noise = torch.randn(CHUNK, generator=g, device=dev)[lo:hi]
+        del nz, val
+        noise = torch.randn(CHUNK, generator=g, device=dev)
         y = (torch.sin(x[:, sel].float()) * coef).sum(1) + noise
-        xs.append(x); ys.append(y)
-        del m
+        xs.append(x[lo:hi].clone()); ys.append(y[lo:hi].clone())
+        del x, y, noise
     return torch.cat(xs), torch.cat(ys)
 
 
@@ -89,10 +93,12 @@ def multiclass(n: int, f: int = 100, k: int = 10, offset: int = 0, seed: int = 0
     xs, ys = [], []
     for c, lo, hi in _chunks(offset, n):
         g = _gen(seed, c, dev)
-        x = torch.randn(CHUNK, f, generator=g, device=dev)[lo:hi]
-        u = torch.rand(CHUNK, k, generator=g, device=dev)[lo:hi].clamp_(1e-9, 1 - 1e-9)
+        x = torch.randn(CHUNK, f, generator=g, device=dev)
+        u = torch.rand(CHUNK, k, generator=g, device=dev).clamp_(1e-9, 1 - 1e-9)
         gum = -torch.log(-torch.log(u))
-        xs.append(x); ys.append((x @ W + gum).argmax(1).float())
+        label = (x @ W + gum).argmax(1).float()
+        xs.append(x[lo:hi].clone()); ys.append(label[lo:hi].clone())
+        del x, u, gum, label
     return torch.cat(xs), torch.cat(ys)
 
 
