@@ -133,6 +133,30 @@ def _to_numpy_2d(data: Any) -> np.ndarray:
     return arr
 
 
+def _dump_pandas_categorical(pandas_categorical: Optional[List[List[Any]]]) -> str:
+    """Trailer line of a text model: the category lists of the pandas categorical columns the model was trained on (JSON)."""
+    import json
+
+    def _default(o: Any) -> Any:
+        if isinstance(o, np.generic):
+            return o.item()
+        raise TypeError(f"cannot serialise a category of type {type(o).__name__}")
+    return "\npandas_categorical:" + json.dumps(pandas_categorical, default=_default) + "\n"
+
+
+def _load_pandas_categorical(model_str: str) -> Optional[List[List[Any]]]:
+    import json
+
+    pos = model_str.rfind("\npandas_categorical:")
+    if pos < 0:
+        return None
+    line = model_str[pos + len("\npandas_categorical:"):].strip().split("\n", 1)[0]
+    try:
+        return json.loads(line)
+    except ValueError:
+        return None
+
+
 def _get_string(fn: Callable, *args: Any) -> str:
     out_len = ctypes.c_int64(0)
     buf_len = 1 << 16
@@ -761,9 +785,14 @@ class Booster:
             _safe_call(lib.FB_BoosterCreate(train_set._handle, _param_str(self.params), ctypes.byref(self._handle)))
         elif model_file is not None:
             _safe_call(lib.FB_BoosterCreateFromModelfile(str(model_file).encode(), ctypes.byref(n_iter), ctypes.byref(self._handle)))
+            with open(model_file, "rb") as f:   # a model file (text or binary) may end with the pandas categories trailer
+                f.seek(max(0, os.path.getsize(model_file) - (1 << 20)))
+                self.pandas_categorical = _load_pandas_categorical(f.read().decode("utf-8", errors="replace"))
         elif model_str is not None:
             raw = model_str if isinstance(model_str, bytes) else model_str.encode("utf-8")
             _safe_call(lib.FB_BoosterLoadModelFromString(raw, ctypes.c_int64(len(raw)), ctypes.byref(n_iter), ctypes.byref(self._handle)))
+            if raw[:4] != b"FALB":
+                self.pandas_categorical = _load_pandas_categorical(raw[-(1 << 20):].decode("utf-8", errors="replace"))
         else:
             raise TypeError("Need at least one training dataset or model file or model string to create Booster instance")
         self._eval_names: Optional[List[str]] = None
@@ -781,7 +810,10 @@ class Booster:
     def __getstate__(self) -> Dict[str, Any]:
         st = {k: v for k, v in self.__dict__.items() if k not in ("_handle", "train_set", "valid_sets")}
         if _PICKLE_FORMAT == "falb":
-            st["_model_bin"] = self.model_to_binary(num_iteration=-1)
+            try:   # statistics and diagnostics ride along: an unpickled booster is the same model in every respect
+                st["_model_bin"] = self.model_to_binary(num_iteration=-1, with_stats=True, with_diagnostics=True)
+            except FalcataError:   # linear trees have no binary form
+                st["_model_str"] = self.model_to_string(num_iteration=-1)
         else:
             st["_model_str"] = self.model_to_string(num_iteration=-1)
         return st
@@ -1090,23 +1122,34 @@ class Booster:
         if num_iteration is None:
             num_iteration = self.best_iteration
         if format == "falb":
-            Path(filename).write_bytes(self.model_to_binary(num_iteration, start_iteration, f32_leaves))
+            Path(filename).write_bytes(self.model_to_binary(num_iteration, start_iteration, importance_type=importance_type, f32_leaves=f32_leaves,
+                                                            **{k: v for k, v in _ignored.items() if k in ("with_stats", "with_diagnostics", "compress_level")})
+                                       + _dump_pandas_categorical(self.pandas_categorical).encode("utf-8"))
             return self
         if format not in ("txt", "text"):
             raise ValueError("format must be 'txt' or 'falb'")
         _safe_call(_lib().FB_BoosterSaveModel(self._handle, start_iteration, num_iteration, 0 if importance_type == "split" else 1, str(filename).encode()))
+        with open(filename, "a") as f:
+            f.write(_dump_pandas_categorical(self.pandas_categorical))
         return self
 
     def model_to_string(self, num_iteration: Optional[int] = None, start_iteration: int = 0, importance_type: str = "split") -> str:
         if num_iteration is None:
             num_iteration = self.best_iteration
-        return _get_string(_lib().FB_BoosterSaveModelToString, self._handle, start_iteration, num_iteration, 0 if importance_type == "split" else 1)
+        return _get_string(_lib().FB_BoosterSaveModelToString, self._handle, start_iteration, num_iteration, 0 if importance_type == "split" else 1) + \
+            _dump_pandas_categorical(self.pandas_categorical)
 
-    def model_to_binary(self, num_iteration: Optional[int] = None, start_iteration: int = 0, f32_leaves: bool = False) -> bytes:
-        """Compressed sectioned binary model (``FALB``)."""
+    def model_to_binary(self, num_iteration: Optional[int] = None, start_iteration: int = 0, importance_type: str = "split", with_stats: bool = False,
+                        with_diagnostics: bool = False, f32_leaves: bool = False, compress_level: int = 6) -> bytes:
+        """The model in the sectioned binary ``FALB`` container (readable by, and reading, the reference's files).
+
+        ``with_stats`` adds per-node counts and weights (needed by ``pred_contrib``, ``trees_to_dataframe`` and
+        ``dump_model``), ``with_diagnostics`` adds split gains and internal values (needed by gain importance);
+        ``f32_leaves`` stores leaf values as float32 (lossy); ``compress_level`` is the zlib level, 0 = raw sections."""
         if num_iteration is None:
             num_iteration = self.best_iteration
-        return _get_bytes(_lib().FB_BoosterSaveModelToBinary, self._handle, start_iteration, num_iteration, 1 if f32_leaves else 0)
+        return _get_bytes(_lib().FB_BoosterSaveModelToBinary, self._handle, start_iteration, num_iteration, 0 if importance_type == "split" else 1,
+                          1 if with_stats else 0, 1 if with_diagnostics else 0, 1 if f32_leaves else 0, int(compress_level))
 
     @classmethod
     def from_binary(cls, data: bytes) -> "Booster":

@@ -814,9 +814,10 @@ int FB_BoosterDumpModel(BoosterHandle handle, int start_iteration, int num_itera
 int FB_BoosterModelToIfElse(BoosterHandle handle, int num_iteration, int64_t buffer_len, int64_t* out_len, char* out_str) {
   API_BEGIN(); BW(); CopyOut(b->gbdt->ModelToIfElse(num_iteration), buffer_len, out_len, out_str); API_END();
 }
-int FB_BoosterSaveModelToBinary(BoosterHandle handle, int start_iteration, int num_iteration, int f32_leaves, int64_t buffer_len, int64_t* out_len, char* out) {
+int FB_BoosterSaveModelToBinary(BoosterHandle handle, int start_iteration, int num_iteration, int feature_importance_type, int with_stats,
+                                int with_diagnostics, int f32_leaves, int compress_level, int64_t buffer_len, int64_t* out_len, char* out) {
   API_BEGIN(); BW();
-  auto buf = b->gbdt->SaveModelToBinary(start_iteration, num_iteration, f32_leaves != 0);
+  auto buf = b->gbdt->SaveModelToBinary(start_iteration, num_iteration, feature_importance_type, with_stats != 0, with_diagnostics != 0, f32_leaves != 0, compress_level);
   *out_len = static_cast<int64_t>(buf.size());
   if (buffer_len >= *out_len && out != nullptr) memcpy(out, buf.data(), buf.size());
   API_END();

@@ -582,7 +582,12 @@ int GBDT::NumPredictOneRow(int predict_type, int start_iter, int num_iter) const
   start_iter = std::max(0, std::min(start_iter, iters));
   int use = num_iter > 0 ? std::min(num_iter, iters - start_iter) : iters - start_iter;
   if (predict_type == 2) return use * K;
-  if (predict_type == 3) return K * (max_feature_idx_ + 2);
+  if (predict_type == 3) {
+    // every prediction entry point sizes its output through here, outside any parallel region
+    if (falb_without_stats_)
+      Log::Fatal("Feature contributions need the per-node counts, which this binary model was saved without; save it with with_stats=true or use the text model");
+    return K * (max_feature_idx_ + 2);
+  }
   return K;
 }
 

@@ -98,8 +98,8 @@ int FB_BoosterSaveModelToString(BoosterHandle handle, int start_iteration, int n
 int FB_BoosterDumpModel(BoosterHandle handle, int start_iteration, int num_iteration, int feature_importance_type, int64_t buffer_len,
                         int64_t* out_len, char* out_str);
 int FB_BoosterModelToIfElse(BoosterHandle handle, int num_iteration, int64_t buffer_len, int64_t* out_len, char* out_str);
-int FB_BoosterSaveModelToBinary(BoosterHandle handle, int start_iteration, int num_iteration, int f32_leaves, int64_t buffer_len, int64_t* out_len,
-                                char* out);
+int FB_BoosterSaveModelToBinary(BoosterHandle handle, int start_iteration, int num_iteration, int feature_importance_type, int with_stats,
+                                int with_diagnostics, int f32_leaves, int compress_level, int64_t buffer_len, int64_t* out_len, char* out);
 int FB_BoosterGetLeafValue(BoosterHandle handle, int tree_idx, int leaf_idx, double* out_val);
 int FB_BoosterSetLeafValue(BoosterHandle handle, int tree_idx, int leaf_idx, double val);
 int FB_BoosterFeatureImportance(BoosterHandle handle, int num_iteration, int importance_type, double* out_results);

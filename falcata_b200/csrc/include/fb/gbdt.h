@@ -73,7 +73,12 @@ class GBDT {
   std::string DumpModel(int start_iter, int num_iter, int importance_type) const;
   std::string ModelToIfElse(int num_iter) const;
   std::vector<double> FeatureImportance(int num_iter, int importance_type) const;
-  std::vector<char> SaveModelToBinary(int start_iter, int num_iter, bool f32_leaves) const;
+  // FALB container (the reference's layout). Node statistics (counts / weights: needed by TreeSHAP, JSON dumps, refit) and
+  // diagnostics (split gains, internal values: needed by gain importance) are optional sections; compress_level 0 leaves every
+  // section raw.
+  std::vector<char> SaveModelToBinary(int start_iter, int num_iter, int importance_type, bool with_stats, bool with_diagnostics, bool f32_leaves,
+                                      int compress_level) const;
+  bool falb_without_stats_ = false;   // loaded from a FALB file that carries no node statistics: contributions cannot be computed
   bool LoadModelFromBinary(const char* data, size_t len);
 
   double GetLeafValue(int tree, int leaf) const { return models_[tree]->leaf_value[leaf]; }
