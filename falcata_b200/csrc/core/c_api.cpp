@@ -401,13 +401,10 @@ int FB_BoosterCalcNumPredict(BoosterHandle handle, int num_row, int predict_type
 int FB_BoosterPredictForMat(BoosterHandle handle, const void* data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, int predict_type,
                             int start_iteration, int num_iteration, const char* parameter, int64_t* out_len, double* out_result) {
   API_BEGIN(); BW();
-  auto m = Config::Str2Map(parameter);
-  if (m.count("pred_early_stop")) b->gbdt->config_.pred_early_stop = m["pred_early_stop"] == "true" || m["pred_early_stop"] == "1";
-  if (m.count("pred_early_stop_freq")) b->gbdt->config_.pred_early_stop_freq = atoi(m["pred_early_stop_freq"].c_str());
-  if (m.count("pred_early_stop_margin")) b->gbdt->config_.pred_early_stop_margin = ParseDouble(m["pred_early_stop_margin"]);
-  if (m.count("predict_disable_shape_check")) b->gbdt->config_.predict_disable_shape_check = m["predict_disable_shape_check"] == "true" || m["predict_disable_shape_check"] == "1";
+  // the options of this call only: nothing is written into the booster, so a later call that omits them gets the defaults
+  const PredictParams pp = PredictParams::FromString(parameter);
   *out_len = static_cast<int64_t>(nrow) * b->gbdt->NumPredictOneRow(predict_type, start_iteration, num_iteration);
-  b->gbdt->PredictMat(data, dtype, nrow, ncol, is_row_major != 0, predict_type, start_iteration, num_iteration, out_result);
+  b->gbdt->PredictMat(data, dtype, nrow, ncol, is_row_major != 0, predict_type, start_iteration, num_iteration, out_result, pp);
   API_END();
 }
 // ---- single-row and sparse entry points --------------------------------------------------------------------
@@ -419,7 +416,8 @@ int FB_BoosterPredictForMatSingleRow(BoosterHandle handle, const void* data, int
 }
 
 namespace {
-struct FastConfig { BoosterHandle booster; int predict_type, start_iteration, num_iteration, dtype; int32_t ncol; std::string parameter; };
+// Everything a single-row prediction needs, resolved once: the parameter string is parsed at FastInit, not per row.
+struct FastConfig { BoosterHandle booster; int predict_type, start_iteration, num_iteration, dtype; int32_t ncol; PredictParams pp; int per_row; };
 // rows [r0, r1) of a CSR matrix as a dense row-major double block
 void DensifyCSR(const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t r0, int64_t r1, int64_t num_col, std::vector<double>* out) {
   out->assign(static_cast<size_t>(r1 - r0) * num_col, 0.0);
@@ -436,13 +434,19 @@ void DensifyCSR(const void* indptr, int indptr_type, const int32_t* indices, con
 int FB_BoosterPredictForMatSingleRowFastInit(BoosterHandle handle, int predict_type, int start_iteration, int num_iteration, int dtype, int32_t ncol,
                                              const char* parameter, void** out_fast_config) {
   API_BEGIN();
-  FastConfig* fc = new FastConfig{handle, predict_type, start_iteration, num_iteration, dtype, ncol, parameter ? parameter : ""};
+  BW();
+  FastConfig* fc = new FastConfig{handle, predict_type, start_iteration, num_iteration, dtype, ncol, PredictParams::FromString(parameter),
+                                  b->gbdt->NumPredictOneRow(predict_type, start_iteration, num_iteration)};
   *out_fast_config = fc;
   API_END();
 }
 int FB_BoosterPredictForMatSingleRowFast(void* fast_config, const void* data, int64_t* out_len, double* out_result) {
+  API_BEGIN();
   const FastConfig* fc = static_cast<const FastConfig*>(fast_config);
-  return FB_BoosterPredictForMat(fc->booster, data, fc->dtype, 1, fc->ncol, 1, fc->predict_type, fc->start_iteration, fc->num_iteration, fc->parameter.c_str(), out_len, out_result);
+  BoosterHandle handle = fc->booster; BW();
+  *out_len = fc->per_row;
+  b->gbdt->PredictMat(data, fc->dtype, 1, fc->ncol, true, fc->predict_type, fc->start_iteration, fc->num_iteration, out_result, fc->pp);
+  API_END();
 }
 int FB_FastConfigFree(void* fast_config) { API_BEGIN(); delete static_cast<FastConfig*>(fast_config); API_END(); }
 
@@ -660,26 +664,42 @@ double ArrowValue(const FBArrowArray* col, const char* fmt, int64_t i) {
   }
 }
 
-// all batches as one row-major double matrix; releases the batches and the schema
+// Releases the batches and the schema when it goes out of scope, whichever way the call ends: the consumer of an Arrow C
+// data structure owns it from the moment it is handed over.
+struct ArrowOwner {
+  int64_t n; FBArrowArray* chunks; FBArrowSchema* schema;
+  ~ArrowOwner() {
+    for (int64_t c = 0; c < n; ++c) if (chunks != nullptr && chunks[c].release != nullptr) chunks[c].release(&chunks[c]);
+    if (schema != nullptr && schema->release != nullptr) schema->release(schema);
+  }
+};
+
+// all batches as one row-major double matrix
 void ArrowToDense(int64_t n_chunks, FBArrowArray* chunks, FBArrowSchema* schema, std::vector<double>* out, int64_t* nrow, int32_t* ncol) {
-  if (schema->format == nullptr || schema->format[0] != '+' || schema->format[1] != 's') Log::Fatal("The Arrow data must be record batches (struct arrays)");
+  ArrowOwner owner{n_chunks, chunks, schema};
+  if (schema == nullptr || schema->format == nullptr || schema->format[0] != '+' || schema->format[1] != 's') Log::Fatal("The Arrow data must be record batches (struct arrays)");
   *ncol = static_cast<int32_t>(schema->n_children);
   *nrow = 0;
   for (int64_t c = 0; c < n_chunks; ++c) *nrow += chunks[c].length;
+  if (*nrow > 2147483647LL) Log::Fatal("Arrow input has %lld rows; at most 2^31 - 1 are supported", static_cast<long long>(*nrow));
   out->assign(static_cast<size_t>(*nrow) * (*ncol), 0.0);
   int64_t at = 0;
   for (int64_t c = 0; c < n_chunks; ++c) {
     const FBArrowArray& batch = chunks[c];
     if (batch.n_children != schema->n_children) Log::Fatal("An Arrow batch has %lld columns, the schema %lld", static_cast<long long>(batch.n_children), static_cast<long long>(schema->n_children));
+    // validity bitmap of the record batch itself: a null struct row reads as missing in every column
+    const uint8_t* row_valid = (batch.n_buffers > 0 && batch.buffers != nullptr) ? static_cast<const uint8_t*>(batch.buffers[0]) : nullptr;
     for (int32_t j = 0; j < *ncol; ++j) {
       const FBArrowArray* col = batch.children[j];
       const char* fmt = schema->children[j]->format;
-      for (int64_t i = 0; i < batch.length; ++i) (*out)[static_cast<size_t>(at + i) * (*ncol) + j] = ArrowValue(col, fmt, batch.offset + i);
+      for (int64_t i = 0; i < batch.length; ++i) {
+        const int64_t r = batch.offset + i;
+        const bool row_null = row_valid != nullptr && !((row_valid[r >> 3] >> (r & 7)) & 1);
+        (*out)[static_cast<size_t>(at + i) * (*ncol) + j] = row_null ? std::numeric_limits<double>::quiet_NaN() : ArrowValue(col, fmt, r);
+      }
     }
     at += batch.length;
   }
-  for (int64_t c = 0; c < n_chunks; ++c) if (chunks[c].release != nullptr) chunks[c].release(&chunks[c]);
-  if (schema->release != nullptr) schema->release(schema);
 }
 }  // namespace
 

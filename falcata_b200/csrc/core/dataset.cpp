@@ -408,4 +408,24 @@ Dataset* Dataset::Subset(const data_size_t* idx, data_size_t n) const {
   return ds.release();
 }
 
+bool Dataset::CheckAlign(const Dataset& o) const {
+  if (num_total_features != o.num_total_features || num_features != o.num_features || num_groups != o.num_groups || num_total_bin != o.num_total_bin) return false;
+  if (used_feature_map != o.used_feature_map || group_bin_start != o.group_bin_start || group_features != o.group_features) return false;
+  for (int f = 0; f < num_total_features; ++f) {
+    const BinMapper* a = mappers[f].get(); const BinMapper* b = o.mappers[f].get();
+    if ((a == nullptr) != (b == nullptr)) return false;
+    if (a == nullptr) continue;
+    if (a->num_bin != b->num_bin || a->bin_type != b->bin_type || a->missing_type != b->missing_type || a->default_bin != b->default_bin ||
+        a->most_freq_bin != b->most_freq_bin || a->is_trivial != b->is_trivial) return false;
+    if (a->bin_type == BinType::Numerical) {
+      if (a->bin_upper_bound.size() != b->bin_upper_bound.size()) return false;
+      for (size_t k = 0; k < a->bin_upper_bound.size(); ++k) {
+        const double x = a->bin_upper_bound[k], y = b->bin_upper_bound[k];
+        if (!(x == y || (std::isnan(x) && std::isnan(y)))) return false;
+      }
+    } else if (a->bin_2_categorical != b->bin_2_categorical) return false;
+  }
+  return true;
+}
+
 }  // namespace fb

@@ -65,6 +65,9 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
 
 // Parity: src/boosting/gbdt.cpp (GBDT::ResetTrainingData: new learner state and score updater, scores replayed tree by tree).
 void GBDT::ResetTrainingData(const Config& cfg, const Dataset* train, ObjectiveFunction* obj, const std::vector<std::string>& metric_names) {
+  // the existing trees are replayed on the new rows by bin index: that is only meaningful when both datasets bin alike
+  if (train_ != nullptr && train != train_ && !models_.empty() && !train_->CheckAlign(*train))
+    Log::Fatal("Cannot reset training data: the new dataset's bin mappers differ from the old one's (construct it with reference= the original training data)");
   std::vector<std::unique_ptr<Tree>> models = std::move(models_);
   const int iter = iter_;
   valid_.clear(); valid_score_.clear();
@@ -591,7 +594,19 @@ int GBDT::NumPredictOneRow(int predict_type, int start_iter, int num_iter) const
   return K;
 }
 
-void GBDT::PredictRow(const double* row, int predict_type, int start_iter, int num_iter, double* out) const {
+PredictParams PredictParams::FromString(const char* parameter) {
+  PredictParams pp;
+  if (parameter == nullptr || *parameter == 0) return pp;
+  auto m = Config::Str2Map(parameter);
+  auto truthy = [](const std::string& v) { return v == "true" || v == "1" || v == "True" || v == "+"; };
+  if (m.count("pred_early_stop")) pp.early_stop = truthy(m["pred_early_stop"]);
+  if (m.count("pred_early_stop_freq")) pp.early_stop_freq = std::max(1, atoi(m["pred_early_stop_freq"].c_str()));
+  if (m.count("pred_early_stop_margin")) pp.early_stop_margin = ParseDouble(m["pred_early_stop_margin"]);
+  if (m.count("predict_disable_shape_check")) pp.disable_shape_check = truthy(m["predict_disable_shape_check"]);
+  return pp;
+}
+
+void GBDT::PredictRow(const double* row, int predict_type, int start_iter, int num_iter, double* out, const PredictParams& pp) const {
   const int K = num_tree_per_iteration_; int iters = static_cast<int>(models_.size()) / K;
   start_iter = std::max(0, std::min(start_iter, iters));
   const int use = num_iter > 0 ? std::min(num_iter, iters - start_iter) : iters - start_iter;
@@ -604,14 +619,14 @@ void GBDT::PredictRow(const double* row, int predict_type, int start_iter, int n
     return;
   }
   std::vector<double> raw(K, 0.0);
-  const bool early = config_.pred_early_stop && predict_type == 0 && (K > 1 || (objective_ && std::string(objective_->GetName()) == "binary"));
+  const bool early = pp.early_stop && predict_type == 0 && (K > 1 || (objective_ && std::string(objective_->GetName()) == "binary"));
   for (int t = begin; t < end; ++t) {
     raw[t % K] += models_[t]->Predict(row);
-    if (early && ((t - begin + 1) % (config_.pred_early_stop_freq * K) == 0)) {
+    if (early && ((t - begin + 1) % (pp.early_stop_freq * K) == 0)) {
       double margin;
       if (K == 1) margin = 2.0 * std::fabs(raw[0]);
       else { std::vector<double> s(raw); std::partial_sort(s.begin(), s.begin() + 2, s.end(), std::greater<double>()); margin = s[0] - s[1]; }
-      if (margin > config_.pred_early_stop_margin) break;
+      if (margin > pp.early_stop_margin) break;
     }
   }
   if (average_output_ && use > 0) for (int k = 0; k < K; ++k) raw[k] /= use;
@@ -619,9 +634,9 @@ void GBDT::PredictRow(const double* row, int predict_type, int start_iter, int n
   else objective_->ConvertOutput(raw.data(), out);
 }
 
-void GBDT::PredictMat(const void* data, int dtype, int nrow, int ncol, bool row_major, int predict_type, int start_iter, int num_iter, double* out) const {
+void GBDT::PredictMat(const void* data, int dtype, int nrow, int ncol, bool row_major, int predict_type, int start_iter, int num_iter, double* out, const PredictParams& pp) const {
   const int per = NumPredictOneRow(predict_type, start_iter, num_iter);
-  if (ncol <= max_feature_idx_ && !config_.predict_disable_shape_check)
+  if (ncol <= max_feature_idx_ && !pp.disable_shape_check)
     Log::Fatal("The number of features in data (%d) is not the same as it was in training data (%d)", ncol, max_feature_idx_ + 1);
 #pragma omp parallel
   {
@@ -641,7 +656,7 @@ void GBDT::PredictMat(const void* data, int dtype, int nrow, int ncol, bool row_
           default: row[j] = 0.0;
         }
       }
-      PredictRow(row.data(), predict_type, start_iter, num_iter, out + static_cast<size_t>(i) * per);
+      PredictRow(row.data(), predict_type, start_iter, num_iter, out + static_cast<size_t>(i) * per, pp);
     }
   }
 }

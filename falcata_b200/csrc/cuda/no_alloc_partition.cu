@@ -48,12 +48,17 @@ int FB_OpPartitionNoAlloc(const uint8_t* rows, int row_stride, const int* idx, i
   try {
     if (count < 0 || count > FB_NO_ALLOC_MAX_ROWS)
       Log::Fatal("FB_OpPartitionNoAlloc handles at most %d rows per call (got %d): split the call or use FB_OpPartition", FB_NO_ALLOC_MAX_ROWS, count);
+    if (row_stride <= 0 || group < 0 || group >= row_stride)
+      Log::Fatal("FB_OpPartitionNoAlloc: feature group %d is outside a row of %d bytes", group, row_stride);
+    if (left_count_device == nullptr || (count > 0 && (rows == nullptr || idx == nullptr || out_idx == nullptr)))
+      Log::Fatal("FB_OpPartitionNoAlloc: a null buffer was passed (rows, idx, out_idx and left_count_device must be device pointers)");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int dev = 0;
     FB_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDevices) Log::Fatal("device ordinal %d is outside the supported range", dev);
     if (g_scratch_addr[dev] == nullptr) {
-      // first call on this device: resolve the device address of the scratch array (no allocation)
+      // first call on this device: resolve the device address of the scratch array (no allocation). Two host
+      // threads that both make a first call may both run the lookup; they store the same value, so the race is harmless.
       void* p = nullptr;
       const cudaError_t e = cudaGetSymbolAddress(&p, g_no_alloc_scratch);
       if (e != cudaSuccess || p == nullptr) Log::Fatal("cudaGetSymbolAddress failed for the scratch array: %s", cudaGetErrorString(e));

@@ -116,6 +116,10 @@ class Dataset {
     return rel >= m.most_freq_bin ? rel + 1 : rel;
   }
   std::string FeatureInfos() const;
+  // True when `other` bins values exactly like this dataset: same features in use, same groups and, per feature, the same
+  // bin boundaries / categories, missing handling and default / most frequent bins. Trees refer to data by bin index, so
+  // only aligned datasets can replay a model's trees. Parity: Dataset::CheckAlign (include/Falcata/dataset.h).
+  bool CheckAlign(const Dataset& other) const;
   bool has_host_bins() const { return !bins8.empty() || !bins16.empty(); }
   void SerializeSchema(std::vector<char>* out) const;
   void DeserializeSchema(const char* p, size_t n, const Config& cfg);

@@ -37,6 +37,12 @@ class DeviceEngine {
 DeviceEngine* CreateDeviceEngine(const Config& cfg, const Dataset* train, const ObjectiveFunction* obj, int num_tree_per_iter);
 bool CudaAvailable();
 
+// Options of ONE predict call (parsed from its parameter string; nothing of them outlives the call).
+struct PredictParams {
+  bool early_stop = false; int early_stop_freq = 10; double early_stop_margin = 10.0; bool disable_shape_check = false;
+  static PredictParams FromString(const char* parameter);
+};
+
 class GBDT {
  public:
   GBDT() {}
@@ -64,8 +70,9 @@ class GBDT {
   // ---- prediction on raw feature rows ----
   // predict_type: 0 normal, 1 raw, 2 leaf index, 3 contrib
   int NumPredictOneRow(int predict_type, int start_iter, int num_iter) const;
-  void PredictRow(const double* row, int predict_type, int start_iter, int num_iter, double* out) const;
-  void PredictMat(const void* data, int dtype, int nrow, int ncol, bool row_major, int predict_type, int start_iter, int num_iter, double* out) const;
+  void PredictRow(const double* row, int predict_type, int start_iter, int num_iter, double* out, const PredictParams& pp = PredictParams()) const;
+  void PredictMat(const void* data, int dtype, int nrow, int ncol, bool row_major, int predict_type, int start_iter, int num_iter, double* out,
+                  const PredictParams& pp = PredictParams()) const;
 
   // ---- model IO ----
   std::string SaveModelToString(int start_iter, int num_iter, int importance_type) const;

@@ -18,7 +18,10 @@
  *  - the scratch array (about 0.6 MB) is part of the library: every GPU that loads the library
  *    holds it until the process exits;
  *  - the first call on each device looks up the array's device address (no allocation, but a
- *    runtime query): make that first call outside of any stream capture;
+ *    runtime query): make that first call outside of any stream capture. Host threads that race
+ *    on that first call each do the lookup and store the same address, which is harmless;
+ *  - the feature group must lie inside a row (0 <= group < row_stride) and the buffers must be
+ *    non-null device pointers; a call with count == 0 is valid and reports 0 rows on the left;
  *  - all calls share the one array and it keeps whatever the previous call left in it, so two
  *    calls that overlap on the same GPU (different streams or threads) corrupt each other: issue
  *    them one after another;

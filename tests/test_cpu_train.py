@@ -236,3 +236,22 @@ def test_cegb_split_penalty_makes_smaller_trees():
     taxed = fb.train({**p, "cegb_penalty_split": 0.05, "cegb_tradeoff": 1.0}, fb.Dataset(X, y), 3)
     leaves = lambda b: sum(t["num_leaves"] for t in b.dump_model()["tree_info"])
     assert leaves(free) == 93 and 3 < leaves(taxed) < leaves(free)
+
+
+def test_reset_training_data_needs_aligned_bins():
+    """Trees refer to rows by bin index, so continuing on a dataset that was binned on its own is refused;
+    a dataset constructed against the original one (same bin mappers) is accepted and scores correctly."""
+    X, y = make_binary(3000, 8)
+    X2, y2 = make_binary(3000, 8, seed=7)
+    train = fb.Dataset(X, y, params={"max_bin": 63})
+    bst = fb.train({"objective": "binary", "device_type": "cpu", "verbosity": -1, "max_bin": 63}, train, 5, keep_training_booster=True)
+    stranger = fb.Dataset(X2, y2, params={"max_bin": 15}).construct()   # own mappers, other bin count
+    with pytest.raises(fb.FalcataError, match="bin mappers differ"):
+        bst.update(train_set=stranger)
+    aligned = fb.Dataset(X2, y2, reference=train)
+    bst.update(train_set=aligned)
+    # the replayed training scores are the model's real scores on the new rows (6 trees now; check via the metric)
+    p = np.clip(bst.predict(X2), 1e-15, 1 - 1e-15)
+    want = float(-np.mean(y2 * np.log(p) + (1 - y2) * np.log(1 - p)))
+    got = [v for (_, name, v, _) in bst.eval_train() if name == "binary_logloss"][0]
+    assert abs(got - want) < 1e-6

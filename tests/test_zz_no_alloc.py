@@ -56,6 +56,38 @@ def test_no_alloc_partition_matches_allocating_entry_twice():
         assert torch.equal(got_out, ref_out)      # integer row ids: exact equality, as in the other partition tests
 
 
+def test_no_alloc_partition_at_the_largest_size_and_with_no_rows():
+    """The two ends of the accepted range: every chunk counter of the fixed scratch array in use, and none."""
+    from falcata_b200 import ops
+    from falcata_b200.basic import _lib
+
+    lib = _lib()
+    n = 1 << 22
+    rows = _rows(n, seed=3)
+    idx = torch.arange(n, dtype=torch.int32, device="cuda")
+    ref_out, ref_left = ops.partition(rows, idx, group=1, threshold=30, default_left=True, missing_type=0, default_bin=0, num_bin=64)
+    got_out, got_left = _no_alloc_partition(lib, rows, idx, 1, 30, True, 0, 0, 64)
+    assert got_left == ref_left and torch.equal(got_out, ref_out)
+    empty = idx[:0].contiguous()
+    got_out, got_left = _no_alloc_partition(lib, rows, empty, 1, 30, True, 0, 0, 64)
+    assert got_left == 0 and got_out.numel() == 0
+
+
+def test_no_alloc_partition_rejects_bad_arguments():
+    from falcata_b200.basic import _lib
+
+    lib = _lib()
+    lib.FB_NoAllocLastError.restype = ctypes.c_char_p
+    rows = _rows(16)
+    idx = torch.zeros(16, dtype=torch.int32, device="cuda")
+    out = torch.empty_like(idx); left = torch.zeros(1, dtype=torch.int32, device="cuda")
+    args = lambda group, idx_ptr: (ctypes.c_void_p(rows.data_ptr()), 16, ctypes.c_void_p(idx_ptr), 16, group, 1, 1, 0, 0, 64,
+                                   ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(left.data_ptr()), ctypes.c_void_p(0))
+    assert lib.FB_OpPartitionNoAlloc(*args(16, idx.data_ptr())) == -1 and b"feature group" in lib.FB_NoAllocLastError()
+    assert lib.FB_OpPartitionNoAlloc(*args(-1, idx.data_ptr())) == -1
+    assert lib.FB_OpPartitionNoAlloc(*args(0, 0)) == -1 and b"null buffer" in lib.FB_NoAllocLastError()
+
+
 def test_no_alloc_partition_rejects_oversized_call():
     from falcata_b200.basic import _lib
 
