@@ -52,7 +52,10 @@ MODEL_NAME = "gbdt binary 11Mx28, num_leaves=255, max_bin=63, quant_mode=stochas
 
 
 class ClockSampler:
-    """nvidia-smi SM clock / throttle-reason samples taken while the timed region runs."""
+    """SM clock and throttle-reason samples taken while the timed region runs (read-only NVML queries every few
+    milliseconds, so that even a 50 ms region yields several samples; `nvidia-smi` as the fallback)."""
+
+    _REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, index: int) -> None:
         self.index = index
@@ -62,7 +65,38 @@ class ClockSampler:
         self._stop = threading.Event()
         self._t = threading.Thread(target=self._run, daemon=True)
 
+    def _run_nvml(self) -> bool:
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            # NVML numbers the GPUs of the whole box: map the CUDA ordinal through CUDA_VISIBLE_DEVICES when it is set
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = self.index
+            if vis:
+                ids = [v.strip() for v in vis.split(",") if v.strip()]
+                if self.index < len(ids) and ids[self.index].isdigit():
+                    idx = int(ids[self.index])
+            h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            return False
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                mask = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)) if hasattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                for name, bit in self._REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.004)
+        return True
+
     def _run(self) -> None:
+        if self._run_nvml():
+            return
         q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         while not self._stop.is_set():
@@ -80,6 +114,7 @@ class ClockSampler:
 
     def __enter__(self):
         self._t.start()
+        time.sleep(0.02)   # the sampler is up before the timed region starts
         return self
 
     def __exit__(self, *a):

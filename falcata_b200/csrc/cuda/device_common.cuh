@@ -27,7 +27,10 @@ namespace fb {
 // Number of kernels launched by this library in this process (reported by bench.py).
 inline std::atomic<int64_t>& LaunchCounter() { static std::atomic<int64_t> c{0}; return c; }
 #define FB_LAUNCHED() (::fb::LaunchCounter().fetch_add(1, std::memory_order_relaxed))
-#define FB_KERNEL_CHECK() FB_CUDA(cudaGetLastError())
+// FALCATA_DEBUG_SYNC=1 serialises the device work: every launcher waits for its kernel and reports an error at the
+// launch site (file:line of the launcher) instead of at the next synchronisation point of the training loop.
+inline bool DebugSyncLaunches() { static const bool v = getenv("FALCATA_DEBUG_SYNC") != nullptr; return v; }
+#define FB_KERNEL_CHECK() do { FB_CUDA(cudaGetLastError()); if (::fb::DebugSyncLaunches()) FB_CUDA(cudaDeviceSynchronize()); } while (0)
 
 template <typename T>
 class DevBuf {

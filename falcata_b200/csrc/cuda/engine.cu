@@ -129,7 +129,7 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   host_leaves_.resize(NL);
   use_ctrl_ = plan_.device_controller && NL <= 1024;
   if (use_ctrl_) {
-    ctrl_.Alloc(1); frontier_.Alloc(NL + 2); journal_.Alloc(NL); h_ctrl_.Alloc(1); h_journal_.Alloc(NL); h_root_.Alloc(1);
+    ctrl_.Alloc(2); frontier_.Alloc(NL + 2); journal_.Alloc(NL); h_ctrl_.Alloc(1); h_journal_.Alloc(NL); h_root_.Alloc(1);
     levels_hint_ = 1; while ((1 << levels_hint_) < NL) ++levels_hint_;
   }
   node_mask_on_ = col_sampler_.by_node();
@@ -198,6 +198,8 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     pool_base_ = pool_.get();
   }
   cand_.Alloc(static_cast<size_t>(NL) * std::max<size_t>(1, owned_features_.size())); cand_.Zero(stream_);
+  root_child_.Alloc(1); child_done_.Alloc(2 * static_cast<size_t>(NL) + 2); child_done_.Zero(stream_); level_done_.Alloc(1); level_done_.Zero(stream_);
+  split_done_.Alloc(NL + 1); split_done_.Zero(stream_);
   hist_tasks_.Alloc(NL); hist_status_.Alloc(1); hist_status_.Zero(stream_); h_hist_status_.Alloc(1); *h_hist_status_.get() = 0;
   const size_t max_chunks = static_cast<size_t>(n_) / kPartChunk + NL + 1;
   bits_.Alloc(max_chunks * (kPartChunk / 32)); chunk_left_.Alloc(max_chunks); split_left_total_.Alloc(NL);

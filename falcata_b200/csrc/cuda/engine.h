@@ -137,7 +137,9 @@ class CudaEngine : public DeviceEngine {
   bool use_ctrl_ = false; int levels_hint_ = 8;
   // score update enqueued from the device's leaf records, before the per-tree read-back
   bool fast_score_ok_ = false, score_done_ = false; double cur_shrinkage_ = 1.0; float* cur_score_ = nullptr;
-  DevBuf<LevelCtrl> ctrl_; DevBuf<int> frontier_; DevBuf<SplitJournal> journal_;
+  DevBuf<LevelCtrl> ctrl_; DevBuf<int> frontier_; DevBuf<SplitJournal> journal_;   // ctrl_: two level records (a ring, see TrainTree)
+  DevBuf<FindChild> root_child_;                                   // the root's search descriptor
+  DevBuf<unsigned int> child_done_, level_done_, split_done_;     // arrival counters of the fused kernels (zero between launches)
   PinnedBuf<LevelCtrl> h_ctrl_; PinnedBuf<SplitJournal> h_journal_; PinnedBuf<LeafInfo> h_root_;
   // bagging (device-drawn; -1 = no bag drawn)
   double bag_fraction_ = 1.0; int bag_freq_ = 0, bag_seed_ = 0;

@@ -16,20 +16,6 @@ namespace fb {
 
 namespace {
 
-// Root leaf record from the device-side sums (no host round trip between quantize and the root histogram).
-__global__ void InitRootKernel(LeafInfo* leaves, const long long* sums_i, const double* sums_d, const float* scales, int quant, int n_local,
-                               long long n_global, SplitParams sp) {
-  LeafInfo L;
-  L.begin = 0; L.count = n_local; L.buffer = 0; L.depth = 0; L.hist_slot = 0; L.num_data_global = static_cast<int>(n_global);
-  if (quant) {
-    L.sum_gi = sums_i[0]; L.sum_hi = sums_i[1];
-    L.sum_g = FB_MUL(static_cast<double>(L.sum_gi), static_cast<double>(scales[0])); L.sum_h = FB_MUL(static_cast<double>(L.sum_hi), static_cast<double>(scales[1]));
-  } else { L.sum_gi = L.sum_hi = 0; L.sum_g = sums_d[0]; L.sum_h = sums_d[1]; }
-  L.output = LeafOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp, L.num_data_global, 0.0);
-  L.min_c = -1.0 / 0.0; L.max_c = 1.0 / 0.0; for (int k = 0; k < 4; ++k) L.pkey[k] = 1.0 / 0.0;
-  leaves[0] = L;
-}
-
 // One split of the device's record applied to the host tree (numerical threshold or categorical set).
 int ApplySplit(Tree* tree, const Dataset* ds, int leaf, const SplitRecord& b) {
   const FeatureMeta& m = ds->feature_meta[b.feature];
@@ -168,9 +154,18 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     LaunchInterleave(cur_grad_, cur_hess_, n_, gh2_.get(), partial_.get(), static_cast<int>(partial_.size() / 2), root_sums_d_.get(), stream_, bag_mask_ptr());
     if (data_parallel()) fabric_->AllReduce(kFabricSumF64, root_sums_d_.get(), root_sums_d_.get(), 2, stream_);
   }
-  InitRootKernel<<<1, 1, 0, stream_>>>(leaves_.get(), root_sums_i_.get(), root_sums_d_.get(), scales_.get(), quant_ ? 1 : 0, root_count_, root_global_, sp_);
-  FB_LAUNCHED(); FB_KERNEL_CHECK();
   const bool bagged = bag_active_;
+  {
+    // root leaf record, level-record ring, frontier, the root's construct task and search descriptor: one small kernel
+    TreeInitArgs ti;
+    ti.leaves = leaves_.get(); ti.sums_i = root_sums_i_.get(); ti.sums_d = root_sums_d_.get(); ti.scales = scales_.get(); ti.quant = quant_ ? 1 : 0;
+    ti.n_local = root_count_; ti.n_global = root_global_; ti.sp = sp_;
+    ti.ctrl = use_ctrl_ ? ctrl_.get() : nullptr; ti.frontier = use_ctrl_ ? frontier_.get() : nullptr;
+    ti.root_task = hist_tasks_.get(); ti.root_child = root_child_.get();
+    const int rpb0 = ChooseRowsPerBlock(root_count_);
+    ti.root_blocks = std::max(1, (root_count_ + rpb0 - 1) / rpb0);
+    LaunchInitTree(ti, stream_);
+  }
   if (bagged) FB_CUDA(cudaMemcpyAsync(idx_[0].get(), bag_idx_.get(), sizeof(int) * static_cast<size_t>(root_count_), cudaMemcpyDeviceToDevice, stream_));
   else LaunchInitIndices(idx_[0].get(), n_, stream_);
   clock_.End(stream_);
@@ -284,6 +279,13 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     fl.wait.world = 1; fl.wait_best.world = 1; fl.sig.world = 1; fl.voted = nullptr; fl.local_vote = 1; fl.vote_sums = vote_sums_.get();
     fl.has_categorical = 0; for (int f : feats_all) if (train_->feature_meta[f].bin_type != 0) fl.has_categorical = 1;
   }
+  // Device-controlled growth keeps two level records: the kernels of level k read ring[k & 1] while the controller
+  // (the tail of level k's search) writes level k + 1's record into the other half, so a block that starts late
+  // never sees the next level's sizes.
+  const bool fused_tail = use_ctrl_ && plan_.fused_tail;
+  CtrlArgs ca = CtrlArgs();
+  fa.fused_tail = fused_tail ? 1 : 0; fa.run_controller = fused_tail ? 1 : 0; fa.child_done = child_done_.get(); fa.level_done = level_done_.get();
+  fl.fused_tail = 0; fl.run_controller = 0;
   auto construct_and_find = [&]() {
     if (rs) { ha.sig.epoch = fabric_->NextEpoch(); fa.wait.epoch = ha.sig.epoch; }
     clock_.Begin(st_hist_, stream_);
@@ -303,7 +305,8 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     if (world_ > 1) { fa.sig.epoch = fabric_->NextEpoch(); fa.wait_best.epoch = fa.sig.epoch; }
     clock_.Begin(st_find_, stream_);
     if (node_mask_on_) { nm.children = fa.children; nm.num_children = fa.num_children; nm.ctrl = fa.ctrl; LaunchNodeMask(nm, stream_); }
-    LaunchFindSplits(fa, stream_); LaunchReduceBest(fa, stream_); LaunchGatherBest(fa, stream_);
+    if (fused_tail) LaunchFindSplits(fa, stream_, &ca);   // search + per-leaf argmax + cross-rank argmax + level controller
+    else { LaunchFindSplits(fa, stream_); LaunchReduceBest(fa, stream_); LaunchGatherBest(fa, stream_); }
     clock_.End(stream_);
   };
 
@@ -312,47 +315,52 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
 
   // ---- root ----
   {
-    HistTask t; t.slot = 0; t.begin = 0; t.count = root_count_; t.buffer = 0; t.block_begin = 0; t.pad0 = t.pad1 = 0;
-    ha.rows_per_block = ChooseRowsPerBlock(root_count_); t.num_blocks = std::max(1, (root_count_ + ha.rows_per_block - 1) / ha.rows_per_block);
-    FindChild fc; fc.leaf = 0; fc.slot = 0; fc.other_slot = 0; fc.is_larger = 0; fc.split = -1; fc.is_left = 1; fc.parent_global = 0; fc.task = 0;
-    memcpy(hb, &t, sizeof(t)); memcpy(hb + sizeof(t), &fc, sizeof(fc));
-    FB_CUDA(cudaMemcpyAsync(db, hb, sizeof(t) + sizeof(fc), cudaMemcpyHostToDevice, stream_));
-    FB_CUDA(cudaMemcpyAsync(hist_tasks_.get(), db, sizeof(t), cudaMemcpyDeviceToDevice, stream_));
-    ha.num_tasks = 1; ha.total_blocks = std::max(1, t.num_blocks); ha.identity_root = bagged ? 0 : 1;
-    fa.children = reinterpret_cast<const FindChild*>(db + sizeof(t)); fa.num_children = 1;
-    construct_and_find();
+    // the root's task and search descriptor were written by the tree-init kernel
+    ha.rows_per_block = ChooseRowsPerBlock(root_count_);
+    ha.num_tasks = 1; ha.total_blocks = std::max(1, (root_count_ + ha.rows_per_block - 1) / ha.rows_per_block); ha.identity_root = bagged ? 0 : 1;
+    fa.children = root_child_.get(); fa.num_children = 1;
   }
+  const int rpb = ChooseRowsPerBlock(std::max(1, n_ / 2));
+  const int max_splits = NL / 2 + 1;
   if (use_ctrl_) {
-    // ---- device-controlled growth: levels are enqueued ahead; the host reads one small record per batch ----
-    LaunchInitLevelCtrl(ctrl_.get(), frontier_.get(), stream_);
-    FB_CUDA(cudaMemcpyAsync(h_root_.get(), leaves_.get(), sizeof(LeafInfo), cudaMemcpyDeviceToHost, stream_));   // the root record, before any split rewrites leaf 0
-    const int rpb = ChooseRowsPerBlock(std::max(1, n_ / 2));
-    const int max_splits = NL / 2 + 1;
-    CtrlArgs ca;
-    ca.ctrl = ctrl_.get(); ca.frontier = frontier_.get(); ca.journal = journal_.get(); ca.leaves = leaves_.get(); ca.best = best_.get(); ca.meta = dd_->feature_meta.get();
+    ca.cur = ctrl_.get(); ca.nxt = fused_tail ? ctrl_.get() + 1 : ctrl_.get(); ca.frontier = frontier_.get(); ca.journal = journal_.get(); ca.leaves = leaves_.get(); ca.best = best_.get(); ca.meta = dd_->feature_meta.get();
     ca.splits = reinterpret_cast<PartSplit*>(db); ca.child_init = reinterpret_cast<ChildInit*>(db + sizeof(PartSplit) * NL);
     ca.children = reinterpret_cast<FindChild*>(db + (sizeof(PartSplit) + sizeof(ChildInit)) * NL);
     ca.leafwise_budget = leafwise_ ? cfg_.num_leaves - 1 : 0; ca.eval_key = leafwise_ ? eval_key_.get() : nullptr;
     ca.max_leaves = NL; ca.rows_per_block = rpb; ca.bin_owner = feature_parallel_ ? bin_owner_.get() : nullptr;
+  }
+  construct_and_find();   // root level (with the fused tail its last block already decides level 1)
+  if (use_ctrl_) {
+    // ---- device-controlled growth: levels are enqueued ahead; the host reads one small record per batch ----
+    FB_CUDA(cudaMemcpyAsync(h_root_.get(), leaves_.get(), sizeof(LeafInfo), cudaMemcpyDeviceToHost, stream_));   // the root record, before any split rewrites leaf 0
     PartArgs pa = PartArgs();
     pa.rows = dd_->rows.get(); pa.row_stride = dd_->row_stride; pa.idx[0] = idx_[0].get(); pa.idx[1] = idx_[1].get();
     pa.cols = dd_->cols.size() ? dd_->cols.get() : nullptr; pa.col_stride = n_;
     pa.splits = ca.splits; pa.num_splits = max_splits; pa.total_chunks = n_ / kPartChunk + max_splits; pa.bits = bits_.get(); pa.chunk_left = chunk_left_.get();
     pa.split_left_total = split_left_total_.get(); pa.leaves = leaves_.get(); pa.child_init = ca.child_init; pa.hist_tasks = hist_tasks_.get(); pa.rows_per_block = rpb;
-    pa.world = dp ? world_ : 1; pa.ctrl = ctrl_.get();
+    pa.world = dp ? world_ : 1;
+    pa.fused_scan = (plan_.fused_scan && !feature_parallel_) ? 1 : 0; pa.split_done = split_done_.get();
     if (dp) for (int r = 0; r < world_; ++r) pa.peer_counts[r] = fabric_->Ptr<int>(r, off_counts_) + static_cast<size_t>(rank_) * NL;
     if (feature_parallel_) SetupBitmapBroadcast(&pa);
-    ha.identity_root = 0; ha.rows_per_block = rpb; ha.ctrl = ctrl_.get(); ha.num_tasks = max_splits; ha.total_blocks = n_ / rpb + max_splits;
-    fa.ctrl = ctrl_.get(); fa.children = ca.children; fa.num_children = 2 * max_splits;
+    ha.identity_root = 0; ha.rows_per_block = rpb; ha.num_tasks = max_splits; ha.total_blocks = n_ / rpb + max_splits;
+    fa.children = ca.children; fa.num_children = 2 * max_splits;
+    int level = 0;   // index of the last level enqueued (0 = root)
     auto enqueue_level = [&]() {
-      LaunchLevelController(ca, stream_);
-      if (num_sets_ > 0) LaunchPathBits(ctrl_.get(), journal_.get(), dd_->feature_meta.get(), path_bits_.get(), path_words_, max_splits, stream_);
+      ++level;
+      // this level's record: fused tail -> the ring half the previous level's tail wrote; otherwise the one record, updated in place
+      LevelCtrl* lc = fused_tail ? ctrl_.get() + (level & 1) : ctrl_.get();
+      if (!fused_tail) LaunchLevelController(ca, stream_);
+      else { ca.cur = lc; ca.nxt = ctrl_.get() + ((level + 1) & 1); }
+      pa.ctrl = lc; ha.ctrl = lc; fa.ctrl = lc;
+      if (num_sets_ > 0) LaunchPathBits(lc, journal_.get(), dd_->feature_meta.get(), path_bits_.get(), path_words_, max_splits, stream_);
       if (feature_parallel_) { pa.bc_sig.epoch = fabric_->NextEpoch(); pa.bc_wait.epoch = pa.bc_sig.epoch; }
       clock_.Begin(st_part_, stream_);
       LaunchPartitionFlags(pa, stream_); LaunchPartitionScanSetup(pa, stream_); LaunchPartitionScatter(pa, stream_);
       clock_.End(stream_);
       construct_and_find();
     };
+    // the record that describes the tree after the last enqueued level: fused tail -> written by that level's tail into the other ring half
+    auto final_ctrl = [&]() -> LevelCtrl* { return fused_tail ? ctrl_.get() + ((level + 1) & 1) : ctrl_.get(); };
     int enqueued = 0; bool records_ready = false;
     LevelCtrl hc;
     for (;;) {
@@ -366,21 +374,23 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
         // the usual case: this batch completes the tree. The score update and the tree's records ride behind it, so
         // the host waits once per tree and the GPU already has the update while the host rebuilds the tree.
         clock_.Begin(st_score_, stream_);
-        LaunchAddLeafOutputsFromRecords(leaves_.get(), ctrl_.get(), cur_shrinkage_, NL, idx_[0].get(), idx_[1].get(), cur_score_, stream_);
+        LaunchAddLeafOutputsFromRecords(leaves_.get(), final_ctrl(), cur_shrinkage_, NL, idx_[0].get(), idx_[1].get(), cur_score_, stream_, fused_tail);
         clock_.End(stream_);
       }
       clock_.Begin(st_sync_, stream_);
-      FB_CUDA(cudaMemcpyAsync(h_ctrl_.get(), ctrl_.get(), sizeof(LevelCtrl), cudaMemcpyDeviceToHost, stream_));
+      FB_CUDA(cudaMemcpyAsync(h_ctrl_.get(), final_ctrl(), sizeof(LevelCtrl), cudaMemcpyDeviceToHost, stream_));
       if (first) { journal_.Download(h_journal_.get(), NL, stream_); leaves_.Download(h_leaves_.get(), NL, stream_); hist_status_.Download(h_hist_status_.get(), 1, stream_); }
       clock_.End(stream_);
       if (world_ > 1) { const int st = fabric_->CheckStatus(stream_); if (st != 0) Log::Fatal("A cross-rank wait gave up (device status %d): a peer rank did not reach the same step", st); }
       else FB_CUDA(cudaStreamSynchronize(stream_));
       hc = *h_ctrl_.get();
       if (first && *h_hist_status_.get() != 0) Log::Fatal("A bounded wait inside the construct kernel gave up (device status %u)", *h_hist_status_.get());
-      const bool complete = hc.done || hc.num_leaves >= NL || hc.frontier_count == 0;
+      // with the fused tail the record is one decision ahead of the partition: splits it counts may still be pending
+      const bool complete = (hc.done || hc.num_leaves >= NL || hc.frontier_count == 0) && (!fused_tail || hc.num_splits == 0);
       if (first && complete) records_ready = true;   // the journal and leaf records fetched with this batch are final
       if (first && complete && fast_score_ok_ && hc.num_leaves > 1) score_done_ = true;   // the device-side update applied itself
-      if (complete || enqueued > 4 * NL) break;
+      if (complete) break;
+      if (enqueued > 4 * NL) Log::Fatal("The device level loop did not finish the tree within %d levels", enqueued);
     }
     levels_hint_ = std::max(1, hc.pad0);
     if (!records_ready) {

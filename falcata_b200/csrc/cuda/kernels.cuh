@@ -131,12 +131,23 @@ struct FindArgs {
   FabricSignal sig;                               // "rank-local best splits published" signal
   FabricWait wait_best;
   const LevelCtrl* ctrl;                          // non-null: num_children comes from the device controller
+  // ---- fused tail (fused_tail != 0): the last block of every child reduces that child's candidates to its best split
+  // (multi-rank: and stores it into every peer); the last of those blocks waits for the peers' records, takes the
+  // argmax over ranks for every child and then runs the level controller. A level then costs one launch from finished
+  // histograms to the next level's descriptors.
+  int fused_tail;
+  unsigned int* child_done;                       // [children] blocks finished per child (zero between launches)
+  unsigned int* level_done;                       // [1] children reduced (zero between launches)
+  int run_controller;                             // 0: the tail stops after the per-leaf records (host-driven growth)
 };
+struct CtrlArgs;
 
 // Device-side level controller: applies the gain-ranked leaf budget to the frontier's best splits
 // and writes the next level's descriptors, the journal and the new frontier.
 struct CtrlArgs {
-  LevelCtrl* ctrl; int* frontier; SplitJournal* journal;
+  const LevelCtrl* cur; LevelCtrl* nxt;   // level record read / written (the same object for the stand-alone launch; the two
+                                          // halves of a ring when the controller runs as the search kernel's tail)
+  int* frontier; SplitJournal* journal;
   LeafInfo* leaves; const SplitRecord* best; const FeatureMeta* meta;
   PartSplit* splits; ChildInit* child_init; FindChild* children;
   int max_leaves; int rows_per_block;
@@ -150,6 +161,14 @@ struct CtrlArgs {
   double* eval_key;                 // [evaluated nodes][4] order keys
 };
 void LaunchLevelController(const CtrlArgs& a, cudaStream_t s);
+// Per-tree start state written on the device: root leaf record (from the gradient sums), both halves of the
+// level-record ring, the frontier, the root's construct task and search descriptor.
+struct TreeInitArgs {
+  LeafInfo* leaves; const long long* sums_i; const double* sums_d; const float* scales; int quant; int n_local; long long n_global; SplitParams sp;
+  LevelCtrl* ctrl; int* frontier;   // null without the device controller
+  HistTask* root_task; FindChild* root_child; int root_blocks;
+};
+void LaunchInitTree(const TreeInitArgs& a, cudaStream_t s);
 
 // Per-node feature masks (feature_fraction_bynode, interaction constraints): mask[child][inner feature] = 1 when
 // the child's split search may use the feature.
@@ -194,8 +213,7 @@ struct VoteArgs {
 void LaunchVoteLocalSums(const VoteArgs& a, cudaStream_t s);
 void LaunchVoteTopK(const VoteArgs& a, cudaStream_t s);
 void LaunchVoteTallyPush(const VoteArgs& a, cudaStream_t s);
-void LaunchInitLevelCtrl(LevelCtrl* ctrl, int* frontier, cudaStream_t s);
-void LaunchFindSplits(const FindArgs& a, cudaStream_t s);      // per (child, feature) search + in-place larger-child subtraction
+void LaunchFindSplits(const FindArgs& a, cudaStream_t s, const CtrlArgs* tail_ctrl = nullptr);   // per (child, feature) search + in-place larger-child subtraction; fused tail when a.fused_tail
 void LaunchReduceBest(const FindArgs& a, cudaStream_t s);      // per child argmax over features -> SplitRecord (world > 1: stored into every peer)
 void LaunchGatherBest(const FindArgs& a, cudaStream_t s);      // world > 1: argmax over the ranks' records
 
@@ -224,6 +242,8 @@ struct PartArgs {
   int rows_per_block;
   int world; int* peer_counts[kMaxRanks];   // world > 1: address of counts[this rank][0] inside every rank's heap
   const LevelCtrl* ctrl;     // non-null: num_splits / total_chunks come from the device controller
+  int fused_scan;            // 1: the last chunk block of each split runs the scan + set-up step (every split has >= 1 chunk)
+  unsigned int* split_done;  // [splits] chunk blocks finished per split (zero between launches)
   // ---- feature-parallel bitmap broadcast (bc_world > 1) ----
   // Every rank holds all rows but only the histograms of the features it owns. The rank that owns a
   // split's feature computes the go-left bit words of the leaf's rows and stores them, with the chunk
@@ -273,8 +293,9 @@ void LaunchGoss(const GossArgs& a, cudaStream_t s);
 // ----------------------------------------------------------------- score ----
 void LaunchCollapseLeafWindows(const LeafInfo* leaves, int num_leaves, int* idx0, const int* idx1, cudaStream_t s);
 void LaunchAddLeafOutputs(const LeafInfo* leaves, const double* leaf_value, int num_leaves, const int* idx0, const int* idx1, float* score, cudaStream_t s);
+// decided_ahead: `ctrl` comes from the fused search tail, which decides the NEXT level's splits: complete only with none pending
 void LaunchAddLeafOutputsFromRecords(const LeafInfo* leaves, const LevelCtrl* ctrl, double shrinkage, int max_leaves, const int* idx0, const int* idx1, float* score,
-                                     cudaStream_t s);
+                                     cudaStream_t s, bool decided_ahead = false);
 void LaunchAddConstant(float* score, int n, float v, cudaStream_t s);
 // per-leaf (sum g, sum h) of float gradients over the leaf windows: partial[2 * (leaf * slices + slice) + {0,1}]
 int LeafGradSumSlices();

@@ -1,7 +1,8 @@
 // K5: level-batched stable row partition. Three launches per level for ALL splitting leaves:
 //   flags   : per 2048-row chunk, go-left ballot words + left count
 //   scan    : per split, exclusive scan of its chunks' counts; child windows, leaf records and the
-//             construct task of the smaller child are written here (no host round trip)
+//             construct task of the smaller child are written here (no host round trip). With
+//             `fused_scan` this step runs inside the flags launch, in the last chunk block of each split.
 //   scatter : popc-ranked stable scatter into the other index buffer (ping-pong, no copy back)
 // Parity: src/treelearner/cuda/cuda_data_partition.cu:L1380-1433 (ballot bit vectors, flat grid),
 // L1479 (per-split scan), L1562-1617 (stable scatter), L1681-1840 (tree-structure bookkeeping),
@@ -33,7 +34,72 @@ __device__ inline bool GoLeft(const PartSplit& sp, int gb) {
   return fb <= sp.threshold;
 }
 
-__global__ void __launch_bounds__(kPartThreads) PartitionFlagsKernel(PartArgs a) {
+// Per split: exclusive scan of its chunks' left counts, then the children's windows, leaf records and the smaller
+// child's construct task (no host round trip). Call with all threads of one block.
+__device__ inline void ScanSetupBody(const PartArgs& a, int si, int* s_scan, int* s_carry_p) {
+  int& s_carry = *s_carry_p;
+  const PartSplit sp = a.splits[si];
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  for (int c0 = 0; c0 < sp.num_chunks; c0 += kPartThreads) {
+    const int c = c0 + threadIdx.x;
+    const int v = c < sp.num_chunks ? __ldcg(a.chunk_left + sp.chunk_begin + c) : 0;   // written by other blocks of this launch when fused
+    s_scan[threadIdx.x] = v;
+    __syncthreads();
+    for (int o = 1; o < kPartThreads; o <<= 1) {
+      const int t = threadIdx.x >= o ? s_scan[threadIdx.x - o] : 0;
+      __syncthreads();
+      s_scan[threadIdx.x] += t;
+      __syncthreads();
+    }
+    if (c < sp.num_chunks) a.chunk_left[sp.chunk_begin + c] = s_carry + s_scan[threadIdx.x] - v;   // exclusive offset
+    __syncthreads();
+    if (threadIdx.x == kPartThreads - 1) s_carry += s_scan[threadIdx.x];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const int nl = s_carry, nr = sp.count - nl;
+    a.split_left_total[si] = nl;
+    // multi-rank: every rank learns every rank's left count (summed by the split search, which runs
+    // after the construct-done flags; this store is ordered before them by the stream)
+    if (a.world > 1) { for (int r = 0; r < a.world; ++r) a.peer_counts[r][si] = nl; __threadfence_system(); }
+    const ChildInit ci = a.child_init[si];
+    const LeafInfo parent = a.leaves[sp.leaf];
+    LeafInfo L = parent, R = parent;
+    L.count = nl; R.begin = parent.begin + nl; R.count = nr;
+    L.buffer = R.buffer = sp.buffer ^ 1;
+    L.depth = R.depth = parent.depth + 1;
+    L.hist_slot = ci.left_slot; R.hist_slot = ci.right_slot;
+    L.sum_g = ci.left_g; L.sum_h = ci.left_h; L.sum_gi = ci.left_gi; L.sum_hi = ci.left_hi; L.output = ci.left_out;
+    R.sum_g = ci.right_g; R.sum_h = ci.right_h; R.sum_gi = ci.right_gi; R.sum_hi = ci.right_hi; R.output = ci.right_out;
+    for (int k = 0; k < 4; ++k) L.pkey[k] = R.pkey[k] = ci.pkey[k];
+    if (ci.monotone != 0) {   // "basic" monotone method: the children's ranges meet at the mid point of their outputs
+      const double mid = (ci.left_out + ci.right_out) / 2.0;
+      if (ci.monotone > 0) { L.max_c = fmin(L.max_c, mid); R.min_c = fmax(R.min_c, mid); }
+      else { L.min_c = fmax(L.min_c, mid); R.max_c = fmin(R.max_c, mid); }
+    }
+    L.num_data_global = nl; R.num_data_global = nr;   // single rank: exact; multi-rank: summed over ranks by the exchange that follows
+    a.leaves[sp.leaf] = L; a.leaves[sp.right_leaf] = R;
+    HistTask t;
+    const LeafInfo& S = ci.smaller_is_left ? L : R;
+    t.slot = S.hist_slot; t.begin = S.begin; t.count = S.count; t.buffer = S.buffer; t.block_begin = ci.hist_block_begin; t.num_blocks = ci.hist_num_blocks; t.pad0 = t.pad1 = 0;
+    a.hist_tasks[si] = t;
+  }
+}
+
+__global__ void __launch_bounds__(kPartThreads) PartitionScanSetupKernel(PartArgs a) {
+  const int si = blockIdx.x;
+  if (si >= (a.ctrl != nullptr ? a.ctrl->num_splits : a.num_splits)) return;
+  // feature-parallel: the bitmaps of this level come from the owners of the split features
+  if (a.bc_world > 1) FabricWaitAll(a.bc_wait);
+  __shared__ int s_scan[kPartThreads];
+  __shared__ int s_carry;
+  ScanSetupBody(a, si, s_scan, &s_carry);
+}
+
+// (The register cap keeps eight blocks per SM for the latency-bound chunk pass; the rarely taken scan step of the
+// last block per split may spill.)
+__global__ void __launch_bounds__(kPartThreads, 8) PartitionFlagsKernel(PartArgs a) {
   const int chunk = blockIdx.x;
   const int nsplits = a.ctrl != nullptr ? a.ctrl->num_splits : a.num_splits;
   const bool bc = a.bc_world > 1;
@@ -78,63 +144,24 @@ __global__ void __launch_bounds__(kPartThreads) PartitionFlagsKernel(PartArgs a)
     if (bc) { for (int r = 0; r < a.bc_world; ++r) a.peer_chunk_left[r][chunk] = t; } else a.chunk_left[chunk] = t;
   }
   if (bc) FabricSignalDone(a.bc_sig, gridDim.x, true);
-}
-
-__global__ void __launch_bounds__(kPartThreads) PartitionScanSetupKernel(PartArgs a) {
-  const int si = blockIdx.x;
-  if (si >= (a.ctrl != nullptr ? a.ctrl->num_splits : a.num_splits)) return;
-  // feature-parallel: the bitmaps of this level come from the owners of the split features
-  if (a.bc_world > 1) FabricWaitAll(a.bc_wait);
-  const PartSplit sp = a.splits[si];
+  if (!a.fused_scan) return;
+  // fused scan + set-up: the last chunk block of a split finds all of the split's counts written and closes the split
+  __shared__ int s_last;
   __shared__ int s_scan[kPartThreads];
   __shared__ int s_carry;
-  if (threadIdx.x == 0) s_carry = 0;
   __syncthreads();
-  for (int c0 = 0; c0 < sp.num_chunks; c0 += kPartThreads) {
-    const int c = c0 + threadIdx.x;
-    const int v = c < sp.num_chunks ? a.chunk_left[sp.chunk_begin + c] : 0;
-    s_scan[threadIdx.x] = v;
-    __syncthreads();
-    for (int o = 1; o < kPartThreads; o <<= 1) {
-      const int t = threadIdx.x >= o ? s_scan[threadIdx.x - o] : 0;
-      __syncthreads();
-      s_scan[threadIdx.x] += t;
-      __syncthreads();
-    }
-    if (c < sp.num_chunks) a.chunk_left[sp.chunk_begin + c] = s_carry + s_scan[threadIdx.x] - v;   // exclusive offset
-    __syncthreads();
-    if (threadIdx.x == kPartThreads - 1) s_carry += s_scan[threadIdx.x];
-    __syncthreads();
-  }
   if (threadIdx.x == 0) {
-    const int nl = s_carry, nr = sp.count - nl;
-    a.split_left_total[si] = nl;
-    // multi-rank: every rank learns every rank's left count (summed by the split search, which runs
-    // after the construct-done flags; this store is ordered before them by the stream)
-    if (a.world > 1) { for (int r = 0; r < a.world; ++r) a.peer_counts[r][si] = nl; __threadfence_system(); }
-    const ChildInit ci = a.child_init[si];
-    const LeafInfo parent = a.leaves[sp.leaf];
-    LeafInfo L = parent, R = parent;
-    L.count = nl; R.begin = parent.begin + nl; R.count = nr;
-    L.buffer = R.buffer = sp.buffer ^ 1;
-    L.depth = R.depth = parent.depth + 1;
-    L.hist_slot = ci.left_slot; R.hist_slot = ci.right_slot;
-    L.sum_g = ci.left_g; L.sum_h = ci.left_h; L.sum_gi = ci.left_gi; L.sum_hi = ci.left_hi; L.output = ci.left_out;
-    R.sum_g = ci.right_g; R.sum_h = ci.right_h; R.sum_gi = ci.right_gi; R.sum_hi = ci.right_hi; R.output = ci.right_out;
-    for (int k = 0; k < 4; ++k) L.pkey[k] = R.pkey[k] = ci.pkey[k];
-    if (ci.monotone != 0) {   // "basic" monotone method: the children's ranges meet at the mid point of their outputs
-      const double mid = (ci.left_out + ci.right_out) / 2.0;
-      if (ci.monotone > 0) { L.max_c = fmin(L.max_c, mid); R.min_c = fmax(R.min_c, mid); }
-      else { L.min_c = fmax(L.min_c, mid); R.max_c = fmin(R.max_c, mid); }
-    }
-    L.num_data_global = nl; R.num_data_global = nr;   // single rank: exact; multi-rank: summed over ranks by the exchange that follows
-    a.leaves[sp.leaf] = L; a.leaves[sp.right_leaf] = R;
-    HistTask t;
-    const LeafInfo& S = ci.smaller_is_left ? L : R;
-    t.slot = S.hist_slot; t.begin = S.begin; t.count = S.count; t.buffer = S.buffer; t.block_begin = ci.hist_block_begin; t.num_blocks = ci.hist_num_blocks; t.pad0 = t.pad1 = 0;
-    a.hist_tasks[si] = t;
+    __threadfence();
+    const unsigned int prev = atomicAdd(a.split_done + si, 1u);
+    s_last = (prev + 1 == static_cast<unsigned int>(sp.num_chunks)) ? 1 : 0;
+    if (s_last) a.split_done[si] = 0;
   }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  ScanSetupBody(a, si, s_scan, &s_carry);
 }
+
 
 __global__ void __launch_bounds__(kPartThreads) PartitionScatterKernel(PartArgs a) {
   const int chunk = blockIdx.x;
@@ -189,7 +216,7 @@ void LaunchPartitionFlags(const PartArgs& a, cudaStream_t s) {
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 void LaunchPartitionScanSetup(const PartArgs& a, cudaStream_t s) {
-  if (a.num_splits <= 0) return;
+  if (a.num_splits <= 0 || a.fused_scan) return;   // fused: the flags kernel's last block per split did it
   PartitionScanSetupKernel<<<a.num_splits, kPartThreads, 0, s>>>(a);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }

@@ -37,9 +37,11 @@ __global__ void CollapseLeafWindowsKernel(const LeafInfo* __restrict__ leaves, i
 // the controller reports the tree complete and split at least once; otherwise it does nothing and the host-side
 // update runs after the read-back.
 __global__ void AddLeafOutputsFromRecordsKernel(const LeafInfo* __restrict__ leaves, const LevelCtrl* __restrict__ ctrl, double shrinkage, int max_leaves,
-                                                const int* __restrict__ idx0, const int* __restrict__ idx1, float* __restrict__ score) {
+                                                const int* __restrict__ idx0, const int* __restrict__ idx1, float* __restrict__ score, int decided_ahead) {
   const LevelCtrl c = *ctrl;
-  const bool complete = c.done || c.num_leaves >= max_leaves || c.frontier_count == 0;
+  // decided_ahead: the record was written by the tail of the last level's search and may already count splits that no
+  // partition has applied yet (their leaf records do not exist): the tree is complete only when none are pending
+  const bool complete = (c.done || c.num_leaves >= max_leaves || c.frontier_count == 0) && (!decided_ahead || c.num_splits == 0);
   if (!complete || c.num_leaves <= 1 || static_cast<int>(blockIdx.x) >= c.num_leaves) return;
   const LeafInfo L = leaves[blockIdx.x];
   const float v = static_cast<float>(L.output * shrinkage);
@@ -208,9 +210,9 @@ void LaunchAddLeafOutputs(const LeafInfo* leaves, const double* leaf_value, int 
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 void LaunchAddLeafOutputsFromRecords(const LeafInfo* leaves, const LevelCtrl* ctrl, double shrinkage, int max_leaves, const int* idx0, const int* idx1, float* score,
-                                     cudaStream_t s) {
+                                     cudaStream_t s, bool decided_ahead) {
   if (max_leaves <= 0) return;
-  AddLeafOutputsFromRecordsKernel<<<dim3(max_leaves, 64), 256, 0, s>>>(leaves, ctrl, shrinkage, max_leaves, idx0, idx1, score);
+  AddLeafOutputsFromRecordsKernel<<<dim3(max_leaves, 64), 256, 0, s>>>(leaves, ctrl, shrinkage, max_leaves, idx0, idx1, score, decided_ahead ? 1 : 0);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 void LaunchCollapseLeafWindows(const LeafInfo* leaves, int num_leaves, int* idx0, const int* idx1, cudaStream_t s) {

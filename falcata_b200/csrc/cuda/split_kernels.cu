@@ -5,7 +5,7 @@
 // tie order), cuda_histogram_constructor.cu:L2641-3107 (subtract / fix kernels that are folded in).
 // The candidate math is fb/split_math.h, shared with the host learner: with integer histograms the
 // two produce bit-identical gains.
-#include "kernels.cuh"
+#include "controller.cuh"
 
 namespace fb {
 
@@ -169,14 +169,10 @@ __device__ void ScanCategoricalWarp(const FindArgs& a, const BinSrc& src, char* 
   a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + fi] = c;
 }
 
+// The search of one (child, feature) by one warp; warps of a block work on different features of the same child and
+// leave independently (only warp-level synchronisation inside).
 template <bool QUANT>
-__global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
-  if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) return;
-  // multi-rank: the owned slices are complete once every rank's construct has raised its flag. The wait also
-  // orders the peers' child counts (stored by their partition, before their construct) ahead of the per-leaf
-  // argmax that follows, so it is taken even when the search itself is skipped.
-  if (a.wait.world > 1) FabricWaitAll(a.wait);
-  if (a.ctrl != nullptr && a.ctrl->skip_search) return;   // the tree is complete: nothing was constructed for these children
+__device__ void FindSplitsWarp(const FindArgs& a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int fi = blockIdx.y * kWarpsPerBlock + warp;
   if (fi >= a.num_features + a.num_sub_features) return;
@@ -339,28 +335,32 @@ __global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a) {
   }
 }
 
-__global__ void ReduceBestKernel(FindArgs a) {
+// Per-leaf argmax over the searched features of one child -> SplitRecord (the CPU's tie order: higher gain, then
+// lower real feature index, then lower threshold). Multi-rank: the record is this rank's best over the features it
+// owns; it is stored into every rank's slot array. Call with all T threads of a block.
+struct ReduceShared { SplitRecord rec; double gain[kFindThreads]; int feat[kFindThreads], thr[kFindThreads], idx[kFindThreads]; };
+
+template <int T>
+__device__ inline void ReduceChildBody(const FindArgs& a, int child, ReduceShared& R) {
   const bool gather = a.wait_best.world > 1;   // data-parallel and feature-parallel both all-gather the rank-local best
-  if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) { if (gather) FabricSignalDone(a.sig, gridDim.x); return; }
-  const FindChild ch = a.children[blockIdx.x];
+  const FindChild ch = a.children[child];
   LeafInfo leaf = a.leaves[ch.leaf];
   leaf.num_data_global = ChildGlobalCount(a, ch, leaf.num_data_global);
-  __shared__ SplitRecord s_rec;
-  __shared__ double s_gain[128]; __shared__ int s_feat[128], s_thr[128], s_idx[128];
   double bg = -1.0 / 0.0; int bf = -1, bt = 0, bi = -1;
   // a level that ended the tree was not searched: its candidate slots hold nothing meaningful, the record stays
   // empty and only the children's global row counts are settled here
   const bool searched = !(a.ctrl != nullptr && a.ctrl->skip_search);
-  for (int k = threadIdx.x; searched && k < a.num_features; k += blockDim.x) {
-    const CandLite c = a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + k];
-    const int rf = c.feature >= 0 ? a.meta[c.feature].real_index : -1;
-    if (SplitBetter(c.gain, rf, c.threshold, bg, bf, bt)) { bg = c.gain; bf = rf; bt = c.threshold; bi = k; }
+  for (int k = threadIdx.x; searched && k < a.num_features; k += T) {
+    const CandLite* cp = a.cand + static_cast<size_t>(child) * a.num_features + k;
+    const double gain = LoadWords(&cp->gain); const int feature = LoadWords(&cp->feature), threshold = LoadWords(&cp->threshold);
+    const int rf = feature >= 0 ? a.meta[feature].real_index : -1;
+    if (SplitBetter(gain, rf, threshold, bg, bf, bt)) { bg = gain; bf = rf; bt = threshold; bi = k; }
   }
-  s_gain[threadIdx.x] = bg; s_feat[threadIdx.x] = bf; s_thr[threadIdx.x] = bt; s_idx[threadIdx.x] = bi;
+  R.gain[threadIdx.x] = bg; R.feat[threadIdx.x] = bf; R.thr[threadIdx.x] = bt; R.idx[threadIdx.x] = bi;
   __syncthreads();
-  for (int o = blockDim.x / 2; o > 0; o >>= 1) {
-    if (threadIdx.x < o && SplitBetter(s_gain[threadIdx.x + o], s_feat[threadIdx.x + o], s_thr[threadIdx.x + o], s_gain[threadIdx.x], s_feat[threadIdx.x], s_thr[threadIdx.x])) {
-      s_gain[threadIdx.x] = s_gain[threadIdx.x + o]; s_feat[threadIdx.x] = s_feat[threadIdx.x + o]; s_thr[threadIdx.x] = s_thr[threadIdx.x + o]; s_idx[threadIdx.x] = s_idx[threadIdx.x + o];
+  for (int o = T / 2; o > 0; o >>= 1) {
+    if (threadIdx.x < o && SplitBetter(R.gain[threadIdx.x + o], R.feat[threadIdx.x + o], R.thr[threadIdx.x + o], R.gain[threadIdx.x], R.feat[threadIdx.x], R.thr[threadIdx.x])) {
+      R.gain[threadIdx.x] = R.gain[threadIdx.x + o]; R.feat[threadIdx.x] = R.feat[threadIdx.x + o]; R.thr[threadIdx.x] = R.thr[threadIdx.x + o]; R.idx[threadIdx.x] = R.idx[threadIdx.x + o];
     }
     __syncthreads();
   }
@@ -368,8 +368,8 @@ __global__ void ReduceBestKernel(FindArgs a) {
     SplitRecord r; InitSplitRecord(&r);
     const bool depth_ok = a.params.max_depth <= 0 || leaf.depth < a.params.max_depth;
     const bool size_ok = leaf.num_data_global >= 2 * a.params.min_data_in_leaf;
-    if (s_idx[0] >= 0 && depth_ok && size_ok) {
-      const CandLite c = a.cand[static_cast<size_t>(blockIdx.x) * a.num_features + s_idx[0]];
+    if (R.idx[0] >= 0 && depth_ok && size_ok) {
+      const CandLite c = LoadWords(a.cand + static_cast<size_t>(child) * a.num_features + R.idx[0]);
       r.gain = c.gain; r.feature = c.feature; r.threshold = c.threshold; r.default_left = c.default_left;
       if (a.params.cegb_split > 0.0) r.gain -= a.params.cegb_split * static_cast<double>(leaf.num_data_global);
       r.left_g = c.left_g; r.left_h = c.left_h; r.right_g = FB_SUB(leaf.sum_g, c.left_g); r.right_h = FB_SUB(leaf.sum_h, c.left_h);
@@ -381,42 +381,103 @@ __global__ void ReduceBestKernel(FindArgs a) {
       r.right_out = LeafOutput(r.right_g, FB_ADD(r.right_h, kEpsilon), p, r.right_cnt, leaf.output);
       if (p.use_mc != 0) { r.left_out = ClampOutput(r.left_out, leaf.min_c, leaf.max_c); r.right_out = ClampOutput(r.right_out, leaf.min_c, leaf.max_c); }
     }
-    if (gather) { s_rec = r; a.leaves_rw[ch.leaf].num_data_global = leaf.num_data_global; }
+    if (gather) { R.rec = r; a.leaves_rw[ch.leaf].num_data_global = leaf.num_data_global; }
     else a.best[ch.leaf] = r;
   }
   if (gather) {
-    // all-gather of the rank-local best split: plain stores into every rank's slot array, then the
-    // last block of the grid raises this rank's flag on every peer
+    // all-gather of the rank-local best split: plain stores into every rank's slot array
     __syncthreads();
-    const unsigned int* src = reinterpret_cast<const unsigned int*>(&s_rec);
+    const unsigned int* src = reinterpret_cast<const unsigned int*>(&R.rec);
     constexpr int kWords = sizeof(SplitRecord) / 4;
     for (int p = 0; p < a.wait_best.world; ++p) {
       unsigned int* dst = reinterpret_cast<unsigned int*>(a.peer_best[p] + ch.leaf);
-      for (int w = threadIdx.x; w < kWords; w += blockDim.x) dst[w] = src[w];
+      for (int w = threadIdx.x; w < kWords; w += T) dst[w] = src[w];
     }
-    FabricSignalDone(a.sig, gridDim.x, true);
   }
 }
 
-// Multi-rank: the best split of a leaf is the best of the ranks' records (each rank searched only
-// the features it owns). Every rank runs this on the same records, so all ranks decide alike.
-__global__ void GatherBestKernel(FindArgs a) {
-  if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) return;
-  FabricWaitAll(a.wait_best);
-  if (threadIdx.x != 0) return;
-  const FindChild ch = a.children[blockIdx.x];
+// Multi-rank: the best split of a leaf is the best of the ranks' records (each rank searched only the features it
+// owns). Every rank runs this on the same records, so all ranks decide alike. One thread per child.
+__device__ inline void GatherChild(const FindArgs& a, int child) {
+  const FindChild ch = a.children[child];
   SplitRecord best; InitSplitRecord(&best);
   int best_real = -1;
-  constexpr int kWords = sizeof(SplitRecord) / 4;
   for (int r = 0; r < a.wait_best.world; ++r) {
-    SplitRecord rec;
-    const unsigned int* src = reinterpret_cast<const unsigned int*>(a.gathered + static_cast<size_t>(r) * a.gathered_stride + ch.leaf);
-    unsigned int* dst = reinterpret_cast<unsigned int*>(&rec);
-    for (int w = 0; w < kWords; ++w) dst[w] = __ldcg(src + w);
+    const SplitRecord rec = LoadWords(a.gathered + static_cast<size_t>(r) * a.gathered_stride + ch.leaf);
     const int real = rec.feature >= 0 ? a.meta[rec.feature].real_index : -1;
     if (SplitBetter(rec.gain, real, rec.threshold, best.gain, best_real, best.threshold)) { best = rec; best_real = real; }
   }
   a.best[ch.leaf] = best;
+}
+
+template <bool QUANT>
+__global__ void __launch_bounds__(kFindThreads) FindSplitsKernel(FindArgs a, CtrlArgs ca) {
+  __shared__ int s_last;
+  __shared__ union TailShared { ReduceShared r; CtrlShared c; } S;
+  const int nchildren = a.ctrl != nullptr ? a.ctrl->num_children : a.num_children;
+  if (nchildren <= 0) {
+    // A level past the end of the tree (levels are enqueued ahead): nothing to search, but the NEXT level's record must
+    // still be written, or that level would run on the stale record its ring half holds from two levels ago.
+    if (a.fused_tail && a.run_controller && blockIdx.x == 0 && blockIdx.y == 0) ControllerBody<kFindThreads>(ca, S.c);
+    return;
+  }
+  if (static_cast<int>(blockIdx.x) >= nchildren) return;
+  // multi-rank: the owned slices are complete once every rank's construct has raised its flag. The wait also
+  // orders the peers' child counts (stored by their partition, before their construct) ahead of the per-leaf
+  // argmax that follows, so it is taken even when the search itself is skipped.
+  if (a.wait.world > 1) FabricWaitAll(a.wait);
+  // skip_search: the tree is complete, nothing was constructed for these children
+  if (!(a.ctrl != nullptr && a.ctrl->skip_search)) FindSplitsWarp<QUANT>(a);
+  if (!a.fused_tail) return;
+
+  // ---- fused tail, step 1: the last block of this child reduces the child's candidates ----
+  __syncthreads();   // every warp's candidate is written
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int prev = atomicAdd(a.child_done + blockIdx.x, 1u);
+    s_last = (prev + 1 == gridDim.y) ? 1 : 0;
+    if (s_last) a.child_done[blockIdx.x] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  ReduceChildBody<kFindThreads>(a, blockIdx.x, S.r);
+  // ---- step 2: the last reducer of the level takes over ----
+  const bool gather = a.wait_best.world > 1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (gather) __threadfence_system(); else __threadfence();   // this block's record (peer stores included) is published before it is counted
+    const unsigned int prev = atomicAdd(a.level_done, 1u);
+    s_last = (prev + 1 == static_cast<unsigned int>(nchildren)) ? 1 : 0;
+    if (s_last) *a.level_done = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (gather) {
+    // every child's record of this rank is on its way: raise "best published" on every peer, wait (bounded) for
+    // theirs, then take the argmax over ranks for every child
+    if (threadIdx.x == 0) { __threadfence_system(); for (int r = 0; r < a.sig.world; ++r) StoreFlagAfterFence(a.sig.peer_flag[r], a.sig.epoch); }
+    FabricWaitAll(a.wait_best);
+    for (int c = threadIdx.x; c < nchildren; c += kFindThreads) GatherChild(a, c);
+  }
+  __threadfence();
+  __syncthreads();
+  if (a.run_controller) ControllerBody<kFindThreads>(ca, S.c);
+}
+
+__global__ void __launch_bounds__(128) ReduceBestKernel(FindArgs a) {
+  const bool gather = a.wait_best.world > 1;
+  if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) { if (gather) FabricSignalDone(a.sig, gridDim.x); return; }
+  __shared__ ReduceShared R;
+  ReduceChildBody<128>(a, blockIdx.x, R);
+  if (gather) FabricSignalDone(a.sig, gridDim.x, true);
+}
+
+__global__ void GatherBestKernel(FindArgs a) {
+  if (static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->num_children : a.num_children)) return;
+  FabricWaitAll(a.wait_best);
+  if (threadIdx.x != 0) return;
+  GatherChild(a, blockIdx.x);
 }
 
 }  // namespace
@@ -427,20 +488,22 @@ void LaunchGatherBest(const FindArgs& a, cudaStream_t s) {
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 
-void LaunchFindSplits(const FindArgs& a, cudaStream_t s) {
+void LaunchFindSplits(const FindArgs& a, cudaStream_t s, const CtrlArgs* tail_ctrl) {
   if (a.num_children <= 0) return;
   const int nf = a.num_features + a.num_sub_features;
-  if (nf <= 0) return;
-  dim3 grid(a.num_children, (nf + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  if (nf <= 0 && !a.fused_tail) return;
+  if (a.fused_tail && a.run_controller && (tail_ctrl == nullptr || tail_ctrl->max_leaves > kCtrlMaxLeaves)) Log::Fatal("The fused level controller handles up to %d leaves", kCtrlMaxLeaves);
+  dim3 grid(a.num_children, std::max(1, (nf + kWarpsPerBlock - 1) / kWarpsPerBlock));
   // categorical features stage their bins in shared memory, one scratch per warp
   const size_t sm = a.has_categorical ? sizeof(CatScratch) * kWarpsPerBlock : 0;
   static bool attr = false;
-  if (sm > 48 * 1024 && !attr) {
+  if (sm > 16 * 1024 && !attr) {   // together with the tail's static shared memory the default limit is passed early
     FB_CUDA(cudaFuncSetAttribute(FindSplitsKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
     FB_CUDA(cudaFuncSetAttribute(FindSplitsKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
     attr = true;
   }
-  if (a.quant) FindSplitsKernel<true><<<grid, kFindThreads, sm, s>>>(a); else FindSplitsKernel<false><<<grid, kFindThreads, sm, s>>>(a);
+  const CtrlArgs ca = tail_ctrl != nullptr ? *tail_ctrl : CtrlArgs();
+  if (a.quant) FindSplitsKernel<true><<<grid, kFindThreads, sm, s>>>(a, ca); else FindSplitsKernel<false><<<grid, kFindThreads, sm, s>>>(a, ca);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 

@@ -191,16 +191,13 @@ struct Config {
 // grammar "auto[,key:on|off]*" (parity: include/Falcata/falcata_plan.h:L44-258).
 // Every key must leave quantized models bit-identical; tests flip each key.
 struct Plan {
-  bool hist_tc = false;          // one-hot tcgen05 construct instance instead of shared-memory atomics
-  bool level_graph = false;      // CUDA-graph captured level loop with the device controller
+  bool hist_tc = false;          // root level of the quantized construct on the tensor cores (one-hot tcgen05 instance, 1 GPU)
   bool device_controller = true; // split arbitration on the device (no per-level host decision)
-  bool fused_rs = true;          // construct epilogue adds straight into the owner rank's slice
-  bool fused_ag = true;          // split find epilogue stores the rank's best split into every peer
+  bool fused_tail = true;        // split search, per-leaf argmax, cross-rank argmax and the level controller in ONE launch
+  bool fused_scan = true;        // the partition's scan + child set-up step inside the flags launch (last chunk block of each split)
   bool pack4 = true;             // 4-bit row storage when every group has <= 16 bins
   bool compact_view = true;      // per-tree gather of feature_fraction-sampled columns
   bool gh_in_row = false;        // packed gradient word stored next to the row's bins (measured slower on B200: the separate 4 B/row array stays L2-resident)
-  bool small_leaf_kernel = true; // one CTA per tiny leaf in the construct
-  bool hist_sub = true;          // larger = parent - smaller
   bool hist_lane = true;         // lane-per-group construct with bank-interleaved warp-private tiles (groups with <= 64 bins)
   bool hist_lane_atomic = false; // lane-per-group construct with one shared tile per block and shared atomics
   bool col_major_part = true;    // partition reads the split column from a column-major copy of the bins

@@ -18,6 +18,7 @@ def main():
     ap.add_argument("--top-k", type=int, default=20)
     ap.add_argument("--categorical", action="store_true", help="treat the last two columns (rounded) as categorical")
     ap.add_argument("--grow-policy", default="level")
+    ap.add_argument("--plan", default="auto", help="cuda_plan string")
     ap.add_argument("--max-spins", type=int, default=0)
     ap.add_argument("--skip-rank", type=int, default=-1, help="this rank leaves before training (failure-detection test)")
     args = ap.parse_args()
@@ -46,7 +47,7 @@ def main():
 
         _lib().FB_FabricSetMaxSpins(int(args.max_spins))
     params = {"objective": "binary", "num_leaves": args.leaves, "max_bin": 63, "quant_mode": args.quant, "grow_policy": args.grow_policy, "tree_learner": args.learner if world > 1 else "serial",
-              "device_type": "cuda", "verbosity": -1, "min_data_in_leaf": 20, "metric": "binary_logloss", "top_k": args.top_k}
+              "device_type": "cuda", "verbosity": -1, "min_data_in_leaf": 20, "metric": "binary_logloss", "top_k": args.top_k, "cuda_plan": args.plan}
     ds = fb.Dataset(X, y.cpu().numpy(), params={"max_bin": 63}, categorical_feature=cat if cat else "auto")
     ds = ds.set_replicated() if replicated else ds.set_global_rows(off, args.rows)
     try:

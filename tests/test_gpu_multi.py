@@ -42,6 +42,20 @@ def test_bit_identical_across_gpu_counts(tmp_path, quant):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_bit_identical_across_gpu_counts_at_benchmark_scale(tmp_path):
+    # the shape of the headline benchmark per rank (millions of rows, 255 leaves, 8 levels deep, 20 rounds): small
+    # data sets do not exercise full-width levels, multi-wave grids or cross-rank timing
+    extra = ("--rows", "2200000", "--leaves", "255", "--rounds", "20")
+    ref = _run(1, str(tmp_path / "m1.txt"), extra)
+    assert "Tree=19" in ref
+    for w in [w for w in (2, 4, 8) if w <= torch.cuda.device_count()]:
+        assert _run(w, str(tmp_path / f"m{w}.txt"), extra) == ref, f"model differs at {w} GPUs"
+    # the unfused level chain (separate argmax / gather / controller / scan launches) grows the same trees
+    w = min(2, torch.cuda.device_count())
+    assert _run(w, str(tmp_path / "m_unfused.txt"), extra + ("--plan", "auto,fused_tail:off,fused_scan:off")) == ref
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_leafwise_growth_bit_identical_across_gpu_counts(tmp_path):
     # exact leaf-wise growth: every rank's controller sees the same gathered best splits, over-grows the same
     # nodes and the host replay keeps the same tree, so the model is the single-GPU model at any GPU count
