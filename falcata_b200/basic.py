@@ -157,6 +157,16 @@ def _load_pandas_categorical(model_str: str) -> Optional[List[List[Any]]]:
         return None
 
 
+def _with_split_search(params: Dict[str, Any], ds: Any) -> Dict[str, Any]:
+    """Several ranks that hold the same (gathered or replicated) bin sample split the bin search by feature."""
+    from .parallel import bootstrap
+
+    _, ws = bootstrap.world()
+    if ws > 1 and (ds._global_rows is not None or ds._replicated) and "distributed_bin_finding" not in params:
+        return dict(params, distributed_bin_finding=True)
+    return params
+
+
 def _get_string(fn: Callable, *args: Any) -> str:
     out_len = ctypes.c_int64(0)
     buf_len = 1 << 16
@@ -201,14 +211,46 @@ def get_num_threads() -> int:
     return out.value
 
 
+_PY_TAGS: Dict[str, List[float]] = {}
+_PY_TAGS_ON = False
+
+
+class _tag:
+    """Wall-clock span of a Python-side stage, accumulated under ``name`` while time tags are on."""
+
+    def __init__(self, name: str) -> None:
+        self.name = name
+
+    def __enter__(self) -> "_tag":
+        if _PY_TAGS_ON:
+            import time
+
+            self.t0 = time.perf_counter()
+        return self
+
+    def __exit__(self, *a: Any) -> None:
+        if _PY_TAGS_ON:
+            import time
+
+            e = _PY_TAGS.setdefault(self.name, [0.0, 0])
+            e[0] += time.perf_counter() - self.t0; e[1] += 1
+
+
 def set_time_tag(enabled: bool) -> None:
-    """Switch the host-side stage timers of the native library on or off (off clears them)."""
+    """Switch the host-side stage timers (native library and Python layer) on or off (off clears them)."""
+    global _PY_TAGS_ON
+    _PY_TAGS_ON = bool(enabled)
+    if not enabled:
+        _PY_TAGS.clear()
     _safe_call(_lib().FB_SetTimeTag(ctypes.c_int(1 if enabled else 0)))
 
 
 def time_tag_report() -> str:
-    """Accumulated host-side stage times, one line per stage."""
-    return _get_string(_lib().FB_GetTimeTagReport)
+    """Accumulated host-side stage times, one line per stage (native stages first, then the Python layer's)."""
+    out = _get_string(_lib().FB_GetTimeTagReport)
+    for name in sorted(_PY_TAGS):
+        out += f"py::{name} costs:\t {_PY_TAGS[name][0]:.6g} s ({int(_PY_TAGS[name][1])} calls)\n"
+    return out
 
 
 # ------------------------------------------------------------------ Dataset ----
@@ -390,14 +432,16 @@ class Dataset:
             with torch.cuda.stream(side):
                 Xd = t.to(dev, non_blocking=True)   # overlaps with the host work below when the matrix is pinned
         goff, gtot = self._global_rows if self._global_rows is not None else (0, 0)
-        sample, total = bootstrap.gather_bin_sample(t, _resolved_int(params, "bin_construct_sample_cnt"), _resolved_int(params, "data_random_seed"), goff, gtot,
-                                                    replicated=self._replicated)
-        sample = np.ascontiguousarray(sample)
-        if sample.dtype not in _DTYPE_CODE:
-            sample = sample.astype(np.float64)
+        with _tag("ingest: bin sample (draw + gather over ranks)"):
+            sample, total = bootstrap.gather_bin_sample(t, _resolved_int(params, "bin_construct_sample_cnt"), _resolved_int(params, "data_random_seed"), goff, gtot,
+                                                        replicated=self._replicated)
+            sample = np.ascontiguousarray(sample)
+            if sample.dtype not in _DTYPE_CODE:
+                sample = sample.astype(np.float64)
         handle = ctypes.c_void_p()
-        _safe_call(lib.FB_DatasetCreateFromSampleTyped(sample.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[sample.dtype], ctypes.c_int32(sample.shape[0]),
-                                                       ctypes.c_int32(ncol), ctypes.c_int64(total), _param_str(params), None, 0, ctypes.byref(handle)))
+        with _tag("ingest: bin boundaries"):
+            _safe_call(lib.FB_DatasetCreateFromSampleTyped(sample.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[sample.dtype], ctypes.c_int32(sample.shape[0]),
+                                                           ctypes.c_int32(ncol), ctypes.c_int64(total), _param_str(_with_split_search(params, self)), None, 0, ctypes.byref(handle)))
         self._handle = handle
         off, tot = self._global_rows if self._global_rows is not None else (0, nrow)
         _safe_call(lib.FB_DatasetInitRows(handle, ctypes.c_int32(nrow), ctypes.c_int64(off), ctypes.c_int64(tot), 0))
@@ -405,9 +449,13 @@ class Dataset:
         if whole:
             # label / weight / group go into the dataset now: tens of milliseconds of host copies for millions of rows,
             # hidden behind the matrix copy that is still in flight
-            self._set_early_fields()
-            side.synchronize()
-            _safe_call(lib.FB_DatasetBinDeviceChunk(handle, ctypes.c_void_p(Xd.data_ptr()), code, ctypes.c_int32(nrow), ctypes.c_int32(ncol), 0, ctypes.c_int32(nrow)))
+            with _tag("ingest: label / weight / group"):
+                self._set_early_fields()
+            with _tag("ingest: wait for the matrix copy"):
+                side.synchronize()
+            with _tag("ingest: bin rows on the device"):
+                _safe_call(lib.FB_DatasetBinDeviceChunk(handle, ctypes.c_void_p(Xd.data_ptr()), code, ctypes.c_int32(nrow), ctypes.c_int32(ncol), 0, ctypes.c_int32(nrow)))
+                torch.cuda.synchronize()
         else:
             rows_per_chunk = max(1, int((free_bytes // 16) // max(1, ncol * t.element_size())))
             for a in range(0, nrow, rows_per_chunk):
@@ -482,7 +530,7 @@ class Dataset:
             sample = sample.astype(np.float64)
         handle = ctypes.c_void_p()
         _safe_call(lib.FB_DatasetCreateFromSampleTyped(sample.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[sample.dtype], ctypes.c_int32(sample.shape[0]),
-                                                       ctypes.c_int32(ncol), ctypes.c_int64(total), _param_str(params), None, 0, ctypes.byref(handle)))
+                                                       ctypes.c_int32(ncol), ctypes.c_int64(total), _param_str(_with_split_search(params, self)), None, 0, ctypes.byref(handle)))
         self._handle = handle
         _safe_call(lib.FB_DatasetInitRows(handle, ctypes.c_int32(nrow), ctypes.c_int64(goff), ctypes.c_int64(total), 1))
         _safe_call(lib.FB_DatasetPushRows(handle, arr.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[arr.dtype], ctypes.c_int32(nrow), ctypes.c_int32(ncol), 1, 0))
@@ -517,7 +565,7 @@ class Dataset:
             if sample.dtype not in _DTYPE_CODE:
                 sample = sample.astype(np.float64)
             _safe_call(lib.FB_DatasetCreateFromSampleTyped(sample.ctypes.data_as(ctypes.c_void_p), _DTYPE_CODE[sample.dtype], ctypes.c_int32(sample.shape[0]),
-                                                           ctypes.c_int32(ncol), ctypes.c_int64(total), _param_str(params), None, 0, ctypes.byref(handle)))
+                                                           ctypes.c_int32(ncol), ctypes.c_int64(total), _param_str(_with_split_search(params, self)), None, 0, ctypes.byref(handle)))
         self._handle = handle
         off, total = self._global_rows if self._global_rows is not None else (0, nrow)
         keep_host = 1 if str(params.get("device_type", "")).lower() == "cpu" or params.get("keep_host_bins") else 0

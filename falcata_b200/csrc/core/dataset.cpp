@@ -4,6 +4,7 @@
 // conflict-bounded grouping), L414-531 (two orderings, fewer groups wins), L533-676 (Construct),
 // L1298-1356 (CopySubrow); src/io/metadata.cpp.
 #include "fb/dataset.h"
+#include "fb/learner.h"
 
 #include <omp.h>
 
@@ -138,11 +139,18 @@ void Dataset::ConstructSchemaTyped(const void* sample, int dtype, int ns, int nc
   // tile's rows are read in order (the sample is row-major, so a single column on its own would stride by a row).
   // The rows where a feature leaves its most frequent bin are collected in the same pass, for the bundling below.
   // narrow data: one column per task keeps every core busy; wide data: up to 16 columns per task
-  const int kTile = std::max(1, std::min(16, ncol / (4 * std::max(1, omp_get_max_threads()))));
+  // Several ranks holding the SAME sample (the global one, gathered by row id) split the bin search by feature: tile t
+  // belongs to rank t % world, the finished mappers are all-gathered, and every rank ends up with the same schema as a
+  // single process would. Parity: src/io/dataset_loader.cpp:L672-759 (features striped over machines, mappers gathered).
+  const bool split_search = cfg.distributed_bin_finding && Network::active() && ncol >= 2;
+  const int my_rank = split_search ? Network::rank() : 0, nranks = split_search ? Network::world() : 1;
+  const int threads = std::max(1, omp_get_max_threads());
+  const int kTile = split_search ? std::max(1, std::min(16, ncol / (4 * threads * nranks))) : std::max(1, std::min(16, ncol / (4 * threads)));
   const int ntiles = (ncol + kTile - 1) / kTile;
   std::vector<std::vector<int>> nz_by_col(cfg.enable_bundle ? ncol : 0);
 #pragma omp parallel for schedule(dynamic, 1)
   for (int t = 0; t < ntiles; ++t) {
+    if (t % nranks != my_rank) continue;
     const int j0 = t * kTile, j1 = std::min(ncol, j0 + kTile), w = j1 - j0;
     std::vector<std::vector<double>> cols(w, std::vector<double>(ns));
     std::vector<int> m(w, 0);
@@ -160,13 +168,40 @@ void Dataset::ConstructSchemaTyped(const void* sample, int dtype, int ns, int nc
       mappers[j]->FindBin(cols[c].data(), m[c], ns, mb, cfg.min_data_in_bin, min_split_data, cfg.feature_pre_filter,
                           is_cat[j] ? BinType::Categorical : BinType::Numerical, cfg.use_missing, cfg.zero_as_missing, {});
     }
-    if (cfg.enable_bundle) {
+    if (cfg.enable_bundle && !split_search) {
       for (int i = 0; i < ns; ++i) {
         for (int c = 0; c < w; ++c) {
           const BinMapper& bm = *mappers[j0 + c];
           if (bm.is_trivial || bm.sparse_rate < 0.5) continue;   // dense features never share a bundle
           if (bm.ValueToBin(ReadValue(sample, dtype, static_cast<size_t>(i) * ncol + j0 + c)) != bm.most_freq_bin) nz_by_col[j0 + c].push_back(i);
         }
+      }
+    }
+  }
+  if (split_search) {
+    // all-gather of the mappers: sizes first, then the serialised stripes padded to the largest
+    std::vector<char> mine;
+    for (int t = my_rank; t < ntiles; t += nranks)
+      for (int j = t * kTile; j < std::min(ncol, (t + 1) * kTile); ++j) mappers[j]->Serialize(&mine);
+    int64_t my_size = static_cast<int64_t>(mine.size());
+    std::vector<char> sizes_raw; Network::Gather(&my_size, sizeof(int64_t), &sizes_raw);
+    const int64_t* sizes = reinterpret_cast<const int64_t*>(sizes_raw.data());
+    int64_t cap = 8; for (int r = 0; r < nranks; ++r) cap = std::max(cap, sizes[r]);
+    mine.resize(static_cast<size_t>(cap), 0);
+    std::vector<char> all; Network::Gather(mine.data(), cap, &all);
+    for (int r = 0; r < nranks; ++r) {
+      if (r == my_rank) continue;
+      const char* p = all.data() + static_cast<size_t>(r) * cap;
+      for (int t = r; t < ntiles; t += nranks)
+        for (int j = t * kTile; j < std::min(ncol, (t + 1) * kTile); ++j) { mappers[j].reset(new BinMapper()); p = mappers[j]->Deserialize(p); }
+    }
+    if (cfg.enable_bundle) {
+      // rows where a sparse feature leaves its most frequent bin, for the bundling below (needs every mapper)
+#pragma omp parallel for schedule(dynamic, 8)
+      for (int j = 0; j < ncol; ++j) {
+        const BinMapper& bm = *mappers[j];
+        if (bm.is_trivial || bm.sparse_rate < 0.5) continue;
+        for (int i = 0; i < ns; ++i) if (bm.ValueToBin(ReadValue(sample, dtype, static_cast<size_t>(i) * ncol + j)) != bm.most_freq_bin) nz_by_col[j].push_back(i);
       }
     }
   }

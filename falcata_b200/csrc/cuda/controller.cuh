@@ -25,15 +25,23 @@ struct CtrlShared {
   int ncand, nkeep;
 };
 
-// A record that another block of the SAME launch may have written a moment ago: read through L2, word by word.
+// A record that another block of the SAME launch may have written a moment ago: read through L2, in 8-byte pieces
+// where the type allows it (the loads of one record are independent and issue back to back).
 template <typename T>
 __device__ inline T LoadWords(const T* p) {
   static_assert(sizeof(T) % 4 == 0, "word-sized records only");
   T v;
-  const unsigned int* s = reinterpret_cast<const unsigned int*>(p);
-  unsigned int* d = reinterpret_cast<unsigned int*>(&v);
+  if constexpr (sizeof(T) % 8 == 0 && alignof(T) >= 8) {
+    const unsigned long long* s = reinterpret_cast<const unsigned long long*>(p);
+    unsigned long long* d = reinterpret_cast<unsigned long long*>(&v);
 #pragma unroll
-  for (int w = 0; w < static_cast<int>(sizeof(T) / 4); ++w) d[w] = __ldcg(s + w);
+    for (int w = 0; w < static_cast<int>(sizeof(T) / 8); ++w) d[w] = __ldcg(s + w);
+  } else {
+    const unsigned int* s = reinterpret_cast<const unsigned int*>(p);
+    unsigned int* d = reinterpret_cast<unsigned int*>(&v);
+#pragma unroll
+    for (int w = 0; w < static_cast<int>(sizeof(T) / 4); ++w) d[w] = __ldcg(s + w);
+  }
   return v;
 }
 

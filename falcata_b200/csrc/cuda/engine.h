@@ -117,6 +117,7 @@ class CudaEngine : public DeviceEngine {
   DevBuf<int> features_, sub_features_;
   // exact leaf-wise growth (grow_policy=leaf): the device grows up to grow_leaves_ leaves, the host keeps the best num_leaves
   bool leafwise_ = false; int grow_leaves_ = 0;
+  bool tc_fallback_logged_ = false;
   DevBuf<double> eval_key_;
   void FinalizeLeafwise(const LevelCtrl& hc, Tree* tree);
   // per-node feature masks (feature_fraction_bynode, interaction constraints)

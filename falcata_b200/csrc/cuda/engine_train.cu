@@ -329,7 +329,17 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     ca.leafwise_budget = leafwise_ ? cfg_.num_leaves - 1 : 0; ca.eval_key = leafwise_ ? eval_key_.get() : nullptr;
     ca.max_leaves = NL; ca.rows_per_block = rpb; ca.bin_owner = feature_parallel_ ? bin_owner_.get() : nullptr;
   }
+  // cuda_plan=hist_tc:on: the root histogram on the tensor cores where the instance applies (one rank, rows in order,
+  // 32-byte rows of the resident matrix, 8-bit quantized values)
+  const bool tc_root = plan_.hist_tc && quant_ && world_ == 1 && !bagged && ha.rows == dd_->rows.get() && dd_->row_stride == 32 && dd_->num_groups <= 32 &&
+                       train_->max_group_bin <= 64 && gh_stride_ == 4 && cfg_.quant_bins_resolved <= 127;
+  if (plan_.hist_tc && !tc_root && !tc_fallback_logged_) {
+    tc_fallback_logged_ = true;
+    Log::Warning("cuda_plan=hist_tc:on does not cover this run (needs one rank, no bagging, quantized gradients of at most 127 levels, at most 32 groups of at most 64 bins in 32-byte rows); the lane kernel builds the root histogram");
+  }
+  if (tc_root) { ha.lane_mode = 3; ha.tc_row_count = root_count_; ha.rows_per_block = HistTcRowsPerBlock(root_count_, num_sms_); ha.total_blocks = (root_count_ + ha.rows_per_block - 1) / ha.rows_per_block; }
   construct_and_find();   // root level (with the fused tail its last block already decides level 1)
+  if (tc_root) ha.lane_mode = lane_mode_;
   if (use_ctrl_) {
     // ---- device-controlled growth: levels are enqueued ahead; the host reads one small record per batch ----
     FB_CUDA(cudaMemcpyAsync(h_root_.get(), leaves_.get(), sizeof(LeafInfo), cudaMemcpyDeviceToHost, stream_));   // the root record, before any split rewrites leaf 0

@@ -453,6 +453,10 @@ int LaneRowsUnit() { return kLaneWarps * 32; }
 
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
   if (a.total_blocks <= 0 || a.num_tasks <= 0) return;
+  if (a.lane_mode == 3) {
+    if (LaunchHistConstructQuantTC(a, s)) return;
+    Log::Fatal("tensor-core histogram: the shape is outside what the instance covers (root level, 32-byte rows, <= 32 groups of <= 64 bins, one rank)");
+  }
   if (a.lane_mode != 0) {
     const int cap = kLaneWarps * a.sub_rows;
     if (a.rows_per_block > cap) Log::Fatal("lane histogram: %d rows per block would overflow the 16-bit lanes (cap %d)", a.rows_per_block, cap);

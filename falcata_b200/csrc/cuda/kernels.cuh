@@ -74,7 +74,9 @@ struct HistArgs {
   int rows_per_block; int sub_rows;
   int identity_root;        // 1: task rows are 0..count-1 (no index load)
   int num_total_bin;
-  int lane_mode;            // 0: flat items + shared atomics; 1: lane-per-group warp-private tiles (no atomics); 2: lane-per-group, one shared tile + atomics
+  int lane_mode;            // 0: flat items + shared atomics; 1: lane-per-group warp-private tiles (no atomics); 2: lane-per-group, one shared tile + atomics;
+                            // 3: one-hot tcgen05 MMA (root level, 32-byte rows; falls back to mode 1 outside its coverage)
+  int tc_row_count;         // mode 3: rows of the task as the host knows them (extent of the TMA tensor maps)
   int lane_bins;            // lane modes: bins per group tile (16 or 64)
   HistDest dest;
   FabricSignal sig;         // world > 1: the last block raises this rank's "construct done" flag on every peer
@@ -88,8 +90,10 @@ int LaneRowsUnit();   // rows per stage of a lane-construct block (warps x 32): 
 void LaunchCompactGather(const uint8_t* cols, long long col_stride, int n, const int* groups, int num_groups, uint8_t* out, int out_stride, cudaStream_t s,
                          bool pack4 = false);   // pack4: out[row][j / 2] holds listed groups j (low nibble) and j + 1 (high nibble)
 void LaunchHistConstructFloat(const HistArgs& a, cudaStream_t s);
-// tcgen05 one-hot instance (same arguments, same result); returns false when the shape is outside what it covers
+// tcgen05 one-hot instance (same arguments, same result); returns false, having launched nothing, when the shape is outside
+// what it covers (see hist_tc_kernel.cu). rows_per_block must come from HistTcRowsPerBlock (whole 32-row steps).
 bool LaunchHistConstructQuantTC(const HistArgs& a, cudaStream_t s);
+int HistTcRowsPerBlock(long long count, int num_sms);
 
 // ------------------------------------------------------------ split find ----
 struct FindChild { int leaf; int slot; int other_slot; int is_larger; int split; int is_left; int parent_global; int task; };   // task: construct task of this pair's smaller child   // larger: bins = pool[slot] - pool[other_slot], written back to pool[slot]

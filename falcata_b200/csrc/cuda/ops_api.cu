@@ -66,9 +66,17 @@ int FB_OpHistogram(const uint8_t* rows, int row_stride, int num_groups, const vo
   int mgb = 0; for (int v : gbins) mgb = std::max(mgb, v);
   a.lane_bins = mgb <= 16 ? 16 : 64;
   if (a.lane_mode != 0 && mgb > 64) Log::Fatal("lane histogram covers groups of at most 64 bins");
+  if (a.lane_mode == 3) {
+    if (quant_bins > 127) Log::Fatal("tensor-core histogram: quantized values must fit 8 bits");
+    a.lane_bins = 64; a.tc_row_count = count;
+    cudaDeviceProp prop; int dev = 0; FB_CUDA(cudaGetDevice(&dev)); FB_CUDA(cudaGetDeviceProperties(&prop, dev));
+    a.rows_per_block = rows_per_block = HistTcRowsPerBlock(count, prop.multiProcessorCount);
+    t.num_blocks = (count + rows_per_block - 1) / rows_per_block; a.total_blocks = t.num_blocks;
+    d_task.Upload(&t, 1, s);
+  }
   if (a.lane_mode == 1 && rows_per_block > 8 * a.sub_rows) { a.rows_per_block = rows_per_block = 8 * a.sub_rows; }
   if (a.lane_mode == 2 && rows_per_block > a.sub_rows) { a.rows_per_block = rows_per_block = a.sub_rows; }
-  if (a.lane_mode != 0) {
+  if (a.lane_mode == 1 || a.lane_mode == 2) {
     t.num_blocks = (count + rows_per_block - 1) / rows_per_block; a.total_blocks = t.num_blocks;
     d_task.Upload(&t, 1, s);
   }

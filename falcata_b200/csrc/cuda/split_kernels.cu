@@ -400,13 +400,17 @@ __device__ inline void ReduceChildBody(const FindArgs& a, int child, ReduceShare
 // owns). Every rank runs this on the same records, so all ranks decide alike. One thread per child.
 __device__ inline void GatherChild(const FindArgs& a, int child) {
   const FindChild ch = a.children[child];
+  // compare on the records' first 16 bytes (gain, feature, threshold), then fetch only the winner whole
   SplitRecord best; InitSplitRecord(&best);
-  int best_real = -1;
+  int best_real = -1, best_rank = -1;
   for (int r = 0; r < a.wait_best.world; ++r) {
-    const SplitRecord rec = LoadWords(a.gathered + static_cast<size_t>(r) * a.gathered_stride + ch.leaf);
-    const int real = rec.feature >= 0 ? a.meta[rec.feature].real_index : -1;
-    if (SplitBetter(rec.gain, real, rec.threshold, best.gain, best_real, best.threshold)) { best = rec; best_real = real; }
+    const SplitRecord* rp = a.gathered + static_cast<size_t>(r) * a.gathered_stride + ch.leaf;
+    const double gain = LoadWords(&rp->gain);
+    const int feature = LoadWords(&rp->feature), threshold = LoadWords(&rp->threshold);
+    const int real = feature >= 0 ? a.meta[feature].real_index : -1;
+    if (SplitBetter(gain, real, threshold, best.gain, best_real, best.threshold)) { best.gain = gain; best.threshold = threshold; best_real = real; best_rank = r; }
   }
+  if (best_rank >= 0) best = LoadWords(a.gathered + static_cast<size_t>(best_rank) * a.gathered_stride + ch.leaf);
   a.best[ch.leaf] = best;
 }
 

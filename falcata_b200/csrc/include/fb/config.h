@@ -96,6 +96,7 @@ namespace fb {
   X(bool, zero_as_missing, false, "") \
   X(bool, feature_pre_filter, true, "") \
   X(bool, pre_partition, false, "is_pre_partition") \
+  X(bool, distributed_bin_finding, false, "") \
   X(bool, two_round, false, "two_round_loading,use_two_round_loading") \
   X(bool, header, false, "has_header") \
   X(std::string, label_column, "", "label") \

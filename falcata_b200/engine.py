@@ -77,11 +77,14 @@ def train(params: Dict[str, Any], train_set: Dataset, num_boost_round: int = 100
     cbs_before = sorted((cb for cb in cbs if getattr(cb, "before_iteration", False)), key=attrgetter("order"))
     cbs_after = sorted((cb for cb in cbs if not getattr(cb, "before_iteration", False)), key=attrgetter("order"))
 
-    booster = Booster(params=params, train_set=train_set)
+    from .basic import _tag
+    with _tag("train: booster set-up (dataset construct included)"):
+        booster = Booster(params=params, train_set=train_set)
     if is_valid_contain_train:
         booster.set_train_data_name(train_data_name)
-    for vd, name in zip(reduced_valid_sets, name_valid_sets):
-        booster.add_valid(vd, name)
+    with _tag("train: add validation sets"):
+        for vd, name in zip(reduced_valid_sets, name_valid_sets):
+            booster.add_valid(vd, name)
     if predictor is not None:
         # continued training: the loaded trees come first in the final model
         import ctypes
@@ -94,12 +97,14 @@ def train(params: Dict[str, Any], train_set: Dataset, num_boost_round: int = 100
         for cb in cbs_before:
             cb(callback.CallbackEnv(model=booster, params=params, iteration=i, begin_iteration=init_iteration,
                                     end_iteration=init_iteration + num_boost_round, evaluation_result_list=None))
-        finished = booster.update(fobj=fobj)
+        with _tag("train: boosting rounds"):
+            finished = booster.update(fobj=fobj)
         evaluation_result_list = []
         if valid_sets is not None or feval is not None:
-            if is_valid_contain_train:
-                evaluation_result_list.extend(booster.eval_train(feval))
-            evaluation_result_list.extend(booster.eval_valid(feval))
+            with _tag("train: metric evaluation"):
+                if is_valid_contain_train:
+                    evaluation_result_list.extend(booster.eval_train(feval))
+                evaluation_result_list.extend(booster.eval_valid(feval))
         try:
             for cb in cbs_after:
                 cb(callback.CallbackEnv(model=booster, params=params, iteration=i, begin_iteration=init_iteration,
@@ -115,7 +120,8 @@ def train(params: Dict[str, Any], train_set: Dataset, num_boost_round: int = 100
         booster.best_score[item[0]][item[1]] = item[2]
     if not keep_training_booster:
         best_it, best_sc = booster.best_iteration, booster.best_score
-        model = Booster(model_str=booster.model_to_string(num_iteration=-1))
+        with _tag("train: copy of the model without training state"):
+            model = Booster(model_str=booster.model_to_string(num_iteration=-1))
         model.best_iteration, model.best_score, model.params = best_it, best_sc, params
         return model
     return booster

@@ -47,6 +47,26 @@ def test_hist_quant_exact(n, groups, nb, qbins, rpb, lane_mode):
     assert torch.equal(out, _ref_hist(rows, nbins, gi, hi, idx).long())
 
 
+@pytest.mark.parametrize("n,nb,qbins", [(1, 64, 4), (33, 64, 4), (1023, 64, 4), (50000, 64, 4), (300001, 64, 64), (70000, 16, 4), (40000, 37, 100)])
+@pytest.mark.parametrize("groups", [28, 32, 5])
+def test_hist_tensor_core_exact(n, nb, qbins, groups):
+    """The one-hot tcgen05 instance (lane_mode 3: int8 MMA, int32 accumulators in tensor memory, TMA-fed row tiles)
+    gives the exact integer histogram, like the SIMT instances: root-level shape, 32-byte rows."""
+    from falcata_b200 import ops
+    nbins = [nb] * groups
+    rows = _rows(n, groups, nbins, stride=32)
+    rows[:, groups:] = 201          # bytes past the last group are not bins: the kernel must ignore them
+    g = torch.Generator(device="cuda"); g.manual_seed(2)
+    gi = torch.randint(-(qbins // 2), qbins // 2 + 1, (n,), generator=g, device="cuda", dtype=torch.int32)
+    hi = torch.randint(0, qbins + 1, (n,), generator=g, device="cuda", dtype=torch.int32)
+    packed = (gi << 16) | (hi & 0xFFFF)
+    ref = _ref_hist(rows, nbins, gi, hi)
+    out = ops.histogram(rows, packed, nbins, quant=True, quant_bins=qbins, lane_mode=3)
+    assert torch.equal(out, ref.long())
+    # same answer as the lane kernel on the same input
+    assert torch.equal(out, ops.histogram(rows, packed, nbins, quant=True, quant_bins=qbins, rows_per_block=8192, lane_mode=1))
+
+
 def test_hist_quant_gh_in_row():
     from falcata_b200 import ops
     n, groups = 5000, 28
