@@ -63,6 +63,7 @@ class ClockSampler:
         self.reasons = set()
         self.max_mhz = None
         self._stop = threading.Event()
+        self._ready = threading.Event()
         self._t = threading.Thread(target=self._run, daemon=True)
 
     def _run_nvml(self) -> bool:
@@ -81,6 +82,7 @@ class ClockSampler:
             self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
         except Exception:
             return False
+        self._ready.set()
         while not self._stop.is_set():
             try:
                 self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
@@ -99,6 +101,7 @@ class ClockSampler:
             return
         q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        self._ready.set()
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
@@ -114,7 +117,7 @@ class ClockSampler:
 
     def __enter__(self):
         self._t.start()
-        time.sleep(0.02)   # the sampler is up before the timed region starts
+        self._ready.wait(timeout=10)   # the sampler is up (NVML initialised) before the timed region starts
         return self
 
     def __exit__(self, *a):
@@ -297,6 +300,10 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
+        # the launcher sets OMP_NUM_THREADS=1 for every rank; the host stages of ingest (bin boundaries, label copies)
+        # get an equal share of the cores instead, through the library's own parameter
+        PARAMS["num_threads"] = max(1, len(os.sched_getaffinity(0)) // world)
+    if world > 1:
         import torch.distributed as dist
 
         torch.cuda.set_device(local_rank)
@@ -389,7 +396,7 @@ def main() -> None:
         t0 = time.perf_counter()
         # the pinned host matrix goes straight into the public API: the library copies it to the device on a side stream
         # while the host finds the bin boundaries, then bins on the device
-        ds2 = fb.Dataset(Xh, yh, params={"max_bin": PARAMS["max_bin"], "device_type": "cuda"}).set_global_rows(off, args.rows)
+        ds2 = fb.Dataset(Xh, yh, params={"max_bin": PARAMS["max_bin"], "device_type": "cuda", "num_threads": PARAMS.get("num_threads", 0)}).set_global_rows(off, args.rows)
         fb.train(dict(PARAMS, is_provide_training_metric=True), ds2, K, valid_sets=[ds2], valid_names=["train"], keep_training_booster=True,
                  callbacks=[fb.record_evaluation({})])
         barrier()

@@ -423,14 +423,15 @@ class Dataset:
         t = self.data if _is_torch_tensor(self.data) else torch.from_numpy(self.data)
         nrow, ncol = t.shape
         dev = torch.device("cuda", torch.cuda.current_device())
-        free_bytes, _ = torch.cuda.mem_get_info(dev)
-        nbytes = t.numel() * t.element_size()
-        whole = nbytes <= free_bytes // 4
-        side = torch.cuda.Stream(device=dev)
-        Xd = None
-        if whole:
-            with torch.cuda.stream(side):
-                Xd = t.to(dev, non_blocking=True)   # overlaps with the host work below when the matrix is pinned
+        with _tag("ingest: device buffer + copy enqueue"):
+            free_bytes, _ = torch.cuda.mem_get_info(dev)
+            nbytes = t.numel() * t.element_size()
+            whole = nbytes <= free_bytes // 4
+            side = torch.cuda.Stream(device=dev)
+            Xd = None
+            if whole:
+                with torch.cuda.stream(side):
+                    Xd = t.to(dev, non_blocking=True)   # overlaps with the host work below when the matrix is pinned
         goff, gtot = self._global_rows if self._global_rows is not None else (0, 0)
         with _tag("ingest: bin sample (draw + gather over ranks)"):
             sample, total = bootstrap.gather_bin_sample(t, _resolved_int(params, "bin_construct_sample_cnt"), _resolved_int(params, "data_random_seed"), goff, gtot,
@@ -829,8 +830,10 @@ class Booster:
                 raise TypeError(f"Training data should be Dataset instance, met {type(train_set).__name__}")
             merged = dict(train_set.params); merged.update(self.params)
             train_set.params = {**train_set.params, **{k: v for k, v in self.params.items() if k in _DATASET_PARAMS}}
-            train_set.construct()
-            _safe_call(lib.FB_BoosterCreate(train_set._handle, _param_str(self.params), ctypes.byref(self._handle)))
+            with _tag("booster: dataset construct"):
+                train_set.construct()
+            with _tag("booster: native create (objective, metrics, device engine)"):
+                _safe_call(lib.FB_BoosterCreate(train_set._handle, _param_str(self.params), ctypes.byref(self._handle)))
         elif model_file is not None:
             _safe_call(lib.FB_BoosterCreateFromModelfile(str(model_file).encode(), ctypes.byref(n_iter), ctypes.byref(self._handle)))
             with open(model_file, "rb") as f:   # a model file (text or binary) may end with the pandas categories trailer

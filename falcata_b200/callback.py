@@ -75,23 +75,35 @@ def record_evaluation(eval_result: Dict[str, Dict[str, List[Any]]]) -> Callable:
 
 
 def reset_parameter(**kwargs: Union[list, Callable]) -> Callable:
+    """Schedule parameters over the boosting rounds: each keyword maps a parameter name to a list (one value per
+    round) or to a function of the round index (counted from the first round of this training call).
+    Parity: python-package/falcata/callback.py (``reset_parameter``: runs before the iteration, order 10)."""
+    schedules = dict(kwargs)
+    for name, sched in schedules.items():
+        if not isinstance(sched, list) and not callable(sched):
+            raise ValueError("Only list and callable values are supported as a mapping from boosting round index to new parameter value.")
+
+    def _value_at(name: str, sched: Union[list, Callable], step: int, n_rounds: int) -> Any:
+        if callable(sched):
+            return sched(step)
+        if len(sched) != n_rounds:
+            raise ValueError(f"Length of list {name!r} has to equal to 'num_boost_round'.")
+        return sched[step]
+
     def _callback(env: CallbackEnv) -> None:
-        new_parameters = {}
-        for key, value in kwargs.items():
-            if isinstance(value, list):
-                if len(value) != env.end_iteration - env.begin_iteration:
-                    raise ValueError(f"Length of list {key!r} has to equal to 'num_boost_round'.")
-                new_param = value[env.iteration - env.begin_iteration]
-            elif callable(value):
-                new_param = value(env.iteration - env.begin_iteration)
-            else:
-                raise ValueError("Only list and callable values are supported as a mapping from boosting round index to new parameter value.")
-            if new_param != env.params.get(key, None):
-                new_parameters[key] = new_param
-        if new_parameters:
-            if hasattr(env.model, "reset_parameter"):
-                env.model.reset_parameter(new_parameters)
-            env.params.update(new_parameters)
+        step = env.iteration - env.begin_iteration
+        n_rounds = env.end_iteration - env.begin_iteration
+        changed = {}
+        for name, sched in schedules.items():
+            v = _value_at(name, sched, step, n_rounds)
+            if name not in env.params or env.params[name] != v:
+                changed[name] = v
+        if not changed:
+            return
+        reset = getattr(env.model, "reset_parameter", None)
+        if reset is not None:
+            reset(changed)
+        env.params.update(changed)
 
     _callback.before_iteration = True  # type: ignore[attr-defined]
     _callback.order = 10  # type: ignore[attr-defined]

@@ -629,7 +629,7 @@ void CudaEngine::ReadBackLevel(int num_leaves) {
 // leaves tile the rows by position; after their rows are gathered into index buffer 0 a pruned subtree is the
 // contiguous range it covered when it was split, and these ranges replace the device leaf records, so the score
 // update and the leaf renewal see the final tree.
-// Parity: src/treelearner/cuda/learner.cpp:L2526-3067 (selective grow-then-prune with a host heap simulation).
+// Parity: src/treelearner/cuda/cuda_single_gpu_tree_learner.cpp:L2524-3067 (selective grow-then-prune with a host heap simulation).
 void CudaEngine::FinalizeLeafwise(const LevelCtrl& hc, Tree* tree) {
   struct Node { int parent = -1, left = -1, right = -1, journal = -1, dev_leaf = 0; bool is_left = true; };
   const int J = hc.journal_count, LD = hc.num_leaves;

@@ -152,7 +152,6 @@ namespace fb {
   X(std::string, cuda_precision, "fp64", "") \
   X(std::string, cuda_plan, "auto", "") \
   X(std::string, grow_policy, "level", "") \
-  X(std::string, comm, "p2p", "")
 
 enum class QuantMode : int { None = 0, Stochastic = 1, FixedPoint = 2 };
 

@@ -255,3 +255,25 @@ def test_reset_training_data_needs_aligned_bins():
     want = float(-np.mean(y2 * np.log(p) + (1 - y2) * np.log(1 - p)))
     got = [v for (_, name, v, _) in bst.eval_train() if name == "binary_logloss"][0]
     assert abs(got - want) < 1e-6
+
+
+def test_reset_parameter_schedules():
+    """List and callable schedules reach the booster before each round; wrong lengths and other types are refused."""
+    rng = np.random.default_rng(3)
+    X = rng.normal(size=(400, 5)); y = X[:, 0] * 2 + rng.normal(size=400) * 0.1
+    seen = []
+
+    def probe(env):
+        seen.append(env.params.get("learning_rate"))
+    probe.before_iteration = True; probe.order = 20
+    params = {"objective": "regression", "num_leaves": 7, "verbosity": -1, "learning_rate": 0.5, "min_data_in_leaf": 5}
+    b1 = fb.train(dict(params), fb.Dataset(X, y), 4, callbacks=[fb.reset_parameter(learning_rate=[0.5, 0.25, 0.125, 0.0625]), probe])
+    assert seen == [0.5, 0.25, 0.125, 0.0625]
+    b2 = fb.train(dict(params), fb.Dataset(X, y), 4, callbacks=[fb.reset_parameter(learning_rate=lambda i: 0.5 * 0.5 ** i)])
+    assert np.allclose(b1.predict(X), b2.predict(X))
+    b3 = fb.train(dict(params), fb.Dataset(X, y), 4)
+    assert not np.allclose(b1.predict(X), b3.predict(X))
+    with pytest.raises(ValueError):
+        fb.train(dict(params), fb.Dataset(X, y), 4, callbacks=[fb.reset_parameter(learning_rate=[0.1, 0.2])])
+    with pytest.raises(ValueError):
+        fb.reset_parameter(learning_rate=0.1)
