@@ -423,19 +423,36 @@ class Dataset:
         t = self.data if _is_torch_tensor(self.data) else torch.from_numpy(self.data)
         nrow, ncol = t.shape
         dev = torch.device("cuda", torch.cuda.current_device())
-        with _tag("ingest: device buffer + copy enqueue"):
-            free_bytes, _ = torch.cuda.mem_get_info(dev)
-            nbytes = t.numel() * t.element_size()
-            whole = nbytes <= free_bytes // 4
-            side = torch.cuda.Stream(device=dev)
-            Xd = None
-            if whole:
-                with torch.cuda.stream(side):
-                    Xd = t.to(dev, non_blocking=True)   # overlaps with the host work below when the matrix is pinned
+        free_bytes, _ = torch.cuda.mem_get_info(dev)
+        nbytes = t.numel() * t.element_size()
+        whole = nbytes <= free_bytes // 4
+        staged: Dict[str, Any] = {}
+
+        def _stage_matrix() -> None:
+            # a helper thread pays for the side stream, the device allocation (tens of milliseconds for hundreds of
+            # megabytes) and the copy's enqueue while this thread draws the sample and finds the bin boundaries
+            try:
+                with _tag("ingest: device buffer + copy enqueue (helper thread)"):
+                    torch.cuda.set_device(dev)
+                    side = torch.cuda.Stream(device=dev)
+                    staged["side"] = side
+                    with torch.cuda.stream(side):
+                        Xd = torch.empty(t.shape, dtype=t.dtype, device=dev)
+                        Xd.copy_(t, non_blocking=True)   # asynchronous when the matrix is pinned
+                    staged["Xd"] = Xd
+            except BaseException as e:   # re-raised by the caller after join()
+                staged["error"] = e
+
+        import threading
+
+        stager = threading.Thread(target=_stage_matrix, daemon=True) if whole else None
+        Xd = None
         goff, gtot = self._global_rows if self._global_rows is not None else (0, 0)
         with _tag("ingest: bin sample (draw + gather over ranks)"):
+            # the helper starts once the row draw (a small kernel of its own) is through: device allocations of two
+            # threads at the same time wait on each other
             sample, total = bootstrap.gather_bin_sample(t, _resolved_int(params, "bin_construct_sample_cnt"), _resolved_int(params, "data_random_seed"), goff, gtot,
-                                                        replicated=self._replicated)
+                                                        replicated=self._replicated, after_draw=stager.start if stager is not None else None)
             sample = np.ascontiguousarray(sample)
             if sample.dtype not in _DTYPE_CODE:
                 sample = sample.astype(np.float64)
@@ -453,7 +470,11 @@ class Dataset:
             with _tag("ingest: label / weight / group"):
                 self._set_early_fields()
             with _tag("ingest: wait for the matrix copy"):
-                side.synchronize()
+                stager.join()
+                if "error" in staged:
+                    raise staged["error"]
+                Xd = staged.pop("Xd")
+                staged.pop("side").synchronize()
             with _tag("ingest: bin rows on the device"):
                 _safe_call(lib.FB_DatasetBinDeviceChunk(handle, ctypes.c_void_p(Xd.data_ptr()), code, ctypes.c_int32(nrow), ctypes.c_int32(ncol), 0, ctypes.c_int32(nrow)))
                 torch.cuda.synchronize()

@@ -271,10 +271,10 @@ int CudaEngine::ChooseRowsPerBlock(long long total_rows) const {
     // the lane kernel runs one block per SM with a fixed cost per block (tile clear, pipeline fill, merge of
     // the warps' tiles): aim at about four waves (measured best at 11M and 1.4M rows), in units of 384 rows,
     // within what the 16-bit lanes of the packed cells allow per warp tile
-    const int unit = LaneRowsUnit();   // rows of one stage across the block's warps
+    const int unit = LaneRowsUnit(plan_.hist_lane_red, sub_rows_);   // rows of one stage across the block's warps
     long long rpb = (total_rows / (4LL * num_sms_) + unit - 1) / unit * unit;
     rpb = std::min<long long>(std::max<long long>(rpb, 3LL * unit), 13LL * unit);
-    rpb = std::min<long long>(rpb, static_cast<long long>(unit / 32) * (sub_rows_ / 32 * 32));
+    rpb = std::min<long long>(rpb, static_cast<long long>(LaneTiles(plan_.hist_lane_red, sub_rows_)) * (sub_rows_ / 32 * 32));
     return static_cast<int>(rpb);
   }
   long long target = total_rows / (static_cast<long long>(num_sms_) * 6) + 1;

@@ -186,11 +186,19 @@ __device__ inline bool MbarWaitBounded(uint64_t* bar, uint32_t parity) {
 // together, and cells that repeat inside the four are forwarded in registers so that every store holds its full sum.
 // P4: two groups per byte (low nibble = even group).
 template <bool P4>
-__device__ __forceinline__ void ConsumeStage(int* __restrict__ tile, const unsigned char* __restrict__ stage_rows, const int* __restrict__ sg, int cnt, int lane, bool active) {
+__device__ __forceinline__ void ConsumeStage(int* __restrict__ tile, const unsigned char* __restrict__ stage_rows, const int* __restrict__ sg, int cnt, int lane, bool active, bool red = false) {
   const unsigned char* sr = stage_rows + (P4 ? (lane >> 1) : lane);
   const int nshift = (lane & 1) * 4;
   auto bin_of = [&](int j) -> int { const int b = sr[j * 32]; return P4 ? ((b >> nshift) & 15) : b; };
-  if (cnt == 32) {
+  if (red && cnt == 32) {
+    // reduction form: one shared-memory add per row and lane, no value comes back, so nothing has to be forwarded
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      const int4 g4 = *reinterpret_cast<const int4*>(sg + j);
+      const int a0 = bin_of(j) * 32 + lane, a1 = bin_of(j + 1) * 32 + lane, a2 = bin_of(j + 2) * 32 + lane, a3 = bin_of(j + 3) * 32 + lane;
+      if (active) { atomicAdd(tile + a0, g4.x); atomicAdd(tile + a1, g4.y); atomicAdd(tile + a2, g4.z); atomicAdd(tile + a3, g4.w); }
+    }
+  } else if (cnt == 32) {
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
       const int a0 = bin_of(j) * 32 + lane, a1 = bin_of(j + 1) * 32 + lane, a2 = bin_of(j + 2) * 32 + lane, a3 = bin_of(j + 3) * 32 + lane;
@@ -205,22 +213,27 @@ __device__ __forceinline__ void ConsumeStage(int* __restrict__ tile, const unsig
       }
     }
   } else {
-    for (int j = 0; j < cnt; ++j) { const int b = bin_of(j); const int g = sg[j]; if (active) tile[b * 32 + lane] += g; }
+    for (int j = 0; j < cnt; ++j) {
+      const int b = bin_of(j); const int g = sg[j];
+      if (active) { if (red) atomicAdd(tile + b * 32 + lane, g); else tile[b * 32 + lane] += g; }
+    }
   }
 }
 
-constexpr int kLaneWarps = 20;
-constexpr int kLaneThreads = kLaneWarps * 32;
-constexpr int kLaneStages = 2;
-template <int NB>
-__global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs a) {
+constexpr int kLaneMaxThreads = 1024;
+// Block shape: `lane_warps` warps (the block size), every `lane_share` consecutive warps add into one tile. Sharing
+// a tile needs the reduction form of the update (`lane_red`); with one warp per tile both forms are valid.
+template <int NB, int kLaneStages>
+__global__ void __launch_bounds__(kLaneMaxThreads, 1) HistQuantLaneKernel(HistArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int kTile = NB * 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int* tiles = reinterpret_cast<int*>(smem_raw);                                                 // [warps][NB][32]
-  unsigned char* rows_w = smem_raw + sizeof(int) * kLaneWarps * kTile + static_cast<size_t>(warp) * kLaneStages * 32 * 32;   // [stages][32 rows][32 B]
-  int* gh_w = reinterpret_cast<int*>(smem_raw + sizeof(int) * kLaneWarps * kTile + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * 32) + warp * kLaneStages * 32;
-  uint64_t* bars_w = reinterpret_cast<uint64_t*>(smem_raw + sizeof(int) * kLaneWarps * kTile + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * (32 + 4)) + warp * kLaneStages;   // one "stage full" barrier per (warp, stage)
+  const int kLaneWarps = blockDim.x >> 5, kLaneThreads = blockDim.x;
+  const int share = max(1, a.lane_share), ntiles = kLaneWarps / share;
+  int* tiles = reinterpret_cast<int*>(smem_raw);                                                 // [tiles][NB][32]
+  unsigned char* rows_w = smem_raw + sizeof(int) * ntiles * kTile + static_cast<size_t>(warp) * kLaneStages * 32 * 32;   // [stages][32 rows][32 B]
+  int* gh_w = reinterpret_cast<int*>(smem_raw + sizeof(int) * ntiles * kTile + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * 32) + warp * kLaneStages * 32;
+  uint64_t* bars_w = reinterpret_cast<uint64_t*>(smem_raw + sizeof(int) * ntiles * kTile + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * (32 + 4)) + warp * kLaneStages;   // one "stage full" barrier per (warp, stage)
   const int num_tasks = a.ctrl != nullptr ? a.ctrl->num_splits : a.num_tasks;
   if (num_tasks <= 0 || static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->total_blocks : a.total_blocks)) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
   const int ti = FindTask(a.tasks, num_tasks, blockIdx.x);
@@ -235,9 +248,14 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
   const int ng = min(32, a.num_groups - g0);
   const int byte0 = a.pack4 ? g0 / 2 : g0;                       // first byte of this 32-group part inside the row
   const int copy16 = a.pack4 ? 1 : min(2, (a.row_stride - g0) / 16);   // 16-byte pieces of this part inside the row
-  int* tile = tiles + warp * kTile;
-  for (int i = lane; i < kTile; i += 32) tile[i] = 0;
-  __syncwarp();
+  int* tile = tiles + (warp / share) * kTile;
+  if (share == 1) {
+    for (int i = lane; i < kTile; i += 32) tile[i] = 0;
+    __syncwarp();
+  } else {
+    for (int i = threadIdx.x; i < ntiles * kTile; i += kLaneThreads) tiles[i] = 0;
+    __syncthreads();   // no exit path lies between here and the merge barrier, so every thread of the block arrives
+  }
   // this warp's slice of the block's rows, in stages of 32 rows
   const int per_warp = ((nrows + kLaneWarps - 1) / kLaneWarps + 31) / 32 * 32;
   const int wbeg = min(nrows, warp * per_warp), wend = min(nrows, wbeg + per_warp);
@@ -271,9 +289,10 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
     __pipeline_commit();
   };
   const bool active = lane < ng;
+  const bool red = a.lane_red != 0 || share > 1;
   auto consume = [&](int slot, int cnt) {   // add the stage's rows into this warp's tile
-    if (a.pack4) ConsumeStage<true>(tile, rows_w + slot * 32 * 32, gh_w + slot * 32, cnt, lane, active);
-    else ConsumeStage<false>(tile, rows_w + slot * 32 * 32, gh_w + slot * 32, cnt, lane, active);
+    if (a.pack4) ConsumeStage<true>(tile, rows_w + slot * 32 * 32, gh_w + slot * 32, cnt, lane, active, red);
+    else ConsumeStage<false>(tile, rows_w + slot * 32 * 32, gh_w + slot * 32, cnt, lane, active, red);
   };
   // Root level of a 32-byte-row data set: a stage's rows are one contiguous kilobyte and its gradient words 128
   // contiguous bytes, so ONE lane hands both to the TMA engine as bulk copies and everybody waits on the stage's
@@ -340,7 +359,7 @@ __global__ void __launch_bounds__(kLaneThreads, 1) HistQuantLaneKernel(HistArgs 
     const int gbins = a.group_bin_count != nullptr ? a.group_bin_count[g] : (g + 1 < a.num_groups ? a.group_bin_start[g + 1] : a.num_total_bin) - gstart;
     if (b >= gbins) continue;
     long long sg = 0, sh = 0;
-    for (int w = 0; w < kLaneWarps; ++w) { const int v = tiles[w * kTile + cell]; const int h = v & 0xFFFF; sg += (v - h) >> 16; sh += h; }
+    for (int w = 0; w < ntiles; ++w) { const int v = tiles[w * kTile + cell]; const int h = v & 0xFFFF; sg += (v - h) >> 16; sh += h; }
     if (sg != 0 || sh != 0) FlushBinQuant(a.dest, task.slot, ti, a.num_total_bin, gstart + b, sg, sh);
   }
   const bool pushed = a.dest.num_ranks > 1 && PushTaskIfLast<true>(a, ti, task);
@@ -449,7 +468,34 @@ void LaunchCompactGather(const uint8_t* cols, long long col_stride, int n, const
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 
-int LaneRowsUnit() { return kLaneWarps * 32; }
+// Block shape of the lane construct, measured on B200 at 11M x 28 and 1.4M x 28 rows (ms per boosting round):
+//   load-add-store form: 20 warps with a tile each              2.82 / 0.986
+//   reduction form:      20 warps x 1 per tile 2.69 / 0.958;  32 x 2: 2.63 / 0.919;  32 x 4: 2.48 / 0.866;
+//                        32 x 8 (4 tiles): 2.46 / 0.858;  32 x 32 (1 tile): 2.46 / 0.859;  3 or 4 stages: 1-2 % slower
+// The environment overrides serve shape sweeps (FALCATA_LANE_WARPS: 4..32 warps per block, FALCATA_LANE_SHARE: warps per
+// tile, a divisor of the warps; FALCATA_LANE_STAGES: 2..4).
+// Many gradient levels leave a tile few rows before its 16-bit lanes could overflow (`sub_rows`): the block then keeps
+// a tile per warp so that it still takes a few thousand rows.
+static void LaneShape(bool red, int sub_rows, int* warps, int* share, int* stages = nullptr) {
+  static int w[3] = {0, 0, 0}, sh[3] = {0, 0, 0}, st = 2;
+  const bool wide = red && sub_rows >= 4096;
+  const int m = !red ? 0 : (wide ? 1 : 2);
+  if (w[m] == 0) {
+    int ww = wide ? 32 : 20, ss = wide ? 8 : 1;
+    if (const char* e = std::getenv("FALCATA_LANE_STAGES")) st = std::atoi(e);
+    if (st < 2 || st > 4) Log::Fatal("FALCATA_LANE_STAGES must be 2, 3 or 4");
+    if (const char* e = std::getenv("FALCATA_LANE_WARPS")) ww = std::atoi(e);
+    if (const char* e = std::getenv("FALCATA_LANE_SHARE")) ss = std::atoi(e);
+    if (!red) ss = 1;   // the load-add-store form needs a tile per warp
+    if (ww < 4 || ww > 32) Log::Fatal("FALCATA_LANE_WARPS must be within 4..32");
+    if (ss < 1 || ww % ss != 0) Log::Fatal("FALCATA_LANE_SHARE must divide the number of warps");
+    sh[m] = ss; w[m] = ww;
+  }
+  *warps = w[m]; *share = sh[m];
+  if (stages != nullptr) *stages = st;
+}
+int LaneRowsUnit(bool red, int sub_rows) { int w, s; LaneShape(red, sub_rows, &w, &s); return w * 32; }
+int LaneTiles(bool red, int sub_rows) { int w, s; LaneShape(red, sub_rows, &w, &s); return w / s; }
 
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
   if (a.total_blocks <= 0 || a.num_tasks <= 0) return;
@@ -458,19 +504,26 @@ void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
     Log::Fatal("tensor-core histogram: the shape is outside what the instance covers (root level, 32-byte rows, <= 32 groups of <= 64 bins, one rank)");
   }
   if (a.lane_mode != 0) {
-    const int cap = kLaneWarps * a.sub_rows;
+    int kLaneWarps, share, kLaneStages;
+    LaneShape(a.lane_red != 0, a.sub_rows, &kLaneWarps, &share, &kLaneStages);
+    const int ntiles = kLaneWarps / share, kLaneThreads = kLaneWarps * 32;
+    const int cap = ntiles * a.sub_rows;
     if (a.rows_per_block > cap) Log::Fatal("lane histogram: %d rows per block would overflow the 16-bit lanes (cap %d)", a.rows_per_block, cap);
     dim3 grid(a.total_blocks, (a.num_groups + 31) / 32);
-    const size_t sm = static_cast<size_t>(a.lane_bins) * 32 * 4 * kLaneWarps + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * (32 + 4) + static_cast<size_t>(kLaneWarps) * kLaneStages * 8;
-#define FB_LANE(NB)                                                                                                                \
+    const size_t sm = static_cast<size_t>(a.lane_bins) * 32 * 4 * ntiles + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * (32 + 4) + static_cast<size_t>(kLaneWarps) * kLaneStages * 8;
+    if (sm > 220 * 1024) Log::Fatal("lane histogram: %d warps with %d tiles of %d bins need %zu bytes of shared memory", kLaneWarps, ntiles, a.lane_bins, sm);
+    HistArgs b = a; b.lane_share = share;
+#define FB_LANE(NB, ST)                                                                                                            \
     {                                                                                                                              \
       static bool attr = false;                                                                                                    \
-      if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantLaneKernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr = true; } \
-      HistQuantLaneKernel<NB><<<grid, kLaneThreads, sm, s>>>(a);                                                                   \
+      if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantLaneKernel<NB, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr = true; } \
+      HistQuantLaneKernel<NB, ST><<<grid, kLaneThreads, sm, s>>>(b);                                                               \
     }
-    if (a.lane_bins == 16) FB_LANE(16)
-    else if (a.lane_bins == 64) FB_LANE(64)
+#define FB_LANE_ST(NB) { if (kLaneStages == 2) FB_LANE(NB, 2) else if (kLaneStages == 3) FB_LANE(NB, 3) else FB_LANE(NB, 4) }
+    if (a.lane_bins == 16) FB_LANE_ST(16)
+    else if (a.lane_bins == 64) FB_LANE_ST(64)
     else Log::Fatal("lane histogram: unsupported tile of %d bins", a.lane_bins);
+#undef FB_LANE_ST
 #undef FB_LANE
     FB_LAUNCHED(); FB_KERNEL_CHECK();
     return;

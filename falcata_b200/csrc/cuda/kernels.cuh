@@ -74,6 +74,8 @@ struct HistArgs {
   int rows_per_block; int sub_rows;
   int identity_root;        // 1: task rows are 0..count-1 (no index load)
   int num_total_bin;
+  int lane_share;           // lane kernel: warps per tile (set by the launcher)
+  int lane_red;             // lane kernel: shared-memory reduction adds instead of load-add-store with forwarding
   int lane_mode;            // 0: flat items + shared atomics; 1: lane-per-group warp-private tiles (no atomics); 2: lane-per-group, one shared tile + atomics;
                             // 3: one-hot tcgen05 MMA (root level, 32-byte rows; falls back to mode 1 outside its coverage)
   int tc_row_count;         // mode 3: rows of the task as the host knows them (extent of the TMA tensor maps)
@@ -83,7 +85,8 @@ struct HistArgs {
   const LevelCtrl* ctrl;    // non-null: num_tasks / total_blocks come from the device controller
 };
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s);
-int LaneRowsUnit();   // rows per stage of a lane-construct block (warps x 32): rows_per_block is chosen in these units
+int LaneTiles(bool red, int sub_rows);      // tiles of a lane-construct block: each takes at most `sub_rows` rows before its 16-bit lanes could overflow
+int LaneRowsUnit(bool red, int sub_rows);   // rows per stage of a lane-construct block (warps x 32): rows_per_block is chosen in these units
 // K9: per-tree compact view. out[row][j] = cols[groups[j]][row] for the listed (sampled) feature groups: a dense
 // row-major matrix with only the columns this tree can split on, read from the column-major copy (coalesced
 // along rows) and written in 32-byte row pieces through a shared-memory transpose tile.

@@ -61,7 +61,7 @@ int FB_OpHistogram(const uint8_t* rows, int row_stride, int num_groups, const vo
   const int qb = std::max(2, quant_bins);
   a.sub_rows = quant ? std::max(1, std::min(65535 / qb, 32767 / std::max(1, qb / 2))) : (1 << 30);
   a.identity_root = idx == nullptr ? 1 : 0;
-  a.num_total_bin = total; a.lane_mode = quant ? lane_mode : 0;
+  a.num_total_bin = total; a.lane_mode = quant ? lane_mode : 0; a.lane_red = 1;
   a.bulk_root = getenv("FALCATA_NO_BULK_ROOT") == nullptr ? 1 : 0;   // the kernel itself decides where the bulk-copy pipeline applies
   int mgb = 0; for (int v : gbins) mgb = std::max(mgb, v);
   a.lane_bins = mgb <= 16 ? 16 : 64;
@@ -74,7 +74,7 @@ int FB_OpHistogram(const uint8_t* rows, int row_stride, int num_groups, const vo
     t.num_blocks = (count + rows_per_block - 1) / rows_per_block; a.total_blocks = t.num_blocks;
     d_task.Upload(&t, 1, s);
   }
-  if (a.lane_mode == 1 && rows_per_block > 8 * a.sub_rows) { a.rows_per_block = rows_per_block = 8 * a.sub_rows; }
+  if (a.lane_mode == 1 && rows_per_block > std::min(8, LaneTiles(true, a.sub_rows)) * a.sub_rows) { a.rows_per_block = rows_per_block = std::min(8, LaneTiles(true, a.sub_rows)) * a.sub_rows; }
   if (a.lane_mode == 2 && rows_per_block > a.sub_rows) { a.rows_per_block = rows_per_block = a.sub_rows; }
   if (a.lane_mode == 1 || a.lane_mode == 2) {
     t.num_blocks = (count + rows_per_block - 1) / rows_per_block; a.total_blocks = t.num_blocks;

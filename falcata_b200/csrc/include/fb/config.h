@@ -200,6 +200,7 @@ struct Plan {
   bool gh_in_row = false;        // packed gradient word stored next to the row's bins (measured slower on B200: the separate 4 B/row array stays L2-resident)
   bool hist_lane = true;         // lane-per-group construct with bank-interleaved warp-private tiles (groups with <= 64 bins)
   bool hist_lane_atomic = false; // lane-per-group construct with one shared tile per block and shared atomics
+  bool hist_lane_red = true;     // lane construct adds with shared-memory reduction instructions into tiles shared by 8 warps (off: load-add-store with forwarding, a tile per warp)
   bool col_major_part = true;    // partition reads the split column from a column-major copy of the bins
   bool bulk_root = true;         // root level of the lane construct staged by bulk asynchronous copies (TMA engine, mbarrier completion)
   static Plan FromString(const std::string& s);

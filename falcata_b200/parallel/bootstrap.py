@@ -55,14 +55,16 @@ def _bernoulli_rows(t: Any, n: int, offset: int, seed: int, p: float) -> Any:
     return out[: cnt.value].to(t.device).long()
 
 
-def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total: int = 0, replicated: bool = False) -> Tuple[np.ndarray, int]:
+def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total: int = 0, replicated: bool = False,
+                      after_draw: Any = None) -> Tuple[np.ndarray, int]:
     """Rows used to find bin boundaries.
 
     A global row is sampled iff a Philox number keyed on (seed, global row id) is below ``sample_cnt / total``. The choice depends only on the GLOBAL
     row id, so the sample - and with it every bin boundary - is the same however the rows are sharded
     over ranks. Each rank contributes the sampled rows of its shard; the shards are concatenated in
     rank order. ``replicated``: every rank holds ALL rows (feature-parallel training), so the local sample
-    is already the global one and nothing is exchanged. Returns (sample [ns, ncol] in the matrix's own element
+    is already the global one and nothing is exchanged. ``after_draw``: called once the row draw (which may run on the
+    device) is done and only host work and collectives remain. Returns (sample [ns, ncol] in the matrix's own element
     type - float16/32/64, int8/16/32, uint8 - so nothing is widened on the way to the host; total rows)."""
     import torch
 
@@ -82,6 +84,8 @@ def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total
             offset = int(sum(offs[:rank]))
     p = min(1.0, sample_cnt / max(1, total))
     idx = _bernoulli_rows(t, n, offset, seed, p)
+    if after_draw is not None:
+        after_draw()
     keep = t.dtype in (torch.float16, torch.float32, torch.float64, torch.int8, torch.int16, torch.int32, torch.uint8)
     sdt = t.dtype if keep else torch.float64
     picked = t[idx].to(sdt)

@@ -51,7 +51,7 @@ def test_quant_run_twice_identical_and_device_ingest():
     assert model_body(c) == model_body(d)
 
 
-@pytest.mark.parametrize("flip", ["device_controller:off", "fused_tail:off", "fused_scan:off", "fused_tail:off,fused_scan:off", "hist_lane:off", "col_major_part:off", "gh_in_row:on", "bulk_root:off", "hist_tc:on"])
+@pytest.mark.parametrize("flip", ["device_controller:off", "fused_tail:off", "fused_scan:off", "fused_tail:off,fused_scan:off", "hist_lane:off", "col_major_part:off", "gh_in_row:on", "bulk_root:off", "hist_tc:on", "hist_lane_red:off"])
 def test_plan_flips_keep_quantized_model_identical(flip):
     # performance-only plan keys must not change a single digit of a quantized model
     X, y = make_binary(30000, 20)
