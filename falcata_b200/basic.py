@@ -1127,6 +1127,25 @@ class Booster:
             t = data if _is_torch_tensor(data) else torch.as_tensor(data, device="cuda")
             host = self.predict(t.detach().cpu().numpy(), start_iteration=start_iteration, num_iteration=num_iteration, raw_score=raw_score)
             return torch.as_tensor(np.asarray(host, dtype=np.float32), device=t.device)
+        if _is_cuda_array(data) and ptype == 2 and cuda_available() and not self._has_linear_trees():
+            # leaf indices on the device: int32 [rows, trees]; forests the kernel does not cover go through the host
+            import torch
+
+            t = data if _is_torch_tensor(data) else torch.as_tensor(data, device="cuda")
+            if t.dtype not in (torch.float32, torch.float64, torch.float16):
+                t = t.float()
+            t = t.contiguous()
+            nrow, ncol = t.shape
+            per_row = ctypes.c_int64(0)
+            _safe_call(lib.FB_BoosterCalcNumPredict(self._handle, 1, 2, start_iteration, num_iteration, ctypes.byref(per_row)))
+            out = torch.zeros((nrow, max(1, per_row.value)), dtype=torch.int32, device=t.device)
+            code = {torch.float32: 0, torch.float64: 1, torch.float16: 6}[t.dtype]
+            rc = lib.FB_BoosterPredictForDeviceMat(self._handle, ctypes.c_void_p(t.data_ptr()), code, ctypes.c_int32(nrow), ctypes.c_int32(ncol), 1,
+                                                   2, start_iteration, num_iteration, ctypes.c_void_p(out.data_ptr()))
+            if rc == 0:
+                return out
+            host = self.predict(t.detach().cpu().numpy(), start_iteration=start_iteration, num_iteration=num_iteration, pred_leaf=True)
+            return torch.as_tensor(np.asarray(host, dtype=np.int32), device=t.device)
         if _is_cuda_array(data) and ptype in (0, 1) and cuda_available():
             import torch
 

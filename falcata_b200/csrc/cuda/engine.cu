@@ -111,9 +111,12 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     const int qb = std::max(2, cfg.quant_bins_resolved);
     sub_rows_ = quant_ ? std::max(1, std::min(65535 / qb, 32767 / std::max(1, qb / 2))) : (1 << 30);
     lane_mode_ = 0; lane_bins_ = 64;
-    if (quant_ && (plan_.hist_lane || plan_.hist_lane_atomic) && train->max_group_bin <= 64) {
+    // lane construct: 16-, 64- or 256-bin tiles; beyond 64 bins (and for fp32 gradients) only in the reduction form,
+    // whose tiles are shared by several warps
+    lane_red_ = quant_ ? plan_.hist_lane_red : plan_.hist_float_red;
+    if ((plan_.hist_lane || plan_.hist_lane_atomic) && train->max_group_bin <= 256 && (!quant_ || train->max_group_bin <= 64 || lane_red_)) {
       lane_mode_ = plan_.hist_lane_atomic ? 2 : 1;
-      lane_bins_ = train->max_group_bin <= 16 ? 16 : 64;
+      lane_bins_ = train->max_group_bin <= 16 ? 16 : (train->max_group_bin <= 64 ? 64 : 256);
     }
     if (plan_.col_major_part) EnsureColumnMajor(dd_, stream_);
   }
@@ -271,10 +274,18 @@ int CudaEngine::ChooseRowsPerBlock(long long total_rows) const {
     // the lane kernel runs one block per SM with a fixed cost per block (tile clear, pipeline fill, merge of
     // the warps' tiles): aim at about four waves (measured best at 11M and 1.4M rows), in units of 384 rows,
     // within what the 16-bit lanes of the packed cells allow per warp tile
-    const int unit = LaneRowsUnit(plan_.hist_lane_red, sub_rows_);   // rows of one stage across the block's warps
+    const int unit = LaneRowsUnit(lane_red_, sub_rows_, lane_bins_, !quant_);   // rows of one stage across the block's warps
     long long rpb = (total_rows / (4LL * num_sms_) + unit - 1) / unit * unit;
+    if (!quant_) {
+      // fp32: every block clears and merges whole tiles of float pairs and nothing can overflow, so fewer, longer blocks:
+      // about two waves over all 32-group parts
+      const long long parts = (train_->num_groups + 31) / 32;
+      const long long row_blocks = std::max<long long>(1, 2LL * num_sms_ / parts);
+      rpb = (total_rows / row_blocks + unit - 1) / unit * unit;
+      return static_cast<int>(std::max<long long>(rpb, 8LL * unit));
+    }
     rpb = std::min<long long>(std::max<long long>(rpb, 3LL * unit), 13LL * unit);
-    rpb = std::min<long long>(rpb, static_cast<long long>(LaneTiles(plan_.hist_lane_red, sub_rows_)) * (sub_rows_ / 32 * 32));
+    rpb = std::min<long long>(rpb, static_cast<long long>(LaneTiles(lane_red_, sub_rows_, lane_bins_, !quant_)) * (sub_rows_ / 32 * 32));
     return static_cast<int>(rpb);
   }
   long long target = total_rows / (static_cast<long long>(num_sms_) * 6) + 1;

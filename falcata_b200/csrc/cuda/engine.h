@@ -118,6 +118,7 @@ class CudaEngine : public DeviceEngine {
   // exact leaf-wise growth (grow_policy=leaf): the device grows up to grow_leaves_ leaves, the host keeps the best num_leaves
   bool leafwise_ = false; int grow_leaves_ = 0;
   bool tc_fallback_logged_ = false;
+  bool lane_red_ = true;   // reduction form of the lane construct (integer: plan hist_lane_red, fp32: plan hist_float_red)
   DevBuf<double> eval_key_;
   void FinalizeLeafwise(const LevelCtrl& hc, Tree* tree);
   // per-node feature masks (feature_fraction_bynode, interaction constraints)

@@ -185,7 +185,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     for (int r = 0; r < world_; ++r) { ha.dest.pool[r] = fabric_->Ptr<char>(r, off_pool_); ha.dest.slot_stride[r] = slot_strides_[r]; ha.dest.peer_stage[r] = fabric_->Ptr<char>(r, off_stage_); }
     ha.dest.stage_local = stage_local_.get(); ha.dest.task_done = task_done_.get(); ha.dest.stage_cap = NL;
   } else { ha.dest.pool[0] = pool_base_; ha.dest.slot_stride[0] = voting_ ? train_->num_total_bin : slot_stride_; }
-  ha.num_total_bin = train_->num_total_bin; ha.lane_mode = lane_mode_; ha.lane_bins = lane_bins_; ha.lane_red = plan_.hist_lane_red ? 1 : 0;
+  ha.num_total_bin = train_->num_total_bin; ha.lane_mode = lane_mode_; ha.lane_bins = lane_bins_; ha.lane_red = lane_red_ ? 1 : 0;
   ha.bulk_root = plan_.bulk_root ? 1 : 0; ha.status = hist_status_.get();
   // K9: when this tree samples few columns, construct from a dense per-tree copy of just those groups
   // (feature-parallel: just the sampled groups this rank owns)

@@ -34,14 +34,13 @@ __device__ inline int FindTask(const HistTask* tasks, int num_tasks, int block) 
 
 // One rank: the bin goes straight into the pool slot. Several ranks: into the LOCAL staging
 // histogram of the task (L2 atomics); PushTaskIfLast ships the finished task to the owners.
-__device__ inline void FlushBinQuant(const HistDest& d, int slot, int task_index, int num_total_bin, int global_bin, long long g, long long h) {
+// `single`: this block is the only one that adds to the task's cells (which were cleared beforehand): a plain store.
+__device__ inline void FlushBinQuant(const HistDest& d, int slot, int task_index, int num_total_bin, int global_bin, long long g, long long h, bool single = false) {
   const hist_q_t v = HistQPack(g, h);
   if (d.owner_only && d.bin_owner[global_bin] != d.rank) return;
-  if (d.num_ranks > 1) {
-    atomicAdd(static_cast<hist_q_t*>(d.stage_local) + static_cast<long long>(task_index) * num_total_bin + global_bin, v);
-  } else {
-    atomicAdd(static_cast<hist_q_t*>(d.pool[0]) + static_cast<long long>(slot) * d.slot_stride[0] + d.bin_local[global_bin], v);
-  }
+  hist_q_t* p = d.num_ranks > 1 ? static_cast<hist_q_t*>(d.stage_local) + static_cast<long long>(task_index) * num_total_bin + global_bin
+                                : static_cast<hist_q_t*>(d.pool[0]) + static_cast<long long>(slot) * d.slot_stride[0] + d.bin_local[global_bin];
+  if (single) *p = v; else atomicAdd(p, v);
 }
 
 // Reduce-scatter step, fused into the construct kernel. Called by every block that worked on task
@@ -220,20 +219,67 @@ __device__ __forceinline__ void ConsumeStage(int* __restrict__ tile, const unsig
   }
 }
 
+// fp32 form of ConsumeStage: the tile holds a (gradient, hessian) float pair per cell, [NB][32] pairs; lane l adds the
+// row's pair into column l. `red`: shared-memory reduction adds (tiles shared by several warps); otherwise the warp owns
+// the tile and the update is a load-add-store, eight rows at a time with repeated cells forwarded in registers - the
+// sums are then those of the rows in order, whatever the timing.
+template <int NB, bool P4>
+__device__ __forceinline__ void ConsumeStageFloat(float2* __restrict__ tile, const unsigned char* __restrict__ stage_rows, const float2* __restrict__ sg, int cnt, int lane, bool active, bool red) {
+  const unsigned char* sr = stage_rows + (P4 ? (lane >> 1) : lane);
+  const int nshift = (lane & 1) * 4;
+  auto bin_of = [&](int j) -> int { const int b = sr[j * 32]; return P4 ? ((b >> nshift) & 15) : b; };
+  float2* col = tile + lane;
+  if (red) {
+    for (int j = 0; j < cnt; ++j) {
+      const float2 g = sg[j]; float* c = reinterpret_cast<float*>(col + bin_of(j) * 32);
+      if (active) { atomicAdd(c, g.x); atomicAdd(c + 1, g.y); }
+    }
+  } else if (cnt == 32) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      int ad[8]; float2 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ad[k] = bin_of(j + k) * 32;
+      if (active) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = col[ad[k]];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          // the latest earlier row of this group of eight that hit the same cell holds the cell's running sum
+#pragma unroll
+          for (int m = 0; m < k; ++m) if (ad[m] == ad[k]) v[k] = v[m];
+          const float2 g = sg[j + k];
+          v[k].x += g.x; v[k].y += g.y;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) col[ad[k]] = v[k];   // program order: the last store to a cell holds its full sum
+      }
+    }
+  } else {
+    for (int j = 0; j < cnt; ++j) {
+      const float2 g = sg[j]; const int a0 = bin_of(j) * 32;
+      if (active) { float2 v = col[a0]; v.x += g.x; v.y += g.y; col[a0] = v; }
+    }
+  }
+}
+
 constexpr int kLaneMaxThreads = 1024;
 // Block shape: `lane_warps` warps (the block size), every `lane_share` consecutive warps add into one tile. Sharing
 // a tile needs the reduction form of the update (`lane_red`); with one warp per tile both forms are valid.
-template <int NB, int kLaneStages>
-__global__ void __launch_bounds__(kLaneMaxThreads, 1) HistQuantLaneKernel(HistArgs a) {
+// FLT: fp32 gradients (a float2 per row) added into (gradient, hessian) float pairs, [NB][32] pairs per tile; otherwise
+// packed int16|uint16 gradient words added into [NB][32] ints.
+template <int NB, int kLaneStages, bool FLT>
+__global__ void __launch_bounds__(FLT ? kLaneMaxThreads / 2 : kLaneMaxThreads, 1) HistQuantLaneKernel(HistArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  constexpr int kTile = NB * 32;
+  constexpr int kTile = NB * 32 * (FLT ? 2 : 1);   // 4-byte cells of a tile
+  constexpr int kGhWords = FLT ? 2 : 1;            // 4-byte words of a row's gradient record
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kLaneWarps = blockDim.x >> 5, kLaneThreads = blockDim.x;
   const int share = max(1, a.lane_share), ntiles = kLaneWarps / share;
-  int* tiles = reinterpret_cast<int*>(smem_raw);                                                 // [tiles][NB][32]
+  int* tiles = reinterpret_cast<int*>(smem_raw);                                                 // [tiles][planes][NB][32]
   unsigned char* rows_w = smem_raw + sizeof(int) * ntiles * kTile + static_cast<size_t>(warp) * kLaneStages * 32 * 32;   // [stages][32 rows][32 B]
-  int* gh_w = reinterpret_cast<int*>(smem_raw + sizeof(int) * ntiles * kTile + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * 32) + warp * kLaneStages * 32;
-  uint64_t* bars_w = reinterpret_cast<uint64_t*>(smem_raw + sizeof(int) * ntiles * kTile + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * (32 + 4)) + warp * kLaneStages;   // one "stage full" barrier per (warp, stage)
+  int* gh_w = reinterpret_cast<int*>(smem_raw + sizeof(int) * ntiles * kTile + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * 32) + warp * kLaneStages * 32 * kGhWords;
+  uint64_t* bars_w = reinterpret_cast<uint64_t*>(smem_raw + sizeof(int) * ntiles * kTile + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * (32 + 4 * kGhWords)) + warp * kLaneStages;   // one "stage full" barrier per (warp, stage)
   const int num_tasks = a.ctrl != nullptr ? a.ctrl->num_splits : a.num_tasks;
   if (num_tasks <= 0 || static_cast<int>(blockIdx.x) >= (a.ctrl != nullptr ? a.ctrl->total_blocks : a.total_blocks)) { if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y); return; }
   const int ti = FindTask(a.tasks, num_tasks, blockIdx.x);
@@ -284,20 +330,25 @@ __global__ void __launch_bounds__(kLaneMaxThreads, 1) HistQuantLaneKernel(HistAr
         __pipeline_memcpy_async(dst, src, 16);
         if (copy16 > 1) __pipeline_memcpy_async(dst + 16, src + 16, 16);
       }
-      __pipeline_memcpy_async(gh_w + slot * 32 + lane, a.gh_base + static_cast<size_t>(row) * a.gh_stride, 4);
+      __pipeline_memcpy_async(gh_w + (slot * 32 + lane) * kGhWords, a.gh_base + static_cast<size_t>(row) * a.gh_stride, 4 * kGhWords);
     }
     __pipeline_commit();
   };
   const bool active = lane < ng;
   const bool red = a.lane_red != 0 || share > 1;
   auto consume = [&](int slot, int cnt) {   // add the stage's rows into this warp's tile
-    if (a.pack4) ConsumeStage<true>(tile, rows_w + slot * 32 * 32, gh_w + slot * 32, cnt, lane, active, red);
-    else ConsumeStage<false>(tile, rows_w + slot * 32 * 32, gh_w + slot * 32, cnt, lane, active, red);
+    if constexpr (FLT) {
+      if (a.pack4) ConsumeStageFloat<NB, true>(reinterpret_cast<float2*>(tile), rows_w + slot * 32 * 32, reinterpret_cast<const float2*>(gh_w + slot * 32 * kGhWords), cnt, lane, active, red);
+      else ConsumeStageFloat<NB, false>(reinterpret_cast<float2*>(tile), rows_w + slot * 32 * 32, reinterpret_cast<const float2*>(gh_w + slot * 32 * kGhWords), cnt, lane, active, red);
+    } else {
+      if (a.pack4) ConsumeStage<true>(tile, rows_w + slot * 32 * 32, gh_w + slot * 32, cnt, lane, active, red);
+      else ConsumeStage<false>(tile, rows_w + slot * 32 * 32, gh_w + slot * 32, cnt, lane, active, red);
+    }
   };
   // Root level of a 32-byte-row data set: a stage's rows are one contiguous kilobyte and its gradient words 128
   // contiguous bytes, so ONE lane hands both to the TMA engine as bulk copies and everybody waits on the stage's
   // mbarrier - no per-lane copy instructions, no address arithmetic in the other 31 lanes.
-  const bool bulk = a.bulk_root != 0 && block_copy && a.gh_stride == 4 && (ident0 & 31) == 0;
+  const bool bulk = a.bulk_root != 0 && block_copy && a.gh_stride == 4 * kGhWords && (ident0 & 31) == 0;
   if (bulk) {
     const int nfull = (wend - wbeg) / 32, tail = (wend - wbeg) - nfull * 32;
     if (lane == 0) { for (int st = 0; st < kLaneStages; ++st) MbarInit(bars_w + st, 1); asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -305,9 +356,9 @@ __global__ void __launch_bounds__(kLaneMaxThreads, 1) HistQuantLaneKernel(HistAr
     auto produce = [&](int s) {
       if (s < nfull && lane == 0) {
         const int slot = s % kLaneStages;
-        MbarExpectTx(bars_w + slot, 32 * 32 + 32 * 4);
+        MbarExpectTx(bars_w + slot, 32 * 32 + 32 * 4 * kGhWords);
         BulkCopyG2S(rows_w + slot * 32 * 32, a.rows + static_cast<size_t>(ident0 + static_cast<long long>(s) * 32) * 32, 32 * 32, bars_w + slot);
-        BulkCopyG2S(gh_w + slot * 32, a.gh_base + static_cast<size_t>(ident0 + static_cast<long long>(s) * 32) * 4, 32 * 4, bars_w + slot);
+        BulkCopyG2S(gh_w + slot * 32 * kGhWords, a.gh_base + static_cast<size_t>(ident0 + static_cast<long long>(s) * 32) * 4 * kGhWords, 32 * 4 * kGhWords, bars_w + slot);
       }
     };
     for (int s = 0; s < kLaneStages - 1; ++s) produce(s);
@@ -331,7 +382,7 @@ __global__ void __launch_bounds__(kLaneMaxThreads, 1) HistQuantLaneKernel(HistAr
         const uint4* src = reinterpret_cast<const uint4*>(a.rows + row * 32);
         uint4* dst = reinterpret_cast<uint4*>(rows_w + lane * 32);
         dst[0] = src[0]; dst[1] = src[1];
-        gh_w[lane] = *reinterpret_cast<const int*>(a.gh_base + row * 4);
+        for (int k = 0; k < kGhWords; ++k) gh_w[lane * kGhWords + k] = reinterpret_cast<const int*>(a.gh_base + row * 4 * kGhWords)[k];
       }
       __syncwarp();
       consume(0, tail);
@@ -351,18 +402,35 @@ __global__ void __launch_bounds__(kLaneMaxThreads, 1) HistQuantLaneKernel(HistAr
   }
   }
   __syncthreads();
-  for (int cell = threadIdx.x; cell < kTile; cell += kLaneThreads) {
+  const bool single_block = row_blocks == 1;   // blocks beyond the task's rows left above: nobody else adds to these cells
+  for (int cell = threadIdx.x; cell < NB * 32; cell += kLaneThreads) {
     const int l = cell & 31, b = cell >> 5;
     if (l >= ng) continue;
     const int g = g0 + l;
     const int gstart = a.group_bin_start[g];
     const int gbins = a.group_bin_count != nullptr ? a.group_bin_count[g] : (g + 1 < a.num_groups ? a.group_bin_start[g + 1] : a.num_total_bin) - gstart;
     if (b >= gbins) continue;
-    long long sg = 0, sh = 0;
-    for (int w = 0; w < ntiles; ++w) { const int v = tiles[w * kTile + cell]; const int h = v & 0xFFFF; sg += (v - h) >> 16; sh += h; }
-    if (sg != 0 || sh != 0) FlushBinQuant(a.dest, task.slot, ti, a.num_total_bin, gstart + b, sg, sh);
+    if constexpr (FLT) {
+      // the tiles of a block are summed in tile order, in double; the blocks of a task meet in double-precision global
+      // adds, and a task with a single block stores (its cells were cleared with the pool)
+      double sg = 0.0, sh = 0.0;
+      const float2* ft = reinterpret_cast<const float2*>(tiles);
+      for (int w = 0; w < ntiles; ++w) { const float2 v = ft[w * (kTile / 2) + cell]; sg += static_cast<double>(v.x); sh += static_cast<double>(v.y); }
+      if (sg != 0.0 || sh != 0.0) {
+        const HistDest& d = a.dest;
+        const int gb = gstart + b;
+        double* p = d.num_ranks > 1 ? static_cast<double*>(d.stage_local) + 2 * (static_cast<long long>(ti) * a.num_total_bin + gb)
+                                    : static_cast<double*>(d.pool[0]) + 2 * (static_cast<long long>(task.slot) * d.slot_stride[0] + d.bin_local[gb]);
+        if (single_block) *reinterpret_cast<double2*>(p) = make_double2(sg, sh);
+        else { atomicAdd(p, sg); atomicAdd(p + 1, sh); }
+      }
+    } else {
+      long long sg = 0, sh = 0;
+      for (int w = 0; w < ntiles; ++w) { const int v = tiles[w * kTile + cell]; const int h = v & 0xFFFF; sg += (v - h) >> 16; sh += h; }
+      if (sg != 0 || sh != 0) FlushBinQuant(a.dest, task.slot, ti, a.num_total_bin, gstart + b, sg, sh, single_block);
+    }
   }
-  const bool pushed = a.dest.num_ranks > 1 && PushTaskIfLast<true>(a, ti, task);
+  const bool pushed = a.dest.num_ranks > 1 && PushTaskIfLast<!FLT>(a, ti, task);
   if (a.sig.world > 1) FabricSignalDone(a.sig, gridDim.x * gridDim.y, pushed);
 }
 
@@ -468,34 +536,79 @@ void LaunchCompactGather(const uint8_t* cols, long long col_stride, int n, const
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 
-// Block shape of the lane construct, measured on B200 at 11M x 28 and 1.4M x 28 rows (ms per boosting round):
+// Block shape of the lane construct, measured on B200 at 11M x 28 and 1.4M x 28 rows (ms per boosting round, 64-bin
+// integer tiles):
 //   load-add-store form: 20 warps with a tile each              2.82 / 0.986
 //   reduction form:      20 warps x 1 per tile 2.69 / 0.958;  32 x 2: 2.63 / 0.919;  32 x 4: 2.48 / 0.866;
 //                        32 x 8 (4 tiles): 2.46 / 0.858;  32 x 32 (1 tile): 2.46 / 0.859;  3 or 4 stages: 1-2 % slower
+// So: 32 warps on up to 4 tiles in the reduction form (fewer when the tiles are large: 256 bins, float planes), 20 warps
+// otherwise. Many gradient levels leave a tile few rows before its 16-bit lanes could overflow (`sub_rows`): the block
+// then keeps as many tiles as fit so that it still takes a few thousand rows.
 // The environment overrides serve shape sweeps (FALCATA_LANE_WARPS: 4..32 warps per block, FALCATA_LANE_SHARE: warps per
 // tile, a divisor of the warps; FALCATA_LANE_STAGES: 2..4).
-// Many gradient levels leave a tile few rows before its 16-bit lanes could overflow (`sub_rows`): the block then keeps
-// a tile per warp so that it still takes a few thousand rows.
-static void LaneShape(bool red, int sub_rows, int* warps, int* share, int* stages = nullptr) {
-  static int w[3] = {0, 0, 0}, sh[3] = {0, 0, 0}, st = 2;
-  const bool wide = red && sub_rows >= 4096;
-  const int m = !red ? 0 : (wide ? 1 : 2);
-  if (w[m] == 0) {
-    int ww = wide ? 32 : 20, ss = wide ? 8 : 1;
-    if (const char* e = std::getenv("FALCATA_LANE_STAGES")) st = std::atoi(e);
-    if (st < 2 || st > 4) Log::Fatal("FALCATA_LANE_STAGES must be 2, 3 or 4");
-    if (const char* e = std::getenv("FALCATA_LANE_WARPS")) ww = std::atoi(e);
-    if (const char* e = std::getenv("FALCATA_LANE_SHARE")) ss = std::atoi(e);
-    if (!red) ss = 1;   // the load-add-store form needs a tile per warp
-    if (ww < 4 || ww > 32) Log::Fatal("FALCATA_LANE_WARPS must be within 4..32");
-    if (ss < 1 || ww % ss != 0) Log::Fatal("FALCATA_LANE_SHARE must divide the number of warps");
-    sh[m] = ss; w[m] = ww;
+struct LaneGeometry { int warps, share, stages; size_t smem; };
+static LaneGeometry LaneShape(bool red, int sub_rows, int nb, bool flt) {
+  LaneGeometry g;
+  g.stages = 2;
+  if (const char* e = std::getenv("FALCATA_LANE_STAGES")) g.stages = std::atoi(e);
+  if (g.stages < 2 || g.stages > 4) Log::Fatal("FALCATA_LANE_STAGES must be 2, 3 or 4");
+  const size_t tile_bytes = static_cast<size_t>(nb) * 32 * 4 * (flt ? 2 : 1);
+  const size_t budget = 220 * 1024;
+  if (flt && !red) {
+    // fp32, load-add-store: a tile per warp, as many warps as fit, and deeper staging since few warps are in flight
+    if (std::getenv("FALCATA_LANE_STAGES") == nullptr) g.stages = 4;
+    const size_t per_warp = tile_bytes + static_cast<size_t>(g.stages) * (32 * (32 + 8) + 8);
+    g.warps = static_cast<int>(std::min<size_t>(16, budget / per_warp));
+    if (const char* e = std::getenv("FALCATA_LANE_WARPS")) g.warps = std::min(g.warps, std::max(1, std::atoi(e)));
+    if (g.warps < 1) Log::Fatal("lane histogram: a %d-bin fp32 tile does not fit in shared memory", nb);
+    g.share = 1;
+    g.smem = per_warp * g.warps;
+    return g;
   }
-  *warps = w[m]; *share = sh[m];
-  if (stages != nullptr) *stages = st;
+  const bool wide = red && sub_rows >= 4096;
+  g.warps = red ? (flt ? 16 : 32) : 20;   // fp32 blocks have at most 16 warps (the kernel is compiled for 128 registers per thread)
+  if (const char* e = std::getenv("FALCATA_LANE_WARPS")) g.warps = std::atoi(e);
+  if (g.warps < 4 || g.warps > (flt ? 16 : 32)) Log::Fatal("FALCATA_LANE_WARPS must be within 4..32 (4..16 for fp32)");
+  const size_t stage_bytes = static_cast<size_t>(g.warps) * g.stages * (32 * (32 + (flt ? 8 : 4)) + 8);
+  if (stage_bytes + tile_bytes > budget) Log::Fatal("lane histogram: a %d-bin tile does not fit beside the stages of %d warps", nb, g.warps);
+  const int fit = static_cast<int>((budget - stage_bytes) / tile_bytes);
+  int tiles = 1;
+  if (!red) tiles = g.warps;   // the load-add-store form needs a tile per warp
+  else for (int t = 1; t <= g.warps; ++t) if (g.warps % t == 0 && t <= fit && (!wide || t <= 4)) tiles = t;
+  if (const char* e = std::getenv("FALCATA_LANE_SHARE")) { const int ss = std::atoi(e); if (red && ss >= 1 && g.warps % ss == 0) tiles = g.warps / ss; }
+  if (tiles > fit) Log::Fatal("lane histogram: %d tiles of %d bins do not fit beside the stages of %d warps", tiles, nb, g.warps);
+  g.share = g.warps / tiles;
+  g.smem = stage_bytes + tile_bytes * tiles;
+  return g;
 }
-int LaneRowsUnit(bool red, int sub_rows) { int w, s; LaneShape(red, sub_rows, &w, &s); return w * 32; }
-int LaneTiles(bool red, int sub_rows) { int w, s; LaneShape(red, sub_rows, &w, &s); return w / s; }
+int LaneRowsUnit(bool red, int sub_rows, int nb, bool flt) { return LaneShape(red, sub_rows, nb, flt).warps * 32; }
+int LaneTiles(bool red, int sub_rows, int nb, bool flt) { const LaneGeometry g = LaneShape(red, sub_rows, nb, flt); return g.warps / g.share; }
+
+template <bool FLT>
+static void LaunchLane(const HistArgs& a, cudaStream_t s) {
+  const LaneGeometry g = LaneShape(a.lane_red != 0, a.sub_rows, a.lane_bins, FLT);
+  const int ntiles = g.warps / g.share;
+  if (!FLT) {
+    const long long cap = static_cast<long long>(ntiles) * a.sub_rows;
+    if (a.rows_per_block > cap) Log::Fatal("lane histogram: %d rows per block would overflow the 16-bit lanes (cap %lld)", a.rows_per_block, cap);
+  }
+  dim3 grid(a.total_blocks, (a.num_groups + 31) / 32);
+  HistArgs b = a; b.lane_share = g.share;
+#define FB_LANE(NB, ST)                                                                                                            \
+  {                                                                                                                                \
+    static bool attr = false;                                                                                                      \
+    if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantLaneKernel<NB, ST, FLT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr = true; } \
+    HistQuantLaneKernel<NB, ST, FLT><<<grid, g.warps * 32, g.smem, s>>>(b);                                                        \
+  }
+#define FB_LANE_ST(NB) { if (g.stages == 2) FB_LANE(NB, 2) else if (g.stages == 3) FB_LANE(NB, 3) else FB_LANE(NB, 4) }
+  if (a.lane_bins == 16) FB_LANE_ST(16)
+  else if (a.lane_bins == 64) FB_LANE_ST(64)
+  else if (a.lane_bins == 256) FB_LANE_ST(256)
+  else Log::Fatal("lane histogram: unsupported tile of %d bins", a.lane_bins);
+#undef FB_LANE_ST
+#undef FB_LANE
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
 
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
   if (a.total_blocks <= 0 || a.num_tasks <= 0) return;
@@ -503,31 +616,7 @@ void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
     if (LaunchHistConstructQuantTC(a, s)) return;
     Log::Fatal("tensor-core histogram: the shape is outside what the instance covers (root level, 32-byte rows, <= 32 groups of <= 64 bins, one rank)");
   }
-  if (a.lane_mode != 0) {
-    int kLaneWarps, share, kLaneStages;
-    LaneShape(a.lane_red != 0, a.sub_rows, &kLaneWarps, &share, &kLaneStages);
-    const int ntiles = kLaneWarps / share, kLaneThreads = kLaneWarps * 32;
-    const int cap = ntiles * a.sub_rows;
-    if (a.rows_per_block > cap) Log::Fatal("lane histogram: %d rows per block would overflow the 16-bit lanes (cap %d)", a.rows_per_block, cap);
-    dim3 grid(a.total_blocks, (a.num_groups + 31) / 32);
-    const size_t sm = static_cast<size_t>(a.lane_bins) * 32 * 4 * ntiles + static_cast<size_t>(kLaneWarps) * kLaneStages * 32 * (32 + 4) + static_cast<size_t>(kLaneWarps) * kLaneStages * 8;
-    if (sm > 220 * 1024) Log::Fatal("lane histogram: %d warps with %d tiles of %d bins need %zu bytes of shared memory", kLaneWarps, ntiles, a.lane_bins, sm);
-    HistArgs b = a; b.lane_share = share;
-#define FB_LANE(NB, ST)                                                                                                            \
-    {                                                                                                                              \
-      static bool attr = false;                                                                                                    \
-      if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantLaneKernel<NB, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr = true; } \
-      HistQuantLaneKernel<NB, ST><<<grid, kLaneThreads, sm, s>>>(b);                                                               \
-    }
-#define FB_LANE_ST(NB) { if (kLaneStages == 2) FB_LANE(NB, 2) else if (kLaneStages == 3) FB_LANE(NB, 3) else FB_LANE(NB, 4) }
-    if (a.lane_bins == 16) FB_LANE_ST(16)
-    else if (a.lane_bins == 64) FB_LANE_ST(64)
-    else Log::Fatal("lane histogram: unsupported tile of %d bins", a.lane_bins);
-#undef FB_LANE_ST
-#undef FB_LANE
-    FB_LAUNCHED(); FB_KERNEL_CHECK();
-    return;
-  }
+  if (a.lane_mode != 0) { LaunchLane<false>(a, s); return; }
   const bool two_phase = a.rows_per_block > a.sub_rows;
   int max_groups = 0;
   // shared bytes: packed (+ wide) + group starts; sized for the largest partition
@@ -546,6 +635,7 @@ void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
 
 void LaunchHistConstructFloat(const HistArgs& a, cudaStream_t s) {
   if (a.total_blocks <= 0 || a.num_tasks <= 0) return;
+  if (a.lane_mode != 0) { LaunchLane<true>(a, s); return; }
   const size_t sm = static_cast<size_t>(a.max_part_bins) * 8 + static_cast<size_t>(a.num_groups) * 4;
   static bool attr = false; if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistFloatKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr = true; }
   dim3 grid(a.total_blocks, a.num_parts);

@@ -85,8 +85,8 @@ struct HistArgs {
   const LevelCtrl* ctrl;    // non-null: num_tasks / total_blocks come from the device controller
 };
 void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s);
-int LaneTiles(bool red, int sub_rows);      // tiles of a lane-construct block: each takes at most `sub_rows` rows before its 16-bit lanes could overflow
-int LaneRowsUnit(bool red, int sub_rows);   // rows per stage of a lane-construct block (warps x 32): rows_per_block is chosen in these units
+int LaneTiles(bool red, int sub_rows, int nb, bool flt);      // tiles of a lane-construct block: each takes at most `sub_rows` rows before its 16-bit lanes could overflow
+int LaneRowsUnit(bool red, int sub_rows, int nb, bool flt);   // rows per stage of a lane-construct block (warps x 32): rows_per_block is chosen in these units
 // K9: per-tree compact view. out[row][j] = cols[groups[j]][row] for the listed (sampled) feature groups: a dense
 // row-major matrix with only the columns this tree can split on, read from the column-major copy (coalesced
 // along rows) and written in 32-byte row pieces through a shared-memory transpose tile.

@@ -61,11 +61,12 @@ int FB_OpHistogram(const uint8_t* rows, int row_stride, int num_groups, const vo
   const int qb = std::max(2, quant_bins);
   a.sub_rows = quant ? std::max(1, std::min(65535 / qb, 32767 / std::max(1, qb / 2))) : (1 << 30);
   a.identity_root = idx == nullptr ? 1 : 0;
-  a.num_total_bin = total; a.lane_mode = quant ? lane_mode : 0; a.lane_red = 1;
+  a.num_total_bin = total; a.lane_mode = quant ? lane_mode : (lane_mode == 1 || lane_mode == 2 ? 1 : 0); a.lane_red = quant ? 1 : (lane_mode == 2 ? 1 : 0);   // fp32: lane_mode 1 load-add-store, 2 reduction adds
   a.bulk_root = getenv("FALCATA_NO_BULK_ROOT") == nullptr ? 1 : 0;   // the kernel itself decides where the bulk-copy pipeline applies
   int mgb = 0; for (int v : gbins) mgb = std::max(mgb, v);
-  a.lane_bins = mgb <= 16 ? 16 : 64;
-  if (a.lane_mode != 0 && mgb > 64) Log::Fatal("lane histogram covers groups of at most 64 bins");
+  a.lane_bins = mgb <= 16 ? 16 : (mgb <= 64 ? 64 : 256);
+  if (a.lane_mode != 0 && mgb > 256) Log::Fatal("lane histogram covers groups of at most 256 bins");
+  if (a.lane_mode == 3 && mgb > 64) Log::Fatal("tensor-core histogram covers groups of at most 64 bins");
   if (a.lane_mode == 3) {
     if (quant_bins > 127) Log::Fatal("tensor-core histogram: quantized values must fit 8 bits");
     a.lane_bins = 64; a.tc_row_count = count;
@@ -74,7 +75,7 @@ int FB_OpHistogram(const uint8_t* rows, int row_stride, int num_groups, const vo
     t.num_blocks = (count + rows_per_block - 1) / rows_per_block; a.total_blocks = t.num_blocks;
     d_task.Upload(&t, 1, s);
   }
-  if (a.lane_mode == 1 && rows_per_block > std::min(8, LaneTiles(true, a.sub_rows)) * a.sub_rows) { a.rows_per_block = rows_per_block = std::min(8, LaneTiles(true, a.sub_rows)) * a.sub_rows; }
+  if (a.lane_mode == 1 && quant && rows_per_block > static_cast<long long>(LaneTiles(true, a.sub_rows, a.lane_bins, false)) * a.sub_rows) { a.rows_per_block = rows_per_block = LaneTiles(true, a.sub_rows, a.lane_bins, false) * a.sub_rows; }
   if (a.lane_mode == 2 && rows_per_block > a.sub_rows) { a.rows_per_block = rows_per_block = a.sub_rows; }
   if (a.lane_mode == 1 || a.lane_mode == 2) {
     t.num_blocks = (count + rows_per_block - 1) / rows_per_block; a.total_blocks = t.num_blocks;

@@ -7,15 +7,38 @@
 
 namespace fb {
 
+bool DevicePredictTiled(const GBDT* gbdt, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, int first_tree, int num_trees, int K,
+                        bool leaf_index, float inv_avg, float* out_device, cudaStream_t s);
+
 void DevicePredict(const GBDT* gbdt, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, int predict_type,
                    int start_iter, int num_iter, float* out_device) {
   if (!CudaAvailable()) Log::Fatal("No CUDA device is available for device prediction");
-  if (predict_type != 0 && predict_type != 1) Log::Fatal("Device prediction supports normal and raw scores");
+  if (predict_type != 0 && predict_type != 1 && predict_type != 2) Log::Fatal("Device prediction supports normal scores, raw scores and leaf indices");
   const int K = gbdt->num_tree_per_iteration_;
   const int iters = static_cast<int>(gbdt->models_.size()) / std::max(1, K);
   start_iter = std::max(0, std::min(start_iter, iters));
   const int use = num_iter > 0 ? std::min(num_iter, iters - start_iter) : iters - start_iter;
   if (ncol <= gbdt->max_feature_idx_) Log::Fatal("The number of features in data (%d) is not the same as it was in training data (%d)", ncol, gbdt->max_feature_idx_ + 1);
+  // the tiled kernel (rows staged in shared memory, trees streamed through it) covers numerical forests; everything
+  // else - categorical splits, very wide or very deep forests - walks the general node array below
+  bool tiled = false;
+  if (use > 0 && std::getenv("FALCATA_PREDICT_GENERAL") == nullptr) {
+    const float inv = (gbdt->average_output_ && use > 0) ? 1.f / use : 1.f;
+    tiled = DevicePredictTiled(gbdt, device_data, dtype, nrow, ncol, row_major, start_iter * K, use * K, K, predict_type == 2, inv, out_device, 0);
+  }
+  if (predict_type == 2) {
+    if (!tiled) Log::Fatal("Leaf-index prediction on the device covers numerical forests of at most 4096 leaves per tree; predict on the host");
+    return;
+  }
+  if (tiled) {
+    if (predict_type == 0 && gbdt->objective_ != nullptr) {
+      const int kind = gbdt->objective_->DeviceKind();
+      const double sig = (kind == kObjBinary || kind == kObjMulticlassOVA) ? gbdt->objective_->DeviceParam(0) : 1.0;
+      if (kind >= 0) LaunchConvertOutput(kind, sig, out_device, nrow, K, 0);
+    }
+    FB_CUDA(cudaStreamSynchronize(0));
+    return;
+  }
   std::vector<ForestNode> nodes; std::vector<int> roots; std::vector<unsigned int> cat_words(1, 0u);
   for (int t = start_iter * K; t < (start_iter + use) * K; ++t) {
     const Tree& T = *gbdt->models_[t];

@@ -31,8 +31,6 @@ def _ref_hist(rows, nbins, g, h, idx=None):
 @pytest.mark.parametrize("lane_mode", [0, 1, 2])
 def test_hist_quant_exact(n, groups, nb, qbins, rpb, lane_mode):
     from falcata_b200 import ops
-    if lane_mode != 0 and nb > 64:
-        pytest.skip("lane tiles cover groups of at most 64 bins")
     nbins = [nb] * groups
     rows = _rows(n, groups, nbins)
     g = torch.Generator(device="cuda"); g.manual_seed(1)
@@ -80,15 +78,22 @@ def test_hist_quant_gh_in_row():
     assert torch.equal(out, _ref_hist(rows, nbins, gi, hi).long())
 
 
-def test_hist_float_close():
+@pytest.mark.parametrize("n,groups,nb", [(1, 1, 2), (33, 3, 16), (30000, 20, 100), (50000, 28, 64), (70001, 100, 255), (20000, 130, 256)])
+@pytest.mark.parametrize("lane_mode", [0, 1, 2])
+def test_hist_float_close(n, groups, nb, lane_mode):
+    """fp32 gradients: the flat shared-atomic instance (0) and the lane instance in its load-add-store (1) and
+    reduction-add (2) forms, whole data set and a row subset, against float64 sums."""
     from falcata_b200 import ops
-    n, groups = 30000, 20
-    nbins = [100] * groups
+    nbins = [nb] * groups
     rows = _rows(n, groups, nbins)
-    gh = torch.randn(n, 2, device="cuda"); gh[:, 1].abs_()
+    g = torch.Generator(device="cuda"); g.manual_seed(3)
+    gh = torch.randn(n, 2, device="cuda", generator=g); gh[:, 1].abs_()
     ref = _ref_hist(rows, nbins, gh[:, 0], gh[:, 1])
-    out = ops.histogram(rows, gh.contiguous(), nbins, quant=False)
+    out = ops.histogram(rows, gh.contiguous(), nbins, quant=False, lane_mode=lane_mode, rows_per_block=8192)
     torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-3)
+    idx = torch.randperm(n, generator=g, device="cuda")[: max(1, n // 3)].int().sort().values
+    out = ops.histogram(rows, gh.contiguous(), nbins, idx=idx, quant=False, lane_mode=lane_mode, rows_per_block=8192)
+    torch.testing.assert_close(out, _ref_hist(rows, nbins, gh[:, 0], gh[:, 1], idx), rtol=1e-4, atol=1e-3)
 
 
 @pytest.mark.parametrize("stochastic", [True, False])
