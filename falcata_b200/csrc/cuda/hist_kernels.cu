@@ -223,16 +223,27 @@ __device__ __forceinline__ void ConsumeStage(int* __restrict__ tile, const unsig
 // row's pair into column l. `red`: shared-memory reduction adds (tiles shared by several warps); otherwise the warp owns
 // the tile and the update is a load-add-store, eight rows at a time with repeated cells forwarded in registers - the
 // sums are then those of the rows in order, whatever the timing.
-template <int NB, bool P4>
-__device__ __forceinline__ void ConsumeStageFloat(float2* __restrict__ tile, const unsigned char* __restrict__ stage_rows, const float2* __restrict__ sg, int cnt, int lane, bool active, bool red) {
+template <int NB, bool P4, bool RED>
+__device__ __forceinline__ void ConsumeStageFloat(float2* __restrict__ tile, const unsigned char* __restrict__ stage_rows, const float2* __restrict__ sg, int cnt, int lane, bool active) {
   const unsigned char* sr = stage_rows + (P4 ? (lane >> 1) : lane);
   const int nshift = (lane & 1) * 4;
   auto bin_of = [&](int j) -> int { const int b = sr[j * 32]; return P4 ? ((b >> nshift) & 15) : b; };
   float2* col = tile + lane;
-  if (red) {
-    for (int j = 0; j < cnt; ++j) {
-      const float2 g = sg[j]; float* c = reinterpret_cast<float*>(col + bin_of(j) * 32);
-      if (active) { atomicAdd(c, g.x); atomicAdd(c + 1, g.y); }
+  if constexpr (RED) {
+    // two planes, [gradient | hessian][NB][32] floats: the 32 lanes of an add hit 32 different banks
+    float* tg = reinterpret_cast<float*>(tile) + lane; float* th = tg + NB * 32;
+    if (cnt == 32) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const float4 g2 = *reinterpret_cast<const float4*>(sg + j);   // two rows' pairs, the same address in every lane
+        const int a0 = bin_of(j) * 32, a1 = bin_of(j + 1) * 32;
+        if (active) { atomicAdd(tg + a0, g2.x); atomicAdd(th + a0, g2.y); atomicAdd(tg + a1, g2.z); atomicAdd(th + a1, g2.w); }
+      }
+    } else {
+      for (int j = 0; j < cnt; ++j) {
+        const float2 g = sg[j]; const int a0 = bin_of(j) * 32;
+        if (active) { atomicAdd(tg + a0, g.x); atomicAdd(th + a0, g.y); }
+      }
     }
   } else if (cnt == 32) {
 #pragma unroll
@@ -268,8 +279,10 @@ constexpr int kLaneMaxThreads = 1024;
 // a tile needs the reduction form of the update (`lane_red`); with one warp per tile both forms are valid.
 // FLT: fp32 gradients (a float2 per row) added into (gradient, hessian) float pairs, [NB][32] pairs per tile; otherwise
 // packed int16|uint16 gradient words added into [NB][32] ints.
-template <int NB, int kLaneStages, bool FLT>
-__global__ void __launch_bounds__(FLT ? kLaneMaxThreads / 2 : kLaneMaxThreads, 1) HistQuantLaneKernel(HistArgs a) {
+// MODE 0: integer; 1: fp32 load-add-store (pairs, a tile per warp, at most 16 warps); 2: fp32 reduction adds (planes).
+template <int NB, int kLaneStages, int MODE>
+__global__ void __launch_bounds__(MODE == 1 ? kLaneMaxThreads / 2 : kLaneMaxThreads, 1) HistQuantLaneKernel(HistArgs a) {
+  constexpr bool FLT = MODE != 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int kTile = NB * 32 * (FLT ? 2 : 1);   // 4-byte cells of a tile
   constexpr int kGhWords = FLT ? 2 : 1;            // 4-byte words of a row's gradient record
@@ -338,8 +351,8 @@ __global__ void __launch_bounds__(FLT ? kLaneMaxThreads / 2 : kLaneMaxThreads, 1
   const bool red = a.lane_red != 0 || share > 1;
   auto consume = [&](int slot, int cnt) {   // add the stage's rows into this warp's tile
     if constexpr (FLT) {
-      if (a.pack4) ConsumeStageFloat<NB, true>(reinterpret_cast<float2*>(tile), rows_w + slot * 32 * 32, reinterpret_cast<const float2*>(gh_w + slot * 32 * kGhWords), cnt, lane, active, red);
-      else ConsumeStageFloat<NB, false>(reinterpret_cast<float2*>(tile), rows_w + slot * 32 * 32, reinterpret_cast<const float2*>(gh_w + slot * 32 * kGhWords), cnt, lane, active, red);
+      if (a.pack4) ConsumeStageFloat<NB, true, MODE == 2>(reinterpret_cast<float2*>(tile), rows_w + slot * 32 * 32, reinterpret_cast<const float2*>(gh_w + slot * 32 * kGhWords), cnt, lane, active);
+      else ConsumeStageFloat<NB, false, MODE == 2>(reinterpret_cast<float2*>(tile), rows_w + slot * 32 * 32, reinterpret_cast<const float2*>(gh_w + slot * 32 * kGhWords), cnt, lane, active);
     } else {
       if (a.pack4) ConsumeStage<true>(tile, rows_w + slot * 32 * 32, gh_w + slot * 32, cnt, lane, active, red);
       else ConsumeStage<false>(tile, rows_w + slot * 32 * 32, gh_w + slot * 32, cnt, lane, active, red);
@@ -414,8 +427,13 @@ __global__ void __launch_bounds__(FLT ? kLaneMaxThreads / 2 : kLaneMaxThreads, 1
       // the tiles of a block are summed in tile order, in double; the blocks of a task meet in double-precision global
       // adds, and a task with a single block stores (its cells were cleared with the pool)
       double sg = 0.0, sh = 0.0;
-      const float2* ft = reinterpret_cast<const float2*>(tiles);
-      for (int w = 0; w < ntiles; ++w) { const float2 v = ft[w * (kTile / 2) + cell]; sg += static_cast<double>(v.x); sh += static_cast<double>(v.y); }
+      if constexpr (MODE == 2) {
+        const float* ft = reinterpret_cast<const float*>(tiles);
+        for (int w = 0; w < ntiles; ++w) { sg += static_cast<double>(ft[w * kTile + cell]); sh += static_cast<double>(ft[w * kTile + NB * 32 + cell]); }
+      } else {
+        const float2* ft = reinterpret_cast<const float2*>(tiles);
+        for (int w = 0; w < ntiles; ++w) { const float2 v = ft[w * (kTile / 2) + cell]; sg += static_cast<double>(v.x); sh += static_cast<double>(v.y); }
+      }
       if (sg != 0.0 || sh != 0.0) {
         const HistDest& d = a.dest;
         const int gb = gstart + b;
@@ -546,7 +564,7 @@ void LaunchCompactGather(const uint8_t* cols, long long col_stride, int n, const
 // then keeps as many tiles as fit so that it still takes a few thousand rows.
 // The environment overrides serve shape sweeps (FALCATA_LANE_WARPS: 4..32 warps per block, FALCATA_LANE_SHARE: warps per
 // tile, a divisor of the warps; FALCATA_LANE_STAGES: 2..4).
-struct LaneGeometry { int warps, share, stages; size_t smem; };
+struct LaneGeometry { int warps, share, stages; size_t smem; bool red; };
 static LaneGeometry LaneShape(bool red, int sub_rows, int nb, bool flt) {
   LaneGeometry g;
   g.stages = 2;
@@ -554,6 +572,9 @@ static LaneGeometry LaneShape(bool red, int sub_rows, int nb, bool flt) {
   if (g.stages < 2 || g.stages > 4) Log::Fatal("FALCATA_LANE_STAGES must be 2, 3 or 4");
   const size_t tile_bytes = static_cast<size_t>(nb) * 32 * 4 * (flt ? 2 : 1);
   const size_t budget = 220 * 1024;
+  // fp32 with 256-bin tiles: a tile per warp leaves room for three warps only, and one warp per scheduler cannot hide the
+  // latency of its own dependent instructions (measured: 445 us against 326 us for a 1M x 100 root): reduction form
+  if (flt && nb > 64) red = true;
   if (flt && !red) {
     // fp32, load-add-store: a tile per warp, as many warps as fit, and deeper staging since few warps are in flight
     if (std::getenv("FALCATA_LANE_STAGES") == nullptr) g.stages = 4;
@@ -563,12 +584,13 @@ static LaneGeometry LaneShape(bool red, int sub_rows, int nb, bool flt) {
     if (g.warps < 1) Log::Fatal("lane histogram: a %d-bin fp32 tile does not fit in shared memory", nb);
     g.share = 1;
     g.smem = per_warp * g.warps;
+    g.red = false;
     return g;
   }
   const bool wide = red && sub_rows >= 4096;
-  g.warps = red ? (flt ? 16 : 32) : 20;   // fp32 blocks have at most 16 warps (the kernel is compiled for 128 registers per thread)
+  g.warps = red ? 32 : 20;
   if (const char* e = std::getenv("FALCATA_LANE_WARPS")) g.warps = std::atoi(e);
-  if (g.warps < 4 || g.warps > (flt ? 16 : 32)) Log::Fatal("FALCATA_LANE_WARPS must be within 4..32 (4..16 for fp32)");
+  if (g.warps < 4 || g.warps > 32) Log::Fatal("FALCATA_LANE_WARPS must be within 4..32");
   const size_t stage_bytes = static_cast<size_t>(g.warps) * g.stages * (32 * (32 + (flt ? 8 : 4)) + 8);
   if (stage_bytes + tile_bytes > budget) Log::Fatal("lane histogram: a %d-bin tile does not fit beside the stages of %d warps", nb, g.warps);
   const int fit = static_cast<int>((budget - stage_bytes) / tile_bytes);
@@ -579,14 +601,15 @@ static LaneGeometry LaneShape(bool red, int sub_rows, int nb, bool flt) {
   if (tiles > fit) Log::Fatal("lane histogram: %d tiles of %d bins do not fit beside the stages of %d warps", tiles, nb, g.warps);
   g.share = g.warps / tiles;
   g.smem = stage_bytes + tile_bytes * tiles;
+  g.red = red;
   return g;
 }
 int LaneRowsUnit(bool red, int sub_rows, int nb, bool flt) { return LaneShape(red, sub_rows, nb, flt).warps * 32; }
 int LaneTiles(bool red, int sub_rows, int nb, bool flt) { const LaneGeometry g = LaneShape(red, sub_rows, nb, flt); return g.warps / g.share; }
 
-template <bool FLT>
-static void LaunchLane(const HistArgs& a, cudaStream_t s) {
-  const LaneGeometry g = LaneShape(a.lane_red != 0, a.sub_rows, a.lane_bins, FLT);
+template <int MODE>
+static void LaunchLane(const HistArgs& a, cudaStream_t s, const LaneGeometry& g) {
+  constexpr bool FLT = MODE != 0;
   const int ntiles = g.warps / g.share;
   if (!FLT) {
     const long long cap = static_cast<long long>(ntiles) * a.sub_rows;
@@ -597,8 +620,8 @@ static void LaunchLane(const HistArgs& a, cudaStream_t s) {
 #define FB_LANE(NB, ST)                                                                                                            \
   {                                                                                                                                \
     static bool attr = false;                                                                                                      \
-    if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantLaneKernel<NB, ST, FLT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr = true; } \
-    HistQuantLaneKernel<NB, ST, FLT><<<grid, g.warps * 32, g.smem, s>>>(b);                                                        \
+    if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistQuantLaneKernel<NB, ST, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr = true; } \
+    HistQuantLaneKernel<NB, ST, MODE><<<grid, g.warps * 32, g.smem, s>>>(b);                                                       \
   }
 #define FB_LANE_ST(NB) { if (g.stages == 2) FB_LANE(NB, 2) else if (g.stages == 3) FB_LANE(NB, 3) else FB_LANE(NB, 4) }
   if (a.lane_bins == 16) FB_LANE_ST(16)
@@ -616,7 +639,7 @@ void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
     if (LaunchHistConstructQuantTC(a, s)) return;
     Log::Fatal("tensor-core histogram: the shape is outside what the instance covers (root level, 32-byte rows, <= 32 groups of <= 64 bins, one rank)");
   }
-  if (a.lane_mode != 0) { LaunchLane<false>(a, s); return; }
+  if (a.lane_mode != 0) { LaunchLane<0>(a, s, LaneShape(a.lane_red != 0, a.sub_rows, a.lane_bins, false)); return; }
   const bool two_phase = a.rows_per_block > a.sub_rows;
   int max_groups = 0;
   // shared bytes: packed (+ wide) + group starts; sized for the largest partition
@@ -635,7 +658,11 @@ void LaunchHistConstructQuant(const HistArgs& a, cudaStream_t s) {
 
 void LaunchHistConstructFloat(const HistArgs& a, cudaStream_t s) {
   if (a.total_blocks <= 0 || a.num_tasks <= 0) return;
-  if (a.lane_mode != 0) { LaunchLane<true>(a, s); return; }
+  if (a.lane_mode != 0) {
+    const LaneGeometry g = LaneShape(a.lane_red != 0, a.sub_rows, a.lane_bins, true);
+    if (g.red) LaunchLane<2>(a, s, g); else LaunchLane<1>(a, s, g);
+    return;
+  }
   const size_t sm = static_cast<size_t>(a.max_part_bins) * 8 + static_cast<size_t>(a.num_groups) * 4;
   static bool attr = false; if (!attr) { FB_CUDA(cudaFuncSetAttribute(HistFloatKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr = true; }
   dim3 grid(a.total_blocks, a.num_parts);
