@@ -62,6 +62,7 @@ const char* FB_GetLastError() { return g_last_error.c_str(); }
 
 int FB_RegisterLogCallback(void (*callback)(const char*)) { API_BEGIN(); Log::callback() = callback; API_END(); }
 int FB_CudaAvailable(int* out) { API_BEGIN(); *out = CudaAvailable() ? 1 : 0; API_END(); }
+int FB_SetLastErrorForCompat(const char* message) { g_last_error = message != nullptr ? message : "error"; return -1; }
 int FB_SetNumThreads(int num_threads) { API_BEGIN(); if (num_threads > 0) omp_set_num_threads(num_threads); API_END(); }
 int FB_GetNumThreads(int* out) { API_BEGIN(); *out = omp_get_max_threads(); API_END(); }
 // Resolved value of an integer parameter (aliases, defaults and seed derivation applied) for the Python layer.
@@ -715,6 +716,136 @@ int FB_BoosterPredictForArrow(BoosterHandle handle, int64_t n_chunks, void* chun
   try { ArrowToDense(n_chunks, static_cast<FBArrowArray*>(chunks), static_cast<FBArrowSchema*>(schema), &dense, &nrow, &ncol); }
   catch (std::exception& ex) { g_last_error = ex.what(); return -1; }
   return FB_BoosterPredictForMat(handle, dense.data(), kF64, static_cast<int32_t>(nrow), ncol, 1, predict_type, start_iteration, num_iteration, parameter, out_len, out_result);
+}
+
+// ---- Arrow C stream interface: the stream is drained into a list of batches, then handled like an array of chunks ----
+namespace {
+struct FBArrowArrayStream {
+  int (*get_schema)(FBArrowArrayStream*, FBArrowSchema* out);
+  int (*get_next)(FBArrowArrayStream*, FBArrowArray* out);
+  const char* (*get_last_error)(FBArrowArrayStream*);
+  void (*release)(FBArrowArrayStream*);
+  void* private_data;
+};
+// Pulls every batch out of the stream and releases the stream. On an error of the producer the batches already pulled are
+// released and the call fails with the producer's message.
+bool DrainArrowStream(void* stream_ptr, std::vector<FBArrowArray>* batches, FBArrowSchema* schema) {
+  FBArrowArrayStream* st = static_cast<FBArrowArrayStream*>(stream_ptr);
+  if (st == nullptr || st->get_schema == nullptr || st->get_next == nullptr) { g_last_error = "The Arrow stream is empty or already released"; return false; }
+  auto fail = [&](const char* what) {
+    const char* why = st->get_last_error != nullptr ? st->get_last_error(st) : nullptr;
+    g_last_error = std::string(what) + (why != nullptr ? std::string(": ") + why : std::string());
+    for (auto& b : *batches) if (b.release != nullptr) b.release(&b);
+    batches->clear();
+    if (st->release != nullptr) st->release(st);
+    return false;
+  };
+  memset(schema, 0, sizeof(*schema));
+  if (st->get_schema(st, schema) != 0) return fail("The Arrow stream gave no schema");
+  for (;;) {
+    FBArrowArray next; memset(&next, 0, sizeof(next));
+    if (st->get_next(st, &next) != 0) { if (schema->release != nullptr) schema->release(schema); return fail("The Arrow stream failed while reading a batch"); }
+    if (next.release == nullptr) break;   // end of the stream
+    batches->push_back(next);
+  }
+  if (st->release != nullptr) st->release(st);
+  return true;
+}
+// One numeric column (a plain array or the single child of a struct), all chunks in order, as doubles.
+void ArrowColumnToDoubles(int64_t n_chunks, FBArrowArray* chunks, FBArrowSchema* schema, std::vector<double>* out) {
+  ArrowOwner owner{n_chunks, chunks, schema};
+  if (schema == nullptr || schema->format == nullptr) Log::Fatal("The Arrow field has no schema");
+  const bool is_struct = schema->format[0] == '+' && schema->format[1] == 's';
+  if (is_struct && schema->n_children != 1) Log::Fatal("A field takes one Arrow column, not %lld", static_cast<long long>(schema->n_children));
+  const char* fmt = is_struct ? schema->children[0]->format : schema->format;
+  out->clear();
+  for (int64_t c = 0; c < n_chunks; ++c) {
+    const FBArrowArray* col = is_struct ? chunks[c].children[0] : &chunks[c];
+    const int64_t len = is_struct ? chunks[c].length : col->length;
+    for (int64_t i = 0; i < len; ++i) out->push_back(ArrowValue(col, fmt, is_struct ? chunks[c].offset + i : i));
+  }
+}
+int SetFieldFromDoubles(DatasetHandle handle, const char* field_name, const std::vector<double>& v) {
+  const std::string f = field_name;
+  if (f == "group" || f == "query") {
+    std::vector<int32_t> g(v.size()); for (size_t i = 0; i < v.size(); ++i) g[i] = static_cast<int32_t>(v[i]);
+    return FB_DatasetSetField(handle, field_name, g.data(), static_cast<int64_t>(g.size()), kI32);
+  }
+  if (f == "init_score") return FB_DatasetSetField(handle, field_name, v.data(), static_cast<int64_t>(v.size()), kF64);
+  std::vector<float> x(v.begin(), v.end());
+  return FB_DatasetSetField(handle, field_name, x.data(), static_cast<int64_t>(x.size()), kF32);
+}
+}  // namespace
+
+// Parity: src/c_api.cpp (dataset creation, field setting and prediction from an ArrowArrayStream).
+int FB_DatasetCreateFromArrowStream(void* stream, const char* parameters, const DatasetHandle reference, DatasetHandle* out) {
+  std::vector<FBArrowArray> batches; FBArrowSchema schema;
+  if (!DrainArrowStream(stream, &batches, &schema)) return -1;
+  return FB_DatasetCreateFromArrow(static_cast<int64_t>(batches.size()), batches.data(), &schema, parameters, reference, out);
+}
+int FB_BoosterPredictForArrowStream(BoosterHandle handle, void* stream, int predict_type, int start_iteration, int num_iteration, const char* parameter,
+                                    int64_t* out_len, double* out_result) {
+  std::vector<FBArrowArray> batches; FBArrowSchema schema;
+  if (!DrainArrowStream(stream, &batches, &schema)) return -1;
+  return FB_BoosterPredictForArrow(handle, static_cast<int64_t>(batches.size()), batches.data(), &schema, predict_type, start_iteration, num_iteration, parameter, out_len, out_result);
+}
+int FB_DatasetSetFieldFromArrow(DatasetHandle handle, const char* field_name, int64_t n_chunks, void* chunks, void* schema) {
+  std::vector<double> v;
+  try { ArrowColumnToDoubles(n_chunks, static_cast<FBArrowArray*>(chunks), static_cast<FBArrowSchema*>(schema), &v); }
+  catch (std::exception& ex) { g_last_error = ex.what(); return -1; }
+  return SetFieldFromDoubles(handle, field_name, v);
+}
+int FB_DatasetSetFieldFromArrowStream(DatasetHandle handle, const char* field_name, void* stream) {
+  std::vector<FBArrowArray> batches; FBArrowSchema schema;
+  if (!DrainArrowStream(stream, &batches, &schema)) return -1;
+  return FB_DatasetSetFieldFromArrow(handle, field_name, static_cast<int64_t>(batches.size()), batches.data(), &schema);
+}
+
+// Rows [start_row, start_row + nindptr - 1) of a streamed data set, given as CSR: densified block by block and pushed.
+// Parity: src/c_api.cpp (LGBM_DatasetPushRowsByCSR).
+int FB_DatasetPushRowsByCSR(DatasetHandle handle, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr,
+                            int64_t nelem, int64_t num_col, int64_t start_row) {
+  API_BEGIN();
+  (void)nelem;
+  const int64_t nrow = nindptr - 1;
+  const int64_t block = std::max<int64_t>(1, (int64_t{32} << 20) / std::max<int64_t>(1, num_col * 8));
+  std::vector<double> dense;
+  for (int64_t a = 0; a < nrow; a += block) {
+    const int64_t b = std::min(nrow, a + block);
+    DensifyCSR(indptr, indptr_type, indices, data, data_type, a, b, num_col, &dense);
+    if (FB_DatasetPushRows(handle, dense.data(), kF64, static_cast<int32_t>(b - a), static_cast<int32_t>(num_col), 1, static_cast<int32_t>(start_row + a)) != 0) return -1;
+  }
+  API_END();
+}
+
+// Fails when `new_parameters` changes a parameter that the binned data depends on.
+// Parity: src/c_api.cpp (LGBM_DatasetUpdateParamChecking).
+int FB_DatasetUpdateParamChecking(const char* old_parameters, const char* new_parameters) {
+  API_BEGIN();
+  static const char* const kBinned[] = {"max_bin", "max_bin_by_feature", "min_data_in_bin", "bin_construct_sample_cnt", "use_missing", "zero_as_missing",
+                                        "categorical_feature", "feature_pre_filter", "enable_bundle", "data_random_seed", "is_enable_sparse", "two_round",
+                                        "header", "label_column", "weight_column", "group_column", "ignore_column", "forcedbins_filename", "linear_tree",
+                                        "min_data_in_leaf", "max_cat_to_onehot", "precise_float_parser"};
+  auto old_map = Config::Str2Map(old_parameters), new_map = Config::Str2Map(new_parameters);
+  Config old_cfg; old_cfg.Set(old_map, CudaAvailable());
+  for (const char* key : kBinned) {
+    auto it = new_map.find(key);
+    if (it == new_map.end()) continue;
+    auto was = old_map.find(key);
+    const std::string before = was != old_map.end() ? was->second : std::string();
+    if (was == old_map.end()) {
+      // the parameter was at its default when the data was binned: only min_data_in_leaf may then be raised freely
+      if (std::string(key) == "min_data_in_leaf" && atoi(it->second.c_str()) >= old_cfg.min_data_in_leaf) continue;
+      Config probe; std::unordered_map<std::string, std::string> one{{key, it->second}}; probe.Set(one, CudaAvailable());
+      if (probe.ToString() == Config().ToString()) continue;   // set to its default value: no change
+      Log::Fatal("Cannot change %s after constructed Dataset handle.", key);
+    }
+    if (before != it->second) {
+      if (std::string(key) == "min_data_in_leaf" && atoi(it->second.c_str()) >= atoi(before.c_str()) && !old_cfg.feature_pre_filter) continue;
+      Log::Fatal("Cannot change %s after constructed Dataset handle.", key);
+    }
+  }
+  API_END();
 }
 
 int FB_GetSampleCount(int32_t num_total_row, const char* parameters, int* out) {

@@ -20,6 +20,7 @@ int FB_CudaAvailable(int* out);
 int FB_ResolveParamInt(const char* parameters, const char* name, int* out);
 int FB_SetTimeTag(int enabled);
 // Host worker threads of the OpenMP loops (bin finding, label scans, host learners). <= 0: leave as is.
+int FB_SetLastErrorForCompat(const char* message);   /* records `message` as the last error and returns -1 (used by fb/c_api_compat.h) */
 int FB_SetNumThreads(int num_threads);
 int FB_GetNumThreads(int* out);
 int FB_GetTimeTagReport(int64_t buffer_len, int64_t* out_len, char* out_str);
@@ -141,6 +142,15 @@ int FB_DatasetPushRowsWithMetadata(DatasetHandle handle, const void* data, int d
 int FB_DatasetMarkFinished(DatasetHandle handle);
 /* Arrow C data interface: `chunks` is an array of n_chunks ArrowArray structs (record batches), `schema` one ArrowSchema; both are released */
 int FB_DatasetCreateFromArrow(int64_t n_chunks, void* chunks, void* schema, const char* parameters, const DatasetHandle reference, DatasetHandle* out);
+/* Arrow C stream interface (`stream`: an ArrowArrayStream*; it is drained and released) and single fields from Arrow */
+int FB_DatasetCreateFromArrowStream(void* stream, const char* parameters, const DatasetHandle reference, DatasetHandle* out);
+int FB_BoosterPredictForArrowStream(BoosterHandle handle, void* stream, int predict_type, int start_iteration, int num_iteration, const char* parameter,
+                                    int64_t* out_len, double* out_result);
+int FB_DatasetSetFieldFromArrow(DatasetHandle handle, const char* field_name, int64_t n_chunks, void* chunks, void* schema);
+int FB_DatasetSetFieldFromArrowStream(DatasetHandle handle, const char* field_name, void* stream);
+int FB_DatasetPushRowsByCSR(DatasetHandle handle, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr,
+                            int64_t nelem, int64_t num_col, int64_t start_row);
+int FB_DatasetUpdateParamChecking(const char* old_parameters, const char* new_parameters);
 int FB_BoosterPredictForArrow(BoosterHandle handle, int64_t n_chunks, void* chunks, void* schema, int predict_type, int start_iteration, int num_iteration,
                               const char* parameter, int64_t* out_len, double* out_result);
 int FB_GetSampleCount(int32_t num_total_row, const char* parameters, int* out);
