@@ -1,6 +1,6 @@
 // Host evaluation metrics and DCG helpers.
 // Parity: src/metric/regression_metric.hpp, binary_metric.hpp (logloss, error, AUC, average
-// precision), multiclass_metric.hpp (multi_logloss, multi_error, auc_mu left out), rank_metric.hpp
+// precision), multiclass_metric.hpp (multi_logloss, multi_error, auc_mu), rank_metric.hpp
 // (ndcg@k), map_metric.hpp, xentropy_metric.hpp, dcg_calculator.cpp:L34-174.
 // Sums go through Network so that every rank reports the global value.
 #include "fb/objective.h"
@@ -182,6 +182,73 @@ struct MultiError : public MetricBase {
   }
 };
 
+// AUC-mu (Kleiman & Page, 2019): the mean over class pairs (i, j) of the probability that a row of class i lies farther
+// on i's side of the pair's separating direction than a row of class j, ties counting one half. With partition weights
+// W (default: 1 off the diagonal, 0 on it), v = W[i] - W[j] and the signed distance of row a is (v[i] - v[j]) * <v, raw
+// scores of a>. Row weights multiply pair counts. Parity: src/metric/multiclass_metric.hpp (AucMuMetric).
+struct AucMu : public MetricBase {
+  int k_; std::vector<double> w_;   // [k x k]
+  explicit AucMu(const Config& c) : k_(c.num_class) {
+    w_.assign(static_cast<size_t>(k_) * k_, 1.0);
+    for (int i = 0; i < k_; ++i) w_[static_cast<size_t>(i) * k_ + i] = 0.0;
+    if (!c.auc_mu_weights.empty()) {
+      std::vector<double> given;
+      for (auto& t : SplitAny(c.auc_mu_weights, ",")) { const std::string s = Trim(t); if (!s.empty()) given.push_back(atof(s.c_str())); }
+      if (given.size() != w_.size()) Log::Fatal("auc_mu_weights must have %d elements, but found %d", k_ * k_, static_cast<int>(given.size()));
+      for (int i = 0; i < k_; ++i) {
+        if (std::fabs(given[static_cast<size_t>(i) * k_ + i]) > kEpsilon) Log::Warning("AUC-mu matrix must have zeros on diagonal. Overwriting value in position %d of auc_mu_weights with 0.", i * k_ + i);
+        given[static_cast<size_t>(i) * k_ + i] = 0.0;
+      }
+      w_ = given;
+    }
+  }
+  std::vector<std::string> Names() const override { return {"auc_mu"}; }
+  bool HigherBetter() const override { return true; }
+  std::vector<double> Eval(const double* score, const ObjectiveFunction*) const override {
+    std::vector<std::vector<int>> rows_of(k_);
+    for (data_size_t a = 0; a < n_; ++a) {
+      const int y = static_cast<int>(label_[a]);
+      if (y < 0 || y >= k_) Log::Fatal("Label must be in [0, %d), but found %d in label", k_, y);
+      rows_of[y].push_back(a);
+    }
+    double total = 0.0;
+    std::vector<double> v(k_);
+    struct Item { double d; double w; int is_i; };
+    std::vector<Item> items;
+    for (int i = 0; i < k_; ++i) {
+      for (int j = i + 1; j < k_; ++j) {
+        for (int m = 0; m < k_; ++m) v[m] = w_[static_cast<size_t>(i) * k_ + m] - w_[static_cast<size_t>(j) * k_ + m];
+        const double t1 = v[i] - v[j];
+        items.clear();
+        double wi = 0.0, wj = 0.0;
+        for (int side = 0; side < 2; ++side) {
+          for (int a : rows_of[side == 0 ? i : j]) {
+            double dot = 0.0;
+            for (int m = 0; m < k_; ++m) dot += v[m] * score[static_cast<size_t>(m) * n_ + a];
+            const double w = weights_ ? weights_[a] : 1.0;
+            items.push_back({t1 * dot, w, side == 0 ? 1 : 0});
+            (side == 0 ? wi : wj) += w;
+          }
+        }
+        if (wi <= 0.0 || wj <= 0.0) continue;   // a class without rows adds nothing for its pairs
+        std::sort(items.begin(), items.end(), [](const Item& a, const Item& b) { return a.d < b.d; });
+        // walk the distances upwards in groups of (near-)equal distance: a class-i row beats all class-j weight strictly
+        // below its group and half of the class-j weight inside it
+        double below_j = 0.0, s = 0.0;
+        for (size_t b = 0; b < items.size();) {
+          size_t e = b; double gi = 0.0, gj = 0.0;
+          while (e < items.size() && std::fabs(items[e].d - items[b].d) < kEpsilon) { if (items[e].is_i) gi += items[e].w; else gj += items[e].w; ++e; }
+          s += gi * (below_j + 0.5 * gj);
+          below_j += gj;
+          b = e;
+        }
+        total += s / (wi * wj);
+      }
+    }
+    return {k_ > 1 ? 2.0 * total / (static_cast<double>(k_) * (k_ - 1)) : 1.0};
+  }
+};
+
 struct NDCGMetric : public MetricBase {
   std::vector<int> ks_; std::vector<double> gains_;
   explicit NDCGMetric(const Config& c) : ks_(c.eval_at_vec), gains_(c.label_gain_vec) {}
@@ -252,6 +319,7 @@ Metric* CreateMetric(const std::string& name, const Config& cfg) {
   if (name == "average_precision") return new AveragePrecision();
   if (name == "multi_logloss") return new MultiLogloss(cfg);
   if (name == "multi_error") return new MultiError(cfg);
+  if (name == "auc_mu") return new AucMu(cfg);
   if (name == "cross_entropy") return new Pointwise<XentLoss>(cfg, "cross_entropy", true);
   if (name == "cross_entropy_lambda") return new Pointwise<XentLoss>(cfg, "cross_entropy_lambda", true);
   if (name == "kullback_leibler") return new Pointwise<KLDivLoss>(cfg, "kullback_leibler", true);

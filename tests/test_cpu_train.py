@@ -277,3 +277,39 @@ def test_reset_parameter_schedules():
         fb.train(dict(params), fb.Dataset(X, y), 4, callbacks=[fb.reset_parameter(learning_rate=[0.1, 0.2])])
     with pytest.raises(ValueError):
         fb.reset_parameter(learning_rate=0.1)
+
+
+def test_auc_mu_matches_pairwise_definition():
+    """auc_mu against a direct evaluation of its definition (all class pairs, all row pairs, ties one half), with the
+    default partition weights, a custom matrix and row weights."""
+    rng = np.random.default_rng(8)
+    n, k = 300, 3
+    X = rng.normal(size=(n, 5))
+    y = np.argmax(X[:, :3] + 0.8 * rng.normal(size=(n, 3)), axis=1).astype(np.float64)
+    w = rng.uniform(0.5, 2.0, size=n)
+
+    def brute(raw, W, weights):
+        tot = 0.0
+        for i in range(k):
+            for j in range(i + 1, k):
+                v = W[i] - W[j]; t1 = v[i] - v[j]
+                d = t1 * (raw @ v)
+                a = np.where(y == i)[0]; b = np.where(y == j)[0]
+                s = 0.0
+                for p in a:
+                    s += weights[p] * (np.sum(weights[b] * (d[b] < d[p] - 1e-15)) + 0.5 * np.sum(weights[b] * (np.abs(d[b] - d[p]) < 1e-15)))
+                tot += s / (weights[a].sum() * weights[b].sum())
+        return 2 * tot / (k * (k - 1))
+
+    for weights, wm in [(None, None), (w, None), (None, [0, 1, 3, 2, 0, 1, 1, 4, 0])]:
+        params = {"objective": "multiclass", "num_class": k, "metric": "auc_mu", "num_leaves": 7, "verbosity": -1, "min_data_in_leaf": 5}
+        if wm is not None:
+            params["auc_mu_weights"] = wm
+        rec = {}
+        ds = fb.Dataset(X, y, weight=weights)
+        bst = fb.train(params, ds, 6, valid_sets=[ds], valid_names=["train"], callbacks=[fb.record_evaluation(rec)])
+        raw = np.asarray(bst.predict(X, raw_score=True))
+        W = np.ones((k, k)) - np.eye(k) if wm is None else np.asarray(wm, dtype=float).reshape(k, k)
+        want = brute(raw, W, np.ones(n) if weights is None else weights)
+        assert abs(rec["train"]["auc_mu"][-1] - want) < 1e-9
+        assert rec["train"]["auc_mu"][-1] > 0.8

@@ -335,3 +335,50 @@ def test_c_api_arrow_record_batches():
     assert lib.FB_DatasetGetNumData(h, ctypes.byref(nd)) == 0 and nd.value == 1000
     assert lib.FB_DatasetGetNumFeature(h, ctypes.byref(nf)) == 0 and nf.value == 4
     lib.FB_DatasetFree(h)
+
+
+def test_c_api_arrow_streams():
+    """ArrowArrayStream inputs: dataset creation, label from a stream, prediction; the stream is drained and released."""
+    import ctypes
+    import pyarrow as pa
+    from falcata_b200.basic import _lib, _param_str
+
+    class ArrowArrayStream(ctypes.Structure):
+        _fields_ = [("get_schema", ctypes.c_void_p), ("get_next", ctypes.c_void_p), ("get_last_error", ctypes.c_void_p), ("release", ctypes.c_void_p),
+                    ("private_data", ctypes.c_void_p)]
+
+    def stream_of(table, chunk=300):
+        st = ArrowArrayStream()
+        pa.RecordBatchReader.from_batches(table.schema, table.to_batches(max_chunksize=chunk))._export_to_c(ctypes.addressof(st))
+        return st
+
+    lib = _lib()
+    rng = np.random.default_rng(12)
+    X = rng.normal(size=(1000, 3))
+    y = (X[:, 0] + X[:, 1] > 0).astype(np.float32)
+    table = pa.table({"a": X[:, 0], "b": X[:, 1], "c": X[:, 2]})
+    st = stream_of(table)
+    h = ctypes.c_void_p()
+    assert lib.FB_DatasetCreateFromArrowStream(ctypes.byref(st), _param_str({"min_data_in_bin": 1}), None, ctypes.byref(h)) == 0
+    assert not st.release
+    nd = ctypes.c_int32(0)
+    assert lib.FB_DatasetGetNumData(h, ctypes.byref(nd)) == 0 and nd.value == 1000
+    lab = stream_of(pa.table({"label": y}), chunk=450)
+    assert lib.FB_DatasetSetFieldFromArrowStream(h, b"label", ctypes.byref(lab)) == 0
+    ln = ctypes.c_int64(0); ptr = ctypes.c_void_p(); tp = ctypes.c_int(0)
+    assert lib.FB_DatasetGetField(h, b"label", ctypes.byref(ln), ctypes.byref(ptr), ctypes.byref(tp)) == 0 and ln.value == 1000
+    got = np.ctypeslib.as_array(ctypes.cast(ptr, ctypes.POINTER(ctypes.c_float)), shape=(1000,))
+    assert np.array_equal(got, y)
+    bh = ctypes.c_void_p()
+    assert lib.FB_BoosterCreate(h, _param_str({"objective": "binary", "num_leaves": 7, "verbose": -1, "min_data_in_leaf": 5}), ctypes.byref(bh)) == 0
+    fin = ctypes.c_int(0)
+    for _ in range(5):
+        assert lib.FB_BoosterUpdateOneIter(bh, ctypes.byref(fin)) == 0
+    out = np.zeros(1000); n = ctypes.c_int64(0)
+    st = stream_of(table, chunk=128)
+    assert lib.FB_BoosterPredictForArrowStream(bh, ctypes.byref(st), 0, 0, -1, b"", ctypes.byref(n), out.ctypes.data_as(ctypes.POINTER(ctypes.c_double))) == 0
+    ref = np.zeros(1000)
+    Xc = np.ascontiguousarray(X)
+    assert lib.FB_BoosterPredictForMat(bh, Xc.ctypes.data_as(ctypes.c_void_p), 1, 1000, 3, 1, 0, 0, -1, b"", ctypes.byref(n), ref.ctypes.data_as(ctypes.POINTER(ctypes.c_double))) == 0
+    assert np.array_equal(out, ref) and ((out > 0.5) == (y > 0.5)).mean() > 0.9
+    lib.FB_BoosterFree(bh); lib.FB_DatasetFree(h)
