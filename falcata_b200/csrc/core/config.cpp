@@ -169,6 +169,7 @@ void Config::Resolve(bool cuda_available) {
   else Log::Fatal("Unknown quant_mode %s (expected auto|none|stochastic|fixedpoint)", quant_mode.c_str());
   if (quant != QuantMode::None) {
     quant_bins_resolved = quant_bins > 0 ? quant_bins : (quant == QuantMode::Stochastic ? 4 : 64);
+    quant_bins_from_auto = quant_bins <= 0;
     if (quant_bins_resolved < 2 || quant_bins_resolved > 65534) Log::Fatal("quant_bins must be in [2, 65534]");
     use_quantized_grad = true;
   }

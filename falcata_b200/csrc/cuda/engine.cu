@@ -99,8 +99,7 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   grad_.Alloc(total); hess_.Alloc(total); maxbuf_.Alloc(2 * K_); scales_.Alloc(2); root_sums_i_.Alloc(2); root_sums_d_.Alloc(2);
   partial_.Alloc(2 * (static_cast<size_t>(n_) / 256 + 2));
   if (quant_) {
-    if (static_cast<double>(train->global_num_data) * cfg.quant_bins_resolved >= 2147483647.0)
-      Log::Fatal("num_data x quant_bins must stay below 2^31 for 32-bit histogram lanes; lower quant_bins");
+    ResolveQuantBins();
     if (plan_.gh_in_row && K_ == 1) { gh_base_ = dd_->rows.get() + dd_->gh_offset; gh_stride_ = dd_->row_stride; }
     else { gh_sep_.Alloc(n_); gh_base_ = reinterpret_cast<const uint8_t*>(gh_sep_.get()); gh_stride_ = 4; }
     hist_elem_ = sizeof(hist_q_t);
@@ -108,7 +107,7 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     gh2_.Alloc(n_); gh_base_ = reinterpret_cast<const uint8_t*>(gh2_.get()); gh_stride_ = 8; hist_elem_ = sizeof(double2);
   }
   {
-    const int qb = std::max(2, cfg.quant_bins_resolved);
+    const int qb = std::max(2, cfg_.quant_bins_resolved);
     sub_rows_ = quant_ ? std::max(1, std::min(65535 / qb, 32767 / std::max(1, qb / 2))) : (1 << 30);
     lane_mode_ = 0; lane_bins_ = 64;
     // lane construct: 16-, 64- or 256-bin tiles; beyond 64 bins (and for fp32 gradients) only in the reduction form,
@@ -267,6 +266,48 @@ void CudaEngine::SetupOwnership() {
   }
   bin_owner_.Upload(owner, stream_); bin_local_.Upload(local, stream_);
   h_bin_owner_ = owner;
+}
+
+// Gradient levels actually used. The global histograms keep 32-bit halves per bin, so rows x levels must stay below
+// 2^31 over ALL ranks' rows; a default count that breaks this is lowered, an explicit one is refused. A default
+// stochastic count (4) is raised where leaves get small on large data, where 4 levels fit rounding noise: to 64 with a
+// constant hessian, else 16; not for multiclass and not for binary labels beyond 50:1, where rare large gradients pin the
+// scale. Every rank takes the same decision (global row count, label counts summed over the ranks).
+// Parity: src/treelearner/cuda/cuda_single_gpu_tree_learner.cpp:L93-193.
+void CudaEngine::ResolveQuantBins() {
+  int qb = cfg_.quant_bins_resolved;
+  const unsigned long long rows = static_cast<unsigned long long>(std::max<long long>(1, train_->global_num_data));
+  if (rows * static_cast<unsigned long long>(qb) >= (1ULL << 31)) {
+    const int max_bins = static_cast<int>((1ULL << 31) / rows) - 1;
+    if (cfg_.quant_bins_from_auto && max_bins >= 2) {
+      Log::Warning("The default quant_bins=%d exceeds the 32-bit histogram range for %llu rows; using quant_bins=%d (set quant_bins to override)", qb, rows, max_bins);
+      qb = max_bins;
+    } else {
+      Log::Fatal("quant_bins=%d is too large for %llu rows: a bin's sum can exceed the 32-bit histogram range. Use quant_bins <= %d for this data set", qb, rows, std::max(0, max_bins));
+    }
+  }
+  if (cfg_.quant == QuantMode::Stochastic && cfg_.quant_bins_from_auto) {
+    const long long depth_cap = (cfg_.max_depth > 0 && cfg_.max_depth < 31) ? (1LL << cfg_.max_depth) : std::numeric_limits<long long>::max();
+    const long long leaves = std::min<long long>(cfg_.num_leaves, depth_cap);
+    const long long rows_per_leaf = static_cast<long long>(rows) / std::max<long long>(1, leaves);
+    bool extreme = false;
+    if (cfg_.objective == "binary") {
+      double cnt[2] = {0.0, static_cast<double>(train_->metadata.label.size())};
+      for (float y : train_->metadata.label) cnt[0] += y > 0 ? 1.0 : 0.0;
+      if (world_ > 1 && !feature_parallel_) Network::SumDouble(cnt, 2);
+      const double minority = std::min(cnt[0], cnt[1] - cnt[0]);
+      extreme = minority <= 0.0 || (cnt[1] - minority) >= 50.0 * minority;
+    }
+    if (rows >= 100000ULL && rows_per_leaf < 4096 && !extreme && K_ == 1) {
+      const int target = (obj_ != nullptr && obj_->IsConstantHessian()) ? 64 : 16;
+      const int raised = static_cast<int>(std::min<unsigned long long>(target, (1ULL << 31) / rows - 1));
+      if (raised > qb) {
+        Log::Info("Stochastic quant_bins raised from the default %d to %d: about %lld rows per leaf is too few for %d levels (set quant_bins to override)", qb, raised, rows_per_leaf, qb);
+        qb = raised;
+      }
+    }
+  }
+  cfg_.quant_bins_resolved = qb;
 }
 
 int CudaEngine::ChooseRowsPerBlock(long long total_rows) const {

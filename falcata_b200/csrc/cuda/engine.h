@@ -67,6 +67,7 @@ class CudaEngine : public DeviceEngine {
   const uint8_t* bag_mask_ptr() const { return bag_active_ ? bag_mask_.get() : nullptr; }
   void UploadTreeForTraversal(const Tree& tree, const Dataset* ds, DevTree* out);
   int ChooseRowsPerBlock(long long total_rows) const;
+  void ResolveQuantBins();
 
   Config cfg_; Plan plan_;
   const Dataset* train_; DeviceDataset* dd_; const ObjectiveFunction* obj_;

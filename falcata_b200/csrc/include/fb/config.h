@@ -163,6 +163,7 @@ struct Config {
   // ---- derived (filled by Resolve) ----
   QuantMode quant = QuantMode::None;
   int quant_bins_resolved = 0;
+  bool quant_bins_from_auto = false;   // quant_bins was left at its default: the learner may pick a safer or finer count
   bool is_cuda = false;
   std::vector<double> label_gain_vec;
   std::vector<int> eval_at_vec;
