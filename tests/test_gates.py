@@ -47,3 +47,40 @@ def test_perf_gate_uses_the_rolling_median_and_needs_two_bad_runs(tmp_path):
     assert len(hist.read_text().splitlines()) == n
     rows = [json.loads(l) for l in hist.read_text().splitlines()]
     assert [r["accepted"] for r in rows if r["key"] == "k"][-2:] == [False, False]
+
+
+def test_lattice_cells_match_their_stored_fingerprints_on_the_host_learner():
+    """A slice of the regression lattice on the host learner: stored md5 fingerprints of the quantized cells,
+    validity checks of all of them. The full matrix (with the plan-flip equalities) runs on the GPU box."""
+    import lattice  # noqa: E402
+
+    rc = lattice.main(["--check", "--device", "cpu", "--only", "dense/"])
+    assert rc == 0
+    rc = lattice.main(["--check", "--device", "cpu", "--only", "/fixedpoint"])
+    assert rc == 0
+
+
+def test_lattice_reports_a_moved_fingerprint(tmp_path):
+    import lattice  # noqa: E402
+
+    stored = json.loads(lattice.FINGERPRINTS.read_text())
+    stored["cpu"]["dense/stochastic"]["md5"] = "0" * 32
+    fp = tmp_path / "fp.json"; fp.write_text(json.dumps(stored))
+    assert lattice.main(["--check", "--device", "cpu", "--only", "dense/stochastic", "--fingerprints", str(fp)]) == 1
+    cells = {c["id"]: c for c in lattice.build_cells()}
+    assert cells["dense/flip-fused_tail:off"]["equal_to"] == "dense/stochastic" and not cells["dense/flip-fused_tail:off"]["fingerprint"]
+    assert all(k.split(":")[0] in {"device_controller", "fused_tail", "fused_scan", "hist_lane", "hist_lane_red", "col_major_part", "gh_in_row", "bulk_root",
+                                   "compact_view", "pack4", "hist_tc"} for k in lattice.PLAN_FLIPS)
+
+
+def test_fuzz_gate_passes_a_few_random_specifications_on_the_host_learner():
+    import numpy as np
+
+    import fuzz  # noqa: E402
+
+    rng = np.random.default_rng(5)
+    specs = [fuzz.sample_spec(rng) for _ in range(4)]
+    for s in specs:
+        s["rows"] = min(s["rows"], 4000); s["rounds"] = min(s["rounds"], 10); s["cols"] = min(s["cols"], 40)
+        fails, _ = fuzz.check_spec(s, "cpu")
+        assert not fails, (fails, s)
