@@ -33,6 +33,65 @@ except ImportError:  # pragma: no cover
 __all__ = ["LGBMModel", "LGBMClassifier", "LGBMRegressor", "LGBMRanker", "FalcataModel", "FalcataClassifier", "FalcataRegressor", "FalcataRanker"]
 
 
+def _positional_arity(func: Callable) -> int:
+    import inspect
+
+    try:
+        params = inspect.signature(func).parameters.values()
+    except (TypeError, ValueError):
+        return 2
+    return sum(1 for q in params if q.kind in (q.POSITIONAL_ONLY, q.POSITIONAL_OR_KEYWORD) and q.default is q.empty)
+
+
+class _ObjectiveFunctionWrapper:
+    """Adapts an sklearn-style objective ``f(y_true, y_pred[, weight[, group]]) -> (grad, hess)`` to the training
+    loop's ``fobj(preds, dataset)``. With two arguments the returned gradients are multiplied by the sample weights
+    here; with three or four the function gets the weights (and query sizes) and applies them itself.
+    Parity: python-package/falcata/sklearn.py (_ObjectiveFunctionWrapper)."""
+
+    def __init__(self, func: Callable) -> None:
+        self.func = func
+        self.arity = _positional_arity(func)
+        if self.arity not in (2, 3, 4):
+            raise TypeError(f"Self-defined objective function should have 2, 3 or 4 arguments, got {self.arity}")
+
+    def __call__(self, preds: Any, dataset: Dataset) -> Any:
+        labels = dataset.get_label()
+        weight = dataset.get_weight()
+        if self.arity == 2:
+            grad, hess = self.func(labels, preds)
+            if weight is not None:
+                w = np.asarray(weight, dtype=np.float64)
+                grad = np.asarray(grad, dtype=np.float64); hess = np.asarray(hess, dtype=np.float64)
+                if grad.ndim == 2:      # [rows, classes]
+                    w = w[:, None]
+                grad = grad * w; hess = hess * w
+            return grad, hess
+        if self.arity == 3:
+            return self.func(labels, preds, weight)
+        return self.func(labels, preds, weight, dataset.get_group())
+
+
+class _EvalFunctionWrapper:
+    """Adapts an sklearn-style metric ``f(y_true, y_pred[, weight[, group]]) -> (name, value, higher_is_better)`` (or a
+    list of such triples) to the training loop's ``feval(preds, dataset)``.
+    Parity: python-package/falcata/sklearn.py (_EvalFunctionWrapper)."""
+
+    def __init__(self, func: Callable) -> None:
+        self.func = func
+        self.arity = _positional_arity(func)
+        if self.arity not in (2, 3, 4):
+            raise TypeError(f"Self-defined eval function should have 2, 3 or 4 arguments, got {self.arity}")
+
+    def __call__(self, preds: Any, dataset: Dataset) -> Any:
+        labels = dataset.get_label()
+        if self.arity == 2:
+            return self.func(labels, preds)
+        if self.arity == 3:
+            return self.func(labels, preds, dataset.get_weight())
+        return self.func(labels, preds, dataset.get_weight(), dataset.get_group())
+
+
 class LGBMModel(BaseEstimator):
     def __init__(self, boosting_type: str = "gbdt", num_leaves: int = 31, max_depth: int = -1, learning_rate: float = 0.1, n_estimators: int = 100,
                  subsample_for_bin: int = 200000, objective: Optional[Union[str, Callable]] = None, class_weight: Any = None, min_split_gain: float = 0.0,
@@ -78,7 +137,7 @@ class LGBMModel(BaseEstimator):
         if p.get("device_type") is None:
             p.pop("device_type", None)
         obj = p.pop("objective", None)
-        self._fobj = obj if callable(obj) else None
+        self._fobj = _ObjectiveFunctionWrapper(obj) if callable(obj) else None
         p["objective"] = "none" if callable(obj) else (obj or self._default_objective())
         alias = {"boosting_type": "boosting", "min_split_gain": "min_gain_to_split", "min_child_weight": "min_sum_hessian_in_leaf", "min_child_samples": "min_data_in_leaf",
                  "subsample": "bagging_fraction", "subsample_freq": "bagging_freq", "colsample_bytree": "feature_fraction", "reg_alpha": "lambda_l1", "reg_lambda": "lambda_l2",
@@ -105,7 +164,7 @@ class LGBMModel(BaseEstimator):
             if names:
                 params["metric"] = ",".join(names)
             if fevals:
-                feval = [(lambda f: (lambda preds, ds: f(ds.get_label(), preds)))(f) for f in fevals]
+                feval = [_EvalFunctionWrapper(f) for f in fevals]
         train_set = Dataset(X, label=y, weight=sample_weight, group=group, init_score=init_score, feature_name=feature_name,
                             categorical_feature=categorical_feature, params={k: params[k] for k in ("max_bin", "bin_construct_sample_cnt", "min_data_in_leaf") if k in params})
         valid_sets: List[Dataset] = []
@@ -131,6 +190,19 @@ class LGBMModel(BaseEstimator):
         self._best_iteration = self._Booster.best_iteration
         self._best_score = self._Booster.best_score
         return self
+
+    def __sklearn_is_fitted__(self) -> bool:
+        return getattr(self, "_Booster", None) is not None
+
+    def _more_tags(self) -> Dict[str, Any]:
+        return {"allow_nan": True, "X_types": ["2darray", "sparse", "1dlabels"],
+                "_xfail_checks": {"check_no_attributes_set_in_init": "the constructor keeps **kwargs for pass-through parameters"}}
+
+    def __sklearn_tags__(self) -> Any:
+        tags = super().__sklearn_tags__()
+        tags.input_tags.allow_nan = True
+        tags.input_tags.sparse = True
+        return tags
 
     def _encode_y(self, y: Any) -> Any:
         return y
@@ -207,12 +279,14 @@ class LGBMClassifier(ClassifierMixin, LGBMModel):
         y = np.asarray(y.detach().cpu().numpy() if hasattr(y, "detach") else y).reshape(-1)
         self._classes, enc = np.unique(y, return_inverse=True)
         self._n_classes = len(self._classes)
-        if self.class_weight is not None and kwargs.get("sample_weight") is None:
+        if self.class_weight is not None:
+            # class weights multiply whatever sample weights were given
             if self.class_weight == "balanced":
                 cw = len(y) / (self._n_classes * np.bincount(enc))
             else:
                 cw = np.array([self.class_weight.get(c, 1.0) for c in self._classes])
-            kwargs["sample_weight"] = cw[enc]
+            given = kwargs.get("sample_weight")
+            kwargs["sample_weight"] = cw[enc] if given is None else cw[enc] * np.asarray(given, dtype=np.float64)
         super().fit(X, enc.astype(np.float32), **kwargs)
         return self
 

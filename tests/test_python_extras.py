@@ -382,3 +382,42 @@ def test_c_api_arrow_streams():
     assert lib.FB_BoosterPredictForMat(bh, Xc.ctypes.data_as(ctypes.c_void_p), 1, 1000, 3, 1, 0, 0, -1, b"", ctypes.byref(n), ref.ctypes.data_as(ctypes.POINTER(ctypes.c_double))) == 0
     assert np.array_equal(out, ref) and ((out > 0.5) == (y > 0.5)).mean() > 0.9
     lib.FB_BoosterFree(bh); lib.FB_DatasetFree(h)
+
+
+def test_sklearn_custom_objective_metric_and_class_weight():
+    """sklearn-style callables: objective f(y_true, y_pred) and metric f(y_true, y_pred[, weight]); class weights
+    multiply the sample weights; the fitted check and the tags exist."""
+    from sklearn.utils.validation import check_is_fitted
+    from falcata_b200.sklearn import LGBMClassifier, LGBMRegressor
+
+    rng = np.random.default_rng(21)
+    X = rng.normal(size=(1500, 6)); y = X[:, 0] * 2 - X[:, 1] + 0.1 * rng.normal(size=1500)
+    w = rng.uniform(0.5, 1.5, size=1500)
+
+    def l2_obj(y_true, y_pred):
+        return y_pred - y_true, np.ones_like(y_true)
+
+    def mae(y_true, y_pred, weight):
+        assert weight is not None and len(weight) == len(y_true)
+        return "wmae", float(np.average(np.abs(y_true - y_pred), weights=weight)), False
+
+    custom = LGBMRegressor(n_estimators=15, num_leaves=7, objective=l2_obj, min_child_samples=5)
+    with pytest.raises(Exception):
+        check_is_fitted(custom)
+    custom.fit(X, y, sample_weight=w, eval_set=[(X, y)], eval_sample_weight=[w], eval_metric=mae)
+    check_is_fitted(custom)
+    builtin = LGBMRegressor(n_estimators=15, num_leaves=7, objective="regression", min_child_samples=5, boost_from_average=False).fit(X, y, sample_weight=w)
+    assert np.allclose(custom.predict(X), builtin.predict(X), atol=1e-6)
+    series = custom.evals_result_["training"]["wmae"]
+    assert len(series) == 15 and series[-1] < series[0]
+    assert custom._more_tags()["allow_nan"]
+
+    yc = (X[:, 0] + 0.3 * rng.normal(size=1500) > 1.0).astype(int)      # about 17 % positives
+    plain = LGBMClassifier(n_estimators=10, num_leaves=7).fit(X, yc)
+    balanced = LGBMClassifier(n_estimators=10, num_leaves=7, class_weight="balanced").fit(X, yc)
+    by_hand = LGBMClassifier(n_estimators=10, num_leaves=7).fit(X, yc, sample_weight=len(yc) / (2 * np.bincount(yc))[yc])
+    assert np.allclose(balanced.predict_proba(X), by_hand.predict_proba(X))
+    assert balanced.predict(X).mean() > plain.predict(X).mean()          # the rare class is predicted more often
+    both = LGBMClassifier(n_estimators=10, num_leaves=7, class_weight={0: 1.0, 1: 3.0}).fit(X, yc, sample_weight=w)
+    manual = LGBMClassifier(n_estimators=10, num_leaves=7).fit(X, yc, sample_weight=w * np.where(yc == 1, 3.0, 1.0))
+    assert np.allclose(both.predict_proba(X), manual.predict_proba(X))
