@@ -148,6 +148,15 @@ class CPUTreeLearner : public TreeLearner {
   const score_t* grad_ = nullptr; const score_t* hess_ = nullptr;
   std::vector<int8_t> node_feature_mask_;
   std::vector<int64_t> voted_hist_i_; std::vector<double> voted_hist_;
+  // cost-effective boosting, per-feature penalties (by real column index). Coupled: charged once per feature, until
+  // the model first splits on it. Lazy: charged per row of the leaf that has not yet been sent through a split on the
+  // feature. Parity: src/treelearner/cost_effective_gradient_boosting.hpp (DeltaGain, UpdateLeafBestSplits simplified:
+  // cached candidates of other leaves are not re-scored when a feature becomes free).
+  std::vector<double> cegb_coupled_, cegb_lazy_;
+  std::vector<char> cegb_feature_used_;
+  std::vector<std::vector<bool>> cegb_row_paid_;   // [real feature with a lazy penalty][row]
+  double CegbFeaturePenalty(int inner_feature, const LeafState& leaf) const;
+  void CegbAfterSplit(int inner_feature, const LeafState& leaf);
   std::vector<int8_t> voted_;      // voting-parallel: features whose histograms are globally reduced for the current leaf
   int cur_tree_index_ = 0, cur_leaf_id_ = 0;
   Random extra_rand_{6};
@@ -166,6 +175,23 @@ void CPUTreeLearner::SetParams() {
   sp_.max_cat_threshold = cfg_.max_cat_threshold; sp_.max_cat_to_onehot = cfg_.max_cat_to_onehot; sp_.min_data_per_group = cfg_.min_data_per_group;
   sp_.cat_l2 = cfg_.cat_l2; sp_.cat_smooth = cfg_.cat_smooth; sp_.extra_trees = cfg_.extra_trees ? 1 : 0;
   sp_.cegb_split = cfg_.cegb_tradeoff * cfg_.cegb_penalty_split;
+  auto parse_penalties = [&](const std::string& text, const char* name, std::vector<double>* out) {
+    out->clear();
+    if (text.empty()) return;
+    for (auto& t : SplitAny(text, ",")) { const std::string s = Trim(t); if (!s.empty()) out->push_back(atof(s.c_str())); }
+    if (static_cast<int>(out->size()) != ds_->num_total_features) Log::Fatal("%s should be the same size as feature number.", name);
+    bool any = false; for (double v : *out) any = any || v != 0.0;
+    if (!any) out->clear();
+  };
+  parse_penalties(cfg_.cegb_penalty_feature_coupled, "cegb_penalty_feature_coupled", &cegb_coupled_);
+  parse_penalties(cfg_.cegb_penalty_feature_lazy, "cegb_penalty_feature_lazy", &cegb_lazy_);
+  if (!cegb_coupled_.empty()) cegb_feature_used_.assign(ds_->num_total_features, 0);
+  if (!cegb_lazy_.empty()) {
+    cegb_row_paid_.assign(ds_->num_total_features, std::vector<bool>());
+    for (int j = 0; j < ds_->num_total_features; ++j) if (cegb_lazy_[j] > 0.0) cegb_row_paid_[j].assign(ds_->num_data, false);
+  }
+  if ((!cegb_coupled_.empty() || !cegb_lazy_.empty()) && Network::active() && cfg_.tree_learner != "serial")
+    Log::Fatal("Per-feature CEGB penalties are not available with a parallel tree learner");
   sp_.use_mc = 0; for (const auto& m : ds_->feature_meta) if (m.monotone != 0) sp_.use_mc = 1;
   quant_ = cfg_.quant != QuantMode::None;
   qs_.bins = cfg_.quant_bins_resolved; qs_.stochastic = cfg_.quant == QuantMode::Stochastic;
@@ -591,8 +617,9 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
       else ScanCategorical(*leaf, f, L, &per[f]);
     }
     for (int f = 0; f < ds_->num_features; ++f) {
-      const SplitRecord& r = per[f];
+      SplitRecord& r = per[f];
       if (r.feature < 0) continue;
+      if (!cegb_coupled_.empty() || !cegb_lazy_.empty()) { r.gain -= CegbFeaturePenalty(f, *leaf); if (!(r.gain > 0.0)) continue; }
       if (SplitBetter(r.gain, ds_->feature_meta[r.feature].real_index, r.threshold, best.gain, best.feature >= 0 ? ds_->feature_meta[best.feature].real_index : -1, best.threshold)) best = r;
     }
   }
@@ -606,6 +633,7 @@ int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
   ScopedTimer timer("CPUTreeLearner::ApplySplit");
   LeafState& P = leaves_[leaf_id];
   const SplitRecord s = P.best;
+  if (!cegb_coupled_.empty() || !cegb_lazy_.empty()) CegbAfterSplit(s.feature, P);   // before the window is partitioned: the whole leaf passes the split
   const FeatureMeta& m = ds_->feature_meta[s.feature];
   const BinMapper& bm = *ds_->mappers[m.real_index];
   // stable partition of the leaf's window
@@ -676,6 +704,28 @@ int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
     SubtractHistogram(parent_copy, *smaller, larger);
   }
   return right_id;
+}
+
+double CPUTreeLearner::CegbFeaturePenalty(int inner_feature, const LeafState& leaf) const {
+  const int real = ds_->feature_meta[inner_feature].real_index;
+  double pen = 0.0;
+  if (!cegb_coupled_.empty() && !cegb_feature_used_[real]) pen += cfg_.cegb_tradeoff * cegb_coupled_[real];
+  if (!cegb_lazy_.empty() && cegb_lazy_[real] > 0.0) {
+    const std::vector<bool>& paid = cegb_row_paid_[real];
+    data_size_t unpaid = 0;
+    for (data_size_t k = 0; k < leaf.count; ++k) unpaid += paid[indices_[leaf.begin + k]] ? 0 : 1;
+    pen += cfg_.cegb_tradeoff * cegb_lazy_[real] * static_cast<double>(unpaid);
+  }
+  return pen;
+}
+
+void CPUTreeLearner::CegbAfterSplit(int inner_feature, const LeafState& leaf) {
+  const int real = ds_->feature_meta[inner_feature].real_index;
+  if (!cegb_coupled_.empty()) cegb_feature_used_[real] = 1;
+  if (!cegb_lazy_.empty() && cegb_lazy_[real] > 0.0) {
+    std::vector<bool>& paid = cegb_row_paid_[real];
+    for (data_size_t k = 0; k < leaf.count; ++k) paid[indices_[leaf.begin + k]] = true;
+  }
 }
 
 Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_index) {

@@ -31,6 +31,10 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
       Log::Warning("linear_tree trains on the host (the leaf regressions need the raw feature values)");
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
+    if ((!cfg.cegb_penalty_feature_coupled.empty() || !cfg.cegb_penalty_feature_lazy.empty()) && is_cuda_) {
+      Log::Warning("Per-feature CEGB penalties (cegb_penalty_feature_coupled / _lazy) train on the host learner");
+      is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
+    }
     if (!cfg.forcedsplits_filename.empty() && is_cuda_) {
       Log::Warning("forcedsplits_filename trains on the host learner");
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";

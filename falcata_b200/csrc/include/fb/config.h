@@ -72,6 +72,14 @@ namespace fb {
   X(double, refit_decay_rate, 0.9, "") \
   X(double, cegb_tradeoff, 1.0, "") \
   X(double, cegb_penalty_split, 0.0, "") \
+  X(std::string, cegb_penalty_feature_lazy, "", "") \
+  X(std::string, cegb_penalty_feature_coupled, "", "") \
+  X(bool, force_col_wise, false, "") \
+  X(bool, force_row_wise, false, "") \
+  X(double, histogram_pool_size, -1.0, "hist_pool_size") \
+  X(std::string, parser_config_file, "", "") \
+  X(bool, precise_float_parser, false, "") \
+  X(int, file_load_progress_interval_bytes, 0, "") \
   X(double, path_smooth, 0.0, "") \
   X(std::string, interaction_constraints, "", "") \
   X(int, verbosity, 1, "verbose") \

@@ -313,3 +313,28 @@ def test_auc_mu_matches_pairwise_definition():
         want = brute(raw, W, np.ones(n) if weights is None else weights)
         assert abs(rec["train"]["auc_mu"][-1] - want) < 1e-9
         assert rec["train"]["auc_mu"][-1] > 0.8
+
+
+def test_cegb_per_feature_penalties_steer_feature_choice():
+    """Coupled penalty: a feature is charged until the model first uses it, so an expensive twin of a cheap feature is
+    never bought. Lazy penalty: charged per row not yet sent through the feature, which keeps a costly feature out
+    unless it pays for itself."""
+    rng = np.random.default_rng(13)
+    n = 3000
+    a = rng.normal(size=n); b = rng.normal(size=n)
+    X = np.column_stack([a, a + 0.01 * rng.normal(size=n), b, rng.normal(size=n)])   # column 1 is a noisy twin of column 0
+    y = a + 0.5 * b + 0.1 * rng.normal(size=n)
+    base = {"objective": "regression", "num_leaves": 15, "verbosity": -1, "min_data_in_leaf": 10, "learning_rate": 0.2}
+    free = fb.train(dict(base), fb.Dataset(X, y), 15)
+    imp_free = free.feature_importance()
+    assert imp_free[0] > 0 and imp_free[1] > 0                                          # without penalties both twins get used
+    coupled = fb.train(dict(base, cegb_tradeoff=1.0, cegb_penalty_feature_coupled=[0.0, 1e6, 0.0, 0.0]), fb.Dataset(X, y), 15)
+    imp = coupled.feature_importance()
+    assert imp[1] == 0 and imp[0] > 0 and imp[2] > 0
+    # a coupled price below the feature's worth is paid once: the feature is used afterwards like any other
+    cheap = fb.train(dict(base, cegb_tradeoff=1.0, cegb_penalty_feature_coupled=[1.0, 1.0, 1.0, 1.0]), fb.Dataset(X, y), 15)
+    assert cheap.feature_importance()[0] + cheap.feature_importance()[1] > 0 and cheap.feature_importance()[2] > 0
+    lazy = fb.train(dict(base, cegb_tradeoff=1.0, cegb_penalty_feature_lazy=[0.0, 0.0, 1e3, 0.0]), fb.Dataset(X, y), 15)
+    assert lazy.feature_importance()[2] == 0 and lazy.feature_importance()[0] > 0
+    with pytest.raises(fb.FalcataError):
+        fb.train(dict(base, cegb_penalty_feature_coupled=[1.0, 2.0]), fb.Dataset(X, y), 2)
