@@ -633,7 +633,10 @@ class Dataset:
             data = data.detach().cpu().numpy()
         if hasattr(data, "values") and not isinstance(data, np.ndarray):
             data = data.values
-        arr = np.ascontiguousarray(np.asarray(data).reshape(-1), dtype=dtype)
+        arr = np.asarray(data)
+        if name == "label" and arr.ndim == 2 and arr.shape[1] > 1:
+            arr = arr.T          # several regression targets: the library keeps them [target][row]
+        arr = np.ascontiguousarray(arr.reshape(-1), dtype=dtype)
         _safe_call(lib.FB_DatasetSetField(self._handle, name.encode(), arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(arr.size), _DTYPE_CODE[arr.dtype]))
 
     def get_field(self, name: str) -> Optional[np.ndarray]:

@@ -234,7 +234,11 @@ int FB_DatasetSetField(DatasetHandle handle, const char* field_name, const void*
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; ++i) (*v)[i] = dtype == kF64 ? static_cast<float>(static_cast<const double*>(data)[i]) : static_cast<float>(static_cast<const int32_t*>(data)[i]);
   };
-  if (f == "label" || f == "target") { if (n != ds->num_data) Log::Fatal("Length of labels (%lld) differs from the number of rows (%d)", static_cast<long long>(n), ds->num_data); std::vector<float> v; as_float(&v); ds->metadata.label.swap(v); }
+  if (f == "label" || f == "target") {
+    // one value per row, or [target][row] for several regression targets (multi_regression)
+    if (ds->num_data <= 0 || n < ds->num_data || n % ds->num_data != 0) Log::Fatal("Length of labels (%lld) differs from the number of rows (%d)", static_cast<long long>(n), ds->num_data);
+    std::vector<float> v; as_float(&v); ds->metadata.label.swap(v);
+  }
   else if (f == "weight" || f == "weights") { if (n == 0) ds->metadata.SetWeights(nullptr, 0); else { std::vector<float> v; as_float(&v); ds->metadata.SetWeights(v.data(), static_cast<data_size_t>(n)); } }
   else if (f == "group" || f == "query") { if (dtype != kI32) Log::Fatal("group must be int32"); ds->metadata.num_data = ds->num_data; ds->metadata.SetGroup(static_cast<const int32_t*>(data), static_cast<data_size_t>(n)); }
   else if (f == "init_score") {

@@ -81,6 +81,7 @@ std::string Config::ParseObjectiveAlias(const std::string& in) {
       n == "l2_root" || n == "root_mean_squared_error" || n == "rmse") return "regression";
   if (n == "regression_l1" || n == "mean_absolute_error" || n == "l1" || n == "mae") return "regression_l1";
   if (n == "multiclass" || n == "softmax") return "multiclass";
+  if (n == "multi_regression" || n == "multi_regression_l2" || n == "multiregression") return "multi_regression";
   if (n == "multiclassova" || n == "multiclass_ova" || n == "ova" || n == "ovr") return "multiclassova";
   if (n == "xentropy" || n == "cross_entropy") return "cross_entropy";
   if (n == "xentlambda" || n == "cross_entropy_lambda") return "cross_entropy_lambda";
@@ -197,14 +198,15 @@ void Config::Resolve(bool cuda_available) {
   for (auto v : ParseNumArray<int>(monotone_constraints, ',')) monotone_vec.push_back(static_cast<int8_t>(v));
   feature_contri_vec = ParseNumArray<double>(feature_contri, ',');
   max_bin_by_feature_vec = ParseNumArray<int>(max_bin_by_feature, ',');
-  if (objective == "multiclass" || objective == "multiclassova") num_tree_per_iteration = num_class;
+  if (objective == "multiclass" || objective == "multiclassova" || objective == "multi_regression") num_tree_per_iteration = num_class;
   else num_tree_per_iteration = (objective == "custom" ? std::max(1, num_class) : 1);
 }
 
 void Config::CheckParamConflict() {
   if ((objective == "multiclass" || objective == "multiclassova") && num_class <= 1)
     Log::Fatal("Number of classes should be specified and greater than 1 for multiclass training");
-  if (objective != "multiclass" && objective != "multiclassova" && objective != "custom" && num_class != 1)
+  if (objective == "multi_regression" && num_class <= 1) Log::Fatal("multi_regression requires num_class > 1 (num_class carries the number of targets)");
+  if (objective != "multiclass" && objective != "multiclassova" && objective != "multi_regression" && objective != "custom" && num_class != 1)
     Log::Fatal("Number of classes must be 1 for non-multiclass training");
   if (num_leaves < 2) Log::Fatal("num_leaves must be >= 2");
   if (num_leaves > 131072) Log::Fatal("num_leaves must be <= 131072");

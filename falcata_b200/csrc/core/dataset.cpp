@@ -423,7 +423,12 @@ Dataset* Dataset::Subset(const data_size_t* idx, data_size_t n) const {
     if (bin_bytes == 1) memcpy(&ds->bins8[d], &bins8[s], row_stride); else memcpy(&ds->bins16[d], &bins16[s], row_stride * 2);
     if (has_raw()) memcpy(&ds->raw[static_cast<size_t>(i) * num_total_features], &raw[static_cast<size_t>(idx[i]) * num_total_features], sizeof(float) * num_total_features);
   }
-  if (!metadata.label.empty()) { ds->metadata.label.resize(n); for (data_size_t i = 0; i < n; ++i) ds->metadata.label[i] = metadata.label[idx[i]]; }
+  if (!metadata.label.empty()) {
+    const size_t targets = num_data > 0 ? std::max<size_t>(1, metadata.label.size() / static_cast<size_t>(num_data)) : 1;   // [target][row]
+    ds->metadata.label.resize(static_cast<size_t>(n) * targets);
+    for (size_t t = 0; t < targets; ++t)
+      for (data_size_t i = 0; i < n; ++i) ds->metadata.label[t * n + i] = metadata.label[t * num_data + idx[i]];
+  }
   if (!metadata.weights.empty()) { ds->metadata.weights.resize(n); for (data_size_t i = 0; i < n; ++i) ds->metadata.weights[i] = metadata.weights[idx[i]]; }
   if (!metadata.init_score.empty()) {
     int k = static_cast<int>(metadata.init_score.size() / num_data);

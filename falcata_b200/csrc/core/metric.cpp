@@ -58,14 +58,18 @@ struct Pointwise : public MetricBase {
   bool HigherBetter() const override { return Loss::kHigherBetter; }
   std::vector<double> Eval(const double* score, const ObjectiveFunction* obj) const override {
     double s = 0;
+    // several regression targets (multi_regression): labels and scores are [target][row]; the loss is averaged over both
+    const int targets = (md_ != nullptr && n_ > 0 && md_->label.size() > static_cast<size_t>(n_) && obj != nullptr && obj->NumModelPerIteration() > 1)
+                            ? static_cast<int>(md_->label.size() / static_cast<size_t>(n_)) : 1;
+    const int64_t total = static_cast<int64_t>(n_) * targets;
 #pragma omp parallel for schedule(static) reduction(+ : s) num_threads(RowThreads(n_))
-    for (data_size_t i = 0; i < n_; ++i) {
+    for (int64_t i = 0; i < total; ++i) {
       double v = score[i];
-      if (convert_ && obj != nullptr) obj->ConvertOutput(&score[i], &v);
-      s += Loss::Point(label_[i], v, cfg_) * (weights_ ? weights_[i] : 1.0);
+      if (convert_ && obj != nullptr && targets == 1) obj->ConvertOutput(&score[i], &v);
+      s += Loss::Point(label_[i], v, cfg_) * (weights_ ? weights_[i % n_] : 1.0);
     }
     Network::SumDouble(&s, 1);
-    double r = s / sum_w_;
+    double r = s / (sum_w_ * targets);
     return {sqrt_out_ ? std::sqrt(r) : r};
   }
 };

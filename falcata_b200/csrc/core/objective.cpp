@@ -290,6 +290,50 @@ class BinaryLogloss : public ObjectiveFunction {
   bool need_train_ = true; double lw_[2]; int64_t num_pos_ = 0, num_neg_ = 0;
 };
 
+// Several regression targets at once: num_class carries the number of targets, labels are [target][row], every round
+// grows one L2 tree per target. Parity: src/objective/multi_regression_objective.hpp (MultiRegressionL2).
+class MultiRegressionL2 : public ObjectiveFunction {
+ public:
+  explicit MultiRegressionL2(const Config& cfg) : k_(cfg.num_class) {
+    if (k_ <= 1) Log::Fatal("multi_regression requires num_class > 1 (num_class carries the number of targets)");
+  }
+  const char* GetName() const override { return "multi_regression"; }
+  void Init(const Metadata& md, data_size_t n) override {
+    n_ = n; label_ = md.label.data(); weights_ = md.weights.empty() ? nullptr : md.weights.data();
+    if (md.label.size() != static_cast<size_t>(n) * k_)
+      Log::Fatal("multi_regression with num_class=%d expects %zu label values (num_data * num_class, target-major), but got %zu. Pass y as a 2D array of shape [num_data, num_class].",
+                 k_, static_cast<size_t>(n) * k_, md.label.size());
+    std::vector<double> sums(k_ + 1, 0.0);
+    for (data_size_t i = 0; i < n; ++i) sums[k_] += weights_ ? weights_[i] : 1.0;
+    for (int t = 0; t < k_; ++t) {
+      const label_t* y = label_ + static_cast<size_t>(t) * n;
+      double s = 0.0;
+#pragma omp parallel for schedule(static) reduction(+ : s) num_threads(RowThreads(n))
+      for (data_size_t i = 0; i < n; ++i) s += y[i] * (weights_ ? weights_[i] : 1.0);
+      sums[t] = s;
+    }
+    Network::SumDouble(sums.data(), k_ + 1);
+    means_.assign(k_, 0.0);
+    for (int t = 0; t < k_; ++t) means_[t] = sums[t] / std::max(sums[k_], kEpsilon);
+  }
+  void GetGradients(const double* s, score_t* g, score_t* h) const override {
+    const int64_t total = static_cast<int64_t>(n_) * k_;
+#pragma omp parallel for schedule(static) num_threads(RowThreads(n_))
+    for (int64_t o = 0; o < total; ++o) {
+      const double w = weights_ ? weights_[o % n_] : 1.0;
+      g[o] = static_cast<score_t>((s[o] - label_[o]) * w); h[o] = static_cast<score_t>(w);
+    }
+  }
+  void ConvertOutput(const double* in, double* out) const override { for (int t = 0; t < k_; ++t) out[t] = in[t]; }
+  std::string ToString() const override { return std::string(GetName()) + " num_class:" + std::to_string(k_); }
+  int NumModelPerIteration() const override { return k_; }
+  bool IsConstantHessian() const override { return weights_ == nullptr; }
+  double BoostFromScore(int t) const override { return means_[t]; }
+
+ private:
+  int k_; data_size_t n_ = 0; const label_t* label_ = nullptr; const label_t* weights_ = nullptr; std::vector<double> means_;
+};
+
 class MulticlassSoftmax : public ObjectiveFunction {
  public:
   explicit MulticlassSoftmax(const Config& cfg) : k_(cfg.num_class) { factor_ = static_cast<double>(k_) / (k_ - 1.0); }
@@ -522,6 +566,7 @@ ObjectiveFunction* CreateObjective(const std::string& name, const Config& cfg) {
   if (name == "tweedie") return new RegressionTweedie(cfg);
   if (name == "binary") return new BinaryLogloss(cfg);
   if (name == "multiclass") return new MulticlassSoftmax(cfg);
+  if (name == "multi_regression") return new MultiRegressionL2(cfg);
   if (name == "multiclassova") return new MulticlassOVA(cfg);
   if (name == "cross_entropy") return new CrossEntropy(cfg);
   if (name == "cross_entropy_lambda") return new CrossEntropyLambda(cfg);

@@ -428,6 +428,7 @@ std::vector<double> CudaEngine::EvalMetric(int data_idx, const std::string& name
   }
   if (kind < 0) return {};
   if ((kind == kMetL2 || kind == kMetRMSE || kind == kMetL1) && cfg_.reg_sqrt) return {};
+  if ((kind == kMetL2 || kind == kMetRMSE || kind == kMetL1) && K_ > 1) return {};   // several regression targets: the host metric averages over targets
   const Dataset* ds = data_idx == 0 ? train_ : valid_[data_idx - 1].ds;
   DeviceDataset* dd = data_idx == 0 ? dd_ : valid_[data_idx - 1].dd;
   const float* score = data_idx == 0 ? score_.get() : valid_[data_idx - 1].score.get();

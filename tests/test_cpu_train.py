@@ -338,3 +338,31 @@ def test_cegb_per_feature_penalties_steer_feature_choice():
     assert lazy.feature_importance()[2] == 0 and lazy.feature_importance()[0] > 0
     with pytest.raises(fb.FalcataError):
         fb.train(dict(base, cegb_penalty_feature_coupled=[1.0, 2.0]), fb.Dataset(X, y), 2)
+
+
+def test_multi_regression_trains_one_tree_per_target():
+    """objective=multi_regression: y is [rows, targets]; each round grows a tree per target; prediction is [rows, targets];
+    each target's column equals a single-target L2 model trained alone on it; l2 is averaged over rows and targets."""
+    rng = np.random.default_rng(17)
+    n = 1200
+    X = rng.normal(size=(n, 6))
+    Y = np.column_stack([X[:, 0] + 0.1 * rng.normal(size=n), -2 * X[:, 1] + X[:, 2] + 5.0, np.sin(X[:, 3])])
+    p = {"objective": "multi_regression", "num_class": 3, "num_leaves": 7, "verbosity": -1, "min_data_in_leaf": 5, "metric": "l2", "learning_rate": 0.3}
+    rec = {}
+    ds = fb.Dataset(X, Y)
+    bst = fb.train(p, ds, 12, valid_sets=[ds], valid_names=["train"], callbacks=[fb.record_evaluation(rec)])
+    assert bst.num_trees() == 36 and bst.num_model_per_iteration() == 3
+    pred = np.asarray(bst.predict(X))
+    assert pred.shape == (n, 3)
+    for t in range(3):
+        one = fb.train({"objective": "regression", "num_leaves": 7, "verbosity": -1, "min_data_in_leaf": 5, "learning_rate": 0.3}, fb.Dataset(X, Y[:, t]), 12)
+        assert np.allclose(pred[:, t], one.predict(X), atol=1e-9)
+    assert abs(rec["train"]["l2"][-1] - np.mean((pred - Y.astype(np.float32)) ** 2)) < 1e-7   # labels are kept in float32
+    again = fb.Booster(model_str=bst.model_to_string())
+    assert np.array_equal(np.asarray(again.predict(X)), pred)
+    with pytest.raises(fb.FalcataError):
+        fb.train(dict(p, num_class=2), fb.Dataset(X, Y), 2)          # three label columns for two targets
+    # cross-validation subsets keep the targets together
+    res = fb.cv(p, fb.Dataset(X, Y), num_boost_round=5, nfold=3, stratified=False, seed=1)
+    key = [k for k in res if k.endswith("l2-mean")][0]
+    assert res[key][-1] < res[key][0]

@@ -430,3 +430,23 @@ def test_linear_tree_with_cuda_inputs_falls_back_to_the_host():
     assert float(np.mean((ph - y) ** 2)) < 0.05
     reloaded = fb.Booster(model_str=b.model_to_string())
     assert np.allclose(reloaded.predict(Xd).cpu().numpy(), ph, atol=1e-5)
+
+
+def test_multi_regression_on_the_device_engine():
+    """Several regression targets on the device: trees are grown by the device engine (gradients come from the host
+    objective), and every target's column equals a single-target device model."""
+    rng = np.random.default_rng(23)
+    n = 5000
+    X = rng.normal(size=(n, 8)).astype(np.float32)
+    Y = np.column_stack([X[:, 0] + 0.1 * rng.normal(size=n), -2 * X[:, 1] + X[:, 2] + 5.0])
+    p = {"objective": "multi_regression", "num_class": 2, "num_leaves": 15, "verbosity": -1, "device_type": "cuda", "quant_mode": "none", "metric": "l2"}
+    rec = {}
+    ds = fb.Dataset(X, Y)
+    bst = fb.train(p, ds, 10, valid_sets=[ds], valid_names=["train"], callbacks=[fb.record_evaluation(rec)])
+    pred = np.asarray(bst.predict(X))
+    assert pred.shape == (n, 2) and bst.num_trees() == 20
+    assert rec["train"]["l2"][-1] < 0.3 * rec["train"]["l2"][0]
+    assert abs(rec["train"]["l2"][-1] - np.mean((pred - Y.astype(np.float32)) ** 2)) < 1e-4
+    for t in range(2):
+        one = fb.train({"objective": "regression", "num_leaves": 15, "verbosity": -1, "device_type": "cuda", "quant_mode": "none"}, fb.Dataset(X, Y[:, t]), 10)
+        np.testing.assert_allclose(pred[:, t], one.predict(X), rtol=1e-4, atol=1e-4)
