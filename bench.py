@@ -174,6 +174,10 @@ def reference_arm(args) -> None:
     # On an NVSwitch box peer-to-peer transport is the natural NCCL setting; the reference only sets
     # NCCL_P2P_DISABLE=1 when the variable is unset (a workaround for PCIe boxes).
     os.environ.setdefault("NCCL_P2P_DISABLE", "0")
+    # The launcher exports OMP_NUM_THREADS=1 to every rank; the reference refuses num_gpu above its thread count and
+    # does its host work (binning) with OpenMP: this one working process gets all the cores, as in a stand-alone run.
+    host_threads = max(n_gpus, len(os.sched_getaffinity(0)))
+    os.environ["OMP_NUM_THREADS"] = str(host_threads)
     _preload(["libnvrtc.so.12", "libnccl.so.2"])
     sys.path.insert(0, ref_dir)
     try:
@@ -201,10 +205,21 @@ def reference_arm(args) -> None:
         for d in range(n_gpus):
             torch.cuda.synchronize(d)
 
+    # With num_gpu > 1 the reference gathers the training scores into a HOST vector and hands that pointer to its CUDA
+    # metric, whose kernel dereferences it (src/boosting/cuda/nccl_gbdt.cpp: EvalOneMetric; src/metric/cuda/
+    # cuda_pointwise_metric.cu: LaunchEvalKernel). On this box that ended in "an illegal memory access was encountered"
+    # at cuda_pointwise_metric.cu:62 (2 GPUs, after 23 clean rounds). So at N > 1 this arm never evaluates a metric:
+    # the kernel-only figure is measured, the training loss is not read, and the end-to-end figure (which needs the
+    # per-round metric read) is reported as unavailable.
+    METRIC_FAULT = ("not run at num_gpu > 1: the reference's CUDA metric is handed a host pointer there and faulted on this box "
+                    "(illegal memory access at src/metric/cuda/cuda_pointwise_metric.cu:62)")
+
     def params_for(depth_capped: bool):
         p = {"objective": "binary", "num_leaves": 255, "max_bin": 63, "learning_rate": 0.1, "quant_mode": "stochastic", "quant_bins": 4,
              "cuda_precision": "fp32", "tree_learner": "serial", "device_type": "cuda", "num_gpu": n_gpus, "verbosity": -1, "min_data_in_leaf": 20,
-             "metric": "binary_logloss"}
+             "metric": "binary_logloss", "num_threads": host_threads}
+        if n_gpus > 1:
+            p["metric"] = "none"   # see METRIC_FAULT below: no metric object is created, none is evaluated
         if depth_capped:
             p["max_depth"] = 8
         return p
@@ -222,7 +237,7 @@ def reference_arm(args) -> None:
                 bst.update()
             sync_all()
             dt = time.perf_counter() - t0
-        ev = bst.eval_train()
+        ev = bst.eval_train() if n_gpus == 1 else []
         logloss = ev[0][2] if ev else None
         md5 = model_md5(bst.model_to_string())
         del bst, ds
@@ -249,7 +264,10 @@ def reference_arm(args) -> None:
         except Exception as e:   # noqa: BLE001
             out["leafwise"] = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
     # ---- end to end: host matrix -> reference Dataset -> K rounds with the training metric read back every round ----
-    if not args.no_e2e:
+    if not args.no_e2e and n_gpus > 1:
+        out["e2e"] = {"unavailable": METRIC_FAULT}
+        out["config"]["train_logloss_after_run"] = METRIC_FAULT
+    elif not args.no_e2e:
         try:
             Xh = X.cpu().numpy()
             del X
