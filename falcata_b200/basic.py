@@ -299,6 +299,24 @@ def _materialize_sequences(data: Any) -> np.ndarray:
     return np.concatenate(parts, axis=0) if parts else np.zeros((0, 0), dtype=np.float32)
 
 
+def _trains_on_host(params: Dict[str, Any]) -> bool:
+    """Parameters with which a device booster hands the training to the host learner (the native side warns)."""
+    def text(*names: str) -> str:
+        for k in names:
+            if params.get(k) is not None:
+                return str(params[k]).lower()
+        return ""
+    if text("boosting", "boosting_type", "boost") in ("dart", "rf", "random_forest"):
+        return True
+    if text("forcedsplits_filename", "fs", "forced_splits_filename", "forced_splits_file", "forced_splits"):
+        return True
+    for k in ("cegb_penalty_feature_coupled", "cegb_penalty_feature_lazy"):
+        v = params.get(k)
+        if v is not None and len(v) > 0:
+            return True
+    return False
+
+
 def _wants_linear(params: Dict[str, Any], reference: Any = None) -> bool:
     """linear_tree keeps the raw feature values beside the bins, which only the host construction does."""
     for k in ("linear_tree", "linear_trees"):
@@ -854,6 +872,8 @@ class Booster:
                 raise TypeError(f"Training data should be Dataset instance, met {type(train_set).__name__}")
             merged = dict(train_set.params); merged.update(self.params)
             train_set.params = {**train_set.params, **{k: v for k, v in self.params.items() if k in _DATASET_PARAMS}}
+            if _trains_on_host(self.params):
+                train_set.params["keep_host_bins"] = True   # the host learner will do the training: it needs host-resident bins
             with _tag("booster: dataset construct"):
                 train_set.construct()
             with _tag("booster: native create (objective, metrics, device engine)"):
