@@ -64,7 +64,7 @@ def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total
     over ranks. Each rank contributes the sampled rows of its shard; the shards are concatenated in
     rank order. ``replicated``: every rank holds ALL rows (feature-parallel training), so the local sample
     is already the global one and nothing is exchanged. ``after_draw``: called once the row draw (which may run on the
-    device) is done and only host work and collectives remain. Returns (sample [ns, ncol] in the matrix's own element
+    device) and, with several ranks, the exchange of the sample are done and only host work remains. Returns (sample [ns, ncol] in the matrix's own element
     type - float16/32/64, int8/16/32, uint8 - so nothing is widened on the way to the host; total rows)."""
     import torch
 
@@ -84,7 +84,8 @@ def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total
             offset = int(sum(offs[:rank]))
     p = min(1.0, sample_cnt / max(1, total))
     idx = _bernoulli_rows(t, n, offset, seed, p)
-    if after_draw is not None:
+    exchange = bool(d and ws > 1)
+    if after_draw is not None and not exchange:
         after_draw()
     keep = t.dtype in (torch.float16, torch.float32, torch.float64, torch.int8, torch.int16, torch.int32, torch.uint8)
     sdt = t.dtype if keep else torch.float64
@@ -103,6 +104,8 @@ def gather_bin_sample(t: Any, sample_cnt: int, seed: int, offset: int = 0, total
         outs = torch.empty((ws, cap, t.shape[1]), dtype=sdt, device=cdev)
         d.all_gather_into_tensor(outs, padded) if on_dev else d.all_gather(list(outs.unbind(0)), padded)
         outs = outs.cpu().numpy()
+        if after_draw is not None:
+            after_draw()   # the sample's small copies are through: the caller's large copy no longer delays them
         local = np.concatenate([outs[r, : sizes[r]] for r in range(ws)], axis=0)
     else:
         local = picked.cpu().numpy()
