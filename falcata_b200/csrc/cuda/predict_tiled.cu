@@ -36,7 +36,11 @@ struct ChunkDesc { long long offset; int bytes; int ntrees; int cls; int first_t
 template <typename T> __device__ inline float ToF(T v) { return static_cast<float>(v); }
 template <> __device__ inline float ToF<__half>(__half v) { return __half2float(v); }
 
+// PLAIN: no node of the forest treats zero or NaN as missing; NaN inputs were replaced by 0 when the tile was staged
+// (that is what such nodes do with them), so a step is one comparison.
+template <bool PLAIN>
 __device__ __forceinline__ bool GoLeft(float v, float thr, unsigned int meta) {
+  if (PLAIN) return v <= thr;
   const unsigned int mt = meta >> 30;
   const bool nan = isnan(v);
   if (nan && mt != 2u) v = 0.f;
@@ -45,7 +49,7 @@ __device__ __forceinline__ bool GoLeft(float v, float thr, unsigned int meta) {
 }
 
 // LEAF: write the leaf index of every (row, tree) instead of summing outputs.
-template <typename T, bool LEAF>
+template <typename T, bool LEAF, bool PLAIN>
 __global__ void __launch_bounds__(kTileThreads, 1)
 PredictTiledKernel(const unsigned char* __restrict__ blob, const ChunkDesc* __restrict__ chunks, int num_chunks, const int* __restrict__ used, int num_used,
                    const T* __restrict__ data, int nrow, int ncol, int row_major, int num_class, int trees_total, float inv_avg, float* __restrict__ out,
@@ -61,7 +65,11 @@ PredictTiledKernel(const unsigned char* __restrict__ blob, const ChunkDesc* __re
     __syncthreads();   // the previous tile's walks are over before its rows and ring buffers are overwritten
     // ---- stage the tile: rows_s[j][r] = value of used feature j in row row0 + r ----
     if (!row_major) {
-      for (int j = 0; j < num_used; ++j) rows_s[j * kTileThreads + tid] = row < nrow ? ToF<T>(data[static_cast<size_t>(used[j]) * nrow + row]) : 0.f;
+      for (int j = 0; j < num_used; ++j) {
+        float v = row < nrow ? ToF<T>(data[static_cast<size_t>(used[j]) * nrow + row]) : 0.f;
+        if (PLAIN && isnan(v)) v = 0.f;
+        rows_s[j * kTileThreads + tid] = v;
+      }
     } else {
       // 32 x 32 pieces: read with the lanes along the features (coalesced), turn in a padded scratch piece that
       // borrows the still unused ring, write with the lanes along the rows (conflict-free)
@@ -74,7 +82,9 @@ PredictTiledKernel(const unsigned char* __restrict__ blob, const ChunkDesc* __re
 #pragma unroll 8
         for (int k = 0; k < 32; ++k) {
           const int r = row0 + rp * 32 + k;
-          scratch[k * 33 + lane] = (col >= 0 && r < nrow) ? ToF<T>(data[static_cast<size_t>(r) * ncol + col]) : 0.f;
+          float v = (col >= 0 && r < nrow) ? ToF<T>(data[static_cast<size_t>(r) * ncol + col]) : 0.f;
+          if (PLAIN && isnan(v)) v = 0.f;
+          scratch[k * 33 + lane] = v;
         }
         __syncwarp();
 #pragma unroll 8
@@ -132,7 +142,7 @@ PredictTiledKernel(const unsigned char* __restrict__ blob, const ChunkDesc* __re
           for (int q = 0; q < kWalks; ++q) v[q] = my[(live[q] ? (nd[q].meta & 0xFFFFu) : 0u) * kTileThreads];
 #pragma unroll
           for (int q = 0; q < kWalks; ++q) {
-            const int next = base[q] + static_cast<int>((nd[q].meta >> 16) & 0x1FFFu) + (GoLeft(v[q], nd[q].value, nd[q].meta) ? 0 : 1);
+            const int next = base[q] + static_cast<int>((nd[q].meta >> 16) & 0x1FFFu) + (GoLeft<PLAIN>(v[q], nd[q].value, nd[q].meta) ? 0 : 1);
             at[q] = live[q] ? next : at[q];
           }
           any = false;
@@ -203,11 +213,13 @@ bool DevicePredictTiled(const GBDT* gbdt, const void* device_data, int dtype, in
   if (dtype != kF32 && dtype != kF64 && dtype != kF16) return false;
   // features the forest reads, in ascending order
   std::vector<int> slot_of_feature(std::max(1, gbdt->max_feature_idx_ + 1), -1);
+  bool plain = true;   // no node with a missing type: NaN reads as 0 everywhere, zero is an ordinary value
   for (int t = first_tree; t < first_tree + num_trees; ++t) {
     const Tree& T = *gbdt->models_[t];
     if (T.is_linear) return false;
     for (int sidx = 0; sidx < T.num_leaves - 1; ++sidx) {
       if (T.decision_type[sidx] & kCategoricalMask) return false;
+      if (Tree::MissingTypeOf(T.decision_type[sidx]) != 0) plain = false;
       const int f = T.split_feature[sidx];
       if (f < 0 || f >= static_cast<int>(slot_of_feature.size())) return false;
       slot_of_feature[f] = 0;
@@ -255,19 +267,21 @@ bool DevicePredictTiled(const GBDT* gbdt, const void* device_data, int dtype, in
   const int tiles = (nrow + kTileThreads - 1) / kTileThreads;
   const int grid = std::min(tiles, sms);
   const int nc = static_cast<int>(chunks.size()), nu = static_cast<int>(used.size());
-#define FB_TILED(T, LEAF)                                                                                                          \
+#define FB_TILED_P(T, LEAF, PLAIN)                                                                                                 \
   {                                                                                                                                \
     static bool attr = false;                                                                                                      \
-    if (!attr) { FB_CUDA(cudaFuncSetAttribute(PredictTiledKernel<T, LEAF>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr = true; } \
-    PredictTiledKernel<T, LEAF><<<grid, kTileThreads, smem, s>>>(d_blob.get(), d_chunks.get(), nc, d_used.get(), nu, static_cast<const T*>(device_data), nrow, ncol, \
-                                                                 row_major ? 1 : 0, K, num_trees, inv_avg, out_device, reinterpret_cast<int*>(out_device));           \
+    if (!attr) { FB_CUDA(cudaFuncSetAttribute(PredictTiledKernel<T, LEAF, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); attr = true; } \
+    PredictTiledKernel<T, LEAF, PLAIN><<<grid, kTileThreads, smem, s>>>(d_blob.get(), d_chunks.get(), nc, d_used.get(), nu, static_cast<const T*>(device_data), nrow, ncol, \
+                                                                        row_major ? 1 : 0, K, num_trees, inv_avg, out_device, reinterpret_cast<int*>(out_device));          \
   }
+#define FB_TILED(T, LEAF) { if (plain) FB_TILED_P(T, LEAF, true) else FB_TILED_P(T, LEAF, false) }
   if (leaf_index) {
     if (dtype == kF32) FB_TILED(float, true) else if (dtype == kF64) FB_TILED(double, true) else FB_TILED(__half, true)
   } else {
     if (dtype == kF32) FB_TILED(float, false) else if (dtype == kF64) FB_TILED(double, false) else FB_TILED(__half, false)
   }
 #undef FB_TILED
+#undef FB_TILED_P
   FB_LAUNCHED(); FB_KERNEL_CHECK();
   FB_CUDA(cudaStreamSynchronize(s));   // the packed forest lives in this call's buffers
   return true;

@@ -79,3 +79,16 @@ def test_predict_with_categorical_forest_takes_general_kernel():
     # leaf indices of a forest the device kernel does not cover come from the host, as a device tensor all the same
     leaf = bst.predict(Xd, pred_leaf=True)
     assert leaf.is_cuda and np.array_equal(leaf.cpu().numpy(), np.asarray(bst.predict(X, pred_leaf=True)).reshape(5000, -1))
+
+
+def test_nan_inputs_to_a_forest_without_missing_handling_read_as_zero():
+    """A forest trained on complete data has no missing-aware node: NaN at prediction time is taken as 0, on the host
+    and in the device kernel's comparison-only walk."""
+    X, rng = _data(5000, 12, seed=9)
+    y = (X[:, 0] - X[:, 1] > 0).astype(np.float32)
+    bst = fb.train({"objective": "binary", "num_leaves": 31, "verbosity": -1}, fb.Dataset(X, y), 15)
+    Xn = X.copy(); Xn[rng.random(size=Xn.shape) < 0.2] = np.nan
+    host = bst.predict(Xn, raw_score=True)
+    dev = bst.predict(torch.from_numpy(Xn).cuda(), raw_score=True).cpu().numpy()
+    np.testing.assert_allclose(dev, host, rtol=1e-5, atol=1e-5)
+    assert np.array_equal(bst.predict(torch.from_numpy(Xn).cuda(), pred_leaf=True).cpu().numpy(), np.asarray(bst.predict(Xn, pred_leaf=True)).reshape(5000, -1))
