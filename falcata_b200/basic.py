@@ -421,6 +421,11 @@ class Dataset:
             return False
         if _wants_linear(params, self.reference):
             return False   # linear leaves are fitted on the host from the raw values
+        try:
+            if int(params.get("max_bin", 255)) > 255:
+                return False   # more than one byte per feature group: binned and trained on the host
+        except (TypeError, ValueError):
+            pass
         if not cuda_available():
             return False
         d = self.data

@@ -31,6 +31,12 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
       Log::Warning("linear_tree trains on the host (the leaf regressions need the raw feature values)");
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
+    if (is_cuda_ && train->max_group_bin > 256) {
+      // the device engine keeps one byte per feature group; wider groups (max_bin above 255) are trained by the host learner
+      if (!train->has_host_bins()) Log::Fatal("max_bin above 255 needs host-resident bins (the device engine stores one byte per feature group): build the Dataset from host data");
+      Log::Warning("max_bin above 255: the device engine stores one byte per feature group, training runs on the host learner");
+      is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
+    }
     if ((!cfg.cegb_penalty_feature_coupled.empty() || !cfg.cegb_penalty_feature_lazy.empty()) && is_cuda_) {
       Log::Warning("Per-feature CEGB penalties (cegb_penalty_feature_coupled / _lazy) train on the host learner");
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";

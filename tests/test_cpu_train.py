@@ -366,3 +366,14 @@ def test_multi_regression_trains_one_tree_per_target():
     res = fb.cv(p, fb.Dataset(X, Y), num_boost_round=5, nfold=3, stratified=False, seed=1)
     key = [k for k in res if k.endswith("l2-mean")][0]
     assert res[key][-1] < res[key][0]
+
+
+def test_more_than_255_bins_train_on_the_host_whatever_the_device():
+    rng = np.random.default_rng(31)
+    X = rng.normal(size=(6000, 4)); y = np.sin(3 * X[:, 0]) + 0.05 * rng.normal(size=6000)
+    p = {"objective": "regression", "num_leaves": 63, "max_bin": 1023, "verbosity": -1, "min_data_in_leaf": 5, "min_data_in_bin": 1}
+    b = fb.train(p, fb.Dataset(X, y, params={"max_bin": 1023, "min_data_in_bin": 1}), 10)
+    fine = np.mean((b.predict(X) - y) ** 2)
+    coarse = np.mean((fb.train(dict(p, max_bin=15), fb.Dataset(X, y, params={"max_bin": 15}), 10).predict(X) - y) ** 2)
+    assert fine < coarse
+    assert b.dump_model()["feature_infos"] is not None

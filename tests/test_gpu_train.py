@@ -450,3 +450,12 @@ def test_multi_regression_on_the_device_engine():
     for t in range(2):
         one = fb.train({"objective": "regression", "num_leaves": 15, "verbosity": -1, "device_type": "cuda", "quant_mode": "none"}, fb.Dataset(X, Y[:, t]), 10)
         np.testing.assert_allclose(pred[:, t], one.predict(X), rtol=1e-4, atol=1e-4)
+
+
+def test_more_than_255_bins_with_a_device_booster_fall_back_to_the_host_learner():
+    rng = np.random.default_rng(31)
+    X = rng.normal(size=(6000, 4)).astype(np.float32); y = np.sin(3 * X[:, 0]) + 0.05 * rng.normal(size=6000)
+    p = {"objective": "regression", "num_leaves": 63, "max_bin": 1023, "verbosity": -1, "min_data_in_leaf": 5, "min_data_in_bin": 1}
+    dev = fb.train(dict(p, device_type="cuda"), fb.Dataset(X, y, params={"max_bin": 1023, "min_data_in_bin": 1}), 10)
+    host = fb.train(dict(p, device_type="cpu"), fb.Dataset(X, y, params={"max_bin": 1023, "min_data_in_bin": 1}), 10)
+    assert model_body(dev.model_to_string()) == model_body(host.model_to_string())
