@@ -541,9 +541,26 @@ void CudaEngine::RenewLeavesFromTrueGradients(Tree* tree) {
 
 // Objectives whose leaf value is a statistic of the residuals (L1: median, quantile: the alpha-quantile): the
 // leaf windows and the scores come back to the host and the objective's own renewal runs there.
+void DeviceRenewPercentile(const LeafInfo* leaves_dev, const LeafInfo* leaves_host, int num_leaves, const int* idx0, const int* idx1, const float* score,
+                           const float* label, int n, double alpha, DevBuf<double>* keys_in, DevBuf<double>* keys_out, DevBuf<int>* offsets, DevBuf<double>* out_dev,
+                           DevBuf<char>* temp, double* out_host, cudaStream_t s);
+
 void CudaEngine::RenewLeavesByObjective(Tree* tree, int class_id) {
   const int nl = tree->num_leaves;
   leaves_.Download(h_leaves_.get(), nl, stream_);
+  const int kind = obj_->DeviceKind();
+  if ((kind == kObjL1 || kind == kObjQuantile) && dd_->weight.size() == 0 && !cfg_.reg_sqrt && getenv("FALCATA_RENEW_ON_HOST") == nullptr) {
+    // unweighted L1 / quantile: per-leaf percentile of the residuals by a segmented sort on the device
+    FB_CUDA(cudaStreamSynchronize(stream_));   // the leaf records are on the host now
+    std::vector<double> outs(nl, 0.0), have(nl, 0.0);
+    DeviceRenewPercentile(leaves_.get(), h_leaves_.get(), nl, idx_[0].get(), idx_[1].get(), score_.get() + static_cast<size_t>(class_id) * n_, dd_->label.get(), n_,
+                          kind == kObjL1 ? 0.5 : obj_->DeviceParam(0), &renew_in_, &renew_out_, &renew_off_, &renew_res_, &renew_temp_, outs.data(), stream_);
+    for (int l = 0; l < nl; ++l) have[l] = h_leaves_[l].count > 0 ? 1.0 : 0.0;
+    for (int l = 0; l < nl; ++l) if (have[l] == 0.0) outs[l] = 0.0;
+    if (data_parallel()) { Network::SumDouble(outs.data(), nl); Network::SumDouble(have.data(), nl); }   // ranks' statistics are averaged
+    for (int l = 0; l < nl; ++l) if (have[l] > 0) tree->SetLeafOutput(l, outs[l] / have[l]);
+    return;
+  }
   std::vector<int> h_idx0(n_), h_idx1(n_); std::vector<float> h_score(n_);
   FB_CUDA(cudaMemcpyAsync(h_idx0.data(), idx_[0].get(), sizeof(int) * n_, cudaMemcpyDeviceToHost, stream_));
   FB_CUDA(cudaMemcpyAsync(h_idx1.data(), idx_[1].get(), sizeof(int) * n_, cudaMemcpyDeviceToHost, stream_));

@@ -459,3 +459,23 @@ def test_more_than_255_bins_with_a_device_booster_fall_back_to_the_host_learner(
     dev = fb.train(dict(p, device_type="cuda"), fb.Dataset(X, y, params={"max_bin": 1023, "min_data_in_bin": 1}), 10)
     host = fb.train(dict(p, device_type="cpu"), fb.Dataset(X, y, params={"max_bin": 1023, "min_data_in_bin": 1}), 10)
     assert model_body(dev.model_to_string()) == model_body(host.model_to_string())
+
+
+@pytest.mark.parametrize("objective,extra", [("regression_l1", {}), ("quantile", {"alpha": 0.8})])
+def test_percentile_leaf_renewal_on_the_device_matches_the_host_path(objective, extra):
+    """L1 / quantile leaves are renewed from a per-leaf percentile of the residuals: the segmented-sort kernel path
+    gives the values of the host computation on downloaded scores."""
+    import os
+    rng = np.random.default_rng(41)
+    X = rng.normal(size=(20000, 8)).astype(np.float32)
+    y = X[:, 0] * 2 + np.abs(X[:, 1]) + rng.standard_t(3, size=20000)
+    p = dict({"objective": objective, "num_leaves": 31, "verbosity": -1, "device_type": "cuda", "quant_mode": "none", "learning_rate": 0.2}, **extra)
+    dev = fb.train(p, fb.Dataset(X, y), 12)
+    os.environ["FALCATA_RENEW_ON_HOST"] = "1"
+    try:
+        host = fb.train(p, fb.Dataset(X, y), 12)
+    finally:
+        del os.environ["FALCATA_RENEW_ON_HOST"]
+    np.testing.assert_allclose(dev.predict(X), host.predict(X), rtol=1e-9, atol=1e-9)
+    med = np.median(y - dev.predict(X)) if objective == "regression_l1" else np.quantile(y - dev.predict(X), 0.8)
+    assert abs(med) < 0.1
