@@ -547,6 +547,9 @@ class RankXENDCG : public ObjectiveFunction {
     if (weights_) for (data_size_t i = 0; i < n_; ++i) { g[i] *= weights_[i]; h[i] *= weights_[i]; }
   }
   std::string ToString() const override { return "rank_xendcg"; }
+  // the device kernel makes the same draws: parameter 0 is the seed; the engine counts the rounds itself
+  int DeviceKind() const override { return kObjXendcg; }
+  double DeviceParam(int i) const override { return i == 0 ? static_cast<double>(seed_) : 0.0; }
  private:
   int seed_; mutable uint32_t iter_ = 0;
   data_size_t n_ = 0, nq_ = 0; const label_t* label_ = nullptr; const label_t* weights_ = nullptr; const data_size_t* qb_ = nullptr;

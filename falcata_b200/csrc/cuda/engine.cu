@@ -81,6 +81,7 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
       Log::Warning("Objective %s has no device gradient kernel: gradients are computed on the host every round", obj->GetName());
       host_gradients_ = true;
     }
+    if (objd_.kind >= 0 && getenv("FALCATA_HOST_GRADIENTS") != nullptr) host_gradients_ = true;   // A/B switch: the objective's host code instead of the gradient kernel
     objd_.p0 = obj->DeviceParam(0); objd_.p1 = obj->DeviceParam(1); objd_.p2 = obj->DeviceParam(2);
     if (objd_.kind == kObjLambdarank) {
       const auto& qb = train->metadata.query_boundaries;

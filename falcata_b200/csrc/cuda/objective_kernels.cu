@@ -114,6 +114,71 @@ __global__ void AbsMaxKernel(const float* __restrict__ grad, const float* __rest
   BlockMax2(g, h, maxbuf + 2 * c);
 }
 
+// XE-NDCG (rank_xendcg): one block per query. rho = softmax of the query's scores; every document draws gamma from a
+// counter-based generator keyed on (row, round, seed), the same draw as the host objective; three passes of block sums
+// give the first-, second- and third-order terms of the gradient. Arithmetic in double, as on the host.
+// Parity: src/objective/cuda/cuda_rank_objective.cu:L864-981, src/objective/rank_objective.hpp (RankXENDCG).
+__device__ inline double BlockSumD(double v, double* scratch) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();                       // scratch may still be read from the previous reduction
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  double t = 0.0;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) t += scratch[w];   // same order in every thread
+  return t;
+}
+__global__ void XendcgKernel(const float* __restrict__ score, const float* __restrict__ label, const float* __restrict__ weight, const int* __restrict__ qb,
+                             unsigned int round, unsigned int seed, float* __restrict__ grad, float* __restrict__ hess, float* __restrict__ maxbuf) {
+  __shared__ double scratch[32];
+  const int q = blockIdx.x;
+  const int b = qb[q], cnt = qb[q + 1] - b;
+  float mg = 0.f, mh = 0.f;
+  if (cnt <= 1) {
+    for (int i = threadIdx.x; i < cnt; i += blockDim.x) { grad[b + i] = 0.f; hess[b + i] = 0.f; }
+  } else {
+    double mx = -1e300;
+    for (int i = threadIdx.x; i < cnt; i += blockDim.x) mx = fmax(mx, static_cast<double>(score[b + i]));
+    for (int o = 16; o > 0; o >>= 1) mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    for (int w = 0; w < (blockDim.x >> 5); ++w) mx = fmax(mx, scratch[w]);
+    double part = 0.0;
+    for (int i = threadIdx.x; i < cnt; i += blockDim.x) part += exp(static_cast<double>(score[b + i]) - mx);
+    const double sum = BlockSumD(part, scratch);
+    part = 0.0;
+    for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
+      const double u = U01From24(Philox4x32_10(static_cast<uint32_t>(b + i), round, 0x1234u, 0x5678u, seed, 0xABCDu).v[0]);
+      part += exp2(static_cast<double>(static_cast<int>(label[b + i]))) - u;
+    }
+    const double inv_denom = 1.0 / fmax(static_cast<double>(kEpsilon), BlockSumD(part, scratch));
+    // the per-document terms are recomputed in each pass instead of being kept: queries can be longer than a block
+    auto rho_of = [&](int i) { return exp(static_cast<double>(score[b + i]) - mx) / sum; };
+    auto l1_of = [&](int i, double rho) {
+      const double u = U01From24(Philox4x32_10(static_cast<uint32_t>(b + i), round, 0x1234u, 0x5678u, seed, 0xABCDu).v[0]);
+      return -(exp2(static_cast<double>(static_cast<int>(label[b + i]))) - u) * inv_denom + rho;
+    };
+    part = 0.0;
+    for (int i = threadIdx.x; i < cnt; i += blockDim.x) { const double rho = rho_of(i); part += l1_of(i, rho) / (1.0 - rho); }
+    const double sum_l1 = BlockSumD(part, scratch);
+    part = 0.0;
+    for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
+      const double rho = rho_of(i); const double p1 = l1_of(i, rho) / (1.0 - rho);
+      part += rho * (sum_l1 - p1) / (1.0 - rho);
+    }
+    const double sum_l2 = BlockSumD(part, scratch);
+    for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
+      const double rho = rho_of(i); const double l1 = l1_of(i, rho); const double p1 = l1 / (1.0 - rho);
+      const double l2 = rho * (sum_l1 - p1); const double p2 = l2 / (1.0 - rho);
+      const float w = weight != nullptr ? weight[b + i] : 1.f;
+      const float g = static_cast<float>(l1 + l2 + rho * (sum_l2 - p2)) * w, h = static_cast<float>(rho * (1.0 - rho)) * w;
+      grad[b + i] = g; hess[b + i] = h;
+      mg = fmaxf(mg, fabsf(g)); mh = fmaxf(mh, fabsf(h));
+    }
+  }
+  BlockMax2(mg, mh, maxbuf);
+}
+
 // LambdaRank: one block per query, documents ranked by counting (stable, no shared-memory sort
 // network), then every document's thread walks all of its pairs.
 constexpr int kRankMaxDocs = 2048;
@@ -272,6 +337,8 @@ void LaunchObjectiveGradients(const ObjDesc& d, const float* score, const float*
     const int t = maxdocs <= 128 ? 128 : 256;
     LambdarankKernel<<<num_queries, t, sm, s>>>(score, label, weight, qb, num_queries, label_gain, num_gain, static_cast<float>(d.p0), d.p1 != 0.0,
                                                static_cast<int>(d.p2), grad, hess, maxbuf);
+  } else if (d.kind == kObjXendcg) {
+    XendcgKernel<<<num_queries, 128, 0, s>>>(score, label, weight, qb, static_cast<unsigned int>(d.p1), static_cast<unsigned int>(static_cast<int>(d.p0)), grad, hess, maxbuf);
   } else if (d.kind == kObjMulticlassOVA) {
     OvaGradKernel<<<dim3(blocks, K), threads, 0, s>>>(d, score, label, weight, n, grad, hess, maxbuf);
   } else {
