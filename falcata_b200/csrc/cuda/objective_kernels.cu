@@ -182,6 +182,7 @@ __global__ void XendcgKernel(const float* __restrict__ score, const float* __res
 // LambdaRank: one block per query, documents ranked by counting (stable, no shared-memory sort
 // network), then every document's thread walks all of its pairs.
 constexpr int kRankMaxDocs = 2048;
+constexpr int kRankMaxLevels = 64;   // label levels counted per query in shared memory (more: the slower scan)
 __global__ void LambdarankKernel(const float* __restrict__ score, const float* __restrict__ label, const float* __restrict__ weight,
                                  const int* __restrict__ qb, int num_queries, const double* __restrict__ label_gain, int num_gain, float sigmoid,
                                  int norm, int trunc, float* __restrict__ grad, float* __restrict__ hess, float* __restrict__ maxbuf) {
@@ -193,23 +194,40 @@ __global__ void LambdarankKernel(const float* __restrict__ score, const float* _
     float* s_score = smem;                                   // by rank
     float* s_gain = smem + cnt;                              // by rank
     int* s_doc = reinterpret_cast<int*>(smem + 2 * cnt);     // rank -> doc
+    float* s_raw = smem + 3 * cnt;                           // by document: the scores, read once from global memory
+    float* s_disc = smem + 4 * cnt;                          // by rank: 1 / log2(2 + rank)
     __shared__ float s_red[32];
     __shared__ float s_inv_max_dcg, s_factor;
+    __shared__ int s_level_count[kRankMaxLevels];
+    for (int i = threadIdx.x; i < cnt; i += blockDim.x) { s_raw[i] = score[begin + i]; s_disc[i] = 1.f / log2f(2.f + i); }
+    for (int i = threadIdx.x; i < kRankMaxLevels; i += blockDim.x) s_level_count[i] = 0;
+    __syncthreads();
+    const bool few_levels = num_gain <= kRankMaxLevels;
     for (int dcur = threadIdx.x; dcur < cnt; dcur += blockDim.x) {
-      const float sd = score[begin + dcur];
+      const float sd = s_raw[dcur];
       int rank = 0;
-      for (int o = 0; o < cnt; ++o) { const float so = score[begin + o]; rank += (so > sd) || (so == sd && o < dcur); }
+      for (int o = 0; o < cnt; ++o) { const float so = s_raw[o]; rank += (so > sd) || (so == sd && o < dcur); }
       s_score[rank] = sd; s_doc[rank] = dcur;
-      const int lab = static_cast<int>(label[begin + dcur]);
-      s_gain[rank] = static_cast<float>(label_gain[lab < num_gain ? lab : num_gain - 1]);
+      int lab = static_cast<int>(label[begin + dcur]);
+      lab = lab < num_gain ? lab : num_gain - 1;
+      s_gain[rank] = static_cast<float>(label_gain[lab]);
+      if (few_levels) atomicAdd(&s_level_count[lab], 1);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-      // ideal DCG at the truncation level: gains sorted descending (counting over the few label values)
+      // ideal DCG at the truncation level: the gains in descending label order, position by position (the same sum,
+      // in the same order, as a scan over all documents per label level would give, from the per-level counts)
       double m = 0.0; int pos = 0;
-      for (int lv = num_gain - 1; lv >= 0 && pos < trunc; --lv) {
-        const float gv = static_cast<float>(label_gain[lv]);
-        for (int r = 0; r < cnt && pos < trunc; ++r) if (s_gain[r] == gv) { m += gv / log2(2.0 + pos); ++pos; }
+      if (few_levels) {
+        for (int lv = num_gain - 1; lv >= 0 && pos < trunc; --lv) {
+          const float gv = static_cast<float>(label_gain[lv]);
+          for (int k = 0; k < s_level_count[lv] && pos < trunc; ++k) { m += gv / log2(2.0 + pos); ++pos; }
+        }
+      } else {
+        for (int lv = num_gain - 1; lv >= 0 && pos < trunc; --lv) {
+          const float gv = static_cast<float>(label_gain[lv]);
+          for (int r = 0; r < cnt && pos < trunc; ++r) if (s_gain[r] == gv) { m += gv / log2(2.0 + pos); ++pos; }
+        }
       }
       s_inv_max_dcg = m > 0.0 ? static_cast<float>(1.0 / m) : 0.f;
     }
@@ -220,7 +238,7 @@ __global__ void LambdarankKernel(const float* __restrict__ score, const float* _
     // pass 1: lambdas of this thread's documents
     for (int p = threadIdx.x; p < cnt; p += blockDim.x) {
       float lg = 0.f, lh = 0.f;
-      const float gp = s_gain[p], sp = s_score[p], dp = 1.f / log2f(2.f + p);
+      const float gp = s_gain[p], sp = s_score[p], dp = s_disc[p];
       for (int o = 0; o < cnt; ++o) {
         if (o == p) continue;
         const int lo_rank = o < p ? o : p;
@@ -229,7 +247,7 @@ __global__ void LambdarankKernel(const float* __restrict__ score, const float* _
         if (go == gp) continue;
         const bool p_high = gp > go;
         const float ds = p_high ? sp - s_score[o] : s_score[o] - sp;
-        const float gap = fabsf(gp - go), pd = fabsf(dp - 1.f / log2f(2.f + o));
+        const float gap = fabsf(gp - go), pd = fabsf(dp - s_disc[o]);
         float delta = gap * pd * inv;
         if (norm && best != worst) delta /= (0.01f + fabsf(ds));
         const float rho = 1.f / (1.f + expf(sigmoid * ds));
@@ -333,7 +351,7 @@ void LaunchObjectiveGradients(const ObjDesc& d, const float* score, const float*
   if (d.kind == kObjLambdarank) {
     int maxdocs = d.max_docs;
     if (maxdocs > kRankMaxDocs) Log::Fatal("lambdarank on the device supports at most %d documents per query (got %d)", kRankMaxDocs, maxdocs);
-    const size_t sm = static_cast<size_t>(maxdocs) * 3 * sizeof(float);
+    const size_t sm = static_cast<size_t>(maxdocs) * 5 * sizeof(float);
     const int t = maxdocs <= 128 ? 128 : 256;
     LambdarankKernel<<<num_queries, t, sm, s>>>(score, label, weight, qb, num_queries, label_gain, num_gain, static_cast<float>(d.p0), d.p1 != 0.0,
                                                static_cast<int>(d.p2), grad, hess, maxbuf);
