@@ -71,11 +71,12 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
       FB_CUDA(cudaMemcpyAsync(hess_.get(), hh.data(), sizeof(float) * total, cudaMemcpyHostToDevice, stream_));
       FB_CUDA(cudaStreamSynchronize(stream_));
       LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_, mask);
-    } else
-    if (objd_.kind == kObjXendcg) objd_.p1 = static_cast<double>(xendcg_round_++);   // the round index keys this round's random draws
-    LaunchObjectiveGradients(objd_, score_.get(), dd_->label.get(), dd_->weight.size() ? dd_->weight.get() : nullptr,
-                             dd_->query_boundaries.size() ? dd_->query_boundaries.get() : nullptr, dd_->num_queries, label_gain_.get(),
-                             static_cast<int>(label_gain_.size()), n_, grad_.get(), hess_.get(), maxbuf_.get(), stream_);
+    } else {
+      if (objd_.kind == kObjXendcg) objd_.p1 = static_cast<double>(xendcg_round_++);   // the round index keys this round's random draws
+      LaunchObjectiveGradients(objd_, score_.get(), dd_->label.get(), dd_->weight.size() ? dd_->weight.get() : nullptr,
+                               dd_->query_boundaries.size() ? dd_->query_boundaries.get() : nullptr, dd_->num_queries, label_gain_.get(),
+                               static_cast<int>(label_gain_.size()), n_, grad_.get(), hess_.get(), maxbuf_.get(), stream_);
+    }
     if (bagging && quant_) LaunchAbsMax(grad, hess, n_, K_, maxbuf_.get(), stream_, mask);   // the scale comes from the bag's rows only
   }
   if (goss) {
