@@ -264,7 +264,7 @@ Plan Plan::FromString(const std::string& s) {
     else Log::Fatal("cuda_plan value '%s' must be on or off", v.c_str());
 #define FB_PK(name) if (k == #name) { p.name = on; continue; }
     FB_PK(hist_tc) FB_PK(device_controller) FB_PK(fused_tail) FB_PK(fused_scan)
-    FB_PK(pack4) FB_PK(compact_view) FB_PK(gh_in_row) FB_PK(hist_lane) FB_PK(hist_lane_atomic) FB_PK(hist_lane_red) FB_PK(hist_float_red) FB_PK(col_major_part) FB_PK(bulk_root)
+    FB_PK(pack4) FB_PK(compact_view) FB_PK(gh_in_row) FB_PK(hist_lane) FB_PK(hist_lane_atomic) FB_PK(hist_lane_red) FB_PK(hist_float_red) FB_PK(robust_scale) FB_PK(quant_ef) FB_PK(col_major_part) FB_PK(bulk_root)
 #undef FB_PK
     Log::Fatal("Unknown cuda_plan key '%s'", k.c_str());
   }
@@ -275,7 +275,7 @@ std::string Plan::ToString() const {
   std::ostringstream os;
 #define FB_PS(name) os << #name << ":" << (name ? "on" : "off") << " ";
   FB_PS(hist_tc) FB_PS(device_controller) FB_PS(fused_tail) FB_PS(fused_scan)
-  FB_PS(pack4) FB_PS(compact_view) FB_PS(gh_in_row) FB_PS(hist_lane) FB_PS(hist_lane_atomic) FB_PS(hist_lane_red) FB_PS(hist_float_red) FB_PS(col_major_part) FB_PS(bulk_root)
+  FB_PS(pack4) FB_PS(compact_view) FB_PS(gh_in_row) FB_PS(hist_lane) FB_PS(hist_lane_atomic) FB_PS(hist_lane_red) FB_PS(hist_float_red) FB_PS(robust_scale) FB_PS(quant_ef) FB_PS(col_major_part) FB_PS(bulk_root)
 #undef FB_PS
   return os.str();
 }

@@ -145,6 +145,7 @@ class CPUTreeLearner : public TreeLearner {
   bool quant_ = false, parallel_data_ = false, parallel_feature_ = false, parallel_voting_ = false;
   QuantState qs_;
   std::vector<int32_t> gh_packed_;
+  std::vector<int8_t> ef_residual_;   // fixed-point error feedback: (hessian, gradient) residuals per row, one slot per class
   const score_t* grad_ = nullptr; const score_t* hess_ = nullptr;
   std::vector<int8_t> node_feature_mask_;
   std::vector<int64_t> voted_hist_i_; std::vector<double> voted_hist_;
@@ -292,17 +293,52 @@ void CPUTreeLearner::Quantize(const score_t* grad, const score_t* hess, int tree
     mg = std::max(mg, static_cast<double>(std::fabs(grad[i]))); mh = std::max(mh, static_cast<double>(std::fabs(hess[i])));
   }
   mg = Network::MaxDouble(mg); mh = Network::MaxDouble(mh);
+  // fixed point: the outlier-robust scale (single-target objectives, at most 256 levels) and the error feedback, as in
+  // the device engine; both are keyed by the same plan switches
+  const Plan plan = Plan::FromString(cfg_.cuda_plan);
+  const bool fixed = !qs_.stochastic;
+  int clamp = 0;
+  float gmax = static_cast<float>(mg);
+  if (fixed && plan.robust_scale && qs_.bins <= 256 && cfg_.num_class <= 1 && gmax > 0.f) {
+    std::vector<int64_t> hist(kQuantMagBuckets, 0);
+    int64_t rows = 0;
+    for (data_size_t k = 0; k < cnt; ++k) {
+      const data_size_t i = use_bag_ ? bag_[k] : k;
+      const float a = std::fabs(grad[i]);
+      if (a > 0.f) ++hist[QuantMagBucket(a, gmax)];
+      ++rows;
+    }
+    Network::SumInt64(hist.data(), kQuantMagBuckets); Network::SumInt64(&rows, 1);
+    const float anchor = RobustGradAnchor(hist.data(), rows, gmax);
+    if (anchor < gmax) { gmax = anchor; clamp = qs_.bins / 2; }
+  }
   // scales are computed in fp32 exactly as on the device
-  float gs = static_cast<float>(mg) / static_cast<float>(qs_.bins / 2), hs = static_cast<float>(mh) / static_cast<float>(qs_.bins);
+  float gs = gmax / static_cast<float>(qs_.bins / 2), hs = static_cast<float>(mh) / static_cast<float>(qs_.bins);
   if (!(gs > 0.f)) gs = 1.f;
   if (!(hs > 0.f)) hs = 1.f;
   qs_.g_scale = gs; qs_.h_scale = hs;
   const float ig = 1.0f / gs, ih = 1.0f / hs;
   gh_packed_.resize(n);
   const uint32_t seed = static_cast<uint32_t>(cfg_.seed);
+  const bool feedback = fixed && plan.quant_ef;
+  int8_t* residual = nullptr;
+  if (feedback) {
+    const int slots = std::max(1, cfg_.num_class);
+    if (ef_residual_.size() != static_cast<size_t>(slots) * 2 * n) ef_residual_.assign(static_cast<size_t>(slots) * 2 * n, 0);
+    residual = ef_residual_.data() + static_cast<size_t>(tree_index % slots) * 2 * n;   // one slot per class tree of a round
+  }
+  std::vector<char> in_bag;
+  if (feedback && use_bag_) { in_bag.assign(n, 0); for (data_size_t i : bag_) in_bag[i] = 1; }
 #pragma omp parallel for schedule(static) num_threads(RowThreads(n))
-  for (data_size_t i = 0; i < n; ++i)
-    gh_packed_[i] = QuantizeRow(grad[i], hess[i], ig, ih, qs_.stochastic, seed, static_cast<uint32_t>(tree_index), static_cast<uint64_t>(ds_->global_row_offset + i));
+  for (data_size_t i = 0; i < n; ++i) {
+    if (fixed && (feedback || clamp > 0)) {
+      // out-of-bag residuals do not move: nothing consumes those rows' values this round
+      int8_t* r = (residual != nullptr && (in_bag.empty() || in_bag[i])) ? residual + 2 * static_cast<size_t>(i) : nullptr;
+      gh_packed_[i] = QuantizeRowFeedback(grad[i], hess[i], ig, ih, clamp, r);
+    } else {
+      gh_packed_[i] = QuantizeRow(grad[i], hess[i], ig, ih, qs_.stochastic, seed, static_cast<uint32_t>(tree_index), static_cast<uint64_t>(ds_->global_row_offset + i));
+    }
+  }
 }
 
 void CPUTreeLearner::ConstructHistogram(LeafState* leaf) {

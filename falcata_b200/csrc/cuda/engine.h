@@ -119,6 +119,7 @@ class CudaEngine : public DeviceEngine {
   // exact leaf-wise growth (grow_policy=leaf): the device grows up to grow_leaves_ leaves, the host keeps the best num_leaves
   bool leafwise_ = false; int grow_leaves_ = 0;
   DevBuf<double> renew_in_, renew_out_, renew_res_; DevBuf<int> renew_off_; DevBuf<char> renew_temp_;   // percentile leaf renewal on the device
+  DevBuf<float> qmax_; DevBuf<int> qclamp_; DevBuf<unsigned long long> mag_hist_; DevBuf<int8_t> ef_residual_;   // fixed-point quantization: robust scale and error feedback
   unsigned int xendcg_round_ = 0;   // rank_xendcg: rounds of gradients computed so far (keys the per-round random draws, like the host objective's counter)
   bool tc_fallback_logged_ = false;
   bool lane_red_ = true;   // reduction form of the lane construct (integer: plan hist_lane_red, fp32: plan hist_float_red)

@@ -147,7 +147,29 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   // The pool is cleared BEFORE this tree's first cross-rank exchange: a peer can only start adding
   // into this rank's slots after it has seen this rank's contribution to that exchange.
   FB_CUDA(cudaMemsetAsync(pool_base_, 0, pool_bytes_, stream_));
-  if (quant_) {
+  const bool fixed_gate = quant_ && cfg_.quant == QuantMode::FixedPoint && plan_.robust_scale && cfg_.quant_bins_resolved <= 256 && cfg_.num_class <= 1;
+  const bool fixed_ef = quant_ && cfg_.quant == QuantMode::FixedPoint && plan_.quant_ef;
+  if (fixed_gate || fixed_ef) {
+    // fixed point with its extras: (gate) log-magnitude histogram over all ranks' rows -> possibly a scale anchored below
+    // an outlier cluster, outliers saturating; (feedback) last round's rounding residuals added before rounding
+    const float* mx = data_parallel() ? global_max_.get() + 2 * class_id : maxbuf_.get() + 2 * class_id;
+    if (qmax_.size() == 0) { qmax_.Alloc(2); qclamp_.Alloc(1); mag_hist_.Alloc(kQuantMagBuckets); }
+    if (fixed_gate) {
+      LaunchGradMagHist(cur_grad_, n_, mx, bag_mask_ptr(), mag_hist_.get(), stream_);
+      if (data_parallel())   // the small all-reduce takes 128 counters at a time
+        for (int off = 0; off < kQuantMagBuckets; off += 128) fabric_->AllReduce(kFabricSumI64, mag_hist_.get() + off, mag_hist_.get() + off, 128, stream_);
+    }
+    LaunchRobustScale(mag_hist_.get(), static_cast<long long>(root_global_), mx, cfg_.quant_bins_resolved, fixed_gate, qmax_.get(), qclamp_.get(), stream_);
+    int8_t* residual = nullptr;
+    if (fixed_ef) {
+      const size_t per_class = 2 * static_cast<size_t>(n_);
+      if (ef_residual_.size() != per_class * K_) { ef_residual_.Alloc(per_class * K_); ef_residual_.Zero(stream_); }
+      residual = ef_residual_.get() + per_class * class_id;
+    }
+    LaunchQuantizeFeedback(cur_grad_, cur_hess_, n_, qmax_.get(), qclamp_.get(), cfg_.quant_bins_resolved, residual, const_cast<uint8_t*>(gh_base_), gh_stride_, scales_.get(),
+                           root_sums_i_.get(), stream_, bag_mask_ptr());
+    if (data_parallel()) fabric_->AllReduce(kFabricSumI64, root_sums_i_.get(), root_sums_i_.get(), 2, stream_);
+  } else if (quant_) {
     LaunchQuantize(cur_grad_, cur_hess_, n_, maxbuf_.get() + 2 * class_id, data_parallel() ? global_max_.get() + 2 * class_id : nullptr, cfg_.quant_bins_resolved,
                    cfg_.quant == QuantMode::Stochastic, static_cast<uint32_t>(cfg_.seed), static_cast<uint32_t>(tree_index),
                    static_cast<uint64_t>(train_->global_row_offset), const_cast<uint8_t*>(gh_base_), gh_stride_, scales_.get(), root_sums_i_.get(), stream_, bag_mask_ptr());

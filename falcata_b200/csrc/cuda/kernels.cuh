@@ -38,6 +38,13 @@ void LaunchObjectiveGradients(const ObjDesc& d, const float* score, const float*
 void LaunchAbsMax(const float* grad, const float* hess, int n, int num_class, float* maxbuf, cudaStream_t s, const uint8_t* mask = nullptr);
 void LaunchQuantize(const float* grad, const float* hess, int n, const float* maxbuf, const float* global_max, int bins, bool stochastic, uint32_t seed,
                     uint32_t iter_key, uint64_t global_row_offset, uint8_t* gh_base, int gh_stride, float* scales_out, long long* root_sums, cudaStream_t s, const uint8_t* mask = nullptr);
+// fixed-point extras: log-magnitude histogram of the gradients (kQuantMagBuckets counters), the gate that may re-anchor
+// the scale below an outlier cluster (qmax: top-level gradient magnitude and hessian maximum; clamp: saturation level or
+// 0), and the quantizer with saturation and int8 error feedback (`residual`: 2 bytes per row, may be null)
+void LaunchGradMagHist(const float* grad, int n, const float* max2, const uint8_t* mask, unsigned long long* hist, cudaStream_t s);
+void LaunchRobustScale(const unsigned long long* hist, long long num_rows, const float* max2, int bins, bool use_gate, float* qmax, int* clamp, cudaStream_t s);
+void LaunchQuantizeFeedback(const float* grad, const float* hess, int n, const float* qmax, const int* clamp, int bins, int8_t* residual, uint8_t* gh_base, int gh_stride,
+                            float* scales_out, long long* root_sums, cudaStream_t s, const uint8_t* mask = nullptr);
 void LaunchInterleave(const float* grad, const float* hess, int n, float2* gh2, double* partial, int partial_capacity, double* root_sums_d, cudaStream_t s,
                       const uint8_t* mask = nullptr);
 

@@ -311,6 +311,64 @@ __global__ void QuantizeKernel(const float* __restrict__ grad, const float* __re
   }
 }
 
+// ---- fixed-point extras: outlier-robust scale and error feedback (shared per-row code in fb/learner.h) ----
+// Rows by log-magnitude of the gradient, per block in shared memory, then one global add per non-empty bucket.
+__global__ void GradMagHistKernel(const float* __restrict__ grad, int n, const float* __restrict__ max2, const uint8_t* __restrict__ mask,
+                                  unsigned long long* __restrict__ hist) {
+  __shared__ unsigned int s_hist[kQuantMagBuckets];
+  for (int b = threadIdx.x; b < kQuantMagBuckets; b += blockDim.x) s_hist[b] = 0u;
+  __syncthreads();
+  const float gmax = max2[0];
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    if (mask != nullptr && mask[i] == 0) continue;
+    const float a = fabsf(grad[i]);
+    if (a > 0.f && gmax > 0.f) atomicAdd(&s_hist[QuantMagBucket(a, gmax)], 1u);
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < kQuantMagBuckets; b += blockDim.x) { const unsigned int v = s_hist[b]; if (v != 0u) atomicAdd(hist + b, static_cast<unsigned long long>(v)); }
+}
+// One thread: the gate. qmax = (gradient magnitude of the top level, hessian maximum); clamp = levels at which the
+// gradient saturates (0: no saturation, the scale is the plain maximum).
+__global__ void RobustScaleKernel(const unsigned long long* __restrict__ hist, long long num_rows, const float* __restrict__ max2, int bins, int use_gate,
+                                  float* __restrict__ qmax, int* __restrict__ clamp) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const float gmax = max2[0];
+  float top = gmax;
+  if (use_gate && gmax > 0.f) top = RobustGradAnchor(hist, num_rows, gmax);
+  qmax[0] = top; qmax[1] = max2[1];
+  clamp[0] = top < gmax ? bins / 2 : 0;
+}
+__global__ void QuantizeFeedbackKernel(const float* __restrict__ grad, const float* __restrict__ hess, int n, const float* __restrict__ qmax, const int* __restrict__ clamp,
+                                       int bins, int8_t* __restrict__ residual, uint8_t* __restrict__ gh_base, int gh_stride, float* __restrict__ scales_out,
+                                       long long* __restrict__ root_sums, const uint8_t* __restrict__ mask) {
+  float gs = qmax[0] / static_cast<float>(bins / 2), hs = qmax[1] / static_cast<float>(bins);
+  if (!(gs > 0.f)) gs = 1.f;
+  if (!(hs > 0.f)) hs = 1.f;
+  const float ig = 1.0f / gs, ih = 1.0f / hs;
+  const int cl = clamp[0];
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  long long sg = 0, sh = 0;
+  if (i < n) {
+    const bool in_bag = mask == nullptr || mask[i] != 0;
+    int8_t* r = (residual != nullptr && in_bag) ? residual + 2 * static_cast<size_t>(i) : nullptr;   // out-of-bag residuals stay
+    const int32_t w = QuantizeRowFeedback(grad[i], hess[i], ig, ih, cl, r);
+    *reinterpret_cast<int32_t*>(gh_base + static_cast<size_t>(i) * gh_stride) = w;
+    if (in_bag) { sg = UnpackG(w); sh = UnpackH(w); }
+  }
+  for (int o = 16; o > 0; o >>= 1) { sg += __shfl_xor_sync(0xffffffffu, sg, o); sh += __shfl_xor_sync(0xffffffffu, sh, o); }
+  __shared__ long long s1[32], s2[32];
+  const int wq = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) { s1[wq] = sg; s2[wq] = sh; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    long long a = 0, b = 0; const int nw = (blockDim.x + 31) >> 5;
+    for (int k = 0; k < nw; ++k) { a += s1[k]; b += s2[k]; }
+    atomicAdd(reinterpret_cast<unsigned long long*>(root_sums), static_cast<unsigned long long>(a));
+    atomicAdd(reinterpret_cast<unsigned long long*>(root_sums + 1), static_cast<unsigned long long>(b));
+    if (blockIdx.x == 0) { scales_out[0] = gs; scales_out[1] = hs; }
+  }
+}
+
 // Full precision: interleave (g, h) and produce per-block partial sums (summed later in a fixed order).
 __global__ void InterleaveKernel(const float* __restrict__ grad, const float* __restrict__ hess, int n, float2* __restrict__ gh2,
                                  double* __restrict__ partial /* 2 per block */, const uint8_t* __restrict__ mask) {
@@ -378,6 +436,25 @@ void LaunchQuantize(const float* grad, const float* hess, int n, const float* ma
   FB_CUDA(cudaMemsetAsync(root_sums, 0, sizeof(long long) * 2, s));
   const int threads = 256, blocks = std::max(1, (n + threads - 1) / threads);
   QuantizeKernel<<<blocks, threads, 0, s>>>(grad, hess, n, maxbuf, global_max, bins, stochastic ? 1 : 0, seed, iter_key, global_row_offset, gh_base, gh_stride, scales_out, root_sums, mask);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+
+void LaunchGradMagHist(const float* grad, int n, const float* max2, const uint8_t* mask, unsigned long long* hist, cudaStream_t s) {
+  FB_CUDA(cudaMemsetAsync(hist, 0, sizeof(unsigned long long) * kQuantMagBuckets, s));
+  if (n <= 0) return;
+  const int threads = 256, blocks = std::max(1, std::min(1184, (n + threads * 8 - 1) / (threads * 8)));
+  GradMagHistKernel<<<blocks, threads, 0, s>>>(grad, n, max2, mask, hist);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+void LaunchRobustScale(const unsigned long long* hist, long long num_rows, const float* max2, int bins, bool use_gate, float* qmax, int* clamp, cudaStream_t s) {
+  RobustScaleKernel<<<1, 32, 0, s>>>(hist, num_rows, max2, bins, use_gate ? 1 : 0, qmax, clamp);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
+void LaunchQuantizeFeedback(const float* grad, const float* hess, int n, const float* qmax, const int* clamp, int bins, int8_t* residual, uint8_t* gh_base, int gh_stride,
+                            float* scales_out, long long* root_sums, cudaStream_t s, const uint8_t* mask) {
+  FB_CUDA(cudaMemsetAsync(root_sums, 0, sizeof(long long) * 2, s));
+  const int threads = 256, blocks = std::max(1, (n + threads - 1) / threads);
+  QuantizeFeedbackKernel<<<blocks, threads, 0, s>>>(grad, hess, n, qmax, clamp, bins, residual, gh_base, gh_stride, scales_out, root_sums, mask);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
 

@@ -210,6 +210,8 @@ struct Plan {
   bool hist_lane = true;         // lane-per-group construct with bank-interleaved warp-private tiles (groups with <= 64 bins)
   bool hist_lane_atomic = false; // lane-per-group construct with one shared tile per block and shared atomics
   bool hist_lane_red = true;     // lane construct adds with shared-memory reduction instructions into tiles shared by 8 warps (off: load-add-store with forwarding, a tile per warp)
+  bool robust_scale = true;      // fixed-point quantization: outlier-robust gradient scale (changes the model only where it fires: a small outlier cluster above an empty octave)
+  bool quant_ef = true;          // fixed-point quantization: int8 error feedback of the rounding residuals from round to round
   bool hist_float_red = false;   // fp32 lane construct with shared-memory reduction adds into shared tiles (off: a tile per warp, load-add-store, sums in row order)
   bool col_major_part = true;    // partition reads the split column from a column-major copy of the bins
   bool bulk_root = true;         // root level of the lane construct staged by bulk asynchronous copies (TMA engine, mbarrier completion)

@@ -97,6 +97,80 @@ FB_HD inline int32_t QuantizeRow(float g, float h, float inv_g_scale, float inv_
   return static_cast<int32_t>((static_cast<uint32_t>(gi) << 16) | (static_cast<uint32_t>(hi) & 0xFFFFu));
 }
 
+// Fixed-point quantization with error feedback and saturation (the same code runs in the device kernel).
+// `residual`: two int8 per row, (hessian, gradient) rounding errors of the previous round in 1/128 of a level; they are
+// added before rounding and replaced by this round's errors, which removes the bias of deterministic rounding over the
+// rounds. `clamp` > 0: the gradient saturates at +-clamp levels (used with the outlier-robust scale); saturation is not
+// fed back, or a saturated row would carry an ever-growing residual.
+// Parity: src/treelearner/cuda/cuda_gradient_discretizer.cu:L300-335.
+FB_HD inline int32_t QuantizeRowFeedback(float g, float h, float inv_g_scale, float inv_h_scale, int clamp, int8_t* residual) {
+  float ge = 0.f, he = 0.f;
+  if (residual != nullptr) { he = static_cast<float>(residual[0]) * 0.0078125f; ge = static_cast<float>(residual[1]) * 0.0078125f; }
+  // one explicitly fused multiply-add per value: the same single rounding on the host and on the device, whatever the
+  // compilers would contract on their own
+#if defined(__CUDA_ARCH__)
+  const float xg = __fmaf_rn(g, inv_g_scale, ge), xh = __fmaf_rn(h, inv_h_scale, he);
+#else
+  const float xg = std::fmaf(g, inv_g_scale, ge), xh = std::fmaf(h, inv_h_scale, he);
+#endif
+  // the double 0.5 keeps the rounding sequence free of fused multiply-adds on every target
+  int q = xg > 0.f ? static_cast<int>(static_cast<double>(xg) + 0.5) : static_cast<int>(static_cast<double>(xg) - 0.5);
+  int qh = static_cast<int>(static_cast<double>(xh) + 0.5);
+  if (residual != nullptr) {
+    const double eh = (static_cast<double>(xh) - qh) * 128.0, eg = (static_cast<double>(xg) - q) * 128.0;
+    int rh = static_cast<int>(eh >= 0 ? eh + 0.5 : eh - 0.5), rg = static_cast<int>(eg >= 0 ? eg + 0.5 : eg - 0.5);
+    rh = rh > 127 ? 127 : (rh < -127 ? -127 : rh); rg = rg > 127 ? 127 : (rg < -127 ? -127 : rg);
+    residual[0] = static_cast<int8_t>(rh); residual[1] = static_cast<int8_t>(rg);
+  }
+  if (clamp > 0) { q = q > clamp ? clamp : (q < -clamp ? -clamp : q); }
+  if (qh < 0) qh = 0;
+  return static_cast<int32_t>((static_cast<uint32_t>(q) << 16) | (static_cast<uint32_t>(qh) & 0xFFFFu));
+}
+
+// Outlier-robust gradient scale of the fixed-point mode. `hist` counts the rows by log-magnitude: bucket b holds
+// |g| in (gmax * 2^-((b+1)/128), gmax * 2^-(b/128)], kQuantMagBuckets buckets in all (16 octaves). Walking down from the
+// largest magnitudes: if a small set of rows (at most 5 % of `num_rows`) is followed by at least one empty octave and
+// then more rows, those first rows are outliers above a gap and the scale is anchored at the upper edge of the first
+// bucket below the gap (the outliers saturate); otherwise the scale stays at the maximum. Returns the magnitude that
+// maps to the top level. Parity: src/treelearner/cuda/cuda_gradient_discretizer.cu:L88-222.
+constexpr int kQuantMagBuckets = 2048;
+constexpr int kQuantMagPerOctave = 128;
+FB_HD inline int QuantMagBucket(float abs_g, float gmax) {
+  // abs_g in (0, gmax]
+#if defined(__CUDA_ARCH__)
+  int b = static_cast<int>(floorf(-log2f(abs_g / gmax) * static_cast<float>(kQuantMagPerOctave)));
+#else
+  int b = static_cast<int>(std::floor(-std::log2(abs_g / gmax) * static_cast<float>(kQuantMagPerOctave)));
+#endif
+  return b < 0 ? 0 : (b >= kQuantMagBuckets ? kQuantMagBuckets - 1 : b);
+}
+template <typename Count>
+FB_HD inline float RobustGradAnchor(const Count* hist, long long num_rows, float gmax) {
+  const long long max_outliers = static_cast<long long>(0.05 * static_cast<double>(num_rows));
+  long long outliers = 0; bool seen = false; int gap = 0, bulk_top = -1;
+  for (int b = 0; b < kQuantMagBuckets; ++b) {
+    const long long c = static_cast<long long>(hist[b]);
+    if (c == 0) { if (seen) ++gap; continue; }
+    if (seen && gap >= kQuantMagPerOctave && outliers <= max_outliers) { bulk_top = b; break; }
+    seen = true; gap = 0; outliers += c;
+    if (outliers > max_outliers) break;
+  }
+  if (bulk_top < 0) return gmax;
+  // gmax * 2^(-bulk_top / 128) by exact halvings and repeated single-precision products with one constant, so that the
+  // host and the device arrive at the same bits
+  float anchor = gmax;
+  for (int o = 0; o < bulk_top / kQuantMagPerOctave; ++o) anchor *= 0.5f;
+  const float step = 0.99459942f;   // 2^(-1/128)
+  for (int k = 0; k < bulk_top % kQuantMagPerOctave; ++k) {
+#if defined(__CUDA_ARCH__)
+    anchor = __fmul_rn(anchor, step);
+#else
+    anchor = anchor * step;
+#endif
+  }
+  return (anchor > 0.f && anchor <= gmax) ? anchor : gmax;
+}
+
 class ObjectiveFunction;
 
 class TreeLearner {

@@ -56,6 +56,9 @@ def build_cells():
     add("ranking/stochastic", "ranking", dict(quant))
     add("ranking/float", "ranking", {"quant_mode": "none"}, fingerprint=False)
     add("large/stochastic", "large", dict(quant), rounds=6)
+    add("dense/fixedpoint-plain", "dense", dict(fixed, cuda_plan="auto,quant_ef:off,robust_scale:off"))
+    add("imbalanced/fixedpoint", "imbalanced", dict(fixed))                                        # the outlier-robust scale fires here
+    add("imbalanced/fixedpoint-norobust", "imbalanced", dict(fixed, cuda_plan="auto,robust_scale:off"))
     add("dense/leafwise", "dense", dict(quant, grow_policy="leaf"))
     add("dense/bagging", "dense", dict(quant, bagging_fraction=0.7, bagging_freq=1))
     add("dense/goss", "dense", dict(quant, data_sample_strategy="goss"))
@@ -115,6 +118,12 @@ def build_profile(name):
         metric, bound = "l2", None
     elif name == "wide_bins":
         base["max_bin"] = 255
+    elif name == "imbalanced":
+        n = 40000
+        X = rng.normal(size=(n, f)).astype(np.float32)
+        logit = 2.0 * X[:, 0] - 1.5 * X[:, 1] + X[:, 2] * X[:, 3] - 7.5          # about one positive in 260
+        base["min_sum_hessian_in_leaf"] = 1.0
+        metric, higher, bound = "auc", True, 0.9
     if name == "multiclass":
         W = rng.normal(size=(f, 4))
         y = np.argmax(X @ W + rng.gumbel(size=(n, 4)), axis=1).astype(np.float32)
@@ -153,8 +162,8 @@ def run_cell(cell, device):
     params = dict(base, **cell["params"])
     params["device_type"] = device
     params.setdefault("metric", metric.split("@")[0])
-    if device == "cpu":
-        params.pop("cuda_plan", None)
+    if device == "cpu" and "quant_ef" not in str(params.get("cuda_plan", "")) and "robust_scale" not in str(params.get("cuda_plan", "")):
+        params.pop("cuda_plan", None)   # the host learner reads only the quantizer switches of the plan
     problems = []
     t0 = time.perf_counter()
     ds = fb.Dataset(X, y, group=group, categorical_feature=params.pop("categorical_feature", "auto"), params={k: params[k] for k in ("max_bin", "enable_bundle", "use_missing") if k in params})

@@ -377,3 +377,21 @@ def test_more_than_255_bins_train_on_the_host_whatever_the_device():
     coarse = np.mean((fb.train(dict(p, max_bin=15), fb.Dataset(X, y, params={"max_bin": 15}), 10).predict(X) - y) ** 2)
     assert fine < coarse
     assert b.dump_model()["feature_infos"] is not None
+
+
+def test_fixedpoint_error_feedback_and_robust_scale_switches():
+    """Fixed-point quantization: the error feedback and the outlier-robust scale are plan switches that the host
+    learner honours too; with both off the rounding is the plain one (a different model), and on balanced data the
+    robust scale does not fire (same model with and without it)."""
+    rng = np.random.default_rng(61)
+    X = rng.normal(size=(5000, 8)); y = (X[:, 0] - X[:, 1] + 0.5 * rng.normal(size=5000) > 0).astype(np.float64)
+    p = {"objective": "binary", "num_leaves": 15, "verbosity": -1, "quant_mode": "fixedpoint", "quant_bins": 16, "min_data_in_leaf": 10}
+    body = lambda b: b.model_to_string().split("\nparameters:")[0]
+    full = fb.train(dict(p), fb.Dataset(X, y), 10)
+    no_gate = fb.train(dict(p, cuda_plan="auto,robust_scale:off"), fb.Dataset(X, y), 10)
+    no_ef = fb.train(dict(p, cuda_plan="auto,quant_ef:off"), fb.Dataset(X, y), 10)
+    assert body(full) == body(no_gate)          # balanced gradients: no gap, no re-anchoring
+    assert body(full) != body(no_ef)            # the residuals change the rounding from the second round on
+    exact = fb.train(dict(p, quant_mode="none"), fb.Dataset(X, y), 10)
+    ll = lambda b: float(np.mean(np.where(y > 0, -np.log(b.predict(X)), -np.log(1 - b.predict(X)))))
+    assert ll(full) <= ll(no_ef) + 0.01 and abs(ll(full) - ll(exact)) < 0.03
