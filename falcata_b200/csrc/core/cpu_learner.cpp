@@ -176,6 +176,7 @@ void CPUTreeLearner::SetParams() {
   sp_.max_cat_threshold = cfg_.max_cat_threshold; sp_.max_cat_to_onehot = cfg_.max_cat_to_onehot; sp_.min_data_per_group = cfg_.min_data_per_group;
   sp_.cat_l2 = cfg_.cat_l2; sp_.cat_smooth = cfg_.cat_smooth; sp_.extra_trees = cfg_.extra_trees ? 1 : 0;
   sp_.cegb_split = cfg_.cegb_tradeoff * cfg_.cegb_penalty_split;
+  sp_.monotone_penalty = cfg_.monotone_penalty;
   auto parse_penalties = [&](const std::string& text, const char* name, std::vector<double>* out) {
     out->clear();
     if (text.empty()) return;
@@ -570,6 +571,7 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
   L.sum_g = leaf->sum_g; L.sum_h = leaf->sum_h; L.sum_gi = leaf->sum_gi; L.sum_hi = leaf->sum_hi;
   L.num_data = static_cast<int>(n_global); L.parent_output = leaf->output; L.min_c = leaf->min_constraint; L.max_c = leaf->max_constraint;
   L.g_scale = quant_ ? qs_.g_scale : 1.0; L.h_scale = quant_ ? qs_.h_scale : 1.0;
+  L.mono_factor = MonotonePenaltyFactor(leaf->depth, sp_.monotone_penalty);
   L.cnt_factor = FB_DIV(static_cast<double>(L.num_data), L.sum_h);
   L.min_gain_shift = FB_ADD(LeafGainGivenOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, leaf->output), sp_.min_gain_to_split);
   if (sp_.max_delta_step <= 0.0 && sp_.path_smooth <= 0.0)

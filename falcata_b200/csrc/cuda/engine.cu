@@ -65,6 +65,7 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   sp_.max_depth = cfg.max_depth; sp_.max_cat_threshold = cfg.max_cat_threshold; sp_.max_cat_to_onehot = cfg.max_cat_to_onehot;
   sp_.min_data_per_group = cfg.min_data_per_group; sp_.cat_l2 = cfg.cat_l2; sp_.cat_smooth = cfg.cat_smooth; sp_.extra_trees = cfg.extra_trees ? 1 : 0;
   sp_.cegb_split = cfg.cegb_tradeoff * cfg.cegb_penalty_split;
+  sp_.monotone_penalty = cfg.monotone_penalty;
   sp_.use_mc = 0; for (const auto& m : train->feature_meta) if (m.monotone != 0) sp_.use_mc = 1;
   col_sampler_.Init(cfg, train);
   clock_.enabled = getenv("FALCATA_STAGE_TIMING") != nullptr;

@@ -95,6 +95,7 @@ __device__ void ScanCategoricalWarp(const FindArgs& a, const BinSrc& src, char* 
   LeafScanInfo L;
   L.sum_g = leaf.sum_g; L.sum_h = leaf.sum_h; L.sum_gi = leaf.sum_gi; L.sum_hi = leaf.sum_hi; L.num_data = leaf.num_data_global;
   L.parent_output = leaf.output; L.g_scale = g_scale; L.h_scale = h_scale; L.min_c = leaf.min_c; L.max_c = leaf.max_c;
+  L.mono_factor = MonotonePenaltyFactor(leaf.depth, a.params.monotone_penalty);
   L.cnt_factor = FB_DIV(static_cast<double>(L.num_data), L.sum_h);
   if (a.params.max_delta_step <= 0.0 && a.params.path_smooth <= 0.0)
     L.min_gain_shift = FB_ADD(LeafGain(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), a.params, L.num_data, leaf.output), a.params.min_gain_to_split);
@@ -234,6 +235,7 @@ __device__ void FindSplitsWarp(const FindArgs& a) {
   LeafScanInfo L;
   L.sum_g = leaf.sum_g; L.sum_h = leaf.sum_h; L.sum_gi = leaf.sum_gi; L.sum_hi = leaf.sum_hi; L.num_data = leaf.num_data_global;
   L.parent_output = leaf.output; L.g_scale = QUANT ? static_cast<double>(a.scales[0]) : 1.0; L.h_scale = QUANT ? static_cast<double>(a.scales[1]) : 1.0; L.min_c = leaf.min_c; L.max_c = leaf.max_c;
+  L.mono_factor = MonotonePenaltyFactor(leaf.depth, a.params.monotone_penalty);
   L.cnt_factor = FB_DIV(static_cast<double>(L.num_data), L.sum_h);
   if (a.params.max_delta_step <= 0.0 && a.params.path_smooth <= 0.0)
     L.min_gain_shift = FB_ADD(LeafGain(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), a.params, L.num_data, leaf.output), a.params.min_gain_to_split);

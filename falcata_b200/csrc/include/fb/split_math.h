@@ -34,6 +34,7 @@ struct SplitParams {
   int max_cat_threshold, max_cat_to_onehot, min_data_per_group;
   double cat_l2, cat_smooth;
   int extra_trees;
+  double monotone_penalty;   // splits on monotone-constrained features near the root are discouraged: their gain is scaled by MonotonePenaltyFactor(depth)
   double cegb_split;   // cost-effective boosting: cegb_tradeoff * cegb_penalty_split, charged per row of the leaf against every split gain
   int use_mc;   // some feature carries a monotone constraint: leaf outputs are clamped to the leaf's [min, max] range
 };
@@ -141,7 +142,25 @@ struct LeafScanInfo {
   double cnt_factor;          // num_data / sum_h
   double g_scale, h_scale;    // quantized: real = int * scale; else 1
   double min_c, max_c;        // monotone range of the leaf's output (-inf, +inf when unconstrained)
+  double mono_factor;         // factor on the gain of splits on monotone-constrained features at this leaf's depth (1: no penalty)
 };
+
+// Gain factor of a monotone split at `depth` (root = 0) for monotone_penalty p: 0 up to depth p - 1 (in effect
+// forbidden), then rising towards 1 with depth. Parity: src/treelearner/monotone_constraints.hpp
+// (ComputeMonotoneSplitGainPenalty).
+FB_HD inline double MonotonePenaltyFactor(int depth, double p) {
+  if (p <= 0.0) return 1.0;
+  if (p >= depth + 1.0) return kEpsilon;
+  double pow2 = 1.0;
+  if (p <= 1.0) { for (int i = 0; i < depth; ++i) pow2 *= 2.0; return 1.0 - p / pow2 + kEpsilon; }
+  // 1 - 2^(p - 1 - depth): the exponent is negative here
+  const double e = p - 1.0 - depth;
+#if defined(__CUDA_ARCH__)
+  return 1.0 - exp2(e) + kEpsilon;
+#else
+  return 1.0 - std::exp2(e) + kEpsilon;
+#endif
+}
 
 // Output of a child of leaf L: the regularised output, clamped to the leaf's monotone range when constraints are on.
 FB_HD inline double ChildOutput(double g, double h, const SplitParams& p, int num_data, const LeafScanInfo& L) {
@@ -164,7 +183,8 @@ FB_HD inline double EvalCandidate(double lg, double lh, int lcnt, const LeafScan
   double gain;
   if (!SplitGain(lg, FB_ADD(lh, kEpsilon), rg, FB_ADD(rh, kEpsilon), p, lcnt, rcnt, L.parent_output, monotone, L.min_c, L.max_c, &gain, lout, rout)) return ninf;
   if (!(gain > L.min_gain_shift)) return ninf;
-  return FB_SUB(gain, L.min_gain_shift);
+  const double above = FB_SUB(gain, L.min_gain_shift);
+  return (monotone != 0 && L.mono_factor != 1.0) ? FB_MUL(above, L.mono_factor) : above;
 }
 
 // Leaf-wise (best-first) order key. Along the path from the root, keep the gains that are smaller than every later

@@ -395,3 +395,18 @@ def test_fixedpoint_error_feedback_and_robust_scale_switches():
     exact = fb.train(dict(p, quant_mode="none"), fb.Dataset(X, y), 10)
     ll = lambda b: float(np.mean(np.where(y > 0, -np.log(b.predict(X)), -np.log(1 - b.predict(X)))))
     assert ll(full) <= ll(no_ef) + 0.01 and abs(ll(full) - ll(exact)) < 0.03
+
+
+def test_monotone_penalty_keeps_constrained_features_out_of_the_top_of_the_tree():
+    rng = np.random.default_rng(71)
+    X = rng.normal(size=(4000, 3)); y = 3 * X[:, 0] + X[:, 1] + 0.1 * rng.normal(size=4000)
+    base = {"objective": "regression", "num_leaves": 15, "verbosity": -1, "min_data_in_leaf": 10, "monotone_constraints": [1, 0, 0]}
+
+    def root_feature(p):
+        return fb.train(p, fb.Dataset(X, y), 1).dump_model()["tree_info"][0]["tree_structure"]["split_feature"]
+    assert root_feature(dict(base)) == 0                               # the strongest feature splits the root
+    assert root_feature(dict(base, monotone_penalty=2.0)) != 0          # its gain is wiped out at depths 0 and 1
+    deep = fb.train(dict(base, monotone_penalty=2.0), fb.Dataset(X, y), 1)
+    assert deep.feature_importance()[0] > 0                             # and comes back further down
+    pr = deep.predict(np.column_stack([np.linspace(-2, 2, 50), np.zeros(50), np.zeros(50)]))
+    assert np.all(np.diff(pr) >= -1e-12)

@@ -513,3 +513,15 @@ def test_rank_xendcg_gradient_kernel_matches_the_host_objective():
     assert nd[-1] > nd[0] and nd[-1] > 0.75
     assert abs(nd[-1] - nh[-1]) < 0.02
     assert np.corrcoef(pd, ph)[0, 1] > 0.99
+
+
+def test_monotone_penalty_on_the_device_matches_the_host_learner():
+    rng = np.random.default_rng(71)
+    X = rng.normal(size=(8000, 3)).astype(np.float32); y = 3 * X[:, 0] + X[:, 1] + 0.1 * rng.normal(size=8000)
+    p = {"objective": "regression", "num_leaves": 15, "verbosity": -1, "min_data_in_leaf": 10, "monotone_constraints": [1, 0, 0], "monotone_penalty": 2.0,
+         "quant_mode": "none"}
+    dev = fb.train(dict(p, device_type="cuda"), fb.Dataset(X, y), 3)
+    host = fb.train(dict(p, device_type="cpu"), fb.Dataset(X, y), 3)
+    root = lambda b: b.dump_model()["tree_info"][0]["tree_structure"]["split_feature"]
+    assert root(dev) != 0 and root(dev) == root(host)
+    np.testing.assert_allclose(dev.predict(X), host.predict(X), rtol=1e-5, atol=1e-5)
