@@ -177,7 +177,46 @@ static void TestLeafwiseKeys() {
   }
 }
 
+// Fixed-point quantizer extras: the error feedback carries what rounding dropped into the next round, saturation is not
+// fed back, and the robust scale re-anchors only below a small outlier cluster that an empty octave separates from the rest.
+static void TestFixedPointExtras() {
+  // feedback: a value of 0.3 levels rounds to 0, 0, 0, 1 ... so that the long-run mean is 0.3 levels
+  int8_t res[2] = {0, 0};
+  long long sum_g = 0, sum_h = 0;
+  const int rounds = 1000;
+  for (int r = 0; r < rounds; ++r) { const int32_t w = QuantizeRowFeedback(0.3f, 0.3f, 1.0f, 1.0f, 0, res); sum_g += UnpackG(w); sum_h += UnpackH(w); }
+  CHECK(std::fabs(static_cast<double>(sum_g) / rounds - 0.3) < 0.01);
+  CHECK(std::fabs(static_cast<double>(sum_h) / rounds - 0.3) < 0.01);
+  long long plain = 0;
+  for (int r = 0; r < rounds; ++r) plain += UnpackG(QuantizeRowFeedback(0.3f, 0.3f, 1.0f, 1.0f, 0, nullptr));
+  CHECK(plain == 0);                                               // without feedback the 0.3 is lost every round
+  res[0] = res[1] = 0;
+  const int32_t sat = QuantizeRowFeedback(-100.0f, 1.0f, 1.0f, 1.0f, 32, res);
+  CHECK(UnpackG(sat) == -32 && res[1] == 0);                       // saturated, and the saturation is not carried
+  // robust scale: 1000 rows around 1e-3 .. 2e-3 and 5 rows at 1.0
+  std::vector<long long> hist(kQuantMagBuckets, 0);
+  for (int i = 0; i < 1000; ++i) ++hist[QuantMagBucket(1e-3f + 1e-6f * i, 1.0f)];
+  for (int i = 0; i < 5; ++i) ++hist[QuantMagBucket(1.0f - 0.01f * i, 1.0f)];
+  const float anchor = RobustGradAnchor(hist.data(), 1005, 1.0f);
+  CHECK(anchor < 1.0f && anchor >= 2e-3f * 0.99f && anchor < 2.1e-3f);   // the upper edge of the bulk's top bucket
+  // the same bulk without a gap below the top (magnitudes spread over every octave): nothing moves
+  std::fill(hist.begin(), hist.end(), 0);
+  for (int i = 0; i < 2000; ++i) ++hist[QuantMagBucket(std::pow(2.0f, -10.0f * i / 2000.0f), 1.0f)];
+  CHECK(RobustGradAnchor(hist.data(), 2000, 1.0f) == 1.0f);
+  // many large values are not outliers
+  std::fill(hist.begin(), hist.end(), 0);
+  for (int i = 0; i < 1000; ++i) ++hist[QuantMagBucket(1e-3f, 1.0f)];
+  for (int i = 0; i < 200; ++i) ++hist[QuantMagBucket(1.0f, 1.0f)];
+  CHECK(RobustGradAnchor(hist.data(), 1200, 1.0f) == 1.0f);
+  // monotone penalty factor: forbidden near the root, towards 1 with depth
+  CHECK(MonotonePenaltyFactor(0, 0.0) == 1.0);
+  CHECK(MonotonePenaltyFactor(0, 2.0) < 1e-10 && MonotonePenaltyFactor(1, 2.0) < 1e-10);
+  CHECK(std::fabs(MonotonePenaltyFactor(2, 2.0) - 0.5) < 1e-9 && std::fabs(MonotonePenaltyFactor(3, 2.0) - 0.75) < 1e-9);
+  CHECK(std::fabs(MonotonePenaltyFactor(2, 0.5) - (1.0 - 0.5 / 4.0)) < 1e-9);
+}
+
 int main() {
+  TestFixedPointExtras();
   TestFormatting();
   TestPhilox();
   TestQuantizeRow();
