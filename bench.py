@@ -272,13 +272,18 @@ def reference_arm(args) -> None:
             Xh = X.cpu().numpy()
             del X
             torch.cuda.empty_cache()
-            t0 = time.perf_counter()
-            ds2 = falcata.Dataset(Xh, yh, params={"max_bin": 63, "device_type": "cuda", "verbosity": -1})
-            rec = {}
-            falcata.train(dict(params_for(True), is_provide_training_metric=True), ds2, K, valid_sets=[ds2], valid_names=["train"], callbacks=[falcata.record_evaluation(rec)])
-            sync_all()
-            dt = time.perf_counter() - t0
-            out["e2e"] = {"value": dt / K * 1000.0, "unit": "s/1000 rounds (ingest from host memory + K rounds + per-round metric read, wall clock / K)",
+            runs = []
+            for rep in range(2):   # the faster of two complete runs, as in the other arm
+                t0 = time.perf_counter()
+                ds2 = falcata.Dataset(Xh, yh, params={"max_bin": 63, "device_type": "cuda", "verbosity": -1})
+                rec = {}
+                falcata.train(dict(params_for(True), is_provide_training_metric=True), ds2, K, valid_sets=[ds2], valid_names=["train"], callbacks=[falcata.record_evaluation(rec)])
+                sync_all()
+                runs.append(time.perf_counter() - t0)
+                del ds2
+            dt = min(runs)
+            out["e2e"] = {"value": dt / K * 1000.0, "unit": "s/1000 rounds (ingest from host memory + K rounds + per-round metric read, wall clock / K; the faster of two complete runs)",
+                          "runs_ms_per_round": [r / K * 1000.0 for r in runs],
                           "h2d_bytes_per_step": int((Xh.nbytes + yh.nbytes) / K), "d2h_bytes_per_step": 16}
         except Exception as e:   # noqa: BLE001
             out["e2e"] = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
@@ -408,20 +413,27 @@ def main() -> None:
         yh = y.cpu().numpy()
         del X
         torch.cuda.empty_cache()
-        barrier()
-        if os.environ.get("FALCATA_TIME_TAG"):
-            fb.set_time_tag(True)
-        t0 = time.perf_counter()
-        # the pinned host matrix goes straight into the public API: the library copies it to the device on a side stream
-        # while the host finds the bin boundaries, then bins on the device
-        ds2 = fb.Dataset(Xh, yh, params={"max_bin": PARAMS["max_bin"], "device_type": "cuda", "num_threads": PARAMS.get("num_threads", 0)}).set_global_rows(off, args.rows)
-        fb.train(dict(PARAMS, is_provide_training_metric=True), ds2, K, valid_sets=[ds2], valid_names=["train"], keep_training_booster=True,
-                 callbacks=[fb.record_evaluation({})])
-        barrier()
-        dt = max_over_ranks(time.perf_counter() - t0)
+        # The whole end-to-end run (ingest + K rounds with a metric read each) is done twice and the faster one reported:
+        # it is a wall-clock figure of about 0.15 s dominated by host work, and a freshly started machine can stall one run.
+        runs = []
+        for rep in range(2):
+            barrier()
+            if os.environ.get("FALCATA_TIME_TAG"):
+                fb.set_time_tag(False); fb.set_time_tag(True)
+            t0 = time.perf_counter()
+            # the pinned host matrix goes straight into the public API: the library copies it to the device on a side stream
+            # while the host finds the bin boundaries, then bins on the device
+            ds2 = fb.Dataset(Xh, yh, params={"max_bin": PARAMS["max_bin"], "device_type": "cuda", "num_threads": PARAMS.get("num_threads", 0)}).set_global_rows(off, args.rows)
+            bst2 = fb.train(dict(PARAMS, is_provide_training_metric=True), ds2, K, valid_sets=[ds2], valid_names=["train"], keep_training_booster=True,
+                            callbacks=[fb.record_evaluation({})])
+            barrier()
+            runs.append(max_over_ranks(time.perf_counter() - t0))
+            del bst2, ds2
+        dt = min(runs)
         if os.environ.get("FALCATA_TIME_TAG") and rank == 0:
             print(fb.time_tag_report(), file=sys.stderr)
-        e2e = {"value": dt / K * 1000.0, "unit": "s/1000 rounds (ingest from pinned host memory + K rounds + per-round metric read, wall clock / K)",
+        e2e = {"value": dt / K * 1000.0, "unit": "s/1000 rounds (ingest from pinned host memory + K rounds + per-round metric read, wall clock / K; the faster of two complete runs)",
+               "runs_ms_per_round": [r / K * 1000.0 for r in runs],
                "h2d_bytes_per_step": int((Xh.numel() * Xh.element_size() + yh.nbytes) / K), "d2h_bytes_per_step": 16}
 
     if rank == 0:
