@@ -272,8 +272,11 @@ def reference_arm(args) -> None:
             Xh = X.cpu().numpy()
             del X
             torch.cuda.empty_cache()
+            import gc
+
             runs = []
             for rep in range(2):   # the faster of two complete runs, as in the other arm
+                gc.collect(); sync_all()
                 t0 = time.perf_counter()
                 ds2 = falcata.Dataset(Xh, yh, params={"max_bin": 63, "device_type": "cuda", "verbosity": -1})
                 rec = {}
@@ -415,8 +418,11 @@ def main() -> None:
         torch.cuda.empty_cache()
         # The whole end-to-end run (ingest + K rounds with a metric read each) is done twice and the faster one reported:
         # it is a wall-clock figure of about 0.15 s dominated by host work, and a freshly started machine can stall one run.
+        import gc
+
         runs = []
         for rep in range(2):
+            gc.collect(); torch.cuda.synchronize()   # boosters of the earlier arms release their device memory now, not inside the timed region
             barrier()
             if os.environ.get("FALCATA_TIME_TAG"):
                 fb.set_time_tag(False); fb.set_time_tag(True)
