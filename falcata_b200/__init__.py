@@ -11,6 +11,7 @@ from .basic import (Booster, Dataset, FalcataError, LightGBMError, cuda_availabl
 from .callback import EarlyStopException, early_stopping, log_evaluation, record_evaluation, reset_parameter
 from .engine import CVBooster, cv, train
 from .importers import from_catboost, from_xgboost
+from . import tuner
 from .oblique import ObliquePool
 from .plotting import create_tree_digraph, plot_importance, plot_metric, plot_split_value_histogram, plot_tree
 

@@ -881,6 +881,12 @@ class Booster:
                 train_set.params["keep_host_bins"] = True   # the host learner will do the training: it needs host-resident bins
             with _tag("booster: dataset construct"):
                 train_set.construct()
+            if str(self.params.get("cuda_plan", "")).strip().lower() == "wisdom":
+                # the plan that tuner.tune() stored for this shape of workload on this kind of device ("auto" when none)
+                from . import tuner
+                from .parallel import bootstrap
+
+                self.params = dict(self.params, cuda_plan=tuner.lookup(self.params, train_set.num_data(), train_set.num_feature(), bootstrap.world()[1]))
             with _tag("booster: native create (objective, metrics, device engine)"):
                 _safe_call(lib.FB_BoosterCreate(train_set._handle, _param_str(self.params), ctypes.byref(self._handle)))
         elif model_file is not None:

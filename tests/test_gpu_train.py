@@ -525,3 +525,18 @@ def test_monotone_penalty_on_the_device_matches_the_host_learner():
     root = lambda b: b.dump_model()["tree_info"][0]["tree_structure"]["split_feature"]
     assert root(dev) != 0 and root(dev) == root(host)
     np.testing.assert_allclose(dev.predict(X), host.predict(X), rtol=1e-5, atol=1e-5)
+
+
+def test_plan_tuner_probes_the_device_and_keeps_the_model(tmp_path, monkeypatch):
+    from falcata_b200 import tuner
+
+    monkeypatch.setenv("FALCATA_WISDOM", str(tmp_path / "wisdom.json"))
+    X, y = make_binary(60000, 12)
+    params = {"objective": "binary", "num_leaves": 31, "verbosity": -1, "quant_mode": "stochastic", "quant_bins": 4, "device_type": "cuda"}
+    plan = tuner.tune(params, fb.Dataset(X, y), rounds=4, warmup=2, switches=["fused_scan", "fused_tail", "hist_lane_red"])
+    assert plan.startswith("auto")
+    entry = tuner.load_wisdom()[tuner.wisdom_key(params, 60000, 12)]
+    assert entry["plan"] == plan and len(entry["probes"]) == 4 and all("ms" in p for p in entry["probes"])
+    a = fb.train(dict(params, cuda_plan="wisdom"), fb.Dataset(X, y), 6).model_to_string()
+    b = fb.train(dict(params), fb.Dataset(X, y), 6).model_to_string()
+    assert model_body(a) == model_body(b)

@@ -421,3 +421,45 @@ def test_sklearn_custom_objective_metric_and_class_weight():
     both = LGBMClassifier(n_estimators=10, num_leaves=7, class_weight={0: 1.0, 1: 3.0}).fit(X, yc, sample_weight=w)
     manual = LGBMClassifier(n_estimators=10, num_leaves=7).fit(X, yc, sample_weight=w * np.where(yc == 1, 3.0, 1.0))
     assert np.allclose(both.predict_proba(X), manual.predict_proba(X))
+
+
+def test_plan_tuner_and_wisdom_file(tmp_path, monkeypatch):
+    """The tuner flips the plan switches one at a time, keeps the flips that a timer calls faster by more than the
+    margin, stores the plan under the workload's key, and cuda_plan="wisdom" picks it up."""
+    from falcata_b200 import tuner
+
+    monkeypatch.setenv("FALCATA_WISDOM", str(tmp_path / "w" / "wisdom.json"))
+    rng = np.random.default_rng(81)
+    X = rng.normal(size=(3000, 6)); y = (X[:, 0] > 0).astype(np.float64)
+    ds = fb.Dataset(X, y)
+    params = {"objective": "binary", "num_leaves": 15, "verbosity": -1, "quant_mode": "stochastic", "quant_bins": 4}
+    seen = []
+
+    def fake_timer(plan):
+        seen.append(plan)
+        ms = 10.0
+        if "fused_scan:off" in plan:
+            ms -= 2.0            # a real gain
+        if "bulk_root:off" in plan:
+            ms -= 0.05           # inside the noise margin: not kept
+        if "gh_in_row:on" in plan:
+            ms += 3.0
+        return ms
+    best = tuner.tune(params, ds, timer=fake_timer)
+    assert best == "auto,fused_scan:off"
+    assert seen[0] == "auto" and len(seen) == 1 + len(tuner.TUNABLE)
+    assert all(p.startswith("auto") for p in seen)
+    stored = tuner.load_wisdom()
+    key = tuner.wisdom_key(params, 3000, 6)
+    assert stored[key]["plan"] == best and abs(stored[key]["ms_per_round"] - 8.0) < 1e-9
+    assert tuner.lookup(params, 3000, 6) == best
+    assert tuner.lookup(params, 3100, 6) == best            # a few more rows: the same entry
+    assert tuner.lookup(params, 300000, 6) == "auto"        # another size: nothing stored
+    # the booster resolves "wisdom" through the same file; the plan never changes the model
+    a = fb.train(dict(params, cuda_plan="wisdom"), fb.Dataset(X, y), 5)
+    b = fb.train(dict(params), fb.Dataset(X, y), 5)
+    assert a.model_to_string().split("\nparameters:")[0] == b.model_to_string().split("\nparameters:")[0]
+    assert "fused_scan:off" in a.model_to_string()           # the resolved plan is what the model records
+    # the built-in measurement runs on the host learner too
+    quick = tuner.tune(params, fb.Dataset(X, y), rounds=2, warmup=1, switches=["fused_scan"], store=False)
+    assert quick in ("auto", "auto,fused_scan:off")
