@@ -38,6 +38,91 @@ def _repeat_trees(fb, bst, n_trees):
     return fb.Booster(model_str=model)
 
 
+def reference_arm(args) -> None:
+    """The same configuration through the reference's own Python API (`falcata` from baseline/_ref), on one GPU; the data
+    generator is loaded by file path so that this repository's package is never imported in the process."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    import bench
+
+    ref_dir = os.path.join(root, "baseline", "_ref")
+    if not os.path.isfile(os.path.join(ref_dir, "falcata", "lib", "lib_falcata.so")):
+        print(json.dumps({"config": args.config, "impl": "reference", "unavailable": "baseline/_ref holds no built reference (python baseline/build_reference.py)"}))
+        return
+    import numpy as np
+    import torch
+
+    os.environ.setdefault("NCCL_P2P_DISABLE", "0")
+    bench._preload(["libnvrtc.so.12", "libnccl.so.2"])
+    sys.path.insert(0, ref_dir)
+    try:
+        import falcata
+    except Exception as e:   # noqa: BLE001
+        print(json.dumps({"config": args.config, "impl": "reference", "unavailable": f"the built reference does not load here: {type(e).__name__}: {str(e)[:160]}"}))
+        return
+
+    class _Quiet:
+        def info(self, msg): pass
+        def warning(self, msg): print(msg, file=sys.stderr)
+    falcata.register_logger(_Quiet())
+    synthetic = bench.load_synthetic()
+    group = None
+    try:
+        if args.config == 1:
+            X, y = synthetic.binary_small(device="cpu")
+            p = {"objective": "binary", "num_leaves": 31, "max_bin": 255, "learning_rate": 0.1, "device_type": "cpu", "verbosity": -1}
+            ds = falcata.Dataset(X.numpy(), y.numpy()); ds.construct()
+            t0 = time.perf_counter()
+            bst = falcata.train(p, ds, 100)
+            dt = time.perf_counter() - t0
+            acc = float(((bst.predict(X.numpy()) > 0.5) == (y.numpy() > 0.5)).mean())
+            print(json.dumps({"config": 1, "impl": "reference", "s_per_1000_rounds": dt * 10, "train_accuracy": acc}))
+            return
+        dev = "cuda:0"
+        torch.cuda.set_device(0)
+        if args.config == 2:
+            total = int(11_000_000 * args.rows_scale)
+            X, y = synthetic.binary_higgs_like(total, device=dev)
+            p = {"objective": "binary", "num_leaves": 255, "max_bin": 63, "learning_rate": 0.1, "quant_mode": "stochastic", "quant_bins": 4, "max_depth": 8}
+        elif args.config == 3:
+            total = int(1_000_000 * args.rows_scale)
+            X, y = synthetic.regression_wide(total, device=dev)
+            p = {"objective": "regression", "num_leaves": 255, "max_bin": 16, "feature_fraction": 0.1, "enable_bundle": True, "quant_mode": "fixedpoint", "quant_bins": 64}
+        elif args.config == 4:
+            total = int(5_000_000 * args.rows_scale)
+            X, y = synthetic.multiclass(total, device=dev)
+            p = {"objective": "multiclass", "num_class": 10, "num_leaves": 127, "max_bin": 255, "quant_mode": "none"}
+        else:
+            totalq = int(100_000 * args.rows_scale)
+            X, y, group = synthetic.ranking(totalq, device=dev)
+            total = totalq * 100
+            p = {"objective": "lambdarank", "metric": "ndcg", "eval_at": "10", "num_leaves": 255}
+        p.update({"device_type": "cuda", "verbosity": -1, "tree_learner": "serial", "cuda_precision": "fp32"})
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        ds = falcata.Dataset(X, y.cpu().numpy(), group=None if group is None else group.numpy(), params={"max_bin": p.get("max_bin", 255), "device_type": "cuda", "verbosity": -1})
+        bst = falcata.Booster(p, ds)
+        torch.cuda.synchronize()
+        construct_s = time.perf_counter() - t0
+        for _ in range(max(3, args.warmup)):
+            bst.update()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.rounds):
+            bst.update()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        out = {"config": args.config, "impl": "reference", "n_gpus": 1, "rows_total": total, "rounds_timed": args.rounds, "s_per_1000_rounds": dt * 1000.0 / args.rounds,
+               "construct_seconds": construct_s, "timing": "wall clock around update() calls with a device synchronize on both sides"}
+        try:
+            out["train_metric"] = bst.eval_train()
+        except Exception as e:   # noqa: BLE001
+            out["train_metric"] = f"unavailable: {type(e).__name__}"
+        print(json.dumps(out, default=str))
+    except Exception as e:   # noqa: BLE001
+        print(json.dumps({"config": args.config, "impl": "reference", "unavailable": f"the reference raised on this configuration: {type(e).__name__}: {str(e)[:200]}"}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", type=int, required=True, choices=[1, 2, 3, 4, 5])
@@ -45,9 +130,14 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--rows-scale", type=float, default=1.0)
     ap.add_argument("--plan", default="auto")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"], help="reference: the unmodified reference built under baseline/_ref, one process, one GPU (config 1: its CPU learner)")
     ap.add_argument("--predict-trees", type=int, default=1000, help="config 5: size of the forest that the timed device prediction walks (the trained trees, repeated)")
     ap.add_argument("--grow-policy", default="level", choices=["level", "leaf"], help="level: gain-ranked budget per level; leaf: exact best-first trees")
     args = ap.parse_args()
+
+    if args.impl == "reference":
+        reference_arm(args)
+        return
 
     import numpy as np
     import torch
