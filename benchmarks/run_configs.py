@@ -71,7 +71,7 @@ def reference_arm(args) -> None:
         if args.config == 1:
             X, y = synthetic.binary_small(device="cpu")
             p = {"objective": "binary", "num_leaves": 31, "max_bin": 255, "learning_rate": 0.1, "device_type": "cpu", "verbosity": -1}
-            ds = falcata.Dataset(X.numpy(), y.numpy()); ds.construct()
+            ds = falcata.Dataset(X.numpy(), y.numpy(), params={"device_type": "cpu", "max_bin": 255, "verbosity": -1}); ds.construct()
             t0 = time.perf_counter()
             bst = falcata.train(p, ds, 100)
             dt = time.perf_counter() - t0
