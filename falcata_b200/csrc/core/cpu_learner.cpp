@@ -349,6 +349,38 @@ void CPUTreeLearner::ConstructHistogram(LeafState* leaf) {
   // large leaves: row blocks on worker threads with private histograms, merged in thread order (integer bins:
   // exact for any thread count; real-valued bins: the summation order follows the thread count)
   const int nthreads = leaf->count >= 8192 ? std::max(1, std::min(omp_get_max_threads(), leaf->count / 4096)) : 1;
+  // medium leaves: the feature groups are dealt to worker threads, each walking all the leaf's rows for its groups. A
+  // bin still receives its rows in row order, so the sums are those of the serial loop whatever the thread count.
+  const int gthreads = nthreads > 1 ? 1 : std::max(1, std::min(std::min(omp_get_max_threads(), ng / 4), static_cast<int>(static_cast<int64_t>(leaf->count) * ng / 16384)));
+  if (gthreads > 1) {
+    if (quant_) leaf->hist_i.assign(2 * static_cast<size_t>(nb), 0); else leaf->hist.assign(2 * static_cast<size_t>(nb), 0.0);
+    const int count = leaf->count;
+#pragma omp parallel num_threads(gthreads)
+    {
+      const int t = omp_get_thread_num();
+      const int g0 = ng * t / gthreads, g1 = ng * (t + 1) / gthreads;
+      const int* start = ds_->group_bin_start.data();
+      if (quant_) {
+        int64_t* H = leaf->hist_i.data();
+        for (int k = 0; k < count; ++k) {
+          const data_size_t i = idx[k];
+          const int32_t w = gh_packed_[i];
+          const int64_t g = UnpackG(w), h = UnpackH(w);
+          for (int gidx = g0; gidx < g1; ++gidx) { const int s = start[gidx] + ds_->GroupBin(i, gidx); H[2 * s] += g; H[2 * s + 1] += h; }
+        }
+      } else {
+        double* H = leaf->hist.data();
+        for (int k = 0; k < count; ++k) {
+          const data_size_t i = idx[k];
+          const double g = grad_[i], h = hess_[i];
+          for (int gidx = g0; gidx < g1; ++gidx) { const int s = start[gidx] + ds_->GroupBin(i, gidx); H[2 * s] += g; H[2 * s + 1] += h; }
+        }
+      }
+    }
+    leaf->has_hist = true;
+    ReduceHistogramAcrossRanks(leaf);
+    return;
+  }
   if (quant_) {
     leaf->hist_i.assign(2 * static_cast<size_t>(nb), 0);
     std::vector<std::vector<int64_t>> priv(nthreads > 1 ? nthreads : 0);
@@ -413,11 +445,76 @@ void CPUTreeLearner::SubtractHistogram(const LeafState& parent, const LeafState&
   larger->has_hist = true;
 }
 
+// Gains of every threshold of one feature from its prefix sums, for the plain regularisation (no L1, no output cap,
+// no smoothing, no monotone range): out[t] = gain above `shift`, or -inf where a child is too small or the gain does
+// not clear the shift. No iteration depends on another, so the compiler vectorises the loop; every operation is a
+// correctly rounded IEEE add / multiply / divide in the order EvalCandidate uses, so the values equal the scalar scan's
+// bit for bit whatever the vector width.
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
+__attribute__((target_clones("default", "avx2", "avx512f")))
+#endif
+static void PlainGainPass(int n, const double* pg, const double* ph, const double* pc, double sum_g, double sum_h, double num_data, double min_data,
+                          double min_h, double l2, double shift, double* out) {
+  const double ninf = -std::numeric_limits<double>::infinity();
+  for (int t = 0; t < n; ++t) {
+    const double lg = pg[t], lh = ph[t], lc = pc[t];
+    const double rg = sum_g - lg, rh = sum_h - lh, rc = num_data - lc;
+    const double gain = (lg * lg) / ((lh + kEpsilon) + l2) + (rg * rg) / ((rh + kEpsilon) + l2);
+    const bool ok = (lc >= min_data) & (rc >= min_data) & (lh >= min_h) & (rh >= min_h) & (gain > shift);
+    out[t] = ok ? gain - shift : ninf;
+  }
+}
+
 // Numerical threshold search of one feature: one forward prefix over the non-missing bins serves
 // both scan directions (see ScanRank in fb/split_math.h).
 void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanInfo& L, SplitRecord* best) const {
   const FeatureMeta& m = ds_->feature_meta[f];
   const int nb = m.num_bin;
+  // The common case - real-valued bins of an unbundled feature without a missing bin, no forced or random threshold -
+  // reads the leaf's histogram in place: the same candidates in the same order with the same arithmetic as the general
+  // scan below (one pass, default direction left), without its per-call scratch arrays.
+  if (!quant_ && !m.bundled && !(m.missing_type != static_cast<int>(MissingType::None) && nb > 2) && !(sp_.extra_trees && nb > 2) &&
+      !(forced_bin_ >= 0 && f == forced_feature_)) {
+    const double* hist = leaf.hist.data() + 2 * static_cast<size_t>(m.hist_offset);
+    double best_gain = -std::numeric_limits<double>::infinity(); int best_t = -1;
+    double best_lg = 0, best_lh = 0; int best_lc = 0;
+    const double ninf = -std::numeric_limits<double>::infinity();
+    const int n = nb - 1;
+    if (sp_.lambda_l1 <= 0.0 && sp_.max_delta_step <= 0.0 && sp_.path_smooth <= 0.0 && sp_.use_mc == 0 && m.monotone == 0 && n > 0) {
+      static thread_local std::vector<double> buf;
+      if (buf.size() < 4 * static_cast<size_t>(n)) buf.resize(4 * static_cast<size_t>(n));
+      double* PG = buf.data(); double* PH = PG + n; double* PC = PH + n; double* G = PC + n;
+      double pg = 0, ph = 0; int pc = 0;
+      for (int t = 0; t < n; ++t) {
+        pg += hist[2 * t]; ph += hist[2 * t + 1]; pc += BinCountEstimate(hist[2 * t + 1], L.cnt_factor);
+        PG[t] = pg; PH[t] = ph; PC[t] = pc;
+      }
+      PlainGainPass(n, PG, PH, PC, L.sum_g, L.sum_h, L.num_data, sp_.min_data_in_leaf, sp_.min_sum_hessian_in_leaf, sp_.lambda_l2, L.min_gain_shift, G);
+      for (int t = 0; t < n; ++t) if (G[t] != ninf && G[t] >= best_gain) { best_gain = G[t]; best_t = t; }   // equal gains: the higher threshold ranks first (ScanRank, pass 0)
+      if (best_t >= 0) { best_lg = PG[best_t]; best_lh = PH[best_t]; best_lc = static_cast<int>(PC[best_t]); }
+    } else {
+      double pg = 0, ph = 0; int pc = 0;
+      for (int t = 0; t < n; ++t) {
+        pg += hist[2 * t]; ph += hist[2 * t + 1]; pc += BinCountEstimate(hist[2 * t + 1], L.cnt_factor);
+        double lo, ro;
+        const double gain = EvalCandidate(pg, ph, pc, L, sp_, m.monotone, &lo, &ro);
+        if (gain == ninf) continue;
+        if (gain >= best_gain) { best_gain = gain; best_t = t; best_lg = pg; best_lh = ph; best_lc = pc; }
+      }
+    }
+    if (best_t >= 0) {
+      SplitRecord cand; InitSplitRecord(&cand);
+      cand.gain = best_gain; cand.feature = f; cand.threshold = best_t; cand.default_left = 1;
+      cand.left_g = best_lg; cand.left_h = best_lh; cand.right_g = FB_SUB(L.sum_g, best_lg); cand.right_h = FB_SUB(L.sum_h, best_lh);
+      cand.left_gi = 0; cand.left_hi = 0; cand.left_cnt = best_lc; cand.right_cnt = L.num_data - best_lc; cand.monotone = m.monotone;
+      cand.left_out = ChildOutput(cand.left_g, FB_ADD(cand.left_h, kEpsilon), sp_, cand.left_cnt, L);
+      cand.right_out = ChildOutput(cand.right_g, FB_ADD(cand.right_h, kEpsilon), sp_, cand.right_cnt, L);
+      cand.gain = FB_MUL(cand.gain, static_cast<double>(m.penalty));
+      if (SplitBetter(cand.gain, ds_->feature_meta[cand.feature].real_index, cand.threshold, best->gain,
+                      best->feature >= 0 ? ds_->feature_meta[best->feature].real_index : -1, best->threshold)) *best = cand;
+    }
+    return;
+  }
   auto slot = [&](int b) { return m.bundled ? m.hist_offset + (b < m.most_freq_bin ? b : b - 1) : m.hist_offset + b; };
   // per-bin values (integers when quantized)
   // scratch per worker thread: four arrays of nb values, zeroed (no allocation per call)
@@ -645,8 +742,8 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
     // one record per feature on the worker threads, merged in feature order (SplitBetter is a total order, so the
     // result does not depend on the thread count)
     std::vector<SplitRecord> per(ds_->num_features);
-    // a thread per ~2048 histogram bins to scan: waking more workers than that costs more than the scan itself
-    const int nt = std::max(1, std::min(std::min(omp_get_max_threads(), ds_->num_features / 2), ds_->num_total_bin / 2048 + 1));
+    // a thread per ~1024 histogram bins to scan: waking more workers than that costs more than the scan itself
+    const int nt = std::max(1, std::min(std::min(omp_get_max_threads(), ds_->num_features / 2), ds_->num_total_bin / 1024 + 1));
 #pragma omp parallel for schedule(dynamic, 1) num_threads(nt)
     for (int f = 0; f < ds_->num_features; ++f) {
       InitSplitRecord(&per[f]);
