@@ -314,6 +314,8 @@ def _trains_on_host(params: Dict[str, Any]) -> bool:
         v = params.get(k)
         if v is not None and len(v) > 0:
             return True
+    if text("monotone_constraints_method", "monotone_constraining_method", "mc_method") in ("intermediate", "advanced"):
+        return True
     return False
 
 

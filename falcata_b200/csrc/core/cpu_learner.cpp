@@ -102,7 +102,7 @@ struct LeafState {
   std::vector<double> hist;          // 2 * num_total_bin (g, h) real-valued, or
   std::vector<int64_t> hist_i;       // 2 * num_total_bin integer sums when quantized
   bool has_hist = false;
-  std::vector<int8_t> lo_bound_hi_bound;  // unused placeholder for monotone ranges
+  std::vector<uint16_t> box;         // monotone_constraints_method=intermediate: per feature the (first, last) bin of the leaf's cell
   double min_constraint = -std::numeric_limits<double>::infinity(), max_constraint = std::numeric_limits<double>::infinity();
 };
 
@@ -164,6 +164,9 @@ class CPUTreeLearner : public TreeLearner {
   // forced splits (forcedsplits_filename): a tree of (feature, threshold) applied from the root before normal growth
   struct ForcedNode { int feature = -1; double threshold = 0.0; int left = -1, right = -1; };
   std::vector<ForcedNode> forced_;
+  bool mono_intermediate_ = false;   // monotone bounds from the neighbouring leaves' outputs instead of the split's mid point
+  std::vector<int> mono_dirty_;      // leaves whose bounds the last ApplySplit tightened (their best split is stale)
+  void TightenMonotoneBounds(const Tree* tree, int left_id, int right_id);
   int forced_feature_ = -1, forced_bin_ = -1;   // non-negative while FindBestSplit evaluates one forced (feature, bin)
   void LoadForcedSplits();
   void ForceSplits(Tree* tree, int tree_index);
@@ -195,6 +198,7 @@ void CPUTreeLearner::SetParams() {
   if ((!cegb_coupled_.empty() || !cegb_lazy_.empty()) && Network::active() && cfg_.tree_learner != "serial")
     Log::Fatal("Per-feature CEGB penalties are not available with a parallel tree learner");
   sp_.use_mc = 0; for (const auto& m : ds_->feature_meta) if (m.monotone != 0) sp_.use_mc = 1;
+  mono_intermediate_ = sp_.use_mc != 0 && cfg_.monotone_constraints_method == "intermediate";
   quant_ = cfg_.quant != QuantMode::None;
   qs_.bins = cfg_.quant_bins_resolved; qs_.stochastic = cfg_.quant == QuantMode::Stochastic;
   const bool net = Network::active();
@@ -821,7 +825,12 @@ int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
   R.global_count = gr; Lf.global_count = gl;
   // monotone (basic): children inherit the parent's bounds, tightened at the mid point
   R.min_constraint = Lf.min_constraint; R.max_constraint = Lf.max_constraint;
-  if (s.monotone != 0) {
+  mono_dirty_.clear();
+  if (mono_intermediate_) {
+    R.box = Lf.box;
+    if (!s.is_categorical) { Lf.box[2 * s.feature + 1] = static_cast<uint16_t>(s.threshold); R.box[2 * s.feature] = static_cast<uint16_t>(s.threshold + 1); }
+    TightenMonotoneBounds(tree, leaf_id, right_id);
+  } else if (s.monotone != 0) {
     const double mid = (s.left_out + s.right_out) / 2.0;
     if (s.monotone > 0) { Lf.max_constraint = std::min(Lf.max_constraint, mid); R.min_constraint = std::max(R.min_constraint, mid); }
     else { Lf.min_constraint = std::max(Lf.min_constraint, mid); R.max_constraint = std::min(R.max_constraint, mid); }
@@ -839,6 +848,49 @@ int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
     SubtractHistogram(parent_copy, *smaller, larger);
   }
   return right_id;
+}
+
+// monotone_constraints_method=intermediate. Two leaves constrain one another when their cells (boxes in bin space)
+// touch along a monotone feature: disjoint in that feature and overlapping in every other one, so that a point can move
+// from one leaf to the other by changing that feature alone. The leaf on the lower side (for an increasing feature)
+// must not exceed the other's output. After a split the two new leaves are checked against every leaf of the tree
+// (and against one another): the lower leaf's upper bound drops to the upper leaf's output and the upper leaf's lower
+// bound rises to the lower leaf's output. Older leaves whose range shrank are listed in mono_dirty_; their best
+// split was found under the wider range and is searched again by the caller. Bounds only tighten, and an output, once
+// set, lies inside its leaf's bounds, so every pair stays ordered. Missing-value bins are not part of the cells.
+// Parity: src/treelearner/monotone_constraints.hpp (IntermediateLeafConstraints: bounds from the outputs of the
+// contiguous leaves, found there by walking up and down the tree from the split leaf).
+void CPUTreeLearner::TightenMonotoneBounds(const Tree* tree, int left_id, int right_id) {
+  const int nf = ds_->num_features;
+  auto relate = [&](int a, int b) {
+    // +1: a lies below b (a's output must not exceed b's); -1: a above b; 0: unrelated
+    const uint16_t* A = leaves_[a].box.data(); const uint16_t* B = leaves_[b].box.data();
+    int sep = -1, dir = 0;
+    for (int f = 0; f < nf; ++f) {
+      const bool a_below = A[2 * f + 1] < B[2 * f], b_below = B[2 * f + 1] < A[2 * f];
+      if (!a_below && !b_below) continue;
+      if (sep >= 0) return 0;                 // apart in two features: no single-feature move connects them
+      sep = f; dir = a_below ? 1 : -1;
+    }
+    if (sep < 0) return 0;                    // only categorical splits between them
+    const int mono = ds_->feature_meta[sep].monotone;
+    return mono == 0 ? 0 : (mono > 0 ? dir : -dir);
+  };
+  auto order = [&](int lower, int upper, bool lower_is_new, bool upper_is_new) {
+    LeafState& lo = leaves_[lower]; LeafState& up = leaves_[upper];
+    if (up.output < lo.max_constraint) { lo.max_constraint = up.output; if (!lower_is_new) mono_dirty_.push_back(lower); }
+    if (lo.output > up.min_constraint) { up.min_constraint = lo.output; if (!upper_is_new) mono_dirty_.push_back(upper); }
+  };
+  { const int r = relate(left_id, right_id); if (r > 0) order(left_id, right_id, true, true); else if (r < 0) order(right_id, left_id, true, true); }
+  for (int c : {left_id, right_id}) {
+    for (int l = 0; l < tree->num_leaves; ++l) {
+      if (l == left_id || l == right_id) continue;
+      const int r = relate(c, l);
+      if (r > 0) order(c, l, true, false); else if (r < 0) order(l, c, false, true);
+    }
+  }
+  std::sort(mono_dirty_.begin(), mono_dirty_.end());
+  mono_dirty_.erase(std::unique(mono_dirty_.begin(), mono_dirty_.end()), mono_dirty_.end());
 }
 
 double CPUTreeLearner::CegbFeaturePenalty(int inner_feature, const LeafState& leaf) const {
@@ -889,6 +941,10 @@ Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_i
     root.sum_g = s[0]; root.sum_h = s[1]; root.global_count = c;
   }
   root.output = LeafOutput(root.sum_g, FB_ADD(root.sum_h, 2 * kEpsilon), sp_, static_cast<int>(root.global_count), 0.0);
+  if (mono_intermediate_) {
+    root.box.resize(2 * static_cast<size_t>(ds_->num_features));
+    for (int f = 0; f < ds_->num_features; ++f) { root.box[2 * f] = 0; root.box[2 * f + 1] = static_cast<uint16_t>(std::min(65535, ds_->feature_meta[f].num_bin - 1)); }
+  }
   tree->leaf_value[0] = root.output; tree->leaf_count[0] = static_cast<int>(root.global_count); tree->leaf_weight[0] = root.sum_h;
   ConstructHistogram(&root);
   FindBestSplit(&root, 0, tree_index);
@@ -904,8 +960,10 @@ Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_i
       }
       if (best_leaf < 0) break;
       int right = ApplySplit(tree.get(), best_leaf);
+      const std::vector<int> dirty = mono_dirty_;   // leaves whose monotone range the split tightened
       FindBestSplit(&leaves_[best_leaf], best_leaf, tree_index);
       FindBestSplit(&leaves_[right], right, tree_index);
+      for (int d : dirty) FindBestSplit(&leaves_[d], d, tree_index);
     }
   } else {
     std::vector<int> frontier(tree->num_leaves); std::iota(frontier.begin(), frontier.end(), 0);   // more than the root after forced splits
@@ -922,7 +980,15 @@ Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_i
       }
       std::sort(cand.begin(), cand.end());   // a level's splits are always applied in ascending leaf order
       std::vector<int> next;
-      for (int l : cand) { int r = ApplySplit(tree.get(), l); next.push_back(l); next.push_back(r); }
+      std::vector<char> stale(mono_intermediate_ ? leaves_.size() + 2 * cand.size() : 0, 0);
+      for (int l : cand) {
+        if (mono_intermediate_ && stale[l]) {   // an earlier split of this level tightened the leaf's monotone range
+          FindBestSplit(&leaves_[l], l, tree_index);
+          if (leaves_[l].best.feature < 0 || !(leaves_[l].best.gain > 0.0)) continue;
+        }
+        int r = ApplySplit(tree.get(), l); next.push_back(l); next.push_back(r);
+        for (int d : mono_dirty_) if (d < static_cast<int>(stale.size())) stale[d] = 1;
+      }
       for (int l : next) FindBestSplit(&leaves_[l], l, tree_index);
       frontier.swap(next);
     }

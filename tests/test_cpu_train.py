@@ -170,6 +170,28 @@ def test_monotone_constraints_hold_over_the_whole_tree():
     assert _monotone_violations(free, 4, 0, +1, rng) > 1e-3   # the target itself is not monotone
 
 
+def test_monotone_intermediate_method_is_monotone_and_less_constraining():
+    """monotone_constraints_method=intermediate bounds a leaf by its neighbours' outputs instead of the split's mid
+    point: still monotone everywhere, with a training loss no worse than the basic method (reference test:
+    tests/python_package_test/test_engine.py test_monotone_constraints, every method)."""
+    rng = np.random.default_rng(3)
+    n = 6000
+    X = rng.normal(size=(n, 4)).astype(np.float32)
+    y = (np.sin(2 * X[:, 0]) + 0.5 * X[:, 0] - np.cos(2 * X[:, 1]) - 0.3 * X[:, 1] + X[:, 2] * X[:, 0] * 0.5
+         + 0.1 * rng.normal(size=n)).astype(np.float32)
+    for policy in ("level", "leaf"):
+        loss = {}
+        for method in ("basic", "intermediate", "advanced"):
+            p = {"objective": "regression", "num_leaves": 31, "learning_rate": 0.2, "verbose": -1, "min_data_in_leaf": 10,
+                 "monotone_constraints": [1, -1, 0, 0], "monotone_constraints_method": method, "grow_policy": policy}
+            b = fb.train(p, fb.Dataset(X, y), 30)
+            assert _monotone_violations(b, 4, 0, +1, rng) <= 1e-10
+            assert _monotone_violations(b, 4, 1, -1, rng) <= 1e-10
+            loss[method] = float(np.mean((b.predict(X) - y) ** 2))
+        assert loss["intermediate"] < loss["basic"]
+        assert loss["advanced"] == loss["intermediate"]   # advanced falls back to intermediate with a warning
+
+
 def _branch_feature_sets(bst):
     """Feature set of every root-to-leaf path of every tree."""
     out = []
