@@ -7,11 +7,7 @@
 
 namespace fb {
 
-int RowThreads(long long rows) {
-  const long long want = rows / 4096 + 1;
-  const long long cap = omp_get_max_threads();
-  return static_cast<int>(want < cap ? want : cap);
-}
+int RowThreads(long long rows) { return rows >= 8192 ? omp_get_max_threads() : 1; }
 
 
 namespace {

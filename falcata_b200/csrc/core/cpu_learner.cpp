@@ -352,78 +352,55 @@ void CPUTreeLearner::ConstructHistogram(LeafState* leaf) {
   const data_size_t* idx = indices_.data() + leaf->begin;
   // large leaves: row blocks on worker threads with private histograms, merged in thread order (integer bins:
   // exact for any thread count; real-valued bins: the summation order follows the thread count)
-  const int nthreads = leaf->count >= 8192 ? std::max(1, std::min(omp_get_max_threads(), leaf->count / 4096)) : 1;
-  // medium leaves: the feature groups are dealt to worker threads, each walking all the leaf's rows for its groups. A
+  // large leaves: row blocks with private histograms, merged in block order (integer bins: exact for any block count;
+  // real-valued bins: the summation order follows the block count, which follows the thread limit)
+  const int team = omp_get_max_threads();
+  const int nblocks = leaf->count >= 8192 ? std::max(1, std::min(team, leaf->count / 4096)) : 1;
+  // medium leaves: the feature groups are dealt to the worker threads, each walking all the leaf's rows for its groups. A
   // bin still receives its rows in row order, so the sums are those of the serial loop whatever the thread count.
-  const int gthreads = nthreads > 1 ? 1 : std::max(1, std::min(std::min(omp_get_max_threads(), ng / 4), static_cast<int>(static_cast<int64_t>(leaf->count) * ng / 16384)));
-  if (gthreads > 1) {
-    if (quant_) leaf->hist_i.assign(2 * static_cast<size_t>(nb), 0); else leaf->hist.assign(2 * static_cast<size_t>(nb), 0.0);
-    const int count = leaf->count;
-#pragma omp parallel num_threads(gthreads)
-    {
-      const int t = omp_get_thread_num();
-      const int g0 = ng * t / gthreads, g1 = ng * (t + 1) / gthreads;
-      const int* start = ds_->group_bin_start.data();
-      if (quant_) {
-        int64_t* H = leaf->hist_i.data();
-        for (int k = 0; k < count; ++k) {
-          const data_size_t i = idx[k];
-          const int32_t w = gh_packed_[i];
-          const int64_t g = UnpackG(w), h = UnpackH(w);
-          for (int gidx = g0; gidx < g1; ++gidx) { const int s = start[gidx] + ds_->GroupBin(i, gidx); H[2 * s] += g; H[2 * s + 1] += h; }
-        }
-      } else {
-        double* H = leaf->hist.data();
-        for (int k = 0; k < count; ++k) {
-          const data_size_t i = idx[k];
-          const double g = grad_[i], h = hess_[i];
-          for (int gidx = g0; gidx < g1; ++gidx) { const int s = start[gidx] + ds_->GroupBin(i, gidx); H[2 * s] += g; H[2 * s + 1] += h; }
-        }
-      }
+  const int gchunks = nblocks > 1 ? 1 : std::max(1, std::min(std::min(team, ng / 2), static_cast<int>(static_cast<int64_t>(leaf->count) * ng / 8192)));
+  const int* start = ds_->group_bin_start.data();
+  if (quant_) leaf->hist_i.assign(2 * static_cast<size_t>(nb), 0); else leaf->hist.assign(2 * static_cast<size_t>(nb), 0.0);
+  // rows [lo, hi) of the leaf, groups [g0, g1), into H
+  auto accumulate_i = [&](int lo, int hi, int g0, int g1, int64_t* H) {
+    for (int k = lo; k < hi; ++k) {
+      const data_size_t i = idx[k];
+      const int32_t w = gh_packed_[i];
+      const int64_t g = UnpackG(w), h = UnpackH(w);
+      for (int gidx = g0; gidx < g1; ++gidx) { const int s = start[gidx] + ds_->GroupBin(i, gidx); H[2 * s] += g; H[2 * s + 1] += h; }
     }
-    leaf->has_hist = true;
-    ReduceHistogramAcrossRanks(leaf);
-    return;
-  }
-  if (quant_) {
-    leaf->hist_i.assign(2 * static_cast<size_t>(nb), 0);
-    std::vector<std::vector<int64_t>> priv(nthreads > 1 ? nthreads : 0);
-#pragma omp parallel num_threads(nthreads)
-    {
-      const int t = omp_get_thread_num();
-      int64_t* H = leaf->hist_i.data();
-      if (nthreads > 1) { priv[t].assign(2 * static_cast<size_t>(nb), 0); H = priv[t].data(); }
-      const int lo = static_cast<int>(static_cast<int64_t>(leaf->count) * t / nthreads), hi = static_cast<int>(static_cast<int64_t>(leaf->count) * (t + 1) / nthreads);
-      for (int k = lo; k < hi; ++k) {
-        const data_size_t i = idx[k];
-        const int32_t w = gh_packed_[i];
-        const int64_t g = UnpackG(w), h = UnpackH(w);
-        for (int gidx = 0; gidx < ng; ++gidx) {
-          const int s = ds_->group_bin_start[gidx] + ds_->GroupBin(i, gidx);
-          H[2 * s] += g; H[2 * s + 1] += h;
-        }
-      }
+  };
+  auto accumulate_d = [&](int lo, int hi, int g0, int g1, double* H) {
+    for (int k = lo; k < hi; ++k) {
+      const data_size_t i = idx[k];
+      const double g = grad_[i], h = hess_[i];
+      for (int gidx = g0; gidx < g1; ++gidx) { const int s = start[gidx] + ds_->GroupBin(i, gidx); H[2 * s] += g; H[2 * s + 1] += h; }
     }
-    for (int t = 0; t < static_cast<int>(priv.size()); ++t) for (size_t b = 0; b < priv[t].size(); ++b) leaf->hist_i[b] += priv[t][b];
+  };
+  const int count = leaf->count;
+  if (nblocks > 1) {
+    std::vector<std::vector<int64_t>> priv_i(quant_ ? nblocks : 0); std::vector<std::vector<double>> priv_d(quant_ ? 0 : nblocks);
+#pragma omp parallel for schedule(static, 1) num_threads(team)
+    for (int b = 0; b < nblocks; ++b) {
+      const int lo = static_cast<int>(static_cast<int64_t>(count) * b / nblocks), hi = static_cast<int>(static_cast<int64_t>(count) * (b + 1) / nblocks);
+      if (quant_) { priv_i[b].assign(2 * static_cast<size_t>(nb), 0); accumulate_i(lo, hi, 0, ng, priv_i[b].data()); }
+      else { priv_d[b].assign(2 * static_cast<size_t>(nb), 0.0); accumulate_d(lo, hi, 0, ng, priv_d[b].data()); }
+    }
+    // merge: bins dealt to the threads, every bin adds its blocks in block order
+    const int64_t cells = 2 * static_cast<int64_t>(nb);
+#pragma omp parallel for schedule(static) num_threads(team)
+    for (int64_t c = 0; c < cells; ++c) {
+      if (quant_) { int64_t s = 0; for (int b = 0; b < nblocks; ++b) s += priv_i[b][c]; leaf->hist_i[c] = s; }
+      else { double s = 0.0; for (int b = 0; b < nblocks; ++b) s += priv_d[b][c]; leaf->hist[c] = s; }
+    }
+  } else if (gchunks > 1) {
+#pragma omp parallel for schedule(static, 1) num_threads(team)
+    for (int c = 0; c < gchunks; ++c) {
+      const int g0 = ng * c / gchunks, g1 = ng * (c + 1) / gchunks;
+      if (quant_) accumulate_i(0, count, g0, g1, leaf->hist_i.data()); else accumulate_d(0, count, g0, g1, leaf->hist.data());
+    }
   } else {
-    leaf->hist.assign(2 * static_cast<size_t>(nb), 0.0);
-    std::vector<std::vector<double>> priv(nthreads > 1 ? nthreads : 0);
-#pragma omp parallel num_threads(nthreads)
-    {
-      const int t = omp_get_thread_num();
-      double* H = leaf->hist.data();
-      if (nthreads > 1) { priv[t].assign(2 * static_cast<size_t>(nb), 0.0); H = priv[t].data(); }
-      const int lo = static_cast<int>(static_cast<int64_t>(leaf->count) * t / nthreads), hi = static_cast<int>(static_cast<int64_t>(leaf->count) * (t + 1) / nthreads);
-      for (int k = lo; k < hi; ++k) {
-        const data_size_t i = idx[k];
-        const double g = grad_[i], h = hess_[i];
-        for (int gidx = 0; gidx < ng; ++gidx) {
-          const int s = ds_->group_bin_start[gidx] + ds_->GroupBin(i, gidx);
-          H[2 * s] += g; H[2 * s + 1] += h;
-        }
-      }
-    }
-    for (int t = 0; t < static_cast<int>(priv.size()); ++t) for (size_t b = 0; b < priv[t].size(); ++b) leaf->hist[b] += priv[t][b];
+    if (quant_) accumulate_i(0, count, 0, ng, leaf->hist_i.data()); else accumulate_d(0, count, 0, ng, leaf->hist.data());
   }
   leaf->has_hist = true;
   ReduceHistogramAcrossRanks(leaf);
@@ -746,9 +723,10 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
     // one record per feature on the worker threads, merged in feature order (SplitBetter is a total order, so the
     // result does not depend on the thread count)
     std::vector<SplitRecord> per(ds_->num_features);
-    // a thread per ~1024 histogram bins to scan: waking more workers than that costs more than the scan itself
-    const int nt = std::max(1, std::min(std::min(omp_get_max_threads(), ds_->num_features / 2), ds_->num_total_bin / 1024 + 1));
-#pragma omp parallel for schedule(dynamic, 1) num_threads(nt)
+    // the whole team or the calling thread alone (a region with a smaller team than the last makes the runtime end and
+    // later restart its workers)
+    const bool spread = omp_get_max_threads() > 1 && ds_->num_features >= 4 && ds_->num_total_bin >= 1024;
+#pragma omp parallel for schedule(dynamic, 1) num_threads(omp_get_max_threads()) if (spread)
     for (int f = 0; f < ds_->num_features; ++f) {
       InitSplitRecord(&per[f]);
       if (!mask[f] || !FeatureOwned(f)) continue;

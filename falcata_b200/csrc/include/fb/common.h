@@ -69,8 +69,10 @@ class Log {
   }
 };
 
-// Worker threads for a loop over `rows` cheap items: one per ~4096 rows, at most the OpenMP maximum. On a host with a
-// hundred cores, waking every one of them for ten thousand rows costs far more than the loop.
+// Worker threads for a loop over `rows` cheap items: the whole team from 8192 rows on, else the calling thread alone.
+// Every parallel region of the library runs either on the full team or on one thread: the OpenMP runtime ends the
+// surplus workers whenever a region asks for a smaller team than the last one and starts new ones for the next larger
+// region, which costs a hundred times the region itself when team sizes alternate (measured: 240 us against 2.5 us).
 int RowThreads(long long rows);
 
 #define FB_CHECK(cond) do { if (!(cond)) ::fb::Log::Fatal("Check failed: " #cond " at %s:%d", __FILE__, __LINE__); } while (0)
