@@ -224,14 +224,14 @@ int FB_DatasetSetField(DatasetHandle handle, const char* field_name, const void*
       v->reserve(static_cast<size_t>(n));
       float* raw = v->data();
       if (raw != nullptr && n > (1 << 20)) {
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) num_threads(TeamThreads())
         for (int64_t i = 0; i < n; i += 1024) raw[i] = 0.f;
       }
       v->assign(static_cast<const float*>(data), static_cast<const float*>(data) + n);
       return;
     }
     v->resize(n);
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) num_threads(TeamThreads())
     for (int64_t i = 0; i < n; ++i) (*v)[i] = dtype == kF64 ? static_cast<float>(static_cast<const double*>(data)[i]) : static_cast<float>(static_cast<const int32_t*>(data)[i]);
   };
   if (f == "label" || f == "target") {

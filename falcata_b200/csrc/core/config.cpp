@@ -7,7 +7,29 @@
 
 namespace fb {
 
-int RowThreads(long long rows) { return rows >= 8192 ? omp_get_max_threads() : 1; }
+const DebugFlags& DebugFlags::Get() {
+  static const DebugFlags flags = [] {
+    DebugFlags f;
+    if (const char* e = getenv("FALCATA_DEBUG")) {
+      std::string s(e); size_t pos = 0;
+      while (pos <= s.size()) {
+        size_t c = s.find(',', pos); if (c == std::string::npos) c = s.size();
+        const std::string k = s.substr(pos, c - pos);
+        if (k == "diag") f.diag = true; else if (k == "dump") f.dump = true; else if (k == "sync" || k == "syncpairs") f.sync = true;
+        else if (k.rfind("maxsplits=", 0) == 0) f.maxsplits = std::max(0, atoi(k.c_str() + 10));
+        else if (!k.empty()) Log::Warning("FALCATA_DEBUG: unknown key %s (diag, dump, sync, maxsplits=N)", k.c_str());
+        pos = c + 1;
+      }
+    }
+    if (const char* e = getenv("FALCATA_DEBUG_SPLITS")) f.splits = e[0] != '\0' && e[0] != '0';
+    if (const char* e = getenv("FALCATA_VERIFY")) f.verify = e[0] != '\0' && e[0] != '0';
+    return f;
+  }();
+  return flags;
+}
+
+int TeamThreads() { return omp_get_max_threads(); }
+int RowThreads(long long rows) { return rows >= 8192 ? TeamThreads() : 1; }
 
 
 namespace {

@@ -753,6 +753,9 @@ int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
   if (!cegb_coupled_.empty() || !cegb_lazy_.empty()) CegbAfterSplit(s.feature, P);   // before the window is partitioned: the whole leaf passes the split
   const FeatureMeta& m = ds_->feature_meta[s.feature];
   const BinMapper& bm = *ds_->mappers[m.real_index];
+  if (DebugFlags::Get().splits)
+    Log::Info("[split] leaf %d depth %d feature %d bin %d gain %.9g left (n=%d g=%.9g h=%.9g out=%.9g) right (n=%d g=%.9g h=%.9g out=%.9g)%s", leaf_id, P.depth,
+              m.real_index, s.threshold, s.gain, s.left_cnt, s.left_g, s.left_h, s.left_out, s.right_cnt, s.right_g, s.right_h, s.right_out, s.is_categorical ? " categorical" : "");
   // stable partition of the leaf's window
   data_size_t* idx = indices_.data() + P.begin;
   int nl = 0, nr = 0;

@@ -148,7 +148,7 @@ void Dataset::ConstructSchemaTyped(const void* sample, int dtype, int ns, int nc
   const int kTile = split_search ? std::max(1, std::min(16, ncol / (4 * threads * nranks))) : std::max(1, std::min(16, ncol / (4 * threads)));
   const int ntiles = (ncol + kTile - 1) / kTile;
   std::vector<std::vector<int>> nz_by_col(cfg.enable_bundle ? ncol : 0);
-#pragma omp parallel for schedule(dynamic, 1)
+#pragma omp parallel for schedule(dynamic, 1) num_threads(TeamThreads())
   for (int t = 0; t < ntiles; ++t) {
     if (t % nranks != my_rank) continue;
     const int j0 = t * kTile, j1 = std::min(ncol, j0 + kTile), w = j1 - j0;
@@ -197,7 +197,7 @@ void Dataset::ConstructSchemaTyped(const void* sample, int dtype, int ns, int nc
     }
     if (cfg.enable_bundle) {
       // rows where a sparse feature leaves its most frequent bin, for the bundling below (needs every mapper)
-#pragma omp parallel for schedule(dynamic, 8)
+#pragma omp parallel for schedule(dynamic, 8) num_threads(TeamThreads())
       for (int j = 0; j < ncol; ++j) {
         const BinMapper& bm = *mappers[j];
         if (bm.is_trivial || bm.sparse_rate < 0.5) continue;
@@ -303,12 +303,12 @@ void Dataset::AllocateRows(data_size_t n) {
 void Dataset::PushDense(const void* data, int dtype, data_size_t n, int ncol, bool row_major, data_size_t row_begin) {
   if (ncol != num_total_features) Log::Fatal("The number of columns (%d) differs from the dataset's (%d)", ncol, num_total_features);
   if (keep_raw && !raw.empty()) {
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) num_threads(TeamThreads())
     for (data_size_t i = 0; i < n; ++i)
       for (int j = 0; j < ncol; ++j)
         raw[static_cast<size_t>(row_begin + i) * ncol + j] = static_cast<float>(ReadValue(data, dtype, row_major ? static_cast<size_t>(i) * ncol + j : static_cast<size_t>(j) * n + i));
   }
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) num_threads(TeamThreads())
   for (data_size_t i = 0; i < n; ++i) {
     const size_t out = static_cast<size_t>(row_begin + i) * row_stride;
     for (int g = 0; g < num_groups; ++g) {

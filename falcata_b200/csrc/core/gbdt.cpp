@@ -7,8 +7,23 @@ namespace fb {
 
 GBDT::~GBDT() {}
 
+// FALCATA_DEBUG=dump: every split of a finished tree, in node order (the same line for the host and the device learner)
+static void DumpTree(const Tree& t, size_t index) {
+  Log::Info("[dump] tree %d: %d leaves, shrinkage %.6g", static_cast<int>(index), t.num_leaves, t.shrinkage);
+  for (int s = 0; s + 1 < t.num_leaves; ++s)
+    Log::Info("[dump]   node %d: feature %d %s %.17g (bin %u) gain %.9g rows %d -> left %d right %d%s", s, t.split_feature[s],
+              (t.decision_type[s] & kCategoricalMask) ? "in set" : "<=", t.threshold[s], s < static_cast<int>(t.threshold_in_bin.size()) ? t.threshold_in_bin[s] : 0u,
+              static_cast<double>(t.split_gain[s]), s < static_cast<int>(t.internal_count.size()) ? t.internal_count[s] : -1, t.left_child[s], t.right_child[s],
+              (t.decision_type[s] & kDefaultLeftMask) ? " default-left" : "");
+  for (int l = 0; l < t.num_leaves; ++l) Log::Info("[dump]   leaf %d: value %.17g rows %d", l, t.leaf_value[l], l < static_cast<int>(t.leaf_count.size()) ? t.leaf_count[l] : -1);
+}
+
 void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj, const std::vector<std::string>& metric_names) {
   config_ = cfg; train_ = train; objective_ = obj; metric_names_ = metric_names;
+  if (DebugFlags::Get().maxsplits > 0 && config_.num_leaves > DebugFlags::Get().maxsplits + 1) {
+    Log::Warning("FALCATA_DEBUG maxsplits=%d: num_leaves lowered from %d to %d", DebugFlags::Get().maxsplits, config_.num_leaves, DebugFlags::Get().maxsplits + 1);
+    config_.num_leaves = DebugFlags::Get().maxsplits + 1;
+  }
   is_dart_ = cfg.boosting == "dart"; is_rf_ = cfg.boosting == "rf";
   is_cuda_ = cfg.is_cuda;
   num_class_ = cfg.num_class;
@@ -207,7 +222,7 @@ void GBDT::FitLinearLeaves(Tree* tree, const float* grad, const float* hess, boo
   const bool bagged = (is_bagging_ || is_goss_) && bag_cnt_ > 0 && bag_cnt_ < ds->num_data;
   const data_size_t m = bagged ? bag_cnt_ : ds->num_data;
   std::vector<int> leaf_of(m);
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) num_threads(TeamThreads())
   for (data_size_t t = 0; t < m; ++t) {
     const data_size_t i = bagged ? bag_indices_[t] : t;
     int node = 0;
@@ -222,7 +237,7 @@ void GBDT::FitLinearLeaves(Tree* tree, const float* grad, const float* hess, boo
   for (data_size_t t = 0; t < m; ++t) rows[leaf_of[t]].push_back(bagged ? bag_indices_[t] : t);
   const int ncol = ds->num_total_features;
   const double lambda = config_.linear_lambda;
-#pragma omp parallel for schedule(dynamic)
+#pragma omp parallel for schedule(dynamic) num_threads(TeamThreads())
   for (int leaf = 0; leaf < nl; ++leaf) {
     const int d = static_cast<int>(path[leaf].size());
     if (d == 0) continue;
@@ -408,7 +423,7 @@ bool GBDT::TrainOneIter(const float* grad_in, const float* hess_in) {
       if (models_.empty()) for (auto& t : trees) models_.push_back(std::move(t));
       return true;
     }
-    for (auto& t : trees) models_.push_back(std::move(t));
+    for (auto& t : trees) { if (DebugFlags::Get().dump) DumpTree(*t, models_.size()); models_.push_back(std::move(t)); }
     ++iter_;
     return false;
   }
@@ -472,6 +487,7 @@ bool GBDT::TrainOneIter(const float* grad_in, const float* hess_in) {
         if (!class_need_train_[k]) { double* ts = train_score_.data() + static_cast<size_t>(k) * n; for (data_size_t i = 0; i < n; ++i) ts[i] += out; }
       } else tree->AsConstantTree(0.0);
     }
+    if (DebugFlags::Get().dump) DumpTree(*tree, models_.size());
     models_.push_back(std::move(tree));
   }
   if (!should_continue) {
@@ -652,7 +668,7 @@ void GBDT::PredictMat(const void* data, int dtype, int nrow, int ncol, bool row_
   const int per = NumPredictOneRow(predict_type, start_iter, num_iter);
   if (ncol <= max_feature_idx_ && !pp.disable_shape_check)
     Log::Fatal("The number of features in data (%d) is not the same as it was in training data (%d)", ncol, max_feature_idx_ + 1);
-#pragma omp parallel
+#pragma omp parallel num_threads(TeamThreads())
   {
     std::vector<double> row(std::max(ncol, max_feature_idx_ + 1), 0.0);
 #pragma omp for schedule(static)

@@ -240,7 +240,7 @@ class BinaryLogloss : public ObjectiveFunction {
     n_ = n; label_ = md.label.data(); weights_ = md.weights.empty() ? nullptr : md.weights.data();
     int64_t cnt[2] = {0, 0};
     { int64_t c0 = 0, c1 = 0;
-#pragma omp parallel for schedule(static) reduction(+ : c0, c1)
+#pragma omp parallel for schedule(static) reduction(+ : c0, c1) num_threads(TeamThreads())
       for (data_size_t i = 0; i < n; ++i) { if (is_pos_(label_[i])) ++c0; else ++c1; }
       cnt[0] = c0; cnt[1] = c1; }
     Network::SumInt64(cnt, 2);
@@ -471,7 +471,7 @@ class LambdarankNDCG : public ObjectiveFunction {
     discount_ = DCG::Discounts(maxn + 1);
   }
   void GetGradients(const double* s, score_t* g, score_t* h) const override {
-#pragma omp parallel for schedule(guided)
+#pragma omp parallel for schedule(guided) num_threads(TeamThreads())
     for (data_size_t q = 0; q < nq_; ++q) OneQuery(q, s + qb_[q], g + qb_[q], h + qb_[q]);
     if (weights_) for (data_size_t i = 0; i < n_; ++i) { g[i] *= weights_[i]; h[i] *= weights_[i]; }
   }

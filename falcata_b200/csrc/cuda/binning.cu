@@ -203,6 +203,31 @@ void DeviceBinDatasetChunk(Dataset* ds, const void* device_data, int dtype, int3
   }
   if (start_row == 0) UploadMeta(ds, dd, 0);
   FB_CUDA(cudaStreamSynchronize(0));
+  if (DebugFlags::Get().verify && nrow > 0) {
+    // self-check: up to 1024 evenly spaced rows of the chunk are binned again by the host's bin mappers and compared
+    // with the device's bytes
+    const int elem = dtype == kF64 ? 8 : (dtype == kF32 || dtype == kI32) ? 4 : (dtype == kI8 || dtype == kU8) ? 1 : 2;
+    const int take = std::min<int32_t>(nrow, 1024);
+    std::vector<char> raw(static_cast<size_t>(take) * ncol * elem);
+    std::vector<uint8_t> dev(static_cast<size_t>(take) * dd->row_stride);
+    for (int k = 0; k < take; ++k) {
+      const size_t r = static_cast<size_t>(static_cast<int64_t>(k) * nrow / take);
+      const char* src = static_cast<const char*>(device_data);
+      if (row_major) FB_CUDA(cudaMemcpy(&raw[static_cast<size_t>(k) * ncol * elem], src + r * ncol * elem, static_cast<size_t>(ncol) * elem, cudaMemcpyDeviceToHost));
+      else FB_CUDA(cudaMemcpy2D(&raw[static_cast<size_t>(k) * ncol * elem], elem, src + r * elem, static_cast<size_t>(nrow) * elem, elem, ncol, cudaMemcpyDeviceToHost));
+      FB_CUDA(cudaMemcpy(&dev[static_cast<size_t>(k) * dd->row_stride], out_rows + r * dd->row_stride, dd->row_stride, cudaMemcpyDeviceToHost));
+    }
+    Dataset host; host.CopySchemaFrom(*ds); host.keep_raw = false; host.bin_bytes = 1; host.row_stride = ds->num_groups;
+    host.AllocateRows(take);
+    host.PushDense(raw.data(), dtype, take, ncol, true, 0);
+    for (int k = 0; k < take; ++k)
+      for (int g = 0; g < ds->num_groups; ++g)
+        if (host.bins8[static_cast<size_t>(k) * host.row_stride + g] != dev[static_cast<size_t>(k) * dd->row_stride + g])
+          Log::Fatal("FALCATA_VERIFY: device binning differs from the host at row %lld, feature group %d: device %d, host %d",
+                     static_cast<long long>(start_row + static_cast<int64_t>(k) * nrow / take), g, dev[static_cast<size_t>(k) * dd->row_stride + g],
+                     host.bins8[static_cast<size_t>(k) * host.row_stride + g]);
+    Log::Info("FALCATA_VERIFY: device binning equals the host's on %d sampled rows of [%d, %d)", take, start_row, start_row + nrow);
+  }
   if (keep_host_copy) {
     std::vector<uint8_t> staged(static_cast<size_t>(nrow) * dd->row_stride);
     FB_CUDA(cudaMemcpy(staged.data(), dd->rows.get(), staged.size(), cudaMemcpyDeviceToHost));

@@ -27,9 +27,9 @@ namespace fb {
 // Number of kernels launched by this library in this process (reported by bench.py).
 inline std::atomic<int64_t>& LaunchCounter() { static std::atomic<int64_t> c{0}; return c; }
 #define FB_LAUNCHED() (::fb::LaunchCounter().fetch_add(1, std::memory_order_relaxed))
-// FALCATA_DEBUG_SYNC=1 serialises the device work: every launcher waits for its kernel and reports an error at the
+// FALCATA_DEBUG_SYNC=1 (or FALCATA_DEBUG=sync) serialises the device work: every launcher waits for its kernel and reports an error at the
 // launch site (file:line of the launcher) instead of at the next synchronisation point of the training loop.
-inline bool DebugSyncLaunches() { static const bool v = getenv("FALCATA_DEBUG_SYNC") != nullptr; return v; }
+inline bool DebugSyncLaunches() { static const bool v = getenv("FALCATA_DEBUG_SYNC") != nullptr || DebugFlags::Get().sync; return v; }
 #define FB_KERNEL_CHECK() do { FB_CUDA(cudaGetLastError()); if (::fb::DebugSyncLaunches()) FB_CUDA(cudaDeviceSynchronize()); } while (0)
 
 template <typename T>

@@ -213,6 +213,10 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   FB_CUDA(cudaStreamSynchronize(stream_));
   Log::Info("CUDA engine: %d rows x %d groups (%d bins, %d partitions), row stride %d B, %s histograms, plan: %s", n_, dd_->num_groups,
             train->num_total_bin, static_cast<int>(h_parts_.size()), dd_->row_stride, quant_ ? "integer" : "fp64", plan_.ToString().c_str());
+  if (DebugFlags::Get().diag)
+    Log::Info("[diag] construct: lane mode %d (%d-bin tiles, %s adds), %d rows per block at %d rows, quant_bins %d, sub-rows %d, %d SMs; growth %s, %d trees per round, ranks %d",
+              lane_mode_, lane_bins_, lane_red_ ? "reduction" : "load-add-store", ChooseRowsPerBlock(n_), n_, cfg_.quant_bins_resolved, sub_rows_, num_sms_,
+              leafwise_ ? "leaf-wise (over-grow + best-first replay)" : "level", K_, world_);
 }
 
 CudaEngine::~CudaEngine() { if (stream_) cudaStreamDestroy(stream_); }

@@ -427,6 +427,9 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
       if (enqueued > 4 * NL) Log::Fatal("The device level loop did not finish the tree within %d levels", enqueued);
     }
     levels_hint_ = std::max(1, hc.pad0);
+    if (DebugFlags::Get().diag)
+      Log::Info("[diag] tree %d: %d leaves, %d journal records, %d levels run on the device, %d enqueued by the host, %lld kernel launches so far", tree_index, hc.num_leaves,
+                hc.journal_count, hc.pad0, enqueued, static_cast<long long>(LaunchCounter().load()));
     if (!records_ready) {
       // the tree needed more levels than the first batch: fetch its records now
       journal_.Download(h_journal_.get(), hc.journal_count, stream_);

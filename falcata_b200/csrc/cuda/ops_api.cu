@@ -169,7 +169,7 @@ int FB_OpBernoulliRowsHost(int n, long long global_offset, unsigned int seed, do
   const int nblocks = (n + kBlock - 1) / kBlock;
   std::vector<int> count(nblocks + 1, 0);
   std::vector<uint8_t> flag(static_cast<size_t>(std::max(1, n)));
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) num_threads(TeamThreads())
   for (int b = 0; b < nblocks; ++b) {
     int c = 0;
     for (int i = b * kBlock; i < std::min(n, (b + 1) * kBlock); ++i) {
@@ -180,7 +180,7 @@ int FB_OpBernoulliRowsHost(int n, long long global_offset, unsigned int seed, do
     count[b + 1] = c;
   }
   for (int b = 0; b < nblocks; ++b) count[b + 1] += count[b];
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) num_threads(TeamThreads())
   for (int b = 0; b < nblocks; ++b) {
     int w = count[b];
     for (int i = b * kBlock; i < std::min(n, (b + 1) * kBlock); ++i) if (flag[i]) out_idx[w++] = i;

@@ -10,6 +10,9 @@ namespace fb {
 bool DevicePredictTiled(const GBDT* gbdt, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, int first_tree, int num_trees, int K,
                         bool leaf_index, float inv_avg, float* out_device, cudaStream_t s);
 
+static void PredictGeneralRaw(const GBDT* gbdt, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, int start_iter, int use, int K,
+                              float* out_device);
+
 void DevicePredict(const GBDT* gbdt, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, int predict_type,
                    int start_iter, int num_iter, float* out_device) {
   if (!CudaAvailable()) Log::Fatal("No CUDA device is available for device prediction");
@@ -31,6 +34,20 @@ void DevicePredict(const GBDT* gbdt, const void* device_data, int dtype, int32_t
     return;
   }
   if (tiled) {
+    if (DebugFlags::Get().verify) {
+      // self-check: the general kernel's raw scores for the same rows and trees
+      const size_t cells = static_cast<size_t>(nrow) * K;
+      DevBuf<float> ref; ref.Alloc(cells);
+      FB_CUDA(cudaStreamSynchronize(0));
+      PredictGeneralRaw(gbdt, device_data, dtype, nrow, ncol, row_major, start_iter, use, K, ref.get());
+      std::vector<float> a(cells), b(cells);
+      FB_CUDA(cudaMemcpy(a.data(), out_device, cells * sizeof(float), cudaMemcpyDeviceToHost));
+      FB_CUDA(cudaMemcpy(b.data(), ref.get(), cells * sizeof(float), cudaMemcpyDeviceToHost));
+      double worst = 0.0; size_t at = 0;
+      for (size_t i = 0; i < cells; ++i) { const double d = std::fabs(static_cast<double>(a[i]) - b[i]) / (1.0 + std::fabs(static_cast<double>(b[i]))); if (d > worst) { worst = d; at = i; } }
+      if (worst > 1e-5) Log::Fatal("FALCATA_VERIFY: the tiled predict kernel differs from the general one at cell %lld: %.9g against %.9g", static_cast<long long>(at), a[at], b[at]);
+      Log::Info("FALCATA_VERIFY: tiled predict equals the general kernel on %lld scores (largest relative difference %.3g)", static_cast<long long>(cells), worst);
+    }
     if (predict_type == 0 && gbdt->objective_ != nullptr) {
       const int kind = gbdt->objective_->DeviceKind();
       const double sig = (kind == kObjBinary || kind == kObjMulticlassOVA) ? gbdt->objective_->DeviceParam(0) : 1.0;
@@ -39,6 +56,18 @@ void DevicePredict(const GBDT* gbdt, const void* device_data, int dtype, int32_t
     FB_CUDA(cudaStreamSynchronize(0));
     return;
   }
+  PredictGeneralRaw(gbdt, device_data, dtype, nrow, ncol, row_major, start_iter, use, K, out_device);
+  if (predict_type == 0 && gbdt->objective_ != nullptr) {
+    const int kind = gbdt->objective_->DeviceKind();
+    const double sig = (kind == kObjBinary || kind == kObjMulticlassOVA) ? gbdt->objective_->DeviceParam(0) : 1.0;
+    if (kind >= 0) LaunchConvertOutput(kind, sig, out_device, nrow, K, 0);
+  }
+  FB_CUDA(cudaStreamSynchronize(0));
+}
+
+// The general kernel: raw scores of trees [start_iter * K, (start_iter + use) * K) into out_device ([K][nrow] floats).
+static void PredictGeneralRaw(const GBDT* gbdt, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, int start_iter, int use, int K,
+                              float* out_device) {
   std::vector<ForestNode> nodes; std::vector<int> roots; std::vector<unsigned int> cat_words(1, 0u);
   for (int t = start_iter * K; t < (start_iter + use) * K; ++t) {
     const Tree& T = *gbdt->models_[t];
@@ -78,11 +107,6 @@ void DevicePredict(const GBDT* gbdt, const void* device_data, int dtype, int32_t
     case kF64: LaunchPredictRaw<double>(d_nodes.get(), d_cat.get(), d_roots.get(), nt, K, static_cast<const double*>(device_data), nrow, ncol, row_major, out_device, gbdt->average_output_, s); break;
     case kF16: LaunchPredictRaw<__half>(d_nodes.get(), d_cat.get(), d_roots.get(), nt, K, static_cast<const __half*>(device_data), nrow, ncol, row_major, out_device, gbdt->average_output_, s); break;
     default: Log::Fatal("Device prediction takes f32, f64 or f16 input");
-  }
-  if (predict_type == 0 && gbdt->objective_ != nullptr) {
-    const int kind = gbdt->objective_->DeviceKind();
-    const double sig = (kind == kObjBinary || kind == kObjMulticlassOVA) ? gbdt->objective_->DeviceParam(0) : 1.0;
-    if (kind >= 0) LaunchConvertOutput(kind, sig, out_device, nrow, K, s);
   }
   FB_CUDA(cudaStreamSynchronize(s));
 }

@@ -74,6 +74,22 @@ class Log {
 // surplus workers whenever a region asks for a smaller team than the last one and starts new ones for the next larger
 // region, which costs a hundred times the region itself when team sizes alternate (measured: 240 us against 2.5 us).
 int RowThreads(long long rows);
+// the team size of every parallel region that is not serial: the OpenMP thread limit
+int TeamThreads();
+
+// Debugging switches read once from the environment.
+//   FALCATA_DEBUG=diag,dump,sync,maxsplits=N   diag: resolved plan, kernel geometry and a line per tree; dump: every
+//     split of every tree (host and device learner alike); sync: every kernel launch is followed by a device
+//     synchronisation so that an error surfaces at its launch site; maxsplits=N: trees stop after N splits (bisecting)
+//   FALCATA_DEBUG_SPLITS=1   the host learner prints each split as it applies it
+//   FALCATA_VERIFY=1         fast paths check themselves against the plain implementation: device binning against the
+//     host bin mappers on a sample of rows, the tiled predict kernel against the general one
+// Parity: src/treelearner/cuda/plan.h:L286-322 (FALCATA_DEBUG keys), tests/gates/README.md:L41-42 (FALCATA_VERIFY).
+struct DebugFlags {
+  bool diag = false, dump = false, sync = false, splits = false, verify = false;
+  int maxsplits = 0;
+  static const DebugFlags& Get();
+};
 
 #define FB_CHECK(cond) do { if (!(cond)) ::fb::Log::Fatal("Check failed: " #cond " at %s:%d", __FILE__, __LINE__); } while (0)
 

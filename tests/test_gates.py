@@ -84,3 +84,22 @@ def test_fuzz_gate_passes_a_few_random_specifications_on_the_host_learner():
         s["rows"] = min(s["rows"], 4000); s["rounds"] = min(s["rounds"], 10); s["cols"] = min(s["cols"], 40)
         fails, _ = fuzz.check_spec(s, "cpu")
         assert not fails, (fails, s)
+
+
+def test_every_openmp_region_names_its_team_size():
+    """A parallel region without ``num_threads`` takes the runtime's default team; a region with a smaller team than
+    the previous one makes libgomp end the surplus workers and start them again for the next larger one (measured:
+    240 us per region against 2.5 us). Every region therefore names its team: the full one or a single thread.
+    Reference: .ci/check-omp-pragmas.sh (the same lint)."""
+    import re
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1] / "falcata_b200" / "csrc"
+    bad = []
+    for path in list(root.rglob("*.cpp")) + list(root.rglob("*.cu")) + list(root.rglob("*.h")) + list(root.rglob("*.cuh")):
+        if "build" in path.relative_to(root).parts:
+            continue
+        for no, line in enumerate(path.read_text().splitlines(), 1):
+            if re.search(r"#\s*pragma\s+omp\s+parallel", line) and "num_threads(" not in line:
+                bad.append(f"{path.relative_to(root)}:{no}")
+    assert not bad, bad

@@ -540,3 +540,33 @@ def test_plan_tuner_probes_the_device_and_keeps_the_model(tmp_path, monkeypatch)
     a = fb.train(dict(params, cuda_plan="wisdom"), fb.Dataset(X, y), 6).model_to_string()
     b = fb.train(dict(params), fb.Dataset(X, y), 6).model_to_string()
     assert model_body(a) == model_body(b)
+
+
+def test_self_verify_mode_checks_device_binning_and_tiled_predict():
+    """FALCATA_VERIFY=1: device binning is compared with the host's bin mappers on sampled rows and the tiled predict
+    kernel with the general one; FALCATA_DEBUG=diag prints the construct geometry and a line per tree (reference:
+    tests/gates/README.md:L41-42, src/treelearner/cuda/plan.h:L286-322)."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    code = (
+        "import torch, numpy as np, falcata_b200 as fb\n"
+        "g = torch.Generator(device='cuda').manual_seed(1)\n"
+        "X = torch.randn(50000, 12, device='cuda', generator=g); X[::7, 3] = float('nan'); X[:, 5] = torch.randint(0, 9, (50000,), device='cuda', generator=g).float()\n"
+        "y = ((X[:, 0] + X[:, 1] * X[:, 2]) > 0).float().cpu().numpy()\n"
+        "p = {'objective': 'binary', 'num_leaves': 31, 'max_bin': 63, 'verbosity': 1, 'device_type': 'cuda', 'categorical_feature': [5]}\n"
+        "b = fb.train(p, fb.Dataset(X, y, categorical_feature=[5]), 3)\n"
+        "q = {'objective': 'binary', 'num_leaves': 31, 'max_bin': 63, 'verbosity': 1, 'device_type': 'cuda'}\n"
+        "b2 = fb.train(q, fb.Dataset(X[:, :5].contiguous(), y), 3)\n"
+        "pr = b2.predict(X[:, :5].contiguous())\n"
+        "print('DONE', float(pr.mean()))\n")
+    env = dict(os.environ, FALCATA_VERIFY="1", FALCATA_DEBUG="diag", PYTHONPATH=str(Path(__file__).resolve().parents[1]))
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    text = out.stdout + out.stderr
+    assert out.returncode == 0, text[-3000:]
+    assert "DONE" in text
+    assert text.count("FALCATA_VERIFY: device binning equals the host's on 1024 sampled rows") >= 2
+    assert "FALCATA_VERIFY: tiled predict equals the general kernel on 50000 scores" in text
+    assert "[diag] construct: lane mode" in text and "[diag] tree 0:" in text

@@ -1,4 +1,5 @@
 """Model conversion CLI, plotting data helpers and the oblique projection pool (all host side)."""
+import os
 import subprocess
 import sys
 
@@ -463,3 +464,22 @@ def test_plan_tuner_and_wisdom_file(tmp_path, monkeypatch):
     # the built-in measurement runs on the host learner too
     quick = tuner.tune(params, fb.Dataset(X, y), rounds=2, warmup=1, switches=["fused_scan"], store=False)
     assert quick in ("auto", "auto,fused_scan:off")
+
+
+def test_debug_environment_switches_dump_splits_and_cap_the_tree():
+    """FALCATA_DEBUG=dump prints every split of every tree, FALCATA_DEBUG_SPLITS the host learner's splits as they are
+    applied, FALCATA_DEBUG=maxsplits=N stops trees after N splits (reference: src/treelearner/cuda/plan.h:L286-322,
+    src/treelearner/serial_tree_learner.cpp:L238-244)."""
+    code = (
+        "import numpy as np, falcata_b200 as fb\n"
+        "rng = np.random.default_rng(0); X = rng.normal(size=(2000, 5)); y = (X[:, 0] + X[:, 1] > 0).astype(float)\n"
+        "b = fb.train({'objective': 'binary', 'num_leaves': 15, 'verbosity': 1, 'device_type': 'cpu'}, fb.Dataset(X, y), 2)\n"
+        "print('LEAVES', [t['num_leaves'] for t in b.dump_model()['tree_info']])\n")
+    env = dict(os.environ, FALCATA_DEBUG="dump,maxsplits=3", FALCATA_DEBUG_SPLITS="1", PYTHONPATH=str(__import__("pathlib").Path(__file__).resolve().parents[1]))
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    text = out.stdout + out.stderr
+    assert out.returncode == 0, text
+    assert "LEAVES [4, 4]" in text                      # three splits per tree
+    assert text.count("[split] leaf") == 6               # the host learner's own lines
+    assert text.count("[dump] tree") == 2 and text.count("[dump]   node") == 6 and text.count("[dump]   leaf") == 8
+    assert "maxsplits=3: num_leaves lowered from 15 to 4" in text
