@@ -15,9 +15,9 @@ const DebugFlags& DebugFlags::Get() {
       while (pos <= s.size()) {
         size_t c = s.find(',', pos); if (c == std::string::npos) c = s.size();
         const std::string k = s.substr(pos, c - pos);
-        if (k == "diag") f.diag = true; else if (k == "dump") f.dump = true; else if (k == "sync" || k == "syncpairs") f.sync = true;
+        if (k == "diag") f.diag = true; else if (k == "dump") f.dump = true; else if (k == "sync" || k == "syncpairs") f.sync = true; else if (k == "canary") f.canary = true;
         else if (k.rfind("maxsplits=", 0) == 0) f.maxsplits = std::max(0, atoi(k.c_str() + 10));
-        else if (!k.empty()) Log::Warning("FALCATA_DEBUG: unknown key %s (diag, dump, sync, maxsplits=N)", k.c_str());
+        else if (!k.empty()) Log::Warning("FALCATA_DEBUG: unknown key %s (diag, dump, sync, canary, maxsplits=N)", k.c_str());
         pos = c + 1;
       }
     }

@@ -427,6 +427,10 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
       if (enqueued > 4 * NL) Log::Fatal("The device level loop did not finish the tree within %d levels", enqueued);
     }
     levels_hint_ = std::max(1, hc.pad0);
+    if (world_ > 1 && DebugFlags::Get().canary) {
+      const int broken = fabric_->CheckCanaries(stream_);
+      if (broken >= 0) Log::Fatal("FALCATA_DEBUG=canary: the guard behind region %d of the symmetric heap was overwritten during tree %d (rank %d)", broken, tree_index, rank_);
+    }
     if (DebugFlags::Get().diag)
       Log::Info("[diag] tree %d: %d leaves, %d journal records, %d levels run on the device, %d enqueued by the host, %lld kernel launches so far", tree_index, hc.num_leaves,
                 hc.journal_count, hc.pad0, enqueued, static_cast<long long>(LaunchCounter().load()));

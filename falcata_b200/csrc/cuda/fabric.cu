@@ -46,7 +46,7 @@ Fabric& Fabric::Get() { static Fabric f; return f; }
 void Fabric::Create(int rank, int world, size_t bytes, char out_handle[64]) {
   if (world < 1 || world > kMaxRanks) Log::Fatal("The symmetric heap supports 1..%d ranks (got %d)", kMaxRanks, world);
   Destroy();
-  rank_ = rank; world_ = world;
+  rank_ = rank; world_ = world; guards_.clear(); fixed_guards_ = 0;
   bytes_ = ((bytes + kFlagRegion + 2 * kMaxRanks * kArSlot + 4095) / 4096) * 4096 + (1 << 20);
   void* p = nullptr;
   FB_CUDA(cudaMalloc(&p, bytes_));
@@ -78,6 +78,7 @@ void Fabric::Connect(const char* handles) {
   ar_data_off_ = Alloc(2 * kMaxRanks * kArSlot);
   flag_bytes_ = cursor_;   // Reset() keeps the all-reduce area
   fixed_flag_cursor_ = flag_cursor_;
+  fixed_guards_ = guards_.size();
 }
 
 void Fabric::Destroy() {
@@ -94,8 +95,22 @@ size_t Fabric::Alloc(size_t bytes, size_t align) {
   cursor_ = (cursor_ + align - 1) / align * align;
   const size_t off = cursor_;
   cursor_ += bytes;
+  const bool guard = DebugFlags::Get().canary;
+  if (guard) { cursor_ = (cursor_ + 15) / 16 * 16; guards_.push_back(cursor_); cursor_ += kGuardBytes; }
   if (cursor_ > bytes_) Log::Fatal("Symmetric heap exhausted: need %zu bytes, have %zu (create the fabric with a larger heap)", cursor_, bytes_);
+  if (guard) FB_CUDA(cudaMemset(base_[rank_] + guards_.back(), 0xC5, kGuardBytes));
   return off;
+}
+
+int Fabric::CheckCanaries(cudaStream_t s) const {
+  if (guards_.empty()) return -1;
+  FB_CUDA(cudaStreamSynchronize(s));
+  std::vector<unsigned char> h(kGuardBytes);
+  for (size_t g = 0; g < guards_.size(); ++g) {
+    FB_CUDA(cudaMemcpy(h.data(), base_[rank_] + guards_[g], kGuardBytes, cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < kGuardBytes; ++i) if (h[i] != 0xC5) return static_cast<int>(g);
+  }
+  return -1;
 }
 
 size_t Fabric::NewFlagSlot() {
@@ -148,6 +163,20 @@ int FB_FabricConnect(const char* handles) {
 }
 int FB_FabricDestroy() {
   try { Fabric::Get().Destroy(); } catch (std::exception& e) { g_fabric_error = e.what(); return -1; }
+  return 0;
+}
+// Test hooks of the debug guards: carve a region, overwrite heap bytes from the host, check the guards.
+int FB_FabricDebugAlloc(int64_t bytes, int64_t* out_offset) {
+  try { *out_offset = static_cast<int64_t>(Fabric::Get().Alloc(static_cast<size_t>(bytes))); } catch (std::exception& e) { g_fabric_error = e.what(); return -1; }
+  return 0;
+}
+int FB_FabricDebugFill(int64_t offset, int64_t bytes, int value) {
+  try { FB_CUDA(cudaMemset(Fabric::Get().Local<char>(static_cast<size_t>(offset)), value, static_cast<size_t>(bytes))); FB_CUDA(cudaDeviceSynchronize()); }
+  catch (std::exception& e) { g_fabric_error = e.what(); return -1; }
+  return 0;
+}
+int FB_FabricCheckCanaries(int* out_broken_region) {
+  try { *out_broken_region = Fabric::Get().CheckCanaries(0); } catch (std::exception& e) { g_fabric_error = e.what(); return -1; }
   return 0;
 }
 int FB_FabricSetMaxSpins(int64_t spins) { Fabric::Get().set_max_spins(static_cast<unsigned long long>(spins)); return 0; }

@@ -57,8 +57,13 @@ class Fabric {
   void Connect(const char* handles /* world x 64 bytes, by rank */);
   void Destroy();
   // Carving. Reset() starts a new layout (one engine at a time uses the heap).
-  void Reset() { cursor_ = flag_bytes_; flag_cursor_ = fixed_flag_cursor_; }
+  void Reset() { cursor_ = flag_bytes_; flag_cursor_ = fixed_flag_cursor_; guards_.resize(fixed_guards_); }
   size_t Alloc(size_t bytes, size_t align = 256);
+  // FALCATA_DEBUG=canary: every region carved by Alloc is followed by kGuardBytes of a fixed pattern in this rank's heap;
+  // CheckCanaries reads them back and returns the index (in allocation order) of the first region whose guard was
+  // overwritten - by this rank or by a peer's store - or -1.
+  static constexpr size_t kGuardBytes = 256;
+  int CheckCanaries(cudaStream_t s) const;
   template <typename T> T* Ptr(int r, size_t off) const { return reinterpret_cast<T*>(base_[r] + off); }
   template <typename T> T* Local(size_t off) const { return Ptr<T>(rank_, off); }
   FabricView View() const;
@@ -84,6 +89,8 @@ class Fabric {
   unsigned int* status_ = nullptr;
   unsigned long long max_spins_ = 20000000ull;
   size_t ar_data_off_ = 0, ar_flag_off_ = 0;
+  std::vector<size_t> guards_;   // offsets of the guard blocks (debug mode)
+  size_t fixed_guards_ = 0;      // guards of the regions that Reset() keeps
 };
 
 // Call with all threads of the block; the block's global writes are ordered before the flag.

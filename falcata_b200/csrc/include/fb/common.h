@@ -78,7 +78,8 @@ int RowThreads(long long rows);
 int TeamThreads();
 
 // Debugging switches read once from the environment.
-//   FALCATA_DEBUG=diag,dump,sync,maxsplits=N   diag: resolved plan, kernel geometry and a line per tree; dump: every
+//   FALCATA_DEBUG=diag,dump,sync,canary,maxsplits=N   canary: guard words behind every region of the symmetric heap,
+//     checked after every tree; diag: resolved plan, kernel geometry and a line per tree; dump: every
 //     split of every tree (host and device learner alike); sync: every kernel launch is followed by a device
 //     synchronisation so that an error surfaces at its launch site; maxsplits=N: trees stop after N splits (bisecting)
 //   FALCATA_DEBUG_SPLITS=1   the host learner prints each split as it applies it
@@ -86,7 +87,7 @@ int TeamThreads();
 //     host bin mappers on a sample of rows, the tiled predict kernel against the general one
 // Parity: src/treelearner/cuda/plan.h:L286-322 (FALCATA_DEBUG keys), tests/gates/README.md:L41-42 (FALCATA_VERIFY).
 struct DebugFlags {
-  bool diag = false, dump = false, sync = false, splits = false, verify = false;
+  bool diag = false, dump = false, sync = false, canary = false, splits = false, verify = false;
   int maxsplits = 0;
   static const DebugFlags& Get();
 };

@@ -142,3 +142,35 @@ def test_cross_rank_wait_is_bounded_and_reports_status():
     assert status == 1 and seen == 0
     x = torch.ones(8, device="cuda")
     assert float(x.sum().item()) == 8.0
+
+
+def test_symmetric_heap_guard_words_catch_an_overrun():
+    """FALCATA_DEBUG=canary puts a guard block behind every region carved from the symmetric heap; a write past a region
+    (made here from the host with a memset inside the heap, so nothing faults) is reported with the region's index."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    code = (
+        "import ctypes, torch, falcata_b200 as fb\n"
+        "from falcata_b200.basic import _lib\n"
+        "lib = _lib()\n"
+        "torch.cuda.init(); torch.zeros(1, device='cuda')\n"
+        "h = ctypes.create_string_buffer(64)\n"
+        "assert lib.FB_FabricCreate(0, 1, ctypes.c_int64(1 << 20), h) == 0\n"
+        "assert lib.FB_FabricConnect(h) == 0\n"
+        "a = ctypes.c_int64(); b = ctypes.c_int64(); bad = ctypes.c_int(7)\n"
+        "assert lib.FB_FabricDebugAlloc(ctypes.c_int64(1000), ctypes.byref(a)) == 0\n"
+        "assert lib.FB_FabricDebugAlloc(ctypes.c_int64(4096), ctypes.byref(b)) == 0\n"
+        "assert b.value >= a.value + 1000 + 256\n"
+        "assert lib.FB_FabricDebugFill(ctypes.c_int64(a.value), ctypes.c_int64(1000), 1) == 0\n"
+        "assert lib.FB_FabricCheckCanaries(ctypes.byref(bad)) == 0 and bad.value == -1\n"
+        "assert lib.FB_FabricDebugFill(ctypes.c_int64(b.value), ctypes.c_int64(4100), 2) == 0\n"
+        "assert lib.FB_FabricCheckCanaries(ctypes.byref(bad)) == 0\n"
+        "print('BROKEN', bad.value)\n"
+        "lib.FB_FabricDestroy()\n")
+    env = dict(os.environ, FALCATA_DEBUG="canary", PYTHONPATH=str(Path(__file__).resolve().parents[1]))
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, (out.stdout + out.stderr)[-3000:]
+    assert "BROKEN 2" in out.stdout   # region 0 is the heap's own all-reduce area, 1 and 2 the two carved here
