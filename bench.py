@@ -435,9 +435,9 @@ def main() -> None:
             barrier()
             runs.append(max_over_ranks(time.perf_counter() - t0))
             del bst2, ds2
+            if os.environ.get("FALCATA_TIME_TAG") and rank == 0:
+                print(f"---- time tags of end-to-end run {rep + 1} ({runs[-1] * 1000.0:.1f} ms) ----\n" + fb.time_tag_report(), file=sys.stderr)
         dt = min(runs)
-        if os.environ.get("FALCATA_TIME_TAG") and rank == 0:
-            print(fb.time_tag_report(), file=sys.stderr)
         e2e = {"value": dt / K * 1000.0, "unit": "s/1000 rounds (ingest from pinned host memory + K rounds + per-round metric read, wall clock / K; the faster of two complete runs)",
                "runs_ms_per_round": [r / K * 1000.0 for r in runs],
                "h2d_bytes_per_step": int((Xh.numel() * Xh.element_size() + yh.nbytes) / K), "d2h_bytes_per_step": 16}

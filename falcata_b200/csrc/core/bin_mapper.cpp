@@ -115,6 +115,36 @@ namespace {
 void SortValues(double* v, int n) {
   if (n < 4096) { std::sort(v, v + n); return; }
   if (std::is_sorted(v, v + n)) return;
+  {
+    // values that are exactly single-precision floats (a float32 matrix, the usual input) sort as 32-bit keys: three
+    // 11-bit passes over arrays of half the size. Floats and doubles order alike (signed zeros included), so the result
+    // is the one of the 64-bit path below.
+    static thread_local std::vector<uint32_t> tl_fa, tl_fb;
+    std::vector<uint32_t>& fa = tl_fa; std::vector<uint32_t>& fb32 = tl_fb;
+    if (fa.size() < static_cast<size_t>(n)) { fa.resize(n); fb32.resize(n); }
+    bool exact = true;
+    for (int i = 0; i < n; ++i) {
+      const float f = static_cast<float>(v[i]);
+      if (static_cast<double>(f) != v[i]) { exact = false; break; }
+      uint32_t u; memcpy(&u, &f, 4); fa[i] = (u >> 31) ? ~u : (u | 0x80000000u);
+    }
+    if (exact) {
+      constexpr int kD = 11, kR = 1 << kD;
+      uint32_t count[3][kR + 1] = {};
+      for (int i = 0; i < n; ++i) { const uint32_t u = fa[i]; ++count[0][(u & (kR - 1)) + 1]; ++count[1][((u >> kD) & (kR - 1)) + 1]; ++count[2][(u >> (2 * kD)) + 1]; }
+      uint32_t* src = fa.data(); uint32_t* dst = fb32.data();
+      for (int p = 0; p < 3; ++p) {
+        uint32_t* c = count[p];
+        const int shift = p * kD;
+        if (c[((src[0] >> shift) & (kR - 1)) + 1] == static_cast<uint32_t>(n)) continue;   // all keys share this digit
+        for (int d = 0; d < kR; ++d) c[d + 1] += c[d];
+        for (int i = 0; i < n; ++i) dst[c[(src[i] >> shift) & (kR - 1)]++] = src[i];
+        std::swap(src, dst);
+      }
+      for (int i = 0; i < n; ++i) { uint32_t u = src[i]; u = (u >> 31) ? (u & 0x7FFFFFFFu) : ~u; float f; memcpy(&f, &u, 4); v[i] = static_cast<double>(f); }
+      return;
+    }
+  }
   static thread_local std::vector<uint64_t> tl_a, tl_b;
   std::vector<uint64_t>& a = tl_a; std::vector<uint64_t>& b = tl_b;
   if (a.size() < static_cast<size_t>(n)) { a.resize(n); b.resize(n); }
@@ -158,25 +188,33 @@ void BinMapper::FindBin(double* values, int num_values, size_t total_sample_cnt,
   const size_t zero_cnt = total_sample_cnt - static_cast<size_t>(num_values) - static_cast<size_t>(na_cnt);
 
   SortValues(values, num_values);
-  std::vector<double> dv; std::vector<int> dc;
-  dv.reserve(static_cast<size_t>(num_values) + 1); dc.reserve(static_cast<size_t>(num_values) + 1);
+  // distinct values with their counts (adjacent doubles merge into the larger one); the implicit zeros of the sample
+  // enter once, between the negative and the positive values. Written through raw indices: with a continuous feature
+  // nearly every sampled value is distinct and the loop runs once per value.
+  std::vector<double> dv(static_cast<size_t>(num_values) + 2); std::vector<int> dc(static_cast<size_t>(num_values) + 2);
+  int top = -1;   // index of the last distinct value
   bool zero_pushed = false;
   auto push_zero = [&] {
     if (!zero_pushed && zero_cnt > 0) {
-      if (!dv.empty() && dv.back() == 0.0) dc.back() += static_cast<int>(zero_cnt);
-      else { dv.push_back(0.0); dc.push_back(static_cast<int>(zero_cnt)); }
+      if (top >= 0 && dv[top] == 0.0) dc[top] += static_cast<int>(zero_cnt);
+      else { ++top; dv[top] = 0.0; dc[top] = static_cast<int>(zero_cnt); }
     }
     zero_pushed = true;
   };
   if (num_values == 0 || values[0] > 0.0) push_zero();
   for (int i = 0; i < num_values; ++i) {
-    if (!zero_pushed && values[i] > 0.0) push_zero();
-    if (!dv.empty() && dv.back() != 0.0 && NearlyEqualOrdered(dv.back(), values[i])) { dv.back() = values[i]; ++dc.back(); }
-    else if (!dv.empty() && dv.back() == values[i]) { ++dc.back(); }
-    else { dv.push_back(values[i]); dc.push_back(1); }
+    const double x = values[i];
+    if (!zero_pushed && x > 0.0) push_zero();
+    if (top >= 0) {
+      const double last = dv[top];
+      if (last != 0.0 && NearlyEqualOrdered(last, x)) { dv[top] = x; ++dc[top]; continue; }
+      if (last == x) { ++dc[top]; continue; }
+    }
+    ++top; dv[top] = x; dc[top] = 1;
   }
   if (!zero_pushed) push_zero();
-  if (dv.empty()) { dv.push_back(0.0); dc.push_back(static_cast<int>(total_sample_cnt)); }
+  if (top < 0) { top = 0; dv[0] = 0.0; dc[0] = static_cast<int>(total_sample_cnt); }
+  dv.resize(static_cast<size_t>(top) + 1); dc.resize(static_cast<size_t>(top) + 1);
   min_val = dv.front(); max_val = dv.back();
   const int nd = static_cast<int>(dv.size());
   std::vector<int> cnt_in_bin;

@@ -3,7 +3,9 @@
 
 #include <nvtx3/nvToolsExt.h>
 
+#include <exception>
 #include <sstream>
+#include <thread>
 
 namespace fb {
 
@@ -42,9 +44,11 @@ DeviceEngine* CreateDeviceEngine(const Config& cfg, const Dataset* train, const 
 CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveFunction* obj, int K)
     : cfg_(cfg), plan_(Plan::FromString(cfg.cuda_plan)), train_(train), obj_(obj), K_(K) {
   if (!CudaAvailable()) Log::Fatal("device_type=cuda needs a CUDA device");
-  cudaDeviceProp prop; int dev = 0; FB_CUDA(cudaGetDevice(&dev)); FB_CUDA(cudaGetDeviceProperties(&prop, dev));
-  if (prop.major < 10) Log::Warning("This build targets sm_100a; device %s is compute %d.%d", prop.name, prop.major, prop.minor);
-  num_sms_ = prop.multiProcessorCount;
+  // single attributes: the full property query reads every field of the device and takes milliseconds
+  int dev = 0, cc_major = 0, cc_minor = 0; FB_CUDA(cudaGetDevice(&dev));
+  FB_CUDA(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, dev)); FB_CUDA(cudaDeviceGetAttribute(&cc_minor, cudaDevAttrComputeCapabilityMinor, dev));
+  FB_CUDA(cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, dev));
+  if (cc_major < 10) Log::Warning("This build targets sm_100a; device %d is compute %d.%d", dev, cc_major, cc_minor);
   if (Fabric::Get().active() && cfg.tree_learner != "serial") {
     if (cfg.tree_learner != "data" && cfg.tree_learner != "feature" && cfg.tree_learner != "voting") Log::Fatal("Unknown tree_learner %s", cfg.tree_learner.c_str());
     voting_ = cfg.tree_learner == "voting";
@@ -57,7 +61,15 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   { ScopedTimer t("Engine::EnsureDeviceDataset"); EnsureDeviceDataset(const_cast<Dataset*>(train)); }
   dd_ = train->device; n_ = train->num_data;
   FB_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
-  { ScopedTimer t("Engine::SyncDeviceMetadata"); SyncDeviceMetadata(train, stream_); }
+  // labels, weights and query boundaries go up on a helper thread (a copy from pageable memory keeps its caller busy
+  // for the whole transfer) while this thread allocates and clears the training state; joined before the first use
+  cudaStream_t meta_stream = nullptr; FB_CUDA(cudaStreamCreateWithFlags(&meta_stream, cudaStreamNonBlocking));
+  std::exception_ptr meta_error;
+  std::thread meta_upload([&, dev]() {
+    try { FB_CUDA(cudaSetDevice(dev)); ScopedTimer t("Engine::SyncDeviceMetadata"); SyncDeviceMetadata(train, meta_stream); }
+    catch (...) { meta_error = std::current_exception(); }
+  });
+  struct JoinMeta { std::thread& t; ~JoinMeta() { if (t.joinable()) t.join(); } } join_meta{meta_upload};
   ScopedTimer t_rest("Engine::AllocAndSetup");
   quant_ = cfg.quant != QuantMode::None;
   sp_.lambda_l1 = cfg.lambda_l1; sp_.lambda_l2 = cfg.lambda_l2; sp_.max_delta_step = cfg.max_delta_step; sp_.path_smooth = cfg.path_smooth;
@@ -211,6 +223,9 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   level_blob_.Alloc(blob); h_level_blob_.Alloc(blob);
   features_.Alloc(std::max(1, train->num_features)); sub_features_.Alloc(std::max(1, train->num_features));
   FB_CUDA(cudaStreamSynchronize(stream_));
+  meta_upload.join();
+  cudaStreamDestroy(meta_stream);
+  if (meta_error) std::rethrow_exception(meta_error);
   Log::Info("CUDA engine: %d rows x %d groups (%d bins, %d partitions), row stride %d B, %s histograms, plan: %s", n_, dd_->num_groups,
             train->num_total_bin, static_cast<int>(h_parts_.size()), dd_->row_stride, quant_ ? "integer" : "fp64", plan_.ToString().c_str());
   if (DebugFlags::Get().diag)
