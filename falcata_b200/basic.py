@@ -36,6 +36,11 @@ class FalcataError(Exception):
 LightGBMError = FalcataError
 
 
+class FalcataDeprecationWarning(FutureWarning):
+    """Deprecation notices of this package. A FutureWarning subclass: Python hides plain DeprecationWarning outside of
+    ``__main__`` by default, and users should see these."""
+
+
 def _safe_call(ret: int) -> None:
     if ret != 0:
         raise FalcataError(_lib().FB_GetLastError().decode("utf-8"))

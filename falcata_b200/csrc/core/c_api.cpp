@@ -13,6 +13,7 @@
 namespace fb {
 // device-side entry points implemented by the CUDA module
 void DeviceBinDataset(Dataset* ds, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, bool keep_host_copy);
+void DeviceGatherRows(const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, const int32_t* rows, int32_t num_rows, std::vector<char>* out);
 void DeviceBinDatasetChunk(Dataset* ds, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, bool keep_host_copy, int32_t start_row,
                            int32_t total_rows);
 void DevicePredict(const GBDT* gbdt, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, int predict_type,
@@ -204,6 +205,32 @@ int FB_DatasetBinDeviceMat(DatasetHandle handle, const void* device_data, int dt
   API_BEGIN();
   ScopedTimer api_timer("FB_DatasetBinDeviceMat");
   DeviceBinDataset(static_cast<Dataset*>(handle), device_data, dtype, nrow, ncol, is_row_major != 0, keep_host_copy != 0);
+  API_END();
+}
+
+// A Dataset from a dense matrix in device memory: the bin sample (the rows the host draw by row id picks) is gathered on
+// the device and copied down, the bin boundaries are found on the host, the rows are binned on the device and stay
+// there. With `reference` the schema is copied instead. Parity: include/Falcata/c_api.h FLC_DatasetCreateFromMatDevice.
+int FB_DatasetCreateFromDeviceMat(const void* device_data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, const char* parameters,
+                                  const DatasetHandle reference, DatasetHandle* out) {
+  API_BEGIN();
+  if (nrow <= 0 || ncol <= 0) Log::Fatal("An empty matrix");
+  Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());
+  std::unique_ptr<Dataset> ds(new Dataset());
+  if (reference != nullptr) ds->CopySchemaFrom(*static_cast<const Dataset*>(reference));
+  else {
+    const double frac = std::min(1.0, static_cast<double>(cfg.bin_construct_sample_cnt) / std::max(1, nrow));
+    std::vector<int32_t> idx(static_cast<size_t>(nrow));
+    int picked = 0;   // the same draw by row id as for a host matrix, so a matrix gets the same bins wherever it lives
+    if (FB_OpBernoulliRowsHost(nrow, 0, static_cast<unsigned int>(cfg.data_random_seed), frac, idx.data(), &picked) != 0) Log::Fatal("Row sampling failed");
+    idx.resize(picked);
+    if (idx.empty()) idx.push_back(0);
+    std::vector<char> sample;
+    DeviceGatherRows(device_data, dtype, nrow, ncol, is_row_major != 0, idx.data(), static_cast<int32_t>(idx.size()), &sample);
+    ds->ConstructSchemaTyped(sample.data(), dtype, static_cast<int>(idx.size()), ncol, nrow, cfg, ParseCategorical(cfg, ncol));
+  }
+  DeviceBinDataset(ds.get(), device_data, dtype, nrow, ncol, is_row_major != 0, false);
+  *out = ds.release();
   API_END();
 }
 
@@ -453,6 +480,24 @@ int FB_BoosterPredictForMatSingleRowFast(void* fast_config, const void* data, in
   b->gbdt->PredictMat(data, fc->dtype, 1, fc->ncol, true, fc->predict_type, fc->start_iteration, fc->num_iteration, out_result, fc->pp);
   API_END();
 }
+// Prepared single-row prediction from one CSR row: the row is scattered into a dense buffer of the prepared width.
+int FB_BoosterPredictForCSRSingleRowFastInit(BoosterHandle handle, int predict_type, int start_iteration, int num_iteration, int data_type, int64_t num_col,
+                                             const char* parameter, void** out_fast_config) {
+  if (num_col <= 0 || num_col > INT32_MAX) return FB_SetLastErrorForCompat("The number of columns must be a positive 32-bit value");
+  (void)data_type;   // the row is densified to f64
+  return FB_BoosterPredictForMatSingleRowFastInit(handle, predict_type, start_iteration, num_iteration, kF64, static_cast<int32_t>(num_col), parameter, out_fast_config);
+}
+int FB_BoosterPredictForCSRSingleRowFast(void* fast_config, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr,
+                                         int64_t nelem, int64_t* out_len, double* out_result) {
+  API_BEGIN();
+  (void)nelem;
+  if (nindptr != 2) Log::Fatal("A single row has two row pointers (got %lld)", static_cast<long long>(nindptr));
+  const FastConfig* fc = static_cast<const FastConfig*>(fast_config);
+  static thread_local std::vector<double> dense;
+  DensifyCSR(indptr, indptr_type, indices, data, data_type, 0, 1, fc->ncol, &dense);
+  if (FB_BoosterPredictForMatSingleRowFast(fast_config, dense.data(), out_len, out_result) != 0) return -1;
+  API_END();
+}
 int FB_FastConfigFree(void* fast_config) { API_BEGIN(); delete static_cast<FastConfig*>(fast_config); API_END(); }
 
 int FB_BoosterPredictForCSR(BoosterHandle handle, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr,
@@ -619,6 +664,62 @@ int FB_DatasetPushRowsWithMetadata(DatasetHandle handle, const void* data, int d
   if (query != nullptr && !st.query_of_row.empty()) std::copy(query, query + nrow, st.query_of_row.begin() + start_row);
   API_END();
 }
+// CSR rows with their metadata: the rows go through the CSR push, the metadata through the dense one's bookkeeping
+int FB_DatasetPushRowsByCSRWithMetadata(DatasetHandle handle, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type,
+                                        int64_t nindptr, int64_t nelem, int64_t start_row, const float* label, const float* weight, const double* init_score,
+                                        const int32_t* query) {
+  API_BEGIN();
+  Dataset* ds = static_cast<Dataset*>(handle);
+  const int64_t nrow = nindptr - 1;
+  if (start_row < 0 || start_row + nrow > ds->num_data) Log::Fatal("Pushed rows [%lld, %lld) are outside the dataset (%d rows)", static_cast<long long>(start_row), static_cast<long long>(start_row + nrow), ds->num_data);
+  if (FB_DatasetPushRowsByCSR(handle, indptr, indptr_type, indices, data, data_type, nindptr, nelem, ds->num_total_features, start_row) != 0) return -1;
+  if (label != nullptr) std::copy(label, label + nrow, ds->metadata.label.begin() + start_row);
+  if (weight != nullptr && !ds->metadata.weights.empty()) std::copy(weight, weight + nrow, ds->metadata.weights.begin() + start_row);
+  std::lock_guard<std::mutex> g(g_stream_mu);
+  StreamState& st = g_stream[ds];
+  if (init_score != nullptr && !ds->metadata.init_score.empty())
+    for (int k = 0; k < st.nclasses; ++k) std::copy(init_score + static_cast<size_t>(k) * nrow, init_score + static_cast<size_t>(k + 1) * nrow,
+                                                     ds->metadata.init_score.begin() + static_cast<size_t>(k) * ds->num_data + start_row);
+  if (query != nullptr && !st.query_of_row.empty()) std::copy(query, query + nrow, st.query_of_row.begin() + start_row);
+  API_END();
+}
+
+// Schema from per-column samples: column j holds num_per_col[j] sampled non-zero values with the sample rows they came
+// from; everything else in the num_sample_row sampled rows is zero. The rows (num_local_row of num_dist_row over all
+// machines) are pushed afterwards. Parity: include/Falcata/c_api.h FLC_DatasetCreateFromSampledColumn.
+int FB_DatasetCreateFromSampledColumn(double** sample_data, int** sample_indices, int32_t ncol, const int* num_per_col, int32_t num_sample_row,
+                                      int32_t num_local_row, int64_t num_dist_row, const char* parameters, DatasetHandle* out) {
+  API_BEGIN();
+  if (ncol <= 0 || num_sample_row <= 0) Log::Fatal("An empty sample");
+  std::vector<double> dense(static_cast<size_t>(num_sample_row) * ncol, 0.0);
+  for (int j = 0; j < ncol; ++j)
+    for (int k = 0; k < num_per_col[j]; ++k) {
+      const int r = sample_indices[j][k];
+      if (r < 0 || r >= num_sample_row) Log::Fatal("Sample row %d of column %d is outside the %d sampled rows", r, j, num_sample_row);
+      dense[static_cast<size_t>(r) * ncol + j] = sample_data[j][k];
+    }
+  if (FB_DatasetCreateFromSample(dense.data(), num_sample_row, ncol, num_dist_row > 0 ? num_dist_row : num_local_row, parameters, nullptr, 0, out) != 0) return -1;
+  if (FB_DatasetInitRows(*out, num_local_row, 0, num_dist_row > 0 ? num_dist_row : num_local_row, 1) != 0) return -1;
+  API_END();
+}
+
+// Rows from a callback: get_row_funptr points to a std::function<void(int row, std::vector<std::pair<int, double>>& out)>
+// that clears and fills `out` with the row's (column, value) pairs. Parity: FLC_DatasetCreateFromCSRFunc.
+int FB_DatasetCreateFromCSRFunc(void* get_row_funptr, int num_rows, int64_t num_col, const char* parameters, const DatasetHandle reference, DatasetHandle* out) {
+  API_BEGIN();
+  if (get_row_funptr == nullptr) Log::Fatal("The row callback is null");
+  auto& get_row = *static_cast<std::function<void(int, std::vector<std::pair<int, double>>&)>*>(get_row_funptr);
+  std::vector<int64_t> indptr(1, 0); std::vector<int32_t> indices; std::vector<double> values; std::vector<std::pair<int, double>> row;
+  for (int i = 0; i < num_rows; ++i) {
+    get_row(i, row);
+    for (const auto& kv : row) { indices.push_back(kv.first); values.push_back(kv.second); }
+    indptr.push_back(static_cast<int64_t>(indices.size()));
+  }
+  if (FB_DatasetCreateFromCSR(indptr.data(), 8 /* int64 row pointers */, indices.data(), values.data(), kF64, static_cast<int64_t>(indptr.size()), static_cast<int64_t>(values.size()), num_col, parameters,
+                              reference, out) != 0) return -1;
+  API_END();
+}
+
 int FB_DatasetMarkFinished(DatasetHandle handle) {
   API_BEGIN();
   Dataset* ds = static_cast<Dataset*>(handle);

@@ -8,6 +8,7 @@ void FreeDeviceDataset(DeviceDataset*) {}
 DeviceEngine* CreateDeviceEngine(const Config&, const Dataset*, const ObjectiveFunction*, int) { Log::Fatal("This build has no CUDA module"); return nullptr; }
 bool CudaAvailable() { return false; }
 void DeviceBinDataset(Dataset*, const void*, int, int32_t, int32_t, bool, bool) { Log::Fatal("This build has no CUDA module"); }
+void DeviceGatherRows(const void*, int, int32_t, int32_t, bool, const int32_t*, int32_t, std::vector<char>*) { Log::Fatal("This build has no CUDA module"); }
 void DeviceBinDatasetChunk(Dataset*, const void*, int, int32_t, int32_t, bool, bool, int32_t, int32_t) { Log::Fatal("This build has no CUDA module"); }
 void DevicePredict(const GBDT*, const void*, int, int32_t, int32_t, bool, int, int, int, float*) { Log::Fatal("This build has no CUDA module"); }
 }  // namespace fb

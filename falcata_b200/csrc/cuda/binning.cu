@@ -135,6 +135,35 @@ void EnsureDeviceDataset(Dataset* ds) {
 void DeviceBinDatasetChunk(Dataset* ds, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, bool keep_host_copy, int32_t start_row,
                            int32_t total_rows);
 
+// Picks rows of a device matrix into a dense row-major block (element size `elem` bytes, any layout of the source).
+__global__ void GatherRowsKernel(const unsigned char* __restrict__ src, int elem, int nrow, int ncol, int row_major, const int* __restrict__ rows, int num_rows,
+                                 unsigned char* __restrict__ dst) {
+  const long long total = static_cast<long long>(num_rows) * ncol;
+  for (long long c = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; c < total; c += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int k = static_cast<int>(c / ncol), j = static_cast<int>(c % ncol);
+    const long long r = rows[k];
+    const unsigned char* s = src + (row_major ? (r * ncol + j) : (static_cast<long long>(j) * nrow + r)) * elem;
+    unsigned char* d = dst + c * elem;
+    for (int b = 0; b < elem; ++b) d[b] = s[b];
+  }
+}
+
+// The listed rows of a device matrix, in its own element type, copied to the host (row-major).
+void DeviceGatherRows(const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, const int32_t* rows, int32_t num_rows, std::vector<char>* out) {
+  if (!CudaAvailable()) Log::Fatal("No CUDA device is available");
+  const int elem = dtype == kF64 ? 8 : (dtype == kF32 || dtype == kI32) ? 4 : (dtype == kI8 || dtype == kU8) ? 1 : 2;
+  out->resize(static_cast<size_t>(num_rows) * ncol * elem);
+  if (num_rows <= 0) return;
+  DevBuf<int> d_rows; DevBuf<unsigned char> d_out;
+  std::vector<int> h_rows(rows, rows + num_rows);
+  d_rows.Upload(h_rows, 0); d_out.Alloc(out->size());
+  const long long total = static_cast<long long>(num_rows) * ncol;
+  const unsigned blocks = static_cast<unsigned>(std::min<long long>((total + 255) / 256, 65535));
+  GatherRowsKernel<<<blocks, 256>>>(static_cast<const unsigned char*>(device_data), elem, nrow, ncol, row_major ? 1 : 0, d_rows.get(), num_rows, d_out.get());
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+  FB_CUDA(cudaMemcpy(out->data(), d_out.get(), out->size(), cudaMemcpyDeviceToHost));
+}
+
 void DeviceBinDataset(Dataset* ds, const void* device_data, int dtype, int32_t nrow, int32_t ncol, bool row_major, bool keep_host_copy) {
   DeviceBinDatasetChunk(ds, device_data, dtype, nrow, ncol, row_major, keep_host_copy, 0, nrow);
 }

@@ -47,6 +47,9 @@ int FB_DatasetPushRows(DatasetHandle handle, const void* data, int dtype, int32_
 /* Bin a dense device matrix on the GPU; the binned rows stay on the device. */
 int FB_DatasetBinDeviceMat(DatasetHandle handle, const void* device_data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, int keep_host_copy);
 // Rows [start_row, start_row + nrow) of a total_rows data set from a device-resident row-major chunk (first chunk: start_row 0).
+/* A whole Dataset from a dense device matrix: sample gathered on the device, bin boundaries on the host, rows binned on the device. */
+int FB_DatasetCreateFromDeviceMat(const void* device_data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, const char* parameters,
+                                  const DatasetHandle reference, DatasetHandle* out);
 int FB_DatasetBinDeviceChunk(DatasetHandle handle, const void* device_data, int dtype, int32_t nrow, int32_t ncol, int32_t start_row, int32_t total_rows);
 int FB_DatasetSetField(DatasetHandle handle, const char* field_name, const void* data, int64_t num_element, int dtype);
 int FB_DatasetGetField(DatasetHandle handle, const char* field_name, int64_t* out_len, const void** out_ptr, int* out_type);
@@ -150,6 +153,17 @@ int FB_DatasetSetFieldFromArrow(DatasetHandle handle, const char* field_name, in
 int FB_DatasetSetFieldFromArrowStream(DatasetHandle handle, const char* field_name, void* stream);
 int FB_DatasetPushRowsByCSR(DatasetHandle handle, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr,
                             int64_t nelem, int64_t num_col, int64_t start_row);
+int FB_DatasetPushRowsByCSRWithMetadata(DatasetHandle handle, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type,
+                                        int64_t nindptr, int64_t nelem, int64_t start_row, const float* label, const float* weight, const double* init_score,
+                                        const int32_t* query);
+int FB_DatasetCreateFromSampledColumn(double** sample_data, int** sample_indices, int32_t ncol, const int* num_per_col, int32_t num_sample_row,
+                                      int32_t num_local_row, int64_t num_dist_row, const char* parameters, DatasetHandle* out);
+/* get_row_funptr: std::function<void(int row, std::vector<std::pair<int, double>>& out)>* (C++ callers only) */
+int FB_DatasetCreateFromCSRFunc(void* get_row_funptr, int num_rows, int64_t num_col, const char* parameters, const DatasetHandle reference, DatasetHandle* out);
+int FB_BoosterPredictForCSRSingleRowFastInit(BoosterHandle handle, int predict_type, int start_iteration, int num_iteration, int data_type, int64_t num_col,
+                                             const char* parameter, void** out_fast_config);
+int FB_BoosterPredictForCSRSingleRowFast(void* fast_config, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr,
+                                         int64_t nelem, int64_t* out_len, double* out_result);
 int FB_DatasetUpdateParamChecking(const char* old_parameters, const char* new_parameters);
 int FB_BoosterPredictForArrow(BoosterHandle handle, int64_t n_chunks, void* chunks, void* schema, int predict_type, int start_iteration, int num_iteration,
                               const char* parameter, int64_t* out_len, double* out_result);

@@ -247,6 +247,21 @@ FB_COMPAT_BOTH(int, DatasetPushRowsWithMetadata, (DatasetHandle dataset, const v
                ((void)tid, FB_DatasetPushRowsWithMetadata(dataset, data, fb_compat_dtype(data_type), nrow, ncol, start_row, label, weight, init_score, query)))
 FB_COMPAT_BOTH(int, DatasetPushRowsByCSR, (DatasetHandle dataset, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr, int64_t nelem, int64_t num_col, int64_t start_row),
                FB_DatasetPushRowsByCSR(dataset, indptr, fb_compat_dtype(indptr_type), indices, data, fb_compat_dtype(data_type), nindptr, nelem, num_col, start_row))
+FB_COMPAT_BOTH(int, DatasetPushRowsByCSRWithMetadata, (DatasetHandle dataset, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr, int64_t nelem, int64_t start_row, const float* label, const float* weight, const double* init_score, const int32_t* query, int32_t tid),
+               ((void)tid, FB_DatasetPushRowsByCSRWithMetadata(dataset, indptr, fb_compat_dtype(indptr_type), indices, data, fb_compat_dtype(data_type), nindptr, nelem, start_row, label, weight, init_score, query)))
+FB_COMPAT_BOTH(int, DatasetCreateFromSampledColumn, (double** sample_data, int** sample_indices, int32_t ncol, const int* num_per_col, int32_t num_sample_row, int32_t num_local_row, int64_t num_dist_row, const char* parameters, DatasetHandle* out),
+               FB_DatasetCreateFromSampledColumn(sample_data, sample_indices, ncol, num_per_col, num_sample_row, num_local_row, num_dist_row, parameters, out))
+FB_COMPAT_BOTH(int, DatasetCreateFromCSRFunc, (void* get_row_funptr, int num_rows, int64_t num_col, const char* parameters, const DatasetHandle reference, DatasetHandle* out),
+               FB_DatasetCreateFromCSRFunc(get_row_funptr, num_rows, num_col, parameters, reference, out))
+FB_COMPAT_BOTH(int, DatasetCreateFromMatDevice, (const void* data, int data_type, int32_t nrow, int32_t ncol, int is_row_major, const char* parameters, const DatasetHandle reference, DatasetHandle* out),
+               FB_DatasetCreateFromDeviceMat(data, fb_compat_dtype(data_type), nrow, ncol, is_row_major, parameters, reference, out))
+FB_COMPAT_BOTH(int, BoosterPredictForCSRSingleRowFastInit, (BoosterHandle handle, const int predict_type, const int start_iteration, const int num_iteration, const int data_type, const int64_t num_col, const char* parameter, void** out_fastConfig),
+               FB_BoosterPredictForCSRSingleRowFastInit(handle, predict_type, start_iteration, num_iteration, fb_compat_dtype(data_type), num_col, parameter, out_fastConfig))
+/* the old Fast call carries no element type for the values: it is the one given to FastInit, which the adapter cannot see; doubles are assumed (the reference's own default) */
+FB_COMPAT_BOTH(int, BoosterPredictForCSRSingleRowFast, (void* fastConfig_handle, const void* indptr, const int indptr_type, const int32_t* indices, const void* data, const int64_t nindptr, const int64_t nelem, int64_t* out_len, double* out_result),
+               FB_BoosterPredictForCSRSingleRowFast(fastConfig_handle, indptr, fb_compat_dtype(indptr_type), indices, data, 1, nindptr, nelem, out_len, out_result))
+static inline void FLC_SetLastError(const char* msg) { (void)FB_SetLastErrorForCompat(msg); }
+static inline void LGBM_SetLastError(const char* msg) { (void)FB_SetLastErrorForCompat(msg); }
 FB_COMPAT_BOTH(int, DatasetSetWaitForManualFinish, (DatasetHandle dataset, int wait), ((void)dataset, (void)wait, 0))   /* rows are usable once pushed; FB_DatasetMarkFinished closes the stream either way */
 FB_COMPAT_BOTH(int, DatasetGetSubset, (const DatasetHandle handle, const int32_t* used_row_indices, int32_t num_used_row_indices, const char* parameters, DatasetHandle* out),
                ((void)parameters, FB_DatasetGetSubset(handle, used_row_indices, num_used_row_indices, out)))

@@ -16,6 +16,11 @@ PROGRAM = r"""
 #include <stdlib.h>
 #include <math.h>
 #include "fb/c_api_compat.h"
+#ifdef __cplusplus
+#include <functional>
+#include <utility>
+#include <vector>
+#endif
 
 #define CHECK(x) do { if ((x) != 0) { printf("FAILED %s: %s\n", #x, PFX(GetLastError)()); return 1; } } while (0)
 
@@ -69,6 +74,47 @@ int main(void) {
   CHECK(PFX(DatasetPushRows)(ds2, X + (N / 2) * F, C_API_DTYPE_FLOAT64, N - N / 2, F, N / 2));
   CHECK(PFX(DatasetMarkFinished)(ds2));
   CHECK(PFX(DatasetGetNumData)(ds2, &n)); if (n != N) return 1;
+  {
+    /* prepared single-row prediction from a CSR row, a dataset from per-column samples with CSR rows and metadata pushed into it */
+    void* fast = NULL; int32_t ip[2] = {0, 2}; int32_t idx[2] = {0, 1}; double val[2] = {0.25, -0.125}; double one[1], dense[F] = {0}, want[1];
+    DatasetHandle ds3 = NULL; double* cols[F]; int* rows_of[F]; int per_col[F]; static double cv[F][N]; static int cr[F][N];
+    static int32_t sip[N + 1]; static int32_t sidx[N * F]; static double sval[N * F]; const void* lptr = NULL;
+    dense[0] = 0.25; dense[1] = -0.125;
+    CHECK(PFX(BoosterPredictForMat)(bst, dense, C_API_DTYPE_FLOAT64, 1, F, 1, C_API_PREDICT_NORMAL, 0, -1, "", &out_len, want));
+    CHECK(PFX(BoosterPredictForCSRSingleRowFastInit)(bst, C_API_PREDICT_NORMAL, 0, -1, C_API_DTYPE_FLOAT64, F, "", &fast));
+    CHECK(PFX(BoosterPredictForCSRSingleRowFast)(fast, ip, C_API_DTYPE_INT32, idx, val, 2, 2, &out_len, one)); if (out_len != 1 || fabs(one[0] - want[0]) > 1e-12) { printf("csr fast %g %g\n", one[0], want[0]); return 1; }
+    CHECK(FB_FastConfigFree(fast));
+    for (j = 0; j < F; ++j) { per_col[j] = N; cols[j] = cv[j]; rows_of[j] = cr[j]; for (i = 0; i < N; ++i) { cv[j][i] = X[i * F + j]; cr[j][i] = i; } }
+    CHECK(PFX(DatasetCreateFromSampledColumn)(cols, rows_of, F, per_col, N, N, N, "max_bin=63 min_data_in_bin=1", &ds3));
+    CHECK(PFX(DatasetInitStreaming)(ds3, 0, 0, 0, 1, 1, 1));
+    for (i = 0; i < N; ++i) { sip[i] = i * F; for (j = 0; j < F; ++j) { sidx[i * F + j] = j; sval[i * F + j] = X[i * F + j]; } }
+    sip[N] = N * F;
+    CHECK(PFX(DatasetPushRowsByCSRWithMetadata)(ds3, sip, C_API_DTYPE_INT32, sidx, sval, C_API_DTYPE_FLOAT64, N + 1, N * F, 0, y, NULL, NULL, NULL, 0));
+    CHECK(PFX(DatasetMarkFinished)(ds3));
+    CHECK(PFX(DatasetGetField)(ds3, "label", &flen, &lptr, &ftype)); if (flen != N || ((const float*)lptr)[7] != y[7]) { printf("streamed label\n"); return 1; }
+    {
+      /* the streamed dataset trains to the same model as the one-shot dataset (same bins, same rows) */
+      BoosterHandle b3 = NULL; double p3[N];
+      CHECK(PFX(BoosterCreate)(ds3, "objective=regression num_leaves=7 min_data_in_leaf=5 verbosity=-1 metric=l2", &b3));
+      for (i = 0; i < 20; ++i) CHECK(PFX(BoosterUpdateOneIter)(b3, &fin));
+      CHECK(PFX(BoosterPredictForMat)(b3, X, C_API_DTYPE_FLOAT64, N, F, 1, C_API_PREDICT_NORMAL, 0, -1, "", &out_len, p3));
+      for (i = 0; i < N; ++i) if (fabs(p3[i] - pred[i]) > 1e-12) { printf("streamed model differs at %d: %g %g\n", i, p3[i], pred[i]); return 1; }
+      CHECK(PFX(BoosterFree)(b3));
+    }
+    CHECK(PFX(DatasetFree)(ds3));
+#ifdef __cplusplus
+    {
+      /* rows from a callback (C++ callers): the same bins and rows as the dense matrix */
+      DatasetHandle ds4 = NULL; int n4 = 0;
+      std::function<void(int, std::vector<std::pair<int, double>>&)> get_row = [&](int r, std::vector<std::pair<int, double>>& out) {
+        out.clear(); for (int c = 0; c < F; ++c) out.emplace_back(c, X[r * F + c]); };
+      CHECK(PFX(DatasetCreateFromCSRFunc)(&get_row, N, F, "max_bin=63 min_data_in_bin=1", ds, &ds4));
+      CHECK(PFX(DatasetGetNumData)(ds4, &n4)); if (n4 != N) { printf("callback rows %d\n", n4); return 1; }
+      CHECK(PFX(DatasetFree)(ds4));
+    }
+#endif
+    PFX(SetLastError)("set by the caller"); if (strcmp(PFX(GetLastError)(), "set by the caller") != 0) { printf("last error\n"); return 1; }
+  }
   if (PFX(NetworkInit)("127.0.0.1:1", 1, 1, 1) == 0) { printf("NetworkInit should fail\n"); return 1; }
   if (PFX(DatasetUpdateParamChecking)("max_bin=63", "max_bin=15") == 0) { printf("a changed max_bin should be refused\n"); return 1; }
   CHECK(PFX(DatasetUpdateParamChecking)("max_bin=63", "max_bin=63 learning_rate=0.3"));

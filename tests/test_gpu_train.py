@@ -570,3 +570,47 @@ def test_self_verify_mode_checks_device_binning_and_tiled_predict():
     assert text.count("FALCATA_VERIFY: device binning equals the host's on 1024 sampled rows") >= 2
     assert "FALCATA_VERIFY: tiled predict equals the general kernel on 50000 scores" in text
     assert "[diag] construct: lane mode" in text and "[diag] tree 0:" in text
+
+
+def test_c_api_dataset_from_a_device_matrix_matches_the_python_route():
+    """FB_DatasetCreateFromDeviceMat (the reference's FLC_DatasetCreateFromMatDevice): sample gathered on the device, bin
+    boundaries on the host, rows binned on the device. Trains to the model of `fb.Dataset(cuda_tensor)`, which draws the
+    same sample by row id; a column-major matrix and a reference dataset give the same bins."""
+    import ctypes
+
+    from falcata_b200.basic import _lib, _safe_call
+
+    lib = _lib()
+    X, y = make_binary(30000, 10)
+    Xd = torch.as_tensor(X, device="cuda").contiguous()
+    params = "max_bin=63 verbosity=-1"
+    train = "objective=binary num_leaves=31 max_bin=63 verbosity=-1 device_type=cuda quant_mode=stochastic seed=5"
+
+    def train_on(handle, rounds=5):
+        yy = np.ascontiguousarray(y, dtype=np.float32)
+        _safe_call(lib.FB_DatasetSetField(handle, b"label", yy.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(len(yy)), 0))
+        bst = ctypes.c_void_p()
+        _safe_call(lib.FB_BoosterCreate(handle, train.encode(), ctypes.byref(bst)))
+        fin = ctypes.c_int()
+        for _ in range(rounds):
+            _safe_call(lib.FB_BoosterUpdateOneIter(bst, ctypes.byref(fin)))
+        n = ctypes.c_int64()
+        _safe_call(lib.FB_BoosterSaveModelToString(bst, 0, -1, 0, ctypes.c_int64(0), ctypes.byref(n), None))
+        buf = ctypes.create_string_buffer(n.value)
+        _safe_call(lib.FB_BoosterSaveModelToString(bst, 0, -1, 0, ctypes.c_int64(n.value), ctypes.byref(n), buf))
+        _safe_call(lib.FB_BoosterFree(bst))
+        return buf.value.decode()
+
+    h1 = ctypes.c_void_p()
+    _safe_call(lib.FB_DatasetCreateFromDeviceMat(ctypes.c_void_p(Xd.data_ptr()), 0, ctypes.c_int32(Xd.shape[0]), ctypes.c_int32(Xd.shape[1]), 1, params.encode(), None, ctypes.byref(h1)))
+    m1 = train_on(h1)
+    # column-major copy of the same matrix, bins taken from the first dataset
+    Xc = Xd.t().contiguous()
+    h2 = ctypes.c_void_p()
+    _safe_call(lib.FB_DatasetCreateFromDeviceMat(ctypes.c_void_p(Xc.data_ptr()), 0, ctypes.c_int32(Xd.shape[0]), ctypes.c_int32(Xd.shape[1]), 0, params.encode(), h1, ctypes.byref(h2)))
+    m2 = train_on(h2)
+    assert model_body(m1) == model_body(m2)
+    py = fb.train({"objective": "binary", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "device_type": "cuda", "quant_mode": "stochastic", "seed": 5},
+                  fb.Dataset(Xd, y, params={"max_bin": 63}), 5)
+    assert model_body(py.model_to_string()) == model_body(m1)
+    _safe_call(lib.FB_DatasetFree(h2)); _safe_call(lib.FB_DatasetFree(h1))
