@@ -102,6 +102,7 @@ struct LeafState {
   std::vector<double> hist;          // 2 * num_total_bin (g, h) real-valued, or
   std::vector<int64_t> hist_i;       // 2 * num_total_bin integer sums when quantized
   bool has_hist = false;
+  int64_t hist_stamp = 0;            // when the histogram was last produced or read (least recently used ones are dropped first)
   std::vector<uint16_t> box;         // monotone_constraints_method=intermediate: per feature the (first, last) bin of the leaf's cell
   double min_constraint = -std::numeric_limits<double>::infinity(), max_constraint = std::numeric_limits<double>::infinity();
 };
@@ -164,6 +165,14 @@ class CPUTreeLearner : public TreeLearner {
   // forced splits (forcedsplits_filename): a tree of (feature, threshold) applied from the root before normal growth
   struct ForcedNode { int feature = -1; double threshold = 0.0; int left = -1, right = -1; };
   std::vector<ForcedNode> forced_;
+  // histogram_pool_size (MB): at most this many leaf histograms are kept; the least recently used are dropped and a leaf
+  // whose histogram is gone gets both children built from the data when it splits. Parity: src/treelearner/feature_histogram.hpp
+  // (HistogramPool: LRU cache of leaf histograms bounded by histogram_pool_size).
+  int hist_pool_cap_ = 0;            // leaves with a histogram allowed at once (0: unbounded)
+  int64_t hist_clock_ = 0;
+  void TouchHistogram(LeafState* leaf) { leaf->hist_stamp = ++hist_clock_; }
+  void DropHistogram(LeafState* leaf) { std::vector<double>().swap(leaf->hist); std::vector<int64_t>().swap(leaf->hist_i); leaf->has_hist = false; }
+  void EnforceHistogramPool(int num_leaves, int keep_a, int keep_b);
   bool mono_intermediate_ = false;   // monotone bounds from the neighbouring leaves' outputs instead of the split's mid point
   std::vector<int> mono_dirty_;      // leaves whose bounds the last ApplySplit tightened (their best split is stale)
   void TightenMonotoneBounds(const Tree* tree, int left_id, int right_id);
@@ -199,6 +208,11 @@ void CPUTreeLearner::SetParams() {
     Log::Fatal("Per-feature CEGB penalties are not available with a parallel tree learner");
   sp_.use_mc = 0; for (const auto& m : ds_->feature_meta) if (m.monotone != 0) sp_.use_mc = 1;
   mono_intermediate_ = sp_.use_mc != 0 && cfg_.monotone_constraints_method == "intermediate";
+  hist_pool_cap_ = 0;
+  if (cfg_.histogram_pool_size > 0.0 && ds_ != nullptr) {
+    const double per_leaf = static_cast<double>(ds_->num_total_bin) * 2.0 * 8.0;   // (g, h) as doubles or 64-bit integers
+    hist_pool_cap_ = std::max(2, static_cast<int>(cfg_.histogram_pool_size * 1024.0 * 1024.0 / std::max(1.0, per_leaf)));
+  }
   quant_ = cfg_.quant != QuantMode::None;
   qs_.bins = cfg_.quant_bins_resolved; qs_.stochastic = cfg_.quant == QuantMode::Stochastic;
   const bool net = Network::active();
@@ -642,6 +656,8 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
   ScopedTimer timer("CPUTreeLearner::FindBestSplit");
   cur_leaf_id_ = leaf_id;
   InitSplitRecord(&leaf->best);
+  if (!leaf->has_hist) ConstructHistogram(leaf);   // dropped by the histogram pool
+  TouchHistogram(leaf);
   if (sp_.max_depth > 0 && leaf->depth >= sp_.max_depth) return;
   const int64_t n_global = leaf->global_count;
   if (n_global < 2LL * sp_.min_data_in_leaf) return;
@@ -820,14 +836,12 @@ int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
   // GLOBAL counts so that every rank constructs the same child.
   LeafState* smaller = gl <= gr ? &Lf : &R;
   LeafState* larger = gl <= gr ? &R : &Lf;
-  if (parallel_voting_) {
-    // local histograms stay local under voting; both children subtract locally
-    ConstructHistogram(smaller);
-    SubtractHistogram(parent_copy, *smaller, larger);
-  } else {
-    ConstructHistogram(smaller);
-    SubtractHistogram(parent_copy, *smaller, larger);
-  }
+  const bool parent_kept = quant_ ? !parent_copy.hist_i.empty() : !parent_copy.hist.empty();
+  ConstructHistogram(smaller);
+  if (parent_kept) SubtractHistogram(parent_copy, *smaller, larger);
+  else ConstructHistogram(larger);   // the pool dropped the parent's histogram: no subtraction to be had
+  TouchHistogram(smaller); TouchHistogram(larger);
+  if (hist_pool_cap_ > 0) EnforceHistogramPool(tree->num_leaves, leaf_id, right_id);
   return right_id;
 }
 
@@ -872,6 +886,18 @@ void CPUTreeLearner::TightenMonotoneBounds(const Tree* tree, int left_id, int ri
   }
   std::sort(mono_dirty_.begin(), mono_dirty_.end());
   mono_dirty_.erase(std::unique(mono_dirty_.begin(), mono_dirty_.end()), mono_dirty_.end());
+}
+
+void CPUTreeLearner::EnforceHistogramPool(int num_leaves, int keep_a, int keep_b) {
+  int held = 0;
+  for (int l = 0; l < num_leaves; ++l) held += leaves_[l].has_hist ? 1 : 0;
+  while (held > hist_pool_cap_) {
+    int victim = -1;
+    for (int l = 0; l < num_leaves; ++l)
+      if (l != keep_a && l != keep_b && leaves_[l].has_hist && (victim < 0 || leaves_[l].hist_stamp < leaves_[victim].hist_stamp)) victim = l;
+    if (victim < 0) break;
+    DropHistogram(&leaves_[victim]); --held;
+  }
 }
 
 double CPUTreeLearner::CegbFeaturePenalty(int inner_feature, const LeafState& leaf) const {

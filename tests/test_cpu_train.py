@@ -451,3 +451,25 @@ def test_vectorised_threshold_scan_equals_the_scalar_scan_bit_for_bit():
     for threads in (1, 3):                    # and the result does not depend on the thread count
         again = fb.train(dict(base, num_threads=threads), fb.Dataset(X, y), 12)
         assert model_body(again.model_to_string()) == model_body(fast.model_to_string())
+
+
+def test_histogram_pool_size_bounds_the_cached_histograms_without_changing_an_integer_model():
+    """histogram_pool_size (MB) keeps only that many leaf histograms (least recently used dropped first); a leaf whose
+    histogram is gone gets both children built from the data. Integer histograms make both routes exact, so the model
+    is the same digit for digit; with real-valued bins the subtraction rounds differently and the predictions agree
+    closely (reference: src/treelearner/feature_histogram.hpp HistogramPool)."""
+    from util import model_body
+
+    rng = np.random.default_rng(21)
+    X = rng.normal(size=(6000, 12)).astype(np.float32)
+    y = (X[:, 0] * X[:, 1] + X[:, 2] + 0.3 * rng.normal(size=6000) > 0).astype(np.float32)
+    per_leaf_mb = 12 * 64 * 2 * 8 / (1 << 20)      # about 12 KB a leaf at max_bin 63
+    for policy in ("level", "leaf"):
+        base = {"objective": "binary", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "device_type": "cpu", "grow_policy": policy, "quant_mode": "fixedpoint", "quant_bins": 64}
+        full = fb.train(dict(base), fb.Dataset(X, y), 8)
+        tiny = fb.train(dict(base, histogram_pool_size=3 * per_leaf_mb), fb.Dataset(X, y), 8)   # three histograms at a time
+        assert model_body(full.model_to_string()) == model_body(tiny.model_to_string())
+    real = {"objective": "binary", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "device_type": "cpu", "grow_policy": "leaf"}
+    a = fb.train(dict(real), fb.Dataset(X, y), 8).predict(X)
+    b = fb.train(dict(real, histogram_pool_size=3 * per_leaf_mb), fb.Dataset(X, y), 8).predict(X)
+    assert np.max(np.abs(a - b)) < 1e-6
