@@ -93,7 +93,7 @@ def _param_str(params: Optional[Dict[str, Any]]) -> bytes:
         return b""
     parts = []
     for k, v in params.items():
-        if v is None:
+        if v is None or k == "keep_host_bins":   # keep_host_bins is a note between Booster and Dataset of this layer, not a native parameter
             continue
         if isinstance(v, (list, tuple, set)):
             v = ",".join(str(x) for x in v)

@@ -20,6 +20,49 @@
 
 namespace fb {
 
+// Forced splits: a JSON tree {"feature": f, "threshold": v, "left": {...}, "right": {...}} flattened depth-first; node 0 is the root.
+std::vector<ForcedSplitNode> LoadForcedSplitsFile(const std::string& filename) {
+  std::vector<ForcedSplitNode> forced_;
+  if (filename.empty()) return forced_;
+  std::ifstream f(filename);
+  if (!f) Log::Fatal("Cannot open forced splits file %s", filename.c_str());
+  std::stringstream ss; ss << f.rdbuf();
+  const std::string t = ss.str();
+  size_t pos = 0;
+  auto skip_ws = [&]() { while (pos < t.size() && isspace(static_cast<unsigned char>(t[pos]))) ++pos; };
+  std::function<int()> parse_object = [&]() -> int {
+    skip_ws();
+    if (pos >= t.size() || t[pos] != '{') Log::Fatal("Forced splits file: expected '{' at offset %d", static_cast<int>(pos));
+    ++pos;
+    const int id = static_cast<int>(forced_.size()); forced_.emplace_back();
+    for (;;) {
+      skip_ws();
+      if (pos < t.size() && t[pos] == '}') { ++pos; break; }
+      if (pos < t.size() && t[pos] == ',') { ++pos; continue; }
+      if (pos >= t.size() || t[pos] != '"') Log::Fatal("Forced splits file: expected a key at offset %d", static_cast<int>(pos));
+      const size_t e = t.find('"', pos + 1);
+      if (e == std::string::npos) Log::Fatal("Forced splits file: unterminated key");
+      const std::string key = t.substr(pos + 1, e - pos - 1);
+      pos = e + 1; skip_ws();
+      if (pos >= t.size() || t[pos] != ':') Log::Fatal("Forced splits file: expected ':' after \"%s\"", key.c_str());
+      ++pos; skip_ws();
+      if (key == "left" || key == "right") { const int c = parse_object(); if (key == "left") forced_[id].left = c; else forced_[id].right = c; }
+      else {
+        size_t e2 = pos; while (e2 < t.size() && t[e2] != ',' && t[e2] != '}') ++e2;
+        const double v = atof(t.substr(pos, e2 - pos).c_str());
+        if (key == "feature") forced_[id].feature = static_cast<int>(v); else if (key == "threshold") forced_[id].threshold = v;
+        pos = e2;
+      }
+    }
+    return id;
+  };
+  skip_ws();
+  if (pos < t.size()) parse_object();
+  if (!forced_.empty() && forced_[0].feature < 0) forced_.clear();   // "{}"
+  return forced_;
+}
+
+
 double Network::MaxDouble(double v) {
   if (!active()) return v;
   std::vector<char> all; Gather(&v, sizeof(double), &all);
@@ -163,7 +206,7 @@ class CPUTreeLearner : public TreeLearner {
   int cur_tree_index_ = 0, cur_leaf_id_ = 0;
   Random extra_rand_{6};
   // forced splits (forcedsplits_filename): a tree of (feature, threshold) applied from the root before normal growth
-  struct ForcedNode { int feature = -1; double threshold = 0.0; int left = -1, right = -1; };
+  using ForcedNode = ForcedSplitNode;
   std::vector<ForcedNode> forced_;
   // histogram_pool_size (MB): at most this many leaf histograms are kept; the least recently used are dropped and a leaf
   // whose histogram is gone gets both children built from the data when it splits. Parity: src/treelearner/feature_histogram.hpp
@@ -234,45 +277,7 @@ void CPUTreeLearner::Init(const Dataset* train, const Config& cfg) {
 // forcedsplits_filename: nested JSON objects {"feature": i, "threshold": v, "left": {...}, "right": {...}} over real
 // feature indices. Parity: src/treelearner/serial_tree_learner.cpp:L641-781 (ForceSplits: breadth-first from the
 // root, a forced split that does not improve the leaf is ignored together with its subtree).
-void CPUTreeLearner::LoadForcedSplits() {
-  forced_.clear();
-  if (cfg_.forcedsplits_filename.empty()) return;
-  std::ifstream f(cfg_.forcedsplits_filename);
-  if (!f) Log::Fatal("Cannot open forced splits file %s", cfg_.forcedsplits_filename.c_str());
-  std::stringstream ss; ss << f.rdbuf();
-  const std::string t = ss.str();
-  size_t pos = 0;
-  auto skip_ws = [&]() { while (pos < t.size() && isspace(static_cast<unsigned char>(t[pos]))) ++pos; };
-  std::function<int()> parse_object = [&]() -> int {
-    skip_ws();
-    if (pos >= t.size() || t[pos] != '{') Log::Fatal("Forced splits file: expected '{' at offset %d", static_cast<int>(pos));
-    ++pos;
-    const int id = static_cast<int>(forced_.size()); forced_.emplace_back();
-    for (;;) {
-      skip_ws();
-      if (pos < t.size() && t[pos] == '}') { ++pos; break; }
-      if (pos < t.size() && t[pos] == ',') { ++pos; continue; }
-      if (pos >= t.size() || t[pos] != '"') Log::Fatal("Forced splits file: expected a key at offset %d", static_cast<int>(pos));
-      const size_t e = t.find('"', pos + 1);
-      if (e == std::string::npos) Log::Fatal("Forced splits file: unterminated key");
-      const std::string key = t.substr(pos + 1, e - pos - 1);
-      pos = e + 1; skip_ws();
-      if (pos >= t.size() || t[pos] != ':') Log::Fatal("Forced splits file: expected ':' after \"%s\"", key.c_str());
-      ++pos; skip_ws();
-      if (key == "left" || key == "right") { const int c = parse_object(); if (key == "left") forced_[id].left = c; else forced_[id].right = c; }
-      else {
-        size_t e2 = pos; while (e2 < t.size() && t[e2] != ',' && t[e2] != '}') ++e2;
-        const double v = atof(t.substr(pos, e2 - pos).c_str());
-        if (key == "feature") forced_[id].feature = static_cast<int>(v); else if (key == "threshold") forced_[id].threshold = v;
-        pos = e2;
-      }
-    }
-    return id;
-  };
-  skip_ws();
-  if (pos < t.size()) parse_object();
-  if (!forced_.empty() && forced_[0].feature < 0) forced_.clear();   // "{}"
-}
+void CPUTreeLearner::LoadForcedSplits() { forced_ = LoadForcedSplitsFile(cfg_.forcedsplits_filename); }
 
 void CPUTreeLearner::ForceSplits(Tree* tree, int tree_index) {
   std::queue<std::pair<int, int>> q;   // (leaf id, forced node)

@@ -60,8 +60,8 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
       Log::Warning("monotone_constraints_method=intermediate trains on the host learner (the device engine has the basic method)");
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
-    if (!cfg.forcedsplits_filename.empty() && is_cuda_) {
-      Log::Warning("forcedsplits_filename trains on the host learner");
+    if (!cfg.forcedsplits_filename.empty() && is_cuda_ && Network::active() && cfg.tree_learner != "serial") {
+      Log::Warning("forcedsplits_filename with several GPUs trains on the host learner (the device engine forces splits on one GPU)");
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
     if (cfg.linear_tree && !train->has_raw()) Log::Fatal("linear_tree needs the raw feature values: build the Dataset from host data with linear_tree=true in its params");

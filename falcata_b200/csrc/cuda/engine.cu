@@ -134,7 +134,9 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     if (plan_.col_major_part) EnsureColumnMajor(dd_, stream_);
   }
   idx_[0].Alloc(n_); idx_[1].Alloc(n_);
-  leafwise_ = cfg.grow_policy == "leaf" && plan_.device_controller && cfg.num_leaves <= 512 && !voting_;
+  forced_ = LoadForcedSplitsFile(cfg.forcedsplits_filename);
+  if (!forced_.empty() && world_ > 1) Log::Fatal("Forced splits on the device are single-GPU (a multi-GPU booster trains them on the host learner)");
+  leafwise_ = cfg.grow_policy == "leaf" && plan_.device_controller && cfg.num_leaves <= 512 && !voting_ && forced_.empty();
   if (cfg.grow_policy == "leaf" && !leafwise_)
     Log::Warning("grow_policy=leaf on the device needs the level controller, num_leaves <= 512 and tree_learner serial, data or feature; growing level-wise with a gain-ranked leaf budget");
   // leaf-wise: the device may grow past the budget (nodes that looked good enough when they were split); the cap bounds every buffer
@@ -144,6 +146,7 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
   leaves_.Alloc(NL); best_.Alloc(NL); h_leaves_.Alloc(NL); h_best_.Alloc(NL); leaf_value_.Alloc(NL);
   host_leaves_.resize(NL);
   use_ctrl_ = plan_.device_controller && NL <= 1024;
+  if (!forced_.empty()) use_ctrl_ = false;   // forced splits: the host decides every level
   if (use_ctrl_) {
     ctrl_.Alloc(2); frontier_.Alloc(NL + 2); journal_.Alloc(NL); h_ctrl_.Alloc(1); h_journal_.Alloc(NL); h_root_.Alloc(1);
     levels_hint_ = 1; while ((1 << levels_hint_) < NL) ++levels_hint_;
@@ -232,6 +235,74 @@ CudaEngine::CudaEngine(const Config& cfg, const Dataset* train, const ObjectiveF
     Log::Info("[diag] construct: lane mode %d (%d-bin tiles, %s adds), %d rows per block at %d rows, quant_bins %d, sub-rows %d, %d SMs; growth %s, %d trees per round, ranks %d",
               lane_mode_, lane_bins_, lane_red_ ? "reduction" : "load-add-store", ChooseRowsPerBlock(n_), n_, cfg_.quant_bins_resolved, sub_rows_, num_sms_,
               leafwise_ ? "leaf-wise (over-grow + best-first replay)" : "level", K_, world_);
+}
+
+// The record of splitting `leaf` on (inner_feature, bin): what the search kernel reports for that one candidate (both
+// missing-value directions where the feature has them; the better one wins), evaluated on the host from the leaf's
+// histogram in the pool. False when the split is not admissible (a child too small, no gain above the leaf's own).
+bool CudaEngine::ForcedRecord(int leaf, int f, int t, SplitRecord* out) {
+  const FeatureMeta& m = train_->feature_meta[f];
+  const int nb = m.num_bin, nstored = m.bundled ? nb - 1 : nb;
+  if (m.bin_type != static_cast<int>(BinType::Numerical) || nb < 2 || t < 0 || t > nb - 2) return false;
+  const LeafInfo& PL = h_leaves_[leaf];
+  const size_t esz = quant_ ? sizeof(hist_q_t) : sizeof(double2);
+  const char* src = pool_base_ + (static_cast<long long>(host_leaves_[leaf].slot) * slot_stride_ + m.hist_offset) * esz;
+  std::vector<char> raw(static_cast<size_t>(nstored) * esz);
+  FB_CUDA(cudaMemcpyAsync(raw.data(), src, raw.size(), cudaMemcpyDeviceToHost, stream_));
+  float sc[2] = {1.f, 1.f};
+  if (quant_) FB_CUDA(cudaMemcpyAsync(sc, scales_.get(), sizeof(sc), cudaMemcpyDeviceToHost, stream_));
+  FB_CUDA(cudaStreamSynchronize(stream_));
+  std::vector<long long> gi(nb, 0), hi(nb, 0); std::vector<double> gd(nb, 0.0), hd(nb, 0.0);
+  long long sgi = 0, shi = 0; double sgd = 0, shd = 0;
+  for (int b = 0; b < nb; ++b) {
+    if (m.bundled && b == m.most_freq_bin) continue;
+    const int j = (m.bundled && b > m.most_freq_bin) ? b - 1 : b;
+    if (quant_) { const hist_q_t v = reinterpret_cast<const hist_q_t*>(raw.data())[j]; gi[b] = HistQGrad(v); hi[b] = HistQHess(v); sgi += gi[b]; shi += hi[b]; }
+    else { const double2 v = reinterpret_cast<const double2*>(raw.data())[j]; gd[b] = v.x; hd[b] = v.y; sgd += v.x; shd += v.y; }
+  }
+  if (m.bundled) { const int q = m.most_freq_bin; gi[q] = PL.sum_gi - sgi; hi[q] = PL.sum_hi - shi; gd[q] = PL.sum_g - sgd; hd[q] = PL.sum_h - shd; }
+  LeafScanInfo L;
+  L.sum_g = PL.sum_g; L.sum_h = PL.sum_h; L.sum_gi = PL.sum_gi; L.sum_hi = PL.sum_hi; L.num_data = PL.num_data_global;
+  L.parent_output = PL.output; L.g_scale = quant_ ? static_cast<double>(sc[0]) : 1.0; L.h_scale = quant_ ? static_cast<double>(sc[1]) : 1.0; L.min_c = PL.min_c; L.max_c = PL.max_c;
+  L.mono_factor = MonotonePenaltyFactor(PL.depth, sp_.monotone_penalty);
+  L.cnt_factor = FB_DIV(static_cast<double>(L.num_data), L.sum_h);
+  if (sp_.max_delta_step <= 0.0 && sp_.path_smooth <= 0.0) L.min_gain_shift = FB_ADD(LeafGain(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, L.num_data, PL.output), sp_.min_gain_to_split);
+  else L.min_gain_shift = FB_ADD(LeafGainGivenOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, PL.output), sp_.min_gain_to_split);
+  const bool two_pass = m.missing_type != 0 && nb > 2;
+  const int skip = two_pass ? (m.missing_type == 1 ? m.default_bin : nb - 1) : -1;
+  auto bin_h = [&](int b) { return quant_ ? FB_MUL(static_cast<double>(hi[b]), L.h_scale) : hd[b]; };
+  long long Mgi = 0, Mhi = 0; double Mgd = 0, Mhd = 0; int Mc = 0;
+  if (skip >= 0) { Mgi = gi[skip]; Mhi = hi[skip]; Mgd = gd[skip]; Mhd = hd[skip]; Mc = BinCountEstimate(bin_h(skip), L.cnt_factor); }
+  long long pgi = 0, phi = 0; double pgd = 0, phd = 0; int pc = 0;
+  for (int b = 0; b <= t; ++b) if (b != skip) { pgi += gi[b]; phi += hi[b]; pgd += gd[b]; phd += hd[b]; pc += BinCountEstimate(bin_h(b), L.cnt_factor); }
+  double best_gain = -std::numeric_limits<double>::infinity(); int best_rank = 1 << 30, best_pass = 0, best_lc = 0;
+  long long best_lgi = 0, best_lhi = 0; double best_lg = 0, best_lh = 0;
+  for (int pass = 0; pass < (two_pass ? 2 : 1); ++pass) {
+    if (t == skip && pass == 1 && m.missing_type == 1) continue;
+    long long lgi = pgi, lhi = phi; int lc = pc; double lg, lh;
+    const bool addm = pass == 0 && skip >= 0;
+    if (addm) { lgi += Mgi; lhi += Mhi; lc += Mc; }
+    if (quant_) { lg = FB_MUL(static_cast<double>(lgi), L.g_scale); lh = FB_MUL(static_cast<double>(lhi), L.h_scale); }
+    else { lg = pgd + (addm ? Mgd : 0.0); lh = phd + (addm ? Mhd : 0.0); }
+    double lo, ro;
+    const double gain = EvalCandidate(lg, lh, lc, L, sp_, m.monotone, &lo, &ro);
+    if (gain == -std::numeric_limits<double>::infinity()) continue;
+    const int rank = ScanRank(pass, t, nb);
+    if (gain > best_gain || (gain == best_gain && rank < best_rank)) { best_gain = gain; best_rank = rank; best_pass = pass; best_lc = lc; best_lgi = lgi; best_lhi = lhi; best_lg = lg; best_lh = lh; }
+  }
+  if (best_gain == -std::numeric_limits<double>::infinity()) return false;
+  if (sp_.max_depth > 0 && PL.depth >= sp_.max_depth) return false;
+  if (PL.num_data_global < 2 * sp_.min_data_in_leaf) return false;
+  SplitRecord r; InitSplitRecord(&r);
+  r.gain = FB_MUL(best_gain, static_cast<double>(m.penalty)); r.feature = f; r.threshold = t; r.default_left = best_pass == 0 ? 1 : 0;
+  if (sp_.cegb_split > 0.0) r.gain -= sp_.cegb_split * static_cast<double>(PL.num_data_global);
+  r.left_g = best_lg; r.left_h = best_lh; r.right_g = FB_SUB(PL.sum_g, best_lg); r.right_h = FB_SUB(PL.sum_h, best_lh);
+  r.left_gi = best_lgi; r.left_hi = best_lhi; r.left_cnt = best_lc; r.right_cnt = PL.num_data_global - best_lc; r.monotone = m.monotone;
+  r.left_out = LeafOutput(r.left_g, FB_ADD(r.left_h, kEpsilon), sp_, r.left_cnt, PL.output);
+  r.right_out = LeafOutput(r.right_g, FB_ADD(r.right_h, kEpsilon), sp_, r.right_cnt, PL.output);
+  if (sp_.use_mc != 0) { r.left_out = ClampOutput(r.left_out, PL.min_c, PL.max_c); r.right_out = ClampOutput(r.right_out, PL.min_c, PL.max_c); }
+  *out = r;
+  return true;
 }
 
 CudaEngine::~CudaEngine() { if (stream_) cudaStreamDestroy(stream_); }

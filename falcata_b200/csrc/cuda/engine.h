@@ -59,6 +59,10 @@ class CudaEngine : public DeviceEngine {
   void SetupOwnership();
   void RunRootHistogram();
   void ReadBackLevel(int num_leaves);
+  // forced splits (forcedsplits_filename): the tree is grown under the host's control and the forced nodes' records are
+  // evaluated on the host from the leaf's histogram (a few hundred bytes from the pool) with the shared split math
+  std::vector<ForcedSplitNode> forced_;
+  bool ForcedRecord(int leaf, int inner_feature, int bin, SplitRecord* out);
   void DrawBag(int round);
   void DrawGoss(int iter);
   void RenewLeavesFromTrueGradients(Tree* tree);

@@ -12,6 +12,8 @@
 // the gather waits for those. Every wait is bounded and reports through the status word.
 #include "engine.h"
 
+#include <numeric>
+
 namespace fb {
 
 namespace {
@@ -463,18 +465,8 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
   int next_slot = 1;
   std::vector<int> frontier = {0};
   ha.identity_root = 0;
-  while (tree->num_leaves < NL && !frontier.empty()) {
-    std::vector<int> cand;
-    for (int l : frontier) if (host_leaves_[l].best.feature >= 0 && host_leaves_[l].best.gain > 0.0) cand.push_back(l);
-    if (cand.empty()) break;
-    const int budget = NL - tree->num_leaves;
-    if (static_cast<int>(cand.size()) > budget) {
-      std::stable_sort(cand.begin(), cand.end(), [&](int a, int b) {
-        if (host_leaves_[a].best.gain != host_leaves_[b].best.gain) return host_leaves_[a].best.gain > host_leaves_[b].best.gain;
-        return a < b; });
-      cand.resize(budget);
-    }
-    std::sort(cand.begin(), cand.end());   // a level's splits are always applied in ascending leaf order
+  // one level: the listed leaves are split by their `best` records in the order given; next_out = the children
+  auto apply_level = [&](const std::vector<int>& cand, std::vector<int>* next_out) {
     const int S = static_cast<int>(cand.size());
     PartSplit* ps = reinterpret_cast<PartSplit*>(hb);
     ChildInit* ci = reinterpret_cast<ChildInit*>(hb + sizeof(PartSplit) * S);
@@ -482,7 +474,7 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
     long long total_rows = 0; for (int l : cand) total_rows += host_leaves_[l].count;
     ha.rows_per_block = ChooseRowsPerBlock(total_rows);
     int chunk_cursor = 0, block_cursor = 0;
-    std::vector<int> next;
+    std::vector<int>& next = *next_out; next.clear();
     for (int s = 0; s < S; ++s) {
       const int l = cand[s];
       HostLeaf& P = host_leaves_[l];
@@ -537,6 +529,59 @@ Tree* CudaEngine::TrainTree(int class_id, int tree_index) {
       hl.begin = R.begin; hl.count = R.count; hl.buffer = R.buffer; hl.depth = R.depth; hl.best = h_best_[l]; hl.valid = true;
       tree->leaf_count[l] = R.num_data_global;
     }
+  };
+  if (!forced_.empty()) {
+    // Forced splits first, breadth first and a level at a time, in the order the host learner's queue visits them (so
+    // the leaves get the same numbers); the other leaves wait. A forced split that is not admissible is dropped with
+    // its subtree and the leaf keeps the split it found itself.
+    std::vector<std::pair<int, int>> queue = {{0, 0}};   // (leaf, forced node)
+    while (!queue.empty() && tree->num_leaves < NL) {
+      std::vector<int> cand; std::vector<int> node_of;
+      for (const auto& e : queue) {
+        if (static_cast<int>(cand.size()) >= NL - tree->num_leaves) break;
+        const ForcedSplitNode& fn = forced_[e.second];
+        if (fn.feature < 0 || fn.feature >= train_->num_total_features) continue;
+        const int inner = train_->used_feature_map[fn.feature];
+        if (inner < 0 || train_->feature_meta[inner].bin_type != static_cast<int>(BinType::Numerical)) {
+          Log::Warning("Forced split on feature %d is ignored (constant or categorical feature)", fn.feature);
+          continue;
+        }
+        const int nb = train_->feature_meta[inner].num_bin;
+        const int bin = std::min(static_cast<int>(train_->mappers[fn.feature]->ValueToBin(fn.threshold)), nb - 2);
+        SplitRecord r;
+        if (!ForcedRecord(e.first, inner, bin, &r) || !(r.gain > 0.0)) {
+          Log::Warning("Forced split on feature %d is ignored: it does not improve the leaf", fn.feature);
+          continue;
+        }
+        host_leaves_[e.first].best = r;
+        cand.push_back(e.first); node_of.push_back(e.second);
+      }
+      if (cand.empty()) break;
+      std::vector<int> next;
+      apply_level(cand, &next);
+      queue.clear();
+      for (size_t s = 0; s < cand.size(); ++s) {
+        const ForcedSplitNode& fn = forced_[node_of[s]];
+        if (fn.left >= 0) queue.push_back({next[2 * s], fn.left});
+        if (fn.right >= 0) queue.push_back({next[2 * s + 1], fn.right});
+      }
+    }
+    frontier.resize(tree->num_leaves); std::iota(frontier.begin(), frontier.end(), 0);   // everything grows on from here
+  }
+  while (tree->num_leaves < NL && !frontier.empty()) {
+    std::vector<int> cand;
+    for (int l : frontier) if (host_leaves_[l].best.feature >= 0 && host_leaves_[l].best.gain > 0.0) cand.push_back(l);
+    if (cand.empty()) break;
+    const int budget = NL - tree->num_leaves;
+    if (static_cast<int>(cand.size()) > budget) {
+      std::stable_sort(cand.begin(), cand.end(), [&](int a, int b) {
+        if (host_leaves_[a].best.gain != host_leaves_[b].best.gain) return host_leaves_[a].best.gain > host_leaves_[b].best.gain;
+        return a < b; });
+      cand.resize(budget);
+    }
+    std::sort(cand.begin(), cand.end());   // a level's splits are always applied in ascending leaf order
+    std::vector<int> next;
+    apply_level(cand, &next);
     frontier.swap(next);
   }
   return tree.release();

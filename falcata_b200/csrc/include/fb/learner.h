@@ -193,6 +193,11 @@ class TreeLearner {
 
 TreeLearner* CreateTreeLearner(const Config& cfg);
 TreeLearner* CreateCPUTreeLearner(const Config& cfg);
+
+// One node of a forced-splits file (forcedsplits_filename): split `feature` (index in the data) at `threshold`; left / right
+// are indices of the child nodes in the same array or -1. Parity: src/treelearner/serial_tree_learner.cpp (ForceSplits).
+struct ForcedSplitNode { int feature = -1; double threshold = 0.0; int left = -1, right = -1; };
+std::vector<ForcedSplitNode> LoadForcedSplitsFile(const std::string& filename);
 TreeLearner* CreateCUDATreeLearner(const Config& cfg);   // defined in the CUDA module
 
 }  // namespace fb

@@ -614,3 +614,38 @@ def test_c_api_dataset_from_a_device_matrix_matches_the_python_route():
                   fb.Dataset(Xd, y, params={"max_bin": 63}), 5)
     assert model_body(py.model_to_string()) == model_body(m1)
     _safe_call(lib.FB_DatasetFree(h2)); _safe_call(lib.FB_DatasetFree(h1))
+
+
+@pytest.mark.parametrize("quant", ["fixedpoint", "none"])
+def test_forced_splits_on_the_device_match_the_host_learner(tmp_path, quant):
+    """forcedsplits_filename on one GPU: the tree grows under the host's control and the forced nodes' records are
+    evaluated on the host from the leaf's histogram in the device pool. With integer histograms the model is the host
+    learner's, digit for digit (same forced top, same leaf numbering); with real-valued bins the trees agree in
+    structure. A forced node on a feature with missing values and one that cannot be applied are part of the file."""
+    import json
+
+    X, y = make_regression(20000, 8)
+    X = X.copy(); X[::9, 2] = np.nan
+    y = np.round(y * 8) / 8
+    forced = {"feature": 3, "threshold": 0.25,
+              "left": {"feature": 2, "threshold": -0.5, "left": {"feature": 5, "threshold": 0.1}},
+              "right": {"feature": 1, "threshold": 0.0, "right": {"feature": 6, "threshold": 1e9}}}   # the last one leaves nothing on the right: ignored
+    path = tmp_path / "forced.json"
+    path.write_text(json.dumps(forced))
+    base = {"objective": "none", "num_leaves": 31, "max_bin": 63, "verbosity": -1, "quant_mode": quant, "grow_policy": "level", "min_data_in_leaf": 20, "seed": 3,
+            "forcedsplits_filename": str(path)}
+    if quant != "none":
+        base["quant_bins"] = 64
+    bc = fb.train({**base, "device_type": "cpu"}, fb.Dataset(X, y, free_raw_data=False), 2, fobj=_l2_exact)
+    bg = fb.train({**base, "device_type": "cuda"}, fb.Dataset(X, y, free_raw_data=False), 2, fobj=_l2_exact)
+    for t in bg.dump_model()["tree_info"]:
+        root = t["tree_structure"]
+        assert root["split_feature"] == 3 and root["left_child"]["split_feature"] == 2 and root["right_child"]["split_feature"] == 1
+        assert root["left_child"]["left_child"]["split_feature"] == 5
+        assert t["num_leaves"] == 31
+    if quant != "none":
+        assert model_body(bc.model_to_string()) == model_body(bg.model_to_string())
+    else:
+        sc, sg = bc.dump_model()["tree_info"][0]["tree_structure"], bg.dump_model()["tree_info"][0]["tree_structure"]
+        assert sc["split_feature"] == sg["split_feature"] and sc["threshold"] == sg["threshold"]
+        assert np.max(np.abs(bc.predict(X) - bg.predict(X))) < 1e-3
