@@ -193,7 +193,7 @@ class RegressionMAPE : public RegressionBase {
   double RenewTreeOutput(double, const double* score, const data_size_t* idx, int cnt) const override {
     return WeightedPercentile(cnt, 0.5, [&](int k) { return static_cast<double>(label_[idx[k]]) - score[idx[k]]; }, [&](int k) { return static_cast<double>(lw_[idx[k]]); }, true);
   }
-  int DeviceKind() const override { return -1; }
+  int DeviceKind() const override { return kObjMape; }
  private:
   std::vector<label_t> lw_;
 };
@@ -316,6 +316,7 @@ class MultiRegressionL2 : public ObjectiveFunction {
     means_.assign(k_, 0.0);
     for (int t = 0; t < k_; ++t) means_[t] = sums[t] / std::max(sums[k_], kEpsilon);
   }
+  int DeviceKind() const override { return kObjMultiReg; }
   void GetGradients(const double* s, score_t* g, score_t* h) const override {
     const int64_t total = static_cast<int64_t>(n_) * k_;
 #pragma omp parallel for schedule(static) num_threads(RowThreads(n_))
@@ -446,6 +447,7 @@ class CrossEntropyLambda : public ObjectiveFunction {
   }
   void ConvertOutput(const double* in, double* out) const override { out[0] = std::log1p(std::exp(in[0])); }
   std::string ToString() const override { return "cross_entropy_lambda"; }
+  int DeviceKind() const override { return kObjXentLambda; }
  private:
   data_size_t n_ = 0; const label_t* label_ = nullptr; const label_t* weights_ = nullptr;
 };

@@ -74,6 +74,16 @@ __global__ void PointwiseGradKernel(ObjDesc d, const float* __restrict__ score, 
         case kObjGamma: { const float e = expf(-s); g = (1.f - y * e) * w; h = y * e * w; break; }
         case kObjTweedie: { const float rho = static_cast<float>(d.p0), e1 = expf((1.f - rho) * s), e2 = expf((2.f - rho) * s); g = (-y * e1 + e2) * w; h = (-y * (1.f - rho) * e1 + (2.f - rho) * e2) * w; break; }
         case kObjXent: { const float z = 1.f / (1.f + expf(-s)); g = (z - y) * w; h = z * (1.f - z) * w; break; }
+        case kObjMape: g = SignF(s - y) * (w / fmaxf(1.f, fabsf(y))); h = w; break;   // the label weight 1 / max(1, |y|) scales the gradient only
+        case kObjXentLambda: {
+          // cross entropy with the weight inside the link: z = 1 - exp(-w log(1 + e^s)); evaluated in double, as the host objective does
+          const double wd = w, yd = y, epf = exp(static_cast<double>(s)), hhat = log1p(epf);
+          const double z = 1.0 - exp(-wd * hhat), enf = 1.0 / epf;
+          g = static_cast<float>((1.0 - yd / z) * wd / (1.0 + enf));
+          const double c = 1.0 / (1.0 - z), dd = 1.0 + epf, a = wd * epf / (dd * dd), b = (c / ((c - 1.0) * (c - 1.0))) * (1.0 + wd * epf - c);
+          h = static_cast<float>(a * (1.0 + yd * b));
+          break;
+        }
         default: g = 0.f; h = 0.f;
       }
       grad[i] = g; hess[i] = h;
@@ -86,6 +96,21 @@ __global__ void PointwiseGradKernel(ObjDesc d, const float* __restrict__ score, 
     BlockMax2(mg, mh, maxbuf + 2 * c);
     __syncthreads();
   }
+}
+
+// Several L2 targets (multi_regression): target c of row i has its label at [c][i]; one tree per target and round.
+__global__ void MultiRegGradKernel(const float* __restrict__ score, const float* __restrict__ label, const float* __restrict__ weight, int n,
+                                   float* __restrict__ grad, float* __restrict__ hess, float* __restrict__ maxbuf) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = blockIdx.y;
+  float g = 0.f, h = 0.f;
+  if (i < n) {
+    const float w = weight ? weight[i] : 1.f;
+    const size_t o = static_cast<size_t>(c) * n + i;
+    g = (score[o] - label[o]) * w; h = w;
+    grad[o] = g; hess[o] = h;
+  }
+  BlockMax2(fabsf(g), fabsf(h), maxbuf + 2 * c);
 }
 
 // OVA: class c is a binary problem "label == c".
@@ -402,7 +427,7 @@ __global__ void __launch_bounds__(1024) SumPartialsKernel(const double* __restri
 
 void LaunchObjectiveGradients(const ObjDesc& d, const float* score, const float* label, const float* weight, const int* qb, int num_queries,
                               const double* label_gain, int num_gain, int n, float* grad, float* hess, float* maxbuf, cudaStream_t s) {
-  const int K = (d.kind == kObjMulticlass || d.kind == kObjMulticlassOVA) ? d.num_class : 1;
+  const int K = (d.kind == kObjMulticlass || d.kind == kObjMulticlassOVA || d.kind == kObjMultiReg) ? d.num_class : 1;
   FB_CUDA(cudaMemsetAsync(maxbuf, 0, sizeof(float) * 2 * K, s));
   const int threads = 256, blocks = (n + threads - 1) / threads;
   if (n <= 0) return;
@@ -417,6 +442,8 @@ void LaunchObjectiveGradients(const ObjDesc& d, const float* score, const float*
     XendcgKernel<<<num_queries, 128, 0, s>>>(score, label, weight, qb, static_cast<unsigned int>(d.p1), static_cast<unsigned int>(static_cast<int>(d.p0)), grad, hess, maxbuf);
   } else if (d.kind == kObjMulticlassOVA) {
     OvaGradKernel<<<dim3(blocks, K), threads, 0, s>>>(d, score, label, weight, n, grad, hess, maxbuf);
+  } else if (d.kind == kObjMultiReg) {
+    MultiRegGradKernel<<<dim3(blocks, K), threads, 0, s>>>(score, label, weight, n, grad, hess, maxbuf);
   } else {
     PointwiseGradKernel<<<blocks, threads, 0, s>>>(d, score, label, weight, n, grad, hess, maxbuf);
   }

@@ -146,6 +146,7 @@ __global__ void ConvertOutputKernel(int obj_kind, float sigmoid, float* out, int
       break;
     }
     case kObjPoisson: case kObjGamma: case kObjTweedie: out[i] = expf(out[i]); break;
+    case kObjXentLambda: out[i] = log1pf(expf(out[i])); break;
     default: break;
   }
 }

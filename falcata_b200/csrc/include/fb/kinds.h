@@ -6,7 +6,7 @@ namespace fb {
 enum ObjKind : int {
   kObjL2 = 0, kObjL1 = 1, kObjHuber = 2, kObjFair = 3, kObjPoisson = 4, kObjQuantile = 5, kObjMape = 6,
   kObjGamma = 7, kObjTweedie = 8, kObjBinary = 9, kObjMulticlass = 10, kObjMulticlassOVA = 11, kObjXent = 12,
-  kObjXentLambda = 13, kObjLambdarank = 14, kObjXendcg = 15, kObjCustom = 16
+  kObjXentLambda = 13, kObjLambdarank = 14, kObjXendcg = 15, kObjCustom = 16, kObjMultiReg = 17
 };
 
 enum MetricKind : int {

@@ -269,6 +269,34 @@ def test_four_bit_packed_view_keeps_the_model(ff):
     assert model_body(a) == model_body(b)
 
 
+@pytest.mark.parametrize("objective", ["mape", "cross_entropy_lambda", "multi_regression"])
+def test_gradient_kernels_of_mape_xentlambda_and_multi_regression_match_the_host_objective(objective, monkeypatch):
+    """These three objectives have device gradient kernels; FALCATA_HOST_GRADIENTS=1 sends the same training through
+    the objective's host code (scores down, gradients up). Both routes must give the same trees."""
+    rng = np.random.default_rng(5)
+    n = 12000
+    X = rng.normal(size=(n, 8)).astype(np.float32)
+    extra = {}
+    if objective == "mape":
+        y = (np.abs(X[:, 0] * 3 + X[:, 1]) + 0.5).astype(np.float32)
+    elif objective == "cross_entropy_lambda":
+        y = (1.0 / (1.0 + np.exp(-(X[:, 0] + 0.5 * X[:, 1])))).astype(np.float32)
+    else:
+        y = np.column_stack([X[:, 0] + 0.1 * rng.normal(size=n), -2 * X[:, 1] + X[:, 2]]).astype(np.float32)
+        extra = {"num_class": 2}
+    w = rng.uniform(0.5, 2.0, size=n).astype(np.float32)
+    p = {"objective": objective, "num_leaves": 15, "verbosity": -1, "device_type": "cuda", "quant_mode": "none", "min_data_in_leaf": 20, **extra}
+    kernel = fb.train(p, fb.Dataset(X, y, weight=w), 6)
+    monkeypatch.setenv("FALCATA_HOST_GRADIENTS", "1")
+    host = fb.train(p, fb.Dataset(X, y, weight=w), 6)
+    monkeypatch.delenv("FALCATA_HOST_GRADIENTS")
+    a, b = np.asarray(kernel.predict(X, raw_score=True)), np.asarray(host.predict(X, raw_score=True))
+    assert np.max(np.abs(a - b)) < 1e-4 * (1.0 + np.max(np.abs(b)))
+    sk = [t["tree_structure"].get("split_feature") for t in kernel.dump_model()["tree_info"]]
+    sh = [t["tree_structure"].get("split_feature") for t in host.dump_model()["tree_info"]]
+    assert sk == sh
+
+
 def test_objective_without_device_kernel_trains_through_host_gradients():
     X, y = make_regression(15000, 8)
     y = np.abs(y) + 1.0
