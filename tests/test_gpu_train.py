@@ -297,7 +297,7 @@ def test_gradient_kernels_of_mape_xentlambda_and_multi_regression_match_the_host
     assert sk == sh
 
 
-def test_objective_without_device_kernel_trains_through_host_gradients():
+def test_mape_on_the_device_reaches_the_host_learners_loss():
     X, y = make_regression(15000, 8)
     y = np.abs(y) + 1.0
     p = {"objective": "mape", "num_leaves": 15, "verbosity": -1, "grow_policy": "level", "metric": "mape"}
