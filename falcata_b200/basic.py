@@ -311,7 +311,7 @@ def _trains_on_host(params: Dict[str, Any]) -> bool:
             if params.get(k) is not None:
                 return str(params[k]).lower()
         return ""
-    if text("boosting", "boosting_type", "boost") in ("dart", "rf", "random_forest"):
+    if text("boosting", "boosting_type", "boost") in ("rf", "random_forest"):
         return True
     if text("forcedsplits_filename", "fs", "forced_splits_filename", "forced_splits_file", "forced_splits"):
         return True

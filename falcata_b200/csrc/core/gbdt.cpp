@@ -65,8 +65,8 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
     if (cfg.linear_tree && !train->has_raw()) Log::Fatal("linear_tree needs the raw feature values: build the Dataset from host data with linear_tree=true in its params");
-    if ((is_dart_ || is_rf_) && is_cuda_) {
-      Log::Warning("boosting=%s keeps its scores on the host; the device engine is used for gbdt", cfg.boosting.c_str());
+    if (is_rf_ && is_cuda_) {
+      Log::Warning("boosting=%s keeps its scores on the host; the device engine is used for gbdt and dart", cfg.boosting.c_str());
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
     if (is_cuda_) {
@@ -360,7 +360,8 @@ void GBDT::DartDropTrees() {
   }
   for (int i : drop_index_) for (int k = 0; k < num_tree_per_iteration_; ++k) {
     const Tree* t = models_[static_cast<size_t>(i) * num_tree_per_iteration_ + k].get();
-    AddTreeScore(t, train_, train_score_.data() + static_cast<size_t>(k) * train_->num_data, -1.0);
+    if (engine_) engine_->AddTreeToScores(*t, k, -1.0, 1);   // device scores: the training rows only, the validation scores keep the tree until it is rescaled
+    else AddTreeScore(t, train_, train_score_.data() + static_cast<size_t>(k) * train_->num_data, -1.0);
   }
   const double k = static_cast<double>(drop_index_.size());
   if (!config_.xgboost_dart_mode) shrinkage_rate_ = config_.learning_rate / (1.0 + k);
@@ -373,9 +374,15 @@ void GBDT::DartNormalize() {
     Tree* t = models_[static_cast<size_t>(i) * num_tree_per_iteration_ + c].get();
     // validation scores still contain the full old tree; train scores contain none of it
     const double factor = config_.xgboost_dart_mode ? k / (k + config_.learning_rate) : k / (k + 1.0);
-    for (size_t v = 0; v < valid_.size(); ++v) AddTreeScore(t, valid_[v], valid_score_[v].data() + static_cast<size_t>(c) * valid_[v]->num_data, factor - 1.0);
-    t->Shrink(factor);
-    AddTreeScore(t, train_, train_score_.data() + static_cast<size_t>(c) * train_->num_data, 1.0);
+    if (engine_) {
+      engine_->AddTreeToScores(*t, c, factor - 1.0, 2);
+      t->Shrink(factor);
+      engine_->AddTreeToScores(*t, c, 1.0, 1);
+    } else {
+      for (size_t v = 0; v < valid_.size(); ++v) AddTreeScore(t, valid_[v], valid_score_[v].data() + static_cast<size_t>(c) * valid_[v]->num_data, factor - 1.0);
+      t->Shrink(factor);
+      AddTreeScore(t, train_, train_score_.data() + static_cast<size_t>(c) * train_->num_data, 1.0);
+    }
     if (!config_.uniform_drop && c == 0) { sum_weight_ -= tree_weight_[i] * (1.0 - factor); tree_weight_[i] *= factor; }
   }
   if (!config_.uniform_drop) { tree_weight_.push_back(shrinkage_rate_); sum_weight_ += shrinkage_rate_; }
@@ -417,13 +424,17 @@ bool GBDT::TrainOneIter(const float* grad_in, const float* hess_in) {
   if (engine_) {
     std::vector<std::unique_ptr<Tree>> trees; bool all_const = false;
     ScopedTimer te("GBDT::EngineIter");
+    if (is_dart_) DartDropTrees();   // the dropped trees leave the device's training scores; sets this round's shrinkage
     engine_->TrainOneIter(grad_in, hess_in, iter_, shrinkage_rate_, inits, &trees, &all_const);
     if (all_const) {
+      if (is_dart_)   // nothing was learnt this round: the dropped trees go back into the training scores as they were
+        for (int i : drop_index_) for (int k = 0; k < K; ++k) engine_->AddTreeToScores(*models_[static_cast<size_t>(i) * K + k], k, 1.0, 1);
       Log::Warning("Stopped training because there are no more leaves that meet the split requirements");
       if (models_.empty()) for (auto& t : trees) models_.push_back(std::move(t));
       return true;
     }
     for (auto& t : trees) { if (DebugFlags::Get().dump) DumpTree(*t, models_.size()); models_.push_back(std::move(t)); }
+    if (is_dart_) DartNormalize();
     ++iter_;
     return false;
   }

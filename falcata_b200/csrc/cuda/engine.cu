@@ -469,10 +469,10 @@ void CudaEngine::UploadTreeForTraversal(const Tree& tree, const Dataset* ds, Dev
   out->threshold = nullptr; out->decision = tree_dec_.get(); out->leaf_value = tree_floats_.get();
 }
 
-void CudaEngine::AddTreeToScores(const Tree& tree, int k, double scale) {
+void CudaEngine::AddTreeToScores(const Tree& tree, int k, double scale, int which) {
   DevTree dt; UploadTreeForTraversal(tree, train_, &dt);
-  LaunchAddTreeBinned(dt, dd_->rows.get(), dd_->row_stride, n_, static_cast<float>(scale), score_.get() + static_cast<size_t>(k) * n_, stream_);
-  for (auto& vs : valid_) LaunchAddTreeBinned(dt, vs.dd->rows.get(), vs.dd->row_stride, vs.ds->num_data, static_cast<float>(scale), vs.score.get() + static_cast<size_t>(k) * vs.ds->num_data, stream_);
+  if (which != 2) LaunchAddTreeBinned(dt, dd_->rows.get(), dd_->row_stride, n_, static_cast<float>(scale), score_.get() + static_cast<size_t>(k) * n_, stream_);
+  if (which != 1) for (auto& vs : valid_) LaunchAddTreeBinned(dt, vs.dd->rows.get(), vs.dd->row_stride, vs.ds->num_data, static_cast<float>(scale), vs.score.get() + static_cast<size_t>(k) * vs.ds->num_data, stream_);
   FB_CUDA(cudaStreamSynchronize(stream_));
 }
 

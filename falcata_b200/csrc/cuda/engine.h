@@ -44,7 +44,7 @@ class CudaEngine : public DeviceEngine {
                     std::vector<std::unique_ptr<Tree>>* out, bool* all_constant) override;
   std::vector<double> EvalMetric(int data_idx, const std::string& metric_name, bool* supported) override;
   void CopyScoresToHost(int data_idx, double* out) override;
-  void AddTreeToScores(const Tree& tree, int class_id, double scale) override;
+  void AddTreeToScores(const Tree& tree, int class_id, double scale, int which = 0) override;
   void* TrainScorePtr() override { return score_.get(); }
   int64_t GpuLaunches() const override { return LaunchCounter().load(); }
   std::string StageReport() const override { return clock_.Report(); }

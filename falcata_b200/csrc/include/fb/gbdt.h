@@ -28,7 +28,8 @@ class DeviceEngine {
                             const std::vector<double>& init_scores, std::vector<std::unique_ptr<Tree>>* out, bool* all_constant) = 0;
   virtual std::vector<double> EvalMetric(int data_idx, const std::string& metric_name, bool* supported) = 0;
   virtual void CopyScoresToHost(int data_idx, double* out) = 0;
-  virtual void AddTreeToScores(const Tree& tree, int class_id, double scale) = 0;   // all data sets, by traversal
+  // by traversal of the binned rows; which: 0 = training and validation scores, 1 = training only, 2 = validation only
+  virtual void AddTreeToScores(const Tree& tree, int class_id, double scale, int which = 0) = 0;
   virtual void* TrainScorePtr() = 0;       // float* on the device, class-major
   virtual int64_t GpuLaunches() const = 0;
   virtual std::string StageReport() const = 0;

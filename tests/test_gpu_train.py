@@ -677,3 +677,24 @@ def test_forced_splits_on_the_device_match_the_host_learner(tmp_path, quant):
         sc, sg = bc.dump_model()["tree_info"][0]["tree_structure"], bg.dump_model()["tree_info"][0]["tree_structure"]
         assert sc["split_feature"] == sg["split_feature"] and sc["threshold"] == sg["threshold"]
         assert np.max(np.abs(bc.predict(X) - bg.predict(X))) < 1e-3
+
+
+def test_dart_on_the_device_engine_follows_the_host_learner():
+    """boosting=dart with device_type=cuda: trees grow on the device; dropped trees leave and re-enter the device's
+    training scores by binned traversal (validation scores are rescaled in place). Same drop draws as the host
+    learner, so with integer histograms the two models agree tree for tree; the recorded validation metric is the
+    metric of the final model's predictions."""
+    X, y = make_binary(20000, 10)
+    Xv, yv = make_binary(5000, 10, seed=9) if "seed" in make_binary.__code__.co_varnames else (X[:5000], y[:5000])
+    p = {"objective": "binary", "boosting": "dart", "drop_rate": 0.3, "skip_drop": 0.2, "num_leaves": 15, "max_bin": 63, "verbosity": -1, "quant_mode": "fixedpoint",
+         "quant_bins": 64, "min_data_in_leaf": 20, "metric": "binary_logloss", "seed": 7}
+    rec = {}
+    dtrain = fb.Dataset(X, y, free_raw_data=False)
+    dev = fb.train({**p, "device_type": "cuda"}, dtrain, 25, valid_sets=[fb.Dataset(Xv, yv, reference=dtrain)], valid_names=["v"], callbacks=[fb.record_evaluation(rec)])
+    cpu = fb.train({**p, "device_type": "cpu"}, fb.Dataset(X, y, free_raw_data=False), 25)
+    assert dev.num_trees() == 25
+    pd_, pc = np.asarray(dev.predict(Xv)), np.asarray(cpu.predict(Xv))
+    assert np.max(np.abs(pd_ - pc)) < 2e-3
+    ll = float(-np.mean(yv * np.log(np.clip(pd_, 1e-15, 1)) + (1 - yv) * np.log(np.clip(1 - pd_, 1e-15, 1))))
+    assert abs(rec["v"]["binary_logloss"][-1] - ll) < 2e-4     # the device's validation scores followed every rescaling
+    assert auc(yv, pd_) > 0.75
