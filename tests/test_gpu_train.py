@@ -684,8 +684,8 @@ def test_dart_on_the_device_engine_follows_the_host_learner():
     training scores by binned traversal (validation scores are rescaled in place). Same drop draws as the host
     learner, so with integer histograms the two models agree tree for tree; the recorded validation metric is the
     metric of the final model's predictions."""
-    X, y = make_binary(20000, 10)
-    Xv, yv = make_binary(5000, 10, seed=9) if "seed" in make_binary.__code__.co_varnames else (X[:5000], y[:5000])
+    Xa, ya = make_binary(25000, 10)
+    X, y, Xv, yv = Xa[:20000], ya[:20000], Xa[20000:], ya[20000:]
     p = {"objective": "binary", "boosting": "dart", "drop_rate": 0.3, "skip_drop": 0.2, "num_leaves": 15, "max_bin": 63, "verbosity": -1, "quant_mode": "fixedpoint",
          "quant_bins": 64, "min_data_in_leaf": 20, "metric": "binary_logloss", "seed": 7}
     rec = {}
