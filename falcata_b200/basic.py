@@ -311,8 +311,9 @@ def _trains_on_host(params: Dict[str, Any]) -> bool:
             if params.get(k) is not None:
                 return str(params[k]).lower()
         return ""
-    if text("boosting", "boosting_type", "boost") in ("rf", "random_forest"):
-        return True
+    if text("boosting", "boosting_type", "boost") in ("rf", "random_forest") and text("objective", "objective_type", "app", "application", "loss") in (
+            "regression_l1", "l1", "mae", "mean_absolute_error", "quantile", "mape", "mean_absolute_percentage_error"):
+        return True   # a forest whose objective renews its leaf outputs trains on the host learner
     if text("forcedsplits_filename", "fs", "forced_splits_filename", "forced_splits_file", "forced_splits"):
         return True
     for k in ("cegb_penalty_feature_coupled", "cegb_penalty_feature_lazy"):

@@ -65,8 +65,8 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
     if (cfg.linear_tree && !train->has_raw()) Log::Fatal("linear_tree needs the raw feature values: build the Dataset from host data with linear_tree=true in its params");
-    if (is_rf_ && is_cuda_) {
-      Log::Warning("boosting=%s keeps its scores on the host; the device engine is used for gbdt and dart", cfg.boosting.c_str());
+    if (is_rf_ && is_cuda_ && (obj == nullptr || obj->IsRenewTreeOutput())) {
+      Log::Warning("boosting=rf with an objective that renews its leaf outputs (or without an objective) trains on the host learner");
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
     if (is_cuda_) {
@@ -425,7 +425,34 @@ bool GBDT::TrainOneIter(const float* grad_in, const float* hess_in) {
     std::vector<std::unique_ptr<Tree>> trees; bool all_const = false;
     ScopedTimer te("GBDT::EngineIter");
     if (is_dart_) DartDropTrees();   // the dropped trees leave the device's training scores; sets this round's shrinkage
-    engine_->TrainOneIter(grad_in, hess_in, iter_, shrinkage_rate_, inits, &trees, &all_const);
+    if (is_rf_) {
+      // Random forest on the device: every tree is trained on the gradients at the start score (computed once on the
+      // host and handed to the engine as this round's gradients), with shrinkage 1; the device scores hold the running
+      // mean of the trees' outputs: s <- m s, the engine adds the new tree, s <- (s + start score) / (m + 1).
+      const data_size_t n = train_->num_data;
+      if (grad_in == nullptr) {
+        if (rf_init_scores_.empty()) {
+          rf_init_scores_.assign(static_cast<size_t>(n) * K, 0.0);
+          for (int k = 0; k < K; ++k) for (data_size_t i = 0; i < n; ++i) rf_init_scores_[static_cast<size_t>(k) * n + i] = init_scores_[k];
+          grad_.resize(static_cast<size_t>(n) * K); hess_.resize(static_cast<size_t>(n) * K);
+          objective_->GetGradients(rf_init_scores_.data(), grad_.data(), hess_.data());
+        }
+        grad_in = grad_.data(); hess_in = hess_.data();
+      }
+      const double m = static_cast<double>(iter_);
+      engine_->ScaleScores(m, {});
+      std::vector<double> zeros(K, 0.0);
+      engine_->TrainOneIter(grad_in, hess_in, iter_, 1.0, zeros, &trees, &all_const);
+      if (all_const) { if (m > 0.0) engine_->ScaleScores(1.0 / m, {}); }   // nothing was added: back to the mean of the m trees
+      else {
+        std::vector<double> bias(K, 0.0);
+        for (int k = 0; k < K; ++k) bias[k] = init_scores_[k] / (m + 1.0);
+        engine_->ScaleScores(1.0 / (m + 1.0), bias);
+      }
+      if (!all_const) for (int k = 0; k < K && k < static_cast<int>(trees.size()); ++k) if (std::fabs(init_scores_[k]) > kEpsilon) trees[k]->AddBias(init_scores_[k]);
+    } else {
+      engine_->TrainOneIter(grad_in, hess_in, iter_, shrinkage_rate_, inits, &trees, &all_const);
+    }
     if (all_const) {
       if (is_dart_)   // nothing was learnt this round: the dropped trees go back into the training scores as they were
         for (int i : drop_index_) for (int k = 0; k < K; ++k) engine_->AddTreeToScores(*models_[static_cast<size_t>(i) * K + k], k, 1.0, 1);

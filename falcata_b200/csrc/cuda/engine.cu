@@ -431,6 +431,14 @@ void CudaEngine::AddConstantToScores(double v, int k) {
   for (auto& vs : valid_) LaunchAddConstant(vs.score.get() + static_cast<size_t>(k) * vs.ds->num_data, vs.ds->num_data, static_cast<float>(v), stream_);
 }
 
+void CudaEngine::ScaleScores(double a, const std::vector<double>& b) {
+  for (int k = 0; k < K_; ++k) {
+    const float bk = k < static_cast<int>(b.size()) ? static_cast<float>(b[k]) : 0.f;
+    LaunchScaleAdd(score_.get() + static_cast<size_t>(k) * n_, n_, static_cast<float>(a), bk, stream_);
+    for (auto& vs : valid_) LaunchScaleAdd(vs.score.get() + static_cast<size_t>(k) * vs.ds->num_data, vs.ds->num_data, static_cast<float>(a), bk, stream_);
+  }
+}
+
 void CudaEngine::AddValid(const Dataset* valid) {
   EnsureDeviceDataset(const_cast<Dataset*>(valid));
   SyncDeviceMetadata(valid, stream_);

@@ -40,6 +40,7 @@ class CudaEngine : public DeviceEngine {
   ~CudaEngine() override;
   void AddValid(const Dataset* valid) override;
   void AddConstantToScores(double v, int class_id) override;
+  void ScaleScores(double a, const std::vector<double>& b) override;
   void TrainOneIter(const float* custom_grad, const float* custom_hess, int iter, double shrinkage, const std::vector<double>& init_scores,
                     std::vector<std::unique_ptr<Tree>>* out, bool* all_constant) override;
   std::vector<double> EvalMetric(int data_idx, const std::string& metric_name, bool* supported) override;

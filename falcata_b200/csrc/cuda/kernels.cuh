@@ -311,6 +311,7 @@ void LaunchAddLeafOutputs(const LeafInfo* leaves, const double* leaf_value, int 
 void LaunchAddLeafOutputsFromRecords(const LeafInfo* leaves, const LevelCtrl* ctrl, double shrinkage, int max_leaves, const int* idx0, const int* idx1, float* score,
                                      cudaStream_t s, bool decided_ahead = false);
 void LaunchAddConstant(float* score, int n, float v, cudaStream_t s);
+void LaunchScaleAdd(float* score, int n, float a, float b, cudaStream_t s);
 // per-leaf (sum g, sum h) of float gradients over the leaf windows: partial[2 * (leaf * slices + slice) + {0,1}]
 int LeafGradSumSlices();
 void LaunchLeafGradSums(const LeafInfo* leaves, int num_leaves, const int* idx0, const int* idx1, const float* grad, const float* hess, double* partial, cudaStream_t s);

@@ -227,6 +227,12 @@ void LaunchLeafGradSums(const LeafInfo* leaves, int num_leaves, const int* idx0,
   LeafGradSumsKernel<<<dim3(num_leaves, kRenewSlices), 256, 0, s>>>(leaves, idx0, idx1, grad, hess, partial);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
+__global__ void ScaleAddKernel(float* score, int n, float a, float b) { const int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < n) score[i] = a * score[i] + b; }
+void LaunchScaleAdd(float* score, int n, float a, float b, cudaStream_t s) {
+  if (n <= 0) return;
+  ScaleAddKernel<<<(n + 255) / 256, 256, 0, s>>>(score, n, a, b);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
 void LaunchAddConstant(float* score, int n, float v, cudaStream_t s) {
   if (n <= 0) return;
   AddConstantKernel<<<(n + 255) / 256, 256, 0, s>>>(score, n, v);

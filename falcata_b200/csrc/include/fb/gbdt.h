@@ -22,6 +22,8 @@ class DeviceEngine {
   virtual ~DeviceEngine() {}
   virtual void AddValid(const Dataset* valid) = 0;
   virtual void AddConstantToScores(double v, int class_id) = 0;
+  // score = a * score + b[class] on the training and every validation set (random forests keep running means)
+  virtual void ScaleScores(double a, const std::vector<double>& b) = 0;
   // Computes gradients on the device (or takes custom device gradients), grows one tree per
   // class, shrinks them, adds them to the train and validation scores. Returns host trees.
   virtual void TrainOneIter(const float* custom_grad, const float* custom_hess, int iter, double shrinkage,

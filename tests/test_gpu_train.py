@@ -698,3 +698,23 @@ def test_dart_on_the_device_engine_follows_the_host_learner():
     ll = float(-np.mean(yv * np.log(np.clip(pd_, 1e-15, 1)) + (1 - yv) * np.log(np.clip(1 - pd_, 1e-15, 1))))
     assert abs(rec["v"]["binary_logloss"][-1] - ll) < 2e-4     # the device's validation scores followed every rescaling
     assert auc(yv, pd_) > 0.75
+
+
+def test_random_forest_on_the_device_engine_follows_the_host_learner():
+    """boosting=rf with device_type=cuda: every tree is trained on the device on the gradients at the start score; the
+    device scores hold the running mean of the trees (each carrying the start score). Same bags as the host learner:
+    with integer histograms both forests predict alike, and the recorded metric is the final forest's."""
+    Xa, ya = make_binary(25000, 10)
+    X, y, Xv, yv = Xa[:20000], ya[:20000], Xa[20000:], ya[20000:]
+    p = {"objective": "binary", "boosting": "rf", "bagging_freq": 1, "bagging_fraction": 0.6, "feature_fraction": 0.8, "num_leaves": 31, "max_bin": 63, "verbosity": -1,
+         "quant_mode": "fixedpoint", "quant_bins": 64, "min_data_in_leaf": 20, "metric": "binary_logloss", "seed": 3}
+    rec = {}
+    dtrain = fb.Dataset(X, y, free_raw_data=False)
+    dev = fb.train({**p, "device_type": "cuda"}, dtrain, 12, valid_sets=[fb.Dataset(Xv, yv, reference=dtrain)], valid_names=["v"], callbacks=[fb.record_evaluation(rec)])
+    cpu = fb.train({**p, "device_type": "cpu"}, fb.Dataset(X, y, free_raw_data=False), 12)
+    assert dev.num_trees() == 12
+    pd_, pc = np.asarray(dev.predict(Xv)), np.asarray(cpu.predict(Xv))
+    assert np.max(np.abs(pd_ - pc)) < 2e-3
+    ll = float(-np.mean(yv * np.log(np.clip(pd_, 1e-15, 1)) + (1 - yv) * np.log(np.clip(1 - pd_, 1e-15, 1))))
+    assert abs(rec["v"]["binary_logloss"][-1] - ll) < 2e-4
+    assert auc(yv, pd_) > 0.8
