@@ -436,8 +436,9 @@ bool GBDT::TrainOneIter(const float* grad_in, const float* hess_in) {
           for (int k = 0; k < K; ++k) for (data_size_t i = 0; i < n; ++i) rf_init_scores_[static_cast<size_t>(k) * n + i] = init_scores_[k];
           grad_.resize(static_cast<size_t>(n) * K); hess_.resize(static_cast<size_t>(n) * K);
           objective_->GetGradients(rf_init_scores_.data(), grad_.data(), hess_.data());
+          engine_->UploadGradients(grad_.data(), hess_.data(), &rf_dev_grad_, &rf_dev_hess_);   // the engine reads device memory only
         }
-        grad_in = grad_.data(); hess_in = hess_.data();
+        grad_in = rf_dev_grad_; hess_in = rf_dev_hess_;
       }
       const double m = static_cast<double>(iter_);
       engine_->ScaleScores(m, {});

@@ -431,6 +431,15 @@ void CudaEngine::AddConstantToScores(double v, int k) {
   for (auto& vs : valid_) LaunchAddConstant(vs.score.get() + static_cast<size_t>(k) * vs.ds->num_data, vs.ds->num_data, static_cast<float>(v), stream_);
 }
 
+void CudaEngine::UploadGradients(const float* host_grad, const float* host_hess, const float** dev_grad, const float** dev_hess) {
+  const size_t total = static_cast<size_t>(n_) * K_;
+  fixed_grad_.Alloc(total); fixed_hess_.Alloc(total);
+  FB_CUDA(cudaMemcpyAsync(fixed_grad_.get(), host_grad, sizeof(float) * total, cudaMemcpyHostToDevice, stream_));
+  FB_CUDA(cudaMemcpyAsync(fixed_hess_.get(), host_hess, sizeof(float) * total, cudaMemcpyHostToDevice, stream_));
+  FB_CUDA(cudaStreamSynchronize(stream_));
+  *dev_grad = fixed_grad_.get(); *dev_hess = fixed_hess_.get();
+}
+
 void CudaEngine::ScaleScores(double a, const std::vector<double>& b) {
   for (int k = 0; k < K_; ++k) {
     const float bk = k < static_cast<int>(b.size()) ? static_cast<float>(b[k]) : 0.f;

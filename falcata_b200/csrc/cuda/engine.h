@@ -41,6 +41,7 @@ class CudaEngine : public DeviceEngine {
   void AddValid(const Dataset* valid) override;
   void AddConstantToScores(double v, int class_id) override;
   void ScaleScores(double a, const std::vector<double>& b) override;
+  void UploadGradients(const float* host_grad, const float* host_hess, const float** dev_grad, const float** dev_hess) override;
   void TrainOneIter(const float* custom_grad, const float* custom_hess, int iter, double shrinkage, const std::vector<double>& init_scores,
                     std::vector<std::unique_ptr<Tree>>* out, bool* all_constant) override;
   std::vector<double> EvalMetric(int data_idx, const std::string& metric_name, bool* supported) override;
@@ -62,6 +63,7 @@ class CudaEngine : public DeviceEngine {
   void ReadBackLevel(int num_leaves);
   // forced splits (forcedsplits_filename): the tree is grown under the host's control and the forced nodes' records are
   // evaluated on the host from the leaf's histogram (a few hundred bytes from the pool) with the shared split math
+  DevBuf<float> fixed_grad_, fixed_hess_;   // gradients uploaded once and reused every round (random forests)
   std::vector<ForcedSplitNode> forced_;
   bool ForcedRecord(int leaf, int inner_feature, int bin, SplitRecord* out);
   void DrawBag(int round);

@@ -22,6 +22,9 @@ class DeviceEngine {
   virtual ~DeviceEngine() {}
   virtual void AddValid(const Dataset* valid) = 0;
   virtual void AddConstantToScores(double v, int class_id) = 0;
+  // Copies host gradients (n * trees-per-round values each) into device buffers owned by the engine and returns the device
+  // pointers, which TrainOneIter takes as its custom gradients (it reads device memory only).
+  virtual void UploadGradients(const float* host_grad, const float* host_hess, const float** dev_grad, const float** dev_hess) = 0;
   // score = a * score + b[class] on the training and every validation set (random forests keep running means)
   virtual void ScaleScores(double a, const std::vector<double>& b) = 0;
   // Computes gradients on the device (or takes custom device gradients), grows one tree per
@@ -146,6 +149,7 @@ class GBDT {
   bool boosted_from_average_ = false;
   double first_grad_norm_ = -1;
   std::vector<double> rf_init_scores_;
+  const float* rf_dev_grad_ = nullptr; const float* rf_dev_hess_ = nullptr;   // device copies of the forest's fixed gradients (owned by the engine)
 };
 
 }  // namespace fb
