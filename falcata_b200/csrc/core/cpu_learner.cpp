@@ -135,6 +135,7 @@ namespace {
 
 struct LeafState {
   int begin = 0, count = 0;          // window in indices_
+  int id = 0;                        // leaf index in the tree
   double sum_g = 0, sum_h = 0;
   int64_t sum_gi = 0, sum_hi = 0;
   int64_t global_count = 0;          // rows of the leaf over all ranks
@@ -169,8 +170,11 @@ class CPUTreeLearner : public TreeLearner {
   void SetParams();
   void Quantize(const score_t* grad, const score_t* hess, int tree_index);
   void ConstructHistogram(LeafState* leaf);
-  void SubtractHistogram(const LeafState& parent_as_larger_src, const LeafState& smaller, LeafState* larger);
+  void SubtractHistogram(LeafState* parent, const LeafState& smaller, LeafState* larger);
   void FindBestSplit(LeafState* leaf, int leaf_id, int tree_index);
+  void FindBestSplitMany(const std::vector<int>& ids, int tree_index);
+  bool PrepareLeafScan(LeafState* leaf, int leaf_id, int tree_index, LeafScanInfo* L, std::vector<int8_t>* mask);
+  void FinishLeafScan(LeafState* leaf, const LeafScanInfo& L, SplitRecord* per);
   void ScanNumerical(const LeafState& leaf, int f, const LeafScanInfo& L, SplitRecord* best) const;
   void ScanCategorical(const LeafState& leaf, int f, const LeafScanInfo& L, SplitRecord* best) const;
   int ApplySplit(Tree* tree, int leaf_id);
@@ -434,13 +438,16 @@ void CPUTreeLearner::ReduceHistogramAcrossRanks(LeafState* leaf) {
   else Network::SumDouble(leaf->hist.data(), static_cast<int64_t>(leaf->hist.size()));
 }
 
-void CPUTreeLearner::SubtractHistogram(const LeafState& parent, const LeafState& smaller, LeafState* larger) {
+// larger = parent - smaller, in the parent's own buffer (the parent is a leaf no more)
+void CPUTreeLearner::SubtractHistogram(LeafState* parent, const LeafState& smaller, LeafState* larger) {
   if (quant_) {
-    larger->hist_i.resize(parent.hist_i.size());
-    for (size_t i = 0; i < parent.hist_i.size(); ++i) larger->hist_i[i] = parent.hist_i[i] - smaller.hist_i[i];
+    larger->hist_i = std::move(parent->hist_i);
+    int64_t* d = larger->hist_i.data(); const int64_t* s = smaller.hist_i.data();
+    for (size_t i = 0, n = larger->hist_i.size(); i < n; ++i) d[i] -= s[i];
   } else {
-    larger->hist.resize(parent.hist.size());
-    for (size_t i = 0; i < parent.hist.size(); ++i) larger->hist[i] = parent.hist[i] - smaller.hist[i];
+    larger->hist = std::move(parent->hist);
+    double* d = larger->hist.data(); const double* s = smaller.hist.data();
+    for (size_t i = 0, n = larger->hist.size(); i < n; ++i) d[i] -= s[i];
   }
   larger->has_hist = true;
 }
@@ -538,7 +545,7 @@ void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanI
   int64_t mgi = 0, mhi = 0; double mgd = 0, mhd = 0; int mcnt = 0;
   if (skip >= 0) { mgi = gi[skip]; mhi = hi[skip]; mgd = gd[skip]; mhd = hd[skip]; mcnt = BinCountEstimate(binh(skip), L.cnt_factor); }
   int rand_t = -1;
-  if (sp_.extra_trees && nb > 2) rand_t = ExtraTreesThreshold(static_cast<uint32_t>(cfg_.extra_seed), cur_tree_index_, cur_leaf_id_, m.real_index, nb);
+  if (sp_.extra_trees && nb > 2) rand_t = ExtraTreesThreshold(static_cast<uint32_t>(cfg_.extra_seed), cur_tree_index_, leaf.id, m.real_index, nb);
   if (forced_bin_ >= 0 && f == forced_feature_) rand_t = forced_bin_;
   double best_gain = -std::numeric_limits<double>::infinity(); int best_rank = 1 << 30;
   SplitRecord cand; InitSplitRecord(&cand);
@@ -657,16 +664,16 @@ void CPUTreeLearner::SyncBestSplit(SplitRecord* rec) const {
   *rec = bestr;
 }
 
-void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index) {
-  ScopedTimer timer("CPUTreeLearner::FindBestSplit");
-  cur_leaf_id_ = leaf_id;
+// Everything FindBestSplit settles before the features are scanned: false when the leaf cannot be split at all.
+bool CPUTreeLearner::PrepareLeafScan(LeafState* leaf, int leaf_id, int tree_index, LeafScanInfo* Lout, std::vector<int8_t>* mask_out) {
+  leaf->id = leaf_id;
   InitSplitRecord(&leaf->best);
   if (!leaf->has_hist) ConstructHistogram(leaf);   // dropped by the histogram pool
   TouchHistogram(leaf);
-  if (sp_.max_depth > 0 && leaf->depth >= sp_.max_depth) return;
+  if (sp_.max_depth > 0 && leaf->depth >= sp_.max_depth) return false;
   const int64_t n_global = leaf->global_count;
-  if (n_global < 2LL * sp_.min_data_in_leaf) return;
-  LeafScanInfo L;
+  if (n_global < 2LL * sp_.min_data_in_leaf) return false;
+  LeafScanInfo& L = *Lout;
   L.sum_g = leaf->sum_g; L.sum_h = leaf->sum_h; L.sum_gi = leaf->sum_gi; L.sum_hi = leaf->sum_hi;
   L.num_data = static_cast<int>(n_global); L.parent_output = leaf->output; L.min_c = leaf->min_constraint; L.max_c = leaf->max_constraint;
   L.g_scale = quant_ ? qs_.g_scale : 1.0; L.h_scale = quant_ ? qs_.h_scale : 1.0;
@@ -675,8 +682,56 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
   L.min_gain_shift = FB_ADD(LeafGainGivenOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, leaf->output), sp_.min_gain_to_split);
   if (sp_.max_delta_step <= 0.0 && sp_.path_smooth <= 0.0)
     L.min_gain_shift = FB_ADD(LeafGain(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, L.num_data, leaf->output), sp_.min_gain_to_split);
-  std::vector<int8_t> mask = col_sampler_.by_node() ? col_sampler_.SampleByNode(tree_index, leaf_id + 1000003 * leaf->depth, &leaf->path) : col_sampler_.used_by_tree();
-  if (forced_feature_ >= 0) { mask.assign(mask.size(), 0); mask[forced_feature_] = 1; }
+  *mask_out = col_sampler_.by_node() ? col_sampler_.SampleByNode(tree_index, leaf_id + 1000003 * leaf->depth, &leaf->path) : col_sampler_.used_by_tree();
+  if (forced_feature_ >= 0) { mask_out->assign(mask_out->size(), 0); (*mask_out)[forced_feature_] = 1; }
+  return true;
+}
+
+// The per-feature records of one leaf merged in feature order into its best split (SplitBetter is a total order, so the
+// result does not depend on which thread scanned which feature).
+void CPUTreeLearner::FinishLeafScan(LeafState* leaf, const LeafScanInfo& L, SplitRecord* per) {
+  SplitRecord best; InitSplitRecord(&best);
+  for (int f = 0; f < ds_->num_features; ++f) {
+    SplitRecord& r = per[f];
+    if (r.feature < 0) continue;
+    if (!cegb_coupled_.empty() || !cegb_lazy_.empty()) { r.gain -= CegbFeaturePenalty(f, *leaf); if (!(r.gain > 0.0)) continue; }
+    if (SplitBetter(r.gain, ds_->feature_meta[r.feature].real_index, r.threshold, best.gain, best.feature >= 0 ? ds_->feature_meta[best.feature].real_index : -1, best.threshold)) best = r;
+  }
+  // Parity: src/treelearner/cost_effective_gradient_boosting.hpp (DeltaGain: tradeoff * penalty_split * rows of the leaf)
+  if (best.feature >= 0 && sp_.cegb_split > 0.0) best.gain -= sp_.cegb_split * static_cast<double>(L.num_data);
+  SyncBestSplit(&best);
+  leaf->best = best;
+}
+
+// Several leaves searched in one parallel region (the two children of a split, the children of a whole level): the
+// tasks are (leaf, feature) pairs. Same records, same merge order and the same sequence of cross-rank exchanges as one
+// FindBestSplit call per leaf in the order given.
+void CPUTreeLearner::FindBestSplitMany(const std::vector<int>& ids, int tree_index) {
+  if (ids.size() <= 1 || parallel_voting_ || forced_feature_ >= 0) { for (int id : ids) FindBestSplit(&leaves_[id], id, tree_index); return; }
+  ScopedTimer timer("CPUTreeLearner::FindBestSplit");
+  const int nf = ds_->num_features, nj = static_cast<int>(ids.size());
+  std::vector<LeafScanInfo> Ls(nj); std::vector<std::vector<int8_t>> masks(nj); std::vector<char> active(nj, 0);
+  for (int j = 0; j < nj; ++j) active[j] = PrepareLeafScan(&leaves_[ids[j]], ids[j], tree_index, &Ls[j], &masks[j]) ? 1 : 0;
+  std::vector<SplitRecord> per(static_cast<size_t>(nj) * nf);
+  const bool spread = omp_get_max_threads() > 1 && static_cast<int64_t>(nj) * nf >= 4 && static_cast<int64_t>(nj) * ds_->num_total_bin >= 1024;
+  const int tasks = nj * nf;
+#pragma omp parallel for schedule(dynamic, 1) num_threads(omp_get_max_threads()) if (spread)
+  for (int t = 0; t < tasks; ++t) {
+    const int j = t / nf, f = t % nf;
+    SplitRecord* rec = &per[static_cast<size_t>(t)];
+    InitSplitRecord(rec);
+    if (!active[j] || !masks[j][f] || !FeatureOwned(f)) continue;
+    const LeafState& leaf = leaves_[ids[j]];
+    if (ds_->feature_meta[f].bin_type == static_cast<int>(BinType::Numerical)) ScanNumerical(leaf, f, Ls[j], rec);
+    else ScanCategorical(leaf, f, Ls[j], rec);
+  }
+  for (int j = 0; j < nj; ++j) if (active[j]) FinishLeafScan(&leaves_[ids[j]], Ls[j], &per[static_cast<size_t>(j) * nf]);
+}
+
+void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index) {
+  ScopedTimer timer("CPUTreeLearner::FindBestSplit");
+  LeafScanInfo L; std::vector<int8_t> mask;
+  if (!PrepareLeafScan(leaf, leaf_id, tree_index, &L, &mask)) return;
 
   if (parallel_voting_) {
     // PV-Tree: local top-k by local gain, global vote, reduce only the voted features.
@@ -739,32 +794,18 @@ void CPUTreeLearner::FindBestSplit(LeafState* leaf, int leaf_id, int tree_index)
     return;
   }
 
-  SplitRecord best; InitSplitRecord(&best);
-  {
-    // one record per feature on the worker threads, merged in feature order (SplitBetter is a total order, so the
-    // result does not depend on the thread count)
-    std::vector<SplitRecord> per(ds_->num_features);
-    // the whole team or the calling thread alone (a region with a smaller team than the last makes the runtime end and
-    // later restart its workers)
-    const bool spread = omp_get_max_threads() > 1 && ds_->num_features >= 4 && ds_->num_total_bin >= 1024;
+  // one record per feature on the worker threads: the whole team or the calling thread alone (a region with a smaller
+  // team than the last makes the runtime end and later restart its workers)
+  std::vector<SplitRecord> per(ds_->num_features);
+  const bool spread = omp_get_max_threads() > 1 && ds_->num_features >= 4 && ds_->num_total_bin >= 1024;
 #pragma omp parallel for schedule(dynamic, 1) num_threads(omp_get_max_threads()) if (spread)
-    for (int f = 0; f < ds_->num_features; ++f) {
-      InitSplitRecord(&per[f]);
-      if (!mask[f] || !FeatureOwned(f)) continue;
-      if (ds_->feature_meta[f].bin_type == static_cast<int>(BinType::Numerical)) ScanNumerical(*leaf, f, L, &per[f]);
-      else ScanCategorical(*leaf, f, L, &per[f]);
-    }
-    for (int f = 0; f < ds_->num_features; ++f) {
-      SplitRecord& r = per[f];
-      if (r.feature < 0) continue;
-      if (!cegb_coupled_.empty() || !cegb_lazy_.empty()) { r.gain -= CegbFeaturePenalty(f, *leaf); if (!(r.gain > 0.0)) continue; }
-      if (SplitBetter(r.gain, ds_->feature_meta[r.feature].real_index, r.threshold, best.gain, best.feature >= 0 ? ds_->feature_meta[best.feature].real_index : -1, best.threshold)) best = r;
-    }
+  for (int f = 0; f < ds_->num_features; ++f) {
+    InitSplitRecord(&per[f]);
+    if (!mask[f] || !FeatureOwned(f)) continue;
+    if (ds_->feature_meta[f].bin_type == static_cast<int>(BinType::Numerical)) ScanNumerical(*leaf, f, L, &per[f]);
+    else ScanCategorical(*leaf, f, L, &per[f]);
   }
-  // Parity: src/treelearner/cost_effective_gradient_boosting.hpp (DeltaGain: tradeoff * penalty_split * rows of the leaf)
-  if (best.feature >= 0 && sp_.cegb_split > 0.0) best.gain -= sp_.cegb_split * static_cast<double>(L.num_data);
-  SyncBestSplit(&best);
-  leaf->best = best;
+  FinishLeafScan(leaf, L, per.data());
 }
 
 int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
@@ -781,14 +822,30 @@ int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
   data_size_t* idx = indices_.data() + P.begin;
   int nl = 0, nr = 0;
   const int nan_bin = m.num_bin - 1;
-  for (int k = 0; k < P.count; ++k) {
-    const data_size_t i = idx[k];
-    const int fbin = ds_->FeatureBin(i, s.feature);
-    bool left;
-    if (s.is_categorical) left = (s.cat_bitset[fbin >> 5] >> (fbin & 31)) & 1;
-    else if ((m.missing_type == 1 && fbin == m.default_bin) || (m.missing_type == 2 && fbin == nan_bin)) left = s.default_left != 0;
-    else left = fbin <= s.threshold;
-    if (left) idx[nl++] = i; else tmp_[nr++] = i;
+  if (!s.is_categorical && !m.bundled && ds_->bin_bytes == 1) {
+    // the usual case, without a branch per row: both destinations are written and only one cursor moves (idx[nl] never
+    // runs ahead of the row being read)
+    const uint8_t* col = ds_->bins8.data() + m.group; const size_t stride = static_cast<size_t>(ds_->row_stride);
+    const int miss_bin = m.missing_type == 1 ? m.default_bin : (m.missing_type == 2 ? nan_bin : -1);
+    const int thr = s.threshold; const int miss_left = s.default_left != 0 ? 1 : 0;
+    data_size_t* right_out = tmp_.data();
+    for (int k = 0; k < P.count; ++k) {
+      const data_size_t i = idx[k];
+      const int fbin = col[static_cast<size_t>(i) * stride];
+      const int left = fbin == miss_bin ? miss_left : (fbin <= thr ? 1 : 0);
+      idx[nl] = i; right_out[nr] = i;
+      nl += left; nr += 1 - left;
+    }
+  } else {
+    for (int k = 0; k < P.count; ++k) {
+      const data_size_t i = idx[k];
+      const int fbin = ds_->FeatureBin(i, s.feature);
+      bool left;
+      if (s.is_categorical) left = (s.cat_bitset[fbin >> 5] >> (fbin & 31)) & 1;
+      else if ((m.missing_type == 1 && fbin == m.default_bin) || (m.missing_type == 2 && fbin == nan_bin)) left = s.default_left != 0;
+      else left = fbin <= s.threshold;
+      if (left) idx[nl++] = i; else tmp_[nr++] = i;
+    }
   }
   std::copy(tmp_.begin(), tmp_.begin() + nr, idx + nl);
   int64_t cnts[2] = {nl, nr};
@@ -818,6 +875,7 @@ int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
   parent_copy.hist.swap(Lf.hist); parent_copy.hist_i.swap(Lf.hist_i);
   LeafState& R = leaves_[right_id];
   R = LeafState();
+  R.id = right_id; Lf.id = leaf_id;
   R.begin = Lf.begin + nl; R.count = nr; Lf.count = nl;
   R.depth = Lf.depth + 1; Lf.depth += 1;
   { const int rf = ds_->feature_meta[s.feature].real_index; if (std::find(Lf.path.begin(), Lf.path.end(), rf) == Lf.path.end()) Lf.path.push_back(rf); R.path = Lf.path; }
@@ -843,7 +901,7 @@ int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
   LeafState* larger = gl <= gr ? &R : &Lf;
   const bool parent_kept = quant_ ? !parent_copy.hist_i.empty() : !parent_copy.hist.empty();
   ConstructHistogram(smaller);
-  if (parent_kept) SubtractHistogram(parent_copy, *smaller, larger);
+  if (parent_kept) SubtractHistogram(&parent_copy, *smaller, larger);
   else ConstructHistogram(larger);   // the pool dropped the parent's histogram: no subtraction to be had
   TouchHistogram(smaller); TouchHistogram(larger);
   if (hist_pool_cap_ > 0) EnforceHistogramPool(tree->num_leaves, leaf_id, right_id);
@@ -973,8 +1031,7 @@ Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_i
       if (best_leaf < 0) break;
       int right = ApplySplit(tree.get(), best_leaf);
       const std::vector<int> dirty = mono_dirty_;   // leaves whose monotone range the split tightened
-      FindBestSplit(&leaves_[best_leaf], best_leaf, tree_index);
-      FindBestSplit(&leaves_[right], right, tree_index);
+      FindBestSplitMany({best_leaf, right}, tree_index);
       for (int d : dirty) FindBestSplit(&leaves_[d], d, tree_index);
     }
   } else {
@@ -1001,7 +1058,7 @@ Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_i
         int r = ApplySplit(tree.get(), l); next.push_back(l); next.push_back(r);
         for (int d : mono_dirty_) if (d < static_cast<int>(stale.size())) stale[d] = 1;
       }
-      for (int l : next) FindBestSplit(&leaves_[l], l, tree_index);
+      FindBestSplitMany(next, tree_index);
       frontier.swap(next);
     }
   }
