@@ -42,8 +42,12 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
     class_need_train_.assign(num_tree_per_iteration_, true);
     if (obj != nullptr) for (int k = 0; k < num_tree_per_iteration_; ++k) class_need_train_[k] = obj->ClassNeedTrain(k);
     init_scores_.assign(num_tree_per_iteration_, 0.0);
-    if (cfg.linear_tree && is_cuda_) {
-      Log::Warning("linear_tree trains on the host (the leaf regressions need the raw feature values)");
+    // Linear trees on a device booster: the trees grow on the device, the leaf regressions are solved on the host from the
+    // raw values the Dataset keeps, and the scores take the difference by row. One GPU, no row sampling (the host does
+    // not see the device's bags), host-resident bins and raw values; everything else trains on the host learner.
+    const bool sampled_rows = cfg.data_sample_strategy == "goss" || (cfg.bagging_freq > 0 && (cfg.bagging_fraction < 1.0 || cfg.pos_bagging_fraction < 1.0 || cfg.neg_bagging_fraction < 1.0));
+    if (cfg.linear_tree && is_cuda_ && (Network::active() || sampled_rows || is_dart_ || is_rf_ || !train->has_raw() || !train->has_host_bins())) {
+      Log::Warning("linear_tree with several ranks, row sampling, dart or rf (or without host-resident raw values and bins) trains on the host learner");
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
     if (is_cuda_ && train->max_group_bin > 256) {
@@ -269,6 +273,37 @@ void GBDT::FitLinearLeaves(Tree* tree, const float* grad, const float* hess, boo
   }
 }
 
+// Linear leaves for trees that the device engine has just grown (and already added to its scores with constant leaves):
+// the round's gradients come down, the regressions are solved on the host as for a host-grown tree, and every data set's
+// scores take (linear tree - constant tree) by row. The first round's trees stay constant, as on the host.
+void GBDT::FitLinearLeavesOnDeviceTrees(std::vector<std::unique_ptr<Tree>>* trees) {
+  const int K = num_tree_per_iteration_;
+  const data_size_t n = train_->num_data;
+  const bool first_round = models_.size() < static_cast<size_t>(K);
+  std::vector<float> hg, hh, delta;
+  for (int k = 0; k < K && k < static_cast<int>(trees->size()); ++k) {
+    Tree* tree = (*trees)[k].get();
+    if (tree->num_leaves <= 1) continue;               // a constant tree stays a plain tree, as on the host
+    if (first_round) { FitLinearLeaves(tree, nullptr, nullptr, true); continue; }
+    const Tree constant = *tree;                       // what the device scores hold for this tree
+    hg.resize(n); hh.resize(n);
+    engine_->DownloadGradients(k, hg.data(), hh.data());
+    tree->Shrink(1.0 / shrinkage_rate_);               // the regressions are solved on the unshrunk outputs
+    FitLinearLeaves(tree, hg.data(), hh.data(), false);
+    tree->Shrink(shrinkage_rate_);
+    auto push_difference = [&](const Dataset* ds, int data_idx) {
+      if (!ds->has_host_bins() || !ds->has_raw()) Log::Fatal("linear_tree on a device booster needs host-resident bins and raw values in every data set (build them from host data with linear_tree=true)");
+      std::vector<double> d(static_cast<size_t>(ds->num_data), 0.0);
+      AddTreeScore(tree, ds, d.data(), 1.0);
+      AddTreeScore(&constant, ds, d.data(), -1.0);
+      delta.assign(d.begin(), d.end());
+      engine_->AddRowValuesToScores(data_idx, k, delta.data());
+    };
+    push_difference(train_, 0);
+    for (size_t v = 0; v < valid_.size(); ++v) push_difference(valid_[v], static_cast<int>(v) + 1);
+  }
+}
+
 void GBDT::BoostFromAverage(int k, double* out) {
   *out = 0.0;
   if (models_.empty() && !boosted_from_average_ && objective_ != nullptr && config_.boost_from_average && train_->metadata.init_score.empty()) {
@@ -461,6 +496,7 @@ bool GBDT::TrainOneIter(const float* grad_in, const float* hess_in) {
       if (models_.empty()) for (auto& t : trees) models_.push_back(std::move(t));
       return true;
     }
+    if (config_.linear_tree) FitLinearLeavesOnDeviceTrees(&trees);
     for (auto& t : trees) { if (DebugFlags::Get().dump) DumpTree(*t, models_.size()); models_.push_back(std::move(t)); }
     if (is_dart_) DartNormalize();
     ++iter_;

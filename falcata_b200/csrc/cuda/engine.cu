@@ -440,6 +440,24 @@ void CudaEngine::UploadGradients(const float* host_grad, const float* host_hess,
   *dev_grad = fixed_grad_.get(); *dev_hess = fixed_hess_.get();
 }
 
+void CudaEngine::DownloadGradients(int class_id, float* host_grad, float* host_hess) {
+  if (round_grad_ == nullptr || class_id < 0 || class_id >= K_) Log::Fatal("No gradients of class %d to copy: no round has been trained yet", class_id);
+  FB_CUDA(cudaMemcpyAsync(host_grad, round_grad_ + static_cast<size_t>(class_id) * n_, sizeof(float) * n_, cudaMemcpyDeviceToHost, stream_));
+  FB_CUDA(cudaMemcpyAsync(host_hess, round_hess_ + static_cast<size_t>(class_id) * n_, sizeof(float) * n_, cudaMemcpyDeviceToHost, stream_));
+  FB_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void CudaEngine::AddRowValuesToScores(int data_idx, int class_id, const float* host_values) {
+  if (data_idx < 0 || data_idx > static_cast<int>(valid_.size()) || class_id < 0 || class_id >= K_) Log::Fatal("AddRowValuesToScores: data set %d / class %d does not exist", data_idx, class_id);
+  const int rows = data_idx == 0 ? n_ : valid_[data_idx - 1].ds->num_data;
+  float* score = (data_idx == 0 ? score_.get() : valid_[data_idx - 1].score.get()) + static_cast<size_t>(class_id) * rows;
+  if (rows <= 0) return;
+  row_values_.Alloc(static_cast<size_t>(rows));
+  FB_CUDA(cudaMemcpyAsync(row_values_.get(), host_values, sizeof(float) * rows, cudaMemcpyHostToDevice, stream_));
+  LaunchAddVector(score, row_values_.get(), rows, stream_);
+  FB_CUDA(cudaStreamSynchronize(stream_));   // the source is the caller's host buffer
+}
+
 void CudaEngine::ScaleScores(double a, const std::vector<double>& b) {
   for (int k = 0; k < K_; ++k) {
     const float bk = k < static_cast<int>(b.size()) ? static_cast<float>(b[k]) : 0.f;

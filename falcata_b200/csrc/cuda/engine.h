@@ -41,6 +41,8 @@ class CudaEngine : public DeviceEngine {
   void AddValid(const Dataset* valid) override;
   void AddConstantToScores(double v, int class_id) override;
   void ScaleScores(double a, const std::vector<double>& b) override;
+  void DownloadGradients(int class_id, float* host_grad, float* host_hess) override;
+  void AddRowValuesToScores(int data_idx, int class_id, const float* host_values) override;
   void UploadGradients(const float* host_grad, const float* host_hess, const float** dev_grad, const float** dev_hess) override;
   void TrainOneIter(const float* custom_grad, const float* custom_hess, int iter, double shrinkage, const std::vector<double>& init_scores,
                     std::vector<std::unique_ptr<Tree>>* out, bool* all_constant) override;
@@ -142,6 +144,8 @@ class CudaEngine : public DeviceEngine {
   // traversal staging
   DevBuf<int> tree_ints_; DevBuf<float> tree_floats_; DevBuf<signed char> tree_dec_;
   const float* cur_grad_ = nullptr; const float* cur_hess_ = nullptr;
+  const float* round_grad_ = nullptr; const float* round_hess_ = nullptr;   // this round's gradients of all class trees ([class][row], device)
+  DevBuf<float> row_values_;
   int lane_mode_ = 0, lane_bins_ = 64, sub_rows_ = 1 << 30;
   // compact per-tree view of the sampled feature groups
   DevBuf<uint8_t> compact_rows_; DevBuf<int> compact_groups_, compact_start_, compact_count_;

@@ -91,6 +91,7 @@ void CudaEngine::TrainOneIter(const float* custom_grad, const float* custom_hess
   if (data_parallel() && quant_) fabric_->AllReduce(kFabricMaxF32, maxbuf_.get(), global_max_.get(), 2 * K_, stream_);
   clock_.End(stream_);
   bool any_split = false;
+  round_grad_ = grad; round_hess_ = hess;
   for (int k = 0; k < K_; ++k) {
     std::unique_ptr<Tree> tree;
     const bool need = obj_ == nullptr || obj_->ClassNeedTrain(k);

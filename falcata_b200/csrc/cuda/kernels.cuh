@@ -312,6 +312,7 @@ void LaunchAddLeafOutputsFromRecords(const LeafInfo* leaves, const LevelCtrl* ct
                                      cudaStream_t s, bool decided_ahead = false);
 void LaunchAddConstant(float* score, int n, float v, cudaStream_t s);
 void LaunchScaleAdd(float* score, int n, float a, float b, cudaStream_t s);
+void LaunchAddVector(float* score, const float* values, int n, cudaStream_t s);
 // per-leaf (sum g, sum h) of float gradients over the leaf windows: partial[2 * (leaf * slices + slice) + {0,1}]
 int LeafGradSumSlices();
 void LaunchLeafGradSums(const LeafInfo* leaves, int num_leaves, const int* idx0, const int* idx1, const float* grad, const float* hess, double* partial, cudaStream_t s);

@@ -233,6 +233,12 @@ void LaunchScaleAdd(float* score, int n, float a, float b, cudaStream_t s) {
   ScaleAddKernel<<<(n + 255) / 256, 256, 0, s>>>(score, n, a, b);
   FB_LAUNCHED(); FB_KERNEL_CHECK();
 }
+__global__ void AddVectorKernel(float* score, const float* __restrict__ values, int n) { const int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < n) score[i] += values[i]; }
+void LaunchAddVector(float* score, const float* values, int n, cudaStream_t s) {
+  if (n <= 0) return;
+  AddVectorKernel<<<(n + 255) / 256, 256, 0, s>>>(score, values, n);
+  FB_LAUNCHED(); FB_KERNEL_CHECK();
+}
 void LaunchAddConstant(float* score, int n, float v, cudaStream_t s) {
   if (n <= 0) return;
   AddConstantKernel<<<(n + 255) / 256, 256, 0, s>>>(score, n, v);

@@ -25,6 +25,10 @@ class DeviceEngine {
   // Copies host gradients (n * trees-per-round values each) into device buffers owned by the engine and returns the device
   // pointers, which TrainOneIter takes as its custom gradients (it reads device memory only).
   virtual void UploadGradients(const float* host_grad, const float* host_hess, const float** dev_grad, const float** dev_hess) = 0;
+  // This round's gradients of one class tree (as the trees were trained on them), copied to the host.
+  virtual void DownloadGradients(int class_id, float* host_grad, float* host_hess) = 0;
+  // score[class][row] += host_values[row] on data set data_idx (0 = training, v + 1 = validation set v)
+  virtual void AddRowValuesToScores(int data_idx, int class_id, const float* host_values) = 0;
   // score = a * score + b[class] on the training and every validation set (random forests keep running means)
   virtual void ScaleScores(double a, const std::vector<double>& b) = 0;
   // Computes gradients on the device (or takes custom device gradients), grows one tree per
@@ -148,6 +152,7 @@ class GBDT {
   std::vector<bool> class_need_train_;
   bool boosted_from_average_ = false;
   double first_grad_norm_ = -1;
+  void FitLinearLeavesOnDeviceTrees(std::vector<std::unique_ptr<Tree>>* trees);
   std::vector<double> rf_init_scores_;
   const float* rf_dev_grad_ = nullptr; const float* rf_dev_hess_ = nullptr;   // device copies of the forest's fixed gradients (owned by the engine)
 };

@@ -718,3 +718,37 @@ def test_random_forest_on_the_device_engine_follows_the_host_learner():
     ll = float(-np.mean(yv * np.log(np.clip(pd_, 1e-15, 1)) + (1 - yv) * np.log(np.clip(1 - pd_, 1e-15, 1))))
     assert abs(rec["v"]["binary_logloss"][-1] - ll) < 2e-4
     assert auc(yv, pd_) > 0.8
+
+
+def test_linear_trees_on_a_device_booster_follow_the_host_learner():
+    """linear_tree with device_type=cuda (one GPU, no row sampling): the trees grow on the device, the leaf regressions
+    are solved on the host from the raw values and the device scores take the difference by row. With integer
+    histograms the trees are the host learner's, so the predictions agree closely; the recorded validation loss is the
+    loss of the final model's predictions (the device scores followed every linear correction)."""
+    rng = np.random.default_rng(0)
+    n = 8000
+
+    def target(A):
+        return np.where(A[:, 0] > 0, 2 * A[:, 1] + 1, -3 * A[:, 2]).astype(np.float32)
+
+    X = rng.normal(size=(n, 5)).astype(np.float32)
+    y = target(X) + 0.05 * rng.normal(size=n).astype(np.float32)
+    Xv = rng.normal(size=(2000, 5)).astype(np.float32)
+    Xv[::50, 1] = np.nan
+    yv = target(np.nan_to_num(Xv))
+    out = {}
+    for dev in ("cpu", "cuda"):
+        p = {"objective": "regression", "num_leaves": 8, "learning_rate": 0.2, "linear_tree": True, "linear_lambda": 0.01, "verbose": -1, "min_data_in_leaf": 20,
+             "device_type": dev, "quant_mode": "fixedpoint", "quant_bins": 64, "max_bin": 63}
+        ds = fb.Dataset(X, y, params=p)
+        dv = fb.Dataset(Xv, yv, reference=ds)
+        ev = {}
+        b = fb.train(p, ds, 20, valid_sets=[dv], valid_names=["v"], callbacks=[fb.record_evaluation(ev)])
+        pr = b.predict(Xv)
+        out[dev] = (pr, ev["v"]["l2"][-1], b)
+        assert "is_linear=1" in b.model_to_string()
+    assert abs(out["cuda"][1] - float(np.mean((out["cuda"][0] - yv) ** 2))) < 1e-4
+    assert np.max(np.abs(out["cuda"][0] - out["cpu"][0])) < 5e-3
+    constant = fb.train({"objective": "regression", "num_leaves": 8, "learning_rate": 0.2, "verbose": -1, "min_data_in_leaf": 20, "device_type": "cuda", "max_bin": 63},
+                        fb.Dataset(X, y), 20)
+    assert float(np.mean((out["cuda"][0] - yv) ** 2)) < 0.5 * float(np.mean((constant.predict(Xv) - yv) ** 2))
