@@ -65,8 +65,23 @@ EvalNames GetEvalNames(BoosterHandle h) {
   return e;
 }
 
-int TaskTrain(const Config& cfg, const std::string& params) {
+int TaskTrain(const Config& cfg, const std::string& params_in) {
   if (cfg.data.empty()) Log::Fatal("No training data: set data=<file>");
+  std::string params = params_in;
+  if (cfg.num_machines > 1) {
+    // distributed training on CPUs: one process per machine list entry, collectives over TCP; every process loads its own
+    // rows (pre_partition=true: its own file; else its block of the shared file) and writes its own copy of the model
+    std::string machines = cfg.machines;
+    if (machines.empty() && !cfg.machine_list_filename.empty()) {
+      std::ifstream f(cfg.machine_list_filename);
+      if (!f) Log::Fatal("Cannot open machine list file %s", cfg.machine_list_filename.c_str());
+      std::stringstream ss; ss << f.rdbuf(); machines = ss.str();
+    }
+    if (machines.empty()) Log::Fatal("num_machines=%d needs machines=host:port,... or machine_list_filename", cfg.num_machines);
+    Check(FB_NetworkInit(machines.c_str(), cfg.local_listen_port, cfg.time_out, cfg.num_machines));
+    params += " device_type=cpu";
+    if (cfg.tree_learner == "serial") { Log::Warning("num_machines > 1 with tree_learner=serial: using tree_learner=data"); params += " tree_learner=data"; }
+  }
   DatasetHandle train = nullptr; Check(FB_DatasetCreateFromFile(cfg.data.c_str(), params.c_str(), nullptr, &train));
   std::vector<DatasetHandle> valids; std::vector<std::string> valid_names;
   for (auto& v : SplitAny(cfg.valid, ",")) { const std::string p = Trim(v); if (p.empty()) continue; DatasetHandle d = nullptr; Check(FB_DatasetCreateFromFile(p.c_str(), params.c_str(), train, &d)); valids.push_back(d); valid_names.push_back(p); }

@@ -86,7 +86,12 @@ int FB_NetworkInitWithFunctions(int num_machines, int rank, void* allreduce_sum_
   Network::allgather() = reinterpret_cast<Network::AllgatherFn>(allgather_fn);
   API_END();
 }
-int FB_NetworkFree() { API_BEGIN(); Network::world() = 1; Network::rank() = 0; Network::allreduce() = nullptr; Network::allgather() = nullptr; API_END(); }
+int FB_NetworkInit(const char* machines, int local_listen_port, int listen_time_out, int num_machines) {
+  API_BEGIN();
+  if (num_machines > 1) SocketNetworkInit(machines != nullptr ? machines : "", local_listen_port, listen_time_out, num_machines);
+  API_END();
+}
+int FB_NetworkFree() { API_BEGIN(); SocketNetworkFree(); Network::world() = 1; Network::rank() = 0; Network::allreduce() = nullptr; Network::allgather() = nullptr; API_END(); }
 
 // ------------------------------------------------------------- Dataset ----
 int FB_DatasetCreateFromMat(const void* data, int dtype, int32_t nrow, int32_t ncol, int is_row_major, const char* parameters,

@@ -3,6 +3,7 @@
 // Parity: src/io/parser.cpp (format detection), src/io/dataset_loader.cpp:L216 (LoadFromFile),
 // src/io/metadata.cpp (side files).
 #include "fb/dataset.h"
+#include "fb/learner.h"
 
 #include <fstream>
 
@@ -102,17 +103,61 @@ Dataset* LoadDatasetFromFile(const std::string& path, const Config& cfg, const D
   std::vector<double>& dense = pf.dense; std::vector<float>& label = pf.label; std::vector<float>& weight = pf.weight; std::vector<double>& groupv = pf.group_ids;
   std::vector<std::string>& names = pf.names;
   std::unique_ptr<Dataset> ds(new Dataset());
+  // Several processes over the TCP mesh (the command line's distributed mode), training data only: with pre_partition
+  // every process has read its own rows and the bin sample is the concatenation of every process's sample in rank order;
+  // without it every process has read the whole file, draws the same sample and keeps its block of consecutive rows. Either
+  // way all processes find the same bin boundaries, and the rows carry their global numbers.
+  const bool distributed = reference == nullptr && SocketNetworkActive() && Network::active();
+  data_size_t keep_begin = 0, keep_end = n; int64_t global_offset = 0, global_total = n;
+  if (distributed) {
+    if (!groupv.empty() && !cfg.pre_partition) Log::Fatal("Distributed ranking data must be pre-partitioned by query (pre_partition=true, one file per machine)");
+    const int W = Network::world(), R = Network::rank();
+    if (cfg.pre_partition) {
+      int64_t mine = n; std::vector<char> raw; Network::Gather(&mine, sizeof(mine), &raw);
+      const int64_t* counts = reinterpret_cast<const int64_t*>(raw.data());
+      global_total = 0; for (int r = 0; r < W; ++r) { if (r == R) global_offset = global_total; global_total += counts[r]; }
+    } else {
+      keep_begin = static_cast<data_size_t>(static_cast<int64_t>(n) * R / W); keep_end = static_cast<data_size_t>(static_cast<int64_t>(n) * (R + 1) / W);
+      global_offset = keep_begin; global_total = n;
+    }
+  }
   if (reference != nullptr) ds->CopySchemaFrom(*reference);
   else {
     Random rnd(cfg.data_random_seed);
-    auto idx = rnd.Sample(n, std::min<int>(n, cfg.bin_construct_sample_cnt));
+    int want = std::min<int>(n, cfg.bin_construct_sample_cnt);
+    if (distributed && cfg.pre_partition) want = static_cast<int>(std::min<int64_t>(n, (static_cast<int64_t>(cfg.bin_construct_sample_cnt) * n + global_total - 1) / std::max<int64_t>(1, global_total)));
+    auto idx = rnd.Sample(n, want);
     std::vector<double> sample(idx.size() * static_cast<size_t>(nfeat));
     for (size_t r = 0; r < idx.size(); ++r) memcpy(&sample[r * nfeat], &dense[static_cast<size_t>(idx[r]) * nfeat], nfeat * sizeof(double));
+    if (distributed && cfg.pre_partition) {
+      // all-gather of the samples: sizes first, then the rows padded to the largest
+      const int W = Network::world();
+      int64_t info[2] = {static_cast<int64_t>(idx.size()), nfeat}; std::vector<char> raw; Network::Gather(info, sizeof(info), &raw);
+      const int64_t* all = reinterpret_cast<const int64_t*>(raw.data());
+      int64_t cap = 1; for (int r = 0; r < W; ++r) { cap = std::max(cap, all[2 * r]); if (all[2 * r + 1] != nfeat) Log::Fatal("The machines' data files have different numbers of columns (%lld against %d)", static_cast<long long>(all[2 * r + 1]), nfeat); }
+      std::vector<double> padded(static_cast<size_t>(cap) * nfeat, 0.0); std::copy(sample.begin(), sample.end(), padded.begin());
+      std::vector<char> gathered; Network::Gather(padded.data(), static_cast<int64_t>(padded.size() * sizeof(double)), &gathered);
+      std::vector<double> merged;
+      for (int r = 0; r < W; ++r) { const double* p = reinterpret_cast<const double*>(gathered.data()) + static_cast<size_t>(r) * cap * nfeat; merged.insert(merged.end(), p, p + static_cast<size_t>(all[2 * r]) * nfeat); }
+      sample.swap(merged);
+      idx.resize(sample.size() / std::max(1, nfeat));
+    }
     std::vector<int> cats;
     for (auto& t : SplitAny(cfg.categorical_feature, ",")) { std::string s = Trim(t); if (StartsWith(s, "name:")) { for (size_t k = 0; k < names.size(); ++k) if (names[k] == s.substr(5)) cats.push_back(static_cast<int>(k)); } else if (!s.empty()) cats.push_back(atoi(s.c_str())); }
     if (pf.has_header) ds->feature_names = names;
-    ds->ConstructSchema(sample.data(), static_cast<int>(idx.size()), nfeat, n, cfg, cats);
+    ds->ConstructSchema(sample.data(), static_cast<int>(idx.size()), nfeat, distributed ? global_total : n, cfg, cats);
   }
+  if (distributed && (keep_begin != 0 || keep_end != n)) {
+    // this process's block of the shared file
+    const data_size_t m = keep_end - keep_begin;
+    ds->global_num_data = global_total; ds->global_row_offset = global_offset;
+    ds->AllocateRows(m);
+    ds->PushDense(dense.data() + static_cast<size_t>(keep_begin) * nfeat, kF64, m, nfeat, true, 0);
+    ds->metadata.label.assign(label.begin() + keep_begin, label.begin() + keep_end);
+    if (!weight.empty()) ds->metadata.SetWeights(weight.data() + keep_begin, m);
+    return ds.release();
+  }
+  if (distributed) { ds->global_num_data = global_total; ds->global_row_offset = global_offset; }
   ds->AllocateRows(n);
   ds->PushDense(dense.data(), kF64, n, nfeat, true, 0);
   ds->metadata.label = label;

@@ -26,6 +26,9 @@ int FB_GetNumThreads(int* out);
 int FB_GetTimeTagReport(int64_t buffer_len, int64_t* out_len, char* out_str);
 
 /* Host collectives supplied by the embedding process (torch.distributed in the Python layer). */
+/* Host collectives over TCP: `machines` = "host:port,host:port,..." (or "host port" lines), this process is the entry that is
+   local and listens on local_listen_port; listen_time_out in minutes. */
+int FB_NetworkInit(const char* machines, int local_listen_port, int listen_time_out, int num_machines);
 int FB_NetworkInitWithFunctions(int num_machines, int rank, void* allreduce_sum_fn, void* allgather_fn);
 int FB_NetworkFree();
 

@@ -309,7 +309,7 @@ FB_COMPAT_BOTH(int, BoosterPredictForArrow, (BoosterHandle handle, int64_t n_chu
 
 /* ---- no counterpart: these fail with a message ---- */
 FB_COMPAT_BOTH(int, NetworkInit, (const char* machines, int local_listen_port, int listen_time_out, int num_machines),
-               ((void)machines, (void)local_listen_port, (void)listen_time_out, (void)num_machines, fb_compat_unsupported("socket networking is not built: ranks are torch.distributed processes (or use NetworkInitWithFunctions)")))
+               FB_NetworkInit(machines, local_listen_port, listen_time_out, num_machines))
 FB_COMPAT_BOTH(int, DatasetAddFeaturesFrom, (DatasetHandle target, DatasetHandle source), ((void)target, (void)source, fb_compat_unsupported("DatasetAddFeaturesFrom is not available")))
 FB_COMPAT_BOTH(int, DatasetSerializeReferenceToBinary, (DatasetHandle handle, ByteBufferHandle* out, int32_t* out_len), ((void)handle, (void)out, (void)out_len, fb_compat_unsupported("serialized dataset references are not available: save the dataset with DatasetSaveBinary")))
 FB_COMPAT_BOTH(int, DatasetCreateFromSerializedReference, (const void* ref_buffer, int32_t ref_buffer_size, int64_t num_row, int32_t num_classes, const char* parameters, DatasetHandle* out),

@@ -37,6 +37,12 @@ struct Network {
   }
 };
 
+// TCP mesh between processes (core/socket_network.cpp): the command line's distributed mode and FB_NetworkInit
+void SocketNetworkInit(const std::string& machines, int local_listen_port, int timeout_minutes, int num_machines);
+void SocketNetworkFree();
+bool SocketNetworkActive();
+std::string ReadMachineListFile(const std::string& path);
+
 // Counter-based per-tree / per-node feature sampling (resumable: depends only on seed and ids).
 class ColSampler {
  public:

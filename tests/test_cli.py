@@ -57,3 +57,73 @@ def test_native_core_unit_tests_pass():
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
     assert " 0 failed" in r.stdout
+
+
+def _free_ports(k):
+    import socket
+
+    socks = [socket.socket() for _ in range(k)]
+    for s in socks:
+        s.bind(("127.0.0.1", 0))
+    ports = [s.getsockname()[1] for s in socks]
+    for s in socks:
+        s.close()
+    return ports
+
+
+def test_cli_distributed_training_over_tcp(tmp_path):
+    """The command line's distributed mode (reference: tests/distributed/_test_distributed.py): one process per machine list
+    entry on 127.0.0.1, collectives over TCP, pre-partitioned data files, tree_learner=data. With integer histograms the
+    processes write the model that a single process trains on the whole file, digit for digit; a shared file that every
+    process splits by itself (pre_partition=false) gives the same model again; three processes with the voting learner
+    agree with one another."""
+    from util import model_body
+
+    rng = np.random.RandomState(3)
+    n = 6000
+    X = rng.randn(n, 8); y = (X[:, 0] + X[:, 1] * X[:, 2] + 0.3 * rng.randn(n) > 0).astype(int)
+    full = np.column_stack([y, X])
+    np.savetxt(tmp_path / "train.txt", full, delimiter="\t", fmt="%.17g")
+    common = ("task = train\nobjective = binary\nnum_trees = 8\nnum_leaves = 15\nmin_data_in_leaf = 20\nmax_bin = 63\nquant_mode = fixedpoint\nquant_bins = 64\n"
+              "verbosity = 1\nnum_threads = 2\n")
+    (tmp_path / "single.conf").write_text(common + "data = train.txt\noutput_model = single.txt\ndevice_type = cpu\n")
+    _run(tmp_path, "config=single.conf")
+    single = (tmp_path / "single.txt").read_text()
+
+    def launch(world, extra, files, tag):
+        ports = _free_ports(world)
+        (tmp_path / f"mlist_{tag}.txt").write_text("".join(f"127.0.0.1 {p}\n" for p in ports))
+        procs = []
+        for r in range(world):
+            (tmp_path / f"{tag}{r}.conf").write_text(common + extra + f"data = {files[r]}\noutput_model = {tag}{r}.txt\nlocal_listen_port = {ports[r]}\n"
+                                                     f"num_machines = {world}\nmachine_list_file = mlist_{tag}.txt\ntime_out = 1\n")
+            procs.append(subprocess.Popen([_exe(), f"config={tag}{r}.conf"], cwd=tmp_path, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+        outs = []
+        for p in procs:
+            try:
+                o, _ = p.communicate(timeout=240)
+            except subprocess.TimeoutExpired:
+                for q in procs:
+                    q.kill()
+                raise
+            outs.append(o)
+            assert p.returncode == 0, o
+        return [(tmp_path / f"{tag}{r}.txt").read_text() for r in range(world)], outs
+
+    # two pre-partitioned files
+    np.savetxt(tmp_path / "part0.txt", full[: n // 2], delimiter="\t", fmt="%.17g")
+    np.savetxt(tmp_path / "part1.txt", full[n // 2:], delimiter="\t", fmt="%.17g")
+    models, outs = launch(2, "pre_partition = true\ntree_learner = data\n", ["part0.txt", "part1.txt"], "pp")
+    assert "this is rank" in outs[0]
+    assert model_body(models[0]) == model_body(models[1]) == model_body(single)
+    # one shared file, every process keeps its block of rows
+    models, _ = launch(2, "pre_partition = false\ntree_learner = data\n", ["train.txt", "train.txt"], "sh")
+    assert model_body(models[0]) == model_body(models[1]) == model_body(single)
+    # three processes, voting
+    thirds = np.array_split(full, 3)
+    for r in range(3):
+        np.savetxt(tmp_path / f"third{r}.txt", thirds[r], delimiter="\t", fmt="%.17g")
+    models, _ = launch(3, "pre_partition = true\ntree_learner = voting\ntop_k = 4\n", [f"third{r}.txt" for r in range(3)], "vt")
+    assert model_body(models[0]) == model_body(models[1]) == model_body(models[2])
+    pr = fb.Booster(model_str=models[0]).predict(X)
+    assert float(np.mean((pr > 0.5) == y)) > 0.85
