@@ -36,6 +36,19 @@ class FalcataError(Exception):
 LightGBMError = FalcataError
 
 
+def network_init(machines: Any, local_listen_port: int = 12400, listen_time_out: int = 120, num_machines: int = 1) -> None:
+    """Open the TCP mesh between the processes of a distributed CPU training. Call it in every process BEFORE its Dataset
+    is constructed: the processes then exchange their bin samples, find the same bin boundaries and number their rows in
+    machine-list order. ``listen_time_out`` is in minutes."""
+    if isinstance(machines, (list, tuple, set)):
+        machines = ",".join(str(m) for m in machines)
+    _safe_call(_lib().FB_NetworkInit(str(machines).encode("utf-8"), ctypes.c_int(int(local_listen_port)), ctypes.c_int(int(listen_time_out)), ctypes.c_int(int(num_machines))))
+
+
+def network_free() -> None:
+    _safe_call(_lib().FB_NetworkFree())
+
+
 class FalcataDeprecationWarning(FutureWarning):
     """Deprecation notices of this package. A FutureWarning subclass: Python hides plain DeprecationWarning outside of
     ``__main__`` by default, and users should see these."""
@@ -887,6 +900,12 @@ class Booster:
             train_set.params = {**train_set.params, **{k: v for k, v in self.params.items() if k in _DATASET_PARAMS}}
             if _trains_on_host(self.params):
                 train_set.params["keep_host_bins"] = True   # the host learner will do the training: it needs host-resident bins
+            # a machine list in the parameters: join the TCP mesh before the Dataset is binned (the processes exchange their bin samples)
+            nm = self.params.get("num_machines", self.params.get("num_machine"))
+            machines = self.params.get("machines", self.params.get("workers", self.params.get("nodes")))
+            if nm is not None and int(nm) > 1 and machines:
+                self.set_network(machines, int(self.params.get("local_listen_port", self.params.get("local_port", self.params.get("port", 12400)))),
+                                 int(self.params.get("time_out", 120)), int(nm))
             with _tag("booster: dataset construct"):
                 train_set.construct()
             if str(self.params.get("cuda_plan", "")).strip().lower() == "wisdom":
@@ -1358,12 +1377,16 @@ class Booster:
             return ret
 
     def set_network(self, machines: Any, local_listen_port: int = 12400, listen_time_out: int = 120, num_machines: int = 1) -> "Booster":
-        """Socket networking of the reference is replaced by torch.distributed + the device fabric: call falcata_b200.parallel.init()."""
-        raise NotImplementedError("Distributed training is set up with torch.distributed and falcata_b200.parallel.init(), not with a machine list")
+        """Join the TCP mesh of a distributed CPU training (host learner): ``machines`` is "host:port,host:port,..." or a
+        list of such strings, this process is the local entry that listens on ``local_listen_port``. Multi-GPU training
+        does not use it: its ranks are torch.distributed processes set up by ``falcata_b200.parallel.init()``."""
+        network_init(machines, local_listen_port, listen_time_out, num_machines)
+        self._network = True
+        return self
 
     def free_network(self) -> "Booster":
-        from . import parallel
-        parallel.shutdown() if hasattr(parallel, "shutdown") else None
+        _safe_call(_lib().FB_NetworkFree())
+        self._network = False
         return self
 
     def model_from_binary(self, data: bytes) -> "Booster":

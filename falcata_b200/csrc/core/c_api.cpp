@@ -99,19 +99,25 @@ int FB_DatasetCreateFromMat(const void* data, int dtype, int32_t nrow, int32_t n
   API_BEGIN();
   Config cfg; cfg.Set(Config::Str2Map(parameters), CudaAvailable());
   std::unique_ptr<Dataset> ds(new Dataset());
+  int64_t mesh_offset = 0, mesh_total = nrow;
   if (reference != nullptr) {
     ds->CopySchemaFrom(*static_cast<const Dataset*>(reference));
   } else {
     // the bin sample: a row is in iff its Philox draw (data_random_seed, row id) is below sample_cnt / nrow - the
     // draw the device ingest makes, so a matrix gets the same bin boundaries whichever way it comes in
-    const double frac = std::min(1.0, static_cast<double>(cfg.bin_construct_sample_cnt) / std::max(1, nrow));
+    // Processes of the TCP mesh (FB_NetworkInit) each hold their own rows, numbered in rank order: every process draws
+    // the rows of the one global sample that fall into its range and the pieces are concatenated on all of them, so the
+    // bins are those of a single process holding all rows.
+    const bool distributed = SocketNetworkActive() && Network::active();
+    if (distributed) GatherRowCounts(nrow, &mesh_offset, &mesh_total);
+    const int64_t total_rows = distributed ? mesh_total : nrow;
+    const double frac = std::min(1.0, static_cast<double>(cfg.bin_construct_sample_cnt) / static_cast<double>(std::max<int64_t>(1, total_rows)));
     std::vector<int> idx(static_cast<size_t>(std::max(1, nrow)));
     int picked = 0;
-    if (FB_OpBernoulliRowsHost(nrow, 0, static_cast<unsigned int>(cfg.data_random_seed), frac, idx.data(), &picked) != 0) Log::Fatal("Row sampling failed");
+    if (FB_OpBernoulliRowsHost(nrow, distributed ? mesh_offset : 0, static_cast<unsigned int>(cfg.data_random_seed), frac, idx.data(), &picked) != 0) Log::Fatal("Row sampling failed");
     idx.resize(picked);
-    if (idx.empty() && nrow > 0) idx.push_back(0);
+    if (idx.empty() && nrow > 0 && !distributed) idx.push_back(0);
     std::vector<double> sample(static_cast<size_t>(idx.size()) * ncol);
-    Dataset tmp;   // reuse the dtype reader through a one-row push? simpler: read directly
     for (size_t r = 0; r < idx.size(); ++r) for (int j = 0; j < ncol; ++j) {
       const size_t src = is_row_major ? static_cast<size_t>(idx[r]) * ncol + j : static_cast<size_t>(j) * nrow + idx[r];
       double v;
@@ -127,7 +133,9 @@ int FB_DatasetCreateFromMat(const void* data, int dtype, int32_t nrow, int32_t n
       }
       sample[r * ncol + j] = v;
     }
-    ds->ConstructSchema(sample.data(), static_cast<int>(idx.size()), ncol, nrow, cfg, ParseCategorical(cfg, ncol));
+    if (distributed) AllGatherSampleRows(&sample, ncol);
+    ds->ConstructSchema(sample.data(), static_cast<int>(sample.size() / std::max(1, ncol)), ncol, total_rows, cfg, ParseCategorical(cfg, ncol));
+    if (distributed) { ds->global_row_offset = mesh_offset; ds->global_num_data = mesh_total; }
   }
   ds->AllocateRows(nrow);
   ds->PushDense(data, dtype, nrow, ncol, is_row_major != 0, 0);

@@ -113,9 +113,7 @@ Dataset* LoadDatasetFromFile(const std::string& path, const Config& cfg, const D
     if (!groupv.empty() && !cfg.pre_partition) Log::Fatal("Distributed ranking data must be pre-partitioned by query (pre_partition=true, one file per machine)");
     const int W = Network::world(), R = Network::rank();
     if (cfg.pre_partition) {
-      int64_t mine = n; std::vector<char> raw; Network::Gather(&mine, sizeof(mine), &raw);
-      const int64_t* counts = reinterpret_cast<const int64_t*>(raw.data());
-      global_total = 0; for (int r = 0; r < W; ++r) { if (r == R) global_offset = global_total; global_total += counts[r]; }
+      GatherRowCounts(n, &global_offset, &global_total);
     } else {
       keep_begin = static_cast<data_size_t>(static_cast<int64_t>(n) * R / W); keep_end = static_cast<data_size_t>(static_cast<int64_t>(n) * (R + 1) / W);
       global_offset = keep_begin; global_total = n;
@@ -129,19 +127,7 @@ Dataset* LoadDatasetFromFile(const std::string& path, const Config& cfg, const D
     auto idx = rnd.Sample(n, want);
     std::vector<double> sample(idx.size() * static_cast<size_t>(nfeat));
     for (size_t r = 0; r < idx.size(); ++r) memcpy(&sample[r * nfeat], &dense[static_cast<size_t>(idx[r]) * nfeat], nfeat * sizeof(double));
-    if (distributed && cfg.pre_partition) {
-      // all-gather of the samples: sizes first, then the rows padded to the largest
-      const int W = Network::world();
-      int64_t info[2] = {static_cast<int64_t>(idx.size()), nfeat}; std::vector<char> raw; Network::Gather(info, sizeof(info), &raw);
-      const int64_t* all = reinterpret_cast<const int64_t*>(raw.data());
-      int64_t cap = 1; for (int r = 0; r < W; ++r) { cap = std::max(cap, all[2 * r]); if (all[2 * r + 1] != nfeat) Log::Fatal("The machines' data files have different numbers of columns (%lld against %d)", static_cast<long long>(all[2 * r + 1]), nfeat); }
-      std::vector<double> padded(static_cast<size_t>(cap) * nfeat, 0.0); std::copy(sample.begin(), sample.end(), padded.begin());
-      std::vector<char> gathered; Network::Gather(padded.data(), static_cast<int64_t>(padded.size() * sizeof(double)), &gathered);
-      std::vector<double> merged;
-      for (int r = 0; r < W; ++r) { const double* p = reinterpret_cast<const double*>(gathered.data()) + static_cast<size_t>(r) * cap * nfeat; merged.insert(merged.end(), p, p + static_cast<size_t>(all[2 * r]) * nfeat); }
-      sample.swap(merged);
-      idx.resize(sample.size() / std::max(1, nfeat));
-    }
+    if (distributed && cfg.pre_partition) { AllGatherSampleRows(&sample, nfeat); idx.resize(sample.size() / std::max(1, nfeat)); }
     std::vector<int> cats;
     for (auto& t : SplitAny(cfg.categorical_feature, ",")) { std::string s = Trim(t); if (StartsWith(s, "name:")) { for (size_t k = 0; k < names.size(); ++k) if (names[k] == s.substr(5)) cats.push_back(static_cast<int>(k)); } else if (!s.empty()) cats.push_back(atoi(s.c_str())); }
     if (pf.has_header) ds->feature_names = names;

@@ -219,6 +219,34 @@ void SocketNetworkFree() {
   CloseMesh();
 }
 
+void GatherRowCounts(int64_t local_rows, int64_t* global_offset, int64_t* global_total) {
+  std::vector<char> raw; Network::Gather(&local_rows, sizeof(local_rows), &raw);
+  const int64_t* counts = reinterpret_cast<const int64_t*>(raw.data());
+  *global_offset = 0; *global_total = 0;
+  for (int r = 0; r < Network::world(); ++r) { if (r == Network::rank()) *global_offset = *global_total; *global_total += counts[r]; }
+}
+
+void AllGatherSampleRows(std::vector<double>* sample, int ncol) {
+  // sizes first, then the rows padded to the largest sample
+  const int W = Network::world();
+  int64_t info[2] = {static_cast<int64_t>(sample->size() / std::max(1, ncol)), ncol};
+  std::vector<char> raw; Network::Gather(info, sizeof(info), &raw);
+  const int64_t* all = reinterpret_cast<const int64_t*>(raw.data());
+  int64_t cap = 1;
+  for (int r = 0; r < W; ++r) {
+    cap = std::max(cap, all[2 * r]);
+    if (all[2 * r + 1] != ncol) Log::Fatal("The processes' data have different numbers of columns (%lld against %d)", static_cast<long long>(all[2 * r + 1]), ncol);
+  }
+  std::vector<double> padded(static_cast<size_t>(cap) * ncol, 0.0); std::copy(sample->begin(), sample->end(), padded.begin());
+  std::vector<char> gathered; Network::Gather(padded.data(), static_cast<int64_t>(padded.size() * sizeof(double)), &gathered);
+  std::vector<double> merged;
+  for (int r = 0; r < W; ++r) {
+    const double* p = reinterpret_cast<const double*>(gathered.data()) + static_cast<size_t>(r) * cap * ncol;
+    merged.insert(merged.end(), p, p + static_cast<size_t>(all[2 * r]) * ncol);
+  }
+  sample->swap(merged);
+}
+
 // The content of a machine list file ("host port" or "host:port" per line).
 std::string ReadMachineListFile(const std::string& path) {
   std::ifstream f(path);

@@ -42,6 +42,11 @@ void SocketNetworkInit(const std::string& machines, int local_listen_port, int t
 void SocketNetworkFree();
 bool SocketNetworkActive();
 std::string ReadMachineListFile(const std::string& path);
+// Helpers for data sets whose rows are spread over the processes of the mesh: this process's first global row number and
+// the total (rows are numbered in rank order), and the concatenation in rank order of every process's bin sample
+// (row-major doubles, ncol values a row), which all processes then hold alike.
+void GatherRowCounts(int64_t local_rows, int64_t* global_offset, int64_t* global_total);
+void AllGatherSampleRows(std::vector<double>* sample, int ncol);
 
 // Counter-based per-tree / per-node feature sampling (resumable: depends only on seed and ids).
 class ColSampler {

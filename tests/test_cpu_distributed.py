@@ -70,3 +70,62 @@ def test_rank_that_dies_is_detected_on_the_host():
     rc0, o0 = res[0]
     assert "KILLED_BY_TEST_TIMEOUT" not in o0, o0[-2000:]
     assert rc0 != 0 and ("TRAIN_ERROR" in o0 or "Error" in o0), o0[-2000:]
+
+
+_TCP_WORKER = r"""
+import sys, numpy as np
+sys.path.insert(0, {root!r})
+import falcata_b200 as fb
+rank, ports = int(sys.argv[1]), [int(p) for p in sys.argv[2].split(",")]
+rng = np.random.RandomState(5)
+n = 6000
+X = rng.randn(n, 8); y = (X[:, 0] + X[:, 1] * X[:, 2] + 0.3 * rng.randn(n) > 0).astype(np.float64)
+lo, hi = (0, n) if rank < 0 else (n * rank // len(ports), n * (rank + 1) // len(ports))
+p = {{"objective": "binary", "num_leaves": 15, "min_data_in_leaf": 20, "max_bin": 63, "quant_mode": "fixedpoint", "quant_bins": 64, "verbosity": -1,
+     "device_type": "cpu", "num_threads": 2}}
+if rank >= 0:
+    p.update(tree_learner="data", num_machines=len(ports), machines=",".join(f"127.0.0.1:{{q}}" for q in ports), local_listen_port=ports[rank], time_out=1)
+b = fb.train(p, fb.Dataset(X[lo:hi], y[lo:hi]), 6)
+if rank >= 0:
+    b.free_network()
+print("MODEL_BEGIN"); print(b.model_to_string().split("\nparameters:")[0]); print("MODEL_END")
+"""
+
+
+def test_python_api_trains_over_the_tcp_mesh_like_one_process(tmp_path):
+    """A machine list in the training parameters (num_machines, machines, local_listen_port) makes every process join the
+    TCP mesh before its Dataset is binned: the processes exchange their pieces of the one global bin sample and number
+    their rows in machine-list order. With integer histograms two processes holding half of the rows each train the model
+    that one process trains on all rows, digit for digit."""
+    import socket
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = str(Path(__file__).resolve().parents[1])
+    script = tmp_path / "worker.py"
+    script.write_text(_TCP_WORKER.format(root=root))
+    socks = [socket.socket() for _ in range(2)]
+    for s in socks:
+        s.bind(("127.0.0.1", 0))
+    ports = ",".join(str(s.getsockname()[1]) for s in socks)
+    for s in socks:
+        s.close()
+
+    def model_of(out):
+        return out.split("MODEL_BEGIN\n")[1].split("MODEL_END")[0]
+
+    single = subprocess.run([sys.executable, str(script), "-1", ports], capture_output=True, text=True, timeout=300)
+    assert single.returncode == 0, single.stdout + single.stderr
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), ports], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = []
+    for pr in procs:
+        try:
+            o, _ = pr.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        assert pr.returncode == 0, o
+        outs.append(o)
+    assert model_of(outs[0]) == model_of(outs[1]) == model_of(single.stdout)
