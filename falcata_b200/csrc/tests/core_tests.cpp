@@ -1,4 +1,6 @@
-// Native unit tests of the core library (plain asserts, no framework): value formatting, binning, tree text round
+// Native unit tests of the core library (plain asserts, no framework): value formatting, binning (order invariance, 32- and
+// 64-bit sort, zero and NaN bins, categorical bins, serialisation), linear leaves, candidate limits and tie order, forced-split
+// files, tree text round
 // trip, single-row prediction, counter-based random numbers, quantization, and the best-first order keys of the
 // device level controller checked against a brute-force best-first growth.
 // Parity: tests/cpp_tests/ (test_common.cpp, test_serialize.cpp, test_single_row.cpp) of the reference.
@@ -215,7 +217,114 @@ static void TestFixedPointExtras() {
   CHECK(std::fabs(MonotonePenaltyFactor(2, 0.5) - (1.0 - 0.5 / 4.0)) < 1e-9);
 }
 
+// Bin finding does not depend on the order of the sample, takes the 32-bit sort for values that are exact floats and the
+// 64-bit sort otherwise (both must order alike), keeps zero in a bin of its own and gives NaN the last bin.
+static void TestBinFindingInvariants() {
+  std::vector<double> base;
+  uint32_t s = 12345u;
+  for (int i = 0; i < 20000; ++i) { s = s * 1664525u + 1013904223u; base.push_back(static_cast<double>(static_cast<float>((static_cast<double>(s >> 8) / 16777216.0 - 0.5) * 8.0))); }
+  auto bounds_of = [](std::vector<double> v, int max_bin) {
+    BinMapper bm; bm.FindBin(v.data(), static_cast<int>(v.size()), v.size(), max_bin, 3, 20, true, BinType::Numerical, true, false, {});
+    return bm.bin_upper_bound;
+  };
+  const std::vector<double> sorted_bounds = bounds_of(base, 63);
+  std::vector<double> shuffled = base;
+  for (size_t i = shuffled.size() - 1; i > 0; --i) { s = s * 1664525u + 1013904223u; std::swap(shuffled[i], shuffled[s % (i + 1)]); }
+  CHECK(bounds_of(shuffled, 63) == sorted_bounds);
+  // the same sample scaled by (1 + 2^-40) is no longer made of exact floats and takes the 64-bit sort; the order of the
+  // values is the same, so every value must land in the bin it had before
+  std::vector<double> scaled = shuffled; for (double& x : scaled) x *= 1.0 + 1.0 / 1099511627776.0;
+  BinMapper m32, m64;
+  { std::vector<double> c = shuffled; m32.FindBin(c.data(), static_cast<int>(c.size()), c.size(), 63, 3, 20, true, BinType::Numerical, true, false, {}); }
+  { std::vector<double> c = scaled; m64.FindBin(c.data(), static_cast<int>(c.size()), c.size(), 63, 3, 20, true, BinType::Numerical, true, false, {}); }
+  CHECK(m32.num_bin == m64.num_bin);
+  int moved = 0; for (size_t i = 0; i < shuffled.size(); ++i) if (m32.ValueToBin(shuffled[i]) != m64.ValueToBin(scaled[i])) ++moved;
+  CHECK(moved == 0);
+  // zeros that are not in the sample (sparse input) get their own bin between the negative and the positive values
+  std::vector<double> sparse; for (int i = 0; i < 300; ++i) sparse.push_back(i % 2 ? 1.0 + i : -1.0 - i);
+  BinMapper z; z.FindBin(sparse.data(), 300, 3000, 32, 3, 20, true, BinType::Numerical, true, false, {});
+  CHECK(z.ValueToBin(0.0) == z.default_bin && z.ValueToBin(-1e-40) == z.default_bin && z.ValueToBin(2.0) > z.default_bin && z.ValueToBin(-2.0) < z.default_bin);
+  CHECK(z.most_freq_bin == z.default_bin && z.sparse_rate > 0.85);
+  // NaN in the sample: the last bin is the missing bin
+  std::vector<double> nanv = base; for (size_t i = 0; i < nanv.size(); i += 10) nanv[i] = std::nan("");
+  BinMapper m; m.FindBin(nanv.data(), static_cast<int>(nanv.size()), nanv.size(), 63, 3, 20, true, BinType::Numerical, true, false, {});
+  CHECK(m.missing_type == MissingType::NaN && static_cast<int>(m.ValueToBin(std::nan(""))) == m.num_bin - 1 && std::isnan(m.bin_upper_bound.back()));
+  // serialisation round trip
+  std::vector<char> buf; m.Serialize(&buf);
+  BinMapper back; back.Deserialize(buf.data());
+  CHECK(back.num_bin == m.num_bin && back.missing_type == m.missing_type && back.default_bin == m.default_bin && back.most_freq_bin == m.most_freq_bin);
+  for (double x : {-3.0, -0.1, 0.0, 0.1, 2.5}) CHECK(back.ValueToBin(x) == m.ValueToBin(x));
+}
+
+// Categorical bins: categories by frequency, rare ones and negatives in bin 0.
+static void TestCategoricalBins() {
+  std::vector<double> v;
+  for (int i = 0; i < 1000; ++i) v.push_back(i % 10 < 6 ? 3.0 : (i % 10 < 9 ? 7.0 : 11.0));
+  v.push_back(-1.0); v.push_back(42.0);
+  BinMapper bm; bm.FindBin(v.data(), static_cast<int>(v.size()), v.size(), 16, 1, 1, false, BinType::Categorical, true, false, {});
+  CHECK(bm.bin_type == BinType::Categorical && bm.num_bin >= 3);
+  CHECK(bm.ValueToBin(3.0) == 1 && bm.ValueToBin(7.0) == 2);           // by count
+  CHECK(bm.ValueToBin(-1.0) == 0 && bm.ValueToBin(12345.0) == 0 && bm.ValueToBin(std::nan("")) == 0);
+}
+
+// Linear leaves: prediction, shrinkage and the fallback to the constant for rows with a missing regressor.
+static void TestLinearLeaves() {
+  Tree t(2);
+  t.Split(0, 0, 0, 3, 0.5, 1.0, 2.0, 60, 40, 6.0, 4.0, 10.f, 0, true);
+  t.is_linear = true;
+  t.leaf_const = {0.5, 2.0}; t.leaf_coeff = {{2.0, -1.0}, {}}; t.leaf_features = {{1, 2}, {}}; t.leaf_features_inner = {{1, 2}, {}};
+  double left[3] = {0.0, 3.0, 4.0}, right[3] = {1.0, 3.0, 4.0}, missing[3] = {0.0, std::nan(""), 4.0};
+  CHECK(t.Predict(left) == 0.5 + 2.0 * 3.0 - 4.0);
+  CHECK(t.Predict(right) == 2.0);
+  CHECK(t.Predict(missing) == 1.0);                                    // the leaf's constant output
+  t.Shrink(0.5);
+  CHECK(t.Predict(left) == 0.5 * (0.5 + 2.0 * 3.0 - 4.0) && t.Predict(missing) == 0.5);
+  size_t used = 0; const std::string text = t.ToString();
+  Tree u(text.c_str(), &used);
+  CHECK(u.is_linear && u.Predict(left) == t.Predict(left) && u.ToString() == text);
+}
+
+// Monotone penalty factor and the candidate evaluation's size limits.
+static void TestCandidateLimits() {
+  CHECK(MonotonePenaltyFactor(3, 0.0) == 1.0);
+  CHECK(MonotonePenaltyFactor(0, 2.0) == kEpsilon && MonotonePenaltyFactor(1, 2.0) == kEpsilon);   // forbidden above the penalty's depth
+  CHECK(MonotonePenaltyFactor(2, 2.0) > 0.4 && MonotonePenaltyFactor(2, 2.0) < MonotonePenaltyFactor(5, 2.0) && MonotonePenaltyFactor(20, 2.0) <= 1.0 + kEpsilon);
+  SplitParams p; memset(&p, 0, sizeof(p)); p.min_data_in_leaf = 10; p.min_sum_hessian_in_leaf = 1e-3;
+  LeafScanInfo L; memset(&L, 0, sizeof(L));
+  L.sum_g = 0.0; L.sum_h = 100.0; L.num_data = 100; L.cnt_factor = 1.0; L.g_scale = L.h_scale = 1.0; L.mono_factor = 1.0;
+  L.min_c = -1.0 / 0.0; L.max_c = 1.0 / 0.0; L.min_gain_shift = LeafGain(0.0, 100.0 + 2 * kEpsilon, p, 100, 0.0);
+  double lo, ro;
+  CHECK(EvalCandidate(-5.0, 9.0, 9, L, p, 0, &lo, &ro) == -1.0 / 0.0);    // nine rows on the left: below min_data_in_leaf
+  CHECK(EvalCandidate(-5.0, 95.0, 95, L, p, 0, &lo, &ro) == -1.0 / 0.0);  // five rows on the right
+  const double g = EvalCandidate(-30.0, 50.0, 50, L, p, 0, &lo, &ro);
+  CHECK(g > 0.0 && std::fabs(g - (900.0 / (50.0 + kEpsilon) * 2)) < 1e-6);
+  CHECK(BinCountEstimate(2.49, 1.0) == 2 && BinCountEstimate(2.5, 1.0) == 3);
+  // tie order of splits: higher gain, then lower feature, then lower threshold
+  CHECK(SplitBetter(1.0, 3, 5, 0.5, 1, 1) && !SplitBetter(0.5, 1, 1, 1.0, 3, 5));
+  CHECK(SplitBetter(1.0, 1, 9, 1.0, 2, 0) && SplitBetter(1.0, 2, 3, 1.0, 2, 4) && !SplitBetter(1.0, 2, 4, 1.0, 2, 4));
+  CHECK(!SplitBetter(5.0, -1, 0, -1.0 / 0.0, -1, 0) && SplitBetter(-5.0, 0, 0, 1.0, -1, 0));
+}
+
+// Forced-split files and the debugging switches' parser.
+static void TestForcedSplitFile() {
+  const char* path = "core_tests_forced.json";
+  FILE* f = fopen(path, "w");
+  fputs("{ \"feature\": 3, \"threshold\": 0.25,\n  \"left\": {\"feature\": 4, \"threshold\": -0.5},\n  \"right\": {\"feature\": 1, \"threshold\": 0, \"right\": {\"feature\": 0, \"threshold\": 7}} }", f);
+  fclose(f);
+  const std::vector<ForcedSplitNode> nodes = LoadForcedSplitsFile(path);
+  remove(path);
+  CHECK(nodes.size() == 4 && nodes[0].feature == 3 && nodes[0].threshold == 0.25);
+  CHECK(nodes[0].left == 1 && nodes[1].feature == 4 && nodes[1].left == -1 && nodes[1].right == -1);
+  CHECK(nodes[0].right == 2 && nodes[2].feature == 1 && nodes[2].right == 3 && nodes[3].feature == 0 && nodes[3].threshold == 7.0);
+  CHECK(LoadForcedSplitsFile("").empty());
+}
+
 int main() {
+  TestBinFindingInvariants();
+  TestCategoricalBins();
+  TestLinearLeaves();
+  TestCandidateLimits();
+  TestForcedSplitFile();
   TestFixedPointExtras();
   TestFormatting();
   TestPhilox();
