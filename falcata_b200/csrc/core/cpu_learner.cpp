@@ -193,6 +193,9 @@ class CPUTreeLearner : public TreeLearner {
   bool quant_ = false, parallel_data_ = false, parallel_feature_ = false, parallel_voting_ = false;
   QuantState qs_;
   std::vector<int32_t> gh_packed_;
+  // reduce-scatter of histograms: per rank the histogram slots of the features it owns, the block sizes in 8-byte elements,
+  // and the packed send / receive buffers (8-byte cells holding doubles or 64-bit integers)
+  std::vector<std::vector<int>> rs_slots_; std::vector<int64_t> rs_counts_; std::vector<int64_t> rs_send_, rs_recv_;
   std::vector<int8_t> ef_residual_;   // fixed-point error feedback: (hessian, gradient) residuals per row, one slot per class
   const score_t* grad_ = nullptr; const score_t* hess_ = nullptr;
   std::vector<int8_t> node_feature_mask_;
@@ -271,6 +274,7 @@ void CPUTreeLearner::SetParams() {
 
 void CPUTreeLearner::Init(const Dataset* train, const Config& cfg) {
   ds_ = train; cfg_ = cfg;
+  rs_counts_.clear(); rs_slots_.clear();
   if (!ds_->has_host_bins()) Log::Fatal("The CPU learner needs host-resident bins (dataset was built device-only)");
   SetParams();
   col_sampler_.Init(cfg_, ds_);
@@ -434,6 +438,35 @@ void CPUTreeLearner::ReduceHistogramAcrossRanks(LeafState* leaf) {
   // Data-parallel: sum every rank's local histogram. (The device path reduce-scatters into
   // owners; on the host a full sum followed by owned-feature search is equivalent.)
   if (parallel_voting_) return;   // voting reduces only voted features, inside FindBestSplit
+  if (Network::reduce_scatter() != nullptr && Network::world() > 1) {
+    // Reduce-scatter: every rank needs the global bins of the features it searches only. The (g, h) pairs of the features
+    // owned by rank r are packed one after the other, in feature order, into r's block; what comes back is the sum over
+    // the ranks of this rank's block. Bins of the other features keep this rank's local sums: nothing reads them but the
+    // subtraction, whose result for those features is local again.
+    const int W = Network::world(), R = Network::rank();
+    if (rs_counts_.empty()) {
+      rs_counts_.assign(W, 0); rs_slots_.assign(W, {});
+      for (int f = 0; f < ds_->num_features; ++f) {
+        const FeatureMeta& m = ds_->feature_meta[f]; const int n = m.bundled ? m.num_bin - 1 : m.num_bin;
+        for (int b = 0; b < n; ++b) rs_slots_[f % W].push_back(m.hist_offset + b);
+      }
+      for (int r = 0; r < W; ++r) rs_counts_[r] = 2 * static_cast<int64_t>(rs_slots_[r].size());
+    }
+    int64_t total = 0; for (int r = 0; r < W; ++r) total += rs_counts_[r];
+    rs_send_.resize(static_cast<size_t>(total)); rs_recv_.resize(static_cast<size_t>(rs_counts_[R]));
+    size_t o = 0;
+    for (int r = 0; r < W; ++r) for (int s : rs_slots_[r]) {
+      if (quant_) { memcpy(&rs_send_[o], &leaf->hist_i[2 * static_cast<size_t>(s)], 16); } else { memcpy(&rs_send_[o], &leaf->hist[2 * static_cast<size_t>(s)], 16); }
+      o += 2;
+    }
+    Network::reduce_scatter()(rs_send_.data(), rs_counts_.data(), rs_recv_.data(), quant_ ? 1 : 0);
+    o = 0;
+    for (int s : rs_slots_[R]) {
+      if (quant_) memcpy(&leaf->hist_i[2 * static_cast<size_t>(s)], &rs_recv_[o], 16); else memcpy(&leaf->hist[2 * static_cast<size_t>(s)], &rs_recv_[o], 16);
+      o += 2;
+    }
+    return;
+  }
   if (quant_) Network::SumInt64(leaf->hist_i.data(), static_cast<int64_t>(leaf->hist_i.size()));
   else Network::SumDouble(leaf->hist.data(), static_cast<int64_t>(leaf->hist.size()));
 }

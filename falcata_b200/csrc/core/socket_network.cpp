@@ -7,7 +7,9 @@
 // and receives the block of rank - s, both directions driven by one poll loop so that large blocks cannot deadlock on
 // full socket buffers) and a sum all-reduce built on it (every rank adds the gathered blocks in rank order, so all
 // ranks hold bit-identical sums). Histograms of the host learner are a few hundred kilobytes, so the all-gather form
-// costs little against the local work; a reduce-scatter form is not built.
+// costs little against the local work. The histogram exchange of the data-parallel learner uses the third collective, a
+// reduce-scatter with per-rank block sizes: a rank sends every peer only the bins of the features that peer searches and
+// sums what it receives for its own features in rank order (the same sums as the all-reduce gives).
 //
 // Parity: src/network/linkers_socket.cpp:L26-222 (listen / connect mesh from the machine list), src/network/network.cpp
 // (Allreduce / Allgather), include/Falcata/c_api.h FLC_NetworkInit.
@@ -115,6 +117,28 @@ void MeshAllreduceSum(void* buf, int64_t count, int dtype) {
   }
 }
 
+void MeshReduceScatter(const void* sendbuf, const int64_t* counts, void* recv, int dtype) {
+  const int W = g_mesh.world, R = g_mesh.rank;
+  const size_t mine = static_cast<size_t>(counts[R]) * 8;
+  std::vector<size_t> start(W + 1, 0);
+  for (int r = 0; r < W; ++r) start[r + 1] = start[r] + static_cast<size_t>(counts[r]) * 8;
+  const char* send = static_cast<const char*>(sendbuf);
+  std::vector<char> stage(mine * W);                       // [source rank][own block]
+  memcpy(stage.data() + static_cast<size_t>(R) * mine, send + start[R], mine);
+  for (int s = 1; s < W; ++s) {
+    const int to = (R + s) % W, from = (R - s + W) % W;
+    SendRecv(g_mesh.fd[to], send + start[to], start[to + 1] - start[to], g_mesh.fd[from], stage.data() + static_cast<size_t>(from) * mine, mine);
+  }
+  const int64_t n = counts[R];
+  if (dtype == 0) {
+    double* d = static_cast<double*>(recv);
+    for (int64_t i = 0; i < n; ++i) { double a = 0.0; for (int r = 0; r < W; ++r) a += reinterpret_cast<const double*>(stage.data() + static_cast<size_t>(r) * mine)[i]; d[i] = a; }
+  } else {
+    int64_t* d = static_cast<int64_t*>(recv);
+    for (int64_t i = 0; i < n; ++i) { int64_t a = 0; for (int r = 0; r < W; ++r) a += reinterpret_cast<const int64_t*>(stage.data() + static_cast<size_t>(r) * mine)[i]; d[i] = a; }
+  }
+}
+
 bool IsLocalAddress(const std::string& host) {
   if (host == "127.0.0.1" || host == "localhost" || host == "0.0.0.0" || host == "::1") return true;
   ifaddrs* list = nullptr;
@@ -207,7 +231,7 @@ void SocketNetworkInit(const std::string& machines, int local_listen_port, int t
   }
   g_mesh.up = true;
   Network::world() = world; Network::rank() = rank;
-  Network::allreduce() = &MeshAllreduceSum; Network::allgather() = &MeshAllgather;
+  Network::allreduce() = &MeshAllreduceSum; Network::allgather() = &MeshAllgather; Network::reduce_scatter() = &MeshReduceScatter;
   Log::Info("Connected to %d other machine(s); this is rank %d of %d", world - 1, rank, world);
 }
 
@@ -215,7 +239,7 @@ bool SocketNetworkActive() { return g_mesh.up; }
 
 void SocketNetworkFree() {
   if (!g_mesh.up) return;
-  Network::world() = 1; Network::rank() = 0; Network::allreduce() = nullptr; Network::allgather() = nullptr;
+  Network::world() = 1; Network::rank() = 0; Network::allreduce() = nullptr; Network::allgather() = nullptr; Network::reduce_scatter() = nullptr;
   CloseMesh();
 }
 

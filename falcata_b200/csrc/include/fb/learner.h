@@ -23,6 +23,11 @@ namespace fb {
 struct Network {
   typedef void (*AllreduceSumFn)(void* buf, int64_t count, int dtype /*0 f64, 1 i64*/);
   typedef void (*AllgatherFn)(const void* in, int64_t bytes, void* out /* world * bytes */);
+  // Optional: sendbuf holds, one after the other, the block of 8-byte elements meant for every rank (counts[r] elements for
+  // rank r); recv gets counts[own rank] elements: the element-wise sum over all ranks of their blocks for this rank, added in
+  // rank order. A transport without it is served by the all-reduce.
+  typedef void (*ReduceScatterFn)(const void* sendbuf, const int64_t* counts, void* recv, int dtype /*0 f64, 1 i64*/);
+  static ReduceScatterFn& reduce_scatter() { static ReduceScatterFn f = nullptr; return f; }
   static int& rank() { static int r = 0; return r; }
   static int& world() { static int w = 1; return w; }
   static AllreduceSumFn& allreduce() { static AllreduceSumFn f = nullptr; return f; }
