@@ -127,3 +127,20 @@ def test_cli_distributed_training_over_tcp(tmp_path):
     assert model_body(models[0]) == model_body(models[1]) == model_body(models[2])
     pr = fb.Booster(model_str=models[0]).predict(X)
     assert float(np.mean((pr > 0.5) == y)) > 0.85
+
+
+def test_examples_run(tmp_path):
+    """The Python quick start (host learner here) and the command-line example files keep working."""
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", "quickstart.py"), "--device", "cpu", "--rows", "6000", "--rounds", "10"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "same predictions" in r.stdout, r.stdout + r.stderr
+    rng = np.random.RandomState(1)
+    X = rng.randn(2000, 10); y = (X[:, 0] + X[:, 1] * X[:, 2] > 0).astype(int)
+    os.makedirs(tmp_path / "examples" / "cli")
+    np.savetxt(tmp_path / "examples" / "cli" / "train.tsv", np.column_stack([y[:1600], X[:1600]]), delimiter="\t", fmt="%.9g")
+    np.savetxt(tmp_path / "examples" / "cli" / "valid.tsv", np.column_stack([y[1600:], X[1600:]]), delimiter="\t", fmt="%.9g")
+    for name in ("train.conf", "predict.conf"):
+        out = _run(tmp_path, "config=" + os.path.join(root, "examples", "cli", name), "num_trees=10")
+    assert "Finished prediction" in out and len(np.loadtxt(tmp_path / "examples" / "cli" / "predictions.txt")) == 400
