@@ -103,3 +103,15 @@ def test_every_openmp_region_names_its_team_size():
             if re.search(r"#\s*pragma\s+omp\s+parallel", line) and "num_threads(" not in line:
                 bad.append(f"{path.relative_to(root)}:{no}")
     assert not bad, bad
+
+
+def test_parameter_reference_is_up_to_date():
+    """docs/Parameters.md is generated from the native parameter table; a parameter added to config.h without running the
+    generator fails here."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    r = subprocess.run([sys.executable, str(root / "docs" / "gen_parameters.py"), "--check"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
