@@ -473,3 +473,34 @@ def test_histogram_pool_size_bounds_the_cached_histograms_without_changing_an_in
     a = fb.train(dict(real), fb.Dataset(X, y), 8).predict(X)
     b = fb.train(dict(real, histogram_pool_size=3 * per_leaf_mb), fb.Dataset(X, y), 8).predict(X)
     assert np.max(np.abs(a - b)) < 1e-6
+
+
+def test_host_learner_is_invariant_to_thread_count_and_histogram_pool():
+    """Random small training jobs on the host learner: the model does not depend on the number of worker threads (below
+    8192 rows the histogram of a bin adds its rows in row order whatever the thread count; the per-feature records are
+    merged in a fixed order) nor, with integer histograms, on a histogram pool that holds a handful of leaves only."""
+    from util import model_body
+
+    rng = np.random.default_rng(123)
+    for _ in range(6):
+        n = int(rng.choice([800, 3000, 7000])); f = int(rng.choice([3, 9, 20]))
+        X = rng.normal(size=(n, f)).astype(np.float32)
+        if rng.random() < 0.5:
+            X[rng.random(size=n) < 0.1, 0] = np.nan
+        if rng.random() < 0.5:
+            X[:, 1] = np.round(X[:, 1] * 2)
+        y = (np.nan_to_num(X[:, 0]) * X[:, 1] + X[:, 2 % f] + 0.3 * rng.normal(size=n) > 0).astype(np.float32)
+        p = {"objective": "binary", "num_leaves": int(rng.choice([7, 31, 63])), "max_bin": int(rng.choice([15, 63, 255])), "verbosity": -1, "device_type": "cpu",
+             "min_data_in_leaf": int(rng.choice([1, 5, 20])), "grow_policy": str(rng.choice(["level", "leaf"])), "feature_fraction": float(rng.choice([1.0, 0.6])),
+             "seed": int(rng.integers(100))}
+        if rng.random() < 0.4:
+            p["extra_trees"] = True
+        if rng.random() < 0.4:
+            p["feature_fraction_bynode"] = 0.7
+        quant = dict(p, quant_mode="fixedpoint", quant_bins=64)
+        base = model_body(fb.train(dict(quant, num_threads=8), fb.Dataset(X, y), 4).model_to_string())
+        assert base == model_body(fb.train(dict(quant, num_threads=1), fb.Dataset(X, y), 4).model_to_string()), p
+        assert base == model_body(fb.train(dict(quant, num_threads=8, histogram_pool_size=0.05), fb.Dataset(X, y), 4).model_to_string()), p
+        real = dict(p, quant_mode="none")
+        assert model_body(fb.train(dict(real, num_threads=8), fb.Dataset(X, y), 4).model_to_string()) == \
+            model_body(fb.train(dict(real, num_threads=1), fb.Dataset(X, y), 4).model_to_string()), p
