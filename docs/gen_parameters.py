@@ -23,7 +23,7 @@ NOTES = {
     "quant_bins": "gradient levels; 0 = automatic (raised for small leaves on large data, lowered to keep 32-bit histograms exact)",
     "cuda_plan": "`auto[,key:on|off]*` or `wisdom` (the plan stored by `falcata_b200.tuner.tune`)",
     "tree_learner": "`serial`, `data`, `feature`, `voting`; on GPUs the collectives run inside the kernels over peer memory, on CPUs over the injected or TCP network",
-    "monotone_constraints_method": "`basic` (host and device), `intermediate` (host learner), `advanced` maps to `intermediate`",
+    "monotone_constraints_method": "`basic` (host and device), `intermediate` and `advanced` (host learner; a device booster hands training to it)",
     "forcedsplits_filename": "host learner and, on one GPU, the device engine",
     "linear_tree": "host learner; on one GPU without row sampling the trees grow on the device and the leaf regressions are solved on the host",
     "boosting": "`gbdt`, `dart`, `rf` (all three on the device engine), `goss` as `data_sample_strategy`",

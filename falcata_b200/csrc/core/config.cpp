@@ -240,11 +240,7 @@ void Config::CheckParamConflict() {
     Log::Fatal("Quantized training does not support monotone constraints");
   if (quant != QuantMode::None && !interaction_constraints.empty())
     Log::Fatal("Quantized training does not support interaction constraints");
-  if (!monotone_vec.empty() && monotone_constraints_method == "advanced") {
-    Log::Warning("monotone_constraints_method=advanced (bounds per threshold) is not built; using intermediate");
-    monotone_constraints_method = "intermediate";
-  }
-  if (!monotone_vec.empty() && monotone_constraints_method != "basic" && monotone_constraints_method != "intermediate")
+  if (!monotone_vec.empty() && monotone_constraints_method != "basic" && monotone_constraints_method != "intermediate" && monotone_constraints_method != "advanced")
     Log::Fatal("Unknown monotone_constraints_method %s (basic, intermediate, advanced)", monotone_constraints_method.c_str());
   if (boosting == "rf") {
     if (!((bagging_freq > 0 && bagging_fraction < 1.0) || feature_fraction < 1.0))

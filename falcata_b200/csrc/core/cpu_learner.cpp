@@ -147,7 +147,11 @@ struct LeafState {
   std::vector<int64_t> hist_i;       // 2 * num_total_bin integer sums when quantized
   bool has_hist = false;
   int64_t hist_stamp = 0;            // when the histogram was last produced or read (least recently used ones are dropped first)
-  std::vector<uint16_t> box;         // monotone_constraints_method=intermediate: per feature the (first, last) bin of the leaf's cell
+  std::vector<uint16_t> box;         // monotone_constraints_method=intermediate / advanced: per feature the (first, last) bin of the leaf's cell
+  // advanced: the leaves whose cells touch this leaf's along a monotone feature, listed when the leaf is about to be
+  // searched: output, +1 when this leaf lies below the neighbour (its output is an upper bound), the separating feature
+  struct Neighbour { double output; int dir; int sep; const uint16_t* box; };
+  std::vector<Neighbour> neighbours;
   double min_constraint = -std::numeric_limits<double>::infinity(), max_constraint = std::numeric_limits<double>::infinity();
 };
 
@@ -224,6 +228,9 @@ class CPUTreeLearner : public TreeLearner {
   void DropHistogram(LeafState* leaf) { std::vector<double>().swap(leaf->hist); std::vector<int64_t>().swap(leaf->hist_i); leaf->has_hist = false; }
   void EnforceHistogramPool(int num_leaves, int keep_a, int keep_b);
   bool mono_intermediate_ = false;   // monotone bounds from the neighbouring leaves' outputs instead of the split's mid point
+  bool mono_advanced_ = false;       // ... and per threshold: a child is bounded only by the neighbours that its own part of the cell touches
+  int mono_num_leaves_ = 0;          // leaves of the tree under construction (for the neighbour lists)
+  int RelateLeaves(int a, int b, int* sep) const;
   std::vector<int> mono_dirty_;      // leaves whose bounds the last ApplySplit tightened (their best split is stale)
   void TightenMonotoneBounds(const Tree* tree, int left_id, int right_id);
   int forced_feature_ = -1, forced_bin_ = -1;   // non-negative while FindBestSplit evaluates one forced (feature, bin)
@@ -257,7 +264,8 @@ void CPUTreeLearner::SetParams() {
   if ((!cegb_coupled_.empty() || !cegb_lazy_.empty()) && Network::active() && cfg_.tree_learner != "serial")
     Log::Fatal("Per-feature CEGB penalties are not available with a parallel tree learner");
   sp_.use_mc = 0; for (const auto& m : ds_->feature_meta) if (m.monotone != 0) sp_.use_mc = 1;
-  mono_intermediate_ = sp_.use_mc != 0 && cfg_.monotone_constraints_method == "intermediate";
+  mono_advanced_ = sp_.use_mc != 0 && cfg_.monotone_constraints_method == "advanced";
+  mono_intermediate_ = sp_.use_mc != 0 && (cfg_.monotone_constraints_method == "intermediate" || mono_advanced_);
   hist_pool_cap_ = 0;
   if (cfg_.histogram_pool_size > 0.0 && ds_ != nullptr) {
     const double per_leaf = static_cast<double>(ds_->num_total_bin) * 2.0 * 8.0;   // (g, h) as doubles or 64-bit integers
@@ -505,6 +513,27 @@ static void PlainGainPass(int n, const double* pg, const double* ph, const doubl
   }
 }
 
+// EvalCandidate with separate output ranges for the two children (monotone_constraints_method=advanced): the outputs
+// are clamped to their own ranges, a split on a monotone feature must order them, and the gain is taken at the clamped
+// outputs. Same primitives and the same order of operations as SplitGain's constrained branch.
+static double EvalCandidateBounded(double lg, double lh, int lcnt, const LeafScanInfo& L, const SplitParams& p, int monotone, double lmin, double lmax,
+                                   double rmin, double rmax, double* lout, double* rout) {
+  const double ninf = -std::numeric_limits<double>::infinity();
+  const int rcnt = L.num_data - lcnt;
+  const double rg = FB_SUB(L.sum_g, lg), rh = FB_SUB(L.sum_h, lh);
+  if (lcnt < p.min_data_in_leaf || rcnt < p.min_data_in_leaf) return ninf;
+  if (lh < p.min_sum_hessian_in_leaf || rh < p.min_sum_hessian_in_leaf) return ninf;
+  if (lmin > lmax || rmin > rmax) return ninf;   // nothing fits between the neighbours
+  const double lhe = FB_ADD(lh, kEpsilon), rhe = FB_ADD(rh, kEpsilon);
+  *lout = ClampOutput(LeafOutput(lg, lhe, p, lcnt, L.parent_output), lmin, lmax);
+  *rout = ClampOutput(LeafOutput(rg, rhe, p, rcnt, L.parent_output), rmin, rmax);
+  if ((monotone > 0 && *lout > *rout) || (monotone < 0 && *lout < *rout)) return ninf;
+  const double gain = FB_ADD(LeafGainGivenOutput(lg, lhe, p, *lout), LeafGainGivenOutput(rg, rhe, p, *rout));
+  if (!(gain > L.min_gain_shift)) return ninf;
+  const double above = FB_SUB(gain, L.min_gain_shift);
+  return (monotone != 0 && L.mono_factor != 1.0) ? FB_MUL(above, L.mono_factor) : above;
+}
+
 // Numerical threshold search of one feature: one forward prefix over the non-missing bins serves
 // both scan directions (see ScanRank in fb/split_math.h).
 void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanInfo& L, SplitRecord* best) const {
@@ -514,7 +543,7 @@ void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanI
   // reads the leaf's histogram in place: the same candidates in the same order with the same arithmetic as the general
   // scan below (one pass, default direction left), without its per-call scratch arrays.
   if (!quant_ && !m.bundled && !(m.missing_type != static_cast<int>(MissingType::None) && nb > 2) && !(sp_.extra_trees && nb > 2) &&
-      !(forced_bin_ >= 0 && f == forced_feature_)) {
+      !(forced_bin_ >= 0 && f == forced_feature_) && !mono_advanced_) {
     const double* hist = leaf.hist.data() + 2 * static_cast<size_t>(m.hist_offset);
     double best_gain = -std::numeric_limits<double>::infinity(); int best_t = -1;
     double best_lg = 0, best_lh = 0; int best_lc = 0;
@@ -582,6 +611,26 @@ void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanI
   if (forced_bin_ >= 0 && f == forced_feature_) rand_t = forced_bin_;
   double best_gain = -std::numeric_limits<double>::infinity(); int best_rank = 1 << 30;
   SplitRecord cand; InitSplitRecord(&cand);
+  // advanced monotone bounds: per threshold the output range of either child from the neighbours that its part of the
+  // cell touches. A neighbour across feature f itself bounds both children at every threshold; a neighbour across
+  // another feature touches the left child when its cell starts at or below the threshold and the right child when it
+  // ends above it, so the left bounds tighten with a growing threshold and the right bounds loosen.
+  static thread_local std::vector<double> adv;   // [lmin | lmax | rmin | rmax][nb]
+  const bool advanced = mono_advanced_ && nb >= 2;
+  if (advanced) {
+    const double inf = std::numeric_limits<double>::infinity();
+    adv.assign(4 * static_cast<size_t>(nb), 0.0);
+    double* lmin = adv.data(); double* lmax = lmin + nb; double* rmin = lmax + nb; double* rmax = rmin + nb;
+    for (int t = 0; t < nb; ++t) { lmin[t] = rmin[t] = -inf; lmax[t] = rmax[t] = inf; }
+    for (const LeafState::Neighbour& q : leaf.neighbours) {
+      const bool upper = q.dir > 0;   // this leaf lies below the neighbour: the neighbour's output bounds it from above
+      int l_from = 0, r_to = nb - 1;  // left child touched for t >= l_from, right child for t <= r_to
+      if (q.sep != f) { l_from = q.box[2 * f]; r_to = static_cast<int>(q.box[2 * f + 1]) - 1; }
+      for (int t = std::max(0, l_from); t < nb; ++t) { if (upper) lmax[t] = std::min(lmax[t], q.output); else lmin[t] = std::max(lmin[t], q.output); }
+      for (int t = 0; t <= std::min(nb - 1, r_to); ++t) { if (upper) rmax[t] = std::min(rmax[t], q.output); else rmin[t] = std::max(rmin[t], q.output); }
+    }
+  }
+  double best_bounds[4] = {L.min_c, L.max_c, L.min_c, L.max_c};
   int64_t pgi = 0, phi = 0; double pgd = 0, phd = 0; int pc = 0;
   for (int t = 0; t <= nb - 2; ++t) {
     if (t != skip) { pgi += gi[t]; phi += hi[t]; pgd += gd[t]; phd += hd[t]; pc += BinCountEstimate(binh(t), L.cnt_factor); }
@@ -593,10 +642,12 @@ void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanI
       if (quant_) { lg = FB_MUL(static_cast<double>(lgi), L.g_scale); lh = FB_MUL(static_cast<double>(lhi), L.h_scale); }
       else { lg = pgd + ((pass == 0 && skip >= 0) ? mgd : 0.0); lh = phd + ((pass == 0 && skip >= 0) ? mhd : 0.0); }
       double lo, ro;
-      const double gain = EvalCandidate(lg, lh, lc, L, sp_, m.monotone, &lo, &ro);
+      const double gain = advanced ? EvalCandidateBounded(lg, lh, lc, L, sp_, m.monotone, adv[t], adv[nb + t], adv[2 * nb + t], adv[3 * nb + t], &lo, &ro)
+                                   : EvalCandidate(lg, lh, lc, L, sp_, m.monotone, &lo, &ro);
       if (gain == -std::numeric_limits<double>::infinity()) continue;
       const int rank = ScanRank(pass, t, nb);
       if (gain > best_gain || (gain == best_gain && rank < best_rank)) {
+        if (advanced) { best_bounds[0] = adv[t]; best_bounds[1] = adv[nb + t]; best_bounds[2] = adv[2 * nb + t]; best_bounds[3] = adv[3 * nb + t]; }
         best_gain = gain; best_rank = rank;
         cand.gain = gain; cand.feature = f; cand.threshold = t; cand.default_left = pass == 0 ? 1 : 0;
         cand.left_g = lg; cand.left_h = lh; cand.right_g = FB_SUB(L.sum_g, lg); cand.right_h = FB_SUB(L.sum_h, lh);
@@ -606,8 +657,13 @@ void CPUTreeLearner::ScanNumerical(const LeafState& leaf, int f, const LeafScanI
     }
   }
   if (cand.feature >= 0) {
-    cand.left_out = ChildOutput(cand.left_g, FB_ADD(cand.left_h, kEpsilon), sp_, cand.left_cnt, L);
-    cand.right_out = ChildOutput(cand.right_g, FB_ADD(cand.right_h, kEpsilon), sp_, cand.right_cnt, L);
+    if (advanced) {
+      cand.left_out = ClampOutput(LeafOutput(cand.left_g, FB_ADD(cand.left_h, kEpsilon), sp_, cand.left_cnt, L.parent_output), best_bounds[0], best_bounds[1]);
+      cand.right_out = ClampOutput(LeafOutput(cand.right_g, FB_ADD(cand.right_h, kEpsilon), sp_, cand.right_cnt, L.parent_output), best_bounds[2], best_bounds[3]);
+    } else {
+      cand.left_out = ChildOutput(cand.left_g, FB_ADD(cand.left_h, kEpsilon), sp_, cand.left_cnt, L);
+      cand.right_out = ChildOutput(cand.right_g, FB_ADD(cand.right_h, kEpsilon), sp_, cand.right_cnt, L);
+    }
     cand.gain = FB_MUL(cand.gain, static_cast<double>(m.penalty));
     if (SplitBetter(cand.gain, ds_->feature_meta[cand.feature].real_index, cand.threshold, best->gain,
                     best->feature >= 0 ? ds_->feature_meta[best->feature].real_index : -1, best->threshold)) *best = cand;
@@ -715,6 +771,14 @@ bool CPUTreeLearner::PrepareLeafScan(LeafState* leaf, int leaf_id, int tree_inde
   L.min_gain_shift = FB_ADD(LeafGainGivenOutput(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, leaf->output), sp_.min_gain_to_split);
   if (sp_.max_delta_step <= 0.0 && sp_.path_smooth <= 0.0)
     L.min_gain_shift = FB_ADD(LeafGain(L.sum_g, FB_ADD(L.sum_h, 2 * kEpsilon), sp_, L.num_data, leaf->output), sp_.min_gain_to_split);
+  if (mono_advanced_) {
+    leaf->neighbours.clear();
+    for (int l = 0; l < mono_num_leaves_; ++l) {
+      if (l == leaf_id || leaves_[l].box.empty()) continue;
+      int sep = -1; const int r = RelateLeaves(leaf_id, l, &sep);
+      if (r != 0) leaf->neighbours.push_back({leaves_[l].output, r, sep, leaves_[l].box.data()});
+    }
+  }
   *mask_out = col_sampler_.by_node() ? col_sampler_.SampleByNode(tree_index, leaf_id + 1000003 * leaf->depth, &leaf->path) : col_sampler_.used_by_tree();
   if (forced_feature_ >= 0) { mask_out->assign(mask_out->size(), 0); (*mask_out)[forced_feature_] = 1; }
   return true;
@@ -922,6 +986,11 @@ int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
   if (mono_intermediate_) {
     R.box = Lf.box;
     if (!s.is_categorical) { Lf.box[2 * s.feature + 1] = static_cast<uint16_t>(s.threshold); R.box[2 * s.feature] = static_cast<uint16_t>(s.threshold + 1); }
+    if (mono_advanced_) {   // a child is bounded by what its own cell touches, not by everything the parent's cell touched
+      Lf.min_constraint = R.min_constraint = -std::numeric_limits<double>::infinity();
+      Lf.max_constraint = R.max_constraint = std::numeric_limits<double>::infinity();
+    }
+    mono_num_leaves_ = tree->num_leaves;
     TightenMonotoneBounds(tree, leaf_id, right_id);
   } else if (s.monotone != 0) {
     const double mid = (s.left_out + s.right_out) / 2.0;
@@ -951,26 +1020,33 @@ int CPUTreeLearner::ApplySplit(Tree* tree, int leaf_id) {
 // set, lies inside its leaf's bounds, so every pair stays ordered. Missing-value bins are not part of the cells.
 // Parity: src/treelearner/monotone_constraints.hpp (IntermediateLeafConstraints: bounds from the outputs of the
 // contiguous leaves, found there by walking up and down the tree from the split leaf).
-void CPUTreeLearner::TightenMonotoneBounds(const Tree* tree, int left_id, int right_id) {
+// +1: leaf a lies below leaf b along a monotone feature (a's output must not exceed b's), -1: above, 0: the two cells do
+// not touch along one feature (apart in two features, or separated by categorical splits only). *sep = that feature.
+int CPUTreeLearner::RelateLeaves(int a, int b, int* sep_out) const {
   const int nf = ds_->num_features;
-  auto relate = [&](int a, int b) {
-    // +1: a lies below b (a's output must not exceed b's); -1: a above b; 0: unrelated
-    const uint16_t* A = leaves_[a].box.data(); const uint16_t* B = leaves_[b].box.data();
-    int sep = -1, dir = 0;
-    for (int f = 0; f < nf; ++f) {
-      const bool a_below = A[2 * f + 1] < B[2 * f], b_below = B[2 * f + 1] < A[2 * f];
-      if (!a_below && !b_below) continue;
-      if (sep >= 0) return 0;                 // apart in two features: no single-feature move connects them
-      sep = f; dir = a_below ? 1 : -1;
-    }
-    if (sep < 0) return 0;                    // only categorical splits between them
-    const int mono = ds_->feature_meta[sep].monotone;
-    return mono == 0 ? 0 : (mono > 0 ? dir : -dir);
-  };
+  const uint16_t* A = leaves_[a].box.data(); const uint16_t* B = leaves_[b].box.data();
+  int sep = -1, dir = 0;
+  for (int f = 0; f < nf; ++f) {
+    const bool a_below = A[2 * f + 1] < B[2 * f], b_below = B[2 * f + 1] < A[2 * f];
+    if (!a_below && !b_below) continue;
+    if (sep >= 0) return 0;
+    sep = f; dir = a_below ? 1 : -1;
+  }
+  *sep_out = sep;
+  if (sep < 0) return 0;
+  const int mono = ds_->feature_meta[sep].monotone;
+  return mono == 0 ? 0 : (mono > 0 ? dir : -dir);
+}
+
+void CPUTreeLearner::TightenMonotoneBounds(const Tree* tree, int left_id, int right_id) {
+  auto relate = [&](int a, int b) { int sep; return RelateLeaves(a, b, &sep); };
   auto order = [&](int lower, int upper, bool lower_is_new, bool upper_is_new) {
     LeafState& lo = leaves_[lower]; LeafState& up = leaves_[upper];
     if (up.output < lo.max_constraint) { lo.max_constraint = up.output; if (!lower_is_new) mono_dirty_.push_back(lower); }
     if (lo.output > up.min_constraint) { up.min_constraint = lo.output; if (!upper_is_new) mono_dirty_.push_back(upper); }
+    // advanced: an older leaf's bounds are per threshold, and a new neighbour can tighten one of them without moving the
+    // leaf's overall range, so every older leaf that touches a new one is searched again
+    if (mono_advanced_) { if (!lower_is_new) mono_dirty_.push_back(lower); if (!upper_is_new) mono_dirty_.push_back(upper); }
   };
   { const int r = relate(left_id, right_id); if (r > 0) order(left_id, right_id, true, true); else if (r < 0) order(right_id, left_id, true, true); }
   for (int c : {left_id, right_id}) {
@@ -1045,6 +1121,7 @@ Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_i
   }
   root.output = LeafOutput(root.sum_g, FB_ADD(root.sum_h, 2 * kEpsilon), sp_, static_cast<int>(root.global_count), 0.0);
   if (mono_intermediate_) {
+    mono_num_leaves_ = 1;
     root.box.resize(2 * static_cast<size_t>(ds_->num_features));
     for (int f = 0; f < ds_->num_features; ++f) { root.box[2 * f] = 0; root.box[2 * f + 1] = static_cast<uint16_t>(std::min(65535, ds_->feature_meta[f].num_bin - 1)); }
   }

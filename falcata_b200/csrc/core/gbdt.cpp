@@ -60,8 +60,8 @@ void GBDT::Init(const Config& cfg, const Dataset* train, ObjectiveFunction* obj,
       Log::Warning("Per-feature CEGB penalties (cegb_penalty_feature_coupled / _lazy) train on the host learner");
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
-    if (!cfg.monotone_vec.empty() && cfg.monotone_constraints_method == "intermediate" && is_cuda_) {
-      Log::Warning("monotone_constraints_method=intermediate trains on the host learner (the device engine has the basic method)");
+    if (!cfg.monotone_vec.empty() && cfg.monotone_constraints_method != "basic" && is_cuda_) {
+      Log::Warning("monotone_constraints_method=%s trains on the host learner (the device engine has the basic method)", cfg.monotone_constraints_method.c_str());
       is_cuda_ = false; config_.is_cuda = false; config_.device_type = "cpu";
     }
     if (!cfg.forcedsplits_filename.empty() && is_cuda_ && Network::active() && cfg.tree_learner != "serial") {
