@@ -199,6 +199,36 @@ int FB_DatasetCreateFromSchema(const char* schema, int64_t len, const char* para
   API_END();
 }
 
+// The schema of a dataset (bin mappers, bundles, feature names) as an opaque byte buffer that another process turns
+// into an empty dataset with the same bins: FB_DatasetCreateFromSerializedReference allocates num_row host rows and
+// opens it for streaming pushes. Parity: FLC_DatasetSerializeReferenceToBinary / FLC_DatasetCreateFromSerializedReference
+// / FLC_ByteBuffer*.
+int FB_DatasetSerializeReferenceToBinary(DatasetHandle handle, void** out_buffer, int32_t* out_len) {
+  API_BEGIN();
+  std::unique_ptr<std::vector<char>> buf(new std::vector<char>());
+  static_cast<Dataset*>(handle)->SerializeSchema(buf.get());
+  if (buf->size() > static_cast<size_t>(INT32_MAX)) Log::Fatal("The serialized reference exceeds 2 GB");
+  *out_len = static_cast<int32_t>(buf->size());
+  *out_buffer = buf.release();
+  API_END();
+}
+int FB_ByteBufferGetAt(void* buffer, int32_t index, uint8_t* out_val) {
+  API_BEGIN();
+  const std::vector<char>* b = static_cast<const std::vector<char>*>(buffer);
+  if (b == nullptr || index < 0 || static_cast<size_t>(index) >= b->size()) Log::Fatal("Byte buffer index %d is out of range", index);
+  *out_val = static_cast<uint8_t>((*b)[static_cast<size_t>(index)]);
+  API_END();
+}
+int FB_ByteBufferFree(void* buffer) { API_BEGIN(); delete static_cast<std::vector<char>*>(buffer); API_END(); }
+int FB_DatasetCreateFromSerializedReference(const void* ref_buffer, int32_t ref_buffer_size, int64_t num_row, int32_t num_classes, const char* parameters,
+                                            DatasetHandle* out) {
+  if (num_row < 0 || num_row > INT32_MAX) return FB_SetLastErrorForCompat("The row count must fit 32 bits");
+  if (FB_DatasetCreateFromSchema(static_cast<const char*>(ref_buffer), ref_buffer_size, parameters, out) != 0) return -1;
+  if (FB_DatasetInitRows(*out, static_cast<int32_t>(num_row), 0, num_row, 1) != 0) return -1;
+  (void)num_classes;   // the init-score layout is fixed by FB_DatasetInitStreaming when the caller opens the stream
+  return 0;
+}
+
 int FB_DatasetInitRows(DatasetHandle handle, int32_t nrow, int64_t global_row_offset, int64_t global_num_row, int host_bins) {
   API_BEGIN();
   ScopedTimer api_timer("FB_DatasetInitRows");
@@ -532,6 +562,45 @@ int FB_BoosterPredictForCSR(BoosterHandle handle, const void* indptr, int indptr
   *out_len = total;
   return 0;
 }
+
+// Feature contributions of CSR rows as a CSR matrix (zeros dropped): [rows x (features + 1) * trees-per-round]. The three
+// output arrays are allocated here and released by FB_BoosterFreePredictSparse. out_len[0] = stored values, out_len[1] =
+// entries of the row pointer. Parity: FLC_BoosterPredictSparseOutput (CSR form; the CSC form is not built).
+int FB_BoosterPredictSparseOutput(BoosterHandle handle, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr,
+                                  int64_t nelem, int64_t num_col, int predict_type, int start_iteration, int num_iteration, const char* parameter, int matrix_type,
+                                  int64_t* out_len, void** out_indptr, int32_t** out_indices, void** out_data) {
+  if (predict_type != 3) return FB_SetLastErrorForCompat("Sparse output is for feature contributions (predict_type = contrib)");
+  if (matrix_type != 0) return FB_SetLastErrorForCompat("Sparse prediction output is built for CSR input and output");
+  const int64_t nrow = nindptr - 1;
+  int64_t per_row = 0;
+  if (FB_BoosterCalcNumPredict(handle, 1, predict_type, start_iteration, num_iteration, &per_row) != 0) return -1;
+  std::vector<double> dense(static_cast<size_t>(std::max<int64_t>(1, nrow * per_row)));
+  int64_t len = 0;
+  if (FB_BoosterPredictForCSR(handle, indptr, indptr_type, indices, data, data_type, nindptr, nelem, num_col, predict_type, start_iteration, num_iteration, parameter, &len,
+                              dense.data()) != 0) return -1;
+  int64_t nnz = 0; for (int64_t i = 0; i < nrow * per_row; ++i) if (dense[static_cast<size_t>(i)] != 0.0) ++nnz;
+  const bool ptr64 = indptr_type != kI32, val32 = data_type == kF32;
+  void* op = malloc(static_cast<size_t>(nrow + 1) * (ptr64 ? 8 : 4));
+  int32_t* oi = static_cast<int32_t*>(malloc(static_cast<size_t>(std::max<int64_t>(1, nnz)) * 4));
+  void* od = malloc(static_cast<size_t>(std::max<int64_t>(1, nnz)) * (val32 ? 4 : 8));
+  if (op == nullptr || oi == nullptr || od == nullptr) { free(op); free(oi); free(od); return FB_SetLastErrorForCompat("Out of memory for the sparse output"); }
+  int64_t k = 0;
+  for (int64_t r = 0; r <= nrow; ++r) {
+    if (ptr64) static_cast<int64_t*>(op)[r] = k; else static_cast<int32_t*>(op)[r] = static_cast<int32_t>(k);
+    if (r == nrow) break;
+    for (int64_t c = 0; c < per_row; ++c) {
+      const double v = dense[static_cast<size_t>(r * per_row + c)];
+      if (v == 0.0) continue;
+      oi[k] = static_cast<int32_t>(c);
+      if (val32) static_cast<float*>(od)[k] = static_cast<float>(v); else static_cast<double*>(od)[k] = v;
+      ++k;
+    }
+  }
+  out_len[0] = nnz; out_len[1] = nrow + 1;
+  *out_indptr = op; *out_indices = oi; *out_data = od;
+  return 0;
+}
+int FB_BoosterFreePredictSparse(void* indptr, int32_t* indices, void* data) { free(indptr); free(indices); free(data); return 0; }
 
 int FB_DatasetCreateFromCSR(const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr, int64_t nelem,
                             int64_t num_col, const char* parameters, const DatasetHandle reference, DatasetHandle* out) {

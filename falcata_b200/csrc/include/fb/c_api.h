@@ -167,6 +167,16 @@ int FB_BoosterPredictForCSRSingleRowFastInit(BoosterHandle handle, int predict_t
                                              const char* parameter, void** out_fast_config);
 int FB_BoosterPredictForCSRSingleRowFast(void* fast_config, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr,
                                          int64_t nelem, int64_t* out_len, double* out_result);
+int FB_DatasetSerializeReferenceToBinary(DatasetHandle handle, void** out_buffer, int32_t* out_len);
+int FB_ByteBufferGetAt(void* buffer, int32_t index, uint8_t* out_val);
+int FB_ByteBufferFree(void* buffer);
+int FB_DatasetCreateFromSerializedReference(const void* ref_buffer, int32_t ref_buffer_size, int64_t num_row, int32_t num_classes, const char* parameters,
+                                            DatasetHandle* out);
+/* contributions of CSR rows as CSR (matrix_type 0); the outputs are allocated here, free them with FB_BoosterFreePredictSparse */
+int FB_BoosterPredictSparseOutput(BoosterHandle handle, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr,
+                                  int64_t nelem, int64_t num_col, int predict_type, int start_iteration, int num_iteration, const char* parameter, int matrix_type,
+                                  int64_t* out_len, void** out_indptr, int32_t** out_indices, void** out_data);
+int FB_BoosterFreePredictSparse(void* indptr, int32_t* indices, void* data);
 int FB_DatasetUpdateParamChecking(const char* old_parameters, const char* new_parameters);
 int FB_BoosterPredictForArrow(BoosterHandle handle, int64_t n_chunks, void* chunks, void* schema, int predict_type, int start_iteration, int num_iteration,
                               const char* parameter, int64_t* out_len, double* out_result);

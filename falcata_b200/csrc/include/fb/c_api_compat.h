@@ -38,6 +38,8 @@ struct ArrowArrayStream;
 #define C_API_PREDICT_RAW_SCORE 1
 #define C_API_PREDICT_LEAF_INDEX 2
 #define C_API_PREDICT_CONTRIB 3
+#define C_API_MATRIX_TYPE_CSR 0
+#define C_API_MATRIX_TYPE_CSC 1
 #define C_API_FEATURE_IMPORTANCE_SPLIT 0
 #define C_API_FEATURE_IMPORTANCE_GAIN 1
 
@@ -311,15 +313,14 @@ FB_COMPAT_BOTH(int, BoosterPredictForArrow, (BoosterHandle handle, int64_t n_chu
 FB_COMPAT_BOTH(int, NetworkInit, (const char* machines, int local_listen_port, int listen_time_out, int num_machines),
                FB_NetworkInit(machines, local_listen_port, listen_time_out, num_machines))
 FB_COMPAT_BOTH(int, DatasetAddFeaturesFrom, (DatasetHandle target, DatasetHandle source), ((void)target, (void)source, fb_compat_unsupported("DatasetAddFeaturesFrom is not available")))
-FB_COMPAT_BOTH(int, DatasetSerializeReferenceToBinary, (DatasetHandle handle, ByteBufferHandle* out, int32_t* out_len), ((void)handle, (void)out, (void)out_len, fb_compat_unsupported("serialized dataset references are not available: save the dataset with DatasetSaveBinary")))
+FB_COMPAT_BOTH(int, DatasetSerializeReferenceToBinary, (DatasetHandle handle, ByteBufferHandle* out, int32_t* out_len), FB_DatasetSerializeReferenceToBinary(handle, out, out_len))
 FB_COMPAT_BOTH(int, DatasetCreateFromSerializedReference, (const void* ref_buffer, int32_t ref_buffer_size, int64_t num_row, int32_t num_classes, const char* parameters, DatasetHandle* out),
-               ((void)ref_buffer, (void)ref_buffer_size, (void)num_row, (void)num_classes, (void)parameters, (void)out, fb_compat_unsupported("serialized dataset references are not available")))
-FB_COMPAT_BOTH(int, ByteBufferGetAt, (ByteBufferHandle handle, int32_t index, uint8_t* out_val), ((void)handle, (void)index, (void)out_val, fb_compat_unsupported("byte buffers are not available")))
-FB_COMPAT_BOTH(int, ByteBufferFree, (ByteBufferHandle handle), ((void)handle, 0))
+               FB_DatasetCreateFromSerializedReference(ref_buffer, ref_buffer_size, num_row, num_classes, parameters, out))
+FB_COMPAT_BOTH(int, ByteBufferGetAt, (ByteBufferHandle handle, int32_t index, uint8_t* out_val), FB_ByteBufferGetAt(handle, index, out_val))
+FB_COMPAT_BOTH(int, ByteBufferFree, (ByteBufferHandle handle), FB_ByteBufferFree(handle))
 FB_COMPAT_BOTH(int, BoosterPredictSparseOutput, (BoosterHandle handle, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr, int64_t nelem, int64_t num_col_or_row, int predict_type, int start_iteration, int num_iteration, const char* parameter, int matrix_type, int64_t* out_len, void** out_indptr, int32_t** out_indices, void** out_data),
-               ((void)handle, (void)indptr, (void)indptr_type, (void)indices, (void)data, (void)data_type, (void)nindptr, (void)nelem, (void)num_col_or_row, (void)predict_type, (void)start_iteration, (void)num_iteration, (void)parameter, (void)matrix_type, (void)out_len, (void)out_indptr, (void)out_indices, (void)out_data,
-                fb_compat_unsupported("sparse prediction output is not available: contributions come back dense")))
-FB_COMPAT_BOTH(int, BoosterFreePredictSparse, (void* indptr, int32_t* indices, void* data, int indptr_type, int data_type), ((void)indptr, (void)indices, (void)data, (void)indptr_type, (void)data_type, 0))
+               FB_BoosterPredictSparseOutput(handle, indptr, fb_compat_dtype(indptr_type), indices, data, fb_compat_dtype(data_type), nindptr, nelem, num_col_or_row, predict_type, start_iteration, num_iteration, parameter, matrix_type, out_len, out_indptr, out_indices, out_data))
+FB_COMPAT_BOTH(int, BoosterFreePredictSparse, (void* indptr, int32_t* indices, void* data, int indptr_type, int data_type), ((void)indptr_type, (void)data_type, FB_BoosterFreePredictSparse(indptr, indices, data)))
 
 #undef FB_COMPAT_BOTH
 #undef FB_COMPAT_NAME_GETTER

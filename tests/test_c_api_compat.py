@@ -113,6 +113,35 @@ int main(void) {
       CHECK(PFX(DatasetFree)(ds4));
     }
 #endif
+    {
+      /* a serialized reference read back byte by byte gives an empty dataset with the same bins; rows are then pushed */
+      ByteBufferHandle bb = NULL; int32_t blen = 0; uint8_t* copy; DatasetHandle ds5 = NULL; int n5 = 0, nf5 = 0;
+      CHECK(PFX(DatasetSerializeReferenceToBinary)(ds, &bb, &blen)); if (blen <= 0) { printf("empty reference\n"); return 1; }
+      copy = (uint8_t*)malloc((size_t)blen);
+      for (i = 0; i < blen; ++i) CHECK(PFX(ByteBufferGetAt)(bb, i, &copy[i]));
+      CHECK(PFX(ByteBufferFree)(bb));
+      CHECK(PFX(DatasetCreateFromSerializedReference)(copy, blen, N, 1, "max_bin=63", &ds5));
+      free(copy);
+      CHECK(PFX(DatasetInitStreaming)(ds5, 0, 0, 0, 1, 1, 1));
+      CHECK(PFX(DatasetPushRowsWithMetadata)(ds5, X, C_API_DTYPE_FLOAT64, N, F, 0, y, NULL, NULL, NULL, 0));
+      CHECK(PFX(DatasetMarkFinished)(ds5));
+      CHECK(PFX(DatasetGetNumData)(ds5, &n5)); CHECK(PFX(DatasetGetNumFeature)(ds5, &nf5)); if (n5 != N || nf5 != F) { printf("reference dataset %d x %d\n", n5, nf5); return 1; }
+      CHECK(PFX(DatasetFree)(ds5));
+    }
+    {
+      /* feature contributions of two CSR rows as CSR: the stored values add up to the raw prediction of each row */
+      int32_t ip[3] = {0, 2, 4}; int32_t idx[4] = {0, 1, 0, 1}; double val[4] = {0.25, -0.125, -0.3, 0.2}; double dense[2 * F] = {0}, raw[2];
+      int64_t lens[2] = {0, 0}; void* optr = NULL; int32_t* oidx = NULL; void* odat = NULL; double sum0 = 0, sum1 = 0; int64_t k;
+      dense[0] = 0.25; dense[1] = -0.125; dense[F] = -0.3; dense[F + 1] = 0.2;
+      CHECK(PFX(BoosterPredictForMat)(bst, dense, C_API_DTYPE_FLOAT64, 2, F, 1, C_API_PREDICT_RAW_SCORE, 0, -1, "", &out_len, raw));
+      CHECK(PFX(BoosterPredictSparseOutput)(bst, ip, C_API_DTYPE_INT32, idx, val, C_API_DTYPE_FLOAT64, 3, 4, F, C_API_PREDICT_CONTRIB, 0, -1, "", C_API_MATRIX_TYPE_CSR, lens, &optr, &oidx, &odat));
+      if (lens[1] != 3 || lens[0] <= 0 || ((int32_t*)optr)[2] != lens[0]) { printf("sparse output shape %lld %lld\n", (long long)lens[0], (long long)lens[1]); return 1; }
+      for (k = ((int32_t*)optr)[0]; k < ((int32_t*)optr)[1]; ++k) sum0 += ((double*)odat)[k];
+      for (k = ((int32_t*)optr)[1]; k < ((int32_t*)optr)[2]; ++k) { if (oidx[k] < 0 || oidx[k] > F) return 1; sum1 += ((double*)odat)[k]; }
+      if (fabs(sum0 - raw[0]) > 1e-9 || fabs(sum1 - raw[1]) > 1e-9) { printf("contributions %g %g against %g %g\n", sum0, sum1, raw[0], raw[1]); return 1; }
+      CHECK(PFX(BoosterFreePredictSparse)(optr, oidx, odat, C_API_DTYPE_INT32, C_API_DTYPE_FLOAT64));
+      if (PFX(BoosterPredictSparseOutput)(bst, ip, C_API_DTYPE_INT32, idx, val, C_API_DTYPE_FLOAT64, 3, 4, F, C_API_PREDICT_NORMAL, 0, -1, "", C_API_MATRIX_TYPE_CSR, lens, &optr, &oidx, &odat) == 0) { printf("sparse output of plain predictions should be refused\n"); return 1; }
+    }
     PFX(SetLastError)("set by the caller"); if (strcmp(PFX(GetLastError)(), "set by the caller") != 0) { printf("last error\n"); return 1; }
   }
   CHECK(PFX(NetworkInit)("127.0.0.1:1", 1, 1, 1));   /* one machine: nothing to connect */
