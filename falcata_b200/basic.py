@@ -762,7 +762,21 @@ class Dataset:
         return int(out.value)
 
     def add_features_from(self, other: "Dataset") -> "Dataset":
-        """Append the columns of `other` (same rows). Both datasets need their raw data; the result is re-binned."""
+        """Append the columns of `other` (same rows). Two constructed datasets with host-resident bins are merged as they
+        are binned (mappers, feature groups and bin columns are concatenated); otherwise both need their raw data and the
+        result is binned again."""
+        if self._handle is not None and other._handle is not None:
+            try:
+                _safe_call(_lib().FB_DatasetAddFeaturesFrom(self._handle, other._handle))
+                if self.data is not None and other.data is not None and not _is_cuda_array(self.data) and not _is_cuda_array(other.data):
+                    self.data = np.concatenate([_to_numpy_2d(self.data).astype(np.float64), _to_numpy_2d(other.data).astype(np.float64)], axis=1)
+                else:
+                    self.data = None
+                self.feature_name = "auto"
+                return self
+            except FalcataError:
+                if self.data is None or other.data is None:
+                    raise
         if self.data is None or other.data is None:
             raise RuntimeError("add_features_from needs the raw data of both datasets (free_raw_data=False)")
         a, b = _to_numpy_2d(self.data), _to_numpy_2d(other.data)

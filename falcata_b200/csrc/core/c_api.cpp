@@ -229,6 +229,12 @@ int FB_DatasetCreateFromSerializedReference(const void* ref_buffer, int32_t ref_
   return 0;
 }
 
+int FB_DatasetAddFeaturesFrom(DatasetHandle target, DatasetHandle source) {
+  API_BEGIN();
+  static_cast<Dataset*>(target)->AddFeaturesFrom(*static_cast<const Dataset*>(source));
+  API_END();
+}
+
 int FB_DatasetInitRows(DatasetHandle handle, int32_t nrow, int64_t global_row_offset, int64_t global_num_row, int host_bins) {
   API_BEGIN();
   ScopedTimer api_timer("FB_DatasetInitRows");

@@ -293,6 +293,53 @@ void Dataset::CopySchemaFrom(const Dataset& ref) {
   bin_bytes = ref.bin_bytes; row_stride = ref.num_groups; keep_raw = ref.keep_raw;
 }
 
+void Dataset::AddFeaturesFrom(const Dataset& other) {
+  if (other.num_data != num_data) Log::Fatal("Cannot add features from a dataset with %d rows to one with %d rows", other.num_data, num_data);
+  if (!has_host_bins() || !other.has_host_bins()) Log::Fatal("AddFeaturesFrom needs host-resident bins in both datasets");
+  if (device != nullptr) { FreeDeviceDataset(device); device = nullptr; }   // a device copy would be stale
+  const int f0 = num_features, t0 = num_total_features, g0 = num_groups, b0 = num_total_bin;
+  for (const auto& m : other.mappers) mappers.emplace_back(m ? new BinMapper(*m) : nullptr);
+  for (int u : other.used_feature_map) used_feature_map.push_back(u < 0 ? -1 : u + f0);
+  for (int r : other.real_feature_idx) real_feature_idx.push_back(r + t0);
+  for (const auto& g : other.group_features) { std::vector<int> v; for (int f : g) v.push_back(f + f0); group_features.push_back(std::move(v)); }
+  for (int s : other.group_bin_start) group_bin_start.push_back(s + b0);
+  group_num_bin.insert(group_num_bin.end(), other.group_num_bin.begin(), other.group_num_bin.end());
+  for (FeatureMeta m : other.feature_meta) { m.hist_offset += b0; m.group += g0; m.real_index += t0; feature_meta.push_back(m); }
+  if (!feature_names.empty() || !other.feature_names.empty()) {
+    std::vector<std::string> names = feature_names;
+    for (int j = static_cast<int>(names.size()); j < t0; ++j) names.push_back("Column_" + std::to_string(j));
+    for (int j = 0; j < other.num_total_features; ++j) {
+      // a default name ("Column_<j>") moves with the column's new position; a given name is kept
+      const bool given = j < static_cast<int>(other.feature_names.size()) && other.feature_names[j] != "Column_" + std::to_string(j);
+      names.push_back(given ? other.feature_names[j] : "Column_" + std::to_string(t0 + j));
+    }
+    feature_names.swap(names);
+  }
+  for (int c : other.categorical_features) categorical_features.push_back(c + t0);
+  // bin columns: rows of [this groups | other groups], in the wider of the two element types
+  const int ng = g0 + other.num_groups;
+  const bool wide = bin_bytes == 2 || other.bin_bytes == 2;
+  auto cell = [](const Dataset& d, data_size_t i, int g) { return d.bin_bytes == 1 ? static_cast<int>(d.bins8[static_cast<size_t>(i) * d.row_stride + g]) : static_cast<int>(d.bins16[static_cast<size_t>(i) * d.row_stride + g]); };
+  std::vector<uint8_t> n8; std::vector<uint16_t> n16;
+  if (wide) n16.assign(static_cast<size_t>(num_data) * ng, 0); else n8.assign(static_cast<size_t>(num_data) * ng, 0);
+  for (data_size_t i = 0; i < num_data; ++i) {
+    for (int g = 0; g < g0; ++g) { const int v = cell(*this, i, g); if (wide) n16[static_cast<size_t>(i) * ng + g] = static_cast<uint16_t>(v); else n8[static_cast<size_t>(i) * ng + g] = static_cast<uint8_t>(v); }
+    for (int g = 0; g < other.num_groups; ++g) { const int v = cell(other, i, g); if (wide) n16[static_cast<size_t>(i) * ng + g0 + g] = static_cast<uint16_t>(v); else n8[static_cast<size_t>(i) * ng + g0 + g] = static_cast<uint8_t>(v); }
+  }
+  bins8.swap(n8); bins16.swap(n16); bin_bytes = wide ? 2 : 1; row_stride = ng;
+  if (has_raw() && other.has_raw()) {
+    std::vector<float> r(static_cast<size_t>(num_data) * (t0 + other.num_total_features));
+    for (data_size_t i = 0; i < num_data; ++i) {
+      std::copy(raw.begin() + static_cast<size_t>(i) * t0, raw.begin() + static_cast<size_t>(i + 1) * t0, r.begin() + static_cast<size_t>(i) * (t0 + other.num_total_features));
+      std::copy(other.raw.begin() + static_cast<size_t>(i) * other.num_total_features, other.raw.begin() + static_cast<size_t>(i + 1) * other.num_total_features,
+                r.begin() + static_cast<size_t>(i) * (t0 + other.num_total_features) + t0);
+    }
+    raw.swap(r);
+  } else { raw.clear(); keep_raw = false; }
+  num_features += other.num_features; num_total_features += other.num_total_features; num_groups = ng; num_total_bin += other.num_total_bin;
+  max_group_bin = std::max(max_group_bin, other.max_group_bin);
+}
+
 void Dataset::AllocateRows(data_size_t n) {
   num_data = n; metadata.num_data = n;
   if (global_num_data == 0) global_num_data = n;

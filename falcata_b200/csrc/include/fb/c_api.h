@@ -177,6 +177,8 @@ int FB_BoosterPredictSparseOutput(BoosterHandle handle, const void* indptr, int 
                                   int64_t nelem, int64_t num_col, int predict_type, int start_iteration, int num_iteration, const char* parameter, int matrix_type,
                                   int64_t* out_len, void** out_indptr, int32_t** out_indices, void** out_data);
 int FB_BoosterFreePredictSparse(void* indptr, int32_t* indices, void* data);
+/* appends the (host-binned) features of `source` behind those of `target`; both hold the same rows */
+int FB_DatasetAddFeaturesFrom(DatasetHandle target, DatasetHandle source);
 int FB_DatasetUpdateParamChecking(const char* old_parameters, const char* new_parameters);
 int FB_BoosterPredictForArrow(BoosterHandle handle, int64_t n_chunks, void* chunks, void* schema, int predict_type, int start_iteration, int num_iteration,
                               const char* parameter, int64_t* out_len, double* out_result);

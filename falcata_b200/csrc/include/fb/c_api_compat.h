@@ -312,7 +312,7 @@ FB_COMPAT_BOTH(int, BoosterPredictForArrow, (BoosterHandle handle, int64_t n_chu
 /* ---- no counterpart: these fail with a message ---- */
 FB_COMPAT_BOTH(int, NetworkInit, (const char* machines, int local_listen_port, int listen_time_out, int num_machines),
                FB_NetworkInit(machines, local_listen_port, listen_time_out, num_machines))
-FB_COMPAT_BOTH(int, DatasetAddFeaturesFrom, (DatasetHandle target, DatasetHandle source), ((void)target, (void)source, fb_compat_unsupported("DatasetAddFeaturesFrom is not available")))
+FB_COMPAT_BOTH(int, DatasetAddFeaturesFrom, (DatasetHandle target, DatasetHandle source), FB_DatasetAddFeaturesFrom(target, source))
 FB_COMPAT_BOTH(int, DatasetSerializeReferenceToBinary, (DatasetHandle handle, ByteBufferHandle* out, int32_t* out_len), FB_DatasetSerializeReferenceToBinary(handle, out, out_len))
 FB_COMPAT_BOTH(int, DatasetCreateFromSerializedReference, (const void* ref_buffer, int32_t ref_buffer_size, int64_t num_row, int32_t num_classes, const char* parameters, DatasetHandle* out),
                FB_DatasetCreateFromSerializedReference(ref_buffer, ref_buffer_size, num_row, num_classes, parameters, out))

@@ -97,6 +97,9 @@ class Dataset {
                        const std::vector<int>& categorical);
   // Copy mappers/groups from another dataset (validation data aligned with training data).
   void CopySchemaFrom(const Dataset& ref);
+  // Appends the features of `other` (the same rows, binned on the host) behind this dataset's: mappers, feature groups
+  // and bin columns are concatenated, nothing is binned again. Parity: Dataset::AddFeaturesFrom (src/io/dataset.cpp).
+  void AddFeaturesFrom(const Dataset& other);
   void AllocateRows(data_size_t n);
   // Bin rows [row_begin, row_begin+n) from a dense host matrix.
   void PushDense(const void* data, int dtype, data_size_t n, int ncol, bool row_major, data_size_t row_begin);

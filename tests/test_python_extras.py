@@ -483,3 +483,22 @@ def test_debug_environment_switches_dump_splits_and_cap_the_tree():
     assert text.count("[split] leaf") == 6               # the host learner's own lines
     assert text.count("[dump] tree") == 2 and text.count("[dump]   node") == 6 and text.count("[dump]   leaf") == 8
     assert "maxsplits=3: num_leaves lowered from 15 to 4" in text
+
+
+def test_add_features_from_merges_binned_datasets():
+    """Dataset.add_features_from on two constructed datasets concatenates mappers, feature groups and bin columns without
+    binning again (reference: Dataset::AddFeaturesFrom); training on the merged dataset gives the model of a dataset built
+    from the concatenated matrix."""
+    rng = np.random.default_rng(8)
+    X = rng.normal(size=(3000, 9)).astype(np.float32)
+    X[::17, 5] = np.nan
+    y = (X[:, 0] + X[:, 6] * X[:, 7] > 0).astype(np.float32)
+    p = {"objective": "binary", "num_leaves": 15, "verbosity": -1, "device_type": "cpu", "max_bin": 63, "min_data_in_leaf": 5}
+    a = fb.Dataset(X[:, :4], y, params=p, free_raw_data=True).construct()
+    b = fb.Dataset(X[:, 4:], params=p, free_raw_data=True).construct()
+    a.add_features_from(b)
+    assert a.num_feature() == 9 and a.num_data() == 3000
+    merged = fb.train(p, a, 8)
+    whole = fb.train(p, fb.Dataset(X, y, params=p), 8)
+    np.testing.assert_allclose(merged.predict(X), whole.predict(X), rtol=0, atol=1e-12)
+    assert merged.feature_name() == whole.feature_name()
