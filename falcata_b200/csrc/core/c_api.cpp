@@ -571,15 +571,45 @@ int FB_BoosterPredictForCSR(BoosterHandle handle, const void* indptr, int indptr
 
 // Feature contributions of CSR rows as a CSR matrix (zeros dropped): [rows x (features + 1) * trees-per-round]. The three
 // output arrays are allocated here and released by FB_BoosterFreePredictSparse. out_len[0] = stored values, out_len[1] =
-// entries of the row pointer. Parity: FLC_BoosterPredictSparseOutput (CSR form; the CSC form is not built).
+// entries of the row pointer. matrix_type 1: CSC in and out (num_col is then the number of rows, the pointer array runs
+// over the output's columns). Parity: FLC_BoosterPredictSparseOutput.
 int FB_BoosterPredictSparseOutput(BoosterHandle handle, const void* indptr, int indptr_type, const int32_t* indices, const void* data, int data_type, int64_t nindptr,
                                   int64_t nelem, int64_t num_col, int predict_type, int start_iteration, int num_iteration, const char* parameter, int matrix_type,
                                   int64_t* out_len, void** out_indptr, int32_t** out_indices, void** out_data) {
   if (predict_type != 3) return FB_SetLastErrorForCompat("Sparse output is for feature contributions (predict_type = contrib)");
-  if (matrix_type != 0) return FB_SetLastErrorForCompat("Sparse prediction output is built for CSR input and output");
-  const int64_t nrow = nindptr - 1;
+  if (matrix_type != 0 && matrix_type != 1) return FB_SetLastErrorForCompat("matrix_type is 0 (CSR) or 1 (CSC)");
   int64_t per_row = 0;
   if (FB_BoosterCalcNumPredict(handle, 1, predict_type, start_iteration, num_iteration, &per_row) != 0) return -1;
+  if (matrix_type == 1) {
+    // CSC in (num_col here = the number of rows), CSC out: column c of the output lists the rows with a non-zero contribution
+    const int64_t rows = num_col;
+    std::vector<double> dense_c(static_cast<size_t>(std::max<int64_t>(1, rows * per_row)));
+    int64_t len_c = 0;
+    if (FB_BoosterPredictForCSC(handle, indptr, indptr_type, indices, data, data_type, nindptr, nelem, rows, predict_type, start_iteration, num_iteration, parameter, &len_c,
+                                dense_c.data()) != 0) return -1;
+    int64_t nnz_c = 0; for (int64_t i = 0; i < rows * per_row; ++i) if (dense_c[static_cast<size_t>(i)] != 0.0) ++nnz_c;
+    const bool p64 = indptr_type != kI32, v32 = data_type == kF32;
+    void* cp = malloc(static_cast<size_t>(per_row + 1) * (p64 ? 8 : 4));
+    int32_t* ci = static_cast<int32_t*>(malloc(static_cast<size_t>(std::max<int64_t>(1, nnz_c)) * 4));
+    void* cd = malloc(static_cast<size_t>(std::max<int64_t>(1, nnz_c)) * (v32 ? 4 : 8));
+    if (cp == nullptr || ci == nullptr || cd == nullptr) { free(cp); free(ci); free(cd); return FB_SetLastErrorForCompat("Out of memory for the sparse output"); }
+    int64_t w = 0;
+    for (int64_t c = 0; c <= per_row; ++c) {
+      if (p64) static_cast<int64_t*>(cp)[c] = w; else static_cast<int32_t*>(cp)[c] = static_cast<int32_t>(w);
+      if (c == per_row) break;
+      for (int64_t r = 0; r < rows; ++r) {
+        const double v = dense_c[static_cast<size_t>(r * per_row + c)];
+        if (v == 0.0) continue;
+        ci[w] = static_cast<int32_t>(r);
+        if (v32) static_cast<float*>(cd)[w] = static_cast<float>(v); else static_cast<double*>(cd)[w] = v;
+        ++w;
+      }
+    }
+    out_len[0] = nnz_c; out_len[1] = per_row + 1;
+    *out_indptr = cp; *out_indices = ci; *out_data = cd;
+    return 0;
+  }
+  const int64_t nrow = nindptr - 1;
   std::vector<double> dense(static_cast<size_t>(std::max<int64_t>(1, nrow * per_row)));
   int64_t len = 0;
   if (FB_BoosterPredictForCSR(handle, indptr, indptr_type, indices, data, data_type, nindptr, nelem, num_col, predict_type, start_iteration, num_iteration, parameter, &len,

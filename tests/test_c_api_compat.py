@@ -140,6 +140,15 @@ int main(void) {
       for (k = ((int32_t*)optr)[1]; k < ((int32_t*)optr)[2]; ++k) { if (oidx[k] < 0 || oidx[k] > F) return 1; sum1 += ((double*)odat)[k]; }
       if (fabs(sum0 - raw[0]) > 1e-9 || fabs(sum1 - raw[1]) > 1e-9) { printf("contributions %g %g against %g %g\n", sum0, sum1, raw[0], raw[1]); return 1; }
       CHECK(PFX(BoosterFreePredictSparse)(optr, oidx, odat, C_API_DTYPE_INT32, C_API_DTYPE_FLOAT64));
+      {
+        /* the same two rows as CSC, contributions back as CSC: F + 1 output columns, row indices below 2, the same total */
+        int32_t cp[F + 1] = {0, 2, 4, 4, 4}; int32_t ridx[4] = {0, 1, 0, 1}; double cval[4] = {0.25, -0.3, -0.125, 0.2}; double total = 0;
+        CHECK(PFX(BoosterPredictSparseOutput)(bst, cp, C_API_DTYPE_INT32, ridx, cval, C_API_DTYPE_FLOAT64, F + 1, 4, 2, C_API_PREDICT_CONTRIB, 0, -1, "", C_API_MATRIX_TYPE_CSC, lens, &optr, &oidx, &odat));
+        if (lens[1] != F + 2) { printf("csc pointer length %lld\n", (long long)lens[1]); return 1; }
+        for (k = 0; k < lens[0]; ++k) { if (oidx[k] < 0 || oidx[k] > 1) return 1; total += ((double*)odat)[k]; }
+        if (fabs(total - raw[0] - raw[1]) > 1e-9) { printf("csc contributions %g against %g\n", total, raw[0] + raw[1]); return 1; }
+        CHECK(PFX(BoosterFreePredictSparse)(optr, oidx, odat, C_API_DTYPE_INT32, C_API_DTYPE_FLOAT64));
+      }
       if (PFX(BoosterPredictSparseOutput)(bst, ip, C_API_DTYPE_INT32, idx, val, C_API_DTYPE_FLOAT64, 3, 4, F, C_API_PREDICT_NORMAL, 0, -1, "", C_API_MATRIX_TYPE_CSR, lens, &optr, &oidx, &odat) == 0) { printf("sparse output of plain predictions should be refused\n"); return 1; }
     }
     PFX(SetLastError)("set by the caller"); if (strcmp(PFX(GetLastError)(), "set by the caller") != 0) { printf("last error\n"); return 1; }
