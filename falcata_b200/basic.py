@@ -1234,6 +1234,10 @@ class Booster:
             _safe_call(lib.FB_BoosterPredictForDeviceMat(self._handle, ctypes.c_void_p(t.data_ptr()), code, ctypes.c_int32(nrow), ctypes.c_int32(ncol), 1,
                                                          ptype, start_iteration, num_iteration, ctypes.c_void_p(out.data_ptr())))
             return out[0] if k == 1 else out.t().contiguous()
+        if hasattr(data, "tocsr") and not isinstance(data, np.ndarray):
+            # scipy sparse input: the rows are densified in blocks inside the library, never as one matrix; contributions
+            # come back sparse as well
+            return self._predict_csr(data.tocsr(), ptype, start_iteration, num_iteration, pred_leaf, pred_contrib, kwargs)
         if isinstance(data, (str, os.PathLike)):
             arr = np.loadtxt(str(data), delimiter="," if str(data).endswith(".csv") else None, skiprows=1 if data_has_header else 0, ndmin=2)[:, 1:]
         else:
@@ -1251,6 +1255,44 @@ class Booster:
         if out.size != nrow:
             return out.reshape(nrow, -1)
         return out
+
+    def _predict_csr(self, csr: Any, ptype: int, start_iteration: int, num_iteration: int, pred_leaf: bool, pred_contrib: bool, kwargs: Dict[str, Any]) -> Any:
+        lib = _lib()
+        nrow, ncol = csr.shape
+        indptr = np.ascontiguousarray(csr.indptr, dtype=np.int64 if csr.indptr.dtype == np.int64 else np.int32)
+        indices = np.ascontiguousarray(csr.indices, dtype=np.int32)
+        values = np.ascontiguousarray(csr.data, dtype=np.float32 if csr.data.dtype == np.float32 else np.float64)
+        ptr_code = 8 if indptr.dtype == np.int64 else 7
+        val_code = 0 if values.dtype == np.float32 else 1
+        if pred_contrib:
+            import scipy.sparse as sp
+
+            lens = (ctypes.c_int64 * 2)(0, 0)
+            optr, oidx, odat = ctypes.c_void_p(), ctypes.POINTER(ctypes.c_int32)(), ctypes.c_void_p()
+            _safe_call(lib.FB_BoosterPredictSparseOutput(self._handle, indptr.ctypes.data_as(ctypes.c_void_p), ptr_code, indices.ctypes.data_as(ctypes.c_void_p),
+                                                         values.ctypes.data_as(ctypes.c_void_p), val_code, ctypes.c_int64(len(indptr)), ctypes.c_int64(len(values)),
+                                                         ctypes.c_int64(ncol), 3, start_iteration, num_iteration, _param_str(kwargs), 0, lens,
+                                                         ctypes.byref(optr), ctypes.byref(oidx), ctypes.byref(odat)))
+            nnz, nptr = int(lens[0]), int(lens[1])
+            try:
+                out_ptr = np.ctypeslib.as_array(ctypes.cast(optr, ctypes.POINTER(ctypes.c_int64 if ptr_code == 8 else ctypes.c_int32)), shape=(nptr,)).copy()
+                out_idx = np.ctypeslib.as_array(oidx, shape=(max(nnz, 1),))[:nnz].copy()
+                out_val = np.ctypeslib.as_array(ctypes.cast(odat, ctypes.POINTER(ctypes.c_float if val_code == 0 else ctypes.c_double)), shape=(max(nnz, 1),))[:nnz].copy()
+            finally:
+                _safe_call(lib.FB_BoosterFreePredictSparse(optr, oidx, odat))
+            per_row = ctypes.c_int64(0)
+            _safe_call(lib.FB_BoosterCalcNumPredict(self._handle, 1, 3, start_iteration, num_iteration, ctypes.byref(per_row)))
+            return sp.csr_matrix((out_val, out_idx, out_ptr), shape=(nrow, int(per_row.value)))
+        n_out = ctypes.c_int64(0)
+        _safe_call(lib.FB_BoosterCalcNumPredict(self._handle, nrow, ptype, start_iteration, num_iteration, ctypes.byref(n_out)))
+        out = np.empty(n_out.value, dtype=np.float64)
+        ln = ctypes.c_int64(0)
+        _safe_call(lib.FB_BoosterPredictForCSR(self._handle, indptr.ctypes.data_as(ctypes.c_void_p), ptr_code, indices.ctypes.data_as(ctypes.c_void_p),
+                                               values.ctypes.data_as(ctypes.c_void_p), val_code, ctypes.c_int64(len(indptr)), ctypes.c_int64(len(values)), ctypes.c_int64(ncol),
+                                               ptype, start_iteration, num_iteration, _param_str(kwargs), ctypes.byref(ln), out.ctypes.data_as(ctypes.c_void_p)))
+        if pred_leaf:
+            return out.astype(np.int32).reshape(nrow, -1)
+        return out.reshape(nrow, -1) if out.size != nrow else out
 
     def _has_linear_trees(self) -> bool:
         if self.train_set is not None:   # a training booster knows from its parameters

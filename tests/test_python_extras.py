@@ -502,3 +502,23 @@ def test_add_features_from_merges_binned_datasets():
     whole = fb.train(p, fb.Dataset(X, y, params=p), 8)
     np.testing.assert_allclose(merged.predict(X), whole.predict(X), rtol=0, atol=1e-12)
     assert merged.feature_name() == whole.feature_name()
+
+
+def test_sparse_input_predicts_through_csr_and_returns_sparse_contributions():
+    """A scipy sparse matrix is predicted through the CSR entry points (densified in blocks inside the library); feature
+    contributions come back as a sparse matrix whose rows add up to the raw scores, equal to the dense route."""
+    import scipy.sparse as sp
+
+    rng = np.random.default_rng(4)
+    dense = rng.normal(size=(1500, 12)) * (rng.random(size=(1500, 12)) < 0.3)
+    y = (dense[:, 0] - dense[:, 3] + 0.5 * dense[:, 7] > 0).astype(np.float32)
+    bst = fb.train({"objective": "binary", "num_leaves": 15, "verbosity": -1, "device_type": "cpu", "min_data_in_leaf": 5}, fb.Dataset(dense, y), 10)
+    for make in (sp.csr_matrix, sp.csc_matrix, sp.coo_matrix):
+        m = make(dense)
+        np.testing.assert_allclose(bst.predict(m), bst.predict(dense), rtol=0, atol=1e-12)
+        np.testing.assert_array_equal(bst.predict(m, pred_leaf=True), bst.predict(dense, pred_leaf=True))
+    contrib = bst.predict(sp.csr_matrix(dense), pred_contrib=True)
+    assert sp.issparse(contrib) and contrib.shape == (1500, 13)
+    np.testing.assert_allclose(contrib.toarray(), bst.predict(dense, pred_contrib=True), rtol=0, atol=1e-12)
+    np.testing.assert_allclose(np.asarray(contrib.sum(axis=1)).ravel(), bst.predict(dense, raw_score=True), atol=1e-9)
+    assert contrib.nnz < 1500 * 13   # unused features have no entries
