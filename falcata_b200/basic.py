@@ -918,6 +918,10 @@ class Booster:
             nm = self.params.get("num_machines", self.params.get("num_machine"))
             machines = self.params.get("machines", self.params.get("workers", self.params.get("nodes")))
             if nm is not None and int(nm) > 1 and machines:
+                if train_set._handle is not None:
+                    raise FalcataError("The training Dataset was constructed before the machines were connected, so its bins were found on this "
+                                       "process's rows alone. Leave the Dataset unconstructed (the Booster constructs it after joining the network) "
+                                       "or call falcata_b200.network_init(...) before constructing it and drop the machine list from the parameters.")
                 self.set_network(machines, int(self.params.get("local_listen_port", self.params.get("local_port", self.params.get("port", 12400)))),
                                  int(self.params.get("time_out", 120)), int(nm))
             with _tag("booster: dataset construct"):
