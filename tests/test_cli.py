@@ -144,3 +144,12 @@ def test_examples_run(tmp_path):
     for name in ("train.conf", "predict.conf"):
         out = _run(tmp_path, "config=" + os.path.join(root, "examples", "cli", name), "num_trees=10")
     assert "Finished prediction" in out and len(np.loadtxt(tmp_path / "examples" / "cli" / "predictions.txt")) == 400
+    # the torchrun example with two CPU workers: both ranks report the model that one process trains
+    import re
+
+    multi = os.path.join(root, "examples", "multi_gpu.py")
+    two = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1", "--nproc-per-node", "2", multi, "--device", "cpu",
+                          "--rows", "12000", "--rounds", "4"], capture_output=True, text=True, timeout=600)
+    one = subprocess.run([sys.executable, multi, "--device", "cpu", "--rows", "12000", "--rounds", "4"], capture_output=True, text=True, timeout=600)
+    md5s = re.findall(r"model md5 ([0-9a-f]{32})", two.stdout + two.stderr) + re.findall(r"model md5 ([0-9a-f]{32})", one.stdout + one.stderr)
+    assert len(md5s) == 3 and len(set(md5s)) == 1, two.stdout + two.stderr + one.stdout + one.stderr
