@@ -922,6 +922,9 @@ class Booster:
                     raise FalcataError("The training Dataset was constructed before the machines were connected, so its bins were found on this "
                                        "process's rows alone. Leave the Dataset unconstructed (the Booster constructs it after joining the network) "
                                        "or call falcata_b200.network_init(...) before constructing it and drop the machine list from the parameters.")
+                learner = self.params.get("tree_learner", self.params.get("tree", self.params.get("tree_type", self.params.get("tree_learner_type"))))
+                if learner is not None:
+                    train_set.params["tree_learner"] = learner   # feature-parallel: every process holds all rows, nothing is exchanged at binning
                 self.set_network(machines, int(self.params.get("local_listen_port", self.params.get("local_port", self.params.get("port", 12400)))),
                                  int(self.params.get("time_out", 120)), int(nm))
             with _tag("booster: dataset construct"):

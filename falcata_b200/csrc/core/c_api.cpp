@@ -108,7 +108,8 @@ int FB_DatasetCreateFromMat(const void* data, int dtype, int32_t nrow, int32_t n
     // Processes of the TCP mesh (FB_NetworkInit) each hold their own rows, numbered in rank order: every process draws
     // the rows of the one global sample that fall into its range and the pieces are concatenated on all of them, so the
     // bins are those of a single process holding all rows.
-    const bool distributed = SocketNetworkActive() && Network::active();
+    // (feature-parallel training keeps all rows on every process: nothing to exchange, the same sample everywhere)
+    const bool distributed = SocketNetworkActive() && Network::active() && cfg.tree_learner != "feature";
     if (distributed) GatherRowCounts(nrow, &mesh_offset, &mesh_total);
     const int64_t total_rows = distributed ? mesh_total : nrow;
     const double frac = std::min(1.0, static_cast<double>(cfg.bin_construct_sample_cnt) / static_cast<double>(std::max<int64_t>(1, total_rows)));

@@ -107,7 +107,8 @@ Dataset* LoadDatasetFromFile(const std::string& path, const Config& cfg, const D
   // every process has read its own rows and the bin sample is the concatenation of every process's sample in rank order;
   // without it every process has read the whole file, draws the same sample and keeps its block of consecutive rows. Either
   // way all processes find the same bin boundaries, and the rows carry their global numbers.
-  const bool distributed = reference == nullptr && SocketNetworkActive() && Network::active();
+  // Feature-parallel training is the exception: every process keeps all rows.
+  const bool distributed = reference == nullptr && SocketNetworkActive() && Network::active() && cfg.tree_learner != "feature";
   data_size_t keep_begin = 0, keep_end = n; int64_t global_offset = 0, global_total = n;
   if (distributed) {
     if (!groupv.empty() && !cfg.pre_partition) Log::Fatal("Distributed ranking data must be pre-partitioned by query (pre_partition=true, one file per machine)");

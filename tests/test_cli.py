@@ -119,6 +119,9 @@ def test_cli_distributed_training_over_tcp(tmp_path):
     # one shared file, every process keeps its block of rows
     models, _ = launch(2, "pre_partition = false\ntree_learner = data\n", ["train.txt", "train.txt"], "sh")
     assert model_body(models[0]) == model_body(models[1]) == model_body(single)
+    # feature-parallel: every process loads the whole file and searches its share of the features
+    models, _ = launch(2, "tree_learner = feature\n", ["train.txt", "train.txt"], "fp")
+    assert model_body(models[0]) == model_body(models[1]) == model_body(single)
     # three processes, voting
     thirds = np.array_split(full, 3)
     for r in range(3):
