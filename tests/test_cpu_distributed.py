@@ -129,3 +129,47 @@ def test_python_api_trains_over_the_tcp_mesh_like_one_process(tmp_path):
         assert pr.returncode == 0, o
         outs.append(o)
     assert model_of(outs[0]) == model_of(outs[1]) == model_of(single.stdout)
+
+
+def test_a_process_that_leaves_the_tcp_mesh_ends_the_others_with_an_error(tmp_path):
+    """Failure detection on the TCP mesh, made on the host: one process exits right after the mesh is up; the other's next
+    collective finds the connection closed and comes back with an error instead of waiting."""
+    import socket
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = str(Path(__file__).resolve().parents[1])
+    script = tmp_path / "leaver.py"
+    script.write_text(
+        "import os, sys, numpy as np\n"
+        f"sys.path.insert(0, {root!r})\n"
+        "import falcata_b200 as fb\n"
+        "rank, ports = int(sys.argv[1]), [int(p) for p in sys.argv[2].split(',')]\n"
+        "fb.network_init(','.join(f'127.0.0.1:{q}' for q in ports), ports[rank], 1, 2)\n"
+        "if rank == 1:\n"
+        "    os._exit(0)                      # leaves without a word\n"
+        "rng = np.random.RandomState(0); X = rng.randn(2000, 5); y = (X[:, 0] > 0).astype(float)\n"
+        "try:\n"
+        "    fb.train({'objective': 'binary', 'tree_learner': 'data', 'device_type': 'cpu', 'verbosity': -1}, fb.Dataset(X, y), 3)\n"
+        "except fb.FalcataError as e:\n"
+        "    print('ERROR', e); sys.exit(5)\n"
+        "print('trained'); sys.exit(0)\n")
+    socks = [socket.socket() for _ in range(2)]
+    for s in socks:
+        s.bind(("127.0.0.1", 0))
+    ports = ",".join(str(s.getsockname()[1]) for s in socks)
+    for s in socks:
+        s.close()
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), ports], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = []
+    for pr in procs:
+        try:
+            o, _ = pr.communicate(timeout=120)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        outs.append((pr.returncode, o))
+    assert outs[1][0] == 0
+    assert outs[0][0] == 5 and "ERROR" in outs[0][1] and ("closed its connection" in outs[0][1] or "Socket" in outs[0][1]), outs[0][1]
