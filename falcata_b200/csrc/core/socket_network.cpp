@@ -38,6 +38,7 @@ namespace {
 struct Mesh {
   int rank = 0, world = 1, listen_fd = -1;
   std::vector<int> fd;   // fd[r]: connection to rank r (-1 for this rank)
+  int op_timeout_ms = 600000;   // a collective without progress for this long ends with an error (time_out, in minutes, at init)
   bool up = false;
 };
 Mesh g_mesh;
@@ -77,9 +78,9 @@ void SendRecv(int fd_s, const char* sp, size_t sn, int fd_r, char* rp, size_t rn
       if (sn > 0) { p[np].fd = fd_s; p[np].events = POLLOUT; p[np].revents = 0; is = np++; }
       if (rn > 0) { p[np].fd = fd_r; p[np].events = POLLIN; p[np].revents = 0; ir = np++; }
     }
-    const int rc = poll(p, np, 600000);
+    const int rc = poll(p, np, g_mesh.op_timeout_ms);
     if (rc < 0) { if (errno == EINTR) continue; Log::Fatal("poll failed: %s", strerror(errno)); }
-    if (rc == 0) Log::Fatal("No progress on a collective for ten minutes: a peer machine is not taking part");
+    if (rc == 0) Log::Fatal("No progress on a collective for %d s (time_out): a peer machine is not taking part", g_mesh.op_timeout_ms / 1000);
     if (sn > 0 && is >= 0 && (p[is].revents & (POLLOUT | POLLERR | POLLHUP))) {
       const ssize_t k = send(fd_s, sp, sn, MSG_NOSIGNAL | MSG_DONTWAIT);
       if (k < 0) { if (errno != EAGAIN && errno != EWOULDBLOCK && errno != EINTR) Log::Fatal("Socket send failed: %s", strerror(errno)); }
@@ -203,6 +204,7 @@ void SocketNetworkInit(const std::string& machines, int local_listen_port, int t
   for (int r = 0; r < world; ++r) if (list[r].port == local_listen_port && IsLocalAddress(list[r].host)) { rank = r; break; }
   if (rank < 0) Log::Fatal("No entry of the machine list is this machine on port %d (local_listen_port)", local_listen_port);
   g_mesh.rank = rank; g_mesh.world = world; g_mesh.fd.assign(world, -1);
+  g_mesh.op_timeout_ms = static_cast<int>(std::min<long long>(static_cast<long long>(std::max(1, timeout_minutes)) * 60000LL, 1LL << 30));
 
   g_mesh.listen_fd = socket(AF_INET, SOCK_STREAM, 0);
   if (g_mesh.listen_fd < 0) Log::Fatal("Cannot create a socket: %s", strerror(errno));
