@@ -109,7 +109,8 @@ def _param_str(params: Optional[Dict[str, Any]]) -> bytes:
         if v is None or k == "keep_host_bins":   # keep_host_bins is a note between Booster and Dataset of this layer, not a native parameter
             continue
         if isinstance(v, (list, tuple, set)):
-            v = ",".join(str(x) for x in v)
+            # a list of lists (interaction_constraints) is written as [a,b],[c,d]: no blanks, which separate parameters
+            v = ",".join("[" + ",".join(str(y) for y in x) + "]" if isinstance(x, (list, tuple, set)) else str(x) for x in v)
         elif isinstance(v, bool):
             v = "true" if v else "false"
         parts.append(f"{k}={v}")

@@ -236,10 +236,11 @@ void Config::CheckParamConflict() {
     double full = std::pow(2.0, max_depth);
     if (full < num_leaves) { num_leaves = static_cast<int>(full); }
   }
-  if (quant != QuantMode::None && !monotone_vec.empty())
-    Log::Fatal("Quantized training does not support monotone constraints");
-  if (quant != QuantMode::None && !interaction_constraints.empty())
-    Log::Fatal("Quantized training does not support interaction constraints");
+  // the host learner combines quantized gradients with both kinds of constraints; the device engine's quantized search does not
+  if (quant != QuantMode::None && !monotone_vec.empty() && is_cuda)
+    Log::Fatal("Quantized training does not support monotone constraints on device_type=cuda: disable one of them or use device_type=cpu");
+  if (quant != QuantMode::None && !interaction_constraints.empty() && is_cuda)
+    Log::Fatal("Quantized training does not support interaction constraints on device_type=cuda: disable one of them or use device_type=cpu");
   if (!monotone_vec.empty() && monotone_constraints_method != "basic" && monotone_constraints_method != "intermediate" && monotone_constraints_method != "advanced")
     Log::Fatal("Unknown monotone_constraints_method %s (basic, intermediate, advanced)", monotone_constraints_method.c_str());
   if (boosting == "rf") {

@@ -1182,7 +1182,15 @@ Tree* CPUTreeLearner::Train(const score_t* grad, const score_t* hess, int tree_i
       sums[2 * l] = g; sums[2 * l + 1] = h;
     }
     if (parallel_data_ || parallel_voting_) Network::SumDouble(sums.data(), static_cast<int64_t>(sums.size()));
-    for (int l = 0; l < tree->num_leaves; ++l) tree->SetLeafOutput(l, LeafOutputRaw(sums[2 * l], sums[2 * l + 1] + kEpsilon, sp_));
+    // Monotone constraints: with the basic method a leaf's range does not depend on other leaves' outputs, so the renewed
+    // output is clamped into it; with the other methods the ranges are the neighbours' (old) outputs and renewing would
+    // break the order, so the outputs found during growth stay.
+    if (!(sp_.use_mc != 0 && mono_intermediate_))
+      for (int l = 0; l < tree->num_leaves; ++l) {
+        double out = LeafOutputRaw(sums[2 * l], sums[2 * l + 1] + kEpsilon, sp_);
+        if (sp_.use_mc != 0) out = ClampOutput(out, leaves_[l].min_constraint, leaves_[l].max_constraint);
+        tree->SetLeafOutput(l, out);
+      }
   }
   return tree.release();
 }

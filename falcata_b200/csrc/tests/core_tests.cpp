@@ -112,9 +112,12 @@ static void TestConfig() {
   bool threw = false;
   try { Config bad; bad.Set(Config::Str2Map("grow_policy=sideways"), false); } catch (const std::exception&) { threw = true; }
   CHECK(threw);
-  threw = false;   // quantized training and monotone constraints do not combine
-  try { Config bad; bad.Set(Config::Str2Map("quant_mode=stochastic monotone_constraints=1,0"), false); } catch (const std::exception&) { threw = true; }
+  threw = false;   // quantized training and monotone constraints combine on the host learner only
+  try { Config bad; bad.Set(Config::Str2Map("quant_mode=stochastic monotone_constraints=1,0 device_type=cuda"), true); } catch (const std::exception&) { threw = true; }
   CHECK(threw);
+  threw = false;
+  try { Config ok; ok.Set(Config::Str2Map("quant_mode=stochastic monotone_constraints=1,0 device_type=cpu"), false); } catch (const std::exception&) { threw = true; }
+  CHECK(!threw);
 }
 
 // Best-first growth over a random gain tree, against the rule of the level controller: a node is split while fewer

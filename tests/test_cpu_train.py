@@ -504,3 +504,24 @@ def test_host_learner_is_invariant_to_thread_count_and_histogram_pool():
         real = dict(p, quant_mode="none")
         assert model_body(fb.train(dict(real, num_threads=8), fb.Dataset(X, y), 4).model_to_string()) == \
             model_body(fb.train(dict(real, num_threads=1), fb.Dataset(X, y), 4).model_to_string()), p
+
+
+def test_quantized_training_keeps_monotone_and_interaction_constraints_on_the_host_learner():
+    """The host learner combines quantized gradients with monotone constraints (every method; with the basic method the
+    leaf renewal from the true gradients is clamped into the leaf's range) and with interaction constraints, given as a
+    list of lists (reference: quantized training with constraints is refused on device_type=cuda only)."""
+    rng = np.random.default_rng(3)
+    n = 6000
+    X = rng.normal(size=(n, 4)).astype(np.float32)
+    y = (np.sin(2 * X[:, 0]) + 0.5 * X[:, 0] - np.cos(2 * X[:, 1]) - 0.3 * X[:, 1] + X[:, 2] * X[:, 0] * 0.5 + 0.1 * rng.normal(size=n)).astype(np.float32)
+    for method, renew in (("basic", True), ("basic", False), ("intermediate", True), ("advanced", True)):
+        p = {"objective": "regression", "num_leaves": 31, "learning_rate": 0.2, "verbose": -1, "min_data_in_leaf": 10, "monotone_constraints": [1, -1, 0, 0],
+             "monotone_constraints_method": method, "quant_mode": "fixedpoint", "quant_bins": 16, "quant_train_renew_leaf": renew, "device_type": "cpu"}
+        b = fb.train(p, fb.Dataset(X, y), 20)
+        assert _monotone_violations(b, 4, 0, +1, rng) <= 1e-10 and _monotone_violations(b, 4, 1, -1, rng) <= 1e-10
+        assert float(np.mean((b.predict(X) - y) ** 2)) < 0.6 * float(np.var(y))
+    z = (X[:, 0] * X[:, 1] + X[:, 2] * X[:, 3] + X[:, 0] * X[:, 2] + 0.1 * rng.normal(size=n)).astype(np.float32)
+    for quant in ("none", "fixedpoint", "stochastic"):
+        p = {"objective": "regression", "num_leaves": 31, "verbose": -1, "interaction_constraints": [[0, 1], [2, 3]], "quant_mode": quant, "device_type": "cpu"}
+        sets = _branch_feature_sets(fb.train(p, fb.Dataset(X, z), 10))
+        assert all(s <= {0, 1} or s <= {2, 3} for s in sets), quant
