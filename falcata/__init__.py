@@ -7,7 +7,7 @@ import sys as _sys
 from falcata_b200 import *  # noqa: F401,F403
 from falcata_b200 import __all__, __version__  # noqa: F401
 
-for _name in ("basic", "engine", "callback", "sklearn", "importers", "plotting", "oblique", "parallel", "ops", "utils"):
+for _name in ("basic", "engine", "callback", "sklearn", "importers", "plotting", "oblique", "parallel", "ops", "utils", "tuner"):
     try:
         _sys.modules[f"{__name__}.{_name}"] = _importlib.import_module(f"falcata_b200.{_name}")
     except ImportError:  # optional dependency of that submodule is absent
