@@ -9,6 +9,8 @@ from falcata_b200 import __all__, __version__  # noqa: F401
 
 for _name in ("basic", "engine", "callback", "sklearn", "importers", "plotting", "oblique", "parallel", "ops", "utils", "tuner"):
     try:
-        _sys.modules[f"{__name__}.{_name}"] = _importlib.import_module(f"falcata_b200.{_name}")
+        _module = _importlib.import_module(f"falcata_b200.{_name}")
+        _sys.modules[f"{__name__}.{_name}"] = _module
+        globals().setdefault(_name, _module)   # `falcata.<submodule>` works as an attribute too
     except ImportError:  # optional dependency of that submodule is absent
         pass
