@@ -684,7 +684,10 @@ class Dataset:
         arr = np.ascontiguousarray(arr.reshape(-1), dtype=dtype)
         _safe_call(lib.FB_DatasetSetField(self._handle, name.encode(), arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(arr.size), _DTYPE_CODE[arr.dtype]))
 
-    def get_field(self, name: str) -> Optional[np.ndarray]:
+    def get_field(self, field_name: Optional[str] = None, name: Optional[str] = None) -> Optional[np.ndarray]:
+        name = field_name if field_name is not None else name
+        if name is None:
+            raise TypeError("get_field() needs field_name")
         lib = _lib()
         n = ctypes.c_int64(0); ptr = ctypes.c_void_p(); typ = ctypes.c_int(0)
         _safe_call(lib.FB_DatasetGetField(self.handle, name.encode(), ctypes.byref(n), ctypes.byref(ptr), ctypes.byref(typ)))
@@ -1383,11 +1386,13 @@ class Booster:
         _safe_call(_lib().FB_BoosterLoadModelFromString(raw, ctypes.c_int64(len(raw)), ctypes.byref(n_iter), ctypes.byref(self._handle)))
         return self
 
-    def dump_model(self, num_iteration: Optional[int] = None, start_iteration: int = 0, importance_type: str = "split") -> Dict[str, Any]:
+    def dump_model(self, num_iteration: Optional[int] = None, start_iteration: int = 0, importance_type: str = "split",
+                   object_hook: Optional[Callable[[Dict[str, Any]], Dict[str, Any]]] = None) -> Dict[str, Any]:
+        """The model as nested dicts; ``object_hook`` is handed to the JSON decoder (called on every decoded object)."""
         if num_iteration is None:
             num_iteration = self.best_iteration
         s = _get_string(_lib().FB_BoosterDumpModel, self._handle, start_iteration, num_iteration, 0 if importance_type == "split" else 1)
-        return json.loads(s)
+        return json.loads(s, object_hook=object_hook)
 
     def model_to_if_else(self, num_iteration: int = -1) -> str:
         return _get_string(_lib().FB_BoosterModelToIfElse, self._handle, num_iteration)
@@ -1453,9 +1458,9 @@ class Booster:
         self._network = False
         return self
 
-    def model_from_binary(self, data: bytes) -> "Booster":
+    def model_from_binary(self, model_bin: Optional[bytes] = None, data: Optional[bytes] = None) -> "Booster":
         """Replace this Booster's model by one serialised with model_to_binary()."""
-        other = Booster.from_binary(data)
+        other = Booster.from_binary(model_bin if model_bin is not None else data)
         return self.model_from_string(other.model_to_string())
 
     def shuffle_models(self, start_iteration: int = 0, end_iteration: int = -1) -> "Booster":

@@ -65,10 +65,10 @@ def record_evaluation(eval_result: Dict[str, Dict[str, List[Any]]]) -> Callable:
             _init(env)
         for item in env.evaluation_result_list or []:
             if len(item) == 4:
-                eval_result[item[0]][item[1]].append(item[2])
+                eval_result.setdefault(item[0], OrderedDict()).setdefault(item[1], []).append(item[2])   # (the first evaluated iteration may come later)
             else:
-                eval_result[item[0]][f"{item[1]}-mean"].append(item[2])
-                eval_result[item[0]][f"{item[1]}-stdv"].append(item[4])
+                eval_result.setdefault(item[0], OrderedDict()).setdefault(f"{item[1]}-mean", []).append(item[2])
+                eval_result[item[0]].setdefault(f"{item[1]}-stdv", []).append(item[4])
 
     _callback.order = 20  # type: ignore[attr-defined]
     return _callback
@@ -113,7 +113,9 @@ def reset_parameter(**kwargs: Union[list, Callable]) -> Callable:
 def early_stopping(stopping_rounds: int, first_metric_only: bool = False, verbose: bool = True, min_delta: Union[float, List[float]] = 0.0) -> Callable:
     if not isinstance(stopping_rounds, int) or stopping_rounds <= 0:
         raise ValueError(f"stopping_rounds should be an integer and greater than 0. got: {stopping_rounds}")
-    state: Dict[str, Any] = {"enabled": True, "best_score": [], "best_iter": [], "best_list": [], "cmp": [], "first_metric": ""}
+    # "evals" counts the evaluations seen and "best_eval" the evaluation at which a score was best: with train(eval_freq=k)
+    # only every k-th iteration is evaluated and stopping_rounds counts evaluations, not iterations
+    state: Dict[str, Any] = {"enabled": True, "inited": False, "evals": 0, "best_eval": [], "best_score": [], "best_iter": [], "best_list": [], "cmp": [], "first_metric": ""}
 
     def _init(env: CallbackEnv) -> None:
         state["enabled"] = bool(env.evaluation_result_list)
@@ -129,10 +131,10 @@ def early_stopping(stopping_rounds: int, first_metric_only: bool = False, verbos
         deltas = min_delta if isinstance(min_delta, list) else [min_delta] * n
         if len(deltas) < n:
             deltas = (deltas * n)[:n]
-        state["best_score"] = []; state["best_iter"] = []; state["best_list"] = []; state["cmp"] = []
+        state["best_score"] = []; state["best_iter"] = []; state["best_list"] = []; state["cmp"] = []; state["best_eval"] = []; state["evals"] = 0
         state["first_metric"] = env.evaluation_result_list[0][1].split(" ")[-1]
         for item, d in zip(env.evaluation_result_list, deltas):
-            state["best_iter"].append(0); state["best_list"].append(None)
+            state["best_iter"].append(0); state["best_list"].append(None); state["best_eval"].append(0)
             if item[3]:
                 state["best_score"].append(float("-inf")); state["cmp"].append(lambda a, b, d=d: a > b + d)
             else:
@@ -147,19 +149,25 @@ def early_stopping(stopping_rounds: int, first_metric_only: bool = False, verbos
 
     def _callback(env: CallbackEnv) -> None:
         if env.iteration == env.begin_iteration:
-            _init(env)
+            state["inited"] = False
+        sparse_evals = int(getattr(env.model, "_eval_freq", 1) or 1) > 1
+        if not env.evaluation_result_list and sparse_evals:
+            return                                   # an iteration that train(eval_freq=k) did not evaluate
+        if not state["inited"]:
+            _init(env); state["inited"] = True
         if not state["enabled"]:
             return
+        state["evals"] += 1
         for i, item in enumerate(env.evaluation_result_list):
             score = item[2]
             if state["best_list"][i] is None or state["cmp"][i](score, state["best_score"][i]):
-                state["best_score"][i] = score; state["best_iter"][i] = env.iteration; state["best_list"][i] = env.evaluation_result_list
+                state["best_score"][i] = score; state["best_iter"][i] = env.iteration; state["best_list"][i] = env.evaluation_result_list; state["best_eval"][i] = state["evals"]
             metric_name = item[1].split(" ")[-1]
             if first_metric_only and state["first_metric"] != metric_name:
                 continue
             if item[0] in ("training", getattr(env.model, "_train_data_name", "training")) and not hasattr(env.model, "cvfolds"):
                 continue
-            if env.iteration - state["best_iter"][i] >= stopping_rounds:
+            if state["evals"] - state["best_eval"][i] >= stopping_rounds:
                 if verbose:
                     best = "\t".join(_format_eval_result(x) for x in state["best_list"][i])
                     print(f"Early stopping, best iteration is:\n[{state['best_iter'][i] + 1}]\t{best}", flush=True)

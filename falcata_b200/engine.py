@@ -27,8 +27,15 @@ def _pop_aliases(params: Dict[str, Any], aliases: Iterable[str], default: Any) -
 def train(params: Dict[str, Any], train_set: Dataset, num_boost_round: int = 100, valid_sets: Optional[List[Dataset]] = None,
           valid_names: Optional[List[str]] = None, feval: Optional[Union[Callable, List[Callable]]] = None,
           init_model: Optional[Union[str, Booster]] = None, keep_training_booster: bool = False,
-          callbacks: Optional[List[Callable]] = None, fobj: Optional[Callable] = None) -> Booster:
-    """Train a booster. ``params['objective']`` may be a callable ``(preds, train_data) -> (grad, hess)``."""
+          callbacks: Optional[List[Callable]] = None, fobj: Optional[Callable] = None, eval_freq: int = 1) -> Booster:
+    """Train a booster. ``params['objective']`` may be a callable ``(preds, train_data) -> (grad, hess)``.
+
+    ``eval_freq``: the validation sets are evaluated every ``eval_freq`` iterations and on the last one; the callbacks
+    that read the results (early stopping, logging, recording) do nothing on the other iterations, and early stopping's
+    ``stopping_rounds`` then counts evaluations."""
+    if int(eval_freq) < 1:
+        raise ValueError(f"eval_freq must be >= 1, got {eval_freq}")
+    eval_freq = int(eval_freq)
     params = copy.deepcopy(params) if params else {}
     if callable(params.get("objective")):
         fobj = params["objective"]; params["objective"] = "none"
@@ -91,6 +98,7 @@ def train(params: Dict[str, Any], train_set: Dataset, num_boost_round: int = 100
         from .basic import _lib, _safe_call
         _safe_call(_lib().FB_BoosterMerge(booster._handle, predictor._handle))
     booster.best_iteration = 0
+    booster._eval_freq = eval_freq
 
     evaluation_result_list: List[Tuple] = []
     for i in range(init_iteration, init_iteration + num_boost_round):
@@ -100,7 +108,8 @@ def train(params: Dict[str, Any], train_set: Dataset, num_boost_round: int = 100
         with _tag("train: boosting rounds"):
             finished = booster.update(fobj=fobj)
         evaluation_result_list = []
-        if valid_sets is not None or feval is not None:
+        due = (i - init_iteration + 1) % eval_freq == 0 or i == init_iteration + num_boost_round - 1 or finished
+        if (valid_sets is not None or feval is not None) and due:
             with _tag("train: metric evaluation"):
                 if is_valid_contain_train:
                     evaluation_result_list.extend(booster.eval_train(feval))
@@ -188,8 +197,10 @@ def _agg_cv_result(raw: List[List[Tuple]]) -> List[Tuple[str, str, float, bool, 
 def cv(params: Dict[str, Any], train_set: Dataset, num_boost_round: int = 100, folds: Any = None, nfold: int = 5, stratified: bool = True,
        shuffle: bool = True, metrics: Optional[Union[str, List[str]]] = None, feval: Any = None, init_model: Any = None,
        callbacks: Optional[List[Callable]] = None, eval_train_metric: bool = False, return_cvbooster: bool = False, seed: int = 0,
-       fobj: Optional[Callable] = None) -> Dict[str, Any]:
-    """K-fold cross-validation. Returns ``{'valid <metric>-mean': [...], 'valid <metric>-stdv': [...]}``."""
+       fobj: Optional[Callable] = None, fpreproc: Optional[Callable] = None) -> Dict[str, Any]:
+    """K-fold cross-validation. Returns ``{'valid <metric>-mean': [...], 'valid <metric>-stdv': [...]}``.
+
+    ``fpreproc(dtrain, dvalid, params) -> (dtrain, dvalid, params)`` is applied to every fold before its booster is made."""
     params = copy.deepcopy(params) if params else {}
     if callable(params.get("objective")):
         fobj = params["objective"]; params["objective"] = "none"
@@ -205,7 +216,10 @@ def cv(params: Dict[str, Any], train_set: Dataset, num_boost_round: int = 100, f
     cvb = CVBooster()
     for tr, te in splits:
         dtrain = train_set.subset(np.asarray(tr)).construct(); dvalid = train_set.subset(np.asarray(te)).construct()
-        b = Booster(params, dtrain)
+        fold_params = params
+        if fpreproc is not None:
+            dtrain, dvalid, fold_params = fpreproc(dtrain, dvalid, copy.deepcopy(params))
+        b = Booster(fold_params, dtrain)
         if eval_train_metric:
             b.set_train_data_name("train")
         b.add_valid(dvalid, "valid")

@@ -522,3 +522,37 @@ def test_sparse_input_predicts_through_csr_and_returns_sparse_contributions():
     np.testing.assert_allclose(contrib.toarray(), bst.predict(dense, pred_contrib=True), rtol=0, atol=1e-12)
     np.testing.assert_allclose(np.asarray(contrib.sum(axis=1)).ravel(), bst.predict(dense, raw_score=True), atol=1e-9)
     assert contrib.nnz < 1500 * 13   # unused features have no entries
+
+
+def test_eval_freq_fpreproc_and_the_remaining_reference_signatures():
+    """train(eval_freq=k) evaluates every k-th iteration (early stopping then counts evaluations), cv(fpreproc=...) edits
+    every fold, and get_field / dump_model / model_from_binary take the reference's argument names."""
+    rng = np.random.default_rng(0)
+    X = rng.normal(size=(3000, 6)); y = (X[:, 0] + X[:, 1] * X[:, 2] + rng.normal(size=3000) > 0).astype(float)
+    tr = fb.Dataset(X[:2000], y[:2000]); va = fb.Dataset(X[2000:], y[2000:], reference=tr)
+    p = {"objective": "binary", "verbosity": -1, "device_type": "cpu", "learning_rate": 0.3}
+    every, sparse = {}, {}
+    fb.train(p, tr, 60, valid_sets=[va], callbacks=[fb.record_evaluation(every)])
+    b = fb.train(p, tr, 60, valid_sets=[va], callbacks=[fb.record_evaluation(sparse), fb.early_stopping(3, verbose=False)], eval_freq=5)
+    got = sparse["valid_0"]["binary_logloss"]
+    assert got == every["valid_0"]["binary_logloss"][4::5][: len(got)]          # iterations 5, 10, ...
+    assert b.best_iteration % 5 == 0 and b.best_iteration == 5 * (1 + int(np.argmin(got)))
+    assert len(got) == int(np.argmin(got)) + 1 + 3                               # three evaluations without improvement
+    with pytest.raises(ValueError):
+        fb.train(p, tr, 5, eval_freq=0)
+    seen = []
+
+    def shrink(dtrain, dvalid, params):
+        seen.append((dtrain.num_data(), dvalid.num_data()))
+        return dtrain, dvalid, dict(params, num_leaves=4)
+
+    res = fb.cv(p, fb.Dataset(X, y), 5, nfold=3, fpreproc=shrink, return_cvbooster=True, stratified=False)
+    assert len(seen) == 3 and all(a + v == 3000 for a, v in seen)
+    assert all(t["num_leaves"] <= 4 for bst in res["cvbooster"].boosters for t in bst.dump_model()["tree_info"])
+    assert tr.get_field(field_name="label").shape == (2000,)
+    counted = []
+    b.dump_model(object_hook=lambda d: counted.append(1) or d)
+    assert len(counted) > 10
+    clone = fb.Booster(model_str=b.model_to_string())
+    clone.model_from_binary(model_bin=b.model_to_binary())
+    np.testing.assert_allclose(clone.predict(X[:50]), b.predict(X[:50]))
