@@ -110,9 +110,14 @@ def reset_parameter(**kwargs: Union[list, Callable]) -> Callable:
     return _callback
 
 
-def early_stopping(stopping_rounds: int, first_metric_only: bool = False, verbose: bool = True, min_delta: Union[float, List[float]] = 0.0) -> Callable:
+def early_stopping(stopping_rounds: int, first_metric_only: bool = False, verbose: bool = True, min_delta: Union[float, List[float]] = 0.0,
+                   min_iterations: int = 0) -> Callable:
+    """``min_iterations``: a warm-up; iterations before it neither record a best score nor count towards stopping, so the best
+    iteration is never below it."""
     if not isinstance(stopping_rounds, int) or stopping_rounds <= 0:
         raise ValueError(f"stopping_rounds should be an integer and greater than 0. got: {stopping_rounds}")
+    if min_iterations < 0:
+        raise ValueError("Early stopping min_iterations must be non-negative.")
     # "evals" counts the evaluations seen and "best_eval" the evaluation at which a score was best: with train(eval_freq=k)
     # only every k-th iteration is evaluated and stopping_rounds counts evaluations, not iterations
     state: Dict[str, Any] = {"enabled": True, "inited": False, "evals": 0, "best_eval": [], "best_score": [], "best_iter": [], "best_list": [], "cmp": [], "first_metric": ""}
@@ -156,6 +161,8 @@ def early_stopping(stopping_rounds: int, first_metric_only: bool = False, verbos
         if not state["inited"]:
             _init(env); state["inited"] = True
         if not state["enabled"]:
+            return
+        if env.iteration + 1 < min_iterations:
             return
         state["evals"] += 1
         for i, item in enumerate(env.evaluation_result_list):

@@ -152,7 +152,28 @@ class LGBMModel(BaseEstimator):
 
     def fit(self, X: Any, y: Any, sample_weight: Any = None, init_score: Any = None, group: Any = None, eval_set: Any = None, eval_names: Any = None,
             eval_sample_weight: Any = None, eval_init_score: Any = None, eval_group: Any = None, eval_metric: Any = None, feature_name: Any = "auto",
-            categorical_feature: Any = "auto", callbacks: Optional[List[Callable]] = None, init_model: Any = None) -> "LGBMModel":
+            categorical_feature: Any = "auto", callbacks: Optional[List[Callable]] = None, init_model: Any = None, eval_X: Any = None, eval_y: Any = None,
+            eval_class_weight: Any = None) -> "LGBMModel":
+        # eval_X / eval_y (one pair or tuples of the same length) are the newer spelling of eval_set
+        if eval_X is not None or eval_y is not None:
+            if eval_set is not None:
+                raise ValueError("Specify either 'eval_set' or 'eval_X' and 'eval_y', but not both.")
+            if (eval_X is None) != (eval_y is None):
+                raise ValueError("You must specify eval_X and eval_y, not just one of them.")
+            if isinstance(eval_X, tuple) != isinstance(eval_y, tuple) or (isinstance(eval_X, tuple) and len(eval_X) != len(eval_y)):
+                raise ValueError("If eval_X is a tuple, eval_y must be a tuple of the same length, and vice versa.")
+            eval_set = list(zip(eval_X, eval_y)) if isinstance(eval_X, tuple) else [(eval_X, eval_y)]
+        if eval_class_weight is not None and eval_set is not None:
+            # per validation set a class -> weight mapping (or "balanced"): multiplied into that set's sample weights
+            weights = list(eval_sample_weight) if eval_sample_weight is not None else [None] * len(eval_set)
+            for i, (cw, (_, ey)) in enumerate(zip(eval_class_weight, eval_set)):
+                if cw is None:
+                    continue
+                ey = np.asarray(ey).reshape(-1)
+                classes, enc = np.unique(ey, return_inverse=True)
+                w = len(ey) / (len(classes) * np.bincount(enc)) if cw == "balanced" else np.array([cw.get(c, 1.0) for c in classes])
+                weights[i] = w[enc] if weights[i] is None else w[enc] * np.asarray(weights[i], dtype=np.float64)
+            eval_sample_weight = weights
         params = self._process_params()
         if self._n_classes > 2 and params["objective"] in ("binary", "multiclass", "multiclassova"):
             params["num_class"] = self._n_classes

@@ -22,3 +22,22 @@ def test_classifier_regressor_ranker():
     Xq, yq, g = make_ranking(100, 20, 8)
     rk = fl.LGBMRanker(n_estimators=10, min_child_samples=5, device_type="cpu").fit(Xq, yq, group=g)
     assert rk.predict(Xq).shape == (2000,)
+
+
+def test_fit_takes_eval_X_eval_y_and_early_stopping_has_a_warm_up():
+    import falcata_b200 as fb
+
+    rng = np.random.default_rng(1)
+    X = rng.normal(size=(2500, 6)); y = (X[:, 0] + X[:, 1] * X[:, 2] + rng.normal(size=2500) > 0).astype(int)
+    clf = fb.FalcataClassifier(n_estimators=60, learning_rate=0.3, verbosity=-1, device_type="cpu")
+    clf.fit(X[:2000], y[:2000], eval_X=X[2000:], eval_y=y[2000:], callbacks=[fb.early_stopping(3, verbose=False, min_iterations=25)])
+    assert clf.best_iteration_ >= 25 and "valid_0" in clf.evals_result_
+    both = fb.FalcataClassifier(n_estimators=5, verbosity=-1, device_type="cpu")
+    both.fit(X[:2000], y[:2000], eval_X=(X[2000:2200], X[2200:]), eval_y=(y[2000:2200], y[2200:]), eval_class_weight=[{0: 1.0, 1: 3.0}, None])
+    assert set(both.evals_result_) == {"valid_0", "valid_1"}
+    import pytest
+
+    with pytest.raises(ValueError):
+        both.fit(X[:2000], y[:2000], eval_X=X[2000:])
+    with pytest.raises(ValueError):
+        both.fit(X[:2000], y[:2000], eval_X=X[2000:], eval_y=y[2000:], eval_set=[(X[2000:], y[2000:])])
